@@ -1,0 +1,154 @@
+"""Op entry points.  Device switch only: CPU tensors run `ops.reference` (pure PyTorch),
+CUDA tensors run the hand-written sm_100a kernels of `ops.native` (libxft_b200_kernels.so).
+
+There is no silent fallback on a GPU: if the kernel library is missing or an op has no
+kernel for the requested variant, the call raises.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+
+from . import reference as R
+
+_native = None
+
+
+def native():
+    global _native
+    if _native is None:
+        from . import native as N
+        _native = N
+    return _native
+
+
+def _cuda(t: torch.Tensor) -> bool:
+    return t.is_cuda
+
+
+# -- embedding / norms ----------------------------------------------------------------------
+def embedding(ids, table, scale=1.0, out_dtype=torch.float32, pos_table=None, positions=None, pos_offset=0):
+    if _cuda(table):
+        return native().embedding(ids, table, scale, out_dtype, pos_table, positions, pos_offset)
+    return R.embedding(ids, table, scale, out_dtype, pos_table, positions, pos_offset)
+
+
+def rmsnorm(x, w, eps, residual=None):
+    if _cuda(x):
+        return native().rmsnorm(x, w, eps, residual)
+    return R.rmsnorm(x, w, eps, residual)
+
+
+def layernorm(x, w, b, eps):
+    if _cuda(x):
+        return native().layernorm(x, w, b, eps)
+    return R.layernorm(x, w, b, eps)
+
+
+# -- GEMMs ---------------------------------------------------------------------------------
+def linear(x, W, bias=None, act=None, residual=None, res_scale=1.0, out_dtype=None):
+    if _cuda(x):
+        return native().linear(x, W, bias, act, residual, res_scale, out_dtype)
+    return R.linear(x, W, bias, act, residual, res_scale, out_dtype)
+
+
+def linear_gated(x, W, act="silu", bias=None):
+    if _cuda(x):
+        return native().linear_gated(x, W, act, bias)
+    return R.linear_gated(x, W, act, bias)
+
+
+def gated_act(gu, act="silu"):
+    if _cuda(gu):
+        return native().gated_act(gu, act)
+    return R.gated_act(gu, act)
+
+
+# -- attention -----------------------------------------------------------------------------
+def qkv_rope_cache(qkv, hq, hkv, d, positions, table, rot_dim, style, kc, vc, ks, vs, slots,
+                   q_scale=None, q_norm_w=None, k_norm_w=None, eps=1e-6, rot_offset=0):
+    """Split packed qkv [T,(hq+2hkv)*d], optional per-head q/k RMSNorm (Qwen3), RoPE on q and k,
+    append k/v to the paged cache at `slots` (int8-quantising when scales are given); returns
+    q [T,hq,d].  One kernel on the GPU (reference: QKPO + storeKVCache,
+    src/layers/attention.h:560-640, src/kernels/attention_kernels.h:45-69)."""
+    if _cuda(qkv):
+        return native().qkv_rope_cache(qkv, hq, hkv, d, positions, table, rot_dim, style, kc, vc, ks, vs, slots,
+                                       q_scale, q_norm_w, k_norm_w, eps, rot_offset)
+    T = qkv.shape[0]
+    q = qkv[:, : hq * d].reshape(T, hq, d)
+    k = qkv[:, hq * d:(hq + hkv) * d].reshape(T, hkv, d)
+    v = qkv[:, (hq + hkv) * d:].reshape(T, hkv, d)
+    if q_norm_w is not None:
+        q = R.rmsnorm(q, q_norm_w, eps)
+        k = R.rmsnorm(k, k_norm_w, eps)
+    if table is not None and rot_dim > 0:
+        q, k = R.rope_apply(q, k, positions, table, rot_dim, style, rot_offset, q_scale)
+    elif q_scale is not None:
+        q = (q.float() * q_scale[:, None, None]).to(q.dtype)
+    R.kv_cache_write(k, v, kc, vc, slots, ks, vs)
+    return q.contiguous()
+
+
+def paged_attention(q, kc, vc, block_table, cu_q, kv_lens, scale, ks=None, vs=None, slopes=None,
+                    causal=True, prefix_lm_lens=None, group=None, q_off=0, meta=None):
+    if _cuda(q):
+        return native().paged_attention(q, kc, vc, block_table, cu_q, kv_lens, scale, ks, vs, slopes,
+                                        causal, prefix_lm_lens, group, q_off, meta)
+    return R.paged_attention(q, kc, vc, block_table, cu_q, kv_lens, scale, ks, vs, slopes, causal,
+                             prefix_lm_lens, group, q_off)
+
+
+def mla_attention(q_nope, q_rope, latent_cache, block_table, cu_q, kv_lens, w_uk, w_uv, scale, absorbed=True,
+                  meta=None):
+    if _cuda(q_nope):
+        return native().mla_attention(q_nope, q_rope, latent_cache, block_table, cu_q, kv_lens, w_uk, w_uv,
+                                      scale, absorbed, meta)
+    return R.mla_attention(q_nope, q_rope, latent_cache, block_table, cu_q, kv_lens, w_uk, w_uv, scale, absorbed)
+
+
+def rope_apply(q, k, positions, table, rot_dim, style="half", rot_offset=0, q_scale=None):
+    if _cuda(q):
+        return native().rope_apply(q, k, positions, table, rot_dim, style, rot_offset, q_scale)
+    return R.rope_apply(q, k, positions, table, rot_dim, style, rot_offset, q_scale)
+
+
+def latent_cache_write(latent, cache, slots):
+    """latent [T, kv_lora+rope] -> cache [nb,1,block,kv_lora+rope] at `slots`."""
+    if _cuda(latent):
+        return native().latent_cache_write(latent, cache, slots)
+    blk = cache.shape[2]
+    cache[(slots // blk).long(), 0, (slots % blk).long()] = latent.to(cache.dtype)
+
+
+# -- MoE -----------------------------------------------------------------------------------
+def route(logits, kind, top_k, bias=None, n_group=1, topk_group=1, routed_scaling=1.0, norm_topk=True,
+          scoring="sigmoid"):
+    if _cuda(logits):
+        return native().route(logits, kind, top_k, bias, n_group, topk_group, routed_scaling, norm_topk, scoring)
+    if kind == "mixtral":
+        return R.route_mixtral(logits, top_k)
+    if kind == "softmax_topk":
+        return R.route_softmax_topk(logits, top_k, norm_topk)
+    if kind == "deepseek":
+        return R.route_deepseek(logits, bias, top_k, n_group, topk_group, routed_scaling, norm_topk, scoring)
+    raise ValueError(kind)
+
+
+def moe_experts(x, idx, w, experts, act="silu", expert_offset=0, packed=None):
+    if _cuda(x):
+        return native().moe_experts(x, idx, w, experts, act, expert_offset, packed)
+    return R.moe_experts(x, idx, w, experts, act, expert_offset)
+
+
+# -- sampling ------------------------------------------------------------------------------
+def argmax_rows(logits):
+    if _cuda(logits):
+        return native().argmax_rows(logits)
+    return R.argmax_rows(logits)
+
+
+def sample_top_k_top_p(logits, top_k, top_p, temperature, uniform):
+    if _cuda(logits):
+        return native().sample_top_k_top_p(logits, top_k, top_p, temperature, uniform)
+    return R.sample_top_k_top_p(logits, top_k, top_p, temperature, uniform)

@@ -1,0 +1,190 @@
+"""Process-group plumbing: one process per GPU, rank 0 drives, the others follow.
+
+Replaces the reference's Messenger / comm_helper / ShmCCL stack
+(``src/utils/messenger.h:38-232``, ``src/comm_helper/comm_helper.cpp:23-129``,
+``src/utils/shm_ccl.h``): bootstrap is ``torch.distributed`` (NCCL on GPUs, gloo on CPU), the
+world is laid out as ``pp_size x tp_size`` with ``color = rank // tp_size`` being the pipeline
+stage exactly like ``comm_helper.cpp:31-38``, and the control plane is ONE self-describing
+message per API call broadcast from rank 0 (`ctrl_send` / `ctrl_recv`) instead of the
+reference's sequence of raw int broadcasts whose order both sides must guess.
+
+The data-plane collectives used by the model (`all_reduce`, `all_gather_cat`) go through NCCL
+here; on B200 the decoder replaces them by the fused GEMM+collective kernels of
+``parallel/fused_comm.py`` when peer memory is available.  Without a launcher (no RANK /
+MPI variables) or with ``SINGLE_INSTANCE=1`` everything degrades to size 1 and every
+collective is the identity (``messenger.h:41-50,241-248``).
+"""
+from __future__ import annotations
+
+import datetime
+import os
+import pickle
+from typing import Any, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..utils.flags import Env
+
+
+class CommError(RuntimeError):
+    """A collective or control message failed or timed out (peer died / never joined)."""
+
+
+def _env_rank_world():
+    e = os.environ
+    for rk, wk in (("RANK", "WORLD_SIZE"), ("PMI_RANK", "PMI_SIZE"), ("OMPI_COMM_WORLD_RANK", "OMPI_COMM_WORLD_SIZE"),
+                   ("PMIX_RANK", "PMIX_SIZE")):
+        if rk in e and wk in e:
+            return int(e[rk]), int(e[wk])
+    return 0, 1
+
+
+class DistContext:
+    """World/TP/PP/EP topology + collectives.  `DistContext.get()` is the process singleton."""
+
+    _inst: Optional["DistContext"] = None
+
+    def __init__(self, device: Optional[torch.device] = None, timeout_s: float = 1800.0):
+        env = Env.get()
+        self.rank, self.world = (0, 1)
+        self.owns_pg = False
+        if Env.launched_multi_rank() or (dist.is_available() and dist.is_initialized()):
+            if dist.is_initialized():
+                self.rank, self.world = dist.get_rank(), dist.get_world_size()
+            else:
+                self.rank, self.world = _env_rank_world()
+        use_cuda = torch.cuda.is_available() and not env.engine.upper().startswith("CPU")
+        if device is None:
+            if use_cuda:
+                local = int(os.environ.get("LOCAL_RANK", os.environ.get("MPI_LOCALRANKID", self.rank)))
+                if env.engine.upper().startswith("GPU:") and self.world == 1:
+                    local = int(env.engine.split(":")[1])
+                device = torch.device("cuda", local % max(torch.cuda.device_count(), 1))
+                torch.cuda.set_device(device)
+            else:
+                device = torch.device("cpu")
+        self.device = device
+        self.backend = "nccl" if device.type == "cuda" else "gloo"
+        self.ctrl_group = None
+        if self.world > 1 and not dist.is_initialized():
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", "29533")
+            kw = dict(backend=self.backend, rank=self.rank, world_size=self.world,
+                      timeout=datetime.timedelta(seconds=timeout_s))
+            if self.backend == "nccl":
+                kw["device_id"] = device
+            dist.init_process_group(**kw)
+            self.owns_pg = True
+        # topology: world = pp_size x tp_size, stage = rank // tp_size
+        self.pp_size = env.pipeline_stage if self.world % max(env.pipeline_stage, 1) == 0 else 1
+        self.tp_size = self.world // self.pp_size
+        self.pp_rank = self.rank // self.tp_size
+        self.tp_rank = self.rank % self.tp_size
+        self.tp_group = None
+        self.world_group = None
+        if self.world > 1:
+            self.world_group = dist.group.WORLD
+            if self.pp_size == 1:
+                self.tp_group = dist.group.WORLD
+            else:
+                for s in range(self.pp_size):
+                    g = dist.new_group(list(range(s * self.tp_size, (s + 1) * self.tp_size)))
+                    if s == self.pp_rank:
+                        self.tp_group = g
+            # host-side control plane: gloo, so no GPU sync is needed to ship a few ints
+            if self.backend == "nccl":
+                self.ctrl_group = dist.new_group(list(range(self.world)), backend="gloo",
+                                                 timeout=datetime.timedelta(seconds=timeout_s))
+            else:
+                self.ctrl_group = dist.group.WORLD
+        # expert parallel runs over the TP group (attention TP + expert EP on the same ranks)
+        self.ep_size = self.tp_size if env.expert_parallel else 1
+        self.ep_rank = self.tp_rank if env.expert_parallel else 0
+        self.stats = {"all_reduce": 0, "all_gather": 0, "ctrl": 0, "p2p": 0}
+
+    # -- singleton ------------------------------------------------------------------
+    @classmethod
+    def get(cls, device: Optional[torch.device] = None) -> "DistContext":
+        if cls._inst is None:
+            cls._inst = cls(device)
+        return cls._inst
+
+    @classmethod
+    def reset(cls) -> None:
+        if cls._inst is not None and cls._inst.owns_pg and dist.is_initialized():
+            dist.destroy_process_group()
+        cls._inst = None
+
+    @property
+    def is_master(self) -> bool:
+        return self.rank == 0
+
+    # -- data plane -----------------------------------------------------------------
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        """In-place sum over the TP group (collectives C1/C2 of the reference:
+        src/layers/decoder_block.h:123,134)."""
+        if self.tp_size > 1:
+            self.stats["all_reduce"] += 1
+            if t.device.type == "cpu" and t.dtype == torch.bfloat16:
+                f = t.float()
+                dist.all_reduce(f, group=self.tp_group)
+                t.copy_(f)
+            else:
+                dist.all_reduce(t, group=self.tp_group)
+        return t
+
+    def all_gather_cat(self, t: torch.Tensor, sizes: Optional[List[int]] = None, dim: int = -1) -> torch.Tensor:
+        """allgatherv along `dim` over the TP group (C3-C6: logits slices, (val,id) pairs)."""
+        if self.tp_size == 1:
+            return t
+        self.stats["all_gather"] += 1
+        t = t.contiguous()
+        if sizes is None or len(set(sizes)) == 1:
+            outs = [torch.empty_like(t) for _ in range(self.tp_size)]
+            dist.all_gather(outs, t, group=self.tp_group)
+            return torch.cat(outs, dim=dim)
+        d = dim % t.dim()
+        mx = max(sizes)
+        pad_shape = list(t.shape)
+        pad_shape[d] = mx
+        buf = t.new_zeros(pad_shape)
+        buf.narrow(d, 0, t.shape[d]).copy_(t)
+        outs = [torch.empty_like(buf) for _ in range(self.tp_size)]
+        dist.all_gather(outs, buf, group=self.tp_group)
+        return torch.cat([o.narrow(d, 0, s) for o, s in zip(outs, sizes)], dim=d)
+
+    def barrier(self) -> None:
+        if self.world > 1:
+            dist.barrier(group=self.ctrl_group)
+
+    # -- pipeline p2p (C8/C9: stage boundary; typed, sized in elements — the reference always
+    #    ships MPI_FLOAT x tokens*hidden, src/models/common_decoder.h:389-391,497-498) ------
+    def send(self, t: torch.Tensor, dst: int):
+        self.stats["p2p"] += 1
+        return dist.isend(t.contiguous(), dst)
+
+    def recv(self, t: torch.Tensor, src: int):
+        self.stats["p2p"] += 1
+        return dist.irecv(t, src)
+
+    # -- control plane ----------------------------------------------------------------
+    def ctrl_broadcast(self, obj: Any = None) -> Any:
+        """Rank 0 passes `obj`; every rank returns it.  One length header + one payload."""
+        if self.world == 1:
+            return obj
+        self.stats["ctrl"] += 1
+        try:
+            if self.rank == 0:
+                blob = pickle.dumps(obj, protocol=pickle.HIGHEST_PROTOCOL)
+                n = torch.tensor([len(blob)], dtype=torch.int64)
+                dist.broadcast(n, 0, group=self.ctrl_group)
+                dist.broadcast(torch.frombuffer(bytearray(blob), dtype=torch.uint8), 0, group=self.ctrl_group)
+                return obj
+            n = torch.zeros(1, dtype=torch.int64)
+            dist.broadcast(n, 0, group=self.ctrl_group)
+            buf = torch.empty(int(n.item()), dtype=torch.uint8)
+            dist.broadcast(buf, 0, group=self.ctrl_group)
+            return pickle.loads(buf.numpy().tobytes())
+        except RuntimeError as e:  # peer gone / timeout
+            raise CommError(f"control broadcast failed on rank {self.rank}: {e}") from e

@@ -1,0 +1,572 @@
+"""Generation driver — the reference's ``xft::Model`` (``include/models.h:25-128``,
+``src/models/models.cpp``) re-designed around a paged cache and a single control message.
+
+API parity (same names and meaning as the torch custom class of the reference,
+``src/pytorch/auto_model.h:23-360``): ``set_input / config / input / forward(=generate step) /
+is_done / finalize / set_input_cb / forward_cb / free_seqs / set_prefix / unset_prefix``.
+
+Multi-rank protocol: rank 0 drives; every state-changing call ships ONE self-describing message
+``(opcode, payload)``; follower ranks call the same API (arguments ignored) or simply loop on
+``generate()`` and execute whatever arrives — they never have to guess which code path rank 0
+took (the reference's followers must, ``models.cpp:202-253`` vs ``:706-717``).  Forward steps
+carry no message: all ranks run the same deterministic step.  A shutdown opcode replaces the
+poison values of ``models.cpp:80-96``.
+
+Differences by design: greedy, sampling and beam search all run on the continuous-batching path
+(the reference's CB ``generate()`` throws for sampling/beams, ``models.cpp:868-884``); prefix
+sharing works on this path too via shared cache blocks.
+"""
+from __future__ import annotations
+
+import sys
+import time
+from typing import Dict, List, Optional, Sequence, Union
+
+import torch
+
+from .. import ops
+from ..config import KV_DTYPES, ModelConfig, split_hybrid_dtype
+from ..models.decoder import Batch, Decoder
+from ..parallel.dist import CommError, DistContext
+from ..utils import log, trace
+from ..utils.flags import Env
+from ..utils.trace import TimeLine
+from . import sampler as S
+from .kv_cache import PagedKVCache
+from .sequence import SamplingMeta, SequenceMeta, SequencePool
+
+OP_SET_INPUT, OP_CONFIG, OP_INPUT, OP_SET_INPUT_CB, OP_FREE_SEQS, OP_SET_PREFIX, OP_UNSET_PREFIX, OP_SHUTDOWN, \
+    OP_FINALIZE = range(9)
+
+
+def _to_lists(ids) -> List[List[int]]:
+    if ids is None:
+        return []
+    if isinstance(ids, torch.Tensor):
+        if ids.dim() == 1:
+            ids = ids.unsqueeze(0)
+        return [[int(t) for t in row] for row in ids.tolist()]
+    if ids and isinstance(ids[0], int):
+        return [list(ids)]
+    return [list(r) for r in ids]
+
+
+class Model:
+    def __init__(self, path: str, dtype: str = "bf16", kv_cache_dtype: str = "fp16",
+                 ctx: Optional[DistContext] = None):
+        if kv_cache_dtype not in KV_DTYPES:
+            raise ValueError(f"don't support KV cache data type: {kv_cache_dtype}.")
+        self.ctx = ctx or DistContext.get()
+        self.cfg = ModelConfig.from_ini(path)
+        self.env = Env.get()
+        d_prefill, d_decode = split_hybrid_dtype(dtype)
+        if self.cfg.model_type == "deepseek_moe" and d_prefill not in ("bf16", "fp8_e4m3"):
+            raise ValueError("deepseek_moe supports bf16 and fp8_e4m3 only")      # model_factory.h:105-114
+        if d_prefill == "fp8_e4m3" and self.cfg.model_type != "deepseek_moe":
+            raise ValueError("fp8_e4m3 is supported for deepseek_moe only")
+        with TimeLine("Model.load"):
+            self.decoder = Decoder(self.cfg, self.ctx, path, d_decode)
+            # hybrid A_B: model A serves the first token, B the next ones; they share embedding,
+            # head, KV cache and buffers (src/models/hybrid_model.h:23-105)
+            self.prefill_decoder = self.decoder if d_prefill == d_decode else \
+                Decoder(self.cfg, self.ctx, path, d_prefill, embed_from=self.decoder)
+        geo = self.decoder.kv_geometry()
+        self.cache = PagedKVCache(len(self.decoder.layers), geo["kv_heads"], geo["k_dim"], geo["v_dim"],
+                                  kv_cache_dtype, self.ctx.device, self.env.kv_block_size,
+                                  self.decoder.act_dtype, geo["latent"])
+        self.pool = SequencePool()
+        self.sampling = SamplingMeta()
+        self.working: List[SequenceMeta] = []          # sequences of the current request (batch API)
+        self.cb_active: List[SequenceMeta] = []        # sequences of the last set_input_cb
+        self.rng = S.Philox(None)
+        self.scorer: Optional[S.BeamSearchScorer] = None
+        self.prefix_seq: Optional[SequenceMeta] = None
+        self._prompts: List[List[int]] = []
+        self._closed = False
+        self.vocab_sizes = [self._vocab_size_of(r) for r in range(self.ctx.tp_size)]
+        self.runner = None
+        if self.ctx.device.type == "cuda":
+            from .cuda_runner import CudaRunner
+            self.runner = CudaRunner(self)
+        self.step_times_ms: List[float] = []
+
+    # ------------------------------------------------------------------------------------
+    def _vocab_size_of(self, r: int) -> int:
+        from ..parallel.partition import vocab_range
+        a, b = vocab_range(self.cfg.vocab_size, self.ctx.tp_size, r)
+        return b - a
+
+    @property
+    def rank(self) -> int:
+        return self.ctx.rank
+
+    def get_rank(self) -> int:
+        return self.ctx.rank
+
+    # ------------------------------------------------------------------------------------
+    # control plane
+    # ------------------------------------------------------------------------------------
+    def _sync(self, op: int, payload):
+        """Rank 0 sends (op, payload); followers receive and return what rank 0 sent."""
+        if self.ctx.world == 1:
+            return op, payload
+        msg = self.ctx.ctrl_broadcast((op, payload) if self.ctx.is_master else None)
+        return msg
+
+    def _dispatch(self, op: int, payload):
+        if op == OP_SET_INPUT:
+            return self._do_set_input(*payload)
+        if op == OP_CONFIG:
+            return self._do_config(payload)
+        if op == OP_INPUT:
+            return self._do_input(payload)
+        if op == OP_SET_INPUT_CB:
+            return self._do_set_input_cb(*payload)
+        if op == OP_FREE_SEQS:
+            return self._do_free_seqs(payload)
+        if op == OP_SET_PREFIX:
+            return self._do_set_prefix(payload)
+        if op == OP_UNSET_PREFIX:
+            return self._do_unset_prefix()
+        if op == OP_SHUTDOWN:
+            self._closed = True
+            if not self.ctx.is_master:
+                log.info(f"rank {self.ctx.rank}: shutdown received")
+                sys.exit(0)
+            return None
+        raise RuntimeError(f"unknown control opcode {op}")
+
+    def _call(self, op: int, payload):
+        op, payload = self._sync(op, payload)
+        return self._dispatch(op, payload)
+
+    def exit_slaves(self) -> None:
+        """Tell follower ranks to leave their serving loop (models.cpp:80-96)."""
+        if self.ctx.world > 1 and self.ctx.is_master and not self._closed:
+            try:
+                self._sync(OP_SHUTDOWN, None)
+            except CommError:
+                pass
+        self._closed = True
+
+    # ------------------------------------------------------------------------------------
+    # batch API (set_input / config+input / forward / is_done / finalize)
+    # ------------------------------------------------------------------------------------
+    def set_input(self, input_ids=None, max_length=20, num_beams=1, num_return_sequences=1, length_penalty=1.0,
+                  early_stopping=False, eos_token_id=-1, pad_token_id=-1, do_sample=False, temperature=1.0,
+                  top_k=50, top_p=1.0, repetition_penalty=1.0, stop_words_ids=None, seed=None, **kw):
+        cfg = SamplingMeta(max_length, num_beams, num_return_sequences, length_penalty, early_stopping, eos_token_id,
+                           pad_token_id, do_sample, temperature, top_k, top_p, repetition_penalty,
+                           stop_words_ids or [], seed)
+        return self._call(OP_SET_INPUT, (_to_lists(input_ids), cfg))
+
+    def config(self, max_length=20, num_beams=1, num_return_sequences=1, length_penalty=1.0, early_stopping=False,
+               eos_token_id=-1, pad_token_id=-1, do_sample=False, temperature=1.0, top_k=50, top_p=1.0,
+               repetition_penalty=1.0, stop_words_ids=None, seed=None, **kw):
+        cfg = SamplingMeta(max_length, num_beams, num_return_sequences, length_penalty, early_stopping, eos_token_id,
+                           pad_token_id, do_sample, temperature, top_k, top_p, repetition_penalty,
+                           stop_words_ids or [], seed)
+        return self._call(OP_CONFIG, cfg)
+
+    def input(self, input_ids=None):
+        return self._call(OP_INPUT, _to_lists(input_ids))
+
+    def _do_config(self, cfg: SamplingMeta):
+        if cfg.eos_token_id == -1:
+            cfg.eos_token_id = self.cfg.end_id
+        if cfg.pad_token_id == -1:
+            cfg.pad_token_id = cfg.eos_token_id
+        cfg.clean_stop_words()
+        self.sampling = cfg
+        self.rng = S.Philox(cfg.seed if cfg.seed is not None else
+                            (int(time.time()) if self.ctx.world == 1 else 1234))
+
+    def _do_input(self, prompts: List[List[int]]):
+        self._release_working()
+        cfg = self.sampling
+        if not prompts:
+            raise ValueError("input_ids is empty")
+        self._prompts = prompts
+        nb = max(cfg.num_beams, 1)
+        total_blocks = sum(self.cache.blocks_for(max(cfg.max_length, len(p)) + 1) for p in prompts) * nb
+        self.cache.reserve(total_blocks)
+        seqs = []
+        for g, p in enumerate(prompts):
+            if len(p) >= cfg.max_length:
+                log.warning(f"prompt {g}: length {len(p)} >= max_length {cfg.max_length}")
+            s = self.pool.new(p, max(cfg.max_length, len(p) + 1), group=g)
+            self.cache.add_sequence(s.seq_id)
+            self._attach_prefix(s)
+            seqs.append(s)
+        self.working = seqs
+        self.scorer = None
+        self._beam_pending = nb > 1
+
+    def _do_set_input(self, prompts, cfg):
+        self._do_config(cfg)
+        self._do_input(prompts)
+
+    def _attach_prefix(self, s: SequenceMeta) -> None:
+        """Share the cached prefix blocks if the prompt starts with the prefix (prefix sharing,
+        src/models/common_decoder.h:337-353,695-771)."""
+        pre = self.prefix_seq
+        if pre is None:
+            return
+        n = len(pre.prompt)
+        if len(s.prompt) > n and s.prompt[:n] == pre.prompt:
+            self.cache.fork(pre.seq_id, s.seq_id)
+            s.past_len = n
+            s.prefix_len = n
+            s.pending = s.prompt[n:]
+
+    def is_done(self) -> bool:
+        if self.scorer is not None:
+            return self.scorer.is_done or all(s.done for s in self.working)
+        return all(s.done for s in self.working) if self.working else True
+
+    def forward(self) -> torch.Tensor:
+        """One generation step for the current request: returns the next token per sequence
+        (``Model::generate``, models.cpp:834-902).  Finished rows keep emitting eos."""
+        cfg = self.sampling
+        seqs = self.working
+        if not seqs:
+            raise RuntimeError("forward() before set_input()/input()")
+        t0 = time.perf_counter()
+        if cfg.num_beams > 1:
+            out = self._beam_step()
+        else:
+            active = [x for x in seqs if not x.done]
+            if not active:
+                out = torch.full((len(seqs),), cfg.eos_token_id, dtype=torch.int64)
+            elif self.runner is not None and self.runner.can_run(active, cfg):
+                toks = self.runner.step(active, cfg)
+                out = self._commit(seqs, toks, cfg)
+            else:
+                local = self._run(active)
+                toks = self._select(local, active, cfg).tolist()
+                out = self._commit(seqs, toks, cfg)
+        self.step_times_ms.append((time.perf_counter() - t0) * 1e3)
+        return out
+
+    def _select(self, local: torch.Tensor, seqs: Sequence[SequenceMeta], cfg: SamplingMeta) -> torch.Tensor:
+        d = self.decoder
+        if cfg.repetition_penalty != 1.0:
+            local = S.apply_repetition_penalty(local, [s.all_tokens() for s in seqs], cfg.repetition_penalty, d.v0)
+        if not cfg.do_sample:
+            return S.greedy_select(local, d.v0, self.ctx).cpu()
+        full = S.gather_logits(local, self.ctx, self.vocab_sizes)
+        return S.sample_select(full, cfg, self.rng).cpu()
+
+    def _commit(self, seqs, toks: List[int], cfg: SamplingMeta) -> torch.Tensor:
+        """`toks` holds one token per not-yet-done sequence, in order."""
+        out = []
+        it = iter(toks)
+        for s in seqs:
+            if s.done:
+                out.append(cfg.eos_token_id)
+                continue
+            t = int(next(it))
+            s.step_forward(t)
+            # stopCheck (sampling.cpp:134-154): eos, or total_len + 1 >= max_len
+            if t == cfg.eos_token_id or s.total_len >= s.max_len or \
+                    (cfg.stop_words and S.match_stop_words(s.generated, cfg.stop_words)):
+                s.done = True
+            out.append(t)
+        return torch.tensor(out, dtype=torch.int64)
+
+    # -- beams ------------------------------------------------------------------------------
+    def _beam_step(self) -> torch.Tensor:
+        cfg = self.sampling
+        nb = cfg.num_beams
+        if self._beam_pending:
+            # prefill once per request, then fork each into num_beams cache-sharing sequences
+            reqs = self.working
+            local = self._run(reqs)
+            full = S.gather_logits(local, self.ctx, self.vocab_sizes).float().cpu()
+            for s in reqs:
+                s.past_len += len(s.pending)
+                s.pending = []
+            beams = []
+            for s in reqs:
+                beams.append(s)
+                for _ in range(nb - 1):
+                    c = self.pool.new(s.prompt, s.max_len, group=s.group)
+                    c.past_len, c.pending = s.past_len, []
+                    self.cache.fork(s.seq_id, c.seq_id)
+                    beams.append(c)
+            self.working = beams
+            self.scorer = S.BeamSearchScorer(len(reqs), cfg, 0)
+            full = full.repeat_interleave(nb, 0)
+            self._beam_pending = False
+        else:
+            local = self._run(self.working)
+            full = S.gather_logits(local, self.ctx, self.vocab_sizes).float().cpu()
+        if cfg.repetition_penalty != 1.0:
+            full = S.apply_repetition_penalty(full, [s.prompt + g for s, g in zip(self.working, self.scorer.seqs)],
+                                              cfg.repetition_penalty, 0)
+        logp = torch.log_softmax(full, -1)
+        toks, src = self.scorer.process(logp)
+        ids = [s.seq_id for s in self.working]
+        self.cache.reorder(ids, src.tolist())                 # beam reorder = block-table permutation
+        old_gen = [list(s.generated) for s in self.working]
+        for i, s in enumerate(self.working):
+            s.generated = old_gen[int(src[i])] + [int(toks[i])]
+            s.past_len = self.cache.lens[s.seq_id]
+            s.pending = [int(toks[i])]
+            if s.total_len >= s.max_len:
+                s.done = True
+        return toks
+
+    def finalize(self) -> torch.Tensor:
+        """prompt+generated of every sequence, padded to a rectangle (models.cpp:734-758)."""
+        cfg = self.sampling
+        if self.scorer is not None:
+            rows = self.scorer.finalize(self._prompts, cfg.max_length)
+        else:
+            rows = [s.all_tokens() for s in self.working]
+            w = max(len(r) for r in rows) if rows else 0
+            pad = cfg.pad_token_id if cfg.pad_token_id >= 0 else cfg.eos_token_id
+            rows = [r + [pad] * (w - len(r)) for r in rows]
+        self._release_working()
+        if trace.enabled():
+            trace.dump()
+        return torch.tensor(rows, dtype=torch.int64)
+
+    def _release_working(self) -> None:
+        for s in self.working:
+            self.cache.free_sequence(s.seq_id)
+            self.pool.remove(s.seq_id)
+        self.working = []
+        self.scorer = None
+        if self.runner is not None:
+            self.runner.reset()
+
+    # ------------------------------------------------------------------------------------
+    # continuous-batching API
+    # ------------------------------------------------------------------------------------
+    def set_input_cb(self, input_ids=None, seq_lens=None, seq_ids=None, max_length=None) -> torch.Tensor:
+        """Prefill: ``input_ids`` = flattened prompts + ``seq_lens``; decode: ``input_ids`` [bs,1] +
+        ``seq_ids``.  Returns the sequence ids (models.cpp:586-674)."""
+        def tl(x):
+            if x is None:
+                return None
+            if isinstance(x, torch.Tensor):
+                return [int(v) for v in x.flatten().tolist()]
+            if isinstance(x, int):
+                return [x]
+            return [int(v) for v in (sum(x, []) if x and isinstance(x[0], (list, tuple)) else x)]
+        ids = tl(input_ids)
+        if seq_lens is None and seq_ids is None and isinstance(input_ids, torch.Tensor) and input_ids.dim() == 2:
+            seq_lens = [input_ids.shape[1]] * input_ids.shape[0]
+        if seq_lens is None and seq_ids is None and isinstance(input_ids, (list, tuple)) and input_ids and \
+                isinstance(input_ids[0], (list, tuple)):
+            seq_lens = [len(r) for r in input_ids]
+        return self._call(OP_SET_INPUT_CB, (ids, tl(seq_lens), tl(seq_ids), tl(max_length)))
+
+    def _do_set_input_cb(self, ids, seq_lens, seq_ids, max_len) -> torch.Tensor:
+        active = []
+        if not seq_ids:                                   # new prompts
+            if not seq_lens or sum(seq_lens) != len(ids):
+                raise ValueError("set_input_cb: seq_lens do not add up to the number of input ids")
+            mls = max_len or [self.cfg.max_pos_seq_len or 2048]
+            if len(mls) == 1:
+                mls = mls * len(seq_lens)
+            self.cache.reserve(sum(self.cache.blocks_for(max(m, n) + 1) for m, n in zip(mls, seq_lens)))
+            off = 0
+            for n, m in zip(seq_lens, mls):
+                s = self.pool.new(ids[off:off + n], max(m, n + 1))
+                off += n
+                self.cache.add_sequence(s.seq_id)
+                self._attach_prefix(s)
+                active.append(s)
+        else:                                             # next tokens of known sequences
+            if len(ids) != len(seq_ids):
+                raise ValueError("set_input_cb: one next token per sequence id expected")
+            for sid, t in zip(seq_ids, ids):
+                s = self.pool.get(sid)
+                if s.pending and s.past_len == 0 and not s.generated:
+                    raise RuntimeError(f"sequence {sid} has not been prefilled")
+                s.step_forward(int(t))
+                active.append(s)
+        self.cb_active = active
+        return torch.tensor([s.seq_id for s in active], dtype=torch.int64)
+
+    def forward_cb(self) -> torch.Tensor:
+        """fp32 logits [bs, vocab] of the sequences of the last set_input_cb (models.cpp:760-830)."""
+        seqs = self.cb_active
+        if not seqs:
+            raise RuntimeError("forward_cb() before set_input_cb()")
+        local = self._run(seqs)
+        for s in seqs:                      # inputs are now in the cache
+            s.past_len += len(s.pending)
+            s.pending = []
+        return S.gather_logits(local, self.ctx, self.vocab_sizes).float()
+
+    def free_seqs(self, seq_ids=None) -> bool:
+        if isinstance(seq_ids, torch.Tensor):
+            seq_ids = seq_ids.tolist()
+        return self._call(OP_FREE_SEQS, list(seq_ids or []))
+
+    def _do_free_seqs(self, seq_ids) -> bool:
+        for sid in seq_ids:
+            if sid in self.pool:
+                self.cache.free_sequence(sid)
+                self.pool.remove(sid)
+        self.cb_active = [s for s in self.cb_active if s.seq_id in self.pool]
+        if trace.enabled():
+            trace.dump()
+        return True
+
+    # ------------------------------------------------------------------------------------
+    # prefix sharing
+    # ------------------------------------------------------------------------------------
+    def set_prefix(self, input_ids=None):
+        return self._call(OP_SET_PREFIX, _to_lists(input_ids))
+
+    def unset_prefix(self):
+        return self._call(OP_UNSET_PREFIX, None)
+
+    def _do_set_prefix(self, prompts):
+        self._do_unset_prefix()
+        if not prompts or not prompts[0]:
+            return
+        ids = prompts[0]
+        # keep whole blocks only, so sharers never write into a shared block
+        n = (len(ids) // self.cache.block) * self.cache.block
+        if n == 0:
+            return
+        s = self.pool.new(ids[:n], n + 1)
+        self.cache.add_sequence(s.seq_id, n)
+        self._run([s])
+        s.past_len, s.pending = n, []
+        self.prefix_seq = s
+
+    def _do_unset_prefix(self):
+        if self.prefix_seq is not None:
+            self.cache.free_sequence(self.prefix_seq.seq_id)
+            self.pool.remove(self.prefix_seq.seq_id)
+            self.prefix_seq = None
+
+    # ------------------------------------------------------------------------------------
+    # the step
+    # ------------------------------------------------------------------------------------
+    def make_batch(self, seqs: Sequence[SequenceMeta], logits_all: bool = False) -> Batch:
+        dev = self.ctx.device
+        ids, pos, slots, cu, kvl, rows = [], [], [], [0], [], []
+        for s in seqs:
+            n = len(s.pending)
+            if n == 0:
+                raise RuntimeError(f"sequence {s.seq_id} has no pending input")
+            # the cache may already hold this sequence's positions (beam fork) — append after them
+            start = s.past_len
+            have = self.cache.lens[s.seq_id]
+            if have > start:
+                self.cache.truncate(s.seq_id, start)
+            sl = self.cache.append_slots(s.seq_id, n)
+            ids.extend(s.pending)
+            pos.extend(range(start, start + n))
+            slots.extend(sl)
+            cu.append(cu[-1] + n)
+            kvl.append(start + n)
+            rows.extend(range(cu[-2], cu[-1]) if logits_all else [cu[-1] - 1])
+        decode = all(cu[i + 1] - cu[i] == 1 for i in range(len(seqs)))
+        bt = self.cache.block_table([s.seq_id for s in seqs])
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32).to(dev, non_blocking=True)
+        b = Batch(ids=i32(ids), positions=i32(pos), slots=i32(slots), cu_q=cu, kv_lens=kvl, block_table=bt.to(dev),
+                  logit_rows=None if (logits_all or decode) else i32(rows).long() if dev.type == "cpu" else i32(rows),
+                  is_decode=decode, max_q=max(cu[i + 1] - cu[i] for i in range(len(seqs))), max_kv=max(kvl))
+        b.cu_q_dev, b.kv_lens_dev = i32(cu), i32(kvl)
+        if self.decoder.spec.rope == "2d":
+            self._chatglm_positions(b, seqs)
+        return b
+
+    def _chatglm_positions(self, b: Batch, seqs) -> None:
+        """ChatGLM-1 2-D positions: position = index up to the [gMASK]/[MASK] slot then frozen;
+        block position = 0 in the context, 1,2,... from bos on (src/models/chatglm.cpp:118-206).
+        Both mask tokens are honoured (the reference only ever detects gMASK, chatglm.cpp:139)."""
+        GMASK, MASK, BOS = 130001, 130000, 130004
+        p1, p2, pl = [], [], []
+        for s in seqs:
+            prompt = s.prompt
+            ctx_len = prompt.index(BOS) if BOS in prompt else len(prompt) - 1
+            mask_pos = prompt.index(GMASK) if GMASK in prompt else (prompt.index(MASK) if MASK in prompt else ctx_len)
+            for p in range(s.past_len, s.past_len + len(s.pending)):
+                if p < ctx_len:
+                    p1.append(p)
+                    p2.append(0)
+                else:
+                    p1.append(mask_pos)
+                    p2.append(p - ctx_len + 1)
+            pl.append(ctx_len)
+        dev = self.ctx.device
+        b.positions = torch.tensor(p1, dtype=torch.int32, device=dev)
+        b.positions2 = torch.tensor(p2, dtype=torch.int32, device=dev)
+        b.prefix_lm_lens = pl
+
+    def _run(self, seqs: Sequence[SequenceMeta], logits_all: bool = False) -> torch.Tensor:
+        """Run the decoder over the pending inputs of `seqs`; returns this rank's logits slice."""
+        b = self.make_batch(seqs, logits_all)
+        dec = self.decoder if b.is_decode else self.prefill_decoder
+        name = "Next Token" if b.is_decode else "1st Token"
+        with TimeLine(name), torch.no_grad():
+            if self.ctx.pp_size == 1:
+                return dec.forward(b, self.cache)
+            return self._pp_forward(dec, b)
+
+    def _pp_forward(self, dec: Decoder, b: Batch) -> torch.Tensor:
+        """Pipeline stage boundary on p2p send/recv of the bf16/fp32 hidden state (C8); the last
+        stage's logits are then shared with the other stages so that every rank selects the same
+        token and steps its sequences (the reference returns tokens to stage 0 only, C9)."""
+        ctx = self.ctx
+        T = b.ids.shape[0]
+        hidden = None
+        if not dec.first_stage:
+            hidden = torch.empty(T, self.cfg.hidden_size, dtype=dec.act_dtype, device=ctx.device)
+            ctx.recv(hidden, ctx.rank - ctx.tp_size).wait()
+        out = dec.forward(b, self.cache, hidden)
+        if not dec.last_stage:
+            ctx.send(out, ctx.rank + ctx.tp_size).wait()
+        rows = b.num_seqs if b.logit_rows is not None or b.is_decode else T
+        import torch.distributed as dist
+        logits = out if dec.last_stage else torch.empty(rows, dec.v1 - dec.v0, dtype=torch.float32, device=ctx.device)
+        # same tp_rank column across stages
+        src = (ctx.pp_size - 1) * ctx.tp_size + ctx.tp_rank
+        grp = self._pp_column_group()
+        dist.broadcast(logits, src, group=grp)
+        return logits
+
+    def _pp_column_group(self):
+        if not hasattr(self, "_pp_groups"):
+            import torch.distributed as dist
+            self._pp_groups = {}
+            for t in range(self.ctx.tp_size):
+                g = dist.new_group([s * self.ctx.tp_size + t for s in range(self.ctx.pp_size)])
+                self._pp_groups[t] = g
+        return self._pp_groups[self.ctx.tp_rank]
+
+    # ------------------------------------------------------------------------------------
+    def forward_logits_all(self, input_ids) -> torch.Tensor:
+        """All-position logits of a batch of prompts (evaluation hook; evaluation/eval.cpp:70-139)."""
+        prompts = _to_lists(input_ids)
+        if self.ctx.world > 1:
+            prompts = self.ctx.ctrl_broadcast(prompts)
+        seqs = []
+        self.cache.reserve(sum(self.cache.blocks_for(len(p) + 1) for p in prompts))
+        for p in prompts:
+            s = self.pool.new(p, len(p) + 1)
+            self.cache.add_sequence(s.seq_id)
+            seqs.append(s)
+        local = self._run(seqs, logits_all=True)
+        full = S.gather_logits(local, self.ctx, self.vocab_sizes).float()
+        for s in seqs:
+            self.cache.free_sequence(s.seq_id)
+            self.pool.remove(s.seq_id)
+        if all(len(p) == len(prompts[0]) for p in prompts):
+            return full.view(len(prompts), len(prompts[0]), -1)
+        return full
+
+    def __del__(self):
+        try:
+            self.exit_slaves()
+        except Exception:
+            pass

@@ -1,0 +1,73 @@
+"""Environment-flag registry (the reference's ``Env`` singleton, ``src/utils/environment.h:21-399``).
+
+Hardware-neutral names are kept; Xeon-only ones (AMX thresholds, THP, NUMA weight
+placement, oneCCL selection) are accepted and ignored so existing launch scripts run.
+torchrun-style rank detection is added next to the MPI variables.
+"""
+from __future__ import annotations
+
+import os
+from typing import List
+
+
+def _int(name: str, default: int) -> int:
+    v = os.environ.get(name)
+    if v is None or v == "":
+        return default
+    try:
+        return int(v)
+    except ValueError:
+        return default
+
+
+class Env:
+    _inst = None
+
+    def __init__(self):
+        self.reload()
+
+    @classmethod
+    def get(cls) -> "Env":
+        if cls._inst is None:
+            cls._inst = cls()
+        return cls._inst
+
+    def reload(self) -> None:
+        e = os.environ
+        self.verbose = _int("XFT_VERBOSE", 0)
+        self.pipeline_stage = max(1, _int("XFT_PIPELINE_STAGE", 1))
+        self.max_request_num = max(1, _int("XFT_MAX_REQUEST_NUM", 1))
+        self.flash_attn_threshold = _int("FLASH_ATTN_THRESHOLD", 8192)
+        self.cat_mlp = _int("ENABLE_CAT_MLP", 1) != 0
+        self.fake_model = _int("XFT_FAKE_MODEL", 0)      # 1: zeros (reference), 2: N(0,0.02) random
+        self.fake_load_info = _int("XFT_FAKE_LOAD_INFO", 0) != 0
+        self.debug_dir = e.get("XFT_DEBUG_DIR", "")
+        wl = e.get("XFT_TIMELINE_WHITELIST", "")
+        self.timeline_whitelist: List[str] = [s for s in wl.split(",") if s]
+        self.timeline = _int("XFT_TIMELINE", 0) != 0
+        self.single_instance = _int("SINGLE_INSTANCE", 0) != 0
+        self.moe_engine = _int("XFT_MOE_ENGINE", 1)
+        self.moe_split_balance_dim = _int("XFT_MOE_SPLIT_BALANCE_DIM", 0)
+        self.engine = e.get("XFT_ENGINE", "")             # "", "CPU", "GPU[:idx]"
+        # new flags of this build
+        self.kv_block_size = _int("XFT_KV_BLOCK_SIZE", 64)
+        self.cuda_graph = _int("XFT_CUDA_GRAPH", 1) != 0
+        self.expert_parallel = _int("XFT_EXPERT_PARALLEL", 0) != 0
+        self.fused_comm = _int("XFT_FUSED_COMM", 1) != 0
+        self.kv_cache_gb = float(e.get("XFT_KV_CACHE_GB", "0") or 0)
+        self.max_batch_tokens = _int("XFT_MAX_BATCH_TOKENS", 8192)
+        self.step_timeout_s = float(e.get("XFT_STEP_TIMEOUT_S", "0") or 0)
+        # accepted, no effect on a GPU build
+        self.ignored = {k: e.get(k) for k in (
+            "XFT_USE_AMX_M", "ENABLE_TUNED_COMM", "ENABLE_KV_TRANS", "ENABLE_THP", "XFT_ONECCL",
+            "XFT_PRIMITIVE_CACHE_M", "FIRST_TOKEN_WEIGHT_LOCATION", "NEXT_TOKEN_WEIGHT_LOCATION") if k in e}
+
+    @staticmethod
+    def launched_multi_rank() -> bool:
+        """True under mpirun (``messenger.h:228-233``) or torchrun."""
+        e = os.environ
+        if _int("SINGLE_INSTANCE", 0):
+            return False
+        mpi = any(k in e for k in ("MPI_LOCALRANKID", "MPI_LOCALNRANKS", "PMI_RANK", "PMI_SIZE", "PMIX_RANK",
+                                   "OMPI_COMM_WORLD_RANK"))
+        return mpi or (_int("WORLD_SIZE", 1) > 1 and "RANK" in e)
