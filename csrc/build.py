@@ -1,0 +1,73 @@
+"""Build the native libraries in-tree with nvcc / g++ (no JIT cache, no torch headers):
+
+  xfastertransformer_b200/lib/libxft_b200_kernels.so   all sm_100a CUDA kernels, C ABI
+  xfastertransformer_b200/lib/libxft_b200_core.so      C++ runtime (INI, loader, sequences, paged KV, samplers,
+                                                        xft::Model C++ API)
+
+Usage: python csrc/build.py [--force] [--verbose]
+"""
+import os
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+OUT = os.path.join(ROOT, "xfastertransformer_b200", "lib")
+OBJ = os.path.join(ROOT, "build", "obj")
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+NVFLAGS = ARCH + ["-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "--use_fast_math", "-Xptxas", "-v"]
+
+
+def _newer(src, dst, deps=()):
+    if not os.path.exists(dst):
+        return True
+    t = os.path.getmtime(dst)
+    return any(os.path.getmtime(s) > t for s in (src,) + tuple(deps))
+
+
+def _run(cmd, verbose):
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
+        raise RuntimeError("build failed: " + cmd[-1])
+    if verbose:
+        sys.stderr.write(r.stderr)
+    return r.stderr
+
+
+def build(force=False, verbose=False):
+    os.makedirs(OUT, exist_ok=True)
+    os.makedirs(OBJ, exist_ok=True)
+    kdir = os.path.join(HERE, "kernels")
+    headers = tuple(os.path.join(kdir, f) for f in os.listdir(kdir) if f.endswith((".cuh", ".h")))
+    cus = sorted(f for f in os.listdir(kdir) if f.endswith(".cu"))
+    objs, jobs = [], []
+    for f in cus:
+        src, obj = os.path.join(kdir, f), os.path.join(OBJ, f[:-3] + ".o")
+        objs.append(obj)
+        if force or _newer(src, obj, headers):
+            jobs.append([NVCC] + NVFLAGS + ["-c", src, "-o", obj])
+    with ThreadPoolExecutor(max_workers=8) as ex:
+        logs = list(ex.map(lambda c: _run(c, verbose), jobs))
+    lib = os.path.join(OUT, "libxft_b200_kernels.so")
+    if jobs or not os.path.exists(lib):
+        _run([NVCC] + ARCH + ["-shared", "-o", lib] + objs + ["-lcudart"], verbose)
+    # C++ runtime
+    cdir = os.path.join(HERE, "core")
+    ccs = sorted(f for f in os.listdir(cdir) if f.endswith(".cc")) if os.path.isdir(cdir) else []
+    if ccs:
+        core = os.path.join(OUT, "libxft_b200_core.so")
+        srcs = [os.path.join(cdir, f) for f in ccs]
+        hdrs = tuple(os.path.join(cdir, f) for f in os.listdir(cdir) if f.endswith(".h")) + \
+            tuple(os.path.join(HERE, "api", f) for f in os.listdir(os.path.join(HERE, "api")) if f.endswith(".h"))
+        if force or any(_newer(s, core, hdrs) for s in srcs):
+            _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-I", os.path.join(HERE, "api"), "-I", cdir,
+                  "-I", "/usr/local/cuda/include", "-o", core] + srcs + ["-ldl", "-lpthread"], verbose)
+    return lib, "".join(logs)
+
+
+if __name__ == "__main__":
+    lib, _ = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    print(lib)

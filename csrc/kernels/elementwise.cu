@@ -1,0 +1,381 @@
+// Memory-bound glue kernels for sm_100a: embedding gather, RMSNorm / LayerNorm, fused
+// QKV-split + per-head q/k norm + RoPE + paged KV-cache append (optional int8 quantisation),
+// generic RoPE, latent (MLA) cache append, gated activation, row arg-max.
+//
+// Reference counterparts: src/kernels/token_embedding_kernels.cpp:24-54, rmsnorm_kernels.cpp:27-180,
+// layernorm_kernels.cpp:27-160, rotary_embedding_kernels.cpp:57-927, attention_kernels.h:45-69
+// (storeKVCache), src/utils/quantize_util.h:22-51, decoder_util.h:495-607, src/searchers/sampling.cpp:22-131.
+// All of them move each byte once with 16-byte accesses; there is no GEMM-shaped work here.
+#include "ptx.cuh"
+
+namespace xft {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+template <int NW>
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = 0.f;
+#pragma unroll
+  for (int i = 0; i < NW; ++i) r += sh[i];
+  __syncthreads();
+  return r;
+}
+
+struct alignas(16) bf16x8 { bf16 v[8]; };
+
+// ------------------------------------------------------------------------------ embedding
+__global__ void embedding_kernel(const int* __restrict__ ids, const bf16* __restrict__ table, bf16* __restrict__ out,
+                                 int H, int vocab, float scale, const bf16* __restrict__ pos_table,
+                                 const int* __restrict__ positions, int pos_offset, int npos, int* status) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) { if (threadIdx.x == 0 && status) atomicCAS(status, 0, XFT_ERR_BOUNDS); id = 0; }
+  const bf16x8* src = reinterpret_cast<const bf16x8*>(table + (size_t)id * H);
+  const bf16x8* ps = nullptr;
+  if (pos_table) {
+    int p = positions[t] + pos_offset;
+    if (p < 0 || p >= npos) { if (threadIdx.x == 0 && status) atomicCAS(status, 0, XFT_ERR_BOUNDS); p = 0; }
+    ps = reinterpret_cast<const bf16x8*>(pos_table + (size_t)p * H);
+  }
+  bf16x8* dst = reinterpret_cast<bf16x8*>(out + (size_t)t * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+    bf16x8 v = src[i];
+    if (scale != 1.f || ps) {
+      bf16x8 pv;
+      if (ps) pv = ps[i];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float x = __bfloat162float(v.v[j]) * scale;
+        if (ps) x += __bfloat162float(pv.v[j]);
+        v.v[j] = __float2bfloat16(x);
+      }
+    }
+    dst[i] = v;
+  }
+}
+
+// ------------------------------------------------------------------------------ norms
+// y = x * rsqrt(mean(x^2)+eps) * w ; optional residual: h = x + r is written to h_out first.
+template <int NT>
+__global__ void __launch_bounds__(NT) rmsnorm_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ res,
+                                                     int ldr, const float* __restrict__ w, bf16* __restrict__ y, int ldy,
+                                                     bf16* __restrict__ h_out, int H, float eps) {
+  __shared__ float sh[NT / 32];
+  extern __shared__ float row[];     // H floats
+  const int t = blockIdx.x;
+  const bf16x8* xp = reinterpret_cast<const bf16x8*>(x + (size_t)t * ldx);
+  const bf16x8* rp = res ? reinterpret_cast<const bf16x8*>(res + (size_t)t * ldr) : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H / 8; i += NT) {
+    bf16x8 v = xp[i];
+    bf16x8 r;
+    if (rp) r = rp[i];
+    bf16x8 hv;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float f = __bfloat162float(v.v[j]);
+      if (rp) { f += __bfloat162float(r.v[j]); hv.v[j] = __float2bfloat16(f); f = __bfloat162float(hv.v[j]); }
+      row[i * 8 + j] = f;
+      ss += f * f;
+    }
+    if (rp && h_out) reinterpret_cast<bf16x8*>(h_out + (size_t)t * H)[i] = hv;
+  }
+  ss = block_sum<NT / 32>(ss, sh);
+  const float inv = rsqrtf(ss / H + eps);
+  bf16x8* yp = reinterpret_cast<bf16x8*>(y + (size_t)t * ldy);
+  for (int i = threadIdx.x; i < H / 8; i += NT) {
+    bf16x8 o;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o.v[j] = __float2bfloat16(row[i * 8 + j] * inv * w[i * 8 + j]);
+    yp[i] = o;
+  }
+}
+
+template <int NT>
+__global__ void __launch_bounds__(NT) layernorm_kernel(const bf16* __restrict__ x, int ldx, const float* __restrict__ w,
+                                                       const float* __restrict__ b, bf16* __restrict__ y, int ldy, int H,
+                                                       float eps) {
+  __shared__ float sh[NT / 32];
+  extern __shared__ float row[];
+  const int t = blockIdx.x;
+  const bf16x8* xp = reinterpret_cast<const bf16x8*>(x + (size_t)t * ldx);
+  float s = 0.f;
+  for (int i = threadIdx.x; i < H / 8; i += NT) {
+    bf16x8 v = xp[i];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { float f = __bfloat162float(v.v[j]); row[i * 8 + j] = f; s += f; }
+  }
+  const float mu = block_sum<NT / 32>(s, sh) / H;
+  float vs = 0.f;
+  for (int i = threadIdx.x; i < H; i += NT) { float d = row[i] - mu; vs += d * d; }
+  const float inv = rsqrtf(block_sum<NT / 32>(vs, sh) / H + eps);
+  bf16x8* yp = reinterpret_cast<bf16x8*>(y + (size_t)t * ldy);
+  for (int i = threadIdx.x; i < H / 8; i += NT) {
+    bf16x8 o;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      int k = i * 8 + j;
+      o.v[j] = __float2bfloat16((row[k] - mu) * inv * w[k] + (b ? b[k] : 0.f));
+    }
+    yp[i] = o;
+  }
+}
+
+// ------------------------------------------------------------------------------ gated activation (unfused fallback)
+__device__ __forceinline__ float act_fn(float x, int act) {
+  if (act == 1) return fmaxf(x, 0.f);
+  if (act == 2) return x / (1.f + __expf(-x));
+  if (act == 3) { float u = 0.7978845608028654f * (x + 0.044715f * x * x * x); return 0.5f * x * (1.f + tanhf(u)); }
+  return x;
+}
+__global__ void gated_act_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int T, int I, int act) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)T * I) return;
+  int t = i / I, c = i % I;
+  float g = __bfloat162float(gu[(size_t)t * 2 * I + c]);
+  float u = __bfloat162float(gu[(size_t)t * 2 * I + I + c]);
+  out[i] = __float2bfloat16(act_fn(g, act) * u);
+}
+
+// ------------------------------------------------------------------------------ QKV split + qk-norm + RoPE + cache append
+// One warp per (token, head).  qkv [T, (hq+2hkv)*D] bf16.  style 0 = half (pairs i, i+rot/2), 1 = interleaved.
+// table [max_pos, rot] = cos(rot/2) ‖ sin(rot/2) fp32.  Cache [nb, hkv, bs, D] bf16 or int8 (+ fp32 scale [nb,hkv,bs]).
+struct RopeCacheParams {
+  const bf16* qkv; int ldq;
+  int T, hq, hkv, D;
+  const int* positions; const float* table; int rot, style, rot_off, max_pos;
+  const float* q_scale; const float* q_norm_w; const float* k_norm_w; float eps;
+  bf16* q_out;
+  void* kc; void* vc; float* ks; float* vs; int int8_cache; int bs; long long nslots;
+  const int* slots;
+  int* status;
+};
+
+__global__ void __launch_bounds__(128) qkv_rope_cache_kernel(const RopeCacheParams p) {
+  __shared__ float sh[4][256];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nheads = p.hq + 2 * p.hkv;
+  const long long gw = (long long)blockIdx.x * 4 + warp;
+  if (gw >= (long long)p.T * nheads) return;
+  const int t = gw / nheads, h = gw % nheads;
+  const int D = p.D;
+  float* v = sh[warp];
+  const bf16* src = p.qkv + (size_t)t * p.ldq + (size_t)h * D;
+  for (int d = lane * 2; d < D; d += 64) {
+    __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(src + d);
+    v[d] = __low2float(x);
+    v[d + 1] = __high2float(x);
+  }
+  __syncwarp();
+  const bool is_q = h < p.hq, is_k = !is_q && h < p.hq + p.hkv;
+  if ((is_q && p.q_norm_w) || (is_k && p.k_norm_w)) {
+    const float* w = is_q ? p.q_norm_w : p.k_norm_w;
+    float ss = 0.f;
+    for (int d = lane; d < D; d += 32) ss += v[d] * v[d];
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / D + p.eps);
+    // round to bf16 like a standalone norm kernel would before RoPE
+    for (int d = lane; d < D; d += 32) v[d] = __bfloat162float(__float2bfloat16(v[d] * inv * w[d]));
+    __syncwarp();
+  }
+  if ((is_q || is_k) && p.table && p.rot > 0) {
+    int pos = p.positions[t];
+    if (pos < 0 || pos >= p.max_pos) { if (lane == 0 && p.status) atomicCAS(p.status, 0, XFT_ERR_BOUNDS); pos = 0; }
+    const float* cs = p.table + (size_t)pos * p.rot;
+    const int half = p.rot / 2;
+    for (int i = lane; i < half; i += 32) {
+      const float c = cs[i], s = cs[half + i];
+      const int a = p.rot_off + (p.style == 0 ? i : 2 * i);
+      const int b = p.rot_off + (p.style == 0 ? i + half : 2 * i + 1);
+      const float x1 = v[a], x2 = v[b];
+      v[a] = x1 * c - x2 * s;
+      v[b] = x2 * c + x1 * s;
+    }
+    __syncwarp();
+  }
+  if (is_q) {
+    const float qs = p.q_scale ? p.q_scale[t] : 1.f;
+    bf16* dst = p.q_out + ((size_t)t * p.hq + h) * D;
+    for (int d = lane * 2; d < D; d += 64)
+      *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(v[d] * qs, v[d + 1] * qs);
+    return;
+  }
+  const int kh = is_k ? h - p.hq : h - p.hq - p.hkv;
+  const long long slot = p.slots[t];
+  if (slot < 0 || slot >= p.nslots) { if (lane == 0 && p.status) atomicCAS(p.status, 0, XFT_ERR_BOUNDS); return; }
+  const long long blk = slot / p.bs, off = slot % p.bs;
+  const size_t base = ((size_t)(blk * p.hkv + kh) * p.bs + off);
+  if (p.int8_cache) {
+    float am = 0.f;
+    for (int d = lane; d < D; d += 32) am = fmaxf(am, fabsf(v[d]));
+    am = warp_max(am);
+    const float sc = am / 127.f;
+    const float inv = sc > 1e-20f ? 1.f / sc : 0.f;
+    int8_t* dst = reinterpret_cast<int8_t*>(is_k ? p.kc : p.vc) + base * D;
+    for (int d = lane; d < D; d += 32) {
+      float r = rintf(v[d] * inv);
+      dst[d] = (int8_t)fminf(fmaxf(r, -127.f), 127.f);
+    }
+    if (lane == 0) (is_k ? p.ks : p.vs)[base] = sc;
+  } else {
+    bf16* dst = reinterpret_cast<bf16*>(is_k ? p.kc : p.vc) + base * D;
+    for (int d = lane * 2; d < D; d += 64)
+      *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(v[d], v[d + 1]);
+  }
+}
+
+// ------------------------------------------------------------------------------ generic RoPE on x [T, nh, D] (in place)
+__global__ void rope_kernel(bf16* __restrict__ x, int T, int nh, int D, const int* __restrict__ positions,
+                            const float* __restrict__ table, int rot, int style, int rot_off, int max_pos,
+                            const float* __restrict__ q_scale, int* status) {
+  const long long gw = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (gw >= (long long)T * nh) return;
+  const int t = gw / nh;
+  bf16* v = x + (size_t)gw * D;
+  int pos = positions[t];
+  if (pos < 0 || pos >= max_pos) { if (lane == 0 && status) atomicCAS(status, 0, XFT_ERR_BOUNDS); pos = 0; }
+  const float* cs = table + (size_t)pos * rot;
+  const int half = rot / 2;
+  const float qs = q_scale ? q_scale[t] : 1.f;
+  for (int i = lane; i < half; i += 32) {
+    const float c = cs[i], s = cs[half + i];
+    const int a = rot_off + (style == 0 ? i : 2 * i);
+    const int b = rot_off + (style == 0 ? i + half : 2 * i + 1);
+    const float x1 = __bfloat162float(v[a]), x2 = __bfloat162float(v[b]);
+    v[a] = __float2bfloat16((x1 * c - x2 * s) * qs);
+    v[b] = __float2bfloat16((x2 * c + x1 * s) * qs);
+  }
+  if (q_scale)
+    for (int d = lane; d < D; d += 32)
+      if (d < rot_off || d >= rot_off + rot) v[d] = __float2bfloat16(__bfloat162float(v[d]) * qs);
+}
+
+// latent [T, W] -> cache [nb, 1, bs, W] rows at slots
+__global__ void latent_write_kernel(const bf16* __restrict__ latent, int ld, bf16* __restrict__ cache, int W,
+                                    const int* __restrict__ slots, long long nslots, int T, int* status) {
+  const int t = blockIdx.x;
+  const long long slot = slots[t];
+  if (slot < 0 || slot >= nslots) { if (threadIdx.x == 0 && status) atomicCAS(status, 0, XFT_ERR_BOUNDS); return; }
+  for (int d = threadIdx.x; d < W; d += blockDim.x) cache[(size_t)slot * W + d] = latent[(size_t)t * ld + d];
+}
+
+// ------------------------------------------------------------------------------ row arg-max (first max wins)
+template <int NT>
+__global__ void __launch_bounds__(NT) argmax_kernel(const float* __restrict__ logits, int ld, int V, float* __restrict__ vals,
+                                                    int* __restrict__ idx) {
+  __shared__ float sv[NT / 32];
+  __shared__ int si[NT / 32];
+  const float* row = logits + (size_t)blockIdx.x * ld;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += NT) {
+    float x = row[i];
+    if (x > best || (x == best && i < bi)) { best = x; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < NT / 32; ++w)
+      if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
+    vals[blockIdx.x] = best;
+    idx[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+  }
+}
+
+}  // namespace xft
+
+using namespace xft;
+
+extern "C" int xft_embedding(const int* ids, const void* table, void* out, int T, int H, int vocab, float scale,
+                             const void* pos_table, const int* positions, int pos_offset, int npos, int* status,
+                             cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H % 8) return -1;
+  embedding_kernel<<<T, 128, 0, st>>>(ids, (const bf16*)table, (bf16*)out, H, vocab, scale, (const bf16*)pos_table,
+                                      positions, pos_offset, npos, status);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int xft_rmsnorm(const void* x, int ldx, const void* res, int ldr, const float* w, void* y, int ldy, void* h_out,
+                           int T, int H, float eps, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H % 8 || ldx % 8 || ldy % 8 || (res && ldr % 8)) return -1;
+  if (H >= 2048)
+    rmsnorm_kernel<256><<<T, 256, H * sizeof(float), st>>>((const bf16*)x, ldx, (const bf16*)res, ldr, w, (bf16*)y, ldy,
+                                                          (bf16*)h_out, H, eps);
+  else
+    rmsnorm_kernel<64><<<T, 64, H * sizeof(float), st>>>((const bf16*)x, ldx, (const bf16*)res, ldr, w, (bf16*)y, ldy,
+                                                        (bf16*)h_out, H, eps);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int xft_layernorm(const void* x, int ldx, const float* w, const float* b, void* y, int ldy, int T, int H,
+                             float eps, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H % 8 || ldx % 8 || ldy % 8) return -1;
+  layernorm_kernel<256><<<T, 256, H * sizeof(float), st>>>((const bf16*)x, ldx, w, b, (bf16*)y, ldy, H, eps);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int xft_gated_act(const void* gu, void* out, int T, int I, int act, cudaStream_t st) {
+  size_t n = (size_t)T * I;
+  if (!n) return 0;
+  gated_act_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const bf16*)gu, (bf16*)out, T, I, act);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int xft_qkv_rope_cache(const void* qkv, int ldq, int T, int hq, int hkv, int D, const int* positions,
+                                  const float* table, int rot, int style, int rot_off, int max_pos, const float* q_scale,
+                                  const float* q_norm_w, const float* k_norm_w, float eps, void* q_out, void* kc,
+                                  void* vc, float* ks, float* vs, int int8_cache, int bs, long long nslots,
+                                  const int* slots, int* status, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (D > 256 || D % 2) return -1;
+  RopeCacheParams p{(const bf16*)qkv, ldq, T, hq, hkv, D, positions, table, rot, style, rot_off, max_pos, q_scale,
+                    q_norm_w, k_norm_w, eps, (bf16*)q_out, kc, vc, ks, vs, int8_cache, bs, nslots, slots, status};
+  long long warps = (long long)T * (hq + 2 * hkv);
+  qkv_rope_cache_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, st>>>(p);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int xft_rope(void* x, int T, int nh, int D, const int* positions, const float* table, int rot, int style,
+                        int rot_off, int max_pos, const float* q_scale, int* status, cudaStream_t st) {
+  long long warps = (long long)T * nh;
+  if (warps <= 0) return 0;
+  rope_kernel<<<(unsigned)((warps * 32 + 127) / 128), 128, 0, st>>>((bf16*)x, T, nh, D, positions, table, rot, style,
+                                                                    rot_off, max_pos, q_scale, status);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int xft_latent_write(const void* latent, int ld, void* cache, int W, const int* slots, long long nslots, int T,
+                                int* status, cudaStream_t st) {
+  if (T <= 0) return 0;
+  latent_write_kernel<<<T, 128, 0, st>>>((const bf16*)latent, ld, (bf16*)cache, W, slots, nslots, T, status);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int xft_argmax(const float* logits, int ld, int rows, int V, float* vals, int* idx, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  argmax_kernel<1024><<<rows, 1024, 0, st>>>(logits, ld, V, vals, idx);
+  return (int)cudaGetLastError();
+}

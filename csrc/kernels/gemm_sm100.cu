@@ -1,0 +1,412 @@
+// bf16 GEMM for sm_100a:  Y[T, N] = epilogue( X[T, K] · W[N, K]^T )
+//
+// Replaces the reference's MMHelper::compute* family (src/utils/matmul_helper.h:565-1705: compute,
+// compute_bias, compute_biasadd_relu, compute_silu, compute_gelu, compute_resmul, compute_residential,
+// compute_resext) — there dispatched to xDNN/oneDNN AMX kernels — with one tcgen05 kernel.
+//
+// Mapping.  The weight is always the 128-row UMMA "A" operand (M = 128 output features per CTA) and
+// the activations are the UMMA "B" operand (N = BN tokens, 16..256), both K-major in shared memory
+// with the 128-byte swizzle, staged by TMA.  The accumulator lives in TMEM as [128 lanes = output
+// features] x [BN columns = tokens].  With few tokens (decode) the tile is still a full-rate MMA
+// and the kernel is a pure weight stream; with many tokens BN = 256 reaches the tensor-core peak
+// of a single-CTA MMA.  A gated variant (DUAL) keeps two accumulators, gate and up, fed by two
+// weight tiles and the same token tile, and applies act(gate)*up on the way out of TMEM
+// (siluSum/geluSum of src/utils/decoder_util.h:495-607 fused into the GEMM).
+//
+// Warp roles (192 threads): warp 0 = TMA producer (one lane), warp 1 = TMEM owner + MMA issuer (one
+// lane), warps 2-5 = epilogue (TMEM lane quadrant = warp_id % 4).
+//
+// Split-K: when the tile count cannot fill 148 SMs (decode, TP slices), grid.y CTAs share an output
+// tile, each reducing a K range.  Partials go to an fp32 scratch in accumulator layout
+// [split][tile][column][128 rows]; the CTA that arrives last on the tile's counter sums the splits
+// in index order (deterministic) and runs the epilogue.  Nobody spins: there is no wait on a peer.
+#include "ptx.cuh"
+
+#include <mutex>
+#include <unordered_map>
+
+namespace xft {
+
+struct GemmParams {
+  int N, T, K;
+  int dual_off;            // DUAL: W row of the first "up" feature (gate rows are [0, dual_off))
+  void* out;               // [T, ldo] bf16 or fp32
+  int ldo;
+  int out_fp32;
+  const float* bias;       // [N] (DUAL: [2N] gate then up at dual_off)
+  const __nv_bfloat16* residual;
+  int ldr;
+  float res_scale;
+  int act;                 // 0 none, 1 relu, 2 silu, 3 gelu(tanh)
+  int splits, kb_per_split, num_kb;
+  float* ws;               // split-K partials
+  int* counters;           // one per output tile, zero between launches
+  int* status;
+  int n_tiles, t_tiles, stages;
+  const float* row_scale;  // optional per-output-feature scale applied to the accumulator (weight-only int8)
+};
+
+__device__ __forceinline__ float apply_act(float x, int act) {
+  switch (act) {
+    case 1: return fmaxf(x, 0.f);
+    case 2: return x / (1.f + __expf(-x));
+    case 3: {
+      const float c = 0.7978845608028654f;
+      float u = c * (x + 0.044715f * x * x * x);
+      return 0.5f * x * (1.f + tanhf(u));
+    }
+    default: return x;
+  }
+}
+
+constexpr int kMaxStages = 12;
+
+template <int BN, bool DUAL>
+__global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW,
+                                                        const __grid_constant__ CUtensorMap tmX, const GemmParams p) {
+  constexpr int A_BYTES = 128 * 64 * 2;
+  constexpr int B_BYTES = BN * 64 * 2;
+  constexpr int NACC = DUAL ? 2 : 1;
+  constexpr int STAGE_BYTES = A_BYTES * NACC + B_BYTES;
+  constexpr uint32_t TMEM_COLS = (BN * NACC <= 32) ? 32 : (BN * NACC <= 64) ? 64 : (BN * NACC <= 128) ? 128
+                                 : (BN * NACC <= 256) ? 256 : 512;
+  constexpr uint32_t IDESC = umma_idesc(128, BN, 1, 1, 1);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], tmem_full_bar;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int s_last;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int stages = p.stages;
+
+  // tile coordinates: groups of 16 feature tiles sweep all token tiles before moving on, so the
+  // CTAs resident together share few distinct weight and token tiles (L2 reuse)
+  int tile_n, tile_t;
+  {
+    const int GN = 16;
+    int bid = blockIdx.x;
+    int per_group = GN * p.t_tiles;
+    int g = bid / per_group, r = bid % per_group;
+    int gn = min(GN, p.n_tiles - g * GN);
+    tile_n = g * GN + r % gn;
+    tile_t = r / gn;
+  }
+  const int split = blockIdx.y;
+  const int kb0 = split * p.kb_per_split;
+  const int kb1 = min(kb0 + p.kb_per_split, p.num_kb);
+  const int tile_id = tile_t * p.n_tiles + tile_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&tmem_full_bar, 1);
+    fence_barrier_init();
+    fence_proxy_async();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_s, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // a weight byte is read once when one token tile covers the batch (decode): stream it past
+      // L2; the small activation tile is re-read by every feature tile: keep it
+      const uint64_t hint_w = p.t_tiles == 1 ? kEvictFirst : kEvictNormal;
+      const uint64_t hint_x = p.n_tiles > 1 ? kEvictLast : kEvictNormal;
+      int it = 0;
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const int s = it % stages;
+        const uint32_t ph = (it / stages) & 1;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1, p.status, XFT_ERR_WAIT_EMPTY)) break;
+        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        uint8_t* a = smem + s * STAGE_BYTES;
+        tma_load_2d(a, &tmW, &full_bar[s], kb * 64, tile_n * 128, hint_w);
+        if (DUAL) tma_load_2d(a + A_BYTES, &tmW, &full_bar[s], kb * 64, p.dual_off + tile_n * 128, hint_w);
+        tma_load_2d(a + A_BYTES * NACC, &tmX, &full_bar[s], kb * 64, tile_t * BN, hint_x);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int it = 0;
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const int s = it % stages;
+        const uint32_t ph = (it / stages) & 1;
+        if (!mbar_wait(&full_bar[s], ph, p.status, XFT_ERR_WAIT_FULL)) break;
+        tcgen05_fence_after();
+        const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+        const uint64_t adesc = umma_desc_k128(a_addr);
+        const uint64_t bdesc = umma_desc_k128(a_addr + A_BYTES * NACC);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {       // 4 x (K = 16) per 64-wide k-block; +32 B = +2 in the address field
+          umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, IDESC, (it > 0 || k > 0) ? 1u : 0u);
+          if (DUAL) {
+            const uint64_t a1desc = umma_desc_k128(a_addr + A_BYTES);
+            umma_bf16(tmem_base + BN, a1desc + 2 * k, bdesc + 2 * k, IDESC, (it > 0 || k > 0) ? 1u : 0u);
+          }
+        }
+        tcgen05_commit(&empty_bar[s]);       // frees the stage when these MMAs have read it
+      }
+      tcgen05_commit(&tmem_full_bar);        // accumulator complete
+    }
+  } else {
+    // ---------------- epilogue: 4 warps, one TMEM lane (= output feature) per thread -------------
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const int n = tile_n * 128 + row;
+    const bool n_ok = n < p.N;
+    const int et = threadIdx.x - 64;                    // 0..127 among epilogue threads
+    bool ok = mbar_wait(&tmem_full_bar, 0, p.status, XFT_ERR_WAIT_TMEM);
+    tcgen05_fence_after();
+    const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16);
+    const int t0 = tile_t * BN;
+    bool last = true;
+    if (p.splits > 1) {
+      // publish this split's partial tile
+      float* wsp = p.ws + ((size_t)split * (p.n_tiles * p.t_tiles) + tile_id) * (size_t)(BN * NACC) * 128;
+      if (ok) {
+#pragma unroll 1
+        for (int c = 0; c < BN * NACC; c += 16) {
+          uint32_t v[16];
+          tmem_ld16(taddr + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) wsp[(size_t)(c + j) * 128 + row] = __uint_as_float(v[j]);
+        }
+      }
+      __threadfence();
+      named_bar_sync(1, 128);
+      if (et == 0) {
+        int old = atomicAdd(&p.counters[tile_id], 1);
+        s_last = (old == p.splits - 1);
+        if (s_last) p.counters[tile_id] = 0;            // ready for the next launch
+      }
+      named_bar_sync(1, 128);
+      last = s_last != 0;
+      if (last) __threadfence();
+    }
+    if (last && ok) {
+      const float bias_g = (p.bias && n_ok) ? p.bias[n] : 0.f;
+      const float bias_u = (DUAL && p.bias && n_ok) ? p.bias[p.dual_off + n] : 0.f;
+      const float rs = (p.row_scale && n_ok) ? p.row_scale[n] : 1.f;
+      const float* ws_tile = p.ws + (size_t)tile_id * (size_t)(BN * NACC) * 128;
+      const size_t ws_split_stride = (size_t)(p.n_tiles * p.t_tiles) * (size_t)(BN * NACC) * 128;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        float g[16], u[16];
+        if (p.splits > 1) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) { g[j] = 0.f; u[j] = 0.f; }
+          for (int s = 0; s < p.splits; ++s) {
+            const float* w = ws_tile + s * ws_split_stride;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              g[j] += __ldcg(w + (size_t)(c + j) * 128 + row);
+              if (DUAL) u[j] += __ldcg(w + (size_t)(BN + c + j) * 128 + row);
+            }
+          }
+        } else {
+          uint32_t v[16];
+          tmem_ld16(taddr + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) g[j] = __uint_as_float(v[j]);
+          if (DUAL) {
+            tmem_ld16(taddr + BN + c, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) u[j] = __uint_as_float(v[j]);
+          }
+        }
+        if (n_ok) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int t = t0 + c + j;
+            if (t < p.T) {
+              float x = g[j] * rs + bias_g;
+              x = apply_act(x, p.act);
+              if (DUAL) x *= (u[j] * rs + bias_u);
+              if (p.residual) x += p.res_scale * __bfloat162float(p.residual[(size_t)t * p.ldr + n]);
+              if (p.out_fp32) reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + n] = x;
+              else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)t * p.ldo + n] = __float2bfloat16(x);
+            }
+          }
+        }
+      }
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess) return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr; uint64_t rows, cols, ld; uint32_t box_rows, esize;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows && esize == o.esize;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    h ^= k.rows * 0x9E3779B97F4A7C15ull + (h << 6);
+    h ^= k.cols * 0xC2B2AE3D27D4EB4Full + (h >> 2);
+    h ^= (k.ld << 20) ^ (uint64_t(k.box_rows) << 8) ^ k.esize;
+    return h;
+  }
+};
+
+// K-major matrix [rows, cols] with row stride `ld` elements; box = 128 bytes x box_rows, 128B swizzle.
+int make_tensor_map(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                    uint32_t esize) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex mu;
+  MapKey key{ptr, rows, cols, ld, box_rows, esize};
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+  }
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return -1;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * esize) & 15)) return -2;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * esize};
+  cuuint32_t box[2] = {128 / esize, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = esize == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUresult r = enc(out, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return -3;
+  std::lock_guard<std::mutex> g(mu);
+  if (cache.size() > 65536) cache.clear();
+  cache[key] = *out;
+  return 0;
+}
+
+template <int BN, bool DUAL>
+static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, GemmParams& p, cudaStream_t st) {
+  constexpr int STAGE_BYTES = 128 * 64 * 2 * (DUAL ? 2 : 1) + BN * 64 * 2;
+  // small token tiles: keep a CTA under half an SM's shared memory so two CTAs (and twice the
+  // loads in flight) share an SM; large tiles take the whole SM
+  int budget = (BN <= 64) ? 110 * 1024 : 220 * 1024;
+  int stages = budget / STAGE_BYTES;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) stages = 2;
+  p.stages = stages;
+  size_t smem = (size_t)stages * STAGE_BYTES + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(gemm_bf16_kernel<BN, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    attr_set = true;
+  }
+  dim3 grid(p.n_tiles * p.t_tiles, p.splits);
+  gemm_bf16_kernel<BN, DUAL><<<grid, 192, smem, st>>>(tmW, tmX, p);
+  return (int)cudaGetLastError();
+}
+
+int pick_bn(int T) {
+  if (T <= 16) return 16;
+  if (T <= 32) return 32;
+  if (T <= 64) return 64;
+  if (T <= 128) return 128;
+  return 256;
+}
+
+// Split-K plan: enough CTAs for ~2 per SM on small tiles, at least 2 k-blocks each, bounded scratch.
+void plan_splits(int tiles, int num_kb, int bn, int nacc, size_t ws_bytes, int max_tiles, int* splits,
+                 int* kb_per_split) {
+  int target = (bn <= 64) ? 296 : 148;
+  int s = 1;
+  if (tiles < target && tiles <= max_tiles) {
+    s = (target + tiles - 1) / tiles;
+    int max_by_k = num_kb / 2 > 0 ? num_kb / 2 : 1;
+    if (s > max_by_k) s = max_by_k;
+    size_t per_split = (size_t)tiles * bn * nacc * 128 * sizeof(float);
+    while (s > 1 && per_split * s > ws_bytes) --s;
+    if (s > 64) s = 64;
+  }
+  int per = (num_kb + s - 1) / s;
+  s = (num_kb + per - 1) / per;
+  *splits = s;
+  *kb_per_split = per;
+}
+
+}  // namespace xft
+
+using namespace xft;
+
+// Y[T,N] = epi(X[T,K] W[N,K]^T).  gated != 0: W holds gate rows [0,N) and up rows [dual_off, dual_off+N),
+// Y = act(gate)*up.  ws/counters: split-K scratch (ws_bytes, n_counters ints, zero-initialised once).
+extern "C" int xft_gemm_bf16(const void* X, int ldx, const void* W, int w_rows, int ldw, void* Y, int ldo, int out_fp32,
+                             int T, int N, int K, int gated, int dual_off, const float* bias, const void* residual,
+                             int ldr, float res_scale, int act, const float* row_scale, float* ws, size_t ws_bytes,
+                             int* counters, int n_counters, int* status, int force_splits, cudaStream_t st) {
+  if (T <= 0 || N <= 0 || K <= 0) return 0;
+  GemmParams p{};
+  p.N = N; p.T = T; p.K = K; p.dual_off = dual_off; p.out = Y; p.ldo = ldo; p.out_fp32 = out_fp32;
+  p.bias = bias; p.residual = reinterpret_cast<const __nv_bfloat16*>(residual); p.ldr = ldr; p.res_scale = res_scale;
+  p.act = act; p.ws = ws; p.counters = counters; p.status = status; p.row_scale = row_scale;
+  const int bn = pick_bn(T);
+  p.n_tiles = (N + 127) / 128;
+  p.t_tiles = (T + bn - 1) / bn;
+  p.num_kb = (K + 63) / 64;
+  const int tiles = p.n_tiles * p.t_tiles;
+  plan_splits(tiles, p.num_kb, bn, gated ? 2 : 1, ws ? ws_bytes : 0, counters ? n_counters : 0, &p.splits, &p.kb_per_split);
+  if (force_splits > 0 && ws && counters && tiles <= n_counters) {
+    int s = force_splits < p.num_kb ? force_splits : p.num_kb;
+    size_t need = (size_t)tiles * bn * (gated ? 2 : 1) * 128 * sizeof(float) * s;
+    if (need <= ws_bytes) {
+      p.kb_per_split = (p.num_kb + s - 1) / s;
+      p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;
+    }
+  }
+  CUtensorMap tmW, tmX;
+  int r = make_tensor_map(&tmW, W, (uint64_t)w_rows, (uint64_t)K, (uint64_t)ldw, 128, 2);
+  if (r) return 1000 - r;
+  r = make_tensor_map(&tmX, X, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, (uint32_t)bn, 2);
+  if (r) return 2000 - r;
+#define XFT_LAUNCH(BN_)                                                        \
+  case BN_:                                                                    \
+    return gated ? launch_gemm<BN_, true>(tmW, tmX, p, st) : launch_gemm<BN_, false>(tmW, tmX, p, st);
+  switch (bn) {
+    XFT_LAUNCH(16)
+    XFT_LAUNCH(32)
+    XFT_LAUNCH(64)
+    XFT_LAUNCH(128)
+    XFT_LAUNCH(256)
+  }
+#undef XFT_LAUNCH
+  return -1;
+}

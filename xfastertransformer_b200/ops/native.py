@@ -1,0 +1,331 @@
+"""ctypes bindings to the hand-written sm_100a kernels (``lib/libxft_b200_kernels.so``).
+
+Tensors are passed as raw device pointers plus the current CUDA stream, so every call is
+capturable in a CUDA graph and costs no framework dispatch.  Nothing here falls back to a
+PyTorch implementation: a missing library or an unsupported variant raises.
+
+A `Workspace` per device owns the scratch the kernels need (split-K partial tiles and tile
+counters, split-KV partials, the status word the bounded waits report into); it is allocated
+once, so steady-state steps allocate only their outputs.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Dict, Optional
+
+import torch
+
+_LIB = None
+_ACT = {None: 0, "none": 0, "relu": 1, "silu": 2, "gelu": 3, "gelu_tanh": 3, "gelu_new": 3, "gelu_pytorch_tanh": 3,
+        "swiglu": 2}
+
+STATUS_TEXT = {0: "ok", 1: "producer timed out waiting for a free stage", 2: "MMA warp timed out waiting for TMA data",
+               3: "epilogue timed out waiting for the accumulator", 4: "timed out waiting for a peer flag",
+               5: "index out of range (access skipped)"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib_path() -> str:
+    return os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib", "libxft_b200_kernels.so")
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        p = lib_path()
+        if not os.path.exists(p):
+            raise KernelError(f"{p} is missing: run `python csrc/build.py` (or __graft_entry__.build())")
+        _LIB = C.CDLL(p)
+        for name in dir(_LIB):
+            pass
+        for fn in ("xft_gemm_bf16", "xft_embedding", "xft_rmsnorm", "xft_layernorm", "xft_gated_act",
+                   "xft_qkv_rope_cache", "xft_rope", "xft_latent_write", "xft_argmax", "xft_paged_attention"):
+            getattr(_LIB, fn).restype = C.c_int
+    return _LIB
+
+
+def _p(t: Optional[torch.Tensor]):
+    return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise KernelError(f"{what} failed with code {rc}")
+
+
+class Workspace:
+    _by_dev: Dict[int, "Workspace"] = {}
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.ws_bytes = 96 << 20
+        self.ws = torch.empty(self.ws_bytes // 4, dtype=torch.float32, device=device)
+        self.n_counters = 8192
+        self.counters = torch.zeros(self.n_counters, dtype=torch.int32, device=device)
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.part_o = None
+        self.part_ml = None
+        self.launches = 0
+
+    @classmethod
+    def get(cls, device: torch.device) -> "Workspace":
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        if idx not in cls._by_dev:
+            cls._by_dev[idx] = cls(torch.device("cuda", idx))
+        return cls._by_dev[idx]
+
+    def attn_partials(self, n_o: int, n_ml: int):
+        if self.part_o is None or self.part_o.numel() < n_o:
+            self.part_o = torch.empty(max(n_o, 1 << 20), dtype=torch.float32, device=self.device)
+        if self.part_ml is None or self.part_ml.numel() < n_ml:
+            self.part_ml = torch.empty(max(n_ml, 1 << 16), dtype=torch.float32, device=self.device)
+        return self.part_o, self.part_ml
+
+    def check_status(self) -> None:
+        """Read the status word (synchronises).  Raises if any kernel reported a time-out or a
+        bad index; the context stays usable."""
+        s = int(self.status[0].item())
+        if s != 0:
+            self.status.zero_()
+            raise KernelError(f"kernel status {s}: {STATUS_TEXT.get(s, '?')}")
+
+
+def launches(device=None) -> int:
+    d = device or torch.device("cuda", torch.cuda.current_device())
+    return Workspace.get(d).launches
+
+
+# ------------------------------------------------------------------------------------------
+def _rows2d(x: torch.Tensor):
+    """[T, K] view with unit inner stride -> (tensor, ld)."""
+    if x.dim() != 2:
+        x = x.reshape(-1, x.shape[-1])
+    if x.stride(1) != 1 or (x.stride(0) * x.element_size()) % 16 or x.data_ptr() % 16:
+        x = x.contiguous()
+    return x, x.stride(0) if x.shape[0] > 1 else max(x.stride(0), x.shape[1])
+
+
+def embedding(ids, table, scale, out_dtype, pos_table=None, positions=None, pos_offset=0):
+    T, H = ids.numel(), table.shape[1]
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=table.device)
+    ws = Workspace.get(table.device)
+    ids32 = ids if ids.dtype == torch.int32 else ids.int()
+    pos32 = None if positions is None else (positions if positions.dtype == torch.int32 else positions.int())
+    rc = lib().xft_embedding(_p(ids32), _p(table), _p(out), T, H, table.shape[0], C.c_float(scale), _p(pos_table),
+                             _p(pos32), pos_offset, 0 if pos_table is None else pos_table.shape[0], _p(ws.status),
+                             _stream())
+    _check(rc, "embedding")
+    ws.launches += 1
+    return out if out_dtype == torch.bfloat16 else out.to(out_dtype)
+
+
+def rmsnorm(x, w, eps, residual=None):
+    x2, ldx = _rows2d(x)
+    T, H = x2.shape
+    y = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+    h = None
+    r2, ldr = (None, 0)
+    if residual is not None:
+        r2, ldr = _rows2d(residual)
+        h = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+    rc = lib().xft_rmsnorm(_p(x2), ldx, _p(r2), ldr, _p(w), _p(y), H, _p(h), T, H, C.c_float(eps), _stream())
+    _check(rc, "rmsnorm")
+    Workspace.get(x.device).launches += 1
+    y = y.view(*x.shape[:-1], H)
+    return (y, h.view_as(y)) if residual is not None else y
+
+
+def layernorm(x, w, b, eps):
+    x2, ldx = _rows2d(x)
+    T, H = x2.shape
+    y = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+    rc = lib().xft_layernorm(_p(x2), ldx, _p(w), _p(b), _p(y), H, T, H, C.c_float(eps), _stream())
+    _check(rc, "layernorm")
+    Workspace.get(x.device).launches += 1
+    return y.view(*x.shape[:-1], H)
+
+
+def gemm_bf16(x, w, N, gated=False, dual_off=0, bias=None, act=None, residual=None, res_scale=1.0, out_dtype=None,
+              out=None, row_scale=None, force_splits=0):
+    """Y[T,N] = epi(X[T,K] · W[rows,K]^T) on tcgen05.  `w`: bf16 [rows, K] (rows = N, or 2 blocks for gated)."""
+    x2, ldx = _rows2d(x)
+    T, K = x2.shape
+    assert w.dtype == torch.bfloat16 and w.stride(1) == 1 and w.shape[1] == K, (w.dtype, w.shape, K)
+    assert x2.dtype == torch.bfloat16
+    if K % 8:
+        raise KernelError(f"K={K} must be a multiple of 8 (16-byte TMA rows)")
+    fp32 = out_dtype == torch.float32
+    if out is None:
+        out = torch.empty(T, N, dtype=torch.float32 if fp32 else torch.bfloat16, device=x.device)
+    r2, ldr = (None, 0)
+    if residual is not None:
+        r2 = residual.reshape(-1, residual.shape[-1])
+        assert r2.stride(1) == 1 and r2.dtype == torch.bfloat16
+        ldr = r2.stride(0)
+    ws = Workspace.get(x.device)
+    rc = lib().xft_gemm_bf16(_p(x2), ldx, _p(w), w.shape[0], w.stride(0), _p(out), out.stride(0), int(fp32), T, N, K,
+                             int(gated), dual_off, _p(bias), _p(r2), ldr, C.c_float(res_scale), _ACT[act],
+                             _p(row_scale), _p(ws.ws), C.c_size_t(ws.ws_bytes), _p(ws.counters), ws.n_counters,
+                             _p(ws.status), force_splits, _stream())
+    _check(rc, "gemm_bf16")
+    ws.launches += 1
+    return out
+
+
+def linear(x, W, bias=None, act=None, residual=None, res_scale=1.0, out_dtype=None):
+    lead = x.shape[:-1]
+    if W.kind == "bf16":
+        y = gemm_bf16(x, W.w, W.out_features, bias=bias, act=act, residual=residual, res_scale=res_scale,
+                      out_dtype=out_dtype)
+    else:
+        from . import native_quant
+        y = native_quant.linear(x, W, bias, act, residual, res_scale, out_dtype)
+    return y.view(*lead, W.out_features)
+
+
+def linear_gated(x, W, act="silu", bias=None):
+    lead = x.shape[:-1]
+    I = W.out_features // 2
+    if W.kind == "bf16":
+        y = gemm_bf16(x, W.w, I, gated=True, dual_off=I, bias=bias, act=act)
+    else:
+        from . import native_quant
+        y = native_quant.linear_gated(x, W, act, bias)
+    return y.view(*lead, I)
+
+
+def gated_act(gu, act="silu"):
+    gu2 = gu.reshape(-1, gu.shape[-1]).contiguous()
+    T, I2 = gu2.shape
+    out = torch.empty(T, I2 // 2, dtype=torch.bfloat16, device=gu.device)
+    _check(lib().xft_gated_act(_p(gu2), _p(out), T, I2 // 2, _ACT[act], _stream()), "gated_act")
+    Workspace.get(gu.device).launches += 1
+    return out.view(*gu.shape[:-1], I2 // 2)
+
+
+# ------------------------------------------------------------------------------------------
+def qkv_rope_cache(qkv, hq, hkv, d, positions, table, rot_dim, style, kc, vc, ks, vs, slots,
+                   q_scale=None, q_norm_w=None, k_norm_w=None, eps=1e-6, rot_offset=0):
+    qkv2, ldq = _rows2d(qkv)
+    T = qkv2.shape[0]
+    q = torch.empty(T, hq, d, dtype=torch.bfloat16, device=qkv.device)
+    ws = Workspace.get(qkv.device)
+    nb, _, bs, _ = kc.shape
+    rc = lib().xft_qkv_rope_cache(_p(qkv2), ldq, T, hq, hkv, d, _p(positions), _p(table),
+                                  rot_dim if table is not None else 0, 0 if style == "half" else 1, rot_offset,
+                                  0 if table is None else table.shape[0], _p(q_scale), _p(q_norm_w), _p(k_norm_w),
+                                  C.c_float(eps), _p(q), _p(kc), _p(vc), _p(ks), _p(vs), int(ks is not None), bs,
+                                  C.c_longlong(nb * bs), _p(slots), _p(ws.status), _stream())
+    _check(rc, "qkv_rope_cache")
+    ws.launches += 1
+    return q
+
+
+def rope_apply(q, k, positions, table, rot_dim, style="half", rot_offset=0, q_scale=None):
+    ws = Workspace.get(q.device)
+    st = 0 if style == "half" else 1
+    q = q.contiguous().clone() if not q.is_contiguous() else q.clone()
+    T, nh, D = q.shape
+    _check(lib().xft_rope(_p(q), T, nh, D, _p(positions), _p(table), rot_dim, st, rot_offset, table.shape[0],
+                          _p(q_scale), _p(ws.status), _stream()), "rope")
+    ws.launches += 1
+    if k is not None:
+        k = k.contiguous().clone()
+        _check(lib().xft_rope(_p(k), T, k.shape[1], k.shape[2], _p(positions), _p(table), rot_dim, st, rot_offset,
+                              table.shape[0], C.c_void_p(0), _p(ws.status), _stream()), "rope")
+        ws.launches += 1
+    return q, k
+
+
+def latent_cache_write(latent, cache, slots):
+    l2, ld = _rows2d(latent)
+    ws = Workspace.get(latent.device)
+    nb, _, bs, W = cache.shape
+    _check(lib().xft_latent_write(_p(l2), ld, _p(cache), W, _p(slots), C.c_longlong(nb * bs), l2.shape[0],
+                                  _p(ws.status), _stream()), "latent_write")
+    ws.launches += 1
+
+
+def paged_attention(q, kc, vc, block_table, cu_q, kv_lens, scale, ks=None, vs=None, slopes=None, causal=True,
+                    prefix_lm_lens=None, group=None, q_off=0, meta=None):
+    assert causal
+    T, hq, D = q.shape
+    nb, hkv, bs, _ = kc.shape
+    dev = q.device
+    ws = Workspace.get(dev)
+    B = len(kv_lens)
+    if meta is not None and getattr(meta, "cu_q_dev", None) is not None:
+        cu_dev, kv_dev = meta.cu_q_dev, meta.kv_lens_dev
+        decode, max_q, max_kv = meta.is_decode, meta.max_q, meta.max_kv
+    else:
+        cu_dev = torch.tensor(list(cu_q), dtype=torch.int32, device=dev)
+        kv_dev = torch.tensor(list(kv_lens), dtype=torch.int32, device=dev)
+        max_q = max(cu_q[i + 1] - cu_q[i] for i in range(B))
+        max_kv = max(kv_lens)
+        decode = max_q == 1 and all(cu_q[i + 1] - cu_q[i] == 1 for i in range(B))
+    pl = None
+    if prefix_lm_lens is not None:
+        pl = torch.tensor(list(prefix_lm_lens), dtype=torch.int32, device=dev)
+    g = group or max(hq // hkv, 1)
+    out = torch.empty_like(q)
+    nsplit, po, pm = 1, None, None
+    if decode:
+        kt = {64: 64, 128: 32, 256: 16}[D]
+        ntiles = (max_kv + kt - 1) // kt
+        ctas = B * hkv * ((g + 15) // 16)
+        nsplit = max(1, min((444 + ctas - 1) // ctas, ntiles // 8 if ntiles >= 16 else 1, 32))
+        if meta is not None and getattr(meta, "meta", None) is not None and "nsplit" in meta.meta:
+            nsplit = meta.meta["nsplit"]
+        if nsplit > 1:
+            po, pm = ws.attn_partials(B * hq * nsplit * D, B * hq * nsplit * 2)
+    q = q.contiguous()
+    rc = lib().xft_paged_attention(_p(q), _p(out), _p(kc), _p(vc), _p(ks), _p(vs), _p(block_table),
+                                   block_table.stride(0), _p(cu_dev), _p(kv_dev), B, max_q, hq, hkv, g, q_off, D, bs,
+                                   nb, C.c_float(scale), _p(slopes), _p(pl), int(decode), nsplit, _p(po), _p(pm),
+                                   _p(ws.status), _stream())
+    _check(rc, "paged_attention")
+    ws.launches += 2 if nsplit > 1 else 1
+    return out
+
+
+def mla_attention(q_nope, q_rope, latent_cache, block_table, cu_q, kv_lens, w_uk, w_uv, scale, absorbed=True,
+                  meta=None):
+    from . import native_mla
+    return native_mla.mla_attention(q_nope, q_rope, latent_cache, block_table, cu_q, kv_lens, w_uk, w_uv, scale,
+                                    absorbed, meta)
+
+
+def route(logits, kind, top_k, bias=None, n_group=1, topk_group=1, routed_scaling=1.0, norm_topk=True,
+          scoring="sigmoid"):
+    from . import native_moe
+    return native_moe.route(logits, kind, top_k, bias, n_group, topk_group, routed_scaling, norm_topk, scoring)
+
+
+def moe_experts(x, idx, w, experts, act="silu", expert_offset=0, packed=None):
+    from . import native_moe
+    return native_moe.moe_experts(x, idx, w, experts, act, expert_offset, packed)
+
+
+# ------------------------------------------------------------------------------------------
+def argmax_rows(logits):
+    l2 = logits.reshape(-1, logits.shape[-1])
+    assert l2.dtype == torch.float32 and l2.stride(1) == 1
+    rows, V = l2.shape
+    vals = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    idx = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _check(lib().xft_argmax(_p(l2), l2.stride(0), rows, V, _p(vals), _p(idx), _stream()), "argmax")
+    Workspace.get(logits.device).launches += 1
+    return vals, idx
+
+
+def sample_top_k_top_p(logits, top_k, top_p, temperature, uniform):
+    from . import native_sample
+    return native_sample.sample_top_k_top_p(logits, top_k, top_p, temperature, uniform)

@@ -1,0 +1,150 @@
+"""Decode fast path on the GPU: one CUDA graph per (batch size, table width), replayed per step.
+
+The reference runs every step through its OpenMP layer loop (``src/models/common_decoder.h:591-693``).
+On B200 a decode step of a large model is a few hundred short kernels, so launch overhead would
+dominate: the whole step — embedding, all layers (GEMMs with fused epilogues, RoPE + cache append,
+flash-decode, the TP reductions), final norm, lm_head, arg-max and the cross-rank (value, id)
+merge — is captured once and replayed.  Per step the host only
+
+  1. appends one cache slot per sequence (block allocator, host side),
+  2. fills ONE pinned int32 staging buffer [ids | positions | slots | kv_lens | block_table],
+  3. issues one H2D copy, one graph launch, one D2H copy of the chosen tokens, and waits.
+
+Greedy decoding with no repetition penalty takes this path; anything else (sampling, beams,
+penalties, prefill, pipeline stages) runs the eager path in `engine.Model`.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Sequence
+
+import torch
+
+from ..models.decoder import Batch
+from ..utils import trace
+from . import sampler as S
+
+
+class _Graph:
+    __slots__ = ("graph", "B", "W", "host", "dev", "tok_dev", "tok_host", "batch", "version", "nsplit")
+
+
+class CudaRunner:
+    def __init__(self, model):
+        self.m = model
+        self.dev = model.ctx.device
+        self.graphs: Dict[tuple, _Graph] = {}
+        self.enabled = model.env.cuda_graph
+        self.stream = torch.cuda.Stream(device=self.dev)
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self.graph_launches = 0
+
+    def reset(self) -> None:
+        pass
+
+    def can_run(self, seqs: Sequence, cfg) -> bool:
+        if not self.enabled or cfg.do_sample or cfg.num_beams > 1 or cfg.repetition_penalty != 1.0:
+            return False
+        if self.m.ctx.pp_size > 1 or self.m.decoder.spec.rope == "2d" or trace.enabled():
+            return False
+        return all(len(s.pending) == 1 and s.past_len > 0 for s in seqs)
+
+    # ------------------------------------------------------------------------------------
+    def _layout(self, B: int, W: int):
+        o_ids, o_pos, o_slot, o_kv = 0, B, 2 * B, 3 * B
+        o_cu = 4 * B
+        o_bt = 5 * B + 1
+        # keep the block table 16-byte aligned
+        o_bt = (o_bt + 3) // 4 * 4
+        return o_ids, o_pos, o_slot, o_kv, o_cu, o_bt, o_bt + B * W
+
+    def _build(self, B: int, W: int, max_kv_hint: int) -> _Graph:
+        m = self.m
+        g = _Graph()
+        g.B, g.W = B, W
+        o_ids, o_pos, o_slot, o_kv, o_cu, o_bt, total = self._layout(B, W)
+        g.host = torch.zeros(total, dtype=torch.int32).pin_memory()
+        g.dev = torch.zeros(total, dtype=torch.int32, device=self.dev)
+        g.tok_dev = torch.zeros(B, dtype=torch.int64, device=self.dev)
+        g.tok_host = torch.zeros(B, dtype=torch.int64).pin_memory()
+        g.host[o_cu:o_cu + B + 1] = torch.arange(B + 1, dtype=torch.int32)
+        d = g.dev
+        kt = {64: 64, 128: 32, 256: 16}.get(m.decoder.D, 32)
+        dec = m.decoder
+        ctas = B * max(dec.hkv, 1) * ((dec.group + 15) // 16)
+        ntiles = (max_kv_hint + kt - 1) // kt
+        g.nsplit = max(1, min((444 + ctas - 1) // ctas, ntiles // 8 if ntiles >= 16 else 1, 32))
+        b = Batch(ids=d[o_ids:o_ids + B], positions=d[o_pos:o_pos + B], slots=d[o_slot:o_slot + B],
+                  cu_q=list(range(B + 1)), kv_lens=[max_kv_hint] * B, block_table=d[o_bt:o_bt + B * W].view(B, W),
+                  logit_rows=None, is_decode=True, max_q=1, max_kv=max_kv_hint)
+        b.cu_q_dev = d[o_cu:o_cu + B + 1]
+        b.kv_lens_dev = d[o_kv:o_kv + B]
+        b.meta["nsplit"] = g.nsplit
+        g.batch = b
+        g.version = m.cache.version
+        g.graph = None
+        return g
+
+    def _step_body(self, g: _Graph) -> None:
+        m = self.m
+        local = m.decoder.forward(g.batch, m.cache)
+        toks = S.greedy_select(local, m.decoder.v0, m.ctx)
+        g.tok_dev.copy_(toks)
+
+    def _fill(self, g: _Graph, seqs) -> None:
+        m = self.m
+        B, W = g.B, g.W
+        o_ids, o_pos, o_slot, o_kv, o_cu, o_bt, total = self._layout(B, W)
+        h = g.host
+        cache = m.cache
+        ids, pos, slots, kvl = [], [], [], []
+        for s in seqs:
+            start = s.past_len
+            if cache.lens[s.seq_id] > start:
+                cache.truncate(s.seq_id, start)
+            slots.append(cache.append_slots(s.seq_id, 1)[0])
+            ids.append(s.pending[0])
+            pos.append(start)
+            kvl.append(start + 1)
+        h[o_ids:o_ids + B] = torch.tensor(ids, dtype=torch.int32)
+        h[o_pos:o_pos + B] = torch.tensor(pos, dtype=torch.int32)
+        h[o_slot:o_slot + B] = torch.tensor(slots, dtype=torch.int32)
+        h[o_kv:o_kv + B] = torch.tensor(kvl, dtype=torch.int32)
+        bt = cache.block_table([s.seq_id for s in seqs], W)
+        h[o_bt:o_bt + B * W] = bt.view(-1)
+
+    def step(self, seqs: Sequence, cfg) -> List[int]:
+        m = self.m
+        B = len(seqs)
+        W = max(m.cache.blocks_for(s.max_len + 1) for s in seqs)
+        W = (W + 7) // 8 * 8
+        key = (B, W)
+        g = self.graphs.get(key)
+        if g is not None and g.version != m.cache.version:
+            g = None                                   # cache pools were reallocated: pointers changed
+        if g is None:
+            g = self._build(B, W, max(s.max_len for s in seqs))
+            self.graphs[key] = g
+        self._fill(g, seqs)
+        st = self.stream
+        st.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(st), torch.no_grad():
+            g.dev.copy_(g.host, non_blocking=True)
+            if g.graph is None:
+                # eager run (allocates workspaces, JIT-free), then capture
+                self._step_body(g)
+                st.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=st):
+                    self._step_body(g)
+                g.graph = graph
+                # the eager run already produced this step's tokens and wrote its K/V; replaying the
+                # captured step would redo identical work — harmless, but skip it
+            else:
+                g.graph.replay()
+                self.graph_launches += 1
+            g.tok_host.copy_(g.tok_dev, non_blocking=True)
+        st.synchronize()
+        self.h2d_bytes += g.host.numel() * 4
+        self.d2h_bytes += g.tok_host.numel() * 8
+        return g.tok_host.tolist()
