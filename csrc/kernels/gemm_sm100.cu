@@ -328,7 +328,7 @@ static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, GemmParam
   size_t smem = (size_t)stages * STAGE_BYTES + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaFuncSetAttribute(gemm_bf16_kernel<BN, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (cudaFuncSetAttribute(gemm_bf16_kernel<BN, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) != cudaSuccess) return 3000 + (int)cudaGetLastError();
     attr_set = true;
   }
   dim3 grid(p.n_tiles * p.t_tiles, p.splits);

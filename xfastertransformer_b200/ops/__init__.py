@@ -15,11 +15,11 @@ from . import reference as R
 _native = None
 
 
-def native():
+def _nat():
     global _native
     if _native is None:
-        from . import native as N
-        _native = N
+        import importlib
+        _native = importlib.import_module(__name__ + ".native")
     return _native
 
 
@@ -30,38 +30,38 @@ def _cuda(t: torch.Tensor) -> bool:
 # -- embedding / norms ----------------------------------------------------------------------
 def embedding(ids, table, scale=1.0, out_dtype=torch.float32, pos_table=None, positions=None, pos_offset=0):
     if _cuda(table):
-        return native().embedding(ids, table, scale, out_dtype, pos_table, positions, pos_offset)
+        return _nat().embedding(ids, table, scale, out_dtype, pos_table, positions, pos_offset)
     return R.embedding(ids, table, scale, out_dtype, pos_table, positions, pos_offset)
 
 
 def rmsnorm(x, w, eps, residual=None):
     if _cuda(x):
-        return native().rmsnorm(x, w, eps, residual)
+        return _nat().rmsnorm(x, w, eps, residual)
     return R.rmsnorm(x, w, eps, residual)
 
 
 def layernorm(x, w, b, eps):
     if _cuda(x):
-        return native().layernorm(x, w, b, eps)
+        return _nat().layernorm(x, w, b, eps)
     return R.layernorm(x, w, b, eps)
 
 
 # -- GEMMs ---------------------------------------------------------------------------------
 def linear(x, W, bias=None, act=None, residual=None, res_scale=1.0, out_dtype=None):
     if _cuda(x):
-        return native().linear(x, W, bias, act, residual, res_scale, out_dtype)
+        return _nat().linear(x, W, bias, act, residual, res_scale, out_dtype)
     return R.linear(x, W, bias, act, residual, res_scale, out_dtype)
 
 
 def linear_gated(x, W, act="silu", bias=None):
     if _cuda(x):
-        return native().linear_gated(x, W, act, bias)
+        return _nat().linear_gated(x, W, act, bias)
     return R.linear_gated(x, W, act, bias)
 
 
 def gated_act(gu, act="silu"):
     if _cuda(gu):
-        return native().gated_act(gu, act)
+        return _nat().gated_act(gu, act)
     return R.gated_act(gu, act)
 
 
@@ -73,7 +73,7 @@ def qkv_rope_cache(qkv, hq, hkv, d, positions, table, rot_dim, style, kc, vc, ks
     q [T,hq,d].  One kernel on the GPU (reference: QKPO + storeKVCache,
     src/layers/attention.h:560-640, src/kernels/attention_kernels.h:45-69)."""
     if _cuda(qkv):
-        return native().qkv_rope_cache(qkv, hq, hkv, d, positions, table, rot_dim, style, kc, vc, ks, vs, slots,
+        return _nat().qkv_rope_cache(qkv, hq, hkv, d, positions, table, rot_dim, style, kc, vc, ks, vs, slots,
                                        q_scale, q_norm_w, k_norm_w, eps, rot_offset)
     T = qkv.shape[0]
     q = qkv[:, : hq * d].reshape(T, hq, d)
@@ -93,7 +93,7 @@ def qkv_rope_cache(qkv, hq, hkv, d, positions, table, rot_dim, style, kc, vc, ks
 def paged_attention(q, kc, vc, block_table, cu_q, kv_lens, scale, ks=None, vs=None, slopes=None,
                     causal=True, prefix_lm_lens=None, group=None, q_off=0, meta=None):
     if _cuda(q):
-        return native().paged_attention(q, kc, vc, block_table, cu_q, kv_lens, scale, ks, vs, slopes,
+        return _nat().paged_attention(q, kc, vc, block_table, cu_q, kv_lens, scale, ks, vs, slopes,
                                         causal, prefix_lm_lens, group, q_off, meta)
     return R.paged_attention(q, kc, vc, block_table, cu_q, kv_lens, scale, ks, vs, slopes, causal,
                              prefix_lm_lens, group, q_off)
@@ -102,21 +102,21 @@ def paged_attention(q, kc, vc, block_table, cu_q, kv_lens, scale, ks=None, vs=No
 def mla_attention(q_nope, q_rope, latent_cache, block_table, cu_q, kv_lens, w_uk, w_uv, scale, absorbed=True,
                   meta=None):
     if _cuda(q_nope):
-        return native().mla_attention(q_nope, q_rope, latent_cache, block_table, cu_q, kv_lens, w_uk, w_uv,
+        return _nat().mla_attention(q_nope, q_rope, latent_cache, block_table, cu_q, kv_lens, w_uk, w_uv,
                                       scale, absorbed, meta)
     return R.mla_attention(q_nope, q_rope, latent_cache, block_table, cu_q, kv_lens, w_uk, w_uv, scale, absorbed)
 
 
 def rope_apply(q, k, positions, table, rot_dim, style="half", rot_offset=0, q_scale=None):
     if _cuda(q):
-        return native().rope_apply(q, k, positions, table, rot_dim, style, rot_offset, q_scale)
+        return _nat().rope_apply(q, k, positions, table, rot_dim, style, rot_offset, q_scale)
     return R.rope_apply(q, k, positions, table, rot_dim, style, rot_offset, q_scale)
 
 
 def latent_cache_write(latent, cache, slots):
     """latent [T, kv_lora+rope] -> cache [nb,1,block,kv_lora+rope] at `slots`."""
     if _cuda(latent):
-        return native().latent_cache_write(latent, cache, slots)
+        return _nat().latent_cache_write(latent, cache, slots)
     blk = cache.shape[2]
     cache[(slots // blk).long(), 0, (slots % blk).long()] = latent.to(cache.dtype)
 
@@ -125,7 +125,7 @@ def latent_cache_write(latent, cache, slots):
 def route(logits, kind, top_k, bias=None, n_group=1, topk_group=1, routed_scaling=1.0, norm_topk=True,
           scoring="sigmoid"):
     if _cuda(logits):
-        return native().route(logits, kind, top_k, bias, n_group, topk_group, routed_scaling, norm_topk, scoring)
+        return _nat().route(logits, kind, top_k, bias, n_group, topk_group, routed_scaling, norm_topk, scoring)
     if kind == "mixtral":
         return R.route_mixtral(logits, top_k)
     if kind == "softmax_topk":
@@ -137,18 +137,18 @@ def route(logits, kind, top_k, bias=None, n_group=1, topk_group=1, routed_scalin
 
 def moe_experts(x, idx, w, experts, act="silu", expert_offset=0, packed=None):
     if _cuda(x):
-        return native().moe_experts(x, idx, w, experts, act, expert_offset, packed)
+        return _nat().moe_experts(x, idx, w, experts, act, expert_offset, packed)
     return R.moe_experts(x, idx, w, experts, act, expert_offset)
 
 
 # -- sampling ------------------------------------------------------------------------------
 def argmax_rows(logits):
     if _cuda(logits):
-        return native().argmax_rows(logits)
+        return _nat().argmax_rows(logits)
     return R.argmax_rows(logits)
 
 
 def sample_top_k_top_p(logits, top_k, top_p, temperature, uniform):
     if _cuda(logits):
-        return native().sample_top_k_top_p(logits, top_k, top_p, temperature, uniform)
+        return _nat().sample_top_k_top_p(logits, top_k, top_p, temperature, uniform)
     return R.sample_top_k_top_p(logits, top_k, top_p, temperature, uniform)
