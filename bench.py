@@ -56,7 +56,18 @@ def _clock_summary(proc, path, dev_index):
         proc.kill()
     sm, mx, reasons = [], [], set()
     try:
-        for line in open(path):
+        lines = open(path).read().splitlines()
+        if not any(l.strip() for l in lines):
+            # region shorter than one sampling period: take one reading now
+            q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+                 "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+                 "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+            try:
+                lines = subprocess.run(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits"],
+                                       capture_output=True, text=True, timeout=20).stdout.splitlines()
+            except Exception:
+                lines = []
+        for line in lines:
             c = [x.strip() for x in line.split(",")]
             if len(c) < 9 or not c[0].isdigit() or int(c[0]) != dev_index:
                 continue

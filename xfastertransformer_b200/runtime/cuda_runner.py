@@ -25,7 +25,7 @@ from . import sampler as S
 
 
 class _Graph:
-    __slots__ = ("graph", "B", "W", "host", "dev", "tok_dev", "tok_host", "batch", "version", "nsplit")
+    __slots__ = ("graph", "B", "W", "host", "dev", "tok_dev", "tok_host", "batch", "version", "nsplit", "kernels")
 
 
 class CudaRunner:
@@ -38,6 +38,9 @@ class CudaRunner:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.graph_launches = 0
+        self.kernel_launches = 0          # kernels of this library launched through replayed graphs / eager steps
+        self.timing = False               # record a CUDA-event pair around each step's launch
+        self.step_events = []
 
     def reset(self) -> None:
         pass
@@ -134,15 +137,27 @@ class CudaRunner:
                 # eager run (allocates workspaces, JIT-free), then capture
                 self._step_body(g)
                 st.synchronize()
+                from ..ops import native as N
+                ws = N.Workspace.get(self.dev)
+                n0 = ws.launches
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph, stream=st):
                     self._step_body(g)
                 g.graph = graph
+                g.kernels = ws.launches - n0
+                self.kernel_launches += g.kernels
                 # the eager run already produced this step's tokens and wrote its K/V; replaying the
                 # captured step would redo identical work — harmless, but skip it
             else:
+                if self.timing:
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(st)
                 g.graph.replay()
+                if self.timing:
+                    e1.record(st)
+                    self.step_events.append((e0, e1))
                 self.graph_launches += 1
+                self.kernel_launches += g.kernels
             g.tok_host.copy_(g.tok_dev, non_blocking=True)
         st.synchronize()
         self.h2d_bytes += g.host.numel() * 4

@@ -505,6 +505,19 @@ class Model:
 
     def _run(self, seqs: Sequence[SequenceMeta], logits_all: bool = False) -> torch.Tensor:
         """Run the decoder over the pending inputs of `seqs`; returns this rank's logits slice."""
+        # prefill of many long prompts is run in groups of at most XFT_MAX_BATCH_TOKENS tokens so
+        # the activation footprint stays bounded (each group is a self-contained ragged batch)
+        cap = self.env.max_batch_tokens
+        if len(seqs) > 1 and sum(len(s.pending) for s in seqs) > cap and any(len(s.pending) > 1 for s in seqs):
+            groups, cur, n = [], [], 0
+            for s in seqs:
+                if cur and n + len(s.pending) > cap:
+                    groups.append(cur)
+                    cur, n = [], 0
+                cur.append(s)
+                n += len(s.pending)
+            groups.append(cur)
+            return torch.cat([self._run(g, logits_all) for g in groups], dim=0)
         b = self.make_batch(seqs, logits_all)
         dec = self.decoder if b.is_decode else self.prefill_decoder
         name = "Next Token" if b.is_decode else "1st Token"
