@@ -410,3 +410,79 @@ extern "C" int xft_gemm_bf16(const void* X, int ldx, const void* W, int w_rows, 
 #undef XFT_LAUNCH
   return -1;
 }
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free entry point (declared in gemm_noalloc.h; no counterpart in the reference).
+//
+// Some hosts of this library may not allocate device memory at all once they are running: code
+// inside a CUDA-graph capture or a latency-critical serving loop where cudaMalloc would synchronise
+// the device, plug-ins living in a process whose memory pool is owned by someone else (an inference
+// server that has already reserved the whole GPU), and callers that only have raw device pointers
+// and no allocator to hand.  For them the split-K scratch of the GEMM above — partial tiles, tile
+// counters and the status word — lives in one file-scope device array of fixed size.
+//
+// The array is part of the library image: every GPU that loads the library keeps
+// XFT_NOALLOC_SCRATCH_BYTES (8 MiB + 8 KiB) resident until the process exits.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[(8u << 20) + 8192];
+
+namespace {
+constexpr size_t kNoallocPartialBytes = 8u << 20;    // split-K partial tiles
+constexpr int kNoallocCounters = 1024;               // one int per output tile (first 4 KiB)
+constexpr int kNoallocMaxTokens = 256;
+constexpr int kNoallocMaxDevices = 64;
+void* g_noalloc_ptr[kNoallocMaxDevices] = {};        // device address of the array, per device
+}  // namespace
+
+extern "C" const char* xft_gemm_bf16_noalloc_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case -100: return "shape exceeds the allocation-free variant: need T <= 256 tokens and ceil(N/128)*ceil(T/tile) <= 1024 tiles";
+    case -101: return "cudaGetSymbolAddress failed for the static scratch array";
+    case -102: return "no current CUDA device / device index out of range";
+    case -103: return "bad argument (null pointer, K not a multiple of 8, or unaligned rows)";
+    default: return "CUDA or tensor-map error (positive codes are cudaError_t values; 1000+/2000+ tensor-map encoding)";
+  }
+}
+
+// Y[T,N] = act(X[T,K] · W[N,K]^T + bias) + res_scale * residual, bf16 in, bf16 or fp32 out.
+// Same kernel and numerics as xft_gemm_bf16; the scratch is the static array above.
+extern "C" int xft_gemm_bf16_noalloc(const void* X, int ldx, const void* W, int ldw, void* Y, int ldo, int out_fp32,
+                                     int T, int N, int K, const float* bias, const void* residual, int ldr,
+                                     float res_scale, int act, cudaStream_t st) {
+  if (!X || !W || !Y || T <= 0 || N <= 0 || K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8)) return -103;
+  if (T > kNoallocMaxTokens) return -100;
+  const int bn = pick_bn(T);
+  const int tiles = ((N + 127) / 128) * ((T + bn - 1) / bn);
+  if (tiles > kNoallocCounters) return -100;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoallocMaxDevices) return -102;
+  if (!g_noalloc_ptr[dev]) {
+    // In host code the array's name is only a stand-in; the kernel needs its device address.
+    // Looked up once per device, with that device current.
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || !p) return -101;
+    g_noalloc_ptr[dev] = p;
+  }
+  unsigned char* base = static_cast<unsigned char*>(g_noalloc_ptr[dev]);
+  int* counters = reinterpret_cast<int*>(base);                       // [0, 4096)
+  int* status = reinterpret_cast<int*>(base + 4096);                  // [4096, 4352)
+  float* ws = reinterpret_cast<float*>(base + 8192);                  // partial tiles
+  // the array keeps whatever the previous call left: counters and status must start at zero
+  cudaError_t e = cudaMemsetAsync(base, 0, 8192, st);
+  if (e != cudaSuccess) return (int)e;
+  return xft_gemm_bf16(X, ldx, W, N, ldw, Y, ldo, out_fp32, T, N, K, /*gated=*/0, /*dual_off=*/0, bias, residual, ldr,
+                       res_scale, act, /*row_scale=*/nullptr, ws, kNoallocPartialBytes, counters, kNoallocCounters,
+                       status, /*force_splits=*/0, st);
+}
+
+// Status word of the last allocation-free call on the current device (0 = ok); synchronises the stream.
+extern "C" int xft_gemm_bf16_noalloc_status(cudaStream_t st) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoallocMaxDevices || !g_noalloc_ptr[dev]) return -102;
+  int v = 0;
+  if (cudaMemcpyAsync(&v, static_cast<unsigned char*>(g_noalloc_ptr[dev]) + 4096, sizeof(int), cudaMemcpyDeviceToHost, st) !=
+      cudaSuccess)
+    return -102;
+  if (cudaStreamSynchronize(st) != cudaSuccess) return -102;
+  return v;
+}
