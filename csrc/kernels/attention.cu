@@ -119,6 +119,14 @@ struct WarpAttn {
                                        int qpos1, float scale, float slope0, float slope1, bool use_alibi, int prefix_len,
                                        const float* kscale, const float* vscale, int lane) {
     float s[KT / 8][4];
+    scores(s, qtile, kt, key0, kv_len, qpos0, qpos1, scale, slope0, slope1, use_alibi, prefix_len, kscale, vscale, lane);
+    pv(s, vt, lane);
+  }
+
+  // phase 1: S = Q K^T, mask, online-softmax update; leaves P (scaled by vscale) in s and rescales O
+  __device__ __forceinline__ void scores(float (&s)[KT / 8][4], const bf16* qtile, const bf16* kt, int key0, int kv_len,
+                                         int qpos0, int qpos1, float scale, float slope0, float slope1, bool use_alibi,
+                                         int prefix_len, const float* kscale, const float* vscale, int lane) {
 #pragma unroll
     for (int j = 0; j < KT / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
     // S = Q K^T
@@ -177,7 +185,10 @@ struct WarpAttn {
     l[1] = l[1] * c1 + sum1;
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
-    // O += P V
+  }
+
+  // phase 2: O += P V
+  __device__ __forceinline__ void pv(float (&s)[KT / 8][4], const bf16* vt, int lane) {
 #pragma unroll
     for (int ks = 0; ks < KT / 16; ++ks) {
       uint32_t a[4];
@@ -366,16 +377,22 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
   const float slope0 = (use_alibi && r0 < nq) ? p.slopes[h_lo + r0] : 0.f;
   const float slope1 = (use_alibi && r1 < nq) ? p.slopes[h_lo + r1] : 0.f;
 
+  // Per warp: the V tile streams in while S is computed, the next K tile while P V is computed.
   int ti = t_begin + warp;
   issue_k(ti);
   issue_v(ti);
   for (; ti < t_end; ti += 4) {
-    cp_async_wait<0>();          // K(ti) and V(ti) landed; other warps' loads keep the memory system busy
+    float s[KT / 8][4];
+    cp_async_wait<1>();          // K(ti) landed (V(ti) may still be in flight)
     __syncwarp();
-    wa.step(qs, kt, vt, ti * KT, kv_len, qpos0, qpos1, p.scale, slope0, slope1, use_alibi, 0, INT8 ? ksc : nullptr,
-            INT8 ? vsc : nullptr, lane);
+    wa.scores(s, qs, kt, ti * KT, kv_len, qpos0, qpos1, p.scale, slope0, slope1, use_alibi, 0, INT8 ? ksc : nullptr,
+              INT8 ? vsc : nullptr, lane);
     __syncwarp();
-    issue_k(ti + 4);
+    issue_k(ti + 4);             // K buffer is free again
+    cp_async_wait<1>();          // V(ti) landed
+    __syncwarp();
+    wa.pv(s, vt, lane);
+    __syncwarp();
     issue_v(ti + 4);
   }
   cp_async_wait<0>();

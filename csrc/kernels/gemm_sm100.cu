@@ -27,6 +27,26 @@
 
 namespace xft {
 
+// Fused one-shot all-reduce (row-parallel o_proj / down_proj at decode sizes): replaces the reference's
+// GEMM followed by Messenger::reduceAdd (src/layers/decoder_block.h:122-134).  Every rank owns a receive
+// area [2 parities][world slots][T_cap x N] fp32 and a flag area [2][max_tiles][8]; `recv[r]` / `flag[r]`
+// are rank r's areas as mapped into this process (CUDA IPC over NVLink).  The CTA that finishes an output
+// tile pushes its partial tile into slot `rank` of every peer, raises the tile's flag there with the
+// call's epoch, waits (bounded) for the same tile from every peer, and sums the slots in rank order, so
+// all ranks produce bit-identical results.  The epoch is a device-side counter bumped by the last CTA of
+// each launch, which keeps the scheme valid under CUDA-graph replay.
+struct CommParams {
+  int world, rank;
+  float* recv[8];
+  int* flag[8];
+  int* epoch;              // local: number of completed fused launches
+  int* done;               // local: CTAs of the current launch that have exited
+  long long slot_stride;   // floats per source slot
+  long long parity_stride; // floats per parity (= world * slot_stride)
+  int flag_parity_stride;  // ints per parity
+  long long wait_cycles;   // bound of the peer wait
+};
+
 struct GemmParams {
   int N, T, K;
   int dual_off;            // DUAL: W row of the first "up" feature (gate rows are [0, dual_off))
@@ -44,6 +64,7 @@ struct GemmParams {
   int* status;
   int n_tiles, t_tiles, stages;
   const float* row_scale;  // optional per-output-feature scale applied to the accumulator (weight-only int8)
+  CommParams ar;           // ar.world > 1: the epilogue all-reduces the tile over peer memory
 };
 
 __device__ __forceinline__ float apply_act(float x, int act) {
@@ -77,6 +98,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
   __shared__ uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], tmem_full_bar;
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_last;
+  __shared__ int s_epoch, s_peer_fail;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int stages = p.stages;
@@ -104,6 +126,8 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(&tmem_full_bar, 1);
+    s_peer_fail = 0;
+    if (p.ar.world > 1) s_epoch = *reinterpret_cast<volatile int*>(p.ar.epoch) + 1;
     fence_barrier_init();
     fence_proxy_async();
     tma_prefetch_desc(&tmW);
@@ -195,15 +219,14 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
       last = s_last != 0;
       if (last) __threadfence();
     }
-    if (last && ok) {
+    if (last) {
       const float bias_g = (p.bias && n_ok) ? p.bias[n] : 0.f;
       const float bias_u = (DUAL && p.bias && n_ok) ? p.bias[p.dual_off + n] : 0.f;
       const float rs = (p.row_scale && n_ok) ? p.row_scale[n] : 1.f;
       const float* ws_tile = p.ws + (size_t)tile_id * (size_t)(BN * NACC) * 128;
       const size_t ws_split_stride = (size_t)(p.n_tiles * p.t_tiles) * (size_t)(BN * NACC) * 128;
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 16) {
-        float g[16], u[16];
+      // accumulator columns [c, c+16): from TMEM, or the sum of the split-K partials in split order
+      auto load_acc = [&](int c, float (&g)[16], float (&u)[16]) {
         if (p.splits > 1) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) { g[j] = 0.f; u[j] = 0.f; }
@@ -228,17 +251,76 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
             for (int j = 0; j < 16; ++j) u[j] = __uint_as_float(v[j]);
           }
         }
-        if (n_ok) {
+      };
+      const bool fused_ar = (!DUAL) && p.ar.world > 1;
+      bool peers_ok = true;
+      const int epoch = fused_ar ? s_epoch : 0;
+      const int par = epoch & 1;
+      if (fused_ar) {
+        // phase 1: push this rank's partial tile into slot `rank` of every rank (its own included)
+        if (ok) {
+#pragma unroll 1
+          for (int c = 0; c < BN; c += 16) {
+            float g[16], u[16];
+            load_acc(c, g, u);
+            if (n_ok) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int t = t0 + c + j;
-            if (t < p.T) {
-              float x = g[j] * rs + bias_g;
-              x = apply_act(x, p.act);
-              if (DUAL) x *= (u[j] * rs + bias_u);
-              if (p.residual) x += p.res_scale * __bfloat162float(p.residual[(size_t)t * p.ldr + n]);
-              if (p.out_fp32) reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + n] = x;
-              else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)t * p.ldo + n] = __float2bfloat16(x);
+              for (int j = 0; j < 16; ++j) {
+                const int t = t0 + c + j;
+                if (t < p.T) {
+                  const float v = g[j] * rs;
+                  const long long off = par * p.ar.parity_stride + p.ar.rank * p.ar.slot_stride + (long long)t * p.N + n;
+                  for (int r = 0; r < p.ar.world; ++r) p.ar.recv[r][off] = v;
+                }
+              }
+            }
+          }
+        }
+        __threadfence_system();
+        named_bar_sync(1, 128);
+        // phase 2: raise the tile's flag on every rank; phase 3: wait for every rank's flag here
+        if (et < p.ar.world) {
+          volatile int* f = p.ar.flag[et] + par * p.ar.flag_parity_stride + tile_id * 8 + p.ar.rank;
+          *f = epoch;
+          volatile int* mine = p.ar.flag[p.ar.rank] + par * p.ar.flag_parity_stride + tile_id * 8 + et;
+          const long long tstart = clock64();
+          while (*mine < epoch) {
+            if (clock64() - tstart > p.ar.wait_cycles) {
+              if (p.status) atomicCAS(p.status, 0, XFT_ERR_WAIT_PEER);
+              s_peer_fail = 1;
+              break;
+            }
+          }
+          __threadfence_system();
+        }
+        named_bar_sync(1, 128);
+        peers_ok = s_peer_fail == 0;
+      }
+      if (ok && peers_ok) {
+        const float* my_recv = fused_ar ? p.ar.recv[p.ar.rank] + par * p.ar.parity_stride : nullptr;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+          float g[16], u[16];
+          if (!fused_ar) load_acc(c, g, u);
+          if (n_ok) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int t = t0 + c + j;
+              if (t < p.T) {
+                float x;
+                if (fused_ar) {
+                  x = 0.f;                      // rank order: identical bits on every rank
+                  for (int r = 0; r < p.ar.world; ++r) x += __ldcg(my_recv + r * p.ar.slot_stride + (long long)t * p.N + n);
+                  x += bias_g;
+                } else {
+                  x = g[j] * rs + bias_g;
+                }
+                x = apply_act(x, p.act);
+                if (DUAL) x *= (u[j] * rs + bias_u);
+                if (p.residual) x += p.res_scale * __bfloat162float(p.residual[(size_t)t * p.ldr + n]);
+                if (p.out_fp32) reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + n] = x;
+                else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)t * p.ldo + n] = __float2bfloat16(x);
+              }
             }
           }
         }
@@ -250,6 +332,15 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
   if (warp == 1) {
     tcgen05_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (p.ar.world > 1 && threadIdx.x == 0) {
+    // last CTA of the launch: the next launch uses the next epoch (and the other buffer parity)
+    const int total = gridDim.x * gridDim.y;
+    if (atomicAdd(p.ar.done, 1) == total - 1) {
+      *reinterpret_cast<volatile int*>(p.ar.done) = 0;
+      __threadfence();
+      atomicAdd(p.ar.epoch, 1);
+    }
   }
 }
 
@@ -344,22 +435,31 @@ int pick_bn(int T) {
   return 256;
 }
 
-// Split-K plan: enough CTAs for ~2 per SM on small tiles, at least 2 k-blocks each, bounded scratch.
+// Split-K plan.  CTAs run in waves of `slots` (2 per SM for small token tiles, 1 otherwise); a split count
+// that spills a few CTAs into an extra wave nearly doubles the time, so the plan minimises
+//   waves(s) * (k-blocks per CTA + fixed per-CTA cost)
+// over the split counts that leave every CTA at least 2 k-blocks and fit the scratch.
 void plan_splits(int tiles, int num_kb, int bn, int nacc, size_t ws_bytes, int max_tiles, int* splits,
                  int* kb_per_split) {
-  int target = (bn <= 64) ? 296 : 148;
-  int s = 1;
-  if (tiles < target && tiles <= max_tiles) {
-    s = (target + tiles - 1) / tiles;
-    int max_by_k = num_kb / 2 > 0 ? num_kb / 2 : 1;
-    if (s > max_by_k) s = max_by_k;
-    size_t per_split = (size_t)tiles * bn * nacc * 128 * sizeof(float);
-    while (s > 1 && per_split * s > ws_bytes) --s;
-    if (s > 64) s = 64;
+  const int slots = (bn <= 64) ? 296 : 148;
+  int best = 1;
+  if (tiles < slots && tiles <= max_tiles && ws_bytes > 0) {
+    const size_t per_split = (size_t)tiles * bn * nacc * 128 * sizeof(float);
+    int smax = num_kb / 2 > 0 ? num_kb / 2 : 1;
+    if (smax > 64) smax = 64;
+    const long long c0 = 6;     // prologue + epilogue of a CTA, in k-block units
+    long long best_cost = -1;
+    for (int s = 1; s <= smax; ++s) {
+      if (s > 1 && per_split * s > ws_bytes) break;
+      const int per = (num_kb + s - 1) / s;
+      const int real = (num_kb + per - 1) / per;
+      const long long waves = ((long long)tiles * real + slots - 1) / slots;
+      const long long cost = waves * (per + c0 + (real > 1 ? 1 : 0));
+      if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = real; }
+    }
   }
-  int per = (num_kb + s - 1) / s;
-  s = (num_kb + per - 1) / per;
-  *splits = s;
+  const int per = (num_kb + best - 1) / best;
+  *splits = (num_kb + per - 1) / per;
   *kb_per_split = per;
 }
 
@@ -369,12 +469,14 @@ using namespace xft;
 
 // Y[T,N] = epi(X[T,K] W[N,K]^T).  gated != 0: W holds gate rows [0,N) and up rows [dual_off, dual_off+N),
 // Y = act(gate)*up.  ws/counters: split-K scratch (ws_bytes, n_counters ints, zero-initialised once).
-extern "C" int xft_gemm_bf16(const void* X, int ldx, const void* W, int w_rows, int ldw, void* Y, int ldo, int out_fp32,
-                             int T, int N, int K, int gated, int dual_off, const float* bias, const void* residual,
-                             int ldr, float res_scale, int act, const float* row_scale, float* ws, size_t ws_bytes,
-                             int* counters, int n_counters, int* status, int force_splits, cudaStream_t st) {
+static int gemm_bf16_impl(const void* X, int ldx, const void* W, int w_rows, int ldw, void* Y, int ldo, int out_fp32,
+                          int T, int N, int K, int gated, int dual_off, const float* bias, const void* residual,
+                          int ldr, float res_scale, int act, const float* row_scale, float* ws, size_t ws_bytes,
+                          int* counters, int n_counters, int* status, int force_splits, const CommParams* ar,
+                          cudaStream_t st) {
   if (T <= 0 || N <= 0 || K <= 0) return 0;
   GemmParams p{};
+  if (ar) p.ar = *ar;
   p.N = N; p.T = T; p.K = K; p.dual_off = dual_off; p.out = Y; p.ldo = ldo; p.out_fp32 = out_fp32;
   p.bias = bias; p.residual = reinterpret_cast<const __nv_bfloat16*>(residual); p.ldr = ldr; p.res_scale = res_scale;
   p.act = act; p.ws = ws; p.counters = counters; p.status = status; p.row_scale = row_scale;
@@ -409,6 +511,29 @@ extern "C" int xft_gemm_bf16(const void* X, int ldx, const void* W, int w_rows, 
   }
 #undef XFT_LAUNCH
   return -1;
+}
+
+extern "C" int xft_gemm_bf16(const void* X, int ldx, const void* W, int w_rows, int ldw, void* Y, int ldo, int out_fp32,
+                             int T, int N, int K, int gated, int dual_off, const float* bias, const void* residual,
+                             int ldr, float res_scale, int act, const float* row_scale, float* ws, size_t ws_bytes,
+                             int* counters, int n_counters, int* status, int force_splits, cudaStream_t st) {
+  return gemm_bf16_impl(X, ldx, W, w_rows, ldw, Y, ldo, out_fp32, T, N, K, gated, dual_off, bias, residual, ldr, res_scale,
+                        act, row_scale, ws, ws_bytes, counters, n_counters, status, force_splits, nullptr, st);
+}
+
+// Row-parallel GEMM fused with the tensor-parallel sum: Y = act(sum_r X_r W_r^T + bias) + res_scale*residual
+// on every rank.  `comm` describes the peer-mapped receive/flag areas (see CommParams); requires
+// T <= t_cap tokens and at most max_tiles output tiles (the capacity of the areas).
+extern "C" int xft_gemm_bf16_ar(const void* X, int ldx, const void* W, int ldw, void* Y, int ldo, int out_fp32, int T,
+                                int N, int K, const float* bias, const void* residual, int ldr, float res_scale, int act,
+                                float* ws, size_t ws_bytes, int* counters, int n_counters, int* status,
+                                const CommParams* comm, int t_cap, int max_tiles, cudaStream_t st) {
+  if (!comm || comm->world < 2 || comm->world > 8) return -10;
+  const int bn = pick_bn(T);
+  const int tiles = ((N + 127) / 128) * ((T + bn - 1) / bn);
+  if (T > t_cap || tiles > max_tiles || (long long)T * N > comm->slot_stride) return -11;
+  return gemm_bf16_impl(X, ldx, W, N, ldw, Y, ldo, out_fp32, T, N, K, 0, 0, bias, residual, ldr, res_scale, act, nullptr,
+                        ws, ws_bytes, counters, n_counters, status, 0, comm, st);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -409,7 +409,14 @@ class Decoder:
         return ops.layernorm(x, w, b, self.eps)
 
     def _row_parallel(self, h, W, bias, residual, res_scale=1.0):
-        """Row-parallel GEMM + sum over TP ranks; residual/bias only on rank 0."""
+        """Row-parallel GEMM + sum over TP ranks.  With peer memory (B200, decode sizes) this is ONE
+        kernel: the GEMM epilogue all-reduces its tiles over NVLink and adds bias/residual after the
+        sum.  Otherwise: partial GEMM with residual/bias on rank 0 only, then a collective."""
+        peer = getattr(self.ctx, "peer", None)
+        if self.tp > 1 and peer is not None and h.is_cuda:
+            T = h.numel() // h.shape[-1]
+            if peer.can_fuse(T, W.out_features, W.kind):
+                return peer.gemm_ar(h, W, bias, None, residual, res_scale)
         lead = self.tpr == 0
         y = ops.linear(h, W, bias if lead else None, None, residual if lead else None, res_scale)
         if self.tp > 1:

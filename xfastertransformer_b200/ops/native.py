@@ -281,7 +281,7 @@ def paged_attention(q, kc, vc, block_table, cu_q, kv_lens, scale, ks=None, vs=No
         kt = {64: 64, 128: 32, 256: 16}[D]
         ntiles = (max_kv + kt - 1) // kt
         ctas = B * hkv * ((g + 15) // 16)
-        nsplit = max(1, min((444 + ctas - 1) // ctas, ntiles // 8 if ntiles >= 16 else 1, 32))
+        nsplit = max(1, min(444 // max(ctas, 1), ntiles // 8 if ntiles >= 16 else 1, 32))
         if meta is not None and getattr(meta, "meta", None) is not None and "nsplit" in meta.meta:
             nsplit = meta.meta["nsplit"]
         if nsplit > 1:

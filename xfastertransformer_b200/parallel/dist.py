@@ -102,6 +102,7 @@ class DistContext:
         self.ep_size = self.tp_size if env.expert_parallel else 1
         self.ep_rank = self.tp_rank if env.expert_parallel else 0
         self.stats = {"all_reduce": 0, "all_gather": 0, "ctrl": 0, "p2p": 0}
+        self.peer = None      # PeerComm (symmetric buffers over CUDA IPC), set by the engine on GPUs
 
     # -- singleton ------------------------------------------------------------------
     @classmethod

@@ -1,0 +1,144 @@
+"""Peer-memory communication for the tensor-parallel group: symmetric buffers over CUDA IPC and
+the kernels that use them (fused GEMM + one-shot all-reduce, stand-alone one-shot all-reduce).
+
+The reference reduces the partial o_proj / down_proj outputs with a separate collective after the
+GEMM (``src/layers/decoder_block.h:122-134`` -> ``Messenger::reduceAdd`` -> oneCCL or the
+shared-memory chain of ``src/utils/shm_ccl.cpp:82-145``).  Here, at decode sizes, the GEMM's epilogue
+pushes each finished output tile straight into every peer's receive slot over NVLink, raises a per-tile
+flag, waits (bounded) for the peers' tiles and sums them in rank order — one kernel, no separate
+collective, bit-identical results on all ranks.  Larger token counts fall back to NCCL.
+
+Buffers per rank (allocated once, mapped by every peer):
+  recv  : [2 parities][world][T_CAP x N_MAX] fp32    flag : [2][MAX_TILES][8] int32
+A device-side epoch (bumped by the last CTA of every launch) selects the parity, so CUDA-graph
+replays stay in step without host involvement.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import native as N
+
+
+class CommParams(C.Structure):
+    _fields_ = [("world", C.c_int), ("rank", C.c_int), ("recv", C.c_void_p * 8), ("flag", C.c_void_p * 8),
+                ("epoch", C.c_void_p), ("done", C.c_void_p), ("slot_stride", C.c_longlong),
+                ("parity_stride", C.c_longlong), ("flag_parity_stride", C.c_int), ("wait_cycles", C.c_longlong)]
+
+
+class ArParams(C.Structure):
+    _fields_ = [("world", C.c_int), ("rank", C.c_int), ("recv", C.c_void_p * 8), ("flag", C.c_void_p * 8),
+                ("epoch", C.c_void_p), ("done", C.c_void_p), ("cap", C.c_longlong), ("flag_parity_stride", C.c_int),
+                ("wait_cycles", C.c_longlong), ("status", C.c_void_p)]
+
+
+class PeerComm:
+    T_CAP = 64
+    MAX_TILES = 1024
+
+    def __init__(self, ctx, n_max: int, wait_ms: float = 2000.0):
+        self.ctx = ctx
+        self.world, self.rank = ctx.tp_size, ctx.tp_rank
+        if not (2 <= self.world <= 8):
+            raise ValueError("PeerComm supports 2..8 ranks")
+        lib = N.lib()
+        for fn in ("xft_comm_alloc", "xft_comm_free", "xft_comm_ipc_handle", "xft_comm_ipc_open", "xft_comm_ipc_close",
+                   "xft_comm_handle_bytes", "xft_gemm_bf16_ar", "xft_allreduce_oneshot"):
+            getattr(lib, fn).restype = C.c_int
+        self.lib = lib
+        self.slot = self.T_CAP * n_max                           # floats per source slot
+        self.recv_floats = 2 * self.world * self.slot
+        self.flag_ints = 2 * self.MAX_TILES * 8
+        nbytes = self.recv_floats * 4 + self.flag_ints * 4
+        self.nbytes = nbytes
+        base = C.c_void_p()
+        N._check(lib.xft_comm_alloc(C.c_size_t(nbytes), C.byref(base)), "comm_alloc")
+        self.base = base.value
+        hb = lib.xft_comm_handle_bytes()
+        h = (C.c_char * hb)()
+        N._check(lib.xft_comm_ipc_handle(C.c_void_p(self.base), h), "ipc_handle")
+        mine = (ctx.rank, bytes(h))
+        allh: List = [None] * ctx.world
+        dist.all_gather_object(allh, mine, group=ctx.ctrl_group)
+        first = ctx.pp_rank * ctx.tp_size
+        self.peer_base: List[int] = []
+        self._opened: List[int] = []
+        for r in range(self.world):
+            if r == self.rank:
+                self.peer_base.append(self.base)
+                continue
+            grank, hbytes = allh[first + r]
+            p = C.c_void_p()
+            buf = (C.c_char * hb).from_buffer_copy(hbytes)
+            N._check(lib.xft_comm_ipc_open(buf, C.byref(p)), f"ipc_open(rank {grank})")
+            self.peer_base.append(p.value)
+            self._opened.append(p.value)
+        self.counters = torch.zeros(4, dtype=torch.int32, device=ctx.device)   # [epoch, done]
+        clock_khz = 1_900_000
+        self.wait_cycles = int(wait_ms * clock_khz)
+        self.gp = CommParams()
+        self.ap = ArParams()
+        for prm in (self.gp, self.ap):
+            prm.world, prm.rank = self.world, self.rank
+            for r in range(self.world):
+                prm.recv[r] = self.peer_base[r]
+                prm.flag[r] = self.peer_base[r] + self.recv_floats * 4
+            prm.epoch = self.counters.data_ptr()
+            prm.done = self.counters.data_ptr() + 4
+            prm.flag_parity_stride = self.MAX_TILES * 8
+            prm.wait_cycles = self.wait_cycles
+        self.gp.slot_stride = self.slot
+        self.gp.parity_stride = self.world * self.slot
+        self.ap.cap = self.slot
+        self.ap.status = N.Workspace.get(ctx.device).status.data_ptr()
+        self.fused_calls = 0
+        dist.barrier(group=ctx.ctrl_group)
+
+    # ------------------------------------------------------------------------------------
+    def can_fuse(self, T: int, n: int, kind: str) -> bool:
+        return kind == "bf16" and T <= self.T_CAP and T * n <= self.slot and (n + 127) // 128 <= self.MAX_TILES
+
+    def gemm_ar(self, x, W, bias=None, act=None, residual=None, res_scale=1.0, out_dtype=None):
+        """Y = act(sum over ranks of x_r @ W_r^T + bias) + res_scale*residual, on every rank."""
+        x2, ldx = N._rows2d(x)
+        T, K = x2.shape
+        n = W.out_features
+        fp32 = out_dtype == torch.float32
+        out = torch.empty(T, n, dtype=torch.float32 if fp32 else torch.bfloat16, device=x.device)
+        r2, ldr = (None, 0)
+        if residual is not None:
+            r2 = residual.reshape(-1, residual.shape[-1])
+            ldr = r2.stride(0)
+        ws = N.Workspace.get(x.device)
+        rc = self.lib.xft_gemm_bf16_ar(N._p(x2), ldx, N._p(W.w), W.w.stride(0), N._p(out), out.stride(0), int(fp32), T, n,
+                                       K, N._p(bias), N._p(r2), ldr, C.c_float(res_scale), N._ACT[act], N._p(ws.ws),
+                                       C.c_size_t(ws.ws_bytes), N._p(ws.counters), ws.n_counters, N._p(ws.status),
+                                       C.byref(self.gp), self.T_CAP, self.MAX_TILES, N._stream())
+        N._check(rc, "gemm_bf16_ar")
+        ws.launches += 1
+        self.fused_calls += 1
+        return out.view(*x.shape[:-1], n)
+
+    def all_reduce(self, t: torch.Tensor, add_f32: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Out-of-place one-shot sum of a small fp32/bf16 tensor (numel <= slot capacity)."""
+        assert t.is_contiguous() and t.numel() <= self.slot and t.dtype in (torch.float32, torch.bfloat16)
+        out = torch.empty_like(t)
+        n = t.numel()
+        nblocks = max(1, min(self.MAX_TILES, (n + 4095) // 4096))
+        rc = self.lib.xft_allreduce_oneshot(N._p(t), N._p(out), N._p(add_f32), C.c_longlong(n),
+                                            0 if t.dtype == torch.float32 else 1, C.byref(self.ap), nblocks, N._stream())
+        N._check(rc, "allreduce_oneshot")
+        N.Workspace.get(t.device).launches += 1
+        return out
+
+    def close(self) -> None:
+        for p in self._opened:
+            self.lib.xft_comm_ipc_close(C.c_void_p(p))
+        self._opened = []
+        if self.base:
+            self.lib.xft_comm_free(C.c_void_p(self.base))
+            self.base = 0

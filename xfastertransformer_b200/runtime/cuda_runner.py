@@ -76,7 +76,7 @@ class CudaRunner:
         dec = m.decoder
         ctas = B * max(dec.hkv, 1) * ((dec.group + 15) // 16)
         ntiles = (max_kv_hint + kt - 1) // kt
-        g.nsplit = max(1, min((444 + ctas - 1) // ctas, ntiles // 8 if ntiles >= 16 else 1, 32))
+        g.nsplit = max(1, min(444 // max(ctas, 1), ntiles // 8 if ntiles >= 16 else 1, 32))
         b = Batch(ids=d[o_ids:o_ids + B], positions=d[o_pos:o_pos + B], slots=d[o_slot:o_slot + B],
                   cu_q=list(range(B + 1)), kv_lens=[max_kv_hint] * B, block_table=d[o_bt:o_bt + B * W].view(B, W),
                   logit_rows=None, is_decode=True, max_q=1, max_kv=max_kv_hint)

@@ -85,6 +85,10 @@ class Model:
         self._closed = False
         self.vocab_sizes = [self._vocab_size_of(r) for r in range(self.ctx.tp_size)]
         self.runner = None
+        if self.ctx.device.type == "cuda" and self.ctx.tp_size > 1 and self.env.fused_comm and self.ctx.peer is None \
+                and self.ctx.tp_size <= 8:
+            from ..parallel.fused_comm import PeerComm
+            self.ctx.peer = PeerComm(self.ctx, n_max=self.cfg.hidden_size)
         if self.ctx.device.type == "cuda":
             from .cuda_runner import CudaRunner
             self.runner = CudaRunner(self)
