@@ -39,7 +39,7 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float
 template <typename T>
 __global__ void __launch_bounds__(256) allreduce_oneshot_kernel(const T* __restrict__ in, T* __restrict__ out,
                                                                 const float* __restrict__ add_f32, long long n,
-                                                                const ArParams p) {
+                                                                const ArParams p, const int gather) {
   __shared__ int s_epoch, s_fail;
   if (threadIdx.x == 0) { s_epoch = *reinterpret_cast<volatile int*>(p.epoch) + 1; s_fail = 0; }
   __syncthreads();
@@ -73,9 +73,13 @@ __global__ void __launch_bounds__(256) allreduce_oneshot_kernel(const T* __restr
   if (!s_fail) {
     const float* mine = p.recv[p.rank] + pbase;
     for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-      float x = 0.f;
-      for (int r = 0; r < p.world; ++r) x += __ldcg(mine + (long long)r * p.cap + i);
-      out[i] = from_f<T>(x);
+      if (gather) {          // all-gather: out[r][i] = rank r's contribution
+        for (int r = 0; r < p.world; ++r) out[(long long)r * n + i] = from_f<T>(__ldcg(mine + (long long)r * p.cap + i));
+      } else {
+        float x = 0.f;       // rank order: identical bits on every rank
+        for (int r = 0; r < p.world; ++r) x += __ldcg(mine + (long long)r * p.cap + i);
+        out[i] = from_f<T>(x);
+      }
     }
   }
   __syncthreads();
@@ -115,15 +119,16 @@ extern "C" int xft_comm_handle_bytes() { return (int)sizeof(cudaIpcMemHandle_t);
 
 // dtype: 0 = fp32, 1 = bf16.  nblocks <= capacity of the flag area.  add_f32: optional fp32 addend applied
 // to this rank's contribution before the sum (e.g. a residual on one rank).
+// gather != 0: all-gather instead of sum, out is [world, n].
 extern "C" int xft_allreduce_oneshot(const void* in, void* out, const float* add_f32, long long n, int dtype,
-                                     const ArParams* p, int nblocks, cudaStream_t st) {
+                                     const ArParams* p, int nblocks, int gather, cudaStream_t st) {
   if (!p || p->world < 2 || p->world > 8 || n > p->cap) return -10;
   if (n <= 0) return 0;
   if (nblocks < 1) nblocks = 1;
   if (dtype == 0)
-    allreduce_oneshot_kernel<float><<<nblocks, 256, 0, st>>>((const float*)in, (float*)out, add_f32, n, *p);
+    allreduce_oneshot_kernel<float><<<nblocks, 256, 0, st>>>((const float*)in, (float*)out, add_f32, n, *p, gather);
   else
     allreduce_oneshot_kernel<__nv_bfloat16><<<nblocks, 256, 0, st>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out,
-                                                                    add_f32, n, *p);
+                                                                    add_f32, n, *p, gather);
   return (int)cudaGetLastError();
 }

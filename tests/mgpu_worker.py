@@ -16,14 +16,23 @@ from xfastertransformer_b200.parallel.fused_comm import PeerComm
 from xfastertransformer_b200.runtime.loader import make_linear
 
 path, out = sys.argv[1], sys.argv[2]
+
+
+def stage(msg):
+    print(f"[rank {os.environ.get('RANK')}] {msg}", file=sys.stderr, flush=True)
+
+
+stage("start")
 ctx = DistContext.get()
 rank, world = ctx.rank, ctx.world
 dev = ctx.device
 res = {}
+stage("dist up")
 
 # --- 1. one-shot all-reduce: each rank contributes rank+1, expect n(n+1)/2; odd size hits the tail -------
 peer = PeerComm(ctx, n_max=8192)
 ctx.peer = peer
+stage("peer comm up")
 for n in (128 * 5120, 1024 * 4096 + 1 if 1024 * 4096 + 1 <= peer.slot else peer.slot - 1, 7):
     n = min(n, peer.slot)
     for dt in (torch.float32, torch.bfloat16):
@@ -33,6 +42,11 @@ for n in (128 * 5120, 1024 * 4096 + 1 if 1024 * 4096 + 1 <= peer.slot else peer.
         want = world * (world + 1) / 2
         assert bool((o.float() == want).all()), (n, dt, o[:4])
 res["allreduce"] = "ok"
+stage("allreduce ok")
+g2 = peer.all_gather(torch.full((5, 2), float(rank), device=dev))
+torch.cuda.synchronize()
+assert all(bool((g2[r] == r).all()) for r in range(world))
+stage("allgather ok")
 
 # --- 2. fused GEMM + all-reduce vs fp32 reference ---------------------------------------------------------
 g = torch.Generator().manual_seed(0)
@@ -57,12 +71,15 @@ dist.all_gather_object(gathered, outs[-1], group=ctx.ctrl_group)
 assert all(torch.equal(gathered[0], t) for t in gathered), "ranks must hold bit-identical results"
 N.Workspace.get(dev).check_status()
 res["gemm_ar"] = "ok"
+stage("gemm_ar ok")
 
 # --- 3. tiny Llama, tensor parallel over the GPUs, CUDA-graph decode with the fused kernels -----------------
 model = xft.AutoModel.from_pretrained(path, dtype="bf16")
+stage("model loaded")
 gi = torch.Generator().manual_seed(1)
 ids = torch.randint(0, 32000, (2, 32), generator=gi)
 tokens = model.generate(ids, max_length=48) if rank == 0 else model.generate()
+stage("generate done")
 N.Workspace.get(dev).check_status()
 m = model.model
 res["fused_calls"] = m.ctx.peer.fused_calls

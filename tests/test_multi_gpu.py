@@ -27,10 +27,10 @@ def test_tp_peer_comm_and_model(world, tmp_path):
     write_synthetic_checkpoint(d, preset("tiny-llama", head_num=8, kv_head_num=8, size_per_head=64, hidden_size=512,
                                          inter_size=1408), seed=0, dtype="bf16", std=0.05)
     out = str(tmp_path / "out.pt")
-    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    env = dict(os.environ, XFT_DIST_TIMEOUT_S="120", PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
            "127.0.0.1", "--master-port", str(29700 + world), os.path.join(ROOT, "tests", "mgpu_worker.py"), d, out]
-    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-4000:] + r.stderr[-4000:]
     got = torch.load(out)
     assert got["res"]["allreduce"] == "ok" and got["res"]["gemm_ar"] == "ok"

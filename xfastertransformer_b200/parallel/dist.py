@@ -47,6 +47,7 @@ class DistContext:
 
     def __init__(self, device: Optional[torch.device] = None, timeout_s: float = 1800.0):
         env = Env.get()
+        timeout_s = float(os.environ.get("XFT_DIST_TIMEOUT_S", timeout_s))
         self.rank, self.world = (0, 1)
         self.owns_pg = False
         if Env.launched_multi_rank() or (dist.is_available() and dist.is_initialized()):

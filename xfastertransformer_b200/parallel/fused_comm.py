@@ -130,8 +130,22 @@ class PeerComm:
         n = t.numel()
         nblocks = max(1, min(self.MAX_TILES, (n + 4095) // 4096))
         rc = self.lib.xft_allreduce_oneshot(N._p(t), N._p(out), N._p(add_f32), C.c_longlong(n),
-                                            0 if t.dtype == torch.float32 else 1, C.byref(self.ap), nblocks, N._stream())
+                                            0 if t.dtype == torch.float32 else 1, C.byref(self.ap), nblocks, 0,
+                                            N._stream())
         N._check(rc, "allreduce_oneshot")
+        N.Workspace.get(t.device).launches += 1
+        return out
+
+    def all_gather(self, t: torch.Tensor) -> torch.Tensor:
+        """[world, *t.shape] of a small fp32/bf16 tensor, through the same push/flag/wait kernel."""
+        assert t.is_contiguous() and t.numel() <= self.slot and t.dtype in (torch.float32, torch.bfloat16)
+        out = torch.empty((self.world,) + tuple(t.shape), dtype=t.dtype, device=t.device)
+        n = t.numel()
+        nblocks = max(1, min(self.MAX_TILES, (n + 4095) // 4096))
+        rc = self.lib.xft_allreduce_oneshot(N._p(t), N._p(out), N._p(None), C.c_longlong(n),
+                                            0 if t.dtype == torch.float32 else 1, C.byref(self.ap), nblocks, 1,
+                                            N._stream())
+        N._check(rc, "allgather_oneshot")
         N.Workspace.get(t.device).launches += 1
         return out
 

@@ -32,7 +32,11 @@ def greedy_select(local: torch.Tensor, vocab_offset: int, ctx: DistContext) -> t
     if ctx.tp_size == 1:
         return i.long()
     pair = torch.stack([v.float(), (i + vocab_offset).float()], dim=-1)       # ids exact below 2^24
-    allp = ctx.all_gather_cat(pair.unsqueeze(0), None, dim=0)                  # [tp, rows, 2]
+    peer = getattr(ctx, "peer", None)
+    if peer is not None and pair.is_cuda and pair.numel() <= peer.slot:
+        allp = peer.all_gather(pair.contiguous())                              # peer-memory kernel, graph-safe
+    else:
+        allp = ctx.all_gather_cat(pair.unsqueeze(0), None, dim=0)              # [tp, rows, 2]
     vals, ids = allp[..., 0], allp[..., 1]
     best = torch.argmax(vals, dim=0)           # first (lowest rank) maximum
     return ids.gather(0, best[None])[0].long()
