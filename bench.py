@@ -227,9 +227,10 @@ def main():
             out["invalid"] = "debug run with fewer layers"
         print(json.dumps(out))
     model.finalize()
-    m.exit_slaves()
+    m._closed = True          # every rank runs this script to the end: nobody sits in a serving loop to be released
     if world > 1:
         dist.barrier(group=m.ctx.ctrl_group)
+        dist.destroy_process_group()
     return 0
 
 

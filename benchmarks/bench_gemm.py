@@ -1,0 +1,106 @@
+#!/usr/bin/env python
+"""Kernel micro-benchmark: the tcgen05 GEMM of this library against torch.matmul (cuBLAS) on the
+per-GPU shapes of the BASELINE configs.  CUDA-event timing on the launching stream, warm-up, and a
+rotation over enough distinct weight copies that every timed launch streams its weight from HBM
+(working set > the 126 MB L2).  Prints achieved GB/s (decode shapes are bandwidth-bound) and TFLOP/s,
+and the fraction of the measured peaks in MEASURED_PEAKS.json.
+
+    python benchmarks/bench_gemm.py [--shapes decode|prefill|all] [--iters 20] [--one T,N,K[,gated]]
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+from xfastertransformer_b200.ops import native as N  # noqa: E402
+
+# (name, T, N, K, gated)  — Llama-2-70B at TP=1 and TP=8, decode batch 16/64 and a prefill chunk
+DECODE = [
+    ("70b tp1 qkv   b16", 16, 10240, 8192, False), ("70b tp1 o     b16", 16, 8192, 8192, False),
+    ("70b tp1 gateup b16", 16, 28672, 8192, True), ("70b tp1 down  b16", 16, 8192, 28672, False),
+    ("70b tp1 lmhead b16", 16, 32000, 8192, False),
+    ("70b tp8 qkv   b16", 16, 1280, 8192, False), ("70b tp8 o     b16", 16, 8192, 1024, False),
+    ("70b tp8 gateup b16", 16, 3584, 8192, True), ("70b tp8 down  b16", 16, 8192, 3584, False),
+    ("70b tp8 gateup b64", 64, 3584, 8192, True), ("70b tp1 gateup b64", 64, 28672, 8192, True),
+]
+PREFILL = [
+    ("70b tp1 qkv   t8192", 8192, 10240, 8192, False), ("70b tp1 gateup t8192", 8192, 28672, 8192, True),
+    ("70b tp1 down  t8192", 8192, 8192, 28672, False), ("70b tp8 gateup t8192", 8192, 3584, 8192, True),
+    ("7b  tp1 qkv   t4096", 4096, 12288, 4096, False),
+]
+
+
+def time_fn(fn, n_variants, iters):
+    for i in range(3):
+        fn(i % n_variants)
+    torch.cuda.synchronize()
+    evs = []
+    for i in range(iters):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn(i % n_variants)
+        b.record()
+        evs.append((a, b))
+    torch.cuda.synchronize()
+    ts = sorted(a.elapsed_time(b) for a, b in evs)
+    return ts[len(ts) // 2]
+
+
+def run(name, T, Nf, K, gated, iters, peaks):
+    rows = 2 * Nf if gated else Nf
+    wbytes = rows * K * 2
+    copies = max(2, min(16, (400 << 20) // wbytes + 1))
+    ws = [(torch.randn(rows, K, device="cuda", dtype=torch.bfloat16) * 0.02) for _ in range(copies)]
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(T, Nf, device="cuda", dtype=torch.bfloat16)
+
+    def ours(i):
+        N.gemm_bf16(x, ws[i], Nf, gated=gated, dual_off=Nf, act="silu" if gated else None, out=out)
+
+    def cublas(i):
+        y = torch.matmul(x, ws[i].t())
+        if gated:
+            torch.nn.functional.silu(y[:, :Nf]).mul_(y[:, Nf:])
+
+    t_ours = time_fn(ours, copies, iters)
+    t_ref = time_fn(cublas, copies, iters)
+    byts = wbytes + T * K * 2 + T * Nf * 2
+    flops = 2.0 * T * rows * K
+    gbs = byts / t_ours / 1e6
+    tf = flops / t_ours / 1e9
+    rec = {"shape": name, "T": T, "N": Nf, "K": K, "gated": gated, "ours_us": round(t_ours * 1e3, 2),
+           "cublas_us": round(t_ref * 1e3, 2), "speedup_vs_cublas": round(t_ref / t_ours, 3), "GBps": round(gbs, 1),
+           "TFLOPs": round(tf, 1)}
+    if peaks:
+        rec["hbm_frac_of_measured"] = round(gbs / peaks["hbm_gbs"], 3)
+        rec["mma_frac_of_measured"] = round(tf / peaks["bf16_tflops"], 3)
+    print(json.dumps(rec), flush=True)
+    N.Workspace.get(torch.device("cuda", 0)).check_status()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shapes", default="all")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--one", default="")
+    a = ap.parse_args()
+    peaks = None
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    if a.one:
+        f = a.one.split(",")
+        shapes = [("custom", int(f[0]), int(f[1]), int(f[2]), len(f) > 3 and f[3] == "gated")]
+    else:
+        shapes = (DECODE if a.shapes in ("decode", "all") else []) + (PREFILL if a.shapes in ("prefill", "all") else [])
+    for s in shapes:
+        run(*s, a.iters, peaks)
+
+
+if __name__ == "__main__":
+    main()
