@@ -35,25 +35,37 @@ PREFILL = [
 
 
 def time_fn(fn, n_variants, iters):
-    for i in range(3):
-        fn(i % n_variants)
+    """Median time per launch.  Each timed sample is one CUDA-graph replay of `n_variants` launches (one per
+    weight copy), so short kernels are not measured through host launch gaps."""
+    for i in range(n_variants):
+        fn(i)
     torch.cuda.synchronize()
-    evs = []
-    for i in range(iters):
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        fn(i % n_variants)
-        b.record()
-        evs.append((a, b))
-    torch.cuda.synchronize()
-    ts = sorted(a.elapsed_time(b) for a, b in evs)
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(g, stream=s):
+            for i in range(n_variants):
+                fn(i)
+        for _ in range(3):
+            g.replay()
+        s.synchronize()
+        evs = []
+        for i in range(iters):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(s)
+            g.replay()
+            b.record(s)
+            evs.append((a, b))
+        s.synchronize()
+    ts = sorted(a.elapsed_time(b) / n_variants for a, b in evs)
     return ts[len(ts) // 2]
 
 
 def run(name, T, Nf, K, gated, iters, peaks):
     rows = 2 * Nf if gated else Nf
     wbytes = rows * K * 2
-    copies = max(2, min(16, (400 << 20) // wbytes + 1))
+    copies = max(4, min(24, (400 << 20) // wbytes + 1))
     ws = [(torch.randn(rows, K, device="cuda", dtype=torch.bfloat16) * 0.02) for _ in range(copies)]
     x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
     out = torch.empty(T, Nf, device="cuda", dtype=torch.bfloat16)

@@ -36,6 +36,7 @@ struct AttnParams {
   int num_blocks;
   // decode split
   int nsplit; float* part_o; float* part_ml;   // [B, hq, nsplit, HD], [B, hq, nsplit, 2]
+  int* split_counters;      // [B * gridDim.y] arrival counters (zero between launches)
   int* status;
 };
 
@@ -438,6 +439,37 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
       if (d == 0) { p.part_ml[pi * 2] = mm; p.part_ml[pi * 2 + 1] = ll; }
     }
   }
+  if (p.nsplit > 1) {
+    // the slice that arrives last merges all slices of this (sequence, kv head): no second kernel, no spinning
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      int* c = p.split_counters + (size_t)b * gridDim.y + blockIdx.y;
+      const int old = atomicAdd(c, 1);
+      s_last = (old == p.nsplit - 1);
+      if (s_last) *c = 0;
+    }
+    __syncthreads();
+    if (s_last) {
+      __threadfence();
+      for (int i = tid; i < nq * HD; i += 128) {
+        const int r = i / HD, d = i % HD;
+        const int h = h_lo + r;
+        const size_t base = ((size_t)b * p.hq + h) * p.nsplit;
+        float mm = -INFINITY;
+        for (int s = 0; s < p.nsplit; ++s) mm = fmaxf(mm, __ldcg(p.part_ml + (base + s) * 2));
+        float acc = 0.f, ll = 0.f;
+        for (int s = 0; s < p.nsplit; ++s) {
+          const float ms = __ldcg(p.part_ml + (base + s) * 2);
+          const float c = (ms == -INFINITY) ? 0.f : __expf(ms - mm);
+          acc += c * __ldcg(p.part_o + (base + s) * HD + d);
+          ll += c * __ldcg(p.part_ml + (base + s) * 2 + 1);
+        }
+        p.out[((size_t)tok * p.hq + h) * HD + d] = __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
+      }
+    }
+  }
 }
 
 // merge split partials: grid (B, hq), HD threads
@@ -489,13 +521,7 @@ static int launch_decode(const AttnParams& p, int B, bool int8, cudaStream_t st)
     cudaFuncSetAttribute(attn_decode_kernel<HD, KT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     attn_decode_kernel<HD, KT, false><<<grid, 128, smem, st>>>(p);
   }
-  int e = (int)cudaGetLastError();
-  if (e) return e;
-  if (p.nsplit > 1) {
-    attn_merge_kernel<<<dim3(B, p.hq), HD, 0, st>>>(p.part_o, p.part_ml, p.out, p.cu_q, p.hq, HD, p.nsplit);
-    e = (int)cudaGetLastError();
-  }
-  return e;
+  return (int)cudaGetLastError();
 }
 
 // decode != 0: every sequence has exactly one query row.  nsplit/part_*: split-KV scratch (decode only).
@@ -503,17 +529,17 @@ extern "C" int xft_paged_attention(const void* q, void* out, const void* kc, con
                                    const int* block_table, int bt_stride, const int* cu_q, const int* kv_lens, int B,
                                    int max_q, int hq, int hkv, int group, int q_off, int HD, int bs, int num_blocks,
                                    float scale, const float* slopes, const int* prefix_lens, int decode, int nsplit,
-                                   float* part_o, float* part_ml, int* status, cudaStream_t st) {
+                                   float* part_o, float* part_ml, int* split_counters, int* status, cudaStream_t st) {
   if (B <= 0) return 0;
   AttnParams p{};
   p.q = (const bf16*)q; p.out = (bf16*)out; p.kc = kc; p.vc = vc; p.ks = ks; p.vs = vs;
   p.block_table = block_table; p.bt_stride = bt_stride; p.cu_q = cu_q; p.kv_lens = kv_lens; p.slopes = slopes;
   p.prefix_lens = prefix_lens; p.hq = hq; p.hkv = hkv; p.group = group; p.q_off = q_off; p.bs = bs; p.scale = scale;
-  p.num_blocks = num_blocks; p.nsplit = nsplit < 1 ? 1 : nsplit; p.part_o = part_o; p.part_ml = part_ml; p.status = status;
+  p.num_blocks = num_blocks; p.nsplit = nsplit < 1 ? 1 : nsplit; p.part_o = part_o; p.part_ml = part_ml; p.split_counters = split_counters; p.status = status;
   const bool int8 = ks != nullptr;
   if (bs % 64) return -2;
   if (decode) {
-    if (p.nsplit > 1 && (!part_o || !part_ml)) return -3;
+    if (p.nsplit > 1 && (!part_o || !part_ml || !split_counters)) return -3;
     // per-warp K+V tiles of 16 KB: a CTA stays at ~64 KB so three CTAs (12 warps) overlap loads and math per SM
     if (HD == 64) return launch_decode<64, 64>(p, B, int8, st);
     if (HD == 128) return launch_decode<128, 32>(p, B, int8, st);

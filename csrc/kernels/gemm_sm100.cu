@@ -412,6 +412,7 @@ static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, GemmParam
   // small token tiles: keep a CTA under half an SM's shared memory so two CTAs (and twice the
   // loads in flight) share an SM; large tiles take the whole SM
   int budget = (BN <= 64) ? 110 * 1024 : 220 * 1024;
+  if (budget / STAGE_BYTES < 4) budget = 220 * 1024;      // a deep pipeline beats a second resident CTA
   int stages = budget / STAGE_BYTES;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) stages = 2;
@@ -435,27 +436,34 @@ int pick_bn(int T) {
   return 256;
 }
 
-// Split-K plan.  CTAs run in waves of `slots` (2 per SM for small token tiles, 1 otherwise); a split count
-// that spills a few CTAs into an extra wave nearly doubles the time, so the plan minimises
-//   waves(s) * (k-blocks per CTA + fixed per-CTA cost)
-// over the split counts that leave every CTA at least 2 k-blocks and fit the scratch.
+// Split-K plan from a small cost model (microseconds):
+//   t(s) = t_fixed + [s > 1] * t_split + waves * (k-blocks per CTA * bytes per k-block * CTAs per wave) / BW(CTAs per wave)
+// BW grows with the number of busy SMs (~70 GB/s for a lone CTA on an SM, ~90 GB/s per SM with two) up to the
+// HBM rate; `waves` charges the tail wave in full; t_split is the price of the partial-tile round trip through
+// scratch plus the arrival counter.  Small problems therefore stay unsplit and large ones avoid a ragged tail.
 void plan_splits(int tiles, int num_kb, int bn, int nacc, size_t ws_bytes, int max_tiles, int* splits,
                  int* kb_per_split) {
-  const int slots = (bn <= 64) ? 296 : 148;
+  const int stage_bytes = 128 * 64 * 2 * nacc + bn * 64 * 2;
+  const int slots = (bn <= 64 && (110 * 1024) / stage_bytes >= 4) ? 296 : 148;
   int best = 1;
   if (tiles < slots && tiles <= max_tiles && ws_bytes > 0) {
     const size_t per_split = (size_t)tiles * bn * nacc * 128 * sizeof(float);
     int smax = num_kb / 2 > 0 ? num_kb / 2 : 1;
     if (smax > 64) smax = 64;
-    const long long c0 = 6;     // prologue + epilogue of a CTA, in k-block units
-    long long best_cost = -1;
+    const double hbm = 6.4e6;                      // bytes per microsecond
+    double best_t = -1.0;
     for (int s = 1; s <= smax; ++s) {
       if (s > 1 && per_split * s > ws_bytes) break;
       const int per = (num_kb + s - 1) / s;
       const int real = (num_kb + per - 1) / per;
-      const long long waves = ((long long)tiles * real + slots - 1) / slots;
-      const long long cost = waves * (per + c0 + (real > 1 ? 1 : 0));
-      if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = real; }
+      const long long ctas = (long long)tiles * real;
+      const long long waves = (ctas + slots - 1) / slots;
+      const long long in_wave = ctas < slots ? ctas : slots;
+      const long long sms = in_wave < 148 ? in_wave : 148;
+      double bw = (double)sms * (in_wave >= 296 ? 9.0e4 : in_wave > 148 ? 8.0e4 : 7.0e4);
+      if (bw > hbm) bw = hbm;
+      const double t = 4.0 + (real > 1 ? 3.5 : 0.0) + (double)waves * ((double)per * stage_bytes * (double)in_wave) / bw;
+      if (best_t < 0 || t < best_t) { best_t = t; best = real; }
     }
   }
   const int per = (num_kb + best - 1) / best;

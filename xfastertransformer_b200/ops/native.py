@@ -70,6 +70,7 @@ class Workspace:
         self.ws = torch.empty(self.ws_bytes // 4, dtype=torch.float32, device=device)
         self.n_counters = 8192
         self.counters = torch.zeros(self.n_counters, dtype=torch.int32, device=device)
+        self.attn_counters = torch.zeros(16384, dtype=torch.int32, device=device)
         self.status = torch.zeros(4, dtype=torch.int32, device=device)
         self.part_o = None
         self.part_ml = None
@@ -284,15 +285,17 @@ def paged_attention(q, kc, vc, block_table, cu_q, kv_lens, scale, ks=None, vs=No
         nsplit = max(1, min(444 // max(ctas, 1), ntiles // 8 if ntiles >= 16 else 1, 32))
         if meta is not None and getattr(meta, "meta", None) is not None and "nsplit" in meta.meta:
             nsplit = meta.meta["nsplit"]
+        if B * hkv * ((g + 15) // 16) > ws.attn_counters.numel():
+            nsplit = 1
         if nsplit > 1:
             po, pm = ws.attn_partials(B * hq * nsplit * D, B * hq * nsplit * 2)
     q = q.contiguous()
     rc = lib().xft_paged_attention(_p(q), _p(out), _p(kc), _p(vc), _p(ks), _p(vs), _p(block_table),
                                    block_table.stride(0), _p(cu_dev), _p(kv_dev), B, max_q, hq, hkv, g, q_off, D, bs,
                                    nb, C.c_float(scale), _p(slopes), _p(pl), int(decode), nsplit, _p(po), _p(pm),
-                                   _p(ws.status), _stream())
+                                   _p(ws.attn_counters), _p(ws.status), _stream())
     _check(rc, "paged_attention")
-    ws.launches += 2 if nsplit > 1 else 1
+    ws.launches += 1
     return out
 
 
