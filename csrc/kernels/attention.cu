@@ -306,6 +306,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);                 // [16][HD]
   bf16* kv = qs + 16 * HD;                                      // per warp: K [KT][HD], V [KT][HD]
   float* scb = reinterpret_cast<float*>(kv + 4 * 2 * KT * HD);  // per warp [2][KT]
+  grid_dep_launch();
+  grid_dep_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int b = blockIdx.x;
   const int qchunks = (p.group + 15) / 16;
@@ -516,10 +518,12 @@ static int launch_decode(const AttnParams& p, int B, bool int8, cudaStream_t st)
   dim3 grid(B, p.hkv * qchunks, p.nsplit);
   if (int8) {
     cudaFuncSetAttribute(attn_decode_kernel<HD, KT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    attn_decode_kernel<HD, KT, true><<<grid, 128, smem, st>>>(p);
+    cudaError_t e = launch_pdl(attn_decode_kernel<HD, KT, true>, grid, dim3(128), smem, st, p);
+    if (e != cudaSuccess) return (int)e;
   } else {
     cudaFuncSetAttribute(attn_decode_kernel<HD, KT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    attn_decode_kernel<HD, KT, false><<<grid, 128, smem, st>>>(p);
+    cudaError_t e = launch_pdl(attn_decode_kernel<HD, KT, false>, grid, dim3(128), smem, st, p);
+    if (e != cudaSuccess) return (int)e;
   }
   return (int)cudaGetLastError();
 }

@@ -41,6 +41,8 @@ __global__ void __launch_bounds__(256) allreduce_oneshot_kernel(const T* __restr
                                                                 const float* __restrict__ add_f32, long long n,
                                                                 const ArParams p, const int gather) {
   __shared__ int s_epoch, s_fail;
+  grid_dep_launch();
+  grid_dep_wait();
   if (threadIdx.x == 0) { s_epoch = *reinterpret_cast<volatile int*>(p.epoch) + 1; s_fail = 0; }
   __syncthreads();
   const int epoch = s_epoch, par = epoch & 1;
@@ -125,10 +127,12 @@ extern "C" int xft_allreduce_oneshot(const void* in, void* out, const float* add
   if (!p || p->world < 2 || p->world > 8 || n > p->cap) return -10;
   if (n <= 0) return 0;
   if (nblocks < 1) nblocks = 1;
+  cudaError_t e;
   if (dtype == 0)
-    allreduce_oneshot_kernel<float><<<nblocks, 256, 0, st>>>((const float*)in, (float*)out, add_f32, n, *p, gather);
+    e = launch_pdl(allreduce_oneshot_kernel<float>, dim3(nblocks), dim3(256), 0, st, (const float*)in, (float*)out, add_f32,
+                   n, *p, gather);
   else
-    allreduce_oneshot_kernel<__nv_bfloat16><<<nblocks, 256, 0, st>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out,
-                                                                    add_f32, n, *p, gather);
-  return (int)cudaGetLastError();
+    e = launch_pdl(allreduce_oneshot_kernel<__nv_bfloat16>, dim3(nblocks), dim3(256), 0, st, (const __nv_bfloat16*)in,
+                   (__nv_bfloat16*)out, add_f32, n, *p, gather);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }

@@ -40,6 +40,8 @@ struct alignas(16) bf16x8 { bf16 v[8]; };
 __global__ void embedding_kernel(const int* __restrict__ ids, const bf16* __restrict__ table, bf16* __restrict__ out,
                                  int H, int vocab, float scale, const bf16* __restrict__ pos_table,
                                  const int* __restrict__ positions, int pos_offset, int npos, int* status) {
+  grid_dep_launch();
+  grid_dep_wait();
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= vocab) { if (threadIdx.x == 0 && status) atomicCAS(status, 0, XFT_ERR_BOUNDS); id = 0; }
@@ -75,6 +77,8 @@ __global__ void __launch_bounds__(NT) rmsnorm_kernel(const bf16* __restrict__ x,
                                                      bf16* __restrict__ h_out, int H, float eps) {
   __shared__ float sh[NT / 32];
   extern __shared__ float row[];     // H floats
+  grid_dep_launch();
+  grid_dep_wait();
   const int t = blockIdx.x;
   const bf16x8* xp = reinterpret_cast<const bf16x8*>(x + (size_t)t * ldx);
   const bf16x8* rp = res ? reinterpret_cast<const bf16x8*>(res + (size_t)t * ldr) : nullptr;
@@ -166,6 +170,8 @@ struct RopeCacheParams {
 
 __global__ void __launch_bounds__(128) qkv_rope_cache_kernel(const RopeCacheParams p) {
   __shared__ float sh[4][256];
+  grid_dep_launch();
+  grid_dep_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nheads = p.hq + 2 * p.hkv;
   const long long gw = (long long)blockIdx.x * 4 + warp;
@@ -279,6 +285,8 @@ __global__ void __launch_bounds__(NT) argmax_kernel(const float* __restrict__ lo
                                                     int* __restrict__ idx) {
   __shared__ float sv[NT / 32];
   __shared__ int si[NT / 32];
+  grid_dep_launch();
+  grid_dep_wait();
   const float* row = logits + (size_t)blockIdx.x * ld;
   float best = -INFINITY;
   int bi = 0x7fffffff;
@@ -311,22 +319,23 @@ extern "C" int xft_embedding(const int* ids, const void* table, void* out, int T
                              cudaStream_t st) {
   if (T <= 0) return 0;
   if (H % 8) return -1;
-  embedding_kernel<<<T, 128, 0, st>>>(ids, (const bf16*)table, (bf16*)out, H, vocab, scale, (const bf16*)pos_table,
-                                      positions, pos_offset, npos, status);
-  return (int)cudaGetLastError();
+  cudaError_t e = launch_pdl(embedding_kernel, dim3(T), dim3(128), 0, st, ids, (const bf16*)table, (bf16*)out, H, vocab,
+                             scale, (const bf16*)pos_table, positions, pos_offset, npos, status);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 extern "C" int xft_rmsnorm(const void* x, int ldx, const void* res, int ldr, const float* w, void* y, int ldy, void* h_out,
                            int T, int H, float eps, cudaStream_t st) {
   if (T <= 0) return 0;
   if (H % 8 || ldx % 8 || ldy % 8 || (res && ldr % 8)) return -1;
+  cudaError_t e;
   if (H >= 2048)
-    rmsnorm_kernel<256><<<T, 256, H * sizeof(float), st>>>((const bf16*)x, ldx, (const bf16*)res, ldr, w, (bf16*)y, ldy,
-                                                          (bf16*)h_out, H, eps);
+    e = launch_pdl(rmsnorm_kernel<256>, dim3(T), dim3(256), H * sizeof(float), st, (const bf16*)x, ldx, (const bf16*)res,
+                   ldr, w, (bf16*)y, ldy, (bf16*)h_out, H, eps);
   else
-    rmsnorm_kernel<64><<<T, 64, H * sizeof(float), st>>>((const bf16*)x, ldx, (const bf16*)res, ldr, w, (bf16*)y, ldy,
-                                                        (bf16*)h_out, H, eps);
-  return (int)cudaGetLastError();
+    e = launch_pdl(rmsnorm_kernel<64>, dim3(T), dim3(64), H * sizeof(float), st, (const bf16*)x, ldx, (const bf16*)res,
+                   ldr, w, (bf16*)y, ldy, (bf16*)h_out, H, eps);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 extern "C" int xft_layernorm(const void* x, int ldx, const float* w, const float* b, void* y, int ldy, int T, int H,
@@ -354,8 +363,8 @@ extern "C" int xft_qkv_rope_cache(const void* qkv, int ldq, int T, int hq, int h
   RopeCacheParams p{(const bf16*)qkv, ldq, T, hq, hkv, D, positions, table, rot, style, rot_off, max_pos, q_scale,
                     q_norm_w, k_norm_w, eps, (bf16*)q_out, kc, vc, ks, vs, int8_cache, bs, nslots, slots, status};
   long long warps = (long long)T * (hq + 2 * hkv);
-  qkv_rope_cache_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, st>>>(p);
-  return (int)cudaGetLastError();
+  cudaError_t e = launch_pdl(qkv_rope_cache_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, st, p);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 extern "C" int xft_rope(void* x, int T, int nh, int D, const int* positions, const float* table, int rot, int style,
@@ -376,6 +385,6 @@ extern "C" int xft_latent_write(const void* latent, int ld, void* cache, int W, 
 
 extern "C" int xft_argmax(const float* logits, int ld, int rows, int V, float* vals, int* idx, cudaStream_t st) {
   if (rows <= 0) return 0;
-  argmax_kernel<1024><<<rows, 1024, 0, st>>>(logits, ld, V, vals, idx);
-  return (int)cudaGetLastError();
+  cudaError_t e = launch_pdl(argmax_kernel<1024>, dim3(rows), dim3(1024), 0, st, logits, ld, V, vals, idx);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }

@@ -27,6 +27,8 @@
 
 namespace xft {
 
+int g_xft_pdl = 1;
+
 // Fused one-shot all-reduce (row-parallel o_proj / down_proj at decode sizes): replaces the reference's
 // GEMM followed by Messenger::reduceAdd (src/layers/decoder_block.h:122-134).  Every rank owns a receive
 // area [2 parities][world slots][T_cap x N] fp32 and a flag area [2][max_tiles][8]; `recv[r]` / `flag[r]`
@@ -127,7 +129,6 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     }
     mbar_init(&tmem_full_bar, 1);
     s_peer_fail = 0;
-    if (p.ar.world > 1) s_epoch = *reinterpret_cast<volatile int*>(p.ar.epoch) + 1;
     fence_barrier_init();
     fence_proxy_async();
     tma_prefetch_desc(&tmW);
@@ -141,6 +142,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = tmem_base_s;
+  grid_dep_launch();          // all CTAs of this grid are (or have been) resident once each has passed here
 
   if (warp == 0) {
     if (lane == 0) {
@@ -148,8 +150,20 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
       // L2; the small activation tile is re-read by every feature tile: keep it
       const uint64_t hint_w = p.t_tiles == 1 ? kEvictFirst : kEvictNormal;
       const uint64_t hint_x = p.n_tiles > 1 ? kEvictLast : kEvictNormal;
-      int it = 0;
-      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+      // Weights never depend on the previous kernel: their first `stages` tiles are requested before the
+      // grid dependency resolves, so the stream from HBM starts while the predecessor drains.
+      const int pre = min(stages, kb1 - kb0);
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+        uint8_t* a = smem + i * STAGE_BYTES;
+        tma_load_2d(a, &tmW, &full_bar[i], (kb0 + i) * 64, tile_n * 128, hint_w);
+        if (DUAL) tma_load_2d(a + A_BYTES, &tmW, &full_bar[i], (kb0 + i) * 64, p.dual_off + tile_n * 128, hint_w);
+      }
+      grid_dep_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(smem + i * STAGE_BYTES + A_BYTES * NACC, &tmX, &full_bar[i], (kb0 + i) * 64, tile_t * BN, hint_x);
+      int it = pre;
+      for (int kb = kb0 + pre; kb < kb1; ++kb, ++it) {
         const int s = it % stages;
         const uint32_t ph = (it / stages) & 1;
         if (!mbar_wait(&empty_bar[s], ph ^ 1, p.status, XFT_ERR_WAIT_EMPTY)) break;
@@ -190,6 +204,8 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     const int n = tile_n * 128 + row;
     const bool n_ok = n < p.N;
     const int et = threadIdx.x - 64;                    // 0..127 among epilogue threads
+    grid_dep_wait();            // scratch, residual and output belong to the stream order from here on
+    if (p.ar.world > 1 && et == 0) s_epoch = *reinterpret_cast<volatile int*>(p.ar.epoch) + 1;
     bool ok = mbar_wait(&tmem_full_bar, 0, p.status, XFT_ERR_WAIT_TMEM);
     tcgen05_fence_after();
     const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16);
@@ -254,6 +270,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
       };
       const bool fused_ar = (!DUAL) && p.ar.world > 1;
       bool peers_ok = true;
+      if (fused_ar) named_bar_sync(1, 128);          // s_epoch was written by epilogue thread 0
       const int epoch = fused_ar ? s_epoch : 0;
       const int par = epoch & 1;
       if (fused_ar) {
@@ -334,6 +351,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
   if (p.ar.world > 1 && threadIdx.x == 0) {
+    grid_dep_wait();
     // last CTA of the launch: the next launch uses the next epoch (and the other buffer parity)
     const int total = gridDim.x * gridDim.y;
     if (atomicAdd(p.ar.done, 1) == total - 1) {
@@ -424,8 +442,8 @@ static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, GemmParam
     attr_set = true;
   }
   dim3 grid(p.n_tiles * p.t_tiles, p.splits);
-  gemm_bf16_kernel<BN, DUAL><<<grid, 192, smem, st>>>(tmW, tmX, p);
-  return (int)cudaGetLastError();
+  cudaError_t e = launch_pdl(gemm_bf16_kernel<BN, DUAL>, grid, dim3(192), smem, st, tmW, tmX, p);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 int pick_bn(int T) {
@@ -520,6 +538,8 @@ static int gemm_bf16_impl(const void* X, int ldx, const void* W, int w_rows, int
 #undef XFT_LAUNCH
   return -1;
 }
+
+extern "C" void xft_set_pdl(int on) { xft::g_xft_pdl = on ? 1 : 0; }
 
 extern "C" int xft_gemm_bf16(const void* X, int ldx, const void* W, int w_rows, int ldw, void* Y, int ldo, int out_fp32,
                              int T, int N, int K, int gated, int dual_off, const float* bias, const void* residual,

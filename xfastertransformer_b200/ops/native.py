@@ -45,6 +45,8 @@ def lib():
         for fn in ("xft_gemm_bf16", "xft_embedding", "xft_rmsnorm", "xft_layernorm", "xft_gated_act",
                    "xft_qkv_rope_cache", "xft_rope", "xft_latent_write", "xft_argmax", "xft_paged_attention"):
             getattr(_LIB, fn).restype = C.c_int
+        # XFT_PDL=0: plain stream order instead of programmatic dependent launch between the kernels
+        _LIB.xft_set_pdl(int(os.environ.get("XFT_PDL", "1") != "0"))
     return _LIB
 
 
