@@ -6,22 +6,26 @@
 // peer's buffer (CUDA IPC) and moves data with plain stores over NVLink from inside the kernel.
 //
 //   xft_comm_alloc / _free / _ipc_handle / _ipc_open / _ipc_close : symmetric buffers
-//   xft_allreduce_oneshot : out = sum_r in_r for small tensors (push to all peers, flag, bounded wait,
-//                           sum in rank order => bit-identical on all ranks)
+//   xft_allreduce_oneshot : out = sum_r in_r (or all-gather) for small tensors: {value, epoch} words pushed to
+//                           all peers, bounded wait per word, sum in rank order => bit-identical on all ranks
 //
 // Every wait is bounded and reports XFT_ERR_WAIT_PEER through the status word instead of spinning.
 #include "ptx.cuh"
 
 namespace xft {
 
+// Low-latency transport: every 8-byte word on the wire is {fp32 value, 32-bit epoch}.  A receiver knows a
+// value has arrived when the epoch next to it equals the epoch of the current call, so no fence, no
+// separate flag and no barrier sit between the producer's store and the consumer's load: the latency of
+// the collective is one NVLink store propagation.  Receive area per rank: [2 parities][world][cap] words;
+// the parity alternates per call (device-side epoch counter), so a slot is rewritten only two calls later,
+// when every rank has long finished reading it.
 struct ArParams {
   int world, rank;
-  float* recv[8];          // rank r's receive area [2][world][cap] as mapped here
-  int* flag[8];            // rank r's flag area   [2][nblocks_cap][8]
-  int* epoch;              // local launch counter
-  int* done;               // local CTA exit counter
-  long long cap;           // floats per slot
-  int flag_parity_stride;
+  unsigned long long* recv[8];   // rank r's receive area as mapped into this process
+  int* epoch;                    // local: completed launches
+  int* done;                     // local: CTAs of the current launch that have exited
+  long long cap;                 // words per source slot
   long long wait_cycles;
   int* status;
 };
@@ -35,55 +39,58 @@ __device__ __forceinline__ T from_f(float v);
 template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
 
-// Each CTA owns a contiguous chunk of the vector: push chunk to all ranks, flag, wait, reduce.
+__device__ __forceinline__ unsigned long long ll_pack(float v, int epoch) {
+  return ((unsigned long long)(unsigned)epoch << 32) | (unsigned long long)__float_as_uint(v);
+}
+// Spin (bounded) until the word carries `epoch`; returns false on time-out.
+__device__ __forceinline__ bool ll_read(const unsigned long long* p, int epoch, long long wait_cycles, float* v) {
+  unsigned long long w = *reinterpret_cast<const volatile unsigned long long*>(p);
+  if ((int)(w >> 32) != epoch) {
+    const long long t0 = clock64();
+    do {
+      if (clock64() - t0 > wait_cycles) return false;
+      w = *reinterpret_cast<const volatile unsigned long long*>(p);
+    } while ((int)(w >> 32) != epoch);
+  }
+  *v = __uint_as_float((unsigned)w);
+  return true;
+}
+
+// out = sum over ranks (gather == 0) or out[r] = rank r's vector (gather != 0).
 template <typename T>
-__global__ void __launch_bounds__(256) allreduce_oneshot_kernel(const T* __restrict__ in, T* __restrict__ out,
-                                                                const float* __restrict__ add_f32, long long n,
-                                                                const ArParams p, const int gather) {
-  __shared__ int s_epoch, s_fail;
+__global__ void __launch_bounds__(256) allreduce_ll_kernel(const T* __restrict__ in, T* __restrict__ out,
+                                                           const float* __restrict__ add_f32, long long n,
+                                                           const ArParams p, const int gather) {
+  __shared__ int s_epoch;
   grid_dep_launch();
   grid_dep_wait();
-  if (threadIdx.x == 0) { s_epoch = *reinterpret_cast<volatile int*>(p.epoch) + 1; s_fail = 0; }
+  if (threadIdx.x == 0) s_epoch = *reinterpret_cast<volatile int*>(p.epoch) + 1;
   __syncthreads();
   const int epoch = s_epoch, par = epoch & 1;
-  const long long per = (n + gridDim.x - 1) / gridDim.x;
-  const long long lo = (long long)blockIdx.x * per, hi = min(n, lo + per);
   const long long pbase = (long long)par * p.world * p.cap;
-  for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (long long i = i0; i < n; i += stride) {
     float v = to_f<T>(in[i]);
     if (add_f32) v += add_f32[i];
-    for (int r = 0; r < p.world; ++r) p.recv[r][pbase + (long long)p.rank * p.cap + i] = v;
+    const unsigned long long w = ll_pack(v, epoch);
+#pragma unroll 8
+    for (int r = 0; r < p.world; ++r) p.recv[r][pbase + (long long)p.rank * p.cap + i] = w;
   }
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x < p.world) {
-    const int r = threadIdx.x;
-    volatile int* f = p.flag[r] + par * p.flag_parity_stride + blockIdx.x * 8 + p.rank;
-    *f = epoch;
-    volatile int* mine = p.flag[p.rank] + par * p.flag_parity_stride + blockIdx.x * 8 + r;
-    const long long t0 = clock64();
-    while (*mine < epoch) {
-      if (clock64() - t0 > p.wait_cycles) {
-        if (p.status) atomicCAS(p.status, 0, XFT_ERR_WAIT_PEER);
-        s_fail = 1;
-        break;
-      }
+  bool ok = true;
+  const unsigned long long* mine = p.recv[p.rank] + pbase;
+  for (long long i = i0; i < n; i += stride) {
+    float x = 0.f;
+    for (int r = 0; r < p.world; ++r) {          // rank order: identical bits on every rank
+      float v;
+      if (!ll_read(mine + (long long)r * p.cap + i, epoch, p.wait_cycles, &v)) { ok = false; break; }
+      if (gather) out[(long long)r * n + i] = from_f<T>(v);
+      else x += v;
     }
-    __threadfence_system();
+    if (!ok) break;
+    if (!gather) out[i] = from_f<T>(x);
   }
-  __syncthreads();
-  if (!s_fail) {
-    const float* mine = p.recv[p.rank] + pbase;
-    for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-      if (gather) {          // all-gather: out[r][i] = rank r's contribution
-        for (int r = 0; r < p.world; ++r) out[(long long)r * n + i] = from_f<T>(__ldcg(mine + (long long)r * p.cap + i));
-      } else {
-        float x = 0.f;       // rank order: identical bits on every rank
-        for (int r = 0; r < p.world; ++r) x += __ldcg(mine + (long long)r * p.cap + i);
-        out[i] = from_f<T>(x);
-      }
-    }
-  }
+  if (!ok && p.status) atomicCAS(p.status, 0, XFT_ERR_WAIT_PEER);
   __syncthreads();
   if (threadIdx.x == 0) {
     if (atomicAdd(p.done, 1) == (int)gridDim.x - 1) {
@@ -119,9 +126,8 @@ extern "C" int xft_comm_ipc_open(const void* handle64, void** ptr) {
 extern "C" int xft_comm_ipc_close(void* ptr) { return (int)cudaIpcCloseMemHandle(ptr); }
 extern "C" int xft_comm_handle_bytes() { return (int)sizeof(cudaIpcMemHandle_t); }
 
-// dtype: 0 = fp32, 1 = bf16.  nblocks <= capacity of the flag area.  add_f32: optional fp32 addend applied
-// to this rank's contribution before the sum (e.g. a residual on one rank).
-// gather != 0: all-gather instead of sum, out is [world, n].
+// dtype: 0 = fp32, 1 = bf16.  add_f32: optional fp32 addend applied to this rank's contribution before the
+// sum.  gather != 0: all-gather instead of sum, out is [world, n].
 extern "C" int xft_allreduce_oneshot(const void* in, void* out, const float* add_f32, long long n, int dtype,
                                      const ArParams* p, int nblocks, int gather, cudaStream_t st) {
   if (!p || p->world < 2 || p->world > 8 || n > p->cap) return -10;
@@ -129,10 +135,10 @@ extern "C" int xft_allreduce_oneshot(const void* in, void* out, const float* add
   if (nblocks < 1) nblocks = 1;
   cudaError_t e;
   if (dtype == 0)
-    e = launch_pdl(allreduce_oneshot_kernel<float>, dim3(nblocks), dim3(256), 0, st, (const float*)in, (float*)out, add_f32,
-                   n, *p, gather);
+    e = launch_pdl(allreduce_ll_kernel<float>, dim3(nblocks), dim3(256), 0, st, (const float*)in, (float*)out, add_f32, n,
+                   *p, gather);
   else
-    e = launch_pdl(allreduce_oneshot_kernel<__nv_bfloat16>, dim3(nblocks), dim3(256), 0, st, (const __nv_bfloat16*)in,
+    e = launch_pdl(allreduce_ll_kernel<__nv_bfloat16>, dim3(nblocks), dim3(256), 0, st, (const __nv_bfloat16*)in,
                    (__nv_bfloat16*)out, add_f32, n, *p, gather);
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }

@@ -30,23 +30,22 @@ namespace xft {
 int g_xft_pdl = 1;
 
 // Fused one-shot all-reduce (row-parallel o_proj / down_proj at decode sizes): replaces the reference's
-// GEMM followed by Messenger::reduceAdd (src/layers/decoder_block.h:122-134).  Every rank owns a receive
-// area [2 parities][world slots][T_cap x N] fp32 and a flag area [2][max_tiles][8]; `recv[r]` / `flag[r]`
-// are rank r's areas as mapped into this process (CUDA IPC over NVLink).  The CTA that finishes an output
-// tile pushes its partial tile into slot `rank` of every peer, raises the tile's flag there with the
-// call's epoch, waits (bounded) for the same tile from every peer, and sums the slots in rank order, so
-// all ranks produce bit-identical results.  The epoch is a device-side counter bumped by the last CTA of
-// each launch, which keeps the scheme valid under CUDA-graph replay.
+// GEMM followed by Messenger::reduceAdd (src/layers/decoder_block.h:122-134).  `recv[r]` is rank r's
+// receive area [2 parities][world slots][slot words] as mapped into this process (CUDA IPC over NVLink);
+// each word is {fp32 value, epoch}.  The CTA that finishes an output tile stores its partial tile into
+// slot `rank` of every rank straight from the accumulator, then reads the world slots of its own area,
+// spinning (bounded) on each word until its epoch matches, and sums them in rank order, so all ranks
+// produce bit-identical results.  No fence, flag or barrier separates a producer's store from the
+// consumer's load.  The epoch is a device-side counter bumped by the last CTA of each launch, which keeps
+// the scheme valid under CUDA-graph replay; the parity (epoch & 1) double-buffers the area.
 struct CommParams {
   int world, rank;
-  float* recv[8];
-  int* flag[8];
+  unsigned long long* recv[8];
   int* epoch;              // local: number of completed fused launches
   int* done;               // local: CTAs of the current launch that have exited
-  long long slot_stride;   // floats per source slot
-  long long parity_stride; // floats per parity (= world * slot_stride)
-  int flag_parity_stride;  // ints per parity
-  long long wait_cycles;   // bound of the peer wait
+  long long slot_stride;   // words per source slot
+  long long parity_stride; // words per parity (= world * slot_stride)
+  long long wait_cycles;   // bound of the wait on a peer's word
 };
 
 struct GemmParams {
@@ -273,65 +272,67 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
       if (fused_ar) named_bar_sync(1, 128);          // s_epoch was written by epilogue thread 0
       const int epoch = fused_ar ? s_epoch : 0;
       const int par = epoch & 1;
-      if (fused_ar) {
-        // phase 1: push this rank's partial tile into slot `rank` of every rank (its own included)
-        if (ok) {
-#pragma unroll 1
-          for (int c = 0; c < BN; c += 16) {
-            float g[16], u[16];
-            load_acc(c, g, u);
-            if (n_ok) {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const int t = t0 + c + j;
-                if (t < p.T) {
-                  const float v = g[j] * rs;
-                  const long long off = par * p.ar.parity_stride + p.ar.rank * p.ar.slot_stride + (long long)t * p.N + n;
-                  for (int r = 0; r < p.ar.world; ++r) p.ar.recv[r][off] = v;
-                }
-              }
-            }
-          }
-        }
-        __threadfence_system();
-        named_bar_sync(1, 128);
-        // phase 2: raise the tile's flag on every rank; phase 3: wait for every rank's flag here
-        if (et < p.ar.world) {
-          volatile int* f = p.ar.flag[et] + par * p.ar.flag_parity_stride + tile_id * 8 + p.ar.rank;
-          *f = epoch;
-          volatile int* mine = p.ar.flag[p.ar.rank] + par * p.ar.flag_parity_stride + tile_id * 8 + et;
-          const long long tstart = clock64();
-          while (*mine < epoch) {
-            if (clock64() - tstart > p.ar.wait_cycles) {
-              if (p.status) atomicCAS(p.status, 0, XFT_ERR_WAIT_PEER);
-              s_peer_fail = 1;
-              break;
-            }
-          }
-          __threadfence_system();
-        }
-        named_bar_sync(1, 128);
-        peers_ok = s_peer_fail == 0;
-      }
-      if (ok && peers_ok) {
-        const float* my_recv = fused_ar ? p.ar.recv[p.ar.rank] + par * p.ar.parity_stride : nullptr;
+      if (fused_ar && ok) {
+        // push this rank's partial tile, tagged with the epoch, into slot `rank` of every rank (its own included)
 #pragma unroll 1
         for (int c = 0; c < BN; c += 16) {
           float g[16], u[16];
-          if (!fused_ar) load_acc(c, g, u);
+          load_acc(c, g, u);
           if (n_ok) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int t = t0 + c + j;
               if (t < p.T) {
-                float x;
-                if (fused_ar) {
-                  x = 0.f;                      // rank order: identical bits on every rank
-                  for (int r = 0; r < p.ar.world; ++r) x += __ldcg(my_recv + r * p.ar.slot_stride + (long long)t * p.N + n);
-                  x += bias_g;
-                } else {
-                  x = g[j] * rs + bias_g;
+                const unsigned long long w =
+                    ((unsigned long long)(unsigned)epoch << 32) | (unsigned long long)__float_as_uint(g[j] * rs);
+                const long long off = par * p.ar.parity_stride + p.ar.rank * p.ar.slot_stride + (long long)t * p.N + n;
+                for (int r = 0; r < p.ar.world; ++r) p.ar.recv[r][off] = w;
+              }
+            }
+          }
+        }
+      }
+      if (ok) {
+        const unsigned long long* my_recv = fused_ar ? p.ar.recv[p.ar.rank] + par * p.ar.parity_stride : nullptr;
+#pragma unroll 1
+        for (int c = 0; c < BN && peers_ok; c += 16) {
+          float g[16], u[16];
+          if (!fused_ar) {
+            load_acc(c, g, u);
+          } else {
+            // Sum the world slots in rank order.  All 16 words of a rank are requested before any is
+            // examined, so the L2 round trips overlap; only words that have not arrived yet are re-polled.
+#pragma unroll
+            for (int j = 0; j < 16; ++j) g[j] = 0.f;
+            for (int r = 0; r < p.ar.world && peers_ok; ++r) {
+              const volatile unsigned long long* base = my_recv + r * p.ar.slot_stride + n;
+              unsigned long long w[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int t = t0 + c + j;
+                w[j] = (n_ok && t < p.T) ? base[(long long)t * p.N] : ((unsigned long long)(unsigned)epoch << 32);
+              }
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if ((int)(w[j] >> 32) != epoch) {
+                  const int t = t0 + c + j;
+                  const long long tstart = clock64();
+                  do {
+                    if (clock64() - tstart > p.ar.wait_cycles) { peers_ok = false; break; }
+                    w[j] = base[(long long)t * p.N];
+                  } while ((int)(w[j] >> 32) != epoch);
                 }
+                g[j] += __uint_as_float((unsigned)w[j]);
+              }
+            }
+            if (!peers_ok) { if (p.status) atomicCAS(p.status, 0, XFT_ERR_WAIT_PEER); break; }
+          }
+          if (n_ok) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int t = t0 + c + j;
+              if (t < p.T) {
+                float x = fused_ar ? g[j] + bias_g : g[j] * rs + bias_g;
                 x = apply_act(x, p.act);
                 if (DUAL) x *= (u[j] * rs + bias_u);
                 if (p.residual) x += p.res_scale * __bfloat162float(p.residual[(size_t)t * p.ldr + n]);

@@ -4,13 +4,14 @@ the kernels that use them (fused GEMM + one-shot all-reduce, stand-alone one-sho
 The reference reduces the partial o_proj / down_proj outputs with a separate collective after the
 GEMM (``src/layers/decoder_block.h:122-134`` -> ``Messenger::reduceAdd`` -> oneCCL or the
 shared-memory chain of ``src/utils/shm_ccl.cpp:82-145``).  Here, at decode sizes, the GEMM's epilogue
-pushes each finished output tile straight into every peer's receive slot over NVLink, raises a per-tile
-flag, waits (bounded) for the peers' tiles and sums them in rank order — one kernel, no separate
+pushes each finished output tile straight into every peer's receive slot over NVLink, waits (bounded) for
+the peers' words and sums them in rank order — one kernel, no separate
 collective, bit-identical results on all ranks.  Larger token counts fall back to NCCL.
 
-Buffers per rank (allocated once, mapped by every peer):
-  recv  : [2 parities][world][T_CAP x N_MAX] fp32    flag : [2][MAX_TILES][8] int32
-A device-side epoch (bumped by the last CTA of every launch) selects the parity, so CUDA-graph
+Buffer per rank (allocated once, mapped by every peer): recv [2 parities][world][T_CAP x N_MAX] 8-byte
+words, each {fp32 value, epoch}.  The epoch next to a value tells the reader it has arrived, so the
+latency of the collective is one NVLink store propagation: no fence, flag or barrier in between.  A
+device-side epoch counter (bumped by the last CTA of every launch) selects the parity, so CUDA-graph
 replays stay in step without host involvement.
 """
 from __future__ import annotations
@@ -25,15 +26,14 @@ from ..ops import native as N
 
 
 class CommParams(C.Structure):
-    _fields_ = [("world", C.c_int), ("rank", C.c_int), ("recv", C.c_void_p * 8), ("flag", C.c_void_p * 8),
-                ("epoch", C.c_void_p), ("done", C.c_void_p), ("slot_stride", C.c_longlong),
-                ("parity_stride", C.c_longlong), ("flag_parity_stride", C.c_int), ("wait_cycles", C.c_longlong)]
+    _fields_ = [("world", C.c_int), ("rank", C.c_int), ("recv", C.c_void_p * 8), ("epoch", C.c_void_p),
+                ("done", C.c_void_p), ("slot_stride", C.c_longlong), ("parity_stride", C.c_longlong),
+                ("wait_cycles", C.c_longlong)]
 
 
 class ArParams(C.Structure):
-    _fields_ = [("world", C.c_int), ("rank", C.c_int), ("recv", C.c_void_p * 8), ("flag", C.c_void_p * 8),
-                ("epoch", C.c_void_p), ("done", C.c_void_p), ("cap", C.c_longlong), ("flag_parity_stride", C.c_int),
-                ("wait_cycles", C.c_longlong), ("status", C.c_void_p)]
+    _fields_ = [("world", C.c_int), ("rank", C.c_int), ("recv", C.c_void_p * 8), ("epoch", C.c_void_p),
+                ("done", C.c_void_p), ("cap", C.c_longlong), ("wait_cycles", C.c_longlong), ("status", C.c_void_p)]
 
 
 class PeerComm:
@@ -50,10 +50,8 @@ class PeerComm:
                    "xft_comm_handle_bytes", "xft_gemm_bf16_ar", "xft_allreduce_oneshot"):
             getattr(lib, fn).restype = C.c_int
         self.lib = lib
-        self.slot = self.T_CAP * n_max                           # floats per source slot
-        self.recv_floats = 2 * self.world * self.slot
-        self.flag_ints = 2 * self.MAX_TILES * 8
-        nbytes = self.recv_floats * 4 + self.flag_ints * 4
+        self.slot = self.T_CAP * n_max                           # {value, epoch} words per source slot
+        nbytes = 2 * self.world * self.slot * 8
         self.nbytes = nbytes
         base = C.c_void_p()
         N._check(lib.xft_comm_alloc(C.c_size_t(nbytes), C.byref(base)), "comm_alloc")
@@ -86,10 +84,8 @@ class PeerComm:
             prm.world, prm.rank = self.world, self.rank
             for r in range(self.world):
                 prm.recv[r] = self.peer_base[r]
-                prm.flag[r] = self.peer_base[r] + self.recv_floats * 4
             prm.epoch = self.counters.data_ptr()
             prm.done = self.counters.data_ptr() + 4
-            prm.flag_parity_stride = self.MAX_TILES * 8
             prm.wait_cycles = self.wait_cycles
         self.gp.slot_stride = self.slot
         self.gp.parity_stride = self.world * self.slot
@@ -123,31 +119,26 @@ class PeerComm:
         self.fused_calls += 1
         return out.view(*x.shape[:-1], n)
 
-    def all_reduce(self, t: torch.Tensor, add_f32: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Out-of-place one-shot sum of a small fp32/bf16 tensor (numel <= slot capacity)."""
-        assert t.is_contiguous() and t.numel() <= self.slot and t.dtype in (torch.float32, torch.bfloat16)
-        out = torch.empty_like(t)
+    def _collective(self, t: torch.Tensor, out: torch.Tensor, add_f32, gather: int) -> torch.Tensor:
         n = t.numel()
-        nblocks = max(1, min(self.MAX_TILES, (n + 4095) // 4096))
+        nblocks = max(1, min(296, (n + 1023) // 1024))
         rc = self.lib.xft_allreduce_oneshot(N._p(t), N._p(out), N._p(add_f32), C.c_longlong(n),
-                                            0 if t.dtype == torch.float32 else 1, C.byref(self.ap), nblocks, 0,
+                                            0 if t.dtype == torch.float32 else 1, C.byref(self.ap), nblocks, gather,
                                             N._stream())
         N._check(rc, "allreduce_oneshot")
         N.Workspace.get(t.device).launches += 1
         return out
 
+    def all_reduce(self, t: torch.Tensor, add_f32: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Out-of-place one-shot sum of a small fp32/bf16 tensor (numel <= slot capacity)."""
+        assert t.is_contiguous() and t.numel() <= self.slot and t.dtype in (torch.float32, torch.bfloat16)
+        return self._collective(t, torch.empty_like(t), add_f32, 0)
+
     def all_gather(self, t: torch.Tensor) -> torch.Tensor:
-        """[world, *t.shape] of a small fp32/bf16 tensor, through the same push/flag/wait kernel."""
+        """[world, *t.shape] of a small fp32/bf16 tensor, through the same kernel."""
         assert t.is_contiguous() and t.numel() <= self.slot and t.dtype in (torch.float32, torch.bfloat16)
         out = torch.empty((self.world,) + tuple(t.shape), dtype=t.dtype, device=t.device)
-        n = t.numel()
-        nblocks = max(1, min(self.MAX_TILES, (n + 4095) // 4096))
-        rc = self.lib.xft_allreduce_oneshot(N._p(t), N._p(out), N._p(None), C.c_longlong(n),
-                                            0 if t.dtype == torch.float32 else 1, C.byref(self.ap), nblocks, 1,
-                                            N._stream())
-        N._check(rc, "allgather_oneshot")
-        N.Workspace.get(t.device).launches += 1
-        return out
+        return self._collective(t, out, None, 1)
 
     def close(self) -> None:
         for p in self._opened:

@@ -26,6 +26,10 @@ PRESETS: Dict[str, dict] = {
                        size_per_head=128, inter_size=11008, vocab_size=32000, max_pos_seq_len=4096),
     "llama-2-70b": dict(model_type="llama", num_layer=80, hidden_size=8192, head_num=64, kv_head_num=8,
                         size_per_head=128, inter_size=28672, vocab_size=32000, max_pos_seq_len=4096),
+    # one tensor-parallel rank's share of Llama-2-70B at TP=8 (8 q heads + 1 kv head, FFN slice 3584, vocab slice
+    # 4000) as a stand-alone model: isolates per-GPU kernel time from communication when profiling on one GPU
+    "llama-2-70b-tp8-slice": dict(model_type="llama", num_layer=80, hidden_size=8192, head_num=8, kv_head_num=1,
+                                  size_per_head=128, inter_size=3584, vocab_size=4000, max_pos_seq_len=4096),
     "mixtral-8x7b": dict(model_type="mixtral", num_layer=32, hidden_size=4096, head_num=32, kv_head_num=8,
                          size_per_head=128, inter_size=14336, vocab_size=32000, max_pos_seq_len=32768,
                          sparse_experts=8, num_experts_per_tok=2, rope=RopeConfig(theta=1e6)),
