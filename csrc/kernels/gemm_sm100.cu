@@ -46,6 +46,12 @@ struct CommParams {
   long long slot_stride;   // words per source slot
   long long parity_stride; // words per parity (= world * slot_stride)
   long long wait_cycles;   // bound of the wait on a peer's word
+  // two_shot != 0 (used for world >= 4): tile i is owned by rank i % world.  Partials go only to the owner
+  // (reduce-scatter), which sums them, applies the epilogue and stores the finished value into `result`
+  // of every rank (all-gather); the other ranks wait for that word.  Traffic per rank falls from
+  // (world-1) x tile to about 2 x (world-1)/world x tile for one extra NVLink hop.
+  int two_shot;
+  unsigned long long* result[8];   // rank r's result area [2 parities][slot words]
 };
 
 struct GemmParams {
@@ -272,6 +278,9 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
       if (fused_ar) named_bar_sync(1, 128);          // s_epoch was written by epilogue thread 0
       const int epoch = fused_ar ? s_epoch : 0;
       const int par = epoch & 1;
+      const bool two_shot = fused_ar && p.ar.two_shot;
+      const int owner = two_shot ? tile_id % p.ar.world : p.ar.rank;
+      const bool i_reduce = !two_shot || owner == p.ar.rank;
       if (fused_ar && ok) {
         // push this rank's partial tile, tagged with the epoch, into slot `rank` of every rank (its own included)
 #pragma unroll 1
@@ -286,7 +295,8 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                 const unsigned long long w =
                     ((unsigned long long)(unsigned)epoch << 32) | (unsigned long long)__float_as_uint(g[j] * rs);
                 const long long off = par * p.ar.parity_stride + p.ar.rank * p.ar.slot_stride + (long long)t * p.N + n;
-                for (int r = 0; r < p.ar.world; ++r) p.ar.recv[r][off] = w;
+                if (two_shot) p.ar.recv[owner][off] = w;
+                else for (int r = 0; r < p.ar.world; ++r) p.ar.recv[r][off] = w;
               }
             }
           }
@@ -299,6 +309,28 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
           float g[16], u[16];
           if (!fused_ar) {
             load_acc(c, g, u);
+          } else if (!i_reduce) {
+            // two-shot, not the owner: the finished values arrive in this rank's result area
+            const volatile unsigned long long* base = p.ar.result[p.ar.rank] + par * p.ar.slot_stride + n;
+            unsigned long long w[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int t = t0 + c + j;
+              w[j] = (n_ok && t < p.T) ? base[(long long)t * p.N] : ((unsigned long long)(unsigned)epoch << 32);
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if ((int)(w[j] >> 32) != epoch) {
+                const int t = t0 + c + j;
+                const long long tstart = clock64();
+                do {
+                  if (clock64() - tstart > p.ar.wait_cycles) { peers_ok = false; break; }
+                  w[j] = base[(long long)t * p.N];
+                } while ((int)(w[j] >> 32) != epoch);
+              }
+              g[j] = __uint_as_float((unsigned)w[j]);
+            }
+            if (!peers_ok) { if (p.status) atomicCAS(p.status, 0, XFT_ERR_WAIT_PEER); break; }
           } else {
             // Sum the world slots in rank order.  All 16 words of a rank are requested before any is
             // examined, so the L2 round trips overlap; only words that have not arrived yet are re-polled.
@@ -332,10 +364,21 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
             for (int j = 0; j < 16; ++j) {
               const int t = t0 + c + j;
               if (t < p.T) {
-                float x = fused_ar ? g[j] + bias_g : g[j] * rs + bias_g;
-                x = apply_act(x, p.act);
-                if (DUAL) x *= (u[j] * rs + bias_u);
-                if (p.residual) x += p.res_scale * __bfloat162float(p.residual[(size_t)t * p.ldr + n]);
+                float x;
+                if (fused_ar && !i_reduce) {
+                  x = g[j];                     // finished by the owner
+                } else {
+                  x = fused_ar ? g[j] + bias_g : g[j] * rs + bias_g;
+                  x = apply_act(x, p.act);
+                  if (DUAL) x *= (u[j] * rs + bias_u);
+                  if (p.residual) x += p.res_scale * __bfloat162float(p.residual[(size_t)t * p.ldr + n]);
+                  if (two_shot) {
+                    const unsigned long long w = ((unsigned long long)(unsigned)epoch << 32) | (unsigned long long)__float_as_uint(x);
+                    const long long off = par * p.ar.slot_stride + (long long)t * p.N + n;
+                    for (int r = 0; r < p.ar.world; ++r)
+                      if (r != p.ar.rank) p.ar.result[r][off] = w;
+                  }
+                }
                 if (p.out_fp32) reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + n] = x;
                 else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)t * p.ldo + n] = __float2bfloat16(x);
               }

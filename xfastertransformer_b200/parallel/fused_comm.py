@@ -28,7 +28,7 @@ from ..ops import native as N
 class CommParams(C.Structure):
     _fields_ = [("world", C.c_int), ("rank", C.c_int), ("recv", C.c_void_p * 8), ("epoch", C.c_void_p),
                 ("done", C.c_void_p), ("slot_stride", C.c_longlong), ("parity_stride", C.c_longlong),
-                ("wait_cycles", C.c_longlong)]
+                ("wait_cycles", C.c_longlong), ("two_shot", C.c_int), ("result", C.c_void_p * 8)]
 
 
 class ArParams(C.Structure):
@@ -51,7 +51,8 @@ class PeerComm:
             getattr(lib, fn).restype = C.c_int
         self.lib = lib
         self.slot = self.T_CAP * n_max                           # {value, epoch} words per source slot
-        nbytes = 2 * self.world * self.slot * 8
+        self.recv_bytes = 2 * self.world * self.slot * 8
+        nbytes = self.recv_bytes + 2 * self.slot * 8           # + result area of the two-shot mode
         self.nbytes = nbytes
         base = C.c_void_p()
         N._check(lib.xft_comm_alloc(C.c_size_t(nbytes), C.byref(base)), "comm_alloc")
@@ -87,6 +88,12 @@ class PeerComm:
             prm.epoch = self.counters.data_ptr()
             prm.done = self.counters.data_ptr() + 4
             prm.wait_cycles = self.wait_cycles
+        for r in range(self.world):
+            self.gp.result[r] = self.peer_base[r] + self.recv_bytes
+        # reduce-scatter + all-gather inside the epilogue pays off from 4 ranks on (XFT_AR_TWO_SHOT overrides)
+        import os
+        ts = os.environ.get("XFT_AR_TWO_SHOT")
+        self.gp.two_shot = int(ts) if ts is not None else int(self.world >= 4)
         self.gp.slot_stride = self.slot
         self.gp.parity_stride = self.world * self.slot
         self.ap.cap = self.slot
