@@ -72,6 +72,12 @@ struct GemmParams {
   int n_tiles, t_tiles, stages;
   const float* row_scale;  // optional per-output-feature scale applied to the accumulator (weight-only int8)
   CommParams ar;           // ar.world > 1: the epilogue all-reduces the tile over peer memory
+  // Grouped mode (MoE experts): token tile i is described by group_tiles[i] = {group, first row, rows, -};
+  // the weight rows of group g start at g * group_w_rows.  num_group_tiles[0] tiles are valid; CTAs past it idle.
+  const int4* group_tiles;
+  const int* num_group_tiles;
+  int group_w_rows;
+  const float* col_scale;  // optional per-token factor applied to the result (routing weight)
 };
 
 __device__ __forceinline__ float apply_act(float x, int act) {
@@ -148,6 +154,21 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
   tcgen05_fence_after();
   const uint32_t tmem_base = tmem_base_s;
   grid_dep_launch();          // all CTAs of this grid are (or have been) resident once each has passed here
+  __shared__ int s_group[4];
+  const bool grouped = p.group_tiles != nullptr;
+  if (grouped) {
+    grid_dep_wait();          // the tile table is produced by the routing plan kernel
+    if (threadIdx.x == 0) {
+      int4 e = make_int4(0, 0, 0, 0);
+      if (tile_t < *p.num_group_tiles) e = p.group_tiles[tile_t];
+      s_group[0] = e.x; s_group[1] = e.y; s_group[2] = e.z;
+    }
+    __syncthreads();
+  }
+  const int w_row0 = grouped ? s_group[0] * p.group_w_rows : 0;      // first weight row of this tile's group
+  const int x_row0 = grouped ? s_group[1] : tile_t * BN;            // first token row of this tile
+  const int x_rows = grouped ? s_group[2] : BN;                     // valid token rows in this tile
+  const bool active = !grouped || x_rows > 0;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -157,30 +178,31 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
       const uint64_t hint_x = p.n_tiles > 1 ? kEvictLast : kEvictNormal;
       // Weights never depend on the previous kernel: their first `stages` tiles are requested before the
       // grid dependency resolves, so the stream from HBM starts while the predecessor drains.
-      const int pre = min(stages, kb1 - kb0);
+      const int kend = active ? kb1 : kb0;
+      const int pre = min(stages, kend - kb0);
       for (int i = 0; i < pre; ++i) {
         mbar_expect_tx(&full_bar[i], STAGE_BYTES);
         uint8_t* a = smem + i * STAGE_BYTES;
-        tma_load_2d(a, &tmW, &full_bar[i], (kb0 + i) * 64, tile_n * 128, hint_w);
-        if (DUAL) tma_load_2d(a + A_BYTES, &tmW, &full_bar[i], (kb0 + i) * 64, p.dual_off + tile_n * 128, hint_w);
+        tma_load_2d(a, &tmW, &full_bar[i], (kb0 + i) * 64, w_row0 + tile_n * 128, hint_w);
+        if (DUAL) tma_load_2d(a + A_BYTES, &tmW, &full_bar[i], (kb0 + i) * 64, w_row0 + p.dual_off + tile_n * 128, hint_w);
       }
       grid_dep_wait();
       for (int i = 0; i < pre; ++i)
-        tma_load_2d(smem + i * STAGE_BYTES + A_BYTES * NACC, &tmX, &full_bar[i], (kb0 + i) * 64, tile_t * BN, hint_x);
+        tma_load_2d(smem + i * STAGE_BYTES + A_BYTES * NACC, &tmX, &full_bar[i], (kb0 + i) * 64, x_row0, hint_x);
       int it = pre;
-      for (int kb = kb0 + pre; kb < kb1; ++kb, ++it) {
+      for (int kb = kb0 + pre; kb < kend; ++kb, ++it) {
         const int s = it % stages;
         const uint32_t ph = (it / stages) & 1;
         if (!mbar_wait(&empty_bar[s], ph ^ 1, p.status, XFT_ERR_WAIT_EMPTY)) break;
         mbar_expect_tx(&full_bar[s], STAGE_BYTES);
         uint8_t* a = smem + s * STAGE_BYTES;
-        tma_load_2d(a, &tmW, &full_bar[s], kb * 64, tile_n * 128, hint_w);
-        if (DUAL) tma_load_2d(a + A_BYTES, &tmW, &full_bar[s], kb * 64, p.dual_off + tile_n * 128, hint_w);
-        tma_load_2d(a + A_BYTES * NACC, &tmX, &full_bar[s], kb * 64, tile_t * BN, hint_x);
+        tma_load_2d(a, &tmW, &full_bar[s], kb * 64, w_row0 + tile_n * 128, hint_w);
+        if (DUAL) tma_load_2d(a + A_BYTES, &tmW, &full_bar[s], kb * 64, w_row0 + p.dual_off + tile_n * 128, hint_w);
+        tma_load_2d(a + A_BYTES * NACC, &tmX, &full_bar[s], kb * 64, x_row0, hint_x);
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (lane == 0 && active) {
       int it = 0;
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % stages;
@@ -211,10 +233,10 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     const int et = threadIdx.x - 64;                    // 0..127 among epilogue threads
     grid_dep_wait();            // scratch, residual and output belong to the stream order from here on
     if (p.ar.world > 1 && et == 0) s_epoch = *reinterpret_cast<volatile int*>(p.ar.epoch) + 1;
-    bool ok = mbar_wait(&tmem_full_bar, 0, p.status, XFT_ERR_WAIT_TMEM);
+    bool ok = active && mbar_wait(&tmem_full_bar, 0, p.status, XFT_ERR_WAIT_TMEM);
     tcgen05_fence_after();
     const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16);
-    const int t0 = tile_t * BN;
+    const int t0 = x_row0;
     bool last = true;
     if (p.splits > 1) {
       // publish this split's partial tile
@@ -363,7 +385,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int t = t0 + c + j;
-              if (t < p.T) {
+              if (t < p.T && c + j < x_rows) {
                 float x;
                 if (fused_ar && !i_reduce) {
                   x = g[j];                     // finished by the owner
@@ -371,6 +393,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                   x = fused_ar ? g[j] + bias_g : g[j] * rs + bias_g;
                   x = apply_act(x, p.act);
                   if (DUAL) x *= (u[j] * rs + bias_u);
+                  if (p.col_scale) x *= p.col_scale[t];
                   if (p.residual) x += p.res_scale * __bfloat162float(p.residual[(size_t)t * p.ldr + n]);
                   if (two_shot) {
                     const unsigned long long w = ((unsigned long long)(unsigned)epoch << 32) | (unsigned long long)__float_as_uint(x);
@@ -591,6 +614,41 @@ extern "C" int xft_gemm_bf16(const void* X, int ldx, const void* W, int w_rows, 
                              int* counters, int n_counters, int* status, int force_splits, cudaStream_t st) {
   return gemm_bf16_impl(X, ldx, W, w_rows, ldw, Y, ldo, out_fp32, T, N, K, gated, dual_off, bias, residual, ldr, res_scale,
                         act, row_scale, ws, ws_bytes, counters, n_counters, status, force_splits, nullptr, st);
+}
+
+// Grouped GEMM over token rows sorted by group (MoE experts): W is [groups * group_w_rows, K]; token tile i of
+// size `bn` (16..128, chosen by the caller and used to build the table) is group_tiles[i] = {group, row0, rows, 0}.
+// gated != 0: each group's rows are gate [0,N) then up [dual_off, dual_off+N).  col_scale: per-row factor.
+extern "C" int xft_gemm_bf16_grouped(const void* X, int ldx, int x_rows, const void* W, int w_rows, int ldw, void* Y,
+                                     int ldo, int out_fp32, int N, int K, int gated, int dual_off, int group_w_rows,
+                                     const void* group_tiles, const int* num_group_tiles, int max_tiles, int bn,
+                                     const float* col_scale, int act, int* status, cudaStream_t st) {
+  if (x_rows <= 0 || N <= 0 || K <= 0 || max_tiles <= 0) return 0;
+  GemmParams p{};
+  p.N = N; p.T = x_rows; p.K = K; p.dual_off = dual_off; p.out = Y; p.ldo = ldo; p.out_fp32 = out_fp32;
+  p.res_scale = 1.f; p.act = act; p.status = status;
+  p.group_tiles = reinterpret_cast<const int4*>(group_tiles); p.num_group_tiles = num_group_tiles;
+  p.group_w_rows = group_w_rows; p.col_scale = col_scale;
+  p.n_tiles = (N + 127) / 128;
+  p.t_tiles = max_tiles;
+  p.num_kb = (K + 63) / 64;
+  p.splits = 1; p.kb_per_split = p.num_kb;
+  CUtensorMap tmW, tmX;
+  int r = make_tensor_map(&tmW, W, (uint64_t)w_rows, (uint64_t)K, (uint64_t)ldw, 128, 2);
+  if (r) return 1000 - r;
+  r = make_tensor_map(&tmX, X, (uint64_t)x_rows, (uint64_t)K, (uint64_t)ldx, (uint32_t)bn, 2);
+  if (r) return 2000 - r;
+#define XFT_LAUNCH(BN_)                                                        \
+  case BN_:                                                                    \
+    return gated ? launch_gemm<BN_, true>(tmW, tmX, p, st) : launch_gemm<BN_, false>(tmW, tmX, p, st);
+  switch (bn) {
+    XFT_LAUNCH(16)
+    XFT_LAUNCH(32)
+    XFT_LAUNCH(64)
+    XFT_LAUNCH(128)
+  }
+#undef XFT_LAUNCH
+  return -1;
 }
 
 // Row-parallel GEMM fused with the tensor-parallel sum: Y = act(sum_r X_r W_r^T + bias) + res_scale*residual

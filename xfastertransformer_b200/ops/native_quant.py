@@ -1,0 +1,119 @@
+"""Bindings of the quantised GEMM kernels (csrc/kernels/quant_gemm_sm100.cu): weight-only int8 / uint4 / nf4 /
+fp8-e4m3 dequant-GEMM and W8A8 (dynamic int8 activations x int8 weights on the int8 tensor path)."""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import native as N
+
+_QT = {"int8": 0, "int4": 1, "nf4": 2, "fp8": 3}
+_ready = False
+
+
+def _lib():
+    global _ready
+    lib = N.lib()
+    if not _ready:
+        for fn in ("xft_qgemm", "xft_quant_act", "xft_row_sum", "xft_w8a8_gemm"):
+            getattr(lib, fn).restype = C.c_int
+        _ready = True
+    return lib
+
+
+def _row_sums(x2, ldx):
+    T, K = x2.shape
+    out = torch.empty(T, dtype=torch.float32, device=x2.device)
+    N._check(_lib().xft_row_sum(N._p(x2), ldx, N._p(out), T, K, N._stream()), "row_sum")
+    N.Workspace.get(x2.device).launches += 1
+    return out
+
+
+def _qgemm(x, W, n_out, gated, bias, act, residual, res_scale, out_dtype):
+    x2, ldx = N._rows2d(x)
+    T, K = x2.shape
+    if K % 8:
+        raise N.KernelError(f"quantised GEMM needs K % 8 == 0 (got {K})")
+    fp32 = out_dtype == torch.float32
+    out = torch.empty(T, n_out, dtype=torch.float32 if fp32 else torch.bfloat16, device=x.device)
+    ws = N.Workspace.get(x.device)
+    zero = W.zero if (W.zero is not None and W.kind != "nf4") else None
+    xsum = _row_sums(x2, ldx) if zero is not None else None
+    r2, ldr = (None, 0)
+    if residual is not None:
+        r2 = residual.reshape(-1, residual.shape[-1])
+        ldr = r2.stride(0)
+    w = W.w if W.w.dtype != torch.float8_e4m3fn else W.w.view(torch.uint8)
+    if (w.stride(0) * w.element_size()) % 16:
+        # TMA rows must start on 16-byte boundaries: keep a copy whose row pitch is padded (zero codes past K
+        # multiply zero-filled activations, so they add nothing)
+        wp = W.cache.get("w_pitch16")
+        if wp is None:
+            cols = w.shape[1]
+            pad = (-cols * w.element_size()) % 16 // w.element_size()
+            wp = torch.nn.functional.pad(w, (0, pad)).contiguous()[:, :cols]
+            W.cache["w_pitch16"] = wp
+        w = wp
+    scale_ld = W.scale.shape[1] if W.kind == "fp8" else 0
+    rc = _lib().xft_qgemm(N._p(x2), ldx, N._p(w), w.shape[0], w.stride(0) * w.element_size(), _QT[W.kind], N._p(out),
+                          out.stride(0), int(fp32), T, n_out, K, int(gated), n_out if gated else 0, N._p(W.scale),
+                          N._p(zero), N._p(xsum), scale_ld, N._p(bias), N._p(r2), ldr, C.c_float(res_scale),
+                          N._ACT[act], N._p(ws.ws), C.c_size_t(ws.ws_bytes), N._p(ws.counters), ws.n_counters,
+                          N._p(ws.status), N._stream())
+    N._check(rc, f"qgemm[{W.kind}]")
+    ws.launches += 1
+    return out
+
+
+def quant_act(x2, ldx):
+    """bf16 [T,K] -> (int8 [T,K], scale[T], zero[T], qsum[T]) per-row dynamic asymmetric."""
+    T, K = x2.shape
+    q = torch.empty(T, K, dtype=torch.int8, device=x2.device)
+    s = torch.empty(3, T, dtype=torch.float32, device=x2.device)
+    N._check(_lib().xft_quant_act(N._p(x2), ldx, N._p(q), K, N._p(s[0]), N._p(s[1]), N._p(s[2]), T, K, N._stream()),
+             "quant_act")
+    N.Workspace.get(x2.device).launches += 1
+    return q, s[0], s[1], s[2]
+
+
+def _w8a8(x, W, rows, bias, act, residual, res_scale, out_dtype, row0=0):
+    x2, ldx = N._rows2d(x)
+    T, K = x2.shape
+    q, sa, za, qs = quant_act(x2, ldx)
+    fp32 = out_dtype == torch.float32
+    out = torch.empty(T, rows, dtype=torch.float32 if fp32 else torch.bfloat16, device=x.device)
+    ws = N.Workspace.get(x.device)
+    r2, ldr = (None, 0)
+    if residual is not None:
+        r2 = residual.reshape(-1, residual.shape[-1])
+        ldr = r2.stride(0)
+    w = W.w[row0:row0 + rows]
+    sl = slice(row0, row0 + rows)
+    rc = _lib().xft_w8a8_gemm(N._p(q), K, N._p(w), W.w.stride(0), N._p(out), out.stride(0), int(fp32), T, rows, K,
+                              N._p(sa), N._p(za), N._p(qs), N._p(W.scale[sl]), N._p(W.zero[sl]), N._p(W.wsum[sl]),
+                              N._p(bias), N._p(r2), ldr, C.c_float(res_scale), N._ACT[act], N._p(ws.ws),
+                              C.c_size_t(ws.ws_bytes), N._p(ws.counters), ws.n_counters, N._p(ws.status), N._stream())
+    N._check(rc, "w8a8_gemm")
+    ws.launches += 1
+    return out
+
+
+def linear(x, W, bias=None, act=None, residual=None, res_scale=1.0, out_dtype=None):
+    if W.kind == "w8a8":
+        return _w8a8(x, W, W.out_features, bias, act, residual, res_scale, out_dtype)
+    if W.kind in _QT:
+        return _qgemm(x, W, W.out_features, False, bias, act, residual, res_scale, out_dtype)
+    raise N.KernelError(f"no sm_100a GEMM for weight kind {W.kind}")
+
+
+def linear_gated(x, W, act="silu", bias=None):
+    I = W.out_features // 2
+    if W.kind == "w8a8":
+        # one int8 GEMM over both halves (activations are quantised once), then act(gate)*up
+        gu = _w8a8(x, W, 2 * I, bias, None, None, 1.0, None)
+        return N.gated_act(gu, act)
+    if W.kind == "fp8" and I % 128:
+        gu = _qgemm(x, W, 2 * I, False, bias, None, None, 1.0, None)
+        return N.gated_act(gu, act)
+    return _qgemm(x, W, I, True, bias, act, None, 1.0, None)
