@@ -82,6 +82,9 @@ class Decoder:
         self.act_dtype = act_dtype or (torch.bfloat16 if self.device.type == "cuda" else torch.float32)
         self.tp, self.tpr = ctx.tp_size, ctx.tp_rank
         self.src = WeightSource(path, cfg.weight_data_type, self.device)
+        # DeepSeek checkpoints keep embedding, lm_head, norms and the router in bf16 whatever the projection type
+        # (deepseek_moe_convert.py:117-180)
+        self.aux_dtype = "bf16" if cfg.model_type == "deepseek_moe" else None
         self.l0, self.l1 = P.pp_layer_range(cfg.num_layer, ctx.pp_size, ctx.pp_rank)
         self.first_stage = ctx.pp_rank == 0
         self.last_stage = ctx.pp_rank == ctx.pp_size - 1
@@ -160,7 +163,7 @@ class Decoder:
     # weight loading
     # ------------------------------------------------------------------------------------
     def _vec(self, name, n, rng=None, ones=False):
-        return self.src.vector(name, n, out_dtype=torch.float32, rng=rng, fake_ones=ones)
+        return self.src.vector(name, n, dtype=self.aux_dtype, out_dtype=torch.float32, rng=rng, fake_ones=ones)
 
     def _opt_vec(self, name, n, rng=None, default_present=False):
         if self.src.fake:
@@ -175,7 +178,7 @@ class Decoder:
         self.wte = self.wpe = None
         if self.first_stage:
             edt = torch.bfloat16 if self.device.type == "cuda" else torch.float32
-            self.wte = self.src.matrix("model.wte.bin", (c.vocab_size, c.hidden_size)).to(edt)
+            self.wte = self.src.matrix("model.wte.bin", (c.vocab_size, c.hidden_size), dtype=self.aux_dtype).to(edt)
             if self.spec.embedding == "opt":
                 npos = c.max_pos_seq_len + 2
                 self.wpe = self.src.matrix("model.wpe.bin", (npos, c.hidden_size)).to(edt)
@@ -194,7 +197,7 @@ class Decoder:
             self.final_b = self._opt_vec("model.final_layernorm.bias.bin", c.hidden_size, default_present=True)
         hk = "bf16" if self.device.type == "cuda" else "fp32"   # DistLinear keeps 16-bit weights (dist_linear.h:38-64)
         self.lm_head = self.src.linear("model.lm_head.weight.bin", c.hidden_size, c.vocab_size, hk,
-                                       out_rng=(self.v0, self.v1), transposed_on_disk=True)
+                                       out_rng=(self.v0, self.v1), transposed_on_disk=True, dtype=self.aux_dtype)
 
     def _lin(self, name, in_f, out_f, in_rng=None, out_rng=None, out_ranges=None, kind=None) -> LinearWeight:
         """A projection by base name: fp file ``<name>.weight.0.bin`` or GPTQ ``<name>.qweight.0.bin``."""

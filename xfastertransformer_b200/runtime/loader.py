@@ -210,7 +210,7 @@ class WeightSource:
 
     def linear(self, name: str, in_f: int, out_f: int, kind: str, in_rng: Optional[Tuple[int, int]] = None,
                out_rng: Optional[Tuple[int, int]] = None, out_ranges: Optional[Sequence[Tuple[int, int]]] = None,
-               transposed_on_disk: bool = False) -> LinearWeight:
+               transposed_on_disk: bool = False, dtype: Optional[str] = None) -> LinearWeight:
         """Load ``<name>`` ([in,out] on disk unless `transposed_on_disk`) -> LinearWeight [out,in].
 
         `in_rng` / `out_rng` select a TP slice; `out_ranges` concatenates several out-ranges
@@ -227,11 +227,12 @@ class WeightSource:
             return make_linear(self._fake((o, i), torch.bfloat16 if kind != "fp16" else torch.float16, name), kind)
         ranges = out_ranges if out_ranges is not None else [out_rng]
         parts = []
+        fdt = dtype or self.dtype
         for rg in ranges:
             if transposed_on_disk:
-                t = read_bin(os.path.join(self.path, name), self.dtype, (out_f, in_f), rows=rg, cols=in_rng)
+                t = read_bin(os.path.join(self.path, name), fdt, (out_f, in_f), rows=rg, cols=in_rng)
             else:
-                t = read_bin(os.path.join(self.path, name), self.dtype, (in_f, out_f), rows=in_rng, cols=rg)
+                t = read_bin(os.path.join(self.path, name), fdt, (in_f, out_f), rows=in_rng, cols=rg)
             parts.append(t)
             self.loaded_bytes += t.numel() * t.element_size()
         if transposed_on_disk:
