@@ -1,0 +1,143 @@
+// Top-k / top-p sampling on the device (reference: src/searchers/sample_search.cpp:118-268): top-k -> /temperature ->
+// top-p prefix that never keeps fewer than 2 candidates -> softmax over the kept -> inverse CDF with ONE uniform
+// draw per row.  The draw comes from the caller (a counter-based stream shared by all ranks), so every tensor-
+// parallel rank picks the same token; the reference reseeds std::random_device per step instead.
+//
+// One CTA per row: a 32-step bisection on the order-preserving integer image of the floats finds the k-th largest
+// logit, the candidates (>= threshold) are compacted into shared memory, bitonic-sorted by (value desc, index asc),
+// and thread 0 walks the at most 1024 survivors.
+#include "ptx.cuh"
+
+namespace xft {
+
+__device__ __forceinline__ unsigned f2key(float f) {
+  unsigned u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+constexpr int kMaxK = 1024;
+
+__global__ void __launch_bounds__(1024) sample_topk_topp_kernel(const float* __restrict__ logits, int ld, int V, int k,
+                                                                float top_p, float temperature,
+                                                                const float* __restrict__ uniform, int* __restrict__ out) {
+  __shared__ unsigned long long cand[kMaxK];      // (key << 32) | (0xffffffff - idx): sorts value desc, idx asc
+  __shared__ int s_cnt;
+  __shared__ unsigned s_red[32];
+  grid_dep_launch();
+  grid_dep_wait();
+  const int row = blockIdx.x, tid = threadIdx.x;
+  const float* x = logits + (size_t)row * ld;
+  if (k > V) k = V;
+  if (k > kMaxK) k = kMaxK;
+  // largest threshold key with count(key >= thr) >= k
+  unsigned thr = 0;
+  for (int bit = 31; bit >= 0; --bit) {
+    const unsigned cand_thr = thr | (1u << bit);
+    unsigned c = 0;
+    for (int i = tid; i < V; i += 1024) c += f2key(x[i]) >= cand_thr;
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+    if ((tid & 31) == 0) s_red[tid >> 5] = c;
+    __syncthreads();
+    unsigned tot = 0;
+    for (int w = 0; w < 32; ++w) tot += s_red[w];
+    __syncthreads();
+    if (tot >= (unsigned)k) thr = cand_thr;
+  }
+  if (tid == 0) s_cnt = 0;
+  for (int i = tid; i < kMaxK; i += 1024) cand[i] = 0ull;
+  __syncthreads();
+  // strictly greater first (always fits: fewer than k of them), then ties in index order until the list is full
+  for (int i = tid; i < V; i += 1024) {
+    const unsigned key = f2key(x[i]);
+    if (key > thr) { const int p = atomicAdd(&s_cnt, 1); if (p < kMaxK) cand[p] = ((unsigned long long)key << 32) | (0xffffffffu - (unsigned)i); }
+  }
+  __syncthreads();
+  for (int i = tid; i < V; i += 1024) {
+    const unsigned key = f2key(x[i]);
+    if (key == thr) { const int p = atomicAdd(&s_cnt, 1); if (p < kMaxK) cand[p] = ((unsigned long long)key << 32) | (0xffffffffu - (unsigned)i); }
+  }
+  __syncthreads();
+  // bitonic sort, descending
+  for (int size = 2; size <= kMaxK; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      const int i = tid, j = i ^ stride;
+      if (j > i) {
+        const bool desc = (i & size) == 0;
+        const unsigned long long a = cand[i], b = cand[j];
+        if ((a < b) == desc) { cand[i] = b; cand[j] = a; }
+      }
+      __syncthreads();
+    }
+  }
+  if (tid == 0) {
+    const int n = min(k, min(s_cnt, kMaxK));
+    auto val = [&](int i) {
+      unsigned key = (unsigned)(cand[i] >> 32);
+      unsigned u = (key & 0x80000000u) ? (key & 0x7fffffffu) : ~key;
+      return __uint_as_float(u);
+    };
+    const float invT = 1.f / fmaxf(temperature, 1e-6f);
+    const float mx = val(0) * invT;
+    float den = 0.f;
+    for (int i = 0; i < n; ++i) den += __expf(val(i) * invT - mx);
+    int keep = n;
+    if (top_p < 1.f && n > 1) {
+      float c = 0.f;
+      keep = 0;
+      for (int i = 0; i < n; ++i) {
+        if (i >= 2 && c >= top_p) break;          // prefix whose mass before the element is < top_p, at least 2
+        c += __expf(val(i) * invT - mx) / den;
+        keep = i + 1;
+      }
+    }
+    float den2 = 0.f;
+    for (int i = 0; i < keep; ++i) den2 += __expf(val(i) * invT - mx);
+    const float u = fminf(fmaxf(uniform[row], 0.f), 1.f - 1e-7f) * den2;
+    float c = 0.f;
+    int pick = keep - 1;
+    for (int i = 0; i < keep; ++i) {
+      c += __expf(val(i) * invT - mx);
+      if (c > u) { pick = i; break; }
+    }
+    out[row] = (int)(0xffffffffu - (unsigned)(cand[pick] & 0xffffffffull));
+  }
+}
+
+// logits[row, id] <- l < 0 ? l*p : l/p for every id in the row's token list (src/searchers/search_utils.cpp:104-172).
+// tokens: [rows, max_len] padded with -1; ids outside [vocab_offset, vocab_offset + V) belong to other ranks.
+__global__ void repetition_penalty_kernel(float* __restrict__ logits, int ld, int V, const int* __restrict__ tokens,
+                                          int max_len, float penalty, int vocab_offset) {
+  grid_dep_launch();
+  grid_dep_wait();
+  const int row = blockIdx.x;
+  float* x = logits + (size_t)row * ld;
+  const int* tk = tokens + (size_t)row * max_len;
+  for (int i = threadIdx.x; i < max_len; i += blockDim.x) {
+    const int id = tk[i];
+    if (id < 0) continue;
+    bool first = true;                         // apply once per distinct id: only its first occurrence acts
+    for (int j = 0; j < i; ++j) if (tk[j] == id) { first = false; break; }
+    const int c = id - vocab_offset;
+    if (first && c >= 0 && c < V) { const float l = x[c]; x[c] = l < 0.f ? l * penalty : l / penalty; }
+  }
+}
+
+}  // namespace xft
+
+using namespace xft;
+
+extern "C" int xft_sample_topk_topp(const float* logits, int ld, int rows, int V, int k, float top_p, float temperature,
+                                    const float* uniform, int* out, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  cudaError_t e = launch_pdl(sample_topk_topp_kernel, dim3(rows), dim3(1024), 0, st, logits, ld, V, k, top_p, temperature,
+                             uniform, out);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}
+
+extern "C" int xft_repetition_penalty(float* logits, int ld, int rows, int V, const int* tokens, int max_len, float penalty,
+                                      int vocab_offset, cudaStream_t st) {
+  if (rows <= 0 || max_len <= 0) return 0;
+  cudaError_t e = launch_pdl(repetition_penalty_kernel, dim3(rows), dim3(256), 0, st, logits, ld, V, tokens, max_len, penalty,
+                             vocab_offset);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}

@@ -1,0 +1,201 @@
+"""API behaviour on the CPU path: continuous-batching invariance, prefix sharing, sampling and beams through the
+engine, max_length semantics, hybrid dtypes, quantised dtypes, int8 KV, model-family smoke matrix, fault handling."""
+import os
+
+import pytest
+import torch
+
+import xfastertransformer_b200 as xft
+from xfastertransformer_b200.config import ModelConfig
+from xfastertransformer_b200.tools.synthetic import preset, write_synthetic_checkpoint
+
+
+@pytest.fixture(autouse=True)
+def _cpu(monkeypatch):
+    monkeypatch.setenv("XFT_ENGINE", "CPU")
+
+
+@pytest.fixture(scope="module")
+def tiny(tmp_path_factory):
+    d = str(tmp_path_factory.mktemp("tiny"))
+    write_synthetic_checkpoint(d, preset("tiny-llama", vocab_size=1000), seed=0, dtype="bf16", std=0.08)
+    return d
+
+
+def _greedy_stream(model, prompt, n):
+    """Decode one sequence alone through the CB API; returns its n tokens."""
+    sid = model.set_input_cb([prompt], None, 128)
+    toks = []
+    logits = model.forward_cb()
+    for _ in range(n):
+        t = int(logits[0].argmax())
+        toks.append(t)
+        model.set_input_cb([t], sid, 128)
+        logits = model.forward_cb()
+    model.free_seqs(sid)
+    return toks
+
+
+def test_continuous_batching_invariance(tiny):
+    """The reference's cb_check scenario (examples/cpp/cb_check.cpp:373-455): the same prompt submitted at three
+    different moments, batched with the others at different depths, must emit identical streams."""
+    m = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+    prompt = [5, 17, 99, 200, 3, 42, 7]
+    want = _greedy_stream(m, prompt, 8)
+    streams = {0: [], 1: [], 2: []}
+    ids = {}
+    last = {}
+
+    def prefill(k):
+        sid = m.set_input_cb([prompt], None, 128)
+        ids[k] = int(sid[0])
+        lg = m.forward_cb()
+        last[k] = int(lg[0].argmax())
+        streams[k].append(last[k])
+
+    def decode(keys):
+        m.set_input_cb([last[k] for k in keys], [ids[k] for k in keys], 128)
+        lg = m.forward_cb()
+        for i, k in enumerate(keys):
+            last[k] = int(lg[i].argmax())
+            streams[k].append(last[k])
+
+    prefill(0); decode([0]); decode([0])
+    prefill(1); decode([0, 1])
+    prefill(2); decode([0, 1, 2]); decode([0, 1, 2])
+    m.free_seqs([ids[0]])
+    while len(streams[2]) < 8:
+        decode([1, 2])
+    m.free_seqs([ids[1], ids[2]])
+    for k in streams:
+        n = min(len(streams[k]), 8)
+        assert streams[k][:n] == want[:n], (k, streams[k], want)
+    assert m.model.cache.alloc.num_free == m.model.cache.alloc.num_blocks, "all KV blocks returned"
+
+
+def test_prefix_sharing_same_tokens(tiny):
+    m = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+    g = torch.Generator().manual_seed(4)
+    prefix = torch.randint(0, 1000, (1, 64), generator=g)
+    tail = torch.randint(0, 1000, (2, 9), generator=g)
+    ids = torch.cat([prefix.expand(2, -1), tail], 1)
+    base = m.generate(ids, max_length=85)
+    m.prefix_sharing(prefix)
+    shared = m.generate(ids, max_length=85)
+    assert m.model.prefix_seq is not None
+    m.disable_prefix_sharing()
+    assert torch.equal(base, shared)
+
+
+def test_max_length_counts_the_prompt_and_eos_stops(tiny):
+    m = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+    ids = torch.randint(0, 1000, (2, 10), generator=torch.Generator().manual_seed(5))
+    out = m.generate(ids, max_length=14)
+    assert out.shape == (2, 14)
+    first = int(out[0, 10])
+    out2 = m.generate(ids, max_length=20, eos_token_id=first, pad_token_id=0)
+    assert out2.shape[1] <= 20 and int(out2[0, 10]) == first
+    assert (out2[0, 11:] == first).all() or (out2[0, 11:] == 0).all()      # finished row is padded
+
+
+def test_sampling_seeded_and_beams(tiny):
+    m = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+    ids = torch.randint(0, 1000, (2, 8), generator=torch.Generator().manual_seed(6))
+    a = m.generate(ids, max_length=16, do_sample=True, top_k=20, top_p=0.9, temperature=0.8, seed=11)
+    b = m.generate(ids, max_length=16, do_sample=True, top_k=20, top_p=0.9, temperature=0.8, seed=11)
+    c = m.generate(ids, max_length=16, do_sample=True, top_k=20, top_p=0.9, temperature=0.8, seed=12)
+    assert torch.equal(a, b) and not torch.equal(a, c)
+    greedy = m.generate(ids, max_length=16)
+    beams = m.generate(ids, max_length=16, num_beams=3)
+    assert beams.shape == (2, 16) and torch.equal(beams[:, :8], ids)
+    one = m.generate(ids, max_length=16, num_beams=1)
+    assert torch.equal(one, greedy)
+    rp = m.generate(ids, max_length=16, repetition_penalty=1.5)
+    assert rp.shape == (2, 16)
+    assert m.model.cache.alloc.num_free == m.model.cache.alloc.num_blocks
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "int8", "w8a8", "int4", "nf4", "bf16_int8", "w8a8_nf4"])
+@pytest.mark.parametrize("kv", ["fp16", "int8"])
+def test_dtype_matrix(tiny, dtype, kv):
+    """The reference's CI matrix (ci/test_case:47-112) as a correctness check: quantised models track the bf16 one."""
+    ids = torch.randint(0, 1000, (2, 12), generator=torch.Generator().manual_seed(7))
+    base = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+    want = base(ids)
+    m = xft.AutoModel.from_pretrained(tiny, dtype=dtype, kv_cache_dtype=kv)
+    got = m(ids)
+    rel = (got - want).abs().max().item() / want.abs().max().item()
+    assert rel < (0.6 if "4" in dtype else 0.2), rel
+    assert m.generate(ids, max_length=16).shape == (2, 16)
+
+
+FAMILIES = {
+    "llama": {}, "yarn_llama": dict(), "gemma": dict(activation_type="gelu"), "qwen": dict(seq_length=64),
+    "qwen2": {}, "qwen3": dict(do_qk_norm=True), "baichuan": {}, "chatglm2": dict(kv_head_num=2),
+    "chatglm3": dict(kv_head_num=2), "chatglm4": dict(kv_head_num=2), "gpt": dict(activation_type="relu"),
+    "telechat": {}, "chatglm": dict(activation_type="gelu"),
+}
+
+
+@pytest.mark.parametrize("mt", sorted(FAMILIES))
+def test_family_smoke_and_decode_consistency(mt, tmp_path):
+    """Every registered family loads a synthetic checkpoint, and incremental decoding reproduces the full-prefill
+    logits (KV cache, RoPE variant, masks and positions agree between the two paths)."""
+    kw = dict(model_type=mt, num_layer=2, hidden_size=128, head_num=4, kv_head_num=4, size_per_head=32, inter_size=256,
+              vocab_size=512, max_pos_seq_len=256, activation_type="silu", weight_data_type="fp32", start_id=1, end_id=2)
+    kw.update(FAMILIES[mt])
+    cfg = ModelConfig(**kw)
+    if mt == "yarn_llama":
+        cfg.rope.scaling_type, cfg.rope.scaling_factor, cfg.rope.original_max_pos = "yarn", 4.0, 64
+    d = str(tmp_path / mt)
+    write_synthetic_checkpoint(d, cfg, seed=1, dtype="fp32", std=0.1)
+    m = xft.AutoModel.from_pretrained(d, dtype="bf16")
+    ids = torch.randint(5, 500, (1, 20), generator=torch.Generator().manual_seed(8))
+    if mt == "chatglm":
+        ids[0, -2], ids[0, -1] = 130001 % 512, 130004 % 512      # shape-only stand-ins (ids above vocab are illegal here)
+    full = m(ids)[0]                                                # [20, vocab]
+    sid = m.set_input_cb([ids[0, :12].tolist()], None, 64)
+    lg = m.forward_cb()
+    if mt != "chatglm":                                             # ChatGLM-1's prefix mask makes prompt logits context-dependent
+        assert torch.allclose(lg[0], full[11], atol=2e-3, rtol=2e-3), (lg[0] - full[11]).abs().max()
+        for t in range(12, 20):
+            m.set_input_cb([int(ids[0, t])], sid, 64)
+            lg = m.forward_cb()
+            assert torch.allclose(lg[0], full[t], atol=2e-3, rtol=2e-3), (t, (lg[0] - full[t]).abs().max())
+    m.free_seqs(sid)
+    assert m.generate(ids, max_length=24).shape == (1, 24)
+
+
+def test_baichuan_alibi_and_fake_model(tmp_path, monkeypatch):
+    cfg = ModelConfig(model_type="baichuan", num_layer=2, hidden_size=128, head_num=4, kv_head_num=4, size_per_head=32,
+                      inter_size=256, vocab_size=512, max_pos_seq_len=0, activation_type="silu", weight_data_type="bf16")
+    d = str(tmp_path / "b13")
+    cfg.to_ini(d)
+    monkeypatch.setenv("XFT_FAKE_MODEL", "2")       # weights drawn in memory, config.ini only
+    from xfastertransformer_b200.utils.flags import Env
+    Env._inst = None
+    m = xft.AutoModel.from_pretrained(d, dtype="bf16")
+    assert m.model.decoder.spec.alibi and m.model.decoder.slopes is not None
+    assert m.generate(torch.randint(0, 512, (2, 9)), max_length=12).shape == (2, 12)
+
+
+def test_faults_are_errors_not_crashes(tiny, tmp_path):
+    import shutil
+    bad = str(tmp_path / "bad")
+    shutil.copytree(tiny, bad)
+    f = os.path.join(bad, "model.layers.0.mlp.down_proj.weight.0.bin")
+    with open(f, "r+b") as fh:
+        fh.truncate(os.path.getsize(f) // 2)                      # truncated tensor file
+    with pytest.raises(ValueError, match="expected"):
+        xft.AutoModel.from_pretrained(bad, dtype="bf16")
+    with pytest.raises(Exception, match="don't support"):
+        xft.AutoModel.from_pretrained(tiny, dtype="fp64")
+    with pytest.raises(Exception, match="KV cache"):
+        xft.AutoModel.from_pretrained(tiny, dtype="bf16", kv_cache_dtype="fp8")
+    with pytest.raises(FileNotFoundError):
+        xft.AutoModel.from_pretrained(str(tmp_path / "nowhere"), dtype="bf16")
+    m = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+    with pytest.raises(KeyError):
+        m.set_input_cb([1], [9999], 32)                            # unknown sequence id
+    with pytest.raises(RuntimeError):
+        m.forward_cb()                                             # nothing scheduled

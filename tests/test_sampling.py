@@ -1,0 +1,64 @@
+"""Samplers, logits processors, beam search and API behaviours on the CPU path (+ GPU kernels where marked)."""
+import pytest
+import torch
+
+from xfastertransformer_b200.ops import reference as R
+from xfastertransformer_b200.runtime import sampler as S
+from xfastertransformer_b200.runtime.sequence import SamplingMeta
+
+
+def test_repetition_penalty_rule():
+    l = torch.tensor([[2.0, -2.0, 1.0, 0.5]])
+    out = R.repetition_penalty(l.clone(), [[0, 1, 1, 9]], 2.0, 0)
+    assert out.tolist() == [[1.0, -4.0, 1.0, 0.5]]
+    # ids outside this rank's vocab slice are ignored
+    out = R.repetition_penalty(l.clone(), [[4, 5]], 2.0, 4)
+    assert out.tolist() == [[1.0, -4.0, 1.0, 0.5]]
+
+
+def test_top_p_keeps_at_least_two():
+    logits = torch.tensor([[10.0, 0.0, -1.0, -2.0]])
+    picks = {int(R.sample_top_k_top_p(logits, 4, 0.01, 1.0, torch.tensor([u]))[0]) for u in (0.0, 0.5, 0.99999)}
+    assert picks <= {0, 1} and 0 in picks
+
+
+def test_stop_words_cleaning_and_matching():
+    cfg = SamplingMeta(eos_token_id=2, stop_words=[[], [0, 3], [2], [5, 6], [7]])
+    cfg.clean_stop_words()
+    assert cfg.stop_words == [[5, 6], [7]]
+    assert S.match_stop_words([1, 5, 6], cfg.stop_words)
+    assert not S.match_stop_words([5, 6, 1], cfg.stop_words)
+
+
+def test_beam_scorer_prefers_higher_logprob():
+    cfg = SamplingMeta(num_beams=2, eos_token_id=3, pad_token_id=0, max_length=8)
+    sc = S.BeamSearchScorer(1, cfg, 0)
+    lp = torch.full((2, 5), -10.0)
+    lp[0, 1] = -0.1
+    lp[0, 2] = -0.5
+    toks, src = sc.process(lp)
+    assert toks.tolist() == [1, 2] and src.tolist() == [0, 0]
+    lp = torch.full((2, 5), -10.0)
+    lp[0, 3] = -0.05          # beam 0 ends with eos
+    lp[1, 4] = -0.2
+    toks, src = sc.process(lp)
+    outs = sc.finalize([[9]], 8)
+    assert outs[0][:3] == [9, 1, 3]
+
+
+@pytest.mark.gpu
+def test_gpu_sampler_matches_reference():
+    from xfastertransformer_b200.ops import native_sample
+    g = torch.Generator().manual_seed(0)
+    logits = torch.randn(9, 32000, generator=g) * 3
+    for k, p, T in ((50, 0.9, 0.8), (1, 1.0, 1.0), (1024, 0.5, 1.3), (5, 1.0, 0.7)):
+        u = torch.rand(9, generator=g)
+        want = R.sample_top_k_top_p(logits, k, p, T, u)
+        got = native_sample.sample_top_k_top_p(logits.cuda(), k, p, T, u).cpu()
+        # identical except where the draw lands within float error of a CDF boundary
+        assert (got == want).float().mean().item() >= 0.85, (k, p, T, got, want)
+    l = torch.randn(3, 100)
+    toks = [[1, 2, 2, 50], [], [99, 0]]
+    want = R.repetition_penalty(l.clone(), toks, 1.7, 0)
+    got = native_sample.repetition_penalty(l.clone().cuda(), toks, 1.7, 0).cpu()
+    assert torch.allclose(got, want)

@@ -44,6 +44,11 @@ def greedy_select(local: torch.Tensor, vocab_offset: int, ctx: DistContext) -> t
 
 def apply_repetition_penalty(local: torch.Tensor, token_lists: Sequence[Sequence[int]], penalty: float,
                              vocab_offset: int) -> torch.Tensor:
+    if local.is_cuda:
+        from ..ops import native_sample
+        if not (local.dtype == torch.float32 and local.stride(-1) == 1):
+            local = local.float().contiguous()
+        return native_sample.repetition_penalty(local, token_lists, penalty, vocab_offset)
     from ..ops import reference as R
     return R.repetition_penalty(local, token_lists, penalty, vocab_offset)
 
