@@ -1,0 +1,84 @@
+// C++ generation API: xft::Model / xft::AutoModel (reference: include/models.h:25-133, src/models/models.cpp).
+//
+//   xft::AutoModel model("/path/to/converted-model", xft::DataType::bf16);
+//   model.config(/*maxLen*/ 128);  model.input(ids, batch);
+//   while (!model.isDone()) { auto next = model.generate(); }
+//   auto all = model.finalize();
+//
+// and the continuous-batching calls set_input(ids, seqIDs, maxLen) / forward() / freeSeqs().  The native engine
+// runs the dense decoder families (llama, yarn_llama, gemma, qwen2, qwen3, baichuan with RoPE) in bf16 on one B200
+// through the same sm_100a kernels as the Python package; errors are exceptions (std::runtime_error), never exit().
+#pragma once
+#include <cstdint>
+#include <memory>
+#include <string>
+#include <tuple>
+#include <vector>
+
+#include "abstract_searcher.h"
+#include "dtype.h"
+
+namespace xft {
+
+class Engine;   // csrc/core/engine.cc
+
+class Model {
+public:
+  Model();
+  ~Model();
+
+  void input(std::vector<int32_t>& inputIds, int batchSize);
+
+  void config(int maxLen = -1, int numBeams = 1, int numBeamHypsToKeep = 1, float lenPenalty = 1.0f,
+              bool doEarlyStopping = false, int eosTokenId = -1, int padTokenId = -1, bool doSample = false,
+              float temperature = 1.0f, int topK = 50, float topP = 1.0f, float repetitionPenalty = 1.0f,
+              const std::vector<std::vector<int>>& stopWordsList = {});
+  void config(SearcherConfig& cfg, const std::vector<std::vector<int>>& stopWordsList = {});
+
+  // batch of equal-length prompts + generation config; returns the sequence ids
+  std::vector<int> set_input(std::vector<int32_t>& inputIds, int batchSize, int maxLen = -1, int numBeams = 1,
+                             int numBeamHypsToKeep = 1, float lenPenalty = 1.0f, bool doEarlyStopping = false,
+                             int eosTokenId = -1, int padTokenId = -1, bool doSample = false, float temperature = 1.0f,
+                             int topK = 50, float topP = 1.0f, float repetitionPenalty = 1.0f,
+                             const std::vector<std::vector<int>>& stopWordsList = {});
+  std::vector<int> set_input(std::vector<int32_t>& inputIds, int batchSize, SearcherConfig& cfg,
+                             const std::vector<std::vector<int>>& stopWordsList = {});
+  std::vector<int> set_input(std::vector<std::vector<int32_t>>& inputIds, SearcherConfig& cfg,
+                             const std::vector<std::vector<int>>& stopWordsList = {});
+  // continuous batching (used with forward()): new prompts when seqIDs is empty, else one next token per sequence
+  std::vector<int> set_input(std::vector<std::vector<int32_t>>& inputIds, std::vector<int> seqIDs = {}, int maxLen = -1);
+  std::vector<int> set_input(std::vector<int32_t>& inputIds, int batchSize, std::vector<int> seqIDs, int maxLen = -1);
+
+  bool isDone();
+  // logits of the scheduled sequences: (pointer to fp32 [rows, vocab] on the host, rows, vocab)
+  std::tuple<float*, int, int> forward(bool logitsAll = false);
+  std::vector<int32_t> generate();     // one step: next token of every sequence of the current request
+  std::vector<int32_t> finalize();     // prompt + generated, flattened, rows padded to equal length
+  bool freeSeqs(std::vector<int>& seqIDs);
+  void setPrefix(std::vector<int32_t>& prefixIDs);
+  void unsetPrefix();
+  bool setStopWords(std::vector<std::vector<int>> stopWordsList);
+
+  bool isMaster() { return true; }
+  int getRank() { return 0; }
+  int getBatchSize() { return batchSize; }
+  int getSeqLen() { return seqLen; }
+  int getVocabSize();
+  int getMaxSeqLen();
+  SearcherConfig getConfig() { return configuration; }
+  void exitSlaves() {}
+
+protected:
+  void load(const std::string& path, DataType dt, DataType kv);
+  std::unique_ptr<Engine> engine;
+  SearcherConfig configuration;
+  std::vector<std::vector<int>> stopWords;
+  int batchSize = 0, seqLen = 0;
+};
+
+class AutoModel : public Model {
+public:
+  AutoModel(std::string modelPath, xft::DataType dataType, xft::DataType KVCacheDataType = xft::DataType::fp16);
+};
+
+}  // namespace xft

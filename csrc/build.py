@@ -54,17 +54,25 @@ def build(force=False, verbose=False):
     lib = os.path.join(OUT, "libxft_b200_kernels.so")
     if jobs or not os.path.exists(lib):
         _run([NVCC] + ARCH + ["-shared", "-o", lib] + objs + ["-lcudart"], verbose)
-    # C++ runtime
+    # C++ runtime (links the kernel library; $ORIGIN rpath keeps the pair relocatable) and the example CLI
     cdir = os.path.join(HERE, "core")
+    api = os.path.join(HERE, "api")
     ccs = sorted(f for f in os.listdir(cdir) if f.endswith(".cc")) if os.path.isdir(cdir) else []
     if ccs:
         core = os.path.join(OUT, "libxft_b200_core.so")
         srcs = [os.path.join(cdir, f) for f in ccs]
         hdrs = tuple(os.path.join(cdir, f) for f in os.listdir(cdir) if f.endswith(".h")) + \
-            tuple(os.path.join(HERE, "api", f) for f in os.listdir(os.path.join(HERE, "api")) if f.endswith(".h"))
-        if force or any(_newer(s, core, hdrs) for s in srcs):
-            _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-I", os.path.join(HERE, "api"), "-I", cdir,
-                  "-I", "/usr/local/cuda/include", "-o", core] + srcs + ["-ldl", "-lpthread"], verbose)
+            tuple(os.path.join(api, "xft", f) for f in os.listdir(os.path.join(api, "xft")))
+        cxx = ["g++", "-O2", "-std=c++17", "-fPIC", "-I", api, "-I", cdir, "-I", "/usr/local/cuda/include"]
+        link = ["-L", OUT, "-lxft_b200_kernels", "-L", "/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath,$ORIGIN",
+                "-Wl,-rpath,/usr/local/cuda/lib64", "-ldl", "-lpthread"]
+        if force or jobs or any(_newer(s, core, hdrs) for s in srcs):
+            _run(cxx + ["-shared", "-o", core] + srcs + link, verbose)
+        ex_src = os.path.join(ROOT, "examples", "cpp", "example.cpp")
+        ex_bin = os.path.join(OUT, "xft_example")
+        if os.path.exists(ex_src) and (force or _newer(ex_src, ex_bin, hdrs) or _newer(core, ex_bin)):
+            _run(cxx + ["-o", ex_bin, ex_src, "-L", OUT, "-lxft_b200_core", "-lxft_b200_kernels", "-L",
+                        "/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,/usr/local/cuda/lib64"], verbose)
     return lib, "".join(logs)
 
 

@@ -1,0 +1,49 @@
+// C ABI over the host-side runtime so that Python (ctypes) and tests can drive the C++ twins of the layout
+// arithmetic, the block allocator and the samplers without a GPU.
+#include <cstring>
+
+#include "runtime.h"
+
+using namespace xft;
+
+extern "C" {
+
+void xftc_task_range(int n, int splits, int idx, int* out2) { auto r = taskRange(n, splits, idx); out2[0] = r.first; out2[1] = r.second; }
+void xftc_head_range(int q, int kv, int splits, int idx, int* out4) { auto r = headRange(q, kv, splits, idx); out4[0] = r.q0; out4[1] = r.q1; out4[2] = r.kv0; out4[3] = r.kv1; }
+
+void* xftc_tables_new(int blockSize, int numBlocks) { return new BlockTables(blockSize, numBlocks); }
+void xftc_tables_delete(void* t) { delete static_cast<BlockTables*>(t); }
+int xftc_tables_add(void* t, int seq) { try { static_cast<BlockTables*>(t)->add(seq); return 0; } catch (...) { return -1; } }
+void xftc_tables_free(void* t, int seq) { static_cast<BlockTables*>(t)->free(seq); }
+int xftc_tables_fork(void* t, int src, int dst) { try { static_cast<BlockTables*>(t)->fork(src, dst); return 0; } catch (...) { return -1; } }
+// returns number of slots written, -1 on exhaustion; cow_pairs receives (src,dst) of a block split (or -1,-1)
+int xftc_tables_append(void* t, int seq, int n, int* slots, int* cow_pairs) {
+  try {
+    cow_pairs[0] = cow_pairs[1] = -1;
+    auto s = static_cast<BlockTables*>(t)->append(seq, n, [&](int a, int b) { cow_pairs[0] = a; cow_pairs[1] = b; });
+    std::memcpy(slots, s.data(), s.size() * sizeof(int));
+    return (int)s.size();
+  } catch (...) { return -1; }
+}
+int xftc_tables_table(void* t, int seq, int* out, int cap) {
+  try {
+    auto& v = static_cast<BlockTables*>(t)->table(seq);
+    int n = (int)v.size() < cap ? (int)v.size() : cap;
+    std::memcpy(out, v.data(), n * sizeof(int));
+    return (int)v.size();
+  } catch (...) { return -1; }
+}
+int xftc_tables_len(void* t, int seq) { try { return static_cast<BlockTables*>(t)->len(seq); } catch (...) { return -1; } }
+int xftc_tables_num_free(void* t) { return static_cast<BlockTables*>(t)->allocator().numFree(); }
+void xftc_tables_grow(void* t, int total) { static_cast<BlockTables*>(t)->allocator().grow(total); }
+int xftc_tables_reorder(void* t, const int* seqs, const int* src, int n) {
+  try { static_cast<BlockTables*>(t)->reorder(std::vector<int>(seqs, seqs + n), std::vector<int>(src, src + n)); return 0; } catch (...) { return -1; }
+}
+
+int xftc_argmax(const float* l, int n) { return argmaxFirst(l, n); }
+int xftc_sample(const float* l, int n, int k, float p, float temp, float u) { return sampleTopKTopP(l, n, k, p, temp, u); }
+void xftc_repetition_penalty(float* l, int n, const int* toks, int nt, float pen, int off) {
+  repetitionPenalty(l, n, std::vector<int32_t>(toks, toks + nt), pen, off);
+}
+
+}  // extern "C"

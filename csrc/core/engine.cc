@@ -1,0 +1,578 @@
+// Native C++ engine behind xft::Model / xft::AutoModel: loads a converted checkpoint (config.ini + .bin), keeps
+// weights as bf16 [out, in] on the device, and runs the dense decoder families through the sm_100a kernels of
+// libxft_b200_kernels.so with a paged KV cache.  Reference: src/models/models.cpp (driver), common_decoder.h
+// (forward), decoder_block.h (weight loading), kvcache_mgr.h, sampling.cpp (greedy / stop check).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <chrono>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <fstream>
+#include <random>
+#include <stdexcept>
+
+#include "ini.h"
+#include "kernels_c.h"
+#include "runtime.h"
+#include "xft/models.h"
+
+namespace xft {
+
+#define XFT_CUDA(x)                                                                                     \
+  do {                                                                                                  \
+    cudaError_t e_ = (x);                                                                               \
+    if (e_ != cudaSuccess) throw std::runtime_error(std::string("CUDA error: ") + cudaGetErrorString(e_) + " at " #x); \
+  } while (0)
+#define XFT_K(x)                                                                          \
+  do {                                                                                    \
+    int rc_ = (x);                                                                        \
+    if (rc_ != 0) throw std::runtime_error("kernel launch failed (" + std::to_string(rc_) + "): " #x); \
+  } while (0)
+
+namespace {
+
+struct DevBuf {
+  void* p = nullptr;
+  size_t bytes = 0;
+  DevBuf() = default;
+  explicit DevBuf(size_t n) { reset(n); }
+  DevBuf(const DevBuf&) = delete;
+  DevBuf& operator=(const DevBuf&) = delete;
+  DevBuf(DevBuf&& o) noexcept : p(o.p), bytes(o.bytes) { o.p = nullptr; o.bytes = 0; }
+  DevBuf& operator=(DevBuf&& o) noexcept { std::swap(p, o.p); std::swap(bytes, o.bytes); return *this; }
+  ~DevBuf() { if (p) cudaFree(p); }
+  void reset(size_t n) {
+    if (p) { cudaFree(p); p = nullptr; }
+    bytes = n;
+    if (n) XFT_CUDA(cudaMalloc(&p, n));
+  }
+  void ensure(size_t n) { if (n > bytes) reset(n + n / 4); }
+  template <class T> T* as() const { return static_cast<T*>(p); }
+};
+
+std::vector<char> readFile(const std::string& path, size_t expect) {
+  std::ifstream f(path, std::ios::binary | std::ios::ate);
+  if (!f) throw std::runtime_error("cannot open " + path);
+  size_t sz = (size_t)f.tellg();
+  if (sz != expect) throw std::runtime_error(path + ": expected " + std::to_string(expect) + " bytes, found " + std::to_string(sz));
+  std::vector<char> buf(sz);
+  f.seekg(0);
+  f.read(buf.data(), (std::streamsize)sz);
+  return buf;
+}
+
+size_t dtypeSize(int dt) { return dt == 0 ? 4 : 2; }   // 0 fp32, 1 fp16, 2 bf16
+
+float halfToFloat(uint16_t h) {
+  uint32_t s = (h >> 15) & 1, e = (h >> 10) & 31, m = h & 1023, u;
+  if (e == 0) {
+    if (m == 0) u = s << 31;
+    else { e = 127 - 15 + 1; while (!(m & 1024)) { m <<= 1; --e; } m &= 1023; u = (s << 31) | (e << 23) | (m << 13); }
+  } else if (e == 31) u = (s << 31) | 0x7f800000u | (m << 13);
+  else u = (s << 31) | ((e + 112) << 23) | (m << 13);
+  float f; std::memcpy(&f, &u, 4); return f;
+}
+float elemToFloat(const char* p, int dt, size_t i) {
+  if (dt == 0) { float f; std::memcpy(&f, p + 4 * i, 4); return f; }
+  uint16_t h; std::memcpy(&h, p + 2 * i, 2);
+  if (dt == 1) return halfToFloat(h);
+  uint32_t u = (uint32_t)h << 16; float f; std::memcpy(&f, &u, 4); return f;
+}
+uint16_t floatToBf16(float f) {
+  uint32_t u; std::memcpy(&u, &f, 4);
+  u += 0x7fffu + ((u >> 16) & 1);
+  return (uint16_t)(u >> 16);
+}
+
+}  // namespace
+
+struct LayerWeights {
+  DevBuf qkv, o, gateUp, down, n1, n2, qkvBias, qNorm, kNorm;
+};
+
+class Engine {
+public:
+  Engine(const std::string& path, DataType dt, DataType kvdt);
+  // hyper-parameters
+  std::string type;
+  int heads = 0, kvHeads = 0, headDim = 0, hidden = 0, inter = 0, layers = 0, vocab = 0, maxPos = 0, endId = 0;
+  float eps = 1e-6f, ropeTheta = 10000.f, ropeFactor = 1.f, embedScale = 1.f;
+  int act = 2;   // kernel activation code: 1 relu, 2 silu, 3 gelu
+  bool qkNorm = false, kvInt8 = false;
+
+  SequencePool pool;
+  std::unique_ptr<BlockTables> tables;
+  std::vector<int> working, cbActive;
+  int prefixSeq = -1;
+  std::vector<float> hostLogits;
+  std::mt19937_64 rng;
+
+  // Runs the pending inputs of `ids`; logits land in hostLogits [rows, vocab].  Returns rows.
+  int forward(const std::vector<int>& ids, bool logitsAll);
+  void ensureBlocks(int extra);
+  void release(int id) { tables->free(id); pool.remove(id); }
+  void attachPrefix(SequenceMeta& s);
+
+private:
+  void loadLinear(const std::string& file, int inF, int outF, void* dst, int dstRowOffset, int dstLd);
+  DevBuf loadVector(const std::string& file, int n, bool optional = false);
+  void copyBlock(int src, int dst);
+  std::string dir;
+  int fileDt = 1;
+  DevBuf wte, lmHead, finalNorm, ropeTable, ws, counters, status, attnCounters, partO, partMl;
+  std::vector<LayerWeights> lw;
+  std::vector<DevBuf> kc, vc, ks, vs;
+  int numBlocks = 0;
+  // activations
+  DevBuf dIds, dPos, dSlots, dCu, dKv, dBt, x, x2, h, qkvBuf, q, att, g, rows, logits;
+  cudaStream_t st = nullptr;
+  static constexpr int kBlock = 64;
+  static constexpr size_t kWsBytes = 64u << 20;
+};
+
+void Engine::loadLinear(const std::string& file, int inF, int outF, void* dst, int dstRowOffset, int dstLd) {
+  auto host = readFile(dir + "/" + file, (size_t)inF * outF * dtypeSize(fileDt));
+  DevBuf tmp(host.size());
+  XFT_CUDA(cudaMemcpy(tmp.p, host.data(), host.size(), cudaMemcpyHostToDevice));
+  XFT_K(xft_transpose_to_bf16(tmp.p, fileDt, outF, inF, outF, static_cast<__nv_bfloat16*>(dst) + (size_t)dstRowOffset * dstLd,
+                              dstLd, st));
+  XFT_CUDA(cudaStreamSynchronize(st));
+}
+
+DevBuf Engine::loadVector(const std::string& file, int n, bool optional) {
+  std::ifstream probe(dir + "/" + file, std::ios::binary);
+  if (!probe) {
+    if (optional) return DevBuf();
+    throw std::runtime_error("missing " + file);
+  }
+  auto host = readFile(dir + "/" + file, (size_t)n * dtypeSize(fileDt));
+  std::vector<float> f(n);
+  for (int i = 0; i < n; ++i) f[i] = elemToFloat(host.data(), fileDt, i);
+  DevBuf d((size_t)n * 4);
+  XFT_CUDA(cudaMemcpy(d.p, f.data(), (size_t)n * 4, cudaMemcpyHostToDevice));
+  return d;
+}
+
+Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) {
+  Ini ini(path + "/config.ini");
+  if (!ini.ok() || ini.sections().empty()) throw std::runtime_error("config.ini not found under " + path);
+  type = ini.sections()[0];
+  static const char* ok[] = {"llama", "yarn_llama", "gemma", "qwen2", "qwen3", "baichuan"};
+  bool supported = false;
+  for (auto t : ok) supported |= type == t;
+  if (!supported) throw std::runtime_error("the native C++ engine runs the dense llama-style families; use the Python API for [" + type + "]");
+  if (dt != DataType::bf16 && dt != DataType::fp16) throw std::runtime_error("the native C++ engine runs bf16 (fp16 weights are kept as bf16)");
+  kvInt8 = kvdt == DataType::int8;
+  heads = (int)ini.getInt(type, "head_num");
+  kvHeads = (int)ini.getInt(type, "kv_head_num", heads);
+  headDim = (int)ini.getInt(type, "size_per_head");
+  hidden = (int)ini.getInt(type, "hidden_size", heads * headDim);
+  inter = (int)ini.getInt(type, "inter_size");
+  layers = (int)ini.getInt(type, "num_layer");
+  vocab = (int)ini.getInt(type, "vocab_size");
+  maxPos = std::max<int>({(int)ini.getInt(type, "max_pos_seq_len", 0), (int)ini.getInt(type, "model_max_length", 0), 2048});
+  if (type == "baichuan" && ini.getInt(type, "max_pos_seq_len", 0) <= 0)
+    throw std::runtime_error("ALiBi Baichuan models run through the Python API");
+  eps = (float)ini.getFloat(type, "layernorm_eps", ini.getFloat(type, "rms_norm_eps", 1e-6));
+  ropeTheta = (float)ini.getFloat(type, "rope_theta", 10000.0);
+  std::string rtype = ini.get(type, "rope_scaling_type", ini.get(type, "rope_type", ""));
+  if (rtype == "linear") ropeFactor = (float)ini.getFloat(type, "rope_scaling_factor", ini.getFloat(type, "scaling_factor", 1.0));
+  else if (!rtype.empty() && rtype != "default") throw std::runtime_error("rope scaling '" + rtype + "' runs through the Python API");
+  endId = (int)ini.getInt(type, "end_id", ini.getInt(type, "start_id", 0));
+  std::string a = ini.get(type, "activation_type", "silu");
+  act = a.rfind("gelu", 0) == 0 ? 3 : a == "relu" ? 1 : 2;
+  qkNorm = ini.getBool(type, "do_qk_norm", false);
+  if (type == "gemma") embedScale = std::sqrt((float)hidden);
+  std::string wdt = ini.get(type, "weight_data_type", "fp16");
+  fileDt = wdt == "fp32" ? 0 : wdt == "bf16" ? 2 : 1;
+  if (ini.get(type, "quant_qweight_data_type", "") != "") throw std::runtime_error("GPTQ checkpoints run through the Python API");
+  if (headDim != 64 && headDim != 128 && headDim != 256) throw std::runtime_error("head size must be 64, 128 or 256");
+
+  XFT_CUDA(cudaStreamCreate(&st));
+  const int qsz = heads * headDim, kvsz = kvHeads * headDim;
+  // embedding and lm_head are stored [vocab, hidden]: convert on the host
+  {
+    auto host = readFile(dir + "/model.wte.bin", (size_t)vocab * hidden * dtypeSize(fileDt));
+    std::vector<uint16_t> b((size_t)vocab * hidden);
+    for (size_t i = 0; i < b.size(); ++i) b[i] = floatToBf16(elemToFloat(host.data(), fileDt, i));
+    wte.reset(b.size() * 2);
+    XFT_CUDA(cudaMemcpy(wte.p, b.data(), b.size() * 2, cudaMemcpyHostToDevice));
+    host = readFile(dir + "/model.lm_head.weight.bin", (size_t)vocab * hidden * dtypeSize(fileDt));
+    for (size_t i = 0; i < b.size(); ++i) b[i] = floatToBf16(elemToFloat(host.data(), fileDt, i));
+    lmHead.reset(b.size() * 2);
+    XFT_CUDA(cudaMemcpy(lmHead.p, b.data(), b.size() * 2, cudaMemcpyHostToDevice));
+  }
+  finalNorm = loadVector("model.final_layernorm.weight.bin", hidden);
+  lw.resize(layers);
+  for (int i = 0; i < layers; ++i) {
+    const std::string p = "model.layers." + std::to_string(i) + ".";
+    LayerWeights& L = lw[i];
+    L.qkv.reset((size_t)(qsz + 2 * kvsz) * hidden * 2);
+    loadLinear(p + "attention.query_key_value.weight.0.bin", hidden, qsz + 2 * kvsz, L.qkv.p, 0, hidden);
+    L.qkvBias = loadVector(p + "attention.query_key_value.bias.0.bin", qsz + 2 * kvsz, true);
+    L.o.reset((size_t)hidden * qsz * 2);
+    loadLinear(p + "attention.dense.weight.0.bin", qsz, hidden, L.o.p, 0, qsz);
+    L.gateUp.reset((size_t)2 * inter * hidden * 2);
+    loadLinear(p + "mlp.gate_proj.weight.0.bin", hidden, inter, L.gateUp.p, 0, hidden);
+    loadLinear(p + "mlp.up_proj.weight.0.bin", hidden, inter, L.gateUp.p, inter, hidden);
+    L.down.reset((size_t)hidden * inter * 2);
+    loadLinear(p + "mlp.down_proj.weight.0.bin", inter, hidden, L.down.p, 0, inter);
+    L.n1 = loadVector(p + "input_layernorm.weight.bin", hidden);
+    L.n2 = loadVector(p + "post_attention_layernorm.weight.bin", hidden);
+    if (qkNorm) {
+      L.qNorm = loadVector(p + "attention.q_norm.weight.bin", headDim);
+      L.kNorm = loadVector(p + "attention.k_norm.weight.bin", headDim);
+    }
+  }
+  // rotary table [maxPos, headDim] = cos(headDim/2) ‖ sin(headDim/2)
+  {
+    std::vector<float> tab((size_t)maxPos * headDim);
+    const int half = headDim / 2;
+    for (int pos = 0; pos < maxPos; ++pos)
+      for (int i = 0; i < half; ++i) {
+        double inv = 1.0 / std::pow((double)ropeTheta, 2.0 * i / headDim) / ropeFactor;
+        tab[(size_t)pos * headDim + i] = (float)std::cos(pos * inv);
+        tab[(size_t)pos * headDim + half + i] = (float)std::sin(pos * inv);
+      }
+    ropeTable.reset(tab.size() * 4);
+    XFT_CUDA(cudaMemcpy(ropeTable.p, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice));
+  }
+  ws.reset(kWsBytes);
+  counters.reset(8192 * 4); XFT_CUDA(cudaMemset(counters.p, 0, counters.bytes));
+  attnCounters.reset(16384 * 4); XFT_CUDA(cudaMemset(attnCounters.p, 0, attnCounters.bytes));
+  status.reset(16); XFT_CUDA(cudaMemset(status.p, 0, 16));
+  tables.reset(new BlockTables(kBlock, 0));
+  kc.resize(layers); vc.resize(layers); ks.resize(layers); vs.resize(layers);
+  rng.seed((unsigned long long)std::chrono::steady_clock::now().time_since_epoch().count());
+}
+
+void Engine::ensureBlocks(int extra) {
+  auto& al = tables->allocator();
+  if (al.numFree() >= extra) return;
+  const int total = std::max(al.numBlocks() - al.numFree() + extra, al.numBlocks() * 3 / 2);
+  const size_t esz = kvInt8 ? 1 : 2;
+  const size_t per = (size_t)kvHeads * kBlock * headDim * esz, sper = (size_t)kvHeads * kBlock * 4;
+  for (int l = 0; l < layers; ++l) {
+    DevBuf nk(per * total), nv(per * total);
+    if (numBlocks) {
+      XFT_CUDA(cudaMemcpy(nk.p, kc[l].p, per * numBlocks, cudaMemcpyDeviceToDevice));
+      XFT_CUDA(cudaMemcpy(nv.p, vc[l].p, per * numBlocks, cudaMemcpyDeviceToDevice));
+    }
+    kc[l] = std::move(nk); vc[l] = std::move(nv);
+    if (kvInt8) {
+      DevBuf a(sper * total), b(sper * total);
+      if (numBlocks) {
+        XFT_CUDA(cudaMemcpy(a.p, ks[l].p, sper * numBlocks, cudaMemcpyDeviceToDevice));
+        XFT_CUDA(cudaMemcpy(b.p, vs[l].p, sper * numBlocks, cudaMemcpyDeviceToDevice));
+      }
+      ks[l] = std::move(a); vs[l] = std::move(b);
+    }
+  }
+  numBlocks = total;
+  al.grow(total);
+}
+
+void Engine::copyBlock(int src, int dst) {
+  const size_t esz = kvInt8 ? 1 : 2;
+  const size_t per = (size_t)kvHeads * kBlock * headDim * esz, sper = (size_t)kvHeads * kBlock * 4;
+  for (int l = 0; l < layers; ++l) {
+    XFT_CUDA(cudaMemcpyAsync(kc[l].as<char>() + per * dst, kc[l].as<char>() + per * src, per, cudaMemcpyDeviceToDevice, st));
+    XFT_CUDA(cudaMemcpyAsync(vc[l].as<char>() + per * dst, vc[l].as<char>() + per * src, per, cudaMemcpyDeviceToDevice, st));
+    if (kvInt8) {
+      XFT_CUDA(cudaMemcpyAsync(ks[l].as<char>() + sper * dst, ks[l].as<char>() + sper * src, sper, cudaMemcpyDeviceToDevice, st));
+      XFT_CUDA(cudaMemcpyAsync(vs[l].as<char>() + sper * dst, vs[l].as<char>() + sper * src, sper, cudaMemcpyDeviceToDevice, st));
+    }
+  }
+}
+
+void Engine::attachPrefix(SequenceMeta& s) {
+  if (prefixSeq < 0) return;
+  const SequenceMeta& pre = pool.get(prefixSeq);
+  const size_t n = pre.prompt.size();
+  if (s.prompt.size() > n && std::equal(pre.prompt.begin(), pre.prompt.end(), s.prompt.begin())) {
+    tables->fork(prefixSeq, s.id);
+    s.pastLen = (int)n;
+    s.pending.assign(s.prompt.begin() + n, s.prompt.end());
+  }
+}
+
+int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
+  std::vector<int> ids, pos, slots, cu{0}, kvl, rowsel;
+  bool decode = true;
+  int maxQ = 0, maxKv = 0;
+  for (int sid : seqIds) {
+    SequenceMeta& s = pool.get(sid);
+    const int n = (int)s.pending.size();
+    if (n == 0) throw std::runtime_error("sequence " + std::to_string(sid) + " has no pending input");
+    if (tables->len(sid) > s.pastLen) tables->truncate(sid, s.pastLen);
+    ensureBlocks((s.pastLen + n + kBlock - 1) / kBlock + 1);
+    auto sl = tables->append(sid, n, [&](int a, int b) { copyBlock(a, b); });
+    for (int i = 0; i < n; ++i) { ids.push_back(s.pending[i]); pos.push_back(s.pastLen + i); slots.push_back(sl[i]); }
+    cu.push_back(cu.back() + n);
+    kvl.push_back(s.pastLen + n);
+    if (n != 1) decode = false;
+    maxQ = std::max(maxQ, n);
+    maxKv = std::max(maxKv, s.pastLen + n);
+    if (logitsAll) for (int i = cu[cu.size() - 2]; i < cu.back(); ++i) rowsel.push_back(i);
+    else rowsel.push_back(cu.back() - 1);
+    if (s.pastLen + n > maxPos) throw std::runtime_error("sequence exceeds max_pos_seq_len");
+  }
+  const int T = (int)ids.size(), B = (int)seqIds.size(), R = (int)rowsel.size();
+  size_t W = 1;
+  for (int sid : seqIds) W = std::max(W, tables->table(sid).size());
+  std::vector<int> bt((size_t)B * W, 0);
+  for (int b = 0; b < B; ++b) { auto& t = tables->table(seqIds[b]); std::copy(t.begin(), t.end(), bt.begin() + (size_t)b * W); }
+  auto up = [&](DevBuf& d, const std::vector<int>& v) {
+    d.ensure(v.size() * 4 + 16);
+    XFT_CUDA(cudaMemcpyAsync(d.p, v.data(), v.size() * 4, cudaMemcpyHostToDevice, st));
+  };
+  up(dIds, ids); up(dPos, pos); up(dSlots, slots); up(dCu, cu); up(dKv, kvl); up(dBt, bt); up(rows, rowsel);
+  XFT_CUDA(cudaStreamSynchronize(st));   // host vectors go out of scope after this call
+  const int qsz = heads * headDim, kvsz = kvHeads * headDim, qkvN = qsz + 2 * kvsz;
+  x.ensure((size_t)T * hidden * 2); x2.ensure((size_t)T * hidden * 2); h.ensure((size_t)T * hidden * 2);
+  qkvBuf.ensure((size_t)T * qkvN * 2); q.ensure((size_t)T * qsz * 2); att.ensure((size_t)T * qsz * 2);
+  g.ensure((size_t)T * inter * 2);
+  int* stp = status.as<int>();
+  auto gemm = [&](const void* X, int K, const void* Wt, int wRows, void* Y, int N, int fp32, int gated, int dualOff,
+                  const float* bias, const void* res, int actc, int rowsT) {
+    XFT_K(xft_gemm_bf16(X, K, Wt, wRows, K, Y, N, fp32, rowsT, N, K, gated, dualOff, bias, res, N, 1.0f, actc, nullptr,
+                        ws.as<float>(), kWsBytes, counters.as<int>(), 8192, stp, 0, st));
+  };
+  XFT_K(xft_embedding(dIds.as<int>(), wte.p, x.p, T, hidden, vocab, embedScale, nullptr, nullptr, 0, 0, stp, st));
+  const int group = std::max(heads / std::max(kvHeads, 1), 1);
+  int nsplit = 1;
+  if (decode) {
+    const int kt = headDim == 64 ? 64 : headDim == 128 ? 32 : 16;
+    const int ntiles = (maxKv + kt - 1) / kt, ctas = B * kvHeads * ((group + 15) / 16);
+    nsplit = std::max(1, std::min({444 / std::max(ctas, 1), ntiles >= 16 ? ntiles / 8 : 1, 32}));
+    if (ctas > 16384) nsplit = 1;
+    if (nsplit > 1) { partO.ensure((size_t)B * heads * nsplit * headDim * 4); partMl.ensure((size_t)B * heads * nsplit * 8); }
+  }
+  const float scale = 1.0f / std::sqrt((float)headDim);
+  void* cur = x.p;
+  void* nxt = x2.p;
+  for (int l = 0; l < layers; ++l) {
+    LayerWeights& L = lw[l];
+    XFT_K(xft_rmsnorm(cur, hidden, nullptr, 0, L.n1.as<float>(), h.p, hidden, nullptr, T, hidden, eps, st));
+    gemm(h.p, hidden, L.qkv.p, qkvN, qkvBuf.p, qkvN, 0, 0, 0, L.qkvBias.as<float>(), nullptr, 0, T);
+    XFT_K(xft_qkv_rope_cache(qkvBuf.p, qkvN, T, heads, kvHeads, headDim, dPos.as<int>(), ropeTable.as<float>(), headDim, 0, 0,
+                             maxPos, nullptr, L.qNorm.as<float>(), L.kNorm.as<float>(), eps, q.p, kc[l].p, vc[l].p,
+                             ks[l].as<float>(), vs[l].as<float>(), kvInt8 ? 1 : 0, kBlock, (long long)numBlocks * kBlock,
+                             dSlots.as<int>(), stp, st));
+    XFT_K(xft_paged_attention(q.p, att.p, kc[l].p, vc[l].p, ks[l].as<float>(), vs[l].as<float>(), dBt.as<int>(), (int)W,
+                              dCu.as<int>(), dKv.as<int>(), B, maxQ, heads, kvHeads, group, 0, headDim, kBlock, numBlocks,
+                              scale, nullptr, nullptr, decode ? 1 : 0, nsplit, partO.as<float>(), partMl.as<float>(),
+                              attnCounters.as<int>(), stp, st));
+    gemm(att.p, qsz, L.o.p, hidden, nxt, hidden, 0, 0, 0, nullptr, cur, 0, T);          // + residual
+    XFT_K(xft_rmsnorm(nxt, hidden, nullptr, 0, L.n2.as<float>(), h.p, hidden, nullptr, T, hidden, eps, st));
+    gemm(h.p, hidden, L.gateUp.p, 2 * inter, g.p, inter, 0, 1, inter, nullptr, nullptr, act, T);
+    gemm(g.p, inter, L.down.p, hidden, cur, hidden, 0, 0, 0, nullptr, nxt, 0, T);        // + residual, back into `cur`
+  }
+  // rows that need logits -> final norm -> lm_head (fp32)
+  h.ensure((size_t)R * hidden * 2);
+  for (int r = 0; r < R; ++r)
+    XFT_CUDA(cudaMemcpyAsync(static_cast<char*>(nxt) + (size_t)r * hidden * 2, static_cast<char*>(cur) + (size_t)rowsel[r] * hidden * 2,
+                             (size_t)hidden * 2, cudaMemcpyDeviceToDevice, st));
+  XFT_K(xft_rmsnorm(nxt, hidden, nullptr, 0, finalNorm.as<float>(), h.p, hidden, nullptr, R, hidden, eps, st));
+  logits.ensure((size_t)R * vocab * 4);
+  gemm(h.p, hidden, lmHead.p, vocab, logits.p, vocab, 1, 0, 0, nullptr, nullptr, 0, R);
+  hostLogits.resize((size_t)R * vocab);
+  XFT_CUDA(cudaMemcpyAsync(hostLogits.data(), logits.p, hostLogits.size() * 4, cudaMemcpyDeviceToHost, st));
+  int hs = 0;
+  XFT_CUDA(cudaMemcpyAsync(&hs, stp, 4, cudaMemcpyDeviceToHost, st));
+  XFT_CUDA(cudaStreamSynchronize(st));
+  if (hs != 0) { cudaMemset(stp, 0, 4); throw std::runtime_error("kernel status " + std::to_string(hs)); }
+  for (int sid : seqIds) { SequenceMeta& s = pool.get(sid); s.pastLen += (int)s.pending.size(); s.pending.clear(); }
+  return R;
+}
+
+// ----------------------------------------------------------------------------------------------------------------
+Model::Model() {}
+Model::~Model() {}
+
+void Model::load(const std::string& path, DataType dt, DataType kv) { engine.reset(new Engine(path, dt, kv)); }
+int Model::getVocabSize() { return engine->vocab; }
+int Model::getMaxSeqLen() { return engine->maxPos; }
+
+void Model::config(int maxLen, int numBeams, int numBeamHypsToKeep, float lenPenalty, bool doEarlyStopping, int eosTokenId,
+                   int padTokenId, bool doSample, float temperature, int topK, float topP, float repetitionPenalty,
+                   const std::vector<std::vector<int>>& stopWordsList) {
+  SearcherConfig c(maxLen, numBeams, numBeamHypsToKeep, lenPenalty, doEarlyStopping, eosTokenId, padTokenId, doSample,
+                   temperature, topK, topP, repetitionPenalty);
+  config(c, stopWordsList);
+}
+void Model::config(SearcherConfig& c, const std::vector<std::vector<int>>& sw) {
+  if (c.numBeams > 1) throw std::runtime_error("beam search runs through the Python API");
+  configuration = c;
+  if (configuration.eosTokenId == -1) configuration.eosTokenId = engine->endId;
+  if (configuration.padTokenId == -1) configuration.padTokenId = configuration.eosTokenId;
+  if (configuration.maxLen <= 0) configuration.maxLen = engine->maxPos;
+  stopWords = cleanStopWords(sw, configuration.eosTokenId);
+  if (c.seed) engine->rng.seed(c.seed);
+}
+bool Model::setStopWords(std::vector<std::vector<int>> sw) { stopWords = cleanStopWords(sw, configuration.eosTokenId); return true; }
+
+void Model::input(std::vector<int32_t>& ids, int batch) {
+  if (batch <= 0 || ids.size() % batch) throw std::invalid_argument("input ids do not divide into the batch");
+  for (int id : engine->working) engine->release(id);
+  engine->working.clear();
+  batchSize = batch;
+  seqLen = (int)ids.size() / batch;
+  for (int b = 0; b < batch; ++b) {
+    std::vector<int32_t> p(ids.begin() + (size_t)b * seqLen, ids.begin() + (size_t)(b + 1) * seqLen);
+    SequenceMeta& s = engine->pool.create(p, std::max(configuration.maxLen, seqLen + 1));
+    engine->tables->add(s.id);
+    engine->attachPrefix(s);
+    engine->working.push_back(s.id);
+  }
+}
+
+std::vector<int> Model::set_input(std::vector<int32_t>& ids, int batch, int maxLen, int numBeams, int numBeamHypsToKeep,
+                                  float lenPenalty, bool doEarlyStopping, int eosTokenId, int padTokenId, bool doSample,
+                                  float temperature, int topK, float topP, float repetitionPenalty,
+                                  const std::vector<std::vector<int>>& sw) {
+  config(maxLen, numBeams, numBeamHypsToKeep, lenPenalty, doEarlyStopping, eosTokenId, padTokenId, doSample, temperature, topK,
+         topP, repetitionPenalty, sw);
+  input(ids, batch);
+  return engine->working;
+}
+std::vector<int> Model::set_input(std::vector<int32_t>& ids, int batch, SearcherConfig& c, const std::vector<std::vector<int>>& sw) {
+  config(c, sw);
+  input(ids, batch);
+  return engine->working;
+}
+std::vector<int> Model::set_input(std::vector<std::vector<int32_t>>& ids, SearcherConfig& c, const std::vector<std::vector<int>>& sw) {
+  config(c, sw);
+  for (int id : engine->working) engine->release(id);
+  engine->working.clear();
+  batchSize = (int)ids.size();
+  seqLen = 0;
+  for (auto& p : ids) {
+    SequenceMeta& s = engine->pool.create(p, std::max(configuration.maxLen, (int)p.size() + 1));
+    engine->tables->add(s.id);
+    engine->attachPrefix(s);
+    engine->working.push_back(s.id);
+    seqLen = std::max(seqLen, (int)p.size());
+  }
+  return engine->working;
+}
+
+std::vector<int> Model::set_input(std::vector<std::vector<int32_t>>& ids, std::vector<int> seqIDs, int maxLen) {
+  engine->cbActive.clear();
+  if (seqIDs.empty()) {
+    for (auto& p : ids) {
+      SequenceMeta& s = engine->pool.create(p, std::max(maxLen > 0 ? maxLen : engine->maxPos, (int)p.size() + 1));
+      engine->tables->add(s.id);
+      engine->attachPrefix(s);
+      engine->cbActive.push_back(s.id);
+    }
+  } else {
+    if (ids.size() != seqIDs.size()) throw std::invalid_argument("one next token per sequence id expected");
+    for (size_t i = 0; i < seqIDs.size(); ++i) {
+      SequenceMeta& s = engine->pool.get(seqIDs[i]);
+      if (ids[i].size() != 1) throw std::invalid_argument("decode inputs carry exactly one token per sequence");
+      s.generated.push_back(ids[i][0]);
+      s.pending.assign(1, ids[i][0]);
+      engine->cbActive.push_back(s.id);
+    }
+  }
+  return engine->cbActive;
+}
+std::vector<int> Model::set_input(std::vector<int32_t>& ids, int batch, std::vector<int> seqIDs, int maxLen) {
+  if (batch <= 0 || ids.size() % batch) throw std::invalid_argument("input ids do not divide into the batch");
+  const size_t n = ids.size() / batch;
+  std::vector<std::vector<int32_t>> rows(batch);
+  for (int b = 0; b < batch; ++b) rows[b].assign(ids.begin() + b * n, ids.begin() + (b + 1) * n);
+  return set_input(rows, seqIDs, maxLen);
+}
+
+std::tuple<float*, int, int> Model::forward(bool logitsAll) {
+  if (engine->cbActive.empty()) throw std::runtime_error("forward() before set_input()");
+  const int rows = engine->forward(engine->cbActive, logitsAll);
+  return std::make_tuple(engine->hostLogits.data(), rows, engine->vocab);
+}
+
+bool Model::isDone() {
+  for (int id : engine->working) if (!engine->pool.get(id).done) return false;
+  return true;
+}
+
+std::vector<int32_t> Model::generate() {
+  if (engine->working.empty()) throw std::runtime_error("generate() before input()/set_input()");
+  std::vector<int> active;
+  for (int id : engine->working) if (!engine->pool.get(id).done) active.push_back(id);
+  std::vector<int32_t> out;
+  if (!active.empty()) {
+    engine->forward(active, false);
+    std::uniform_real_distribution<float> uni(0.f, 1.f);
+    const SearcherConfig& c = configuration;
+    size_t r = 0;
+    for (int id : active) {
+      SequenceMeta& s = engine->pool.get(id);
+      float* l = engine->hostLogits.data() + r++ * engine->vocab;
+      if (c.repetitionPenalty != 1.0f) {
+        std::vector<int32_t> all(s.prompt);
+        all.insert(all.end(), s.generated.begin(), s.generated.end());
+        repetitionPenalty(l, engine->vocab, all, c.repetitionPenalty);
+      }
+      int tok = c.doSample ? sampleTopKTopP(l, engine->vocab, c.topK, c.topP, c.temperature, uni(engine->rng))
+                           : argmaxFirst(l, engine->vocab);
+      s.stepForward(tok);
+      // stop check (src/searchers/sampling.cpp:134-154): eos, or total_len + 1 >= max_len
+      if (tok == c.eosTokenId || s.totalLen() >= s.maxLen || (!stopWords.empty() && matchStopWords(s.generated, stopWords)))
+        s.done = true;
+    }
+  }
+  for (int id : engine->working) {
+    SequenceMeta& s = engine->pool.get(id);
+    bool wasActive = std::find(active.begin(), active.end(), id) != active.end();
+    out.push_back(wasActive ? s.generated.back() : configuration.eosTokenId);
+  }
+  return out;
+}
+
+std::vector<int32_t> Model::finalize() {
+  size_t w = 0;
+  for (int id : engine->working) w = std::max<size_t>(w, engine->pool.get(id).totalLen());
+  std::vector<int32_t> out;
+  for (int id : engine->working) {
+    SequenceMeta& s = engine->pool.get(id);
+    out.insert(out.end(), s.prompt.begin(), s.prompt.end());
+    out.insert(out.end(), s.generated.begin(), s.generated.end());
+    out.insert(out.end(), w - s.totalLen(), configuration.padTokenId);
+    engine->release(id);
+  }
+  engine->working.clear();
+  return out;
+}
+
+bool Model::freeSeqs(std::vector<int>& seqIDs) {
+  for (int id : seqIDs)
+    if (engine->pool.has(id)) engine->release(id);
+  auto& a = engine->cbActive;
+  a.erase(std::remove_if(a.begin(), a.end(), [&](int id) { return !engine->pool.has(id); }), a.end());
+  return true;
+}
+
+void Model::setPrefix(std::vector<int32_t>& prefix) {
+  unsetPrefix();
+  const int n = (int)prefix.size() / 64 * 64;      // whole blocks only: sharers never write into a shared block
+  if (n == 0) return;
+  std::vector<int32_t> p(prefix.begin(), prefix.begin() + n);
+  SequenceMeta& s = engine->pool.create(p, n + 1);
+  engine->tables->add(s.id);
+  engine->forward({s.id}, false);
+  engine->prefixSeq = s.id;
+}
+void Model::unsetPrefix() {
+  if (engine->prefixSeq >= 0) { engine->release(engine->prefixSeq); engine->prefixSeq = -1; }
+}
+
+AutoModel::AutoModel(std::string modelPath, xft::DataType dataType, xft::DataType KVCacheDataType) {
+  load(modelPath, dataType, KVCacheDataType);
+}
+
+}  // namespace xft

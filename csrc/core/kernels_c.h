@@ -1,0 +1,33 @@
+// C ABI of libxft_b200_kernels.so as used by the C++ runtime (definitions: csrc/kernels/*.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+extern "C" {
+int xft_gemm_bf16(const void* X, int ldx, const void* W, int w_rows, int ldw, void* Y, int ldo, int out_fp32, int T, int N,
+                  int K, int gated, int dual_off, const float* bias, const void* residual, int ldr, float res_scale,
+                  int act, const float* row_scale, float* ws, size_t ws_bytes, int* counters, int n_counters, int* status,
+                  int force_splits, cudaStream_t st);
+int xft_embedding(const int* ids, const void* table, void* out, int T, int H, int vocab, float scale, const void* pos_table,
+                  const int* positions, int pos_offset, int npos, int* status, cudaStream_t st);
+int xft_rmsnorm(const void* x, int ldx, const void* res, int ldr, const float* w, void* y, int ldy, void* h_out, int T, int H,
+                float eps, cudaStream_t st);
+int xft_layernorm(const void* x, int ldx, const float* w, const float* b, void* y, int ldy, int T, int H, float eps,
+                  cudaStream_t st);
+int xft_qkv_rope_cache(const void* qkv, int ldq, int T, int hq, int hkv, int D, const int* positions, const float* table,
+                       int rot, int style, int rot_off, int max_pos, const float* q_scale, const float* q_norm_w,
+                       const float* k_norm_w, float eps, void* q_out, void* kc, void* vc, float* ks, float* vs,
+                       int int8_cache, int bs, long long nslots, const int* slots, int* status, cudaStream_t st);
+int xft_rope(void* x, int T, int nh, int D, const int* positions, const float* table, int rot, int style, int rot_off,
+             int max_pos, const float* q_scale, int* status, cudaStream_t st);
+int xft_paged_attention(const void* q, void* out, const void* kc, const void* vc, const float* ks, const float* vs,
+                        const int* block_table, int bt_stride, const int* cu_q, const int* kv_lens, int B, int max_q, int hq,
+                        int hkv, int group, int q_off, int HD, int bs, int num_blocks, float scale, const float* slopes,
+                        const int* prefix_lens, int decode, int nsplit, float* part_o, float* part_ml, int* split_counters,
+                        int* status, cudaStream_t st);
+int xft_argmax(const float* logits, int ld, int rows, int V, float* vals, int* idx, cudaStream_t st);
+int xft_transpose_to_bf16(const void* src, int dtype, long long ld_src, int rows, int cols, void* dst, long long ld_dst,
+                          cudaStream_t st);
+int xft_sample_topk_topp(const float* logits, int ld, int rows, int V, int k, float top_p, float temperature,
+                         const float* uniform, int* out, cudaStream_t st);
+}

@@ -388,3 +388,42 @@ extern "C" int xft_argmax(const float* logits, int ld, int rows, int V, float* v
   cudaError_t e = launch_pdl(argmax_kernel<1024>, dim3(rows), dim3(1024), 0, st, logits, ld, V, vals, idx);
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------------------ load-time layout kernels
+// Checkpoint tensors are [in, out] (fp32 / fp16 / bf16); the device layout is bf16 [out, in].  One pass:
+// convert + transpose through a padded shared-memory tile (reference: MMHelper::convertWeight / packWeight,
+// src/utils/matmul_helper.h:149-562, done on the host there).
+namespace xft {
+template <typename S>
+__device__ __forceinline__ float load_as_float(const S* p);
+template <> __device__ __forceinline__ float load_as_float<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float load_as_float<__half>(const __half* p) { return __half2float(*p); }
+template <> __device__ __forceinline__ float load_as_float<bf16>(const bf16* p) { return __bfloat162float(*p); }
+
+template <typename S>
+__global__ void transpose_to_bf16_kernel(const S* __restrict__ src, long long ld_src, int rows, int cols,
+                                         bf16* __restrict__ dst, long long ld_dst) {
+  __shared__ float tile[32][33];
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int i = threadIdx.y; i < 32; i += 8) {
+    const int r = r0 + i, c = c0 + threadIdx.x;
+    tile[i][threadIdx.x] = (r < rows && c < cols) ? load_as_float<S>(src + (long long)r * ld_src + c) : 0.f;
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += 8) {
+    const int c = c0 + i, r = r0 + threadIdx.x;           // dst[c][r]
+    if (c < cols && r < rows) dst[(long long)c * ld_dst + r] = __float2bfloat16(tile[threadIdx.x][i]);
+  }
+}
+}  // namespace xft
+
+// src: [rows, cols] of dtype (0 fp32, 1 fp16, 2 bf16) on the device -> dst bf16 [cols, rows]
+extern "C" int xft_transpose_to_bf16(const void* src, int dtype, long long ld_src, int rows, int cols, void* dst,
+                                     long long ld_dst, cudaStream_t st) {
+  if (rows <= 0 || cols <= 0) return 0;
+  dim3 grid((cols + 31) / 32, (rows + 31) / 32), block(32, 8);
+  if (dtype == 0) transpose_to_bf16_kernel<float><<<grid, block, 0, st>>>((const float*)src, ld_src, rows, cols, (bf16*)dst, ld_dst);
+  else if (dtype == 1) transpose_to_bf16_kernel<__half><<<grid, block, 0, st>>>((const __half*)src, ld_src, rows, cols, (bf16*)dst, ld_dst);
+  else transpose_to_bf16_kernel<bf16><<<grid, block, 0, st>>>((const bf16*)src, ld_src, rows, cols, (bf16*)dst, ld_dst);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,77 @@
+// Command-line generation with the C++ API (reference: examples/cpp/example.cpp:352-545; token ids in, token ids
+// out — tokenisation is left to the caller, as in the reference's `--input_ids` style use).
+//
+//   example -m <model dir> [-d bf16] [--kv_cache_dtype fp16|int8] [-i "1 2 3 4"] [-b batch] [-o out_len]
+//           [--loop n] [--topK k] [--topP p] [--temperature t] [--repetPen r] [--do_sample] [--no_stream]
+// Prints the generated ids, first-token latency and average next-token latency (the reference's metrics).
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <iostream>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "xft/models.h"
+
+int main(int argc, char** argv) {
+  std::string model, dtype = "bf16", kv = "fp16", input = "1 15043 29892 920 526 366 29973";
+  int batch = 1, outLen = 32, loop = 1, topK = 50;
+  float topP = 1.0f, temp = 1.0f, rep = 1.0f;
+  bool sample = false, stream = true;
+  for (int i = 1; i < argc; ++i) {
+    std::string a = argv[i];
+    auto next = [&]() -> std::string { if (i + 1 >= argc) { std::fprintf(stderr, "missing value for %s\n", a.c_str()); std::exit(2); } return argv[++i]; };
+    if (a == "-m" || a == "--model") model = next();
+    else if (a == "-d" || a == "--dtype") dtype = next();
+    else if (a == "--kv_cache_dtype") kv = next();
+    else if (a == "-i" || a == "--input_ids") input = next();
+    else if (a == "-b" || a == "--batch_size") batch = std::atoi(next().c_str());
+    else if (a == "-o" || a == "--output_len") outLen = std::atoi(next().c_str());
+    else if (a == "-l" || a == "--loop") loop = std::atoi(next().c_str());
+    else if (a == "--topK") topK = std::atoi(next().c_str());
+    else if (a == "--topP") topP = (float)std::atof(next().c_str());
+    else if (a == "--temperature") temp = (float)std::atof(next().c_str());
+    else if (a == "--repetPen") rep = (float)std::atof(next().c_str());
+    else if (a == "--do_sample") sample = true;
+    else if (a == "--no_stream") stream = false;
+    else { std::fprintf(stderr, "unknown flag %s\n", a.c_str()); return 2; }
+  }
+  if (model.empty()) { std::fprintf(stderr, "usage: example -m <model dir> [options]\n"); return 2; }
+  std::vector<int32_t> prompt;
+  { std::istringstream is(input); int v; while (is >> v) prompt.push_back(v); }
+  try {
+    xft::AutoModel m(model, dtype == "fp16" ? xft::DataType::fp16 : xft::DataType::bf16,
+                     kv == "int8" ? xft::DataType::int8 : xft::DataType::fp16);
+    for (int it = 0; it < loop; ++it) {
+      std::vector<int32_t> ids;
+      for (int b = 0; b < batch; ++b) ids.insert(ids.end(), prompt.begin(), prompt.end());
+      m.config((int)prompt.size() + outLen, 1, 1, 1.0f, false, -1, -1, sample, temp, topK, topP, rep);
+      m.input(ids, batch);
+      double first = 0, rest = 0;
+      int steps = 0;
+      while (!m.isDone()) {
+        auto t0 = std::chrono::steady_clock::now();
+        auto next = m.generate();
+        double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+        if (steps == 0) first = ms; else rest += ms;
+        ++steps;
+        if (stream && batch == 1) { std::printf("%d ", next[0]); std::fflush(stdout); }
+      }
+      auto out = m.finalize();
+      if (stream && batch == 1) std::printf("\n");
+      const size_t w = out.size() / batch;
+      for (int b = 0; b < batch; ++b) {
+        std::printf("[%d] ", b);
+        for (size_t i = prompt.size(); i < w; ++i) std::printf("%d ", out[b * w + i]);
+        std::printf("\n");
+      }
+      std::printf("first token: %.2f ms, next tokens: %.2f ms avg over %d\n", first, steps > 1 ? rest / (steps - 1) : 0.0, steps - 1);
+    }
+  } catch (const std::exception& e) {
+    std::fprintf(stderr, "error: %s\n", e.what());
+    return 1;
+  }
+  return 0;
+}

@@ -1,0 +1,104 @@
+"""The C++ runtime twins (libxft_b200_core.so: layout arithmetic, block tables, samplers) against the Python
+implementations, through the C ABI.  No GPU needed."""
+import ctypes as C
+import os
+import random
+
+import pytest
+import torch
+
+from xfastertransformer_b200.ops import reference as R
+from xfastertransformer_b200.parallel import partition as P
+from xfastertransformer_b200.runtime.kv_cache import PagedKVCache
+
+LIB = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "xfastertransformer_b200", "lib",
+                   "libxft_b200_core.so")
+
+
+@pytest.fixture(scope="module")
+def core():
+    if not os.path.exists(LIB):
+        import importlib.util
+        spec = importlib.util.spec_from_file_location("b", os.path.join(os.path.dirname(LIB), "..", "..", "csrc", "build.py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        mod.build()
+    lib = C.CDLL(LIB)
+    lib.xftc_tables_new.restype = C.c_void_p
+    return lib
+
+
+def test_split_util_matches_python(core):
+    out = (C.c_int * 4)()
+    for n in (688, 11008, 28672, 4096, 32000, 14336, 130, 64):
+        for splits in (1, 2, 3, 4, 8):
+            for i in range(splits):
+                core.xftc_task_range(n, splits, i, out)
+                assert (out[0], out[1]) == P.task_range(n, splits, i), (n, splits, i)
+    assert [P.task_range(11008, 8, i)[1] - P.task_range(11008, 8, i)[0] for i in range(8)] == [1408] * 4 + [1344] * 4
+    assert [P.task_range(688, 2, i) for i in range(2)] == [(0, 352), (352, 688)]
+    for q, kv in ((64, 8), (32, 32), (40, 40), (28, 4), (12, 2)):
+        for splits in (1, 2, 3, 4, 8):
+            for i in range(splits):
+                core.xftc_head_range(q, kv, splits, i, out)
+                (a, b), (c, d) = P.head_range(q, kv, splits, i)
+                assert tuple(out) == (a, b, c, d)
+
+
+def test_block_tables_match_python(core):
+    rng = random.Random(0)
+    t = C.c_void_p(core.xftc_tables_new(64, 40))
+    py = PagedKVCache(1, 1, 8, 8, "fp16", torch.device("cpu"), 64, torch.float32)
+    py.ensure_blocks(40)
+    slots = (C.c_int * 512)()
+    cow = (C.c_int * 2)()
+    tab = (C.c_int * 64)()
+    live = []
+    for step in range(300):
+        op = rng.choice(["add", "append", "append", "fork", "free"])
+        if op == "add" and len(live) < 6:
+            sid = step
+            assert core.xftc_tables_add(t, sid) == 0
+            py.add_sequence(sid)
+            live.append(sid)
+        elif op == "append" and live:
+            sid = rng.choice(live)
+            n = rng.randint(1, 90)
+            if py.alloc.num_free < (n + 63) // 64 + 1:
+                continue
+            got = core.xftc_tables_append(t, sid, n, slots, cow)
+            want = py.append_slots(sid, n)
+            assert got == n and list(slots[:n]) == want
+        elif op == "fork" and live and len(live) < 6:
+            src, dst = rng.choice(live), 1000 + step
+            assert core.xftc_tables_fork(t, src, dst) == 0
+            py.tables[dst] = []
+            py.lens[dst] = 0
+            py.fork(src, dst)
+            live.append(dst)
+        elif op == "free" and live:
+            sid = live.pop(rng.randrange(len(live)))
+            core.xftc_tables_free(t, sid)
+            py.free_sequence(sid)
+        assert core.xftc_tables_num_free(t) == py.alloc.num_free
+        for sid in live:
+            n = core.xftc_tables_table(t, sid, tab, 64)
+            assert list(tab[:n]) == py.tables[sid] and core.xftc_tables_len(t, sid) == py.lens[sid]
+    core.xftc_tables_delete(t)
+
+
+def test_samplers_match_reference(core):
+    g = torch.Generator().manual_seed(0)
+    for _ in range(20):
+        l = torch.randn(500, generator=g) * 3
+        arr = (C.c_float * 500)(*l.tolist())
+        assert core.xftc_argmax(arr, 500) == int(l.argmax())
+        u = float(torch.rand(1, generator=g))
+        want = int(R.sample_top_k_top_p(l[None], 40, 0.9, 0.8, torch.tensor([u]))[0])
+        got = core.xftc_sample(arr, 500, 40, C.c_float(0.9), C.c_float(0.8), C.c_float(u))
+        assert got == want
+    l = torch.tensor([2.0, -2.0, 1.0, 0.5])
+    arr = (C.c_float * 4)(*l.tolist())
+    toks = (C.c_int * 4)(0, 1, 1, 9)
+    core.xftc_repetition_penalty(arr, 4, toks, 4, C.c_float(2.0), 0)
+    assert list(arr) == [1.0, -4.0, 1.0, 0.5]
