@@ -1,0 +1,132 @@
+"""Converters against HuggingFace: a random tiny HF model is saved, converted, loaded by the engine (CPU path),
+and the engine's all-position logits must equal the HF model's — orientation, q/k/v merge, w2/w3 swap, norm
+conventions and config keys are all exercised.  Plus a checkpoint round trip through the GPTQ layout."""
+import os
+
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+import xfastertransformer_b200 as xft
+
+
+@pytest.fixture(autouse=True)
+def _cpu(monkeypatch):
+    monkeypatch.setenv("XFT_ENGINE", "CPU")
+
+
+def _roundtrip(hf_model, conv, tmp_path, ids, tol=1.5e-2, dtype="fp32"):   # engine weights are bf16-rounded
+    src = str(tmp_path / "hf")
+    hf_model.save_pretrained(src, safe_serialization=True)
+    out = conv().convert(src, str(tmp_path / "xft"), dtype=dtype)
+    m = xft.AutoModel.from_pretrained(out, dtype="bf16")
+    got = m(ids)
+    with torch.no_grad():
+        want = hf_model(ids).logits.float()
+    assert torch.allclose(got, want, atol=tol, rtol=tol), (got - want).abs().max()
+    return out
+
+
+def test_llama_convert(tmp_path):
+    from transformers import LlamaConfig, LlamaForCausalLM
+    torch.manual_seed(0)
+    cfg = LlamaConfig(vocab_size=512, hidden_size=128, intermediate_size=352, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, max_position_embeddings=256, rms_norm_eps=1e-5, tie_word_embeddings=False)
+    model = LlamaForCausalLM(cfg).eval()
+    ids = torch.randint(0, 512, (2, 17))
+    out = _roundtrip(model, xft.LlamaConvert, tmp_path, ids)
+    from xfastertransformer_b200.config import ModelConfig
+    c = ModelConfig.from_ini(out)
+    assert (c.model_type, c.head_num, c.kv_head_num, c.inter_size, c.layernorm_eps) == ("llama", 4, 2, 352, 1e-5)
+
+
+def test_qwen2_convert_with_bias(tmp_path):
+    from transformers import Qwen2Config, Qwen2ForCausalLM
+    torch.manual_seed(1)
+    cfg = Qwen2Config(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=4, max_position_embeddings=256, tie_word_embeddings=True)
+    model = Qwen2ForCausalLM(cfg).eval()
+    _roundtrip(model, xft.Qwen2Convert, tmp_path, torch.randint(0, 512, (1, 23)))
+
+
+def test_mixtral_convert_swaps_w2_w3(tmp_path):
+    from transformers import MixtralConfig, MixtralForCausalLM
+    torch.manual_seed(2)
+    cfg = MixtralConfig(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                        num_key_value_heads=2, num_local_experts=4, num_experts_per_tok=2, max_position_embeddings=256)
+    model = MixtralForCausalLM(cfg).eval()
+    _roundtrip(model, xft.MixtralConvert, tmp_path, torch.randint(0, 512, (2, 11)))
+
+
+def test_opt_convert(tmp_path):
+    from transformers import OPTConfig, OPTForCausalLM
+    torch.manual_seed(3)
+    cfg = OPTConfig(vocab_size=512, hidden_size=128, ffn_dim=256, num_hidden_layers=2, num_attention_heads=4,
+                    max_position_embeddings=128, word_embed_proj_dim=128, do_layer_norm_before=True)
+    model = OPTForCausalLM(cfg).eval()
+    _roundtrip(model, xft.OPTConvert, tmp_path, torch.randint(3, 512, (2, 13)))
+
+
+def test_gemma_convert(tmp_path):
+    from transformers import GemmaConfig, GemmaForCausalLM
+    torch.manual_seed(4)
+    cfg = GemmaConfig(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=1, head_dim=32, max_position_embeddings=256)
+    model = GemmaForCausalLM(cfg).eval()
+    _roundtrip(model, xft.GemmaConvert, tmp_path, torch.randint(0, 512, (1, 19)))
+
+
+def test_qwen3_convert(tmp_path):
+    try:
+        from transformers import Qwen3Config, Qwen3ForCausalLM
+    except ImportError:
+        pytest.skip("transformers without Qwen3")
+    torch.manual_seed(5)
+    cfg = Qwen3Config(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=48, max_position_embeddings=256, tie_word_embeddings=False)
+    model = Qwen3ForCausalLM(cfg).eval()
+    _roundtrip(model, xft.Qwen3Convert, tmp_path, torch.randint(0, 512, (2, 9)))
+
+
+def test_gptq_layout_roundtrip(tmp_path):
+    """Write a GPTQ-style converted directory by hand (int8 and uint4 qweight + scales + zeros) and load it."""
+    from xfastertransformer_b200.config import ModelConfig
+    from xfastertransformer_b200.ops import reference as R
+    from xfastertransformer_b200.tools.synthetic import preset, write_synthetic_checkpoint
+    import numpy as np
+    for qt in ("int8", "uint4"):
+        d = str(tmp_path / qt)
+        cfg = preset("tiny-llama", vocab_size=512)
+        write_synthetic_checkpoint(d, cfg, seed=0, dtype="fp32", std=0.08)
+        base = xft.AutoModel.from_pretrained(d, dtype="bf16")
+        ids = torch.randint(0, 512, (1, 12))
+        want = base(ids)
+        H, I = cfg.hidden_size, cfg.inter_size
+        q_all = cfg.head_num * cfg.size_per_head + 2 * cfg.kv_head_num * cfg.size_per_head
+        for i in range(cfg.num_layer):
+            for name, (inf, outf) in {"attention.query_key_value": (H, q_all), "attention.dense": (H, H),
+                                      "mlp.gate_proj": (H, I), "mlp.up_proj": (H, I), "mlp.down_proj": (I, H)}.items():
+                f = os.path.join(d, f"model.layers.{i}.{name}.weight.0.bin")
+                w = torch.from_numpy(np.fromfile(f, dtype=np.float32).reshape(inf, outf)).t().contiguous()   # [out,in]
+                if qt == "int8":
+                    q, s, z = R.quantize_int8_per_channel(w)
+                    q.t().contiguous().numpy().tofile(f.replace(".weight.0.bin", ".qweight.0.bin"))
+                else:
+                    p, s, z = R.quantize_uint4_per_channel(w)
+                    qq = R.unpack_nibbles(p).t().contiguous()                    # [in, out], packed along out
+                    R.pack_nibbles(qq).numpy().tofile(f.replace(".weight.0.bin", ".qweight.0.bin"))
+                s.numpy().tofile(f.replace(".weight.0.bin", ".scales.0.bin"))
+                z.numpy().tofile(f.replace(".weight.0.bin", ".zeros.0.bin"))
+                os.remove(f)
+        import configparser
+        cp = configparser.ConfigParser()
+        cp.read(os.path.join(d, "config.ini"))
+        cp["llama"].update({"quant_qweight_data_type": qt, "quant_scales_data_type": "fp32",
+                            "quant_zeros_data_type": "fp32", "quant_groupsize": "-1"})
+        with open(os.path.join(d, "config.ini"), "w") as fh:
+            cp.write(fh)
+        m = xft.AutoModel.from_pretrained(d, dtype="int8" if qt == "int8" else "int4")
+        got = m(ids)
+        rel = (got - want).abs().max().item() / want.abs().max().item()
+        assert rel < (0.1 if qt == "int8" else 0.6), rel
