@@ -1,0 +1,55 @@
+#!/usr/bin/env python
+"""Gradio chat demo (reference: ``examples/web_demo/*.py``, one file per family there; one generic file here since
+the engine is config-driven).  Needs ``gradio`` and a HuggingFace tokenizer directory.
+
+    python examples/web_demo/web_demo.py -m <xft model dir> -t <tokenizer dir> [-d bf16] [--port 7860]
+"""
+import argparse
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("-m", "--model_path", required=True)
+    ap.add_argument("-t", "--token_path", required=True)
+    ap.add_argument("-d", "--dtype", default="bf16")
+    ap.add_argument("--port", type=int, default=7860)
+    a = ap.parse_args()
+    try:
+        import gradio as gr
+    except ImportError:
+        sys.exit("gradio is not installed in this environment: pip install gradio")
+    from transformers import AutoTokenizer
+
+    import xfastertransformer_b200 as xft
+    tok = AutoTokenizer.from_pretrained(a.token_path)
+    model = xft.AutoModel.from_pretrained(a.model_path, dtype=a.dtype)
+    if model.rank != 0:
+        while True:
+            model.generate()
+
+    def chat(message, history, max_new, temperature, top_p):
+        msgs = [{"role": r, "content": c} for u, b in history for r, c in (("user", u), ("assistant", b))]
+        msgs.append({"role": "user", "content": message})
+        try:
+            ids = tok.apply_chat_template(msgs, add_generation_prompt=True, return_tensors="pt")
+        except Exception:
+            ids = tok(message, return_tensors="pt").input_ids
+        model.set_input(ids, max_length=ids.shape[1] + int(max_new), do_sample=temperature > 0, temperature=max(temperature, 1e-3),
+                        top_p=top_p, eos_token_id=tok.eos_token_id or -1)
+        out = []
+        while not model.is_done():
+            out.append(int(model.forward()[0]))
+            yield tok.decode(out, skip_special_tokens=True)
+        model.finalize()
+
+    gr.ChatInterface(chat, additional_inputs=[gr.Slider(16, 2048, 256, label="max new tokens"),
+                                              gr.Slider(0, 2, 0.7, label="temperature"), gr.Slider(0, 1, 0.9, label="top-p")]
+                     ).launch(server_name="0.0.0.0", server_port=a.port)
+
+
+if __name__ == "__main__":
+    main()
