@@ -78,6 +78,10 @@ struct GemmParams {
   const int* num_group_tiles;
   int group_w_rows;
   const float* col_scale;  // optional per-token factor applied to the result (routing weight)
+  // pair != 0 (DUAL instantiation, no gating): the two accumulators are two independent 128-feature tiles
+  // (rows n and n + 128 of W) sharing one token tile — 256 x BN of output per CTA, which halves the
+  // operand bytes per FLOP of the compute-bound (prefill) shapes.
+  int pair;
 };
 
 __device__ __forceinline__ float apply_act(float x, int act) {
@@ -169,6 +173,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
   const int x_row0 = grouped ? s_group[1] : tile_t * BN;            // first token row of this tile
   const int x_rows = grouped ? s_group[2] : BN;                     // valid token rows in this tile
   const bool active = !grouped || x_rows > 0;
+  const int tn_stride = (DUAL && p.pair) ? 256 : 128;      // output features covered per CTA
 
   if (warp == 0) {
     if (lane == 0) {
@@ -183,8 +188,8 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
       for (int i = 0; i < pre; ++i) {
         mbar_expect_tx(&full_bar[i], STAGE_BYTES);
         uint8_t* a = smem + i * STAGE_BYTES;
-        tma_load_2d(a, &tmW, &full_bar[i], (kb0 + i) * 64, w_row0 + tile_n * 128, hint_w);
-        if (DUAL) tma_load_2d(a + A_BYTES, &tmW, &full_bar[i], (kb0 + i) * 64, w_row0 + p.dual_off + tile_n * 128, hint_w);
+        tma_load_2d(a, &tmW, &full_bar[i], (kb0 + i) * 64, w_row0 + tile_n * tn_stride, hint_w);
+        if (DUAL) tma_load_2d(a + A_BYTES, &tmW, &full_bar[i], (kb0 + i) * 64, w_row0 + p.dual_off + tile_n * tn_stride, hint_w);
       }
       grid_dep_wait();
       for (int i = 0; i < pre; ++i)
@@ -196,8 +201,8 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
         if (!mbar_wait(&empty_bar[s], ph ^ 1, p.status, XFT_ERR_WAIT_EMPTY)) break;
         mbar_expect_tx(&full_bar[s], STAGE_BYTES);
         uint8_t* a = smem + s * STAGE_BYTES;
-        tma_load_2d(a, &tmW, &full_bar[s], kb * 64, w_row0 + tile_n * 128, hint_w);
-        if (DUAL) tma_load_2d(a + A_BYTES, &tmW, &full_bar[s], kb * 64, w_row0 + p.dual_off + tile_n * 128, hint_w);
+        tma_load_2d(a, &tmW, &full_bar[s], kb * 64, w_row0 + tile_n * tn_stride, hint_w);
+        if (DUAL) tma_load_2d(a + A_BYTES, &tmW, &full_bar[s], kb * 64, w_row0 + p.dual_off + tile_n * tn_stride, hint_w);
         tma_load_2d(a + A_BYTES * NACC, &tmX, &full_bar[s], kb * 64, x_row0, hint_x);
       }
     }
@@ -228,7 +233,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     // ---------------- epilogue: 4 warps, one TMEM lane (= output feature) per thread -------------
     const int q = warp & 3;
     const int row = q * 32 + lane;
-    const int n = tile_n * 128 + row;
+    const int n = tile_n * tn_stride + row;
     const bool n_ok = n < p.N;
     const int et = threadIdx.x - 64;                    // 0..127 among epilogue threads
     grid_dep_wait();            // scratch, residual and output belong to the stream order from here on
@@ -264,7 +269,10 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     }
     if (last) {
       const float bias_g = (p.bias && n_ok) ? p.bias[n] : 0.f;
-      const float bias_u = (DUAL && p.bias && n_ok) ? p.bias[p.dual_off + n] : 0.f;
+      const bool pair = DUAL && p.pair;
+      const int n2 = n + 128;                            // pair mode: the second tile's feature
+      const bool n2_ok = pair && n2 < p.N;
+      const float bias_u = (DUAL && p.bias && (pair ? n2_ok : n_ok)) ? p.bias[pair ? n2 : p.dual_off + n] : 0.f;
       const float rs = (p.row_scale && n_ok) ? p.row_scale[n] : 1.f;
       const float* ws_tile = p.ws + (size_t)tile_id * (size_t)(BN * NACC) * 128;
       const size_t ws_split_stride = (size_t)(p.n_tiles * p.t_tiles) * (size_t)(BN * NACC) * 128;
@@ -392,7 +400,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                 } else {
                   x = fused_ar ? g[j] + bias_g : g[j] * rs + bias_g;
                   x = apply_act(x, p.act);
-                  if (DUAL) x *= (u[j] * rs + bias_u);
+                  if (DUAL && !pair) x *= (u[j] * rs + bias_u);
                   if (p.col_scale) x *= p.col_scale[t];
                   if (p.residual) x += p.res_scale * __bfloat162float(p.residual[(size_t)t * p.ldr + n]);
                   if (two_shot) {
@@ -404,6 +412,19 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                 }
                 if (p.out_fp32) reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + n] = x;
                 else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)t * p.ldo + n] = __float2bfloat16(x);
+              }
+            }
+          }
+          if (n2_ok) {          // pair mode: second independent tile
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int t = t0 + c + j;
+              if (t < p.T && c + j < x_rows) {
+                float x = apply_act(u[j] + bias_u, p.act);
+                if (p.col_scale) x *= p.col_scale[t];
+                if (p.residual) x += p.res_scale * __bfloat162float(p.residual[(size_t)t * p.ldr + n2]);
+                if (p.out_fp32) reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + n2] = x;
+                else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)t * p.ldo + n2] = __float2bfloat16(x);
               }
             }
           }
@@ -577,6 +598,12 @@ static int gemm_bf16_impl(const void* X, int ldx, const void* W, int w_rows, int
   p.n_tiles = (N + 127) / 128;
   p.t_tiles = (T + bn - 1) / bn;
   p.num_kb = (K + 63) / 64;
+  // compute-bound shapes: one CTA owns two adjacent feature tiles (pair mode) when that still fills the GPU
+  if (!gated && !ar && !row_scale && bn == 256 && ((N + 255) / 256) * p.t_tiles >= 148) {
+    p.pair = 1;
+    p.dual_off = 128;
+    p.n_tiles = (N + 255) / 256;
+  }
   const int tiles = p.n_tiles * p.t_tiles;
   plan_splits(tiles, p.num_kb, bn, gated ? 2 : 1, ws ? ws_bytes : 0, counters ? n_counters : 0, &p.splits, &p.kb_per_split);
   if (force_splits > 0 && ws && counters && tiles <= n_counters) {
@@ -594,7 +621,7 @@ static int gemm_bf16_impl(const void* X, int ldx, const void* W, int w_rows, int
   if (r) return 2000 - r;
 #define XFT_LAUNCH(BN_)                                                        \
   case BN_:                                                                    \
-    return gated ? launch_gemm<BN_, true>(tmW, tmX, p, st) : launch_gemm<BN_, false>(tmW, tmX, p, st);
+    return (gated || p.pair) ? launch_gemm<BN_, true>(tmW, tmX, p, st) : launch_gemm<BN_, false>(tmW, tmX, p, st);
   switch (bn) {
     XFT_LAUNCH(16)
     XFT_LAUNCH(32)

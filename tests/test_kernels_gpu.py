@@ -40,6 +40,23 @@ def test_gemm_bf16(T, N, K):
     _close(got, want, 2e-2, 2e-2, f"gemm {T}x{N}x{K}")
 
 
+@pytest.mark.parametrize("T,N,K", [(4096, 2560, 512), (2500, 3968, 256)])
+def test_gemm_pair_mode(T, N, K):
+    """Compute-bound shapes take the paired-tile path (two 128-feature tiles per CTA); N = 3968 leaves the last
+    pair half empty."""
+    from xfastertransformer_b200.ops import native as N_
+    g = torch.Generator().manual_seed(N)
+    x = (torch.randn(T, K, generator=g) * 0.5).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    bias = torch.randn(N, generator=g) * 0.1
+    res = torch.randn(T, N, generator=g).bfloat16()
+    W = make_linear(w, "bf16")
+    want = R.linear(x.float(), W, bias, "gelu", res.float(), 1.0, out_dtype=torch.float32)
+    got = N_.linear(x.cuda(), W.to("cuda"), bias.cuda(), "gelu", res.cuda(), 1.0)
+    _ws().check_status()
+    _close(got, want, 3e-2, 2e-2, "pair mode")
+
+
 @pytest.mark.parametrize("splits", [2, 3, 8])
 def test_gemm_split_k(splits):
     from xfastertransformer_b200.ops import native as N_
