@@ -26,6 +26,11 @@ DECODE = [
     ("70b tp8 qkv   b16", 16, 1280, 8192, False), ("70b tp8 o     b16", 16, 8192, 1024, False),
     ("70b tp8 gateup b16", 16, 3584, 8192, True), ("70b tp8 down  b16", 16, 8192, 3584, False),
     ("70b tp8 gateup b64", 64, 3584, 8192, True), ("70b tp1 gateup b64", 64, 28672, 8192, True),
+    ("70b tp2 qkv   b16", 16, 5120, 8192, False), ("70b tp2 o     b16", 16, 8192, 4096, False),
+    ("70b tp2 gateup b16", 16, 14336, 8192, True), ("70b tp2 down  b16", 16, 8192, 14336, False),
+    ("70b tp4 gateup b16", 16, 7168, 8192, True), ("70b tp4 down  b16", 16, 8192, 7168, False),
+    ("70b tp8 lmhead b16", 16, 4000, 8192, False), ("7b  tp1 qkv   b16", 16, 12288, 4096, False),
+    ("7b  tp1 gateup b16", 16, 11008, 4096, True), ("7b  tp1 down  b16", 16, 4096, 11008, False),
 ]
 PREFILL = [
     ("70b tp1 qkv   t8192", 8192, 10240, 8192, False), ("70b tp1 gateup t8192", 8192, 28672, 8192, True),
@@ -94,8 +99,30 @@ def run(name, T, Nf, K, gated, iters, peaks):
     N.Workspace.get(torch.device("cuda", 0)).check_status()
 
 
+def sweep(name, T, Nf, K, gated, iters):
+    """Time every split-K factor of one shape (force_splits) next to the planner's own choice (0)."""
+    rows = 2 * Nf if gated else Nf
+    wbytes = rows * K * 2
+    copies = max(4, min(24, (400 << 20) // wbytes + 1))
+    ws = [(torch.randn(rows, K, device="cuda", dtype=torch.bfloat16) * 0.02) for _ in range(copies)]
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(T, Nf, device="cuda", dtype=torch.bfloat16)
+    res = {}
+    for s in (0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 12, 14, 16, 20, 24, 32):
+        if s > max(1, K // 128):
+            break
+
+        def f(i):
+            N.gemm_bf16(x, ws[i], Nf, gated=gated, dual_off=Nf, act="silu" if gated else None, out=out, force_splits=s)
+        res[s] = round(time_fn(f, copies, iters) * 1e3, 2)
+    best = min((v, k) for k, v in res.items() if k)[1]
+    print(json.dumps({"shape": name, "T": T, "N": Nf, "K": K, "gated": gated, "planner_us": res[0], "best_split": best,
+                      "best_us": res[best], "us_by_split": {str(k): v for k, v in res.items() if k}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--sweep-splits", action="store_true", help="time each split-K factor per shape")
     ap.add_argument("--shapes", default="all")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--one", default="")
@@ -111,7 +138,10 @@ def main():
     else:
         shapes = (DECODE if a.shapes in ("decode", "all") else []) + (PREFILL if a.shapes in ("prefill", "all") else [])
     for s in shapes:
-        run(*s, a.iters, peaks)
+        if a.sweep_splits:
+            sweep(*s, a.iters)
+        else:
+            run(*s, a.iters, peaks)
 
 
 if __name__ == "__main__":

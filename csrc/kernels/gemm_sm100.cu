@@ -22,6 +22,7 @@
 // in index order (deterministic) and runs the epilogue.  Nobody spins: there is no wait on a peer.
 #include "ptx.cuh"
 
+#include <cmath>
 #include <mutex>
 #include <unordered_map>
 
@@ -518,7 +519,7 @@ static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, GemmParam
   // small token tiles: keep a CTA under half an SM's shared memory so two CTAs (and twice the
   // loads in flight) share an SM; large tiles take the whole SM
   int budget = (BN <= 64) ? 110 * 1024 : 220 * 1024;
-  if (budget / STAGE_BYTES < 4) budget = 220 * 1024;      // a deep pipeline beats a second resident CTA
+  if (budget / STAGE_BYTES < 3) budget = 220 * 1024;      // a deep pipeline beats a second resident CTA
   int stages = budget / STAGE_BYTES;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) stages = 2;
@@ -542,33 +543,43 @@ int pick_bn(int T) {
   return 256;
 }
 
-// Split-K plan from a small cost model (microseconds):
-//   t(s) = t_fixed + [s > 1] * t_split + waves * (k-blocks per CTA * bytes per k-block * CTAs per wave) / BW(CTAs per wave)
-// BW grows with the number of busy SMs (~70 GB/s for a lone CTA on an SM, ~90 GB/s per SM with two) up to the
-// HBM rate; `waves` charges the tail wave in full; t_split is the price of the partial-tile round trip through
-// scratch plus the arrival counter.  Small problems therefore stay unsplit and large ones avoid a ragged tail.
+// Split-K plan from a cost model (microseconds) whose constants were fitted to a sweep of every split factor on
+// the decode shapes of 7B and 70B models at TP 1/2/4/8 (benchmarks/bench_gemm.py --sweep-splits):
+//   t(s) = 4 + [s > 1] * 2 + s * partial-tile bytes / 25 GB/s + sum over waves of weight bytes / rate(CTAs in the wave)
+//   rate(n) = smooth-min(n * bytes a CTA keeps in flight / 3 us,  min(6.3 TB/s, 90 GB/s * busy SMs))
+// A CTA's pull rate follows from its pipeline depth (Little's law), so few CTAs cannot saturate HBM; a nearly
+// empty tail wave is expensive and a nearly full one is not; the last-arriver reduction grows with the split
+// count and the tile's token width.
 void plan_splits(int tiles, int num_kb, int bn, int nacc, size_t ws_bytes, int max_tiles, int* splits,
                  int* kb_per_split) {
   const int stage_bytes = 128 * 64 * 2 * nacc + bn * 64 * 2;
-  const int slots = (bn <= 64 && (110 * 1024) / stage_bytes >= 4) ? 296 : 148;
+  const double w_stage = 128.0 * 64 * 2 * nacc;   // the token tile comes from L2
+  const bool two_per_sm = bn <= 64 && (110 * 1024) / stage_bytes >= 3;
+  const int slots = two_per_sm ? 296 : 148;
   int best = 1;
   if (tiles < slots && tiles <= max_tiles && ws_bytes > 0) {
     const size_t per_split = (size_t)tiles * bn * nacc * 128 * sizeof(float);
     int smax = num_kb / 2 > 0 ? num_kb / 2 : 1;
     if (smax > 64) smax = 64;
-    const double hbm = 6.4e6;                      // bytes per microsecond
+    int stages = (two_per_sm ? 110 * 1024 : 220 * 1024) / stage_bytes;
+    if (stages > kMaxStages) stages = kMaxStages;
+    const double r_cta = (double)stages * stage_bytes / 3.0;      // bytes per microsecond
+    auto wave = [&](long long n, double kb_avg) {
+      const double cap = fmin(6.3e6, (double)(n < 148 ? n : 148) * 9.0e4);
+      const double nr = (double)n * r_cta;
+      const double rate = pow(pow(cap, -8.0) + pow(nr, -8.0), -1.0 / 8.0);
+      return (double)n * kb_avg * w_stage / rate;
+    };
     double best_t = -1.0;
     for (int s = 1; s <= smax; ++s) {
       if (s > 1 && per_split * s > ws_bytes) break;
       const int per = (num_kb + s - 1) / s;
       const int real = (num_kb + per - 1) / per;
       const long long ctas = (long long)tiles * real;
-      const long long waves = (ctas + slots - 1) / slots;
-      const long long in_wave = ctas < slots ? ctas : slots;
-      const long long sms = in_wave < 148 ? in_wave : 148;
-      double bw = (double)sms * (in_wave >= 296 ? 9.0e4 : in_wave > 148 ? 8.0e4 : 7.0e4);
-      if (bw > hbm) bw = hbm;
-      const double t = 4.0 + (real > 1 ? 3.5 : 0.0) + (double)waves * ((double)per * stage_bytes * (double)in_wave) / bw;
+      const double kb_avg = (double)num_kb / real;
+      const long long full = ctas / slots, tail = ctas % slots;
+      double t = 4.0 + (double)full * wave(slots, kb_avg) + (tail ? wave(tail, kb_avg) : 0.0);
+      if (real > 1) t += 2.0 + (double)real * bn * nacc * 512.0 / 2.5e4;
       if (best_t < 0 || t < best_t) { best_t = t; best = real; }
     }
   }
@@ -634,6 +645,12 @@ static int gemm_bf16_impl(const void* X, int ldx, const void* W, int w_rows, int
 }
 
 extern "C" void xft_set_pdl(int on) { xft::g_xft_pdl = on ? 1 : 0; }
+
+// The split-K planner on its own (host arithmetic only), for tests and tuning.
+extern "C" void xft_plan_splits(int tiles, int num_kb, int bn, int nacc, size_t ws_bytes, int max_tiles, int* splits,
+                                int* kb_per_split) {
+  xft::plan_splits(tiles, num_kb, bn, nacc, ws_bytes, max_tiles, splits, kb_per_split);
+}
 
 extern "C" int xft_gemm_bf16(const void* X, int ldx, const void* W, int w_rows, int ldw, void* Y, int ldo, int out_fp32,
                              int T, int N, int K, int gated, int dual_off, const float* bias, const void* residual,

@@ -102,3 +102,36 @@ def test_samplers_match_reference(core):
     toks = (C.c_int * 4)(0, 1, 1, 9)
     core.xftc_repetition_penalty(arr, 4, toks, 4, C.c_float(2.0), 0)
     assert list(arr) == [1.0, -4.0, 1.0, 0.5]
+
+
+def test_split_k_planner_choices():
+    """The GEMM's split-K planner is host arithmetic: its choices for the 70B decode shapes must land on
+    single-wave grids (tiles x splits <= 296 resident CTAs) and leave full grids unsplit."""
+    import ctypes
+    import os
+    import xfastertransformer_b200 as pkg
+    path = os.path.join(os.path.dirname(pkg.__file__), "lib", "libxft_b200_kernels.so")
+    if not os.path.exists(path):
+        pytest.skip("kernel library not built")
+    try:
+        lib = ctypes.CDLL(path)
+    except OSError as e:
+        pytest.skip(f"kernel library does not load here: {e}")
+    lib.xft_plan_splits.argtypes = [ctypes.c_int] * 4 + [ctypes.c_size_t, ctypes.c_int, ctypes.POINTER(ctypes.c_int),
+                                                         ctypes.POINTER(ctypes.c_int)]
+    lib.xft_plan_splits.restype = None
+
+    def plan(tiles, num_kb, bn=16, nacc=1):
+        s, per = ctypes.c_int(), ctypes.c_int()
+        lib.xft_plan_splits(tiles, num_kb, bn, nacc, 96 << 20, 1024, ctypes.byref(s), ctypes.byref(per))
+        assert (s.value - 1) * per.value < num_kb <= s.value * per.value
+        return s.value
+
+    assert plan(80, 128) == 3           # qkv 10240 x 8192
+    assert plan(64, 128) in (3, 4)      # o_proj
+    assert plan(64, 448) == 4           # down 8192 x 28672
+    assert plan(224, 128, nacc=2) == 1  # gate|up already fills the machine
+    assert plan(250, 128) == 1          # lm_head
+    assert plan(400, 128) == 1          # more tiles than slots: never split
+    assert 8 <= plan(10, 128) <= 16     # a TP=8 slice needs many splits to reach the HBM rate
+    assert plan(28, 128, bn=64, nacc=2) <= 3   # wide token tiles pay for the reduction
