@@ -257,6 +257,10 @@ void Engine::ensureBlocks(int extra) {
   const size_t per = (size_t)kvHeads * kBlock * headDim * esz, sper = (size_t)kvHeads * kBlock * 4;
   for (int l = 0; l < layers; ++l) {
     DevBuf nk(per * total), nv(per * total);
+    // new blocks start zeroed: the TMA decode kernel reads whole tiles and masks rows past kv_len by P = 0,
+    // which needs the masked V rows to be finite
+    XFT_CUDA(cudaMemset(nk.as<char>() + per * numBlocks, 0, per * (total - numBlocks)));
+    XFT_CUDA(cudaMemset(nv.as<char>() + per * numBlocks, 0, per * (total - numBlocks)));
     if (numBlocks) {
       XFT_CUDA(cudaMemcpy(nk.p, kc[l].p, per * numBlocks, cudaMemcpyDeviceToDevice));
       XFT_CUDA(cudaMemcpy(nv.p, vc[l].p, per * numBlocks, cudaMemcpyDeviceToDevice));
@@ -345,9 +349,11 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
   const int group = std::max(heads / std::max(kvHeads, 1), 1);
   int nsplit = 1;
   if (decode) {
-    const int kt = headDim == 64 ? 64 : headDim == 128 ? 32 : 16;
+    // bf16 caches run the TMA-ring kernel (64-key tiles, two CTAs per SM); int8 caches the cp.async kernel
+    const int kt = !kvInt8 ? 64 : headDim == 64 ? 64 : headDim == 128 ? 32 : 16;
+    const int slots = kvInt8 ? 444 : headDim <= 128 ? 296 : 148;
     const int ntiles = (maxKv + kt - 1) / kt, ctas = B * kvHeads * ((group + 15) / 16);
-    nsplit = std::max(1, std::min({444 / std::max(ctas, 1), ntiles >= 16 ? ntiles / 8 : 1, 32}));
+    nsplit = std::max(1, std::min({slots / std::max(ctas, 1), ntiles >= 16 ? ntiles / 8 : 1, 32}));
     if (ctas > 16384) nsplit = 1;
     if (nsplit > 1) { partO.ensure((size_t)B * heads * nsplit * headDim * 4); partMl.ensure((size_t)B * heads * nsplit * 8); }
   }

@@ -13,14 +13,19 @@
 // BS x HD tile, fetched with 16-byte cp.async into XOR-swizzled shared memory and consumed through
 // ldmatrix by mma.sync.m16n8k16 (bf16 in, fp32 accumulate).  Decode is bandwidth-bound (every K/V byte is
 // read once): a CTA owns one kv head of one sequence and a slice of its blocks, the GQA group's query
-// heads are the 16 MMA rows, the four warps walk different blocks and merge at the end; slices are merged
-// by a second tiny kernel.  Prefill gives each warp 16 query rows of one head and shares K/V tiles
+// heads are the 16 MMA rows, the four warps walk different tiles and merge at the end; the slice that arrives
+// last merges all slices.  bf16 caches are fed by TMA into a CTA-wide ring (attn_decode_tma_kernel); int8 caches
+// keep the cp.async path, which converts to bf16 on the way into shared memory.  Prefill gives each warp 16 query rows of one head and shares K/V tiles
 // across the CTA.
 #include "ptx.cuh"
 
 namespace xft {
 
 typedef __nv_bfloat16 bf16;
+
+// gemm_sm100.cu: cached 2-D tensor map with a 128-byte-wide, SWIZZLE_128B box of `box_rows` rows
+int make_tensor_map(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                    uint32_t esize);
 
 struct AttnParams {
   const bf16* q;            // [T, hq, HD]
@@ -71,6 +76,13 @@ __device__ __forceinline__ bf16* tile_ptr(bf16* base, int row, int chunk) {
   return base + row * HD + ((chunk ^ (row & 7)) << 3);
 }
 
+// K/V tile as a TMA box sequence: HD/64 column halves of [rows][64] bf16, each 128-byte row swizzled by the
+// hardware (SWIZZLE_128B: 16-byte chunk index ^= row & 7); `rows` is the tile's key count.
+template <int HD, int KT>
+__device__ __forceinline__ bf16* tile_ptr_tma(bf16* base, int row, int chunk) {
+  return base + (chunk >> 3) * (KT * 64) + row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
+}
+
 // Copy `rows` x HD bf16 from global (row stride = gstride elements) into a swizzled tile; rows >= valid are zeroed.
 template <int HD, int NT>
 __device__ __forceinline__ void load_tile_bf16(bf16* tile, const bf16* g, long long gstride, int rows, int valid, int tid) {
@@ -101,10 +113,15 @@ __device__ __forceinline__ void load_tile_int8(bf16* tile, const int8_t* g, int 
 
 // One warp: 16 query rows (A fragments re-read from the swizzled Q tile) against a KT-key tile.
 // Updates the running max m[2], sum l[2] and O accumulator (two rows per thread: lane/4 and lane/4+8).
-template <int HD, int KT>
+template <int HD, int KT, bool KV_TMA = false, int TROWS = KT>
 struct WarpAttn {
   float m[2], l[2];
   float o[HD / 8][4];
+
+  static __device__ __forceinline__ bf16* kv_ptr(const bf16* base, int row, int chunk) {
+    if (KV_TMA) return tile_ptr_tma<HD, TROWS>(const_cast<bf16*>(base), row, chunk);
+    return tile_ptr<HD>(const_cast<bf16*>(base), row, chunk);
+  }
 
   __device__ __forceinline__ void init() {
     m[0] = m[1] = -INFINITY;
@@ -124,13 +141,10 @@ struct WarpAttn {
     pv(s, vt, lane);
   }
 
-  // phase 1: S = Q K^T, mask, online-softmax update; leaves P (scaled by vscale) in s and rescales O
-  __device__ __forceinline__ void scores(float (&s)[KT / 8][4], const bf16* qtile, const bf16* kt, int key0, int kv_len,
-                                         int qpos0, int qpos1, float scale, float slope0, float slope1, bool use_alibi,
-                                         int prefix_len, const float* kscale, const float* vscale, int lane) {
+  // S = Q K^T for one tile
+  __device__ __forceinline__ void qk(float (&s)[KT / 8][4], const bf16* qtile, const bf16* kt, int lane) {
 #pragma unroll
     for (int j = 0; j < KT / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
-    // S = Q K^T
 #pragma unroll
     for (int ks = 0; ks < HD / 16; ++ks) {
       uint32_t a[4];
@@ -139,13 +153,33 @@ struct WarpAttn {
       for (int j = 0; j < KT / 8; j += 2) {
         // matrices: (keys j*8.., dims ks*16), (keys j*8.., dims ks*16+8), (keys (j+1)*8.., dims ks*16), (.., +8)
         uint32_t b[4];
-        ldsm_x4(b, tile_ptr<HD>(const_cast<bf16*>(kt), j * 8 + (lane & 7) + ((lane >> 4) & 1) * 8, ks * 2 + ((lane >> 3) & 1)));
+        ldsm_x4(b, kv_ptr(kt, j * 8 + (lane & 7) + ((lane >> 4) & 1) * 8, ks * 2 + ((lane >> 3) & 1)));
         mma16816(s[j], a, b[0], b[1]);
         mma16816(s[j + 1], a, b[2], b[3]);
       }
     }
-    // scale, bias, mask; thread holds rows r0 = lane/4 (c0,c1) and r0+8 (c2,c3), key cols j*8 + 2*(lane%4) + {0,1}
-    float mx0 = -INFINITY, mx1 = -INFINITY;
+  }
+
+  // same with the Q fragments already in registers (qa[ks] = the ldmatrix result of k-step ks)
+  __device__ __forceinline__ void qk_frag(float (&s)[KT / 8][4], const uint32_t (&qa)[HD / 16][4], const bf16* kt, int lane) {
+#pragma unroll
+    for (int j = 0; j < KT / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+      for (int j = 0; j < KT / 8; j += 2) {
+        uint32_t b[4];
+        ldsm_x4(b, kv_ptr(kt, j * 8 + (lane & 7) + ((lane >> 4) & 1) * 8, ks * 2 + ((lane >> 3) & 1)));
+        mma16816(s[j], qa[ks], b[0], b[1]);
+        mma16816(s[j + 1], qa[ks], b[2], b[3]);
+      }
+    }
+  }
+
+  // scale, bias, mask; thread holds rows r0 = lane/4 (c0,c1) and r0+8 (c2,c3), key cols j*8 + 2*(lane%4) + {0,1}
+  __device__ __forceinline__ void mask(float (&s)[KT / 8][4], int key0, int kv_len, int qpos0, int qpos1, float scale,
+                                       float slope0, float slope1, bool use_alibi, int prefix_len, const float* kscale,
+                                       int lane) {
 #pragma unroll
     for (int j = 0; j < KT / 8; ++j) {
 #pragma unroll
@@ -157,10 +191,18 @@ struct WarpAttn {
         if (kscale) v *= kscale[kl];
         if (use_alibi) v += ((e < 2) ? slope0 : slope1) * (float)(key - qp);
         const bool vis = key < kv_len && qp >= 0 && (key <= qp || key < prefix_len);
-        v = vis ? v : -INFINITY;
-        s[j][e] = v;
-        if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+        s[j][e] = vis ? v : -INFINITY;
       }
+    }
+  }
+
+  // online-softmax update: leaves P (scaled by vscale) in s, updates m and l, rescales O when a maximum moved
+  __device__ __forceinline__ void softmax_update(float (&s)[KT / 8][4], const float* vscale, int lane) {
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < KT / 8; ++j) {
+      mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+      mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
     }
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
@@ -184,8 +226,19 @@ struct WarpAttn {
     }
     l[0] = l[0] * c0 + sum0;     // per-thread partial row sums; reduced across the quad at the end
     l[1] = l[1] * c1 + sum1;
+    if (__any_sync(0xffffffffu, c0 != 1.f || c1 != 1.f)) {   // after the first tiles the maxima rarely move
 #pragma unroll
-    for (int i = 0; i < HD / 8; ++i) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
+      for (int i = 0; i < HD / 8; ++i) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
+    }
+  }
+
+  // phase 1: S = Q K^T, mask, online-softmax update; leaves P (scaled by vscale) in s and rescales O
+  __device__ __forceinline__ void scores(float (&s)[KT / 8][4], const bf16* qtile, const bf16* kt, int key0, int kv_len,
+                                         int qpos0, int qpos1, float scale, float slope0, float slope1, bool use_alibi,
+                                         int prefix_len, const float* kscale, const float* vscale, int lane) {
+    qk(s, qtile, kt, lane);
+    mask(s, key0, kv_len, qpos0, qpos1, scale, slope0, slope1, use_alibi, prefix_len, kscale, lane);
+    softmax_update(s, vscale, lane);
   }
 
   // phase 2: O += P V
@@ -201,7 +254,7 @@ struct WarpAttn {
       for (int j = 0; j < HD / 8; j += 2) {
         // transposed matrices: (keys ks*16.., dims j*8), (keys ks*16+8.., dims j*8), (keys ks*16.., dims (j+1)*8), (+8, ..)
         uint32_t b[4];
-        ldsm_x4_t(b, tile_ptr<HD>(const_cast<bf16*>(vt), ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, j + (lane >> 4)));
+        ldsm_x4_t(b, kv_ptr(vt, ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, j + (lane >> 4)));
         mma16816(o[j], a, b[0], b[1]);
         mma16816(o[j + 1], a, b[2], b[3]);
       }
@@ -294,6 +347,85 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnParams p) {
       *reinterpret_cast<uint32_t*>(p.out + ((size_t)(q0 + rq0) * p.hq + h) * HD + d) = pack_bf16(wa.o[j][0] * i0, wa.o[j][1] * i0);
     if (rq1 < q_len)
       *reinterpret_cast<uint32_t*>(p.out + ((size_t)(q0 + rq1) * p.hq + h) * HD + d) = pack_bf16(wa.o[j][2] * i1, wa.o[j][3] * i1);
+  }
+}
+
+// Tail of a decode CTA: merge the four consumer warps' (m, l, O) through shared memory `mo` ([4][16][HD+2] floats),
+// then either store the result (nsplit == 1) or write this slice's partial and let the slice that arrives last
+// merge all slices of the (sequence, kv head) — no second kernel, no spinning.  Every thread of the CTA calls it.
+template <int HD, class WA>
+__device__ __forceinline__ void decode_finish(const AttnParams& p, WA& wa, float* mo, bool consumer, int warp, int lane,
+                                              int tid, int nthreads, int nq, int h_lo, int b, int tok, int split) {
+  constexpr int RS = HD + 2;
+  const int r0 = lane >> 2, r1 = r0 + 8;
+  if (consumer) {
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) {
+      const int d = j * 8 + 2 * (lane & 3);
+      mo[(warp * 16 + r0) * RS + d] = wa.o[j][0];
+      mo[(warp * 16 + r0) * RS + d + 1] = wa.o[j][1];
+      mo[(warp * 16 + r1) * RS + d] = wa.o[j][2];
+      mo[(warp * 16 + r1) * RS + d + 1] = wa.o[j][3];
+    }
+    if ((lane & 3) == 0) {
+      mo[(warp * 16 + r0) * RS + HD] = wa.m[0];
+      mo[(warp * 16 + r0) * RS + HD + 1] = wa.l[0];
+      mo[(warp * 16 + r1) * RS + HD] = wa.m[1];
+      mo[(warp * 16 + r1) * RS + HD + 1] = wa.l[1];
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < nq * HD; i += nthreads) {
+    const int r = i / HD, d = i % HD;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, mo[(w * 16 + r) * RS + HD]);
+    float acc = 0.f, ll = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = mo[(w * 16 + r) * RS + HD];
+      const float c = (mw == -INFINITY) ? 0.f : __expf(mw - mm);
+      acc += c * mo[(w * 16 + r) * RS + d];
+      ll += c * mo[(w * 16 + r) * RS + HD + 1];
+    }
+    const int h = h_lo + r;
+    if (p.nsplit == 1) {
+      p.out[((size_t)tok * p.hq + h) * HD + d] = __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
+    } else {
+      const size_t pi = ((size_t)b * p.hq + h) * p.nsplit + split;
+      p.part_o[pi * HD + d] = acc;
+      if (d == 0) { p.part_ml[pi * 2] = mm; p.part_ml[pi * 2 + 1] = ll; }
+    }
+  }
+  if (p.nsplit > 1) {
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      int* c = p.split_counters + (size_t)b * gridDim.y + blockIdx.y;
+      const int old = atomicAdd(c, 1);
+      s_last = (old == p.nsplit - 1);
+      if (s_last) *c = 0;
+    }
+    __syncthreads();
+    if (s_last) {
+      __threadfence();
+      for (int i = tid; i < nq * HD; i += nthreads) {
+        const int r = i / HD, d = i % HD;
+        const int h = h_lo + r;
+        const size_t base = ((size_t)b * p.hq + h) * p.nsplit;
+        float mm = -INFINITY;
+        for (int s = 0; s < p.nsplit; ++s) mm = fmaxf(mm, __ldcg(p.part_ml + (base + s) * 2));
+        float acc = 0.f, ll = 0.f;
+        for (int s = 0; s < p.nsplit; ++s) {
+          const float ms = __ldcg(p.part_ml + (base + s) * 2);
+          const float c = (ms == -INFINITY) ? 0.f : __expf(ms - mm);
+          acc += c * __ldcg(p.part_o + (base + s) * HD + d);
+          ll += c * __ldcg(p.part_ml + (base + s) * 2 + 1);
+        }
+        p.out[((size_t)tok * p.hq + h) * HD + d] = __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
+      }
+    }
   }
 }
 
@@ -401,77 +533,152 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
   cp_async_wait<0>();
   wa.reduce_l();
   __syncthreads();
-  // merge the four warps through shared memory (reuse the K/V buffers): [4][16][HD+2] floats
-  float* mo = reinterpret_cast<float*>(kv);
-  constexpr int RS = HD + 2;
-#pragma unroll
-  for (int j = 0; j < HD / 8; ++j) {
-    const int d = j * 8 + 2 * (lane & 3);
-    mo[(warp * 16 + r0) * RS + d] = wa.o[j][0];
-    mo[(warp * 16 + r0) * RS + d + 1] = wa.o[j][1];
-    mo[(warp * 16 + r1) * RS + d] = wa.o[j][2];
-    mo[(warp * 16 + r1) * RS + d + 1] = wa.o[j][3];
+  decode_finish<HD>(p, wa, reinterpret_cast<float*>(kv), true, warp, lane, tid, 128, nq, h_lo, b, tok, split);
+}
+
+// ------------------------------------------------------------------------------------------ decode, TMA ring
+// bf16 caches.  grid (B, hkv * qchunks, nsplit); 160 threads: one lane of warp 4 feeds a CTA-wide ring of 64-key
+// K/V tiles with TMA (a tile is one box per 64-column half of 64 cache rows, hardware-swizzled, so no thread
+// computes a load address); warps 0-3 each take 16 keys of every tile, so all four wait on the same barrier in the
+// same order (a waiter is never more than one phase away from its barrier) and release the stage with one arrival
+// each.  About 96 KB of tiles are in flight per CTA and two CTAs share an SM, which covers the HBM latency without
+// any warp waiting on its own request.
+// Rows of a block past kv_len hold finite stale data (the pool starts zeroed), so P = 0 masks them exactly.
+constexpr int kDecTile = 64;            // keys per ring stage (= the cache block size granule)
+constexpr int kDecMaxBlocks = 512;      // block ids of this CTA's slice cached in shared memory
+template <int HD>
+struct DecCfg {
+  static constexpr int STAGE_BYTES = 2 * kDecTile * HD * 2;
+  static constexpr int STAGES = (96 * 1024) / STAGE_BYTES >= 3 ? (96 * 1024) / STAGE_BYTES : 3;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(160, (HD <= 128 ? 2 : 1)) attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK,
+                                                                                  const __grid_constant__ CUtensorMap tmV,
+                                                                                  const AttnParams p) {
+  constexpr int KT = kDecTile, KW = KT / 4;             // keys per tile, keys per warp and tile
+  constexpr int TILE = KT * HD;                         // elements of one K (or V) tile
+  constexpr int STAGES = DecCfg<HD>::STAGES;
+  constexpr uint32_t STAGE_BYTES = DecCfg<HD>::STAGE_BYTES;
+  extern __shared__ __align__(1024) uint8_t smem_dyn[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  bf16* ring = reinterpret_cast<bf16*>(base);                               // [STAGES][K tile | V tile]
+  bf16* qs = reinterpret_cast<bf16*>(base + (size_t)STAGES * STAGE_BYTES);  // [16][HD]
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES];
+  __shared__ int s_blk[kDecMaxBlocks];
+  __shared__ int s_abort;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    for (int i = 0; i < STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 4); }
+    s_abort = 0;
+    fence_barrier_init();
   }
-  if ((lane & 3) == 0) {
-    mo[(warp * 16 + r0) * RS + HD] = wa.m[0];
-    mo[(warp * 16 + r0) * RS + HD + 1] = wa.l[0];
-    mo[(warp * 16 + r1) * RS + HD] = wa.m[1];
-    mo[(warp * 16 + r1) * RS + HD + 1] = wa.l[1];
+  if (warp == 4 && lane == 0) { tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); }
+  grid_dep_launch();
+  grid_dep_wait();
+  const int b = blockIdx.x;
+  const int qchunks = (p.group + 15) / 16;
+  const int kvh = blockIdx.y / qchunks, qc = blockIdx.y % qchunks;
+  const int split = blockIdx.z;
+  const int kv_len = p.kv_lens[b];
+  const int tok = p.cu_q[b];
+  const int h_lo = max(0, kvh * p.group - p.q_off) + qc * 16;
+  const int h_hi = min(min(p.hq, (kvh + 1) * p.group - p.q_off), h_lo + 16);
+  const int nq = h_hi - h_lo;
+  if (nq <= 0) return;
+  const int ntiles = (kv_len + KT - 1) / KT;
+  const int per = (ntiles + p.nsplit - 1) / p.nsplit;
+  const int t_begin = split * per, t_end = min(ntiles, t_begin + per);
+  const int nloc = max(t_end - t_begin, 0);
+  const int* bt = p.block_table + (size_t)b * p.bt_stride;
+  const int tiles_per_block = p.bs / KT;
+
+  if (tid < 128) load_tile_bf16<HD, 128>(qs, p.q + ((size_t)tok * p.hq + h_lo) * HD, HD, 16, nq, tid);
+  cp_async_commit();
+  const int blk_first = t_begin / tiles_per_block;
+  const int nblk = nloc > 0 ? (t_end - 1) / tiles_per_block - blk_first + 1 : 0;
+  for (int i = tid; i < min(nblk, kDecMaxBlocks); i += 160) {
+    int blk = bt[blk_first + i];
+    if (blk < 0 || blk >= p.num_blocks) { if (p.status) atomicCAS(p.status, 0, XFT_ERR_BOUNDS); blk = 0; }
+    s_blk[i] = blk;
   }
+  cp_async_wait<0>();
   __syncthreads();
-  for (int i = tid; i < nq * HD; i += 128) {
-    const int r = i / HD, d = i % HD;
-    float mm = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, mo[(w * 16 + r) * RS + HD]);
-    float acc = 0.f, ll = 0.f;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float mw = mo[(w * 16 + r) * RS + HD];
-      const float c = (mw == -INFINITY) ? 0.f : __expf(mw - mm);
-      acc += c * mo[(w * 16 + r) * RS + d];
-      ll += c * mo[(w * 16 + r) * RS + HD + 1];
-    }
-    const int h = h_lo + r;
-    if (p.nsplit == 1) {
-      p.out[((size_t)tok * p.hq + h) * HD + d] = __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
-    } else {
-      const size_t pi = ((size_t)b * p.hq + h) * p.nsplit + split;
-      p.part_o[pi * HD + d] = acc;
-      if (d == 0) { p.part_ml[pi * 2] = mm; p.part_ml[pi * 2 + 1] = ll; }
-    }
-  }
-  if (p.nsplit > 1) {
-    // the slice that arrives last merges all slices of this (sequence, kv head): no second kernel, no spinning
-    __shared__ int s_last;
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-      int* c = p.split_counters + (size_t)b * gridDim.y + blockIdx.y;
-      const int old = atomicAdd(c, 1);
-      s_last = (old == p.nsplit - 1);
-      if (s_last) *c = 0;
-    }
-    __syncthreads();
-    if (s_last) {
-      __threadfence();
-      for (int i = tid; i < nq * HD; i += 128) {
-        const int r = i / HD, d = i % HD;
-        const int h = h_lo + r;
-        const size_t base = ((size_t)b * p.hq + h) * p.nsplit;
-        float mm = -INFINITY;
-        for (int s = 0; s < p.nsplit; ++s) mm = fmaxf(mm, __ldcg(p.part_ml + (base + s) * 2));
-        float acc = 0.f, ll = 0.f;
-        for (int s = 0; s < p.nsplit; ++s) {
-          const float ms = __ldcg(p.part_ml + (base + s) * 2);
-          const float c = (ms == -INFINITY) ? 0.f : __expf(ms - mm);
-          acc += c * __ldcg(p.part_o + (base + s) * HD + d);
-          ll += c * __ldcg(p.part_ml + (base + s) * 2 + 1);
+
+  WarpAttn<HD, KW, true, KT> wa;
+  wa.init();
+  if (warp == 4) {
+    if (lane == 0) {
+      for (int n = 0; n < nloc; ++n) {
+        const int st = n % STAGES;
+        if (!mbar_wait(&empty_bar[st], ((n / STAGES) & 1) ^ 1, p.status, XFT_ERR_WAIT_EMPTY)) { s_abort = 1; break; }
+        const int ti = t_begin + n;
+        const int bi = ti / tiles_per_block - blk_first;
+        int blk;
+        if (bi < kDecMaxBlocks) {
+          blk = s_blk[bi];
+        } else {
+          blk = bt[blk_first + bi];
+          if (blk < 0 || blk >= p.num_blocks) { if (p.status) atomicCAS(p.status, 0, XFT_ERR_BOUNDS); blk = 0; }
         }
-        p.out[((size_t)tok * p.hq + h) * HD + d] = __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
+        const int row = (blk * p.hkv + kvh) * p.bs + (ti % tiles_per_block) * KT;
+        bf16* kt = ring + (size_t)st * 2 * TILE;
+        mbar_expect_tx(&full_bar[st], STAGE_BYTES);
+#pragma unroll
+        for (int h = 0; h < HD / 64; ++h) {
+          tma_load_2d(kt + h * KT * 64, &tmK, &full_bar[st], h * 64, row, kEvictFirst);
+          tma_load_2d(kt + TILE + h * KT * 64, &tmV, &full_bar[st], h * 64, row, kEvictFirst);
+        }
       }
     }
+  } else {
+    const int r0 = lane >> 2, r1 = r0 + 8;
+    const int qpos = kv_len - 1;
+    const int qpos0 = r0 < nq ? qpos : -1, qpos1 = r1 < nq ? qpos : -1;
+    const bool use_alibi = p.slopes != nullptr;
+    const float slope0 = (use_alibi && r0 < nq) ? p.slopes[h_lo + r0] : 0.f;
+    const float slope1 = (use_alibi && r1 < nq) ? p.slopes[h_lo + r1] : 0.f;
+    constexpr bool QREG = HD <= 128;            // Q fragments live in registers when they fit
+    uint32_t qa[QREG ? HD / 16 : 1][4];
+    if (QREG) {
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks)
+        ldsm_x4(qa[QREG ? ks : 0], tile_ptr<HD>(qs, (lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4)));
+    }
+    for (int n = 0; n < nloc; ++n) {
+      const int st = n % STAGES;
+      if (!mbar_wait(&full_bar[st], (n / STAGES) & 1, p.status, XFT_ERR_WAIT_FULL)) { s_abort = 1; break; }
+      // this warp's 16 keys of the tile: rows warp*16 .. +15 of both halves (the row offset keeps row & 7)
+      const bf16* kt = ring + (size_t)st * 2 * TILE + warp * KW * 64;
+      const int key0 = (t_begin + n) * KT + warp * KW;
+      if (key0 < kv_len) {
+        float s[KW / 8][4];
+        if constexpr (QREG) wa.qk_frag(s, reinterpret_cast<const uint32_t (&)[HD / 16][4]>(qa), kt, lane);
+        else wa.qk(s, qs, kt, lane);
+        if (use_alibi || key0 + KW > kv_len) {
+          wa.mask(s, key0, kv_len, qpos0, qpos1, p.scale, slope0, slope1, use_alibi, 0, nullptr, lane);
+        } else {
+          // every key is visible; rows past nq carry a zero query and are never stored
+#pragma unroll
+          for (int j = 0; j < KW / 8; ++j) { s[j][0] *= p.scale; s[j][1] *= p.scale; s[j][2] *= p.scale; s[j][3] *= p.scale; }
+        }
+        wa.softmax_update(s, nullptr, lane);
+        wa.pv(s, kt + TILE, lane);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[st]);
+    }
+    wa.reduce_l();
   }
+  __syncthreads();
+  if (s_abort) {
+    // a wait ran out (status holds the reason): let copies already issued land before the CTA's memory is released
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) {}
+    return;
+  }
+  // every issued tile was consumed, so the ring is idle and can carry the merge
+  decode_finish<HD>(p, wa, reinterpret_cast<float*>(ring), warp < 4, warp, lane, tid, 160, nq, h_lo, b, tok, split);
 }
 
 // merge split partials: grid (B, hq), HD threads
@@ -528,7 +735,26 @@ static int launch_decode(const AttnParams& p, int B, bool int8, cudaStream_t st)
   return (int)cudaGetLastError();
 }
 
-// decode != 0: every sequence has exactly one query row.  nsplit/part_*: split-KV scratch (decode only).
+template <int HD>
+static int launch_decode_tma(const AttnParams& p, int B, cudaStream_t st) {
+  CUtensorMap tmK, tmV;
+  const uint64_t rows = (uint64_t)p.num_blocks * p.hkv * p.bs;
+  if (make_tensor_map(&tmK, p.kc, rows, HD, HD, kDecTile, 2) || make_tensor_map(&tmV, p.vc, rows, HD, HD, kDecTile, 2)) return -4;
+  const size_t smem = (size_t)DecCfg<HD>::STAGES * DecCfg<HD>::STAGE_BYTES + 16 * HD * 2 + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(attn_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return -5;
+    attr_set = true;
+  }
+  const int qchunks = (p.group + 15) / 16;
+  dim3 grid(B, p.hkv * qchunks, p.nsplit);
+  cudaError_t e = launch_pdl(attn_decode_tma_kernel<HD>, grid, dim3(160), smem, st, tmK, tmV, p);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaGetLastError();
+}
+
+// decode != 0: every sequence has exactly one query row (2 forces the cp.async kernel for bf16 caches too).  nsplit/part_*: split-KV scratch (decode only).
 extern "C" int xft_paged_attention(const void* q, void* out, const void* kc, const void* vc, const float* ks, const float* vs,
                                    const int* block_table, int bt_stride, const int* cu_q, const int* kv_lens, int B,
                                    int max_q, int hq, int hkv, int group, int q_off, int HD, int bs, int num_blocks,
@@ -544,6 +770,12 @@ extern "C" int xft_paged_attention(const void* q, void* out, const void* kc, con
   if (bs % 64) return -2;
   if (decode) {
     if (p.nsplit > 1 && (!part_o || !part_ml || !split_counters)) return -3;
+    if (!int8 && decode != 2) {
+      if (HD == 64) return launch_decode_tma<64>(p, B, st);
+      if (HD == 128) return launch_decode_tma<128>(p, B, st);
+      if (HD == 256) return launch_decode_tma<256>(p, B, st);
+      return -1;
+    }
     // per-warp K+V tiles of 16 KB: a CTA stays at ~64 KB so three CTAs (12 warps) overlap loads and math per SM
     if (HD == 64) return launch_decode<64, 64>(p, B, int8, st);
     if (HD == 128) return launch_decode<128, 32>(p, B, int8, st);

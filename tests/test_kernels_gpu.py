@@ -218,6 +218,41 @@ def test_attention_decode(int8, D, hq, hkv):
     _close(got, want, 2e-2, 2e-2, "split-KV decode attention")
 
 
+@pytest.mark.parametrize("tma", [True, False])
+@pytest.mark.parametrize("alibi", [False, True])
+def test_attention_decode_long_context_both_kernels(tma, alibi):
+    """bf16 decode through the TMA-ring kernel and through the cp.async kernel: long ragged contexts (ring wraps
+    several times, last tile partial), GQA group 8, ALiBi, planned and forced split counts."""
+    from xfastertransformer_b200.ops import native as N_
+    from xfastertransformer_b200.utils.flags import Env
+    g = torch.Generator().manual_seed(11)
+    D, hq, hkv = 128, 16, 2
+    kv_lens = [2060, 4097, 130, 33, 3000]
+    B, bs = len(kv_lens), 64
+    kc, vc, _, _, bt = _fill_paged(B, kv_lens, hkv, D, bs, False, g)
+    q = torch.randn(B, hq, D, generator=g).bfloat16()
+    cu = list(range(B + 1))
+    scale = 1 / math.sqrt(D)
+    sl = R.alibi_slopes(hq) if alibi else None
+    want = R.paged_attention(q.float(), kc, vc, bt, cu, kv_lens, scale, None, None, sl)
+    env = Env.get()
+    old = env.attn_tma
+    env.attn_tma = tma
+    try:
+        for ns in (None, 1, 2, 3, 7):
+            class M:
+                cu_q_dev = torch.tensor(cu, dtype=torch.int32, device="cuda")
+                kv_lens_dev = torch.tensor(kv_lens, dtype=torch.int32, device="cuda")
+                is_decode, max_q, max_kv = True, 1, max(kv_lens)
+                meta = {} if ns is None else {"nsplit": ns}
+            got = N_.paged_attention(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), cu, kv_lens, scale,
+                                     slopes=None if sl is None else sl.cuda(), meta=M)
+            _ws().check_status()
+            _close(got, want, 4e-3, 1e-2, f"decode tma={tma} alibi={alibi} nsplit={ns}")
+    finally:
+        env.attn_tma = old
+
+
 @pytest.mark.parametrize("int8", [False, True])
 @pytest.mark.parametrize("D,hq,hkv", [(128, 8, 2), (64, 4, 4), (256, 2, 1)])
 def test_attention_prefill(int8, D, hq, hkv):

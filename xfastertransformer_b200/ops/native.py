@@ -29,6 +29,11 @@ class KernelError(RuntimeError):
     pass
 
 
+def _ENV():
+    from ..utils.flags import Env
+    return Env.get()
+
+
 def lib_path() -> str:
     return os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib", "libxft_b200_kernels.so")
 
@@ -257,6 +262,21 @@ def latent_cache_write(latent, cache, slots):
     ws.launches += 1
 
 
+def plan_attn_splits(B, hkv, group, D, max_kv, int8=False):
+    """Split-KV factor of a decode launch and the tile count it was planned on: fill the resident CTA slots (two
+    CTAs per SM for the TMA-ring kernel of bf16 caches, three for the cp.async kernel of int8 caches) while leaving
+    every slice at least eight tiles."""
+    tma = not int8 and _ENV().attn_tma
+    kt = 64 if tma else {64: 64, 128: 32, 256: 16}[D]
+    slots = (296 if D <= 128 else 148) if tma else 444
+    ntiles = (max_kv + kt - 1) // kt
+    ctas = B * max(hkv, 1) * ((group + 15) // 16)
+    nsplit = max(1, min(slots // max(ctas, 1), ntiles // 8 if ntiles >= 16 else 1, 32))
+    if _ENV().attn_splits > 0:
+        nsplit = max(1, min(_ENV().attn_splits, ntiles, 32))
+    return nsplit, ntiles
+
+
 def paged_attention(q, kc, vc, block_table, cu_q, kv_lens, scale, ks=None, vs=None, slopes=None, causal=True,
                     prefix_lm_lens=None, group=None, q_off=0, meta=None):
     assert causal
@@ -281,10 +301,7 @@ def paged_attention(q, kc, vc, block_table, cu_q, kv_lens, scale, ks=None, vs=No
     out = torch.empty_like(q)
     nsplit, po, pm = 1, None, None
     if decode:
-        kt = {64: 64, 128: 32, 256: 16}[D]
-        ntiles = (max_kv + kt - 1) // kt
-        ctas = B * hkv * ((g + 15) // 16)
-        nsplit = max(1, min(444 // max(ctas, 1), ntiles // 8 if ntiles >= 16 else 1, 32))
+        nsplit, ntiles = plan_attn_splits(B, hkv, g, D, max_kv, ks is not None)
         if meta is not None and getattr(meta, "meta", None) is not None and "nsplit" in meta.meta:
             nsplit = meta.meta["nsplit"]
         if B * hkv * ((g + 15) // 16) > ws.attn_counters.numel():
@@ -294,7 +311,7 @@ def paged_attention(q, kc, vc, block_table, cu_q, kv_lens, scale, ks=None, vs=No
     q = q.contiguous()
     rc = lib().xft_paged_attention(_p(q), _p(out), _p(kc), _p(vc), _p(ks), _p(vs), _p(block_table),
                                    block_table.stride(0), _p(cu_dev), _p(kv_dev), B, max_q, hq, hkv, g, q_off, D, bs,
-                                   nb, C.c_float(scale), _p(slopes), _p(pl), int(decode), nsplit, _p(po), _p(pm),
+                                   nb, C.c_float(scale), _p(slopes), _p(pl), (1 if _ENV().attn_tma else 2) if decode else 0, nsplit, _p(po), _p(pm),
                                    _p(ws.attn_counters), _p(ws.status), _stream())
     _check(rc, "paged_attention")
     ws.launches += 1

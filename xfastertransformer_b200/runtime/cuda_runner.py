@@ -72,11 +72,9 @@ class CudaRunner:
         g.tok_host = torch.zeros(B, dtype=torch.int64).pin_memory()
         g.host[o_cu:o_cu + B + 1] = torch.arange(B + 1, dtype=torch.int32)
         d = g.dev
-        kt = {64: 64, 128: 32, 256: 16}.get(m.decoder.D, 32)
         dec = m.decoder
-        ctas = B * max(dec.hkv, 1) * ((dec.group + 15) // 16)
-        ntiles = (max_kv_hint + kt - 1) // kt
-        g.nsplit = max(1, min(444 // max(ctas, 1), ntiles // 8 if ntiles >= 16 else 1, 32))
+        from ..ops import native as N
+        g.nsplit, _ = N.plan_attn_splits(B, max(dec.hkv, 1), dec.group, dec.D, max_kv_hint, m.cache.int8)
         b = Batch(ids=d[o_ids:o_ids + B], positions=d[o_pos:o_pos + B], slots=d[o_slot:o_slot + B],
                   cu_q=list(range(B + 1)), kv_lens=[max_kv_hint] * B, block_table=d[o_bt:o_bt + B * W].view(B, W),
                   logit_rows=None, is_decode=True, max_q=1, max_kv=max_kv_hint)
