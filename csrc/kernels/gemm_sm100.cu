@@ -83,6 +83,14 @@ struct GemmParams {
   // (rows n and n + 128 of W) sharing one token tile — 256 x BN of output per CTA, which halves the
   // operand bytes per FLOP of the compute-bound (prefill) shapes.
   int pair;
+  // rms_x != null: the GEMM input is the un-normalised hidden state and the RMSNorm gain is already folded into W's
+  // columns, so  RMSNorm(x) W^T = rsqrt(mean(x^2) + eps) * (x W'^T): the epilogue warps compute each token's sum
+  // of squares over this CTA's K slice while the main loop runs (split-K slices add up through rms_ws) and apply
+  // the factor to the accumulator.  Only for token tiles of at most 64 rows (decode).
+  const __nv_bfloat16* rms_x;
+  int rms_ldx;
+  float rms_eps;
+  float* rms_ws;           // [tile][split][BN] partial sums of squares
 };
 
 __device__ __forceinline__ float apply_act(float x, int act) {
@@ -117,6 +125,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_last;
   __shared__ int s_epoch, s_peer_fail;
+  __shared__ float s_ssq[64];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int stages = p.stages;
@@ -239,6 +248,32 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     const int et = threadIdx.x - 64;                    // 0..127 among epilogue threads
     grid_dep_wait();            // scratch, residual and output belong to the stream order from here on
     if (p.ar.world > 1 && et == 0) s_epoch = *reinterpret_cast<volatile int*>(p.ar.epoch) + 1;
+    const bool rms = BN <= 64 && p.rms_x != nullptr;
+    if (BN <= 64 && rms) {
+      // sum of squares of this CTA's K slice for each of its BN tokens: 128 / BN threads per token, 16-byte loads
+      constexpr int TPT = 128 / (BN <= 64 ? BN : 64);
+      const int tok = et / TPT, sub = et % TPT;
+      const int t = x_row0 + tok;
+      const int k_begin = kb0 * 64, k_end = min(kb1 * 64, p.K);
+      float acc = 0.f;
+      if (t < p.T) {
+        const __nv_bfloat16* xr = p.rms_x + (size_t)t * p.rms_ldx;
+#pragma unroll 4
+        for (int k = k_begin + sub * 8; k < k_end; k += TPT * 8) {
+          const uint4 v = __ldg(reinterpret_cast<const uint4*>(xr + k));
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h[i]);
+            acc += f.x * f.x + f.y * f.y;
+          }
+        }
+      }
+#pragma unroll
+      for (int o = TPT / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (sub == 0) s_ssq[tok] = acc;
+      named_bar_sync(1, 128);
+    }
     bool ok = active && mbar_wait(&tmem_full_bar, 0, p.status, XFT_ERR_WAIT_TMEM);
     tcgen05_fence_after();
     const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16);
@@ -257,6 +292,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
           for (int j = 0; j < 16; ++j) wsp[(size_t)(c + j) * 128 + row] = __uint_as_float(v[j]);
         }
       }
+      if (BN <= 64 && rms && et < BN) p.rms_ws[((size_t)tile_id * p.splits + split) * BN + et] = s_ssq[et];
       __threadfence();
       named_bar_sync(1, 128);
       if (et == 0) {
@@ -267,6 +303,14 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
       named_bar_sync(1, 128);
       last = s_last != 0;
       if (last) __threadfence();
+      if (BN <= 64 && rms && last) {
+        if (et < BN) {
+          float a = 0.f;
+          for (int sp = 0; sp < p.splits; ++sp) a += __ldcg(p.rms_ws + ((size_t)tile_id * p.splits + sp) * BN + et);
+          s_ssq[et] = a;
+        }
+        named_bar_sync(1, 128);
+      }
     }
     if (last) {
       const float bias_g = (p.bias && n_ok) ? p.bias[n] : 0.f;
@@ -399,9 +443,10 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                 if (fused_ar && !i_reduce) {
                   x = g[j];                     // finished by the owner
                 } else {
-                  x = fused_ar ? g[j] + bias_g : g[j] * rs + bias_g;
+                  const float ts = (BN <= 64 && rms) ? rsqrtf(s_ssq[(c + j) & 63] / (float)p.K + p.rms_eps) : 1.f;
+                  x = fused_ar ? g[j] + bias_g : g[j] * (rs * ts) + bias_g;
                   x = apply_act(x, p.act);
-                  if (DUAL && !pair) x *= (u[j] * rs + bias_u);
+                  if (DUAL && !pair) x *= (u[j] * (rs * ts) + bias_u);
                   if (p.col_scale) x *= p.col_scale[t];
                   if (p.residual) x += p.res_scale * __bfloat162float(p.residual[(size_t)t * p.ldr + n]);
                   if (two_shot) {
@@ -598,7 +643,7 @@ static int gemm_bf16_impl(const void* X, int ldx, const void* W, int w_rows, int
                           int T, int N, int K, int gated, int dual_off, const float* bias, const void* residual,
                           int ldr, float res_scale, int act, const float* row_scale, float* ws, size_t ws_bytes,
                           int* counters, int n_counters, int* status, int force_splits, const CommParams* ar,
-                          cudaStream_t st) {
+                          cudaStream_t st, const float* rms_eps = nullptr) {
   if (T <= 0 || N <= 0 || K <= 0) return 0;
   GemmParams p{};
   if (ar) p.ar = *ar;
@@ -610,6 +655,11 @@ static int gemm_bf16_impl(const void* X, int ldx, const void* W, int w_rows, int
   p.t_tiles = (T + bn - 1) / bn;
   p.num_kb = (K + 63) / 64;
   // compute-bound shapes: one CTA owns two adjacent feature tiles (pair mode) when that still fills the GPU
+  constexpr size_t kRmsWsBytes = 1 << 20;        // tail of the split-K scratch kept for partial sums of squares
+  if (rms_eps) {
+    if (bn > 64 || ar || (K & 7) || (ldx & 7)) return -7;
+    ws_bytes = (ws && ws_bytes > kRmsWsBytes) ? ws_bytes - kRmsWsBytes : 0;
+  }
   if (!gated && !ar && !row_scale && bn == 256 && ((N + 255) / 256) * p.t_tiles >= 148) {
     p.pair = 1;
     p.dual_off = 128;
@@ -624,6 +674,13 @@ static int gemm_bf16_impl(const void* X, int ldx, const void* W, int w_rows, int
       p.kb_per_split = (p.num_kb + s - 1) / s;
       p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;
     }
+  }
+  if (rms_eps) {
+    if (p.splits > 1 && (size_t)tiles * p.splits * bn * sizeof(float) > kRmsWsBytes) { p.splits = 1; p.kb_per_split = p.num_kb; }
+    p.rms_x = reinterpret_cast<const __nv_bfloat16*>(X);
+    p.rms_ldx = ldx;
+    p.rms_eps = *rms_eps;
+    p.rms_ws = ws ? reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + ws_bytes) : nullptr;
   }
   CUtensorMap tmW, tmX;
   int r = make_tensor_map(&tmW, W, (uint64_t)w_rows, (uint64_t)K, (uint64_t)ldw, 128, 2);
@@ -645,6 +702,18 @@ static int gemm_bf16_impl(const void* X, int ldx, const void* W, int w_rows, int
 }
 
 extern "C" void xft_set_pdl(int on) { xft::g_xft_pdl = on ? 1 : 0; }
+
+// RMSNorm fused into the GEMM: X is the un-normalised hidden state, W carries the norm's gain folded into its
+// columns, and the kernel scales each token's accumulator by rsqrt(mean(x^2) + eps).  T <= 64 only (returns -7
+// otherwise).  Replaces the reference's separate norm kernel in front of the QKV and gate/up products
+// (src/layers/attention.h: norm.forward + qkv gemm; src/layers/mlp_llama.h).
+extern "C" int xft_gemm_bf16_rms(const void* X, int ldx, const void* W, int w_rows, int ldw, void* Y, int ldo, int out_fp32,
+                                 int T, int N, int K, int gated, int dual_off, const float* bias, int act, float eps,
+                                 float* ws, size_t ws_bytes, int* counters, int n_counters, int* status,
+                                 cudaStream_t st) {
+  return gemm_bf16_impl(X, ldx, W, w_rows, ldw, Y, ldo, out_fp32, T, N, K, gated, dual_off, bias, nullptr, 0, 1.0f, act,
+                        nullptr, ws, ws_bytes, counters, n_counters, status, 0, nullptr, st, &eps);
+}
 
 // The split-K planner on its own (host arithmetic only), for tests and tuning.
 extern "C" void xft_plan_splits(int tiles, int num_kb, int bn, int nacc, size_t ws_bytes, int max_tiles, int* splits,

@@ -57,6 +57,36 @@ def test_gemm_pair_mode(T, N, K):
     _close(got, want, 3e-2, 2e-2, "pair mode")
 
 
+@pytest.mark.parametrize("gated", [False, True])
+@pytest.mark.parametrize("T,N,K", [(1, 128, 64), (16, 256, 8192), (7, 1000, 328), (33, 384, 1024), (64, 4096, 4096),
+                                   (16, 1408, 4096), (200, 512, 256)])
+def test_gemm_with_fused_rmsnorm(T, N, K, gated):
+    """RMSNorm folded into the GEMM: gain pre-multiplied into W's columns, 1/rms per token computed by the kernel
+    (split-K slices add their sums of squares).  T = 200 takes the unfused route (norm kernel + GEMM)."""
+    from xfastertransformer_b200.ops import native as N_
+    g = torch.Generator().manual_seed(T + N + K)
+    x = (torch.randn(T, K, generator=g) * 3.0).bfloat16()
+    rows = 2 * N if gated else N
+    w = (torch.randn(rows, K, generator=g) * 0.05).bfloat16()
+    gain = 1.0 + 0.2 * torch.randn(K, generator=g)
+    bias = torch.randn(rows, generator=g) * 0.1
+    eps = 1e-5
+    h = R.rmsnorm(x.float(), gain, eps)
+    Wref = make_linear(w, "bf16")
+    if gated:
+        want = R.linear_gated(h, Wref, "silu", bias)
+    else:
+        want = R.linear(h, Wref, bias, "gelu", None, 1.0, out_dtype=torch.float32)
+    Wf = make_linear((w.float() * gain[None, :]).bfloat16(), "bf16").to("cuda")
+    got = N_.linear_rms(x.cuda(), Wf, eps, bias.cuda(), "silu" if gated else "gelu", gated=gated)
+    _ws().check_status()
+    # the folded weight is rounded to bf16 once more, so the tolerance follows the output's scale
+    scale = float(want.abs().max())
+    _close(got, want, 1.5e-2 * scale, 3e-2, f"rms-fused gemm {T}x{N}x{K} gated={gated}")
+    rel = float((got.float().cpu() - want).norm() / want.norm())
+    assert rel < 1e-2, rel
+
+
 @pytest.mark.parametrize("splits", [2, 3, 8])
 def test_gemm_split_k(splits):
     from xfastertransformer_b200.ops import native as N_

@@ -105,6 +105,7 @@ class Decoder:
             self._load_embedding(embed_from)
             self.layers: List[Layer] = [self._load_layer(i) for i in range(self.l0, self.l1)]
             self._load_head(embed_from)
+            self._fold_norms()
 
     # ------------------------------------------------------------------------------------
     # rotary tables
@@ -403,6 +404,37 @@ class Decoder:
         L.o = self.src.fp8_linear(p + "attention.dense", c.head_num * vd, H, in_rng=(hs * vd, he * vd), kind=self.kind)
         L.o_b = None
 
+    def _fold_norms(self) -> None:
+        """On a GPU, multiply the RMSNorm gain into the columns of the bf16 projection that consumes the
+        normalised state (QKV, gate|up, lm_head).  What is left of the norm is one factor per token,
+        rsqrt(mean(x^2) + eps), which the GEMM computes itself at decode sizes (ops.linear_rms): two launches
+        per layer disappear from the decode step.  The reference keeps the norm as its own kernel
+        (src/layers/attention.h, src/layers/mlp_llama.h call norm.forward before the first GEMM)."""
+        s = self.spec
+        self.head_fold = False
+        for L in self.layers:
+            L.attn_fold = L.mlp_fold = False
+        if self.device.type != "cuda" or s.norm != "rms" or s.resid_from_norm or not Env.get().fuse_norm:
+            return
+
+        def fold(W: LinearWeight, g: torch.Tensor) -> bool:
+            if W is None or W.kind != "bf16" or W.w.dtype != torch.bfloat16:
+                return False
+            if not W.cache.get("norm_folded"):
+                gf = g.to(W.w.device, torch.float32)[None, :]
+                for r in range(0, W.w.shape[0], 8192):
+                    W.w[r:r + 8192] = (W.w[r:r + 8192].float() * gf).to(torch.bfloat16)
+                W.cache["norm_folded"] = True
+            return True
+
+        for L in self.layers:
+            if s.attention != "mla" and L.attn_norm_b is None:
+                L.attn_fold = fold(L.qkv, L.attn_norm_w)
+            if L.mlp_kind == "llama" and L.mlp_norm_b is None:
+                L.mlp_fold = fold(L.gate_up, L.mlp_norm_w)
+        if self.last_stage and self.lm_head is not None and self.final_b is None:
+            self.head_fold = fold(self.lm_head, self.final_w)
+
     # ------------------------------------------------------------------------------------
     # forward
     # ------------------------------------------------------------------------------------
@@ -436,13 +468,15 @@ class Decoder:
 
     def _attention(self, L: Layer, x, b: Batch, cache: PagedKVCache, li: int):
         c, s = self.cfg, self.spec
-        with TimeLine("Attention.norm"):
-            h = self._norm(x, L.attn_norm_w, L.attn_norm_b)
+        h = None
+        if not L.attn_fold:
+            with TimeLine("Attention.norm"):
+                h = self._norm(x, L.attn_norm_w, L.attn_norm_b)
         if s.attention == "mla":
             a = self._mla(L, h, b, cache, li)
         else:
             with TimeLine("QKV.linear"):
-                qkv = ops.linear(h, L.qkv, L.qkv_b)
+                qkv = ops.linear_rms(x, L.qkv, self.eps, L.qkv_b) if L.attn_fold else ops.linear(h, L.qkv, L.qkv_b)
             with TimeLine("QKPO"):
                 table, q_scale, positions = self.rope_table, None, b.positions
                 if s.logn_ntk and table is not None:
@@ -508,10 +542,14 @@ class Decoder:
 
     def _mlp(self, L: Layer, x, b: Batch):
         s = self.spec
+        k = L.mlp_kind
+        if L.mlp_fold:
+            with TimeLine("LlamaMLP"):
+                g = ops.linear_rms(x, L.gate_up, self.eps, None, L.act, gated=True)
+                return self._row_parallel(g, L.down, None, x, 1.0)
         with TimeLine("MLP.norm"):
             h = self._norm(x, L.mlp_norm_w, L.mlp_norm_b)
         resid, rs = (h, math.sqrt(2 * self.cfg.num_layer)) if s.resid_from_norm else (x, 1.0)
-        k = L.mlp_kind
         if k == "llama":
             with TimeLine("LlamaMLP"):
                 g = ops.linear_gated(h, L.gate_up, L.act)
@@ -556,6 +594,9 @@ class Decoder:
         """Final norm on the rows that need logits + vocab-split lm_head -> fp32 [rows, vocab/tp]."""
         if b.logit_rows is not None:
             x = x.index_select(0, b.logit_rows)
+        if self.head_fold:
+            with TimeLine("DistLinear.forward"):
+                return ops.linear_rms(x, self.lm_head, self.eps, out_dtype=torch.float32)
         x = self._norm(x, self.final_w, self.final_b)
         with TimeLine("DistLinear.forward"):
             return ops.linear(x, self.lm_head, out_dtype=torch.float32)

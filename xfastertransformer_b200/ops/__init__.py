@@ -53,6 +53,14 @@ def linear(x, W, bias=None, act=None, residual=None, res_scale=1.0, out_dtype=No
     return R.linear(x, W, bias, act, residual, res_scale, out_dtype)
 
 
+def linear_rms(x, W, eps, bias=None, act=None, gated=False, out_dtype=None):
+    """RMSNorm(x) @ W^T for a weight whose columns already carry the norm's gain (loader.fold_norm_gain)."""
+    if _cuda(x):
+        return _nat().linear_rms(x, W, eps, bias, act, gated, out_dtype)
+    h = R.rmsnorm(x, torch.ones(x.shape[-1], dtype=torch.float32), eps)
+    return R.linear_gated(h, W, act, bias) if gated else R.linear(h, W, bias, act, None, 1.0, out_dtype)
+
+
 def linear_gated(x, W, act="silu", bias=None):
     if _cuda(x):
         return _nat().linear_gated(x, W, act, bias)

@@ -188,6 +188,41 @@ def gemm_bf16(x, w, N, gated=False, dual_off=0, bias=None, act=None, residual=No
     return out
 
 
+RMS_FUSE_MAX_TOKENS = 64
+_ones_cache: Dict[tuple, torch.Tensor] = {}
+
+
+def _ones(n: int, device) -> torch.Tensor:
+    key = (n, str(device))
+    if key not in _ones_cache:
+        _ones_cache[key] = torch.ones(n, dtype=torch.float32, device=device)
+    return _ones_cache[key]
+
+
+def linear_rms(x, W, eps, bias=None, act=None, gated=False, out_dtype=None):
+    """RMSNorm(x) @ W^T where W already carries the norm's gain in its columns (see fold_norm_gain).  Up to
+    RMS_FUSE_MAX_TOKENS rows this is ONE kernel: the GEMM computes each token's 1/rms beside its main loop and
+    scales the accumulator.  Larger batches (prefill) run the gain-free norm kernel, then the GEMM."""
+    assert W.kind == "bf16"
+    x2, ldx = _rows2d(x)
+    T, K = x2.shape
+    N = W.out_features // 2 if gated else W.out_features
+    if T > RMS_FUSE_MAX_TOKENS:
+        h = rmsnorm(x, _ones(K, x.device), eps)
+        return linear_gated(h, W, act, bias) if gated else linear(h, W, bias, act, out_dtype=out_dtype)
+    w = W.w
+    assert w.dtype == torch.bfloat16 and w.stride(1) == 1 and w.shape[1] == K and x2.dtype == torch.bfloat16
+    fp32 = out_dtype == torch.float32
+    out = torch.empty(T, N, dtype=torch.float32 if fp32 else torch.bfloat16, device=x.device)
+    ws = Workspace.get(x.device)
+    rc = lib().xft_gemm_bf16_rms(_p(x2), ldx, _p(w), w.shape[0], w.stride(0), _p(out), out.stride(0), int(fp32), T, N, K,
+                                 int(gated), N if gated else 0, _p(bias), _ACT[act], C.c_float(eps), _p(ws.ws),
+                                 C.c_size_t(ws.ws_bytes), _p(ws.counters), ws.n_counters, _p(ws.status), _stream())
+    _check(rc, "gemm_bf16_rms")
+    ws.launches += 1
+    return out.view(*x.shape[:-1], N)
+
+
 def linear(x, W, bias=None, act=None, residual=None, res_scale=1.0, out_dtype=None):
     lead = x.shape[:-1]
     if W.kind == "bf16":

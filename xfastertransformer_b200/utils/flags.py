@@ -57,6 +57,7 @@ class Env:
         self.kv_cache_gb = float(e.get("XFT_KV_CACHE_GB", "0") or 0)
         self.max_batch_tokens = _int("XFT_MAX_BATCH_TOKENS", 8192)
         self.step_timeout_s = float(e.get("XFT_STEP_TIMEOUT_S", "0") or 0)
+        self.fuse_norm = _int("XFT_FUSE_NORM", 1) != 0    # fold RMSNorm gains into the consuming bf16 GEMM
         self.attn_tma = _int("XFT_ATTN_TMA", 1) != 0      # bf16 decode attention through the TMA ring kernel
         self.attn_splits = _int("XFT_ATTN_SPLITS", 0)     # decode split-KV factor; 0 = planned per launch
         # accepted, no effect on a GPU build
