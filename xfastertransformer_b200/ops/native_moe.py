@@ -13,7 +13,6 @@ from . import reference as R
 
 _KIND = {"mixtral": 0, "softmax_topk": 1, "deepseek": 2}
 _ready = False
-_PACK: Dict[int, dict] = {}
 
 
 def _lib():
@@ -44,11 +43,12 @@ def route(logits, kind, top_k, bias=None, n_group=1, topk_group=1, routed_scalin
 def pack_experts(experts) -> dict:
     """Stack the local experts' weights: gate‖up [E*2I, H] and down [E*H, I] (bf16; other kinds are expanded
     once here).  The per-expert LinearWeights are re-pointed at views of the stacks so nothing is held twice."""
-    key = id(experts)
-    pk = _PACK.get(key)
-    if pk is not None:
-        return pk
+    # the pack lives in the first expert's weight object (an id()-keyed table would hand a dead list's pack to a
+    # new list that happens to reuse its address)
     gu0, dn0 = experts[0]
+    pk = gu0.cache.get("moe_pack")
+    if pk is not None and pk["E"] == len(experts) and pk["last"] is experts[-1][0]:
+        return pk
     I, H = dn0.in_features, dn0.out_features
     E = len(experts)
     dev = gu0.w.device
@@ -62,8 +62,8 @@ def pack_experts(experts) -> dict:
             g.w = gv
         if d.kind == "bf16":
             d.w = dv
-    pk = dict(gu=gu, dn=dn, I=I, H=H, E=E)
-    _PACK[key] = pk
+    pk = dict(gu=gu, dn=dn, I=I, H=H, E=E, last=experts[-1][0])
+    gu0.cache["moe_pack"] = pk
     return pk
 
 
