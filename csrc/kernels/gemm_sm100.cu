@@ -33,7 +33,7 @@ int g_xft_pdl = 1;
 // Fused one-shot all-reduce (row-parallel o_proj / down_proj at decode sizes): replaces the reference's
 // GEMM followed by Messenger::reduceAdd (src/layers/decoder_block.h:122-134).  `recv[r]` is rank r's
 // receive area [2 parities][world slots][slot words] as mapped into this process (CUDA IPC over NVLink);
-// each word is {fp32 value, epoch}.  The CTA that finishes an output tile stores its partial tile into
+// each word is {two bf16 values (tokens t, t + 1 of one feature), epoch}.  The CTA that finishes an output tile stores its partial tile into
 // slot `rank` of every rank straight from the accumulator, then reads the world slots of its own area,
 // spinning (bounded) on each word until its epoch matches, and sums them in rank order, so all ranks
 // produce bit-identical results.  No fence, flag or barrier separates a producer's store from the
@@ -92,6 +92,18 @@ struct GemmParams {
   float rms_eps;
   float* rms_ws;           // [tile][split][BN] partial sums of squares
 };
+
+// Payload of one LL word of the fused all-reduce: two bf16 values (tokens t and t + 1 of one feature).  Partials are
+// rounded to bf16 before they cross NVLink, as a bf16 all-reduce does; the sum itself runs in fp32.
+__device__ __forceinline__ unsigned long long ll_pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return (unsigned long long)(*reinterpret_cast<unsigned*>(&v));
+}
+__device__ __forceinline__ void ll_unpack2(unsigned w, float& lo, float& hi) {
+  const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&w);
+  const float2 f = __bfloat1622float2(v);
+  lo = f.x; hi = f.y;
+}
 
 __device__ __forceinline__ float apply_act(float x, int act) {
   switch (act) {
@@ -364,12 +376,11 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
           load_acc(c, g, u);
           if (n_ok) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int t = t0 + c + j;
+            for (int j = 0; j < 16; j += 2) {
+              const int t = t0 + c + j;           // even: one word carries tokens t and t + 1 of feature n
               if (t < p.T) {
-                const unsigned long long w =
-                    ((unsigned long long)(unsigned)epoch << 32) | (unsigned long long)__float_as_uint(g[j] * rs);
-                const long long off = par * p.ar.parity_stride + p.ar.rank * p.ar.slot_stride + (long long)t * p.N + n;
+                const unsigned long long w = ((unsigned long long)(unsigned)epoch << 32) | ll_pack2(g[j] * rs, g[j + 1] * rs);
+                const long long off = par * p.ar.parity_stride + p.ar.rank * p.ar.slot_stride + (long long)(t >> 1) * p.N + n;
                 if (two_shot) p.ar.recv[owner][off] = w;
                 else for (int r = 0; r < p.ar.world; ++r) p.ar.recv[r][off] = w;
               }
@@ -387,23 +398,23 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
           } else if (!i_reduce) {
             // two-shot, not the owner: the finished values arrive in this rank's result area
             const volatile unsigned long long* base = p.ar.result[p.ar.rank] + par * p.ar.slot_stride + n;
-            unsigned long long w[16];
+            unsigned long long w[8];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int t = t0 + c + j;
-              w[j] = (n_ok && t < p.T) ? base[(long long)t * p.N] : ((unsigned long long)(unsigned)epoch << 32);
+            for (int j = 0; j < 8; ++j) {
+              const int t = t0 + c + 2 * j;
+              w[j] = (n_ok && t < p.T) ? base[(long long)(t >> 1) * p.N] : ((unsigned long long)(unsigned)epoch << 32);
             }
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
+            for (int j = 0; j < 8; ++j) {
               if ((int)(w[j] >> 32) != epoch) {
-                const int t = t0 + c + j;
+                const int t = t0 + c + 2 * j;
                 const long long tstart = clock64();
                 do {
                   if (clock64() - tstart > p.ar.wait_cycles) { peers_ok = false; break; }
-                  w[j] = base[(long long)t * p.N];
+                  w[j] = base[(long long)(t >> 1) * p.N];
                 } while ((int)(w[j] >> 32) != epoch);
               }
-              g[j] = __uint_as_float((unsigned)w[j]);
+              ll_unpack2((unsigned)w[j], g[2 * j], g[2 * j + 1]);
             }
             if (!peers_ok) { if (p.status) atomicCAS(p.status, 0, XFT_ERR_WAIT_PEER); break; }
           } else {
@@ -413,23 +424,26 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
             for (int j = 0; j < 16; ++j) g[j] = 0.f;
             for (int r = 0; r < p.ar.world && peers_ok; ++r) {
               const volatile unsigned long long* base = my_recv + r * p.ar.slot_stride + n;
-              unsigned long long w[16];
+              unsigned long long w[8];
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const int t = t0 + c + j;
-                w[j] = (n_ok && t < p.T) ? base[(long long)t * p.N] : ((unsigned long long)(unsigned)epoch << 32);
+              for (int j = 0; j < 8; ++j) {
+                const int t = t0 + c + 2 * j;
+                w[j] = (n_ok && t < p.T) ? base[(long long)(t >> 1) * p.N] : ((unsigned long long)(unsigned)epoch << 32);
               }
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
+              for (int j = 0; j < 8; ++j) {
                 if ((int)(w[j] >> 32) != epoch) {
-                  const int t = t0 + c + j;
+                  const int t = t0 + c + 2 * j;
                   const long long tstart = clock64();
                   do {
                     if (clock64() - tstart > p.ar.wait_cycles) { peers_ok = false; break; }
-                    w[j] = base[(long long)t * p.N];
+                    w[j] = base[(long long)(t >> 1) * p.N];
                   } while ((int)(w[j] >> 32) != epoch);
                 }
-                g[j] += __uint_as_float((unsigned)w[j]);
+                float lo, hi;
+                ll_unpack2((unsigned)w[j], lo, hi);
+                g[2 * j] += lo;
+                g[2 * j + 1] += hi;
               }
             }
             if (!peers_ok) { if (p.status) atomicCAS(p.status, 0, XFT_ERR_WAIT_PEER); break; }
@@ -449,15 +463,24 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                   if (DUAL && !pair) x *= (u[j] * (rs * ts) + bias_u);
                   if (p.col_scale) x *= p.col_scale[t];
                   if (p.residual) x += p.res_scale * __bfloat162float(p.residual[(size_t)t * p.ldr + n]);
-                  if (two_shot) {
-                    const unsigned long long w = ((unsigned long long)(unsigned)epoch << 32) | (unsigned long long)__float_as_uint(x);
-                    const long long off = par * p.ar.slot_stride + (long long)t * p.N + n;
-                    for (int r = 0; r < p.ar.world; ++r)
-                      if (r != p.ar.rank) p.ar.result[r][off] = w;
-                  }
+                  g[j] = x;                     // kept for the two-shot broadcast below
                 }
                 if (p.out_fp32) reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + n] = x;
                 else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)t * p.ldo + n] = __float2bfloat16(x);
+              }
+            }
+            if (two_shot && i_reduce) {
+              // all-gather half of the two-shot scheme: the owner hands the finished values (two tokens per word)
+              // to every other rank
+#pragma unroll
+              for (int j = 0; j < 16; j += 2) {
+                const int t = t0 + c + j;
+                if (t < p.T) {
+                  const unsigned long long w = ((unsigned long long)(unsigned)epoch << 32) | ll_pack2(g[j], g[j + 1]);
+                  const long long off = par * p.ar.slot_stride + (long long)(t >> 1) * p.N + n;
+                  for (int r = 0; r < p.ar.world; ++r)
+                    if (r != p.ar.rank) p.ar.result[r][off] = w;
+                }
               }
             }
           }
