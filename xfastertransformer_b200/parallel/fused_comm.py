@@ -90,10 +90,13 @@ class PeerComm:
             prm.wait_cycles = self.wait_cycles
         for r in range(self.world):
             self.gp.result[r] = self.peer_base[r] + self.recv_bytes
-        # reduce-scatter + all-gather inside the epilogue pays off from 4 ranks on (XFT_AR_TWO_SHOT overrides)
+        # Reduce-scatter + all-gather inside the epilogue (two-shot) trades one more NVLink hop for less traffic: it
+        # pays off from 4 ranks on and more than 16 tokens; up to 16 tokens the one-shot push wins at every world
+        # size measured (8 ranks, 70B decode: 10.3 vs 11.1 ms per step).  XFT_AR_TWO_SHOT=0/1 overrides.
         import os
         ts = os.environ.get("XFT_AR_TWO_SHOT")
-        self.gp.two_shot = int(ts) if ts is not None else int(self.world >= 4)
+        self._two_shot_env = int(ts) if ts is not None else None
+        self.gp.two_shot = 0
         self.gp.slot_stride = self.slot
         self.gp.parity_stride = self.world * self.slot
         self.ap.cap = self.slot
@@ -117,6 +120,7 @@ class PeerComm:
             r2 = residual.reshape(-1, residual.shape[-1])
             ldr = r2.stride(0)
         ws = N.Workspace.get(x.device)
+        self.gp.two_shot = self._two_shot_env if self._two_shot_env is not None else int(self.world >= 4 and T > 16)
         rc = self.lib.xft_gemm_bf16_ar(N._p(x2), ldx, N._p(W.w), W.w.stride(0), N._p(out), out.stride(0), int(fp32), T, n,
                                        K, N._p(bias), N._p(r2), ldr, C.c_float(res_scale), N._ACT[act], N._p(ws.ws),
                                        C.c_size_t(ws.ws_bytes), N._p(ws.counters), ws.n_counters, N._p(ws.status),
