@@ -73,6 +73,27 @@ def build(force=False, verbose=False):
         if os.path.exists(ex_src) and (force or _newer(ex_src, ex_bin, hdrs) or _newer(core, ex_bin)):
             _run(cxx + ["-o", ex_bin, ex_src, "-L", OUT, "-lxft_b200_core", "-lxft_b200_kernels", "-L",
                         "/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,/usr/local/cuda/lib64"], verbose)
+        cb_src = os.path.join(ROOT, "examples", "cpp", "cb_check.cpp")
+        cb_bin = os.path.join(OUT, "xft_cb_check")
+        if os.path.exists(cb_src) and (force or _newer(cb_src, cb_bin, hdrs) or _newer(core, cb_bin)):
+            _run(cxx + ["-o", cb_bin, cb_src, "-L", OUT, "-lxft_b200_core", "-lxft_b200_kernels", "-L",
+                        "/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,/usr/local/cuda/lib64"], verbose)
+        # torch custom-class binding (torch.classes.xfastertransformer.AutoModel) on top of the C++ runtime
+        tb_src = os.path.join(api, "torch_binding.cc")
+        tb_lib = os.path.join(OUT, "libxft_b200_torch.so")
+        if os.path.exists(tb_src) and os.environ.get("XFT_BUILD_TORCH_BINDING", "1") != "0" and \
+                (force or _newer(tb_src, tb_lib, hdrs) or _newer(core, tb_lib)):
+            try:
+                import torch
+                from torch.utils import cpp_extension as ce
+                inc = sum((["-isystem", d] for d in ce.include_paths()), [])
+                tlib = os.path.join(os.path.dirname(torch.__file__), "lib")
+                abi = "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI)
+                _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", abi, "-I", api, "-I", cdir] + inc +
+                     ["-o", tb_lib, tb_src, "-L", OUT, "-lxft_b200_core", "-L", tlib, "-ltorch", "-ltorch_cpu", "-lc10",
+                      "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + tlib], verbose)
+            except ImportError:
+                pass
     return lib, "".join(logs)
 
 
