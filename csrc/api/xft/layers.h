@@ -30,4 +30,42 @@ int invokeMLPLLaMA(DataType dt, ActivationType act, int tokens, int hidden, int 
                    const void* gateUp, const void* down, void* scratch /* tokens*inter bf16 */, const void* residual = nullptr,
                    cudaStream_t stream = 0);
 
+
+// ---- stateful entries (csrc/core/layer_objects.cc).  Weights here are row-major [in, out] bf16 on the device, as in
+// the reference's calls; one object per set of weight pointers keeps the [out, in] copies, the rotary table and its
+// own paged KV cache (batch x maxPositions).  Keys of a call are appended at positions pastSeqLen ...
+// output = attention(input) Wo + bias + input
+int invokeAttentionLLaMA(DataType dt, int batchSize, int inputSeqLen, int attHeadDim, int attHeadNum, int kvHeadNum,
+                         int maxPositions, int maxPosEmbed, int pastSeqLen, int currentSeqLen, int step, int hiddenSize,
+                         void* output, int outputStride, const void* input, int inputStride, const void* queryWeight,
+                         const void* keyWeight, const void* valueWeight, const void* attnOutWeight,
+                         const float* queryBias = nullptr, const float* keyBias = nullptr, const float* valueBias = nullptr,
+                         const float* attnOutBias = nullptr, cudaStream_t stream = 0);
+// a whole pre-norm decoder layer: x1 = x + attn(norm1(x)); output = x1 + mlp(norm2(x1))
+int invokeLayerLLaMA(DataType dt, ActivationType at, NormType nt, int batchSize, int inputSeqLen, int attHeadDim,
+                     int attHeadNum, int kvHeadNum, int maxPositions, int maxPosEmbed, int pastSeqLen, int currentSeqLen,
+                     int step, int hiddenSize, int intermediateSize, void* output, int outputStride, const void* input,
+                     int inputStride, const float* ln1Gamma, const float* ln1Beta, const void* queryWeight,
+                     const void* keyWeight, const void* valueWeight, const void* attnOutWeight, const float* ln2Gamma,
+                     const float* ln2Beta, const void* gateWeight, const void* upWeight, const void* downWeight,
+                     const float* queryBias = nullptr, const float* keyBias = nullptr, const float* valueBias = nullptr,
+                     const float* attnOutBias = nullptr, cudaStream_t stream = 0);
+
+// DeepSeek routed experts.  gateUpWeights [E, 2*inter, hidden] (gate rows, then up rows) and downWeights
+// [E, hidden, inter], in [out, in] layout: bf16 when the scales are null, else e4m3 with one fp32 scale per
+// blockSize x blockSize tile ([E, rows/blockSize, cols/blockSize]); they are expanded to bf16 once, here.
+// tpRank / tpSize select the local experts (expert parallelism); the caller sums the ranks' outputs.
+void* createDeepSeekMoE(int layerId, int numExperts, int numExpPerTok, int hiddenSize, int intermediateSize, bool normTopKProb,
+                        int nGroup, int topkGroup, const void* gateUpWeights, const void* downWeights,
+                        const void* gateUpScales, const void* downScales, const void* gatingCorrBias = nullptr,
+                        int blockSize = 128, int tpRank = 0, int tpSize = 1, float routedScalingFactor = 1.0f,
+                        cudaStream_t stream = 0);
+// routingLogits: fp32 [nTokens, numExperts] (sigmoid scores + correction bias + group-limited top-k happen inside)
+int forwardDeepSeekMoE(void* moe, void* input, void* output, int nTokens, void* routingLogits, int iStride = 0,
+                       int oStride = 0, cudaStream_t stream = 0);
+// experts already selected: selExperts int32 [nTokens, k], expertWeights fp32 [nTokens, k]
+int forwardDeepSeekMoE(void* moe, void* input, void* output, int nTokens, int* selExperts, float* expertWeights,
+                       int iStride = 0, int oStride = 0, cudaStream_t stream = 0);
+void destroyDeepSeekMoE(void* moe);
+
 }  // namespace xft

@@ -3,6 +3,7 @@
 #include <cstring>
 
 #include "runtime.h"
+#include "xft/layers.h"
 
 using namespace xft;
 
@@ -46,4 +47,31 @@ void xftc_repetition_penalty(float* l, int n, const int* toks, int nt, float pen
   repetitionPenalty(l, n, std::vector<int32_t>(toks, toks + nt), pen, off);
 }
 
+
+// ---- the stateful layer API (csrc/core/layer_objects.cc) on device pointers, stream 0
+int xftc_layer_llama(int batch, int seq, int headDim, int heads, int kvHeads, int maxPos, int past, int hidden, int inter,
+                     void* out, const void* in, const float* ln1, const void* qW, const void* kW, const void* vW,
+                     const void* oW, const float* ln2, const void* gate, const void* up, const void* down) {
+  return xft::invokeLayerLLaMA(xft::DataType::bf16, xft::SILU, xft::RMS, batch, seq, headDim, heads, kvHeads, maxPos, maxPos,
+                               past, past + seq, past == 0 ? 0 : 1, hidden, inter, out, hidden, in, hidden, ln1, nullptr, qW,
+                               kW, vW, oW, ln2, nullptr, gate, up, down);
+}
+int xftc_attention_llama(int batch, int seq, int headDim, int heads, int kvHeads, int maxPos, int past, int hidden, void* out,
+                         const void* in, const void* qW, const void* kW, const void* vW, const void* oW) {
+  return xft::invokeAttentionLLaMA(xft::DataType::bf16, batch, seq, headDim, heads, kvHeads, maxPos, maxPos, past, past + seq,
+                                   past == 0 ? 0 : 1, hidden, out, hidden, in, hidden, qW, kW, vW, oW);
+}
+void* xftc_dsmoe_create(int E, int k, int hidden, int inter, int normTopK, int nGroup, int topkGroup, const void* gateUp,
+                        const void* down, const void* guScales, const void* dnScales, const void* bias, int block, int rank,
+                        int world, float scaling) {
+  return xft::createDeepSeekMoE(0, E, k, hidden, inter, normTopK != 0, nGroup, topkGroup, gateUp, down, guScales, dnScales, bias,
+                                block, rank, world, scaling);
+}
+int xftc_dsmoe_forward_logits(void* moe, void* in, void* out, int T, void* logits) {
+  return xft::forwardDeepSeekMoE(moe, in, out, T, logits);
+}
+int xftc_dsmoe_forward_selected(void* moe, void* in, void* out, int T, int* idx, float* w) {
+  return xft::forwardDeepSeekMoE(moe, in, out, T, idx, w);
+}
+void xftc_dsmoe_destroy(void* moe) { xft::destroyDeepSeekMoE(moe); }
 }  // extern "C"

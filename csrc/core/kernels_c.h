@@ -28,6 +28,19 @@ int xft_paged_attention(const void* q, void* out, const void* kc, const void* vc
 int xft_argmax(const float* logits, int ld, int rows, int V, float* vals, int* idx, cudaStream_t st);
 int xft_transpose_to_bf16(const void* src, int dtype, long long ld_src, int rows, int cols, void* dst, long long ld_dst,
                           cudaStream_t st);
+int xft_fp8_block_dequant(const void* src, const float* scale, long long rows, int cols, int block, void* dst,
+                          cudaStream_t st);
+int xft_moe_route(const float* logits, int ld, int T, int E, int k, int kind, const float* bias, int n_group, int topk_group,
+                  float scaling, int norm_topk, int sigmoid, int* idx, float* w, cudaStream_t st);
+int xft_moe_plan(const int* idx, const float* w, int T, int k, int e0, int e1, int bn, int* pos, int* src_tok, float* row_w,
+                 void* tiles, int* meta, int max_tiles, int max_rows, cudaStream_t st);
+int xft_moe_gather(const void* x, int ldx, const int* src_tok, const int* meta, void* xs, int max_rows, int H, cudaStream_t st);
+int xft_moe_combine(const float* ys, const int* pos, int k, const float* add1, const void* add2, int ld2, void* y, float* y32,
+                    int T, int H, cudaStream_t st);
+int xft_gemm_bf16_grouped(const void* X, int ldx, int x_rows, const void* W, int w_rows, int ldw, void* Y, int ldo,
+                          int out_fp32, int N, int K, int gated, int dual_off, int group_w_rows, const void* group_tiles,
+                          const int* num_group_tiles, int max_tiles, int bn, const float* col_scale, int act, int* status,
+                          cudaStream_t st);
 int xft_sample_topk_topp(const float* logits, int ld, int rows, int V, int k, float top_p, float temperature,
                          const float* uniform, int* out, cudaStream_t st);
 }

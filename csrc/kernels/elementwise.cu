@@ -417,6 +417,39 @@ __global__ void transpose_to_bf16_kernel(const S* __restrict__ src, long long ld
 }
 }  // namespace xft
 
+namespace xft {
+// e4m3 byte -> float (no NaN/Inf handling beyond what the format encodes: 0x7f / 0xff are NaN)
+__device__ __forceinline__ float e4m3_to_float(uint8_t v) {
+  const int s = v >> 7, e = (v >> 3) & 15, m = v & 7;
+  float f;
+  if (e == 0) f = ldexpf((float)m, -9);                 // subnormal: m * 2^-3 * 2^-6
+  else if (e == 15 && m == 7) f = __int_as_float(0x7fc00000);
+  else f = ldexpf(1.0f + (float)m * 0.125f, e - 7);
+  return s ? -f : f;
+}
+__global__ void fp8_block_dequant_kernel(const uint8_t* __restrict__ src, const float* __restrict__ scale, long long rows,
+                                         int cols, int block, __nv_bfloat16* __restrict__ dst) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * cols) return;
+  const long long r = i / cols;
+  const int c = (int)(i % cols);
+  const int sc_cols = (cols + block - 1) / block;
+  dst[i] = __float2bfloat16(e4m3_to_float(src[i]) * scale[(r / block) * sc_cols + c / block]);
+}
+}  // namespace xft
+
+// e4m3 [rows, cols] with one fp32 scale per block x block tile (scale [ceil(rows/block), ceil(cols/block)]) -> bf16.
+// `rows` may span several stacked matrices when each one's row count is a multiple of `block`.
+extern "C" int xft_fp8_block_dequant(const void* src, const float* scale, long long rows, int cols, int block, void* dst,
+                                     cudaStream_t st) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (block <= 0) return -1;
+  const long long n = rows * cols;
+  xft::fp8_block_dequant_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const uint8_t*)src, scale, rows, cols, block,
+                                                                            (__nv_bfloat16*)dst);
+  return (int)cudaGetLastError();
+}
+
 // src: [rows, cols] of dtype (0 fp32, 1 fp16, 2 bf16) on the device -> dst bf16 [cols, rows]
 extern "C" int xft_transpose_to_bf16(const void* src, int dtype, long long ld_src, int rows, int cols, void* dst,
                                      long long ld_dst, cudaStream_t st) {
