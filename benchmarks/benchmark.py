@@ -21,7 +21,9 @@ sys.path.insert(0, ROOT)
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--model_path", "-m", required=True)
+    ap.add_argument("--model_path", "-m", default="")
+    ap.add_argument("--model_name", default="", help="a preset of tools/synthetic.py (e.g. llama-2-7b): config only, fake weights")
+    ap.add_argument("--token_path", "-tp", default="", help="HF tokenizer dir: prompts come from prompt.json instead of random ids")
     ap.add_argument("--dtype", "-d", default="bf16")
     ap.add_argument("--kv_cache_dtype", "-kvd", default="fp16")
     ap.add_argument("--batch_size", "-bs", type=int, default=1)
@@ -33,6 +35,14 @@ def main():
     ap.add_argument("--csv", default="")
     ap.add_argument("--fake", type=int, default=0, help="XFT_FAKE_MODEL value (1 zeros, 2 random)")
     a = ap.parse_args()
+    if not a.model_path and not a.model_name:
+        ap.error("one of --model_path / --model_name is required")
+    if a.model_name and not a.model_path:
+        import tempfile
+        from xfastertransformer_b200.tools.synthetic import config_only, preset
+        a.model_path = os.path.join(tempfile.gettempdir(), f"xft_bench_{a.model_name}_{os.environ.get('RANK', '0')}")
+        config_only(a.model_path, preset(a.model_name))
+        a.fake = a.fake or 2
     if a.fake:
         os.environ["XFT_FAKE_MODEL"] = str(a.fake)
     import torch
@@ -42,6 +52,17 @@ def main():
     cuda = model.model.ctx.device.type == "cuda"
     vocab = model.model.cfg.vocab_size
     ids = torch.randint(5, max(vocab - 1, 6), (a.batch_size, a.input_tokens), generator=torch.Generator().manual_seed(1))
+    if a.token_path:
+        # real text: the prompt.json entry of that length, or the filler sentence repeated, cut to the token count
+        import json
+        from transformers import AutoTokenizer
+        tok = AutoTokenizer.from_pretrained(a.token_path)
+        prompts = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "prompt.json")))
+        text = prompts.get(str(a.input_tokens)) or prompts["long_unit"] * (a.input_tokens // 8 + 1)
+        t = tok(text, add_special_tokens=True)["input_ids"]
+        while len(t) < a.input_tokens:
+            t = t + t
+        ids = torch.tensor([t[:a.input_tokens]] * a.batch_size)
     max_len = a.input_tokens + a.output_tokens
 
     def sync():

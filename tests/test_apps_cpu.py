@@ -103,3 +103,42 @@ def test_mlserver_runtime_object(tiny):
     assert rt.load_sync()
     out = rt.predict_ids([[5, 6, 7, 8]])
     assert out.shape == (1, 9)
+
+
+def test_lora_finetune_reduces_loss_and_merges(tmp_path):
+    """finetune/llama/finetune.py on a tiny random Llama (CPU, pre-tokenised data): loss falls, the adapter is saved,
+    the merged checkpoint differs from the base only in the wrapped projections and converts to an engine model."""
+    import importlib.util
+    import json
+    import transformers
+    spec = importlib.util.spec_from_file_location("ft", os.path.join(ROOT, "finetune", "llama", "finetune.py"))
+    ft = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ft)
+    cfg = transformers.LlamaConfig(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                                   num_attention_heads=4, num_key_value_heads=4, max_position_embeddings=64)
+    torch.manual_seed(0)
+    base = transformers.LlamaForCausalLM(cfg)
+    bdir = str(tmp_path / "base")
+    base.save_pretrained(bdir, safe_serialization=True)
+    g = torch.Generator().manual_seed(0)
+    pattern = torch.randint(3, 128, (12,), generator=g).tolist()
+    with open(tmp_path / "data.jsonl", "w") as f:
+        for i in range(32):
+            ids = (pattern * 3)[i % 5:i % 5 + 24]
+            f.write(json.dumps({"input_ids": ids}) + "\n")
+    out = str(tmp_path / "out")
+    args = ft.parse(["--base_model", bdir, "--data_path", str(tmp_path / "data.jsonl"), "--output_dir", out, "--cpu",
+                     "--batch_size", "8", "--micro_batch_size", "8", "--max_steps", "30", "--learning_rate", "2e-2",
+                     "--warmup_steps", "2", "--lora_r", "8", "--lora_dropout", "0", "--merge", "--logging_steps", "100",
+                     "--lora_target_modules", "q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"])
+    res = ft.train(args)
+    assert res["last_loss"] < 0.9 * res["first_loss"], res      # frozen random embeddings bound what LoRA can reach
+    ad = torch.load(os.path.join(out, "adapter_model.pt"))
+    assert len(ad) == 7 * 2 * 2 and all(v.abs().sum() > 0 for k, v in ad.items() if "lora_B" in k)
+    merged = transformers.LlamaForCausalLM.from_pretrained(os.path.join(out, "merged"))
+    sd0, sd1 = base.state_dict(), merged.state_dict()
+    changed = {k for k in sd0 if not torch.equal(sd0[k], sd1[k])}
+    assert changed and all("_proj" in k for k in changed), changed
+    from xfastertransformer_b200 import LlamaConvert
+    conv = LlamaConvert().convert(os.path.join(out, "merged"), str(tmp_path / "xft"), dtype="fp32")
+    assert os.path.exists(os.path.join(conv, "config.ini"))
