@@ -26,7 +26,7 @@ int make_tensor_map(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t c
 void plan_splits(int tiles, int num_kb, int bn, int nacc, size_t ws_bytes, int max_tiles, int* splits, int* kb_per_split);
 int pick_bn(int T);
 
-enum { Q_INT8 = 0, Q_INT4 = 1, Q_NF4 = 2, Q_FP8 = 3 };
+enum { Q_INT8 = 0, Q_INT4 = 1, Q_NF4 = 2, Q_FP8 = 3, Q_INT4F = 4 };
 
 struct QGemmParams {
   int N, T, K;
@@ -93,12 +93,60 @@ __device__ __forceinline__ void expand_row(const uint8_t* raw_row, uint8_t* a_ti
   }
 }
 
+// Cooperative expansion of a whole raw tile by the 128 expand threads, 16 bytes per thread and step, so that the
+// loads are consecutive and the swizzled 16-byte stores of a quarter warp never share a bank.
+//   Q_INT8:  the byte u = q + 128 is dropped into the mantissa of 2^23 (one PRMT), 2^23 + 128 is subtracted (exact),
+//            and the upper halves of two such floats are one bf16 pair (one PRMT): no integer-to-float conversion.
+//   Q_INT4F: words are stored nibble-interleaved (nibble i = element 2i, nibble i + 4 = element 2i + 1), so
+//            (w >> 4i) & 0x000F000F | 0x43004300 IS the bf16 pair (128 + e_2i, 128 + e_2i+1): one shift and one
+//            logic op per two elements.  The constant 128 is removed in the epilogue through the activations' row
+//            sums (the caller passes zero - 128 * scale).
+template <int QT>
+__device__ __forceinline__ void expand_tile(const uint8_t* raw, uint8_t* a_tile, int et) {
+  if (QT == Q_INT8) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int ci = et + 128 * i, row = ci >> 2, part = ci & 3;
+      const uint4 w = *reinterpret_cast<const uint4*>(raw + ci * 16);
+      const uint32_t x[4] = {w.x ^ 0x80808080u, w.y ^ 0x80808080u, w.z ^ 0x80808080u, w.w ^ 0x80808080u};
+      uint32_t o[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float f0 = __uint_as_float(__byte_perm(x[j], 0x4B000000u, 0x7540)) - 8388736.0f;
+        const float f1 = __uint_as_float(__byte_perm(x[j], 0x4B000000u, 0x7541)) - 8388736.0f;
+        const float f2 = __uint_as_float(__byte_perm(x[j], 0x4B000000u, 0x7542)) - 8388736.0f;
+        const float f3 = __uint_as_float(__byte_perm(x[j], 0x4B000000u, 0x7543)) - 8388736.0f;
+        o[2 * j] = __byte_perm(__float_as_uint(f0), __float_as_uint(f1), 0x7632);
+        o[2 * j + 1] = __byte_perm(__float_as_uint(f2), __float_as_uint(f3), 0x7632);
+      }
+      uint8_t* dst = a_tile + row * 128;
+      *reinterpret_cast<uint4*>(dst + (((2 * part) ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+      *reinterpret_cast<uint4*>(dst + (((2 * part + 1) ^ (row & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+  } else {   // Q_INT4F
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int ci = et + 128 * i, row = ci >> 1, part = ci & 1;
+      const uint4 w = *reinterpret_cast<const uint4*>(raw + ci * 16);
+      const uint32_t x[4] = {w.x, w.y, w.z, w.w};
+      uint8_t* dst = a_tile + row * 128;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t v = x[j];
+        *reinterpret_cast<uint4*>(dst + (((4 * part + j) ^ (row & 7)) << 4)) =
+            make_uint4((v & 0x000F000Fu) | 0x43004300u, ((v >> 4) & 0x000F000Fu) | 0x43004300u,
+                       ((v >> 8) & 0x000F000Fu) | 0x43004300u, ((v >> 12) & 0x000F000Fu) | 0x43004300u);
+      }
+    }
+  }
+}
+
 constexpr int kQMaxStages = 8;
 
 template <int BN, bool DUAL, int QT>
 __global__ void __launch_bounds__(192) qgemm_kernel(const __grid_constant__ CUtensorMap tmW,
                                                     const __grid_constant__ CUtensorMap tmX, const QGemmParams p) {
-  constexpr int RAW_BYTES = (QT == Q_INT8 || QT == Q_FP8) ? 128 * 64 : 128 * 32;
+  constexpr int RAW_BYTES = (QT == Q_INT8 || QT == Q_FP8) ? 128 * 64 : 128 * 32;      // Q_INT4F is packed like Q_INT4
   constexpr int RAW_ROW = RAW_BYTES / 128;
   constexpr int A_BYTES = 128 * 64 * 2;
   constexpr int B_BYTES = BN * 64 * 2;
@@ -160,9 +208,20 @@ __global__ void __launch_bounds__(192) qgemm_kernel(const __grid_constant__ CUte
       const uint64_t hint_w = p.t_tiles == 1 ? kEvictFirst : kEvictNormal;
       const uint64_t hint_x = p.n_tiles > 1 ? kEvictLast : kEvictNormal;
       constexpr int KEL = (QT == Q_INT8 || QT == Q_FP8) ? 64 : 32;      // raw bytes per k-block row
+      // weights never depend on the previous kernel: the first `stages` raw tiles are requested before the grid
+      // dependency resolves
+      const int pre = min(stages, kb1 - kb0);
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(&raw_full[i], TX_BYTES);
+        uint8_t* st = smem + i * STAGE_BYTES;
+        tma_load_2d(st, &tmW, &raw_full[i], (kb0 + i) * KEL, tile_n * 128, hint_w);
+        if (DUAL) tma_load_2d(st + RAW_BYTES, &tmW, &raw_full[i], (kb0 + i) * KEL, p.dual_off + tile_n * 128, hint_w);
+      }
       grid_dep_wait();
-      int it = 0;
-      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(smem + i * STAGE_BYTES + (RAW_BYTES + A_BYTES) * NACC, &tmX, &raw_full[i], (kb0 + i) * 64, tile_t * BN, hint_x);
+      int it = pre;
+      for (int kb = kb0 + pre; kb < kb1; ++kb, ++it) {
         const int s = it % stages;
         const uint32_t ph = (it / stages) & 1;
         if (!mbar_wait(&empty_bar[s], ph ^ 1, p.status, XFT_ERR_WAIT_EMPTY)) break;
@@ -217,8 +276,13 @@ __global__ void __launch_bounds__(192) qgemm_kernel(const __grid_constant__ CUte
             sc0 = p.scale[(size_t)tile_n * p.scale_ld + (kb >> 1)];
             if (DUAL) sc1 = p.scale[(size_t)((p.dual_off >> 7) + tile_n) * p.scale_ld + (kb >> 1)];
           }
-          expand_row<QT>(st + row * RAW_ROW, st + RAW_BYTES * NACC, row, sc0);
-          if (DUAL) expand_row<QT>(st + RAW_BYTES + row * RAW_ROW, st + RAW_BYTES * NACC + A_BYTES, row, sc1);
+          if (QT == Q_INT8 || QT == Q_INT4F) {
+            expand_tile<QT>(st, st + RAW_BYTES * NACC, et);
+            if (DUAL) expand_tile<QT>(st + RAW_BYTES, st + RAW_BYTES * NACC + A_BYTES, et);
+          } else {
+            expand_row<QT>(st + row * RAW_ROW, st + RAW_BYTES * NACC, row, sc0);
+            if (DUAL) expand_row<QT>(st + RAW_BYTES + row * RAW_ROW, st + RAW_BYTES * NACC + A_BYTES, row, sc1);
+          }
           fence_proxy_async();            // generic-proxy stores -> visible to the tensor core's async reads
         }
         mbar_arrive(&a_ready[s]);
@@ -555,6 +619,7 @@ static int launch_qt(int qt, const CUtensorMap& a, const CUtensorMap& b, QGemmPa
     case Q_INT4: return launch_q<BN, DUAL, Q_INT4>(a, b, p, st);
     case Q_NF4: return launch_q<BN, DUAL, Q_NF4>(a, b, p, st);
     case Q_FP8: return launch_q<BN, DUAL, Q_FP8>(a, b, p, st);
+    case Q_INT4F: return launch_q<BN, DUAL, Q_INT4F>(a, b, p, st);
   }
   return -1;
 }
@@ -563,7 +628,9 @@ static int launch_qt(int qt, const CUtensorMap& a, const CUtensorMap& b, QGemmPa
 
 using namespace xft;
 
-// qtype: 0 int8, 1 uint4, 2 nf4, 3 fp8-e4m3 (block 128x128).  Wq: [w_rows, K] int8/fp8 or [w_rows, K/2] packed.
+// qtype: 0 int8, 1 uint4, 2 nf4, 3 fp8-e4m3 (block 128x128), 4 uint4 with nibble-interleaved words (nibble i of a
+// 32-bit word = element 2i, nibble i + 4 = element 2i + 1; the kernel feeds 128 + q, so the caller passes
+// zero - 128 * scale and always the row sums).  Wq: [w_rows, K] int8/fp8 or [w_rows, K/2] packed.
 // scale/zero: see QGemmParams.  xsum: [T] row sums of X, required when zero != null.
 extern "C" int xft_qgemm(const void* X, int ldx, const void* Wq, int w_rows, int ldw_bytes, int qtype, void* Y, int ldo,
                          int out_fp32, int T, int N, int K, int gated, int dual_off, const float* scale, const float* zero,

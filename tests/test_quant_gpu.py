@@ -16,9 +16,11 @@ def _close(got, want, atol, rtol, what):
 
 
 @pytest.mark.parametrize("kind", ["int8", "int4", "nf4", "fp8", "w8a8"])
-@pytest.mark.parametrize("T,N,K", [(5, 384, 512), (48, 256, 1024), (130, 640, 256), (16, 1024, 4096)])
+@pytest.mark.parametrize("T,N,K", [(5, 384, 512), (48, 256, 1024), (130, 640, 256), (16, 1024, 4096), (7, 200, 328)])
 def test_quant_linear(kind, T, N, K):
     from xfastertransformer_b200.ops import native as Nat
+    if kind == "w8a8" and K % 16:
+        pytest.skip("the int8 tensor path needs K % 16 == 0")
     g = torch.Generator().manual_seed(T + N + len(kind))
     x = (torch.randn(T, K, generator=g) * 0.5).bfloat16()
     w = torch.randn(N, K, generator=g) * 0.05

@@ -8,7 +8,7 @@ import torch
 
 from . import native as N
 
-_QT = {"int8": 0, "int4": 1, "nf4": 2, "fp8": 3}
+_QT = {"int8": 0, "int4": 1, "nf4": 2, "fp8": 3, "int4f": 4}
 _ready = False
 
 
@@ -28,6 +28,25 @@ def _row_sums(x2, ldx):
     N._check(_lib().xft_row_sum(N._p(x2), ldx, N._p(out), T, K, N._stream()), "row_sum")
     N.Workspace.get(x2.device).launches += 1
     return out
+
+
+def _int4_fast(W, w):
+    """uint4 weights in the kernel's fast layout (cached on the weight): within every 32-bit word the eight codes
+    e0..e7 move from nibble order [e0 e1 ... e7] to [e0 e2 e4 e6 | e1 e3 e5 e7], which lets the kernel build a bf16
+    pair with one shift and one logic op; and the zero point absorbs the constant 128 the kernel adds to each code."""
+    c = W.cache.get("int4f")
+    if c is None:
+        w32 = w.contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+        out = torch.zeros_like(w32)
+        for i in range(4):
+            out |= ((w32 >> (8 * i)) & 0xF) << (4 * i)                 # e_{2i}   -> nibble i
+            out |= ((w32 >> (8 * i + 4)) & 0xF) << (16 + 4 * i)        # e_{2i+1} -> nibble i + 4
+        out = torch.where(out >= 2 ** 31, out - 2 ** 32, out).to(torch.int32)
+        wf = out.view(torch.uint8).view(w.shape[0], -1)
+        zero = (W.zero if W.zero is not None else torch.zeros_like(W.scale)) - 128.0 * W.scale
+        c = (wf, zero.contiguous())
+        W.cache["int4f"] = c
+    return c
 
 
 def _qgemm(x, W, n_out, gated, bias, act, residual, res_scale, out_dtype):
@@ -56,7 +75,16 @@ def _qgemm(x, W, n_out, gated, bias, act, residual, res_scale, out_dtype):
             W.cache["w_pitch16"] = wp
         w = wp
     scale_ld = W.scale.shape[1] if W.kind == "fp8" else 0
-    rc = _lib().xft_qgemm(N._p(x2), ldx, N._p(w), w.shape[0], w.stride(0) * w.element_size(), _QT[W.kind], N._p(out),
+    kind = W.kind
+    if kind == "int4":
+        cols = w.shape[1]
+        full = w if w.is_contiguous() else torch.as_strided(w, (w.shape[0], w.stride(0)), (w.stride(0), 1))
+        wq, zero = _int4_fast(W, full)
+        w = wq[:, :cols]
+        kind = "int4f"
+        if xsum is None:
+            xsum = _row_sums(x2, ldx)
+    rc = _lib().xft_qgemm(N._p(x2), ldx, N._p(w), w.shape[0], w.stride(0) * w.element_size(), _QT[kind], N._p(out),
                           out.stride(0), int(fp32), T, n_out, K, int(gated), n_out if gated else 0, N._p(W.scale),
                           N._p(zero), N._p(xsum), scale_ld, N._p(bias), N._p(r2), ldr, C.c_float(res_scale),
                           N._ACT[act], N._p(ws.ws), C.c_size_t(ws.ws_bytes), N._p(ws.counters), ws.n_counters,
