@@ -45,6 +45,12 @@ struct QGemmParams {
   // w8a8
   const float* a_scale; const float* a_zero; const float* a_qsum;   // [T]
   const float* w_sum;      // [N] sum_k qw
+  // Grouped mode (MoE experts, fp8 block-scaled weights): token tile i is group_tiles[i] = {group, first row, rows, -};
+  // the weight rows (and, /128, the scale rows) of group g start at g * group_w_rows.  No split-K.
+  const int4* group_tiles;
+  const int* num_group_tiles;
+  int group_w_rows;
+  const float* col_scale;  // optional per-token factor on the result (routing weight)
 };
 
 __device__ __forceinline__ float q_act(float x, int act) {
@@ -201,6 +207,22 @@ __global__ void __launch_bounds__(192) qgemm_kernel(const __grid_constant__ CUte
   tcgen05_fence_after();
   const uint32_t tmem_base = tmem_base_s;
   grid_dep_launch();
+  __shared__ int s_group[4];
+  const bool grouped = p.group_tiles != nullptr;
+  if (grouped) {
+    grid_dep_wait();          // the tile table comes from the routing plan kernel
+    if (threadIdx.x == 0) {
+      int4 e = make_int4(0, 0, 0, 0);
+      if (tile_t < *p.num_group_tiles) e = p.group_tiles[tile_t];
+      s_group[0] = e.x; s_group[1] = e.y; s_group[2] = e.z;
+    }
+    __syncthreads();
+  }
+  const int w_row0 = grouped ? s_group[0] * p.group_w_rows : 0;
+  const int x_row0 = grouped ? s_group[1] : tile_t * BN;
+  const int x_rows = grouped ? s_group[2] : BN;
+  const bool active = !grouped || x_rows > 0;
+  const int kend = active ? kb1 : kb0;
 
   // stage layout: [raw A (xNACC)] [bf16 A (xNACC)] [B]
   if (warp == 0) {
@@ -210,30 +232,30 @@ __global__ void __launch_bounds__(192) qgemm_kernel(const __grid_constant__ CUte
       constexpr int KEL = (QT == Q_INT8 || QT == Q_FP8) ? 64 : 32;      // raw bytes per k-block row
       // weights never depend on the previous kernel: the first `stages` raw tiles are requested before the grid
       // dependency resolves
-      const int pre = min(stages, kb1 - kb0);
+      const int pre = min(stages, kend - kb0);
       for (int i = 0; i < pre; ++i) {
         mbar_expect_tx(&raw_full[i], TX_BYTES);
         uint8_t* st = smem + i * STAGE_BYTES;
-        tma_load_2d(st, &tmW, &raw_full[i], (kb0 + i) * KEL, tile_n * 128, hint_w);
-        if (DUAL) tma_load_2d(st + RAW_BYTES, &tmW, &raw_full[i], (kb0 + i) * KEL, p.dual_off + tile_n * 128, hint_w);
+        tma_load_2d(st, &tmW, &raw_full[i], (kb0 + i) * KEL, w_row0 + tile_n * 128, hint_w);
+        if (DUAL) tma_load_2d(st + RAW_BYTES, &tmW, &raw_full[i], (kb0 + i) * KEL, w_row0 + p.dual_off + tile_n * 128, hint_w);
       }
       grid_dep_wait();
       for (int i = 0; i < pre; ++i)
-        tma_load_2d(smem + i * STAGE_BYTES + (RAW_BYTES + A_BYTES) * NACC, &tmX, &raw_full[i], (kb0 + i) * 64, tile_t * BN, hint_x);
+        tma_load_2d(smem + i * STAGE_BYTES + (RAW_BYTES + A_BYTES) * NACC, &tmX, &raw_full[i], (kb0 + i) * 64, x_row0, hint_x);
       int it = pre;
-      for (int kb = kb0 + pre; kb < kb1; ++kb, ++it) {
+      for (int kb = kb0 + pre; kb < kend; ++kb, ++it) {
         const int s = it % stages;
         const uint32_t ph = (it / stages) & 1;
         if (!mbar_wait(&empty_bar[s], ph ^ 1, p.status, XFT_ERR_WAIT_EMPTY)) break;
         mbar_expect_tx(&raw_full[s], TX_BYTES);
         uint8_t* st = smem + s * STAGE_BYTES;
-        tma_load_2d(st, &tmW, &raw_full[s], kb * KEL, tile_n * 128, hint_w);
-        if (DUAL) tma_load_2d(st + RAW_BYTES, &tmW, &raw_full[s], kb * KEL, p.dual_off + tile_n * 128, hint_w);
-        tma_load_2d(st + (RAW_BYTES + A_BYTES) * NACC, &tmX, &raw_full[s], kb * 64, tile_t * BN, hint_x);
+        tma_load_2d(st, &tmW, &raw_full[s], kb * KEL, w_row0 + tile_n * 128, hint_w);
+        if (DUAL) tma_load_2d(st + RAW_BYTES, &tmW, &raw_full[s], kb * KEL, w_row0 + p.dual_off + tile_n * 128, hint_w);
+        tma_load_2d(st + (RAW_BYTES + A_BYTES) * NACC, &tmX, &raw_full[s], kb * 64, x_row0, hint_x);
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (lane == 0 && active) {
       int it = 0;
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % stages;
@@ -265,7 +287,7 @@ __global__ void __launch_bounds__(192) qgemm_kernel(const __grid_constant__ CUte
     {
       int it = 0;
       bool alive = true;
-      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+      for (int kb = kb0; kb < kend; ++kb, ++it) {
         const int s = it % stages;
         const uint32_t ph = (it / stages) & 1;
         if (alive && !mbar_wait(&raw_full[s], ph, p.status, XFT_ERR_WAIT_FULL)) alive = false;
@@ -273,8 +295,8 @@ __global__ void __launch_bounds__(192) qgemm_kernel(const __grid_constant__ CUte
           uint8_t* st = smem + s * STAGE_BYTES;
           float sc0 = 1.f, sc1 = 1.f;
           if (QT == Q_FP8) {
-            sc0 = p.scale[(size_t)tile_n * p.scale_ld + (kb >> 1)];
-            if (DUAL) sc1 = p.scale[(size_t)((p.dual_off >> 7) + tile_n) * p.scale_ld + (kb >> 1)];
+            sc0 = p.scale[(size_t)((w_row0 >> 7) + tile_n) * p.scale_ld + (kb >> 1)];
+            if (DUAL) sc1 = p.scale[(size_t)((w_row0 >> 7) + (p.dual_off >> 7) + tile_n) * p.scale_ld + (kb >> 1)];
           }
           if (QT == Q_INT8 || QT == Q_INT4F) {
             expand_tile<QT>(st, st + RAW_BYTES * NACC, et);
@@ -289,10 +311,10 @@ __global__ void __launch_bounds__(192) qgemm_kernel(const __grid_constant__ CUte
       }
     }
     grid_dep_wait();
-    bool ok = mbar_wait(&tmem_full_bar, 0, p.status, XFT_ERR_WAIT_TMEM);
+    bool ok = active && mbar_wait(&tmem_full_bar, 0, p.status, XFT_ERR_WAIT_TMEM);
     tcgen05_fence_after();
     const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16);
-    const int t0 = tile_t * BN;
+    const int t0 = x_row0;
     bool last = true;
     if (p.splits > 1) {
       float* wsp = p.ws + ((size_t)split * (p.n_tiles * p.t_tiles) + tile_id) * (size_t)(BN * NACC) * 128;
@@ -358,11 +380,12 @@ __global__ void __launch_bounds__(192) qgemm_kernel(const __grid_constant__ CUte
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int t = t0 + c + j;
-            if (t < p.T) {
+            if (t < p.T && c + j < x_rows) {
               const float xs = (p.zero && p.xsum) ? p.xsum[t] : 0.f;
               float x = g[j] * sg + zg * xs + bias_g;
               x = q_act(x, p.act);
               if (DUAL) x *= (u[j] * su + zu * xs + bias_u);
+              if (p.col_scale) x *= p.col_scale[t];
               if (p.residual) x += p.res_scale * __bfloat162float(p.residual[(size_t)t * p.ldr + n]);
               if (p.out_fp32) reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + n] = x;
               else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)t * p.ldo + n] = __float2bfloat16(x);
@@ -659,6 +682,37 @@ extern "C" int xft_qgemm(const void* X, int ldx, const void* Wq, int w_rows, int
 #define XFT_Q(BN_) case BN_: return gated ? launch_qt<BN_, true>(qtype, tmW, tmX, p, st) : launch_qt<BN_, false>(qtype, tmW, tmX, p, st);
   switch (bn) { XFT_Q(16) XFT_Q(32) XFT_Q(64) XFT_Q(128) }
 #undef XFT_Q
+  return -1;
+}
+
+// Grouped (MoE expert) form of the fp8 block-scaled GEMM: Wq stacks the experts' [group_w_rows, K] e4m3 matrices,
+// scale stacks their [group_w_rows/128, ceil(K/128)] block scales, group_tiles / num_group_tiles come from
+// xft_moe_plan (csrc/kernels/moe.cu).  gated: rows [0, N) of an expert are the gate, rows [dual_off, dual_off + N) the
+// up projection.  col_scale: per-row factor on the result (routing weight).  Keeps DeepSeek-V3/R1 experts in fp8 on the
+// device (the reference's fp8 expert GEMM: src/layers/moe_deepseek.h, xdnn_*_f8e4m3 calls in src/utils/matmul_helper.h).
+extern "C" int xft_qgemm_grouped(const void* X, int ldx, int x_rows, const void* Wq, int w_rows, int ldw_bytes, void* Y,
+                                 int ldo, int out_fp32, int N, int K, int gated, int dual_off, int group_w_rows,
+                                 const float* scale, int scale_ld, const void* group_tiles, const int* num_group_tiles,
+                                 int max_tiles, int bn, const float* col_scale, int act, int* status, cudaStream_t st) {
+  if (x_rows <= 0 || N <= 0 || K <= 0 || max_tiles <= 0) return 0;
+  if ((group_w_rows & 127) || (gated && (dual_off & 127)) || (K & 15)) return -4;
+  QGemmParams p{};
+  p.N = N; p.T = x_rows; p.K = K; p.dual_off = dual_off; p.out = Y; p.ldo = ldo; p.out_fp32 = out_fp32;
+  p.res_scale = 1.f; p.act = act; p.status = status; p.scale = scale; p.scale_ld = scale_ld;
+  p.group_tiles = reinterpret_cast<const int4*>(group_tiles); p.num_group_tiles = num_group_tiles;
+  p.group_w_rows = group_w_rows; p.col_scale = col_scale;
+  p.n_tiles = (N + 127) / 128;
+  p.t_tiles = max_tiles;
+  p.num_kb = (K + 63) / 64;
+  p.splits = 1; p.kb_per_split = p.num_kb;
+  CUtensorMap tmW, tmX;
+  int r = make_raw_map(&tmW, Wq, (uint64_t)w_rows, (uint64_t)K, (uint64_t)ldw_bytes, 128, 64);
+  if (r) return 1000 - r;
+  r = make_tensor_map(&tmX, X, (uint64_t)x_rows, (uint64_t)K, (uint64_t)ldx, (uint32_t)bn, 2);
+  if (r) return 2000 - r;
+#define XFT_QG(BN_) case BN_: return gated ? launch_q<BN_, true, Q_FP8>(tmW, tmX, p, st) : launch_q<BN_, false, Q_FP8>(tmW, tmX, p, st);
+  switch (bn) { XFT_QG(16) XFT_QG(32) XFT_QG(64) XFT_QG(128) }
+#undef XFT_QG
   return -1;
 }
 

@@ -90,3 +90,31 @@ def test_tiny_moe_models(mt, tmp_path):
     want = torch.load(str(tmp_path / "cpu.pt"))
     rel = (got - want).abs().max().item() / max(want.abs().max().item(), 1e-6)
     assert rel < 0.08, rel
+
+
+@pytest.mark.parametrize("T,E,k,I,H", [(5, 8, 2, 256, 512), (70, 8, 4, 128, 256), (300, 16, 2, 256, 512)])
+def test_moe_experts_fp8_grouped(T, E, k, I, H):
+    """fp8 block-scaled experts run through the grouped fp8 GEMM (weights stay e4m3 on the device)."""
+    from xfastertransformer_b200.ops import native as Nat
+    from xfastertransformer_b200.ops import native_moe
+    g = torch.Generator().manual_seed(T + E + 1)
+    x = (torch.randn(T, H, generator=g) * 0.5).bfloat16()
+    experts = []
+    for _ in range(E):
+        gu = make_linear(torch.randn(2 * I, H, generator=g) * 0.05, "fp8")
+        dn = make_linear(torch.randn(H, I, generator=g) * 0.05, "fp8")
+        experts.append((gu, dn))
+    logits = torch.randn(T, E, generator=g)
+    idx, w = R.route_mixtral(logits, k)
+    want = R.moe_experts(x.float(), idx, w, experts, "silu")
+    cuda_experts = [(a.to("cuda"), b.to("cuda")) for a, b in experts]
+    pk = native_moe.pack_experts(cuda_experts)
+    assert pk.get("fp8") and pk["gu"].dtype == torch.uint8
+    got = Nat.moe_experts(x.cuda(), idx.cuda().int(), w.cuda(), cuda_experts, "silu", packed=pk)
+    Nat.Workspace.get(torch.device("cuda", 0)).check_status()
+    err = (got.cpu() - want).abs().max().item()
+    assert err < 3e-2 * max(1.0, want.abs().max().item()), err
+    lo = 3
+    want2 = R.moe_experts(x.float(), idx, w, experts[lo:], "silu", expert_offset=lo)
+    got2 = Nat.moe_experts(x.cuda(), idx.cuda().int(), w.cuda(), cuda_experts[lo:], "silu", expert_offset=lo)
+    assert (got2.cpu() - want2).abs().max().item() < 3e-2 * max(1.0, want2.abs().max().item())

@@ -19,7 +19,8 @@ def _lib():
     global _ready
     lib = N.lib()
     if not _ready:
-        for fn in ("xft_moe_route", "xft_moe_plan", "xft_moe_gather", "xft_moe_combine", "xft_gemm_bf16_grouped"):
+        for fn in ("xft_moe_route", "xft_moe_plan", "xft_moe_gather", "xft_moe_combine", "xft_gemm_bf16_grouped",
+                   "xft_qgemm_grouped"):
             getattr(lib, fn).restype = C.c_int
         _ready = True
     return lib
@@ -49,6 +50,8 @@ def pack_experts(experts) -> dict:
     pk = gu0.cache.get("moe_pack")
     if pk is not None and pk["E"] == len(experts) and pk["last"] is experts[-1][0]:
         return pk
+    if all(g.kind == "fp8" and d.kind == "fp8" for g, d in experts) and _fp8_packable(gu0, dn0):
+        return _pack_fp8(experts)
     I, H = dn0.in_features, dn0.out_features
     E = len(experts)
     dev = gu0.w.device
@@ -63,6 +66,35 @@ def pack_experts(experts) -> dict:
         if d.kind == "bf16":
             d.w = dv
     pk = dict(gu=gu, dn=dn, I=I, H=H, E=E, last=experts[-1][0])
+    gu0.cache["moe_pack"] = pk
+    return pk
+
+
+def _fp8_packable(gu: "object", dn: "object") -> bool:
+    I, H = dn.in_features, dn.out_features
+    return gu.block == 128 and dn.block == 128 and I % 128 == 0 and H % 128 == 0
+
+
+def _pack_fp8(experts) -> dict:
+    """fp8 experts stay fp8 on the device: the e4m3 matrices and their 128x128 block scales are stacked and the
+    grouped fp8 GEMM expands tiles to bf16 in shared memory on the way to the tensor core."""
+    gu0, dn0 = experts[0]
+    I, H = dn0.in_features, dn0.out_features
+    E = len(experts)
+    dev = gu0.w.device
+    gu = torch.empty(E * 2 * I, H, dtype=torch.uint8, device=dev)
+    dn = torch.empty(E * H, I, dtype=torch.uint8, device=dev)
+    gus = torch.empty(E * (2 * I // 128), gu0.scale.shape[1], dtype=torch.float32, device=dev)
+    dns = torch.empty(E * (H // 128), dn0.scale.shape[1], dtype=torch.float32, device=dev)
+    for e, (g, d) in enumerate(experts):
+        gv, dv = gu[e * 2 * I:(e + 1) * 2 * I], dn[e * H:(e + 1) * H]
+        gv.copy_(g.w.view(torch.uint8))
+        dv.copy_(d.w.view(torch.uint8))
+        gus[e * (2 * I // 128):(e + 1) * (2 * I // 128)].copy_(g.scale)
+        dns[e * (H // 128):(e + 1) * (H // 128)].copy_(d.scale)
+        g.w = gv.view(torch.float8_e4m3fn)               # re-point at the stack: nothing is held twice
+        d.w = dv.view(torch.float8_e4m3fn)
+    pk = dict(gu=gu, dn=dn, gus=gus, dns=dns, I=I, H=H, E=E, fp8=True, last=experts[-1][0])
     gu0.cache["moe_pack"] = pk
     return pk
 
@@ -93,6 +125,19 @@ def moe_experts(x, idx, w, experts, act="silu", expert_offset=0, packed=None):
     xs = torch.empty(max_rows, H, dtype=torch.bfloat16, device=dev)
     N._check(lib.xft_moe_gather(N._p(x2), ldx, N._p(src), N._p(meta), N._p(xs), max_rows, H, N._stream()), "moe_gather")
     h1 = torch.empty(max_rows, I, dtype=torch.bfloat16, device=dev)
+    if pk.get("fp8"):
+        ys = torch.empty(max_rows, H, dtype=torch.float32, device=dev)
+        N._check(lib.xft_qgemm_grouped(N._p(xs), H, max_rows, N._p(pk["gu"]), E * 2 * I, H, N._p(h1), I, 0, I, H, 1, I, 2 * I,
+                                       N._p(pk["gus"]), pk["gus"].shape[1], N._p(tiles), N._p(meta), max_tiles, min(bn, 128),
+                                       N._p(None), N._ACT[act], N._p(ws.status), N._stream()), "grouped fp8 gate_up")
+        N._check(lib.xft_qgemm_grouped(N._p(h1), I, max_rows, N._p(pk["dn"]), E * H, I, N._p(ys), H, 1, H, I, 0, 0, H,
+                                       N._p(pk["dns"]), pk["dns"].shape[1], N._p(tiles), N._p(meta), max_tiles, min(bn, 128),
+                                       N._p(row_w), 0, N._p(ws.status), N._stream()), "grouped fp8 down")
+        out = torch.empty(T, H, dtype=torch.float32, device=dev)
+        N._check(lib.xft_moe_combine(N._p(ys), N._p(pos), k, N._p(None), N._p(None), 0, N._p(None), N._p(out), T, H,
+                                     N._stream()), "moe_combine")
+        ws.launches += 5
+        return out
     N._check(lib.xft_gemm_bf16_grouped(N._p(xs), H, max_rows, N._p(pk["gu"]), E * 2 * I, H, N._p(h1), I, 0, I, H, 1, I,
                                        2 * I, N._p(tiles), N._p(meta), max_tiles, bn, N._p(None), N._ACT[act],
                                        N._p(ws.status), N._stream()), "grouped gate_up")
