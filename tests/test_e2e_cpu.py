@@ -61,3 +61,21 @@ def test_ws2_gloo(tiny, tmp_path):
     # TP really split the work: FFN 688 over 2 ranks -> 352 + 336, two allreduces per layer per step
     assert got["ffn"] == [352, 336]
     assert got["all_reduce"] > 0
+
+
+def test_pipeline_parallel_two_stages_gloo(tiny, tmp_path):
+    """XFT_PIPELINE_STAGE=2 on two gloo ranks: stage 0 owns layer 0, stage 1 layer 1 and the head; the hidden state
+    crosses by send/recv and the logits come back to every stage; tokens equal the single-process greedy result."""
+    out = str(tmp_path / "pp2.pt")
+    env = dict(os.environ, XFT_ENGINE="CPU", XFT_PIPELINE_STAGE="2",
+               PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29613", os.path.join(ROOT, "tests", "pp_worker.py"), tiny, out]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    got = torch.load(out)
+    ids = _prompt()
+    ref = EagerLlama(tiny)
+    assert torch.allclose(got["logits"], ref.logits(ids)[:, -1], atol=2e-3, rtol=2e-3)
+    assert torch.equal(got["tokens"], ref.greedy(ids, 16))
+    assert sorted(got["layers"]) == [(0, 1, 0, 0), (1, 2, 1, 0)]

@@ -43,3 +43,28 @@ def test_tp_peer_comm_and_model(world, tmp_path):
         for t in range(32, tokens.shape[1]):
             row = full[b, t - 1]
             assert row[tokens[b, t]] >= row.max() - 0.1 * max(1.0, row.abs().max().item()), (b, t)
+
+
+def test_pipeline_parallel_two_gpus(tmp_path):
+    """Two pipeline stages on two GPUs (NCCL send/recv of the hidden state, logits broadcast back): every generated
+    token is (near-)argmax of the fp32 eager model's logits."""
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    d = str(tmp_path / "tiny")
+    write_synthetic_checkpoint(d, preset("tiny-llama"), seed=0, dtype="bf16", std=0.05)
+    out = str(tmp_path / "pp.pt")
+    env = dict(os.environ, XFT_DIST_TIMEOUT_S="120", XFT_PIPELINE_STAGE="2", NCCL_NVLS_ENABLE="0",
+               PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29731", os.path.join(ROOT, "tests", "pp_worker.py"), d, out]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-4000:] + r.stderr[-4000:]
+    got = torch.load(out)
+    assert sorted(got["layers"]) == [(0, 1, 0, 0), (1, 2, 1, 0)]
+    tokens = got["tokens"]
+    ref = EagerLlama(d)
+    full = ref.logits(tokens[:, :-1])
+    for b in range(tokens.shape[0]):
+        for t in range(32, tokens.shape[1]):
+            row = full[b, t - 1]
+            assert row[tokens[b, t]] >= row.max() - 0.1 * max(1.0, row.abs().max().item()), (b, t)

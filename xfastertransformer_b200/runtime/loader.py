@@ -245,7 +245,7 @@ class WeightSource:
 
     def fp8_linear(self, name: str, in_f: int, out_f: int, in_rng=None, out_rng=None, kind: str = "fp8") -> LinearWeight:
         """DeepSeek projection: ``<name>.weight.bin`` uint8 e4m3 [in,out] (or bf16 when converted so) +
-        ``<name>.weight_scale_inv.bin`` fp32 [ceil(in/128), ceil(out/128)] (SURVEY of the format:
+        ``<name>.weight_scale_inv.bin`` fp32 [ceil(in/128), ceil(out/128)] (format:
         deepseek_moe_convert.py:117-180; decoder_block.h:526-587).  Slices must be 128-aligned."""
         wname = name + ".weight.bin"
         if self.fake or self.dtype != "fp8_e4m3":
