@@ -1,7 +1,10 @@
 // C ABI over the host-side runtime so that Python (ctypes) and tests can drive the C++ twins of the layout
 // arithmetic, the block allocator and the samplers without a GPU.
+#include <chrono>
 #include <cstring>
+#include <string>
 
+#include "env.h"
 #include "runtime.h"
 #include "xft/layers.h"
 
@@ -47,6 +50,35 @@ void xftc_repetition_penalty(float* l, int n, const int* toks, int nt, float pen
   repetitionPenalty(l, n, std::vector<int32_t>(toks, toks + nt), pen, off);
 }
 
+
+// ---- environment flags and the timeline (csrc/core/env.cc)
+void xftc_env_reload() { Env::get().reload(); }
+int xftc_env_int(const char* name) {
+  const Env& e = Env::get();
+  const std::string n(name);
+  if (n == "verbose") return e.verbose;
+  if (n == "pipeline_stage") return e.pipelineStage;
+  if (n == "fake_model") return e.fakeModel;
+  if (n == "timeline") return e.timeline ? 1 : 0;
+  if (n == "kv_block_size") return e.kvBlockSize;
+  if (n == "cuda_graph") return e.cudaGraph ? 1 : 0;
+  if (n == "max_batch_tokens") return e.maxBatchTokens;
+  if (n == "attn_splits") return e.attnSplits;
+  if (n == "whitelist_size") return (int)e.timelineWhitelist.size();
+  return -1;
+}
+void xftc_timeline_enable(int on) { TimeLine::enable(on != 0); }
+void xftc_timeline_scope(const char* name, int spin_us) {
+  TimeLine t(name);
+  const auto t0 = std::chrono::steady_clock::now();
+  while (std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count() < spin_us) {}
+}
+int xftc_timeline_pending() { return (int)TimeLine::pending(); }
+int xftc_timeline_dump(const char* path, char* out, int cap) {
+  const std::string f = TimeLine::dump(path ? path : "");
+  if (out && cap > 0) { std::strncpy(out, f.c_str(), cap - 1); out[cap - 1] = 0; }
+  return (int)f.size();
+}
 
 // ---- the stateful layer API (csrc/core/layer_objects.cc) on device pointers, stream 0
 int xftc_layer_llama(int batch, int seq, int headDim, int heads, int kvHeads, int maxPos, int past, int hidden, int inter,

@@ -14,6 +14,7 @@
 #include <random>
 #include <stdexcept>
 
+#include "env.h"
 #include "ini.h"
 #include "kernels_c.h"
 #include "runtime.h"
@@ -304,6 +305,16 @@ void Engine::attachPrefix(SequenceMeta& s) {
 }
 
 int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
+  TimeLine tl("Decoder.forward");
+  const auto t_begin = std::chrono::steady_clock::now();
+  struct StepLog {
+    const std::chrono::steady_clock::time_point t0; size_t n;
+    ~StepLog() {
+      if (Env::get().verbose >= 1)
+        log(LogLevel::Info, "forward: %zu sequences, %.3f ms", n,
+            std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count());
+    }
+  } step_log{t_begin, seqIds.size()};
   std::vector<int> ids, pos, slots, cu{0}, kvl, rowsel;
   bool decode = true;
   int maxQ = 0, maxKv = 0;
@@ -507,6 +518,7 @@ bool Model::isDone() {
 }
 
 std::vector<int32_t> Model::generate() {
+  TimeLine tl("Model.generate");
   if (engine->working.empty()) throw std::runtime_error("generate() before input()/set_input()");
   std::vector<int> active;
   for (int id : engine->working) if (!engine->pool.get(id).done) active.push_back(id);
@@ -541,6 +553,7 @@ std::vector<int32_t> Model::generate() {
 }
 
 std::vector<int32_t> Model::finalize() {
+  if (Env::get().timeline) TimeLine::dump();       // as the reference: the trace is written when a request ends
   size_t w = 0;
   for (int id : engine->working) w = std::max<size_t>(w, engine->pool.get(id).totalLen());
   std::vector<int32_t> out;

@@ -135,3 +135,40 @@ def test_split_k_planner_choices():
     assert plan(400, 128) == 1          # more tiles than slots: never split
     assert 8 <= plan(10, 128) <= 16     # a TP=8 slice needs many splits to reach the HBM rate
     assert plan(28, 128, bn=64, nacc=2) <= 3   # wide token tiles pay for the reduction
+
+
+def test_cpp_env_flags_and_timeline(core, tmp_path, monkeypatch):
+    """csrc/core/env.cc: the Env singleton reads the same variables as the Python package; TimeLine scopes honour the
+    whitelist and dump a chrome trace."""
+    import ctypes
+    import json
+    core.xftc_env_int.argtypes = [ctypes.c_char_p]
+    monkeypatch.setenv("XFT_VERBOSE", "2")
+    monkeypatch.setenv("XFT_PIPELINE_STAGE", "3")
+    monkeypatch.setenv("XFT_TIMELINE", "1")
+    monkeypatch.setenv("XFT_TIMELINE_WHITELIST", "A.scope,B.scope")
+    monkeypatch.setenv("XFT_MAX_BATCH_TOKENS", "4096")
+    core.xftc_env_reload()
+    assert core.xftc_env_int(b"verbose") == 2
+    assert core.xftc_env_int(b"pipeline_stage") == 3
+    assert core.xftc_env_int(b"timeline") == 1
+    assert core.xftc_env_int(b"whitelist_size") == 2
+    assert core.xftc_env_int(b"max_batch_tokens") == 4096
+    assert core.xftc_env_int(b"kv_block_size") == 64
+    core.xftc_timeline_scope.argtypes = [ctypes.c_char_p, ctypes.c_int]
+    core.xftc_timeline_scope(b"A.scope", 200)
+    core.xftc_timeline_scope(b"not.listed", 10)
+    core.xftc_timeline_scope(b"B.scope", 100)
+    assert core.xftc_timeline_pending() == 2
+    path = str(tmp_path / "trace.json").encode()
+    buf = ctypes.create_string_buffer(512)
+    core.xftc_timeline_dump.argtypes = [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_int]
+    assert core.xftc_timeline_dump(path, buf, 512) > 0
+    ev = json.load(open(path.decode()))["traceEvents"]
+    assert [e["name"] for e in ev] == ["A.scope", "B.scope"] and ev[0]["dur"] >= 200 and ev[0]["ph"] == "X"
+    assert core.xftc_timeline_pending() == 0
+    monkeypatch.delenv("XFT_TIMELINE")
+    monkeypatch.delenv("XFT_TIMELINE_WHITELIST")
+    core.xftc_env_reload()
+    core.xftc_timeline_scope(b"A.scope", 10)
+    assert core.xftc_timeline_pending() == 0
