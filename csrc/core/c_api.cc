@@ -1,9 +1,11 @@
 // C ABI over the host-side runtime so that Python (ctypes) and tests can drive the C++ twins of the layout
 // arithmetic, the block allocator and the samplers without a GPU.
 #include <chrono>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 
+#include "arena.h"
 #include "env.h"
 #include "runtime.h"
 #include "xft/layers.h"
@@ -50,6 +52,18 @@ void xftc_repetition_penalty(float* l, int n, const int* toks, int nt, float pen
   repetitionPenalty(l, n, std::vector<int32_t>(toks, toks + nt), pen, off);
 }
 
+
+// ---- caching arena (csrc/core/arena.cc) over malloc/free, for tests without a GPU
+void* xftc_arena_new_host() { return new Arena([](size_t n) { return std::malloc(n); }, [](void* p) { std::free(p); }); }
+void xftc_arena_delete(void* a) { delete static_cast<Arena*>(a); }
+void* xftc_arena_alloc(void* a, size_t n) { return static_cast<Arena*>(a)->allocate(n); }
+void xftc_arena_release(void* a, void* p) { static_cast<Arena*>(a)->release(p); }
+void xftc_arena_trim(void* a) { static_cast<Arena*>(a)->trim(); }
+size_t xftc_arena_stat(void* a, int what) {
+  Arena* ar = static_cast<Arena*>(a);
+  return what == 0 ? ar->bytesInUse() : what == 1 ? ar->bytesCached() : ar->backendCalls();
+}
+size_t xftc_arena_round(size_t n) { return Arena::roundUp(n); }
 
 // ---- environment flags and the timeline (csrc/core/env.cc)
 void xftc_env_reload() { Env::get().reload(); }

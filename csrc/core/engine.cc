@@ -14,6 +14,7 @@
 #include <random>
 #include <stdexcept>
 
+#include "arena.h"
 #include "env.h"
 #include "ini.h"
 #include "kernels_c.h"
@@ -44,11 +45,16 @@ struct DevBuf {
   DevBuf& operator=(const DevBuf&) = delete;
   DevBuf(DevBuf&& o) noexcept : p(o.p), bytes(o.bytes) { o.p = nullptr; o.bytes = 0; }
   DevBuf& operator=(DevBuf&& o) noexcept { std::swap(p, o.p); std::swap(bytes, o.bytes); return *this; }
-  ~DevBuf() { if (p) cudaFree(p); }
+  ~DevBuf() { if (p) Arena::device().release(p); }
+  // device memory comes from the caching arena: buffers that are dropped and re-created between requests
+  // (scratch that grows, KV pools that are reallocated) reuse cached blocks instead of calling cudaMalloc
   void reset(size_t n) {
-    if (p) { cudaFree(p); p = nullptr; }
+    if (p) { Arena::device().release(p); p = nullptr; }
     bytes = n;
-    if (n) XFT_CUDA(cudaMalloc(&p, n));
+    if (n) {
+      p = Arena::device().allocate(n);
+      if (!p) throw std::runtime_error("out of device memory allocating " + std::to_string(n) + " bytes");
+    }
   }
   void ensure(size_t n) { if (n > bytes) reset(n + n / 4); }
   template <class T> T* as() const { return static_cast<T*>(p); }
@@ -408,7 +414,10 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
 
 // ----------------------------------------------------------------------------------------------------------------
 Model::Model() {}
-Model::~Model() {}
+Model::~Model() {
+  engine.reset();                 // buffers go back to the arena ...
+  Arena::device().trim();         // ... and a destroyed model returns its memory to the device
+}
 
 void Model::load(const std::string& path, DataType dt, DataType kv) { engine.reset(new Engine(path, dt, kv)); }
 int Model::getVocabSize() { return engine->vocab; }

@@ -172,3 +172,41 @@ def test_cpp_env_flags_and_timeline(core, tmp_path, monkeypatch):
     core.xftc_env_reload()
     core.xftc_timeline_scope(b"A.scope", 10)
     assert core.xftc_timeline_pending() == 0
+
+
+def test_cpp_arena_reuses_blocks(core):
+    """csrc/core/arena.cc over malloc/free: size classes, reuse from the free list (no backend call in steady state),
+    trim."""
+    import ctypes
+    c = core
+    c.xftc_arena_new_host.restype = ctypes.c_void_p
+    c.xftc_arena_alloc.restype = ctypes.c_void_p
+    c.xftc_arena_alloc.argtypes = [ctypes.c_void_p, ctypes.c_size_t]
+    c.xftc_arena_release.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+    c.xftc_arena_trim.argtypes = [ctypes.c_void_p]
+    c.xftc_arena_delete.argtypes = [ctypes.c_void_p]
+    c.xftc_arena_stat.restype = ctypes.c_size_t
+    c.xftc_arena_stat.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    c.xftc_arena_round.restype = ctypes.c_size_t
+    c.xftc_arena_round.argtypes = [ctypes.c_size_t]
+    assert c.xftc_arena_round(1) == 512 and c.xftc_arena_round(513) == 1024
+    assert c.xftc_arena_round((1 << 20) + 1) == 2 << 20 and c.xftc_arena_round(3 << 20) == 4 << 20
+    a = c.xftc_arena_new_host()
+    p1 = c.xftc_arena_alloc(a, 1000)
+    p2 = c.xftc_arena_alloc(a, 3 << 20)
+    assert p1 and p2 and c.xftc_arena_stat(a, 0) == 1024 + (4 << 20) and c.xftc_arena_stat(a, 2) == 2
+    c.xftc_arena_release(a, p1)
+    assert c.xftc_arena_stat(a, 1) == 1024
+    p3 = c.xftc_arena_alloc(a, 900)                 # same class: comes from the free list
+    assert p3 == p1 and c.xftc_arena_stat(a, 2) == 2 and c.xftc_arena_stat(a, 1) == 0
+    for _ in range(50):                             # a steady loop allocates nothing new
+        q = c.xftc_arena_alloc(a, 2 << 20)
+        c.xftc_arena_release(a, q)
+    assert c.xftc_arena_stat(a, 2) == 3
+    c.xftc_arena_release(a, p2)
+    c.xftc_arena_release(a, p3)
+    c.xftc_arena_release(a, 12345)                  # unknown pointer: ignored
+    assert c.xftc_arena_stat(a, 0) == 0 and c.xftc_arena_stat(a, 1) > 0
+    c.xftc_arena_trim(a)
+    assert c.xftc_arena_stat(a, 1) == 0
+    c.xftc_arena_delete(a)
