@@ -1,0 +1,346 @@
+#!/usr/bin/env python
+"""OpenAI-compatible HTTP server with an in-process continuous-batching scheduler.
+
+The reference reaches this surface through its vLLM fork (``serving/vllm-xft.md``: an OpenAI API server on rank 0, slave
+entry points on the other ranks).  Here the scheduler is part of the repository: one thread owns the engine and drives
+``set_input_cb`` / ``forward_cb`` / ``free_seqs`` — waiting prompts are admitted between decode steps, all running
+sequences decode together, finished ones free their KV blocks — while HTTP handler threads only enqueue requests and
+read their token streams.  Ranks other than 0 follow rank 0's control messages, as in ``serving/server.py``.
+
+    python serving/openai_server.py --model_path <dir> [--token_path <hf tokenizer dir>] --port 8000
+    torchrun --nproc-per-node 8 --master-addr 127.0.0.1 serving/openai_server.py --model_path <dir> ...
+
+Endpoints: ``POST /v1/completions``, ``POST /v1/chat/completions`` (both with ``stream``), ``GET /v1/models``,
+``GET /health``, ``GET /metrics`` (Prometheus text: requests, tokens, TTFT and per-token latency sums).  ``prompt`` may
+be a string (needs a tokenizer) or a list of token ids (answered with ``token_ids`` next to ``text``).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import queue
+import sys
+import threading
+import time
+import uuid
+from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+from typing import Dict, List, Optional
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+class Request:
+    def __init__(self, prompt_ids: List[int], max_tokens: int, temperature: float, top_p: float, top_k: int,
+                 stop_ids: List[int], seed: Optional[int]):
+        self.id = uuid.uuid4().hex[:24]
+        self.prompt_ids = prompt_ids
+        self.max_tokens = max(1, max_tokens)
+        self.temperature, self.top_p, self.top_k = temperature, top_p, top_k
+        self.stop_ids = set(stop_ids)
+        self.seed = seed
+        self.out: "queue.Queue" = queue.Queue()       # ints, then None (or an Exception) at the end
+        self.generated: List[int] = []
+        self.finish_reason = "length"
+        self.t_arrive = time.perf_counter()
+        self.t_first: Optional[float] = None
+        self.t_last: Optional[float] = None
+
+
+class Scheduler(threading.Thread):
+    """Continuous batching on one engine.  ``max_batch`` bounds the running set, ``prefill_per_step`` the prompts
+    admitted between two decode steps (a long queue must not starve the running sequences)."""
+
+    def __init__(self, model, max_batch: int = 64, prefill_per_step: int = 4, eos_id: int = -1):
+        super().__init__(daemon=True)
+        import torch
+        self.torch = torch
+        self.model = model
+        self.max_batch, self.prefill_per_step, self.eos_id = max_batch, prefill_per_step, eos_id
+        self.waiting: "queue.Queue[Request]" = queue.Queue()
+        self.running: Dict[int, Request] = {}
+        self.stop_flag = threading.Event()
+        self.metrics = dict(requests=0, finished=0, prompt_tokens=0, generated_tokens=0, ttft_sum=0.0, tpot_sum=0.0,
+                            tpot_count=0, steps=0, errors=0)
+        self.max_len = int(getattr(model.model.cfg, "max_pos_seq_len", 0) or 0)
+
+    # -- API for handler threads ------------------------------------------------------------
+    def submit(self, req: Request) -> Request:
+        self.metrics["requests"] += 1
+        self.waiting.put(req)
+        return req
+
+    def shutdown(self):
+        self.stop_flag.set()
+        self.waiting.put(None)
+
+    # -- token selection on the host (one row of fp32 logits) --------------------------------
+    def _select(self, req: Request, row) -> int:
+        torch = self.torch
+        if req.temperature <= 1e-5:
+            return int(row.argmax())
+        logits = row.float() / req.temperature
+        if req.top_k > 0 and req.top_k < logits.numel():
+            kth = torch.topk(logits, req.top_k).values[-1]
+            logits = torch.where(logits < kth, torch.full_like(logits, float("-inf")), logits)
+        probs = torch.softmax(logits, -1)
+        if req.top_p < 1.0:
+            sp, si = torch.sort(probs, descending=True)
+            keep = (torch.cumsum(sp, 0) - sp) < req.top_p
+            keep[0] = True
+            mask = torch.zeros_like(probs, dtype=torch.bool)
+            mask[si[keep]] = True
+            probs = torch.where(mask, probs, torch.zeros_like(probs))
+            probs = probs / probs.sum()
+        g = None
+        if req.seed is not None:
+            g = torch.Generator(device=probs.device).manual_seed(req.seed + len(req.generated))
+        return int(torch.multinomial(probs, 1, generator=g))
+
+    def _emit(self, req: Request, tok: int) -> bool:
+        """Record a token; returns True when the request is finished."""
+        now = time.perf_counter()
+        if req.t_first is None:
+            req.t_first = now
+            self.metrics["ttft_sum"] += now - req.t_arrive
+        else:
+            self.metrics["tpot_sum"] += now - req.t_last
+            self.metrics["tpot_count"] += 1
+        req.t_last = now
+        req.generated.append(tok)
+        self.metrics["generated_tokens"] += 1
+        req.out.put(tok)
+        if tok == self.eos_id or tok in req.stop_ids:
+            req.finish_reason = "stop"
+            return True
+        return len(req.generated) >= req.max_tokens
+
+    def _finish(self, sids: List[int]):
+        if not sids:
+            return
+        self.model.free_seqs(sids)
+        for s in sids:
+            r = self.running.pop(s)
+            self.metrics["finished"] += 1
+            r.out.put(None)
+
+    def _fail(self, reqs: List[Request], err: Exception):
+        self.metrics["errors"] += len(reqs)
+        for r in reqs:
+            r.out.put(err)
+
+    # -- the loop ---------------------------------------------------------------------------
+    def run(self):
+        while not self.stop_flag.is_set():
+            admitted: List[Request] = []
+            block = not self.running
+            while len(self.running) + len(admitted) < self.max_batch and len(admitted) < self.prefill_per_step:
+                try:
+                    r = self.waiting.get(block=block and not admitted, timeout=0.2 if block else None)
+                except queue.Empty:
+                    break
+                if r is None:
+                    return
+                admitted.append(r)
+                block = False
+            try:
+                if admitted:
+                    ok = []
+                    for r in admitted:
+                        total = len(r.prompt_ids) + r.max_tokens + 1
+                        if not r.prompt_ids or (self.max_len and total > self.max_len):
+                            self._fail([r], ValueError(f"prompt + max_tokens = {total - 1} tokens exceeds the model's "
+                                                       f"{self.max_len} positions" if r.prompt_ids else "empty prompt"))
+                        else:
+                            ok.append(r)
+                    if ok:
+                        sids = self.model.set_input_cb([r.prompt_ids for r in ok], None,
+                                                       [len(r.prompt_ids) + r.max_tokens + 1 for r in ok])
+                        logits = self.model.forward_cb()
+                        done = []
+                        for r, sid, row in zip(ok, [int(s) for s in sids], logits):
+                            self.running[sid] = r
+                            self.metrics["prompt_tokens"] += len(r.prompt_ids)
+                            if self._emit(r, self._select(r, row)):
+                                done.append(sid)
+                        self._finish(done)
+                        self.metrics["steps"] += 1
+                if self.running:
+                    sids = list(self.running)
+                    self.model.set_input_cb([self.running[s].generated[-1] for s in sids], sids, None)
+                    logits = self.model.forward_cb()
+                    done = [s for s, row in zip(sids, logits) if self._emit(self.running[s], self._select(self.running[s], row))]
+                    self._finish(done)
+                    self.metrics["steps"] += 1
+            except Exception as e:      # an engine error ends the affected requests, not the server
+                victims = list(self.running.values()) + [r for r in admitted if r not in self.running.values()]
+                try:
+                    if self.running:
+                        self.model.free_seqs(list(self.running))
+                except Exception:
+                    pass
+                self.running.clear()
+                self._fail(victims, e)
+
+
+class Tokenizer:
+    """HF tokenizer when a path is given; otherwise only token-id prompts are accepted and text is the ids joined."""
+
+    def __init__(self, path: str = ""):
+        self.tok = None
+        if path:
+            from transformers import AutoTokenizer
+            self.tok = AutoTokenizer.from_pretrained(path)
+
+    def encode(self, prompt) -> List[int]:
+        if isinstance(prompt, list):
+            if prompt and isinstance(prompt[0], list):
+                prompt = prompt[0]
+            return [int(t) for t in prompt]
+        if self.tok is None:
+            raise ValueError("text prompts need --token_path; send a list of token ids instead")
+        return self.tok(prompt, add_special_tokens=True)["input_ids"]
+
+    def chat(self, messages) -> List[int]:
+        if self.tok is not None and getattr(self.tok, "chat_template", None):
+            return self.tok.apply_chat_template(messages, add_generation_prompt=True, tokenize=True)
+        text = "".join(f"<|{m.get('role', 'user')}|>\n{m.get('content', '')}\n" for m in messages) + "<|assistant|>\n"
+        return self.encode(text)
+
+    def decode(self, ids: List[int]) -> str:
+        if self.tok is None:
+            return " ".join(str(i) for i in ids)
+        return self.tok.decode(ids, skip_special_tokens=True)
+
+    @property
+    def eos(self) -> int:
+        return self.tok.eos_token_id if self.tok is not None and self.tok.eos_token_id is not None else -1
+
+
+def make_handler(sched: Scheduler, tok: Tokenizer, model_name: str):
+    class H(BaseHTTPRequestHandler):
+        protocol_version = "HTTP/1.1"
+
+        def log_message(self, *a):
+            pass
+
+        def _json(self, code: int, obj):
+            body = json.dumps(obj).encode()
+            self.send_response(code)
+            self.send_header("Content-Type", "application/json")
+            self.send_header("Content-Length", str(len(body)))
+            self.end_headers()
+            self.wfile.write(body)
+
+        def do_GET(self):
+            if self.path == "/health":
+                return self._json(200, {"status": "ok", "running": len(sched.running), "waiting": sched.waiting.qsize()})
+            if self.path == "/v1/models":
+                return self._json(200, {"object": "list", "data": [{"id": model_name, "object": "model", "owned_by": "xft"}]})
+            if self.path == "/metrics":
+                m = sched.metrics
+                lines = [f"xft_{k} {v}" for k, v in m.items()]
+                lines.append(f"xft_running {len(sched.running)}")
+                lines.append(f"xft_waiting {sched.waiting.qsize()}")
+                body = ("\n".join(lines) + "\n").encode()
+                self.send_response(200)
+                self.send_header("Content-Type", "text/plain; version=0.0.4")
+                self.send_header("Content-Length", str(len(body)))
+                self.end_headers()
+                return self.wfile.write(body)
+            self._json(404, {"error": {"message": f"no route {self.path}"}})
+
+        def do_POST(self):
+            try:
+                q = json.loads(self.rfile.read(int(self.headers.get("Content-Length", 0))) or b"{}")
+                chat = self.path == "/v1/chat/completions"
+                if not chat and self.path != "/v1/completions":
+                    return self._json(404, {"error": {"message": f"no route {self.path}"}})
+                ids = tok.chat(q.get("messages", [])) if chat else tok.encode(q.get("prompt", ""))
+                stop_ids = [int(s) for s in q.get("stop_token_ids", [])]
+                req = Request(ids, int(q.get("max_tokens", 16)), float(q.get("temperature", 1.0 if q.get("do_sample") else 0.0)),
+                              float(q.get("top_p", 1.0)), int(q.get("top_k", 0)), stop_ids, q.get("seed"))
+            except Exception as e:
+                return self._json(400, {"error": {"message": str(e), "type": "invalid_request_error"}})
+            sched.submit(req)
+            created = int(time.time())
+            kind = "chat.completion" if chat else "text_completion"
+            if q.get("stream"):
+                self.send_response(200)
+                self.send_header("Content-Type", "text/event-stream")
+                self.send_header("Cache-Control", "no-cache")
+                self.send_header("Connection", "close")
+                self.end_headers()
+                sent = 0
+                while True:
+                    t = req.out.get()
+                    if t is None or isinstance(t, Exception):
+                        break
+                    text = tok.decode(req.generated[:sent + 1])[len(tok.decode(req.generated[:sent])):] if tok.tok else str(t) + " "
+                    sent += 1
+                    delta = {"delta": {"content": text}} if chat else {"text": text, "token_ids": [t]}
+                    chunk = {"id": req.id, "object": kind + ".chunk", "created": created, "model": model_name,
+                             "choices": [dict(index=0, finish_reason=None, **delta)]}
+                    self.wfile.write(b"data: " + json.dumps(chunk).encode() + b"\n\n")
+                    self.wfile.flush()
+                self.wfile.write(b"data: [DONE]\n\n")
+                self.wfile.flush()
+                self.close_connection = True
+                return
+            err = None
+            while True:
+                t = req.out.get()
+                if t is None:
+                    break
+                if isinstance(t, Exception):
+                    err = t
+                    break
+            if err is not None:
+                return self._json(400 if isinstance(err, ValueError) else 500, {"error": {"message": str(err)}})
+            text = tok.decode(req.generated)
+            choice = {"index": 0, "finish_reason": req.finish_reason}
+            if chat:
+                choice["message"] = {"role": "assistant", "content": text}
+            else:
+                choice.update(text=text, token_ids=req.generated)
+            self._json(200, {"id": req.id, "object": kind, "created": created, "model": model_name, "choices": [choice],
+                             "usage": {"prompt_tokens": len(req.prompt_ids), "completion_tokens": len(req.generated),
+                                       "total_tokens": len(req.prompt_ids) + len(req.generated)}})
+    return H
+
+
+def serve(model, port: int, token_path: str = "", max_batch: int = 64, prefill_per_step: int = 4, model_name: str = "xft"):
+    """Start scheduler + HTTP server (threads); returns (httpd, scheduler, bound_port)."""
+    tok = Tokenizer(token_path)
+    sched = Scheduler(model, max_batch, prefill_per_step, eos_id=tok.eos)
+    sched.start()
+    httpd = ThreadingHTTPServer(("0.0.0.0", port), make_handler(sched, tok, model_name))
+    httpd.daemon_threads = True
+    threading.Thread(target=httpd.serve_forever, daemon=True).start()
+    return httpd, sched, httpd.server_address[1]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model_path", required=True)
+    ap.add_argument("--token_path", default="")
+    ap.add_argument("--dtype", default="bf16")
+    ap.add_argument("--kv_cache_dtype", default="fp16")
+    ap.add_argument("--port", type=int, default=8000)
+    ap.add_argument("--max_batch", type=int, default=64)
+    ap.add_argument("--prefill_per_step", type=int, default=4)
+    a = ap.parse_args()
+    import xfastertransformer_b200 as xft
+    model = xft.AutoModel.from_pretrained(a.model_path, dtype=a.dtype, kv_cache_dtype=a.kv_cache_dtype)
+    if model.rank != 0:
+        model.follow_cb()                # follower ranks mirror rank 0's engine calls until shutdown
+        return
+    _, _, port = serve(model, a.port, a.token_path, a.max_batch, a.prefill_per_step,
+                       os.path.basename(a.model_path.rstrip("/")))
+    print(f"OpenAI-compatible server on :{port}", flush=True)
+    threading.Event().wait()
+
+
+if __name__ == "__main__":
+    main()

@@ -142,3 +142,85 @@ def test_lora_finetune_reduces_loss_and_merges(tmp_path):
     from xfastertransformer_b200 import LlamaConvert
     conv = LlamaConvert().convert(os.path.join(out, "merged"), str(tmp_path / "xft"), dtype="fp32")
     assert os.path.exists(os.path.join(conv, "config.ini"))
+
+
+def test_openai_server_continuous_batching(tmp_path):
+    """serving/openai_server.py on the CPU engine with token-id prompts: concurrent /v1/completions requests are batched
+    by the scheduler and return what a lone greedy generate() returns; streaming, /v1/models, /metrics, errors."""
+    import importlib.util
+    import threading
+    spec = importlib.util.spec_from_file_location("oai", os.path.join(ROOT, "serving", "openai_server.py"))
+    oai = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(oai)
+    d = str(tmp_path / "tiny")
+    write_synthetic_checkpoint(d, preset("tiny-llama", vocab_size=500), seed=3, dtype="fp32", std=0.1)
+    model = xft.AutoModel.from_pretrained(d, dtype="bf16")
+    prompts = [[5, 9, 100, 42, 7], [11, 12, 13], [400, 3, 77, 8, 19, 21, 6], [50, 60]]
+    want = [model.generate(torch.tensor([p]), max_length=len(p) + 6)[0, len(p):].tolist() for p in prompts]
+    httpd, sched, port = oai.serve(model, 0, max_batch=8, prefill_per_step=2, model_name="tiny")
+    base = f"http://127.0.0.1:{port}"
+
+    def post(path, body):
+        req = urllib.request.Request(base + path, data=json.dumps(body).encode(), headers={"Content-Type": "application/json"})
+        try:
+            with urllib.request.urlopen(req, timeout=120) as r:
+                return r.status, r.read()
+        except urllib.error.HTTPError as e:
+            return e.code, e.read()
+
+    try:
+        got = [None] * len(prompts)
+
+        def one(i):
+            code, body = post("/v1/completions", {"prompt": prompts[i], "max_tokens": 6})
+            assert code == 200, body
+            got[i] = json.loads(body)
+
+        ths = [threading.Thread(target=one, args=(i,)) for i in range(len(prompts))]
+        [t.start() for t in ths]
+        [t.join() for t in ths]
+        for i, r in enumerate(got):
+            assert r["choices"][0]["token_ids"] == want[i], (i, r, want[i])
+            assert r["usage"]["prompt_tokens"] == len(prompts[i]) and r["usage"]["completion_tokens"] == 6
+        # streaming returns the same tokens as server-sent events
+        code, body = post("/v1/completions", {"prompt": prompts[0], "max_tokens": 6, "stream": True})
+        assert code == 200
+        toks = [json.loads(l[6:])["choices"][0]["token_ids"][0] for l in body.decode().split("\n\n")
+                if l.startswith("data: {")]
+        assert toks == want[0] and body.decode().strip().endswith("[DONE]")
+        # text prompt without a tokenizer, and a prompt longer than the model: 400, server keeps serving
+        assert post("/v1/completions", {"prompt": "hello"})[0] == 400
+        assert post("/v1/completions", {"prompt": [1] * 40, "max_tokens": 100000})[0] == 400
+        assert json.loads(urllib.request.urlopen(base + "/v1/models").read())["data"][0]["id"] == "tiny"
+        m = urllib.request.urlopen(base + "/metrics").read().decode()
+        assert "xft_finished 5" in m and "xft_generated_tokens 30" in m
+        assert sched.metrics["steps"] < 5 * 7          # requests shared engine steps
+    finally:
+        sched.shutdown()
+        httpd.shutdown()
+
+
+def test_benchmark_serving_client(tmp_path, capsys):
+    """benchmarks/benchmark_serving.py against the in-process OpenAI server: all requests succeed, TTFT/TPOT reported."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("oai", os.path.join(ROOT, "serving", "openai_server.py"))
+    oai = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(oai)
+    spec = importlib.util.spec_from_file_location("bs", os.path.join(ROOT, "benchmarks", "benchmark_serving.py"))
+    bs = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bs)
+    d = str(tmp_path / "tiny")
+    write_synthetic_checkpoint(d, preset("tiny-llama", vocab_size=500), seed=4, dtype="fp32", std=0.1)
+    model = xft.AutoModel.from_pretrained(d, dtype="bf16")
+    httpd, sched, port = oai.serve(model, 0, max_batch=8, prefill_per_step=4)
+    try:
+        old = sys.argv
+        sys.argv = ["benchmark_serving.py", "--url", f"http://127.0.0.1:{port}", "--num_prompts", "6", "--input_len", "12",
+                    "--output_len", "5", "--vocab", "500"]
+        res = bs.main()
+        sys.argv = old
+        assert res["successful_requests"] == 6 and res["failed_requests"] == 0
+        assert res["output_token_throughput_per_s"] > 0 and res["mean_ttft_ms"] > 0 and res["mean_tpot_ms"] > 0
+    finally:
+        sched.shutdown()
+        httpd.shutdown()

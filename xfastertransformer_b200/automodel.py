@@ -53,6 +53,10 @@ class AutoModel:
                 input_ids = [t for r in input_ids for t in r]
         return self.model.set_input_cb(input_ids, seq_lens, seq_ids, max_length)
 
+    def follow_cb(self):
+        """Follower ranks of a continuous-batching server: mirror rank 0 until it shuts down."""
+        return self.model.follow_cb()
+
     def forward_cb(self):
         return self.model.forward_cb()
 

@@ -406,6 +406,18 @@ class Model:
             s.pending = []
         return S.gather_logits(local, self.ctx, self.vocab_sizes).float()
 
+    def follow_cb(self) -> None:
+        """Follower ranks of a continuous-batching server: execute rank 0's control messages until shutdown.  A
+        serving scheduler runs exactly one ``forward_cb`` after every ``set_input_cb`` (forward steps carry no
+        message), so the follower does the same."""
+        if self.ctx.world == 1 or self.ctx.is_master:
+            return
+        while not self._closed:
+            op, payload = self._sync(0, None)
+            self._dispatch(op, payload)
+            if op == OP_SET_INPUT_CB:
+                self.forward_cb()
+
     def free_seqs(self, seq_ids=None) -> bool:
         if isinstance(seq_ids, torch.Tensor):
             seq_ids = seq_ids.tolist()
