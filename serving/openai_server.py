@@ -98,6 +98,14 @@ class Scheduler(threading.Thread):
             g = torch.Generator(device=probs.device).manual_seed(req.seed + len(req.generated))
         return int(torch.multinomial(probs, 1, generator=g))
 
+    def _forward(self, reqs: List[Request], greedy: bool) -> List[int]:
+        """One engine step for `reqs` (already announced with set_input_cb).  All-greedy batches pick their tokens on
+        the device (decode steps replay the CUDA graph); otherwise the logits come back and each request samples."""
+        if greedy:
+            return [int(t) for t in self.model.forward_cb_greedy()]
+        logits = self.model.forward_cb()
+        return [self._select(r, row) for r, row in zip(reqs, logits)]
+
     def _emit(self, req: Request, tok: int) -> bool:
         """Record a token; returns True when the request is finished."""
         now = time.perf_counter()
@@ -155,22 +163,25 @@ class Scheduler(threading.Thread):
                         else:
                             ok.append(r)
                     if ok:
+                        greedy = all(r.temperature <= 1e-5 for r in ok)
                         sids = self.model.set_input_cb([r.prompt_ids for r in ok], None,
-                                                       [len(r.prompt_ids) + r.max_tokens + 1 for r in ok])
-                        logits = self.model.forward_cb()
+                                                       [len(r.prompt_ids) + r.max_tokens + 1 for r in ok], greedy=greedy)
+                        picks = self._forward(ok, greedy)
                         done = []
-                        for r, sid, row in zip(ok, [int(s) for s in sids], logits):
+                        for r, sid, tok in zip(ok, [int(s) for s in sids], picks):
                             self.running[sid] = r
                             self.metrics["prompt_tokens"] += len(r.prompt_ids)
-                            if self._emit(r, self._select(r, row)):
+                            if self._emit(r, tok):
                                 done.append(sid)
                         self._finish(done)
                         self.metrics["steps"] += 1
                 if self.running:
                     sids = list(self.running)
-                    self.model.set_input_cb([self.running[s].generated[-1] for s in sids], sids, None)
-                    logits = self.model.forward_cb()
-                    done = [s for s, row in zip(sids, logits) if self._emit(self.running[s], self._select(self.running[s], row))]
+                    reqs = [self.running[s] for s in sids]
+                    greedy = all(r.temperature <= 1e-5 for r in reqs)
+                    self.model.set_input_cb([r.generated[-1] for r in reqs], sids, None, greedy=greedy)
+                    picks = self._forward(reqs, greedy)
+                    done = [s for s, r, tok in zip(sids, reqs, picks) if self._emit(r, tok)]
                     self._finish(done)
                     self.metrics["steps"] += 1
             except Exception as e:      # an engine error ends the affected requests, not the server

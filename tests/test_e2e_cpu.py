@@ -79,3 +79,18 @@ def test_pipeline_parallel_two_stages_gloo(tiny, tmp_path):
     assert torch.allclose(got["logits"], ref.logits(ids)[:, -1], atol=2e-3, rtol=2e-3)
     assert torch.equal(got["tokens"], ref.greedy(ids, 16))
     assert sorted(got["layers"]) == [(0, 1, 0, 0), (1, 2, 1, 0)]
+
+
+def test_cb_follower_loop_and_greedy_fast_path(tiny, tmp_path):
+    """Two gloo ranks: rank 1 only runs follow_cb(); rank 0 mixes forward_cb_greedy and forward_cb steps.  Tokens equal
+    the single-process greedy continuation and the follower exits on shutdown."""
+    out = str(tmp_path / "cbf.pt")
+    env = dict(os.environ, XFT_ENGINE="CPU", PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29615", os.path.join(ROOT, "tests", "cb_follow_worker.py"), tiny, out]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    got = torch.load(out)["tokens"]
+    ids = _prompt()
+    ref = EagerLlama(tiny)
+    assert torch.equal(got, ref.greedy(ids, 7)[:, ids.shape[1]:])

@@ -47,3 +47,25 @@ def test_tiny_llama_gpu(tiny, kv):
             assert row[out[b, t]] >= row.max() - tol * max(1.0, row.abs().max().item()), (b, t)
     assert model.model.runner.graph_launches > 0, "decode did not run through the CUDA graph"
     assert N.launches() > 0
+
+
+def test_forward_cb_greedy_replays_the_decode_graph(tiny):
+    """Continuous batching with on-device token selection: decode steps go through the CUDA-graph runner and yield
+    the tokens of generate()."""
+    import xfastertransformer_b200 as xft
+    model = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+    g = torch.Generator().manual_seed(2)
+    ids = torch.randint(0, 32000, (3, 20), generator=g)
+    want = model.generate(ids, max_length=30)[:, 20:]
+    runner = model.model.runner
+    assert runner is not None
+    g0 = runner.graph_launches
+    sids = model.set_input_cb(ids.tolist(), None, 40, greedy=True)
+    toks = [model.forward_cb_greedy()]
+    for _ in range(9):
+        model.set_input_cb([[int(t)] for t in toks[-1]], sids, None, greedy=True)
+        toks.append(model.forward_cb_greedy())
+    model.free_seqs(sids)
+    got = torch.stack(toks, 1)
+    assert torch.equal(got, want), (got, want)
+    assert runner.graph_launches - g0 >= 8

@@ -40,7 +40,7 @@ class AutoModel:
     # -- continuous batching ------------------------------------------------------------
     def set_input_cb(self, input_ids: Optional[Union[List[int], List[List[int]], torch.Tensor]] = None,
                      seq_ids: Optional[Union[List[int], torch.Tensor]] = None,
-                     max_length: Optional[Union[int, List[int], torch.Tensor]] = None):
+                     max_length: Optional[Union[int, List[int], torch.Tensor]] = None, greedy: bool = False):
         seq_lens = None
         if isinstance(input_ids, list):
             if seq_ids is None:
@@ -51,7 +51,7 @@ class AutoModel:
                     raise ValueError("For prompts, input_ids should not be List[int].")
             elif input_ids and isinstance(input_ids[0], list):
                 input_ids = [t for r in input_ids for t in r]
-        return self.model.set_input_cb(input_ids, seq_lens, seq_ids, max_length)
+        return self.model.set_input_cb(input_ids, seq_lens, seq_ids, max_length, greedy)
 
     def follow_cb(self):
         """Follower ranks of a continuous-batching server: mirror rank 0 until it shuts down."""
@@ -59,6 +59,11 @@ class AutoModel:
 
     def forward_cb(self):
         return self.model.forward_cb()
+
+    def forward_cb_greedy(self):
+        """Greedy next tokens of the last ``set_input_cb(..., greedy=True)``, selected on the device (decode steps
+        replay the CUDA graph).  Not in the reference's API."""
+        return self.model.forward_cb_greedy()
 
     def free_seqs(self, seq_ids: Optional[Union[List[int], torch.Tensor]] = None):
         return self.model.free_seqs(seq_ids)

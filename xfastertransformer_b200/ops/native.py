@@ -90,11 +90,16 @@ class Workspace:
             cls._by_dev[idx] = cls(torch.device("cuda", idx))
         return cls._by_dev[idx]
 
+    PART_O_FLOATS = 16 << 20          # split-KV partial outputs: fixed size, so captured graphs never see it move
+
     def attn_partials(self, n_o: int, n_ml: int):
-        if self.part_o is None or self.part_o.numel() < n_o:
-            self.part_o = torch.empty(max(n_o, 1 << 20), dtype=torch.float32, device=self.device)
-        if self.part_ml is None or self.part_ml.numel() < n_ml:
-            self.part_ml = torch.empty(max(n_ml, 1 << 16), dtype=torch.float32, device=self.device)
+        """Scratch of the split-KV decode.  Allocated once at a fixed size: a CUDA graph captured earlier keeps
+        pointing at it, so it must never be reallocated; callers clamp their split count to its capacity."""
+        if self.part_o is None:
+            self.part_o = torch.empty(self.PART_O_FLOATS, dtype=torch.float32, device=self.device)
+            self.part_ml = torch.empty(self.PART_O_FLOATS // 32, dtype=torch.float32, device=self.device)
+        if n_o > self.part_o.numel() or n_ml > self.part_ml.numel():
+            raise KernelError(f"split-KV scratch too small for {n_o} partial outputs")
         return self.part_o, self.part_ml
 
     def check_status(self) -> None:
@@ -341,6 +346,8 @@ def paged_attention(q, kc, vc, block_table, cu_q, kv_lens, scale, ks=None, vs=No
             nsplit = meta.meta["nsplit"]
         if B * hkv * ((g + 15) // 16) > ws.attn_counters.numel():
             nsplit = 1
+        # the partial buffers have a fixed capacity (D >= 64, so the (m, l) buffer of 1/32 the size always suffices)
+        nsplit = max(1, min(nsplit, ws.PART_O_FLOATS // max(B * hq * D, 1)))
         if nsplit > 1:
             po, pm = ws.attn_partials(B * hq * nsplit * D, B * hq * nsplit * 2)
     q = q.contiguous()

@@ -76,6 +76,8 @@ class Model:
                                   self.decoder.act_dtype, geo["latent"])
         self.pool = SequencePool()
         self.sampling = SamplingMeta()
+        self._greedy_cfg = SamplingMeta()
+        self._cb_greedy = False
         self.working: List[SequenceMeta] = []          # sequences of the current request (batch API)
         self.cb_active: List[SequenceMeta] = []        # sequences of the last set_input_cb
         self.rng = S.Philox(None)
@@ -348,9 +350,10 @@ class Model:
     # ------------------------------------------------------------------------------------
     # continuous-batching API
     # ------------------------------------------------------------------------------------
-    def set_input_cb(self, input_ids=None, seq_lens=None, seq_ids=None, max_length=None) -> torch.Tensor:
+    def set_input_cb(self, input_ids=None, seq_lens=None, seq_ids=None, max_length=None, greedy: bool = False) -> torch.Tensor:
         """Prefill: ``input_ids`` = flattened prompts + ``seq_lens``; decode: ``input_ids`` [bs,1] +
-        ``seq_ids``.  Returns the sequence ids (models.cpp:586-674)."""
+        ``seq_ids``.  Returns the sequence ids (models.cpp:586-674).  ``greedy=True`` announces that the step will be
+        run with ``forward_cb_greedy`` (followers need to know which forward follows)."""
         def tl(x):
             if x is None:
                 return None
@@ -365,10 +368,11 @@ class Model:
         if seq_lens is None and seq_ids is None and isinstance(input_ids, (list, tuple)) and input_ids and \
                 isinstance(input_ids[0], (list, tuple)):
             seq_lens = [len(r) for r in input_ids]
-        return self._call(OP_SET_INPUT_CB, (ids, tl(seq_lens), tl(seq_ids), tl(max_length)))
+        return self._call(OP_SET_INPUT_CB, (ids, tl(seq_lens), tl(seq_ids), tl(max_length), bool(greedy)))
 
-    def _do_set_input_cb(self, ids, seq_lens, seq_ids, max_len) -> torch.Tensor:
+    def _do_set_input_cb(self, ids, seq_lens, seq_ids, max_len, greedy: bool = False) -> torch.Tensor:
         active = []
+        self._cb_greedy = bool(greedy)
         if not seq_ids:                                   # new prompts
             if not seq_lens or sum(seq_lens) != len(ids):
                 raise ValueError("set_input_cb: seq_lens do not add up to the number of input ids")
@@ -406,6 +410,26 @@ class Model:
             s.pending = []
         return S.gather_logits(local, self.ctx, self.vocab_sizes).float()
 
+    def forward_cb_greedy(self) -> torch.Tensor:
+        """Greedy next token [bs] of the sequences of the last ``set_input_cb(..., greedy=True)``, chosen on the device:
+        no logits leave the GPU, and a pure decode step replays the captured CUDA graph (one H2D copy, one replay,
+        one D2H copy of the tokens).  Extension of the reference's API for serving schedulers."""
+        seqs = self.cb_active
+        if not seqs:
+            raise RuntimeError("forward_cb_greedy() before set_input_cb()")
+        if self.ctx.world > 1 and not getattr(self, "_cb_greedy", False):
+            raise RuntimeError("forward_cb_greedy() needs set_input_cb(..., greedy=True) on more than one rank")
+        cfg = self._greedy_cfg
+        if self.runner is not None and self.runner.can_run(seqs, cfg):
+            toks = self.runner.step(seqs, cfg)
+        else:
+            local = self._run(seqs)
+            toks = S.greedy_select(local, self.decoder.v0, self.ctx).cpu().tolist()
+        for s in seqs:
+            s.past_len += len(s.pending)
+            s.pending = []
+        return torch.tensor([int(t) for t in toks], dtype=torch.int64)
+
     def follow_cb(self) -> None:
         """Follower ranks of a continuous-batching server: execute rank 0's control messages until shutdown.  A
         serving scheduler runs exactly one ``forward_cb`` after every ``set_input_cb`` (forward steps carry no
@@ -416,7 +440,10 @@ class Model:
             op, payload = self._sync(0, None)
             self._dispatch(op, payload)
             if op == OP_SET_INPUT_CB:
-                self.forward_cb()
+                if getattr(self, "_cb_greedy", False):
+                    self.forward_cb_greedy()
+                else:
+                    self.forward_cb()
 
     def free_seqs(self, seq_ids=None) -> bool:
         if isinstance(seq_ids, torch.Tensor):
