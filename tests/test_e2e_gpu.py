@@ -68,4 +68,4 @@ def test_forward_cb_greedy_replays_the_decode_graph(tiny):
     model.free_seqs(sids)
     got = torch.stack(toks, 1)
     assert torch.equal(got, want), (got, want)
-    assert runner.graph_launches - g0 >= 8
+    assert runner.graph_launches - g0 >= 6      # first decode step eager, second captures, the rest replay

@@ -52,6 +52,20 @@ class CudaRunner:
             return False
         return all(len(s.pending) == 1 and s.past_len > 0 for s in seqs)
 
+    def _key(self, seqs: Sequence):
+        W = max(self.m.cache.blocks_for(s.max_len + 1) for s in seqs)
+        return len(seqs), (W + 7) // 8 * 8
+
+    def worth_capturing(self, seqs: Sequence) -> bool:
+        """For callers whose batch composition changes from step to step (serving): a shape is captured only when
+        it is requested twice in a row or already has a graph; a shape seen once runs eagerly."""
+        key = self._key(seqs)
+        hit = key in self.graphs or key == getattr(self, "_last_key", None)
+        self._last_key = key
+        if len(self.graphs) > 64 and key not in self.graphs:      # bound the memory held by captured shapes
+            self.graphs.pop(next(iter(self.graphs)))
+        return hit
+
     # ------------------------------------------------------------------------------------
     def _layout(self, B: int, W: int):
         o_ids, o_pos, o_slot, o_kv = 0, B, 2 * B, 3 * B

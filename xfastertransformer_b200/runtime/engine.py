@@ -420,7 +420,7 @@ class Model:
         if self.ctx.world > 1 and not getattr(self, "_cb_greedy", False):
             raise RuntimeError("forward_cb_greedy() needs set_input_cb(..., greedy=True) on more than one rank")
         cfg = self._greedy_cfg
-        if self.runner is not None and self.runner.can_run(seqs, cfg):
+        if self.runner is not None and self.runner.can_run(seqs, cfg) and self.runner.worth_capturing(seqs):
             toks = self.runner.step(seqs, cfg)
         else:
             local = self._run(seqs)
