@@ -11,7 +11,6 @@ from . import native as N
 
 _ready = False
 _tables: Dict[tuple, tuple] = {}
-_wcache: Dict[int, torch.Tensor] = {}
 
 
 def _lib():
@@ -61,10 +60,12 @@ def mla_attention(q_nope, q_rope, latent_cache, block_table, cu_q, kv_lens, w_uk
     dev = q_nope.device
     ws = N.Workspace.get(dev)
     # W_uk^T stacked per head: [Hl*L, nope] (linear weight [out=L, in=nope])
-    wk = _wcache.get(id(w_uk))
-    if wk is None:
+    # cached on the tensor itself (an id()-keyed table would hand a dead tensor's copy to a new tensor that reuses
+    # its address)
+    wk = getattr(w_uk, "_xft_wk_t", None)
+    if wk is None or wk.shape != (Hl * L, nope):
         wk = w_uk.transpose(1, 2).contiguous().view(Hl * L, nope)
-        _wcache[id(w_uk)] = wk
+        w_uk._xft_wk_t = wk
     wv = w_uv.reshape(Hl * vd, L)
     q_ht = q_nope.transpose(0, 1).contiguous().view(Hl * T, nope)
     q_abs = _per_head_gemm(q_ht, wk, Hl, T, L, nope)                 # [Hl*T, L]
