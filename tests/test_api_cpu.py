@@ -199,3 +199,37 @@ def test_faults_are_errors_not_crashes(tiny, tmp_path):
         m.set_input_cb([1], [9999], 32)                            # unknown sequence id
     with pytest.raises(RuntimeError):
         m.forward_cb()                                             # nothing scheduled
+
+
+def test_model_zoo_configs_parse_and_split():
+    """Every examples/model_config/<name>/config.ini parses, maps to a registered family, and its tensor-parallel
+    layout is valid for 1, 2, 4 and 8 ranks; the files are what tools/model_zoo.py generates."""
+    import glob
+    from xfastertransformer_b200.config import ModelConfig
+    from xfastertransformer_b200.models.registry import family_for
+    from xfastertransformer_b200.parallel import partition as P
+    from xfastertransformer_b200.tools.synthetic import preset
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "model_config")
+    dirs = sorted(glob.glob(os.path.join(root, "*", "config.ini")))
+    assert len(dirs) >= 40
+    for ini in dirs:
+        name = os.path.basename(os.path.dirname(ini))
+        cfg = ModelConfig.from_ini(os.path.dirname(ini))
+        spec = family_for(cfg)
+        assert spec is not None, name
+        assert cfg.head_num > 0 and cfg.hidden_size > 0 and cfg.num_layer > 0 and cfg.vocab_size > 0, name
+        if name != "deepseek-r1":
+            ref = preset(name)
+            assert (ref.model_type, ref.num_layer, ref.hidden_size, ref.head_num, ref.kv_head_num, ref.inter_size) == \
+                   (cfg.model_type, cfg.num_layer, cfg.hidden_size, cfg.head_num, cfg.kv_head_num, cfg.inter_size), name
+        for tp in (1, 2, 4, 8):
+            q_total = 0
+            for r in range(tp):
+                (q0, q1), (k0, k1) = P.head_range(cfg.head_num, cfg.kv_head_num, tp, r)
+                assert q1 >= q0 and k1 > k0 or q1 == q0, (name, tp, r)
+                q_total += q1 - q0
+            assert q_total == cfg.head_num, (name, tp)
+            inter = cfg.moe_intermediate_size or cfg.inter_size
+            if cfg.model_type != "deepseek_moe":
+                spans = [P.task_range(inter, tp, r) for r in range(tp)]
+                assert spans[0][0] == 0 and spans[-1][1] == inter and all(a[1] == b[0] for a, b in zip(spans, spans[1:])), (name, tp)

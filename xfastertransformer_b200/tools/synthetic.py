@@ -46,7 +46,13 @@ PRESETS: Dict[str, dict] = {
 
 
 def preset(name: str, **over) -> ModelConfig:
-    d = dict(PRESETS[name])
+    if name not in PRESETS:
+        from .model_zoo import ZOO          # public model architectures (examples/model_config)
+        if name not in ZOO:
+            raise KeyError(f"unknown model preset '{name}'; known: {sorted(set(PRESETS) | set(ZOO))}")
+        d = dict(ZOO[name])
+    else:
+        d = dict(PRESETS[name])
     d.update(over)
     d.setdefault("activation_type", "silu")
     d.setdefault("weight_data_type", "bf16")
