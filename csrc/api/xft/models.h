@@ -7,7 +7,8 @@
 //
 // and the continuous-batching calls set_input(ids, seqIDs, maxLen) / forward() / freeSeqs().  The native engine
 // runs the dense decoder families (llama, yarn_llama, gemma, qwen2, qwen3, baichuan with RoPE) in bf16 on one B200
-// through the same sm_100a kernels as the Python package; errors are exceptions (std::runtime_error), never exit().
+// through the same sm_100a kernels as the Python package — greedy, top-k / top-p sampling and beam search (host scorer,
+// beams fork and reorder paged KV block tables); errors are exceptions (std::runtime_error), never exit().
 #pragma once
 #include <cstdint>
 #include <memory>

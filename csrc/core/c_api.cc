@@ -4,8 +4,10 @@
 #include <cstdlib>
 #include <cstring>
 #include <string>
+#include <vector>
 
 #include "arena.h"
+#include "beam.h"
 #include "env.h"
 #include "runtime.h"
 #include "xft/layers.h"
@@ -52,6 +54,30 @@ void xftc_repetition_penalty(float* l, int n, const int* toks, int nt, float pen
   repetitionPenalty(l, n, std::vector<int32_t>(toks, toks + nt), pen, off);
 }
 
+
+// ---- beam search scorer (csrc/core/beam.cc)
+void* xftc_beam_new(int batch, int beams, float lenPenalty, int earlyStopping, int eos, int pad, int nret) {
+  return new BeamSearchScorer(batch, beams, lenPenalty, earlyStopping != 0, eos, pad, nret);
+}
+void xftc_beam_delete(void* s) { delete static_cast<BeamSearchScorer*>(s); }
+int xftc_beam_done(void* s) { return static_cast<BeamSearchScorer*>(s)->isDone() ? 1 : 0; }
+void xftc_beam_process(void* s, const float* logprobs, int vocab, int32_t* tokens, int* src, int n) {
+  std::vector<int32_t> t; std::vector<int> b;
+  static_cast<BeamSearchScorer*>(s)->process(logprobs, vocab, t, b);
+  for (int i = 0; i < n && i < (int)t.size(); ++i) { tokens[i] = t[i]; src[i] = b[i]; }
+}
+// prompts: [batch, promptLen] row-major; out: [rows, width] written up to cap ints; returns rows * 65536 + width
+int xftc_beam_finalize(void* s, const int32_t* prompts, int batch, int promptLen, int maxLength, int32_t* out, int cap) {
+  std::vector<std::vector<int32_t>> p(batch);
+  for (int b = 0; b < batch; ++b) p[b].assign(prompts + (size_t)b * promptLen, prompts + (size_t)(b + 1) * promptLen);
+  auto res = static_cast<BeamSearchScorer*>(s)->finalize(p, maxLength);
+  const int rows = (int)res.size(), width = rows ? (int)res[0].size() : 0;
+  for (int r = 0; r < rows; ++r)
+    for (int c = 0; c < width; ++c)
+      if ((size_t)r * width + c < (size_t)cap) out[(size_t)r * width + c] = res[r][c];
+  return rows * 65536 + width;
+}
+void xftc_log_softmax(float* row, int n) { logSoftmaxRow(row, n); }
 
 // ---- caching arena (csrc/core/arena.cc) over malloc/free, for tests without a GPU
 void* xftc_arena_new_host() { return new Arena([](size_t n) { return std::malloc(n); }, [](void* p) { std::free(p); }); }

@@ -15,6 +15,7 @@
 #include <stdexcept>
 
 #include "arena.h"
+#include "beam.h"
 #include "env.h"
 #include "ini.h"
 #include "kernels_c.h"
@@ -116,6 +117,10 @@ public:
   int prefixSeq = -1;
   std::vector<float> hostLogits;
   std::mt19937_64 rng;
+  // beam search state of the current request (numBeams > 1): beam i of request r is beamSeqs[r * numBeams + i]
+  std::unique_ptr<BeamSearchScorer> scorer;
+  std::vector<int> beamSeqs;
+  std::vector<std::vector<int32_t>> beamPrompts;
 
   // Runs the pending inputs of `ids`; logits land in hostLogits [rows, vocab].  Returns rows.
   int forward(const std::vector<int>& ids, bool logitsAll);
@@ -430,8 +435,73 @@ void Model::config(int maxLen, int numBeams, int numBeamHypsToKeep, float lenPen
                    temperature, topK, topP, repetitionPenalty);
   config(c, stopWordsList);
 }
+namespace {
+// beams other than beam 0 are extra sequences of the pool; the request's own sequence stays in `working`
+void clearBeams(Engine& e) {
+  for (size_t i = 0; i < e.beamSeqs.size(); ++i)
+    if (std::find(e.working.begin(), e.working.end(), e.beamSeqs[i]) == e.working.end() && e.pool.has(e.beamSeqs[i]))
+      e.release(e.beamSeqs[i]);
+  e.beamSeqs.clear();
+  e.beamPrompts.clear();
+  e.scorer.reset();
+}
+
+// One beam-search step (src/searchers/beam_search.cpp:27-345): the first call prefills the prompts and forks every
+// request into numBeams sequences that share its KV blocks; later calls run all beams, pick the next beams on the
+// host and reorder the block tables (reference counts move, no KV data is copied until a shared tail block is written).
+std::vector<int32_t> beamStep(Engine& e, const SearcherConfig& c) {
+  const int nb = c.numBeams, bs = (int)e.working.size(), V = e.vocab;
+  std::vector<float> lp((size_t)bs * nb * V);
+  if (!e.scorer) {
+    e.forward(e.working, false);
+    for (int r = 0; r < bs; ++r) {
+      float* row = e.hostLogits.data() + (size_t)r * V;
+      logSoftmaxRow(row, V);
+      for (int j = 0; j < nb; ++j) std::copy(row, row + V, lp.begin() + ((size_t)r * nb + j) * V);
+    }
+    for (int r = 0; r < bs; ++r) {
+      SequenceMeta& s = e.pool.get(e.working[r]);
+      e.beamPrompts.push_back(s.prompt);
+      e.beamSeqs.push_back(s.id);
+      for (int j = 1; j < nb; ++j) {
+        SequenceMeta& b = e.pool.create(s.prompt, s.maxLen);
+        b.pastLen = s.pastLen;
+        b.pending.clear();
+        e.tables->fork(s.id, b.id);
+        e.beamSeqs.push_back(b.id);
+      }
+    }
+    e.scorer.reset(new BeamSearchScorer(bs, nb, c.lenPenalty, c.doEarlyStopping, c.eosTokenId, c.padTokenId, c.numBeamHypsToKeep));
+  } else {
+    e.forward(e.beamSeqs, false);
+    for (int i = 0; i < bs * nb; ++i) {
+      float* row = e.hostLogits.data() + (size_t)i * V;
+      logSoftmaxRow(row, V);
+      std::copy(row, row + V, lp.begin() + (size_t)i * V);
+    }
+  }
+  std::vector<int32_t> toks;
+  std::vector<int> src;
+  e.scorer->process(lp.data(), V, toks, src);
+  // beams take over the history (block table + generated tokens) of their source beam, then append their token
+  e.tables->reorder(e.beamSeqs, src);
+  std::vector<std::vector<int32_t>> gen(e.beamSeqs.size());
+  for (size_t i = 0; i < e.beamSeqs.size(); ++i) gen[i] = e.pool.get(e.beamSeqs[src[i]]).generated;
+  bool full = false;
+  for (size_t i = 0; i < e.beamSeqs.size(); ++i) {
+    SequenceMeta& b = e.pool.get(e.beamSeqs[i]);
+    b.generated = gen[i];
+    b.stepForward(toks[i]);
+    full = full || b.totalLen() >= b.maxLen;
+  }
+  if (e.scorer->isDone() || full)
+    for (int id : e.beamSeqs) e.pool.get(id).done = true;
+  return toks;
+}
+}  // namespace
+
 void Model::config(SearcherConfig& c, const std::vector<std::vector<int>>& sw) {
-  if (c.numBeams > 1) throw std::runtime_error("beam search runs through the Python API");
+  if (c.numBeams > 1 && c.doSample) throw std::runtime_error("beam search with sampling is not supported");
   configuration = c;
   if (configuration.eosTokenId == -1) configuration.eosTokenId = engine->endId;
   if (configuration.padTokenId == -1) configuration.padTokenId = configuration.eosTokenId;
@@ -443,6 +513,7 @@ bool Model::setStopWords(std::vector<std::vector<int>> sw) { stopWords = cleanSt
 
 void Model::input(std::vector<int32_t>& ids, int batch) {
   if (batch <= 0 || ids.size() % batch) throw std::invalid_argument("input ids do not divide into the batch");
+  clearBeams(*engine);
   for (int id : engine->working) engine->release(id);
   engine->working.clear();
   batchSize = batch;
@@ -472,6 +543,7 @@ std::vector<int> Model::set_input(std::vector<int32_t>& ids, int batch, Searcher
 }
 std::vector<int> Model::set_input(std::vector<std::vector<int32_t>>& ids, SearcherConfig& c, const std::vector<std::vector<int>>& sw) {
   config(c, sw);
+  clearBeams(*engine);
   for (int id : engine->working) engine->release(id);
   engine->working.clear();
   batchSize = (int)ids.size();
@@ -529,6 +601,10 @@ bool Model::isDone() {
 std::vector<int32_t> Model::generate() {
   TimeLine tl("Model.generate");
   if (engine->working.empty()) throw std::runtime_error("generate() before input()/set_input()");
+  if (configuration.numBeams > 1) {
+    if (isDone()) return std::vector<int32_t>((size_t)engine->working.size() * configuration.numBeams, configuration.eosTokenId);
+    return beamStep(*engine, configuration);
+  }
   std::vector<int> active;
   for (int id : engine->working) if (!engine->pool.get(id).done) active.push_back(id);
   std::vector<int32_t> out;
@@ -563,6 +639,15 @@ std::vector<int32_t> Model::generate() {
 
 std::vector<int32_t> Model::finalize() {
   if (Env::get().timeline) TimeLine::dump();       // as the reference: the trace is written when a request ends
+  if (engine->scorer) {
+    auto rows = engine->scorer->finalize(engine->beamPrompts, configuration.maxLen);
+    std::vector<int32_t> flat;
+    for (auto& r : rows) flat.insert(flat.end(), r.begin(), r.end());
+    clearBeams(*engine);
+    for (int id : engine->working) engine->release(id);
+    engine->working.clear();
+    return flat;
+  }
   size_t w = 0;
   for (int id : engine->working) w = std::max<size_t>(w, engine->pool.get(id).totalLen());
   std::vector<int32_t> out;

@@ -210,3 +210,54 @@ def test_cpp_arena_reuses_blocks(core):
     c.xftc_arena_trim(a)
     assert c.xftc_arena_stat(a, 1) == 0
     c.xftc_arena_delete(a)
+
+
+@pytest.mark.parametrize("early,lp,eos", [(False, 1.0, 3), (True, 0.7, 3), (False, 1.3, -1)])
+def test_cpp_beam_scorer_matches_python(core, early, lp, eos):
+    """csrc/core/beam.cc against runtime/sampler.py on random log-probabilities: same tokens, source beams, done flag
+    at every step and the same final hypotheses."""
+    import ctypes
+    import torch
+    from xfastertransformer_b200.runtime.sampler import BeamSearchScorer
+    from xfastertransformer_b200.runtime.sequence import SamplingMeta
+    c = core
+    c.xftc_beam_new.restype = ctypes.c_void_p
+    c.xftc_beam_new.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int]
+    c.xftc_beam_process.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]
+    c.xftc_beam_done.argtypes = [ctypes.c_void_p]
+    c.xftc_beam_delete.argtypes = [ctypes.c_void_p]
+    c.xftc_beam_finalize.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int]
+    bs, nb, V, steps, P = 3, 4, 23, 9, 5
+    cfg = SamplingMeta(max_length=P + steps, num_beams=nb, num_return_sequences=2, length_penalty=lp, early_stopping=early,
+                       eos_token_id=eos, pad_token_id=0)
+    py = BeamSearchScorer(bs, cfg, P)
+    cc = c.xftc_beam_new(bs, nb, lp, int(early), eos, 0, 2)
+    g = torch.Generator().manual_seed(int(lp * 10) + eos + 5)
+    for step in range(steps):
+        lp_t = torch.log_softmax(torch.randn(bs * nb, V, generator=g) * 2.0, -1).contiguous()
+        want_tok, want_src = py.process(lp_t.clone())
+        tok = torch.zeros(bs * nb, dtype=torch.int32)
+        src = torch.zeros(bs * nb, dtype=torch.int32)
+        c.xftc_beam_process(cc, lp_t.data_ptr(), V, tok.data_ptr(), src.data_ptr(), bs * nb)
+        live = [b for b in range(bs) if not py.done[b]]          # rows of finished requests carry padding
+        for b in live:
+            sl = slice(b * nb, (b + 1) * nb)
+            assert tok[sl].tolist() == want_tok[sl].tolist(), (step, b)
+            assert src[sl].tolist() == want_src[sl].tolist(), (step, b)
+        assert bool(c.xftc_beam_done(cc)) == py.is_done, step
+        if py.is_done:
+            break
+    prompts = torch.arange(bs * P, dtype=torch.int32).view(bs, P) + 100
+    want = py.finalize(prompts.tolist(), P + steps)
+    out = torch.zeros(bs * 2 * (P + steps + 2), dtype=torch.int32)
+    rw = c.xftc_beam_finalize(cc, prompts.data_ptr(), bs, P, P + steps, out.data_ptr(), out.numel())
+    rows, width = rw >> 16, rw & 0xFFFF
+    assert rows == len(want) and width == len(want[0])
+    assert out[:rows * width].view(rows, width).tolist() == want
+    c.xftc_beam_delete(cc)
+    # log-softmax helper
+    x = torch.randn(50)
+    y = x.clone()
+    c.xftc_log_softmax.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    c.xftc_log_softmax(y.data_ptr(), 50)
+    assert torch.allclose(y, torch.log_softmax(x, -1), atol=1e-5)
