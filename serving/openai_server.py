@@ -64,6 +64,37 @@ class Scheduler(threading.Thread):
         self.metrics = dict(requests=0, finished=0, prompt_tokens=0, generated_tokens=0, ttft_sum=0.0, tpot_sum=0.0,
                             tpot_count=0, steps=0, errors=0)
         self.max_len = int(getattr(model.model.cfg, "max_pos_seq_len", 0) or 0)
+        self.kv_fraction = 0.8            # share of the free device memory the warm-up gives to the KV pools
+
+    def warmup(self, max_context: int = 0) -> int:
+        """Capture the decode CUDA graphs of every batch bucket up to ``max_batch`` before the first request arrives
+        (a capture costs an eager step plus the capture itself, which would otherwise land on live requests).  All
+        graphs share one block-table width, sized for ``max_context`` tokens.  Returns the number of buckets run."""
+        runner = getattr(self.model.model, "runner", None)
+        if runner is None or not getattr(runner, "enabled", False):
+            return 0
+        cache = self.model.model.cache
+        ctx = max_context or self.max_len or 4096
+        runner.fixed_width = (cache.blocks_for(ctx + 1) + 7) // 8 * 8
+        # Size the KV pools once, now: a pool that grows under load moves, and every captured graph would have to be
+        # captured again.  kv_fraction of the free device memory, capped at what max_batch full contexts need.
+        try:
+            free, _ = self.torch.cuda.mem_get_info(self.model.model.ctx.device)
+            want = min(int(self.kv_fraction * free) // max(cache.bytes_per_block(), 1),
+                       self.max_batch * cache.blocks_for(ctx + 1) + 8)
+            if want > cache.alloc.num_blocks:
+                cache.ensure_blocks(want)
+        except Exception:
+            pass
+        sizes = sorted({runner.bucket(n) for n in range(1, self.max_batch + 1)})
+        for b in sizes:
+            sids = self.model.set_input_cb([[1, 2, 3, 4]] * b, None, [16] * b, greedy=True)
+            toks = self.model.forward_cb_greedy()
+            for _ in range(3):                       # eager, capture, replay
+                self.model.set_input_cb([[int(t)] for t in toks], sids, None, greedy=True)
+                toks = self.model.forward_cb_greedy()
+            self.model.free_seqs(sids)
+        return len(sizes)
 
     # -- API for handler threads ------------------------------------------------------------
     def submit(self, req: Request) -> Request:
@@ -321,10 +352,13 @@ def make_handler(sched: Scheduler, tok: Tokenizer, model_name: str):
     return H
 
 
-def serve(model, port: int, token_path: str = "", max_batch: int = 64, prefill_per_step: int = 4, model_name: str = "xft"):
+def serve(model, port: int, token_path: str = "", max_batch: int = 64, prefill_per_step: int = 4, model_name: str = "xft",
+          warmup: bool = False, max_context: int = 0):
     """Start scheduler + HTTP server (threads); returns (httpd, scheduler, bound_port)."""
     tok = Tokenizer(token_path)
     sched = Scheduler(model, max_batch, prefill_per_step, eos_id=tok.eos)
+    if warmup:
+        sched.warmup(max_context)
     sched.start()
     httpd = ThreadingHTTPServer(("0.0.0.0", port), make_handler(sched, tok, model_name))
     httpd.daemon_threads = True
@@ -341,6 +375,8 @@ def main():
     ap.add_argument("--port", type=int, default=8000)
     ap.add_argument("--max_batch", type=int, default=64)
     ap.add_argument("--prefill_per_step", type=int, default=4)
+    ap.add_argument("--no_warmup", action="store_true", help="do not pre-capture the decode graphs of every batch bucket")
+    ap.add_argument("--max_context", type=int, default=0, help="longest prompt + output the graphs are sized for")
     a = ap.parse_args()
     import xfastertransformer_b200 as xft
     model = xft.AutoModel.from_pretrained(a.model_path, dtype=a.dtype, kv_cache_dtype=a.kv_cache_dtype)
@@ -348,7 +384,7 @@ def main():
         model.follow_cb()                # follower ranks mirror rank 0's engine calls until shutdown
         return
     _, _, port = serve(model, a.port, a.token_path, a.max_batch, a.prefill_per_step,
-                       os.path.basename(a.model_path.rstrip("/")))
+                       os.path.basename(a.model_path.rstrip("/")), warmup=not a.no_warmup, max_context=a.max_context)
     print(f"OpenAI-compatible server on :{port}", flush=True)
     threading.Event().wait()
 

@@ -52,9 +52,33 @@ class CudaRunner:
             return False
         return all(len(s.pending) == 1 and s.past_len > 0 for s in seqs)
 
+    @staticmethod
+    def bucket(n: int) -> int:
+        """Batch sizes are padded up to a bucket so that a serving loop whose batch shrinks and grows by one sequence at
+        a time replays a handful of graphs: powers of two up to 8, multiples of 8 up to 32, of 16 up to 128, of 32 beyond."""
+        if n <= 8:
+            b = 1
+            while b < n:
+                b *= 2
+            return b
+        step = 8 if n <= 32 else 16 if n <= 128 else 32
+        return (n + step - 1) // step * step
+
     def _key(self, seqs: Sequence):
         W = max(self.m.cache.blocks_for(s.max_len + 1) for s in seqs)
-        return len(seqs), (W + 7) // 8 * 8
+        W = (W + 7) // 8 * 8
+        fw = getattr(self, "fixed_width", None)      # serving: one block-table width for every request length
+        if fw is not None and W <= fw:
+            W = fw
+        return self.bucket(len(seqs)), W
+
+    def _scratch(self) -> int:
+        """One KV block owned by the runner: padding rows of a bucketed batch write their key/value there and attend
+        to it (a context of one token), so they touch no live sequence."""
+        if getattr(self, "_scratch_block", None) is None:
+            self.m.cache.reserve(1)
+            self._scratch_block = self.m.cache.alloc.alloc()
+        return self._scratch_block
 
     def worth_capturing(self, seqs: Sequence) -> bool:
         """For callers whose batch composition changes from step to step (serving): a shape is captured only when
@@ -106,41 +130,59 @@ class CudaRunner:
         toks = S.greedy_select(local, m.decoder.v0, m.ctx)
         g.tok_dev.copy_(toks)
 
-    def _fill(self, g: _Graph, seqs) -> None:
-        m = self.m
-        B, W = g.B, g.W
-        o_ids, o_pos, o_slot, o_kv, o_cu, o_bt, total = self._layout(B, W)
-        h = g.host
-        cache = m.cache
-        ids, pos, slots, kvl = [], [], [], []
+    def _reserve_slots(self, seqs) -> List[int]:
+        """Cache positions of this step's tokens.  Runs before the graph is chosen: appending may grow the pools, which
+        moves them and invalidates every captured graph."""
+        cache = self.m.cache
+        slots = []
         for s in seqs:
             start = s.past_len
             if cache.lens[s.seq_id] > start:
                 cache.truncate(s.seq_id, start)
             slots.append(cache.append_slots(s.seq_id, 1)[0])
-            ids.append(s.pending[0])
-            pos.append(start)
-            kvl.append(start + 1)
+        return slots
+
+    def _fill(self, g: _Graph, seqs, slots: List[int]) -> None:
+        m = self.m
+        B, W = g.B, g.W
+        o_ids, o_pos, o_slot, o_kv, o_cu, o_bt, total = self._layout(B, W)
+        h = g.host
+        cache = m.cache
+        slots = list(slots)
+        ids = [s.pending[0] for s in seqs]
+        pos = [s.past_len for s in seqs]
+        kvl = [s.past_len + 1 for s in seqs]
+        pad = B - len(seqs)
+        if pad:                                        # padding rows of the bucket: one token in the scratch block
+            sb = self._scratch()
+            ids += [0] * pad
+            pos += [0] * pad
+            slots += [sb * cache.block] * pad
+            kvl += [1] * pad
         h[o_ids:o_ids + B] = torch.tensor(ids, dtype=torch.int32)
         h[o_pos:o_pos + B] = torch.tensor(pos, dtype=torch.int32)
         h[o_slot:o_slot + B] = torch.tensor(slots, dtype=torch.int32)
         h[o_kv:o_kv + B] = torch.tensor(kvl, dtype=torch.int32)
         bt = cache.block_table([s.seq_id for s in seqs], W)
-        h[o_bt:o_bt + B * W] = bt.view(-1)
+        n = len(seqs)
+        h[o_bt:o_bt + n * W] = bt.view(-1)
+        if pad:
+            h[o_bt + n * W:o_bt + B * W] = self._scratch()
 
     def step(self, seqs: Sequence, cfg) -> List[int]:
         m = self.m
-        B = len(seqs)
-        W = max(m.cache.blocks_for(s.max_len + 1) for s in seqs)
-        W = (W + 7) // 8 * 8
-        key = (B, W)
+        n_real = len(seqs)
+        self._scratch()                                # both may grow the pools: before the version check below
+        slots = self._reserve_slots(seqs)
+        key = self._key(seqs)
+        B, W = key
         g = self.graphs.get(key)
         if g is not None and g.version != m.cache.version:
             g = None                                   # cache pools were reallocated: pointers changed
         if g is None:
             g = self._build(B, W, max(s.max_len for s in seqs))
             self.graphs[key] = g
-        self._fill(g, seqs)
+        self._fill(g, seqs, slots)
         st = self.stream
         st.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(st), torch.no_grad():
@@ -174,4 +216,4 @@ class CudaRunner:
         st.synchronize()
         self.h2d_bytes += g.host.numel() * 4
         self.d2h_bytes += g.tok_host.numel() * 8
-        return g.tok_host.tolist()
+        return g.tok_host.tolist()[:n_real]
