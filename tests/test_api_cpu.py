@@ -233,3 +233,29 @@ def test_model_zoo_configs_parse_and_split():
             if cfg.model_type != "deepseek_moe":
                 spans = [P.task_range(inter, tp, r) for r in range(tp)]
                 assert spans[0][0] == 0 and spans[-1][1] == inter and all(a[1] == b[0] for a, b in zip(spans, spans[1:])), (name, tp)
+
+
+def test_debug_dir_dumps_layer_outputs(tmp_path, monkeypatch):
+    """XFT_DEBUG_DIR: every forward writes the hidden state after each attention / FFN block and a summary log."""
+    import glob
+    import torch
+    import xfastertransformer_b200 as xft
+    from xfastertransformer_b200.tools.synthetic import preset, write_synthetic_checkpoint
+    from xfastertransformer_b200.utils.flags import Env
+    d = str(tmp_path / "tiny")
+    write_synthetic_checkpoint(d, preset("tiny-llama", vocab_size=300), seed=0, dtype="fp32", std=0.05)
+    dbg = str(tmp_path / "dbg")
+    monkeypatch.setenv("XFT_DEBUG_DIR", dbg)
+    Env.get().reload()
+    try:
+        m = xft.AutoModel.from_pretrained(d, dtype="bf16")
+        m.generate(torch.tensor([[5, 6, 7, 8]]), max_length=6)
+    finally:
+        monkeypatch.delenv("XFT_DEBUG_DIR")
+        Env.get().reload()
+    files = sorted(os.path.basename(f) for f in glob.glob(os.path.join(dbg, "*.pt")))
+    assert any(f.endswith("_layer0_attn_out.pt") for f in files) and any(f.endswith("_layer1_ffn_out.pt") for f in files)
+    t = torch.load(os.path.join(dbg, [f for f in files if f.endswith("_embedding.pt")][0]))
+    assert t.shape == (4, 256) and torch.isfinite(t).all()
+    log = open(os.path.join(dbg, "rank0.log")).read()
+    assert "layer1_attn_out" in log and "absmax" in log

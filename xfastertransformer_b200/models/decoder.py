@@ -28,6 +28,7 @@ from ..parallel.dist import DistContext
 from ..runtime.kv_cache import PagedKVCache
 from ..runtime.loader import LinearWeight, WeightSource, cat_linear, make_linear
 from ..utils.flags import Env
+from ..utils import debugger
 from ..utils.trace import TimeLine
 from .registry import FamilySpec, family_for
 
@@ -583,11 +584,19 @@ class Decoder:
         return y
 
     def forward_layers(self, x: torch.Tensor, b: Batch, cache: PagedKVCache) -> torch.Tensor:
+        dbg = debugger.enabled()
+        step = debugger.next_step() if dbg else 0
+        if dbg:
+            debugger.dump("embedding", x, self.ctx.rank, step)
         for li, L in enumerate(self.layers):
             with TimeLine("Decoder.forwardAttention"):
                 x = self._attention(L, x, b, cache, li)
+            if dbg:
+                debugger.dump(f"layer{self.l0 + li}_attn_out", x, self.ctx.rank, step)
             with TimeLine("Decoder.forwardFFN"):
                 x = self._mlp(L, x, b)
+            if dbg:
+                debugger.dump(f"layer{self.l0 + li}_ffn_out", x, self.ctx.rank, step)
         return x
 
     def head(self, x: torch.Tensor, b: Batch) -> torch.Tensor:

@@ -48,7 +48,7 @@ class CudaRunner:
     def can_run(self, seqs: Sequence, cfg) -> bool:
         if not self.enabled or cfg.do_sample or cfg.num_beams > 1 or cfg.repetition_penalty != 1.0:
             return False
-        if self.m.ctx.pp_size > 1 or self.m.decoder.spec.rope == "2d" or trace.enabled():
+        if self.m.ctx.pp_size > 1 or self.m.decoder.spec.rope == "2d" or trace.enabled() or self.m.env.debug_dir:
             return False
         return all(len(s.pending) == 1 and s.past_len > 0 for s in seqs)
 
