@@ -41,6 +41,11 @@ class CudaRunner:
         self.kernel_launches = 0          # kernels of this library launched through replayed graphs / eager steps
         self.timing = False               # record a CUDA-event pair around each step's launch
         self.step_events = []
+        self._scratch_block = None
+        if self.enabled:
+            # taken now, while the pools are empty: a block taken after a request reserved its blocks would leave that
+            # request one block short and make the pools grow (and move) in the middle of its decode
+            self._scratch()
 
     def reset(self) -> None:
         pass

@@ -94,6 +94,10 @@ class Model:
         if self.ctx.device.type == "cuda":
             from .cuda_runner import CudaRunner
             self.runner = CudaRunner(self)
+        if self.env.kv_cache_gb > 0:
+            # size the KV pools once: pools that never grow never move, so captured decode graphs stay valid
+            per = max(self.cache.bytes_per_block(), 1)
+            self.cache.ensure_blocks(max(int(self.env.kv_cache_gb * (1 << 30)) // per, 1))
         self.step_times_ms: List[float] = []
 
     # ------------------------------------------------------------------------------------
