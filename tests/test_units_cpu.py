@@ -1,0 +1,209 @@
+"""Host-side units on CPU: layout arithmetic, paged KV bookkeeping, checkpoint files, config.ini, timeline, rotary and
+ALiBi tables, batch buckets.  (The reference tests the corresponding C++ units one gtest binary each: kv_reorder_test,
+alibi_embedding_test, rotary_embedding_test, timeline_test, transpose_test.)"""
+import json
+import math
+import os
+
+import pytest
+import torch
+
+from xfastertransformer_b200.config import ModelConfig, RopeConfig
+from xfastertransformer_b200.ops import reference as R
+from xfastertransformer_b200.parallel import partition as P
+from xfastertransformer_b200.runtime.kv_cache import PagedKVCache
+from xfastertransformer_b200.runtime.loader import read_bin, write_bin
+
+
+# ------------------------------------------------------------------------------------------- partition
+def test_task_range_granularity_and_coverage():
+    # the reference's SplitUtil: 64-granular when it divides, else 16, else 2 (split_util.h:8-50)
+    assert [P.task_range(11008, 8, r) for r in range(8)] == \
+        [(0, 1408), (1408, 2816), (2816, 4224), (4224, 5632), (5632, 6976), (6976, 8320), (8320, 9664), (9664, 11008)]
+    assert [P.task_range(688, 2, r) for r in range(2)] == [(0, 352), (352, 688)]
+    for n in (64, 688, 1000, 4096, 11008, 28672, 13696):
+        for s in (1, 2, 3, 4, 8):
+            spans = [P.task_range(n, s, r) for r in range(s)]
+            assert spans[0][0] == 0 and spans[-1][1] == n
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            assert all(b >= a for a, b in spans)
+
+
+def test_head_range_gqa_cover_and_vocab_split():
+    # 64 q heads / 8 kv heads over 8 ranks: 8 q heads and exactly their kv head each
+    for r in range(8):
+        (q0, q1), (k0, k1) = P.head_range(64, 8, 8, r)
+        assert (q0, q1) == (8 * r, 8 * r + 8) and (k0, k1) == (r, r + 1)
+    # more ranks than kv heads: several ranks share one kv head
+    seen = []
+    for r in range(4):
+        (q0, q1), (k0, k1) = P.head_range(32, 2, 4, r)
+        assert k1 - k0 == 1 and k0 == q0 // 16
+        seen += list(range(q0, q1))
+    assert seen == list(range(32))
+    spans = [P.vocab_range(32000, 8, r) for r in range(8)]
+    assert spans[0][0] == 0 and spans[-1][1] == 32000 and all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+
+
+def test_pp_layers_and_expert_owner():
+    assert [P.pp_layer_range(80, 4, s) for s in range(4)] == [(0, 20), (20, 40), (40, 60), (60, 80)]
+    owners = [P.expert_owner(e, 256, 8) for e in range(256)]
+    assert owners[0] == 0 and owners[-1] == 7 and sorted(set(owners)) == list(range(8))
+    for r in range(8):
+        e0, e1 = P.expert_range(256, 8, r)
+        assert all(owners[e] == r for e in range(e0, e1)) and e1 - e0 == 32
+
+
+# ------------------------------------------------------------------------------------------- paged KV cache
+def _cache(blocks=0):
+    c = PagedKVCache(2, 2, 8, 8, "fp16", torch.device("cpu"), 64)
+    if blocks:
+        c.ensure_blocks(blocks)
+    return c
+
+
+def test_kv_fork_copy_on_write_and_free():
+    c = _cache()
+    c.reserve(4)
+    c.add_sequence(1)
+    slots = c.append_slots(1, 70)                       # two blocks, the second partially filled
+    assert len(slots) == 70 and len(c.tables[1]) == 2
+    c.k[0].view(-1, 2, 8)                               # layout sanity: [blocks, heads, 64, d]
+    c.k[0][c.tables[1][1], :, 5] = 7.0                  # token 69 of the sequence
+    c.fork(1, 2)
+    assert c.tables[2] == c.tables[1] and all(c.alloc.ref[b] == 2 for b in c.tables[1])
+    s2 = c.append_slots(2, 1)                           # writing into the shared tail block copies it first
+    assert c.tables[2][0] == c.tables[1][0] and c.tables[2][1] != c.tables[1][1]
+    assert float(c.k[0][c.tables[2][1], 0, 5, 0]) == 7.0          # the copy carries the history
+    assert s2[0] == c.tables[2][1] * 64 + 6
+    free_before = c.alloc.num_free
+    c.free_sequence(2)
+    assert c.alloc.num_free == free_before + 1 and c.alloc.ref[c.tables[1][0]] == 1
+    c.free_sequence(1)
+    assert c.alloc.num_free == c.alloc.num_blocks
+
+
+def test_kv_reorder_is_a_permutation_of_tables():
+    c = _cache()
+    c.reserve(8)
+    for s in (10, 11, 12):
+        c.add_sequence(s)
+        c.append_slots(s, 64 + s)
+    before = {s: list(c.tables[s]) for s in (10, 11, 12)}
+    lens = {s: c.lens[s] for s in (10, 11, 12)}
+    c.reorder([10, 11, 12], [2, 2, 0])                  # beams 0 and 1 continue beam 2, beam 2 continues beam 0
+    assert c.tables[10] == before[12] and c.tables[11] == before[12] and c.tables[12] == before[10]
+    assert c.lens[10] == lens[12] and c.lens[12] == lens[10]
+    assert all(c.alloc.ref[b] == 2 for b in before[12]) and all(c.alloc.ref[b] == 0 for b in before[11])
+    c.truncate(10, 3)
+    assert c.lens[10] == 3 and len(c.tables[10]) == 1
+
+
+def test_kv_pools_grow_without_losing_contents():
+    c = _cache(2)
+    c.add_sequence(0)
+    c.append_slots(0, 100)
+    c.k[1][c.tables[0][1], 1, 3] = 5.0
+    v0 = c.version
+    c.reserve(50)
+    assert c.version > v0 and c.alloc.num_blocks >= 52
+    assert float(c.k[1][c.tables[0][1], 1, 3, 0]) == 5.0
+    bt = c.block_table([0], 8)
+    assert bt.shape == (1, 8) and bt[0, :2].tolist() == c.tables[0]
+
+
+# ------------------------------------------------------------------------------------------- files and config
+@pytest.mark.parametrize("dtype,tol", [("fp32", 0.0), ("fp16", 1e-3), ("bf16", 8e-3)])
+def test_bin_round_trip_and_slices(tmp_path, dtype, tol):
+    t = torch.randn(6, 10)
+    f = str(tmp_path / "w.bin")
+    write_bin(f, t, dtype)
+    assert os.path.getsize(f) == 60 * (4 if dtype == "fp32" else 2)
+    back = read_bin(f, dtype, (6, 10)).float()
+    assert torch.allclose(back, t, atol=tol, rtol=tol)
+    rows = read_bin(f, dtype, (6, 10), rows=(2, 5)).float()
+    assert torch.allclose(rows, t[2:5], atol=tol, rtol=tol)
+
+
+def test_config_ini_round_trip_with_rope_and_moe_keys(tmp_path):
+    cfg = ModelConfig(model_type="deepseek_moe", head_num=16, kv_head_num=16, size_per_head=128, hidden_size=1024,
+                      inter_size=2048, num_layer=4, vocab_size=1000, max_pos_seq_len=4096, weight_data_type="fp8_e4m3",
+                      q_lora_rank=256, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128,
+                      moe_intermediate_size=256, sparse_experts=16, num_experts_per_tok=4, n_group=4, topk_group=2,
+                      first_k_dense_replace=1, routed_scaling_factor=2.5, topk_method="noaux_tc", scoring_func="sigmoid",
+                      norm_topk_prob=True,
+                      rope=RopeConfig(theta=10000, scaling_type="yarn", scaling_factor=40, original_max_pos=4096, mscale=1.0,
+                                      mscale_all_dim=1.0))
+    d = str(tmp_path / "m")
+    os.makedirs(d)
+    cfg.to_ini(d)
+    back = ModelConfig.from_ini(d)
+    for k in ("model_type", "head_num", "hidden_size", "num_layer", "kv_lora_rank", "qk_rope_head_dim", "sparse_experts",
+              "num_experts_per_tok", "n_group", "topk_group", "first_k_dense_replace", "topk_method", "weight_data_type"):
+        assert getattr(back, k) == getattr(cfg, k), k
+    assert back.rope.scaling_type == "yarn" and back.rope.scaling_factor == 40 and back.routed_scaling_factor == 2.5
+    assert back.attn_scale == pytest.approx(cfg.attn_scale)
+
+
+# ------------------------------------------------------------------------------------------- tables
+def test_rope_table_values_and_half_rotation():
+    tab = R.rope_table(16, 8, 10000.0)
+    assert tab.shape == (16, 8)
+    for pos in (0, 3, 15):
+        for i in range(4):
+            inv = 10000.0 ** (-2.0 * i / 8)
+            assert tab[pos, i].item() == pytest.approx(math.cos(pos * inv), abs=1e-5)
+            assert tab[pos, 4 + i].item() == pytest.approx(math.sin(pos * inv), abs=1e-5)
+    q = torch.randn(3, 2, 8)
+    k = torch.randn(3, 1, 8)
+    pos = torch.tensor([0, 5, 9])
+    q2, k2 = R.rope_apply(q, k, pos, tab, 8, "half")
+    assert torch.allclose(q2[0], q[0]) and torch.allclose(k2[0], k[0])          # position 0 is the identity
+    # rotation preserves the norm of every (i, i + half) pair
+    assert torch.allclose((q2 ** 2).sum(-1), (q ** 2).sum(-1), atol=1e-4)
+    x, y = q[1, 0, 1].item(), q[1, 0, 5].item()
+    c, s = tab[5, 1].item(), tab[5, 5].item()
+    assert q2[1, 0, 1].item() == pytest.approx(x * c - y * s, abs=1e-5)
+    assert q2[1, 0, 5].item() == pytest.approx(y * c + x * s, abs=1e-5)
+
+
+def test_alibi_slopes_powers_of_two_and_odd_counts():
+    s8 = R.alibi_slopes(8)
+    assert torch.allclose(s8, torch.tensor([2.0 ** (-(i + 1)) for i in range(8)]))
+    s12 = R.alibi_slopes(12)                          # 8 regular slopes + 4 interleaved from the next power of two
+    assert s12.shape == (12,) and torch.allclose(s12[:8], s8)
+    assert torch.allclose(s12[8:], torch.tensor([2.0 ** (-(2 * i + 1) / 2) for i in range(4)]))
+
+
+# ------------------------------------------------------------------------------------------- timeline, buckets
+def test_python_timeline_whitelist_and_dump(tmp_path, monkeypatch):
+    from xfastertransformer_b200.utils import trace
+    from xfastertransformer_b200.utils.flags import Env
+    monkeypatch.setenv("XFT_TIMELINE_WHITELIST", "A,B")
+    monkeypatch.chdir(tmp_path)
+    Env.get().reload()
+    trace.enable(True)
+    try:
+        with trace.TimeLine("A"):
+            pass
+        with trace.TimeLine("not listed"):
+            pass
+        with trace.TimeLine("B"):
+            pass
+        path = trace.dump()
+    finally:
+        trace.enable(False)
+        monkeypatch.delenv("XFT_TIMELINE_WHITELIST")
+        Env.get().reload()
+    ev = json.load(open(path))
+    ev = ev["traceEvents"] if isinstance(ev, dict) else ev
+    assert [e["name"] for e in ev] == ["A", "B"] and all(e["ph"] == "X" for e in ev)
+
+
+def test_runner_batch_buckets():
+    from xfastertransformer_b200.runtime.cuda_runner import CudaRunner
+    b = [CudaRunner.bucket(n) for n in range(1, 300)]
+    assert all(x >= n for n, x in zip(range(1, 300), b))
+    assert b == sorted(b) and len(set(b)) <= 24                 # a handful of graphs covers every batch size
+    assert CudaRunner.bucket(16) == 16 and CudaRunner.bucket(17) == 24 and CudaRunner.bucket(64) == 64
+    assert max(x / n for n, x in zip(range(9, 300), b[8:])) <= 1.5     # padding waste is bounded

@@ -60,13 +60,14 @@ class CudaRunner:
     @staticmethod
     def bucket(n: int) -> int:
         """Batch sizes are padded up to a bucket so that a serving loop whose batch shrinks and grows by one sequence at
-        a time replays a handful of graphs: powers of two up to 8, multiples of 8 up to 32, of 16 up to 128, of 32 beyond."""
+        a time replays a handful of graphs: powers of two up to 8, multiples of 4 up to 16, of 8 up to 64, of 16 up to
+        128, of 32 beyond (padding never exceeds half of the real rows above 8)."""
         if n <= 8:
             b = 1
             while b < n:
                 b *= 2
             return b
-        step = 8 if n <= 32 else 16 if n <= 128 else 32
+        step = 4 if n <= 16 else 8 if n <= 64 else 16 if n <= 128 else 32
         return (n + step - 1) // step * step
 
     def _key(self, seqs: Sequence):
