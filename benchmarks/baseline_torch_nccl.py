@@ -10,7 +10,6 @@ bench.py (decode tokens/s, device-timed, max over ranks) so the two can be put s
 """
 import argparse
 import json
-import math
 import os
 import sys
 

@@ -1,5 +1,4 @@
 """torchrun worker for the multi-GPU tests (one process per GPU)."""
-import json
 import os
 import sys
 

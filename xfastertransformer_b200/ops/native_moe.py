@@ -4,8 +4,6 @@ synchronises with the host, so the whole MoE layer is capturable in the decode C
 from __future__ import annotations
 
 import ctypes as C
-from typing import Dict
-
 import torch
 
 from . import native as N

@@ -20,11 +20,10 @@ from __future__ import annotations
 
 import sys
 import time
-from typing import Dict, List, Optional, Sequence, Union
+from typing import List, Optional, Sequence
 
 import torch
 
-from .. import ops
 from ..config import KV_DTYPES, ModelConfig, split_hybrid_dtype
 from ..models.decoder import Batch, Decoder
 from ..parallel.dist import CommError, DistContext
