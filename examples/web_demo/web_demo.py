@@ -17,6 +17,8 @@ def main():
     ap.add_argument("-t", "--token_path", required=True)
     ap.add_argument("-d", "--dtype", default="bf16")
     ap.add_argument("--port", type=int, default=7860)
+    ap.add_argument("--chat_format", default="", help="prompt format when the tokenizer has no chat template: "
+                    "llama2, llama3, qwen, qwen2, qwen3, yi, chatglm, chatglm2, chatglm3, chatglm4, baichuan2, gemma")
     a = ap.parse_args()
     try:
         import gradio as gr
@@ -37,7 +39,12 @@ def main():
         try:
             ids = tok.apply_chat_template(msgs, add_generation_prompt=True, return_tensors="pt")
         except Exception:
-            ids = tok(message, return_tensors="pt").input_ids
+            if a.chat_format:
+                from prompts import build_prompt       # examples/web_demo/prompts.py
+                ids = tok(build_prompt(a.chat_format, list(history), message), return_tensors="pt",
+                          add_special_tokens=False).input_ids
+            else:
+                ids = tok(message, return_tensors="pt").input_ids
         model.set_input(ids, max_length=ids.shape[1] + int(max_new), do_sample=temperature > 0, temperature=max(temperature, 1e-3),
                         top_p=top_p, eos_token_id=tok.eos_token_id or -1)
         out = []

@@ -224,3 +224,26 @@ def test_benchmark_serving_client(tmp_path, capsys):
     finally:
         sched.shutdown()
         httpd.shutdown()
+
+
+def test_chat_prompt_formats():
+    """examples/web_demo/prompts.py: the per-family chat formats."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("prompts", os.path.join(ROOT, "examples", "web_demo", "prompts.py"))
+    P = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(P)
+    h = [("hi", "hello")]
+    assert P.build_prompt("llama2", h, "how are you?") == "<s>[INST] hi [/INST] hello </s><s>[INST] how are you? [/INST]"
+    assert P.build_prompt("llama2", [], "q", "be brief").startswith("<s>[INST] <<SYS>>\nbe brief\n<</SYS>>\n\nq [/INST]")
+    l3 = P.build_prompt("llama3", h, "x")
+    assert l3.startswith("<|begin_of_text|><|start_header_id|>user<|end_header_id|>\n\nhi<|eot_id|>")
+    assert l3.endswith("<|start_header_id|>assistant<|end_header_id|>\n\n")
+    q = P.build_prompt("qwen2", h, "x")
+    assert q.count("<|im_start|>") == 5 and q.endswith("<|im_start|>assistant\n")
+    assert P.build_prompt("chatglm2", h, "x") == "[Round 1]\n\n问：hi\n\n答：hello\n\n[Round 2]\n\n问：x\n\n答："
+    assert P.build_prompt("chatglm", [], "x") == "x"
+    assert P.build_prompt("chatglm3", h, "x").endswith("<|user|>\n x<|assistant|>")
+    assert P.build_prompt("baichuan2", h, "x") == "<reserved_106>hi<reserved_107>hello<reserved_106>x<reserved_107>"
+    assert P.build_prompt("gemma", [], "x") == "<bos><start_of_turn>user\nx<end_of_turn>\n<start_of_turn>model\n"
+    with pytest.raises(KeyError):
+        P.build_prompt("nope", [], "x")
