@@ -247,3 +247,22 @@ def test_chat_prompt_formats():
     assert P.build_prompt("gemma", [], "x") == "<bos><start_of_turn>user\nx<end_of_turn>\n<start_of_turn>model\n"
     with pytest.raises(KeyError):
         P.build_prompt("nope", [], "x")
+
+
+def test_bench_reference_arm_prints_unavailable_line():
+    """`bench.py --impl reference` prints exactly one JSON line saying why the reference cannot run here and exits 0."""
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "4",
+                        "--warmup", "3"], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stderr
+    lines = [l for l in r.stdout.splitlines() if l.strip()]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and isinstance(d["unavailable"], str) and d["unavailable"]
+
+
+def test_bench_cli_contract_flags():
+    """The driver's command line (`--gpus N --steps K --warmup W`) parses, and unknown models fail with a clear message."""
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--help"], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0
+    for flag in ("--gpus", "--steps", "--warmup", "--impl", "--model", "--batch", "--input-len", "--dtype"):
+        assert flag in r.stdout, flag
