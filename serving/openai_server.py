@@ -62,7 +62,8 @@ class Scheduler(threading.Thread):
         self.running: Dict[int, Request] = {}
         self.stop_flag = threading.Event()
         self.metrics = dict(requests=0, finished=0, prompt_tokens=0, generated_tokens=0, ttft_sum=0.0, tpot_sum=0.0,
-                            tpot_count=0, steps=0, errors=0)
+                            tpot_count=0, steps=0, mixed_steps=0, errors=0)
+        self.mixed_steps = False          # prefill new prompts in the same forward as the running sequences' decode
         self.max_len = int(getattr(model.model.cfg, "max_pos_seq_len", 0) or 0)
         self.kv_fraction = 0.8            # share of the free device memory the warm-up gives to the KV pools
 
@@ -193,6 +194,27 @@ class Scheduler(threading.Thread):
                                                        f"{self.max_len} positions" if r.prompt_ids else "empty prompt"))
                         else:
                             ok.append(r)
+                    if ok and self.mixed_steps and self.running:
+                        # one forward for the new prompts AND the running sequences: decoding does not pause for prefill
+                        sids_run = list(self.running)
+                        reqs_run = [self.running[s] for s in sids_run]
+                        greedy = all(r.temperature <= 1e-5 for r in ok + reqs_run)
+                        sids_new = self.model.set_input_cb([r.prompt_ids for r in ok], None,
+                                                           [len(r.prompt_ids) + r.max_tokens + 1 for r in ok], greedy=greedy,
+                                                           hold=True)
+                        self.model.set_input_cb([r.generated[-1] for r in reqs_run], sids_run, None, greedy=greedy, append=True)
+                        picks = self._forward(ok + reqs_run, greedy)
+                        done = []
+                        for r, sid, tok in zip(ok, [int(s) for s in sids_new], picks[:len(ok)]):
+                            self.running[sid] = r
+                            self.metrics["prompt_tokens"] += len(r.prompt_ids)
+                            if self._emit(r, tok):
+                                done.append(sid)
+                        done += [s for s, r, tok in zip(sids_run, reqs_run, picks[len(ok):]) if self._emit(r, tok)]
+                        self._finish(done)
+                        self.metrics["steps"] += 1
+                        self.metrics["mixed_steps"] += 1
+                        continue
                     if ok:
                         greedy = all(r.temperature <= 1e-5 for r in ok)
                         sids = self.model.set_input_cb([r.prompt_ids for r in ok], None,
@@ -353,10 +375,11 @@ def make_handler(sched: Scheduler, tok: Tokenizer, model_name: str):
 
 
 def serve(model, port: int, token_path: str = "", max_batch: int = 64, prefill_per_step: int = 4, model_name: str = "xft",
-          warmup: bool = False, max_context: int = 0):
+          warmup: bool = False, max_context: int = 0, mixed_steps: bool = False):
     """Start scheduler + HTTP server (threads); returns (httpd, scheduler, bound_port)."""
     tok = Tokenizer(token_path)
     sched = Scheduler(model, max_batch, prefill_per_step, eos_id=tok.eos)
+    sched.mixed_steps = mixed_steps
     if warmup:
         sched.warmup(max_context)
     sched.start()
@@ -377,6 +400,9 @@ def main():
     ap.add_argument("--prefill_per_step", type=int, default=4)
     ap.add_argument("--no_warmup", action="store_true", help="do not pre-capture the decode graphs of every batch bucket")
     ap.add_argument("--max_context", type=int, default=0, help="longest prompt + output the graphs are sized for")
+    ap.add_argument("--mixed_steps", action="store_true",
+                    help="prefill new prompts in the same forward as the running sequences (lower time per output token "
+                         "under load; the step runs eagerly instead of replaying the decode graph)")
     a = ap.parse_args()
     import xfastertransformer_b200 as xft
     model = xft.AutoModel.from_pretrained(a.model_path, dtype=a.dtype, kv_cache_dtype=a.kv_cache_dtype)
@@ -384,7 +410,8 @@ def main():
         model.follow_cb()                # follower ranks mirror rank 0's engine calls until shutdown
         return
     _, _, port = serve(model, a.port, a.token_path, a.max_batch, a.prefill_per_step,
-                       os.path.basename(a.model_path.rstrip("/")), warmup=not a.no_warmup, max_context=a.max_context)
+                       os.path.basename(a.model_path.rstrip("/")), warmup=not a.no_warmup, max_context=a.max_context,
+                       mixed_steps=a.mixed_steps)
     print(f"OpenAI-compatible server on :{port}", flush=True)
     threading.Event().wait()
 

@@ -259,3 +259,37 @@ def test_debug_dir_dumps_layer_outputs(tmp_path, monkeypatch):
     assert t.shape == (4, 256) and torch.isfinite(t).all()
     log = open(os.path.join(dbg, "rank0.log")).read()
     assert "layer1_attn_out" in log and "absmax" in log
+
+
+def test_mixed_prefill_and_decode_in_one_forward(tiny):
+    """set_input_cb(hold=True) + set_input_cb(append=True): new prompts and running sequences share one forward and
+    get the logits they get in separate forwards."""
+    import torch
+    import xfastertransformer_b200 as xft
+    m = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+    g = torch.Generator().manual_seed(3)
+    p1 = torch.randint(5, 900, (2, 12), generator=g).tolist()
+    p2 = torch.randint(5, 900, (1, 20), generator=g).tolist()
+    # separate: prefill p1, decode one step, prefill p2
+    s1 = m.set_input_cb(p1, None, 40)
+    l1 = m.forward_cb()
+    t1 = l1.argmax(-1).tolist()
+    m.set_input_cb([[t] for t in t1], s1, None)
+    want_dec = m.forward_cb().clone()
+    s2 = m.set_input_cb(p2, None, 40)
+    want_pre = m.forward_cb().clone()
+    m.free_seqs(torch.cat([s1, s2]))
+    # mixed: prefill p1, then ONE forward with p2's prefill and p1's decode step
+    s1 = m.set_input_cb(p1, None, 40)
+    m.forward_cb()
+    s2 = m.set_input_cb(p2, None, 40, hold=True)
+    m.set_input_cb([[t] for t in t1], s1, None, append=True)
+    both = m.forward_cb()
+    assert both.shape[0] == 3
+    assert torch.allclose(both[:1], want_pre, atol=2e-3, rtol=2e-3)
+    assert torch.allclose(both[1:], want_dec, atol=2e-3, rtol=2e-3)
+    # the sequences keep going after a mixed step
+    nxt = both.argmax(-1).tolist()
+    m.set_input_cb([[nxt[1]], [nxt[2]], [nxt[0]]], torch.cat([s1, s2]), None)
+    assert m.forward_cb().shape[0] == 3
+    m.free_seqs(torch.cat([s1, s2]))

@@ -266,3 +266,38 @@ def test_bench_cli_contract_flags():
     assert r.returncode == 0
     for flag in ("--gpus", "--steps", "--warmup", "--impl", "--model", "--batch", "--input-len", "--dtype"):
         assert flag in r.stdout, flag
+
+
+def test_openai_server_mixed_prefill_decode_steps(tmp_path):
+    """--mixed_steps: prompts admitted while others decode share one forward with them; outputs stay those of a lone
+    greedy generate()."""
+    import importlib.util
+    import threading
+    spec = importlib.util.spec_from_file_location("oai", os.path.join(ROOT, "serving", "openai_server.py"))
+    oai = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(oai)
+    d = str(tmp_path / "tiny")
+    write_synthetic_checkpoint(d, preset("tiny-llama", vocab_size=500), seed=6, dtype="fp32", std=0.1)
+    model = xft.AutoModel.from_pretrained(d, dtype="bf16")
+    prompts = [[5, 9, 100, 42, 7], [11, 12, 13], [400, 3, 77, 8, 19, 21, 6], [50, 60], [7, 7, 7, 9]]
+    want = [model.generate(torch.tensor([p]), max_length=len(p) + 8)[0, len(p):].tolist() for p in prompts]
+    httpd, sched, port = oai.serve(model, 0, max_batch=8, prefill_per_step=1, model_name="tiny", mixed_steps=True)
+    base = f"http://127.0.0.1:{port}"
+    got = [None] * len(prompts)
+
+    def one(i):
+        req = urllib.request.Request(base + "/v1/completions", data=json.dumps({"prompt": prompts[i], "max_tokens": 8}).encode(),
+                                     headers={"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=120) as r:
+            got[i] = json.loads(r.read())
+
+    try:
+        ths = [threading.Thread(target=one, args=(i,)) for i in range(len(prompts))]
+        [t.start() for t in ths]
+        [t.join() for t in ths]
+        for i, r in enumerate(got):
+            assert r["choices"][0]["token_ids"] == want[i], (i, r["choices"][0]["token_ids"], want[i])
+        assert sched.metrics["mixed_steps"] >= 1
+    finally:
+        sched.shutdown()
+        httpd.shutdown()

@@ -40,7 +40,10 @@ class AutoModel:
     # -- continuous batching ------------------------------------------------------------
     def set_input_cb(self, input_ids: Optional[Union[List[int], List[List[int]], torch.Tensor]] = None,
                      seq_ids: Optional[Union[List[int], torch.Tensor]] = None,
-                     max_length: Optional[Union[int, List[int], torch.Tensor]] = None, greedy: bool = False):
+                     max_length: Optional[Union[int, List[int], torch.Tensor]] = None, greedy: bool = False,
+                     append: bool = False, hold: bool = False):
+        """``append`` / ``hold`` build one forward out of new prompts and running sequences (see
+        ``runtime.engine.Model.set_input_cb``); both are extensions of the reference's call."""
         seq_lens = None
         if isinstance(input_ids, list):
             if seq_ids is None:
@@ -51,7 +54,7 @@ class AutoModel:
                     raise ValueError("For prompts, input_ids should not be List[int].")
             elif input_ids and isinstance(input_ids[0], list):
                 input_ids = [t for r in input_ids for t in r]
-        return self.model.set_input_cb(input_ids, seq_lens, seq_ids, max_length, greedy)
+        return self.model.set_input_cb(input_ids, seq_lens, seq_ids, max_length, greedy, append, hold)
 
     def follow_cb(self):
         """Follower ranks of a continuous-batching server: mirror rank 0 until it shuts down."""

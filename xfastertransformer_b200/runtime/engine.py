@@ -353,10 +353,15 @@ class Model:
     # ------------------------------------------------------------------------------------
     # continuous-batching API
     # ------------------------------------------------------------------------------------
-    def set_input_cb(self, input_ids=None, seq_lens=None, seq_ids=None, max_length=None, greedy: bool = False) -> torch.Tensor:
+    def set_input_cb(self, input_ids=None, seq_lens=None, seq_ids=None, max_length=None, greedy: bool = False,
+                     append: bool = False, hold: bool = False) -> torch.Tensor:
         """Prefill: ``input_ids`` = flattened prompts + ``seq_lens``; decode: ``input_ids`` [bs,1] +
         ``seq_ids``.  Returns the sequence ids (models.cpp:586-674).  ``greedy=True`` announces that the step will be
-        run with ``forward_cb_greedy`` (followers need to know which forward follows)."""
+        run with ``forward_cb_greedy`` (followers need to know which forward follows).
+
+        Mixed steps (new prompts and running sequences in ONE forward, so decoding does not pause while prompts are
+        prefilled): call once with the prompts and ``hold=True`` (followers do not run a forward yet), then once with
+        the next tokens and ``append=True``; the logits rows come back in that order."""
         def tl(x):
             if x is None:
                 return None
@@ -371,11 +376,14 @@ class Model:
         if seq_lens is None and seq_ids is None and isinstance(input_ids, (list, tuple)) and input_ids and \
                 isinstance(input_ids[0], (list, tuple)):
             seq_lens = [len(r) for r in input_ids]
-        return self._call(OP_SET_INPUT_CB, (ids, tl(seq_lens), tl(seq_ids), tl(max_length), bool(greedy)))
+        return self._call(OP_SET_INPUT_CB, (ids, tl(seq_lens), tl(seq_ids), tl(max_length), bool(greedy), bool(append),
+                                            bool(hold)))
 
-    def _do_set_input_cb(self, ids, seq_lens, seq_ids, max_len, greedy: bool = False) -> torch.Tensor:
+    def _do_set_input_cb(self, ids, seq_lens, seq_ids, max_len, greedy: bool = False, append: bool = False,
+                         hold: bool = False) -> torch.Tensor:
         active = []
         self._cb_greedy = bool(greedy)
+        self._cb_hold = bool(hold)
         if not seq_ids:                                   # new prompts
             if not seq_lens or sum(seq_lens) != len(ids):
                 raise ValueError("set_input_cb: seq_lens do not add up to the number of input ids")
@@ -399,7 +407,7 @@ class Model:
                     raise RuntimeError(f"sequence {sid} has not been prefilled")
                 s.step_forward(int(t))
                 active.append(s)
-        self.cb_active = active
+        self.cb_active = (self.cb_active + active) if append else active
         return torch.tensor([s.seq_id for s in active], dtype=torch.int64)
 
     def forward_cb(self) -> torch.Tensor:
@@ -442,7 +450,7 @@ class Model:
         while not self._closed:
             op, payload = self._sync(0, None)
             self._dispatch(op, payload)
-            if op == OP_SET_INPUT_CB:
+            if op == OP_SET_INPUT_CB and not getattr(self, "_cb_hold", False):
                 if getattr(self, "_cb_greedy", False):
                     self.forward_cb_greedy()
                 else:
