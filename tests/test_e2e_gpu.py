@@ -77,3 +77,32 @@ def test_forward_cb_greedy_replays_the_decode_graph(tiny):
             assert row[full_ids[b, t]] >= row.max() - 0.1 * max(1.0, row.abs().max().item()), (b, t)
     assert (got == want).float().mean() > 0.5
     assert runner.graph_launches - g0 >= 6      # first decode step eager, second captures, the rest replay
+
+
+def test_mixed_prefill_and_decode_step_on_gpu(tiny):
+    """One forward carrying a new prompt and running sequences (set_input_cb hold / append) on the CUDA path: the ragged
+    attention kernel serves rows of length 20 and 1 together; logits match the separate forwards."""
+    import xfastertransformer_b200 as xft
+    from xfastertransformer_b200.ops import native as N
+    m = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+    g = torch.Generator().manual_seed(3)
+    p1 = torch.randint(5, 30000, (2, 12), generator=g).tolist()
+    p2 = torch.randint(5, 30000, (1, 20), generator=g).tolist()
+    s1 = m.set_input_cb(p1, None, 40)
+    t1 = m.forward_cb().argmax(-1).tolist()
+    m.set_input_cb([[t] for t in t1], s1, None)
+    want_dec = m.forward_cb().clone()
+    s2 = m.set_input_cb(p2, None, 40)
+    want_pre = m.forward_cb().clone()
+    m.free_seqs(torch.cat([s1, s2]))
+    s1 = m.set_input_cb(p1, None, 40)
+    m.forward_cb()
+    s2 = m.set_input_cb(p2, None, 40, hold=True)
+    m.set_input_cb([[t] for t in t1], s1, None, append=True)
+    both = m.forward_cb()
+    N.Workspace.get(m.model.ctx.device).check_status()
+    assert both.shape[0] == 3
+    scale = max(1.0, want_pre.abs().max().item())
+    assert (both[:1] - want_pre).abs().max().item() < 0.05 * scale
+    assert (both[1:] - want_dec).abs().max().item() < 0.05 * scale
+    m.free_seqs(torch.cat([s1, s2]))
