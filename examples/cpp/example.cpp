@@ -2,7 +2,7 @@
 // out — tokenisation is left to the caller, as in the reference's `--input_ids` style use).
 //
 //   example -m <model dir> [-d bf16] [--kv_cache_dtype fp16|int8] [-i "1 2 3 4"] [-b batch] [-o out_len]
-//           [--loop n] [--topK k] [--topP p] [--temperature t] [--repetPen r] [--do_sample] [--no_stream]
+//           [--loop n] [--num_beams n] [--topK k] [--topP p] [--temperature t] [--repetPen r] [--do_sample] [--no_stream]
 // Prints the generated ids, first-token latency and average next-token latency (the reference's metrics).
 #include <chrono>
 #include <cstdio>
@@ -17,7 +17,7 @@
 
 int main(int argc, char** argv) {
   std::string model, dtype = "bf16", kv = "fp16", input = "1 15043 29892 920 526 366 29973";
-  int batch = 1, outLen = 32, loop = 1, topK = 50;
+  int batch = 1, outLen = 32, loop = 1, topK = 50, numBeams = 1;
   float topP = 1.0f, temp = 1.0f, rep = 1.0f;
   bool sample = false, stream = true;
   for (int i = 1; i < argc; ++i) {
@@ -31,6 +31,7 @@ int main(int argc, char** argv) {
     else if (a == "-o" || a == "--output_len") outLen = std::atoi(next().c_str());
     else if (a == "-l" || a == "--loop") loop = std::atoi(next().c_str());
     else if (a == "--topK") topK = std::atoi(next().c_str());
+    else if (a == "--num_beams") numBeams = std::atoi(next().c_str());
     else if (a == "--topP") topP = (float)std::atof(next().c_str());
     else if (a == "--temperature") temp = (float)std::atof(next().c_str());
     else if (a == "--repetPen") rep = (float)std::atof(next().c_str());
@@ -47,7 +48,7 @@ int main(int argc, char** argv) {
     for (int it = 0; it < loop; ++it) {
       std::vector<int32_t> ids;
       for (int b = 0; b < batch; ++b) ids.insert(ids.end(), prompt.begin(), prompt.end());
-      m.config((int)prompt.size() + outLen, 1, 1, 1.0f, false, -1, -1, sample, temp, topK, topP, rep);
+      m.config((int)prompt.size() + outLen, numBeams, 1, 1.0f, false, -1, -1, sample, temp, topK, topP, rep);
       m.input(ids, batch);
       double first = 0, rest = 0;
       int steps = 0;
@@ -57,10 +58,10 @@ int main(int argc, char** argv) {
         double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
         if (steps == 0) first = ms; else rest += ms;
         ++steps;
-        if (stream && batch == 1) { std::printf("%d ", next[0]); std::fflush(stdout); }
+        if (stream && batch == 1 && numBeams == 1) { std::printf("%d ", next[0]); std::fflush(stdout); }
       }
       auto out = m.finalize();
-      if (stream && batch == 1) std::printf("\n");
+      if (stream && batch == 1 && numBeams == 1) std::printf("\n");
       const size_t w = out.size() / batch;
       for (int b = 0; b < batch; ++b) {
         std::printf("[%d] ", b);
