@@ -94,3 +94,18 @@ def test_cb_follower_loop_and_greedy_fast_path(tiny, tmp_path):
     ids = _prompt()
     ref = EagerLlama(tiny)
     assert torch.equal(got, ref.greedy(ids, 7)[:, ids.shape[1]:])
+
+
+def test_lost_rank_raises_comm_error_not_hang(tiny, tmp_path):
+    """Failure detection on the host: a rank that leaves between requests makes the driver's next request fail with
+    CommError within XFT_DIST_TIMEOUT_S."""
+    out = str(tmp_path / "lost.txt")
+    env = dict(os.environ, XFT_ENGINE="CPU", XFT_DIST_TIMEOUT_S="8",
+               PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29617", os.path.join(ROOT, "tests", "lost_rank_worker.py"), tiny, out]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert os.path.exists(out), r.stdout[-2000:] + r.stderr[-2000:]
+    res, secs, width = open(out).read().split("\n")[:3]
+    assert res == "CommError", (res, r.stderr[-1500:])
+    assert float(secs) < 60 and int(width) == 12

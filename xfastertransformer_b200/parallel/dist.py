@@ -128,12 +128,15 @@ class DistContext:
         src/layers/decoder_block.h:123,134)."""
         if self.tp_size > 1:
             self.stats["all_reduce"] += 1
-            if t.device.type == "cpu" and t.dtype == torch.bfloat16:
-                f = t.float()
-                dist.all_reduce(f, group=self.tp_group)
-                t.copy_(f)
-            else:
-                dist.all_reduce(t, group=self.tp_group)
+            try:
+                if t.device.type == "cpu" and t.dtype == torch.bfloat16:
+                    f = t.float()
+                    dist.all_reduce(f, group=self.tp_group)
+                    t.copy_(f)
+                else:
+                    dist.all_reduce(t, group=self.tp_group)
+            except RuntimeError as e:      # a peer left or the group timed out: an error for the caller, not a hang
+                raise CommError(f"all-reduce failed on rank {self.rank}: {e}") from e
         return t
 
     def all_gather_cat(self, t: torch.Tensor, sizes: Optional[List[int]] = None, dim: int = -1) -> torch.Tensor:
@@ -142,19 +145,22 @@ class DistContext:
             return t
         self.stats["all_gather"] += 1
         t = t.contiguous()
-        if sizes is None or len(set(sizes)) == 1:
-            outs = [torch.empty_like(t) for _ in range(self.tp_size)]
-            dist.all_gather(outs, t, group=self.tp_group)
-            return torch.cat(outs, dim=dim)
-        d = dim % t.dim()
-        mx = max(sizes)
-        pad_shape = list(t.shape)
-        pad_shape[d] = mx
-        buf = t.new_zeros(pad_shape)
-        buf.narrow(d, 0, t.shape[d]).copy_(t)
-        outs = [torch.empty_like(buf) for _ in range(self.tp_size)]
-        dist.all_gather(outs, buf, group=self.tp_group)
-        return torch.cat([o.narrow(d, 0, s) for o, s in zip(outs, sizes)], dim=d)
+        try:
+            if sizes is None or len(set(sizes)) == 1:
+                outs = [torch.empty_like(t) for _ in range(self.tp_size)]
+                dist.all_gather(outs, t, group=self.tp_group)
+                return torch.cat(outs, dim=dim)
+            d = dim % t.dim()
+            mx = max(sizes)
+            pad_shape = list(t.shape)
+            pad_shape[d] = mx
+            buf = t.new_zeros(pad_shape)
+            buf.narrow(d, 0, t.shape[d]).copy_(t)
+            outs = [torch.empty_like(buf) for _ in range(self.tp_size)]
+            dist.all_gather(outs, buf, group=self.tp_group)
+            return torch.cat([o.narrow(d, 0, s) for o, s in zip(outs, sizes)], dim=d)
+        except RuntimeError as e:
+            raise CommError(f"all-gather failed on rank {self.rank}: {e}") from e
 
     def barrier(self) -> None:
         if self.world > 1:
