@@ -121,6 +121,10 @@ class PeerComm:
             ldr = r2.stride(0)
         ws = N.Workspace.get(x.device)
         self.gp.two_shot = self._two_shot_env if self._two_shot_env is not None else int(self.world >= 4 and T > 16)
+        if fp32:
+            # the two-shot form hands the finished values to the other ranks as bf16 pairs, which would leave the
+            # owner with fp32 and everyone else with rounded values: fp32 outputs always take the one-shot form
+            self.gp.two_shot = 0
         rc = self.lib.xft_gemm_bf16_ar(N._p(x2), ldx, N._p(W.w), W.w.stride(0), N._p(out), out.stride(0), int(fp32), T, n,
                                        K, N._p(bias), N._p(r2), ldr, C.c_float(res_scale), N._ACT[act], N._p(ws.ws),
                                        C.c_size_t(ws.ws_bytes), N._p(ws.counters), ws.n_counters, N._p(ws.status),
