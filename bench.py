@@ -94,7 +94,8 @@ def run_reference(args):
     why = ("reference cannot be installed offline: pip --no-deps build of the unmodified tree stops in CMake "
            "(\"Your compiler has issues to support avx512bf16\"; it would next download xDNN/oneDNN/oneCCL/MKL); "
            "it has no CUDA path at all")
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+    if int(os.environ.get("RANK", "0")) == 0:            # one line per job, also under torchrun
+        print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
 
 
