@@ -207,3 +207,26 @@ def test_runner_batch_buckets():
     assert b == sorted(b) and len(set(b)) <= 24                 # a handful of graphs covers every batch size
     assert CudaRunner.bucket(16) == 16 and CudaRunner.bucket(17) == 24 and CudaRunner.bucket(64) == 64
     assert max(x / n for n, x in zip(range(9, 300), b[8:])) <= 1.5     # padding waste is bounded
+
+
+@pytest.mark.parametrize("mask_tok", [130001, 130000])
+def test_chatglm_2d_positions_honour_both_mask_tokens(mask_tok):
+    """ChatGLM-1 positions: index up to the [gMASK] / [MASK] slot, frozen there from bos on; block positions count from
+    bos.  The reference only ever detects gMASK (a comparison where an assignment was meant); here both work."""
+    from types import SimpleNamespace as NS
+    from xfastertransformer_b200.runtime.engine import Model
+    BOS = 130004
+    prompt = [11, 12, mask_tok, BOS]                 # context of 3 tokens, mask at index 2, then bos
+    stub = NS(ctx=NS(device=torch.device("cpu")))
+    # prefill of the whole prompt
+    b = NS()
+    Model._chatglm_positions(stub, b, [NS(prompt=prompt, past_len=0, pending=prompt)])
+    assert b.positions.tolist() == [0, 1, 2, 2] and b.positions2.tolist() == [0, 0, 0, 1] and b.prefix_lm_lens == [3]
+    # two decode steps later
+    b = NS()
+    Model._chatglm_positions(stub, b, [NS(prompt=prompt, past_len=5, pending=[99])])
+    assert b.positions.tolist() == [2] and b.positions2.tolist() == [3]
+    # no mask token at all: the position freezes at the end of the context
+    b = NS()
+    Model._chatglm_positions(stub, b, [NS(prompt=[11, 12, 13, BOS], past_len=0, pending=[11, 12, 13, BOS])])
+    assert b.positions.tolist() == [0, 1, 2, 3]
