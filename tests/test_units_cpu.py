@@ -230,3 +230,39 @@ def test_chatglm_2d_positions_honour_both_mask_tokens(mask_tok):
     b = NS()
     Model._chatglm_positions(stub, b, [NS(prompt=[11, 12, 13, BOS], past_len=0, pending=[11, 12, 13, BOS])])
     assert b.positions.tolist() == [0, 1, 2, 3]
+
+
+def test_runner_staging_buffer_layout_with_padding_rows():
+    """The decode runner's per-step staging buffer: [ids | positions | slots | kv lengths | cu_q | block table], real rows
+    first, padding rows of the bucket pointing at the runner's scratch block with a context of one token."""
+    from types import SimpleNamespace
+    from xfastertransformer_b200.runtime.cuda_runner import CudaRunner, _Graph
+    cache = PagedKVCache(1, 1, 8, 8, "bf16", torch.device("cpu"), block_size=4)
+    r = CudaRunner.__new__(CudaRunner)
+    r.m = SimpleNamespace(cache=cache)
+    r._scratch_block = None
+    sb = r._scratch()
+    seqs = []
+    for sid, past in ((10, 5), (11, 9), (12, 2)):
+        cache.add_sequence(sid, 16)
+        cache.append_slots(sid, past)
+        seqs.append(SimpleNamespace(seq_id=sid, pending=[100 + sid], past_len=past, max_len=16))
+    slots = r._reserve_slots(seqs)
+    B, W = 4, 8
+    g = _Graph()
+    g.B, g.W = B, W
+    o_ids, o_pos, o_slot, o_kv, o_cu, o_bt, total = r._layout(B, W)
+    g.host = torch.full((total,), -7, dtype=torch.int32)
+    r._fill(g, seqs, slots)
+    h = g.host
+    assert h[o_ids:o_ids + B].tolist() == [110, 111, 112, 0]
+    assert h[o_pos:o_pos + B].tolist() == [5, 9, 2, 0]
+    assert h[o_kv:o_kv + B].tolist() == [6, 10, 3, 1]
+    assert h[o_slot:o_slot + B].tolist() == slots + [sb * cache.block]
+    for i, s in enumerate(seqs):
+        tab = cache.tables[s.seq_id]
+        assert slots[i] == tab[s.past_len // 4] * 4 + s.past_len % 4
+        row = h[o_bt + i * W:o_bt + (i + 1) * W].tolist()
+        assert row[:len(tab)] == tab and row[len(tab):] == [0] * (W - len(tab))
+    assert h[o_bt + 3 * W:o_bt + 4 * W].tolist() == [sb] * W
+    assert o_bt % 4 == 0 and sb not in sum((cache.tables[s.seq_id] for s in seqs), [])

@@ -165,10 +165,9 @@ class CudaRunner:
             pos += [0] * pad
             slots += [sb * cache.block] * pad
             kvl += [1] * pad
-        h[o_ids:o_ids + B] = torch.tensor(ids, dtype=torch.int32)
-        h[o_pos:o_pos + B] = torch.tensor(pos, dtype=torch.int32)
-        h[o_slot:o_slot + B] = torch.tensor(slots, dtype=torch.int32)
-        h[o_kv:o_kv + B] = torch.tensor(kvl, dtype=torch.int32)
+        # ids | positions | slots | kv lengths are adjacent in the staging buffer: one conversion, one copy
+        assert (o_ids, o_pos, o_slot, o_kv) == (0, B, 2 * B, 3 * B)
+        h[0:4 * B] = torch.tensor(ids + pos + slots + kvl, dtype=torch.int32)
         bt = cache.block_table([s.seq_id for s in seqs], W)
         n = len(seqs)
         h[o_bt:o_bt + n * W] = bt.view(-1)

@@ -215,9 +215,11 @@ class PagedKVCache:
     def block_table(self, seq_ids: Sequence[int], width: Optional[int] = None) -> torch.Tensor:
         """int32 [len(seq_ids), width] on the host (unused entries 0)."""
         w = max([len(self.tables[s]) for s in seq_ids] + [1]) if width is None else width
-        t = torch.zeros(len(seq_ids), w, dtype=torch.int32)
-        for i, s in enumerate(seq_ids):
+        # one conversion for the whole table: this runs once per decode step on the host
+        rows = []
+        for s in seq_ids:
             tab = self.tables[s]
-            if tab:
-                t[i, :len(tab)] = torch.tensor(tab, dtype=torch.int32)
-        return t
+            if len(tab) > w:
+                raise ValueError(f"sequence {s} holds {len(tab)} blocks, more than the table width {w}")
+            rows.append(tab + [0] * (w - len(tab)))
+        return torch.tensor(rows, dtype=torch.int32).view(len(seq_ids), w)
