@@ -157,13 +157,19 @@ def main():
             dist.barrier(group=m.ctx.ctrl_group)
         torch.cuda.synchronize()
 
-    # eos = -2 never matches: all sequences decode the full length
-    model.set_input(ids, max_length=L + total_new + 1, eos_token_id=-2, pad_token_id=0)
-    sync_all()
-    t0 = time.perf_counter()
-    model.forward()                              # prefill + first token
-    torch.cuda.synchronize()
-    ttft_ms = (time.perf_counter() - t0) * 1e3
+    # eos = -2 never matches: all sequences decode the full length.  The first pass is the warm-up of the prefill (first
+    # use of every kernel, the allocator's first blocks, NCCL's channels); the reference's benchmark also reports
+    # first-token latency of warmed iterations (benchmark/benchmark.py: --warmup).  A new set_input releases the first
+    # pass's sequences, so the second pass prefills the same prompts from an empty cache.
+    ttft = []
+    for _ in range(2):
+        model.set_input(ids, max_length=L + total_new + 1, eos_token_id=-2, pad_token_id=0)
+        sync_all()
+        t0 = time.perf_counter()
+        model.forward()                          # prefill + first token
+        torch.cuda.synchronize()
+        ttft.append((time.perf_counter() - t0) * 1e3)
+    ttft_cold_ms, ttft_ms = ttft
     for _ in range(args.warmup):
         model.forward()
     runner = m.runner
@@ -187,10 +193,10 @@ def main():
     runner.timing = False
     ws.check_status()
     n_launch = runner.kernel_launches - launches0
-    t = torch.tensor([dev_ms, wall * 1e3, ttft_ms], dtype=torch.float64, device=dev)
+    t = torch.tensor([dev_ms, wall * 1e3, ttft_ms, ttft_cold_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    dev_ms, wall_ms, ttft_ms = t.tolist()
+    dev_ms, wall_ms, ttft_ms, ttft_cold_ms = t.tolist()
     if rank == 0:
         K = args.steps
         value = B * K / (dev_ms / 1e3)
@@ -205,7 +211,7 @@ def main():
                        "parallelism": f"tp{world}", "kv_cache": f"paged-64 {args.kv_dtype}",
                        "l2": "inputs larger than L2 (each step streams %.1f GB of weights per GPU)" % (wbytes / 1e9),
                        "layers": cfg.num_layer},
-            "ttft_ms": round(ttft_ms, 2),
+            "ttft_ms": round(ttft_ms, 2), "ttft_cold_ms": round(ttft_cold_ms, 2),
             "next_token_ms": {"avg": round(statistics.mean(step_ms), 4), "min": round(min(step_ms), 4),
                               "max": round(max(step_ms), 4),
                               "p90": round(sorted(step_ms)[int(0.9 * (len(step_ms) - 1))], 4)},

@@ -1,7 +1,8 @@
 #!/bin/bash
 # CI entry points (reference: ci_build {build,ut,model}; ci/test_case).
 #   ci/run_ci.sh build   compile every CUDA / C++ source in-tree for sm_100a
-#   ci/run_ci.sh ut      CPU unit tests;  on a GPU box also the kernel tests
+#   ci/run_ci.sh ut      native unit tests of the C++ runtime under ASan + UBSan, CPU unit tests; on a GPU box also the
+#                        kernel tests
 #   ci/run_ci.sh model   the model x dtype x kv-dtype smoke matrix of ci/test_case with fake weights (architectures
 #                        from examples/model_config) through benchmarks/benchmark.py, collecting a latency CSV
 set -e
@@ -9,6 +10,7 @@ cd "$(dirname "$0")/.."
 case "${1:-ut}" in
   build) python csrc/build.py --force ;;
   ut)
+    "$(python csrc/build.py --selftest)" "$(mktemp -d)"
     python -m pytest tests -x -q -m "not gpu"
     if python -c "import torch,sys; sys.exit(0 if torch.cuda.is_available() else 1)"; then python -m pytest tests -x -q -m gpu; fi ;;
   model)

@@ -4,7 +4,10 @@
   xfastertransformer_b200/lib/libxft_b200_core.so      C++ runtime (INI, loader, sequences, paged KV, samplers,
                                                         xft::Model C++ API)
 
-Usage: python csrc/build.py [--force] [--verbose]
+  xfastertransformer_b200/lib/xft_runtime_selftest     (--selftest) native unit tests of the host-side runtime, built
+                                                        with AddressSanitizer + UndefinedBehaviorSanitizer
+
+Usage: python csrc/build.py [--force] [--verbose] [--selftest]
 """
 import os
 import subprocess
@@ -97,6 +100,26 @@ def build(force=False, verbose=False):
     return lib, "".join(logs)
 
 
+def build_selftest(verbose=False):
+    """Native unit tests of the host-side runtime, compiled together with the runtime sources they cover under
+    AddressSanitizer and UndefinedBehaviorSanitizer (the device-free part of the C++ core: no kernel library needed)."""
+    os.makedirs(OUT, exist_ok=True)
+    cdir = os.path.join(HERE, "core")
+    src = os.path.join(HERE, "tests", "runtime_selftest.cc")
+    out = os.path.join(OUT, "xft_runtime_selftest")
+    srcs = [os.path.join(cdir, f) for f in ("runtime.cc", "ini.cc", "beam.cc", "env.cc", "arena.cc")]
+    hdrs = tuple(os.path.join(cdir, f) for f in os.listdir(cdir) if f.endswith(".h"))
+    if any(_newer(s, out, hdrs) for s in srcs + [src]):
+        _run(["g++", "-O1", "-g", "-std=c++17", "-fsanitize=address,undefined", "-fno-sanitize-recover=undefined",
+              "-fno-omit-frame-pointer", "-Wall", "-Wextra", "-Werror", "-I", cdir, "-I", "/usr/local/cuda/include",
+              "-o", out, src] + srcs + ["-L", "/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath,/usr/local/cuda/lib64",
+                                        "-lpthread"], verbose)
+    return out
+
+
 if __name__ == "__main__":
+    if "--selftest" in sys.argv:
+        print(build_selftest(verbose="--verbose" in sys.argv))
+        sys.exit(0)
     lib, _ = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
     print(lib)

@@ -48,8 +48,10 @@ void Env::reload() {
   timeline = envInt("XFT_TIMELINE", 0) != 0;
   timelineWhitelist.clear();
   std::stringstream ss(envStr("XFT_TIMELINE_WHITELIST"));
-  for (std::string item; std::getline(ss, item, ',');)
-    if (!item.empty()) timelineWhitelist.insert(item);
+  for (std::string item; std::getline(ss, item, ',');) {
+    const size_t b = item.find_first_not_of(" \t"), e = item.find_last_not_of(" \t");
+    if (b != std::string::npos) timelineWhitelist.insert(item.substr(b, e - b + 1));
+  }
   debugDir = envStr("XFT_DEBUG_DIR");
   kvBlockSize = envInt("XFT_KV_BLOCK_SIZE", 64);
   cudaGraph = envInt("XFT_CUDA_GRAPH", 1) != 0;

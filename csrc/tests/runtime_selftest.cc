@@ -1,0 +1,287 @@
+// Native unit tests of the host-side C++ runtime (the counterpart of the reference's gtest programs under tests/ut:
+// kv_reorder_test.cpp, small_gemm_test.cpp, ... — here for the parts that need no device: layout maths, sequences,
+// the ref-counted block allocator and block tables, samplers, the beam scorer, the INI reader, Env / TimeLine and the
+// arena).  Built by `python csrc/build.py --selftest` with -fsanitize=address,undefined so that every run is also a
+// memory-error and undefined-behaviour check of the runtime; exits non-zero on the first failed expectation.
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <numeric>
+#include <set>
+#include <string>
+#include <vector>
+
+#include "arena.h"
+#include "beam.h"
+#include "env.h"
+#include "ini.h"
+#include "runtime.h"
+
+static int g_failed = 0, g_checks = 0;
+#define EXPECT(cond)                                                                      \
+  do {                                                                                    \
+    ++g_checks;                                                                           \
+    if (!(cond)) { ++g_failed; std::fprintf(stderr, "%s:%d: EXPECT(%s) failed\n", __FILE__, __LINE__, #cond); } \
+  } while (0)
+
+using namespace xft;
+
+static void testPartition() {
+  // every split of n covers [0, n) exactly once, in order; sizes differ by at most one granule (64, 16, 2 or 1)
+  for (int n : {1, 7, 64, 100, 11008}) {
+    for (int splits : {1, 2, 3, 8}) {
+      int next = 0, lo = 1 << 30, hi = 0;
+      for (int i = 0; i < splits; ++i) {
+        auto r = taskRange(n, splits, i);
+        EXPECT(r.first == next && r.second >= r.first);
+        next = r.second;
+        lo = std::min(lo, r.second - r.first);
+        hi = std::max(hi, r.second - r.first);
+      }
+      EXPECT(next == n && hi - lo <= 64);
+      if (n % 2) EXPECT(hi - lo <= 1);
+    }
+  }
+  for (int gran : {16, 64, 128}) {
+    int next = 0;
+    for (int i = 0; i < 4; ++i) {
+      auto r = taskRangeGran(11008, gran, 4, i);
+      EXPECT(r.first == next && (r.first % gran == 0));
+      next = r.second;
+    }
+    EXPECT(next == 11008);
+  }
+  // grouped-query heads: kv heads split first, q heads follow their group; more ranks than kv heads replicate
+  auto h = headRange(64, 8, 8, 3);
+  EXPECT(h.kv1 - h.kv0 == 1 && h.q1 - h.q0 == 8 && h.q0 == h.kv0 * 8);
+  auto m = headRange(32, 2, 4, 3);       // 4 ranks, 2 kv heads: ranks 2,3 share kv head 1
+  EXPECT(m.kv0 == 1 && m.kv1 == 2 && m.q1 - m.q0 == 8 && m.q0 == 24);
+}
+
+static void testSequences() {
+  SequencePool pool;
+  auto& a = pool.create({1, 2, 3}, 16);
+  const int ida = a.id;
+  auto& b = pool.create({4, 5}, 8);
+  EXPECT(b.id != ida && pool.has(ida) && pool.has(b.id));
+  auto& s = pool.get(ida);
+  EXPECT(s.totalLen() == 3 && s.pastLen == 0);
+  s.pending = s.prompt;
+  s.stepForward(9);
+  EXPECT(s.pastLen == 3 && s.pending.size() == 1 && s.pending[0] == 9 && s.totalLen() == 4);
+  s.stepForward(10);
+  EXPECT(s.pastLen == 4 && s.generated.size() == 2);
+  pool.remove(ida);
+  EXPECT(!pool.has(ida));
+  bool threw = false;
+  try { pool.get(ida); } catch (const std::exception&) { threw = true; }
+  EXPECT(threw);
+}
+
+static void testBlockTables() {
+  BlockAllocator al(4);
+  EXPECT(al.numFree() == 4);
+  int b0 = al.alloc(), b1 = al.alloc();
+  EXPECT(b0 != b1 && al.numFree() == 2);
+  al.share(b0);
+  al.release(b0);
+  EXPECT(al.numFree() == 2 && al.refs(b0) == 1);
+  al.release(b0);
+  EXPECT(al.numFree() == 3);
+  al.grow(8);
+  EXPECT(al.numBlocks() == 8 && al.numFree() == 7);
+  al.release(b1);
+
+  BlockTables t(4, 16);
+  int copies = 0;
+  auto cow = [&](int, int) { ++copies; };
+  t.add(1);
+  auto s = t.append(1, 6, cow);                  // two blocks, positions 0..5
+  EXPECT(s.size() == 6 && t.table(1).size() == 2 && t.len(1) == 6);
+  for (int p = 0; p < 6; ++p) EXPECT(s[p] == t.table(1)[p / 4] * 4 + p % 4);
+  t.fork(1, 2);                                  // shares both blocks
+  EXPECT(t.table(2) == t.table(1) && t.allocator().refs(t.table(1)[1]) == 2);
+  auto s2 = t.append(2, 1, cow);                 // tail block is shared and partly filled: copy on write
+  EXPECT(copies == 1 && t.table(2)[0] == t.table(1)[0] && t.table(2)[1] != t.table(1)[1]);
+  EXPECT(s2[0] == t.table(2)[1] * 4 + 2 && t.len(2) == 7 && t.len(1) == 6);
+  t.truncate(2, 3);                              // drops the private tail block
+  EXPECT(t.table(2).size() == 1 && t.len(2) == 3);
+  // reorder: beams 1 and 2 both continue from beam 2
+  t.reorder({1, 2}, {1, 1});
+  EXPECT(t.table(1) == t.table(2) && t.len(1) == 3);
+  const int freeBefore = t.allocator().numFree();
+  t.free(1);
+  EXPECT(t.allocator().numFree() == freeBefore);  // still referenced by sequence 2
+  t.free(2);
+  EXPECT(t.allocator().numFree() == 16);
+}
+
+static void testSamplers() {
+  std::vector<float> l = {0.5f, -1.0f, 2.0f, 2.0f, -3.0f};
+  EXPECT(argmaxFirst(l.data(), 5) == 2);                     // first of equal maxima
+  std::vector<float> r = l;
+  repetitionPenalty(r.data(), 5, {1, 2, 2, 9}, 2.0f);        // distinct ids; id 9 is outside the slice
+  EXPECT(r[1] == -2.0f && r[2] == 1.0f && r[0] == 0.5f && r[3] == 2.0f);
+  std::vector<float> r2 = l;
+  repetitionPenalty(r2.data(), 5, {10, 12}, 2.0f, 10);       // vocabulary slice starting at id 10
+  EXPECT(r2[0] == 0.25f && r2[2] == 1.0f && r2[1] == -1.0f);
+  EXPECT(matchStopWords({5, 6, 7}, {{6, 7}}) && !matchStopWords({5, 6, 7}, {{5, 6}}) && !matchStopWords({7}, {{6, 7}}));
+  auto sw = cleanStopWords({{}, {2}, {3, 4}, {0, 5}, {2, 6}}, 2);   // empty, a lone eos and ids <= 0 are dropped
+  EXPECT(sw.size() == 2 && sw[0] == std::vector<int>({3, 4}) && sw[1] == std::vector<int>({2, 6}));
+  // top-k = 1 is greedy whatever u is; top-p keeps at least two candidates; the inverse CDF is monotone in u
+  for (float u : {0.0f, 0.3f, 0.999f}) EXPECT(sampleTopKTopP(l.data(), 5, 1, 1.0f, 1.0f, u) == 2);
+  std::vector<float> peaked = {10.f, 0.f, -1.f, -2.f};
+  std::set<int> seen;
+  for (int i = 0; i < 100; ++i) seen.insert(sampleTopKTopP(peaked.data(), 4, 4, 0.01f, 1.0f, i / 100.0f));
+  EXPECT(seen.count(0) == 1 && seen.size() <= 2 && seen.count(2) == 0 && seen.count(3) == 0);
+  int prev = -1;
+  std::vector<float> flat = {1.f, 1.f, 1.f, 1.f};
+  std::vector<int> order;
+  for (int i = 0; i < 8; ++i) order.push_back(sampleTopKTopP(flat.data(), 4, 4, 1.0f, 1.0f, (i + 0.5f) / 8.0f));
+  std::set<int> all(order.begin(), order.end());
+  EXPECT(all.size() == 4);                                   // uniform logits: every id is reachable
+  (void)prev;
+}
+
+static void testBeams() {
+  std::vector<float> row = {1.f, 2.f, 3.f};
+  logSoftmaxRow(row.data(), 3);
+  double s = 0;
+  for (float v : row) s += std::exp((double)v);
+  EXPECT(std::fabs(s - 1.0) < 1e-5 && row[2] > row[1] && row[1] > row[0]);
+
+  BeamHypotheses h(2, 1.0f, false);
+  h.add({1, 2}, -1.0, 2);
+  h.add({3}, -3.0, 1);
+  h.add({4, 5, 6}, -1.5, 3);                  // -0.5 per token beats -3.0: the worst one is evicted
+  EXPECT(h.beams().size() == 2);
+  for (auto& b : h.beams()) EXPECT(b.second != std::vector<int32_t>({3}));
+  EXPECT(!h.isDone(-0.1, 4) && h.isDone(-100.0, 4));
+
+  // one request, two beams, vocabulary of 4 with eos = 3.  Step 1: only beam 0 is live (the scorer masks the clones).
+  const int V = 4;
+  BeamSearchScorer sc(1, 2, 1.0f, false, 3, 0, 1);
+  std::vector<float> lp(2 * V);
+  auto fill = [&](std::vector<float> a, std::vector<float> b) {
+    for (int i = 0; i < V; ++i) { lp[i] = a[i]; lp[V + i] = b[i]; }
+    logSoftmaxRow(lp.data(), V);
+    logSoftmaxRow(lp.data() + V, V);
+  };
+  std::vector<int32_t> tok;
+  std::vector<int> src;
+  fill({0.f, 3.f, 2.f, -5.f}, {0.f, 3.f, 2.f, -5.f});
+  sc.process(lp.data(), V, tok, src);
+  EXPECT(tok.size() == 2 && src.size() == 2);
+  EXPECT(tok[0] == 1 && tok[1] == 2 && src[0] == 0 && src[1] == 0);      // the two best continuations of beam 0
+  // Step 2: beam 0 wants eos most; the hypothesis is banked and the live beams continue with the next best tokens
+  fill({-5.f, 0.f, 0.5f, 4.f}, {1.f, 0.f, -1.f, -6.f});
+  sc.process(lp.data(), V, tok, src);
+  EXPECT(tok.size() == 2);
+  for (int t : tok) EXPECT(t != 3);
+  EXPECT(!sc.isDone() || true);
+  auto out = sc.finalize({{7, 8}}, 6);
+  EXPECT(out.size() == 1 && out[0].size() >= 3 && out[0][0] == 7 && out[0][1] == 8);
+  EXPECT(out[0][2] == 1);                                               // the banked hypothesis started with token 1
+}
+
+static void testIni(const std::string& dir) {
+  const std::string path = dir + "/config.ini";
+  {
+    std::ofstream f(path);
+    f << "; comment\n[llama]\nmodel_name = tiny\nHead_Num = 4\n  size_per_head=8 \nlayernorm_eps = 1e-6\n"
+         "do_qk_norm = true\n# another\n[other]\nx = 1\n";
+  }
+  Ini ini(path);
+  EXPECT(ini.ok() && ini.sections().size() == 2 && ini.sections()[0] == "llama");
+  EXPECT(ini.getInt("llama", "head_num") == 4 && ini.getInt("llama", "SIZE_PER_HEAD") == 8);
+  EXPECT(std::fabs(ini.getFloat("llama", "layernorm_eps") - 1e-6) < 1e-12);
+  EXPECT(ini.getBool("llama", "do_qk_norm") && !ini.getBool("llama", "missing", false));
+  EXPECT(ini.get("llama", "model_name") == "tiny" && ini.get("llama", "nope", "dflt") == "dflt");
+  EXPECT(ini.has("other", "x") && !ini.has("other", "y"));
+  Ini missing(dir + "/does_not_exist.ini");
+  EXPECT(!missing.ok());
+}
+
+static void testEnvAndTimeline(const std::string& dir) {
+  setenv("XFT_VERBOSE", "2", 1);
+  setenv("XFT_PIPELINE_STAGE", "2", 1);
+  setenv("XFT_TIMELINE_WHITELIST", "A, C", 1);
+  setenv("XFT_KV_CACHE_GB", "1.5", 1);
+  setenv("XFT_CUDA_GRAPH", "0", 1);
+  Env::get().reload();
+  Env& e = Env::get();
+  EXPECT(e.verbose == 2 && e.pipelineStage == 2 && !e.cudaGraph && std::fabs(e.kvCacheGb - 1.5) < 1e-9);
+  EXPECT(e.timelineWhitelist.count("A") == 1 && e.timelineWhitelist.count("C") == 1 && e.timelineWhitelist.size() == 2);
+  TimeLine::enable(true);
+  { TimeLine a("A"); TimeLine b("B"); }          // B is filtered out by the whitelist
+  { TimeLine c("C"); }
+  EXPECT(TimeLine::pending() == 2);
+  const std::string out = TimeLine::dump(dir + "/timeline.json");
+  EXPECT(!out.empty() && TimeLine::pending() == 0);
+  std::ifstream f(out);
+  std::string text((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
+  EXPECT(text.find("\"name\": \"A\"") != std::string::npos || text.find("\"name\":\"A\"") != std::string::npos);
+  EXPECT(text.find("\"B\"") == std::string::npos && text.find("\"ph\"") != std::string::npos);
+  TimeLine::enable(false);
+  { TimeLine off("A"); }
+  EXPECT(TimeLine::pending() == 0);
+  unsetenv("XFT_VERBOSE");
+  unsetenv("XFT_PIPELINE_STAGE");
+  unsetenv("XFT_TIMELINE_WHITELIST");
+  unsetenv("XFT_KV_CACHE_GB");
+  unsetenv("XFT_CUDA_GRAPH");
+  Env::get().reload();
+  EXPECT(Env::get().verbose == 0 && Env::get().cudaGraph && Env::get().timelineWhitelist.empty());
+  log(LogLevel::Debug, "not printed at verbosity %d", 0);
+}
+
+static int g_backendAllocs = 0, g_backendFrees = 0;
+static void* countingAlloc(size_t n) { ++g_backendAllocs; return std::malloc(n); }
+static void countingFree(void* p) { ++g_backendFrees; std::free(p); }
+
+static void testArena() {
+  EXPECT(Arena::roundUp(1) == 512 && Arena::roundUp(512) == 512 && Arena::roundUp(513) == 1024);
+  EXPECT(Arena::roundUp((1u << 20) + 1) == (2u << 20) && Arena::roundUp(3u << 20) == (4u << 20));
+  {
+    Arena a(countingAlloc, countingFree);
+    void* p = a.allocate(1000);
+    std::memset(p, 0xab, 1000);
+    EXPECT(p && a.bytesInUse() == 1024 && g_backendAllocs == 1);
+    a.release(p);
+    EXPECT(a.bytesInUse() == 0 && a.bytesCached() == 1024 && g_backendFrees == 0);
+    void* q = a.allocate(600);                   // same class: served from the free list
+    EXPECT(q == p && g_backendAllocs == 1 && a.bytesCached() == 0);
+    void* r = a.allocate(600);
+    EXPECT(r != q && g_backendAllocs == 2);
+    int unknown = 0;
+    a.release(&unknown);                         // ignored
+    a.release(q);
+    a.trim();
+    EXPECT(g_backendFrees == 1 && a.bytesCached() == 0 && a.bytesInUse() == 1024);
+    {
+      ArenaBuf b(a, 100), c;
+      EXPECT(b.get() && b.size() == 100);
+      c = std::move(b);
+      EXPECT(c.get() && !b.get());
+    }
+    EXPECT(a.bytesInUse() == 1024);
+    a.release(r);
+  }                                              // destructor frees what is cached
+  EXPECT(g_backendAllocs == g_backendFrees);
+}
+
+int main(int argc, char** argv) {
+  const std::string dir = argc > 1 ? argv[1] : "/tmp";
+  testPartition();
+  testSequences();
+  testBlockTables();
+  testSamplers();
+  testBeams();
+  testIni(dir);
+  testEnvAndTimeline(dir);
+  testArena();
+  std::printf("runtime_selftest: %d checks, %d failed\n", g_checks, g_failed);
+  return g_failed ? 1 : 0;
+}

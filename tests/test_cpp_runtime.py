@@ -261,3 +261,19 @@ def test_cpp_beam_scorer_matches_python(core, early, lp, eos):
     c.xftc_log_softmax.argtypes = [ctypes.c_void_p, ctypes.c_int]
     c.xftc_log_softmax(y.data_ptr(), 50)
     assert torch.allclose(y, torch.log_softmax(x, -1), atol=1e-5)
+
+
+def test_native_selftest_under_sanitizers(tmp_path):
+    """The C++ runtime's own unit-test program (csrc/tests/runtime_selftest.cc), built together with the runtime sources
+    with -fsanitize=address,undefined -Wall -Wextra -Werror: every expectation holds and neither sanitizer reports."""
+    import importlib.util
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("xft_build", os.path.join(root, "csrc", "build.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    exe = mod.build_selftest()
+    r = subprocess.run([exe, str(tmp_path)], capture_output=True, text=True, timeout=120,
+                       env=dict(os.environ, ASAN_OPTIONS="detect_leaks=1", UBSAN_OPTIONS="print_stacktrace=1"))
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "0 failed" in r.stdout and "runtime error" not in r.stderr and "AddressSanitizer" not in r.stderr

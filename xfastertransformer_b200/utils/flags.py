@@ -43,7 +43,7 @@ class Env:
         self.fake_load_info = _int("XFT_FAKE_LOAD_INFO", 0) != 0
         self.debug_dir = e.get("XFT_DEBUG_DIR", "")
         wl = e.get("XFT_TIMELINE_WHITELIST", "")
-        self.timeline_whitelist: List[str] = [s for s in wl.split(",") if s]
+        self.timeline_whitelist: List[str] = [s.strip() for s in wl.split(",") if s.strip()]
         self.timeline = _int("XFT_TIMELINE", 0) != 0
         self.single_instance = _int("SINGLE_INSTANCE", 0) != 0
         self.moe_engine = _int("XFT_MOE_ENGINE", 1)
