@@ -299,7 +299,11 @@ def make_handler(sched: Scheduler, tok: Tokenizer, model_name: str):
 
         def do_GET(self):
             if self.path == "/health":
-                return self._json(200, {"status": "ok", "running": len(sched.running), "waiting": sched.waiting.qsize()})
+                wd = getattr(getattr(sched.model, "model", sched.model), "watchdog", None)
+                stuck = bool(wd is not None and wd.overdue)        # an engine step is past XFT_STEP_TIMEOUT_S right now
+                return self._json(503 if stuck else 200,
+                                  {"status": "stuck" if stuck else "ok", "running": len(sched.running),
+                                   "waiting": sched.waiting.qsize(), "overdue_steps": wd.trips if wd is not None else 0})
             if self.path == "/v1/models":
                 return self._json(200, {"object": "list", "data": [{"id": model_name, "object": "model", "owned_by": "xft"}]})
             if self.path == "/metrics":

@@ -293,3 +293,59 @@ def test_mixed_prefill_and_decode_in_one_forward(tiny):
     m.set_input_cb([[nxt[1]], [nxt[2]], [nxt[0]]], torch.cat([s1, s2]), None)
     assert m.forward_cb().shape[0] == 3
     m.free_seqs(torch.cat([s1, s2]))
+
+
+def test_step_watchdog_reports_an_overdue_step_and_the_step_raises(tiny, capfd):
+    """XFT_STEP_TIMEOUT_S: a step that runs over the limit is reported by the monitor thread while it is still running
+    (log line, stack dump, hook) and raises StepTimeout when it returns; steps within the limit are untouched and the
+    engine stays usable afterwards."""
+    import time
+    from xfastertransformer_b200.utils.watchdog import StepTimeout, StepWatchdog
+    seen = []
+    wd = StepWatchdog(0.05, on_timeout=lambda what, late: seen.append((what, late)))
+    with wd.scope("fast"):
+        pass
+    assert wd.trips == 0 and not seen
+    t0 = time.monotonic()
+    with pytest.raises(StepTimeout, match="slow step"):
+        with wd.scope("slow step"):
+            while not seen and time.monotonic() - t0 < 5:      # the hook fires while the step is still inside
+                time.sleep(0.01)
+            assert wd.overdue                  # what a health check sees while the step is stuck
+    assert not wd.overdue
+    assert wd.trips == 1 and seen[0][0] == "slow step" and seen[0][1] >= 0.05
+    cap = capfd.readouterr()
+    assert "step watchdog" in cap.out and "slow step" in cap.out            # the log line (the logger writes stdout)
+    assert "most recent call first" in cap.err                              # faulthandler's dump of every thread
+    with pytest.raises(KeyError):              # the step's own exception is not replaced by the time-out
+        with wd.scope("raises"):
+            time.sleep(0.12)
+            raise KeyError("x")
+    with wd.scope("fast again"):
+        pass
+    wd.close()
+    off = StepWatchdog(0.0)
+    with off.scope("never guarded"):
+        time.sleep(0.01)
+    assert off._thread is None
+
+    # through the engine: a forward slowed down beyond the limit raises, the next one works
+    model = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+    m = model.model
+    m.watchdog = StepWatchdog(0.05, dump_stacks=False)
+    ids = torch.tensor([[5, 6, 7, 8]])
+    model.set_input(ids, max_length=12)
+    real_run = m._run
+
+    def slow_run(seqs, logits_all=False):
+        time.sleep(0.15)
+        return real_run(seqs, logits_all)
+    m._run = slow_run
+    with pytest.raises(StepTimeout):
+        model.forward()
+    m._run = real_run
+    m.watchdog.close()
+    m.watchdog = StepWatchdog(30.0)
+    model.set_input(ids, max_length=12)
+    assert model.forward().shape[0] == 1
+    m.watchdog.close()

@@ -266,3 +266,22 @@ def test_runner_staging_buffer_layout_with_padding_rows():
         assert row[:len(tab)] == tab and row[len(tab):] == [0] * (W - len(tab))
     assert h[o_bt + 3 * W:o_bt + 4 * W].tolist() == [sb] * W
     assert o_bt % 4 == 0 and sb not in sum((cache.tables[s.seq_id] for s in seqs), [])
+
+
+def test_progress_bar_draws_on_request_only(monkeypatch):
+    import io
+    from xfastertransformer_b200.utils.progress import ProgressBar
+    buf = io.StringIO()
+    out = list(ProgressBar.wrap(range(4), "Loading layers", width=8, stream=buf, enabled=True))
+    text = buf.getvalue()
+    assert out == [0, 1, 2, 3] and "Loading layers [####....] 2/4" in text and text.rstrip().endswith("s")
+    assert "[########] 4/4" in text and text.endswith("\n")
+    quiet = io.StringIO()                                 # not a terminal, not forced: silent
+    monkeypatch.delenv("XFT_PROGRESS", raising=False)
+    assert list(ProgressBar.wrap(range(3), "x", stream=quiet)) == [0, 1, 2] and quiet.getvalue() == ""
+    monkeypatch.setenv("XFT_PROGRESS", "1")
+    monkeypatch.setenv("RANK", "1")                       # follower ranks never draw
+    assert list(ProgressBar.wrap(range(3), "x", stream=quiet)) == [0, 1, 2] and quiet.getvalue() == ""
+    monkeypatch.setenv("RANK", "0")
+    list(ProgressBar.wrap(range(3), "x", stream=quiet))
+    assert "3/3" in quiet.getvalue()

@@ -29,6 +29,7 @@ from ..runtime.kv_cache import PagedKVCache
 from ..runtime.loader import LinearWeight, WeightSource, cat_linear, make_linear
 from ..utils.flags import Env
 from ..utils import debugger
+from ..utils.progress import ProgressBar
 from ..utils.trace import TimeLine
 from .registry import FamilySpec, family_for
 
@@ -104,7 +105,8 @@ class Decoder:
         # weights
         with TimeLine("Decoder.loadWeights"):
             self._load_embedding(embed_from)
-            self.layers: List[Layer] = [self._load_layer(i) for i in range(self.l0, self.l1)]
+            self.layers: List[Layer] = [self._load_layer(i)
+                                        for i in ProgressBar.wrap(range(self.l0, self.l1), "Loading layers")]
             self._load_head(embed_from)
             self._fold_norms()
 

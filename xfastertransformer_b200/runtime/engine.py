@@ -30,6 +30,7 @@ from ..parallel.dist import CommError, DistContext
 from ..utils import log, trace
 from ..utils.flags import Env
 from ..utils.trace import TimeLine
+from ..utils.watchdog import StepTimeout, StepWatchdog  # noqa: F401  (StepTimeout is re-exported)
 from . import sampler as S
 from .kv_cache import PagedKVCache
 from .sequence import SamplingMeta, SequenceMeta, SequencePool
@@ -98,6 +99,9 @@ class Model:
             per = max(self.cache.bytes_per_block(), 1)
             self.cache.ensure_blocks(max(int(self.env.kv_cache_gb * (1 << 30)) // per, 1))
         self.step_times_ms: List[float] = []
+        # XFT_STEP_TIMEOUT_S > 0: a monitor thread reports a step that runs over (log + stack dump) and the step raises
+        # StepTimeout when it returns
+        self.watchdog = StepWatchdog(self.env.step_timeout_s)
 
     # ------------------------------------------------------------------------------------
     def _vocab_size_of(self, r: int) -> int:
@@ -241,19 +245,20 @@ class Model:
         if not seqs:
             raise RuntimeError("forward() before set_input()/input()")
         t0 = time.perf_counter()
-        if cfg.num_beams > 1:
-            out = self._beam_step()
-        else:
-            active = [x for x in seqs if not x.done]
-            if not active:
-                out = torch.full((len(seqs),), cfg.eos_token_id, dtype=torch.int64)
-            elif self.runner is not None and self.runner.can_run(active, cfg):
-                toks = self.runner.step(active, cfg)
-                out = self._commit(seqs, toks, cfg)
+        with self.watchdog.scope("forward"):
+            if cfg.num_beams > 1:
+                out = self._beam_step()
             else:
-                local = self._run(active)
-                toks = self._select(local, active, cfg).tolist()
-                out = self._commit(seqs, toks, cfg)
+                active = [x for x in seqs if not x.done]
+                if not active:
+                    out = torch.full((len(seqs),), cfg.eos_token_id, dtype=torch.int64)
+                elif self.runner is not None and self.runner.can_run(active, cfg):
+                    toks = self.runner.step(active, cfg)
+                    out = self._commit(seqs, toks, cfg)
+                else:
+                    local = self._run(active)
+                    toks = self._select(local, active, cfg).tolist()
+                    out = self._commit(seqs, toks, cfg)
         self.step_times_ms.append((time.perf_counter() - t0) * 1e3)
         return out
 
@@ -415,11 +420,12 @@ class Model:
         seqs = self.cb_active
         if not seqs:
             raise RuntimeError("forward_cb() before set_input_cb()")
-        local = self._run(seqs)
-        for s in seqs:                      # inputs are now in the cache
-            s.past_len += len(s.pending)
-            s.pending = []
-        return S.gather_logits(local, self.ctx, self.vocab_sizes).float()
+        with self.watchdog.scope("forward_cb"):
+            local = self._run(seqs)
+            for s in seqs:                      # inputs are now in the cache
+                s.past_len += len(s.pending)
+                s.pending = []
+            return S.gather_logits(local, self.ctx, self.vocab_sizes).float()
 
     def forward_cb_greedy(self) -> torch.Tensor:
         """Greedy next token [bs] of the sequences of the last ``set_input_cb(..., greedy=True)``, chosen on the device:
@@ -431,11 +437,12 @@ class Model:
         if self.ctx.world > 1 and not getattr(self, "_cb_greedy", False):
             raise RuntimeError("forward_cb_greedy() needs set_input_cb(..., greedy=True) on more than one rank")
         cfg = self._greedy_cfg
-        if self.runner is not None and self.runner.can_run(seqs, cfg) and self.runner.worth_capturing(seqs):
-            toks = self.runner.step(seqs, cfg)
-        else:
-            local = self._run(seqs)
-            toks = S.greedy_select(local, self.decoder.v0, self.ctx).cpu().tolist()
+        with self.watchdog.scope("forward_cb_greedy"):
+            if self.runner is not None and self.runner.can_run(seqs, cfg) and self.runner.worth_capturing(seqs):
+                toks = self.runner.step(seqs, cfg)
+            else:
+                local = self._run(seqs)
+                toks = S.greedy_select(local, self.decoder.v0, self.ctx).cpu().tolist()
         for s in seqs:
             s.past_len += len(s.pending)
             s.pending = []
