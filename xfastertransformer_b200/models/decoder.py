@@ -109,6 +109,7 @@ class Decoder:
                                         for i in ProgressBar.wrap(range(self.l0, self.l1), "Loading layers")]
             self._load_head(embed_from)
             self._fold_norms()
+        self.has_moe = any(L.mlp_kind not in ("llama", "gpt") for L in self.layers)
 
     # ------------------------------------------------------------------------------------
     # rotary tables
@@ -580,10 +581,14 @@ class Decoder:
             out = out + ops.linear(g, L.shared[1], out_dtype=torch.float32)
         if self.tpr == 0:
             out = out + x.float()
-        y = out.to(x.dtype)
         if self.tp > 1:
-            y = self.ctx.all_reduce(y)
-        return y
+            peer = getattr(self.ctx, "peer", None)
+            if peer is not None and out.is_cuda and out.numel() <= peer.slot:
+                # decode sizes: the peer-memory one-shot kernel sums the fp32 partials (it can be captured in a CUDA
+                # graph, which a NCCL call cannot safely be)
+                return peer.all_reduce(out.contiguous()).to(x.dtype)
+            return self.ctx.all_reduce(out.to(x.dtype))
+        return out.to(x.dtype)
 
     def forward_layers(self, x: torch.Tensor, b: Batch, cache: PagedKVCache) -> torch.Tensor:
         dbg = debugger.enabled()

@@ -55,6 +55,12 @@ class CudaRunner:
             return False
         if self.m.ctx.pp_size > 1 or self.m.decoder.spec.rope == "2d" or trace.enabled() or self.m.env.debug_dir:
             return False
+        if self.m.ctx.tp_size > 1 and self.m.decoder.has_moe:
+            # the experts' partial sums cross ranks through the peer-memory all-reduce, which holds at most `slot`
+            # values; without it the step would put a NCCL collective inside the captured graph
+            peer = getattr(self.m.ctx, "peer", None)
+            if peer is None or self.bucket(len(seqs)) * self.m.cfg.hidden_size > peer.slot:
+                return False
         return all(len(s.pending) == 1 and s.past_len > 0 for s in seqs)
 
     @staticmethod
