@@ -109,3 +109,57 @@ def test_lost_rank_raises_comm_error_not_hang(tiny, tmp_path):
     res, secs, width = open(out).read().split("\n")[:3]
     assert res == "CommError", (res, r.stderr[-1500:])
     assert float(secs) < 60 and int(width) == 12
+
+
+@pytest.mark.parametrize("mt,ep", [("mixtral", 0), ("mixtral", 1), ("deepseek_moe", 1), ("qwen3_moe", 0)])
+def test_moe_two_ranks_sliced_and_expert_parallel(mt, ep, tmp_path):
+    """MoE across two gloo ranks against the single-rank engine on the same files: XFT_EXPERT_PARALLEL=0 slices every
+    expert's intermediate dimension (the reference's only mode, src/layers/moe_deepseek.h / mlp_llama.h:70-79), =1
+    places whole experts on ranks (each rank runs its own experts on the replicated tokens; the row-parallel reduction
+    combines).  Prefill and one decode step."""
+    import xfastertransformer_b200 as xft
+    from xfastertransformer_b200.config import ModelConfig, RopeConfig
+    from xfastertransformer_b200.parallel.dist import DistContext
+    from xfastertransformer_b200.tools.synthetic import write_synthetic_checkpoint
+    if mt == "deepseek_moe":
+        cfg = ModelConfig(model_type=mt, head_num=4, kv_head_num=4, size_per_head=32, hidden_size=128, inter_size=256,
+                          num_layer=2, vocab_size=1000, max_pos_seq_len=512, weight_data_type="bf16", q_lora_rank=64,
+                          kv_lora_rank=32, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32,
+                          moe_intermediate_size=64, sparse_experts=8, dense_experts=1, num_experts_per_tok=2, n_group=4,
+                          topk_group=2, first_k_dense_replace=1, routed_scaling_factor=2.5, topk_method="noaux_tc",
+                          scoring_func="sigmoid", norm_topk_prob=True, activation_type="silu", start_id=1, end_id=2,
+                          rope=RopeConfig(theta=10000))
+    else:
+        cfg = ModelConfig(model_type=mt, num_layer=2, hidden_size=128, head_num=4, kv_head_num=2, size_per_head=32,
+                          inter_size=128, moe_intermediate_size=128, vocab_size=1000, max_pos_seq_len=512,
+                          sparse_experts=8, num_experts_per_tok=2, norm_topk_prob=True, activation_type="silu",
+                          weight_data_type="bf16", do_qk_norm=(mt == "qwen3_moe"), start_id=1, end_id=2)
+    d = str(tmp_path / "m")
+    write_synthetic_checkpoint(d, cfg, seed=0, dtype="bf16", std=0.05)
+    out = str(tmp_path / "moe.pt")
+    env = dict(os.environ, XFT_ENGINE="CPU", XFT_EXPERT_PARALLEL=str(ep),
+               PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    port = 29621 + 2 * (ep + 2 * ["mixtral", "deepseek_moe", "qwen3_moe"].index(mt))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "moe_tp_worker.py"), d, out]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    got = torch.load(out)
+    # single rank, same files
+    os.environ["XFT_ENGINE"] = "CPU"
+    DistContext.reset()
+    m = xft.AutoModel.from_pretrained(d, dtype="bf16")
+    ids = torch.randint(0, 1000, (3, 20), generator=torch.Generator().manual_seed(2))
+    sid = m.set_input_cb(ids.tolist(), None, 64)
+    want = m.forward_cb()
+    m.set_input_cb(want.argmax(-1).tolist(), sid, 64)
+    want2 = m.forward_cb()
+    m.free_seqs(sid)
+    scale = want.abs().max().item()
+    assert (got["logits"] - want).abs().max().item() < 2e-3 * max(scale, 1.0)
+    assert (got["logits2"] - want2).abs().max().item() < 2e-3 * max(scale, 1.0)
+    I = cfg.moe_intermediate_size if mt != "mixtral" else cfg.inter_size
+    if ep:
+        assert got["held"] == [(4, 0, I), (4, 4, I)]              # whole experts, half of them each
+    else:
+        assert [h[0] for h in got["held"]] == [8, 8] and sum(h[2] for h in got["held"]) == I     # every expert, sliced
