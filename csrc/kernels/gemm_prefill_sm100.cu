@@ -1,0 +1,438 @@
+// Persistent prefill GEMM for sm_100a with the tensor-parallel reduction fused in:
+//     Y[T, N] = act( sum over ranks ( X_r[T, K_r] · W_r[N, K_r]^T ) + bias ) + res_scale * residual        (bf16 in / out)
+//
+// The reference runs a row-parallel linear and then a separate collective (o_proj / down_proj followed by
+// Messenger::reduceAdd, src/layers/decoder_block.h:122-134; DistLinear in src/layers/dist_linear.h).  At prefill sizes
+// that collective moves T x N values per layer twice and leaves the tensor cores idle while it runs.  Here one kernel
+// does both, tile by tile:
+//
+//   * One CTA per SM walks a list of 128-feature x BN-token output tiles.  Warp 0 streams operands with TMA into a
+//     shared-memory ring, warp 1 issues tcgen05.mma into one of TWO TMEM accumulators, warps 2-5 drain the other one:
+//     the epilogue of tile i (conversion, NVLink stores, waits on peers) overlaps the main loop of tile i + 1.
+//   * Token blocks are owned round-robin by the ranks (block j belongs to rank j % world).  A rank that finishes a tile
+//     of a block it does not own stores its bf16 partial straight into the owner's memory (reduce-scatter half) and
+//     raises a flag there; the owner adds the partials of all ranks to its own fp32 accumulator in rank order, applies
+//     bias / activation / residual and stores the finished tile into the output buffer of EVERY rank (all-gather half),
+//     again followed by a flag.  The kernel ends on a rank when the finished tiles of all other owners have arrived,
+//     so its output is complete in local memory and the next kernel needs no collective.
+//   * Each rank visits the blocks it owns a few positions late (the host passes the visiting order), so the partials
+//     of its peers are normally there when it gets to them and the waits cost nothing.
+//
+// Peer memory is touched with plain global stores only (no TMA, no multicast); the operands of the MMA always come
+// from this GPU's own memory.  Ordering: data stores, __threadfence_system() by every storing thread, a CTA barrier,
+// then one st.release.sys of the flag; the consumer polls with ld.acquire.sys.  Every wait is bounded and reports
+// through the status word.  With world == 1 the same kernel is a plain persistent GEMM with a double-buffered
+// accumulator.
+#include "ptx.cuh"
+
+namespace xft {
+
+int make_tensor_map(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                    uint32_t esize);
+
+struct BulkArParams {
+  int world, rank;
+  __nv_bfloat16* part[8];     // rank r's partial area as mapped here: [world source slots][part_stride]
+  unsigned* flag_part[8];     // rank r's arrival flags: [owned tile][world]
+  __nv_bfloat16* out[8];      // rank r's output buffer [T, ldo] (out[rank] is this rank's own)
+  unsigned* flag_res[8];      // rank r's result flags: [tile]
+  int* epoch;                 // local: completed launches
+  int* done;                  // local: CTAs of the current launch that have finished their tiles
+  long long part_stride;      // elements per source slot of the partial area
+  long long wait_cycles;      // bound of every wait on a peer
+};
+
+struct PrefillParams {
+  int N, T, K;
+  __nv_bfloat16* out;
+  int ldo;
+  const float* bias;
+  const __nv_bfloat16* residual;
+  int ldr;
+  float res_scale;
+  int act;
+  int n_tiles, t_tiles, num_kb, stages;
+  int gn;                     // feature tiles per group: a group sweeps all token blocks before the next one starts
+  const int* order;           // optional: i-th visited token block (a permutation of 0..t_tiles-1)
+  int* status;
+  BulkArParams ar;
+};
+
+__device__ __forceinline__ float prefill_act(float x, int act) {
+  switch (act) {
+    case 1: return fmaxf(x, 0.f);
+    case 2: return x / (1.f + __expf(-x));
+    case 3: {
+      const float c = 0.7978845608028654f;
+      const float u = c * (x + 0.044715f * x * x * x);
+      return 0.5f * x * (1.f + tanhf(u));
+    }
+    default: return x;
+  }
+}
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bounded poll of a flag another GPU writes; false on time-out.
+__device__ __forceinline__ bool wait_flag(const unsigned* p, unsigned want, long long limit) {
+  if (ld_acquire_sys(p) == want) return true;
+  const long long t0 = clock64();
+  while (ld_acquire_sys(p) != want) {
+    if (clock64() - t0 > limit) return false;
+  }
+  return true;
+}
+
+// work item -> (feature tile, visited block index)
+__device__ __forceinline__ void decode_item(const PrefillParams& p, int item, int& nt, int& blk) {
+  const int per_group = p.gn * p.t_tiles;
+  const int g = item / per_group, r = item % per_group;
+  const int gn = min(p.gn, p.n_tiles - g * p.gn);
+  nt = g * p.gn + r % gn;
+  const int bi = r / gn;
+  blk = p.order ? p.order[bi] : bi;
+}
+
+// mbarrier wait that also gives up as soon as another role of this CTA has raised the abort flag
+__device__ __forceinline__ bool mbar_wait_or_abort(uint64_t* bar, uint32_t parity, int* status, int code,
+                                                   volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      if (status) atomicCAS(status, 0, code);
+      *abort_flag = 1;
+      return false;
+    }
+  }
+  return true;
+}
+
+constexpr int kPrefillMaxStages = 8;
+
+template <int BN>
+__global__ void __launch_bounds__(192, 1) gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmW,
+                                                              const __grid_constant__ CUtensorMap tmX,
+                                                              const PrefillParams p) {
+  constexpr int A_BYTES = 128 * 64 * 2;
+  constexpr int B_BYTES = BN * 64 * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = 2 * BN;                 // two accumulators of BN fp32 columns
+  constexpr uint32_t IDESC = umma_idesc(128, BN, 1, 1, 1);
+  static_assert(BN == 128 || BN == 256, "token tile of the prefill kernel");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t full_bar[kPrefillMaxStages], empty_bar[kPrefillMaxStages], tmem_full[2], tmem_empty[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int s_abort_mem, s_epoch, s_last;
+  volatile int* s_abort = &s_abort_mem;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int stages = p.stages;
+  const int total = p.n_tiles * p.t_tiles;
+  const int world = p.ar.world, rank = p.ar.rank;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 4);          // one arrival per epilogue warp
+    }
+    s_abort_mem = 0;
+    s_last = 0;
+    s_epoch = world > 1 ? *reinterpret_cast<volatile int*>(p.ar.epoch) + 1 : 0;
+    fence_barrier_init();
+    fence_proxy_async();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_s, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+  const unsigned epoch = (unsigned)s_epoch;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const uint64_t hint = kEvictNormal;          // both operands are re-read by other CTAs out of L2
+      int it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
+        int nt, blk;
+        decode_item(p, item, nt, blk);
+        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+          const int s = it % stages;
+          const uint32_t ph = (it / stages) & 1;
+          if (*s_abort || !mbar_wait_or_abort(&empty_bar[s], ph ^ 1, p.status, XFT_ERR_WAIT_EMPTY, s_abort)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          uint8_t* a = smem + s * STAGE_BYTES;
+          tma_load_2d(a, &tmW, &full_bar[s], kb * 64, nt * 128, hint);
+          tma_load_2d(a + A_BYTES, &tmX, &full_bar[s], kb * 64, blk * BN, hint);
+        }
+      }
+      if (!ok) {
+        // loads already issued still write into this CTA's shared memory: give them time to land before the CTA exits
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int it = 0, lt = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++lt) {
+        const int a = lt & 1;
+        const uint32_t aph = (lt >> 1) & 1;
+        if (*s_abort || !mbar_wait_or_abort(&tmem_empty[a], aph ^ 1, p.status, XFT_ERR_WAIT_TMEM, s_abort)) break;
+        tcgen05_fence_after();
+        const uint32_t acc = tmem_base + (uint32_t)(a * BN);
+        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+          const int s = it % stages;
+          const uint32_t ph = (it / stages) & 1;
+          if (!mbar_wait_or_abort(&full_bar[s], ph, p.status, XFT_ERR_WAIT_FULL, s_abort)) {
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+          const uint64_t adesc = umma_desc_k128(a_addr);
+          const uint64_t bdesc = umma_desc_k128(a_addr + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)          // 4 x (K = 16) per 64-wide k-block; +32 B = +2 in the address field
+            umma_bf16(acc, adesc + 2 * k, bdesc + 2 * k, IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+          tcgen05_commit(&empty_bar[s]);
+        }
+        if (ok) tcgen05_commit(&tmem_full[a]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (4 warps, one TMEM lane per thread)
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const int et = threadIdx.x - 64;
+    int lt = 0;
+    for (int item = blockIdx.x; item < total; item += gridDim.x, ++lt) {
+      int nt, blk;
+      decode_item(p, item, nt, blk);
+      const int a = lt & 1;
+      const uint32_t aph = (lt >> 1) & 1;
+      mbar_wait_or_abort(&tmem_full[a], aph, p.status, XFT_ERR_WAIT_TMEM, s_abort);
+      const int owner = world > 1 ? blk % world : 0;
+      const bool owned = world <= 1 || owner == rank;
+      const int own_idx = world > 1 ? blk / world : 0;          // index of this block among its owner's blocks
+      if (world > 1 && owned && et < world && et != rank && !*s_abort) {
+        // the partial of rank `et` for this tile must have landed in this rank's memory
+        const unsigned* f = p.ar.flag_part[rank] + ((size_t)own_idx * p.n_tiles + nt) * world + et;
+        if (!wait_flag(f, epoch, p.ar.wait_cycles)) {
+          if (p.status) atomicCAS(p.status, 0, XFT_ERR_WAIT_PEER);
+          *s_abort = 1;
+        }
+      }
+      named_bar_sync(1, 128);                  // every epilogue thread sees the same abort state from here on
+      if (*s_abort) break;
+      tcgen05_fence_after();
+      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + (uint32_t)(a * BN);
+      const int n = nt * 128 + row;
+      const bool n_ok = n < p.N;
+      const int t0 = blk * BN;
+      const float bias = (p.bias && n_ok) ? p.bias[n] : 0.f;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        uint32_t v[16];
+        tmem_ld16(taddr + c, v);
+        tmem_ld_wait();
+        if (c + 16 >= BN) {
+          // the accumulator is in registers: hand the TMEM buffer back to the MMA warp before the stores
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[a]);
+        }
+        if (!n_ok) continue;
+        if (!owned) {
+          __nv_bfloat16* dst = p.ar.part[owner] + (size_t)rank * p.ar.part_stride +
+                               ((size_t)own_idx * BN + c) * p.N + n;
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (t0 + c + j < p.T) dst[(size_t)j * p.N] = __float2bfloat16(__uint_as_float(v[j]));
+          continue;
+        }
+        float x[16];
+        if (world > 1) {
+          // sum in rank order; this rank's own term is its fp32 accumulator, the others arrive rounded to bf16
+#pragma unroll
+          for (int j = 0; j < 16; ++j) x[j] = 0.f;
+          for (int r = 0; r < world; ++r) {
+            if (r == rank) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) x[j] += __uint_as_float(v[j]);
+            } else {
+              const __nv_bfloat16* src = p.ar.part[rank] + (size_t)r * p.ar.part_stride +
+                                         ((size_t)own_idx * BN + c) * p.N + n;
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (t0 + c + j < p.T) x[j] += __bfloat162float(__ldcg(src + (size_t)j * p.N));
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) x[j] = __uint_as_float(v[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int t = t0 + c + j;
+          if (t < p.T) {
+            float y = prefill_act(x[j] + bias, p.act);
+            if (p.residual) y += p.res_scale * __bfloat162float(p.residual[(size_t)t * p.ldr + n]);
+            const __nv_bfloat16 yb = __float2bfloat16(y);
+            if (world > 1) {
+              for (int r = 0; r < world; ++r) p.ar.out[r][(size_t)t * p.ldo + n] = yb;
+            } else {
+              p.out[(size_t)t * p.ldo + n] = yb;
+            }
+          }
+        }
+      }
+      if (world > 1) {
+        __threadfence_system();               // this thread's stores to peer memory, before the flag below
+        named_bar_sync(1, 128);
+        if (!owned) {
+          if (et == 0)
+            st_release_sys(p.ar.flag_part[owner] + ((size_t)own_idx * p.n_tiles + nt) * world + rank, epoch);
+        } else if (et < world && et != rank) {
+          st_release_sys(p.ar.flag_res[et] + (size_t)blk * p.n_tiles + nt, epoch);
+        }
+      }
+    }
+    if (world > 1) {
+      // The launch is complete on this rank when the finished tiles of every other owner are here.  The CTA that
+      // finishes last checks them all, then opens the next epoch.
+      named_bar_sync(1, 128);
+      if (et == 0) {
+        __threadfence();
+        s_last = (atomicAdd(p.ar.done, 1) == (int)gridDim.x - 1);
+      }
+      named_bar_sync(1, 128);
+      if (s_last) {
+        bool ok = !*s_abort;
+        for (int idx = et; idx < total && ok; idx += 128) {
+          const int blk = idx / p.n_tiles;
+          if (blk % world == rank) continue;
+          if (!wait_flag(p.ar.flag_res[rank] + idx, epoch, p.ar.wait_cycles)) {
+            if (p.status) atomicCAS(p.status, 0, XFT_ERR_WAIT_PEER);
+            ok = false;
+          }
+        }
+        named_bar_sync(1, 128);
+        if (et == 0) {
+          *reinterpret_cast<volatile int*>(p.ar.done) = 0;
+          __threadfence();
+          atomicAdd(p.ar.epoch, 1);
+        }
+      }
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int BN>
+static int launch_prefill(const CUtensorMap& tmW, const CUtensorMap& tmX, PrefillParams& p, int num_ctas,
+                          cudaStream_t st) {
+  constexpr int STAGE_BYTES = 128 * 64 * 2 + BN * 64 * 2;
+  int stages = (220 * 1024) / STAGE_BYTES;
+  if (stages > kPrefillMaxStages) stages = kPrefillMaxStages;
+  p.stages = stages;
+  const size_t smem = (size_t)stages * STAGE_BYTES + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_prefill_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) !=
+        cudaSuccess)
+      return 3000 + (int)cudaGetLastError();
+    attr_set = true;
+  }
+  const int total = p.n_tiles * p.t_tiles;
+  const int grid = total < num_ctas ? total : num_ctas;
+  gemm_prefill_kernel<BN><<<grid, 192, smem, st>>>(tmW, tmX, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace xft
+
+using namespace xft;
+
+// Elements of one source slot of the partial area and the flag counts a launch of (T, N) needs at `world` ranks.
+extern "C" void xft_prefill_ar_sizes(int T, int N, int world, long long* part_elems_per_slot, long long* n_flag_part,
+                                     long long* n_flag_res) {
+  const int bn = T > 128 ? 256 : 128;
+  const long long t_tiles = (T + bn - 1) / bn, n_tiles = (N + 127) / 128;
+  const long long own = (t_tiles + world - 1) / world;
+  *part_elems_per_slot = own * bn * (long long)N;
+  *n_flag_part = own * n_tiles * world;
+  *n_flag_res = t_tiles * n_tiles;
+}
+
+// Y = act(X W^T (+ the same product of every other rank) + bias) + res_scale * residual, bf16.  ar == nullptr or
+// ar->world <= 1: plain persistent GEMM.  order: optional device array, the order in which token blocks are visited
+// (with ar it must hold the same multiset on every rank, see the file comment).  Returns 0, a negative argument
+// error, or a CUDA error code.
+extern "C" int xft_gemm_bf16_prefill(const void* X, int ldx, const void* W, int w_rows, int ldw, void* Y, int ldo, int T,
+                                     int N, int K, const float* bias, const void* residual, int ldr, float res_scale,
+                                     int act, const int* order, int* status, const BulkArParams* ar, int num_ctas,
+                                     cudaStream_t st) {
+  if (T <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K & 7) || (ldx & 7) || (ldw & 7)) return -2;
+  PrefillParams p{};
+  p.N = N; p.T = T; p.K = K; p.out = reinterpret_cast<__nv_bfloat16*>(Y); p.ldo = ldo; p.bias = bias;
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(residual); p.ldr = ldr; p.res_scale = res_scale; p.act = act;
+  p.order = order; p.status = status;
+  const int bn = T > 128 ? 256 : 128;
+  p.n_tiles = (N + 127) / 128;
+  p.t_tiles = (T + bn - 1) / bn;
+  p.num_kb = (K + 63) / 64;
+  p.gn = 16;
+  if (ar && ar->world > 1) {
+    if (ar->world > 8 || ar->rank < 0 || ar->rank >= ar->world) return -3;
+    long long need_part, nfp, nfr;
+    xft_prefill_ar_sizes(T, N, ar->world, &need_part, &nfp, &nfr);
+    if (ar->part_stride < need_part) return -4;
+    if (ar->out[ar->rank] != p.out) return -5;
+    p.ar = *ar;
+    p.gn = p.n_tiles;                 // block-major: all feature tiles of a token block are visited together
+  }
+  if (num_ctas <= 0) {
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    num_ctas = sms > 0 ? sms : 148;
+  }
+  CUtensorMap tmW, tmX;
+  int r = make_tensor_map(&tmW, W, (uint64_t)w_rows, (uint64_t)K, (uint64_t)ldw, 128, 2);
+  if (r) return 1000 - r;
+  r = make_tensor_map(&tmX, X, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, (uint32_t)bn, 2);
+  if (r) return 2000 - r;
+  return bn == 256 ? launch_prefill<256>(tmW, tmX, p, num_ctas, st) : launch_prefill<128>(tmW, tmX, p, num_ctas, st);
+}

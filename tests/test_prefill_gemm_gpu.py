@@ -1,0 +1,89 @@
+"""The persistent prefill GEMM (csrc/kernels/gemm_prefill_sm100.cu): on one GPU against the fp32 product, and on 2+
+GPUs with the all-reduce fused in.  The kernel is opt-in (XFT_GEMM_PERSISTENT / XFT_PREFILL_FUSED_AR) and so are these
+tests: set XFT_TEST_PREFILL_GEMM=1 to run them."""
+import ctypes as C
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(os.environ.get("XFT_TEST_PREFILL_GEMM") != "1",
+                                 reason="opt-in kernel: set XFT_TEST_PREFILL_GEMM=1")]
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _call(x, w, N, bias=None, act=None, residual=None, res_scale=1.0, order=None, ctas=0):
+    from xfastertransformer_b200.ops import native as N_
+    T, K = x.shape
+    out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+    ws = N_.Workspace.get(x.device)
+    lib = N_.lib()
+    lib.xft_gemm_bf16_prefill.restype = C.c_int
+    rc = lib.xft_gemm_bf16_prefill(N_._p(x), x.stride(0), N_._p(w), w.shape[0], w.stride(0), N_._p(out), N, T, N, K,
+                                   N_._p(bias), N_._p(residual), residual.stride(0) if residual is not None else 0,
+                                   C.c_float(res_scale), N_._ACT[act], N_._p(order), N_._p(ws.status), C.c_void_p(0),
+                                   ctas, N_._stream())
+    assert rc == 0, rc
+    torch.cuda.synchronize()
+    ws.check_status()
+    return out
+
+
+@pytest.mark.parametrize("T,N,K", [(100, 256, 128), (130, 640, 512), (300, 1280, 768), (1024, 2048, 1024),
+                                   (2500, 3968, 256), (8192, 1024, 512)])
+def test_persistent_gemm_matches_fp32(T, N, K):
+    g = torch.Generator().manual_seed(T + N)
+    x = (torch.randn(T, K, generator=g) * 0.5).bfloat16().cuda()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16().cuda()
+    bias = (torch.randn(N, generator=g) * 0.1).cuda()
+    res = torch.randn(T, N, generator=g).bfloat16().cuda()
+    want = torch.nn.functional.gelu(x.float() @ w.float().t() + bias, approximate="tanh") + 0.5 * res.float()
+    got = _call(x, w, N, bias, "gelu", res, 0.5)
+    err = (got.float() - want).abs()
+    assert bool((err <= 3e-2 + 2e-2 * want.abs()).all()), err.max().item()
+    # plain product, few CTAs (every CTA walks many tiles: both accumulators and all ring phases are reused) and a
+    # reversed visiting order
+    bn = 256 if T > 128 else 128
+    nb = (T + bn - 1) // bn
+    order = torch.arange(nb - 1, -1, -1, dtype=torch.int32, device="cuda")
+    got2 = _call(x, w, N, order=order, ctas=5)
+    want2 = x.float() @ w.float().t()
+    err2 = (got2.float() - want2).abs()
+    assert bool((err2 <= 3e-2 + 2e-2 * want2.abs()).all()), err2.max().item()
+    assert torch.equal(got2, _call(x, w, N))       # the schedule does not change the numbers
+
+
+def test_linear_takes_the_persistent_kernel_when_asked(monkeypatch):
+    from xfastertransformer_b200.ops import native as N_
+    from xfastertransformer_b200.utils.flags import Env
+    g = torch.Generator().manual_seed(3)
+    x = (torch.randn(600, 512, generator=g) * 0.5).bfloat16().cuda()
+    w = (torch.randn(768, 512, generator=g) * 0.05).bfloat16().cuda()
+    a = N_.gemm_bf16(x, w, 768)
+    monkeypatch.setenv("XFT_GEMM_PERSISTENT", "1")
+    Env.get().reload()
+    try:
+        b = N_.gemm_bf16(x, w, 768)
+    finally:
+        monkeypatch.delenv("XFT_GEMM_PERSISTENT")
+        Env.get().reload()
+    torch.cuda.synchronize()
+    assert (a.float() - b.float()).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_prefill_gemm_allreduce(world, tmp_path):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    out = str(tmp_path / "r.pt")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29700 + world), os.path.join(ROOT, "tests", "prefill_ar_worker.py"), out]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    got = torch.load(out)
+    assert got["calls"] >= 12 and got["worst"] < 6e-2

@@ -285,3 +285,58 @@ def test_progress_bar_draws_on_request_only(monkeypatch):
     monkeypatch.setenv("RANK", "0")
     list(ProgressBar.wrap(range(3), "x", stream=quiet))
     assert "3/3" in quiet.getvalue()
+
+
+def _simulate_fused_prefill(num_blocks, n_tiles, world, ctas, lag):
+    """Discrete simulation of the fused prefill GEMM + all-reduce schedule: every rank has `ctas` persistent CTAs that
+    take work items round-robin from the rank's visiting order; a tile of a block the rank does not own completes at
+    once (it only sends), a tile of an owned block completes when every other rank has completed the same tile.
+    Returns the number of sweeps until everything is done, or -1 if the system stops making progress."""
+    orders = [P.block_visit_order(num_blocks, world, r, lag) for r in range(world)]
+    items = [[(b, nt) for b in orders[r] for nt in range(n_tiles)] for r in range(world)]
+    queues = [[items[r][c::ctas] for c in range(ctas)] for r in range(world)]
+    heads = [[0] * ctas for _ in range(world)]
+    sent = [set() for _ in range(world)]           # (block, tile) whose partial rank r has delivered
+    sweeps = 0
+    while True:
+        progressed, pending = False, False
+        for r in range(world):
+            for c in range(ctas):
+                h = heads[r][c]
+                if h >= len(queues[r][c]):
+                    continue
+                pending = True
+                b, nt = queues[r][c][h]
+                if P.block_owner(b, world) != r:
+                    sent[r].add((b, nt))
+                elif not all((b, nt) in sent[s] for s in range(world) if s != r):
+                    continue                         # the owner waits for its peers' partial sums
+                heads[r][c] = h + 1
+                progressed = True
+        sweeps += 1
+        if not pending:
+            return sweeps
+        if not progressed:
+            return -1
+
+
+def test_fused_prefill_visit_order_is_a_live_permutation():
+    import random
+    for world in (2, 3, 4, 8):
+        for nb in (1, 2, 7, 32, 33):
+            for lag in (-1, 0, 1, 5):
+                for r in range(world):
+                    o = P.block_visit_order(nb, world, r, lag)
+                    assert sorted(o) == list(range(nb))
+                    eff = world if lag < 0 else lag
+                    for j in range(nb):
+                        if P.block_owner(j, world) == r:
+                            # an owned block comes after every foreign block up to j + lag (those it may wait for)
+                            later = [b for b in o[o.index(j) + 1:] if P.block_owner(b, world) != r]
+                            assert all(b > j + eff for b in later), (world, nb, lag, r, j)
+    rng = random.Random(0)
+    for _ in range(60):
+        world = rng.choice((2, 4, 8))
+        nb, nt, ctas = rng.randint(1, 40), rng.randint(1, 5), rng.randint(1, 9)
+        lag = rng.choice((-1, 0, 2, 8))
+        assert _simulate_fused_prefill(nb, nt, world, ctas, lag) > 0, (world, nb, nt, ctas, lag)

@@ -456,6 +456,10 @@ class Decoder:
             T = h.numel() // h.shape[-1]
             if peer.can_fuse(T, W.out_features, W.kind):
                 return peer.gemm_ar(h, W, bias, None, residual, res_scale)
+            if peer.can_fuse_bulk(T, W.out_features, h.shape[-1], W.kind):      # prefill sizes, opt-in
+                y = peer.gemm_ar_bulk(h, W, bias, None, residual, res_scale)
+                if y is not None:
+                    return y
         lead = self.tpr == 0
         y = ops.linear(h, W, bias if lead else None, None, residual if lead else None, res_scale)
         if self.tp > 1:

@@ -17,6 +17,7 @@ replays stay in step without host involvement.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import List, Optional
 
 import torch
@@ -36,6 +37,26 @@ class ArParams(C.Structure):
                 ("done", C.c_void_p), ("cap", C.c_longlong), ("wait_cycles", C.c_longlong), ("status", C.c_void_p)]
 
 
+class _RawCuda:
+    """__cuda_array_interface__ holder: lets torch view a range of the symmetric buffer without copying."""
+
+    def __init__(self, ptr: int, shape, owner):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": "<i2", "data": (ptr, False), "version": 3,
+                                         "strides": None}
+        self._owner = owner
+
+
+def _view_bf16(ptr: int, rows: int, cols: int, device, owner) -> torch.Tensor:
+    return torch.as_tensor(_RawCuda(ptr, (rows, cols), owner), device=device).view(torch.bfloat16)
+
+
+class BulkArParams(C.Structure):
+    """Mirror of the struct of the same name in csrc/kernels/gemm_prefill_sm100.cu."""
+    _fields_ = [("world", C.c_int), ("rank", C.c_int), ("part", C.c_void_p * 8), ("flag_part", C.c_void_p * 8),
+                ("out", C.c_void_p * 8), ("flag_res", C.c_void_p * 8), ("epoch", C.c_void_p), ("done", C.c_void_p),
+                ("part_stride", C.c_longlong), ("wait_cycles", C.c_longlong)]
+
+
 class PeerComm:
     T_CAP = 64
     MAX_TILES = 1024
@@ -47,12 +68,29 @@ class PeerComm:
             raise ValueError("PeerComm supports 2..8 ranks")
         lib = N.lib()
         for fn in ("xft_comm_alloc", "xft_comm_free", "xft_comm_ipc_handle", "xft_comm_ipc_open", "xft_comm_ipc_close",
-                   "xft_comm_handle_bytes", "xft_gemm_bf16_ar", "xft_allreduce_oneshot"):
+                   "xft_comm_handle_bytes", "xft_gemm_bf16_ar", "xft_allreduce_oneshot", "xft_gemm_bf16_prefill"):
             getattr(lib, fn).restype = C.c_int
         self.lib = lib
         self.slot = self.T_CAP * n_max                           # {value, epoch} words per source slot
         self.recv_bytes = 2 * self.world * self.slot * 8
         nbytes = self.recv_bytes + 2 * self.slot * 8           # + result area of the two-shot mode
+        # Optional area of the fused prefill GEMM + all-reduce (XFT_PREFILL_FUSED_AR=1): partial sums from every rank
+        # for the token blocks this rank owns, two output buffers that the owners of the other blocks write into
+        # (consecutive launches alternate between them, so a launch never overwrites the residual it reads), flags.
+        self.bulk = None
+        self.bulk_tokens = int(os.environ.get("XFT_MAX_BATCH_TOKENS", "8192")) \
+            if os.environ.get("XFT_PREFILL_FUSED_AR", "0") == "1" else 0
+        if self.bulk_tokens > 0:
+            pe, nfp, nfr = C.c_longlong(), C.c_longlong(), C.c_longlong()
+            lib.xft_prefill_ar_sizes(self.bulk_tokens, n_max, self.world, C.byref(pe), C.byref(nfp), C.byref(nfr))
+            al = lambda v: (v + 255) // 256 * 256
+            self._b_part_stride = pe.value
+            self._b_off_part = al(nbytes)
+            self._b_off_out = [al(self._b_off_part + self.world * pe.value * 2)]
+            self._b_off_out.append(al(self._b_off_out[0] + self.bulk_tokens * n_max * 2))
+            self._b_off_fp = al(self._b_off_out[1] + self.bulk_tokens * n_max * 2)
+            self._b_off_fr = al(self._b_off_fp + nfp.value * 4)
+            nbytes = al(self._b_off_fr + nfr.value * 4)
         self.nbytes = nbytes
         base = C.c_void_p()
         N._check(lib.xft_comm_alloc(C.c_size_t(nbytes), C.byref(base)), "comm_alloc")
@@ -93,7 +131,6 @@ class PeerComm:
         # Reduce-scatter + all-gather inside the epilogue (two-shot) trades one more NVLink hop for less traffic: it
         # pays off from 4 ranks on and more than 16 tokens; up to 16 tokens the one-shot push wins at every world
         # size measured (8 ranks, 70B decode: 10.3 vs 11.1 ms per step).  XFT_AR_TWO_SHOT=0/1 overrides.
-        import os
         ts = os.environ.get("XFT_AR_TWO_SHOT")
         self._two_shot_env = int(ts) if ts is not None else None
         self.gp.two_shot = 0
@@ -102,6 +139,27 @@ class PeerComm:
         self.ap.cap = self.slot
         self.ap.status = N.Workspace.get(ctx.device).status.data_ptr()
         self.fused_calls = 0
+        if self.bulk_tokens > 0:
+            self.bulk_counters = torch.zeros(4, dtype=torch.int32, device=ctx.device)   # [epoch, done]
+            self.bulk = []
+            for which in range(2):
+                bp = BulkArParams()
+                bp.world, bp.rank = self.world, self.rank
+                for r in range(self.world):
+                    b = self.peer_base[r]
+                    bp.part[r] = b + self._b_off_part
+                    bp.out[r] = b + self._b_off_out[which]
+                    bp.flag_part[r] = b + self._b_off_fp
+                    bp.flag_res[r] = b + self._b_off_fr
+                bp.epoch = self.bulk_counters.data_ptr()
+                bp.done = self.bulk_counters.data_ptr() + 4
+                bp.part_stride = self._b_part_stride
+                bp.wait_cycles = self.wait_cycles
+                self.bulk.append(bp)
+            self._bulk_next = 0
+            self._bulk_orders = {}
+            self.n_max = n_max
+            self.bulk_calls = 0
         dist.barrier(group=ctx.ctrl_group)
 
     # ------------------------------------------------------------------------------------
@@ -132,6 +190,57 @@ class PeerComm:
         N._check(rc, "gemm_bf16_ar")
         ws.launches += 1
         self.fused_calls += 1
+        return out.view(*x.shape[:-1], n)
+
+    # ------------------------------------------------------------------------------------
+    def can_fuse_bulk(self, T: int, n: int, K: int, kind: str) -> bool:
+        return (self.bulk is not None and kind == "bf16" and self.T_CAP < T <= self.bulk_tokens and n <= self.n_max
+                and K % 8 == 0)
+
+    def _bulk_order(self, T: int, device) -> torch.Tensor:
+        from .partition import block_visit_order
+        bn = 256 if T > 128 else 128
+        nb = (T + bn - 1) // bn
+        t = self._bulk_orders.get(nb)
+        if t is None:
+            t = torch.tensor(block_visit_order(nb, self.world, self.rank), dtype=torch.int32, device=device)
+            self._bulk_orders[nb] = t
+        return t
+
+    def gemm_ar_bulk(self, x, W, bias=None, act=None, residual=None, res_scale=1.0):
+        """Prefill sizes: Y = act(sum over ranks of x_r @ W_r^T + bias) + res_scale * residual on every rank, as one
+        persistent kernel that reduce-scatters its tiles into the owners' memory and all-gathers the finished tiles
+        (csrc/kernels/gemm_prefill_sm100.cu).  The result is a view of one of two symmetric buffers and stays valid
+        until the second next call."""
+        x2, ldx = N._rows2d(x)
+        T, K = x2.shape
+        n = W.out_features
+        which = self._bulk_next
+        span = self.bulk_tokens * self.n_max * 2
+
+        def inside(t, w):
+            lo = self.base + self._b_off_out[w]
+            return t is not None and lo <= t.data_ptr() < lo + span
+        if inside(residual, which) or inside(x, which):
+            which ^= 1                 # never write the buffer this call still reads
+            if inside(residual, which) or inside(x, which):
+                return None            # both in use: the caller takes the unfused path
+        self._bulk_next = which ^ 1
+        bp = self.bulk[which]
+        out_ptr = self.base + self._b_off_out[which]
+        r2, ldr = (None, 0)
+        if residual is not None:
+            r2 = residual.reshape(-1, residual.shape[-1])
+            ldr = r2.stride(0)
+        ws = N.Workspace.get(x.device)
+        order = self._bulk_order(T, x.device)
+        rc = self.lib.xft_gemm_bf16_prefill(N._p(x2), ldx, N._p(W.w), W.w.shape[0], W.w.stride(0), C.c_void_p(out_ptr), n,
+                                            T, n, K, N._p(bias), N._p(r2), ldr, C.c_float(res_scale), N._ACT[act],
+                                            N._p(order), N._p(ws.status), C.byref(bp), 0, N._stream())
+        N._check(rc, "gemm_bf16_prefill(all-reduce)")
+        ws.launches += 1
+        self.bulk_calls += 1
+        out = _view_bf16(out_ptr, T, n, x.device, self)
         return out.view(*x.shape[:-1], n)
 
     def _collective(self, t: torch.Tensor, out: torch.Tensor, add_f32, gather: int) -> torch.Tensor:

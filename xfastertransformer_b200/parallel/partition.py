@@ -13,7 +13,7 @@ tensor exactly where the reference would (``src/utils/split_util.h:8-99``):
 """
 from __future__ import annotations
 
-from typing import Tuple
+from typing import List, Tuple
 
 
 def task_range(n: int, splits: int, idx: int) -> Tuple[int, int]:
@@ -93,3 +93,28 @@ def expert_owner(expert_id: int, num_experts: int, ep_size: int) -> int:
     if expert_id < cut:
         return expert_id // (base + 1)
     return rem + (expert_id - cut) // max(base, 1)
+
+
+def block_owner(block: int, world: int) -> int:
+    """Rank that reduces token block `block` in the fused prefill GEMM + all-reduce (round-robin)."""
+    return block % world
+
+
+def block_visit_order(num_blocks: int, world: int, rank: int, lag: int = -1) -> List[int]:
+    """Order in which one rank's persistent CTAs visit the token blocks of a fused prefill GEMM + all-reduce.
+
+    All ranks walk the blocks in index order, but a rank reaches a block it OWNS `lag` steps late (default: one round
+    of `world` blocks): by then the other ranks, which pass that block at its natural position, have normally
+    delivered their partial sums, so the owner's reduction does not wait.  Every rank's list is a permutation of
+    ``range(num_blocks)``.  Liveness: give block j the key j on the ranks that do not own it and j + lag + 1/2 on its
+    owner; each rank visits in key order, a wait at key j + lag + 1/2 depends on work at key j, and a CTA that is stuck
+    earlier in its list is stuck at a smaller key, so every chain of waits runs down the keys and ends."""
+    if lag < 0:
+        lag = world
+    out: List[int] = []
+    for k in range(num_blocks + lag):
+        if k < num_blocks and block_owner(k, world) != rank:
+            out.append(k)
+        if k >= lag and block_owner(k - lag, world) == rank:
+            out.append(k - lag)
+    return out
