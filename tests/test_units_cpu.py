@@ -340,3 +340,77 @@ def test_fused_prefill_visit_order_is_a_live_permutation():
         nb, nt, ctas = rng.randint(1, 40), rng.randint(1, 5), rng.randint(1, 9)
         lag = rng.choice((-1, 0, 2, 8))
         assert _simulate_fused_prefill(nb, nt, world, ctas, lag) > 0, (world, nb, nt, ctas, lag)
+
+
+@pytest.mark.parametrize("world,T,N", [(2, 300, 256), (4, 1000, 1000), (8, 2048, 384), (3, 130, 128)])
+def test_fused_prefill_allreduce_addressing_emulated(world, T, N):
+    """The addressing of the fused prefill GEMM + all-reduce, replayed on the CPU with the kernel's own formulas
+    (csrc/kernels/gemm_prefill_sm100.cu): partial tiles go to slot `rank` of the owner's partial area at row
+    (block / world) * BN + t, flags live at [(block / world) * n_tiles + tile][source], finished tiles are stored into
+    every rank's output and flagged at [block * n_tiles + tile].  Every offset must stay inside the sizes that
+    xft_prefill_ar_sizes reports, no two writers may touch the same element, and all ranks end with the same sum."""
+    import ctypes as C
+    from xfastertransformer_b200.ops import native as N_
+    lib = C.CDLL(N_.lib_path())
+    pe, nfp, nfr = C.c_longlong(), C.c_longlong(), C.c_longlong()
+    lib.xft_prefill_ar_sizes(T, N, world, C.byref(pe), C.byref(nfp), C.byref(nfr))
+    pe, nfp, nfr = pe.value, nfp.value, nfr.value
+    BN = 256 if T > 128 else 128
+    t_tiles, n_tiles = (T + BN - 1) // BN, (N + 127) // 128
+    g = torch.Generator().manual_seed(world * 1000 + T)
+    partial = [torch.randn(T, N, generator=g) for _ in range(world)]       # each rank's local product
+    part = [torch.zeros(world * pe) for _ in range(world)]
+    part_writes = [torch.zeros(world * pe, dtype=torch.int32) for _ in range(world)]
+    flag_part = [torch.zeros(nfp, dtype=torch.int64) for _ in range(world)]
+    flag_res = [torch.zeros(nfr, dtype=torch.int64) for _ in range(world)]
+    out = [torch.full((T * N,), float("nan")) for _ in range(world)]
+    epoch = 1
+    orders = [P.block_visit_order(t_tiles, world, r) for r in range(world)]
+    todo = [[(b, nt) for b in orders[r] for nt in range(n_tiles)] for r in range(world)]
+    head = [0] * world
+    while any(head[r] < len(todo[r]) for r in range(world)):
+        moved = False
+        for r in range(world):
+            if head[r] >= len(todo[r]):
+                continue
+            blk, nt = todo[r][head[r]]
+            owner, own_idx = blk % world, blk // world
+            t0, n0 = blk * BN, nt * 128
+            rows = torch.arange(t0, min(t0 + BN, T))
+            cols = torch.arange(n0, min(n0 + 128, N))
+            if owner != r:
+                off = r * pe + ((own_idx * BN + (rows - t0))[:, None] * N + cols[None, :]).reshape(-1)
+                assert int(off.max()) < (r + 1) * pe and int(off.min()) >= r * pe      # stays inside its slot
+                part[owner][off] = partial[r][rows][:, cols].reshape(-1)
+                part_writes[owner][off] += 1
+                f = (own_idx * n_tiles + nt) * world + r
+                assert f < nfp
+                flag_part[owner][f] = epoch
+            else:
+                fl = [(own_idx * n_tiles + nt) * world + s for s in range(world) if s != r]
+                if not all(int(flag_part[r][f]) == epoch for f in fl):
+                    continue                                     # peers have not delivered yet: wait
+                acc = torch.zeros(len(rows), len(cols))
+                for s in range(world):                           # rank order
+                    if s == r:
+                        acc += partial[r][rows][:, cols]
+                    else:
+                        off = s * pe + ((own_idx * BN + (rows - t0))[:, None] * N + cols[None, :]).reshape(-1)
+                        acc += part[r][off].view(len(rows), len(cols))
+                dst = (rows[:, None] * N + cols[None, :]).reshape(-1)
+                for s in range(world):
+                    assert bool(torch.isnan(out[s][dst]).all())  # nobody wrote these before
+                    out[s][dst] = acc.reshape(-1)
+                    if s != r:
+                        assert blk * n_tiles + nt < nfr
+                        flag_res[s][blk * n_tiles + nt] = epoch
+            head[r] += 1
+            moved = True
+        assert moved, "schedule stopped making progress"
+    want = sum(partial).reshape(-1)
+    for r in range(world):
+        assert int(part_writes[r].max()) <= 1                  # no element of the partial area has two writers
+        assert torch.allclose(out[r], want, atol=1e-5)
+        for blk in range(t_tiles):
+            for nt in range(n_tiles):
+                assert (int(flag_res[r][blk * n_tiles + nt]) == epoch) == (blk % world != r)
