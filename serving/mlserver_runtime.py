@@ -11,7 +11,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 try:                                       # pragma: no cover - optional dependency
     from mlserver import MLModel
     from mlserver.codecs import NumpyCodec
-    from mlserver.types import InferenceRequest, InferenceResponse
+    from mlserver.types import InferenceResponse
     _HAVE = True
 except Exception:                          # MLServer not installed: keep the runtime usable as a library
     MLModel = object

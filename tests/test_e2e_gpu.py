@@ -1,6 +1,5 @@
 """Tiny-Llama end to end on one B200: the CUDA path (tcgen05 GEMMs, paged attention, CUDA-graph decode)
 against the eager fp32 oracle."""
-import os
 
 import pytest
 import torch

@@ -5,7 +5,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 from xfastertransformer_b200.ops import reference as R
-from xfastertransformer_b200.runtime.loader import cat_linear, make_linear
+from xfastertransformer_b200.runtime.loader import make_linear
 
 
 @pytest.mark.parametrize("kind,E,k", [("mixtral", 8, 2), ("softmax_topk", 128, 8), ("deepseek", 256, 8), ("deepseek", 64, 6)])

@@ -45,8 +45,6 @@ def lib():
         if not os.path.exists(p):
             raise KernelError(f"{p} is missing: run `python csrc/build.py` (or __graft_entry__.build())")
         _LIB = C.CDLL(p)
-        for name in dir(_LIB):
-            pass
         for fn in ("xft_gemm_bf16", "xft_embedding", "xft_rmsnorm", "xft_layernorm", "xft_gated_act",
                    "xft_qkv_rope_cache", "xft_rope", "xft_latent_write", "xft_argmax", "xft_paged_attention"):
             getattr(_LIB, fn).restype = C.c_int

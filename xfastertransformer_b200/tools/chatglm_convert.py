@@ -3,7 +3,6 @@ q/k/v), ``chatglm2_convert.py`` / ``chatglm3_convert.py`` / ``chatglm4_convert.p
 SwiGLU ``dense_h_to_4h`` = gate‖up, half-dim interleaved RoPE, ``rope_ratio``)."""
 from __future__ import annotations
 
-import torch
 
 from .convert import BaseModelConvert
 

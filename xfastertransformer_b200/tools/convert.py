@@ -17,7 +17,7 @@ import configparser
 import glob
 import json
 import os
-from typing import Callable, Dict, Iterator, List, Optional
+from typing import Callable, Dict, Iterator, Optional
 
 import torch
 

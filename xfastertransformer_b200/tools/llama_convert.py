@@ -8,7 +8,6 @@ import configparser
 import os
 
 import numpy as np
-import torch
 
 from .convert import BaseModelConvert, StateDict
 

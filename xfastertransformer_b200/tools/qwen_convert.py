@@ -2,7 +2,6 @@
 ``qwen2_convert.py`` (Llama layout + QKV bias), ``qwen3_convert.py`` (per-head q/k norm; dense and MoE)."""
 from __future__ import annotations
 
-import torch
 
 from .convert import BaseModelConvert
 from .llama_convert import LlamaConvert
