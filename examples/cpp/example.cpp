@@ -1,8 +1,13 @@
 // Command-line generation with the C++ API (reference: examples/cpp/example.cpp:352-545; token ids in, token ids
 // out — tokenisation is left to the caller, as in the reference's `--input_ids` style use).
 //
-//   example -m <model dir> [-d bf16] [--kv_cache_dtype fp16|int8] [-i "1 2 3 4"] [-b batch] [-o out_len]
-//           [--loop n] [--num_beams n] [--topK k] [--topP p] [--temperature t] [--repetPen r] [--do_sample] [--no_stream]
+//   example -m <model dir> [-t <ignored>] [-d bf16] [--kv_cache_dtype fp16|int8] [-i "1 2 3 4"] [-l input_len]
+//           [-o out_len] [--prefix_len n] [-n num_beams] [-b batch] [--loop n] [--topK k] [--topP p]
+//           [--temperature t] [--repetPen r] [--do_sample] [--no_stream]
+// Same flag names as the reference.  -l pads the prompt to `input_len` tokens by repeating its third token (the
+// reference's way of making a long prompt for timing); --prefix_len shares the first n prompt tokens between the rows
+// of the batch through Model::setPrefix (whole 64-token blocks).  -t is accepted for command-line compatibility:
+// the prompt is given as ids.
 // Prints the generated ids, first-token latency and average next-token latency (the reference's metrics).
 #include <chrono>
 #include <cstdio>
@@ -17,7 +22,7 @@
 
 int main(int argc, char** argv) {
   std::string model, dtype = "bf16", kv = "fp16", input = "1 15043 29892 920 526 366 29973";
-  int batch = 1, outLen = 32, loop = 1, topK = 50, numBeams = 1;
+  int batch = 1, outLen = 32, loop = 1, topK = 50, numBeams = 1, inputLen = -1, prefixLen = 0;
   float topP = 1.0f, temp = 1.0f, rep = 1.0f;
   bool sample = false, stream = true;
   for (int i = 1; i < argc; ++i) {
@@ -29,9 +34,12 @@ int main(int argc, char** argv) {
     else if (a == "-i" || a == "--input_ids") input = next();
     else if (a == "-b" || a == "--batch_size") batch = std::atoi(next().c_str());
     else if (a == "-o" || a == "--output_len") outLen = std::atoi(next().c_str());
-    else if (a == "-l" || a == "--loop") loop = std::atoi(next().c_str());
+    else if (a == "--loop") loop = std::atoi(next().c_str());
+    else if (a == "-l" || a == "--input_len") inputLen = std::atoi(next().c_str());
+    else if (a == "--prefix_len") prefixLen = std::atoi(next().c_str());
+    else if (a == "-t" || a == "--token") (void)next();
     else if (a == "--topK") topK = std::atoi(next().c_str());
-    else if (a == "--num_beams") numBeams = std::atoi(next().c_str());
+    else if (a == "-n" || a == "--num_beams") numBeams = std::atoi(next().c_str());
     else if (a == "--topP") topP = (float)std::atof(next().c_str());
     else if (a == "--temperature") temp = (float)std::atof(next().c_str());
     else if (a == "--repetPen") rep = (float)std::atof(next().c_str());
@@ -42,9 +50,21 @@ int main(int argc, char** argv) {
   if (model.empty()) { std::fprintf(stderr, "usage: example -m <model dir> [options]\n"); return 2; }
   std::vector<int32_t> prompt;
   { std::istringstream is(input); int v; while (is >> v) prompt.push_back(v); }
+  if (prompt.empty()) { std::fprintf(stderr, "-i takes token ids separated by spaces\n"); return 2; }
+  if (inputLen > (int)prompt.size()) {
+    const size_t at = prompt.size() > 2 ? 2 : prompt.size() - 1;
+    prompt.insert(prompt.begin() + at, inputLen - prompt.size(), prompt[at]);
+  } else if (inputLen > 0) {
+    std::fprintf(stderr, "[Warning] input_len %d is not longer than the prompt, using %zu tokens\n", inputLen, prompt.size());
+  }
+  if (prefixLen < 0 || prefixLen >= (int)prompt.size()) { std::fprintf(stderr, "--prefix_len must be below the prompt length\n"); return 2; }
   try {
     xft::AutoModel m(model, dtype == "fp16" ? xft::DataType::fp16 : xft::DataType::bf16,
                      kv == "int8" ? xft::DataType::int8 : xft::DataType::fp16);
+    if (prefixLen > 0) {
+      std::vector<int32_t> prefix(prompt.begin(), prompt.begin() + prefixLen);
+      m.setPrefix(prefix);
+    }
     for (int it = 0; it < loop; ++it) {
       std::vector<int32_t> ids;
       for (int b = 0; b < batch; ++b) ids.insert(ids.end(), prompt.begin(), prompt.end());

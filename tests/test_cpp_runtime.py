@@ -277,3 +277,22 @@ def test_native_selftest_under_sanitizers(tmp_path):
                        env=dict(os.environ, ASAN_OPTIONS="detect_leaks=1", UBSAN_OPTIONS="print_stacktrace=1"))
     assert r.returncode == 0, r.stdout + r.stderr
     assert "0 failed" in r.stdout and "runtime error" not in r.stderr and "AddressSanitizer" not in r.stderr
+
+
+def test_example_cli_flags_follow_the_reference(core):
+    """examples/cpp/example.cpp takes the reference's flag names (-m -t -i -d --kv_cache_dtype -l -o --prefix_len -n -b
+    --loop --topK --temperature --topP --repetPen --no_stream --do_sample); argument errors are reported before any
+    device work."""
+    import subprocess
+    exe = os.path.join(os.path.dirname(LIB), "xft_example")
+    if not os.path.exists(exe):
+        pytest.skip("example not built")
+    run = lambda *a: subprocess.run([exe, *a], capture_output=True, text=True, timeout=60)
+    assert run().returncode == 2
+    assert run("-m", "/nonexistent", "--bogus").returncode == 2
+    r = run("-m", "/nonexistent", "-t", "tok", "-i", "1 2 3", "-d", "bf16", "--kv_cache_dtype", "int8", "-l", "2", "-o", "4",
+            "--prefix_len", "0", "-n", "2", "-b", "2", "--loop", "1", "--topK", "4", "--temperature", "0.7", "--topP", "0.9",
+            "--repetPen", "1.1", "--no_stream", "--do_sample")
+    assert r.returncode == 1 and "config.ini" in r.stderr and "input_len 2 is not longer" in r.stderr
+    assert run("-m", "/nonexistent", "-i", "hello").returncode == 2           # the prompt is given as ids
+    assert run("-m", "/nonexistent", "-i", "1 2 3", "--prefix_len", "3").returncode == 2
