@@ -40,8 +40,19 @@ def test_grpc_and_http_serving(tiny):
         assert torch.equal(torch.tensor(r["Ids"]).view(2, -1), want)
         steps = list(c.predict_stream([[5, 6, 7, 8]], max_length=10))
         assert [s["Ids"][0] for s in steps] == want[0, 4:].tolist()
+        # the command-line client (serving/client.py): health poll, unary and streaming calls on token ids
+        import contextlib
+        import io
+        from serving import client as cli
+        for extra in ([], ["--stream"]):
+            buf = io.StringIO()
+            with contextlib.redirect_stdout(buf):
+                assert cli.main(["--port", str(port), "--ids", "5 6 7 8", "--max_length", "10", *extra]) == 0
+            assert [int(t) for t in buf.getvalue().split()] == want[0, 4:].tolist()
     finally:
         srv.stop(0)
+    from serving import client as cli
+    assert cli.main(["--port", "1", "--ids", "5", "--health_timeout", "0.5"]) == 1      # nobody serves there
     httpd, hport = serve_http(model, 0)
     try:
         req = urllib.request.Request(f"http://127.0.0.1:{hport}/", data=json.dumps(
