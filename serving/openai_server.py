@@ -33,19 +33,30 @@ sys.path.insert(0, ROOT)
 
 class Request:
     def __init__(self, prompt_ids: List[int], max_tokens: int, temperature: float, top_p: float, top_k: int,
-                 stop_ids: List[int], seed: Optional[int]):
+                 stop_ids: List[int], seed: Optional[int], repetition_penalty: float = 1.0,
+                 logprobs: Optional[int] = None, stop_fn=None):
         self.id = uuid.uuid4().hex[:24]
         self.prompt_ids = prompt_ids
         self.max_tokens = max(1, max_tokens)
         self.temperature, self.top_p, self.top_k = temperature, top_p, top_k
         self.stop_ids = set(stop_ids)
         self.seed = seed
+        self.repetition_penalty = float(repetition_penalty)
+        self.logprobs = logprobs                      # None, or how many alternatives to report per position (0 = chosen only)
+        self.stop_fn = stop_fn                        # callable(generated ids) -> bool: a stop string has appeared
+        self.token_logprobs: List[float] = []
+        self.top_logprobs: List[Dict[int, float]] = []
         self.out: "queue.Queue" = queue.Queue()       # ints, then None (or an Exception) at the end
         self.generated: List[int] = []
         self.finish_reason = "length"
         self.t_arrive = time.perf_counter()
         self.t_first: Optional[float] = None
         self.t_last: Optional[float] = None
+
+    @property
+    def greedy_on_device(self) -> bool:
+        """True when the token can be picked on the device: arg-max, no penalty, no log-probabilities wanted."""
+        return self.temperature <= 1e-5 and self.repetition_penalty == 1.0 and self.logprobs is None
 
 
 class Scheduler(threading.Thread):
@@ -110,9 +121,27 @@ class Scheduler(threading.Thread):
     # -- token selection on the host (one row of fp32 logits) --------------------------------
     def _select(self, req: Request, row) -> int:
         torch = self.torch
+        row = row.float()
+        if req.repetition_penalty != 1.0:
+            seen = torch.tensor(sorted(set(req.prompt_ids) | set(req.generated)), dtype=torch.long, device=row.device)
+            seen = seen[seen < row.numel()]
+            v = row[seen]
+            row = row.clone()
+            row[seen] = torch.where(v < 0, v * req.repetition_penalty, v / req.repetition_penalty)
+        tok = self._pick(req, row)
+        if req.logprobs is not None:
+            lp = torch.log_softmax(row, -1)
+            req.token_logprobs.append(float(lp[tok]))
+            k = min(int(req.logprobs), 20)
+            top = torch.topk(lp, k) if k > 0 else None
+            req.top_logprobs.append({int(i): float(x) for x, i in zip(top.values, top.indices)} if top is not None else {})
+        return tok
+
+    def _pick(self, req: Request, row) -> int:
+        torch = self.torch
         if req.temperature <= 1e-5:
             return int(row.argmax())
-        logits = row.float() / req.temperature
+        logits = row / req.temperature
         if req.top_k > 0 and req.top_k < logits.numel():
             kth = torch.topk(logits, req.top_k).values[-1]
             logits = torch.where(logits < kth, torch.full_like(logits, float("-inf")), logits)
@@ -151,7 +180,7 @@ class Scheduler(threading.Thread):
         req.generated.append(tok)
         self.metrics["generated_tokens"] += 1
         req.out.put(tok)
-        if tok == self.eos_id or tok in req.stop_ids:
+        if tok == self.eos_id or tok in req.stop_ids or (req.stop_fn is not None and req.stop_fn(req.generated)):
             req.finish_reason = "stop"
             return True
         return len(req.generated) >= req.max_tokens
@@ -198,7 +227,7 @@ class Scheduler(threading.Thread):
                         # one forward for the new prompts AND the running sequences: decoding does not pause for prefill
                         sids_run = list(self.running)
                         reqs_run = [self.running[s] for s in sids_run]
-                        greedy = all(r.temperature <= 1e-5 for r in ok + reqs_run)
+                        greedy = all(r.greedy_on_device for r in ok + reqs_run)
                         sids_new = self.model.set_input_cb([r.prompt_ids for r in ok], None,
                                                            [len(r.prompt_ids) + r.max_tokens + 1 for r in ok], greedy=greedy,
                                                            hold=True)
@@ -216,7 +245,7 @@ class Scheduler(threading.Thread):
                         self.metrics["mixed_steps"] += 1
                         continue
                     if ok:
-                        greedy = all(r.temperature <= 1e-5 for r in ok)
+                        greedy = all(r.greedy_on_device for r in ok)
                         sids = self.model.set_input_cb([r.prompt_ids for r in ok], None,
                                                        [len(r.prompt_ids) + r.max_tokens + 1 for r in ok], greedy=greedy)
                         picks = self._forward(ok, greedy)
@@ -231,7 +260,7 @@ class Scheduler(threading.Thread):
                 if self.running:
                     sids = list(self.running)
                     reqs = [self.running[s] for s in sids]
-                    greedy = all(r.temperature <= 1e-5 for r in reqs)
+                    greedy = all(r.greedy_on_device for r in reqs)
                     self.model.set_input_cb([r.generated[-1] for r in reqs], sids, None, greedy=greedy)
                     picks = self._forward(reqs, greedy)
                     done = [s for s, r, tok in zip(sids, reqs, picks) if self._emit(r, tok)]
@@ -319,62 +348,126 @@ def make_handler(sched: Scheduler, tok: Tokenizer, model_name: str):
                 return self.wfile.write(body)
             self._json(404, {"error": {"message": f"no route {self.path}"}})
 
+        def _prompts(self, q, chat: bool) -> List[List[int]]:
+            """One id list per prompt: a string, a list of strings, a list of ids or a list of id lists."""
+            if chat:
+                return [tok.chat(q.get("messages", []))]
+            p = q.get("prompt", "")
+            if isinstance(p, list) and p and isinstance(p[0], (str, list)):
+                return [tok.encode(x) for x in p]
+            return [tok.encode(p)]
+
         def do_POST(self):
             try:
                 q = json.loads(self.rfile.read(int(self.headers.get("Content-Length", 0))) or b"{}")
                 chat = self.path == "/v1/chat/completions"
                 if not chat and self.path != "/v1/completions":
                     return self._json(404, {"error": {"message": f"no route {self.path}"}})
-                ids = tok.chat(q.get("messages", [])) if chat else tok.encode(q.get("prompt", ""))
+                prompts = self._prompts(q, chat)
+                n = max(1, int(q.get("n", 1)))
                 stop_ids = [int(s) for s in q.get("stop_token_ids", [])]
-                req = Request(ids, int(q.get("max_tokens", 16)), float(q.get("temperature", 1.0 if q.get("do_sample") else 0.0)),
-                              float(q.get("top_p", 1.0)), int(q.get("top_k", 0)), stop_ids, q.get("seed"))
+                stops = q.get("stop") or []
+                stops = [stops] if isinstance(stops, str) else [str(x) for x in stops if x]
+                lp = q.get("logprobs")
+                if chat:                  # chat API: logprobs is a flag, top_logprobs the count
+                    lp = int(q.get("top_logprobs", 0)) if lp else None
+                elif lp is not None and lp is not False:
+                    lp = int(lp)
+                else:
+                    lp = None
+                if q.get("stream") and (n > 1 or len(prompts) > 1):
+                    raise ValueError("stream supports one prompt and n = 1")
+                stop_fn = (lambda ids: any(x in tok.decode(ids) for x in stops)) if stops else None
+                temp = float(q.get("temperature", 1.0 if q.get("do_sample") else 0.0))
+                reqs = []
+                for ids in prompts:
+                    for k in range(n):
+                        seed = q.get("seed")
+                        reqs.append(Request(ids, int(q.get("max_tokens", 16)), temp, float(q.get("top_p", 1.0)),
+                                            int(q.get("top_k", 0)), stop_ids, None if seed is None else int(seed) + 7919 * k,
+                                            float(q.get("repetition_penalty", 1.0)), lp, stop_fn))
             except Exception as e:
                 return self._json(400, {"error": {"message": str(e), "type": "invalid_request_error"}})
-            sched.submit(req)
+            for r in reqs:
+                sched.submit(r)
             created = int(time.time())
             kind = "chat.completion" if chat else "text_completion"
+
+            def cut(text: str):
+                """Text up to the first stop string, and whether one was found."""
+                at = min((text.find(x) for x in stops if x in text), default=-1)
+                return (text[:at], True) if at >= 0 else (text, False)
+
             if q.get("stream"):
+                req = reqs[0]
                 self.send_response(200)
                 self.send_header("Content-Type", "text/event-stream")
                 self.send_header("Cache-Control", "no-cache")
                 self.send_header("Connection", "close")
                 self.end_headers()
-                sent = 0
+                sent_text = ""
                 while True:
                     t = req.out.get()
                     if t is None or isinstance(t, Exception):
                         break
-                    text = tok.decode(req.generated[:sent + 1])[len(tok.decode(req.generated[:sent])):] if tok.tok else str(t) + " "
-                    sent += 1
+                    if tok.tok:
+                        full, hit = cut(tok.decode(req.generated))
+                        text = full[len(sent_text):]
+                        sent_text = full
+                    else:
+                        text, hit = str(t) + " ", False
+                    if not text and not hit:
+                        continue
                     delta = {"delta": {"content": text}} if chat else {"text": text, "token_ids": [t]}
                     chunk = {"id": req.id, "object": kind + ".chunk", "created": created, "model": model_name,
                              "choices": [dict(index=0, finish_reason=None, **delta)]}
                     self.wfile.write(b"data: " + json.dumps(chunk).encode() + b"\n\n")
                     self.wfile.flush()
+                end = {"id": req.id, "object": kind + ".chunk", "created": created, "model": model_name,
+                       "choices": [dict(index=0, finish_reason=req.finish_reason, **({"delta": {}} if chat else {"text": "", "token_ids": []}))]}
+                self.wfile.write(b"data: " + json.dumps(end).encode() + b"\n\n")
                 self.wfile.write(b"data: [DONE]\n\n")
                 self.wfile.flush()
                 self.close_connection = True
                 return
             err = None
-            while True:
-                t = req.out.get()
-                if t is None:
-                    break
-                if isinstance(t, Exception):
-                    err = t
-                    break
+            for req in reqs:
+                while True:
+                    t = req.out.get()
+                    if t is None:
+                        break
+                    if isinstance(t, Exception):
+                        err = t
+                        break
             if err is not None:
                 return self._json(400 if isinstance(err, ValueError) else 500, {"error": {"message": str(err)}})
-            text = tok.decode(req.generated)
-            choice = {"index": 0, "finish_reason": req.finish_reason}
-            if chat:
-                choice["message"] = {"role": "assistant", "content": text}
-            else:
-                choice.update(text=text, token_ids=req.generated)
-            self._json(200, {"id": req.id, "object": kind, "created": created, "model": model_name, "choices": [choice],
-                             "usage": {"prompt_tokens": len(req.prompt_ids), "completion_tokens": len(req.generated),
-                                       "total_tokens": len(req.prompt_ids) + len(req.generated)}})
+            choices = []
+            for i, req in enumerate(reqs):
+                text, hit = cut(tok.decode(req.generated))
+                choice = {"index": i, "finish_reason": "stop" if hit else req.finish_reason}
+                if req.logprobs is not None:
+                    pieces = [tok.decode([t]) for t in req.generated]
+                    if chat:
+                        choice["logprobs"] = {"content": [
+                            {"token": pc, "logprob": l, "top_logprobs": [{"token": tok.decode([j]), "logprob": x}
+                                                                          for j, x in top.items()]}
+                            for pc, l, top in zip(pieces, req.token_logprobs, req.top_logprobs)]}
+                    else:
+                        choice["logprobs"] = {"tokens": pieces, "token_logprobs": req.token_logprobs,
+                                              "top_logprobs": [{tok.decode([j]): x for j, x in top.items()}
+                                                               for top in req.top_logprobs]}
+                if chat:
+                    choice["message"] = {"role": "assistant", "content": text}
+                else:
+                    if q.get("echo"):
+                        text = tok.decode(req.prompt_ids) + (" " if not tok.tok else "") + text
+                    choice.update(text=text, token_ids=req.generated)
+                choices.append(choice)
+            n_prompt = sum(len(r.prompt_ids) for r in reqs)
+            n_gen = sum(len(r.generated) for r in reqs)
+            self._json(200, {"id": reqs[0].id, "object": kind, "created": created, "model": model_name, "choices": choices,
+                             "usage": {"prompt_tokens": n_prompt, "completion_tokens": n_gen,
+                                       "total_tokens": n_prompt + n_gen}})
     return H
 
 

@@ -196,16 +196,36 @@ def test_openai_server_continuous_batching(tmp_path):
         # streaming returns the same tokens as server-sent events
         code, body = post("/v1/completions", {"prompt": prompts[0], "max_tokens": 6, "stream": True})
         assert code == 200
-        toks = [json.loads(l[6:])["choices"][0]["token_ids"][0] for l in body.decode().split("\n\n")
-                if l.startswith("data: {")]
+        chunks = [json.loads(l[6:])["choices"][0] for l in body.decode().split("\n\n") if l.startswith("data: {")]
+        toks = [c["token_ids"][0] for c in chunks if c["token_ids"]]
         assert toks == want[0] and body.decode().strip().endswith("[DONE]")
+        assert chunks[-1]["finish_reason"] == "length" and all(c["finish_reason"] is None for c in chunks[:-1])
+        # n choices, several prompts, echo, log-probabilities, repetition penalty, stop strings (ids joined by spaces
+        # are the "text" when no tokenizer is loaded)
+        code, body = post("/v1/completions", {"prompt": [prompts[0], prompts[1]], "max_tokens": 6, "n": 2, "logprobs": 3})
+        r = json.loads(body)
+        assert code == 200 and [c["index"] for c in r["choices"]] == [0, 1, 2, 3]
+        assert [c["token_ids"] for c in r["choices"]] == [want[0], want[0], want[1], want[1]]      # greedy: n copies agree
+        lp = r["choices"][0]["logprobs"]
+        assert len(lp["token_logprobs"]) == 6 and all(x <= 0 for x in lp["token_logprobs"])
+        assert all(len(t) == 3 and abs(max(t.values()) - l) < 1e-6 for t, l in zip(lp["top_logprobs"], lp["token_logprobs"]))
+        assert r["usage"]["completion_tokens"] == 24
+        stop_at = f" {want[0][2]} "
+        code, body = post("/v1/completions", {"prompt": prompts[0], "max_tokens": 6, "stop": [stop_at.strip()], "echo": True})
+        c = json.loads(body)["choices"][0]
+        assert c["finish_reason"] == "stop" and c["token_ids"] == want[0][:3]
+        assert c["text"].split() == [str(t) for t in prompts[0] + want[0][:2]]
+        code, body = post("/v1/completions", {"prompt": prompts[0], "max_tokens": 6, "repetition_penalty": 50.0})
+        pen = json.loads(body)["choices"][0]["token_ids"]
+        assert code == 200 and len(set(pen)) == 6 and not set(pen) & set(prompts[0])     # a huge penalty forbids repeats
+        assert post("/v1/completions", {"prompt": prompts[0], "n": 2, "stream": True})[0] == 400
         # text prompt without a tokenizer, and a prompt longer than the model: 400, server keeps serving
         assert post("/v1/completions", {"prompt": "hello"})[0] == 400
         assert post("/v1/completions", {"prompt": [1] * 40, "max_tokens": 100000})[0] == 400
         assert json.loads(urllib.request.urlopen(base + "/v1/models").read())["data"][0]["id"] == "tiny"
         m = urllib.request.urlopen(base + "/metrics").read().decode()
-        assert "xft_finished 5" in m and "xft_generated_tokens 30" in m
-        assert sched.metrics["steps"] < 5 * 7          # requests shared engine steps
+        assert "xft_finished 11" in m and "xft_generated_tokens 63" in m
+        assert sched.metrics["steps"] < 11 * 7         # requests shared engine steps
     finally:
         sched.shutdown()
         httpd.shutdown()
