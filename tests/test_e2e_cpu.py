@@ -163,3 +163,21 @@ def test_moe_two_ranks_sliced_and_expert_parallel(mt, ep, tmp_path):
         assert got["held"] == [(4, 0, I), (4, 4, I)]              # whole experts, half of them each
     else:
         assert [h[0] for h in got["held"]] == [8, 8] and sum(h[2] for h in got["held"]) == I     # every expert, sliced
+
+
+def test_pipeline_parallel_microbatches_gloo(tiny, tmp_path):
+    """XFT_MAX_REQUEST_NUM=2 with two pipeline stages: every forward of a 4-sequence batch is cut into two micro-batches
+    that the stages process one behind the other; results equal the single-process greedy decode."""
+    out = str(tmp_path / "pp2mb.pt")
+    env = dict(os.environ, XFT_ENGINE="CPU", XFT_PIPELINE_STAGE="2", XFT_MAX_REQUEST_NUM="2",
+               PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29619", os.path.join(ROOT, "tests", "pp_worker.py"), tiny, out, "4"]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    got = torch.load(out)
+    ids = torch.randint(0, 32000, (4, 32), generator=torch.Generator().manual_seed(1))
+    ref = EagerLlama(tiny)
+    assert torch.allclose(got["logits"], ref.logits(ids)[:, -1], atol=2e-3, rtol=2e-3)
+    assert torch.equal(got["tokens"], ref.greedy(ids, 16))
+    assert got["microbatches"] == 2 * 17      # forward_cb, then a prefill and 15 decode steps: two micro-batches each

@@ -564,11 +564,14 @@ class Model:
         b.positions2 = torch.tensor(p2, dtype=torch.int32, device=dev)
         b.prefix_lm_lens = pl
 
-    def _run(self, seqs: Sequence[SequenceMeta], logits_all: bool = False) -> torch.Tensor:
-        """Run the decoder over the pending inputs of `seqs`; returns this rank's logits slice."""
-        # prefill of many long prompts is run in groups of at most XFT_MAX_BATCH_TOKENS tokens so
-        # the activation footprint stays bounded (each group is a self-contained ragged batch)
+    def _groups(self, seqs: Sequence[SequenceMeta]) -> List[List[SequenceMeta]]:
+        """How one call is cut into forward passes.  Prefill of many long prompts runs in groups of at most
+        XFT_MAX_BATCH_TOKENS tokens so the activation footprint stays bounded (each group is a self-contained ragged
+        batch).  With pipeline stages, XFT_MAX_REQUEST_NUM > 1 additionally cuts a batch into that many micro-batches
+        so the stages work on different micro-batches at the same time (the reference's in-flight request limit,
+        src/utils/environment.h:233; src/models/common_decoder.h:384-391)."""
         cap = self.env.max_batch_tokens
+        groups = [list(seqs)]
         if len(seqs) > 1 and sum(len(s.pending) for s in seqs) > cap and any(len(s.pending) > 1 for s in seqs):
             groups, cur, n = [], [], 0
             for s in seqs:
@@ -578,36 +581,66 @@ class Model:
                 cur.append(s)
                 n += len(s.pending)
             groups.append(cur)
+        m = self.env.max_request_num
+        if self.ctx.pp_size > 1 and m > 1 and len(groups) == 1 and len(seqs) > 1:
+            per = (len(seqs) + min(m, len(seqs)) - 1) // min(m, len(seqs))
+            groups = [list(seqs[i:i + per]) for i in range(0, len(seqs), per)]
+        return groups
+
+    def _run(self, seqs: Sequence[SequenceMeta], logits_all: bool = False) -> torch.Tensor:
+        """Run the decoder over the pending inputs of `seqs`; returns this rank's logits slice."""
+        groups = self._groups(seqs)
+        if self.ctx.pp_size > 1:
+            return self._pp_forward(groups, logits_all)
+        if len(groups) > 1:
             return torch.cat([self._run(g, logits_all) for g in groups], dim=0)
         b = self.make_batch(seqs, logits_all)
         dec = self.decoder if b.is_decode else self.prefill_decoder
         name = "Next Token" if b.is_decode else "1st Token"
         with TimeLine(name), torch.no_grad():
-            if self.ctx.pp_size == 1:
-                return dec.forward(b, self.cache)
-            return self._pp_forward(dec, b)
+            return dec.forward(b, self.cache)
 
-    def _pp_forward(self, dec: Decoder, b: Batch) -> torch.Tensor:
-        """Pipeline stage boundary on p2p send/recv of the bf16/fp32 hidden state (C8); the last
-        stage's logits are then shared with the other stages so that every rank selects the same
-        token and steps its sequences (the reference returns tokens to stage 0 only, C9)."""
-        ctx = self.ctx
-        T = b.ids.shape[0]
-        hidden = None
-        if not dec.first_stage:
-            hidden = torch.empty(T, self.cfg.hidden_size, dtype=dec.act_dtype, device=ctx.device)
-            ctx.recv(hidden, ctx.rank - ctx.tp_size).wait()
-        out = dec.forward(b, self.cache, hidden)
-        if not dec.last_stage:
-            ctx.send(out, ctx.rank + ctx.tp_size).wait()
-        rows = b.num_seqs if b.logit_rows is not None or b.is_decode else T
+    def _pp_forward(self, groups: List[List[SequenceMeta]], logits_all: bool) -> torch.Tensor:
+        """Pipeline stages over p2p send / recv of the hidden state (C8).  Every group is one micro-batch: a stage
+        posts the receives of all micro-batches up front, runs them in order and sends each result on without
+        waiting, so stage s works on micro-batch m while stage s + 1 works on m - 1.  The last stage's logits are
+        then shared with the other stages so that every rank selects the same token and steps its sequences (the
+        reference returns tokens to stage 0 only, C9)."""
         import torch.distributed as dist
-        logits = out if dec.last_stage else torch.empty(rows, dec.v1 - dec.v0, dtype=torch.float32, device=ctx.device)
+        ctx = self.ctx
+        batches = [self.make_batch(g, logits_all) for g in groups]
+        decs = [self.decoder if b.is_decode else self.prefill_decoder for b in batches]
+        first, last = decs[0].first_stage, decs[0].last_stage
+        recvs = []
+        if not first:
+            for b, dec in zip(batches, decs):
+                h = torch.empty(b.ids.shape[0], self.cfg.hidden_size, dtype=dec.act_dtype, device=ctx.device)
+                recvs.append((ctx.recv(h, ctx.rank - ctx.tp_size), h))
+        outs, sends = [], []
+        with torch.no_grad():
+            for i, (b, dec) in enumerate(zip(batches, decs)):
+                hidden = None
+                if not first:
+                    recvs[i][0].wait()
+                    hidden = recvs[i][1]
+                with TimeLine("Next Token" if b.is_decode else "1st Token"):
+                    out = dec.forward(b, self.cache, hidden)
+                if not last:
+                    sends.append((ctx.send(out, ctx.rank + ctx.tp_size), out))     # the tensor stays alive until wait()
+                outs.append(out)
+        for h, _ in sends:
+            h.wait()
+        self.pp_microbatches = getattr(self, "pp_microbatches", 0) + len(batches)
         # same tp_rank column across stages
         src = (ctx.pp_size - 1) * ctx.tp_size + ctx.tp_rank
         grp = self._pp_column_group()
-        dist.broadcast(logits, src, group=grp)
-        return logits
+        res = []
+        for b, dec, out in zip(batches, decs, outs):
+            rows = b.num_seqs if b.logit_rows is not None or b.is_decode else b.ids.shape[0]
+            logits = out if last else torch.empty(rows, dec.v1 - dec.v0, dtype=torch.float32, device=ctx.device)
+            dist.broadcast(logits, src, group=grp)
+            res.append(logits)
+        return res[0] if len(res) == 1 else torch.cat(res, dim=0)
 
     def _pp_column_group(self):
         if not hasattr(self, "_pp_groups"):
