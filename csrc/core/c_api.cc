@@ -9,6 +9,7 @@
 #include "arena.h"
 #include "beam.h"
 #include "env.h"
+#include "rope_tables.h"
 #include "runtime.h"
 #include "xft/layers.h"
 
@@ -78,6 +79,20 @@ int xftc_beam_finalize(void* s, const int32_t* prompts, int batch, int promptLen
   return rows * 65536 + width;
 }
 void xftc_log_softmax(float* row, int n) { logSoftmaxRow(row, n); }
+
+// ---- position tables (csrc/core/rope_tables.cc).  scaling: 0 none, 1 linear, 2 yarn; table_scale < 0 = default
+void xftc_rope_table(int max_pos, int rot_dim, double theta, int scaling, double factor, int original_max_pos,
+                     double beta_fast, double beta_slow, double mscale, double mscale_all_dim, double table_scale,
+                     float* out) {
+  RopeScaling s;
+  s.type = scaling == 1 ? "linear" : scaling == 2 ? "yarn" : "";
+  s.factor = factor; s.originalMaxPos = original_max_pos; s.betaFast = beta_fast; s.betaSlow = beta_slow;
+  s.mscale = mscale; s.mscaleAllDim = mscale_all_dim; s.tableScale = table_scale;
+  auto t = ropeTable(max_pos, rot_dim, theta, s);
+  std::memcpy(out, t.data(), t.size() * sizeof(float));
+}
+double xftc_qwen_ntk_theta(double theta, int rot_dim, int max_kv, int seq_len) { return qwenNtkTheta(theta, rot_dim, max_kv, seq_len); }
+void xftc_alibi_slopes(int n_heads, float* out) { auto v = alibiSlopes(n_heads); std::memcpy(out, v.data(), v.size() * sizeof(float)); }
 
 // ---- caching arena (csrc/core/arena.cc) over malloc/free, for tests without a GPU
 void* xftc_arena_new_host() { return new Arena([](size_t n) { return std::malloc(n); }, [](void* p) { std::free(p); }); }

@@ -19,6 +19,7 @@
 #include "env.h"
 #include "ini.h"
 #include "kernels_c.h"
+#include "rope_tables.h"
 #include "runtime.h"
 #include "xft/models.h"
 
@@ -107,7 +108,7 @@ public:
   // hyper-parameters
   std::string type;
   int heads = 0, kvHeads = 0, headDim = 0, hidden = 0, inter = 0, layers = 0, vocab = 0, maxPos = 0, endId = 0;
-  float eps = 1e-6f, ropeTheta = 10000.f, ropeFactor = 1.f, embedScale = 1.f;
+  float eps = 1e-6f, ropeTheta = 10000.f, embedScale = 1.f;
   int act = 2;   // kernel activation code: 1 relu, 2 silu, 3 gelu
   bool qkNorm = false, kvInt8 = false;
 
@@ -134,7 +135,7 @@ private:
   void copyBlock(int src, int dst);
   std::string dir;
   int fileDt = 1;
-  DevBuf wte, lmHead, finalNorm, ropeTable, ws, counters, status, attnCounters, partO, partMl;
+  DevBuf wte, lmHead, finalNorm, ropeTable_, ws, counters, status, attnCounters, partO, partMl;
   std::vector<LayerWeights> lw;
   std::vector<DevBuf> kc, vc, ks, vs;
   int numBlocks = 0;
@@ -191,8 +192,20 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
   eps = (float)ini.getFloat(type, "layernorm_eps", ini.getFloat(type, "rms_norm_eps", 1e-6));
   ropeTheta = (float)ini.getFloat(type, "rope_theta", 10000.0);
   std::string rtype = ini.get(type, "rope_scaling_type", ini.get(type, "rope_type", ""));
-  if (rtype == "linear") ropeFactor = (float)ini.getFloat(type, "rope_scaling_factor", ini.getFloat(type, "scaling_factor", 1.0));
-  else if (!rtype.empty() && rtype != "default") throw std::runtime_error("rope scaling '" + rtype + "' runs through the Python API");
+  RopeScaling rs;
+  if (type == "yarn_llama" && (rtype.empty() || rtype == "default")) rtype = "yarn";
+  if (rtype == "linear" || rtype == "yarn") {
+    rs.type = rtype;
+    rs.factor = ini.getFloat(type, "rope_scaling_factor", ini.getFloat(type, "scaling_factor", 1.0));
+    rs.originalMaxPos = (int)ini.getInt(type, "rope_scaling_original_max_position_embeddings",
+                                        ini.getInt(type, "original_max_position_embeddings", 2048));
+    rs.betaFast = ini.getFloat(type, "rope_scaling_beta_fast", 32.0);
+    rs.betaSlow = ini.getFloat(type, "rope_scaling_beta_slow", 1.0);
+    // Llama YaRN scales the table by 0.1 ln(factor) + 1 (yarn_scaled_rotary_embedding.cpp:26-84)
+    if (rtype == "yarn") rs.tableScale = yarnMscale(rs.factor, 1.0);
+  } else if (!rtype.empty() && rtype != "default") {
+    throw std::runtime_error("rope scaling '" + rtype + "' runs through the Python API");
+  }
   endId = (int)ini.getInt(type, "end_id", ini.getInt(type, "start_id", 0));
   std::string a = ini.get(type, "activation_type", "silu");
   act = a.rfind("gelu", 0) == 0 ? 3 : a == "relu" ? 1 : 2;
@@ -241,16 +254,9 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
   }
   // rotary table [maxPos, headDim] = cos(headDim/2) ‖ sin(headDim/2)
   {
-    std::vector<float> tab((size_t)maxPos * headDim);
-    const int half = headDim / 2;
-    for (int pos = 0; pos < maxPos; ++pos)
-      for (int i = 0; i < half; ++i) {
-        double inv = 1.0 / std::pow((double)ropeTheta, 2.0 * i / headDim) / ropeFactor;
-        tab[(size_t)pos * headDim + i] = (float)std::cos(pos * inv);
-        tab[(size_t)pos * headDim + half + i] = (float)std::sin(pos * inv);
-      }
-    ropeTable.reset(tab.size() * 4);
-    XFT_CUDA(cudaMemcpy(ropeTable.p, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice));
+    const std::vector<float> tab = ropeTable(maxPos, headDim, ropeTheta, rs);
+    ropeTable_.reset(tab.size() * 4);
+    XFT_CUDA(cudaMemcpy(ropeTable_.p, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice));
   }
   ws.reset(kWsBytes);
   counters.reset(8192 * 4); XFT_CUDA(cudaMemset(counters.p, 0, counters.bytes));
@@ -386,7 +392,7 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
     LayerWeights& L = lw[l];
     XFT_K(xft_rmsnorm(cur, hidden, nullptr, 0, L.n1.as<float>(), h.p, hidden, nullptr, T, hidden, eps, st));
     gemm(h.p, hidden, L.qkv.p, qkvN, qkvBuf.p, qkvN, 0, 0, 0, L.qkvBias.as<float>(), nullptr, 0, T);
-    XFT_K(xft_qkv_rope_cache(qkvBuf.p, qkvN, T, heads, kvHeads, headDim, dPos.as<int>(), ropeTable.as<float>(), headDim, 0, 0,
+    XFT_K(xft_qkv_rope_cache(qkvBuf.p, qkvN, T, heads, kvHeads, headDim, dPos.as<int>(), ropeTable_.as<float>(), headDim, 0, 0,
                              maxPos, nullptr, L.qNorm.as<float>(), L.kNorm.as<float>(), eps, q.p, kc[l].p, vc[l].p,
                              ks[l].as<float>(), vs[l].as<float>(), kvInt8 ? 1 : 0, kBlock, (long long)numBlocks * kBlock,
                              dSlots.as<int>(), stp, st));

@@ -17,6 +17,7 @@
 #include "beam.h"
 #include "env.h"
 #include "ini.h"
+#include "rope_tables.h"
 #include "runtime.h"
 
 static int g_failed = 0, g_checks = 0;
@@ -272,6 +273,41 @@ static void testArena() {
   EXPECT(g_backendAllocs == g_backendFrees);
 }
 
+static void testRopeTables() {
+  RopeScaling none;
+  auto t = ropeTable(16, 8, 10000.0, none);
+  EXPECT(t.size() == 16 * 8);
+  for (int i = 0; i < 4; ++i) EXPECT(t[i] == 1.0f && t[4 + i] == 0.0f);               // position 0: cos 1, sin 0
+  EXPECT(std::fabs(t[8 + 0] - std::cos(1.0)) < 1e-6 && std::fabs(t[8 + 4] - std::sin(1.0)) < 1e-6);   // pos 1, freq 1
+  for (size_t p = 0; p < 16; ++p)
+    for (int i = 0; i < 4; ++i) {
+      const float c = t[p * 8 + i], s = t[p * 8 + 4 + i];
+      EXPECT(std::fabs(c * c + s * s - 1.0f) < 1e-5);
+    }
+  RopeScaling lin;
+  lin.type = "linear";
+  lin.factor = 4.0;
+  auto tl = ropeTable(16, 8, 10000.0, lin);
+  for (int i = 0; i < 8; ++i) EXPECT(std::fabs(tl[4 * 8 + i] - t[1 * 8 + i]) < 1e-6);   // position 4 at factor 4 = position 1
+  RopeScaling yarn;
+  yarn.type = "yarn";
+  yarn.factor = 8.0;
+  yarn.originalMaxPos = 64;
+  auto inv0 = ropeInvFreq(64, 10000.0, none), inv = ropeInvFreq(64, 10000.0, yarn);
+  EXPECT(inv.size() == 32 && inv[0] == inv0[0]);                                       // fastest dimension is kept
+  EXPECT(std::fabs(inv[31] - inv0[31] / 8.0) < 1e-12);                                 // slowest is interpolated
+  for (int i = 0; i < 32; ++i) EXPECT(inv[i] <= inv0[i] * (1 + 1e-12) && inv[i] >= inv0[i] / 8.0 * (1 - 1e-12));
+  EXPECT(std::fabs(yarnMscale(8.0, 1.0) - (0.1 * std::log(8.0) + 1.0)) < 1e-12 && yarnMscale(1.0, 1.0) == 1.0);
+  auto ty = ropeTable(4, 64, 10000.0, yarn);
+  EXPECT(std::fabs(ty[0] - (float)yarnMscale(8.0, 1.0)) < 1e-6);                       // cos(0) times the YaRN scale
+  EXPECT(qwenNtkTheta(10000.0, 128, 4096, 8192) == 10000.0);
+  EXPECT(std::fabs(qwenNtkTheta(10000.0, 128, 16384, 8192) - 10000.0 * std::pow(3.0, 128.0 / 126.0)) < 1e-6);
+  auto a8 = alibiSlopes(8);
+  EXPECT(a8.size() == 8 && std::fabs(a8[0] - 0.5f) < 1e-7 && std::fabs(a8[7] - 1.0f / 256) < 1e-9);
+  auto a12 = alibiSlopes(12);
+  EXPECT(a12.size() == 12 && a12[7] == a8[7] && std::fabs(a12[8] - std::pow(2.0, -0.5)) < 1e-6);
+}
+
 int main(int argc, char** argv) {
   const std::string dir = argc > 1 ? argv[1] : "/tmp";
   testPartition();
@@ -282,6 +318,7 @@ int main(int argc, char** argv) {
   testIni(dir);
   testEnvAndTimeline(dir);
   testArena();
+  testRopeTables();
   std::printf("runtime_selftest: %d checks, %d failed\n", g_checks, g_failed);
   return g_failed ? 1 : 0;
 }

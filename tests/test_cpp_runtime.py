@@ -296,3 +296,35 @@ def test_example_cli_flags_follow_the_reference(core):
     assert r.returncode == 1 and "config.ini" in r.stderr and "input_len 2 is not longer" in r.stderr
     assert run("-m", "/nonexistent", "-i", "hello").returncode == 2           # the prompt is given as ids
     assert run("-m", "/nonexistent", "-i", "1 2 3", "--prefix_len", "3").returncode == 2
+
+
+def test_rope_and_alibi_tables_match_python(core):
+    """csrc/core/rope_tables.cc against ops/reference.py: plain, linear, YaRN (DeepSeek's mscale ratio and Llama-YaRN's
+    table scale), Qwen's dynamic-NTK base, ALiBi slopes for power-of-two and other head counts."""
+    import math
+    core.xftc_qwen_ntk_theta.restype = C.c_double
+    D = C.c_double
+    cases = [(0, "", dict()), (1, "linear", dict(factor=4.0)),
+             (2, "yarn", dict(factor=40.0, original_max_pos=4096, beta_fast=32, beta_slow=1, mscale=1.0, mscale_all_dim=1.0)),
+             (2, "yarn", dict(factor=16.0, original_max_pos=2048, mscale=0.707, mscale_all_dim=0.0)),
+             (2, "yarn", dict(factor=8.0, original_max_pos=512, table_scale=R.yarn_mscale(8.0, 1.0)))]
+    for code, name, kw in cases:
+        for rot, theta in ((64, 10000.0), (128, 1e6)):
+            max_pos = 600
+            want = R.rope_table(max_pos, rot, theta, name, **kw)
+            out = (C.c_float * (max_pos * rot))()
+            core.xftc_rope_table(max_pos, rot, D(theta), code, D(kw.get("factor", 1.0)), kw.get("original_max_pos", 2048),
+                                 D(kw.get("beta_fast", 32)), D(kw.get("beta_slow", 1)), D(kw.get("mscale", 1.0)),
+                                 D(kw.get("mscale_all_dim", 0.0)), D(kw.get("table_scale", -1.0)), out)
+            got = torch.tensor(list(out)).view(max_pos, rot)
+            assert torch.allclose(got, want, atol=3e-4), (name, kw, rot, (got - want).abs().max())
+    for max_kv, seq in ((4096, 8192), (8193, 8192), (40000, 8192), (3000, 2048)):
+        want = 10000.0
+        if max_kv > seq:
+            alpha = max(2 ** math.ceil(math.log(max_kv / seq, 2) + 1) - 1, 1)
+            want = 10000.0 * alpha ** (128 / 126)
+        assert abs(core.xftc_qwen_ntk_theta(D(10000.0), 128, max_kv, seq) - want) < 1e-6 * want
+    for n in (1, 8, 12, 32, 40, 52, 64):
+        out = (C.c_float * n)()
+        core.xftc_alibi_slopes(n, out)
+        assert torch.allclose(torch.tensor(list(out)), R.alibi_slopes(n), rtol=1e-6), n
