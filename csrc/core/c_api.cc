@@ -20,6 +20,16 @@ extern "C" {
 void xftc_task_range(int n, int splits, int idx, int* out2) { auto r = taskRange(n, splits, idx); out2[0] = r.first; out2[1] = r.second; }
 void xftc_head_range(int q, int kv, int splits, int idx, int* out4) { auto r = headRange(q, kv, splits, idx); out4[0] = r.q0; out4[1] = r.q1; out4[2] = r.kv0; out4[3] = r.kv1; }
 
+void xftc_pp_layer_range(int layers, int pp, int rank, int* out2) { auto r = ppLayerRange(layers, pp, rank); out2[0] = r.first; out2[1] = r.second; }
+int xftc_moe_slice_index(int tpRank, int tpSize, int layer, int expert, int dim) { return moeSliceIndex(tpRank, tpSize, layer, expert, dim); }
+void xftc_expert_range(int experts, int ep, int rank, int* out2) { auto r = expertRange(experts, ep, rank); out2[0] = r.first; out2[1] = r.second; }
+int xftc_expert_owner(int expert, int experts, int ep) { return expertOwner(expert, experts, ep); }
+int xftc_block_visit_order(int blocks, int world, int rank, int lag, int* out) {
+  auto v = blockVisitOrder(blocks, world, rank, lag);
+  std::memcpy(out, v.data(), v.size() * sizeof(int));
+  return (int)v.size();
+}
+
 void* xftc_tables_new(int blockSize, int numBlocks) { return new BlockTables(blockSize, numBlocks); }
 void xftc_tables_delete(void* t) { delete static_cast<BlockTables*>(t); }
 int xftc_tables_add(void* t, int seq) { try { static_cast<BlockTables*>(t)->add(seq); return 0; } catch (...) { return -1; } }

@@ -30,6 +30,38 @@ HeadRange headRange(int qHeads, int kvHeads, int splits, int idx) {
   return {s, e, s / expand, e > s ? (e - 1) / expand + 1 : s / expand};
 }
 
+std::pair<int, int> ppLayerRange(int numLayers, int ppSize, int ppRank) {
+  if (ppSize <= 0 || ppRank < 0 || ppRank >= ppSize) throw std::invalid_argument("bad pipeline stage");
+  const int base = numLayers / ppSize, rem = numLayers % ppSize;
+  const int start = ppRank * base + std::min(ppRank, rem);
+  return {start, start + base + (ppRank < rem ? 1 : 0)};
+}
+int moeSliceIndex(int tpRank, int tpSize, int layerId, int expertId, int balanceDim) {
+  return (tpRank + (balanceDim == 0 ? layerId : expertId)) % tpSize;
+}
+std::pair<int, int> expertRange(int numExperts, int epSize, int epRank) {
+  if (epSize <= 0 || epRank < 0 || epRank >= epSize) throw std::invalid_argument("bad expert-parallel rank");
+  const int base = numExperts / epSize, rem = numExperts % epSize;
+  const int start = epRank * base + std::min(epRank, rem);
+  return {start, start + base + (epRank < rem ? 1 : 0)};
+}
+int expertOwner(int expertId, int numExperts, int epSize) {
+  const int base = numExperts / epSize, rem = numExperts % epSize;
+  const int cut = rem * (base + 1);
+  if (expertId < cut) return expertId / (base + 1);
+  return rem + (expertId - cut) / std::max(base, 1);
+}
+std::vector<int> blockVisitOrder(int numBlocks, int world, int rank, int lag) {
+  if (lag < 0) lag = world;
+  std::vector<int> out;
+  out.reserve(numBlocks);
+  for (int k = 0; k < numBlocks + lag; ++k) {
+    if (k < numBlocks && k % world != rank) out.push_back(k);
+    if (k >= lag && (k - lag) % world == rank) out.push_back(k - lag);
+  }
+  return out;
+}
+
 SequenceMeta& SequencePool::create(const std::vector<int32_t>& prompt, int maxLen) {
   for (int tries = 0; tries < kMaxId; ++tries) {
     int id = next_;

@@ -15,6 +15,17 @@ std::pair<int, int> taskRange(int n, int splits, int idx);
 std::pair<int, int> taskRangeGran(int n, int gran, int splits, int idx);
 struct HeadRange { int q0, q1, kv0, kv1; };
 HeadRange headRange(int qHeads, int kvHeads, int splits, int idx);
+// layers of one pipeline stage (src/layers/decoder_block.h:33-40; a remainder goes to the first stages)
+std::pair<int, int> ppLayerRange(int numLayers, int ppSize, int ppRank);
+// rotated tensor-parallel slice of an expert, so uneven slices even out over layers (dim 0) or experts (dim 1)
+// (src/layers/mlp_llama.h:70-79, XFT_MOE_SPLIT_BALANCE_DIM)
+int moeSliceIndex(int tpRank, int tpSize, int layerId, int expertId, int balanceDim);
+// expert parallelism: contiguous block of experts per rank, and the rank that owns an expert
+std::pair<int, int> expertRange(int numExperts, int epSize, int epRank);
+int expertOwner(int expertId, int numExperts, int epSize);
+// fused prefill GEMM + all-reduce: order in which a rank visits the token blocks (its own blocks `lag` steps late;
+// lag < 0 = one round of `world`)
+std::vector<int> blockVisitOrder(int numBlocks, int world, int rank, int lag = -1);
 
 // ---- sequences (src/common/sequence.h) ----------------------------------------------------------------------
 struct SequenceMeta {

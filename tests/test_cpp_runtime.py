@@ -328,3 +328,33 @@ def test_rope_and_alibi_tables_match_python(core):
         out = (C.c_float * n)()
         core.xftc_alibi_slopes(n, out)
         assert torch.allclose(torch.tensor(list(out)), R.alibi_slopes(n), rtol=1e-6), n
+
+
+def test_parallel_layout_twins_match_python(core):
+    """Pipeline stage ranges, the MoE slice rotation, expert placement and the fused prefill kernel's visiting order:
+    C++ (csrc/core/runtime.cc) against parallel/partition.py."""
+    out = (C.c_int * 2)()
+    for layers in (1, 7, 32, 61, 80):
+        for pp in (1, 2, 3, 8):
+            for r in range(pp):
+                core.xftc_pp_layer_range(layers, pp, r, out)
+                assert (out[0], out[1]) == P.pp_layer_range(layers, pp, r)
+    for E in (8, 60, 128, 256):
+        for ep in (1, 2, 3, 8):
+            owners = []
+            for r in range(ep):
+                core.xftc_expert_range(E, ep, r, out)
+                assert (out[0], out[1]) == P.expert_range(E, ep, r)
+                owners += [r] * (out[1] - out[0])
+            assert [core.xftc_expert_owner(e, E, ep) for e in range(E)] == owners == [P.expert_owner(e, E, ep) for e in range(E)]
+    for tp in (2, 8):
+        for dim in (0, 1):
+            assert all(core.xftc_moe_slice_index(r, tp, l, e, dim) == P.moe_slice_index(r, tp, l, e, dim)
+                       for r in range(tp) for l in (0, 3, 9) for e in (0, 5))
+    buf = (C.c_int * 64)()
+    for world in (2, 4, 8):
+        for nb in (1, 5, 33):
+            for lag in (-1, 0, 3):
+                for r in range(world):
+                    n = core.xftc_block_visit_order(nb, world, r, lag, buf)
+                    assert list(buf[:n]) == P.block_visit_order(nb, world, r, lag)
