@@ -111,12 +111,15 @@ def test_lost_rank_raises_comm_error_not_hang(tiny, tmp_path):
     assert float(secs) < 60 and int(width) == 12
 
 
-@pytest.mark.parametrize("mt,ep", [("mixtral", 0), ("mixtral", 1), ("deepseek_moe", 1), ("qwen3_moe", 0)])
+@pytest.mark.parametrize("mt,ep", [("mixtral", 0), ("mixtral", 1), ("deepseek_moe", 1), ("qwen3_moe", 0),
+                                   ("mixtral", 2), ("deepseek_moe", 2)])
 def test_moe_two_ranks_sliced_and_expert_parallel(mt, ep, tmp_path):
     """MoE across two gloo ranks against the single-rank engine on the same files: XFT_EXPERT_PARALLEL=0 slices every
     expert's intermediate dimension (the reference's only mode, src/layers/moe_deepseek.h / mlp_llama.h:70-79), =1
     places whole experts on ranks (each rank runs its own experts on the replicated tokens; the row-parallel reduction
-    combines).  Prefill and one decode step."""
+    combines).  ep = 2 stands for XFT_ATTENTION_DP=1: no tensor parallelism, every rank runs attention for its own
+    sequences (3 prompts over 2 ranks: 2 + 1) and tokens travel to their experts' ranks and back by all-to-all.
+    Prefill and one decode step."""
     import xfastertransformer_b200 as xft
     from xfastertransformer_b200.config import ModelConfig, RopeConfig
     from xfastertransformer_b200.parallel.dist import DistContext
@@ -137,7 +140,7 @@ def test_moe_two_ranks_sliced_and_expert_parallel(mt, ep, tmp_path):
     d = str(tmp_path / "m")
     write_synthetic_checkpoint(d, cfg, seed=0, dtype="bf16", std=0.05)
     out = str(tmp_path / "moe.pt")
-    env = dict(os.environ, XFT_ENGINE="CPU", XFT_EXPERT_PARALLEL=str(ep),
+    env = dict(os.environ, XFT_ENGINE="CPU", XFT_EXPERT_PARALLEL=str(int(ep == 1)), XFT_ATTENTION_DP=str(int(ep == 2)),
                PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
     port = 29621 + 2 * (ep + 2 * ["mixtral", "deepseek_moe", "qwen3_moe"].index(mt))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
@@ -181,3 +184,46 @@ def test_pipeline_parallel_microbatches_gloo(tiny, tmp_path):
     assert torch.allclose(got["logits"], ref.logits(ids)[:, -1], atol=2e-3, rtol=2e-3)
     assert torch.equal(got["tokens"], ref.greedy(ids, 16))
     assert got["microbatches"] == 2 * 17      # forward_cb, then a prefill and 15 decode steps: two micro-batches each
+
+
+def test_data_parallel_attention_scenarios(tmp_path):
+    """XFT_ATTENTION_DP=1 on two gloo ranks against the single-rank engine: a batch of one (rank 1 owns no sequence and
+    only serves its experts), prompts whose prefill needs more passes on one rank than on the other
+    (XFT_MAX_BATCH_TOKENS=32), beam search (beams stay on their request's rank) and all-position logits."""
+    import xfastertransformer_b200 as xft
+    from xfastertransformer_b200.config import ModelConfig
+    from xfastertransformer_b200.parallel.dist import DistContext
+    from xfastertransformer_b200.utils.flags import Env
+    cfg = ModelConfig(model_type="mixtral", num_layer=2, hidden_size=128, head_num=4, kv_head_num=2, size_per_head=32,
+                      inter_size=128, moe_intermediate_size=128, vocab_size=1000, max_pos_seq_len=512, sparse_experts=8,
+                      num_experts_per_tok=2, norm_topk_prob=True, activation_type="silu", weight_data_type="bf16",
+                      start_id=1, end_id=2)
+    d = str(tmp_path / "m")
+    write_synthetic_checkpoint(d, cfg, seed=0, dtype="bf16", std=0.05)
+    out = str(tmp_path / "dp.pt")
+    env = dict(os.environ, XFT_ENGINE="CPU", XFT_ATTENTION_DP="1", XFT_MAX_BATCH_TOKENS="32",
+               PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29641", os.path.join(ROOT, "tests", "dp_worker.py"), d, out]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    got = torch.load(out)
+    os.environ["XFT_ENGINE"] = "CPU"
+    DistContext.reset()
+    Env.get().reload()
+    m = xft.AutoModel.from_pretrained(d, dtype="bf16")
+    g = torch.Generator().manual_seed(4)
+    one = torch.randint(0, 1000, (1, 9), generator=g)
+    three = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (40, 7, 33)]
+    two = torch.randint(0, 1000, (2, 11), generator=g)
+    assert torch.equal(got["one"], m.generate(one, max_length=15))
+    sid = m.set_input_cb(three, None, 64)
+    want = m.forward_cb()
+    m.free_seqs(sid)
+    assert torch.allclose(got["three"], want, atol=2e-3 * max(1.0, want.abs().max().item()))
+    assert torch.equal(got["beams"], m.generate(two, max_length=16, num_beams=2))
+    full = m(two)
+    assert torch.allclose(got["all"], full, atol=2e-3 * max(1.0, full.abs().max().item()))
+    # no tensor parallelism (o_proj sees all 4 heads), both ranks took part in the expert exchange
+    assert [i[:2] for i in got["info"]] == [(2, 1), (2, 1)] and all(i[2] > 0 and i[3] == 128 for i in got["info"])
+    assert got["info"][0][2] == got["info"][1][2]

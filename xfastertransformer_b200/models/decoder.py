@@ -569,7 +569,72 @@ class Decoder:
         with TimeLine("MoE"):
             return self._moe(L, h, x)
 
+    def _route(self, L: Layer, h):
+        c = self.cfg
+        logits = ops.linear(h, L.router, out_dtype=torch.float32)
+        if L.route_kind == "deepseek":
+            return ops.route(logits, "deepseek", L.top_k, L.router_bias, max(c.n_group, 1), max(c.topk_group, 1),
+                             c.routed_scaling_factor, c.norm_topk_prob, c.scoring_func or "sigmoid")
+        if L.route_kind == "softmax_topk":
+            return ops.route(logits, "softmax_topk", L.top_k, norm_topk=c.norm_topk_prob or True)
+        return ops.route(logits, "mixtral", L.top_k)
+
+    def _moe_dp(self, L: Layer, h, x):
+        """MoE block with data-parallel attention (XFT_ATTENTION_DP=1): this rank holds only ITS sequences' tokens.
+        Dispatch: every (token, expert) pair travels to the rank that owns the expert (all-to-all, rows grouped by
+        destination).  The owners run their experts on what they received.  Combine: the expert outputs travel back
+        the same way and are summed with the routing weights at the token's home rank.  `h` may have no rows (a rank
+        without work in this step still serves its experts to the others); then `x` is unused."""
+        ctx, c = self.ctx, self.cfg
+        T, H = h.shape[0], c.hidden_size
+        E, k = c.sparse_experts, L.top_k
+        dev = h.device
+        if T > 0:
+            idx, w = self._route(L, h)
+            flat_e = idx.reshape(-1).long()
+            flat_t = torch.arange(T, device=dev).repeat_interleave(k)
+            if not hasattr(self, "_expert_owner"):
+                self._expert_owner = torch.tensor([P.expert_owner(e, E, ctx.ep_size) for e in range(E)], device=dev)
+            dest = self._expert_owner[flat_e]
+            order = torch.argsort(dest, stable=True)
+            send_counts = torch.bincount(dest, minlength=ctx.ep_size).tolist()
+            send_tok = h[flat_t[order]]
+            send_e = flat_e[order].int()
+        else:
+            send_counts = [0] * ctx.ep_size
+            send_tok = h.new_zeros(0, H)
+            send_e = torch.zeros(0, dtype=torch.int32, device=dev)
+        recv_tok, recv_counts = ctx.all_to_all(send_tok, send_counts)
+        recv_e = ctx.all_to_all_known(torch.empty(sum(recv_counts), dtype=torch.int32, device=dev), send_e, recv_counts,
+                                      send_counts)
+        R = recv_tok.shape[0]
+        if R > 0:
+            ones = torch.ones(R, 1, dtype=torch.float32, device=dev)
+            y = ops.moe_experts(recv_tok, recv_e.view(R, 1), ones, L.experts, L.act, L.e0, getattr(L, "packed", None))
+        else:
+            y = torch.zeros(0, H, dtype=torch.float32, device=dev)
+        back = ctx.all_to_all_known(torch.empty(sum(send_counts), H, dtype=torch.float32, device=dev), y, send_counts,
+                                    recv_counts)
+        if T == 0:
+            return h
+        out = torch.zeros(T, H, dtype=torch.float32, device=dev)
+        out.index_add_(0, flat_t[order], back * w.reshape(-1)[order].float()[:, None])
+        if getattr(L, "shared", None) is not None:
+            g = ops.linear_gated(h, L.shared[0], L.act)
+            out = out + ops.linear(g, L.shared[1], out_dtype=torch.float32)
+        return (out + x.float()).to(x.dtype)
+
+    def forward_idle(self) -> None:
+        """Data-parallel attention: a rank with no sequence in this pass still takes part in the dispatch / combine
+        of every MoE layer (its experts may be needed by the others)."""
+        empty = torch.zeros(0, self.cfg.hidden_size, dtype=self.act_dtype, device=self.device)
+        for L in self.layers:
+            if L.mlp_kind not in ("llama", "gpt"):
+                self._moe_dp(L, empty, None)
+
     def _moe(self, L: Layer, h, x):
+        if self.ctx.dp_size > 1:
+            return self._moe_dp(L, h, x)
         c = self.cfg
         logits = ops.linear(h, L.router, out_dtype=torch.float32)
         if L.route_kind == "deepseek":

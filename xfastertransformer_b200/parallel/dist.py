@@ -102,7 +102,16 @@ class DistContext:
         # expert parallel runs over the TP group (attention TP + expert EP on the same ranks)
         self.ep_size = self.tp_size if env.expert_parallel else 1
         self.ep_rank = self.tp_rank if env.expert_parallel else 0
-        self.stats = {"all_reduce": 0, "all_gather": 0, "ctrl": 0, "p2p": 0}
+        # XFT_ATTENTION_DP=1: no tensor parallelism at all.  Every rank holds the dense weights in full and serves its
+        # own share of the sequences (its own KV cache); only the routed experts are spread over the ranks, and tokens
+        # reach them through `all_to_all`.  From here on the rank looks like a single-rank job (tp_size 1, every
+        # tensor-parallel collective is the identity) with ep_size = dp_size = world.
+        self.dp_size, self.dp_rank, self.dp_group = 1, 0, None
+        if env.attention_dp and self.world > 1 and self.pp_size == 1:
+            self.dp_size, self.dp_rank, self.dp_group = self.world, self.rank, self.tp_group
+            self.tp_size, self.tp_rank, self.tp_group = 1, 0, None
+            self.ep_size, self.ep_rank = self.world, self.rank
+        self.stats = {"all_reduce": 0, "all_gather": 0, "ctrl": 0, "p2p": 0, "all_to_all": 0}
         self.peer = None      # PeerComm (symmetric buffers over CUDA IPC), set by the engine on GPUs
 
     # -- singleton ------------------------------------------------------------------
@@ -161,6 +170,47 @@ class DistContext:
             return torch.cat([o.narrow(d, 0, s) for o, s in zip(outs, sizes)], dim=d)
         except RuntimeError as e:
             raise CommError(f"all-gather failed on rank {self.rank}: {e}") from e
+
+    def all_to_all(self, send: torch.Tensor, send_counts: List[int]):
+        """Variable all-to-all over the data-parallel group: rows [sum(send_counts), ...] of `send`, grouped by
+        destination rank in rank order, go out; returns (received rows grouped by source rank, receive counts)."""
+        self.stats["all_to_all"] += 1
+        try:
+            sc = torch.tensor(send_counts, dtype=torch.int64, device=send.device)
+            rc = torch.empty_like(sc)
+            dist.all_to_all_single(rc, sc, group=self.dp_group)
+            recv_counts = [int(v) for v in rc.tolist()]
+            recv = send.new_empty((sum(recv_counts),) + tuple(send.shape[1:]))
+            self.all_to_all_known(recv, send, recv_counts, send_counts)
+            return recv, recv_counts
+        except RuntimeError as e:
+            raise CommError(f"all-to-all failed on rank {self.rank}: {e}") from e
+
+    def all_to_all_known(self, recv: torch.Tensor, send: torch.Tensor, recv_counts: List[int], send_counts: List[int]):
+        """all_to_all with both count lists known (the way back of a dispatch)."""
+        try:
+            if send.device.type == "cpu" and send.dtype == torch.bfloat16:       # gloo has no bf16
+                r32 = recv.float()
+                dist.all_to_all_single(r32, send.float().contiguous(), recv_counts, send_counts, group=self.dp_group)
+                recv.copy_(r32)
+            else:
+                dist.all_to_all_single(recv, send.contiguous(), recv_counts, send_counts, group=self.dp_group)
+            return recv
+        except RuntimeError as e:
+            raise CommError(f"all-to-all failed on rank {self.rank}: {e}") from e
+
+    def all_gather_rows(self, t: torch.Tensor, counts: List[int]) -> List[torch.Tensor]:
+        """Every rank's rows (rank r contributes counts[r] rows, known everywhere) over the data-parallel group."""
+        self.stats["all_gather"] += 1
+        mx = max(counts)
+        buf = t.new_zeros((mx,) + tuple(t.shape[1:]))
+        buf[:t.shape[0]] = t
+        outs = [torch.empty_like(buf) for _ in range(self.dp_size)]
+        try:
+            dist.all_gather(outs, buf, group=self.dp_group)
+        except RuntimeError as e:
+            raise CommError(f"all-gather failed on rank {self.rank}: {e}") from e
+        return [o[:n] for o, n in zip(outs, counts)]
 
     def barrier(self) -> None:
         if self.world > 1:

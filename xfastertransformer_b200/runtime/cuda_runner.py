@@ -55,6 +55,8 @@ class CudaRunner:
             return False
         if self.m.ctx.pp_size > 1 or self.m.decoder.spec.rope == "2d" or trace.enabled() or self.m.env.debug_dir:
             return False
+        if self.m.ctx.dp_size > 1:          # data-parallel attention: ranks run different batches and exchange tokens
+            return False
         if self.m.ctx.tp_size > 1 and self.m.decoder.has_moe:
             # the experts' partial sums cross ranks through the peer-memory all-reduce, which holds at most `slot`
             # values; without it the step would put a NCCL collective inside the captured graph

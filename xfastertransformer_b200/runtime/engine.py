@@ -201,13 +201,15 @@ class Model:
             raise ValueError("input_ids is empty")
         self._prompts = prompts
         nb = max(cfg.num_beams, 1)
-        total_blocks = sum(self.cache.blocks_for(max(cfg.max_length, len(p)) + 1) for p in prompts) * nb
+        dp, me = self.ctx.dp_size, self.ctx.dp_rank          # data-parallel attention: a rank caches only its own requests
+        total_blocks = sum(self.cache.blocks_for(max(cfg.max_length, len(p)) + 1)
+                           for g, p in enumerate(prompts) if g % dp == me) * nb
         self.cache.reserve(total_blocks)
         seqs = []
         for g, p in enumerate(prompts):
             if len(p) >= cfg.max_length:
                 log.warning(f"prompt {g}: length {len(p)} >= max_length {cfg.max_length}")
-            s = self.pool.new(p, max(cfg.max_length, len(p) + 1), group=g)
+            s = self.pool.new(p, max(cfg.max_length, len(p) + 1), group=g, owner=g % self.ctx.dp_size)
             self.cache.add_sequence(s.seq_id)
             self._attach_prefix(s)
             seqs.append(s)
@@ -304,7 +306,7 @@ class Model:
             for s in reqs:
                 beams.append(s)
                 for _ in range(nb - 1):
-                    c = self.pool.new(s.prompt, s.max_len, group=s.group)
+                    c = self.pool.new(s.prompt, s.max_len, group=s.group, owner=s.owner)      # beams stay with their request
                     c.past_len, c.pending = s.past_len, []
                     self.cache.fork(s.seq_id, c.seq_id)
                     beams.append(c)
@@ -395,14 +397,17 @@ class Model:
             mls = max_len or [self.cfg.max_pos_seq_len or 2048]
             if len(mls) == 1:
                 mls = mls * len(seq_lens)
-            self.cache.reserve(sum(self.cache.blocks_for(max(m, n) + 1) for m, n in zip(mls, seq_lens)))
             off = 0
             for n, m in zip(seq_lens, mls):
                 s = self.pool.new(ids[off:off + n], max(m, n + 1))
+                s.owner = s.seq_id % self.ctx.dp_size
                 off += n
+                active.append(s)
+            # data-parallel attention: a rank caches only the sequences it owns
+            self.cache.reserve(sum(self.cache.blocks_for(s.max_len + 1) for s in active if s.owner == self.ctx.dp_rank))
+            for s in active:
                 self.cache.add_sequence(s.seq_id)
                 self._attach_prefix(s)
-                active.append(s)
         else:                                             # next tokens of known sequences
             if len(ids) != len(seq_ids):
                 raise ValueError("set_input_cb: one next token per sequence id expected")
@@ -496,6 +501,8 @@ class Model:
         n = (len(ids) // self.cache.block) * self.cache.block
         if n == 0:
             return
+        if self.ctx.dp_size > 1:
+            raise RuntimeError("prefix sharing is not available with XFT_ATTENTION_DP=1 (a prefix lives on one rank)")
         s = self.pool.new(ids[:n], n + 1)
         self.cache.add_sequence(s.seq_id, n)
         self._run([s])
@@ -589,6 +596,8 @@ class Model:
 
     def _run(self, seqs: Sequence[SequenceMeta], logits_all: bool = False) -> torch.Tensor:
         """Run the decoder over the pending inputs of `seqs`; returns this rank's logits slice."""
+        if self.ctx.dp_size > 1:
+            return self._dp_forward(seqs, logits_all)
         groups = self._groups(seqs)
         if self.ctx.pp_size > 1:
             return self._pp_forward(groups, logits_all)
@@ -599,6 +608,42 @@ class Model:
         name = "Next Token" if b.is_decode else "1st Token"
         with TimeLine(name), torch.no_grad():
             return dec.forward(b, self.cache)
+
+    def _dp_forward(self, seqs: Sequence[SequenceMeta], logits_all: bool) -> torch.Tensor:
+        """Data-parallel attention (XFT_ATTENTION_DP=1): every rank runs the decoder on the sequences it owns; inside
+        the MoE layers tokens visit the ranks that own their experts (Decoder._moe_dp).  All ranks know all sequences,
+        so each one can tell how many passes the busiest rank needs and joins the expert exchange of every pass, with
+        or without tokens of its own.  The logits rows are then gathered so that every rank returns the same
+        [rows, vocab] tensor, in the order of `seqs`, and steps its sequences identically."""
+        ctx = self.ctx
+        mine = [s for s in seqs if s.owner == ctx.dp_rank]
+        per_rank = [self._groups([s for s in seqs if s.owner == r]) if any(s.owner == r for s in seqs) else []
+                    for r in range(ctx.dp_size)]
+        n_pass = max(len(g) for g in per_rank)
+        my_groups = per_rank[ctx.dp_rank]
+        outs = []
+        with torch.no_grad():
+            for i in range(n_pass):
+                if i < len(my_groups):
+                    b = self.make_batch(my_groups[i], logits_all)
+                    dec = self.decoder if b.is_decode else self.prefill_decoder
+                    with TimeLine("Next Token" if b.is_decode else "1st Token"):
+                        outs.append(dec.forward(b, self.cache).float())
+                else:
+                    self.decoder.forward_idle()
+        rows_of = (lambda s: len(s.pending)) if logits_all else (lambda s: 1)
+        counts = [sum(rows_of(s) for s in seqs if s.owner == r) for r in range(ctx.dp_size)]
+        vocab = self.decoder.v1 - self.decoder.v0
+        local = torch.cat(outs, dim=0) if outs else torch.zeros(0, vocab, dtype=torch.float32, device=ctx.device)
+        assert local.shape[0] == counts[ctx.dp_rank], (local.shape, counts, len(mine))
+        parts = ctx.all_gather_rows(local, counts)
+        offs = [0] * ctx.dp_size
+        rows = []
+        for s in seqs:                              # back to the caller's order
+            n = rows_of(s)
+            rows.append(parts[s.owner][offs[s.owner]:offs[s.owner] + n])
+            offs[s.owner] += n
+        return torch.cat(rows, dim=0)
 
     def _pp_forward(self, groups: List[List[SequenceMeta]], logits_all: bool) -> torch.Tensor:
         """Pipeline stages over p2p send / recv of the hidden state (C8).  Every group is one micro-batch: a stage
@@ -661,6 +706,7 @@ class Model:
         self.cache.reserve(sum(self.cache.blocks_for(len(p) + 1) for p in prompts))
         for p in prompts:
             s = self.pool.new(p, len(p) + 1)
+            s.owner = s.seq_id % self.ctx.dp_size
             self.cache.add_sequence(s.seq_id)
             seqs.append(s)
         local = self._run(seqs, logits_all=True)

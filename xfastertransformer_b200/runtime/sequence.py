@@ -67,6 +67,7 @@ class SequenceMeta:
     done: bool = False
     group: int = -1                   # request index for beams
     prefix_len: int = 0               # tokens inherited from a shared prefix
+    owner: int = 0                    # data-parallel attention: the rank that holds this sequence's KV cache
 
     @property
     def total_len(self) -> int:
@@ -88,9 +89,10 @@ class SequencePool:
         self.seqs: Dict[int, SequenceMeta] = {}
         self.ids = SequenceIDManager()
 
-    def new(self, prompt: List[int], max_len: int, group: int = -1, seq_id: Optional[int] = None) -> SequenceMeta:
+    def new(self, prompt: List[int], max_len: int, group: int = -1, seq_id: Optional[int] = None,
+            owner: int = 0) -> SequenceMeta:
         sid = self.ids.create(self.seqs) if seq_id is None else seq_id
-        s = SequenceMeta(sid, list(prompt), max_len, pending=list(prompt), group=group)
+        s = SequenceMeta(sid, list(prompt), max_len, pending=list(prompt), group=group, owner=owner)
         self.seqs[sid] = s
         return s
 

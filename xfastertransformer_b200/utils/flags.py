@@ -54,6 +54,9 @@ class Env:
         self.cuda_graph = _int("XFT_CUDA_GRAPH", 1) != 0
         self.expert_parallel = _int("XFT_EXPERT_PARALLEL", 0) != 0
         self.fused_comm = _int("XFT_FUSED_COMM", 1) != 0
+        # data-parallel attention + expert-parallel MoE: every rank keeps the whole attention stack and runs it on its
+        # own share of the sequences; tokens travel to the ranks that own their experts and back (all-to-all)
+        self.attention_dp = _int("XFT_ATTENTION_DP", 0) != 0
         self.kv_cache_gb = float(e.get("XFT_KV_CACHE_GB", "0") or 0)
         self.max_batch_tokens = _int("XFT_MAX_BATCH_TOKENS", 8192)
         self.step_timeout_s = float(e.get("XFT_STEP_TIMEOUT_S", "0") or 0)
