@@ -414,3 +414,64 @@ def test_fused_prefill_allreduce_addressing_emulated(world, T, N):
         for blk in range(t_tiles):
             for nt in range(n_tiles):
                 assert (int(flag_res[r][blk * n_tiles + nt]) == epoch) == (blk % world != r)
+
+
+@pytest.mark.parametrize("world,E,k", [(2, 8, 2), (4, 8, 2), (8, 60, 4), (3, 8, 3)])
+def test_expert_exchange_addressing_emulated(world, E, k):
+    """The peer-memory expert exchange (csrc/kernels/ep_comm.cu) replayed on the CPU with the kernels' formulas: a pair
+    goes to slot [source][p] of the owner's receive area with {expert id, pair index}, comes back to the source's
+    return area at the pair index, and the weighted sum at home equals the dense reference.  Ranks may have no tokens."""
+    g = torch.Generator().manual_seed(world * 100 + E)
+    H, max_tokens = 16, 6
+    cap = pairs_cap = max_tokens * k
+    Ts = [int(torch.randint(0, max_tokens + 1, (1,), generator=g)) for _ in range(world)]
+    Ts[0] = 0                                                  # an idle rank
+    Ts[-1] = max_tokens
+    h = [torch.randn(T, H, generator=g) for T in Ts]
+    idx = [torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]) if T else torch.zeros(0, k, dtype=torch.long)
+           for T in Ts]
+    w = [torch.rand(T, k, generator=g) for T in Ts]
+    expert = [torch.randn(H, H, generator=g) * 0.3 for _ in range(E)]        # expert e: y = x @ M_e
+    owner = [P.expert_owner(e, E, world) for e in range(E)]
+    rx_tok = [torch.full((world * cap, H), float("nan")) for _ in range(world)]
+    rx_meta = [torch.full((world * cap, 2), -7, dtype=torch.long) for _ in range(world)]
+    rx_cnt = [[None] * world for _ in range(world)]
+    ret = [torch.full((pairs_cap, H), float("nan")) for _ in range(world)]
+    dest, slot = [], []
+    # plan + dispatch on every home rank
+    for r in range(world):
+        cnt = [0] * world
+        d_r, s_r = [], []
+        for i in range(Ts[r] * k):
+            e = int(idx[r].reshape(-1)[i])
+            d = owner[e]
+            p = cnt[d]
+            cnt[d] += 1
+            assert p < cap and i < pairs_cap
+            d_r.append(d)
+            s_r.append(p)
+            row = r * cap + p
+            assert bool(torch.isnan(rx_tok[d][row]).all())          # nobody else writes this slot
+            rx_tok[d][row] = h[r][i // k]
+            rx_meta[d][row, 0], rx_meta[d][row, 1] = e, i
+        for d in range(world):
+            rx_cnt[d][r] = cnt[d]
+        dest.append(d_r)
+        slot.append(s_r)
+    # receive + experts + return on every expert rank
+    for d in range(world):
+        e0, e1 = P.expert_range(E, world, d)
+        for j in range(world * cap):
+            s, q = j // cap, j % cap
+            if q >= rx_cnt[d][s]:
+                continue
+            e, pair = int(rx_meta[d][j, 0]), int(rx_meta[d][j, 1])
+            assert e0 <= e < e1 and 0 <= pair < pairs_cap             # only this rank's experts arrive here
+            assert bool(torch.isnan(ret[s][pair]).all())
+            ret[s][pair] = rx_tok[d][j] @ expert[e]
+    # combine at home
+    for r in range(world):
+        for t in range(Ts[r]):
+            got = sum(w[r][t, j] * ret[r][t * k + j] for j in range(k))
+            want = sum(w[r][t, j] * (h[r][t] @ expert[int(idx[r][t, j])]) for j in range(k))
+            assert torch.allclose(got, want, atol=1e-5)

@@ -589,6 +589,17 @@ class Decoder:
         T, H = h.shape[0], c.hidden_size
         E, k = c.sparse_experts, L.top_k
         dev = h.device
+        ep = getattr(ctx, "epcomm", None)
+        if ep is not None and h.is_cuda and ep.fits(ctx.dp_max_tokens, k):
+            # decode sizes, opt-in (XFT_MOE_FUSED_A2A=1): the rows cross NVLink as stores from the dispatch / return
+            # kernels, no host-side count exchange (csrc/kernels/ep_comm.cu).  dp_max_tokens is the largest local
+            # token count over the ranks in this pass, so all ranks take the same branch.
+            idx, w = self._route(L, h) if T > 0 else (None, None)
+            shared = None
+            if T > 0 and getattr(L, "shared", None) is not None:
+                shared = ops.linear(ops.linear_gated(h, L.shared[0], L.act), L.shared[1], out_dtype=torch.float32)
+            run = lambda rows, ids, ones: ops.moe_experts(rows, ids, ones, L.experts, L.act, L.e0, getattr(L, "packed", None))
+            return ep.exchange(h, idx, w, E, run, shared, x)
         if T > 0:
             idx, w = self._route(L, h)
             flat_e = idx.reshape(-1).long()

@@ -107,6 +107,8 @@ class DistContext:
         # reach them through `all_to_all`.  From here on the rank looks like a single-rank job (tp_size 1, every
         # tensor-parallel collective is the identity) with ep_size = dp_size = world.
         self.dp_size, self.dp_rank, self.dp_group = 1, 0, None
+        self.epcomm = None              # EpComm (peer-memory token exchange), set by the engine on GPUs when asked for
+        self.dp_max_tokens = 1 << 30    # largest local token count over the ranks in the current pass (engine sets it)
         if env.attention_dp and self.world > 1 and self.pp_size == 1:
             self.dp_size, self.dp_rank, self.dp_group = self.world, self.rank, self.tp_group
             self.tp_size, self.tp_rank, self.tp_group = 1, 0, None

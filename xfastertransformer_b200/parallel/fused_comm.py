@@ -271,3 +271,117 @@ class PeerComm:
         if self.base:
             self.lib.xft_comm_free(C.c_void_p(self.base))
             self.base = 0
+
+
+class EpParams(C.Structure):
+    """Mirror of the struct of the same name in csrc/kernels/ep_comm.cu."""
+    _fields_ = [("world", C.c_int), ("rank", C.c_int), ("rx_tok", C.c_void_p * 8), ("rx_meta", C.c_void_p * 8),
+                ("rx_cnt", C.c_void_p * 8), ("ret", C.c_void_p * 8), ("ret_flag", C.c_void_p * 8), ("epoch", C.c_void_p),
+                ("done", C.c_void_p), ("cap", C.c_int), ("pairs_cap", C.c_int), ("H", C.c_int),
+                ("wait_cycles", C.c_longlong), ("status", C.c_void_p)]
+
+
+class EpComm:
+    """Expert-parallel token exchange over peer memory for data-parallel attention (decode sizes): dispatch, receive,
+    return and combine kernels of csrc/kernels/ep_comm.cu around the grouped expert GEMMs.  One symmetric buffer per
+    rank, mapped by every peer through CUDA IPC: a receive area of `cap` rows per source rank, a return area of
+    `max_tokens * top_k` rows, count / flag words.  Nothing here synchronises with the host."""
+
+    def __init__(self, ctx, hidden: int, top_k: int, max_tokens: int = 64, wait_ms: float = 2000.0):
+        self.ctx = ctx
+        self.world, self.rank = ctx.dp_size, ctx.dp_rank
+        if not (2 <= self.world <= 8):
+            raise ValueError("EpComm supports 2..8 ranks")
+        lib = N.lib()
+        for fn in ("xft_comm_alloc", "xft_comm_free", "xft_comm_ipc_handle", "xft_comm_ipc_open", "xft_comm_ipc_close",
+                   "xft_comm_handle_bytes", "xft_ep_dispatch", "xft_ep_receive", "xft_ep_return", "xft_ep_combine"):
+            getattr(lib, fn).restype = C.c_int
+        self.lib = lib
+        self.H, self.k, self.max_tokens = hidden, top_k, max_tokens
+        self.cap = max_tokens * top_k                  # worst case: every pair of one source goes to one rank
+        self.pairs_cap = max_tokens * top_k
+        al = lambda v: (v + 255) // 256 * 256
+        self.off_tok = 0
+        self.off_meta = al(self.world * self.cap * hidden * 2)
+        self.off_cnt = al(self.off_meta + self.world * self.cap * 2 * 4)
+        self.off_ret = al(self.off_cnt + self.world * 8)
+        self.off_flag = al(self.off_ret + self.pairs_cap * hidden * 2)
+        self.nbytes = al(self.off_flag + self.world * 8)
+        base = C.c_void_p()
+        N._check(lib.xft_comm_alloc(C.c_size_t(self.nbytes), C.byref(base)), "comm_alloc")
+        self.base = base.value
+        hb = lib.xft_comm_handle_bytes()
+        h = (C.c_char * hb)()
+        N._check(lib.xft_comm_ipc_handle(C.c_void_p(self.base), h), "ipc_handle")
+        allh: List = [None] * ctx.world
+        dist.all_gather_object(allh, (ctx.rank, bytes(h)), group=ctx.ctrl_group)
+        self.peer_base: List[int] = []
+        self._opened: List[int] = []
+        for r in range(self.world):
+            if r == self.rank:
+                self.peer_base.append(self.base)
+                continue
+            p = C.c_void_p()
+            buf = (C.c_char * hb).from_buffer_copy(allh[r][1])
+            N._check(lib.xft_comm_ipc_open(buf, C.byref(p)), f"ipc_open(rank {r})")
+            self.peer_base.append(p.value)
+            self._opened.append(p.value)
+        dev = ctx.device
+        self.counters = torch.zeros(8, dtype=torch.int32, device=dev)          # [epoch, done x 3]
+        self.prm = EpParams()
+        q = self.prm
+        q.world, q.rank, q.cap, q.pairs_cap, q.H = self.world, self.rank, self.cap, self.pairs_cap, hidden
+        for r in range(self.world):
+            b = self.peer_base[r]
+            q.rx_tok[r], q.rx_meta[r], q.rx_cnt[r] = b + self.off_tok, b + self.off_meta, b + self.off_cnt
+            q.ret[r], q.ret_flag[r] = b + self.off_ret, b + self.off_flag
+        q.epoch = self.counters.data_ptr()
+        q.done = self.counters.data_ptr() + 4
+        q.wait_cycles = int(wait_ms * 1_900_000)
+        q.status = N.Workspace.get(dev).status.data_ptr()
+        rows = self.world * self.cap
+        self.dest = torch.empty(self.pairs_cap, dtype=torch.int32, device=dev)
+        self.slot = torch.empty(self.pairs_cap, dtype=torch.int32, device=dev)
+        self.cnt = torch.zeros(8, dtype=torch.int32, device=dev)
+        self.rx_idx = torch.empty(rows, 1, dtype=torch.int32, device=dev)
+        self.rx_cnt = torch.zeros(8, dtype=torch.int32, device=dev)
+        self.ones = torch.ones(rows, 1, dtype=torch.float32, device=dev)
+        self.rx_view = _view_bf16(self.base + self.off_tok, rows, hidden, dev, self)
+        self.exchanges = 0
+        dist.barrier(group=ctx.ctrl_group)
+
+    def fits(self, T: int, k: int) -> bool:
+        return T <= self.max_tokens and k == self.k
+
+    def exchange(self, h, idx, w, num_experts, run_experts, add_f32=None, residual=None):
+        """h [T, H] bf16 (T may be 0), idx / w [T, k]; run_experts(rows bf16 [R, H], expert ids int32 [R, 1], ones) ->
+        fp32 [R, H].  Returns sum_k w * expert(h) + add_f32 + residual as bf16 [T, H]."""
+        T = h.shape[0]
+        k = self.k
+        ws = N.Workspace.get(h.device)
+        st = N._stream()
+        x2, ldx = (h, self.H) if T == 0 else N._rows2d(h)
+        idx32 = idx if idx is None or idx.dtype == torch.int32 else idx.int()
+        N._check(self.lib.xft_ep_dispatch(N._p(x2 if T else None), ldx, N._p(idx32), T, k, num_experts, N._p(self.dest),
+                                          N._p(self.slot), N._p(self.cnt), C.byref(self.prm), st), "ep_dispatch")
+        N._check(self.lib.xft_ep_receive(N._p(self.rx_idx), N._p(self.rx_cnt), C.byref(self.prm), st), "ep_receive")
+        y = run_experts(self.rx_view, self.rx_idx, self.ones)
+        N._check(self.lib.xft_ep_return(N._p(y), N._p(self.rx_cnt), C.byref(self.prm), st), "ep_return")
+        out = torch.empty(T, self.H, dtype=torch.bfloat16, device=h.device)
+        r2, ldr = (None, 0)
+        if residual is not None and T:
+            r2, ldr = N._rows2d(residual)
+        wf = None if w is None else w.float().contiguous()
+        N._check(self.lib.xft_ep_combine(N._p(wf), N._p(self.dest), T, k, N._p(add_f32), N._p(r2), ldr, N._p(out),
+                                         C.byref(self.prm), st), "ep_combine")
+        ws.launches += 5
+        self.exchanges += 1
+        return out
+
+    def close(self) -> None:
+        for p in self._opened:
+            self.lib.xft_comm_ipc_close(C.c_void_p(p))
+        self._opened = []
+        if self.base:
+            self.lib.xft_comm_free(C.c_void_p(self.base))
+            self.base = 0

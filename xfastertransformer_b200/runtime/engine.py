@@ -91,6 +91,10 @@ class Model:
                 and self.ctx.tp_size <= 8:
             from ..parallel.fused_comm import PeerComm
             self.ctx.peer = PeerComm(self.ctx, n_max=self.cfg.hidden_size)
+        if self.ctx.device.type == "cuda" and self.ctx.dp_size > 1 and self.env.moe_fused_a2a and self.decoder.has_moe \
+                and self.ctx.epcomm is None and self.ctx.dp_size <= 8:
+            from ..parallel.fused_comm import EpComm
+            self.ctx.epcomm = EpComm(self.ctx, self.cfg.hidden_size, self.cfg.num_experts_per_tok)
         if self.ctx.device.type == "cuda":
             from .cuda_runner import CudaRunner
             self.runner = CudaRunner(self)
@@ -624,6 +628,7 @@ class Model:
         outs = []
         with torch.no_grad():
             for i in range(n_pass):
+                ctx.dp_max_tokens = max(sum(len(s.pending) for s in g[i]) if i < len(g) else 0 for g in per_rank)
                 if i < len(my_groups):
                     b = self.make_batch(my_groups[i], logits_all)
                     dec = self.decoder if b.is_decode else self.prefill_decoder

@@ -57,6 +57,7 @@ class Env:
         # data-parallel attention + expert-parallel MoE: every rank keeps the whole attention stack and runs it on its
         # own share of the sequences; tokens travel to the ranks that own their experts and back (all-to-all)
         self.attention_dp = _int("XFT_ATTENTION_DP", 0) != 0
+        self.moe_fused_a2a = _int("XFT_MOE_FUSED_A2A", 0) != 0      # with attention_dp: token exchange as peer-memory stores
         self.kv_cache_gb = float(e.get("XFT_KV_CACHE_GB", "0") or 0)
         self.max_batch_tokens = _int("XFT_MAX_BATCH_TOKENS", 8192)
         self.step_timeout_s = float(e.get("XFT_STEP_TIMEOUT_S", "0") or 0)
