@@ -182,17 +182,27 @@ def main():
     sync_all()
     wall0 = time.perf_counter()
     step_ms = []
+    eager_events = []            # steps that do not go through the graph runner (pipeline stages, data-parallel attention)
+    launches_ws0 = ws.launches
     for _ in range(args.steps):
         t1 = time.perf_counter()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
         model.forward()
+        e1.record()
+        eager_events.append((e0, e1))
         step_ms.append((time.perf_counter() - t1) * 1e3)
     sync_all()
     wall = time.perf_counter() - wall0
     clocks = _clock_summary(sampler, spath, dev.index or 0) if rank == 0 else None
-    dev_ms = sum(a.elapsed_time(b) for a, b in runner.step_events)
+    if len(runner.step_events) == args.steps:
+        dev_ms = sum(a.elapsed_time(b) for a, b in runner.step_events)
+        n_launch = runner.kernel_launches - launches0
+    else:
+        dev_ms = sum(a.elapsed_time(b) for a, b in eager_events)
+        n_launch = ws.launches - launches_ws0
     runner.timing = False
     ws.check_status()
-    n_launch = runner.kernel_launches - launches0
     t = torch.tensor([dev_ms, wall * 1e3, ttft_ms, ttft_cold_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -208,7 +218,10 @@ def main():
             "scaling": "strong", "vs_baseline": None, "dtype": args.dtype,
             "data": "synthetic token ids; random-init N(0,0.02) weights of the named architecture",
             "config": {"model": args.model, "global_batch": B, "seq_len": L, "output_len": total_new,
-                       "parallelism": f"tp{world}", "kv_cache": f"paged-64 {args.kv_dtype}",
+                       "parallelism": (f"dp{world}+ep{world}" if m.ctx.dp_size > 1 else
+                                       f"pp{m.ctx.pp_size}xtp{m.ctx.tp_size}" if m.ctx.pp_size > 1 else
+                                       f"tp{world}+ep{world}" if m.ctx.ep_size > 1 else f"tp{world}"),
+                       "kv_cache": f"paged-64 {args.kv_dtype}",
                        "l2": "inputs larger than L2 (each step streams %.1f GB of weights per GPU)" % (wbytes / 1e9),
                        "layers": cfg.num_layer},
             "ttft_ms": round(ttft_ms, 2), "ttft_cold_ms": round(ttft_cold_ms, 2),
