@@ -13,6 +13,10 @@ words, each {fp32 value, epoch}.  The epoch next to a value tells the reader it 
 latency of the collective is one NVLink store propagation: no fence, flag or barrier in between.  A
 device-side epoch counter (bumped by the last CTA of every launch) selects the parity, so CUDA-graph
 replays stay in step without host involvement.
+
+Also here, both opt-in: the plumbing of the fused prefill GEMM + reduce-scatter + all-gather kernel
+(``PeerComm.gemm_ar_bulk``, csrc/kernels/gemm_prefill_sm100.cu) and `EpComm`, the expert-parallel token exchange of
+data-parallel attention (csrc/kernels/ep_comm.cu).
 """
 from __future__ import annotations
 
@@ -48,6 +52,32 @@ class _RawCuda:
 
 def _view_bf16(ptr: int, rows: int, cols: int, device, owner) -> torch.Tensor:
     return torch.as_tensor(_RawCuda(ptr, (rows, cols), owner), device=device).view(torch.bfloat16)
+
+
+def _symmetric_alloc(ctx, lib, nbytes: int, first: int, world: int, rank: int):
+    """Allocate `nbytes` (zeroed) on this GPU and map the same allocation of the other `world - 1` ranks of the group
+    that starts at global rank `first` (CUDA IPC).  Returns (own base address, base address per group rank, the peer
+    mappings to close later).  Collective over ctx.ctrl_group."""
+    base = C.c_void_p()
+    N._check(lib.xft_comm_alloc(C.c_size_t(nbytes), C.byref(base)), "comm_alloc")
+    hb = lib.xft_comm_handle_bytes()
+    h = (C.c_char * hb)()
+    N._check(lib.xft_comm_ipc_handle(C.c_void_p(base.value), h), "ipc_handle")
+    allh: List = [None] * ctx.world
+    dist.all_gather_object(allh, (ctx.rank, bytes(h)), group=ctx.ctrl_group)
+    peer_base: List[int] = []
+    opened: List[int] = []
+    for r in range(world):
+        if r == rank:
+            peer_base.append(base.value)
+            continue
+        grank, hbytes = allh[first + r]
+        p = C.c_void_p()
+        buf = (C.c_char * hb).from_buffer_copy(hbytes)
+        N._check(lib.xft_comm_ipc_open(buf, C.byref(p)), f"ipc_open(rank {grank})")
+        peer_base.append(p.value)
+        opened.append(p.value)
+    return base.value, peer_base, opened
 
 
 class BulkArParams(C.Structure):
@@ -92,28 +122,8 @@ class PeerComm:
             self._b_off_fr = al(self._b_off_fp + nfp.value * 4)
             nbytes = al(self._b_off_fr + nfr.value * 4)
         self.nbytes = nbytes
-        base = C.c_void_p()
-        N._check(lib.xft_comm_alloc(C.c_size_t(nbytes), C.byref(base)), "comm_alloc")
-        self.base = base.value
-        hb = lib.xft_comm_handle_bytes()
-        h = (C.c_char * hb)()
-        N._check(lib.xft_comm_ipc_handle(C.c_void_p(self.base), h), "ipc_handle")
-        mine = (ctx.rank, bytes(h))
-        allh: List = [None] * ctx.world
-        dist.all_gather_object(allh, mine, group=ctx.ctrl_group)
-        first = ctx.pp_rank * ctx.tp_size
-        self.peer_base: List[int] = []
-        self._opened: List[int] = []
-        for r in range(self.world):
-            if r == self.rank:
-                self.peer_base.append(self.base)
-                continue
-            grank, hbytes = allh[first + r]
-            p = C.c_void_p()
-            buf = (C.c_char * hb).from_buffer_copy(hbytes)
-            N._check(lib.xft_comm_ipc_open(buf, C.byref(p)), f"ipc_open(rank {grank})")
-            self.peer_base.append(p.value)
-            self._opened.append(p.value)
+        self.base, self.peer_base, self._opened = _symmetric_alloc(ctx, lib, nbytes, ctx.pp_rank * ctx.tp_size,
+                                                                   self.world, self.rank)
         self.counters = torch.zeros(4, dtype=torch.int32, device=ctx.device)   # [epoch, done]
         clock_khz = 1_900_000
         self.wait_cycles = int(wait_ms * clock_khz)
@@ -307,25 +317,7 @@ class EpComm:
         self.off_ret = al(self.off_cnt + self.world * 8)
         self.off_flag = al(self.off_ret + self.pairs_cap * hidden * 2)
         self.nbytes = al(self.off_flag + self.world * 8)
-        base = C.c_void_p()
-        N._check(lib.xft_comm_alloc(C.c_size_t(self.nbytes), C.byref(base)), "comm_alloc")
-        self.base = base.value
-        hb = lib.xft_comm_handle_bytes()
-        h = (C.c_char * hb)()
-        N._check(lib.xft_comm_ipc_handle(C.c_void_p(self.base), h), "ipc_handle")
-        allh: List = [None] * ctx.world
-        dist.all_gather_object(allh, (ctx.rank, bytes(h)), group=ctx.ctrl_group)
-        self.peer_base: List[int] = []
-        self._opened: List[int] = []
-        for r in range(self.world):
-            if r == self.rank:
-                self.peer_base.append(self.base)
-                continue
-            p = C.c_void_p()
-            buf = (C.c_char * hb).from_buffer_copy(allh[r][1])
-            N._check(lib.xft_comm_ipc_open(buf, C.byref(p)), f"ipc_open(rank {r})")
-            self.peer_base.append(p.value)
-            self._opened.append(p.value)
+        self.base, self.peer_base, self._opened = _symmetric_alloc(ctx, lib, self.nbytes, 0, self.world, self.rank)
         dev = ctx.device
         self.counters = torch.zeros(8, dtype=torch.int32, device=dev)          # [epoch, done x 3]
         self.prm = EpParams()
