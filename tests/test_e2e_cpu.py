@@ -81,13 +81,16 @@ def test_pipeline_parallel_two_stages_gloo(tiny, tmp_path):
     assert sorted(got["layers"]) == [(0, 1, 0, 0), (1, 2, 1, 0)]
 
 
-def test_cb_follower_loop_and_greedy_fast_path(tiny, tmp_path):
+@pytest.mark.parametrize("dp", [0, 1])
+def test_cb_follower_loop_and_greedy_fast_path(tiny, tmp_path, dp):
     """Two gloo ranks: rank 1 only runs follow_cb(); rank 0 mixes forward_cb_greedy and forward_cb steps.  Tokens equal
-    the single-process greedy continuation and the follower exits on shutdown."""
+    the single-process greedy continuation and the follower exits on shutdown.  dp = 1: the same under
+    XFT_ATTENTION_DP=1 (a dense model: each rank serves its own sequences with the full weights)."""
     out = str(tmp_path / "cbf.pt")
-    env = dict(os.environ, XFT_ENGINE="CPU", PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    env = dict(os.environ, XFT_ENGINE="CPU", XFT_ATTENTION_DP=str(dp),
+               PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", "29615", os.path.join(ROOT, "tests", "cb_follow_worker.py"), tiny, out]
+           "127.0.0.1", "--master-port", str(29615 + 40 * dp), os.path.join(ROOT, "tests", "cb_follow_worker.py"), tiny, out]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     got = torch.load(out)["tokens"]
