@@ -204,8 +204,10 @@ class PeerComm:
 
     # ------------------------------------------------------------------------------------
     def can_fuse_bulk(self, T: int, n: int, K: int, kind: str) -> bool:
-        return (self.bulk is not None and kind == "bf16" and self.T_CAP < T <= self.bulk_tokens and n <= self.n_max
-                and K % 8 == 0)
+        """Must give the same answer on every rank (a rank that took the unfused path would leave the others waiting),
+        so it looks only at what all ranks share: token count, output width, weight type.  A slice whose K is not a
+        multiple of 8 is rejected by the kernel's entry point with an error on that rank."""
+        return self.bulk is not None and kind == "bf16" and self.T_CAP < T <= self.bulk_tokens and n <= self.n_max
 
     def _bulk_order(self, T: int, device) -> torch.Tensor:
         from .partition import block_visit_order
