@@ -157,7 +157,7 @@ __global__ void __launch_bounds__(1024) ep_receive_kernel(const EpParams p, int*
   const int total = p.world * p.cap;
   for (int j = threadIdx.x; j < total; j += blockDim.x) {
     const int s = j / p.cap, q = j % p.cap;
-    idx_out[j] = (!s_fail && q < s_cnt[s]) ? p.rx_meta[p.rank][(size_t)j * 2] : -1;
+    idx_out[j] = (!s_fail && q < s_cnt[s]) ? __ldcg(p.rx_meta[p.rank] + (size_t)j * 2) : -1;   // written by a peer: read at L2
   }
   if (threadIdx.x < p.world) cnt_out[threadIdx.x] = s_fail ? 0 : s_cnt[threadIdx.x];
 }
@@ -171,7 +171,7 @@ __global__ void __launch_bounds__(128) ep_return_kernel(const float* __restrict_
   const int j = blockIdx.x;
   const int s = j / p.cap, q = j % p.cap;
   if (s < p.world && q < cnt[s]) {
-    const int pair = p.rx_meta[p.rank][(size_t)j * 2 + 1];
+    const int pair = __ldcg(p.rx_meta[p.rank] + (size_t)j * 2 + 1);
     if (pair >= 0 && pair < p.pairs_cap) {
       const float4* src = reinterpret_cast<const float4*>(y + (size_t)j * p.H);
       uint2* dst = reinterpret_cast<uint2*>(p.ret[s] + (size_t)pair * p.H);
