@@ -25,6 +25,8 @@
 // accumulator.
 #include "ptx.cuh"
 
+#include <cstdlib>
+
 namespace xft {
 
 int make_tensor_map(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
@@ -54,6 +56,7 @@ struct PrefillParams {
   int n_tiles, t_tiles, num_kb, stages;
   int gn;                     // feature tiles per group: a group sweeps all token blocks before the next one starts
   const int* order;           // optional: i-th visited token block (a permutation of 0..t_tiles-1)
+  int wide;                   // != 0: bf16 rows leave through shared memory as 256-byte runs (full 128-feature tiles)
   int* status;
   BulkArParams ar;
 };
@@ -133,6 +136,10 @@ __global__ void __launch_bounds__(192, 1) gemm_prefill_kernel(const __grid_const
   __shared__ uint64_t full_bar[kPrefillMaxStages], empty_bar[kPrefillMaxStages], tmem_full[2], tmem_empty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_abort_mem, s_epoch, s_last;
+  // wide stores: 16 token rows x 128 features of bf16, rows padded by 8 elements so that both the per-feature writes
+  // and the 16-byte row reads spread over the banks
+  constexpr int kStageLd = 128 + 8;
+  __shared__ __align__(16) __nv_bfloat16 s_stage[16 * kStageLd];
   volatile int* s_abort = &s_abort_mem;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -267,6 +274,25 @@ __global__ void __launch_bounds__(192, 1) gemm_prefill_kernel(const __grid_const
           __syncwarp();
           if (lane == 0) mbar_arrive(&tmem_empty[a]);
         }
+        // full 128-feature tile and the caller asked for it: rows go out as 256-byte runs through shared memory.
+        // Uniform over the 128 epilogue threads (it depends on the tile only), so the barriers inside are safe.
+        const bool wide = p.wide && (nt * 128 + 128 <= p.N) && (p.N % 8 == 0) && (p.ldo % 8 == 0);
+        if (!owned && wide) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) s_stage[j * kStageLd + row] = __float2bfloat16(__uint_as_float(v[j]));
+          named_bar_sync(1, 128);
+          __nv_bfloat16* base = p.ar.part[owner] + (size_t)rank * p.ar.part_stride +
+                                ((size_t)own_idx * BN + c) * p.N + nt * 128;
+#pragma unroll
+          for (int it = 0; it < 2; ++it) {
+            const int j = (et >> 4) + 8 * it, seg = et & 15;          // 16 threads write one 256-byte row
+            if (t0 + c + j < p.T)
+              *reinterpret_cast<uint4*>(base + (size_t)j * p.N + seg * 8) =
+                  *reinterpret_cast<const uint4*>(&s_stage[j * kStageLd + seg * 8]);
+          }
+          named_bar_sync(1, 128);                                      // the buffer is reused by the next chunk
+          continue;
+        }
         if (!n_ok) continue;
         if (!owned) {
           __nv_bfloat16* dst = p.ar.part[owner] + (size_t)rank * p.ar.part_stride +
@@ -304,12 +330,32 @@ __global__ void __launch_bounds__(192, 1) gemm_prefill_kernel(const __grid_const
             float y = prefill_act(x[j] + bias, p.act);
             if (p.residual) y += p.res_scale * __bfloat162float(p.residual[(size_t)t * p.ldr + n]);
             const __nv_bfloat16 yb = __float2bfloat16(y);
-            if (world > 1) {
+            if (wide) {
+              s_stage[j * kStageLd + row] = yb;
+            } else if (world > 1) {
               for (int r = 0; r < world; ++r) p.ar.out[r][(size_t)t * p.ldo + n] = yb;
             } else {
               p.out[(size_t)t * p.ldo + n] = yb;
             }
           }
+        }
+        if (wide) {
+          named_bar_sync(1, 128);
+#pragma unroll
+          for (int it = 0; it < 2; ++it) {
+            const int j = (et >> 4) + 8 * it, seg = et & 15;
+            const int t = t0 + c + j;
+            if (t < p.T) {
+              const uint4 val = *reinterpret_cast<const uint4*>(&s_stage[j * kStageLd + seg * 8]);
+              const size_t off = (size_t)t * p.ldo + nt * 128 + seg * 8;
+              if (world > 1) {
+                for (int r = 0; r < world; ++r) *reinterpret_cast<uint4*>(p.ar.out[r] + off) = val;
+              } else {
+                *reinterpret_cast<uint4*>(p.out + off) = val;
+              }
+            }
+          }
+          named_bar_sync(1, 128);
         }
       }
       if (world > 1) {
@@ -409,6 +455,8 @@ extern "C" int xft_gemm_bf16_prefill(const void* X, int ldx, const void* W, int 
   p.N = N; p.T = T; p.K = K; p.out = reinterpret_cast<__nv_bfloat16*>(Y); p.ldo = ldo; p.bias = bias;
   p.residual = reinterpret_cast<const __nv_bfloat16*>(residual); p.ldr = ldr; p.res_scale = res_scale; p.act = act;
   p.order = order; p.status = status;
+  static const int wide_env = [] { const char* v = getenv("XFT_PREFILL_WIDE_STORES"); return v && v[0] == '1' ? 1 : 0; }();
+  p.wide = wide_env;
   const int bn = T > 128 ? 256 : 128;
   p.n_tiles = (N + 127) / 128;
   p.t_tiles = (T + bn - 1) / bn;

@@ -75,14 +75,26 @@ def test_linear_takes_the_persistent_kernel_when_asked(monkeypatch):
     assert (a.float() - b.float()).abs().max().item() < 2e-2
 
 
+def test_persistent_gemm_with_wide_stores():
+    """The same single-GPU cases with XFT_PREFILL_WIDE_STORES=1 (rows leave through shared memory as 256-byte runs); the
+    switch is read once per process, hence the child process."""
+    if os.environ.get("XFT_PREFILL_WIDE_STORES") == "1":
+        pytest.skip("already the wide-store run")
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.abspath(__file__), "-q", "-x", "-k", "matches_fp32"],
+                       env=dict(os.environ, XFT_PREFILL_WIDE_STORES="1"), capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+
+
+@pytest.mark.parametrize("wide", [0, 1])
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_fused_prefill_gemm_allreduce(world, tmp_path):
+def test_fused_prefill_gemm_allreduce(world, wide, tmp_path):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     out = str(tmp_path / "r.pt")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", XFT_PREFILL_WIDE_STORES=str(wide),
+               PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
-           "127.0.0.1", "--master-port", str(29700 + world), os.path.join(ROOT, "tests", "prefill_ar_worker.py"), out]
+           "127.0.0.1", "--master-port", str(29700 + 2 * world + wide), os.path.join(ROOT, "tests", "prefill_ar_worker.py"), out]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     got = torch.load(out)
