@@ -12,6 +12,9 @@ graphs of 16 back-to-back calls over distinct weight copies (so weights stream f
   nccl          the partial GEMM followed by an NCCL all-reduce (eager launches; the PyTorch baseline)
 and reports the fused kernel against its roofline: the slower of (weight bytes / measured HBM rate) and
 (bytes that must cross NVLink per GPU / 770 GB/s).
+
+`--prefill [tokens]` times the prefill-size kernel instead (persistent GEMM with reduce-scatter + all-gather fused in,
+opt-in path of the engine) against GEMM + NCCL all-reduce.
 """
 import json
 import os
@@ -73,9 +76,59 @@ def eager_time(fn, n_calls, iters=10):
     return ts[len(ts) // 2]
 
 
+def prefill(ctx, peaks, tokens):
+    """Prefill sizes (`--prefill`): the row-parallel GEMMs of Llama-2-70B over `tokens` rows, eager launches, max over
+    ranks: the partial GEMM alone, the persistent kernel with reduce-scatter + all-gather fused in
+    (PeerComm.gemm_ar_bulk), and GEMM followed by an NCCL all-reduce.  Roofline of the fused kernel: the slower of
+    FLOPs / measured bf16 rate and the bytes a GPU must send, 2 (w-1)/w T N 2 B, over 770 GB/s."""
+    world, rank, dev = ctx.world, ctx.rank, ctx.device
+    os.environ["XFT_PREFILL_FUSED_AR"] = "1"
+    os.environ["XFT_MAX_BATCH_TOKENS"] = str(tokens)
+    peer = PeerComm(ctx, n_max=8192)
+    H = 8192
+    for name, K in (("o_proj", 8192 // world), ("down_proj", 28672 // world)):
+        K = (K + 63) // 64 * 64
+        W = make_linear((torch.randn(H, K, device=dev, dtype=torch.bfloat16) * 0.02), "bf16")
+        x = torch.randn(tokens, K, device=dev, dtype=torch.bfloat16)
+        resid = torch.randn(tokens, H, device=dev, dtype=torch.bfloat16)
+        t_gemm = eager_time(lambda i: N.gemm_bf16(x, W.w, H, residual=resid), 4)
+        t_fused = eager_time(lambda i: peer.gemm_ar_bulk(x, W, None, None, resid, 1.0), 4)
+
+        def nccl(i):
+            y = N.gemm_bf16(x, W.w, H, residual=resid)
+            dist.all_reduce(y)
+        t_nccl = eager_time(nccl, 4)
+        t = torch.tensor([t_gemm, t_fused, t_nccl], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t_gemm, t_fused, t_nccl = t.tolist()
+        flops = 2.0 * tokens * H * K
+        link_bytes = 2.0 * (world - 1) / world * tokens * H * 2
+        roof_ms = max(flops / (peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops", 1400.0)) * 1e12),
+                      link_bytes / 770e9) * 1e3
+        if rank == 0:
+            print(json.dumps({"shape": f"{name} T={tokens} N={H} K={K}", "world": world, "gemm_us": round(t_gemm * 1e3, 1),
+                              "fused_us": round(t_fused * 1e3, 1), "gemm_plus_nccl_us": round(t_nccl * 1e3, 1),
+                              "roofline_us": round(roof_ms * 1e3, 1), "fused_frac_of_roofline": round(roof_ms / t_fused, 3),
+                              "fused_vs_nccl": round(t_nccl / t_fused, 2),
+                              "wide_stores": os.environ.get("XFT_PREFILL_WIDE_STORES", "0")}), flush=True)
+    N.Workspace.get(dev).check_status()
+    dist.barrier()
+    peer.close()
+    dist.destroy_process_group()
+
+
 def main():
     ctx = DistContext.get()
     world, rank, dev = ctx.world, ctx.rank, ctx.device
+    if "--prefill" in sys.argv:
+        peaks = {"hbm_gbs": 6459.6, "bf16_tflops": 1590.0}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        i = sys.argv.index("--prefill")
+        tokens = int(sys.argv[i + 1]) if len(sys.argv) > i + 1 and sys.argv[i + 1].isdigit() else 8192
+        return prefill(ctx, peaks, tokens)
     peer = PeerComm(ctx, n_max=8192)
     peaks = {"hbm_gbs": 6459.6}
     try:
