@@ -55,6 +55,7 @@ struct PrefillParams {
   int act;
   int n_tiles, t_tiles, num_kb, stages;
   int gn;                     // feature tiles per group: a group sweeps all token blocks before the next one starts
+  int dual_off;               // gated form: W row of the first "up" feature (gate rows are [0, dual_off)); bias likewise
   const int* order;           // optional: i-th visited token block (a permutation of 0..t_tiles-1)
   int wide;                   // != 0: bf16 rows leave through shared memory as 256-byte runs (full 128-feature tiles)
   int* status;
@@ -120,16 +121,21 @@ __device__ __forceinline__ bool mbar_wait_or_abort(uint64_t* bar, uint32_t parit
 
 constexpr int kPrefillMaxStages = 8;
 
-template <int BN>
+// DUAL: gated form (column-parallel gate ‖ up projection, no reduction over ranks): two weight tiles, gate rows n and up
+// rows dual_off + n, share one token tile and feed two accumulators; the epilogue stores act(gate) * up.  With BN = 128
+// the four accumulators (2 x double buffer) fill the 512 TMEM columns and a stage moves the same bytes per FLOP as the
+// plain 128 x 256 tile.
+template <int BN, bool DUAL>
 __global__ void __launch_bounds__(192, 1) gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmW,
                                                               const __grid_constant__ CUtensorMap tmX,
                                                               const PrefillParams p) {
   constexpr int A_BYTES = 128 * 64 * 2;
   constexpr int B_BYTES = BN * 64 * 2;
-  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr uint32_t TMEM_COLS = 2 * BN;                 // two accumulators of BN fp32 columns
+  constexpr int NACC = DUAL ? 2 : 1;
+  constexpr int STAGE_BYTES = A_BYTES * NACC + B_BYTES;
+  constexpr uint32_t TMEM_COLS = 2 * BN * NACC;          // double-buffered accumulators of BN fp32 columns each
   constexpr uint32_t IDESC = umma_idesc(128, BN, 1, 1, 1);
-  static_assert(BN == 128 || BN == 256, "token tile of the prefill kernel");
+  static_assert(BN == 128 || (BN == 256 && !DUAL), "token tile of the prefill kernel");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -193,7 +199,8 @@ __global__ void __launch_bounds__(192, 1) gemm_prefill_kernel(const __grid_const
           mbar_expect_tx(&full_bar[s], STAGE_BYTES);
           uint8_t* a = smem + s * STAGE_BYTES;
           tma_load_2d(a, &tmW, &full_bar[s], kb * 64, nt * 128, hint);
-          tma_load_2d(a + A_BYTES, &tmX, &full_bar[s], kb * 64, blk * BN, hint);
+          if (DUAL) tma_load_2d(a + A_BYTES, &tmW, &full_bar[s], kb * 64, p.dual_off + nt * 128, hint);
+          tma_load_2d(a + A_BYTES * NACC, &tmX, &full_bar[s], kb * 64, blk * BN, hint);
         }
       }
       if (!ok) {
@@ -212,7 +219,7 @@ __global__ void __launch_bounds__(192, 1) gemm_prefill_kernel(const __grid_const
         const uint32_t aph = (lt >> 1) & 1;
         if (*s_abort || !mbar_wait_or_abort(&tmem_empty[a], aph ^ 1, p.status, XFT_ERR_WAIT_TMEM, s_abort)) break;
         tcgen05_fence_after();
-        const uint32_t acc = tmem_base + (uint32_t)(a * BN);
+        const uint32_t acc = tmem_base + (uint32_t)(a * BN * NACC);
         for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
           const int s = it % stages;
           const uint32_t ph = (it / stages) & 1;
@@ -223,10 +230,15 @@ __global__ void __launch_bounds__(192, 1) gemm_prefill_kernel(const __grid_const
           tcgen05_fence_after();
           const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
           const uint64_t adesc = umma_desc_k128(a_addr);
-          const uint64_t bdesc = umma_desc_k128(a_addr + A_BYTES);
+          const uint64_t bdesc = umma_desc_k128(a_addr + A_BYTES * NACC);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)          // 4 x (K = 16) per 64-wide k-block; +32 B = +2 in the address field
+          for (int k = 0; k < 4; ++k) {        // 4 x (K = 16) per 64-wide k-block; +32 B = +2 in the address field
             umma_bf16(acc, adesc + 2 * k, bdesc + 2 * k, IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+            if (DUAL) {
+              const uint64_t a1desc = umma_desc_k128(a_addr + A_BYTES);
+              umma_bf16(acc + BN, a1desc + 2 * k, bdesc + 2 * k, IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+            }
+          }
           tcgen05_commit(&empty_bar[s]);
         }
         if (ok) tcgen05_commit(&tmem_full[a]);
@@ -258,15 +270,18 @@ __global__ void __launch_bounds__(192, 1) gemm_prefill_kernel(const __grid_const
       named_bar_sync(1, 128);                  // every epilogue thread sees the same abort state from here on
       if (*s_abort) break;
       tcgen05_fence_after();
-      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + (uint32_t)(a * BN);
+      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + (uint32_t)(a * BN * NACC);
       const int n = nt * 128 + row;
       const bool n_ok = n < p.N;
       const int t0 = blk * BN;
       const float bias = (p.bias && n_ok) ? p.bias[n] : 0.f;
+      const float bias_u = (DUAL && p.bias && n_ok) ? p.bias[p.dual_off + n] : 0.f;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 16) {
         uint32_t v[16];
+        uint32_t vu[DUAL ? 16 : 1];
         tmem_ld16(taddr + c, v);
+        if constexpr (DUAL) tmem_ld16(taddr + BN + c, vu);
         tmem_ld_wait();
         if (c + 16 >= BN) {
           // the accumulator is in registers: hand the TMEM buffer back to the MMA warp before the stores
@@ -328,6 +343,7 @@ __global__ void __launch_bounds__(192, 1) gemm_prefill_kernel(const __grid_const
           const int t = t0 + c + j;
           if (t < p.T) {
             float y = prefill_act(x[j] + bias, p.act);
+            if constexpr (DUAL) y *= __uint_as_float(vu[j]) + bias_u;
             if (p.residual) y += p.res_scale * __bfloat162float(p.residual[(size_t)t * p.ldr + n]);
             const __nv_bfloat16 yb = __float2bfloat16(y);
             if (wide) {
@@ -405,24 +421,24 @@ __global__ void __launch_bounds__(192, 1) gemm_prefill_kernel(const __grid_const
   }
 }
 
-template <int BN>
+template <int BN, bool DUAL>
 static int launch_prefill(const CUtensorMap& tmW, const CUtensorMap& tmX, PrefillParams& p, int num_ctas,
                           cudaStream_t st) {
-  constexpr int STAGE_BYTES = 128 * 64 * 2 + BN * 64 * 2;
+  constexpr int STAGE_BYTES = 128 * 64 * 2 * (DUAL ? 2 : 1) + BN * 64 * 2;
   int stages = (220 * 1024) / STAGE_BYTES;
   if (stages > kPrefillMaxStages) stages = kPrefillMaxStages;
   p.stages = stages;
   const size_t smem = (size_t)stages * STAGE_BYTES + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_prefill_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) !=
+    if (cudaFuncSetAttribute(gemm_prefill_kernel<BN, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) !=
         cudaSuccess)
       return 3000 + (int)cudaGetLastError();
     attr_set = true;
   }
   const int total = p.n_tiles * p.t_tiles;
   const int grid = total < num_ctas ? total : num_ctas;
-  gemm_prefill_kernel<BN><<<grid, 192, smem, st>>>(tmW, tmX, p);
+  gemm_prefill_kernel<BN, DUAL><<<grid, 192, smem, st>>>(tmW, tmX, p);
   return (int)cudaGetLastError();
 }
 
@@ -482,5 +498,36 @@ extern "C" int xft_gemm_bf16_prefill(const void* X, int ldx, const void* W, int 
   if (r) return 1000 - r;
   r = make_tensor_map(&tmX, X, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, (uint32_t)bn, 2);
   if (r) return 2000 - r;
-  return bn == 256 ? launch_prefill<256>(tmW, tmX, p, num_ctas, st) : launch_prefill<128>(tmW, tmX, p, num_ctas, st);
+  return bn == 256 ? launch_prefill<256, false>(tmW, tmX, p, num_ctas, st)
+                   : launch_prefill<128, false>(tmW, tmX, p, num_ctas, st);
+}
+
+// Gated form: Y[T, N] = act(X Wg^T + bias_g) * (X Wu^T + bias_u), W holds gate rows [0, N) and up rows
+// [dual_off, dual_off + N) (bias likewise).  Token tiles of 128.
+extern "C" int xft_gemm_bf16_prefill_gated(const void* X, int ldx, const void* W, int w_rows, int ldw, void* Y, int ldo,
+                                           int T, int N, int K, int dual_off, const float* bias, int act, int* status,
+                                           int num_ctas, cudaStream_t st) {
+  if (T <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K & 7) || (ldx & 7) || (ldw & 7)) return -2;
+  PrefillParams p{};
+  p.N = N; p.T = T; p.K = K; p.out = reinterpret_cast<__nv_bfloat16*>(Y); p.ldo = ldo; p.bias = bias; p.act = act;
+  p.status = status; p.dual_off = dual_off;
+  static const int wide_env = [] { const char* v = getenv("XFT_PREFILL_WIDE_STORES"); return v && v[0] == '1' ? 1 : 0; }();
+  p.wide = wide_env;
+  p.n_tiles = (N + 127) / 128;
+  p.t_tiles = (T + 127) / 128;
+  p.num_kb = (K + 63) / 64;
+  p.gn = 16;
+  if (num_ctas <= 0) {
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    num_ctas = sms > 0 ? sms : 148;
+  }
+  CUtensorMap tmW, tmX;
+  int r = make_tensor_map(&tmW, W, (uint64_t)w_rows, (uint64_t)K, (uint64_t)ldw, 128, 2);
+  if (r) return 1000 - r;
+  r = make_tensor_map(&tmX, X, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, 128, 2);
+  if (r) return 2000 - r;
+  return launch_prefill<128, true>(tmW, tmX, p, num_ctas, st);
 }

@@ -57,6 +57,29 @@ def test_persistent_gemm_matches_fp32(T, N, K):
     assert torch.equal(got2, _call(x, w, N))       # the schedule does not change the numbers
 
 
+@pytest.mark.parametrize("T,N,K", [(130, 256, 128), (1000, 1408, 512), (4096, 3584, 1024)])
+def test_persistent_gated_gemm_matches_fp32(T, N, K):
+    """Gated form: silu(x Wg^T + bg) * (x Wu^T + bu) with gate rows [0, N) and up rows [N, 2N) of one weight."""
+    from xfastertransformer_b200.ops import native as N_
+    g = torch.Generator().manual_seed(T + N)
+    x = (torch.randn(T, K, generator=g) * 0.5).bfloat16().cuda()
+    w = (torch.randn(2 * N, K, generator=g) * 0.05).bfloat16().cuda()
+    bias = (torch.randn(2 * N, generator=g) * 0.1).cuda()
+    out = torch.empty(T, N, dtype=torch.bfloat16, device="cuda")
+    ws = N_.Workspace.get(x.device)
+    lib = N_.lib()
+    lib.xft_gemm_bf16_prefill_gated.restype = C.c_int
+    rc = lib.xft_gemm_bf16_prefill_gated(N_._p(x), K, N_._p(w), 2 * N, K, N_._p(out), N, T, N, K, N, N_._p(bias),
+                                         N_._ACT["silu"], N_._p(ws.status), 0, N_._stream())
+    assert rc == 0, rc
+    torch.cuda.synchronize()
+    ws.check_status()
+    y = x.float() @ w.float().t() + bias
+    want = torch.nn.functional.silu(y[:, :N]) * y[:, N:]
+    err = (out.float() - want).abs()
+    assert bool((err <= 3e-2 + 2e-2 * want.abs()).all()), err.max().item()
+
+
 def test_linear_takes_the_persistent_kernel_when_asked(monkeypatch):
     from xfastertransformer_b200.ops import native as N_
     from xfastertransformer_b200.utils.flags import Env

@@ -182,6 +182,14 @@ def gemm_bf16(x, w, N, gated=False, dual_off=0, bias=None, act=None, residual=No
         assert r2.stride(1) == 1 and r2.dtype == torch.bfloat16
         ldr = r2.stride(0)
     ws = Workspace.get(x.device)
+    if _ENV().gemm_persistent and T > 128 and gated and not fp32 and row_scale is None and out.stride(1) == 1 \
+            and residual is None:
+        # gated form of the persistent kernel: four 128-column accumulators, act(gate) * up on the way out
+        rc = lib().xft_gemm_bf16_prefill_gated(_p(x2), ldx, _p(w), w.shape[0], w.stride(0), _p(out), out.stride(0), T, N, K,
+                                               dual_off, _p(bias), _ACT[act], _p(ws.status), 0, _stream())
+        _check(rc, "gemm_bf16_prefill_gated")
+        ws.launches += 1
+        return out
     if _ENV().gemm_persistent and T > 128 and not gated and not fp32 and row_scale is None and out.stride(1) == 1:
         # persistent tile loop with two TMEM accumulators (csrc/kernels/gemm_prefill_sm100.cu), opt-in
         rc = lib().xft_gemm_bf16_prefill(_p(x2), ldx, _p(w), w.shape[0], w.stride(0), _p(out), out.stride(0), T, N, K,
