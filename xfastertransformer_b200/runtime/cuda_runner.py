@@ -55,8 +55,17 @@ class CudaRunner:
             return False
         if self.m.ctx.pp_size > 1 or self.m.decoder.spec.rope == "2d" or trace.enabled() or self.m.env.debug_dir:
             return False
-        if self.m.ctx.dp_size > 1:          # data-parallel attention: ranks run different batches and exchange tokens
-            return False
+        if self.m.ctx.dp_size > 1:
+            # data-parallel attention: every rank replays a graph over ITS sequences.  The MoE token exchange must then
+            # be the peer-memory kernels (no host-side count exchange inside a captured step), and every rank's local
+            # batch must fit them.
+            ctx = self.m.ctx
+            if self.m.decoder.has_moe:
+                if ctx.epcomm is None:
+                    return False
+                per_rank = [sum(1 for s in seqs if s.owner == r) for r in range(ctx.dp_size)]
+                if max(self.bucket(n) if n else 0 for n in per_rank) > ctx.epcomm.max_tokens:
+                    return False
         if self.m.ctx.tp_size > 1 and self.m.decoder.has_moe:
             # the experts' partial sums cross ranks through the peer-memory all-reduce, which holds at most `slot`
             # values; without it the step would put a NCCL collective inside the captured graph
@@ -183,6 +192,50 @@ class CudaRunner:
             h[o_bt + n * W:o_bt + B * W] = self._scratch()
 
     def step(self, seqs: Sequence, cfg) -> List[int]:
+        if self.m.ctx.dp_size > 1:
+            return self._step_dp(seqs, cfg)
+        return self._step_local(seqs, cfg)
+
+    def _step_dp(self, seqs: Sequence, cfg) -> List[int]:
+        """Data-parallel attention: this rank decodes the sequences it owns (a graph per local batch bucket; a rank
+        without sequences replays a graph that only serves its experts), then the chosen tokens are exchanged on the
+        host so that every rank steps all sequences."""
+        import torch.distributed as dist
+        ctx = self.m.ctx
+        local = [s for s in seqs if s.owner == ctx.dp_rank]
+        per_rank = [sum(1 for s in seqs if s.owner == r) for r in range(ctx.dp_size)]
+        ctx.dp_max_tokens = max(self.bucket(n) if n else 0 for n in per_rank)
+        toks = self._step_local(local, cfg) if local else self._step_idle()
+        allt = [None] * ctx.world
+        dist.all_gather_object(allt, [int(t) for t in toks], group=ctx.ctrl_group)
+        its = [iter(t) for t in allt]
+        return [next(its[s.owner]) for s in seqs]
+
+    def _step_idle(self) -> List[int]:
+        """No sequence of this step lives here: run (and capture once) the expert exchange of every MoE layer."""
+        if not self.m.decoder.has_moe:
+            return []                              # dense model: nothing to serve
+        g = self.graphs.get("idle")
+        st = self.stream
+        st.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(st), torch.no_grad():
+            if g is None:
+                self.m.decoder.forward_idle()
+                st.synchronize()
+                g = _Graph()
+                g.version = -1
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=st):
+                    self.m.decoder.forward_idle()
+                g.graph = graph
+                self.graphs["idle"] = g
+            else:
+                g.graph.replay()
+                self.graph_launches += 1
+        st.synchronize()
+        return []
+
+    def _step_local(self, seqs: Sequence, cfg) -> List[int]:
         m = self.m
         n_real = len(seqs)
         self._scratch()                                # both may grow the pools: before the version check below
