@@ -31,6 +31,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
 
+MAX_BODY_BYTES = 16 << 20          # a request body larger than this is refused with 413
+
+
 class Request:
     def __init__(self, prompt_ids: List[int], max_tokens: int, temperature: float, top_p: float, top_k: int,
                  stop_ids: List[int], seed: Optional[int], repetition_penalty: float = 1.0,
@@ -359,7 +362,11 @@ def make_handler(sched: Scheduler, tok: Tokenizer, model_name: str):
 
         def do_POST(self):
             try:
-                q = json.loads(self.rfile.read(int(self.headers.get("Content-Length", 0))) or b"{}")
+                n_body = int(self.headers.get("Content-Length", 0))
+                if n_body > MAX_BODY_BYTES:
+                    return self._json(413, {"error": {"message": f"request body over {MAX_BODY_BYTES} bytes",
+                                                      "type": "invalid_request_error"}})
+                q = json.loads(self.rfile.read(n_body) or b"{}")
                 chat = self.path == "/v1/chat/completions"
                 if not chat and self.path != "/v1/completions":
                     return self._json(404, {"error": {"message": f"no route {self.path}"}})

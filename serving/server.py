@@ -87,9 +87,14 @@ def serve_http(model, port: int):
             self.send_response(200); self.send_header("Content-Type", "application/json"); self.end_headers(); self.wfile.write(body)
 
         def do_POST(self):
-            q = _dec(self.rfile.read(int(self.headers.get("Content-Length", 0))))
+            n_body = int(self.headers.get("Content-Length", 0))
+            if n_body > (16 << 20):
+                self.send_response(413)
+                self.end_headers()
+                return
+            raw = self.rfile.read(n_body)
             try:
-                body, code = _enc(sv.predict(q)), 200
+                body, code = _enc(sv.predict(_dec(raw))), 200
             except Exception as e:      # report, keep serving
                 body, code = _enc({"error": str(e)}), 400
             self.send_response(code); self.send_header("Content-Type", "application/json"); self.end_headers(); self.wfile.write(body)

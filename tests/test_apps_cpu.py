@@ -219,13 +219,28 @@ def test_openai_server_continuous_batching(tmp_path):
         pen = json.loads(body)["choices"][0]["token_ids"]
         assert code == 200 and len(set(pen)) == 6 and not set(pen) & set(prompts[0])     # a huge penalty forbids repeats
         assert post("/v1/completions", {"prompt": prompts[0], "n": 2, "stream": True})[0] == 400
+        # malformed and oversized bodies are refused, the server keeps serving
+        bad = urllib.request.Request(base + "/v1/completions", data=b"{not json", headers={"Content-Type": "application/json"})
+        try:
+            urllib.request.urlopen(bad, timeout=30)
+            assert False, "malformed JSON must not be accepted"
+        except urllib.error.HTTPError as e:
+            assert e.code == 400
+        import http.client
+        conn = http.client.HTTPConnection("127.0.0.1", port, timeout=30)
+        conn.putrequest("POST", "/v1/completions")
+        conn.putheader("Content-Length", str(oai.MAX_BODY_BYTES + 1))
+        conn.endheaders()
+        assert conn.getresponse().status == 413
+        conn.close()
+        assert post("/v1/completions", {"prompt": prompts[1], "max_tokens": 2})[0] == 200
         # text prompt without a tokenizer, and a prompt longer than the model: 400, server keeps serving
         assert post("/v1/completions", {"prompt": "hello"})[0] == 400
         assert post("/v1/completions", {"prompt": [1] * 40, "max_tokens": 100000})[0] == 400
         assert json.loads(urllib.request.urlopen(base + "/v1/models").read())["data"][0]["id"] == "tiny"
         m = urllib.request.urlopen(base + "/metrics").read().decode()
-        assert "xft_finished 11" in m and "xft_generated_tokens 63" in m
-        assert sched.metrics["steps"] < 11 * 7         # requests shared engine steps
+        assert "xft_finished 12" in m and "xft_generated_tokens 65" in m
+        assert sched.metrics["steps"] < 12 * 7         # requests shared engine steps
     finally:
         sched.shutdown()
         httpd.shutdown()
