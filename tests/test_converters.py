@@ -130,3 +130,23 @@ def test_gptq_layout_roundtrip(tmp_path):
         got = m(ids)
         rel = (got - want).abs().max().item() / want.abs().max().item()
         assert rel < (0.1 if qt == "int8" else 0.6), rel
+
+
+def test_reference_tool_module_names_resolve():
+    """`xfastertransformer.tools` and the reference's per-family module names import the same converter classes."""
+    import importlib
+    import xfastertransformer as ref_name
+    from xfastertransformer.tools import LlamaConvert, DeepSeekR1Convert
+    assert LlamaConvert is ref_name.LlamaConvert is xft.LlamaConvert and DeepSeekR1Convert is xft.DeepSeekR1Convert
+    for mod, cls in (("llama_convert", "LlamaConvert"), ("yarn_llama_convert", "YaRNLlamaConvert"),
+                     ("qwen_convert", "QwenConvert"), ("qwen2_convert", "Qwen2Convert"), ("qwen3_convert", "Qwen3Convert"),
+                     ("chatglm_convert", "ChatGLMConvert"), ("chatglm2_convert", "ChatGLM2Convert"),
+                     ("chatglm3_convert", "ChatGLM3Convert"), ("chatglm4_convert", "ChatGLM4Convert"),
+                     ("opt_convert", "OPTConvert"), ("baichuan_convert", "BaichuanConvert"),
+                     ("baichuan2_convert", "Baichuan2Convert"), ("telechat_convert", "TelechatConvert"),
+                     ("mixtral_convert", "MixtralConvert"), ("deepseek_moe_convert", "DeepSeekV3Convert"),
+                     ("convert", "BaseModelConvert")):
+        m = importlib.import_module(f"xfastertransformer.tools.{mod}")
+        assert getattr(m, cls) is getattr(xft.tools, cls), (mod, cls)
+    with pytest.raises(ImportError):
+        importlib.import_module("xfastertransformer.tools.no_such_convert")
