@@ -475,3 +475,106 @@ def test_expert_exchange_addressing_emulated(world, E, k):
             got = sum(w[r][t, j] * ret[r][t * k + j] for j in range(k))
             want = sum(w[r][t, j] * (h[r][t] @ expert[int(idx[r][t, j])]) for j in range(k))
             assert torch.allclose(got, want, atol=1e-5)
+
+
+def test_persistent_gemm_barrier_protocol_model():
+    """Model check of the persistent prefill kernel's synchronisation (csrc/kernels/gemm_prefill_sm100.cu): three
+    actors (TMA producer, MMA issuer, epilogue) over a ring of `stages` shared-memory stages and two TMEM accumulators,
+    with mbarrier semantics (a phase completes after `count` arrivals; waiting on parity P succeeds once the phase of
+    that parity has completed, and a fresh barrier counts as having completed the phase of parity 1).  The parities are
+    the kernel's: producer waits empty[s] on ((it / stages) & 1) ^ 1, the MMA issuer waits full[s] on (it / stages) & 1
+    and tmem_empty[a] on ((tile >> 1) & 1) ^ 1, the epilogue waits tmem_full[a] on (tile >> 1) & 1.  Under random
+    interleavings nothing deadlocks, no stage is overwritten before it was consumed and no accumulator is reused before
+    it was drained."""
+    import random
+
+    class Bar:
+        def __init__(self, count):
+            self.count, self.pending, self.phase = count, count, 0
+
+        def arrive(self):
+            self.pending -= 1
+            if self.pending == 0:
+                self.pending, self.phase = self.count, self.phase ^ 1
+
+        def done(self, parity):            # try_wait.parity
+            return self.phase != parity
+
+    for trial in range(40):
+        rng = random.Random(trial)
+        stages, num_kb, tiles = rng.choice((2, 3, 4, 6)), rng.randint(1, 7), rng.randint(1, 9)
+        full = [Bar(1) for _ in range(stages)]
+        empty = [Bar(1) for _ in range(stages)]
+        tmem_full, tmem_empty = [Bar(1), Bar(1)], [Bar(4), Bar(4)]
+        stage_data = [None] * stages            # (tile, kb) held by the stage, None = free
+        acc = [None, None]                      # None = free, else [tile, k-blocks accumulated]
+        P_ = dict(tile=0, kb=0, it=0)
+        M_ = dict(tile=0, kb=0, it=0, started=False)
+        E_ = dict(tile=0, warps_left=0)
+        drained = []
+
+        def producer():
+            if P_["tile"] >= tiles:
+                return False
+            s, ph = P_["it"] % stages, (P_["it"] // stages) & 1
+            if not empty[s].done(ph ^ 1):
+                return False
+            assert stage_data[s] is None, "stage overwritten before it was consumed"
+            stage_data[s] = (P_["tile"], P_["kb"])
+            full[s].arrive()                    # the TMA transaction completes
+            P_["it"] += 1
+            P_["kb"] += 1
+            if P_["kb"] == num_kb:
+                P_["kb"], P_["tile"] = 0, P_["tile"] + 1
+            return True
+
+        def mma():
+            if M_["tile"] >= tiles:
+                return False
+            a, aph = M_["tile"] & 1, (M_["tile"] >> 1) & 1
+            if not M_["started"]:
+                if not tmem_empty[a].done(aph ^ 1):
+                    return False
+                assert acc[a] is None, "accumulator reused before it was drained"
+                acc[a] = [M_["tile"], 0]
+                M_["started"] = True
+                return True
+            s, ph = M_["it"] % stages, (M_["it"] // stages) & 1
+            if not full[s].done(ph):
+                return False
+            assert stage_data[s] == (M_["tile"], M_["kb"]), "MMA read a stage that holds another k-block"
+            acc[a][1] += 1
+            stage_data[s] = None
+            empty[s].arrive()                   # tcgen05.commit on the stage
+            M_["it"] += 1
+            M_["kb"] += 1
+            if M_["kb"] == num_kb:
+                tmem_full[a].arrive()           # tcgen05.commit on the accumulator
+                M_["kb"], M_["tile"], M_["started"] = 0, M_["tile"] + 1, False
+            return True
+
+        def epilogue():
+            if E_["tile"] >= tiles:
+                return False
+            a, aph = E_["tile"] & 1, (E_["tile"] >> 1) & 1
+            if E_["warps_left"] == 0:
+                if not tmem_full[a].done(aph):
+                    return False
+                assert acc[a] == [E_["tile"], num_kb], "epilogue read an incomplete or foreign accumulator"
+                E_["warps_left"] = 4
+                return True
+            E_["warps_left"] -= 1               # one epilogue warp finished its TMEM loads and arrives
+            if E_["warps_left"] == 0:
+                drained.append(acc[a][0])
+                acc[a] = None
+            tmem_empty[a].arrive()
+            if E_["warps_left"] == 0:
+                E_["tile"] += 1
+            return True
+
+        actors = [producer, mma, epilogue]
+        while E_["tile"] < tiles:
+            order = actors[:]
+            rng.shuffle(order)
+            assert any(f() for f in order), f"deadlock: stages={stages} kb={num_kb} tiles={tiles} P={P_} M={M_} E={E_}"
+        assert drained == list(range(tiles))
