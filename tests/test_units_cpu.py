@@ -578,3 +578,130 @@ def test_persistent_gemm_barrier_protocol_model():
             rng.shuffle(order)
             assert any(f() for f in order), f"deadlock: stages={stages} kb={num_kb} tiles={tiles} P={P_} M={M_} E={E_}"
         assert drained == list(range(tiles))
+
+
+def test_expert_exchange_protocol_model_over_consecutive_layers():
+    """Model check of the peer-memory expert exchange across consecutive exchanges (csrc/kernels/ep_comm.cu): ranks run
+    dispatch -> receive -> experts -> return -> combine at independent speeds, with one receive area per (destination,
+    source), one return area per source and {payload, epoch} words.  No buffer is double-buffered, so the check is that
+    a rank never overwrites data its peer has not consumed yet and never reads data of another exchange."""
+    import random
+    for trial in range(30):
+        rng = random.Random(trial)
+        world, rounds = rng.choice((2, 3, 4)), 4
+        rx = [[dict(epoch=0, consumed=True) for _ in range(world)] for _ in range(world)]       # rx[dest][src]
+        rx_cnt = [[0] * world for _ in range(world)]
+        ret = [[dict(epoch=0, consumed=True) for _ in range(world)] for _ in range(world)]      # ret[home][expert rank]
+        ret_flag = [[0] * world for _ in range(world)]
+        epoch = [0] * world                       # completed exchanges per rank
+        stage = [0] * world                       # 0 dispatch, 1 receive, 2 return, 3 combine
+        done_rounds = [0] * world
+
+        def step(r):
+            e = epoch[r] + 1
+            if done_rounds[r] == rounds:
+                return False
+            if stage[r] == 0:                     # dispatch: rows, then the count words
+                for d in range(world):
+                    assert rx[d][r]["consumed"], f"rank {r} overwrites rows rank {d} has not read (exchange {e})"
+                    rx[d][r] = dict(epoch=e, consumed=False)
+                    rx_cnt[d][r] = e
+                stage[r] = 1
+                return True
+            if stage[r] == 1:                     # receive: wait for every source's count word of this exchange
+                if any(rx_cnt[r][s] != e for s in range(world)):
+                    return False
+                stage[r] = 2
+                return True
+            if stage[r] == 2:                     # experts read the receive area, outputs go back, then the flags
+                for s in range(world):
+                    assert rx[r][s]["epoch"] == e and not rx[r][s]["consumed"]
+                    rx[r][s]["consumed"] = True
+                    assert ret[s][r]["consumed"], f"rank {r} overwrites a return row rank {s} has not combined"
+                    ret[s][r] = dict(epoch=e, consumed=False)
+                    ret_flag[s][r] = e
+                stage[r] = 3
+                return True
+            if any(ret_flag[r][d] != e for d in range(world)):     # combine: wait for every expert rank
+                return False
+            for d in range(world):
+                assert ret[r][d]["epoch"] == e
+                ret[r][d]["consumed"] = True
+            epoch[r] += 1
+            done_rounds[r] += 1
+            stage[r] = 0
+            return True
+
+        while any(n < rounds for n in done_rounds):
+            order = list(range(world))
+            rng.shuffle(order)
+            # a random subset runs in each sweep: ranks drift apart as far as the protocol lets them
+            progressed = [step(r) for r in order if rng.random() < 0.6]
+            if not any(progressed):
+                assert any(step(r) for r in order), "deadlock"
+
+
+def test_fused_prefill_protocol_model_over_consecutive_launches():
+    """Model check of the fused prefill GEMM + all-reduce across consecutive launches (the decoder's chain: the output of
+    one launch is the residual of the next, two output buffers alternate).  Ranks walk their tiles at independent
+    speeds.  Checked: a partial slot is never overwritten before its owner has reduced it, an output buffer is never
+    written while its rank still reads it as the residual of the previous launch, every read sees the data of the
+    launch it belongs to, and nothing deadlocks."""
+    import random
+    for trial in range(25):
+        rng = random.Random(100 + trial)
+        world, nb, launches = rng.choice((2, 3, 4)), rng.randint(1, 7), 4
+        orders = [P.block_visit_order(nb, world, r) for r in range(world)]
+        part = [[[dict(epoch=0, consumed=True) for _ in range(world)] for _ in range(nb)] for _ in range(world)]
+        flag_part = [[[0] * world for _ in range(nb)] for _ in range(world)]        # [owner][block][src]
+        out = [[[0] * nb for _ in range(2)] for _ in range(world)]                  # [rank][buffer][block] = epoch held
+        reading = [[False, False] for _ in range(world)]                            # rank still reads buffer as residual
+        flag_res = [[0] * nb for _ in range(world)]
+        launch = [1] * world
+        pos = [0] * world                                                           # next position in the visiting order
+
+        def step(r):
+            e = launch[r]
+            if e > launches:
+                return False
+            w, prev = e % 2, (e - 1) % 2
+            if pos[r] == 0:
+                reading[r][prev] = e > 1           # the launch reads the previous output as its residual
+            if pos[r] < nb:
+                b = orders[r][pos[r]]
+                owner = b % world
+                if owner != r:
+                    slot = part[owner][b][r]
+                    assert slot["consumed"], f"rank {r} overwrites a partial rank {owner} has not reduced (launch {e})"
+                    part[owner][b][r] = dict(epoch=e, consumed=False)
+                    flag_part[owner][b][r] = e
+                else:
+                    if any(flag_part[r][b][s] != e for s in range(world) if s != r):
+                        return False
+                    for s in range(world):
+                        if s != r:
+                            assert part[r][b][s]["epoch"] == e and not part[r][b][s]["consumed"]
+                            part[r][b][s]["consumed"] = True
+                    if e > 1:
+                        assert out[r][prev][b] == e - 1, "residual of another launch"
+                    for s in range(world):
+                        assert not reading[s][w], f"rank {r} writes buffer {w} of rank {s} while {s} still reads it"
+                        out[s][w][b] = e
+                        if s != r:
+                            flag_res[s][b] = e
+                pos[r] += 1
+                return True
+            if any(flag_res[r][b] != e for b in range(nb) if b % world != r):      # the launch's last CTA
+                return False
+            assert all(out[r][w][b] == e for b in range(nb))
+            reading[r][prev] = False
+            launch[r] += 1
+            pos[r] = 0
+            return True
+
+        while any(l <= launches for l in launch):
+            order = list(range(world))
+            rng.shuffle(order)
+            progressed = [step(r) for r in order if rng.random() < 0.6]
+            if not any(progressed):
+                assert any(step(r) for r in order), f"deadlock world={world} nb={nb} launch={launch} pos={pos}"
