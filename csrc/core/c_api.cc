@@ -53,6 +53,8 @@ int xftc_tables_table(void* t, int seq, int* out, int cap) {
   } catch (...) { return -1; }
 }
 int xftc_tables_len(void* t, int seq) { try { return static_cast<BlockTables*>(t)->len(seq); } catch (...) { return -1; } }
+int xftc_tables_truncate(void* t, int seq, int newLen) { try { static_cast<BlockTables*>(t)->truncate(seq, newLen); return 0; } catch (...) { return -1; } }
+int xftc_tables_refs(void* t, int block) { return static_cast<BlockTables*>(t)->allocator().refs(block); }
 int xftc_tables_num_free(void* t) { return static_cast<BlockTables*>(t)->allocator().numFree(); }
 void xftc_tables_grow(void* t, int total) { static_cast<BlockTables*>(t)->allocator().grow(total); }
 int xftc_tables_reorder(void* t, const int* seqs, const int* src, int n) {

@@ -121,7 +121,8 @@ void BlockTables::fork(int src, int dst) {
 void BlockTables::truncate(int seq, int newLen) {
   auto& tab = tables_.at(seq);
   size_t keep = (newLen + bs_ - 1) / bs_;
-  while (tab.size() > keep) { alloc_.release(tab.back()); tab.pop_back(); }
+  for (size_t i = keep; i < tab.size(); ++i) alloc_.release(tab[i]);     // same release order as the Python twin
+  if (tab.size() > keep) tab.resize(keep);
   lens_[seq] = newLen;
 }
 void BlockTables::reorder(const std::vector<int>& seqs, const std::vector<int>& srcIndex) {

@@ -55,7 +55,7 @@ def test_block_tables_match_python(core):
     tab = (C.c_int * 64)()
     live = []
     for step in range(300):
-        op = rng.choice(["add", "append", "append", "fork", "free"])
+        op = rng.choice(["add", "append", "append", "fork", "free", "truncate", "reorder"])
         if op == "add" and len(live) < 6:
             sid = step
             assert core.xftc_tables_add(t, sid) == 0
@@ -80,10 +80,27 @@ def test_block_tables_match_python(core):
             sid = live.pop(rng.randrange(len(live)))
             core.xftc_tables_free(t, sid)
             py.free_sequence(sid)
+        elif op == "truncate" and live:
+            sid = rng.choice(live)
+            new_len = rng.randint(0, py.lens[sid])
+            assert core.xftc_tables_truncate(t, sid, new_len) == 0
+            py.truncate(sid, new_len)
+        elif op == "reorder" and len(live) >= 2:
+            group = rng.sample(live, rng.randint(2, min(4, len(live))))
+            src = [rng.randrange(len(group)) for _ in group]              # beam i continues from beam src[i]
+            assert core.xftc_tables_reorder(t, (C.c_int * len(group))(*group), (C.c_int * len(group))(*src), len(group)) == 0
+            py.reorder(group, src)
         assert core.xftc_tables_num_free(t) == py.alloc.num_free
+        refs = {}
         for sid in live:
             n = core.xftc_tables_table(t, sid, tab, 64)
             assert list(tab[:n]) == py.tables[sid] and core.xftc_tables_len(t, sid) == py.lens[sid]
+            assert len(py.tables[sid]) == (py.lens[sid] + 63) // 64            # no block beyond the length
+            for b in py.tables[sid]:
+                refs[b] = refs.get(b, 0) + 1
+        # reference counts equal the number of tables that hold the block; every other block is free
+        assert all(core.xftc_tables_refs(t, b) == n for b, n in refs.items())
+        assert len(refs) + py.alloc.num_free == 40
     core.xftc_tables_delete(t)
 
 
