@@ -241,6 +241,10 @@ def test_openai_server_continuous_batching(tmp_path):
         m = urllib.request.urlopen(base + "/metrics").read().decode()
         assert "xft_finished 12" in m and "xft_generated_tokens 65" in m
         assert sched.metrics["steps"] < 12 * 7         # requests shared engine steps
+        # nothing leaks: every sequence was freed and every KV block is back in the pool
+        eng = model.model
+        assert not sched.running and not eng.pool.seqs and not eng.cache.tables
+        assert eng.cache.alloc.num_free == eng.cache.alloc.num_blocks
     finally:
         sched.shutdown()
         httpd.shutdown()
