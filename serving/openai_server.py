@@ -47,6 +47,7 @@ class Request:
         self.repetition_penalty = float(repetition_penalty)
         self.logprobs = logprobs                      # None, or how many alternatives to report per position (0 = chosen only)
         self.stop_fn = stop_fn                        # callable(generated ids) -> bool: a stop string has appeared
+        self.cancelled = False                        # set by the handler when the client went away
         self.token_logprobs: List[float] = []
         self.top_logprobs: List[Dict[int, float]] = []
         self.out: "queue.Queue" = queue.Queue()       # ints, then None (or an Exception) at the end
@@ -76,7 +77,7 @@ class Scheduler(threading.Thread):
         self.running: Dict[int, Request] = {}
         self.stop_flag = threading.Event()
         self.metrics = dict(requests=0, finished=0, prompt_tokens=0, generated_tokens=0, ttft_sum=0.0, tpot_sum=0.0,
-                            tpot_count=0, steps=0, mixed_steps=0, errors=0)
+                            tpot_count=0, steps=0, mixed_steps=0, errors=0, cancelled=0)
         self.mixed_steps = False          # prefill new prompts in the same forward as the running sequences' decode
         self.max_len = int(getattr(model.model.cfg, "max_pos_seq_len", 0) or 0)
         self.kv_fraction = 0.8            # share of the free device memory the warm-up gives to the KV pools
@@ -183,6 +184,10 @@ class Scheduler(threading.Thread):
         req.generated.append(tok)
         self.metrics["generated_tokens"] += 1
         req.out.put(tok)
+        if req.cancelled:                          # the client closed its stream: stop spending steps on it
+            req.finish_reason = "cancelled"
+            self.metrics["cancelled"] += 1
+            return True
         if tok == self.eos_id or tok in req.stop_ids or (req.stop_fn is not None and req.stop_fn(req.generated)):
             req.finish_reason = "stop"
             return True
@@ -428,8 +433,13 @@ def make_handler(sched: Scheduler, tok: Tokenizer, model_name: str):
                     delta = {"delta": {"content": text}} if chat else {"text": text, "token_ids": [t]}
                     chunk = {"id": req.id, "object": kind + ".chunk", "created": created, "model": model_name,
                              "choices": [dict(index=0, finish_reason=None, **delta)]}
-                    self.wfile.write(b"data: " + json.dumps(chunk).encode() + b"\n\n")
-                    self.wfile.flush()
+                    try:
+                        self.wfile.write(b"data: " + json.dumps(chunk).encode() + b"\n\n")
+                        self.wfile.flush()
+                    except (BrokenPipeError, ConnectionResetError, ConnectionAbortedError):
+                        req.cancelled = True       # the scheduler drops the request at its next token
+                        self.close_connection = True
+                        return
                 end = {"id": req.id, "object": kind + ".chunk", "created": created, "model": model_name,
                        "choices": [dict(index=0, finish_reason=req.finish_reason, **({"delta": {}} if chat else {"text": "", "token_ids": []}))]}
                 self.wfile.write(b"data: " + json.dumps(end).encode() + b"\n\n")

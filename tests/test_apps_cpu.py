@@ -351,3 +351,40 @@ def test_openai_server_mixed_prefill_decode_steps(tmp_path):
     finally:
         sched.shutdown()
         httpd.shutdown()
+
+
+def test_openai_server_drops_a_request_whose_client_left(tmp_path):
+    """A streaming client that closes its connection: the handler marks the request, the scheduler frees it at the next
+    token instead of generating all max_tokens, and the engine is clean afterwards."""
+    import importlib.util
+    import socket
+    import time
+    spec = importlib.util.spec_from_file_location("oai", os.path.join(ROOT, "serving", "openai_server.py"))
+    oai = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(oai)
+    d = str(tmp_path / "tiny")
+    write_synthetic_checkpoint(d, preset("tiny-llama", vocab_size=500), seed=3, dtype="fp32", std=0.1)
+    model = xft.AutoModel.from_pretrained(d, dtype="bf16")
+    httpd, sched, port = oai.serve(model, 0, max_batch=4, model_name="tiny")
+    try:
+        body = json.dumps({"prompt": [5, 9, 100], "max_tokens": 1500, "stream": True}).encode()
+        s = socket.create_connection(("127.0.0.1", port), timeout=30)
+        s.sendall(b"POST /v1/completions HTTP/1.1\r\nHost: x\r\nContent-Type: application/json\r\nContent-Length: "
+                  + str(len(body)).encode() + b"\r\n\r\n" + body)
+        got = b""
+        while got.count(b"data: ") < 3:                 # a few tokens arrive, then the client leaves
+            got += s.recv(4096)
+        s.setsockopt(socket.SOL_SOCKET, socket.SO_LINGER, b"\x01\x00\x00\x00\x00\x00\x00\x00")      # reset on close
+        s.close()
+        t0 = time.time()
+        while sched.metrics["cancelled"] == 0 and time.time() - t0 < 60:
+            time.sleep(0.05)
+        assert sched.metrics["cancelled"] == 1 and sched.metrics["generated_tokens"] < 1500
+        t0 = time.time()
+        while sched.running and time.time() - t0 < 10:
+            time.sleep(0.05)
+        eng = model.model
+        assert not sched.running and not eng.cache.tables and eng.cache.alloc.num_free == eng.cache.alloc.num_blocks
+    finally:
+        sched.shutdown()
+        httpd.shutdown()
