@@ -265,6 +265,12 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
   tables.reset(new BlockTables(kBlock, 0));
   kc.resize(layers); vc.resize(layers); ks.resize(layers); vs.resize(layers);
   rng.seed((unsigned long long)std::chrono::steady_clock::now().time_since_epoch().count());
+  if (Env::get().kvCacheGb > 0) {
+    // XFT_KV_CACHE_GB: size the KV pools once, so that they never grow (and move) under load
+    const size_t esz = kvInt8 ? 1 : 2;
+    const size_t per = (size_t)layers * kvHeads * kBlock * (2 * headDim * esz + (kvInt8 ? 8 : 0));
+    ensureBlocks((int)std::max<size_t>(1, (size_t)(Env::get().kvCacheGb * (double)(1ull << 30)) / per));
+  }
 }
 
 void Engine::ensureBlocks(int extra) {
