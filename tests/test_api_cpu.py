@@ -349,3 +349,25 @@ def test_step_watchdog_reports_an_overdue_step_and_the_step_raises(tiny, capfd):
     model.set_input(ids, max_length=12)
     assert model.forward().shape[0] == 1
     m.watchdog.close()
+
+
+def test_xft_verbose_prints_one_line_per_gemm(tiny, monkeypatch, capfd):
+    """XFT_VERBOSE=1: every GEMM-shaped op prints the reference's line xft_verbose,exec,<dev>,api,<kernel>,m..n..k..,<ms>."""
+    import re
+    from xfastertransformer_b200.utils.flags import Env
+    monkeypatch.setenv("XFT_VERBOSE", "1")
+    Env.get().reload()
+    try:
+        model = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+        capfd.readouterr()
+        model.generate(torch.tensor([[5, 6, 7, 8]]), max_length=6)
+        out = capfd.readouterr().out
+    finally:
+        monkeypatch.delenv("XFT_VERBOSE")
+        Env.get().reload()
+    lines = [l for l in out.splitlines() if l.startswith("xft_verbose,exec,cpu,api,")]
+    # per forward of the 2-layer model: (qkv, o_proj, gate-up, down) x 2 + lm_head = 9 GEMMs; prefill + 1 decode step
+    assert len(lines) == 18, len(lines)
+    assert all(re.fullmatch(r"xft_verbose,exec,cpu,api,[a-z_]+,m\d+n\d+k\d+,\d+\.\d+", l) for l in lines), lines[:3]
+    assert any(",m4n" in l for l in lines) and any(",m1n" in l for l in lines)        # prefill rows, then one row
+    assert sum("gated" in l for l in lines) == 4 and sum("n1000k256" in l for l in lines) == 2

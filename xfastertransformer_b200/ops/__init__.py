@@ -47,21 +47,59 @@ def layernorm(x, w, b, eps):
 
 
 # -- GEMMs ---------------------------------------------------------------------------------
+def _verbose() -> bool:
+    from ..utils.flags import Env
+    return Env.get().verbose >= 1
+
+
+def _timed(kernel: str, x, W, fn):
+    """XFT_VERBOSE >= 1: run one GEMM-shaped op between two time stamps (device-synchronised on a GPU) and print the
+    reference's per-call line ``xft_verbose,exec,<dev>,api,<kernel>,m<M>n<N>k<K>,<ms>`` (src/utils/verbose.h:24-83).
+    The decode graph runner steps aside while this is on, so every call is a real launch."""
+    import time
+    from ..utils import log
+    cuda = _cuda(x)
+    if cuda:
+        torch.cuda.synchronize(x.device)
+    t0 = time.perf_counter()
+    y = fn()
+    if cuda:
+        torch.cuda.synchronize(x.device)
+    ms = (time.perf_counter() - t0) * 1e3
+    log.verbose_line("gpu" if cuda else "cpu", kernel, x.numel() // x.shape[-1], W.out_features, x.shape[-1], ms)
+    return y
+
+
 def linear(x, W, bias=None, act=None, residual=None, res_scale=1.0, out_dtype=None):
+    if _verbose():
+        name = "gemm" + ("_bias" if bias is not None else "") + (f"_{act}" if act else "") + \
+            ("_residual" if residual is not None else "")
+        impl = _nat().linear if _cuda(x) else R.linear
+        return _timed(name, x, W, lambda: impl(x, W, bias, act, residual, res_scale, out_dtype))
     if _cuda(x):
         return _nat().linear(x, W, bias, act, residual, res_scale, out_dtype)
     return R.linear(x, W, bias, act, residual, res_scale, out_dtype)
 
 
-def linear_rms(x, W, eps, bias=None, act=None, gated=False, out_dtype=None):
-    """RMSNorm(x) @ W^T for a weight whose columns already carry the norm's gain (loader.fold_norm_gain)."""
+def _linear_rms(x, W, eps, bias, act, gated, out_dtype):
     if _cuda(x):
         return _nat().linear_rms(x, W, eps, bias, act, gated, out_dtype)
     h = R.rmsnorm(x, torch.ones(x.shape[-1], dtype=torch.float32), eps)
     return R.linear_gated(h, W, act, bias) if gated else R.linear(h, W, bias, act, None, 1.0, out_dtype)
 
 
+def linear_rms(x, W, eps, bias=None, act=None, gated=False, out_dtype=None):
+    """RMSNorm(x) @ W^T for a weight whose columns already carry the norm's gain (loader.fold_norm_gain)."""
+    if _verbose():
+        return _timed("rmsnorm_gemm" + ("_gated" if gated else ""), x, W,
+                      lambda: _linear_rms(x, W, eps, bias, act, gated, out_dtype))
+    return _linear_rms(x, W, eps, bias, act, gated, out_dtype)
+
+
 def linear_gated(x, W, act="silu", bias=None):
+    if _verbose():
+        impl = _nat().linear_gated if _cuda(x) else R.linear_gated
+        return _timed(f"gemm_gated_{act}", x, W, lambda: impl(x, W, act, bias))
     if _cuda(x):
         return _nat().linear_gated(x, W, act, bias)
     return R.linear_gated(x, W, act, bias)

@@ -55,6 +55,8 @@ class CudaRunner:
             return False
         if self.m.ctx.pp_size > 1 or self.m.decoder.spec.rope == "2d" or trace.enabled() or self.m.env.debug_dir:
             return False
+        if self.m.env.verbose >= 1:          # per-GEMM timing lines need real launches with a synchronise around each
+            return False
         if self.m.ctx.dp_size > 1:
             # data-parallel attention: every rank replays a graph over ITS sequences.  The MoE token exchange must then
             # be the peer-memory kernels (no host-side count exchange inside a captured step), and every rank's local
