@@ -65,7 +65,8 @@ class Env:
         self.attn_tma = _int("XFT_ATTN_TMA", 1) != 0      # bf16 decode attention through the TMA ring kernel
         self.attn_splits = _int("XFT_ATTN_SPLITS", 0)     # decode split-KV factor; 0 = planned per launch
         self.gemm_persistent = _int("XFT_GEMM_PERSISTENT", 0) != 0     # prefill GEMMs through the persistent kernel
-        self.prefill_fused_ar = _int("XFT_PREFILL_FUSED_AR", 0) != 0   # row-parallel prefill GEMM + all-reduce fused
+        # XFT_PREFILL_FUSED_AR (row-parallel prefill GEMM + all-reduce as one kernel) and XFT_MAX_BATCH_TOKENS size the
+        # symmetric buffers: parallel/fused_comm.py reads them when the peer communicator is built
         # accepted, no effect on a GPU build
         self.ignored = {k: e.get(k) for k in (
             "XFT_USE_AMX_M", "ENABLE_TUNED_COMM", "ENABLE_KV_TRANS", "ENABLE_THP", "XFT_ONECCL",
