@@ -1,6 +1,7 @@
 """Apps around the engine on the CPU path: serving launcher (gRPC + HTTP), offline continuous-batching scheduler,
 evaluation adapter, benchmark CLI, timeline, MLServer runtime object."""
 import json
+import math
 import os
 import subprocess
 import sys
@@ -88,6 +89,28 @@ def test_eval_adapter_and_perplexity(tiny):
     assert is_greedy and ll < 0
     ll2, g2 = ev.loglikelihood_tokens(ids[:10].tolist(), [(greedy[0] + 1) % 800] + greedy[1:])
     assert ll2 < ll and not g2
+    # several requests per forward (ragged lengths) give the same numbers as one by one
+    pairs = [(ids[:10].tolist(), greedy), (ids[:5].tolist(), ids[5:9].tolist()), (ids[3:20].tolist(), ids[20:22].tolist()),
+             (ids[:10].tolist(), ids[10:13].tolist())]
+    ev.batch_size = 3
+    batch = ev.loglikelihood_batch(pairs)
+    for (c, t), (bl, bg) in zip(pairs, batch):
+        sl, sg = ev.loglikelihood_tokens(c, t)
+        assert abs(sl - bl) < 1e-3 * max(1.0, abs(sl)) and sg == bg
+    assert batch[0][1] and abs(batch[0][0] - ll) < 1e-3 * abs(ll)
+    # rolling log-likelihood: windows add up to the sum over the text; consistent with the perplexity
+    ev.max_length = 16
+    total = ev.rolling_loglikelihood(ids.tolist())
+    assert total < 0
+    ev.max_length = 64
+    whole = ev.rolling_loglikelihood(ids.tolist())
+    assert abs(math.exp(-whole / (ids.numel() - 1)) - perplexity(model, ids, window=64)) < 1e-2 * perplexity(model, ids, window=64)
+    # greedy generation cut at a stop string ("text" = ids joined by spaces)
+    dec = lambda t: " ".join(map(str, t))
+    full = ev.generate_until(ids[:10].tolist(), dec, [], 6)
+    assert full.split() == [str(t) for t in model.generate(ids[None, :10], max_length=16)[0, 10:].tolist()]
+    stop = " " + full.split()[2]
+    assert ev.generate_until(ids[:10].tolist(), dec, [stop], 6) == " ".join(full.split()[:2])
 
 
 def test_benchmark_cli_and_timeline(tiny, tmp_path):

@@ -230,3 +230,29 @@ def test_data_parallel_attention_scenarios(tmp_path):
     # no tensor parallelism (o_proj sees all 4 heads), both ranks took part in the expert exchange
     assert [i[:2] for i in got["info"]] == [(2, 1), (2, 1)] and all(i[2] > 0 and i[3] == 128 for i in got["info"])
     assert got["info"][0][2] == got["info"][1][2]
+
+
+def test_general_follower_loop_gloo(tiny, tmp_path):
+    """Rank 1 only runs model.follow(); rank 0 mixes generate (greedy, beams), config + input + forward, continuous
+    batching and all-position logits.  Everything equals the single-process results and the follower exits on shutdown."""
+    import xfastertransformer_b200 as xft
+    from xfastertransformer_b200.parallel.dist import DistContext
+    from xfastertransformer_b200.utils.flags import Env
+    out = str(tmp_path / "follow.pt")
+    env = dict(os.environ, XFT_ENGINE="CPU", PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29671", os.path.join(ROOT, "tests", "follow_worker.py"), tiny, out]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    got = torch.load(out)
+    ids = _prompt()
+    ref = EagerLlama(tiny)
+    assert torch.equal(got["greedy"], ref.greedy(ids, 8))
+    assert torch.equal(got["stepwise"], ref.greedy(ids, 4))
+    assert torch.allclose(got["cb_logits"], ref.logits(ids)[:, -1], atol=2e-3, rtol=2e-3)
+    assert torch.allclose(got["all"], ref.logits(ids[:, :16]), atol=2e-3, rtol=2e-3)
+    os.environ["XFT_ENGINE"] = "CPU"
+    DistContext.reset()
+    Env.get().reload()
+    m = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+    assert torch.equal(got["beams"], m.generate(ids[:, :12], max_length=18, num_beams=2))

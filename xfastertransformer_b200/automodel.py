@@ -56,6 +56,10 @@ class AutoModel:
                 input_ids = [t for r in input_ids for t in r]
         return self.model.set_input_cb(input_ids, seq_lens, seq_ids, max_length, greedy, append, hold)
 
+    def follow(self):
+        """Follower ranks: run rank 0's calls (generate, continuous batching, all-position logits) until shutdown."""
+        return self.model.follow()
+
     def follow_cb(self):
         """Follower ranks of a continuous-batching server: mirror rank 0 until it shuts down."""
         return self.model.follow_cb()

@@ -36,7 +36,7 @@ from .kv_cache import PagedKVCache
 from .sequence import SamplingMeta, SequenceMeta, SequencePool
 
 OP_SET_INPUT, OP_CONFIG, OP_INPUT, OP_SET_INPUT_CB, OP_FREE_SEQS, OP_SET_PREFIX, OP_UNSET_PREFIX, OP_SHUTDOWN, \
-    OP_FINALIZE = range(9)
+    OP_FINALIZE, OP_LOGITS_ALL = range(10)
 
 
 def _to_lists(ids) -> List[List[int]]:
@@ -145,6 +145,8 @@ class Model:
             return self._do_set_prefix(payload)
         if op == OP_UNSET_PREFIX:
             return self._do_unset_prefix()
+        if op == OP_LOGITS_ALL:
+            return self._do_logits_all(payload)
         if op == OP_SHUTDOWN:
             self._closed = True
             if not self.ctx.is_master:
@@ -457,20 +459,31 @@ class Model:
             s.pending = []
         return torch.tensor([int(t) for t in toks], dtype=torch.int64)
 
-    def follow_cb(self) -> None:
-        """Follower ranks of a continuous-batching server: execute rank 0's control messages until shutdown.  A
-        serving scheduler runs exactly one ``forward_cb`` after every ``set_input_cb`` (forward steps carry no
-        message), so the follower does the same."""
+    def follow(self) -> None:
+        """Follower ranks: execute rank 0's control messages until shutdown, whatever API rank 0 uses.  Forward steps
+        carry no message, so the follower runs the ones that rank 0 is bound to run: after ``set_input`` / ``input``
+        the decode loop of ``generate`` (``forward`` until ``is_done``), after every ``set_input_cb`` exactly one
+        ``forward_cb`` (a serving scheduler does the same) unless the message said hold; all-position logits run
+        inside their own message.  The reference's followers sit in ``while True: model.generate()``, which covers the
+        first case only (serving/grpc_launcher/server.py:144-152)."""
         if self.ctx.world == 1 or self.ctx.is_master:
             return
         while not self._closed:
             op, payload = self._sync(0, None)
             self._dispatch(op, payload)
-            if op == OP_SET_INPUT_CB and not getattr(self, "_cb_hold", False):
+            if op in (OP_SET_INPUT, OP_INPUT):
+                while not self.is_done():
+                    self.forward()
+                self.finalize()
+            elif op == OP_SET_INPUT_CB and not getattr(self, "_cb_hold", False):
                 if getattr(self, "_cb_greedy", False):
                     self.forward_cb_greedy()
                 else:
                     self.forward_cb()
+
+    def follow_cb(self) -> None:
+        """Follower loop of a continuous-batching server (same loop as `follow`)."""
+        self.follow()
 
     def free_seqs(self, seq_ids=None) -> bool:
         if isinstance(seq_ids, torch.Tensor):
@@ -704,9 +717,9 @@ class Model:
     # ------------------------------------------------------------------------------------
     def forward_logits_all(self, input_ids) -> torch.Tensor:
         """All-position logits of a batch of prompts (evaluation hook; evaluation/eval.cpp:70-139)."""
-        prompts = _to_lists(input_ids)
-        if self.ctx.world > 1:
-            prompts = self.ctx.ctrl_broadcast(prompts)
+        return self._call(OP_LOGITS_ALL, _to_lists(input_ids))
+
+    def _do_logits_all(self, prompts) -> torch.Tensor:
         seqs = []
         self.cache.reserve(sum(self.cache.blocks_for(len(p) + 1) for p in prompts))
         for p in prompts:
