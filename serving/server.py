@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Token-id serving launcher (reference: ``serving/grpc_launcher/server.py:70-152``): rank 0 serves ``predict`` /
-``predict_stream`` / ``health`` over gRPC; every other rank sits in ``while True: model.generate()`` and executes
-what rank 0 broadcasts.  Messages are JSON objects with the fields of ``xft.proto``.
+``predict_stream`` / ``health`` over gRPC; every other rank sits in ``model.follow()`` (the reference:
+``while True: model.generate()``) and executes what rank 0 broadcasts.  Messages are JSON objects with the fields of ``xft.proto``.
 
     python serving/server.py --model_path <dir> --dtype bf16 --port 50051
     torchrun --nproc-per-node 8 ... serving/server.py --model_path <dir> --dtype bf16
@@ -49,10 +49,16 @@ class Servicer:
     def predict_stream(self, q, ctx=None):
         with self.lock:
             self.model.set_input(self._ids(q), **self._kwargs(q))
-            while not self.model.is_done():
-                t = self.model.forward()
-                yield {"Ids": t.flatten().tolist(), "batch_size": t.shape[0], "seq_len": 1}
-            self.model.finalize()
+            try:
+                while not self.model.is_done():
+                    t = self.model.forward()
+                    yield {"Ids": t.flatten().tolist(), "batch_size": t.shape[0], "seq_len": 1}
+            finally:
+                # a client that left early must not leave the follower ranks ahead of rank 0: they run the request to
+                # its end, so rank 0 does too
+                while not self.model.is_done():
+                    self.model.forward()
+                self.model.finalize()
 
     def health(self, q=None, ctx=None):
         return {"status": "SERVING"}
@@ -134,8 +140,8 @@ def main():
     import xfastertransformer_b200 as xft
     model = xft.AutoModel.from_pretrained(a.model_path, dtype=a.dtype, kv_cache_dtype=a.kv_cache_dtype)
     if model.rank != 0:
-        while True:                      # follower: execute whatever rank 0 broadcasts (exits on shutdown)
-            model.generate()
+        model.follow()                   # follower: execute whatever rank 0 calls (exits on shutdown)
+        return
     if a.http:
         srv, port = serve_http(model, a.port)
         print(f"HTTP serving on :{port}", flush=True)
