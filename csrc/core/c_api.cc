@@ -8,6 +8,7 @@
 
 #include "arena.h"
 #include "beam.h"
+#include "dtypes.h"
 #include "env.h"
 #include "rope_tables.h"
 #include "runtime.h"
@@ -91,6 +92,13 @@ int xftc_beam_finalize(void* s, const int32_t* prompts, int batch, int promptLen
   return rows * 65536 + width;
 }
 void xftc_log_softmax(float* row, int n) { logSoftmaxRow(row, n); }
+// host-side numeric conversions (csrc/core/dtypes.h): kind 1 = fp16, 2 = bf16
+void xftc_convert_from_float(const float* in, uint16_t* out, int n, int kind) {
+  for (int i = 0; i < n; ++i) out[i] = kind == 1 ? floatToHalf(in[i]) : floatToBf16(in[i]);
+}
+void xftc_convert_to_float(const uint16_t* in, float* out, int n, int kind) {
+  for (int i = 0; i < n; ++i) out[i] = kind == 1 ? halfToFloat(in[i]) : bf16ToFloat(in[i]);
+}
 
 // ---- position tables (csrc/core/rope_tables.cc).  scaling: 0 none, 1 linear, 2 yarn; table_scale < 0 = default
 void xftc_rope_table(int max_pos, int rot_dim, double theta, int scaling, double factor, int original_max_pos,

@@ -16,6 +16,7 @@
 
 #include "arena.h"
 #include "beam.h"
+#include "dtypes.h"
 #include "env.h"
 #include "ini.h"
 #include "kernels_c.h"
@@ -62,7 +63,27 @@ struct DevBuf {
   template <class T> T* as() const { return static_cast<T*>(p); }
 };
 
-std::vector<char> readFile(const std::string& path, size_t expect) {
+// XFT_FAKE_MODEL (reference: src/utils/weight_util.h:76-82 zero-fills): 1 = zeros, 2 = N(0, 0.02) weights, norm gains
+// of one and zero biases, so that a model of any size runs without files.  `dt`: 0 fp32, 1 fp16, 2 bf16.
+std::vector<char> fakeTensor(const std::string& path, size_t bytes, int dt, int mode) {
+  std::vector<char> buf(bytes, 0);
+  if (mode < 2) return buf;
+  const bool bias = path.find("bias") != std::string::npos;
+  const bool gain = !bias && (path.find("norm") != std::string::npos);
+  if (bias) return buf;
+  std::mt19937 gen((uint32_t)std::hash<std::string>()(path));
+  std::normal_distribution<float> nd(0.f, 0.02f);
+  const size_t n = bytes / (dt == 0 ? 4 : 2);
+  for (size_t i = 0; i < n; ++i) {
+    const float v = gain ? 1.f : nd(gen);
+    if (dt == 0) std::memcpy(buf.data() + 4 * i, &v, 4);
+    else { const uint16_t h = dt == 1 ? floatToHalf(v) : floatToBf16(v); std::memcpy(buf.data() + 2 * i, &h, 2); }
+  }
+  return buf;
+}
+
+std::vector<char> readFile(const std::string& path, size_t expect, int dt) {
+  if (const int fake = xft::Env::get().fakeModel) return fakeTensor(path, expect, dt, fake);
   std::ifstream f(path, std::ios::binary | std::ios::ate);
   if (!f) throw std::runtime_error("cannot open " + path);
   size_t sz = (size_t)f.tellg();
@@ -71,29 +92,6 @@ std::vector<char> readFile(const std::string& path, size_t expect) {
   f.seekg(0);
   f.read(buf.data(), (std::streamsize)sz);
   return buf;
-}
-
-size_t dtypeSize(int dt) { return dt == 0 ? 4 : 2; }   // 0 fp32, 1 fp16, 2 bf16
-
-float halfToFloat(uint16_t h) {
-  uint32_t s = (h >> 15) & 1, e = (h >> 10) & 31, m = h & 1023, u;
-  if (e == 0) {
-    if (m == 0) u = s << 31;
-    else { e = 127 - 15 + 1; while (!(m & 1024)) { m <<= 1; --e; } m &= 1023; u = (s << 31) | (e << 23) | (m << 13); }
-  } else if (e == 31) u = (s << 31) | 0x7f800000u | (m << 13);
-  else u = (s << 31) | ((e + 112) << 23) | (m << 13);
-  float f; std::memcpy(&f, &u, 4); return f;
-}
-float elemToFloat(const char* p, int dt, size_t i) {
-  if (dt == 0) { float f; std::memcpy(&f, p + 4 * i, 4); return f; }
-  uint16_t h; std::memcpy(&h, p + 2 * i, 2);
-  if (dt == 1) return halfToFloat(h);
-  uint32_t u = (uint32_t)h << 16; float f; std::memcpy(&f, &u, 4); return f;
-}
-uint16_t floatToBf16(float f) {
-  uint32_t u; std::memcpy(&u, &f, 4);
-  u += 0x7fffu + ((u >> 16) & 1);
-  return (uint16_t)(u >> 16);
 }
 
 }  // namespace
@@ -147,7 +145,7 @@ private:
 };
 
 void Engine::loadLinear(const std::string& file, int inF, int outF, void* dst, int dstRowOffset, int dstLd) {
-  auto host = readFile(dir + "/" + file, (size_t)inF * outF * dtypeSize(fileDt));
+  auto host = readFile(dir + "/" + file, (size_t)inF * outF * dtypeSize(fileDt), fileDt);
   DevBuf tmp(host.size());
   XFT_CUDA(cudaMemcpy(tmp.p, host.data(), host.size(), cudaMemcpyHostToDevice));
   XFT_K(xft_transpose_to_bf16(tmp.p, fileDt, outF, inF, outF, static_cast<__nv_bfloat16*>(dst) + (size_t)dstRowOffset * dstLd,
@@ -159,9 +157,9 @@ DevBuf Engine::loadVector(const std::string& file, int n, bool optional) {
   std::ifstream probe(dir + "/" + file, std::ios::binary);
   if (!probe) {
     if (optional) return DevBuf();
-    throw std::runtime_error("missing " + file);
+    if (!Env::get().fakeModel) throw std::runtime_error("missing " + file);
   }
-  auto host = readFile(dir + "/" + file, (size_t)n * dtypeSize(fileDt));
+  auto host = readFile(dir + "/" + file, (size_t)n * dtypeSize(fileDt), fileDt);
   std::vector<float> f(n);
   for (int i = 0; i < n; ++i) f[i] = elemToFloat(host.data(), fileDt, i);
   DevBuf d((size_t)n * 4);
@@ -220,12 +218,12 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
   const int qsz = heads * headDim, kvsz = kvHeads * headDim;
   // embedding and lm_head are stored [vocab, hidden]: convert on the host
   {
-    auto host = readFile(dir + "/model.wte.bin", (size_t)vocab * hidden * dtypeSize(fileDt));
+    auto host = readFile(dir + "/model.wte.bin", (size_t)vocab * hidden * dtypeSize(fileDt), fileDt);
     std::vector<uint16_t> b((size_t)vocab * hidden);
     for (size_t i = 0; i < b.size(); ++i) b[i] = floatToBf16(elemToFloat(host.data(), fileDt, i));
     wte.reset(b.size() * 2);
     XFT_CUDA(cudaMemcpy(wte.p, b.data(), b.size() * 2, cudaMemcpyHostToDevice));
-    host = readFile(dir + "/model.lm_head.weight.bin", (size_t)vocab * hidden * dtypeSize(fileDt));
+    host = readFile(dir + "/model.lm_head.weight.bin", (size_t)vocab * hidden * dtypeSize(fileDt), fileDt);
     for (size_t i = 0; i < b.size(); ++i) b[i] = floatToBf16(elemToFloat(host.data(), fileDt, i));
     lmHead.reset(b.size() * 2);
     XFT_CUDA(cudaMemcpy(lmHead.p, b.data(), b.size() * 2, cudaMemcpyHostToDevice));

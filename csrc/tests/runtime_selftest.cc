@@ -15,6 +15,7 @@
 
 #include "arena.h"
 #include "beam.h"
+#include "dtypes.h"
 #include "env.h"
 #include "ini.h"
 #include "rope_tables.h"
@@ -308,6 +309,30 @@ static void testRopeTables() {
   EXPECT(a12.size() == 12 && a12[7] == a8[7] && std::fabs(a12[8] - std::pow(2.0, -0.5)) < 1e-6);
 }
 
+static void testDtypes() {
+  // every finite half survives the round trip; conversions of exact values are exact
+  for (uint32_t h = 0; h < 65536; ++h) {
+    const uint32_t e = (h >> 10) & 31;
+    if (e == 31 && (h & 1023)) continue;                       // NaN payloads are not preserved bit for bit
+    EXPECT(floatToHalf(halfToFloat((uint16_t)h)) == (uint16_t)h);
+  }
+  EXPECT(floatToHalf(1.0f) == 0x3c00 && floatToHalf(-2.0f) == 0xc000 && floatToHalf(65504.0f) == 0x7bff);
+  EXPECT(floatToHalf(65520.0f) == 0x7c00 && floatToHalf(1e9f) == 0x7c00 && floatToHalf(-1e9f) == 0xfc00);
+  EXPECT(floatToHalf(5.9604645e-8f) == 0x0001 && floatToHalf(2.0e-8f) == 0x0000);      // smallest subnormal; below half of it
+  // ties go to even: 1 + 2^-11 is halfway between 1 and 1 + 2^-10
+  EXPECT(floatToHalf(1.0f + 0.00048828125f) == 0x3c00 && floatToHalf(1.0f + 3 * 0.00048828125f) == 0x3c02);
+  EXPECT(floatToHalf(1.0f + 0.0005f) == 0x3c01);
+  EXPECT(floatToBf16(1.0f) == 0x3f80 && bf16ToFloat(0x3f80) == 1.0f && floatToBf16(-0.0f) == 0x8000);
+  EXPECT(floatToBf16(1.0f + 0.00390625f) == 0x3f80 && floatToBf16(1.0f + 3 * 0.00390625f) == 0x3f82);   // ties to even
+  const float vals[3] = {0.5f, -3.25f, 100.0f};
+  char buf[12];
+  std::memcpy(buf, vals, 12);
+  EXPECT(elemToFloat(buf, 0, 1) == -3.25f && dtypeSize(0) == 4 && dtypeSize(1) == 2 && dtypeSize(2) == 2);
+  uint16_t hs[2] = {floatToHalf(-3.25f), floatToBf16(100.0f)};
+  EXPECT(elemToFloat(reinterpret_cast<const char*>(hs), 1, 0) == -3.25f);
+  EXPECT(elemToFloat(reinterpret_cast<const char*>(hs), 2, 1) == 100.0f);
+}
+
 int main(int argc, char** argv) {
   const std::string dir = argc > 1 ? argv[1] : "/tmp";
   testPartition();
@@ -319,6 +344,7 @@ int main(int argc, char** argv) {
   testEnvAndTimeline(dir);
   testArena();
   testRopeTables();
+  testDtypes();
   std::printf("runtime_selftest: %d checks, %d failed\n", g_checks, g_failed);
   return g_failed ? 1 : 0;
 }

@@ -375,3 +375,24 @@ def test_parallel_layout_twins_match_python(core):
                 for r in range(world):
                     n = core.xftc_block_visit_order(nb, world, r, lag, buf)
                     assert list(buf[:n]) == P.block_visit_order(nb, world, r, lag)
+
+
+def test_host_numeric_conversions_match_torch(core):
+    """csrc/core/dtypes.h (float <-> fp16 / bf16 on the host, used while loading checkpoints) against torch's casts:
+    random values over many magnitudes, subnormals, ties and overflow."""
+    g = torch.Generator().manual_seed(0)
+    x = torch.cat([torch.randn(4000, generator=g) * 10 ** torch.randint(-9, 6, (4000,), generator=g).float(),
+                   torch.tensor([0.0, -0.0, 1.0, 65504.0, 65519.9, 65520.0, 1e9, -1e9, 5.96e-8, 2.9e-8, 3.1e-8, 6.1e-5,
+                                 1.0 + 2.0 ** -11, 1.0 + 3 * 2.0 ** -11, 1.0 + 2.0 ** -8, 1.0 + 3 * 2.0 ** -8])]).float()
+    n = x.numel()
+    src = (C.c_float * n)(*x.tolist())
+    for kind, dt in ((1, torch.float16), (2, torch.bfloat16)):
+        out = (C.c_uint16 * n)()
+        core.xftc_convert_from_float(src, out, n, kind)
+        want = x.to(dt).view(torch.int16).to(torch.int32) & 0xffff
+        got = torch.tensor(list(out), dtype=torch.int32)
+        assert torch.equal(got, want), (kind, x[(got != want).nonzero()[:5, 0]])
+        back = (C.c_float * n)()
+        core.xftc_convert_to_float(out, back, n, kind)
+        ref = x.to(dt).float()
+        assert torch.equal(torch.tensor(list(back)), ref)
