@@ -371,3 +371,48 @@ def test_xft_verbose_prints_one_line_per_gemm(tiny, monkeypatch, capfd):
     assert all(re.fullmatch(r"xft_verbose,exec,cpu,api,[a-z_]+,m\d+n\d+k\d+,\d+\.\d+", l) for l in lines), lines[:3]
     assert any(",m4n" in l for l in lines) and any(",m1n" in l for l in lines)        # prefill rows, then one row
     assert sum("gated" in l for l in lines) == 4 and sum("n1000k256" in l for l in lines) == 2
+
+
+def test_automatic_prefix_reuse_keeps_results_and_skips_work(tiny, monkeypatch):
+    """XFT_PREFIX_CACHE=1: a prompt that starts with tokens an earlier prefill has cached adopts those KV blocks and
+    runs only the rest; logits and generated tokens equal the engine without reuse."""
+    from xfastertransformer_b200.utils.flags import Env
+    g = torch.Generator().manual_seed(11)
+    common = torch.randint(5, 900, (150,), generator=g).tolist()              # two full 64-token blocks + 22
+    p1 = common + torch.randint(5, 900, (9,), generator=g).tolist()
+    p2 = common + torch.randint(5, 900, (30,), generator=g).tolist()
+    p3 = common[:100] + torch.randint(5, 900, (7,), generator=g).tolist()     # shares one full block only
+    plain = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+    want = {}
+    for name, p in (("p1", p1), ("p2", p2), ("p3", p3)):
+        sid = plain.set_input_cb([p], None, 256)
+        want[name] = plain.forward_cb()
+        plain.free_seqs(sid)
+    want_gen = plain.generate(torch.tensor([p2]), max_length=len(p2) + 6)
+    monkeypatch.setenv("XFT_PREFIX_CACHE", "1")
+    Env.get().reload()
+    try:
+        m = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+    finally:
+        monkeypatch.delenv("XFT_PREFIX_CACHE")
+        Env.get().reload()
+    eng = m.model
+    idx = eng.cache.prefix_index
+    assert idx is not None
+    ran = []
+    real = eng.make_batch
+    eng.make_batch = lambda seqs, la=False: (ran.append(sum(len(s.pending) for s in seqs)), real(seqs, la))[1]
+    sid = m.set_input_cb([p1], None, 256)
+    got1 = m.forward_cb()
+    m.free_seqs(sid)
+    assert ran[-1] == len(p1) and idx.hit_blocks == 0 and len(idx.entries) == 2
+    sid = m.set_input_cb([p2, p3], None, 256)                  # both reuse blocks of p1, in one ragged prefill
+    got23 = m.forward_cb()
+    m.free_seqs(sid)
+    assert ran[-1] == (len(p2) - 128) + (len(p3) - 64) and idx.hit_blocks == 3
+    for got, name in ((got1[0], "p1"), (got23[0], "p2"), (got23[1], "p3")):
+        assert torch.allclose(got, want[name][0], atol=2e-3, rtol=2e-3), name
+    out = m.generate(torch.tensor([p2]), max_length=len(p2) + 6)            # batch API: prefill of 2 full blocks is skipped
+    assert torch.equal(out, want_gen) and ran[-6] == len(p2) - 128
+    # nothing leaks: the only blocks still held are the remembered ones
+    assert not eng.cache.tables and eng.cache.alloc.num_blocks - eng.cache.alloc.num_free == len(idx.entries)

@@ -256,3 +256,33 @@ def test_general_follower_loop_gloo(tiny, tmp_path):
     Env.get().reload()
     m = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
     assert torch.equal(got["beams"], m.generate(ids[:, :12], max_length=18, num_beams=2))
+
+
+def test_prefix_reuse_under_tensor_parallelism_gloo(tiny, tmp_path):
+    """XFT_PREFIX_CACHE=1 on two tensor-parallel gloo ranks: both ranks adopt the same cached blocks (the index is a
+    pure function of the token stream), results equal the single-process engine without reuse."""
+    import xfastertransformer_b200 as xft
+    from xfastertransformer_b200.parallel.dist import DistContext
+    from xfastertransformer_b200.utils.flags import Env
+    out = str(tmp_path / "prefix.pt")
+    env = dict(os.environ, XFT_ENGINE="CPU", XFT_PREFIX_CACHE="1",
+               PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29681", os.path.join(ROOT, "tests", "prefix_worker.py"), tiny, out]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    got = torch.load(out)
+    os.environ["XFT_ENGINE"] = "CPU"
+    os.environ.pop("XFT_PREFIX_CACHE", None)
+    DistContext.reset()
+    Env.get().reload()
+    m = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+    g = torch.Generator().manual_seed(11)
+    common = torch.randint(5, 900, (150,), generator=g).tolist()
+    p2 = common + torch.randint(5, 900, (20,), generator=g).tolist()
+    sid = m.set_input_cb([p2], None, 256)
+    want = m.forward_cb()
+    m.free_seqs(sid)
+    assert torch.allclose(got["logits"], want, atol=2e-3, rtol=2e-3)
+    assert torch.equal(got["tokens"], m.generate(torch.tensor([p2]), max_length=len(p2) + 5))
+    assert got["stats"][0] == got["stats"][1] and got["stats"][0][0] == 4          # 2 blocks reused, twice

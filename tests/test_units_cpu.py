@@ -705,3 +705,49 @@ def test_fused_prefill_protocol_model_over_consecutive_launches():
             progressed = [step(r) for r in order if rng.random() < 0.6]
             if not any(progressed):
                 assert any(step(r) for r in order), f"deadlock world={world} nb={nb} launch={launch} pos={pos}"
+
+
+def test_prefix_index_shares_full_blocks_and_evicts_lru():
+    """Automatic prefix reuse at the block level: a chain of digests over full token blocks, one reference per remembered
+    block, longest-prefix lookup that always leaves a token to run, LRU eviction of blocks nobody else holds."""
+    from xfastertransformer_b200.runtime.kv_cache import PrefixIndex
+    cache = PagedKVCache(1, 1, 8, 8, "bf16", torch.device("cpu"), block_size=4)
+    cache.ensure_blocks(12)
+    idx = PrefixIndex(cache)
+    cache.prefix_index = idx
+    a = list(range(100, 111))                      # 11 tokens: two full blocks + 3
+    cache.add_sequence(1)
+    cache.append_slots(1, len(a))
+    assert idx.insert(a, cache.tables[1]) == 2 and idx.insert(a, cache.tables[1]) == 0
+    full = cache.tables[1][:2]
+    assert [cache.alloc.ref[b] for b in cache.tables[1]] == [2, 2, 1]
+    # same first block, different second block: one hit; a prompt that IS the remembered prefix keeps a token to run
+    assert idx.lookup(a[:4] + [7, 7, 7, 7, 7]) == full[:1]
+    assert idx.lookup(a[:8]) == full[:1] and idx.lookup(a[:9]) == full and idx.lookup([1, 2, 3, 4, 5]) == []
+    cache.add_sequence(2)
+    assert cache.adopt(2, idx.lookup(a[:8] + [5, 6])) == 8 and cache.tables[2] == full
+    slots = cache.append_slots(2, 2)               # continues in a fresh block, the shared ones stay untouched
+    assert cache.tables[2][:2] == full and slots[0] // 4 == cache.tables[2][2] and cache.tables[2][2] not in cache.tables[1]
+    cache.free_sequence(1)
+    cache.free_sequence(2)
+    assert [cache.alloc.ref[b] for b in full] == [1, 1] and cache.alloc.num_free == 10      # only the index holds them
+    # a second chain; then pressure: the least recently used chain goes first, children before parents
+    b = list(range(200, 209))
+    cache.add_sequence(3)
+    cache.append_slots(3, len(b))
+    idx.insert(b, cache.tables[3])
+    tab_b = list(cache.tables[3][:2])
+    cache.free_sequence(3)
+    idx.lookup(a + [0])                            # chain a is now the most recently used one
+    assert cache.alloc.num_free == 8
+    cache.reserve(10)                              # needs two more blocks: both come from chain b, nothing grows
+    assert cache.alloc.num_blocks == 12 and cache.alloc.num_free == 10 and idx.evicted == 2
+    assert idx.lookup(b + [0]) == [] and idx.lookup(a + [0]) == full
+    assert all(cache.alloc.ref[x] == 0 for x in tab_b)
+    cache.add_sequence(4)
+    cache.adopt(4, idx.lookup(a + [0]))
+    cache.reserve(12)                              # blocks held by a live sequence are never evicted: the pools grow
+    assert cache.alloc.num_blocks > 12 and idx.lookup(a + [0]) == full
+    cache.free_sequence(4)
+    idx.clear()
+    assert cache.alloc.num_free == cache.alloc.num_blocks

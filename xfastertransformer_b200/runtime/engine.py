@@ -74,6 +74,11 @@ class Model:
         self.cache = PagedKVCache(len(self.decoder.layers), geo["kv_heads"], geo["k_dim"], geo["v_dim"],
                                   kv_cache_dtype, self.ctx.device, self.env.kv_block_size,
                                   self.decoder.act_dtype, geo["latent"])
+        if self.env.prefix_cache and self.ctx.dp_size == 1:
+            # data-parallel attention keeps each sequence's cache on one rank only, while all ranks must agree on how
+            # many tokens a prompt still has to run: automatic reuse stays off there
+            from .kv_cache import PrefixIndex
+            self.cache.prefix_index = PrefixIndex(self.cache)
         self.pool = SequencePool()
         self.sampling = SamplingMeta()
         self._greedy_cfg = SamplingMeta()
@@ -208,17 +213,17 @@ class Model:
         self._prompts = prompts
         nb = max(cfg.num_beams, 1)
         dp, me = self.ctx.dp_size, self.ctx.dp_rank          # data-parallel attention: a rank caches only its own requests
-        total_blocks = sum(self.cache.blocks_for(max(cfg.max_length, len(p)) + 1)
-                           for g, p in enumerate(prompts) if g % dp == me) * nb
-        self.cache.reserve(total_blocks)
         seqs = []
         for g, p in enumerate(prompts):
             if len(p) >= cfg.max_length:
                 log.warning(f"prompt {g}: length {len(p)} >= max_length {cfg.max_length}")
             s = self.pool.new(p, max(cfg.max_length, len(p) + 1), group=g, owner=g % self.ctx.dp_size)
             self.cache.add_sequence(s.seq_id)
-            self._attach_prefix(s)
+            self._attach_prefix(s)                # before the reservation: adopted blocks must not be evicted for it
             seqs.append(s)
+        total_blocks = sum(self.cache.blocks_for(max(cfg.max_length, len(p)) + 1)
+                           for g, p in enumerate(prompts) if g % dp == me) * nb
+        self.cache.reserve(total_blocks)
         self.working = seqs
         self.scorer = None
         self._beam_pending = nb > 1
@@ -232,6 +237,13 @@ class Model:
         src/models/common_decoder.h:337-353,695-771)."""
         pre = self.prefix_seq
         if pre is None:
+            idx = self.cache.prefix_index
+            if idx is not None and s.past_len == 0 and len(s.pending) == len(s.prompt):
+                blocks = idx.lookup(s.prompt)
+                if blocks:
+                    n = self.cache.adopt(s.seq_id, blocks)
+                    s.past_len = s.prefix_len = n
+                    s.pending = s.prompt[n:]
             return
         n = len(pre.prompt)
         if len(s.prompt) > n and s.prompt[:n] == pre.prompt:
@@ -409,11 +421,12 @@ class Model:
                 s.owner = s.seq_id % self.ctx.dp_size
                 off += n
                 active.append(s)
-            # data-parallel attention: a rank caches only the sequences it owns
-            self.cache.reserve(sum(self.cache.blocks_for(s.max_len + 1) for s in active if s.owner == self.ctx.dp_rank))
             for s in active:
                 self.cache.add_sequence(s.seq_id)
-                self._attach_prefix(s)
+                self._attach_prefix(s)            # before the reservation: adopted blocks must not be evicted for it
+            # data-parallel attention: a rank caches only the sequences it owns
+            self.cache.reserve(sum(self.cache.blocks_for(s.max_len + 1) - len(self.cache.tables[s.seq_id])
+                                   for s in active if s.owner == self.ctx.dp_rank))
         else:                                             # next tokens of known sequences
             if len(ids) != len(seq_ids):
                 raise ValueError("set_input_cb: one next token per sequence id expected")
@@ -624,7 +637,19 @@ class Model:
         dec = self.decoder if b.is_decode else self.prefill_decoder
         name = "Next Token" if b.is_decode else "1st Token"
         with TimeLine(name), torch.no_grad():
-            return dec.forward(b, self.cache)
+            out = dec.forward(b, self.cache)
+        self._remember_prefixes(seqs)
+        return out
+
+    def _remember_prefixes(self, seqs: Sequence[SequenceMeta]) -> None:
+        """Automatic prefix reuse: the full blocks a prefill has just written become available to later prompts."""
+        idx = self.cache.prefix_index
+        if idx is None:
+            return
+        for s in seqs:
+            if len(s.pending) > 1 and s.seq_id in self.cache.tables:
+                n = s.past_len + len(s.pending)               # tokens of this sequence now in the cache
+                idx.insert(s.all_tokens()[:n], self.cache.tables[s.seq_id])
 
     def _dp_forward(self, seqs: Sequence[SequenceMeta], logits_all: bool) -> torch.Tensor:
         """Data-parallel attention (XFT_ATTENTION_DP=1): every rank runs the decoder on the sequences it owns; inside
@@ -693,6 +718,8 @@ class Model:
                 outs.append(out)
         for h, _ in sends:
             h.wait()
+        for g in groups:
+            self._remember_prefixes(g)
         self.pp_microbatches = getattr(self, "pp_microbatches", 0) + len(batches)
         # same tp_rank column across stages
         src = (ctx.pp_size - 1) * ctx.tp_size + ctx.tp_rank

@@ -58,6 +58,77 @@ class BlockAllocator:
             raise RuntimeError(f"double free of KV block {b}")
 
 
+class PrefixIndex:
+    """Automatic prefix reuse: full token blocks that a prefill has written are remembered under a hash chain of their
+    tokens (the digest of block j covers blocks 0..j), so a later prompt that starts with the same tokens adopts those
+    blocks instead of recomputing them.  The index holds one reference per remembered block; blocks are immutable once
+    full (a sequence only ever writes into its own tail block), so sharing them is safe.  Least recently used entries
+    whose block nobody else holds are dropped when the allocator runs short.  (The reference only has the explicit,
+    single-prefix ``setPrefix`` API: src/models/common_decoder.h:337-353.)"""
+
+    def __init__(self, cache: "PagedKVCache"):
+        from collections import OrderedDict
+        self.cache = cache
+        self.entries: "OrderedDict[bytes, int]" = OrderedDict()       # chain digest -> block id
+        self.lookups = self.hit_blocks = self.evicted = 0
+
+    def _digests(self, tokens: Sequence[int], n_blocks: int) -> List[bytes]:
+        import hashlib
+        import struct
+        b = self.cache.block
+        out, prev = [], b""
+        for j in range(n_blocks):
+            chunk = tokens[j * b:(j + 1) * b]
+            prev = hashlib.blake2b(prev + struct.pack(f"<{b}i", *chunk), digest_size=16).digest()
+            out.append(prev)
+        return out
+
+    def lookup(self, tokens: Sequence[int]) -> List[int]:
+        """Blocks holding the longest remembered prefix of `tokens`, leaving at least one token to run."""
+        self.lookups += 1
+        n = (len(tokens) - 1) // self.cache.block
+        hit: List[bytes] = []
+        for d in self._digests(tokens, n):
+            if d not in self.entries:
+                break
+            hit.append(d)
+        for d in reversed(hit):                   # a parent ends up more recent than its children: evicted after them
+            self.entries.move_to_end(d)
+        self.hit_blocks += len(hit)
+        return [self.entries[d] for d in hit]
+
+    def insert(self, tokens: Sequence[int], table: Sequence[int]) -> int:
+        """Remember the full blocks of `tokens` (already written to `table`); returns how many were new."""
+        n = min(len(tokens) // self.cache.block, len(table))
+        new = 0
+        for j, d in enumerate(self._digests(tokens, n)):
+            if d in self.entries:
+                self.entries.move_to_end(d)
+                continue
+            self.entries[d] = self.cache.alloc.share(table[j])
+            new += 1
+        return new
+
+    def evict(self, want: int) -> int:
+        """Drop up to `want` least recently used entries whose block only the index still holds."""
+        freed = 0
+        for d in list(self.entries):
+            if freed >= want:
+                break
+            b = self.entries[d]
+            if self.cache.alloc.ref[b] == 1:
+                del self.entries[d]
+                self.cache.alloc.release(b)
+                freed += 1
+        self.evicted += freed
+        return freed
+
+    def clear(self) -> None:
+        for b in self.entries.values():
+            self.cache.alloc.release(b)
+        self.entries.clear()
+
+
 class PagedKVCache:
     def __init__(self, num_layers: int, kv_heads: int, k_dim: int, v_dim: int, dtype: str, device: torch.device,
                  block_size: int = 64, act_dtype: torch.dtype = torch.bfloat16, latent: bool = False):
@@ -83,6 +154,7 @@ class PagedKVCache:
         self.tables: Dict[int, List[int]] = {}
         self.lens: Dict[int, int] = {}
         self.version = 0                         # bumped when pools are reallocated
+        self.prefix_index: Optional[PrefixIndex] = None      # set by the engine when automatic prefix reuse is on
 
     # -- capacity -------------------------------------------------------------------
     def bytes_per_block(self) -> int:
@@ -133,6 +205,11 @@ class PagedKVCache:
         """Make sure `extra_blocks` free blocks exist (grows geometrically)."""
         if self.alloc.num_free >= extra_blocks:
             return
+        if self.prefix_index is not None and self.alloc.num_blocks > 0:
+            # remembered prefixes give way before the pools grow (growing moves the pools and invalidates graphs)
+            self.prefix_index.evict(extra_blocks - self.alloc.num_free)
+            if self.alloc.num_free >= extra_blocks:
+                return
         need = self.alloc.num_blocks - self.alloc.num_free + extra_blocks
         self.ensure_blocks(max(need, int(self.alloc.num_blocks * 1.5)))
 
@@ -149,6 +226,13 @@ class PagedKVCache:
         for b in self.tables.pop(seq_id, []):
             self.alloc.release(b)
         self.lens.pop(seq_id, None)
+
+    def adopt(self, seq_id: int, blocks: Sequence[int]) -> int:
+        """Start a fresh sequence on shared, full blocks (automatic prefix reuse); returns the tokens they hold."""
+        assert not self.tables[seq_id], "adopt() is for a sequence that holds nothing yet"
+        self.tables[seq_id] = [self.alloc.share(b) for b in blocks]
+        self.lens[seq_id] = len(blocks) * self.block
+        return self.lens[seq_id]
 
     def fork(self, src: int, dst: int) -> None:
         """dst shares all of src's blocks (prefix sharing, beam expansion)."""
