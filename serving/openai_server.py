@@ -347,6 +347,10 @@ def make_handler(sched: Scheduler, tok: Tokenizer, model_name: str):
                 m = sched.metrics
                 lines = [f"xft_{k} {v}" for k, v in m.items()]
                 lines.append(f"xft_running {len(sched.running)}")
+                idx = getattr(getattr(getattr(sched.model, "model", None), "cache", None), "prefix_index", None)
+                if idx is not None:               # automatic prefix reuse (XFT_PREFIX_CACHE=1)
+                    lines += [f"xft_prefix_lookups {idx.lookups}", f"xft_prefix_hit_blocks {idx.hit_blocks}",
+                              f"xft_prefix_cached_blocks {len(idx.entries)}", f"xft_prefix_evicted_blocks {idx.evicted}"]
                 lines.append(f"xft_waiting {sched.waiting.qsize()}")
                 body = ("\n".join(lines) + "\n").encode()
                 self.send_response(200)
