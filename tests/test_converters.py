@@ -150,3 +150,35 @@ def test_reference_tool_module_names_resolve():
         assert getattr(m, cls) is getattr(xft.tools, cls), (mod, cls)
     with pytest.raises(ImportError):
         importlib.import_module("xfastertransformer.tools.no_such_convert")
+
+
+def test_converter_cli_picks_the_family(tmp_path, capsys):
+    """python -m xfastertransformer_b200.tools: the converter follows from config.json; the converted model matches HF."""
+    from transformers import Qwen2Config, Qwen2ForCausalLM
+    from xfastertransformer_b200.tools.__main__ import main, pick_converter
+    torch.manual_seed(5)
+    cfg = Qwen2Config(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, max_position_embeddings=256, tie_word_embeddings=False)
+    model = Qwen2ForCausalLM(cfg).eval()
+    src, out = str(tmp_path / "hf"), str(tmp_path / "xft")
+    model.save_pretrained(src, safe_serialization=True)
+    assert main(["-i", src, "-o", out, "-d", "fp32"]) == 0
+    assert "Qwen2Convert: wrote" in capsys.readouterr().out
+    ids = torch.randint(0, 512, (1, 15))
+    got = xft.AutoModel.from_pretrained(out, dtype="bf16")(ids)
+    with torch.no_grad():
+        want = model(ids).logits.float()
+    assert torch.allclose(got, want, atol=1.5e-2, rtol=1.5e-2)
+    assert main(["--list"]) == 0 and "DeepSeekR1Convert" in capsys.readouterr().out
+    pick = lambda **kw: pick_converter(kw)
+    assert pick(model_type="llama") == "LlamaConvert" and pick(model_type="mixtral") == "MixtralConvert"
+    assert pick(model_type="llama", rope_scaling={"type": "yarn", "factor": 4}) == "YaRNLlamaConvert"
+    assert pick(model_type="deepseek_v3") == "DeepSeekV3Convert" and pick(model_type="qwen3_moe") == "Qwen3Convert"
+    assert pick(model_type="chatglm", multi_query_attention=True, _name_or_path="THUDM/chatglm3-6b") == "ChatGLM3Convert"
+    assert pick(model_type="chatglm", multi_query_attention=True, _name_or_path="THUDM/glm-4-9b") == "ChatGLM4Convert"
+    assert pick(model_type="chatglm", num_layers=28) == "ChatGLMConvert"
+    assert pick(architectures=["BaichuanForCausalLM"], vocab_size=125696) == "Baichuan2Convert"
+    with pytest.raises(ValueError):
+        pick(model_type="mamba")
+    with pytest.raises(SystemExit):
+        main(["-i", src, "--family", "NoSuchConvert"])
