@@ -416,3 +416,78 @@ def test_automatic_prefix_reuse_keeps_results_and_skips_work(tiny, monkeypatch):
     assert torch.equal(out, want_gen) and ran[-6] == len(p2) - 128
     # nothing leaks: the only blocks still held are the remembered ones
     assert not eng.cache.tables and eng.cache.alloc.num_blocks - eng.cache.alloc.num_free == len(idx.entries)
+
+
+@pytest.mark.parametrize("prefix_cache", [0, 1])
+def test_continuous_batching_random_schedules(tiny, monkeypatch, prefix_cache):
+    """Randomised continuous-batching sessions: prompts arrive at random steps (sometimes several at once, sometimes in
+    the same forward as the running sequences), sequences leave at random lengths, some prompts repeat a long common
+    beginning.  Every sequence's tokens must equal its stand-alone greedy decode, whatever it shared a batch with, and
+    the cache must be empty at the end (apart from remembered prefix blocks)."""
+    import random
+    from xfastertransformer_b200.utils.flags import Env
+    monkeypatch.setenv("XFT_PREFIX_CACHE", str(prefix_cache))
+    Env.get().reload()
+    try:
+        model = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+    finally:
+        monkeypatch.delenv("XFT_PREFIX_CACHE")
+        Env.get().reload()
+    rng = random.Random(7 + prefix_cache)
+    common = [rng.randrange(5, 900) for _ in range(70)]
+    prompts = []
+    for i in range(9):
+        body = [rng.randrange(5, 900) for _ in range(rng.randint(1, 40))]
+        prompts.append((common + body) if i % 3 == 0 else body)
+    want_len = [rng.randint(1, 9) for _ in prompts]
+    solo = [_greedy_stream(model, p, n) for p, n in zip(prompts, want_len)]
+    arrive = sorted(rng.randint(0, 12) for _ in prompts)
+    got = {i: [] for i in range(len(prompts))}
+    sid_of, last = {}, {}
+    step, nxt = 0, 0
+    while nxt < len(prompts) or sid_of:
+        new = []
+        while nxt < len(prompts) and arrive[nxt] <= step:
+            new.append(nxt)
+            nxt += 1
+        running = list(sid_of)
+        if new and running and rng.random() < 0.5:
+            # mixed step: the new prompts and the running sequences' next tokens in ONE forward
+            sids = model.set_input_cb([prompts[i] for i in new], None, 256, hold=True)
+            model.set_input_cb([last[i] for i in running], [sid_of[i] for i in running], None, append=True)
+            logits = model.forward_cb()
+            for i, s in zip(new, sids.tolist()):
+                sid_of[i] = s
+            order = new + running
+        else:
+            order = []
+            if new:
+                sids = model.set_input_cb([prompts[i] for i in new], None, 256)
+                logits_new = model.forward_cb()
+                for i, s in zip(new, sids.tolist()):
+                    sid_of[i] = s
+                order += new
+            if running:
+                model.set_input_cb([last[i] for i in running], [sid_of[i] for i in running], None)
+                logits_run = model.forward_cb()
+                order += running
+            parts = ([logits_new] if new else []) + ([logits_run] if running else [])
+            logits = torch.cat(parts, 0) if parts else None
+        done = []
+        for row, i in enumerate(order):
+            t = int(logits[row].argmax())
+            got[i].append(t)
+            last[i] = t
+            if len(got[i]) >= want_len[i]:
+                done.append(i)
+        if done:
+            model.free_seqs([sid_of.pop(i) for i in done])
+        step += 1
+        assert step < 200
+    for i in range(len(prompts)):
+        assert got[i] == solo[i], (i, got[i], solo[i])
+    eng = model.model
+    held = len(eng.cache.prefix_index.entries) if eng.cache.prefix_index is not None else 0
+    assert not eng.cache.tables and eng.cache.alloc.num_blocks - eng.cache.alloc.num_free == held
+    if prefix_cache:
+        assert eng.cache.prefix_index.hit_blocks >= 2          # the common beginning (one full block) was reused
