@@ -48,6 +48,7 @@ class Request:
         self.logprobs = logprobs                      # None, or how many alternatives to report per position (0 = chosen only)
         self.stop_fn = stop_fn                        # callable(generated ids) -> bool: a stop string has appeared
         self.cancelled = False                        # set by the handler when the client went away
+        self.fed = 0                                  # chunked prefill: prompt tokens already given to the engine
         self.token_logprobs: List[float] = []
         self.top_logprobs: List[Dict[int, float]] = []
         self.out: "queue.Queue" = queue.Queue()       # ints, then None (or an Exception) at the end
@@ -77,8 +78,11 @@ class Scheduler(threading.Thread):
         self.running: Dict[int, Request] = {}
         self.stop_flag = threading.Event()
         self.metrics = dict(requests=0, finished=0, prompt_tokens=0, generated_tokens=0, ttft_sum=0.0, tpot_sum=0.0,
-                            tpot_count=0, steps=0, mixed_steps=0, errors=0, cancelled=0)
+                            tpot_count=0, steps=0, mixed_steps=0, errors=0, cancelled=0, prefill_chunks=0)
         self.mixed_steps = False          # prefill new prompts in the same forward as the running sequences' decode
+        self.prefill_chunk = 0            # > 0: prompts longer than this are fed in pieces of this many tokens, one piece
+        #                                   per scheduler turn, so a long prompt does not stall the running sequences
+        self.prefilling: Dict[int, Request] = {}      # sequences whose prompt is still being fed (req.fed tokens so far)
         self.max_len = int(getattr(model.model.cfg, "max_pos_seq_len", 0) or 0)
         self.kv_fraction = 0.8            # share of the free device memory the warm-up gives to the KV pools
 
@@ -169,7 +173,8 @@ class Scheduler(threading.Thread):
         if greedy:
             return [int(t) for t in self.model.forward_cb_greedy()]
         logits = self.model.forward_cb()
-        return [self._select(r, row) for r, row in zip(reqs, logits)]
+        # a request whose prompt is still being fed has no token to pick yet
+        return [self._select(r, row) if r.fed >= len(r.prompt_ids) else -1 for r, row in zip(reqs, logits)]
 
     def _emit(self, req: Request, tok: int) -> bool:
         """Record a token; returns True when the request is finished."""
@@ -211,8 +216,9 @@ class Scheduler(threading.Thread):
     def run(self):
         while not self.stop_flag.is_set():
             admitted: List[Request] = []
-            block = not self.running
-            while len(self.running) + len(admitted) < self.max_batch and len(admitted) < self.prefill_per_step:
+            block = not self.running and not self.prefilling
+            while len(self.running) + len(self.prefilling) + len(admitted) < self.max_batch and \
+                    len(admitted) < self.prefill_per_step:
                 try:
                     r = self.waiting.get(block=block and not admitted, timeout=0.2 if block else None)
                 except queue.Empty:
@@ -231,6 +237,22 @@ class Scheduler(threading.Thread):
                                                        f"{self.max_len} positions" if r.prompt_ids else "empty prompt"))
                         else:
                             ok.append(r)
+                    long = [r for r in ok if self.prefill_chunk > 0 and len(r.prompt_ids) > self.prefill_chunk]
+                    if long:
+                        # chunked prefill: the first piece creates the sequence (sized for the whole request); the
+                        # rest follows one piece per turn below
+                        ok = [r for r in ok if r not in long]
+                        c = self.prefill_chunk
+                        sids = self.model.set_input_cb([r.prompt_ids[:c] for r in long], None,
+                                                       [len(r.prompt_ids) + r.max_tokens + 1 for r in long], greedy=True)
+                        for r, sid in zip(long, [int(x) for x in sids]):
+                            r.fed = c
+                            self.prefilling[sid] = r
+                        self.model.forward_cb_greedy()
+                        self.metrics["steps"] += 1
+                        self.metrics["prefill_chunks"] += len(long)
+                    for r in ok:
+                        r.fed = len(r.prompt_ids)
                     if ok and self.mixed_steps and self.running:
                         # one forward for the new prompts AND the running sequences: decoding does not pause for prefill
                         sids_run = list(self.running)
@@ -265,6 +287,8 @@ class Scheduler(threading.Thread):
                                 done.append(sid)
                         self._finish(done)
                         self.metrics["steps"] += 1
+                if self.prefilling:
+                    self._feed_prompts()
                 if self.running:
                     sids = list(self.running)
                     reqs = [self.running[s] for s in sids]
@@ -275,14 +299,51 @@ class Scheduler(threading.Thread):
                     self._finish(done)
                     self.metrics["steps"] += 1
             except Exception as e:      # an engine error ends the affected requests, not the server
-                victims = list(self.running.values()) + [r for r in admitted if r not in self.running.values()]
+                known = list(self.running.values()) + list(self.prefilling.values())
+                victims = known + [r for r in admitted if r not in known]
                 try:
-                    if self.running:
-                        self.model.free_seqs(list(self.running))
+                    if self.running or self.prefilling:
+                        self.model.free_seqs(list(self.running) + list(self.prefilling))
                 except Exception:
                     pass
                 self.running.clear()
+                self.prefilling.clear()
                 self._fail(victims, e)
+
+    def _feed_prompts(self):
+        """Chunked prefill: the next piece of up to ``prefill_per_step`` long prompts, in one forward.  A prompt whose
+        last piece went in gets its first token from this forward and joins the running set."""
+        c = self.prefill_chunk
+        sids = list(self.prefilling)[:self.prefill_per_step]
+        gone = [s for s in sids if self.prefilling[s].cancelled]
+        if gone:                                        # the client left while its prompt was still being fed
+            self.model.free_seqs(gone)
+            for s in gone:
+                r = self.prefilling.pop(s)
+                self.metrics["cancelled"] += 1
+                r.finish_reason = "cancelled"
+                r.out.put(None)
+            sids = [s for s in sids if s not in gone]
+        if not sids:
+            return
+        reqs = [self.prefilling[s] for s in sids]
+        pieces = [r.prompt_ids[r.fed:r.fed + c] for r in reqs]
+        greedy = all(r.greedy_on_device for r in reqs)
+        self.model.set_input_cb(pieces, sids, None, greedy=greedy, extend=True)
+        for r, p in zip(reqs, pieces):
+            r.fed += len(p)
+        picks = self._forward(reqs, greedy)
+        self.metrics["steps"] += 1
+        self.metrics["prefill_chunks"] += len(sids)
+        done = []
+        for sid, r, tok in zip(sids, reqs, picks):
+            if r.fed >= len(r.prompt_ids):
+                del self.prefilling[sid]
+                self.running[sid] = r
+                self.metrics["prompt_tokens"] += len(r.prompt_ids)
+                if self._emit(r, tok):
+                    done.append(sid)
+        self._finish(done)
 
 
 class Tokenizer:
@@ -493,11 +554,12 @@ def make_handler(sched: Scheduler, tok: Tokenizer, model_name: str):
 
 
 def serve(model, port: int, token_path: str = "", max_batch: int = 64, prefill_per_step: int = 4, model_name: str = "xft",
-          warmup: bool = False, max_context: int = 0, mixed_steps: bool = False):
+          warmup: bool = False, max_context: int = 0, mixed_steps: bool = False, prefill_chunk: int = 0):
     """Start scheduler + HTTP server (threads); returns (httpd, scheduler, bound_port)."""
     tok = Tokenizer(token_path)
     sched = Scheduler(model, max_batch, prefill_per_step, eos_id=tok.eos)
     sched.mixed_steps = mixed_steps
+    sched.prefill_chunk = max(0, int(prefill_chunk))
     if warmup:
         sched.warmup(max_context)
     sched.start()
@@ -518,6 +580,8 @@ def main():
     ap.add_argument("--prefill_per_step", type=int, default=4)
     ap.add_argument("--no_warmup", action="store_true", help="do not pre-capture the decode graphs of every batch bucket")
     ap.add_argument("--max_context", type=int, default=0, help="longest prompt + output the graphs are sized for")
+    ap.add_argument("--prefill_chunk", type=int, default=0,
+                    help="feed prompts longer than this many tokens in pieces, one per scheduler turn (0 = whole prompts)")
     ap.add_argument("--mixed_steps", action="store_true",
                     help="prefill new prompts in the same forward as the running sequences (lower time per output token "
                          "under load; the step runs eagerly instead of replaying the decode graph)")
@@ -529,7 +593,7 @@ def main():
         return
     _, _, port = serve(model, a.port, a.token_path, a.max_batch, a.prefill_per_step,
                        os.path.basename(a.model_path.rstrip("/")), warmup=not a.no_warmup, max_context=a.max_context,
-                       mixed_steps=a.mixed_steps)
+                       mixed_steps=a.mixed_steps, prefill_chunk=a.prefill_chunk)
     print(f"OpenAI-compatible server on :{port}", flush=True)
     threading.Event().wait()
 

@@ -491,3 +491,49 @@ def test_continuous_batching_random_schedules(tiny, monkeypatch, prefix_cache):
     assert not eng.cache.tables and eng.cache.alloc.num_blocks - eng.cache.alloc.num_free == held
     if prefix_cache:
         assert eng.cache.prefix_index.hit_blocks >= 2          # the common beginning (one full block) was reused
+
+
+def test_chunked_prefill_through_extend(tiny):
+    """set_input_cb(extend=True): a prompt fed in pieces, with another sequence decoding in between (also in the same
+    forward), ends with the logits of the one-shot prefill and continues with the same tokens."""
+    model = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+    g = torch.Generator().manual_seed(21)
+    long_p = torch.randint(5, 900, (150,), generator=g).tolist()
+    other = torch.randint(5, 900, (12,), generator=g).tolist()
+    sid = model.set_input_cb([long_p], None, 256)
+    want = model.forward_cb()[0]
+    model.free_seqs(sid)
+    want_other = _greedy_stream(model, other, 6)
+    so = model.set_input_cb([other], None, 64)
+    lo = model.forward_cb()
+    toks = [int(lo[0].argmax())]
+    s1 = model.set_input_cb([long_p[:64]], None, [200])                       # first piece; max_length of the whole request
+    model.forward_cb()
+    model.set_input_cb([toks[-1]], so, None)                                   # the other sequence decodes in between
+    toks.append(int(model.forward_cb()[0].argmax()))
+    # second piece in the same forward as the other sequence's next token
+    model.set_input_cb([long_p[64:130]], s1, None, extend=True, hold=True)
+    model.set_input_cb([toks[-1]], so, None, append=True)
+    both = model.forward_cb()
+    toks.append(int(both[1].argmax()))
+    model.set_input_cb([long_p[130:]], s1, None, extend=True)
+    got = model.forward_cb()[0]
+    assert torch.allclose(got, want, atol=2e-3, rtol=2e-3), (got - want).abs().max()
+    for _ in range(3):
+        model.set_input_cb([toks[-1]], so, None)
+        toks.append(int(model.forward_cb()[0].argmax()))
+    assert toks == want_other
+    # the sequence decodes on from here like any other
+    t = int(got.argmax())
+    model.set_input_cb([t], s1, None)
+    nxt = model.forward_cb()
+    sid = model.set_input_cb([long_p + [t]], None, 256)
+    assert torch.allclose(nxt[0], model.forward_cb()[0], atol=2e-3, rtol=2e-3)
+    model.free_seqs(sid)
+    with pytest.raises(RuntimeError):
+        model.set_input_cb([[1, 2]], s1, None, extend=True)                   # a prompt does not grow after generation started
+    model.free_seqs(torch.cat([s1, so]))
+    with pytest.raises(ValueError):
+        s2 = model.set_input_cb([[1, 2, 3]], None, [6])
+        model.forward_cb()
+        model.set_input_cb([[4, 5, 6, 7]], s2, None, extend=True)             # beyond the sequence's max_length

@@ -411,3 +411,50 @@ def test_openai_server_drops_a_request_whose_client_left(tmp_path):
     finally:
         sched.shutdown()
         httpd.shutdown()
+
+
+def test_openai_server_chunked_prefill(tmp_path):
+    """--prefill_chunk: long prompts are fed in pieces between the decode steps of the running sequences; every request
+    still returns what a lone greedy generate() returns, sampled requests included, and nothing leaks."""
+    import importlib.util
+    import threading
+    spec = importlib.util.spec_from_file_location("oai", os.path.join(ROOT, "serving", "openai_server.py"))
+    oai = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(oai)
+    d = str(tmp_path / "tiny")
+    write_synthetic_checkpoint(d, preset("tiny-llama", vocab_size=500), seed=3, dtype="fp32", std=0.1)
+    model = xft.AutoModel.from_pretrained(d, dtype="bf16")
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(5, 490, (n,), generator=g).tolist() for n in (50, 7, 33, 16, 70, 3)]
+    want = [model.generate(torch.tensor([p]), max_length=len(p) + 5)[0, len(p):].tolist() for p in prompts]
+    httpd, sched, port = oai.serve(model, 0, max_batch=8, prefill_per_step=2, model_name="tiny", prefill_chunk=16)
+    base = f"http://127.0.0.1:{port}"
+
+    def post(body):
+        req = urllib.request.Request(base + "/v1/completions", data=json.dumps(body).encode(),
+                                     headers={"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=120) as r:
+            return json.loads(r.read())
+
+    try:
+        got = [None] * len(prompts)
+
+        def one(i):
+            got[i] = post({"prompt": prompts[i], "max_tokens": 5})
+
+        ths = [threading.Thread(target=one, args=(i,)) for i in range(len(prompts))]
+        [t.start() for t in ths]
+        [t.join() for t in ths]
+        for i, r in enumerate(got):
+            assert r["choices"][0]["token_ids"] == want[i], (i, r["choices"][0]["token_ids"], want[i])
+        # 50, 33 and 70 tokens at 16 per piece: 4 + 3 + 5 pieces
+        assert sched.metrics["prefill_chunks"] == 12 and sched.metrics["prompt_tokens"] == sum(map(len, prompts))
+        # a request that needs the logits (log-probabilities) through the chunked path
+        r = post({"prompt": prompts[0], "max_tokens": 5, "logprobs": 1})
+        assert r["choices"][0]["token_ids"] == want[0] and len(r["choices"][0]["logprobs"]["token_logprobs"]) == 5
+        eng = model.model
+        assert not sched.running and not sched.prefilling and not eng.cache.tables
+        assert eng.cache.alloc.num_free == eng.cache.alloc.num_blocks
+    finally:
+        sched.shutdown()
+        httpd.shutdown()

@@ -41,10 +41,17 @@ class AutoModel:
     def set_input_cb(self, input_ids: Optional[Union[List[int], List[List[int]], torch.Tensor]] = None,
                      seq_ids: Optional[Union[List[int], torch.Tensor]] = None,
                      max_length: Optional[Union[int, List[int], torch.Tensor]] = None, greedy: bool = False,
-                     append: bool = False, hold: bool = False):
-        """``append`` / ``hold`` build one forward out of new prompts and running sequences (see
-        ``runtime.engine.Model.set_input_cb``); both are extensions of the reference's call."""
+                     append: bool = False, hold: bool = False, extend: bool = False):
+        """``append`` / ``hold`` build one forward out of new prompts and running sequences, ``extend`` feeds further
+        pieces of the prompts of known sequences (chunked prefill; ``input_ids`` = one list per sequence id); see
+        ``runtime.engine.Model.set_input_cb``.  All three are extensions of the reference's call."""
         seq_lens = None
+        if extend:
+            if seq_ids is None or not isinstance(input_ids, list) or not input_ids or not isinstance(input_ids[0], list):
+                raise ValueError("extend=True takes seq_ids and one list of tokens per sequence")
+            seq_lens = [len(r) for r in input_ids]
+            input_ids = [t for r in input_ids for t in r]
+            return self.model.set_input_cb(input_ids, seq_lens, seq_ids, max_length, greedy, append, hold, True)
         if isinstance(input_ids, list):
             if seq_ids is None:
                 if input_ids and isinstance(input_ids[0], list):

@@ -379,14 +379,19 @@ class Model:
     # continuous-batching API
     # ------------------------------------------------------------------------------------
     def set_input_cb(self, input_ids=None, seq_lens=None, seq_ids=None, max_length=None, greedy: bool = False,
-                     append: bool = False, hold: bool = False) -> torch.Tensor:
+                     append: bool = False, hold: bool = False, extend: bool = False) -> torch.Tensor:
         """Prefill: ``input_ids`` = flattened prompts + ``seq_lens``; decode: ``input_ids`` [bs,1] +
         ``seq_ids``.  Returns the sequence ids (models.cpp:586-674).  ``greedy=True`` announces that the step will be
         run with ``forward_cb_greedy`` (followers need to know which forward follows).
 
         Mixed steps (new prompts and running sequences in ONE forward, so decoding does not pause while prompts are
         prefilled): call once with the prompts and ``hold=True`` (followers do not run a forward yet), then once with
-        the next tokens and ``append=True``; the logits rows come back in that order."""
+        the next tokens and ``append=True``; the logits rows come back in that order.
+
+        Chunked prefill (``extend=True``, with ``seq_ids`` and ``seq_lens``): the tokens continue the PROMPTS of known
+        sequences that have not generated anything yet, so a long prompt can be fed in pieces between the decode steps
+        of the other sequences.  Create the sequence with its first piece and the ``max_length`` of the whole request;
+        the logits of every piece but the last are of no use to the caller."""
         def tl(x):
             if x is None:
                 return None
@@ -402,10 +407,10 @@ class Model:
                 isinstance(input_ids[0], (list, tuple)):
             seq_lens = [len(r) for r in input_ids]
         return self._call(OP_SET_INPUT_CB, (ids, tl(seq_lens), tl(seq_ids), tl(max_length), bool(greedy), bool(append),
-                                            bool(hold)))
+                                            bool(hold), bool(extend)))
 
     def _do_set_input_cb(self, ids, seq_lens, seq_ids, max_len, greedy: bool = False, append: bool = False,
-                         hold: bool = False) -> torch.Tensor:
+                         hold: bool = False, extend: bool = False) -> torch.Tensor:
         active = []
         self._cb_greedy = bool(greedy)
         self._cb_hold = bool(hold)
@@ -427,6 +432,21 @@ class Model:
             # data-parallel attention: a rank caches only the sequences it owns
             self.cache.reserve(sum(self.cache.blocks_for(s.max_len + 1) - len(self.cache.tables[s.seq_id])
                                    for s in active if s.owner == self.ctx.dp_rank))
+        elif extend:                                      # further prompt pieces of known sequences
+            if not seq_lens or len(seq_lens) != len(seq_ids) or sum(seq_lens) != len(ids):
+                raise ValueError("set_input_cb(extend=True): one piece per sequence id, seq_lens adding up to the ids")
+            off = 0
+            for sid, n in zip(seq_ids, seq_lens):
+                s = self.pool.get(sid)
+                if s.pending or s.generated:
+                    raise RuntimeError(f"sequence {sid}: a prompt grows only between forwards and before generation")
+                if len(s.prompt) + n >= s.max_len:
+                    raise ValueError(f"sequence {sid}: prompt of {len(s.prompt) + n} tokens exceeds its max_length {s.max_len}")
+                piece = ids[off:off + n]
+                off += n
+                s.prompt = s.prompt + piece
+                s.pending = list(piece)
+                active.append(s)
         else:                                             # next tokens of known sequences
             if len(ids) != len(seq_ids):
                 raise ValueError("set_input_cb: one next token per sequence id expected")
