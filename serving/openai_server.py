@@ -78,8 +78,9 @@ class Scheduler(threading.Thread):
         self.running: Dict[int, Request] = {}
         self.stop_flag = threading.Event()
         self.metrics = dict(requests=0, finished=0, prompt_tokens=0, generated_tokens=0, ttft_sum=0.0, tpot_sum=0.0,
-                            tpot_count=0, steps=0, mixed_steps=0, errors=0, cancelled=0, prefill_chunks=0)
+                            tpot_count=0, steps=0, mixed_steps=0, errors=0, cancelled=0, prefill_chunks=0, rejected=0)
         self.mixed_steps = False          # prefill new prompts in the same forward as the running sequences' decode
+        self.max_queue = 0                # > 0: requests beyond this many waiting ones are refused with 429
         self.prefill_chunk = 0            # > 0: prompts longer than this are fed in pieces of this many tokens, one piece
         #                                   per scheduler turn, so a long prompt does not stall the running sequences
         self.prefilling: Dict[int, Request] = {}      # sequences whose prompt is still being fed (req.fed tokens so far)
@@ -465,6 +466,10 @@ def make_handler(sched: Scheduler, tok: Tokenizer, model_name: str):
                                             float(q.get("repetition_penalty", 1.0)), lp, stop_fn))
             except Exception as e:
                 return self._json(400, {"error": {"message": str(e), "type": "invalid_request_error"}})
+            if sched.max_queue > 0 and sched.waiting.qsize() + len(reqs) > sched.max_queue:
+                sched.metrics["rejected"] += len(reqs)
+                return self._json(429, {"error": {"message": f"{sched.waiting.qsize()} requests are already waiting",
+                                                  "type": "server_overloaded"}})
             for r in reqs:
                 sched.submit(r)
             created = int(time.time())
@@ -554,12 +559,14 @@ def make_handler(sched: Scheduler, tok: Tokenizer, model_name: str):
 
 
 def serve(model, port: int, token_path: str = "", max_batch: int = 64, prefill_per_step: int = 4, model_name: str = "xft",
-          warmup: bool = False, max_context: int = 0, mixed_steps: bool = False, prefill_chunk: int = 0):
+          warmup: bool = False, max_context: int = 0, mixed_steps: bool = False, prefill_chunk: int = 0,
+          max_queue: int = 0):
     """Start scheduler + HTTP server (threads); returns (httpd, scheduler, bound_port)."""
     tok = Tokenizer(token_path)
     sched = Scheduler(model, max_batch, prefill_per_step, eos_id=tok.eos)
     sched.mixed_steps = mixed_steps
     sched.prefill_chunk = max(0, int(prefill_chunk))
+    sched.max_queue = max(0, int(max_queue))
     if warmup:
         sched.warmup(max_context)
     sched.start()
@@ -580,6 +587,7 @@ def main():
     ap.add_argument("--prefill_per_step", type=int, default=4)
     ap.add_argument("--no_warmup", action="store_true", help="do not pre-capture the decode graphs of every batch bucket")
     ap.add_argument("--max_context", type=int, default=0, help="longest prompt + output the graphs are sized for")
+    ap.add_argument("--max_queue", type=int, default=0, help="refuse requests with 429 beyond this many waiting ones (0 = no limit)")
     ap.add_argument("--prefill_chunk", type=int, default=0,
                     help="feed prompts longer than this many tokens in pieces, one per scheduler turn (0 = whole prompts)")
     ap.add_argument("--mixed_steps", action="store_true",
@@ -593,7 +601,7 @@ def main():
         return
     _, _, port = serve(model, a.port, a.token_path, a.max_batch, a.prefill_per_step,
                        os.path.basename(a.model_path.rstrip("/")), warmup=not a.no_warmup, max_context=a.max_context,
-                       mixed_steps=a.mixed_steps, prefill_chunk=a.prefill_chunk)
+                       mixed_steps=a.mixed_steps, prefill_chunk=a.prefill_chunk, max_queue=a.max_queue)
     print(f"OpenAI-compatible server on :{port}", flush=True)
     threading.Event().wait()
 

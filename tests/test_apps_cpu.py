@@ -455,6 +455,16 @@ def test_openai_server_chunked_prefill(tmp_path):
         eng = model.model
         assert not sched.running and not sched.prefilling and not eng.cache.tables
         assert eng.cache.alloc.num_free == eng.cache.alloc.num_blocks
+        # back-pressure: with a queue limit, a burst beyond it is refused with 429 and counted
+        sched.max_queue = 1
+        req = urllib.request.Request(base + "/v1/completions", data=json.dumps({"prompt": [prompts[1]] * 3, "max_tokens": 2}).encode(),
+                                     headers={"Content-Type": "application/json"})
+        try:
+            urllib.request.urlopen(req, timeout=30)
+            assert False, "three prompts must not fit a queue of one"
+        except urllib.error.HTTPError as e:
+            assert e.code == 429
+        assert sched.metrics["rejected"] == 3 and post({"prompt": prompts[1], "max_tokens": 2})["choices"][0]["token_ids"] == want[1][:2]
     finally:
         sched.shutdown()
         httpd.shutdown()
