@@ -599,11 +599,21 @@ def main():
     if model.rank != 0:
         model.follow_cb()                # follower ranks mirror rank 0's engine calls until shutdown
         return
-    _, _, port = serve(model, a.port, a.token_path, a.max_batch, a.prefill_per_step,
-                       os.path.basename(a.model_path.rstrip("/")), warmup=not a.no_warmup, max_context=a.max_context,
-                       mixed_steps=a.mixed_steps, prefill_chunk=a.prefill_chunk, max_queue=a.max_queue)
+    httpd, sched, port = serve(model, a.port, a.token_path, a.max_batch, a.prefill_per_step,
+                               os.path.basename(a.model_path.rstrip("/")), warmup=not a.no_warmup,
+                               max_context=a.max_context, mixed_steps=a.mixed_steps, prefill_chunk=a.prefill_chunk,
+                               max_queue=a.max_queue)
     print(f"OpenAI-compatible server on :{port}", flush=True)
-    threading.Event().wait()
+    # SIGTERM / Ctrl-C: stop accepting, let the scheduler finish its turn, release the follower ranks
+    import signal
+    stop = threading.Event()
+    for sig in (signal.SIGINT, signal.SIGTERM):
+        signal.signal(sig, lambda *_: stop.set())
+    stop.wait()
+    httpd.shutdown()
+    sched.shutdown()
+    sched.join(timeout=30)
+    model.model.exit_slaves()
 
 
 if __name__ == "__main__":
