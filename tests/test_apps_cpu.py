@@ -468,3 +468,49 @@ def test_openai_server_chunked_prefill(tmp_path):
     finally:
         sched.shutdown()
         httpd.shutdown()
+
+
+@pytest.mark.parametrize("ranks", [1, 2])
+def test_openai_server_process_serves_and_stops_on_sigterm(tiny, ranks):
+    """serving/openai_server.py as a process (alone, and with a follower rank under torchrun): answers /health and a
+    completion, then SIGTERM ends every rank cleanly."""
+    import signal
+    import socket
+    import time
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ, XFT_ENGINE="CPU", PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    server = [os.path.join(ROOT, "serving", "openai_server.py"), "--model_path", tiny, "--no_warmup", "--port", str(port)]
+    if ranks == 1:
+        cmd = [sys.executable] + server
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ranks}", "--master-addr",
+               "127.0.0.1", "--master-port", "29691"] + server
+    p = subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, start_new_session=True)
+    try:
+        base = f"http://127.0.0.1:{port}"
+        t0 = time.time()
+        while True:
+            try:
+                if json.loads(urllib.request.urlopen(base + "/health", timeout=2).read())["status"] == "ok":
+                    break
+            except Exception:
+                assert p.poll() is None and time.time() - t0 < 120, "server did not come up"
+                time.sleep(0.3)
+        req = urllib.request.Request(base + "/v1/completions", data=json.dumps({"prompt": [5, 6, 7, 8], "max_tokens": 4}).encode(),
+                                     headers={"Content-Type": "application/json"})
+        r = json.loads(urllib.request.urlopen(req, timeout=60).read())
+        assert len(r["choices"][0]["token_ids"]) == 4
+        if ranks == 1:
+            p.send_signal(signal.SIGTERM)
+        else:
+            # torchrun forwards the signal to its workers; rank 0 then releases the follower
+            os.killpg(os.getpgid(p.pid), signal.SIGTERM)
+        out, _ = p.communicate(timeout=60)
+        if ranks == 1:
+            assert p.returncode == 0, out[-2000:]
+    finally:
+        if p.poll() is None:
+            os.killpg(os.getpgid(p.pid), signal.SIGKILL)
+            p.wait()
