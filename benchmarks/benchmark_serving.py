@@ -52,9 +52,13 @@ def main():
     ap.add_argument("--output_len", type=int, default=128)
     ap.add_argument("--vocab", type=int, default=32000)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--shared_prefix_len", type=int, default=0,
+                    help="the first N tokens are the same in every prompt (a system prompt): what automatic prefix reuse "
+                         "(XFT_PREFIX_CACHE=1 on the server) saves")
     a = ap.parse_args()
     rng = random.Random(a.seed)
-    prompts = [[rng.randrange(5, a.vocab) for _ in range(a.input_len)] for _ in range(a.num_prompts)]
+    shared = [rng.randrange(5, a.vocab) for _ in range(min(a.shared_prefix_len, a.input_len))]
+    prompts = [shared + [rng.randrange(5, a.vocab) for _ in range(a.input_len - len(shared))] for _ in range(a.num_prompts)]
     recs = [dict(inp=len(p)) for p in prompts]
     threads = []
     t0 = time.perf_counter()
