@@ -537,3 +537,53 @@ def test_chunked_prefill_through_extend(tiny):
         s2 = model.set_input_cb([[1, 2, 3]], None, [6])
         model.forward_cb()
         model.set_input_cb([[4, 5, 6, 7]], s2, None, extend=True)             # beyond the sequence's max_length
+
+
+def test_ngram_speculative_decoding_is_exact(tiny, monkeypatch):
+    """XFT_SPEC_NGRAM=k: drafts are verified in one forward and the output equals plain greedy decoding token for
+    token.  First with the real n-gram drafts (random text: few are accepted), then with drafts taken from the known
+    continuation with every third token falsified: two accepted + one corrected token per step, rejected cache
+    positions rewritten later, eos and max_length honoured inside a run of accepted tokens."""
+    from xfastertransformer_b200.runtime.engine import Model
+    from xfastertransformer_b200.utils.flags import Env
+    g = torch.Generator().manual_seed(3)
+    motif = torch.randint(5, 900, (6,), generator=g)
+    ids = torch.stack([motif.repeat(5), torch.randint(5, 900, (30,), generator=g), torch.randint(5, 900, (30,), generator=g)])
+    plain = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+    want = plain.generate(ids, max_length=30 + 48)
+    eos = int(want[0, 30 + 9])                                   # a token that does occur: row 0 stops on it
+    want_eos = plain.generate(ids, max_length=30 + 48, eos_token_id=eos, pad_token_id=0)
+    assert Model._ngram_draft([1, 2, 3, 9, 9, 1, 2, 3], 4) == [9, 9, 1, 2] and Model._ngram_draft([1, 2, 3], 4) == []
+    assert Model._ngram_draft([5, 6, 7, 5], 2) == [6, 7] and Model._ngram_draft([4, 4, 4, 4], 3) == [4]
+    monkeypatch.setenv("XFT_SPEC_NGRAM", "4")
+    Env.get().reload()
+    try:
+        m = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+        eng = m.model
+        assert torch.equal(m.generate(ids, max_length=30 + 48), want) and eng.spec_steps > 0
+        # oracle drafts: the true continuation, the third draft token wrong
+        rows = {tuple(r[:30].tolist()): r.tolist() for r in want}
+
+        def oracle(tokens, k, window=1024):
+            full = rows[tuple(tokens[:30])]
+            d = full[len(tokens):len(tokens) + k]
+            if len(d) > 2:
+                d[2] = (d[2] + 1) % 900
+            return d
+        monkeypatch.setattr(Model, "_ngram_draft", staticmethod(oracle))
+        s0, e0, a0, f0 = eng.spec_steps, eng.spec_emitted, eng.spec_accepted, len(eng.step_times_ms)
+        assert torch.equal(m.generate(ids, max_length=30 + 48), want)
+        steps = eng.spec_steps - s0
+        # two accepted drafts + the corrected token per sequence and step, except near max_length where the drafts shrink
+        assert eng.spec_accepted - a0 >= 2 * 3 * (steps - 2) and eng.spec_emitted - e0 >= 3 * 42
+        assert len(eng.step_times_ms) - f0 <= 20                    # instead of 48 forwards
+        assert torch.equal(m.generate(ids, max_length=30 + 48, eos_token_id=eos, pad_token_id=0), want_eos)
+        assert not eng.cache.tables and eng.cache.alloc.num_free == eng.cache.alloc.num_blocks
+        # sampling and beams do not take the speculative path
+        s1 = eng.spec_steps
+        m.generate(ids[:1], max_length=40, num_beams=2)
+        m.generate(ids[:1], max_length=40, do_sample=True, seed=1)
+        assert eng.spec_steps == s1
+    finally:
+        monkeypatch.delenv("XFT_SPEC_NGRAM")
+        Env.get().reload()

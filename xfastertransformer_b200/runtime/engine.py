@@ -108,6 +108,7 @@ class Model:
             per = max(self.cache.bytes_per_block(), 1)
             self.cache.ensure_blocks(max(int(self.env.kv_cache_gb * (1 << 30)) // per, 1))
         self.step_times_ms: List[float] = []
+        self.spec_steps = self.spec_emitted = self.spec_accepted = 0      # n-gram speculative decoding counters
         # XFT_STEP_TIMEOUT_S > 0: a monitor thread reports a step that runs over (log + stack dump) and the step raises
         # StepTimeout when it returns
         self.watchdog = StepWatchdog(self.env.step_timeout_s)
@@ -272,6 +273,9 @@ class Model:
                 active = [x for x in seqs if not x.done]
                 if not active:
                     out = torch.full((len(seqs),), cfg.eos_token_id, dtype=torch.int64)
+                elif self._spec_ok(active, cfg) and self._spec_step(active, cfg):
+                    out = torch.tensor([s.generated[-1] if s.generated else cfg.eos_token_id for s in seqs],
+                                       dtype=torch.int64)
                 elif self.runner is not None and self.runner.can_run(active, cfg):
                     toks = self.runner.step(active, cfg)
                     out = self._commit(seqs, toks, cfg)
@@ -281,6 +285,65 @@ class Model:
                     out = self._commit(seqs, toks, cfg)
         self.step_times_ms.append((time.perf_counter() - t0) * 1e3)
         return out
+
+    # -- n-gram speculative decoding (greedy only) -----------------------------------------------
+    def _spec_ok(self, seqs: Sequence[SequenceMeta], cfg: SamplingMeta) -> bool:
+        return (self.env.spec_ngram > 0 and not cfg.do_sample and cfg.num_beams == 1 and cfg.repetition_penalty == 1.0
+                and self.ctx.pp_size == 1 and self.ctx.dp_size == 1 and self.decoder.spec.rope != "2d"
+                and all(len(s.pending) == 1 and s.past_len > 0 for s in seqs))
+
+    @staticmethod
+    def _ngram_draft(tokens: List[int], k: int, window: int = 1024) -> List[int]:
+        """Up to k tokens that followed the most recent earlier occurrence of the current suffix (3, 2 or 1 tokens)."""
+        n_tok = len(tokens)
+        lo = max(0, n_tok - window)
+        for n in (3, 2, 1):
+            if n_tok <= n:
+                continue
+            pat = tokens[-n:]
+            for i in range(n_tok - n - 1, lo - 1, -1):
+                if tokens[i:i + n] == pat:
+                    return tokens[i + n:i + n + k]
+        return []
+
+    def _spec_step(self, seqs: Sequence[SequenceMeta], cfg: SamplingMeta) -> bool:
+        """One decode step that may emit several tokens per sequence.  Each sequence proposes draft tokens from its own
+        history; one forward scores the pending token and the drafts; the longest draft prefix that greedy decoding
+        would have produced itself is kept, plus the token after it, and the cache positions of rejected drafts are
+        dropped.  The result is exactly plain greedy decoding (a decode step is bound by the weight stream, so a few
+        extra rows are nearly free).  Returns False when no sequence had a draft: the caller runs a normal step."""
+        k = self.env.spec_ngram
+        drafts = []
+        for s in seqs:
+            room = s.max_len - s.total_len - 1               # tokens that may still follow the one after the draft
+            drafts.append(self._ngram_draft(s.all_tokens(), min(k, room)) if room > 0 else [])
+        if not any(drafts):
+            return False
+        starts = [s.past_len for s in seqs]
+        lasts = [s.pending[0] for s in seqs]
+        for s, d in zip(seqs, drafts):
+            s.pending = s.pending + d
+        local = self._run(seqs, logits_all=True)             # one row per pending token, sequence after sequence
+        preds = S.greedy_select(local, self.decoder.v0, self.ctx).cpu().tolist()
+        row = 0
+        for s, d, p0, last in zip(seqs, drafts, starts, lasts):
+            p = preds[row:row + 1 + len(d)]
+            row += 1 + len(d)
+            acc = 0
+            while acc < len(d) and int(p[acc]) == d[acc]:
+                acc += 1
+            s.past_len, s.pending = p0, [last]
+            for t in d[:acc] + [int(p[acc])]:
+                s.step_forward(t)
+                self.spec_emitted += 1
+                if t == cfg.eos_token_id or s.total_len >= s.max_len or \
+                        (cfg.stop_words and S.match_stop_words(s.generated, cfg.stop_words)):
+                    s.done = True
+                    break
+            self.spec_accepted += acc
+            self.cache.truncate(s.seq_id, s.past_len)        # positions of rejected drafts are written again later
+        self.spec_steps += 1
+        return True
 
     def _select(self, local: torch.Tensor, seqs: Sequence[SequenceMeta], cfg: SamplingMeta) -> torch.Tensor:
         d = self.decoder

@@ -60,6 +60,9 @@ class Env:
         self.moe_fused_a2a = _int("XFT_MOE_FUSED_A2A", 0) != 0      # with attention_dp: token exchange as peer-memory stores
         self.kv_cache_gb = float(e.get("XFT_KV_CACHE_GB", "0") or 0)
         self.prefix_cache = _int("XFT_PREFIX_CACHE", 0) != 0      # reuse the KV blocks of prompts that share a prefix
+        # greedy decoding with n-gram drafts: up to this many tokens are copied from an earlier occurrence of the current
+        # suffix and checked in ONE forward; accepted ones cost no extra step (output identical to plain greedy)
+        self.spec_ngram = max(0, _int("XFT_SPEC_NGRAM", 0))
         self.max_batch_tokens = _int("XFT_MAX_BATCH_TOKENS", 8192)
         self.step_timeout_s = float(e.get("XFT_STEP_TIMEOUT_S", "0") or 0)
         self.fuse_norm = _int("XFT_FUSE_NORM", 1) != 0    # fold RMSNorm gains into the consuming bf16 GEMM
