@@ -46,11 +46,15 @@ def test_logits_and_greedy_ws1(tiny, monkeypatch):
     assert torch.equal(out, ref.greedy(ids, 16))
 
 
-def test_ws2_gloo(tiny, tmp_path):
+@pytest.mark.parametrize("spec", [0, 4])
+def test_ws2_gloo(tiny, tmp_path, spec):
+    """Two tensor-parallel gloo ranks against the eager reference; spec = 4: the same with n-gram speculative decoding
+    (every rank derives the same drafts from the token stream, so the ranks stay in step)."""
     out = str(tmp_path / "ws2.pt")
-    env = dict(os.environ, XFT_ENGINE="CPU", PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    env = dict(os.environ, XFT_ENGINE="CPU", XFT_SPEC_NGRAM=str(spec),
+               PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", "29611", os.path.join(ROOT, "tests", "ws2_worker.py"), tiny, out]
+           "127.0.0.1", "--master-port", str(29611 + 50 * (spec > 0)), os.path.join(ROOT, "tests", "ws2_worker.py"), tiny, out]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     got = torch.load(out)
