@@ -396,3 +396,25 @@ def test_host_numeric_conversions_match_torch(core):
         core.xftc_convert_to_float(out, back, n, kind)
         ref = x.to(dt).float()
         assert torch.equal(torch.tensor(list(back)), ref)
+
+
+def test_cmake_tree_configures_and_runs_the_native_tests(tmp_path):
+    """CMakeLists.txt: the tree configures for sm_100a, the native unit-test target builds and passes under ctest (the
+    kernel and core libraries are built the same way; that takes minutes and is left to `cmake --build`)."""
+    import shutil
+    import subprocess
+    if shutil.which("cmake") is None:
+        pytest.skip("cmake not installed")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    b = str(tmp_path / "b")
+    env = dict(os.environ, CXX="/usr/bin/g++") if os.path.exists("/usr/bin/g++") else dict(os.environ)
+    r = subprocess.run(["cmake", "-S", root, "-B", b, "-DXFT_BUILD_TESTS=ON", f"-DXFT_OUT={b}/out"], capture_output=True,
+                       text=True, timeout=300, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    flags = open(os.path.join(b, "CMakeFiles", "xft_b200_kernels.dir", "flags.make")).read()
+    assert "compute_100a" in flags and "sm_100a" in flags                  # Blackwell's architecture-specific target
+    r = subprocess.run(["cmake", "--build", b, "--target", "xft_runtime_selftest", "-j", "4"], capture_output=True, text=True,
+                       timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    r = subprocess.run(["ctest", "--output-on-failure"], cwd=b, capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0 and "100% tests passed" in r.stdout, r.stdout[-2000:]
