@@ -115,6 +115,11 @@ class Scheduler(threading.Thread):
                 self.model.set_input_cb([[int(t)] for t in toks], sids, None, greedy=True)
                 toks = self.model.forward_cb_greedy()
             self.model.free_seqs(sids)
+        # one prompt-sized prefill as well: the first request should not pay for the first use of the prefill kernels
+        n = max(8, min(512, ctx - 16))
+        sids = self.model.set_input_cb([[1 + (i % 7) for i in range(n)]], None, [n + 8], greedy=True)
+        self.model.forward_cb_greedy()
+        self.model.free_seqs(sids)
         return len(sizes)
 
     # -- API for handler threads ------------------------------------------------------------
