@@ -514,3 +514,35 @@ def test_openai_server_process_serves_and_stops_on_sigterm(tiny, ranks):
         if p.poll() is None:
             os.killpg(os.getpgid(p.pid), signal.SIGKILL)
             p.wait()
+
+
+def test_server_warmup_walks_every_bucket_and_leaves_the_cache_clean(tiny):
+    """Scheduler.warmup on a stand-in runner (the real one needs a GPU): one short session per batch bucket plus one
+    prompt-sized prefill, every sequence freed again."""
+    import importlib.util
+    from xfastertransformer_b200.runtime.cuda_runner import CudaRunner
+    spec = importlib.util.spec_from_file_location("oai", os.path.join(ROOT, "serving", "openai_server.py"))
+    oai = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(oai)
+    model = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+    eng = model.model
+
+    class StandIn:
+        enabled = True
+        fixed_width = None
+        bucket = staticmethod(CudaRunner.bucket)
+        seen = []
+
+        def can_run(self, seqs, cfg):
+            self.seen.append(len(seqs))
+            return False
+
+        def reset(self):
+            pass
+    eng.runner = StandIn()
+    sched = oai.Scheduler(model, max_batch=20, prefill_per_step=2)
+    n = sched.warmup(max_context=300)
+    assert n == len({CudaRunner.bucket(b) for b in range(1, 21)}) == 7
+    assert eng.runner.fixed_width == (eng.cache.blocks_for(301) + 7) // 8 * 8
+    assert sorted(set(eng.runner.seen)) == [1, 2, 4, 8, 12, 16, 24]
+    assert not eng.cache.tables and not eng.pool.seqs and eng.cache.alloc.num_free == eng.cache.alloc.num_blocks
