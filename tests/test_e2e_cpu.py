@@ -290,3 +290,37 @@ def test_prefix_reuse_under_tensor_parallelism_gloo(tiny, tmp_path):
     assert torch.allclose(got["logits"], want, atol=2e-3, rtol=2e-3)
     assert torch.equal(got["tokens"], m.generate(torch.tensor([p2]), max_length=len(p2) + 5))
     assert got["stats"][0] == got["stats"][1] and got["stats"][0][0] == 4          # 2 blocks reused, twice
+
+
+def test_data_parallel_decode_runner_logic_gloo(tmp_path):
+    """The decode runner's data-parallel step (each rank decodes its own sequences, a rank without sequences serves its
+    experts, tokens are exchanged on the host) with eager stand-ins for the CUDA-graph parts, on two gloo ranks."""
+    import xfastertransformer_b200 as xft
+    from xfastertransformer_b200.config import ModelConfig
+    from xfastertransformer_b200.parallel.dist import DistContext
+    from xfastertransformer_b200.utils.flags import Env
+    cfg = ModelConfig(model_type="mixtral", num_layer=2, hidden_size=128, head_num=4, kv_head_num=2, size_per_head=32,
+                      inter_size=128, moe_intermediate_size=128, vocab_size=1000, max_pos_seq_len=512, sparse_experts=8,
+                      num_experts_per_tok=2, norm_topk_prob=True, activation_type="silu", weight_data_type="bf16",
+                      start_id=1, end_id=2)
+    d = str(tmp_path / "m")
+    write_synthetic_checkpoint(d, cfg, seed=0, dtype="bf16", std=0.05)
+    out = str(tmp_path / "dpr.pt")
+    env = dict(os.environ, XFT_ENGINE="CPU", XFT_ATTENTION_DP="1",
+               PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29695", os.path.join(ROOT, "tests", "dp_runner_worker.py"), d, out]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    got = torch.load(out)
+    os.environ["XFT_ENGINE"] = "CPU"
+    DistContext.reset()
+    Env.get().reload()
+    m = xft.AutoModel.from_pretrained(d, dtype="bf16")
+    g = torch.Generator().manual_seed(4)
+    one = torch.randint(0, 1000, (1, 9), generator=g)
+    three = torch.randint(0, 1000, (3, 11), generator=g)
+    assert torch.equal(got["one"], m.generate(one, max_length=15))
+    assert torch.equal(got["three"], m.generate(three, max_length=17))
+    # 5 + 5 decode steps after the prefills; rank 1 owns nothing in the first request and one sequence in the second
+    assert got["stats"] == [(10, 0), (5, 5)]
