@@ -579,6 +579,20 @@ def test_ngram_speculative_decoding_is_exact(tiny, monkeypatch):
         assert len(eng.step_times_ms) - f0 <= 20                    # instead of 48 forwards
         assert torch.equal(m.generate(ids, max_length=30 + 48, eos_token_id=eos, pad_token_id=0), want_eos)
         assert not eng.cache.tables and eng.cache.alloc.num_free == eng.cache.alloc.num_blocks
+
+        class Streamer:                      # a streamer sees every token, also those accepted several at a time
+            def __init__(self):
+                self.chunks, self.ended = [], False
+
+            def put(self, t):
+                self.chunks.append(t.flatten().tolist())
+
+            def end(self):
+                self.ended = True
+        st = Streamer()
+        out1 = m.generate(ids[:1], max_length=30 + 48, streamer=st)
+        assert st.ended and st.chunks[0] == ids[0].tolist() and sum(st.chunks[1:], []) == out1[0, 30:].tolist()
+        assert max(len(c) for c in st.chunks[1:]) == 3
         # sampling and beams do not take the speculative path
         s1 = eng.spec_steps
         m.generate(ids[:1], max_length=40, num_beams=2)

@@ -134,10 +134,15 @@ class AutoModel:
         self.set_input(input_ids, max_length, num_beams, num_return_sequences, length_penalty, early_stopping,
                        eos_token_id, pad_token_id, do_sample, temperature, top_k, top_p, repetition_penalty,
                        stop_words_ids, **kwargs)
+        sent = 0
         while not self.is_done():
             next_tokens = self.forward()
             if streamer is not None and input_ids is not None:
-                streamer.put(next_tokens.cpu())
+                # everything the step produced: one token, or several when drafts were accepted (XFT_SPEC_NGRAM)
+                gen = self.model.working[0].generated if self.model.working else []
+                new = gen[sent:] if len(gen) > sent else next_tokens.flatten().tolist()[:1]
+                sent = max(len(gen), sent + len(new))
+                streamer.put(torch.tensor(new, dtype=torch.int64))
         if streamer is not None and input_ids is not None:
             streamer.end()
         return self.finalize()
