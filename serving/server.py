@@ -50,9 +50,24 @@ class Servicer:
         with self.lock:
             self.model.set_input(self._ids(q), **self._kwargs(q))
             try:
+                sent = None
                 while not self.model.is_done():
                     t = self.model.forward()
-                    yield {"Ids": t.flatten().tolist(), "batch_size": t.shape[0], "seq_len": 1}
+                    seqs = getattr(getattr(self.model, "model", None), "working", None)
+                    if not seqs or len(seqs) != t.shape[0]:
+                        yield {"Ids": t.flatten().tolist(), "batch_size": t.shape[0], "seq_len": 1}
+                        continue
+                    # a step may produce several tokens per sequence (XFT_SPEC_NGRAM): send them all; rows that got
+                    # fewer are padded with -1 and `counts` says how many are real
+                    sent = sent or [0] * len(seqs)
+                    new = [s.generated[n:] for s, n in zip(seqs, sent)]
+                    new = [r if r else [int(t[i])] for i, r in enumerate(new)]          # finished rows keep emitting eos
+                    sent = [max(len(s.generated), n) for s, n in zip(seqs, sent)]
+                    w = max(len(r) for r in new)
+                    msg = {"Ids": [x for r in new for x in r + [-1] * (w - len(r))], "batch_size": len(new), "seq_len": w}
+                    if w > 1:
+                        msg["counts"] = [len(r) for r in new]
+                    yield msg
             finally:
                 # a client that left early must not leave the follower ranks ahead of rank 0: they run the request to
                 # its end, so rank 0 does too

@@ -546,3 +546,39 @@ def test_server_warmup_walks_every_bucket_and_leaves_the_cache_clean(tiny):
     assert eng.runner.fixed_width == (eng.cache.blocks_for(301) + 7) // 8 * 8
     assert sorted(set(eng.runner.seen)) == [1, 2, 4, 8, 12, 16, 24]
     assert not eng.cache.tables and not eng.pool.seqs and eng.cache.alloc.num_free == eng.cache.alloc.num_blocks
+
+
+def test_grpc_stream_carries_every_token_under_speculative_decoding(tiny, monkeypatch):
+    """predict_stream with XFT_SPEC_NGRAM on: steps that emit several tokens send them all (rows padded with -1, `counts`
+    says how many are real); the concatenation equals generate()."""
+    from serving.server import Servicer
+    from xfastertransformer_b200.runtime.engine import Model
+    from xfastertransformer_b200.utils.flags import Env
+    plain = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+    ids = torch.randint(5, 790, (2, 12), generator=torch.Generator().manual_seed(9))
+    want = plain.generate(ids, max_length=12 + 20)
+    rows = {tuple(r[:12].tolist()): r.tolist() for r in want}
+
+    def oracle(tokens, k, window=1024):          # row 0 always gets two right drafts, row 1 none
+        full = rows[tuple(tokens[:12])]
+        return full[len(tokens):len(tokens) + 2] if full == rows[tuple(ids[0].tolist())] else []
+    monkeypatch.setenv("XFT_SPEC_NGRAM", "4")
+    Env.get().reload()
+    try:
+        model = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+        monkeypatch.setattr(Model, "_ngram_draft", staticmethod(oracle))
+        sv = Servicer(model)
+        got = [[], []]
+        widths = set()
+        for msg in sv.predict_stream({"Ids": ids.flatten().tolist(), "batch_size": 2, "max_length": 32}):
+            w = msg["seq_len"]
+            widths.add(w)
+            cnt = msg.get("counts", [w] * 2)
+            for i in range(2):
+                got[i] += msg["Ids"][i * w:i * w + cnt[i]]
+        assert 3 in widths
+        eos_free = lambda r: [t for t in r if t != -1]
+        assert eos_free(got[0])[:20] == want[0, 12:].tolist() and eos_free(got[1])[:20] == want[1, 12:].tolist()
+    finally:
+        monkeypatch.delenv("XFT_SPEC_NGRAM")
+        Env.get().reload()
