@@ -46,15 +46,17 @@ def test_logits_and_greedy_ws1(tiny, monkeypatch):
     assert torch.equal(out, ref.greedy(ids, 16))
 
 
-@pytest.mark.parametrize("spec", [0, 4])
-def test_ws2_gloo(tiny, tmp_path, spec):
+@pytest.mark.parametrize("spec,overlap", [(0, 0), (4, 0), (0, 1)])
+def test_ws2_gloo(tiny, tmp_path, spec, overlap):
     """Two tensor-parallel gloo ranks against the eager reference; spec = 4: the same with n-gram speculative decoding
-    (every rank derives the same drafts from the token stream, so the ranks stay in step)."""
+    (every rank derives the same drafts from the token stream, so the ranks stay in step); overlap = 1: the prefill of
+    the two prompts interleaved block by block with asynchronous all-reduces (XFT_PREFILL_OVERLAP)."""
     out = str(tmp_path / "ws2.pt")
-    env = dict(os.environ, XFT_ENGINE="CPU", XFT_SPEC_NGRAM=str(spec),
+    env = dict(os.environ, XFT_ENGINE="CPU", XFT_SPEC_NGRAM=str(spec), XFT_PREFILL_OVERLAP=str(overlap),
                PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", str(29611 + 50 * (spec > 0)), os.path.join(ROOT, "tests", "ws2_worker.py"), tiny, out]
+           "127.0.0.1", "--master-port", str(29611 + 50 * (spec > 0) + 90 * overlap),
+           os.path.join(ROOT, "tests", "ws2_worker.py"), tiny, out]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     got = torch.load(out)
@@ -65,6 +67,7 @@ def test_ws2_gloo(tiny, tmp_path, spec):
     # TP really split the work: FFN 688 over 2 ranks -> 352 + 336, two allreduces per layer per step
     assert got["ffn"] == [352, 336]
     assert got["all_reduce"] > 0
+    assert got["pairs"] == (2 if overlap else 0)          # the forward_cb prefill and generate's prefill, both as a pair
 
 
 def test_pipeline_parallel_two_stages_gloo(tiny, tmp_path):

@@ -25,6 +25,7 @@ else:
 ffn = [None, None]
 dist.all_gather_object(ffn, m.decoder.layers[0].down.in_features)
 if model.rank == 0:
-    torch.save({"logits": logits, "tokens": tokens, "ffn": ffn, "all_reduce": m.ctx.stats["all_reduce"]}, out)
+    torch.save({"logits": logits, "tokens": tokens, "ffn": ffn, "all_reduce": m.ctx.stats["all_reduce"],
+                "pairs": m.prefill_decoder.pairs_run}, out)
 m._closed = True
 dist.barrier()

@@ -110,6 +110,9 @@ class Decoder:
             self._load_head(embed_from)
             self._fold_norms()
         self.has_moe = any(L.mlp_kind not in ("llama", "gpt") for L in self.layers)
+        self.pairs_run = 0          # forward_pair calls
+        self._overlap = False       # True while forward_pair interleaves two batches (all-reduces are started, not awaited)
+        self._work = None
 
     # ------------------------------------------------------------------------------------
     # rotary tables
@@ -463,7 +466,12 @@ class Decoder:
         lead = self.tpr == 0
         y = ops.linear(h, W, bias if lead else None, None, residual if lead else None, res_scale)
         if self.tp > 1:
-            y = self.ctx.all_reduce(y)
+            if self._overlap:
+                # interleaved prefill: the sum is started here and waited for by the driver of the two interleaved
+                # batches, after it has enqueued the other batch's next block (Decoder.forward_pair)
+                self._work = self.ctx.all_reduce_async(y)
+            else:
+                y = self.ctx.all_reduce(y)
         return y
 
     def embed(self, b: Batch) -> torch.Tensor:
@@ -685,6 +693,49 @@ class Decoder:
             if dbg:
                 debugger.dump(f"layer{self.l0 + li}_ffn_out", x, self.ctx.rank, step)
         return x
+
+    def _layers_interleaved(self, x: torch.Tensor, b: Batch, cache: PagedKVCache):
+        """forward_layers as a generator: after every block whose row-parallel sum was only started, it hands the
+        pending handle to the driver and continues when asked to."""
+        for li, L in enumerate(self.layers):
+            x = self._attention(L, x, b, cache, li)
+            w, self._work = self._work, None
+            yield w
+            x = self._mlp(L, x, b)
+            w, self._work = self._work, None
+            yield w
+        return x
+
+    def forward_pair(self, b0: Batch, b1: Batch, cache: PagedKVCache):
+        """Prefill of two batches with the tensor-parallel sums of one overlapping the compute of the other
+        (XFT_PREFILL_OVERLAP=1).  The reference waits for every all-reduce before it goes on
+        (src/layers/decoder_block.h:122-134); here batch A starts the sum of its block and, while NVLink carries it,
+        batch B's next block runs on the SMs, and so on alternately.  Results are those of two forward() calls."""
+        assert self.first_stage and self.last_stage and not self.has_moe
+        xs = [self.embed(b0), self.embed(b1)]
+        bs = [b0, b1]
+        self.pairs_run += 1
+        self._overlap = True
+        try:
+            gens = [self._layers_interleaved(xs[i], bs[i], cache) for i in range(2)]
+            pending = [None, None]
+            alive = [True, True]
+            while any(alive):
+                for i in range(2):
+                    if not alive[i]:
+                        continue
+                    if pending[i] is not None:
+                        pending[i].wait()
+                        pending[i] = None
+                    try:
+                        pending[i] = next(gens[i])
+                    except StopIteration as e:
+                        xs[i] = e.value
+                        alive[i] = False
+        finally:
+            self._overlap = False
+            self._work = None
+        return self.head(xs[0], b0), self.head(xs[1], b1)
 
     def head(self, x: torch.Tensor, b: Batch) -> torch.Tensor:
         """Final norm on the rows that need logits + vocab-split lm_head -> fp32 [rows, vocab/tp]."""

@@ -150,6 +150,24 @@ class DistContext:
                 raise CommError(f"all-reduce failed on rank {self.rank}: {e}") from e
         return t
 
+    def all_reduce_async(self, t: torch.Tensor):
+        """Start an in-place sum over the TP group and return a handle whose ``wait()`` makes the result usable on the
+        current stream; the caller may enqueue unrelated work in between, which then overlaps with the transfer."""
+        self.stats["all_reduce"] += 1
+        try:
+            if t.device.type == "cpu" and t.dtype == torch.bfloat16:
+                f = t.float()
+                w = dist.all_reduce(f, group=self.tp_group, async_op=True)
+
+                class _Back:
+                    def wait(self_inner):
+                        w.wait()
+                        t.copy_(f)
+                return _Back()
+            return dist.all_reduce(t, group=self.tp_group, async_op=True)
+        except RuntimeError as e:
+            raise CommError(f"all-reduce failed on rank {self.rank}: {e}") from e
+
     def all_gather_cat(self, t: torch.Tensor, sizes: Optional[List[int]] = None, dim: int = -1) -> torch.Tensor:
         """allgatherv along `dim` over the TP group (C3-C6: logits slices, (val,id) pairs)."""
         if self.tp_size == 1:

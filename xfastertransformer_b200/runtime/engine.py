@@ -714,6 +714,9 @@ class Model:
         groups = self._groups(seqs)
         if self.ctx.pp_size > 1:
             return self._pp_forward(groups, logits_all)
+        if self.env.prefill_overlap and self.ctx.tp_size > 1 and not self.decoder.has_moe and len(seqs) > 1 and \
+                all(len(s.pending) > 1 for s in seqs):
+            return self._run_overlapped(seqs, groups, logits_all)
         if len(groups) > 1:
             return torch.cat([self._run(g, logits_all) for g in groups], dim=0)
         b = self.make_batch(seqs, logits_all)
@@ -723,6 +726,35 @@ class Model:
             out = dec.forward(b, self.cache)
         self._remember_prefixes(seqs)
         return out
+
+    def _run_overlapped(self, seqs, groups, logits_all: bool) -> torch.Tensor:
+        """Tensor-parallel prefill with XFT_PREFILL_OVERLAP=1: the groups are taken two at a time and interleaved block
+        by block (Decoder.forward_pair), so the all-reduce of one group travels while the other one computes.  A single
+        group is cut in two halves of about the same number of tokens first."""
+        if len(groups) == 1:
+            total, acc, cut = sum(len(s.pending) for s in seqs), 0, 1
+            for i, s in enumerate(seqs[:-1]):
+                acc += len(s.pending)
+                cut = i + 1
+                if acc * 2 >= total:
+                    break
+            groups = [list(seqs[:cut]), list(seqs[cut:])]
+        outs = []
+        dec = self.prefill_decoder
+        with torch.no_grad():
+            for i in range(0, len(groups) - 1, 2):
+                b0, b1 = self.make_batch(groups[i], logits_all), self.make_batch(groups[i + 1], logits_all)
+                with TimeLine("1st Token"):
+                    o0, o1 = dec.forward_pair(b0, b1, self.cache)
+                self._remember_prefixes(groups[i])
+                self._remember_prefixes(groups[i + 1])
+                outs += [o0, o1]
+            if len(groups) % 2:
+                b = self.make_batch(groups[-1], logits_all)
+                with TimeLine("1st Token"):
+                    outs.append(dec.forward(b, self.cache))
+                self._remember_prefixes(groups[-1])
+        return torch.cat(outs, dim=0)
 
     def _remember_prefixes(self, seqs: Sequence[SequenceMeta]) -> None:
         """Automatic prefix reuse: the full blocks a prefill has just written become available to later prompts."""

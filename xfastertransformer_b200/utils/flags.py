@@ -69,6 +69,9 @@ class Env:
         self.attn_tma = _int("XFT_ATTN_TMA", 1) != 0      # bf16 decode attention through the TMA ring kernel
         self.attn_splits = _int("XFT_ATTN_SPLITS", 0)     # decode split-KV factor; 0 = planned per launch
         self.gemm_persistent = _int("XFT_GEMM_PERSISTENT", 0) != 0     # prefill GEMMs through the persistent kernel
+        # tensor-parallel prefill: two groups of prompts are interleaved block by block, so that the all-reduce of one
+        # overlaps the compute of the other
+        self.prefill_overlap = _int("XFT_PREFILL_OVERLAP", 0) != 0
         # XFT_PREFILL_FUSED_AR (row-parallel prefill GEMM + all-reduce as one kernel) and XFT_MAX_BATCH_TOKENS size the
         # symmetric buffers: parallel/fused_comm.py reads them when the peer communicator is built
         # accepted, no effect on a GPU build
