@@ -122,7 +122,7 @@ def test_lost_rank_raises_comm_error_not_hang(tiny, tmp_path):
 
 
 @pytest.mark.parametrize("mt,ep", [("mixtral", 0), ("mixtral", 1), ("deepseek_moe", 1), ("qwen3_moe", 0),
-                                   ("mixtral", 2), ("deepseek_moe", 2)])
+                                   ("mixtral", 2), ("deepseek_moe", 2), ("mixtral", 3), ("deepseek_moe", 4)])
 def test_moe_two_ranks_sliced_and_expert_parallel(mt, ep, tmp_path):
     """MoE across two gloo ranks against the single-rank engine on the same files: XFT_EXPERT_PARALLEL=0 slices every
     expert's intermediate dimension (the reference's only mode, src/layers/moe_deepseek.h / mlp_llama.h:70-79), =1
@@ -150,9 +150,11 @@ def test_moe_two_ranks_sliced_and_expert_parallel(mt, ep, tmp_path):
     d = str(tmp_path / "m")
     write_synthetic_checkpoint(d, cfg, seed=0, dtype="bf16", std=0.05)
     out = str(tmp_path / "moe.pt")
+    # ep = 3 / 4: sliced / whole experts with the prefill of the three prompts interleaved (XFT_PREFILL_OVERLAP=1)
+    overlap, ep = int(ep >= 3), {3: 0, 4: 1}.get(ep, ep)
     env = dict(os.environ, XFT_ENGINE="CPU", XFT_EXPERT_PARALLEL=str(int(ep == 1)), XFT_ATTENTION_DP=str(int(ep == 2)),
-               PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
-    port = 29621 + 2 * (ep + 2 * ["mixtral", "deepseek_moe", "qwen3_moe"].index(mt))
+               XFT_PREFILL_OVERLAP=str(overlap), PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    port = 29621 + 2 * (ep + 2 * ["mixtral", "deepseek_moe", "qwen3_moe"].index(mt)) + 100 * overlap
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
            "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "moe_tp_worker.py"), d, out]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)

@@ -675,7 +675,11 @@ class Decoder:
                 # decode sizes: the peer-memory one-shot kernel sums the fp32 partials (it can be captured in a CUDA
                 # graph, which a NCCL call cannot safely be)
                 return peer.all_reduce(out.contiguous()).to(x.dtype)
-            return self.ctx.all_reduce(out.to(x.dtype))
+            y = out.to(x.dtype)
+            if self._overlap:                 # interleaved prefill: started here, awaited by forward_pair's driver
+                self._work = self.ctx.all_reduce_async(y)
+                return y
+            return self.ctx.all_reduce(y)
         return out.to(x.dtype)
 
     def forward_layers(self, x: torch.Tensor, b: Batch, cache: PagedKVCache) -> torch.Tensor:
@@ -711,7 +715,7 @@ class Decoder:
         (XFT_PREFILL_OVERLAP=1).  The reference waits for every all-reduce before it goes on
         (src/layers/decoder_block.h:122-134); here batch A starts the sum of its block and, while NVLink carries it,
         batch B's next block runs on the SMs, and so on alternately.  Results are those of two forward() calls."""
-        assert self.first_stage and self.last_stage and not self.has_moe
+        assert self.first_stage and self.last_stage and self.ctx.dp_size == 1
         xs = [self.embed(b0), self.embed(b1)]
         bs = [b0, b1]
         self.pairs_run += 1

@@ -714,8 +714,7 @@ class Model:
         groups = self._groups(seqs)
         if self.ctx.pp_size > 1:
             return self._pp_forward(groups, logits_all)
-        if self.env.prefill_overlap and self.ctx.tp_size > 1 and not self.decoder.has_moe and len(seqs) > 1 and \
-                all(len(s.pending) > 1 for s in seqs):
+        if self.env.prefill_overlap and self.ctx.tp_size > 1 and len(seqs) > 1 and all(len(s.pending) > 1 for s in seqs):
             return self._run_overlapped(seqs, groups, logits_all)
         if len(groups) > 1:
             return torch.cat([self._run(g, logits_all) for g in groups], dim=0)
