@@ -223,7 +223,10 @@ def main():
                                        f"tp{world}+ep{world}" if m.ctx.ep_size > 1 else f"tp{world}"),
                        "kv_cache": f"paged-64 {args.kv_dtype}",
                        "l2": "inputs larger than L2 (each step streams %.1f GB of weights per GPU)" % (wbytes / 1e9),
-                       "layers": cfg.num_layer},
+                       "layers": cfg.num_layer,
+                       # every XFT_* variable that was set for this run (opt-in kernels and modes change what is timed)
+                       "env": {k: v for k, v in sorted(os.environ.items())
+                               if k.startswith("XFT_") and k != "XFT_FAKE_MODEL"}},
             "ttft_ms": round(ttft_ms, 2), "ttft_cold_ms": round(ttft_cold_ms, 2),
             "next_token_ms": {"avg": round(statistics.mean(step_ms), 4), "min": round(min(step_ms), 4),
                               "max": round(max(step_ms), 4),
