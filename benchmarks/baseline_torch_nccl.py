@@ -96,14 +96,19 @@ def main():
 
     ids = torch.randint(0, V, (B, S), generator=torch.Generator().manual_seed(1)).to(dev)
     with torch.no_grad():
-        torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        # prefill in chunks of 4 sequences to bound activations
-        nxt = step(ids, 0)
-        e1.record()
-        torch.cuda.synchronize()
-        ttft = e0.elapsed_time(e1)
+        ttfts = []
+        for _ in range(2):             # the first prefill is the warm-up (cold: first use of every kernel and of NCCL)
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0.record()
+            # prefill in chunks of 4 sequences to bound activations
+            nxt = step(ids, 0)
+            e1.record()
+            torch.cuda.synchronize()
+            ttfts.append(e0.elapsed_time(e1))
+        ttft_cold, ttft = ttfts
         p = S
         for _ in range(a.warmup):
             nxt = step(nxt[:, None], p)
@@ -118,13 +123,13 @@ def main():
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1)
-    t = torch.tensor([ms, ttft], device=dev, dtype=torch.float64)
+    t = torch.tensor([ms, ttft, ttft_cold], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     if rank == 0:
         print(json.dumps({"impl": "torch cuBLAS + SDPA + NCCL (eager)", "metric": "decode_tokens_per_s",
                           "value": round(B * a.steps / (t[0].item() / 1e3), 2), "ms_per_step": round(t[0].item() / a.steps, 4),
-                          "ttft_ms": round(t[1].item(), 2), "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+                          "ttft_ms": round(t[1].item(), 2), "ttft_cold_ms": round(t[2].item(), 2), "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
                           "config": {"model": a.model, "global_batch": B, "seq_len": S, "layers": L}}))
     if world > 1:
         dist.barrier()
