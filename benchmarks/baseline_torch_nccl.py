@@ -44,7 +44,10 @@ def main():
     total = S + 1 + a.warmup + a.steps
     bf = torch.bfloat16
     rnd = lambda *s: torch.empty(*s, dtype=bf, device=dev).normal_(0, 0.02)
-    layers = [dict(qkv=rnd((hq + 2 * hkv) * D, H), o=rnd(H, hq * D), gu=rnd(2 * Il, H), dn=rnd(H, Il), n1=torch.ones(H, dtype=bf, device=dev),
+    E, topk = int(c.get("sparse_experts", 0) or 0), int(c.get("num_experts_per_tok", 2) or 2)
+    mlp_w = (lambda: dict(router=rnd(E, H), gu=rnd(E, 2 * Il, H), dn=rnd(E, H, Il))) if E else \
+        (lambda: dict(gu=rnd(2 * Il, H), dn=rnd(H, Il)))
+    layers = [dict(qkv=rnd((hq + 2 * hkv) * D, H), o=rnd(H, hq * D), **mlp_w(), n1=torch.ones(H, dtype=bf, device=dev),
                    n2=torch.ones(H, dtype=bf, device=dev), k=torch.zeros(B, hkv, total, D, dtype=bf, device=dev),
                    v=torch.zeros(B, hkv, total, D, dtype=bf, device=dev)) for _ in range(L)]
     wte, head, fn = rnd(V, H), rnd(Vl, H), torch.ones(H, dtype=bf, device=dev)
@@ -79,8 +82,22 @@ def main():
                 dist.all_reduce(o)
             x = x + o
             h = rms(x, l["n2"])
-            gu = h @ l["gu"].t()
-            y = (F.silu(gu[..., :Il]) * gu[..., Il:]) @ l["dn"].t()
+            if E:
+                # Mixtral-style MoE the eager way: every rank holds a slice of every expert; tokens are gathered per
+                # expert, run through its two matmuls and scattered back with the routing weight
+                flat = h.reshape(-1, H)
+                wts, sel = torch.topk(flat.float() @ l["router"].float().t(), topk, dim=-1)
+                wts = torch.softmax(wts, -1).to(bf)
+                y = torch.zeros_like(flat)
+                for e in range(E):
+                    tok, slot = (sel == e).nonzero(as_tuple=True)
+                    if tok.numel():
+                        g = flat[tok] @ l["gu"][e].t()
+                        y.index_add_(0, tok, ((F.silu(g[:, :Il]) * g[:, Il:]) @ l["dn"][e].t()) * wts[tok, slot, None])
+                y = y.view_as(h)
+            else:
+                gu = h @ l["gu"].t()
+                y = (F.silu(gu[..., :Il]) * gu[..., Il:]) @ l["dn"].t()
             if world > 1:
                 dist.all_reduce(y)
             x = x + y
