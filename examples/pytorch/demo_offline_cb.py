@@ -53,6 +53,9 @@ def main():
     a = ap.parse_args()
     import xfastertransformer_b200 as xft
     model = xft.AutoModel.from_pretrained(a.model_path, dtype=a.dtype)
+    if model.rank != 0:                  # several GPUs (torchrun): the other ranks execute rank 0's calls
+        model.follow()
+        return
     rng = random.Random(0)
     v = model.model.cfg.vocab_size
     prompts = [[rng.randrange(5, v) for _ in range(rng.randint(8, 64))] for _ in range(a.num_prompts)]
@@ -61,6 +64,7 @@ def main():
     dt = time.perf_counter() - t0
     n = sum(len(o) for o in outs)
     print(f"{len(prompts)} requests, {n} tokens, {steps} engine steps, {n / dt:.1f} tokens/s")
+    model.model.exit_slaves()
 
 
 if __name__ == "__main__":
