@@ -564,13 +564,23 @@ def test_ngram_speculative_decoding_is_exact(tiny, monkeypatch):
         # oracle drafts: the true continuation, the third draft token wrong
         rows = {tuple(r[:30].tolist()): r.tolist() for r in want}
 
-        def oracle(tokens, k, window=1024):
+        # the incremental table gives what the plain search gives, step by step over a growing sequence
+        from xfastertransformer_b200.runtime.sequence import SequenceMeta
+        import random
+        rng = random.Random(0)
+        seq = SequenceMeta(0, [rng.randrange(4) for _ in range(9)], 500)
+        for _ in range(120):
+            assert eng._draft_for(seq, 4) == Model._ngram_draft(seq.all_tokens(), 4, window=10 ** 6)
+            seq.generated.append(rng.randrange(4))
+
+        def oracle(self, s, k):
+            tokens = s.all_tokens()
             full = rows[tuple(tokens[:30])]
             d = full[len(tokens):len(tokens) + k]
             if len(d) > 2:
                 d[2] = (d[2] + 1) % 900
             return d
-        monkeypatch.setattr(Model, "_ngram_draft", staticmethod(oracle))
+        monkeypatch.setattr(Model, "_draft_for", oracle)
         s0, e0, a0, f0 = eng.spec_steps, eng.spec_emitted, eng.spec_accepted, len(eng.step_times_ms)
         assert torch.equal(m.generate(ids, max_length=30 + 48), want)
         steps = eng.spec_steps - s0

@@ -559,14 +559,15 @@ def test_grpc_stream_carries_every_token_under_speculative_decoding(tiny, monkey
     want = plain.generate(ids, max_length=12 + 20)
     rows = {tuple(r[:12].tolist()): r.tolist() for r in want}
 
-    def oracle(tokens, k, window=1024):          # row 0 always gets two right drafts, row 1 none
+    def oracle(self, s, k):                      # row 0 always gets two right drafts, row 1 none
+        tokens = s.all_tokens()
         full = rows[tuple(tokens[:12])]
         return full[len(tokens):len(tokens) + 2] if full == rows[tuple(ids[0].tolist())] else []
     monkeypatch.setenv("XFT_SPEC_NGRAM", "4")
     Env.get().reload()
     try:
         model = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
-        monkeypatch.setattr(Model, "_ngram_draft", staticmethod(oracle))
+        monkeypatch.setattr(Model, "_draft_for", oracle)
         sv = Servicer(model)
         got = [[], []]
         widths = set()

@@ -306,6 +306,26 @@ class Model:
                     return tokens[i + n:i + n + k]
         return []
 
+    def _draft_for(self, s: SequenceMeta, k: int) -> List[int]:
+        """`_ngram_draft` for a live sequence, in time independent of its length: the sequence carries a table from
+        every 1-, 2- and 3-gram that has a successor to the position of that successor (latest occurrence wins), which
+        is extended by the few tokens that arrived since the last step."""
+        toks = s.all_tokens()
+        n_tok = len(toks)
+        table = s.__dict__.setdefault("_ngrams", {})
+        upto = s.__dict__.get("_ngrams_upto", 0)
+        for j in range(upto, n_tok - 1):                     # n-grams ending at j have the successor toks[j + 1]
+            for n in (1, 2, 3):
+                if j + 1 >= n:
+                    table[tuple(toks[j - n + 1:j + 1])] = j + 1
+        s.__dict__["_ngrams_upto"] = max(upto, n_tok - 1)
+        for n in (3, 2, 1):
+            if n_tok > n:
+                pos = table.get(tuple(toks[-n:]))
+                if pos is not None:
+                    return toks[pos:pos + k]
+        return []
+
     def _spec_step(self, seqs: Sequence[SequenceMeta], cfg: SamplingMeta) -> bool:
         """One decode step that may emit several tokens per sequence.  Each sequence proposes draft tokens from its own
         history; one forward scores the pending token and the drafts; the longest draft prefix that greedy decoding
@@ -316,7 +336,7 @@ class Model:
         drafts = []
         for s in seqs:
             room = s.max_len - s.total_len - 1               # tokens that may still follow the one after the draft
-            drafts.append(self._ngram_draft(s.all_tokens(), min(k, room)) if room > 0 else [])
+            drafts.append(self._draft_for(s, min(k, room)) if room > 0 else [])
         if not any(drafts):
             return False
         starts = [s.past_len for s in seqs]
