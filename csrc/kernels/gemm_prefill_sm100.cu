@@ -267,8 +267,9 @@ __global__ void __launch_bounds__(192, 1) gemm_prefill_kernel(const __grid_const
           *s_abort = 1;
         }
       }
-      named_bar_sync(1, 128);                  // every epilogue thread sees the same abort state from here on
-      if (*s_abort) break;
+      // one answer for all 128 epilogue threads: a flag read per thread could change between two reads (the other
+      // roles raise it too) and leave part of the group in front of a barrier the rest never reaches
+      if (named_bar_or(1, 128, *s_abort != 0)) break;
       tcgen05_fence_after();
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + (uint32_t)(a * BN * NACC);
       const int n = nt * 128 + row;

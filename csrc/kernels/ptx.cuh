@@ -181,6 +181,22 @@ __device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
+// Named barrier that also ORs a predicate over its threads: every thread gets the same answer, so a branch on it
+// cannot split the group in front of a later barrier.
+__device__ __forceinline__ bool named_bar_or(int id, int nthreads, bool pred) {
+  int r;
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.s32 q, %3, 0;\n"
+      "bar.red.or.pred p, %1, %2, q;\n"
+      "selp.s32 %0, 1, 0, p;\n"
+      "}"
+      : "=r"(r)
+      : "r"(id), "r"(nthreads), "r"((int)pred)
+      : "memory");
+  return r != 0;
+}
 
 
 // Host: launch with the programmatic-stream-serialization attribute (captured into CUDA graphs as a

@@ -208,9 +208,15 @@ class CudaRunner:
         per_rank = [sum(1 for s in seqs if s.owner == r) for r in range(ctx.dp_size)]
         ctx.dp_max_tokens = max(self.bucket(n) if n else 0 for n in per_rank)
         toks = self._step_local(local, cfg) if local else self._step_idle()
-        allt = [None] * ctx.world
-        dist.all_gather_object(allt, [int(t) for t in toks], group=ctx.ctrl_group)
-        its = [iter(t) for t in allt]
+        # one fixed-size gather of token ids (rows padded with -1): no pickling, one round on the control group
+        n = max(max(per_rank), 1)
+        mine = torch.full((n,), -1, dtype=torch.int64)
+        if toks:
+            mine[:len(toks)] = torch.tensor([int(t) for t in toks], dtype=torch.int64)
+        allt = torch.empty(ctx.world * n, dtype=torch.int64)
+        dist.all_gather_into_tensor(allt, mine, group=ctx.ctrl_group)
+        rows = allt.view(ctx.world, n).tolist()
+        its = [iter(r) for r in rows]
         return [next(its[s.owner]) for s in seqs]
 
     def _step_idle(self) -> List[int]:
