@@ -142,3 +142,13 @@ extern "C" int xft_allreduce_oneshot(const void* in, void* out, const float* add
                    (__nv_bfloat16*)out, add_f32, n, *p, gather);
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
+
+// Size and field offsets of ArParams, for the layout check of the Python mirror.
+extern "C" int xft_ar_params_layout(long long* out, int n) {
+  const long long v[] = {sizeof(ArParams),         offsetof(ArParams, world), offsetof(ArParams, rank),
+                         offsetof(ArParams, recv), offsetof(ArParams, epoch), offsetof(ArParams, done),
+                         offsetof(ArParams, cap),  offsetof(ArParams, wait_cycles), offsetof(ArParams, status)};
+  const int m = (int)(sizeof(v) / sizeof(v[0]));
+  for (int i = 0; i < m && i < n; ++i) out[i] = v[i];
+  return m;
+}

@@ -288,3 +288,15 @@ extern "C" int xft_ep_combine(const float* w, const int* dest, int T, int k, con
                              (const __nv_bfloat16*)add2, ld2, (__nv_bfloat16*)out, *p);
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
+
+// Size and field offsets of EpParams, for the layout check of the Python mirror.
+extern "C" int xft_ep_layout(long long* out, int n) {
+  const long long v[] = {sizeof(EpParams),           offsetof(EpParams, world),   offsetof(EpParams, rank),
+                         offsetof(EpParams, rx_tok), offsetof(EpParams, rx_meta), offsetof(EpParams, rx_cnt),
+                         offsetof(EpParams, ret),    offsetof(EpParams, ret_flag), offsetof(EpParams, epoch),
+                         offsetof(EpParams, done),   offsetof(EpParams, cap),     offsetof(EpParams, pairs_cap),
+                         offsetof(EpParams, H),      offsetof(EpParams, wait_cycles), offsetof(EpParams, status)};
+  const int m = (int)(sizeof(v) / sizeof(v[0]));
+  for (int i = 0; i < m && i < n; ++i) out[i] = v[i];
+  return m;
+}

@@ -532,3 +532,14 @@ extern "C" int xft_gemm_bf16_prefill_gated(const void* X, int ldx, const void* W
   if (r) return 2000 - r;
   return launch_prefill<128, true>(tmW, tmX, p, num_ctas, st);
 }
+
+// Size and field offsets of BulkArParams, for the layout check of the Python mirror.
+extern "C" int xft_bulk_ar_layout(long long* out, int n) {
+  const long long v[] = {sizeof(BulkArParams),           offsetof(BulkArParams, world),       offsetof(BulkArParams, rank),
+                         offsetof(BulkArParams, part),   offsetof(BulkArParams, flag_part),   offsetof(BulkArParams, out),
+                         offsetof(BulkArParams, flag_res), offsetof(BulkArParams, epoch),     offsetof(BulkArParams, done),
+                         offsetof(BulkArParams, part_stride), offsetof(BulkArParams, wait_cycles)};
+  const int m = (int)(sizeof(v) / sizeof(v[0]));
+  for (int i = 0; i < m && i < n; ++i) out[i] = v[i];
+  return m;
+}

@@ -877,3 +877,15 @@ extern "C" int xft_gemm_bf16_noalloc_status(cudaStream_t st) {
   if (cudaStreamSynchronize(st) != cudaSuccess) return -102;
   return v;
 }
+
+// Size and field offsets of CommParams, for the layout check of the Python mirror.
+extern "C" int xft_comm_params_layout(long long* out, int n) {
+  using xft::CommParams;
+  const long long v[] = {sizeof(CommParams),           offsetof(CommParams, world),        offsetof(CommParams, rank),
+                         offsetof(CommParams, recv),   offsetof(CommParams, epoch),        offsetof(CommParams, done),
+                         offsetof(CommParams, slot_stride), offsetof(CommParams, parity_stride),
+                         offsetof(CommParams, wait_cycles), offsetof(CommParams, two_shot), offsetof(CommParams, result)};
+  const int m = (int)(sizeof(v) / sizeof(v[0]));
+  for (int i = 0; i < m && i < n; ++i) out[i] = v[i];
+  return m;
+}

@@ -418,3 +418,27 @@ def test_cmake_tree_configures_and_runs_the_native_tests(tmp_path):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     r = subprocess.run(["ctest", "--output-on-failure"], cwd=b, capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0 and "100% tests passed" in r.stdout, r.stdout[-2000:]
+
+
+def test_ctypes_mirrors_of_kernel_parameter_structs_have_the_c_layout():
+    """Each struct that Python fills and a kernel reads by value: the ctypes mirror has the size and the field offsets
+    the compiler gave the C struct (the library reports them)."""
+    import xfastertransformer_b200 as pkg
+    from xfastertransformer_b200.parallel import fused_comm as F
+    path = os.path.join(os.path.dirname(pkg.__file__), "lib", "libxft_b200_kernels.so")
+    if not os.path.exists(path):
+        pytest.skip("kernel library not built")
+    try:
+        lib = C.CDLL(path)
+    except OSError as e:
+        pytest.skip(f"kernel library does not load here: {e}")
+    for fn, mirror in (("xft_comm_params_layout", F.CommParams), ("xft_ar_params_layout", F.ArParams),
+                       ("xft_bulk_ar_layout", F.BulkArParams), ("xft_ep_layout", F.EpParams)):
+        out = (C.c_longlong * 32)()
+        f = getattr(lib, fn)
+        f.restype = C.c_int
+        n = f(out, 32)
+        names = [name for name, _ in mirror._fields_]
+        assert n == 1 + len(names), fn
+        assert out[0] == C.sizeof(mirror), fn
+        assert [out[1 + i] for i in range(len(names))] == [getattr(mirror, name).offset for name in names], fn
