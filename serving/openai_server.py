@@ -78,7 +78,7 @@ class Scheduler(threading.Thread):
         self.running: Dict[int, Request] = {}
         self.stop_flag = threading.Event()
         self.metrics = dict(requests=0, finished=0, prompt_tokens=0, generated_tokens=0, ttft_sum=0.0, tpot_sum=0.0,
-                            tpot_count=0, steps=0, mixed_steps=0, errors=0, cancelled=0, prefill_chunks=0, rejected=0)
+                            tpot_count=0, steps=0, mixed_steps=0, errors=0, cancelled=0, prefill_chunks=0, rejected=0, spec_tokens=0)
         self.mixed_steps = False          # prefill new prompts in the same forward as the running sequences' decode
         self.max_queue = 0                # > 0: requests beyond this many waiting ones are refused with 429
         self.prefill_chunk = 0            # > 0: prompts longer than this are fed in pieces of this many tokens, one piece
@@ -301,7 +301,16 @@ class Scheduler(threading.Thread):
                     greedy = all(r.greedy_on_device for r in reqs)
                     self.model.set_input_cb([r.generated[-1] for r in reqs], sids, None, greedy=greedy)
                     picks = self._forward(reqs, greedy)
-                    done = [s for s, r, tok in zip(sids, reqs, picks) if self._emit(r, tok)]
+                    # with XFT_SPEC_NGRAM the engine may have accepted draft tokens: every request then gets all the
+                    # tokens of the step, in order, and stops at the first one that ends it
+                    many = getattr(getattr(self.model, "model", None), "cb_emitted", None) if greedy else None
+                    if not many or len(many) != len(reqs) or [m[-1] for m in many] != picks:
+                        many = [[tok] for tok in picks]
+                    done = []
+                    for sid, r, toks in zip(sids, reqs, many):
+                        self.metrics["spec_tokens"] += len(toks) - 1
+                        if any(self._emit(r, t) for t in toks):
+                            done.append(sid)
                     self._finish(done)
                     self.metrics["steps"] += 1
             except Exception as e:      # an engine error ends the affected requests, not the server

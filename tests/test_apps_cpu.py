@@ -583,3 +583,70 @@ def test_grpc_stream_carries_every_token_under_speculative_decoding(tiny, monkey
     finally:
         monkeypatch.delenv("XFT_SPEC_NGRAM")
         Env.get().reload()
+
+
+def test_openai_server_emits_every_token_of_a_speculative_step(tmp_path, monkeypatch):
+    """XFT_SPEC_NGRAM in the serving scheduler: a decode step that accepted drafts hands all its tokens to the request,
+    in order; requests stop exactly where plain greedy decoding stops (max_tokens in the middle of an accepted run,
+    a stop token inside it); the cache ends empty."""
+    import importlib.util
+    import threading
+    from xfastertransformer_b200.runtime.engine import Model
+    from xfastertransformer_b200.utils.flags import Env
+    spec = importlib.util.spec_from_file_location("oai", os.path.join(ROOT, "serving", "openai_server.py"))
+    oai = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(oai)
+    d = str(tmp_path / "tiny")
+    write_synthetic_checkpoint(d, preset("tiny-llama", vocab_size=500), seed=5, dtype="fp32", std=0.1)
+    model = xft.AutoModel.from_pretrained(d, dtype="bf16")
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(5, 490, (n,), generator=g).tolist() for n in (12, 5, 9)]
+    full = {tuple(p): p + model.generate(torch.tensor([p]), max_length=len(p) + 14)[0, len(p):].tolist() for p in prompts}
+    want = [full[tuple(p)][len(p):] for p in prompts]
+
+    def oracle(self, s, k):                      # the true continuation, with every fourth draft position falsified
+        toks = s.all_tokens()
+        ref = full[tuple(toks[:len(s.prompt)])]
+        dr = ref[len(toks):len(toks) + k]
+        return [t if (len(toks) + i) % 4 else (t + 1) % 500 for i, t in enumerate(dr)]
+
+    monkeypatch.setenv("XFT_SPEC_NGRAM", "3")
+    Env.get().reload()
+    monkeypatch.setattr(Model, "_draft_for", oracle)
+    httpd, sched, port = oai.serve(model, 0, max_batch=8, model_name="tiny")
+    base = f"http://127.0.0.1:{port}"
+
+    def post(body):
+        req = urllib.request.Request(base + "/v1/completions", data=json.dumps(body).encode(),
+                                     headers={"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=120) as r:
+            return json.loads(r.read())
+
+    try:
+        lens = [14, 7, 10]
+        got = [None] * len(prompts)
+
+        def one(i):
+            got[i] = post({"prompt": prompts[i], "max_tokens": lens[i]})
+
+        ths = [threading.Thread(target=one, args=(i,)) for i in range(len(prompts))]
+        [t.start() for t in ths]
+        [t.join() for t in ths]
+        for i, r in enumerate(got):
+            assert r["choices"][0]["token_ids"] == want[i][:lens[i]], (i, r["choices"][0]["token_ids"], want[i])
+        eng = model.model
+        assert sched.metrics["spec_tokens"] > 0 and eng.spec_accepted >= sched.metrics["spec_tokens"]
+        # fewer engine steps than tokens: one prefill per request group, then decode steps that emit several tokens
+        assert sched.metrics["steps"] < sum(lens)
+        # a stop token inside an accepted run ends the request there
+        stop_at = want[0][6]
+        first = want[0].index(stop_at)
+        r = post({"prompt": prompts[0], "max_tokens": 14, "stop_token_ids": [stop_at]})
+        assert r["choices"][0]["token_ids"] == want[0][:first + 1], (r["choices"][0]["token_ids"], want[0], stop_at)
+        assert not sched.running and not eng.cache.tables
+        assert eng.cache.alloc.num_free == eng.cache.alloc.num_blocks
+    finally:
+        sched.shutdown()
+        httpd.shutdown()
+        monkeypatch.delenv("XFT_SPEC_NGRAM")
+        Env.get().reload()

@@ -339,13 +339,30 @@ class Model:
             drafts.append(self._draft_for(s, min(k, room)) if room > 0 else [])
         if not any(drafts):
             return False
+        for s, e in zip(seqs, self._spec_score(seqs, drafts)):
+            for t in e:
+                s.step_forward(t)
+                self.spec_emitted += 1
+                if t == cfg.eos_token_id or s.total_len >= s.max_len or \
+                        (cfg.stop_words and S.match_stop_words(s.generated, cfg.stop_words)):
+                    s.done = True
+                    break
+            self.cache.truncate(s.seq_id, s.past_len)        # positions of rejected drafts are written again later
+        self.spec_steps += 1
+        return True
+
+    def _spec_score(self, seqs: Sequence[SequenceMeta], drafts: List[List[int]]) -> List[List[int]]:
+        """One forward over every sequence's pending token followed by its drafts.  Returns per sequence the tokens
+        greedy decoding emits from here: the drafts it would have chosen itself, then its own next token.  The
+        sequences come back as they went in (same past length, the one pending token); the cache holds the draft
+        positions too, and the caller truncates it to what it keeps."""
         starts = [s.past_len for s in seqs]
         lasts = [s.pending[0] for s in seqs]
         for s, d in zip(seqs, drafts):
             s.pending = s.pending + d
         local = self._run(seqs, logits_all=True)             # one row per pending token, sequence after sequence
         preds = S.greedy_select(local, self.decoder.v0, self.ctx).cpu().tolist()
-        row = 0
+        out, row = [], 0
         for s, d, p0, last in zip(seqs, drafts, starts, lasts):
             p = preds[row:row + 1 + len(d)]
             row += 1 + len(d)
@@ -353,17 +370,9 @@ class Model:
             while acc < len(d) and int(p[acc]) == d[acc]:
                 acc += 1
             s.past_len, s.pending = p0, [last]
-            for t in d[:acc] + [int(p[acc])]:
-                s.step_forward(t)
-                self.spec_emitted += 1
-                if t == cfg.eos_token_id or s.total_len >= s.max_len or \
-                        (cfg.stop_words and S.match_stop_words(s.generated, cfg.stop_words)):
-                    s.done = True
-                    break
             self.spec_accepted += acc
-            self.cache.truncate(s.seq_id, s.past_len)        # positions of rejected drafts are written again later
-        self.spec_steps += 1
-        return True
+            out.append(d[:acc] + [int(p[acc])])
+        return out
 
     def _select(self, local: torch.Tensor, seqs: Sequence[SequenceMeta], cfg: SamplingMeta) -> torch.Tensor:
         d = self.decoder
@@ -564,6 +573,24 @@ class Model:
         if self.ctx.world > 1 and not getattr(self, "_cb_greedy", False):
             raise RuntimeError("forward_cb_greedy() needs set_input_cb(..., greedy=True) on more than one rank")
         cfg = self._greedy_cfg
+        if self._spec_ok(seqs, cfg):
+            # XFT_SPEC_NGRAM: a decode step may emit several tokens per sequence.  The accepted drafts become part of
+            # the sequence here; the caller reads all emitted tokens from `cb_emitted` and feeds back only the last.
+            k = self.env.spec_ngram
+            drafts = [self._draft_for(s, max(min(k, s.max_len - s.total_len - 1), 0)) for s in seqs]
+            if any(drafts):
+                with self.watchdog.scope("forward_cb_greedy"):
+                    emitted = self._spec_score(seqs, drafts)
+                for s, e in zip(seqs, emitted):
+                    for t in e[:-1]:
+                        s.step_forward(t)
+                    s.past_len += len(s.pending)
+                    s.pending = []
+                    self.cache.truncate(s.seq_id, s.past_len)
+                    self.spec_emitted += len(e)
+                self.spec_steps += 1
+                self.cb_emitted = emitted
+                return torch.tensor([e[-1] for e in emitted], dtype=torch.int64)
         with self.watchdog.scope("forward_cb_greedy"):
             if self.runner is not None and self.runner.can_run(seqs, cfg) and self.runner.worth_capturing(seqs):
                 toks = self.runner.step(seqs, cfg)
@@ -573,6 +600,7 @@ class Model:
         for s in seqs:
             s.past_len += len(s.pending)
             s.pending = []
+        self.cb_emitted = [[int(t)] for t in toks]
         return torch.tensor([int(t) for t in toks], dtype=torch.int64)
 
     def follow(self) -> None:
