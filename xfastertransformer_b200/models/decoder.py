@@ -606,7 +606,9 @@ class Decoder:
             shared = None
             if T > 0 and getattr(L, "shared", None) is not None:
                 shared = ops.linear(ops.linear_gated(h, L.shared[0], L.act), L.shared[1], out_dtype=torch.float32)
-            run = lambda rows, ids, ones: ops.moe_experts(rows, ids, ones, L.experts, L.act, L.e0, getattr(L, "packed", None))
+            # the receive area has room for the worst case; about dp_max_tokens * k of its rows are real on average
+            run = lambda rows, ids, ones: ops.moe_experts(rows, ids, ones, L.experts, L.act, L.e0, getattr(L, "packed", None),
+                                                          expected_pairs=max(ctx.dp_max_tokens, 1) * k)
             return ep.exchange(h, idx, w, E, run, shared, x)
         if T > 0:
             idx, w = self._route(L, h)

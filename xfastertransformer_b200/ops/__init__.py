@@ -181,9 +181,9 @@ def route(logits, kind, top_k, bias=None, n_group=1, topk_group=1, routed_scalin
     raise ValueError(kind)
 
 
-def moe_experts(x, idx, w, experts, act="silu", expert_offset=0, packed=None):
+def moe_experts(x, idx, w, experts, act="silu", expert_offset=0, packed=None, expected_pairs=None):
     if _cuda(x):
-        return _nat().moe_experts(x, idx, w, experts, act, expert_offset, packed)
+        return _nat().moe_experts(x, idx, w, experts, act, expert_offset, packed, expected_pairs)
     return R.moe_experts(x, idx, w, experts, act, expert_offset)
 
 

@@ -387,9 +387,9 @@ def route(logits, kind, top_k, bias=None, n_group=1, topk_group=1, routed_scalin
     return native_moe.route(logits, kind, top_k, bias, n_group, topk_group, routed_scaling, norm_topk, scoring)
 
 
-def moe_experts(x, idx, w, experts, act="silu", expert_offset=0, packed=None):
+def moe_experts(x, idx, w, experts, act="silu", expert_offset=0, packed=None, expected_pairs=None):
     from . import native_moe
-    return native_moe.moe_experts(x, idx, w, experts, act, expert_offset, packed)
+    return native_moe.moe_experts(x, idx, w, experts, act, expert_offset, packed, expected_pairs)
 
 
 # ------------------------------------------------------------------------------------------

@@ -97,8 +97,10 @@ def _pack_fp8(experts) -> dict:
     return pk
 
 
-def moe_experts(x, idx, w, experts, act="silu", expert_offset=0, packed=None):
-    """sum_k w[t,k] * down_e(act(gate_e x) * up_e x) over the local experts -> fp32 [T, H]."""
+def moe_experts(x, idx, w, experts, act="silu", expert_offset=0, packed=None, expected_pairs=None):
+    """sum_k w[t,k] * down_e(act(gate_e x) * up_e x) over the local experts -> fp32 [T, H].  `expected_pairs`: about how
+    many (token, expert) pairs are real when most rows of `idx` are padding (-1), e.g. the receive area of the expert
+    exchange; it only picks the token tile of the grouped GEMMs."""
     pk = packed or pack_experts(experts)
     x2, ldx = N._rows2d(x)
     T, H = x2.shape
@@ -107,7 +109,7 @@ def moe_experts(x, idx, w, experts, act="silu", expert_offset=0, packed=None):
     dev = x.device
     ws = N.Workspace.get(dev)
     lib = _lib()
-    avg = max(1, (T * k + E - 1) // E)
+    avg = max(1, ((T * k if expected_pairs is None else min(int(expected_pairs), T * k)) + E - 1) // E)
     bn = 16 if avg <= 16 else 32 if avg <= 32 else 64 if avg <= 64 else 128
     max_rows = T * k
     max_tiles = (max_rows + bn - 1) // bn + E
