@@ -81,14 +81,14 @@ __global__ void __launch_bounds__(1024) ep_plan_kernel(const int* __restrict__ i
   for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
     const int e = idx[i];
     int d = -1, s = -1;
-    if (e >= 0 && e < E) {
+    if (e >= 0 && e < E && i < p.pairs_cap) {
       d = ep_owner(e, E, p.world);
       s = atomicAdd(&s_cnt[d], 1);
-      if (s >= p.cap || i >= p.pairs_cap) {            // does not fit the receive / return area: drop and report
+      if (s >= p.cap) {                                // does not fit the receive area: drop and report
         if (p.status) atomicCAS(p.status, 0, XFT_ERR_BOUNDS);
         d = -1;
       }
-    } else if (p.status) {
+    } else if (p.status) {                             // bad expert id, or a pair beyond the return area: no slot is taken
       atomicCAS(p.status, 0, XFT_ERR_BOUNDS);
     }
     dest[i] = d;

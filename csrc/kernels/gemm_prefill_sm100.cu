@@ -432,7 +432,9 @@ static int launch_prefill(const CUtensorMap& tmW, const CUtensorMap& tmX, Prefil
   const size_t smem = (size_t)stages * STAGE_BYTES + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_prefill_kernel<BN, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) !=
+    // the request is the ring itself: the kernel's static shared memory (barriers, the 4 KB store staging tile)
+    // counts against the same 227 KB, so asking for more than the ring needs can be refused
+    if (cudaFuncSetAttribute(gemm_prefill_kernel<BN, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)
       return 3000 + (int)cudaGetLastError();
     attr_set = true;

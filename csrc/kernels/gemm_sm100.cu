@@ -20,6 +20,7 @@
 // tile, each reducing a K range.  Partials go to an fp32 scratch in accumulator layout
 // [split][tile][column][128 rows]; the CTA that arrives last on the tile's counter sums the splits
 // in index order (deterministic) and runs the epilogue.  Nobody spins: there is no wait on a peer.
+#include "gemm_noalloc.h"
 #include "ptx.cuh"
 
 #include <cmath>
@@ -814,13 +815,19 @@ extern "C" int xft_gemm_bf16_ar(const void* X, int ldx, const void* W, int ldw, 
 //
 // The array is part of the library image: every GPU that loads the library keeps
 // XFT_NOALLOC_SCRATCH_BYTES (8 MiB + 8 KiB) resident until the process exits.
-static __device__ __align__(256) unsigned char g_noalloc_scratch[(8u << 20) + 8192];
+static __device__ __align__(256) unsigned char g_noalloc_scratch[XFT_NOALLOC_SCRATCH_BYTES];
 
 namespace {
 constexpr size_t kNoallocPartialBytes = 8u << 20;    // split-K partial tiles
 constexpr int kNoallocCounters = 1024;               // one int per output tile (first 4 KiB)
 constexpr int kNoallocMaxTokens = 256;
 constexpr int kNoallocMaxDevices = 64;
+constexpr size_t kNoallocHeadBytes = 8192;           // counters [0, 4096), status word at 4096
+// the limits published in gemm_noalloc.h are the ones enforced here
+static_assert(kNoallocMaxTokens == XFT_NOALLOC_MAX_TOKENS, "token limit differs from gemm_noalloc.h");
+static_assert(kNoallocCounters == XFT_NOALLOC_MAX_TILES, "tile limit differs from gemm_noalloc.h");
+static_assert(kNoallocHeadBytes + kNoallocPartialBytes == XFT_NOALLOC_SCRATCH_BYTES, "scratch size differs from gemm_noalloc.h");
+static_assert(kNoallocCounters * sizeof(int) <= 4096, "tile counters overlap the status word");
 void* g_noalloc_ptr[kNoallocMaxDevices] = {};        // device address of the array, per device
 }  // namespace
 
@@ -830,7 +837,7 @@ extern "C" const char* xft_gemm_bf16_noalloc_strerror(int code) {
     case -100: return "shape exceeds the allocation-free variant: need T <= 256 tokens and ceil(N/128)*ceil(T/tile) <= 1024 tiles";
     case -101: return "cudaGetSymbolAddress failed for the static scratch array";
     case -102: return "no current CUDA device / device index out of range";
-    case -103: return "bad argument (null pointer, K not a multiple of 8, or unaligned rows)";
+    case -103: return "bad argument (null pointer, K not a multiple of 8, unaligned rows, or ldo / ldr smaller than N)";
     default: return "CUDA or tensor-map error (positive codes are cudaError_t values; 1000+/2000+ tensor-map encoding)";
   }
 }
@@ -841,6 +848,7 @@ extern "C" int xft_gemm_bf16_noalloc(const void* X, int ldx, const void* W, int 
                                      int T, int N, int K, const float* bias, const void* residual, int ldr,
                                      float res_scale, int act, cudaStream_t st) {
   if (!X || !W || !Y || T <= 0 || N <= 0 || K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8)) return -103;
+  if (ldx < K || ldw < K || ldo < N || (residual && ldr < N)) return -103;
   if (T > kNoallocMaxTokens) return -100;
   const int bn = pick_bn(T);
   const int tiles = ((N + 127) / 128) * ((T + bn - 1) / bn);
@@ -857,9 +865,9 @@ extern "C" int xft_gemm_bf16_noalloc(const void* X, int ldx, const void* W, int 
   unsigned char* base = static_cast<unsigned char*>(g_noalloc_ptr[dev]);
   int* counters = reinterpret_cast<int*>(base);                       // [0, 4096)
   int* status = reinterpret_cast<int*>(base + 4096);                  // [4096, 4352)
-  float* ws = reinterpret_cast<float*>(base + 8192);                  // partial tiles
+  float* ws = reinterpret_cast<float*>(base + kNoallocHeadBytes);     // partial tiles
   // the array keeps whatever the previous call left: counters and status must start at zero
-  cudaError_t e = cudaMemsetAsync(base, 0, 8192, st);
+  cudaError_t e = cudaMemsetAsync(base, 0, kNoallocHeadBytes, st);
   if (e != cudaSuccess) return (int)e;
   return xft_gemm_bf16(X, ldx, W, N, ldw, Y, ldo, out_fp32, T, N, K, /*gated=*/0, /*dual_off=*/0, bias, residual, ldr,
                        res_scale, act, /*row_scale=*/nullptr, ws, kNoallocPartialBytes, counters, kNoallocCounters,

@@ -5,7 +5,9 @@
 //
 // One CTA per row: a 32-step bisection on the order-preserving integer image of the floats finds the k-th largest
 // logit, the candidates (>= threshold) are compacted into shared memory, bitonic-sorted by (value desc, index asc),
-// and thread 0 walks the at most 1024 survivors.
+// and thread 0 walks the at most 1024 survivors.  k is clamped to [1, min(V, 1024)] (the CPU oracle applies the same
+// cap).  Logits equal to the threshold are admitted in index order through a block-wide prefix count, so the kept
+// set — and with it the token every tensor-parallel rank picks — does not depend on thread timing.
 #include "ptx.cuh"
 
 namespace xft {
@@ -29,6 +31,7 @@ __global__ void __launch_bounds__(1024) sample_topk_topp_kernel(const float* __r
   const float* x = logits + (size_t)row * ld;
   if (k > V) k = V;
   if (k > kMaxK) k = kMaxK;
+  if (k < 1) k = 1;
   // largest threshold key with count(key >= thr) >= k
   unsigned thr = 0;
   for (int bit = 31; bit >= 0; --bit) {
@@ -46,15 +49,28 @@ __global__ void __launch_bounds__(1024) sample_topk_topp_kernel(const float* __r
   if (tid == 0) s_cnt = 0;
   for (int i = tid; i < kMaxK; i += 1024) cand[i] = 0ull;
   __syncthreads();
-  // strictly greater first (always fits: fewer than k of them), then ties in index order until the list is full
+  // strictly greater first (always fits: fewer than k of them; their order is settled by the sort below)
   for (int i = tid; i < V; i += 1024) {
     const unsigned key = f2key(x[i]);
     if (key > thr) { const int p = atomicAdd(&s_cnt, 1); if (p < kMaxK) cand[p] = ((unsigned long long)key << 32) | (0xffffffffu - (unsigned)i); }
   }
   __syncthreads();
-  for (int i = tid; i < V; i += 1024) {
-    const unsigned key = f2key(x[i]);
-    if (key == thr) { const int p = atomicAdd(&s_cnt, 1); if (p < kMaxK) cand[p] = ((unsigned long long)key << 32) | (0xffffffffu - (unsigned)i); }
+  // then ties with the threshold, lowest index first, until k candidates are held: chunks of 1024 logits in index
+  // order, a ballot + warp totals give every tie its rank among the ties seen so far
+  int held = min(s_cnt, kMaxK);                       // same value in every thread
+  __syncthreads();
+  for (int i0 = 0; i0 < V && held < k; i0 += 1024) {
+    const int i = i0 + tid;
+    const bool tie = i < V && f2key(x[i]) == thr;
+    const unsigned b = __ballot_sync(0xffffffffu, tie);
+    if ((tid & 31) == 0) s_red[tid >> 5] = __popc(b);
+    __syncthreads();
+    int before = 0, tot = 0;
+    for (int w = 0; w < 32; ++w) { const int c = (int)s_red[w]; if (w < (tid >> 5)) before += c; tot += c; }
+    __syncthreads();
+    const int pos = held + before + __popc(b & ((1u << (tid & 31)) - 1u));
+    if (tie && pos < k) cand[pos] = ((unsigned long long)thr << 32) | (0xffffffffu - (unsigned)i);
+    held += tot;
   }
   __syncthreads();
   // bitonic sort, descending
@@ -70,7 +86,7 @@ __global__ void __launch_bounds__(1024) sample_topk_topp_kernel(const float* __r
     }
   }
   if (tid == 0) {
-    const int n = min(k, min(s_cnt, kMaxK));
+    const int n = max(1, min(k, held));
     auto val = [&](int i) {
       unsigned key = (unsigned)(cand[i] >> 32);
       unsigned u = (key & 0x80000000u) ? (key & 0x7fffffffu) : ~key;

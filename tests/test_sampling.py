@@ -57,6 +57,22 @@ def test_gpu_sampler_matches_reference():
         got = native_sample.sample_top_k_top_p(logits.cuda(), k, p, T, u).cpu()
         # identical except where the draw lands within float error of a CDF boundary
         assert (got == want).float().mean().item() >= 0.85, (k, p, T, got, want)
+    # k outside [1, 1024] is clamped the same way on both sides (0 -> 1, above the candidate capacity -> 1024, V)
+    small = torch.randn(5, 700, generator=g) * 2
+    for k, src in ((0, logits), (-3, logits), (1, logits), (4000, logits), (700, small), (5000, small)):
+        u = torch.rand(src.shape[0], generator=g)
+        want = R.sample_top_k_top_p(src, k, 0.95, 1.0, u)
+        got = native_sample.sample_top_k_top_p(src.cuda(), k, 0.95, 1.0, u).cpu()
+        assert int(got.min()) >= 0 and int(got.max()) < src.shape[1]
+        assert (got == want).float().mean().item() >= 0.8, (k, got, want)
+    # ties: all-equal logits keep the k lowest indices, whatever the thread timing (every rank picks the same token)
+    flat = torch.zeros(4, 5000)
+    u = torch.tensor([0.0, 0.3, 0.6, 0.999])
+    for k in (1, 7, 1024, 3000):
+        got = native_sample.sample_top_k_top_p(flat.cuda(), k, 1.0, 1.0, u).cpu()
+        kk = max(1, min(k, 1024))
+        assert int(got.max()) < kk and got.tolist() == [min(kk - 1, int(x * kk)) for x in u.tolist()], (k, got)
+        assert got.tolist() == native_sample.sample_top_k_top_p(flat.cuda(), k, 1.0, 1.0, u).cpu().tolist()
     l = torch.randn(3, 100)
     toks = [[1, 2, 2, 50], [], [99, 0]]
     want = R.repetition_penalty(l.clone(), toks, 1.7, 0)

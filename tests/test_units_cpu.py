@@ -477,6 +477,35 @@ def test_expert_exchange_addressing_emulated(world, E, k):
             assert torch.allclose(got, want, atol=1e-5)
 
 
+def test_expert_exchange_plan_drops_take_no_slot():
+    """Plan rule of csrc/kernels/ep_comm.cu (ep_plan_kernel) replayed on the CPU for the overflow cases: a pair beyond
+    the return area (index >= pairs_cap) or with a bad expert id is dropped BEFORE a receive slot is taken, so every
+    slot below a destination's published count holds exactly one dispatched pair and the receiver never reads a slot
+    that nothing wrote; a pair that finds its destination's receive area full is dropped too and the count is capped."""
+    E, world, k, cap, pairs_cap = 8, 2, 2, 5, 9
+    g = torch.Generator().manual_seed(3)
+    idx = torch.randint(0, E, (14,), generator=g).tolist()
+    idx[4] = E + 3                                               # a bad expert id
+    s_cnt, dest, slot, status = [0] * world, [], [], 0
+    for i, e in enumerate(idx):
+        d = s = -1
+        if 0 <= e < E and i < pairs_cap:
+            d = P.expert_owner(e, E, world)
+            s = s_cnt[d]
+            s_cnt[d] += 1
+            if s >= cap:
+                status, d = 5, -1
+        else:
+            status = 5
+        dest.append(d)
+        slot.append(s)
+    cnt = [min(c, cap) for c in s_cnt]
+    assert status == 5 and all(d == -1 for d in dest[pairs_cap:]) and dest[4] == -1
+    for d in range(world):
+        filled = sorted(slot[i] for i in range(len(idx)) if dest[i] == d)
+        assert filled == list(range(cnt[d]))                    # no published slot is empty, none is written twice
+
+
 def test_persistent_gemm_barrier_protocol_model():
     """Model check of the persistent prefill kernel's synchronisation (csrc/kernels/gemm_prefill_sm100.cu): three
     actors (TMA producer, MMA issuer, epilogue) over a ring of `stages` shared-memory stages and two TMEM accumulators,

@@ -50,7 +50,7 @@ def test_peer_wait_runs_out_and_reports_through_the_status_word():
     # (epoch 1 selects parity 1: words [parity 1][source 0][i])
     assert int((recv[1][2 * cap:2 * cap + n] >> 32).min()) == 1 and int((recv[0][2 * cap:2 * cap + n] >> 32).min()) == 1
     # the context is usable: an ordinary kernel of the library and a torch op run afterwards
-    w = torch.ones(64, dtype=torch.bfloat16, device=dev)
+    w = torch.ones(64, dtype=torch.float32, device=dev)
     y = N.rmsnorm(torch.ones(4, 64, dtype=torch.bfloat16, device=dev), w, 1e-6)
     assert torch.allclose(y.float(), torch.ones(4, 64, device=dev), atol=1e-2)
     assert float((x + 1).sum()) == 2 * n

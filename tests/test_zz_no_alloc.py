@@ -37,6 +37,13 @@ def _call(lib, x, w, y, bias, res, res_scale, act):
 def test_no_alloc_matches_regular_entry_point_twice(T, N, K):
     from xfastertransformer_b200.ops import native as Nat
     lib = _lib()
+    # both shapes must plan a split-K launch, otherwise the static scratch would never be touched: ask the planner
+    # with the entry point's own scratch size and tile limit
+    bn = 16
+    tiles = (N + 127) // 128
+    splits, per = C.c_int(0), C.c_int(0)
+    lib.xft_plan_splits(tiles, (K + 63) // 64, bn, 1, C.c_size_t(8 << 20), 1024, C.byref(splits), C.byref(per))
+    assert splits.value > 1, "shape no longer exercises the static split-K scratch"
     g = torch.Generator().manual_seed(T + N)
     x = (torch.randn(T, K, generator=g) * 0.5).bfloat16().cuda()
     w = (torch.randn(N, K, generator=g) * 0.05).bfloat16().cuda()
@@ -67,3 +74,16 @@ def test_no_alloc_rejects_sizes_beyond_its_scratch():
     rc = _call(lib, x, w, y, None, None, 1.0, 0)
     assert rc == -100
     assert b"256" in lib.xft_gemm_bf16_noalloc_strerror(rc)
+
+
+def test_no_alloc_rejects_short_leading_dimensions():
+    lib = _lib()
+    x = torch.zeros(4, 64, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda")
+    y = torch.zeros(4, 128, dtype=torch.bfloat16, device="cuda")
+    T, K, N = 4, 64, 128
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p = lambda t: C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+    # ldo < N, then a residual with ldr < N: refused before anything is launched
+    assert lib.xft_gemm_bf16_noalloc(p(x), K, p(w), K, p(y), 64, 0, T, N, K, p(None), p(None), 0, C.c_float(1.0), 0, st) == -103
+    assert lib.xft_gemm_bf16_noalloc(p(x), K, p(w), K, p(y), N, 0, T, N, K, p(None), p(y), 64, C.c_float(1.0), 0, st) == -103

@@ -552,8 +552,9 @@ def repetition_penalty(logits: torch.Tensor, token_lists, penalty: float, vocab_
 def sample_top_k_top_p(logits: torch.Tensor, top_k: int, top_p: float, temperature: float,
                        uniform: torch.Tensor) -> torch.Tensor:
     """top-k -> /T -> top-p prefix (never fewer than 2 kept) -> softmax -> inverse CDF with one
-    uniform draw per row (src/searchers/sample_search.cpp:118-268)."""
-    k = max(1, min(top_k, logits.shape[-1]))
+    uniform draw per row (src/searchers/sample_search.cpp:118-268).  top_k is clamped to [1, min(V, 1024)], the
+    candidate capacity of the device kernel, so both implementations keep the same set."""
+    k = max(1, min(top_k, logits.shape[-1], 1024))
     v, idx = torch.topk(logits.float(), k, dim=-1)
     v = v / max(temperature, 1e-6)
     p = torch.softmax(v, -1)

@@ -53,11 +53,13 @@ class LlamaConvert(BaseModelConvert):
             qz = sd.get(name + ".qzeros").numpy().astype(np.uint32)
             z = ((qz[:, :, None] >> (np.arange(pack, dtype=np.uint32) * bits)[None, None, :]) & ((1 << bits) - 1)).reshape(-1)
             s = sd.get(name + ".scales").float().numpy().reshape(-1)
+            # AutoGPTQ stores zero - 1: add the 1 back modulo 2^bits (a true zero point of 0 is stored as all ones)
+            z = (z + 1) & ((1 << bits) - 1)
             if bits == 8:
                 qi = (q.astype(np.int32) - 128).astype(np.int8)
-                zeros = -s * (z.astype(np.float32) + 1 - 128)
+                zeros = -s * (z.astype(np.float32) - 128)
                 return qi, s, zeros
-            return q.astype(np.uint8), s, -s * (z.astype(np.float32) + 1)
+            return q.astype(np.uint8), s, -s * z.astype(np.float32)
 
         def put(name, parts):
             qs, ss, zs = zip(*parts)
