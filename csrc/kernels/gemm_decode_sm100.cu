@@ -1,0 +1,706 @@
+// Decode-size bf16 GEMM for sm_100a (at most 64 tokens):  Y[T, N] = epilogue( X[T, K] · W[N, K]^T ), written as a
+// balanced weight stream with the layer's neighbouring work fused into its two ends.
+//
+// The reference runs a decoder layer's linears as separate xDNN/oneDNN calls with a norm in front, a RoPE + cache
+// copy behind the QKV product and an all-reduce behind o_proj / down_proj (src/layers/attention.h, mlp_llama.h,
+// decoder_block.h:122-134, src/utils/matmul_helper.h:565-1705).  At decode sizes every one of these products is a pure
+// weight stream, so what matters is (a) that all SMs pull the same number of bytes and (b) how few dependent kernels a
+// layer needs.  This kernel therefore differs from the tile-per-CTA GEMM of gemm_sm100.cu in three ways:
+//
+//   * Work is cut into units of one 128-feature x 64-deep weight block.  The units, in (tile, k-block) order, are
+//     dealt to one CTA per SM in equal contiguous runs, whatever the shape ("stream-K"): a CTA's run may end in the
+//     middle of one output tile and begin in the middle of another.  Runs that cover a whole tile finish it from TMEM;
+//     the others leave an fp32 partial in scratch and the CTA that arrives last on the tile's counter adds the
+//     partials in CTA order (deterministic) and finishes the tile.  Nobody waits for another CTA.
+//   * Two TMEM accumulators: the epilogue warps drain run i while the MMA warp already accumulates run i + 1.
+//     A CTA uses about half an SM's shared memory, so the CTAs of the next kernel in the stream (programmatic
+//     dependent launch) can become resident and request their first weight blocks while this one drains.
+//   * Fused ends.  Front: RMSNorm folded in (the gain lives in W's columns, 1/rms is computed beside the main loop).
+//     Back, one of: bias / activation / act(gate) * up / residual; split + RoPE + paged KV-cache append of a QKV
+//     product (one 128-feature tile = one head); or the tensor-parallel all-reduce over peer memory.
+//
+// All-reduce form.  The CTA that finishes a tile pushes it, as 8-byte words {two bf16 values, epoch}, into the receive
+// areas of the other ranks (one-shot: every rank; two-shot: the rank that owns that range of the output).  The sum
+// itself is not done by that CTA: once a CTA has run out of GEMM work, its four epilogue warps take an equal share of
+// the WHOLE output, poll the world's words for it (all loads of a 16-byte unit in flight at once, bounded), add them in
+// rank order — bit-identical on every rank — apply bias / residual and store.  In the two-shot form the owners also
+// hand the finished words to every other rank, and all CTAs copy out the ranges they do not own.  No fence, flag or
+// barrier separates a store from the load that consumes it, and the reduction runs on every SM instead of in the
+// few CTAs that happened to finish a tile.
+#include "gemm_common.cuh"
+
+#include <cstdlib>
+
+namespace xft {
+
+constexpr int kSkMaxStages = 12;
+
+// split + RoPE + cache append as the epilogue of a QKV product (head_dim 128, bf16 cache)
+struct SkQkv {
+  __nv_bfloat16* q_out;      // [T, hq, 128]; null = mode off
+  int hq, hkv;
+  const int* positions;      // [T]
+  const float* table;        // [max_pos, rot] = cos(rot/2) ‖ sin(rot/2), or null (no rotation)
+  int rot, style, rot_off, max_pos;   // style 0: pairs (i, i + rot/2); 1: pairs (2i, 2i + 1)
+  const float* q_scale;      // optional per-token factor on q
+  __nv_bfloat16* kc;         // [nb, hkv, bs, 128]
+  __nv_bfloat16* vc;
+  int bs;
+  long long nslots;
+  const int* slots;          // [T] flat slot = block * bs + offset
+};
+
+struct SkParams {
+  int N, T, K;
+  int dual_off;              // DUAL: W row of the first "up" feature
+  void* out; int ldo; int out_fp32;
+  const float* bias;
+  const __nv_bfloat16* residual; int ldr; float res_scale;
+  int act;
+  int n_tiles, num_kb, stages;
+  long long units;           // n_tiles * num_kb
+  float* ws;                 // partial tiles [2 * gridDim.x][BN * NACC][128]
+  float* rms_ws;             // partial sums of squares [2 * gridDim.x][BN]
+  int* counters;             // one per output tile, zero between launches
+  int* status;
+  const float* row_scale;    // optional per-feature factor on the accumulator
+  const __nv_bfloat16* rms_x; int rms_ldx; float rms_eps;     // folded RMSNorm (see gemm_sm100.cu)
+  CommParams ar;             // ar.world > 1: all-reduce form
+  SkQkv qkv;
+};
+
+// CTA that holds unit u when `units` units are dealt to `G` CTAs as [i * units / G, (i + 1) * units / G)
+__host__ __device__ __forceinline__ int sk_cta_of(long long u, long long units, int G) {
+  return (int)(((u + 1) * G + units - 1) / units) - 1;
+}
+__host__ __device__ __forceinline__ long long sk_first_unit(int cta, long long units, int G) {
+  return (long long)cta * units / G;
+}
+
+// two 8-byte transport words with one 16-byte load
+__device__ __forceinline__ void ld_volatile_2w(const unsigned long long* p, unsigned long long& a, unsigned long long& b) {
+  asm volatile("ld.volatile.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+__device__ __forceinline__ void st_2w(unsigned long long* p, unsigned long long a, unsigned long long b) {
+  asm volatile("st.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
+}
+
+template <int BN, bool DUAL>
+__global__ void __launch_bounds__(192, 1) gemm_sk_kernel(const __grid_constant__ CUtensorMap tmW,
+                                                         const __grid_constant__ CUtensorMap tmX, const SkParams p) {
+  constexpr int A_BYTES = 128 * 64 * 2;
+  constexpr int B_BYTES = BN * 64 * 2;
+  constexpr int NACC = DUAL ? 2 : 1;
+  constexpr int STAGE_BYTES = A_BYTES * NACC + B_BYTES;
+  constexpr int ACC_COLS = BN * NACC;
+  constexpr uint32_t TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;
+  constexpr uint32_t IDESC = umma_idesc(128, BN, 1, 1, 1);
+  static_assert(BN == 16 || BN == 32 || BN == 64, "token tile of the decode kernel");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t full_bar[kSkMaxStages], empty_bar[kSkMaxStages], tmem_full[2], tmem_empty[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int s_last, s_epoch, s_fail;
+  __shared__ float s_ssq[BN];
+  constexpr int kHeadLd = 128 + 2;                        // bf16 elements per staged token row (odd word count)
+  __shared__ __nv_bfloat16 s_head[DUAL ? 1 : BN * kHeadLd];   // QKV mode: one head of every token
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int stages = p.stages;
+  const int G = gridDim.x, bid = blockIdx.x;
+  const long long u0 = sk_first_unit(bid, p.units, G), u1 = sk_first_unit(bid + 1, p.units, G);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 4);                        // one arrival per epilogue warp
+    }
+    s_fail = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_s, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+  grid_dep_launch();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      // a weight byte is read once: stream it past L2; the token tile is re-read by every CTA: keep it
+      const uint64_t hint_w = kEvictFirst, hint_x = kEvictLast;
+      const int n_units = (int)(u1 - u0);
+      const int pre = min(stages, n_units);
+      int tile = (int)(u0 / p.num_kb), kb = (int)(u0 % p.num_kb);
+      const int tile0 = tile, kb0 = kb;
+      // weights never depend on the previous kernel: the first blocks are requested before the grid dependency
+      // resolves, so the stream from HBM starts while the predecessor drains
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+        uint8_t* a = smem + i * STAGE_BYTES;
+        tma_load_2d(a, &tmW, &full_bar[i], kb * 64, tile * 128, hint_w);
+        if (DUAL) tma_load_2d(a + A_BYTES, &tmW, &full_bar[i], kb * 64, p.dual_off + tile * 128, hint_w);
+        if (++kb == p.num_kb) { kb = 0; ++tile; }
+      }
+      grid_dep_wait();
+      {
+        int kb2 = kb0, tile2 = tile0;
+        for (int i = 0; i < pre; ++i) {
+          tma_load_2d(smem + i * STAGE_BYTES + A_BYTES * NACC, &tmX, &full_bar[i], kb2 * 64, 0, hint_x);
+          if (++kb2 == p.num_kb) { kb2 = 0; ++tile2; }
+        }
+      }
+      for (int it = pre; it < n_units; ++it) {
+        const int s = it % stages;
+        const uint32_t ph = (it / stages) & 1;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1, p.status, XFT_ERR_WAIT_EMPTY)) break;
+        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        uint8_t* a = smem + s * STAGE_BYTES;
+        tma_load_2d(a, &tmW, &full_bar[s], kb * 64, tile * 128, hint_w);
+        if (DUAL) tma_load_2d(a + A_BYTES, &tmW, &full_bar[s], kb * 64, p.dual_off + tile * 128, hint_w);
+        tma_load_2d(a + A_BYTES * NACC, &tmX, &full_bar[s], kb * 64, 0, hint_x);
+        if (++kb == p.num_kb) { kb = 0; ++tile; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int it = 0, seg = 0;
+      bool ok = true;
+      for (long long u = u0; u < u1 && ok; ++seg) {
+        const int kb_begin = (int)(u % p.num_kb);
+        const int kb_end = (int)min((long long)p.num_kb, kb_begin + (u1 - u));
+        const int a = seg & 1;
+        const uint32_t aph = (seg >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[a], aph ^ 1, p.status, XFT_ERR_WAIT_TMEM)) break;
+        tcgen05_fence_after();
+        const uint32_t acc = tmem_base + (uint32_t)(a * ACC_COLS);
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+          const int s = it % stages;
+          const uint32_t ph = (it / stages) & 1;
+          if (!mbar_wait(&full_bar[s], ph, p.status, XFT_ERR_WAIT_FULL)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+          const uint64_t adesc = umma_desc_k128(a_addr);
+          const uint64_t bdesc = umma_desc_k128(a_addr + A_BYTES * NACC);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {          // 4 x (K = 16) per 64-wide k-block; +32 B = +2 in the address field
+            umma_bf16(acc, adesc + 2 * k, bdesc + 2 * k, IDESC, (kb > kb_begin || k > 0) ? 1u : 0u);
+            if (DUAL) {
+              const uint64_t a1desc = umma_desc_k128(a_addr + A_BYTES);
+              umma_bf16(acc + BN, a1desc + 2 * k, bdesc + 2 * k, IDESC, (kb > kb_begin || k > 0) ? 1u : 0u);
+            }
+          }
+          tcgen05_commit(&empty_bar[s]);
+        }
+        if (ok) tcgen05_commit(&tmem_full[a]);
+        u += kb_end - kb_begin;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue: 4 warps, one TMEM lane per thread
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const int et = threadIdx.x - 64;                      // 0..127 among the epilogue threads
+    const bool fused_ar = (!DUAL) && p.ar.world > 1;
+    const bool qkv_mode = (!DUAL) && p.qkv.q_out != nullptr;
+    const bool rms = p.rms_x != nullptr;
+    grid_dep_wait();              // scratch, residual, tokens and outputs belong to the stream order from here on
+    if (fused_ar && et == 0) s_epoch = *reinterpret_cast<volatile int*>(p.ar.epoch) + 1;
+    if (fused_ar) named_bar_sync(1, 128);
+    const int epoch = fused_ar ? s_epoch : 0;
+    const int par = epoch & 1;
+    const long long E2 = (long long)((p.T + 1) >> 1) * (p.N >> 1);   // 16-byte units of the all-reduce (N is even)
+    bool ssq_full = false;                                  // s_ssq holds the sums over the whole K
+    bool alive = true;
+
+    int seg = 0;
+    for (long long u = u0; u < u1 && alive; ++seg) {
+      const int tile = (int)(u / p.num_kb);
+      const int kb_begin = (int)(u % p.num_kb);
+      const int kb_end = (int)min((long long)p.num_kb, kb_begin + (u1 - u));
+      u += kb_end - kb_begin;
+      const bool complete = kb_begin == 0 && kb_end == p.num_kb;
+      const int a = seg & 1;
+      const uint32_t aph = (seg >> 1) & 1;
+      const int n = tile * 128 + row;
+      const bool n_ok = n < p.N;
+
+      if (rms && !(complete && ssq_full)) {
+        // sum of squares over this run's K range for each token: 128 / BN threads per token, 16-byte loads
+        constexpr int TPT = 128 / BN;
+        const int tok = et / TPT, sub = et % TPT;
+        const int k_begin = kb_begin * 64, k_end = min(kb_end * 64, p.K);
+        float acc = 0.f;
+        if (tok < p.T) {
+          const __nv_bfloat16* xr = p.rms_x + (size_t)tok * p.rms_ldx;
+#pragma unroll 4
+          for (int k = k_begin + sub * 8; k < k_end; k += TPT * 8) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(xr + k));
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 f = __bfloat1622float2(h[i]);
+              acc += f.x * f.x + f.y * f.y;
+            }
+          }
+        }
+#pragma unroll
+        for (int o = TPT / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        named_bar_sync(1, 128);                             // the previous run's readers of s_ssq are done
+        if (sub == 0) s_ssq[tok] = acc;
+        named_bar_sync(1, 128);
+        ssq_full = complete;
+      }
+
+      const bool got = mbar_wait(&tmem_full[a], aph, p.status, XFT_ERR_WAIT_TMEM);
+      // one answer for all 128 threads, so nobody is left alone in front of a later barrier
+      if (named_bar_or(1, 128, !got)) { alive = false; break; }
+      tcgen05_fence_after();
+      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + (uint32_t)(a * ACC_COLS);
+
+      bool last = true;
+      int c_lo = bid, c_hi = bid;
+      if (!complete) {
+        // publish this run's partial tile, then see whether it was the last one of the tile
+        const int slot = 2 * bid + (seg == 0 ? 0 : 1);
+        float* wsp = p.ws + (size_t)slot * (ACC_COLS * 128);
+#pragma unroll 1
+        for (int c = 0; c < ACC_COLS; c += 16) {
+          uint32_t v[16];
+          tmem_ld16(taddr + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) wsp[(size_t)(c + j) * 128 + row] = __uint_as_float(v[j]);
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[a]);
+        if (rms && et < BN) p.rms_ws[(size_t)slot * BN + et] = s_ssq[et];
+        c_lo = sk_cta_of((long long)tile * p.num_kb, p.units, G);
+        c_hi = sk_cta_of((long long)(tile + 1) * p.num_kb - 1, p.units, G);
+        __threadfence();
+        named_bar_sync(1, 128);
+        if (et == 0) {
+          const int old = atomicAdd(&p.counters[tile], 1);
+          s_last = (old == c_hi - c_lo);
+          if (s_last) p.counters[tile] = 0;                 // ready for the next launch
+        }
+        named_bar_sync(1, 128);
+        last = s_last != 0;
+        if (last) {
+          __threadfence();
+          if (rms) {
+            if (et < BN) {
+              float acc = 0.f;
+              for (int cta = c_lo; cta <= c_hi; ++cta) {
+                const int sl = 2 * cta + ((int)(sk_first_unit(cta, p.units, G) / p.num_kb) == tile ? 0 : 1);
+                acc += __ldcg(p.rms_ws + (size_t)sl * BN + et);
+              }
+              s_ssq[et] = acc;
+            }
+            named_bar_sync(1, 128);
+            ssq_full = false;
+          }
+        }
+      }
+      if (!last) continue;
+
+      // ---------------- finish the tile: accumulator columns [c, c + 16) from TMEM or from the partials ----------
+      const float rs = (p.row_scale && n_ok) ? p.row_scale[n] : 1.f;
+      const float bias_g = (p.bias && n_ok) ? p.bias[n] : 0.f;
+      const float bias_u = (DUAL && p.bias && n_ok) ? p.bias[p.dual_off + n] : 0.f;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        float g[16], uu[DUAL ? 16 : 1];
+        if (complete) {
+          uint32_t v[16];
+          tmem_ld16(taddr + c, v);
+          if constexpr (DUAL) {
+            uint32_t v2[16];
+            tmem_ld16(taddr + BN + c, v2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) uu[j] = __uint_as_float(v2[j]);
+          } else {
+            tmem_ld_wait();
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) g[j] = __uint_as_float(v[j]);
+          if (c + 16 >= BN) {
+            // the accumulator is in registers: hand the TMEM buffer back to the MMA warp before the stores
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[a]);
+          }
+        } else {
+          // sum of the runs that share this tile, in CTA order; four runs' loads are in flight together
+#pragma unroll
+          for (int j = 0; j < 16; ++j) { g[j] = 0.f; if (DUAL) uu[j] = 0.f; }
+          for (int cta = c_lo; cta <= c_hi; cta += 4) {
+            float pv[4][16], pu[DUAL ? 4 : 1][DUAL ? 16 : 1];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int cc = cta + i;
+              if (cc <= c_hi) {
+                const int sl = 2 * cc + ((int)(sk_first_unit(cc, p.units, G) / p.num_kb) == tile ? 0 : 1);
+                const float* w = p.ws + (size_t)sl * (ACC_COLS * 128) + row;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  pv[i][j] = __ldcg(w + (size_t)(c + j) * 128);
+                  if constexpr (DUAL) pu[i][j] = __ldcg(w + (size_t)(BN + c + j) * 128);
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) { pv[i][j] = 0.f; if constexpr (DUAL) pu[i][j] = 0.f; }
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+              for (int j = 0; j < 16; ++j) { g[j] += pv[i][j]; if constexpr (DUAL) uu[j] += pu[i][j]; }
+          }
+        }
+
+        if (fused_ar) {
+          // push the partial sums of this rank, two tokens per word, to the ranks that reduce them
+          if (n_ok) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 2) {
+              const int t = c + j;
+              if (t < p.T) {
+                const unsigned long long w = ((unsigned long long)(unsigned)epoch << 32) | ll_pack2(g[j] * rs, g[j + 1] * rs);
+                const long long wi = (long long)(t >> 1) * p.N + n;
+                const long long off = par * p.ar.parity_stride + p.ar.rank * p.ar.slot_stride + wi;
+                if (p.ar.two_shot) {
+                  const int owner = (int)(((wi >> 1) * p.ar.world) / E2);
+                  p.ar.recv[owner][off] = w;
+                } else {
+                  for (int r = 0; r < p.ar.world; ++r) p.ar.recv[r][off] = w;
+                }
+              }
+            }
+          }
+          continue;
+        }
+        if (qkv_mode) {
+          // stage the head (bias added, rounded to bf16 as a separate product would store it); rotated below
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float ts = rms ? rsqrtf(s_ssq[(c + j) % BN] / (float)p.K + p.rms_eps) : 1.f;
+            s_head[(c + j) * kHeadLd + row] = __float2bfloat16(g[j] * (rs * ts) + bias_g);
+          }
+          continue;
+        }
+        if (n_ok) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int t = c + j;
+            if (t < p.T) {
+              const float ts = rms ? rsqrtf(s_ssq[(c + j) % BN] / (float)p.K + p.rms_eps) : 1.f;
+              float x = apply_act(g[j] * (rs * ts) + bias_g, p.act);
+              if constexpr (DUAL) x *= (uu[j] * (rs * ts) + bias_u);
+              if (p.residual) x += p.res_scale * __bfloat162float(p.residual[(size_t)t * p.ldr + n]);
+              if (p.out_fp32) reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + n] = x;
+              else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)t * p.ldo + n] = __float2bfloat16(x);
+            }
+          }
+        }
+      }
+      if (qkv_mode) {
+        // tile = one head of q, k or v for every token: rotate and hand it to the attention kernel's inputs
+        if constexpr (!DUAL) {
+          named_bar_sync(1, 128);
+          const SkQkv& qp = p.qkv;
+          const int h = tile;
+          const bool is_q = h < qp.hq, is_k = !is_q && h < qp.hq + qp.hkv;
+          const int d = row;
+          const int half = qp.rot >> 1;
+          const int rd = d - qp.rot_off;                     // index inside the rotary range
+          const bool rotate = (is_q || is_k) && qp.table != nullptr && qp.rot > 0 && rd >= 0 && rd < qp.rot;
+          int pi = 0, partner = d;
+          float sign = 0.f;
+          if (rotate) {
+            if (qp.style == 0) { pi = rd < half ? rd : rd - half; partner = rd < half ? d + half : d - half; sign = rd < half ? -1.f : 1.f; }
+            else { pi = rd >> 1; partner = d ^ 1; sign = (rd & 1) ? 1.f : -1.f; }
+          }
+          for (int t = 0; t < p.T; ++t) {
+            float x = __bfloat162float(s_head[t * kHeadLd + d]);
+            if (rotate) {
+              int pos = qp.positions[t];
+              if (pos < 0 || pos >= qp.max_pos) { if (p.status) atomicCAS(p.status, 0, XFT_ERR_BOUNDS); pos = 0; }
+              const float* cs = qp.table + (size_t)pos * qp.rot;
+              const float y = __bfloat162float(s_head[t * kHeadLd + partner]);
+              x = x * cs[pi] + sign * y * cs[half + pi];
+            }
+            if (is_q) {
+              if (qp.q_scale) x *= qp.q_scale[t];
+              qp.q_out[((size_t)t * qp.hq + h) * 128 + d] = __float2bfloat16(x);
+            } else {
+              const int kh = is_k ? h - qp.hq : h - qp.hq - qp.hkv;
+              const long long slot = qp.slots[t];
+              if (slot < 0 || slot >= qp.nslots) { if (p.status) atomicCAS(p.status, 0, XFT_ERR_BOUNDS); continue; }
+              const long long blk = slot / qp.bs, off = slot % qp.bs;
+              __nv_bfloat16* dst = (is_k ? qp.kc : qp.vc) + ((size_t)(blk * qp.hkv + kh) * qp.bs + off) * 128;
+              dst[d] = __float2bfloat16(x);
+            }
+          }
+          named_bar_sync(1, 128);                            // s_head is reused by the next tile
+        }
+      }
+    }
+
+    // ------------------------------------------------------------------ all-reduce: every CTA reduces its share
+    if (fused_ar && alive) {
+      const int world = p.ar.world, rank = p.ar.rank;
+      const unsigned long long* my_recv = p.ar.recv[rank] + par * p.ar.parity_stride;
+      const int halfN = p.N >> 1;
+      bool peers_ok = true;
+      // finished values of unit i2 (features n, n + 1 of tokens t, t + 1) -> output, from the sum `f`
+      auto store_unit = [&](long long i2, const float (&f)[4]) {
+        const int tp = (int)(i2 / halfN), n = (int)(i2 % halfN) * 2;
+        const int t = 2 * tp;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          if (t + k < p.T) {
+            if (p.out_fp32) {
+              float* o = reinterpret_cast<float*>(p.out) + (size_t)(t + k) * p.ldo + n;
+              o[0] = f[k]; o[1] = f[2 + k];
+            } else {
+              *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)(t + k) * p.ldo + n) =
+                  __floats2bfloat162_rn(f[k], f[2 + k]);
+            }
+          }
+        }
+      };
+      // owned range of this rank (one-shot: everything), then this CTA's share of it
+      long long r0 = 0, r1 = E2;
+      if (p.ar.two_shot) {
+        r0 = ((long long)rank * E2 + world - 1) / world;
+        r1 = ((long long)(rank + 1) * E2 + world - 1) / world;
+      }
+      const long long a0 = r0 + (r1 - r0) * bid / G, a1 = r0 + (r1 - r0) * (bid + 1) / G;
+      for (long long i2 = a0 + et; i2 < a1 && peers_ok; i2 += 128) {
+        unsigned long long w[8][2];
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          if (r < world) ld_volatile_2w(my_recv + r * p.ar.slot_stride + 2 * i2, w[r][0], w[r][1]);
+        float f[4] = {0.f, 0.f, 0.f, 0.f};                   // (n, t), (n, t + 1), (n + 1, t), (n + 1, t + 1)
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          if (r < world) {
+            if ((int)(w[r][0] >> 32) != epoch || (int)(w[r][1] >> 32) != epoch) {
+              const long long tstart = clock64();
+              do {
+                if (clock64() - tstart > p.ar.wait_cycles) { peers_ok = false; break; }
+                ld_volatile_2w(my_recv + r * p.ar.slot_stride + 2 * i2, w[r][0], w[r][1]);
+              } while ((int)(w[r][0] >> 32) != epoch || (int)(w[r][1] >> 32) != epoch);
+            }
+            float lo, hi;
+            ll_unpack2((unsigned)w[r][0], lo, hi); f[0] += lo; f[1] += hi;
+            ll_unpack2((unsigned)w[r][1], lo, hi); f[2] += lo; f[3] += hi;
+          }
+        }
+        if (!peers_ok) break;
+        const int tp = (int)(i2 / halfN), n = (int)(i2 % halfN) * 2;
+        const int t = 2 * tp;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int nn = n + (k >> 1), tt = t + (k & 1);
+          float x = f[k] + (p.bias ? p.bias[nn] : 0.f);
+          x = apply_act(x, p.act);
+          if (p.residual && tt < p.T) x += p.res_scale * __bfloat162float(p.residual[(size_t)tt * p.ldr + nn]);
+          f[k] = x;
+        }
+        if (p.ar.two_shot) {
+          // all-gather half: the owner hands the finished values to every other rank, rounded as they are stored
+          const unsigned long long w0 = ((unsigned long long)(unsigned)epoch << 32) | ll_pack2(f[0], f[1]);
+          const unsigned long long w1 = ((unsigned long long)(unsigned)epoch << 32) | ll_pack2(f[2], f[3]);
+          for (int r = 0; r < world; ++r)
+            if (r != rank) st_2w(p.ar.result[r] + par * p.ar.slot_stride + 2 * i2, w0, w1);
+        }
+        store_unit(i2, f);
+      }
+      if (p.ar.two_shot && peers_ok) {
+        // copy out the ranges the other ranks own as their finished words arrive
+        const unsigned long long* res = p.ar.result[rank] + par * p.ar.slot_stride;
+        const long long b0 = E2 * bid / G, b1 = E2 * (bid + 1) / G;
+        for (long long i2 = b0 + et; i2 < b1 && peers_ok; i2 += 128) {
+          if (i2 >= r0 && i2 < r1) continue;
+          unsigned long long w0, w1;
+          ld_volatile_2w(res + 2 * i2, w0, w1);
+          if ((int)(w0 >> 32) != epoch || (int)(w1 >> 32) != epoch) {
+            const long long tstart = clock64();
+            do {
+              if (clock64() - tstart > p.ar.wait_cycles) { peers_ok = false; break; }
+              ld_volatile_2w(res + 2 * i2, w0, w1);
+            } while ((int)(w0 >> 32) != epoch || (int)(w1 >> 32) != epoch);
+          }
+          if (!peers_ok) break;
+          float f[4];
+          ll_unpack2((unsigned)w0, f[0], f[1]);
+          ll_unpack2((unsigned)w1, f[2], f[3]);
+          store_unit(i2, f);
+        }
+      }
+      if (!peers_ok && p.status) atomicCAS(p.status, 0, XFT_ERR_WAIT_PEER);
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (p.ar.world > 1 && threadIdx.x == 0) {
+    grid_dep_wait();
+    // last CTA of the launch: the next launch uses the next epoch (and the other buffer parity)
+    if (atomicAdd(p.ar.done, 1) == (int)gridDim.x - 1) {
+      *reinterpret_cast<volatile int*>(p.ar.done) = 0;
+      __threadfence();
+      atomicAdd(p.ar.epoch, 1);
+    }
+  }
+}
+
+// pipeline depth and shared memory of one CTA: about half an SM when that still gives three stages
+static void sk_smem_plan(int bn, int nacc, int* stages, size_t* smem) {
+  const int stage_bytes = 128 * 64 * 2 * nacc + bn * 64 * 2;
+  int budget = 106 * 1024;
+  if (budget / stage_bytes < 3) budget = 200 * 1024;
+  int s = budget / stage_bytes;
+  if (s > kSkMaxStages) s = kSkMaxStages;
+  if (s < 2) s = 2;
+  *stages = s;
+  *smem = (size_t)s * stage_bytes + 1024;
+}
+
+template <int BN, bool DUAL>
+static int launch_sk(const CUtensorMap& tmW, const CUtensorMap& tmX, SkParams& p, int grid, cudaStream_t st) {
+  size_t smem;
+  sk_smem_plan(BN, DUAL ? 2 : 1, &p.stages, &smem);
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_sk_kernel<BN, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return 3000 + (int)cudaGetLastError();
+    attr_set = true;
+  }
+  cudaError_t e = launch_pdl(gemm_sk_kernel<BN, DUAL>, dim3(grid), dim3(192), smem, st, tmW, tmX, p);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}
+
+static int sk_num_sms() {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        sms <= 0)
+      sms = 148;
+  }
+  return sms;
+}
+
+}  // namespace xft
+
+using namespace xft;
+
+// CTAs of a launch: one per SM, fewer when that would leave a CTA less than two weight blocks.  XFT_SK_CTAS overrides
+// the upper bound (tuning).
+extern "C" int xft_gemm_sk_grid(int N, int K) {
+  static const int env_ctas = [] { const char* v = getenv("XFT_SK_CTAS"); return v ? atoi(v) : 0; }();
+  const long long units = (long long)((N + 127) / 128) * ((K + 63) / 64);
+  long long g = env_ctas > 0 ? env_ctas : sk_num_sms();
+  if (g > units / 2) g = units / 2;
+  if (g < 1) g = 1;
+  return (int)g;
+}
+
+// Scratch a launch needs: bytes of partial tiles + sums of squares, and tile counters.
+extern "C" void xft_gemm_sk_scratch(int T, int N, int K, int gated, size_t* ws_bytes, int* n_counters) {
+  const int bn = pick_bn(T), nacc = gated ? 2 : 1;
+  const int g = xft_gemm_sk_grid(N, K);
+  *ws_bytes = (size_t)2 * g * bn * nacc * 128 * sizeof(float) + (size_t)2 * g * bn * sizeof(float);
+  *n_counters = (N + 127) / 128;
+}
+
+// Y[T, N] = epi(X[T, K] W[N, K]^T) for T <= 64.  gated: W holds gate rows [0, N) and up rows [dual_off, dual_off + N),
+// Y = act(gate) * up.  rms_eps != null: X is the un-normalised hidden state and W carries the norm's gain.
+// comm != null: row-parallel product, summed over the ranks (see the file comment); qkv != null: the output goes
+// through RoPE into q_out and the paged cache instead of Y (N = (hq + 2 hkv) * 128).
+// Returns 0, a negative argument error (-21 shape, -22 scratch too small, -23 all-reduce capacity), or a CUDA error.
+extern "C" int xft_gemm_sk(const void* X, int ldx, const void* W, int w_rows, int ldw, void* Y, int ldo, int out_fp32,
+                           int T, int N, int K, int gated, int dual_off, const float* bias, const void* residual, int ldr,
+                           float res_scale, int act, const float* row_scale, const float* rms_eps, float* ws,
+                           size_t ws_bytes, int* counters, int n_counters, int* status, const CommParams* comm,
+                           const SkQkv* qkv, cudaStream_t st) {
+  if (T <= 0 || N <= 0 || K <= 0) return 0;
+  if (T > 64 || (K & 7) || (ldx & 7) || (ldw & 7)) return -21;
+  if (comm && (gated || rms_eps || qkv || (N & 1))) return -21;
+  if (qkv && (gated || N != (qkv->hq + 2 * qkv->hkv) * 128 || act != 0 || residual)) return -21;
+  SkParams p{};
+  p.N = N; p.T = T; p.K = K; p.dual_off = dual_off; p.out = Y; p.ldo = ldo; p.out_fp32 = out_fp32;
+  p.bias = bias; p.residual = reinterpret_cast<const __nv_bfloat16*>(residual); p.ldr = ldr; p.res_scale = res_scale;
+  p.act = act; p.row_scale = row_scale; p.counters = counters; p.status = status;
+  const int bn = pick_bn(T), nacc = gated ? 2 : 1;
+  p.n_tiles = (N + 127) / 128;
+  p.num_kb = (K + 63) / 64;
+  p.units = (long long)p.n_tiles * p.num_kb;
+  const int grid = xft_gemm_sk_grid(N, K);
+  const size_t part_bytes = (size_t)2 * grid * bn * nacc * 128 * sizeof(float);
+  const size_t rms_bytes = (size_t)2 * grid * bn * sizeof(float);
+  if (!ws || !counters || ws_bytes < part_bytes + rms_bytes || n_counters < p.n_tiles) return -22;
+  p.ws = ws;
+  p.rms_ws = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + part_bytes);
+  if (rms_eps) {
+    p.rms_x = reinterpret_cast<const __nv_bfloat16*>(X);
+    p.rms_ldx = ldx;
+    p.rms_eps = *rms_eps;
+  }
+  if (comm) {
+    if (comm->world < 2 || comm->world > 8) return -23;
+    if ((long long)((T + 1) / 2) * N > comm->slot_stride) return -23;
+    p.ar = *comm;
+  }
+  if (qkv) p.qkv = *qkv;
+  CUtensorMap tmW, tmX;
+  int r = make_tensor_map(&tmW, W, (uint64_t)w_rows, (uint64_t)K, (uint64_t)ldw, 128, 2);
+  if (r) return 1000 - r;
+  r = make_tensor_map(&tmX, X, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, (uint32_t)bn, 2);
+  if (r) return 2000 - r;
+#define XFT_LAUNCH(BN_) \
+  case BN_: return gated ? launch_sk<BN_, true>(tmW, tmX, p, grid, st) : launch_sk<BN_, false>(tmW, tmX, p, grid, st);
+  switch (bn) {
+    XFT_LAUNCH(16)
+    XFT_LAUNCH(32)
+    XFT_LAUNCH(64)
+  }
+#undef XFT_LAUNCH
+  return -21;
+}
+
+// The work decomposition on its own (host arithmetic only), for tests: CTA that holds unit u, first unit of a CTA.
+extern "C" int xft_sk_cta_of(long long u, long long units, int G) { return xft::sk_cta_of(u, units, G); }
+extern "C" long long xft_sk_first_unit(int cta, long long units, int G) { return xft::sk_first_unit(cta, units, G); }
+
+// Size and field offsets of SkQkv, for the layout check of the Python mirror.
+extern "C" int xft_sk_qkv_layout(long long* out, int n) {
+  const long long v[] = {sizeof(SkQkv),           offsetof(SkQkv, q_out),   offsetof(SkQkv, hq),       offsetof(SkQkv, hkv),
+                         offsetof(SkQkv, positions), offsetof(SkQkv, table), offsetof(SkQkv, rot),      offsetof(SkQkv, style),
+                         offsetof(SkQkv, rot_off), offsetof(SkQkv, max_pos), offsetof(SkQkv, q_scale),  offsetof(SkQkv, kc),
+                         offsetof(SkQkv, vc),      offsetof(SkQkv, bs),      offsetof(SkQkv, nslots),   offsetof(SkQkv, slots)};
+  const int m = (int)(sizeof(v) / sizeof(v[0]));
+  for (int i = 0; i < m && i < n; ++i) out[i] = v[i];
+  return m;
+}

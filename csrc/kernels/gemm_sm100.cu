@@ -20,8 +20,8 @@
 // tile, each reducing a K range.  Partials go to an fp32 scratch in accumulator layout
 // [split][tile][column][128 rows]; the CTA that arrives last on the tile's counter sums the splits
 // in index order (deterministic) and runs the epilogue.  Nobody spins: there is no wait on a peer.
+#include "gemm_common.cuh"
 #include "gemm_noalloc.h"
-#include "ptx.cuh"
 
 #include <cmath>
 #include <mutex>
@@ -30,31 +30,6 @@
 namespace xft {
 
 int g_xft_pdl = 1;
-
-// Fused one-shot all-reduce (row-parallel o_proj / down_proj at decode sizes): replaces the reference's
-// GEMM followed by Messenger::reduceAdd (src/layers/decoder_block.h:122-134).  `recv[r]` is rank r's
-// receive area [2 parities][world slots][slot words] as mapped into this process (CUDA IPC over NVLink);
-// each word is {two bf16 values (tokens t, t + 1 of one feature), epoch}.  The CTA that finishes an output tile stores its partial tile into
-// slot `rank` of every rank straight from the accumulator, then reads the world slots of its own area,
-// spinning (bounded) on each word until its epoch matches, and sums them in rank order, so all ranks
-// produce bit-identical results.  No fence, flag or barrier separates a producer's store from the
-// consumer's load.  The epoch is a device-side counter bumped by the last CTA of each launch, which keeps
-// the scheme valid under CUDA-graph replay; the parity (epoch & 1) double-buffers the area.
-struct CommParams {
-  int world, rank;
-  unsigned long long* recv[8];
-  int* epoch;              // local: number of completed fused launches
-  int* done;               // local: CTAs of the current launch that have exited
-  long long slot_stride;   // words per source slot
-  long long parity_stride; // words per parity (= world * slot_stride)
-  long long wait_cycles;   // bound of the wait on a peer's word
-  // two_shot != 0 (used for world >= 4): tile i is owned by rank i % world.  Partials go only to the owner
-  // (reduce-scatter), which sums them, applies the epilogue and stores the finished value into `result`
-  // of every rank (all-gather); the other ranks wait for that word.  Traffic per rank falls from
-  // (world-1) x tile to about 2 x (world-1)/world x tile for one extra NVLink hop.
-  int two_shot;
-  unsigned long long* result[8];   // rank r's result area [2 parities][slot words]
-};
 
 struct GemmParams {
   int N, T, K;
@@ -93,31 +68,6 @@ struct GemmParams {
   float rms_eps;
   float* rms_ws;           // [tile][split][BN] partial sums of squares
 };
-
-// Payload of one LL word of the fused all-reduce: two bf16 values (tokens t and t + 1 of one feature).  Partials are
-// rounded to bf16 before they cross NVLink, as a bf16 all-reduce does; the sum itself runs in fp32.
-__device__ __forceinline__ unsigned long long ll_pack2(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return (unsigned long long)(*reinterpret_cast<unsigned*>(&v));
-}
-__device__ __forceinline__ void ll_unpack2(unsigned w, float& lo, float& hi) {
-  const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&w);
-  const float2 f = __bfloat1622float2(v);
-  lo = f.x; hi = f.y;
-}
-
-__device__ __forceinline__ float apply_act(float x, int act) {
-  switch (act) {
-    case 1: return fmaxf(x, 0.f);
-    case 2: return x / (1.f + __expf(-x));
-    case 3: {
-      const float c = 0.7978845608028654f;
-      float u = c * (x + 0.044715f * x * x * x);
-      return 0.5f * x * (1.f + tanhf(u));
-    }
-    default: return x;
-  }
-}
 
 constexpr int kMaxStages = 12;
 

@@ -432,8 +432,10 @@ def test_ctypes_mirrors_of_kernel_parameter_structs_have_the_c_layout():
         lib = C.CDLL(path)
     except OSError as e:
         pytest.skip(f"kernel library does not load here: {e}")
+    from xfastertransformer_b200.ops import native as NAT
     for fn, mirror in (("xft_comm_params_layout", F.CommParams), ("xft_ar_params_layout", F.ArParams),
-                       ("xft_bulk_ar_layout", F.BulkArParams), ("xft_ep_layout", F.EpParams)):
+                       ("xft_bulk_ar_layout", F.BulkArParams), ("xft_ep_layout", F.EpParams),
+                       ("xft_sk_qkv_layout", NAT.SkQkv)):
         out = (C.c_longlong * 32)()
         f = getattr(lib, fn)
         f.restype = C.c_int
@@ -442,3 +444,63 @@ def test_ctypes_mirrors_of_kernel_parameter_structs_have_the_c_layout():
         assert n == 1 + len(names), fn
         assert out[0] == C.sizeof(mirror), fn
         assert [out[1 + i] for i in range(len(names))] == [getattr(mirror, name).offset for name in names], fn
+
+
+def test_decode_gemm_work_decomposition_covers_every_unit_once():
+    """The balanced decode GEMM (csrc/kernels/gemm_decode_sm100.cu) deals n_tiles x num_kb weight blocks to G CTAs as
+    contiguous runs.  With the library's own arithmetic: the runs partition the units; the CTAs that share a tile are
+    exactly c_lo..c_hi as the kernel computes them; a CTA leaves at most two partial tiles, and the scratch slot rule
+    (2 * cta + 0 for the CTA's first tile, + 1 otherwise) gives every partial its own slot and lets the reducer find it;
+    the all-reduce ownership formula cuts the output into `world` contiguous ranges that match the owners' bounds."""
+    import xfastertransformer_b200 as pkg
+    path = os.path.join(os.path.dirname(pkg.__file__), "lib", "libxft_b200_kernels.so")
+    if not os.path.exists(path):
+        pytest.skip("kernel library not built")
+    try:
+        lib = C.CDLL(path)
+    except OSError as e:
+        pytest.skip(f"kernel library does not load here: {e}")
+    lib.xft_sk_cta_of.restype = C.c_int
+    lib.xft_sk_first_unit.restype = C.c_longlong
+    cta_of = lambda u, U, G: lib.xft_sk_cta_of(C.c_longlong(u), C.c_longlong(U), G)
+    first = lambda c, U, G: lib.xft_sk_first_unit(c, C.c_longlong(U), G)
+    for n_tiles, num_kb, G in ((10, 128, 148), (64, 16, 148), (28, 128, 148), (250, 128, 148), (6, 4, 12), (3, 7, 10),
+                               (1, 9, 4), (80, 128, 148), (5, 2, 5), (64, 56, 148), (7, 3, 1)):
+        U = n_tiles * num_kb
+        assert G <= max(1, U // 2) or G == 1
+        bounds = [first(c, U, G) for c in range(G + 1)]
+        assert bounds[0] == 0 and bounds[-1] == U and all(b1 > b0 for b0, b1 in zip(bounds, bounds[1:]))
+        for u in range(U):
+            c = cta_of(u, U, G)
+            assert bounds[c] <= u < bounds[c + 1]
+        slots = {}
+        arrivals = [0] * n_tiles
+        for c in range(G):
+            u, seg, partial = bounds[c], 0, 0
+            while u < bounds[c + 1]:
+                tile, kb0 = divmod(u, num_kb)
+                kb1 = min(num_kb, kb0 + bounds[c + 1] - u)
+                if not (kb0 == 0 and kb1 == num_kb):
+                    partial += 1
+                    slot = 2 * c + (0 if seg == 0 else 1)
+                    assert slot not in slots
+                    slots[slot] = tile
+                    arrivals[tile] += 1
+                u += kb1 - kb0
+                seg += 1
+            assert partial <= 2
+        for tile in range(n_tiles):
+            lo, hi = cta_of(tile * num_kb, U, G), cta_of((tile + 1) * num_kb - 1, U, G)
+            if lo == hi:
+                assert arrivals[tile] == 0
+                continue
+            assert arrivals[tile] == hi - lo + 1
+            for c in range(lo, hi + 1):                  # the reducer's slot rule finds the writer's slot
+                sl = 2 * c + (0 if first(c, U, G) // num_kb == tile else 1)
+                assert slots.get(sl) == tile
+    for E2, world in ((32768, 8), (1000, 3), (7, 8), (4096, 2), (131072, 4)):
+        owner = [(i * world) // E2 for i in range(E2)]
+        for r in range(world):
+            r0, r1 = (r * E2 + world - 1) // world, ((r + 1) * E2 + world - 1) // world
+            assert all(owner[i] == r for i in range(r0, r1))
+            assert owner.count(r) == r1 - r0

@@ -333,3 +333,65 @@ def test_bounded_wait_reports_bad_index_without_faulting():
         _ws().check_status()
     _ws().check_status()            # cleared
     assert torch.isfinite(N_.rmsnorm(qkv, torch.ones(qkv.shape[1]).cuda(), 1e-6).float()).all()
+
+
+@pytest.mark.parametrize("T,N,K,gated", [(16, 1280, 8192, False), (16, 8192, 1024, False), (5, 896, 2048, True),
+                                         (64, 1024, 3584, False), (33, 640, 512, True), (2, 130, 72, False)])
+def test_decode_gemm_balanced_stream(T, N, K, gated):
+    """Decode-size GEMM whose weight blocks are dealt to the CTAs in equal runs: runs that end inside a tile leave
+    partials, the last arriver adds them in CTA order.  Same answer twice (deterministic), counters back at zero, and
+    the result equals the tile-per-CTA kernel's within rounding."""
+    from xfastertransformer_b200.ops import native as N_
+    from xfastertransformer_b200.utils.flags import Env
+    g = torch.Generator().manual_seed(T + N + K)
+    x = (torch.randn(T, K, generator=g) * 0.5).bfloat16().cuda()
+    rows = 2 * N if gated else N
+    w = (torch.randn(rows, K, generator=g) * 0.05).bfloat16().cuda()
+    bias = (torch.randn(rows, generator=g) * 0.1).cuda()
+    res = None if gated else torch.randn(T, N, generator=g).bfloat16().cuda()
+    y = x.float() @ w.float().t() + bias
+    want = torch.nn.functional.silu(y[:, :N]) * y[:, N:] if gated else y + 0.5 * res.float()
+    assert Env.get().gemm_streamk
+    kw = dict(gated=gated, dual_off=N if gated else 0, bias=bias, act="silu" if gated else None, residual=res,
+              res_scale=0.5)
+    a = N_.gemm_bf16(x, w, N, **kw)
+    b = N_.gemm_bf16(x, w, N, **kw)
+    _ws().check_status()
+    _close(a, want, 3e-2, 2e-2, f"balanced decode gemm {T}x{N}x{K}")
+    assert torch.equal(a, b)
+    assert int(_ws().counters.abs().sum().item()) == 0
+    a32 = N_.gemm_bf16(x, w[:N], N, out_dtype=torch.float32)
+    _close(a32, x.float() @ w[:N].float().t(), 5e-3, 5e-3, "fp32 out")
+
+
+@pytest.mark.parametrize("style,rot_frac,fold", [("half", 1.0, True), ("interleaved", 0.5, False), ("half", 0.5, False)])
+@pytest.mark.parametrize("T", [1, 16, 37])
+def test_qkv_product_with_rope_and_cache_append_epilogue(style, rot_frac, fold, T):
+    """QKV product + split + RoPE + paged cache append as one kernel against the three separate steps of the oracle."""
+    from xfastertransformer_b200.ops import native as N_
+    from xfastertransformer_b200 import ops
+    hq, hkv, D, bs, nb, K = 8, 2, 128, 64, 6, 1024
+    rot = int(D * rot_frac)
+    g = torch.Generator().manual_seed(T)
+    x = (torch.randn(T, K, generator=g) * (3.0 if fold else 0.5)).bfloat16()
+    w = (torch.randn((hq + 2 * hkv) * D, K, generator=g) * 0.05).bfloat16()
+    bias = torch.randn((hq + 2 * hkv) * D, generator=g) * 0.1
+    pos = torch.randint(0, 500, (T,), generator=g, dtype=torch.int32)
+    slots = torch.randperm(nb * bs, generator=g)[:T].int()
+    table = R.rope_table(512, rot)
+    qs = 1.0 + torch.rand(T, generator=g)
+    eps = 1e-5
+    h = R.rmsnorm(x.float(), torch.ones(K), eps) if fold else x.float()
+    qkv = (h @ w.float().t() + bias).bfloat16()
+    cpu = _mk_cache(nb, hkv, bs, D, False, "cpu")
+    gpu = _mk_cache(nb, hkv, bs, D, False, "cuda")
+    want = ops.qkv_rope_cache(qkv.float(), hq, hkv, D, pos, table, rot, style, *cpu, slots, qs, None, None, eps)
+    W = make_linear(w, "bf16").to("cuda")
+    assert N_.can_fuse_qkv_rope(W, T, D, gpu[0], None, None, None, style)
+    got = N_.qkv_linear_rope_cache(x.cuda(), W, bias.cuda(), eps if fold else None, hq, hkv, pos.cuda(), table.cuda(),
+                                   rot, style, gpu[0], gpu[1], slots.cuda(), qs.cuda())
+    _ws().check_status()
+    scale = float(want.abs().max())
+    _close(got, want, 2e-2 * scale, 3e-2, "q")
+    _close(gpu[0], cpu[0], 2e-2 * scale, 3e-2, "k cache")
+    _close(gpu[1], cpu[1], 2e-2 * scale, 3e-2, "v cache")

@@ -491,15 +491,28 @@ class Decoder:
         if s.attention == "mla":
             a = self._mla(L, h, b, cache, li)
         else:
-            with TimeLine("QKV.linear"):
-                qkv = ops.linear_rms(x, L.qkv, self.eps, L.qkv_b) if L.attn_fold else ops.linear(h, L.qkv, L.qkv_b)
+            table, q_scale, positions = self.rope_table, None, b.positions
+            if s.logn_ntk and table is not None:
+                table, seq_len = self._qwen_rope(b.max_kv)
+                if c.use_logn_attn and b.max_kv > seq_len:
+                    q_scale = torch.clamp(torch.log(b.positions.float() + 1) / math.log(seq_len), min=1.0)
+            xin = x if L.attn_fold else h
+            fused_qkv = (xin.is_cuda and s.rope != "2d" and
+                         ops.can_fuse_qkv_rope(L.qkv, xin.numel() // xin.shape[-1], self.D, cache.k[li], cache.ks[li],
+                                               L.q_norm, L.k_norm, self.rope_style))
+            if fused_qkv:
+                # decode sizes: RoPE and the cache append are the epilogue of the QKV product (one kernel)
+                with TimeLine("QKV.linear+QKPO"):
+                    q = ops.qkv_linear_rope_cache(xin, L.qkv, L.qkv_b, self.eps if L.attn_fold else None, self.hq,
+                                                  self.hkv, positions, table, self.rot_dim, self.rope_style,
+                                                  cache.k[li], cache.v[li], b.slots, q_scale)
+            else:
+                with TimeLine("QKV.linear"):
+                    qkv = ops.linear_rms(x, L.qkv, self.eps, L.qkv_b) if L.attn_fold else ops.linear(h, L.qkv, L.qkv_b)
             with TimeLine("QKPO"):
-                table, q_scale, positions = self.rope_table, None, b.positions
-                if s.logn_ntk and table is not None:
-                    table, seq_len = self._qwen_rope(b.max_kv)
-                    if c.use_logn_attn and b.max_kv > seq_len:
-                        q_scale = torch.clamp(torch.log(b.positions.float() + 1) / math.log(seq_len), min=1.0)
-                if s.rope == "2d":
+                if fused_qkv:
+                    pass
+                elif s.rope == "2d":
                     q = self._rope2d_cache(L, qkv, b, cache, li)
                 else:
                     q = ops.qkv_rope_cache(qkv, self.hq, self.hkv, self.D, positions, table, self.rot_dim,

@@ -136,6 +136,18 @@ def qkv_rope_cache(qkv, hq, hkv, d, positions, table, rot_dim, style, kc, vc, ks
     return q.contiguous()
 
 
+def can_fuse_qkv_rope(W, T, D, kc, ks, q_norm_w, k_norm_w, style) -> bool:
+    """True when the QKV product, RoPE and the cache append can run as one kernel (GPU, decode sizes)."""
+    return _cuda(kc) and _nat().can_fuse_qkv_rope(W, T, D, kc, ks, q_norm_w, k_norm_w, style)
+
+
+def qkv_linear_rope_cache(x, W, bias, rms_eps, hq, hkv, positions, table, rot_dim, style, kc, vc, slots, q_scale=None):
+    """QKV product with split + RoPE + paged cache append as its epilogue; returns q [T, hq, D].  GPU only: callers
+    ask can_fuse_qkv_rope first and otherwise run linear / linear_rms followed by qkv_rope_cache."""
+    return _nat().qkv_linear_rope_cache(x, W, bias, rms_eps, hq, hkv, positions, table, rot_dim, style, kc, vc, slots,
+                                        q_scale)
+
+
 def paged_attention(q, kc, vc, block_table, cu_q, kv_lens, scale, ks=None, vs=None, slopes=None,
                     causal=True, prefix_lm_lens=None, group=None, q_off=0, meta=None):
     if _cuda(q):

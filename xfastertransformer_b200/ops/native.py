@@ -182,6 +182,9 @@ def gemm_bf16(x, w, N, gated=False, dual_off=0, bias=None, act=None, residual=No
         assert r2.stride(1) == 1 and r2.dtype == torch.bfloat16
         ldr = r2.stride(0)
     ws = Workspace.get(x.device)
+    if T <= SK_MAX_TOKENS and force_splits == 0 and _ENV().gemm_streamk:
+        _gemm_sk(x2, ldx, w, out, T, N, K, gated, dual_off, bias, r2, ldr, res_scale, act, row_scale, None, None, None)
+        return out
     if _ENV().gemm_persistent and T > 128 and gated and not fp32 and row_scale is None and out.stride(1) == 1 \
             and residual is None:
         # gated form of the persistent kernel: four 128-column accumulators, act(gate) * up on the way out
@@ -205,6 +208,66 @@ def gemm_bf16(x, w, N, gated=False, dual_off=0, bias=None, act=None, residual=No
     _check(rc, "gemm_bf16")
     ws.launches += 1
     return out
+
+
+SK_MAX_TOKENS = 64
+
+
+class SkQkv(C.Structure):
+    """Mirror of the struct of the same name in csrc/kernels/gemm_decode_sm100.cu."""
+    _fields_ = [("q_out", C.c_void_p), ("hq", C.c_int), ("hkv", C.c_int), ("positions", C.c_void_p),
+                ("table", C.c_void_p), ("rot", C.c_int), ("style", C.c_int), ("rot_off", C.c_int), ("max_pos", C.c_int),
+                ("q_scale", C.c_void_p), ("kc", C.c_void_p), ("vc", C.c_void_p), ("bs", C.c_int),
+                ("nslots", C.c_longlong), ("slots", C.c_void_p)]
+
+
+def _gemm_sk(x2, ldx, w, out, T, N, K, gated, dual_off, bias, r2, ldr, res_scale, act, row_scale, rms_eps, comm, qkv):
+    """One launch of the decode-size weight-stream GEMM (T <= 64)."""
+    ws = Workspace.get(x2.device)
+    L = lib()
+    L.xft_gemm_sk.restype = C.c_int
+    eps = C.byref(C.c_float(rms_eps)) if rms_eps is not None else None
+    rc = L.xft_gemm_sk(_p(x2), ldx, _p(w), w.shape[0], w.stride(0), _p(out), out.stride(0) if out is not None else 0,
+                       int(out is not None and out.dtype == torch.float32), T, N, K, int(gated), dual_off, _p(bias),
+                       _p(r2), ldr, C.c_float(res_scale), _ACT[act], _p(row_scale), eps, _p(ws.ws),
+                       C.c_size_t(ws.ws_bytes), _p(ws.counters), ws.n_counters, _p(ws.status),
+                       C.byref(comm) if comm is not None else None, C.byref(qkv) if qkv is not None else None, _stream())
+    _check(rc, "gemm_sk")
+    ws.launches += 1
+
+
+def can_fuse_qkv_rope(W, T, D, kc, ks, q_norm_w, k_norm_w, style) -> bool:
+    """The QKV product can end in RoPE + paged cache append (one kernel instead of two): bf16 weights, head_dim 128,
+    a bf16 cache, no per-head q/k norm, at most SK_MAX_TOKENS rows."""
+    e = _ENV()
+    return (e.gemm_streamk and e.fuse_qkv_rope and W.kind == "bf16" and T <= SK_MAX_TOKENS and D == 128 and ks is None
+            and kc.dtype == torch.bfloat16 and q_norm_w is None and k_norm_w is None and style in ("half", "interleaved"))
+
+
+def qkv_linear_rope_cache(x, W, bias, rms_eps, hq, hkv, positions, table, rot_dim, style, kc, vc, slots, q_scale=None,
+                          rot_offset=0):
+    """q = RoPE(split(x W^T + b)) and K / V appended to the paged cache, as ONE kernel: the QKV product's epilogue
+    rotates each finished head and stores it where the attention kernel reads it.  `rms_eps` set: `x` is the
+    un-normalised hidden state and W carries the norm's gain (see fold_norm_gain)."""
+    x2, ldx = _rows2d(x)
+    T, K = x2.shape
+    N = (hq + 2 * hkv) * 128
+    assert W.w.shape[0] == N and W.w.shape[1] == K and x2.dtype == torch.bfloat16
+    q = torch.empty(T, hq, 128, dtype=torch.bfloat16, device=x.device)
+    nb, _, bs, _ = kc.shape
+    qp = SkQkv()
+    qp.q_out, qp.hq, qp.hkv = q.data_ptr(), hq, hkv
+    qp.positions = positions.data_ptr()
+    qp.table = table.data_ptr() if table is not None else None
+    qp.rot = rot_dim if table is not None else 0
+    qp.style = 0 if style == "half" else 1
+    qp.rot_off = rot_offset
+    qp.max_pos = table.shape[0] if table is not None else 0
+    qp.q_scale = q_scale.data_ptr() if q_scale is not None else None
+    qp.kc, qp.vc, qp.bs, qp.nslots = kc.data_ptr(), vc.data_ptr(), bs, nb * bs
+    qp.slots = slots.data_ptr()
+    _gemm_sk(x2, ldx, W.w, None, T, N, K, False, 0, bias, None, 0, 1.0, None, None, rms_eps, None, qp)
+    return q
 
 
 RMS_FUSE_MAX_TOKENS = 64
@@ -233,6 +296,9 @@ def linear_rms(x, W, eps, bias=None, act=None, gated=False, out_dtype=None):
     assert w.dtype == torch.bfloat16 and w.stride(1) == 1 and w.shape[1] == K and x2.dtype == torch.bfloat16
     fp32 = out_dtype == torch.float32
     out = torch.empty(T, N, dtype=torch.float32 if fp32 else torch.bfloat16, device=x.device)
+    if _ENV().gemm_streamk:
+        _gemm_sk(x2, ldx, w, out, T, N, K, gated, N if gated else 0, bias, None, 0, 1.0, act, None, eps, None, None)
+        return out.view(*x.shape[:-1], N)
     ws = Workspace.get(x.device)
     rc = lib().xft_gemm_bf16_rms(_p(x2), ldx, _p(w), w.shape[0], w.stride(0), _p(out), out.stride(0), int(fp32), T, N, K,
                                  int(gated), N if gated else 0, _p(bias), _ACT[act], C.c_float(eps), _p(ws.ws),

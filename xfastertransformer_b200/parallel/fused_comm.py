@@ -189,6 +189,16 @@ class PeerComm:
             ldr = r2.stride(0)
         ws = N.Workspace.get(x.device)
         self.gp.two_shot = self._two_shot_env if self._two_shot_env is not None else int(self.world >= 4 and T > 16)
+        if N._ENV().gemm_streamk:
+            # balanced weight-stream kernel: finished tiles are pushed to the peers and every CTA reduces its share of
+            # the whole output (one-shot up to 16 tokens, reduce-scatter + all-gather above)
+            if self._two_shot_env is None:
+                self.gp.two_shot = int(self.world >= 4 and T > 16)
+            if fp32:
+                self.gp.two_shot = 0
+            N._gemm_sk(x2, ldx, W.w, out, T, n, K, False, 0, bias, r2, ldr, res_scale, act, None, None, self.gp, None)
+            self.fused_calls += 1
+            return out.view(*x.shape[:-1], n)
         if fp32:
             # the two-shot form hands the finished values to the other ranks as bf16 pairs, which would leave the
             # owner with fp32 and everyone else with rounded values: fp32 outputs always take the one-shot form

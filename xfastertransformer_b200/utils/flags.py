@@ -69,6 +69,10 @@ class Env:
         self.attn_tma = _int("XFT_ATTN_TMA", 1) != 0      # bf16 decode attention through the TMA ring kernel
         self.attn_splits = _int("XFT_ATTN_SPLITS", 0)     # decode split-KV factor; 0 = planned per launch
         self.gemm_persistent = _int("XFT_GEMM_PERSISTENT", 0) != 0     # prefill GEMMs through the persistent kernel
+        # decode-size bf16 GEMMs (up to 64 tokens) through the balanced weight-stream kernel (gemm_decode_sm100.cu);
+        # XFT_FUSE_QKV_ROPE: RoPE + cache append as the epilogue of the QKV product (head_dim 128, bf16 cache)
+        self.gemm_streamk = _int("XFT_GEMM_STREAMK", 1) != 0
+        self.fuse_qkv_rope = _int("XFT_FUSE_QKV_ROPE", 1) != 0
         # tensor-parallel prefill: two groups of prompts are interleaved block by block, so that the all-reduce of one
         # overlaps the compute of the other
         self.prefill_overlap = _int("XFT_PREFILL_OVERLAP", 0) != 0
