@@ -111,6 +111,8 @@ void xftc_rope_table(int max_pos, int rot_dim, double theta, int scaling, double
   auto t = ropeTable(max_pos, rot_dim, theta, s);
   std::memcpy(out, t.data(), t.size() * sizeof(float));
 }
+double xftc_telechat_ntk_theta(double theta, int rot_dim, int kv_len, int train_len) { return telechatNtkTheta(theta, rot_dim, kv_len, train_len); }
+double xftc_telechat_mscale(int input_len, int train_len) { return telechatMscale(input_len, train_len); }
 double xftc_qwen_ntk_theta(double theta, int rot_dim, int max_kv, int seq_len) { return qwenNtkTheta(theta, rot_dim, max_kv, seq_len); }
 void xftc_alibi_slopes(int n_heads, float* out) { auto v = alibiSlopes(n_heads); std::memcpy(out, v.data(), v.size() * sizeof(float)); }
 

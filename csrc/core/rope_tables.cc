@@ -56,6 +56,18 @@ double qwenNtkTheta(double theta, int rotDim, int maxKv, int seqLen) {
   return theta * std::pow(alpha, (double)rotDim / (rotDim - 2));
 }
 
+double telechatNtkTheta(double theta, int rotDim, int kvLen, int trainLen) {
+  if (rotDim <= 2) return theta;
+  const int len = std::max(kvLen, trainLen);
+  const double ctx = std::log((double)len / 4096.0) / std::log(2.0) + 1.0;
+  const double alpha = std::max(std::pow(2.0, std::ceil(ctx)) - 1.0, 1.0);
+  return theta * std::pow(alpha, (double)rotDim / (rotDim - 2));
+}
+
+double telechatMscale(int inputLen, int trainLen) {
+  return inputLen > trainLen ? 0.1 * std::log((double)inputLen / trainLen) + 1.0 : 1.0;
+}
+
 static void pow2Slopes(int n, std::vector<float>& out) {
   const double start = std::pow(2.0, -8.0 / n);
   double v = start;

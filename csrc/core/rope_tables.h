@@ -27,6 +27,11 @@ std::vector<float> ropeTable(int maxPos, int rotDim, double theta, const RopeSca
 // Qwen-1 dynamic NTK: base for a context of maxKv tokens when the model was trained on seqLen (alpha = 2^ceil(log2(
 // maxKv / seqLen) + 1) - 1, base * alpha^(rot / (rot - 2))); returns theta unchanged for maxKv <= seqLen
 double qwenNtkTheta(double theta, int rotDim, int maxKv, int seqLen);
+// TeleChat NTK (src/layers/rotary_embedding_telechat.cpp:29-35,68-117): the base for a context of kvLen tokens is
+// computed from max(kvLen, trainLen), alpha = max(2^ceil(log2(len / 4096) + 1) - 1, 1), base * alpha^(rot / (rot - 2));
+// a table first built during a pass with more than trainLen input tokens is scaled by 0.1 ln(inputLen / trainLen) + 1
+double telechatNtkTheta(double theta, int rotDim, int kvLen, int trainLen);
+double telechatMscale(int inputLen, int trainLen);
 // ALiBi slopes for nHeads heads: powers of 2^(-8/n) of the next lower power of two, interleaved tail for the rest
 std::vector<float> alibiSlopes(int nHeads);
 

@@ -67,7 +67,17 @@ struct SkParams {
   const __nv_bfloat16* rms_x; int rms_ldx; float rms_eps;     // folded RMSNorm (see gemm_sm100.cu)
   CommParams ar;             // ar.world > 1: all-reduce form
   SkQkv qkv;
+  // optional time line: 8 globaltimer stamps (ns) per CTA — 0 entry, 1 set-up done, 2 grid dependency resolved
+  // (producer), 3 first weight block landed, 4 last MMA issued, 5 last accumulator ready, 6 epilogue done, 7 exit
+  unsigned long long* trace;
 };
+
+__device__ __forceinline__ unsigned long long sk_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define SK_STAMP(ev) do { if (p.trace) p.trace[(size_t)blockIdx.x * 8 + (ev)] = sk_now(); } while (0)
 
 // CTA that holds unit u when `units` units are dealt to `G` CTAs as [i * units / G, (i + 1) * units / G)
 __host__ __device__ __forceinline__ int sk_cta_of(long long u, long long units, int G) {
@@ -86,7 +96,7 @@ __device__ __forceinline__ void st_2w(unsigned long long* p, unsigned long long 
 }
 
 template <int BN, bool DUAL>
-__global__ void __launch_bounds__(192, 1) gemm_sk_kernel(const __grid_constant__ CUtensorMap tmW,
+__global__ void __launch_bounds__(192, 2) gemm_sk_kernel(const __grid_constant__ CUtensorMap tmW,
                                                          const __grid_constant__ CUtensorMap tmX, const SkParams p) {
   constexpr int A_BYTES = 128 * 64 * 2;
   constexpr int B_BYTES = BN * 64 * 2;
@@ -112,6 +122,7 @@ __global__ void __launch_bounds__(192, 1) gemm_sk_kernel(const __grid_constant__
   const long long u0 = sk_first_unit(bid, p.units, G), u1 = sk_first_unit(bid + 1, p.units, G);
 
   if (threadIdx.x == 0) {
+    SK_STAMP(0);
     for (int s = 0; s < stages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
@@ -135,6 +146,7 @@ __global__ void __launch_bounds__(192, 1) gemm_sk_kernel(const __grid_constant__
   tcgen05_fence_after();
   const uint32_t tmem_base = tmem_base_s;
   grid_dep_launch();
+  if (threadIdx.x == 0) SK_STAMP(1);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -155,6 +167,7 @@ __global__ void __launch_bounds__(192, 1) gemm_sk_kernel(const __grid_constant__
         if (++kb == p.num_kb) { kb = 0; ++tile; }
       }
       grid_dep_wait();
+      SK_STAMP(2);
       {
         int kb2 = kb0, tile2 = tile0;
         for (int i = 0; i < pre; ++i) {
@@ -191,6 +204,7 @@ __global__ void __launch_bounds__(192, 1) gemm_sk_kernel(const __grid_constant__
           const int s = it % stages;
           const uint32_t ph = (it / stages) & 1;
           if (!mbar_wait(&full_bar[s], ph, p.status, XFT_ERR_WAIT_FULL)) { ok = false; break; }
+          if (it == 0) SK_STAMP(3);
           tcgen05_fence_after();
           const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
           const uint64_t adesc = umma_desc_k128(a_addr);
@@ -208,6 +222,7 @@ __global__ void __launch_bounds__(192, 1) gemm_sk_kernel(const __grid_constant__
         if (ok) tcgen05_commit(&tmem_full[a]);
         u += kb_end - kb_begin;
       }
+      SK_STAMP(4);
     }
   } else {
     // ------------------------------------------------------------------ epilogue: 4 warps, one TMEM lane per thread
@@ -268,6 +283,7 @@ __global__ void __launch_bounds__(192, 1) gemm_sk_kernel(const __grid_constant__
       const bool got = mbar_wait(&tmem_full[a], aph, p.status, XFT_ERR_WAIT_TMEM);
       // one answer for all 128 threads, so nobody is left alone in front of a later barrier
       if (named_bar_or(1, 128, !got)) { alive = false; break; }
+      if (et == 0 && u >= u1) SK_STAMP(5);
       tcgen05_fence_after();
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + (uint32_t)(a * ACC_COLS);
 
@@ -346,13 +362,14 @@ __global__ void __launch_bounds__(192, 1) gemm_sk_kernel(const __grid_constant__
             if (lane == 0) mbar_arrive(&tmem_empty[a]);
           }
         } else {
-          // sum of the runs that share this tile, in CTA order; four runs' loads are in flight together
+          // sum of the runs that share this tile, in CTA order; the loads of NB runs are in flight together
 #pragma unroll
           for (int j = 0; j < 16; ++j) { g[j] = 0.f; if (DUAL) uu[j] = 0.f; }
-          for (int cta = c_lo; cta <= c_hi; cta += 4) {
-            float pv[4][16], pu[DUAL ? 4 : 1][DUAL ? 16 : 1];
+          constexpr int NB = DUAL ? 2 : 4;
+          for (int cta = c_lo; cta <= c_hi; cta += NB) {
+            float pv[NB][16], pu[DUAL ? NB : 1][DUAL ? 16 : 1];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
+            for (int i = 0; i < NB; ++i) {
               const int cc = cta + i;
               if (cc <= c_hi) {
                 const int sl = 2 * cc + ((int)(sk_first_unit(cc, p.units, G) / p.num_kb) == tile ? 0 : 1);
@@ -368,7 +385,7 @@ __global__ void __launch_bounds__(192, 1) gemm_sk_kernel(const __grid_constant__
               }
             }
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < NB; ++i)
 #pragma unroll
               for (int j = 0; j < 16; ++j) { g[j] += pv[i][j]; if constexpr (DUAL) uu[j] += pu[i][j]; }
           }
@@ -558,12 +575,14 @@ __global__ void __launch_bounds__(192, 1) gemm_sk_kernel(const __grid_constant__
       if (!peers_ok && p.status) atomicCAS(p.status, 0, XFT_ERR_WAIT_PEER);
     }
   }
+  if (threadIdx.x == 64) SK_STAMP(6);
   tcgen05_fence_before();
   __syncthreads();
   if (warp == 1) {
     tcgen05_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  if (threadIdx.x == 0) SK_STAMP(7);
   if (p.ar.world > 1 && threadIdx.x == 0) {
     grid_dep_wait();
     // last CTA of the launch: the next launch uses the next epoch (and the other buffer parity)
@@ -578,8 +597,10 @@ __global__ void __launch_bounds__(192, 1) gemm_sk_kernel(const __grid_constant__
 // pipeline depth and shared memory of one CTA: about half an SM when that still gives three stages
 static void sk_smem_plan(int bn, int nacc, int* stages, size_t* smem) {
   const int stage_bytes = 128 * 64 * 2 * nacc + bn * 64 * 2;
-  int budget = 106 * 1024;
+  static const int env_kb = [] { const char* v = getenv("XFT_SK_SMEM_KB"); return v ? atoi(v) : 0; }();
+  int budget = (env_kb > 0 ? env_kb : 106) * 1024;
   if (budget / stage_bytes < 3) budget = 200 * 1024;
+  if (budget > 216 * 1024) budget = 216 * 1024;
   int s = budget / stage_bytes;
   if (s > kSkMaxStages) s = kSkMaxStages;
   if (s < 2) s = 2;
@@ -600,6 +621,8 @@ static int launch_sk(const CUtensorMap& tmW, const CUtensorMap& tmX, SkParams& p
   cudaError_t e = launch_pdl(gemm_sk_kernel<BN, DUAL>, dim3(grid), dim3(192), smem, st, tmW, tmX, p);
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
+
+static unsigned long long* g_sk_trace = nullptr;
 
 static int sk_num_sms() {
   static int sms = 0;
@@ -674,6 +697,7 @@ extern "C" int xft_gemm_sk(const void* X, int ldx, const void* W, int w_rows, in
     p.ar = *comm;
   }
   if (qkv) p.qkv = *qkv;
+  p.trace = g_sk_trace;
   CUtensorMap tmW, tmX;
   int r = make_tensor_map(&tmW, W, (uint64_t)w_rows, (uint64_t)K, (uint64_t)ldw, 128, 2);
   if (r) return 1000 - r;
@@ -689,6 +713,10 @@ extern "C" int xft_gemm_sk(const void* X, int ldx, const void* W, int w_rows, in
 #undef XFT_LAUNCH
   return -21;
 }
+
+// Time line of the following launches: `buf` holds 8 stamps (nanoseconds of the GPU's global timer) per CTA, see
+// SkParams::trace; null switches it off.  A debugging aid: the stamps cost a predicated store each.
+extern "C" void xft_gemm_sk_set_trace(unsigned long long* buf) { xft::g_sk_trace = buf; }
 
 // The work decomposition on its own (host arithmetic only), for tests: CTA that holds unit u, first unit of a CTA.
 extern "C" int xft_sk_cta_of(long long u, long long units, int G) { return xft::sk_cta_of(u, units, G); }

@@ -301,6 +301,9 @@ static void testRopeTables() {
   EXPECT(std::fabs(yarnMscale(8.0, 1.0) - (0.1 * std::log(8.0) + 1.0)) < 1e-12 && yarnMscale(1.0, 1.0) == 1.0);
   auto ty = ropeTable(4, 64, 10000.0, yarn);
   EXPECT(std::fabs(ty[0] - (float)yarnMscale(8.0, 1.0)) < 1e-6);                       // cos(0) times the YaRN scale
+  EXPECT(telechatNtkTheta(10000.0, 128, 100, 4096) == 10000.0);
+  EXPECT(std::fabs(telechatNtkTheta(10000.0, 128, 100, 8192) - 10000.0 * std::pow(3.0, 128.0 / 126.0)) < 1e-6);
+  EXPECT(telechatMscale(4096, 8192) == 1.0 && std::fabs(telechatMscale(16384, 8192) - (0.1 * std::log(2.0) + 1.0)) < 1e-12);
   EXPECT(qwenNtkTheta(10000.0, 128, 4096, 8192) == 10000.0);
   EXPECT(std::fabs(qwenNtkTheta(10000.0, 128, 16384, 8192) - 10000.0 * std::pow(3.0, 128.0 / 126.0)) < 1e-6);
   auto a8 = alibiSlopes(8);

@@ -611,3 +611,77 @@ def test_ngram_speculative_decoding_is_exact(tiny, monkeypatch):
     finally:
         monkeypatch.delenv("XFT_SPEC_NGRAM")
         Env.get().reload()
+
+
+def test_telechat_long_prompt_matches_eager_ntk_oracle(tmp_path):
+    """TeleChat's rotary table: the NTK base comes from max(context, training length) and a prompt longer than the
+    training length also scales cos / sin by 0.1 ln(len / training) + 1
+    (src/layers/rotary_embedding_telechat.cpp:29-35,68-117).  Checked against an independent eager model for a prompt
+    inside the training length (base of the training length, no scale) and one beyond it (larger base, scaled table);
+    plain RoPE would fail both."""
+    import math
+    from eager_llama import EagerLlama, _load
+    train = 8192          # alpha = 3 inside the training length; a 9000-token prompt would be too slow on CPU, so the
+    # "long" case shrinks the training length instead (alpha = 1, mscale > 1)
+    for train, S in ((8192, 40), (32, 70)):
+        cfg = ModelConfig(model_type="telechat", num_layer=2, hidden_size=128, head_num=4, kv_head_num=4,
+                          size_per_head=32, inter_size=256, vocab_size=512, max_pos_seq_len=train,
+                          activation_type="silu", weight_data_type="bf16", start_id=1, end_id=2)
+        d = str(tmp_path / f"tc{train}")
+        write_synthetic_checkpoint(d, cfg, seed=3, dtype="bf16", std=0.1)
+        ids = torch.randint(5, 500, (1, S), generator=torch.Generator().manual_seed(S))
+        got = xft.AutoModel.from_pretrained(d, dtype="bf16")(ids)[0]
+
+        class EagerTeleChat(EagerLlama):
+            def __init__(self, path):
+                super().__init__(path)
+                for i, l in enumerate(self.layers):
+                    l["ob"] = _load(path, f"model.layers.{i}.attention.dense.bias.bin", (self.H,), "bf16")
+                true_len = max(S, train)
+                alpha = max(2.0 ** math.ceil(math.log2(true_len / 4096.0) + 1) - 1, 1.0)
+                self.theta = self.theta * alpha ** (self.D / (self.D - 2))
+                self.mscale = 0.1 * math.log(S / train) + 1.0 if S > train else 1.0
+
+            def _rope(self, x, pos):
+                D = self.D
+                inv = 1.0 / (self.theta ** (torch.arange(0, D, 2).float() / D))
+                f = torch.outer(pos.float(), inv)
+                cos, sin = f.cos()[None, :, None, :] * self.mscale, f.sin()[None, :, None, :] * self.mscale
+                x1, x2 = x[..., : D // 2], x[..., D // 2:]
+                return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], -1)
+
+        e = EagerTeleChat(d)
+        # the o_proj bias: fold it into the residual stream by patching the product (x + a @ o + b)
+        want = _eager_with_o_bias(e, ids)[0]
+        err = (got - want).abs().max().item()
+        assert err < 2e-3, (train, err)
+        plain = EagerLlama(d)
+        for l_p, l_e in zip(plain.layers, e.layers):
+            l_p["ob"] = l_e["ob"]
+        off = (got - _eager_with_o_bias(plain, ids)[0]).abs().max().item()
+        assert off > 5 * max(err, 1e-2), (train, err, off)
+
+
+def _eager_with_o_bias(e, ids):
+    """EagerLlama.logits with a bias on the attention output projection (TeleChat)."""
+    import math
+    import torch.nn.functional as F
+    B, S = ids.shape
+    x = e.wte[ids]
+    pos = torch.arange(S)
+    mask = torch.full((S, S), float("-inf")).triu(1)
+    g = e.nh // e.nkv
+    for l in e.layers:
+        h = e._norm(x, l["n1"])
+        qkv = h @ l["qkv"]
+        q = qkv[..., : e.nh * e.D].view(B, S, e.nh, e.D)
+        k = qkv[..., e.nh * e.D:(e.nh + e.nkv) * e.D].view(B, S, e.nkv, e.D)
+        v = qkv[..., (e.nh + e.nkv) * e.D:].view(B, S, e.nkv, e.D)
+        q, k = e._rope(q, pos), e._rope(k, pos)
+        k, v = k.repeat_interleave(g, 2), v.repeat_interleave(g, 2)
+        s = torch.einsum("bqhd,bkhd->bhqk", q, k) / math.sqrt(e.D) + mask
+        a = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, -1), v).reshape(B, S, -1)
+        x = x + a @ l["o"] + l["ob"]
+        h = e._norm(x, l["n2"])
+        x = x + (F.silu(h @ l["g"]) * (h @ l["u"])) @ l["d"]
+    return e._norm(x, e.fn) @ e.head.t()

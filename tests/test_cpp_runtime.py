@@ -341,6 +341,13 @@ def test_rope_and_alibi_tables_match_python(core):
             alpha = max(2 ** math.ceil(math.log(max_kv / seq, 2) + 1) - 1, 1)
             want = 10000.0 * alpha ** (128 / 126)
         assert abs(core.xftc_qwen_ntk_theta(D(10000.0), 128, max_kv, seq) - want) < 1e-6 * want
+    core.xftc_telechat_ntk_theta.restype = C.c_double
+    core.xftc_telechat_mscale.restype = C.c_double
+    for kv, train in ((100, 4096), (100, 8192), (9000, 8192), (70000, 8192), (5000, 2048)):
+        want = 10000.0 * R.telechat_ntk_alpha(max(kv, train)) ** (128 / 126)
+        assert abs(core.xftc_telechat_ntk_theta(D(10000.0), 128, kv, train) - want) < 1e-6 * want
+    assert core.xftc_telechat_mscale(100, 8192) == 1.0
+    assert abs(core.xftc_telechat_mscale(20000, 8192) - (0.1 * math.log(20000 / 8192) + 1)) < 1e-12
     for n in (1, 8, 12, 32, 40, 52, 64):
         out = (C.c_float * n)()
         core.xftc_alibi_slopes(n, out)

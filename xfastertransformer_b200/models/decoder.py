@@ -167,6 +167,21 @@ class Decoder:
             table = self._ntk_tables[alpha]
         return table, seq_len
 
+    def _telechat_rope(self, max_kv: int, max_q: int):
+        """TeleChat: NTK-scaled base computed from max(context length, training length) — so even short contexts use
+        the base of the training length — and, when the table for a base is first built during a pass whose input is
+        longer than the training length, cos / sin scaled by 0.1 ln(input / training) + 1
+        (src/layers/rotary_embedding_telechat.cpp:29-35,68-117, rotary_embedding_telechat.h:26-75).  Tables are kept
+        per base, as the reference keeps them."""
+        c = self.cfg
+        train = c.max_pos_seq_len if c.max_pos_seq_len > 0 else 2048
+        alpha = R.telechat_ntk_alpha(max(max_kv, train))
+        if alpha not in self._ntk_tables:
+            mscale = 0.1 * math.log(max_q / train) + 1.0 if max_q > train else 1.0
+            base = c.rope.theta * alpha ** (self.rot_dim / (self.rot_dim - 2))
+            self._ntk_tables[alpha] = R.rope_table(self.max_rope_pos, self.rot_dim, base, table_scale=mscale).to(self.device)
+        return self._ntk_tables[alpha]
+
     # ------------------------------------------------------------------------------------
     # weight loading
     # ------------------------------------------------------------------------------------
@@ -496,6 +511,8 @@ class Decoder:
                 table, seq_len = self._qwen_rope(b.max_kv)
                 if c.use_logn_attn and b.max_kv > seq_len:
                     q_scale = torch.clamp(torch.log(b.positions.float() + 1) / math.log(seq_len), min=1.0)
+            if s.telechat_ntk and table is not None:
+                table = self._telechat_rope(b.max_kv, b.max_q)
             xin = x if L.attn_fold else h
             fused_qkv = (xin.is_cuda and s.rope != "2d" and
                          ops.can_fuse_qkv_rope(L.qkv, xin.numel() // xin.shape[-1], self.D, cache.k[li], cache.ks[li],

@@ -25,6 +25,7 @@ class FamilySpec:
     attention: str = "gqa"          # gqa | mla
     alibi: bool = False             # decided per config for baichuan
     logn_ntk: bool = False          # qwen-1 dynamic NTK + log-n scaling
+    telechat_ntk: bool = False      # telechat: NTK base from max(context, training length) + mscale on long inputs
     resid_from_norm: bool = False   # chatglm-1: residual = alpha * normed input
     prefix_lm: bool = False         # chatglm-1 bidirectional prompt
     final_norm: bool = True
@@ -48,7 +49,7 @@ FAMILIES: Dict[str, FamilySpec] = {
     "chatglm3": FamilySpec("chatglm3", rope="interleaved", rot_frac=0.5, qkv_bias=True, mlp="chatglm2"),
     "chatglm4": FamilySpec("chatglm4", rope="interleaved", rot_frac=0.5, qkv_bias=True, mlp="chatglm2"),
     "gpt": FamilySpec("gpt", norm="layer", rope="none", qkv_bias=True, dense_bias=True, mlp="gpt", embedding="opt"),
-    "telechat": FamilySpec("telechat", dense_bias=True),
+    "telechat": FamilySpec("telechat", dense_bias=True, telechat_ntk=True),
 }
 
 

@@ -264,6 +264,13 @@ def rope_table(max_pos: int, rot_dim: int, theta: float = 10000.0, scaling_type:
     return torch.cat([fr.cos() * s, fr.sin() * s], dim=-1)
 
 
+def telechat_ntk_alpha(true_seq_len: int) -> float:
+    """TeleChat's NTK factor for a context of `true_seq_len` tokens: 2^ceil(log2(len / 4096) + 1) - 1, at least 1; the
+    rotary base becomes theta * alpha^(dim / (dim - 2)) (src/layers/rotary_embedding_telechat.cpp:29-35)."""
+    ctx = math.log(true_seq_len / 4096.0) / math.log(2.0) + 1
+    return max(2.0 ** math.ceil(ctx) - 1, 1.0)
+
+
 def _rotate(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, style: str) -> torch.Tensor:
     """x [T,H,rot] fp32; cos/sin [T,rot/2]."""
     c, s = cos[:, None, :], sin[:, None, :]
