@@ -51,6 +51,16 @@ int invokeLayerLLaMA(DataType dt, ActivationType at, NormType nt, int batchSize,
                      const float* queryBias = nullptr, const float* keyBias = nullptr, const float* valueBias = nullptr,
                      const float* attnOutBias = nullptr, cudaStream_t stream = 0);
 
+// Stateless DeepSeek MoE block (reference: include/layers_mlp.h:25, src/layers/moe_deepseek.cpp:24-118).  As in the
+// reference's entry point, ONE gate / up / down weight set (bf16 [in, out] on the device) serves every routed expert and
+// the shared expert, and routing uses DeepSeek-V3's constants (sigmoid + correction bias, 8 groups / 4 kept, top 8,
+// normalised, scaled by 2.5).  gatingWeight fp32 [hidden, experts], gatingBias fp32 [experts] or null.
+// numRoutedExperts == 0: a dense SwiGLU layer of width intermediateSize.  The [out, in] copies are kept per pointer set.
+int invokeMoEDeepSeek(DataType dt, ActivationType at, int numTokens, int hiddenSize, int intermediateSize,
+                      int moeIntermediateSize, int numSharedExperts, int numRoutedExperts, void* output, int outputStride,
+                      const void* input, int inputStride, const void* gatingWeight, const float* gatingBias,
+                      const void* gateWeight, const void* upWeight, const void* downWeight, cudaStream_t stream = 0);
+
 // DeepSeek routed experts.  gateUpWeights [E, 2*inter, hidden] (gate rows, then up rows) and downWeights
 // [E, hidden, inter], in [out, in] layout: bf16 when the scales are null, else e4m3 with one fp32 scale per
 // blockSize x blockSize tile ([E, rows/blockSize, cols/blockSize]); they are expanded to bf16 once, here.

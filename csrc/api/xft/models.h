@@ -16,6 +16,7 @@
 #include <tuple>
 #include <vector>
 
+#include "abstract_decoder.h"
 #include "abstract_searcher.h"
 #include "dtype.h"
 
@@ -70,6 +71,7 @@ public:
   void exitSlaves() {}
 
 protected:
+  friend class ModelDecoder;          // the AbstractDecoder view of this model (makeDecoder)
   void load(const std::string& path, DataType dt, DataType kv);
   std::unique_ptr<Engine> engine;
   SearcherConfig configuration;

@@ -183,4 +183,9 @@ int xftc_dsmoe_forward_selected(void* moe, void* in, void* out, int T, int* idx,
   return xft::forwardDeepSeekMoE(moe, in, out, T, idx, w);
 }
 void xftc_dsmoe_destroy(void* moe) { xft::destroyDeepSeekMoE(moe); }
+int xftc_invoke_moe_deepseek(int T, int hidden, int inter, int moeInter, int nShared, int nRouted, void* out, const void* in,
+                             const void* gatingW, const float* gatingBias, const void* gate, const void* up, const void* down) {
+  return xft::invokeMoEDeepSeek(xft::DataType::bf16, xft::SILU, T, hidden, inter, moeInter, nShared, nRouted, out, 0, in, 0,
+                                gatingW, gatingBias, gate, up, down);
+}
 }  // extern "C"

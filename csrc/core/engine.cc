@@ -603,6 +603,73 @@ std::tuple<float*, int, int> Model::forward(bool logitsAll) {
   return std::make_tuple(engine->hostLogits.data(), rows, engine->vocab);
 }
 
+// AbstractDecoder over a loaded model (reference: the decoder objects behind include/abstract_decoder.h, i.e.
+// CommonDecoder::forward / reorderCache / setPrefix in src/models/common_decoder.h:295-590,771-850).
+class ModelDecoder : public AbstractDecoder {
+public:
+  explicit ModelDecoder(Model& m) : model(m) {}
+
+  std::tuple<float*, int, int> forward(int* ids, int64_t* dims, int step, bool logitsAll) override {
+    const int rows = (int)(dims[0] * dims[1]), len = (int)dims[2];
+    if (rows <= 0 || len <= 0) throw std::invalid_argument("decoder forward: empty input");
+    Engine& e = *model.engine;
+    if (step == 0) {
+      for (int id : seqs) e.release(id);
+      seqs.clear();
+      std::vector<std::vector<int32_t>> prompts(rows);
+      for (int r = 0; r < rows; ++r) prompts[r].assign(ids + (size_t)r * len, ids + (size_t)(r + 1) * len);
+      seqs = model.set_input(prompts, std::vector<int>{}, -1);
+    } else {
+      if ((int)seqs.size() != rows) throw std::invalid_argument("decoder forward: batch differs from step 0");
+      for (int r = 0; r < rows; ++r) {
+        SequenceMeta& s = e.pool.get(seqs[r]);
+        for (int i = 0; i < len; ++i) s.generated.push_back(ids[(size_t)r * len + i]);
+        s.pending.assign(ids + (size_t)r * len, ids + (size_t)(r + 1) * len);
+      }
+    }
+    e.forward(seqs, logitsAll);
+    return std::make_tuple(e.hostLogits.data(), 0, e.vocab);
+  }
+
+  std::tuple<float*, int, int> forward(const std::vector<int>& seqIDs, bool logitsAll) override {
+    Engine& e = *model.engine;
+    e.forward(seqIDs, logitsAll);
+    return std::make_tuple(e.hostLogits.data(), 0, e.vocab);
+  }
+
+  void reorderCache(int* idx, int size) override {
+    if (size != (int)seqs.size()) throw std::invalid_argument("reorderCache: size differs from the running batch");
+    Engine& e = *model.engine;
+    std::vector<int> src(idx, idx + size);
+    for (int v : src) if (v < 0 || v >= size) throw std::invalid_argument("reorderCache: index out of range");
+    // rows take over the block tables (copy-on-write of a shared tail block) and the token history of their sources
+    e.tables->reorder(seqs, src);
+    std::vector<std::vector<int32_t>> gen(size);
+    std::vector<int> past(size);
+    for (int i = 0; i < size; ++i) { gen[i] = e.pool.get(seqs[src[i]]).generated; past[i] = e.pool.get(seqs[src[i]]).pastLen; }
+    for (int i = 0; i < size; ++i) { e.pool.get(seqs[i]).generated = gen[i]; e.pool.get(seqs[i]).pastLen = past[i]; }
+  }
+
+  bool isMaster() override { return model.isMaster(); }
+  int getRank() override { return model.getRank(); }
+  int getEndId() override { return model.engine->endId; }
+  void setPrefix(int* ids, int seqLen) override {
+    std::vector<int32_t> v(ids, ids + seqLen);
+    model.setPrefix(v);
+  }
+  void unsetPrefix() override { model.unsetPrefix(); }
+
+  ~ModelDecoder() override {
+    for (int id : seqs) model.engine->release(id);
+  }
+
+private:
+  Model& model;
+  std::vector<int> seqs;
+};
+
+std::unique_ptr<AbstractDecoder> makeDecoder(Model& model) { return std::unique_ptr<AbstractDecoder>(new ModelDecoder(model)); }
+
 bool Model::isDone() {
   for (int id : engine->working) if (!engine->pool.get(id).done) return false;
   return true;

@@ -376,4 +376,97 @@ int forwardDeepSeekMoE(void* moe, void* input, void* output, int nTokens, int* s
 
 void destroyDeepSeekMoE(void* moe) { delete static_cast<MoeObj*>(moe); }
 
+// ---------------------------------------------------------------------------------------------- stateless DeepSeek MoE
+namespace {
+struct MoeCallObj {
+  MlpObj mlp;                 // the one weight set every expert uses, as [out, in] copies
+  Buf router, bias, logits, idx, wts, pos, src, rowW, tiles, meta, xs, h1, ys, shared, hid;
+  int E = 0;
+};
+std::map<std::tuple<const void*, const void*, const void*, const void*>, std::unique_ptr<MoeCallObj>> g_moeCall;
+}  // namespace
+
+int invokeMoEDeepSeek(DataType dt, ActivationType at, int numTokens, int hiddenSize, int intermediateSize,
+                      int moeIntermediateSize, int numSharedExperts, int numRoutedExperts, void* output, int outputStride,
+                      const void* input, int inputStride, const void* gatingWeight, const float* gatingBias,
+                      const void* gateWeight, const void* upWeight, const void* downWeight, cudaStream_t st) {
+  if (dt != DataType::bf16 || at != SILU) return -1;
+  if (numTokens <= 0) return 0;
+  if (!input || !output || !gateWeight || !upWeight || !downWeight) return -25;
+  const int H = hiddenSize, T = numTokens;
+  const int I = numRoutedExperts > 0 ? moeIntermediateSize : intermediateSize;
+  if (H % 8 || I % 8 || (outputStride != 0 && outputStride != H)) return -24;
+  const int ldx = inputStride > 0 ? inputStride : H;
+  Work& w = work();
+  std::lock_guard<std::mutex> g(g_mu);
+  if (!w.init()) return -22;
+  auto key = std::make_tuple(gateWeight, upWeight, downWeight, gatingWeight);
+  auto it = g_moeCall.find(key);
+  if (it == g_moeCall.end()) {
+    auto o = std::make_unique<MoeCallObj>();
+    if (!o->mlp.build(H, I, gateWeight, upWeight, downWeight, st)) return -22;
+    o->E = numRoutedExperts;
+    if (numRoutedExperts > 0) {
+      if (!gatingWeight) return -25;
+      // router weight: fp32 [hidden, experts] -> bf16 [experts, hidden]; correction bias fp32 [experts]
+      if (!o->router.ensure((size_t)numRoutedExperts * H * 2)) return -22;
+      if (xft_transpose_to_bf16(gatingWeight, 0, numRoutedExperts, H, numRoutedExperts, o->router.p, H, st)) return -22;
+      if (gatingBias) {
+        if (!o->bias.ensure((size_t)numRoutedExperts * 4)) return -22;
+        cudaMemcpyAsync(o->bias.p, gatingBias, (size_t)numRoutedExperts * 4, cudaMemcpyDefault, st);
+      }
+    }
+    it = g_moeCall.emplace(key, std::move(o)).first;
+  }
+  MoeCallObj* m = it->second.get();
+  const int act = 2;   // silu
+  if (numRoutedExperts <= 0) {
+    // dense layer (the first layers of the model): down(silu(x gate) * (x up))
+    if (!m->hid.ensure((size_t)T * I * 2)) return -22;
+    int rc = gemm(w, input, ldx, m->mlp.gateUp.p, 2 * I, H, m->hid.p, I, T, I, 1, I, nullptr, nullptr, 0, act, 0, st);
+    if (rc) return rc;
+    return gemm(w, m->hid.p, I, m->mlp.down.p, H, I, output, H, T, H, 0, 0, nullptr, nullptr, 0, 0, 0, st);
+  }
+  // routing as DeepSeek-V3 does it: sigmoid scores + correction bias, 8 groups / best 4, top 8, weights normalised and
+  // scaled by 2.5 (the constants of the reference's entry point, src/layers/moe_deepseek.cpp:43-55)
+  const int E = numRoutedExperts, k = E < 8 ? E : 8;
+  const int nGroup = E % 8 == 0 ? 8 : 1, topkGroup = nGroup == 8 ? 4 : 1;
+  if (!m->logits.ensure((size_t)T * E * 4) || !m->idx.ensure((size_t)T * k * 4) || !m->wts.ensure((size_t)T * k * 4)) return -22;
+  int rc = gemm(w, input, ldx, m->router.p, E, H, m->logits.p, E, T, E, 0, 0, nullptr, nullptr, 0, 0, 1, st);
+  if (rc) return rc;
+  rc = xft_moe_route(m->logits.as<float>(), E, T, E, k, 2 /* deepseek */, m->bias.as<float>(), nGroup, topkGroup, 2.5f, 1, 1,
+                     m->idx.as<int>(), m->wts.as<float>(), st);
+  if (rc) return rc;
+  const int avg = std::max(1, (T * k + E - 1) / E);
+  const int bn = avg <= 16 ? 16 : avg <= 32 ? 32 : avg <= 64 ? 64 : 128;
+  const int maxRows = T * k, maxTiles = (maxRows + bn - 1) / bn + E;
+  if (!m->pos.ensure((size_t)maxRows * 4) || !m->src.ensure((size_t)maxRows * 4) || !m->rowW.ensure((size_t)maxRows * 4) ||
+      !m->tiles.ensure((size_t)maxTiles * 16) || !m->meta.ensure(8) || !m->xs.ensure((size_t)maxRows * H * 2) ||
+      !m->h1.ensure((size_t)maxRows * I * 2) || !m->ys.ensure((size_t)maxRows * H * 4))
+    return -22;
+  rc = xft_moe_plan(m->idx.as<int>(), m->wts.as<float>(), T, k, 0, E, bn, m->pos.as<int>(), m->src.as<int>(),
+                    m->rowW.as<float>(), m->tiles.p, m->meta.as<int>(), maxTiles, maxRows, st);
+  if (rc) return rc;
+  rc = xft_moe_gather(input, ldx, m->src.as<int>(), m->meta.as<int>(), m->xs.p, maxRows, H, st);
+  if (rc) return rc;
+  // every routed expert reads the same weight set: a group stride of 0 rows points all groups at it
+  rc = xft_gemm_bf16_grouped(m->xs.p, H, maxRows, m->mlp.gateUp.p, 2 * I, H, m->h1.p, I, 0, I, H, 1, I, 0, m->tiles.p,
+                             m->meta.as<int>(), maxTiles, bn, nullptr, act, w.status.as<int>(), st);
+  if (rc) return rc;
+  rc = xft_gemm_bf16_grouped(m->h1.p, I, maxRows, m->mlp.down.p, H, I, m->ys.p, H, 1, H, I, 0, 0, 0, m->tiles.p,
+                             m->meta.as<int>(), maxTiles, bn, m->rowW.as<float>(), 0, w.status.as<int>(), st);
+  if (rc) return rc;
+  const void* add = nullptr;
+  if (numSharedExperts > 0) {
+    // the shared expert sees every token (same weight pointers in this entry point)
+    if (!m->hid.ensure((size_t)T * I * 2) || !m->shared.ensure((size_t)T * H * 2)) return -22;
+    rc = gemm(w, input, ldx, m->mlp.gateUp.p, 2 * I, H, m->hid.p, I, T, I, 1, I, nullptr, nullptr, 0, act, 0, st);
+    if (rc) return rc;
+    rc = gemm(w, m->hid.p, I, m->mlp.down.p, H, I, m->shared.p, H, T, H, 0, 0, nullptr, nullptr, 0, 0, 0, st);
+    if (rc) return rc;
+    add = m->shared.p;
+  }
+  return xft_moe_combine(m->ys.as<float>(), m->pos.as<int>(), k, nullptr, add, H, output, nullptr, T, H, st);
+}
+
 }  // namespace xft

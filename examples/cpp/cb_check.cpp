@@ -12,6 +12,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <map>
+#include <memory>
 #include <random>
 #include <stdexcept>
 #include <string>
@@ -125,7 +126,31 @@ int main(int argc, char** argv) {
       }
       ++step;
     }
-    int bad = 0;
+    // pass 3: the AbstractDecoder view (xft/abstract_decoder.h).  Two copies of prompt 0 run as a (batch 1, beam 2)
+    // step; after the first token the two rows are swapped with reorderCache, which must not change what they
+    // generate (both rows hold the same history), and the tokens must equal pass 1.
+    int decoderBad = 0;
+    {
+      std::unique_ptr<xft::AbstractDecoder> dec = xft::makeDecoder(m);
+      const std::vector<int32_t>& p0 = prompts[0];
+      std::vector<int> ids(p0.begin(), p0.end());
+      ids.insert(ids.end(), p0.begin(), p0.end());
+      int64_t dims[3] = {1, 2, (int64_t)p0.size()};
+      std::vector<int> out;
+      for (int t = 0; t < outLen; ++t) {
+        auto [logits, off, size] = dec->forward(ids.data(), dims, t);
+        const int a = argmaxRow(logits, size), b = argmaxRow(logits + size, size);
+        if (off != 0 || size != vocab || a != b) { ++decoderBad; break; }
+        out.push_back(a);
+        if (t == 0) { int swap[2] = {1, 0}; dec->reorderCache(swap, 2); }
+        ids = {a, b};
+        dims[2] = 1;
+      }
+      if ((int)out.size() == outLen && out != alone[0]) ++decoderBad;
+      if (dec->getEndId() < 0 || !dec->isMaster() || dec->getRank() != 0) ++decoderBad;
+      std::printf("decoder view: %s\n", decoderBad ? "MISMATCH" : "identical to the model API");
+    }
+    int bad = decoderBad;
     for (int i = 0; i < nPrompts; ++i) {
       int first = -1;
       for (int t = 0; t < outLen; ++t)

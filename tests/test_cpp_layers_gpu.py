@@ -134,3 +134,38 @@ def test_deepseek_moe_object(fp8):
     torch.cuda.synchronize()
     assert (out2.float() - out.float()).abs().max().item() < 2e-2 * max(1.0, want.abs().max().item())
     lib.xftc_dsmoe_destroy(moe)
+
+
+@pytest.mark.parametrize("routed,shared", [(16, 1), (16, 0), (0, 0)])
+def test_invoke_moe_deepseek_stateless(routed, shared):
+    """invokeMoEDeepSeek: one weight set for every routed expert and the shared expert, DeepSeek-V3 routing constants
+    (include/layers_mlp.h:25 of the reference); routed == 0 is the dense layer."""
+    lib = _core()
+    lib.xftc_invoke_moe_deepseek.restype = C.c_int
+    g = torch.Generator().manual_seed(routed + shared)
+    T, H, I, MI = 21, 256, 384, 128
+    x = (torch.randn(T, H, generator=g) * 0.5).bfloat16()
+    inter = MI if routed else I
+    gate = (torch.randn(H, inter, generator=g) * 0.05).bfloat16()          # [in, out], as the reference passes them
+    up = (torch.randn(H, inter, generator=g) * 0.05).bfloat16()
+    down = (torch.randn(inter, H, generator=g) * 0.05).bfloat16()
+    gw = torch.randn(H, max(routed, 1), generator=g) * 0.3
+    gb = torch.randn(max(routed, 1), generator=g) * 0.1
+    mlp = lambda v: (torch.nn.functional.silu(v @ gate.float()) * (v @ up.float())).bfloat16().float() @ down.float()
+    xf = x.float()
+    if routed:
+        logits = xf @ gw.bfloat16().float()
+        idx, w = R.route_deepseek(logits, gb, 8, 8, 4, 2.5, True, "sigmoid")
+        want = w.sum(-1, keepdim=True) * mlp(xf)
+        if shared:
+            want = want + mlp(xf)
+    else:
+        want = mlp(xf)
+    out = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+    dev = [t.cuda() for t in (x, gw, gb, gate, up, down)]
+    rc = lib.xftc_invoke_moe_deepseek(T, H, I, MI, shared, routed, _p(out), _p(dev[0]), _p(dev[1]), _p(dev[2]), _p(dev[3]),
+                                      _p(dev[4]), _p(dev[5]))
+    assert rc == 0, rc
+    torch.cuda.synchronize()
+    err = (out.float().cpu() - want).abs().max().item()
+    assert err < 3e-2 * max(1.0, want.abs().max().item()), err
