@@ -99,6 +99,24 @@ def run_reference(args):
     return 0
 
 
+def _vs_baseline(model, batch, input_len, n_gpus, dtype, value):
+    """value / the decode tokens/s of the plain PyTorch (cuBLAS + SDPA + NCCL) arm measured on this pool for the same
+    model, batch, prompt length and GPU count (benchmarks/baseline_results.json, written from runs of
+    benchmarks/baseline_torch_nccl.py; the reference itself publishes no number).  None when no such row exists."""
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "benchmarks", "baseline_results.json")
+    try:
+        with open(path) as f:
+            rows = json.load(f)["rows"]
+    except (OSError, ValueError, KeyError):
+        return None
+    for r in rows:
+        c = r.get("config", {})
+        if (c.get("model") == model and c.get("global_batch") == batch and c.get("seq_len") == input_len
+                and r.get("n_gpus") == n_gpus and r.get("dtype", "bf16") == dtype and r.get("value")):
+            return round(value / float(r["value"]), 3)
+    return None
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -215,7 +233,7 @@ def main():
         out = {
             "metric": "decode_tokens_per_s", "value": round(value, 2), "unit": "tokens/s", "n_gpus": world,
             "steps": K, "warmup": args.warmup, "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": args.dtype,
+            "scaling": "strong", "vs_baseline": _vs_baseline(args.model, B, L, world, args.dtype, value), "dtype": args.dtype,
             "data": "synthetic token ids; random-init N(0,0.02) weights of the named architecture",
             "config": {"model": args.model, "global_batch": B, "seq_len": L, "output_len": total_new,
                        "parallelism": (f"dp{world}+ep{world}" if m.ctx.dp_size > 1 else

@@ -182,3 +182,59 @@ def test_converter_cli_picks_the_family(tmp_path, capsys):
         pick(model_type="mamba")
     with pytest.raises(SystemExit):
         main(["-i", src, "--family", "NoSuchConvert"])
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_gptq_checkpoint_conversion_with_wrapped_zero_points(tmp_path, bits):
+    """An AutoGPTQ-format Llama checkpoint written by hand (qweight packed along the input dimension, qzeros holding
+    zero - 1, per-channel scales) goes through LlamaConvert and must reproduce the dense model built from the same
+    dequantised weights.  Half of the channels use a true zero point of 0, which AutoGPTQ stores as all ones
+    (2^bits - 1): the converter has to add the 1 back modulo 2^bits (reference tools/llama_convert.py:360-364)."""
+    import json
+    import numpy as np
+    from safetensors.torch import save_file
+    from transformers import LlamaConfig, LlamaForCausalLM
+    torch.manual_seed(bits)
+    cfg = LlamaConfig(vocab_size=256, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, max_position_embeddings=128, tie_word_embeddings=False)
+    model = LlamaForCausalLM(cfg).eval()
+    sd = {k: v.detach().clone() for k, v in model.state_dict().items()}
+    pack, qmax = 32 // bits, (1 << bits) - 1
+    out = {}
+    for name, w in list(sd.items()):
+        if not (name.endswith("_proj.weight") and ".layers." in name):
+            out[name] = w.contiguous()
+            continue
+        W = w.float().t().contiguous()                                   # [in, out]
+        zero = torch.where(torch.arange(W.shape[1]) % 2 == 0, 0, (qmax + 1) // 2)   # true zero points: 0 or mid-range
+        lo, hi = W.min(0).values, W.max(0).values
+        # zero = 0 channels hold only non-negative levels: shift those channels so they are representable
+        scale = torch.where(zero == 0, (hi - lo).clamp_min(1e-6) / qmax, torch.maximum(hi, -lo).clamp_min(1e-6) / ((qmax - 1) // 2))
+        shift = torch.where(zero == 0, lo, torch.zeros_like(lo))
+        q = torch.clamp(torch.round((W - shift) / scale) + zero, 0, qmax).to(torch.int64)
+        deq = (q - zero).float() * scale                                  # what GPTQ inference computes
+        sd[name] = deq.t().contiguous()                                   # the dense twin uses exactly these weights
+        qw = q.view(W.shape[0] // pack, pack, W.shape[1])
+        packed = sum((qw[:, j, :] << (bits * j)) for j in range(pack))
+        zstore = ((zero - 1) & qmax).view(1, W.shape[1] // pack, pack)   # AutoGPTQ stores zero - 1 (0 -> all ones)
+        zpacked = sum((zstore[:, :, j] << (bits * j)) for j in range(pack))
+        to_i32 = lambda t: torch.from_numpy(t.numpy().astype(np.uint32).view(np.int32).copy())
+        base = name[: -len(".weight")]
+        out[base + ".qweight"], out[base + ".qzeros"] = to_i32(packed), to_i32(zpacked)
+        out[base + ".scales"] = scale.view(1, -1).half()
+        assert int(zstore.max()) == qmax                                 # the all-ones case is present
+    src = tmp_path / "gptq"
+    src.mkdir()
+    save_file(out, str(src / "model.safetensors"))
+    hf = cfg.to_dict()
+    hf["quantization_config"] = {"quant_method": "gptq", "bits": bits, "group_size": -1}
+    (src / "config.json").write_text(json.dumps(hf))
+    dst = str(tmp_path / "xft")
+    assert xft.LlamaConvert().convert(str(src), dst, from_quantized_model="gptq")
+    got = xft.AutoModel.from_pretrained(dst, dtype="int4" if bits == 4 else "int8")(torch.randint(0, 256, (1, 9),
+                                        generator=torch.Generator().manual_seed(1)))
+    model.load_state_dict(sd)
+    ids = torch.randint(0, 256, (1, 9), generator=torch.Generator().manual_seed(1))
+    want = model(ids).logits.float()
+    rel = (got - want).abs().max().item() / want.abs().max().item()
+    assert rel < 3e-2, rel            # fp16 scales are the only rounding left; a wrong zero point is an O(1) error
