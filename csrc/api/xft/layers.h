@@ -55,7 +55,8 @@ int invokeLayerLLaMA(DataType dt, ActivationType at, NormType nt, int batchSize,
 // reference's entry point, ONE gate / up / down weight set (bf16 [in, out] on the device) serves every routed expert and
 // the shared expert, and routing uses DeepSeek-V3's constants (sigmoid + correction bias, 8 groups / 4 kept, top 8,
 // normalised, scaled by 2.5).  gatingWeight fp32 [hidden, experts], gatingBias fp32 [experts] or null.
-// numRoutedExperts == 0: a dense SwiGLU layer of width intermediateSize.  The [out, in] copies are kept per pointer set.
+// numRoutedExperts == 0: a dense SwiGLU layer of width intermediateSize.  The [out, in] copies are kept per set of weight
+// ADDRESSES (as the reference keys its objects): weights must stay at their address, unchanged, while they are in use.
 int invokeMoEDeepSeek(DataType dt, ActivationType at, int numTokens, int hiddenSize, int intermediateSize,
                       int moeIntermediateSize, int numSharedExperts, int numRoutedExperts, void* output, int outputStride,
                       const void* input, int inputStride, const void* gatingWeight, const float* gatingBias,

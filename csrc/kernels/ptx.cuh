@@ -19,6 +19,7 @@ enum : int {
   XFT_ERR_WAIT_TMEM = 3,    // epilogue gave up waiting for the accumulator
   XFT_ERR_WAIT_PEER = 4,    // a flag owned by another rank never arrived
   XFT_ERR_BOUNDS = 5,       // an index derived from a table was out of range (access skipped)
+  XFT_ERR_WAIT_GRID = 6,    // a CTA gave up waiting for the other CTAs of its own grid
 };
 
 // ~2 s at 1.9 GHz; a healthy kernel never gets near it

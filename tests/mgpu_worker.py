@@ -78,6 +78,21 @@ model = xft.AutoModel.from_pretrained(path, dtype="bf16")
 stage("model loaded")
 gi = torch.Generator().manual_seed(1)
 ids = torch.randint(0, 32000, (2, 32), generator=gi)
+# prompt logits of the last position, then one decode step through the CUDA-graph runner: both go to the fp32 oracle
+if rank == 0:
+    sid = model.set_input_cb(ids.tolist(), None, 64)
+    logits0 = model.forward_cb().float().cpu()
+    nxt = logits0.argmax(-1)
+    model.set_input_cb([[int(t)] for t in nxt], sid, 64)
+    logits1 = model.forward_cb().float().cpu()
+    model.free_seqs(sid)
+else:
+    model.set_input_cb()
+    model.forward_cb()
+    model.set_input_cb()
+    model.forward_cb()
+    model.free_seqs()
+stage("logits done")
 tokens = model.generate(ids, max_length=48) if rank == 0 else model.generate()
 stage("generate done")
 N.Workspace.get(dev).check_status()
@@ -85,6 +100,6 @@ m = model.model
 res["fused_calls"] = m.ctx.peer.fused_calls
 res["graph_launches"] = m.runner.graph_launches
 if rank == 0:
-    torch.save({"tokens": tokens, "res": res}, out)
+    torch.save({"tokens": tokens, "res": res, "logits0": logits0, "logits1": logits1, "next": nxt}, out)
 m._closed = True
 dist.barrier(group=ctx.ctrl_group)

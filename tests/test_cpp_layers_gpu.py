@@ -136,6 +136,9 @@ def test_deepseek_moe_object(fp8):
     lib.xftc_dsmoe_destroy(moe)
 
 
+_KEEP = []
+
+
 @pytest.mark.parametrize("routed,shared", [(16, 1), (16, 0), (0, 0)])
 def test_invoke_moe_deepseek_stateless(routed, shared):
     """invokeMoEDeepSeek: one weight set for every routed expert and the shared expert, DeepSeek-V3 routing constants
@@ -163,6 +166,7 @@ def test_invoke_moe_deepseek_stateless(routed, shared):
         want = mlp(xf)
     out = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
     dev = [t.cuda() for t in (x, gw, gb, gate, up, down)]
+    _KEEP.append(dev)       # the entry point keeps [out, in] copies per weight ADDRESS: the weights must stay where they are
     rc = lib.xftc_invoke_moe_deepseek(T, H, I, MI, shared, routed, _p(out), _p(dev[0]), _p(dev[1]), _p(dev[2]), _p(dev[3]),
                                       _p(dev[4]), _p(dev[5]))
     assert rc == 0, rc

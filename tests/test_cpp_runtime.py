@@ -496,6 +496,15 @@ def test_decode_gemm_work_decomposition_covers_every_unit_once():
                 u += kb1 - kb0
                 seg += 1
             assert partial <= 2
+        # the list of split tiles every CTA builds: CTA c >= 1 names the tile its first unit falls into when that unit is
+        # not the tile's first and CTA c - 1 holds the tile's first unit
+        named = []
+        for c in range(1, G):
+            b = bounds[c]
+            t = b // num_kb
+            if b % num_kb != 0 and cta_of(t * num_kb, U, G) == c - 1:
+                named.append(t)
+        assert named == [t for t in range(n_tiles) if cta_of(t * num_kb, U, G) != cta_of((t + 1) * num_kb - 1, U, G)]
         for tile in range(n_tiles):
             lo, hi = cta_of(tile * num_kb, U, G), cta_of((tile + 1) * num_kb - 1, U, G)
             if lo == hi:

@@ -38,11 +38,19 @@ def test_tp_peer_comm_and_model(world, tmp_path):
     assert got["res"]["graph_launches"] > 0
     tokens = got["tokens"]
     ref = EagerLlama(d)
+    # tensor-parallel logits against the fp32 eager model, within what bf16 activations allow: the prompt's last
+    # position (prefill path) and the step after it (decode graph with the fused GEMM + all-reduce kernels)
+    prompt = tokens[:, :32]
+    want0 = ref.logits(prompt)[:, -1]
+    scale = want0.abs().max().item()
+    assert (got["logits0"] - want0).abs().max().item() < 4e-2 * scale
+    want1 = ref.logits(torch.cat([prompt, got["next"][:, None]], 1))[:, -1]
+    assert (got["logits1"] - want1).abs().max().item() < 4e-2 * scale
     full = ref.logits(tokens[:, :-1])
     for b in range(tokens.shape[0]):
         for t in range(32, tokens.shape[1]):
             row = full[b, t - 1]
-            assert row[tokens[b, t]] >= row.max() - 0.1 * max(1.0, row.abs().max().item()), (b, t)
+            assert row[tokens[b, t]] >= row.max() - 0.05 * max(1.0, row.abs().max().item()), (b, t)
 
 
 def test_pipeline_parallel_two_gpus(tmp_path):

@@ -22,7 +22,7 @@ _ACT = {None: 0, "none": 0, "relu": 1, "silu": 2, "gelu": 3, "gelu_tanh": 3, "ge
 
 STATUS_TEXT = {0: "ok", 1: "producer timed out waiting for a free stage", 2: "MMA warp timed out waiting for TMA data",
                3: "epilogue timed out waiting for the accumulator", 4: "timed out waiting for a peer flag",
-               5: "index out of range (access skipped)"}
+               5: "index out of range (access skipped)", 6: "a CTA timed out waiting for the other CTAs of its grid"}
 
 
 class KernelError(RuntimeError):
@@ -182,7 +182,7 @@ def gemm_bf16(x, w, N, gated=False, dual_off=0, bias=None, act=None, residual=No
         assert r2.stride(1) == 1 and r2.dtype == torch.bfloat16
         ldr = r2.stride(0)
     ws = Workspace.get(x.device)
-    if T <= SK_MAX_TOKENS and force_splits == 0 and _ENV().gemm_streamk:
+    if T <= SK_MAX_TOKENS and force_splits == 0 and _sk_choice(T, N, K, gated):
         _gemm_sk(x2, ldx, w, out, T, N, K, gated, dual_off, bias, r2, ldr, res_scale, act, row_scale, None, None, None)
         return out
     if _ENV().gemm_persistent and T > 128 and gated and not fp32 and row_scale is None and out.stride(1) == 1 \
@@ -219,6 +219,25 @@ class SkQkv(C.Structure):
                 ("table", C.c_void_p), ("rot", C.c_int), ("style", C.c_int), ("rot_off", C.c_int), ("max_pos", C.c_int),
                 ("q_scale", C.c_void_p), ("kc", C.c_void_p), ("vc", C.c_void_p), ("bs", C.c_int),
                 ("nslots", C.c_longlong), ("slots", C.c_void_p)]
+
+
+_sk_choices: Dict[tuple, int] = {}
+
+
+def _sk_choice(T, N, K, gated) -> int:
+    """Which kernel runs this decode-size product: 0 = the tile-per-CTA kernel (gemm_sm100.cu), otherwise the kernel of
+    gemm_decode_sm100.cu (1 = balanced stream, s >= 2 = clusters of s CTAs per tile); see xft_gemm_sk_choice."""
+    if not _ENV().gemm_streamk:
+        return 0
+    key = (pick_bn(T), N, K, bool(gated))
+    c = _sk_choices.get(key)
+    if c is None:
+        c = _sk_choices[key] = int(lib().xft_gemm_sk_choice(T, N, K, int(gated), 0))
+    return c
+
+
+def pick_bn(T: int) -> int:
+    return 16 if T <= 16 else 32 if T <= 32 else 64 if T <= 64 else 128 if T <= 128 else 256
 
 
 def _gemm_sk(x2, ldx, w, out, T, N, K, gated, dual_off, bias, r2, ldr, res_scale, act, row_scale, rms_eps, comm, qkv):
@@ -296,7 +315,7 @@ def linear_rms(x, W, eps, bias=None, act=None, gated=False, out_dtype=None):
     assert w.dtype == torch.bfloat16 and w.stride(1) == 1 and w.shape[1] == K and x2.dtype == torch.bfloat16
     fp32 = out_dtype == torch.float32
     out = torch.empty(T, N, dtype=torch.float32 if fp32 else torch.bfloat16, device=x.device)
-    if _ENV().gemm_streamk:
+    if _sk_choice(T, N, K, gated):
         _gemm_sk(x2, ldx, w, out, T, N, K, gated, N if gated else 0, bias, None, 0, 1.0, act, None, eps, None, None)
         return out.view(*x.shape[:-1], N)
     ws = Workspace.get(x.device)
@@ -431,6 +450,17 @@ def paged_attention(q, kc, vc, block_table, cu_q, kv_lens, scale, ks=None, vs=No
         if nsplit > 1:
             po, pm = ws.attn_partials(B * hq * nsplit * D, B * hq * nsplit * 2)
     q = q.contiguous()
+    if (not decode and D == 128 and bs == 64 and ks is None and slopes is None and pl is None and kc.dtype == torch.bfloat16
+            and max_q >= _ENV().attn_tc_min_q):
+        # prompt phase on the tcgen05 tensor cores (csrc/kernels/attention_prefill_sm100.cu)
+        L = lib()
+        L.xft_attn_prefill_tc.restype = C.c_int
+        rc = L.xft_attn_prefill_tc(_p(q), _p(out), _p(kc), _p(vc), _p(block_table), block_table.stride(0), _p(cu_dev),
+                                   _p(kv_dev), B, T, max_q, hq, hkv, g, q_off, bs, nb, C.c_float(scale), _p(ws.status),
+                                   _stream())
+        _check(rc, "attn_prefill_tc")
+        ws.launches += 1
+        return out
     rc = lib().xft_paged_attention(_p(q), _p(out), _p(kc), _p(vc), _p(ks), _p(vs), _p(block_table),
                                    block_table.stride(0), _p(cu_dev), _p(kv_dev), B, max_q, hq, hkv, g, q_off, D, bs,
                                    nb, C.c_float(scale), _p(slopes), _p(pl), (1 if _ENV().attn_tma else 2) if decode else 0, nsplit, _p(po), _p(pm),

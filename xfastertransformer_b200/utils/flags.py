@@ -71,6 +71,9 @@ class Env:
         self.gemm_persistent = _int("XFT_GEMM_PERSISTENT", 0) != 0     # prefill GEMMs through the persistent kernel
         # decode-size bf16 GEMMs (up to 64 tokens) through the balanced weight-stream kernel (gemm_decode_sm100.cu);
         # XFT_FUSE_QKV_ROPE: RoPE + cache append as the epilogue of the QKV product (head_dim 128, bf16 cache)
+        # prompt attention through the tcgen05 kernel from this many query rows on (head_dim 128, bf16 cache, no ALiBi);
+        # a very large value switches it off
+        self.attn_tc_min_q = _int("XFT_ATTN_TC_MIN_Q", 2)
         self.gemm_streamk = _int("XFT_GEMM_STREAMK", 1) != 0
         self.fuse_qkv_rope = _int("XFT_FUSE_QKV_ROPE", 1) != 0
         # tensor-parallel prefill: two groups of prompts are interleaved block by block, so that the all-reduce of one
