@@ -36,6 +36,10 @@ PREFILL = [
     ("70b tp1 qkv   t8192", 8192, 10240, 8192, False), ("70b tp1 gateup t8192", 8192, 28672, 8192, True),
     ("70b tp1 down  t8192", 8192, 8192, 28672, False), ("70b tp8 gateup t8192", 8192, 3584, 8192, True),
     ("7b  tp1 qkv   t4096", 4096, 12288, 4096, False),
+    # tensor-parallel slices: the row-parallel products have a short reduction, so the epilogue weighs most
+    ("70b tp8 qkv   t8192", 8192, 1280, 8192, False), ("70b tp8 o     t8192", 8192, 8192, 1024, False),
+    ("70b tp8 down  t8192", 8192, 8192, 3584, False), ("70b tp2 o     t8192", 8192, 8192, 4096, False),
+    ("70b tp2 down  t8192", 8192, 8192, 14336, False), ("70b tp4 down  t8192", 8192, 8192, 7168, False),
 ]
 
 

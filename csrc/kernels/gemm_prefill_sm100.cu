@@ -422,6 +422,235 @@ __global__ void __launch_bounds__(192, 1) gemm_prefill_kernel(const __grid_const
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// Token-major form (one GPU, or the local product in front of a library collective).  Same pipeline, but the operands
+// trade places: the 128 rows of the MMA are 128 TOKENS (A = the activation tile) and its columns are BNF output features
+// (B = the weight tile), so the accumulator is [token lane][feature column] — the layout of Y itself.  Each epilogue
+// thread owns one token row and handles 16 consecutive features per step: bias and residual arrive as 16-byte vectors
+// and the result leaves as two 16-byte stores, instead of one 2-byte store per element in the feature-major form, whose
+// epilogue (a dependent chain per element on four warps) took ten times longer than the main loop of the short-K
+// row-parallel products.  Gated form: gate and up accumulators of 128 features each, act(gate) * up on the way out.
+template <int BNF, bool DUAL>
+__global__ void __launch_bounds__(192, 1) gemm_prefill_tm_kernel(const __grid_constant__ CUtensorMap tmX,
+                                                                 const __grid_constant__ CUtensorMap tmW,
+                                                                 const PrefillParams p) {
+  constexpr int A_BYTES = 128 * 64 * 2;                  // 128 tokens x 64 k
+  constexpr int B_BYTES = BNF * 64 * 2;                  // BNF features x 64 k
+  constexpr int NACC = DUAL ? 2 : 1;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES * NACC;
+  constexpr uint32_t TMEM_COLS = 2 * BNF * NACC;         // double-buffered accumulators
+  constexpr uint32_t IDESC = umma_idesc(128, BNF, 1, 1, 1);
+  static_assert((BNF == 256 && !DUAL) || (BNF == 128 && DUAL), "feature tile of the token-major kernel");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t full_bar[kPrefillMaxStages], empty_bar[kPrefillMaxStages], tmem_full[2], tmem_empty[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int s_abort_mem;
+  volatile int* s_abort = &s_abort_mem;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int stages = p.stages;
+  const int total = p.n_tiles * p.t_tiles;               // n_tiles: feature tiles of BNF, t_tiles: token blocks of 128
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 4);
+    }
+    s_abort_mem = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_s, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint64_t hint = kEvictNormal;
+      int it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
+        int nt, blk;
+        decode_item(p, item, nt, blk);
+        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+          const int s = it % stages;
+          const uint32_t ph = (it / stages) & 1;
+          if (*s_abort || !mbar_wait_or_abort(&empty_bar[s], ph ^ 1, p.status, XFT_ERR_WAIT_EMPTY, s_abort)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          uint8_t* a = smem + s * STAGE_BYTES;
+          tma_load_2d(a, &tmX, &full_bar[s], kb * 64, blk * 128, hint);
+          tma_load_2d(a + A_BYTES, &tmW, &full_bar[s], kb * 64, nt * BNF, hint);
+          if (DUAL) tma_load_2d(a + A_BYTES + B_BYTES, &tmW, &full_bar[s], kb * 64, p.dual_off + nt * BNF, hint);
+        }
+      }
+      if (!ok) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {}
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int it = 0, lt = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++lt) {
+        const int a = lt & 1;
+        const uint32_t aph = (lt >> 1) & 1;
+        if (*s_abort || !mbar_wait_or_abort(&tmem_empty[a], aph ^ 1, p.status, XFT_ERR_WAIT_TMEM, s_abort)) break;
+        tcgen05_fence_after();
+        const uint32_t acc = tmem_base + (uint32_t)(a * BNF * NACC);
+        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+          const int s = it % stages;
+          const uint32_t ph = (it / stages) & 1;
+          if (!mbar_wait_or_abort(&full_bar[s], ph, p.status, XFT_ERR_WAIT_FULL, s_abort)) {
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+          const uint64_t adesc = umma_desc_k128(a_addr);                      // tokens
+          const uint64_t bdesc = umma_desc_k128(a_addr + A_BYTES);            // features (gate)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            umma_bf16(acc, adesc + 2 * k, bdesc + 2 * k, IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+            if (DUAL) {
+              const uint64_t b1desc = umma_desc_k128(a_addr + A_BYTES + B_BYTES);
+              umma_bf16(acc + BNF, adesc + 2 * k, b1desc + 2 * k, IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+            }
+          }
+          tcgen05_commit(&empty_bar[s]);
+        }
+        if (ok) tcgen05_commit(&tmem_full[a]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue: one token row per thread
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const bool vec = (p.N % 8 == 0) && (p.ldo % 8 == 0) && (!p.residual || p.ldr % 8 == 0);
+    int lt = 0;
+    for (int item = blockIdx.x; item < total; item += gridDim.x, ++lt) {
+      int nt, blk;
+      decode_item(p, item, nt, blk);
+      const int a = lt & 1;
+      const uint32_t aph = (lt >> 1) & 1;
+      mbar_wait_or_abort(&tmem_full[a], aph, p.status, XFT_ERR_WAIT_TMEM, s_abort);
+      if (named_bar_or(1, 128, *s_abort != 0)) break;
+      tcgen05_fence_after();
+      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + (uint32_t)(a * BNF * NACC);
+      const int t = blk * 128 + row;
+      const bool t_ok = t < p.T;
+      __nv_bfloat16* orow = p.out + (size_t)t * p.ldo;
+      const __nv_bfloat16* rrow = p.residual ? p.residual + (size_t)t * p.ldr : nullptr;
+#pragma unroll 1
+      for (int c = 0; c < BNF; c += 16) {
+        uint32_t v[16];
+        uint32_t vu[DUAL ? 16 : 1];
+        tmem_ld16(taddr + c, v);
+        if constexpr (DUAL) tmem_ld16(taddr + BNF + c, vu);
+        tmem_ld_wait();
+        if (c + 16 >= BNF) {
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[a]);
+        }
+        const int n0 = nt * BNF + c;
+        if (!t_ok || n0 >= p.N) continue;
+        float x[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) x[j] = __uint_as_float(v[j]);
+        const bool full = vec && n0 + 16 <= p.N;
+        if (p.bias) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) if (full || n0 + j < p.N) x[j] += __ldg(p.bias + n0 + j);
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) x[j] = prefill_act(x[j], p.act);
+        if constexpr (DUAL) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float u = __uint_as_float(vu[j]);
+            if (p.bias && (full || n0 + j < p.N)) u += __ldg(p.bias + p.dual_off + n0 + j);
+            x[j] *= u;
+          }
+        }
+        if (full) {
+          if (rrow) {
+            const uint4 r0 = *reinterpret_cast<const uint4*>(rrow + n0), r1 = *reinterpret_cast<const uint4*>(rrow + n0 + 8);
+            const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&r0);
+            const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&r1);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f0 = __bfloat1622float2(h0[j]), f1 = __bfloat1622float2(h1[j]);
+              x[2 * j] += p.res_scale * f0.x; x[2 * j + 1] += p.res_scale * f0.y;
+              x[8 + 2 * j] += p.res_scale * f1.x; x[8 + 2 * j + 1] += p.res_scale * f1.y;
+            }
+          }
+          uint32_t w[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const __nv_bfloat162 b = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
+            w[j] = *reinterpret_cast<const uint32_t*>(&b);
+          }
+          *reinterpret_cast<uint4*>(orow + n0) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(orow + n0 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (n0 + j < p.N) {
+              float y = x[j];
+              if (rrow) y += p.res_scale * __bfloat162float(rrow[n0 + j]);
+              orow[n0 + j] = __float2bfloat16(y);
+            }
+          }
+        }
+      }
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int BNF, bool DUAL>
+static int launch_prefill_tm(const CUtensorMap& tmX, const CUtensorMap& tmW, PrefillParams& p, int num_ctas,
+                             cudaStream_t st) {
+  constexpr int STAGE_BYTES = 128 * 64 * 2 + BNF * 64 * 2 * (DUAL ? 2 : 1);
+  int stages = (196 * 1024) / STAGE_BYTES;
+  if (stages > kPrefillMaxStages) stages = kPrefillMaxStages;
+  p.stages = stages;
+  const size_t smem = (size_t)stages * STAGE_BYTES + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_prefill_tm_kernel<BNF, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return 3000 + (int)cudaGetLastError();
+    attr_set = true;
+  }
+  const int total = p.n_tiles * p.t_tiles;
+  const int grid = total < num_ctas ? total : num_ctas;
+  gemm_prefill_tm_kernel<BNF, DUAL><<<grid, 192, smem, st>>>(tmX, tmW, p);
+  return (int)cudaGetLastError();
+}
+
 template <int BN, bool DUAL>
 static int launch_prefill(const CUtensorMap& tmW, const CUtensorMap& tmX, PrefillParams& p, int num_ctas,
                           cudaStream_t st) {
@@ -544,4 +773,34 @@ extern "C" int xft_bulk_ar_layout(long long* out, int n) {
   const int m = (int)(sizeof(v) / sizeof(v[0]));
   for (int i = 0; i < m && i < n; ++i) out[i] = v[i];
   return m;
+}
+
+// Token-major persistent GEMM (see gemm_prefill_tm_kernel): Y[T, N] = act(X W^T + bias) [* (X Wu^T + bias_u)] +
+// res_scale * residual, bf16.  gated != 0: gate rows [0, N) and up rows [dual_off, dual_off + N) of W.
+extern "C" int xft_gemm_bf16_prefill_tm(const void* X, int ldx, const void* W, int w_rows, int ldw, void* Y, int ldo, int T,
+                                        int N, int K, int gated, int dual_off, const float* bias, const void* residual,
+                                        int ldr, float res_scale, int act, int* status, int num_ctas, cudaStream_t st) {
+  if (T <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K & 7) || (ldx & 7) || (ldw & 7)) return -2;
+  PrefillParams p{};
+  p.N = N; p.T = T; p.K = K; p.out = reinterpret_cast<__nv_bfloat16*>(Y); p.ldo = ldo; p.bias = bias;
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(residual); p.ldr = ldr; p.res_scale = res_scale; p.act = act;
+  p.status = status; p.dual_off = dual_off;
+  const int bnf = gated ? 128 : 256;
+  p.n_tiles = (N + bnf - 1) / bnf;
+  p.t_tiles = (T + 127) / 128;
+  p.num_kb = (K + 63) / 64;
+  p.gn = 8;
+  if (num_ctas <= 0) {
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    num_ctas = sms > 0 ? sms : 148;
+  }
+  CUtensorMap tmW, tmX;
+  int r = make_tensor_map(&tmW, W, (uint64_t)w_rows, (uint64_t)K, (uint64_t)ldw, (uint32_t)bnf, 2);
+  if (r) return 1000 - r;
+  r = make_tensor_map(&tmX, X, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, 128, 2);
+  if (r) return 2000 - r;
+  return gated ? launch_prefill_tm<128, true>(tmX, tmW, p, num_ctas, st) : launch_prefill_tm<256, false>(tmX, tmW, p, num_ctas, st);
 }

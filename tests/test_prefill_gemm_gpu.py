@@ -122,3 +122,32 @@ def test_fused_prefill_gemm_allreduce(world, wide, tmp_path):
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     got = torch.load(out)
     assert got["calls"] >= 12 and got["worst"] < 6e-2
+
+
+@pytest.mark.parametrize("T,N,K,gated", [(130, 256, 128, False), (260, 200, 64, False), (300, 1288, 768, False),
+                                         (8192, 1024, 512, False), (1000, 1408, 512, True), (4096, 3584, 1024, True),
+                                         (257, 136, 72, True)])
+def test_token_major_prefill_gemm_matches_fp32(T, N, K, gated):
+    """Token-major persistent kernel (the default for more than 128 tokens): tokens on the MMA rows, features on its
+    columns, vector epilogue; partial token blocks, feature tiles that are not full, N not a multiple of 16."""
+    from xfastertransformer_b200.ops import native as N_
+    g = torch.Generator().manual_seed(T + N + K)
+    x = (torch.randn(T, K, generator=g) * 0.5).bfloat16().cuda()
+    rows = 2 * N if gated else N
+    w = (torch.randn(rows, K, generator=g) * 0.05).bfloat16().cuda()
+    bias = (torch.randn(rows, generator=g) * 0.1).cuda()
+    res = None if gated else torch.randn(T, N, generator=g).bfloat16().cuda()
+    y = x.float() @ w.float().t() + bias
+    if gated:
+        want = torch.nn.functional.silu(y[:, :N]) * y[:, N:]
+    else:
+        want = torch.nn.functional.gelu(y, approximate="tanh") + 0.5 * res.float()
+    N_._ENV().gemm_prefill_tm, N_._ENV().gemm_prefill_tm_all = True, True      # every shape through the token-major kernel
+    got = N_.gemm_bf16(x, w, N, gated=gated, dual_off=N if gated else 0, bias=bias, act="silu" if gated else "gelu",
+                       residual=res, res_scale=0.5)
+    torch.cuda.synchronize()
+    N_.Workspace.get(x.device).check_status()
+    err = (got.float() - want).abs()
+    assert bool((err <= 3e-2 + 2e-2 * want.abs()).all()), err.max().item()
+    assert torch.equal(got, N_.gemm_bf16(x, w, N, gated=gated, dual_off=N if gated else 0, bias=bias,
+                                         act="silu" if gated else "gelu", residual=res, res_scale=0.5))

@@ -185,6 +185,21 @@ def gemm_bf16(x, w, N, gated=False, dual_off=0, bias=None, act=None, residual=No
     if T <= SK_MAX_TOKENS and force_splits == 0 and _sk_choice(T, N, K, gated):
         _gemm_sk(x2, ldx, w, out, T, N, K, gated, dual_off, bias, r2, ldr, res_scale, act, row_scale, None, None, None)
         return out
+    # measured on B200 (benchmarks/bench_gemm.py --shapes prefill): the token-major kernel wins wherever the epilogue
+    # weighs (reductions up to 8192, ungated); long reductions and the gated form stay on the tile-per-CTA kernel, whose
+    # paired 256 x 256 tiles read fewer operand bytes per FLOP
+    if _ENV().gemm_prefill_tm and T > 128 and not fp32 and row_scale is None and out.stride(1) == 1 \
+            and out.dtype == torch.bfloat16 and (K <= 8192 and not gated or _ENV().gemm_prefill_tm_all):
+        # prompt sizes: persistent token-major kernel (tokens are the MMA rows, so bias / residual / output move as
+        # 16-byte vectors along a token's features; two TMEM accumulators overlap the epilogue with the next tile)
+        L = lib()
+        L.xft_gemm_bf16_prefill_tm.restype = C.c_int
+        rc = L.xft_gemm_bf16_prefill_tm(_p(x2), ldx, _p(w), w.shape[0], w.stride(0), _p(out), out.stride(0), T, N, K,
+                                        int(gated), dual_off, _p(bias), _p(r2), ldr, C.c_float(res_scale), _ACT[act],
+                                        _p(ws.status), 0, _stream())
+        _check(rc, "gemm_bf16_prefill_tm")
+        ws.launches += 1
+        return out
     if _ENV().gemm_persistent and T > 128 and gated and not fp32 and row_scale is None and out.stride(1) == 1 \
             and residual is None:
         # gated form of the persistent kernel: four 128-column accumulators, act(gate) * up on the way out

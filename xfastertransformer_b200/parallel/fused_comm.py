@@ -193,7 +193,9 @@ class PeerComm:
             # balanced weight-stream kernel: finished tiles are pushed to the peers and every CTA reduces its share of
             # the whole output (one-shot up to 16 tokens, reduce-scatter + all-gather above)
             if self._two_shot_env is None:
-                self.gp.two_shot = int(self.world >= 4 and T > 16)
+                # from 4 ranks on the owners reduce and hand the result out (two-shot): the one-shot form makes the
+                # finishing CTAs store every word world times, which costs more than the extra NVLink hop at any size
+                self.gp.two_shot = int(self.world >= 4)
             if fp32:
                 self.gp.two_shot = 0
             N._gemm_sk(x2, ldx, W.w, out, T, n, K, False, 0, bias, r2, ldr, res_scale, act, None, None, self.gp, None)

@@ -69,6 +69,9 @@ class Env:
         self.attn_tma = _int("XFT_ATTN_TMA", 1) != 0      # bf16 decode attention through the TMA ring kernel
         self.attn_splits = _int("XFT_ATTN_SPLITS", 0)     # decode split-KV factor; 0 = planned per launch
         self.gemm_persistent = _int("XFT_GEMM_PERSISTENT", 0) != 0     # prefill GEMMs through the persistent kernel
+        # prompt-size bf16 GEMMs (more than 128 tokens) through the persistent token-major kernel
+        self.gemm_prefill_tm = _int("XFT_GEMM_PREFILL_TM", 1) != 0
+        self.gemm_prefill_tm_all = _int("XFT_GEMM_PREFILL_TM", 1) == 2     # 2: also gated and long-K products
         # decode-size bf16 GEMMs (up to 64 tokens) through the balanced weight-stream kernel (gemm_decode_sm100.cu);
         # XFT_FUSE_QKV_ROPE: RoPE + cache append as the epilogue of the QKV product (head_dim 128, bf16 cache)
         # prompt attention through the tcgen05 kernel from this many query rows on (head_dim 128, bf16 cache, no ALiBi);
