@@ -575,7 +575,9 @@ __global__ void __launch_bounds__(160, (HD <= 128 ? 2 : 1)) attn_decode_tma_kern
   }
   if (warp == 4 && lane == 0) { tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); }
   grid_dep_launch();
-  grid_dep_wait();
+  // Until grid_dep_wait() below only step inputs are read (lengths, block table: written before the first kernel of
+  // the step) and cache rows of EARLIER tokens; the query and the newest token's K / V row come from the kernel in
+  // front of this one and are touched after the wait.
   const int b = blockIdx.x;
   const int qchunks = (p.group + 15) / 16;
   const int kvh = blockIdx.y / qchunks, qc = blockIdx.y % qchunks;
@@ -593,8 +595,6 @@ __global__ void __launch_bounds__(160, (HD <= 128 ? 2 : 1)) attn_decode_tma_kern
   const int* bt = p.block_table + (size_t)b * p.bt_stride;
   const int tiles_per_block = p.bs / KT;
 
-  if (tid < 128) load_tile_bf16<HD, 128>(qs, p.q + ((size_t)tok * p.hq + h_lo) * HD, HD, 16, nq, tid);
-  cp_async_commit();
   const int blk_first = t_begin / tiles_per_block;
   const int nblk = nloc > 0 ? (t_end - 1) / tiles_per_block - blk_first + 1 : 0;
   for (int i = tid; i < min(nblk, kDecMaxBlocks); i += 160) {
@@ -602,6 +602,36 @@ __global__ void __launch_bounds__(160, (HD <= 128 ? 2 : 1)) attn_decode_tma_kern
     if (blk < 0 || blk >= p.num_blocks) { if (p.status) atomicCAS(p.status, 0, XFT_ERR_BOUNDS); blk = 0; }
     s_blk[i] = blk;
   }
+  __syncthreads();
+  // tiles of this slice that cannot hold the token appended in this step: their loads start before the kernel in
+  // front has finished (the first STAGES tiles find their stage free without a wait)
+  const int newest_tile = (kv_len - 1) / KT;
+  const int npre = max(0, min(min(STAGES, nloc), newest_tile - t_begin));
+  auto issue_tile = [&](int n) {
+    const int st = n % STAGES;
+    const int ti = t_begin + n;
+    const int bi = ti / tiles_per_block - blk_first;
+    int blk;
+    if (bi < kDecMaxBlocks) {
+      blk = s_blk[bi];
+    } else {
+      blk = bt[blk_first + bi];
+      if (blk < 0 || blk >= p.num_blocks) { if (p.status) atomicCAS(p.status, 0, XFT_ERR_BOUNDS); blk = 0; }
+    }
+    const int row = (blk * p.hkv + kvh) * p.bs + (ti % tiles_per_block) * KT;
+    bf16* kt = ring + (size_t)st * 2 * TILE;
+    mbar_expect_tx(&full_bar[st], STAGE_BYTES);
+#pragma unroll
+    for (int h = 0; h < HD / 64; ++h) {
+      tma_load_2d(kt + h * KT * 64, &tmK, &full_bar[st], h * 64, row, kEvictFirst);
+      tma_load_2d(kt + TILE + h * KT * 64, &tmV, &full_bar[st], h * 64, row, kEvictFirst);
+    }
+  };
+  if (warp == 4 && lane == 0)
+    for (int n = 0; n < npre; ++n) issue_tile(n);
+  grid_dep_wait();
+  if (tid < 128) load_tile_bf16<HD, 128>(qs, p.q + ((size_t)tok * p.hq + h_lo) * HD, HD, 16, nq, tid);
+  cp_async_commit();
   cp_async_wait<0>();
   __syncthreads();
 
@@ -609,26 +639,10 @@ __global__ void __launch_bounds__(160, (HD <= 128 ? 2 : 1)) attn_decode_tma_kern
   wa.init();
   if (warp == 4) {
     if (lane == 0) {
-      for (int n = 0; n < nloc; ++n) {
+      for (int n = npre; n < nloc; ++n) {
         const int st = n % STAGES;
         if (!mbar_wait(&empty_bar[st], ((n / STAGES) & 1) ^ 1, p.status, XFT_ERR_WAIT_EMPTY)) { s_abort = 1; break; }
-        const int ti = t_begin + n;
-        const int bi = ti / tiles_per_block - blk_first;
-        int blk;
-        if (bi < kDecMaxBlocks) {
-          blk = s_blk[bi];
-        } else {
-          blk = bt[blk_first + bi];
-          if (blk < 0 || blk >= p.num_blocks) { if (p.status) atomicCAS(p.status, 0, XFT_ERR_BOUNDS); blk = 0; }
-        }
-        const int row = (blk * p.hkv + kvh) * p.bs + (ti % tiles_per_block) * KT;
-        bf16* kt = ring + (size_t)st * 2 * TILE;
-        mbar_expect_tx(&full_bar[st], STAGE_BYTES);
-#pragma unroll
-        for (int h = 0; h < HD / 64; ++h) {
-          tma_load_2d(kt + h * KT * 64, &tmK, &full_bar[st], h * 64, row, kEvictFirst);
-          tma_load_2d(kt + TILE + h * KT * 64, &tmV, &full_bar[st], h * 64, row, kEvictFirst);
-        }
+        issue_tile(n);
       }
     }
   } else {

@@ -108,6 +108,54 @@ __global__ void __launch_bounds__(NT) rmsnorm_kernel(const bf16* __restrict__ x,
   }
 }
 
+// The same for rows of at most NT * 8 * CH elements (every hidden size in use): each thread keeps its CH chunks of
+// eight values in registers between the two passes, so a row is read once and written once with nothing staged in
+// shared memory.  A warp owns a row when the row is short enough (NT = 32), else a CTA of NT threads.
+template <int NT, int CH>
+__global__ void __launch_bounds__(NT) rmsnorm_reg_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ res,
+                                                         int ldr, const float* __restrict__ w, bf16* __restrict__ y, int ldy,
+                                                         bf16* __restrict__ h_out, int H, float eps) {
+  __shared__ float sh[NT / 32];
+  grid_dep_launch();
+  grid_dep_wait();
+  const int t = blockIdx.x;
+  const bf16x8* xp = reinterpret_cast<const bf16x8*>(x + (size_t)t * ldx);
+  const bf16x8* rp = res ? reinterpret_cast<const bf16x8*>(res + (size_t)t * ldr) : nullptr;
+  const int nch = H / 8;
+  bf16x8 v[CH];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int i = threadIdx.x + c * NT;
+    if (i < nch) {
+      v[c] = xp[i];
+      if (rp) {
+        const bf16x8 r = rp[i];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[c].v[j] = __float2bfloat16(__bfloat162float(v[c].v[j]) + __bfloat162float(r.v[j]));
+        if (h_out) reinterpret_cast<bf16x8*>(h_out + (size_t)t * H)[i] = v[c];
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { const float f = __bfloat162float(v[c].v[j]); ss += f * f; }
+    }
+  }
+  ss = block_sum<NT / 32>(ss, sh);
+  const float inv = rsqrtf(ss / H + eps);
+  bf16x8* yp = reinterpret_cast<bf16x8*>(y + (size_t)t * ldy);
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int i = threadIdx.x + c * NT;
+    if (i < nch) {
+      const float4 w0 = __ldg(reinterpret_cast<const float4*>(w) + 2 * i), w1 = __ldg(reinterpret_cast<const float4*>(w) + 2 * i + 1);
+      const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      bf16x8 o;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o.v[j] = __float2bfloat16(__bfloat162float(v[c].v[j]) * inv * wv[j]);
+      yp[i] = o;
+    }
+  }
+}
+
 template <int NT>
 __global__ void __launch_bounds__(NT) layernorm_kernel(const bf16* __restrict__ x, int ldx, const float* __restrict__ w,
                                                        const float* __restrict__ b, bf16* __restrict__ y, int ldy, int H,
@@ -329,7 +377,14 @@ extern "C" int xft_rmsnorm(const void* x, int ldx, const void* res, int ldr, con
   if (T <= 0) return 0;
   if (H % 8 || ldx % 8 || ldy % 8 || (res && ldr % 8)) return -1;
   cudaError_t e;
-  if (H >= 2048)
+  const bool w16 = (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+  if (w16 && H >= 2048 && H <= 256 * 8 * 4)
+    e = launch_pdl(rmsnorm_reg_kernel<256, 4>, dim3(T), dim3(256), 0, st, (const bf16*)x, ldx, (const bf16*)res, ldr, w,
+                   (bf16*)y, ldy, (bf16*)h_out, H, eps);
+  else if (w16 && H >= 2048 && H <= 512 * 8 * 4)
+    e = launch_pdl(rmsnorm_reg_kernel<512, 4>, dim3(T), dim3(512), 0, st, (const bf16*)x, ldx, (const bf16*)res, ldr, w,
+                   (bf16*)y, ldy, (bf16*)h_out, H, eps);
+  else if (H >= 2048)
     e = launch_pdl(rmsnorm_kernel<256>, dim3(T), dim3(256), H * sizeof(float), st, (const bf16*)x, ldx, (const bf16*)res,
                    ldr, w, (bf16*)y, ldy, (bf16*)h_out, H, eps);
   else

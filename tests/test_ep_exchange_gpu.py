@@ -1,6 +1,6 @@
 """Data-parallel attention + expert-parallel MoE on 2+ GPUs (XFT_ATTENTION_DP=1): the NCCL all-to-all path and the
 peer-memory exchange kernels (XFT_MOE_FUSED_A2A=1, csrc/kernels/ep_comm.cu) against the single-GPU engine on the same
-checkpoint.  Opt-in until the mode has had its first GPU run: set XFT_TEST_EP_EXCHANGE=1."""
+checkpoint."""
 import os
 import subprocess
 import sys
@@ -8,9 +8,7 @@ import sys
 import pytest
 import torch
 
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("XFT_TEST_EP_EXCHANGE") != "1",
-                                 reason="opt-in mode: set XFT_TEST_EP_EXCHANGE=1")]
+pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 

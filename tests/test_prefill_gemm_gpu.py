@@ -1,6 +1,6 @@
 """The persistent prefill GEMM (csrc/kernels/gemm_prefill_sm100.cu): on one GPU against the fp32 product, and on 2+
-GPUs with the all-reduce fused in.  The kernel is opt-in (XFT_GEMM_PERSISTENT / XFT_PREFILL_FUSED_AR) and so are these
-tests: set XFT_TEST_PREFILL_GEMM=1 to run them."""
+GPUs with the all-reduce fused in (XFT_GEMM_PERSISTENT / XFT_PREFILL_FUSED_AR), and its token-major form, the default
+for prompt-size products."""
 import ctypes as C
 import os
 import subprocess
@@ -9,9 +9,7 @@ import sys
 import pytest
 import torch
 
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("XFT_TEST_PREFILL_GEMM") != "1",
-                                 reason="opt-in kernel: set XFT_TEST_PREFILL_GEMM=1")]
+pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 

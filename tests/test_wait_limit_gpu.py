@@ -1,17 +1,14 @@
 """Failure detection on the device without a fault: a kernel that waits for a peer's word gives up after its limit,
 records a code in the status word and returns, and the context stays usable.  The peer-memory all-reduce is launched
 as rank 0 of 2 on ONE GPU with both receive areas in local memory, so rank 1's words never arrive (nothing sets them)
-and the wait, limited to about a millisecond here, runs out.  Opt-in until the give-up path has had its first GPU run:
-set XFT_TEST_WAIT_LIMIT=1."""
+and the wait, limited to about a millisecond here, runs out."""
 import ctypes as C
 import os
 
 import pytest
 import torch
 
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("XFT_TEST_WAIT_LIMIT") != "1",
-                                 reason="opt-in: set XFT_TEST_WAIT_LIMIT=1")]
+pytestmark = pytest.mark.gpu
 
 
 def test_peer_wait_runs_out_and_reports_through_the_status_word():
