@@ -71,7 +71,40 @@ def time_fn(fn, n_variants, iters):
     return ts[len(ts) // 2]
 
 
-def run(name, T, Nf, K, gated, iters, peaks):
+def kernel_timeline(fn, copies):
+    """Time line of one launch of the decode GEMM (csrc/kernels/gemm_decode_sm100.cu) inside an eager chain of launches
+    over distinct weights: the kernel stamps the GPU's global timer at eight points per CTA (xft_gemm_sk_set_trace);
+    returned are min / median / max over the CTAs in microseconds after the first CTA's entry, plus the exit of the
+    launch in front.  Empty when the product did not go through that kernel."""
+    import ctypes as C
+    lib = N.lib()
+    max_ctas = 320
+    buf = torch.zeros(copies, max_ctas * 8, dtype=torch.int64, device="cuda")
+    torch.cuda.synchronize()
+    for i in range(copies):
+        lib.xft_gemm_sk_set_trace(C.c_void_p(buf[i].data_ptr()))
+        fn(i)
+    lib.xft_gemm_sk_set_trace(C.c_void_p(0))
+    torch.cuda.synchronize()
+    b = buf.cpu().view(copies, max_ctas, 8)
+    i = copies - 2
+    live = b[i][:, 0] > 0
+    if int(live.sum()) == 0:
+        return {}
+    t = b[i][live].double()
+    prev = b[i - 1][b[i - 1][:, 0] > 0]
+    t0 = t[:, 0].min().item()
+    names = ["entry", "setup_done", "dependency_resolved", "first_block_landed", "last_mma_issued", "last_accumulator_ready",
+             "epilogue_done", "exit"]
+    out = {n: [round((f(t[:, k]).item() - t0) / 1e3, 2) for f in (torch.min, torch.median, torch.max)]
+           for k, n in enumerate(names)}
+    out["ctas"] = int(live.sum())
+    if prev.numel():
+        out["previous_exit"] = round((prev[:, 7].max().item() - t0) / 1e3, 2)
+    return out
+
+
+def run(name, T, Nf, K, gated, iters, peaks, timeline=False):
     rows = 2 * Nf if gated else Nf
     wbytes = rows * K * 2
     copies = max(4, min(24, (400 << 20) // wbytes + 1))
@@ -99,6 +132,8 @@ def run(name, T, Nf, K, gated, iters, peaks):
     if peaks:
         rec["hbm_frac_of_measured"] = round(gbs / peaks["hbm_gbs"], 3)
         rec["mma_frac_of_measured"] = round(tf / peaks["bf16_tflops"], 3)
+    if timeline and T <= 64:
+        rec["timeline_us"] = kernel_timeline(ours, copies)
     print(json.dumps(rec), flush=True)
     N.Workspace.get(torch.device("cuda", 0)).check_status()
 
@@ -130,6 +165,7 @@ def main():
     ap.add_argument("--shapes", default="all")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--one", default="")
+    ap.add_argument("--timeline", action="store_true", help="decode shapes: per-CTA time line of one launch")
     a = ap.parse_args()
     peaks = None
     try:
@@ -145,7 +181,7 @@ def main():
         if a.sweep_splits:
             sweep(*s, a.iters)
         else:
-            run(*s, a.iters, peaks)
+            run(*s, a.iters, peaks, a.timeline)
 
 
 if __name__ == "__main__":
