@@ -12,6 +12,7 @@
 #include "env.h"
 #include "rope_tables.h"
 #include "runtime.h"
+#include "tokenizer.h"
 #include "xft/layers.h"
 
 using namespace xft;
@@ -183,6 +184,27 @@ int xftc_dsmoe_forward_selected(void* moe, void* in, void* out, int T, int* idx,
   return xft::forwardDeepSeekMoE(moe, in, out, T, idx, w);
 }
 void xftc_dsmoe_destroy(void* moe) { xft::destroyDeepSeekMoE(moe); }
+
+// ---- SentencePiece model reader (csrc/core/tokenizer.h): handle-based wrappers for tests and bindings
+void* xftc_tok_load(const char* path) {
+  try { return new xft::SentencePieceTokenizer(path); } catch (const std::exception&) { return nullptr; }
+}
+void xftc_tok_free(void* h) { delete static_cast<xft::SentencePieceTokenizer*>(h); }
+int xftc_tok_info(void* h, int what) {
+  auto* t = static_cast<xft::SentencePieceTokenizer*>(h);
+  switch (what) { case 0: return t->vocabSize(); case 1: return t->bosId(); case 2: return t->eosId(); case 3: return t->unkId(); default: return t->isBpe() ? 1 : 0; }
+}
+int xftc_tok_encode(void* h, const char* text, int add_bos, int add_eos, int* out, int cap) {
+  const std::vector<int32_t> ids = static_cast<xft::SentencePieceTokenizer*>(h)->encode(text, add_bos != 0, add_eos != 0);
+  for (int i = 0; i < (int)ids.size() && i < cap; ++i) out[i] = ids[i];
+  return (int)ids.size();
+}
+int xftc_tok_decode(void* h, const int* ids, int n, char* out, int cap) {
+  const std::string s = static_cast<xft::SentencePieceTokenizer*>(h)->decode(std::vector<int32_t>(ids, ids + n));
+  const int m = (int)s.size() < cap - 1 ? (int)s.size() : cap - 1;
+  if (cap > 0) { std::memcpy(out, s.data(), m); out[m] = 0; }
+  return (int)s.size();
+}
 int xftc_invoke_moe_deepseek(int T, int hidden, int inter, int moeInter, int nShared, int nRouted, void* out, const void* in,
                              const void* gatingW, const float* gatingBias, const void* gate, const void* up, const void* down) {
   return xft::invokeMoEDeepSeek(xft::DataType::bf16, xft::SILU, T, hidden, inter, moeInter, nShared, nRouted, out, 0, in, 0,

@@ -1,27 +1,30 @@
-// Command-line generation with the C++ API (reference: examples/cpp/example.cpp:352-545; token ids in, token ids
-// out — tokenisation is left to the caller, as in the reference's `--input_ids` style use).
+// Command-line generation with the C++ API (reference: examples/cpp/example.cpp:352-545).
 //
-//   example -m <model dir> [-t <ignored>] [-d bf16] [--kv_cache_dtype fp16|int8] [-i "1 2 3 4"] [-l input_len]
+//   example -m <model dir> [-t <tokenizer.model>] [-d bf16] [--kv_cache_dtype fp16|int8] [-i "1 2 3 4"] [-l input_len]
 //           [-o out_len] [--prefix_len n] [-n num_beams] [-b batch] [--loop n] [--topK k] [--topP p]
 //           [--temperature t] [--repetPen r] [--do_sample] [--no_stream]
 // Same flag names as the reference.  -l pads the prompt to `input_len` tokens by repeating its third token (the
 // reference's way of making a long prompt for timing); --prefix_len shares the first n prompt tokens between the rows
-// of the batch through Model::setPrefix (whole 64-token blocks).  -t is accepted for command-line compatibility:
-// the prompt is given as ids.
-// Prints the generated ids, first-token latency and average next-token latency (the reference's metrics).
+// of the batch through Model::setPrefix (whole 64-token blocks).  With -t (a SentencePiece model file: Llama, Mistral,
+// Gemma, Yi, Baichuan, ChatGLM families) -i may be TEXT: it is tokenised by the built-in reader (csrc/core/tokenizer.h,
+// BOS prepended) and the generated ids are printed as text too; without -t, or when -i holds only numbers, -i is a list of
+// token ids.  Prints the generated ids / text, first-token latency and average next-token latency (the reference's
+// metrics).
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <iostream>
+#include <memory>
 #include <sstream>
 #include <string>
 #include <vector>
 
+#include "tokenizer.h"
 #include "xft/models.h"
 
 int main(int argc, char** argv) {
-  std::string model, dtype = "bf16", kv = "fp16", input = "1 15043 29892 920 526 366 29973";
+  std::string model, dtype = "bf16", kv = "fp16", input = "1 15043 29892 920 526 366 29973", tokenPath;
   int batch = 1, outLen = 32, loop = 1, topK = 50, numBeams = 1, inputLen = -1, prefixLen = 0;
   float topP = 1.0f, temp = 1.0f, rep = 1.0f;
   bool sample = false, stream = true;
@@ -37,7 +40,7 @@ int main(int argc, char** argv) {
     else if (a == "--loop") loop = std::atoi(next().c_str());
     else if (a == "-l" || a == "--input_len") inputLen = std::atoi(next().c_str());
     else if (a == "--prefix_len") prefixLen = std::atoi(next().c_str());
-    else if (a == "-t" || a == "--token") (void)next();
+    else if (a == "-t" || a == "--token") tokenPath = next();
     else if (a == "--topK") topK = std::atoi(next().c_str());
     else if (a == "-n" || a == "--num_beams") numBeams = std::atoi(next().c_str());
     else if (a == "--topP") topP = (float)std::atof(next().c_str());
@@ -49,8 +52,22 @@ int main(int argc, char** argv) {
   }
   if (model.empty()) { std::fprintf(stderr, "usage: example -m <model dir> [options]\n"); return 2; }
   std::vector<int32_t> prompt;
-  { std::istringstream is(input); int v; while (is >> v) prompt.push_back(v); }
-  if (prompt.empty()) { std::fprintf(stderr, "-i takes token ids separated by spaces\n"); return 2; }
+  std::unique_ptr<xft::SentencePieceTokenizer> tok;
+  const bool numeric = input.find_first_not_of("0123456789 \t") == std::string::npos;
+  try {
+    if (!tokenPath.empty()) tok.reset(new xft::SentencePieceTokenizer(tokenPath));
+  } catch (const std::exception& e) {
+    std::fprintf(stderr, "error: %s\n", e.what());
+    return 1;
+  }
+  if (tok && !numeric) {
+    prompt = tok->encode(input, /*addBos=*/true);
+  } else {
+    std::istringstream is(input);
+    int v;
+    while (is >> v) prompt.push_back(v);
+  }
+  if (prompt.empty()) { std::fprintf(stderr, "-i takes token ids separated by spaces (or text, with -t <tokenizer.model>)\n"); return 2; }
   if (inputLen > (int)prompt.size()) {
     const size_t at = prompt.size() > 2 ? 2 : prompt.size() - 1;
     prompt.insert(prompt.begin() + at, inputLen - prompt.size(), prompt[at]);
@@ -78,7 +95,12 @@ int main(int argc, char** argv) {
         double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
         if (steps == 0) first = ms; else rest += ms;
         ++steps;
-        if (stream && batch == 1 && numBeams == 1) { std::printf("%d ", next[0]); std::fflush(stdout); }
+        if (stream && batch == 1 && numBeams == 1) {
+          // ids stream one by one; text is printed once per run below (pieces only join into characters and words in
+          // context)
+          std::printf("%d ", next[0]);
+          std::fflush(stdout);
+        }
       }
       auto out = m.finalize();
       if (stream && batch == 1 && numBeams == 1) std::printf("\n");
@@ -87,6 +109,10 @@ int main(int argc, char** argv) {
         std::printf("[%d] ", b);
         for (size_t i = prompt.size(); i < w; ++i) std::printf("%d ", out[b * w + i]);
         std::printf("\n");
+        if (tok) {
+          std::vector<int32_t> gen(out.begin() + b * w + prompt.size(), out.begin() + (b + 1) * w);
+          std::printf("[%d] %s\n", b, tok->decode(gen).c_str());
+        }
       }
       std::printf("first token: %.2f ms, next tokens: %.2f ms avg over %d\n", first, steps > 1 ? rest / (steps - 1) : 0.0, steps - 1);
     }

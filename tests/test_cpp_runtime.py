@@ -307,11 +307,13 @@ def test_example_cli_flags_follow_the_reference(core):
     run = lambda *a: subprocess.run([exe, *a], capture_output=True, text=True, timeout=60)
     assert run().returncode == 2
     assert run("-m", "/nonexistent", "--bogus").returncode == 2
-    r = run("-m", "/nonexistent", "-t", "tok", "-i", "1 2 3", "-d", "bf16", "--kv_cache_dtype", "int8", "-l", "2", "-o", "4",
+    r = run("-m", "/nonexistent", "-t", "/nonexistent/tokenizer.model", "-i", "1 2 3")
+    assert r.returncode == 1 and "cannot open tokenizer model" in r.stderr
+    r = run("-m", "/nonexistent", "-i", "1 2 3", "-d", "bf16", "--kv_cache_dtype", "int8", "-l", "2", "-o", "4",
             "--prefix_len", "0", "-n", "2", "-b", "2", "--loop", "1", "--topK", "4", "--temperature", "0.7", "--topP", "0.9",
             "--repetPen", "1.1", "--no_stream", "--do_sample")
     assert r.returncode == 1 and "config.ini" in r.stderr and "input_len 2 is not longer" in r.stderr
-    assert run("-m", "/nonexistent", "-i", "hello").returncode == 2           # the prompt is given as ids
+    assert run("-m", "/nonexistent", "-i", "hello").returncode == 2           # text needs -t <tokenizer.model>
     assert run("-m", "/nonexistent", "-i", "1 2 3", "--prefix_len", "3").returncode == 2
 
 
@@ -520,3 +522,45 @@ def test_decode_gemm_work_decomposition_covers_every_unit_once():
             r0, r1 = (r * E2 + world - 1) // world, ((r + 1) * E2 + world - 1) // world
             assert all(owner[i] == r for i in range(r0, r1))
             assert owner.count(r) == r1 - r0
+
+
+@pytest.mark.parametrize("model_type,byte_fallback", [("bpe", True), ("bpe", False), ("unigram", False), ("unigram", True)])
+def test_cpp_sentencepiece_reader_matches_the_library(core, tmp_path, model_type, byte_fallback):
+    """csrc/core/tokenizer.cc reads a SentencePiece model file and segments text with the file's own algorithm; ids
+    and the decoded text equal the sentencepiece library's on a model trained here (BPE as in Llama / Mistral, unigram as
+    in ChatGLM), with and without byte fallback, including characters outside the vocabulary and repeated spaces."""
+    spm = pytest.importorskip("sentencepiece")
+    words = ("the quick brown fox jumps over the lazy dog while seven wizards quietly mix potions under a pale moon "
+             "tensor kernels stream weights through shared memory and the decoder appends a token to every sequence "
+             "Paris London Tokyo Berlin 2023 2024 3.14159 hello world foo bar baz café naïve über").split()
+    rng = random.Random(0)
+    corpus = tmp_path / "corpus.txt"
+    corpus.write_text("\n".join(" ".join(rng.choice(words) for _ in range(rng.randint(4, 14))) for _ in range(600)))
+    prefix = str(tmp_path / f"tok_{model_type}_{int(byte_fallback)}")
+    spm.SentencePieceTrainer.train(input=str(corpus), model_prefix=prefix, vocab_size=420 if byte_fallback else 180, model_type=model_type,
+                                   byte_fallback=byte_fallback, character_coverage=0.98, normalization_rule_name="identity",
+                                   remove_extra_whitespaces=(model_type == "unigram"), hard_vocab_limit=False, minloglevel=2)
+    sp = spm.SentencePieceProcessor(model_file=prefix + ".model")
+    core.xftc_tok_load.restype = C.c_void_p
+    h = core.xftc_tok_load((prefix + ".model").encode())
+    assert h
+    info = lambda w: core.xftc_tok_info(C.c_void_p(h), w)
+    assert info(0) == sp.get_piece_size() and info(1) == sp.bos_id() and info(2) == sp.eos_id() and info(3) == sp.unk_id()
+    assert info(4) == (1 if model_type == "bpe" else 0)
+    texts = ["the quick brown fox", "hello world", "seven wizards quietly mix potions", "Tokyo 2024  and   Berlin",
+             "unseen zebra xylophone", "café über naïve", "日本語 text with 😀 emoji", "", "a", " leading and trailing "]
+    for t in texts:
+        want = sp.encode(t)
+        out = (C.c_int * 512)()
+        n = core.xftc_tok_encode(C.c_void_p(h), t.encode(), 0, 0, out, 512)
+        got = list(out[:n])
+        assert got == want, (model_type, byte_fallback, t, got, want)
+        buf = C.create_string_buffer(2048)
+        ids = (C.c_int * max(1, len(want)))(*want)
+        core.xftc_tok_decode(C.c_void_p(h), ids, len(want), buf, 2048)
+        assert buf.value.decode("utf-8", "replace") == sp.decode(want), (t, buf.value, sp.decode(want))
+    out = (C.c_int * 16)()
+    n = core.xftc_tok_encode(C.c_void_p(h), b"hello", 1, 1, out, 16)
+    assert out[0] == sp.bos_id() and out[n - 1] == sp.eos_id()
+    core.xftc_tok_free(C.c_void_p(h))
+    assert not core.xftc_tok_load(str(tmp_path / "missing.model").encode())
