@@ -79,3 +79,38 @@ def build_prompt(family: str, history: History, message: str, system: str = "") 
     if family not in FORMATS:
         raise KeyError(f"unknown chat format '{family}'; known: {sorted(FORMATS)}")
     return FORMATS[family](history, message, system) if system else FORMATS[family](history, message)
+
+
+# Per-family settings of the chat demos (the reference's ten demo files differ in exactly these): page title, prompt
+# format, the strings that end an assistant turn besides the tokenizer's EOS (looked up as single tokens), and how many
+# past rounds are put back into the prompt.
+FAMILIES = {
+    "llama2": dict(title="Llama2", chat_format="llama2", stop=["</s>"], max_rounds=2),
+    "llama3": dict(title="Llama3", chat_format="llama3", stop=["<|eot_id|>", "<|end_of_text|>"], max_rounds=8),
+    "qwen": dict(title="Qwen", chat_format="qwen", stop=["<|im_end|>", "<|endoftext|>"], max_rounds=8),
+    "qwen2": dict(title="Qwen2", chat_format="qwen2", stop=["<|im_end|>", "<|endoftext|>"], max_rounds=8),
+    "yi": dict(title="Yi", chat_format="yi", stop=["<|im_end|>", "<|endoftext|>"], max_rounds=8),
+    "chatglm": dict(title="ChatGLM", chat_format="chatglm", stop=["<eop>"], max_rounds=8),
+    "chatglm2": dict(title="ChatGLM2", chat_format="chatglm2", stop=[], max_rounds=8),
+    "chatglm3": dict(title="ChatGLM3", chat_format="chatglm3", stop=["<|user|>", "<|observation|>"], max_rounds=8),
+    "chatglm4": dict(title="ChatGLM4", chat_format="chatglm4", stop=["<|user|>", "<|observation|>", "<|endoftext|>"], max_rounds=8),
+    "baichuan2": dict(title="Baichuan2", chat_format="baichuan2", stop=[], max_rounds=8),
+    "gemma": dict(title="Gemma", chat_format="gemma", stop=["<end_of_turn>"], max_rounds=8),
+}
+
+
+def stop_token_ids(tokenizer, family: str):
+    """Ids of the family's end-of-turn strings that the tokenizer knows as ONE token (others are ignored), plus its EOS."""
+    ids = []
+    unk = getattr(tokenizer, "unk_token_id", None)
+    for s in FAMILIES.get(family, {}).get("stop", []):
+        try:
+            t = tokenizer.convert_tokens_to_ids(s)
+        except Exception:
+            t = None
+        if isinstance(t, int) and t >= 0 and t != unk and t not in ids:
+            ids.append(t)
+    eos = getattr(tokenizer, "eos_token_id", None)
+    if isinstance(eos, int) and eos >= 0 and eos not in ids:
+        ids.append(eos)
+    return ids

@@ -320,6 +320,21 @@ def test_chat_prompt_formats():
     assert P.build_prompt("gemma", [], "x") == "<bos><start_of_turn>user\nx<end_of_turn>\n<start_of_turn>model\n"
     with pytest.raises(KeyError):
         P.build_prompt("nope", [], "x")
+    # per-family demo settings: every family of the reference's demo files has a launcher, a known prompt format, and its
+    # end-of-turn strings resolve to token ids only when the tokenizer knows them as one token
+    for fn, fam in (("Llama2", "llama2"), ("Llama3", "llama3"), ("Qwen", "qwen"), ("Qwen2", "qwen2"), ("Yi", "yi"),
+                    ("ChatGLM", "chatglm"), ("ChatGLM2", "chatglm2"), ("ChatGLM3", "chatglm3"), ("ChatGLM4", "chatglm4"),
+                    ("Baichuan2", "baichuan2"), ("Gemma", "gemma")):
+        src = open(os.path.join(ROOT, "examples", "web_demo", fn + ".py")).read()
+        assert f'main("{fam}")' in src
+        assert P.FAMILIES[fam]["chat_format"] in P.FORMATS and P.FAMILIES[fam]["max_rounds"] >= 1
+
+    class Tok:
+        unk_token_id, eos_token_id = 0, 2
+
+        def convert_tokens_to_ids(self, s):
+            return {"<|eot_id|>": 9}.get(s, 0)
+    assert P.stop_token_ids(Tok(), "llama3") == [9, 2] and P.stop_token_ids(Tok(), "gemma") == [2]
 
 
 def test_bench_reference_arm_prints_unavailable_line():
