@@ -336,7 +336,10 @@ def test_bounded_wait_reports_bad_index_without_faulting():
 
 
 @pytest.mark.parametrize("T,N,K,gated", [(16, 1280, 8192, False), (16, 8192, 1024, False), (5, 896, 2048, True),
-                                         (64, 1024, 3584, False), (33, 640, 512, True), (2, 130, 72, False)])
+                                         (64, 1024, 3584, False), (33, 640, 512, True), (2, 130, 72, False),
+                                         # the planner's balanced-stream mode (few tiles, > 32 MB of weights): tiles shared
+                                         # by more than four CTAs, added up by all CTAs behind the grid-wide wait
+                                         (16, 2560, 8192, False), (7, 1536, 8192, True), (40, 3072, 8192, False)])
 def test_decode_gemm_balanced_stream(T, N, K, gated):
     """Decode-size GEMM whose weight blocks are dealt to the CTAs in equal runs: runs that end inside a tile leave
     partials, the last arriver adds them in CTA order.  Same answer twice (deterministic), counters back at zero, and
@@ -366,15 +369,16 @@ def test_decode_gemm_balanced_stream(T, N, K, gated):
 
 @pytest.mark.parametrize("style,rot_frac,fold", [("half", 1.0, True), ("interleaved", 0.5, False), ("half", 0.5, False)])
 @pytest.mark.parametrize("T", [1, 16, 37])
-def test_qkv_product_with_rope_and_cache_append_epilogue(style, rot_frac, fold, T):
+@pytest.mark.parametrize("hq,hkv,K", [(8, 2, 1024), (16, 2, 8192)])      # cluster mode; balanced stream + grid-wide fixup
+def test_qkv_product_with_rope_and_cache_append_epilogue(style, rot_frac, fold, T, hq, hkv, K):
     """QKV product + split + RoPE + paged cache append as one kernel against the three separate steps of the oracle."""
     from xfastertransformer_b200.ops import native as N_
     from xfastertransformer_b200 import ops
-    hq, hkv, D, bs, nb, K = 8, 2, 128, 64, 6, 1024
+    D, bs, nb = 128, 64, 6
     rot = int(D * rot_frac)
     g = torch.Generator().manual_seed(T)
     x = (torch.randn(T, K, generator=g) * (3.0 if fold else 0.5)).bfloat16()
-    w = (torch.randn((hq + 2 * hkv) * D, K, generator=g) * 0.05).bfloat16()
+    w = (torch.randn((hq + 2 * hkv) * D, K, generator=g) * (0.05 if K <= 1024 else 0.02)).bfloat16()
     bias = torch.randn((hq + 2 * hkv) * D, generator=g) * 0.1
     pos = torch.randint(0, 500, (T,), generator=g, dtype=torch.int32)
     slots = torch.randperm(nb * bs, generator=g)[:T].int()
