@@ -18,6 +18,10 @@ int xft_qkv_rope_cache(const void* qkv, int ldq, int T, int hq, int hkv, int D, 
                        int rot, int style, int rot_off, int max_pos, const float* q_scale, const float* q_norm_w,
                        const float* k_norm_w, float eps, void* q_out, void* kc, void* vc, float* ks, float* vs,
                        int int8_cache, int bs, long long nslots, const int* slots, int* status, cudaStream_t st);
+int xft_qkv_rope2d_cache(const void* qkv, int ldq, int T, int hq, int hkv, int D, const int* positions,
+                         const int* positions2, const float* table, int rot, int max_pos, void* q_out, void* kc,
+                         void* vc, float* ks, float* vs, int int8_cache, int bs, long long nslots, const int* slots,
+                         int* status, cudaStream_t st);
 int xft_rope(void* x, int T, int nh, int D, const int* positions, const float* table, int rot, int style, int rot_off,
              int max_pos, const float* q_scale, int* status, cudaStream_t st);
 int xft_paged_attention(const void* q, void* out, const void* kc, const void* vc, const float* ks, const float* vs,

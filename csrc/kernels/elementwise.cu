@@ -214,6 +214,7 @@ struct RopeCacheParams {
   void* kc; void* vc; float* ks; float* vs; int int8_cache; int bs; long long nslots;
   const int* slots;
   int* status;
+  const int* positions2;      // two-stream rotary (ChatGLM-1): a second rotation of `rot` dims at rot_off + rot, or null
 };
 
 __global__ void __launch_bounds__(128) qkv_rope_cache_kernel(const RopeCacheParams p) {
@@ -257,6 +258,20 @@ __global__ void __launch_bounds__(128) qkv_rope_cache_kernel(const RopeCachePara
       const float x1 = v[a], x2 = v[b];
       v[a] = x1 * c - x2 * s;
       v[b] = x2 * c + x1 * s;
+    }
+    if (p.positions2) {
+      int pos2 = p.positions2[t];
+      if (pos2 < 0 || pos2 >= p.max_pos) { if (lane == 0 && p.status) atomicCAS(p.status, 0, XFT_ERR_BOUNDS); pos2 = 0; }
+      const float* cs2 = p.table + (size_t)pos2 * p.rot;
+      const int off2 = p.rot_off + p.rot;
+      for (int i = lane; i < half; i += 32) {
+        const float c = cs2[i], s = cs2[half + i];
+        const int a = off2 + (p.style == 0 ? i : 2 * i);
+        const int b = off2 + (p.style == 0 ? i + half : 2 * i + 1);
+        const float x1 = v[a], x2 = v[b];
+        v[a] = x1 * c - x2 * s;
+        v[b] = x2 * c + x1 * s;
+      }
     }
     __syncwarp();
   }
@@ -325,6 +340,68 @@ __global__ void latent_write_kernel(const bf16* __restrict__ latent, int ld, bf1
   const long long slot = slots[t];
   if (slot < 0 || slot >= nslots) { if (threadIdx.x == 0 && status) atomicCAS(status, 0, XFT_ERR_BOUNDS); return; }
   for (int d = threadIdx.x; d < W; d += blockDim.x) cache[(size_t)slot * W + d] = latent[(size_t)t * ld + d];
+}
+
+// Everything between the MLA projections and the MLA attention kernel in one launch (reference: the QKPO + cache-store
+// steps of DeepSeekAttention, src/layers/attention_deepseek.h): one warp per (token, head) splits a query head into its
+// no-position part [nope] and its rotated part [rope] (interleaved pairs); one more warp per token RMS-normalises the
+// compressed KV [kvl], rotates the shared key part [rope] and stores both as the token's latent row in the paged cache.
+struct MlaPrepParams {
+  const bf16* q; int ldq;            // [T, Hl * (nope + rope)]
+  const bf16* kv; int ldkv;          // [T, kvl + rope]
+  int T, Hl, nope, rope, kvl;
+  const int* positions; const float* table; int max_pos;      // table [max_pos, rope] = cos(rope/2) ‖ sin(rope/2)
+  const float* kv_norm_w; float eps;
+  bf16* q_nope; bf16* q_rope;        // [T, Hl, nope], [T, Hl, rope]
+  bf16* cache; long long nslots; const int* slots;            // [nslots, kvl + rope]
+  int* status;
+};
+
+__global__ void __launch_bounds__(128) mla_prep_kernel(const MlaPrepParams p) {
+  grid_dep_launch();
+  grid_dep_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long gw = (long long)blockIdx.x * 4 + warp;
+  if (gw >= (long long)p.T * (p.Hl + 1)) return;
+  const int t = (int)(gw / (p.Hl + 1)), h = (int)(gw % (p.Hl + 1));
+  int pos = p.positions[t];
+  if (pos < 0 || pos >= p.max_pos) { if (lane == 0 && p.status) atomicCAS(p.status, 0, XFT_ERR_BOUNDS); pos = 0; }
+  const float* cs = p.table + (size_t)pos * p.rope;
+  const int half = p.rope / 2;
+  if (h < p.Hl) {
+    const bf16* src = p.q + (size_t)t * p.ldq + (size_t)h * (p.nope + p.rope);
+    bf16* dn = p.q_nope + ((size_t)t * p.Hl + h) * p.nope;
+    for (int d = lane * 2; d < p.nope; d += 64)
+      *reinterpret_cast<__nv_bfloat162*>(dn + d) = *reinterpret_cast<const __nv_bfloat162*>(src + d);
+    bf16* dr = p.q_rope + ((size_t)t * p.Hl + h) * p.rope;
+    for (int i = lane; i < half; i += 32) {
+      const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(src + p.nope + 2 * i);
+      const float x1 = __low2float(x), x2 = __high2float(x), c = cs[i], s = cs[half + i];
+      *reinterpret_cast<__nv_bfloat162*>(dr + 2 * i) = __floats2bfloat162_rn(x1 * c - x2 * s, x2 * c + x1 * s);
+    }
+    return;
+  }
+  const long long slot = p.slots[t];
+  if (slot < 0 || slot >= p.nslots) { if (lane == 0 && p.status) atomicCAS(p.status, 0, XFT_ERR_BOUNDS); return; }
+  const bf16* src = p.kv + (size_t)t * p.ldkv;
+  bf16* dst = p.cache + (size_t)slot * (p.kvl + p.rope);
+  float ss = 0.f;
+  for (int d = lane * 2; d < p.kvl; d += 64) {
+    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(src + d);
+    ss += __low2float(x) * __low2float(x) + __high2float(x) * __high2float(x);
+  }
+  ss = warp_sum(ss);
+  const float inv = rsqrtf(ss / p.kvl + p.eps);
+  for (int d = lane * 2; d < p.kvl; d += 64) {
+    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(src + d);
+    *reinterpret_cast<__nv_bfloat162*>(dst + d) =
+        __floats2bfloat162_rn(__low2float(x) * inv * p.kv_norm_w[d], __high2float(x) * inv * p.kv_norm_w[d + 1]);
+  }
+  for (int i = lane; i < half; i += 32) {
+    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(src + p.kvl + 2 * i);
+    const float x1 = __low2float(x), x2 = __high2float(x), c = cs[i], s = cs[half + i];
+    *reinterpret_cast<__nv_bfloat162*>(dst + p.kvl + 2 * i) = __floats2bfloat162_rn(x1 * c - x2 * s, x2 * c + x1 * s);
+  }
 }
 
 // ------------------------------------------------------------------------------ row arg-max (first max wins)
@@ -422,6 +499,23 @@ extern "C" int xft_qkv_rope_cache(const void* qkv, int ldq, int T, int hq, int h
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
+// Two-stream rotary of ChatGLM-1 (reference: src/layers/rope_2d.cpp) in the same launch as the split and the cache
+// append: dims [0, rot) of every q / k head turn by positions[t], dims [rot, 2 rot) by positions2[t], both from one
+// table [max_pos, rot]; 2 rot <= D.
+extern "C" int xft_qkv_rope2d_cache(const void* qkv, int ldq, int T, int hq, int hkv, int D, const int* positions,
+                                    const int* positions2, const float* table, int rot, int max_pos, void* q_out,
+                                    void* kc, void* vc, float* ks, float* vs, int int8_cache, int bs, long long nslots,
+                                    const int* slots, int* status, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (D > 256 || D % 2 || rot <= 0 || rot % 2 || 2 * rot > D || !positions || !positions2 || !table) return -1;
+  RopeCacheParams p{(const bf16*)qkv, ldq, T, hq, hkv, D, positions, table, rot, 0, 0, max_pos, nullptr,
+                    nullptr, nullptr, 0.f, (bf16*)q_out, kc, vc, ks, vs, int8_cache, bs, nslots, slots, status,
+                    positions2};
+  long long warps = (long long)T * (hq + 2 * hkv);
+  cudaError_t e = launch_pdl(qkv_rope_cache_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, st, p);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}
+
 extern "C" int xft_rope(void* x, int T, int nh, int D, const int* positions, const float* table, int rot, int style,
                         int rot_off, int max_pos, const float* q_scale, int* status, cudaStream_t st) {
   long long warps = (long long)T * nh;
@@ -436,6 +530,22 @@ extern "C" int xft_latent_write(const void* latent, int ld, void* cache, int W, 
   if (T <= 0) return 0;
   latent_write_kernel<<<T, 128, 0, st>>>((const bf16*)latent, ld, (bf16*)cache, W, slots, nslots, T, status);
   return (int)cudaGetLastError();
+}
+
+// q rows [T, Hl * (nope + rope)] (row stride ldq), kv rows [T, kvl + rope] (row stride ldkv); all of nope, rope, kvl,
+// ldq, ldkv and the cache row width even, pointers 4-byte aligned.
+extern "C" int xft_mla_prep(const void* q, int ldq, const void* kv, int ldkv, int T, int Hl, int nope, int rope, int kvl,
+                            const int* positions, const float* table, int max_pos, const float* kv_norm_w, float eps,
+                            void* q_nope, void* q_rope, void* cache, long long nslots, const int* slots, int* status,
+                            cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (Hl <= 0 || nope < 0 || rope <= 0 || kvl <= 0 || ((nope | rope | kvl | ldq | ldkv) & 1)) return -1;
+  if (((uintptr_t)q | (uintptr_t)kv | (uintptr_t)q_nope | (uintptr_t)q_rope | (uintptr_t)cache) & 3) return -1;
+  MlaPrepParams p{(const bf16*)q, ldq, (const bf16*)kv, ldkv, T, Hl, nope, rope, kvl, positions, table, max_pos,
+                  kv_norm_w, eps, (bf16*)q_nope, (bf16*)q_rope, (bf16*)cache, nslots, slots, status};
+  const long long warps = (long long)T * (Hl + 1);
+  cudaError_t e = launch_pdl(mla_prep_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, st, p);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 extern "C" int xft_argmax(const float* logits, int ld, int rows, int V, float* vals, int* idx, cudaStream_t st) {

@@ -119,6 +119,104 @@ __global__ void __launch_bounds__(1024) sample_topk_topp_kernel(const float* __r
   }
 }
 
+// Beam-search step on the device (reference: src/searchers/beam_search.cpp:356-540 computes log-softmax over the whole
+// vocabulary and the top 2 x beams of every request on the host): per row (= one beam) the log-softmax normaliser and
+// the k best entries, as (log-probability, token id) sorted by value descending, ties by lower id.  Only rows x k pairs
+// leave the GPU; the host merges the beams of a request (k = 2 x beams candidates per beam are enough for the global
+// top 2 x beams).  Same selection scheme as the sampler above: bisection for the k-th largest key, ordered admission of
+// ties, bitonic sort of the candidates.  k <= 64.
+constexpr int kBeamMaxK = 64;
+
+__global__ void __launch_bounds__(1024) beam_topk_kernel(const float* __restrict__ logits, int ld, int V, int k,
+                                                         float* __restrict__ out_logp, int* __restrict__ out_idx) {
+  __shared__ unsigned long long cand[kBeamMaxK];
+  __shared__ int s_cnt;
+  __shared__ unsigned s_red[32];
+  __shared__ float s_f[32];
+  grid_dep_launch();
+  grid_dep_wait();
+  const int row = blockIdx.x, tid = threadIdx.x;
+  const float* x = logits + (size_t)row * ld;
+  if (k > V) k = V;
+  if (k > kBeamMaxK) k = kBeamMaxK;
+  if (k < 1) k = 1;
+  // log-sum-exp of the row
+  float mx = -INFINITY;
+  for (int i = tid; i < V; i += 1024) mx = fmaxf(mx, x[i]);
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if ((tid & 31) == 0) s_f[tid >> 5] = mx;
+  __syncthreads();
+  mx = s_f[0];
+  for (int w = 1; w < 32; ++w) mx = fmaxf(mx, s_f[w]);
+  __syncthreads();
+  float se = 0.f;
+  for (int i = tid; i < V; i += 1024) se += expf(x[i] - mx);
+  for (int o = 16; o > 0; o >>= 1) se += __shfl_xor_sync(0xffffffffu, se, o);
+  if ((tid & 31) == 0) s_f[tid >> 5] = se;
+  __syncthreads();
+  se = 0.f;
+  for (int w = 0; w < 32; ++w) se += s_f[w];
+  const float lse = mx + logf(se);
+  // largest threshold key with count(key >= thr) >= k
+  unsigned thr = 0;
+  for (int bit = 31; bit >= 0; --bit) {
+    const unsigned cand_thr = thr | (1u << bit);
+    unsigned c = 0;
+    for (int i = tid; i < V; i += 1024) c += f2key(x[i]) >= cand_thr;
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+    if ((tid & 31) == 0) s_red[tid >> 5] = c;
+    __syncthreads();
+    unsigned tot = 0;
+    for (int w = 0; w < 32; ++w) tot += s_red[w];
+    __syncthreads();
+    if (tot >= (unsigned)k) thr = cand_thr;
+  }
+  if (tid == 0) s_cnt = 0;
+  if (tid < kBeamMaxK) cand[tid] = 0ull;
+  __syncthreads();
+  for (int i = tid; i < V; i += 1024) {
+    const unsigned key = f2key(x[i]);
+    if (key > thr) { const int p = atomicAdd(&s_cnt, 1); if (p < kBeamMaxK) cand[p] = ((unsigned long long)key << 32) | (0xffffffffu - (unsigned)i); }
+  }
+  __syncthreads();
+  int held = min(s_cnt, kBeamMaxK);
+  __syncthreads();
+  for (int i0 = 0; i0 < V && held < k; i0 += 1024) {
+    const int i = i0 + tid;
+    const bool tie = i < V && f2key(x[i]) == thr;
+    const unsigned b = __ballot_sync(0xffffffffu, tie);
+    if ((tid & 31) == 0) s_red[tid >> 5] = __popc(b);
+    __syncthreads();
+    int before = 0, tot = 0;
+    for (int w = 0; w < 32; ++w) { const int c = (int)s_red[w]; if (w < (tid >> 5)) before += c; tot += c; }
+    __syncthreads();
+    const int pos = held + before + __popc(b & ((1u << (tid & 31)) - 1u));
+    if (tie && pos < k) cand[pos] = ((unsigned long long)thr << 32) | (0xffffffffu - (unsigned)i);
+    held += tot;
+  }
+  __syncthreads();
+  // bitonic sort of the 64 slots, descending (empty slots are 0 and sink to the end)
+  for (int size = 2; size <= kBeamMaxK; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      if (tid < kBeamMaxK) {
+        const int i = tid, j = i ^ stride;
+        if (j > i) {
+          const bool desc = (i & size) == 0;
+          const unsigned long long a = cand[i], b = cand[j];
+          if ((a < b) == desc) { cand[i] = b; cand[j] = a; }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  if (tid < k) {
+    const unsigned key = (unsigned)(cand[tid] >> 32);
+    const unsigned u = (key & 0x80000000u) ? (key & 0x7fffffffu) : ~key;
+    out_logp[(size_t)row * k + tid] = __uint_as_float(u) - lse;
+    out_idx[(size_t)row * k + tid] = (int)(0xffffffffu - (unsigned)(cand[tid] & 0xffffffffull));
+  }
+}
+
 // logits[row, id] <- l < 0 ? l*p : l/p for every id in the row's token list (src/searchers/search_utils.cpp:104-172).
 // tokens: [rows, max_len] padded with -1; ids outside [vocab_offset, vocab_offset + V) belong to other ranks.
 __global__ void repetition_penalty_kernel(float* __restrict__ logits, int ld, int V, const int* __restrict__ tokens,
@@ -155,5 +253,15 @@ extern "C" int xft_repetition_penalty(float* logits, int ld, int rows, int V, co
   if (rows <= 0 || max_len <= 0) return 0;
   cudaError_t e = launch_pdl(repetition_penalty_kernel, dim3(rows), dim3(256), 0, st, logits, ld, V, tokens, max_len, penalty,
                              vocab_offset);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}
+
+// Per row: log-softmax and its k best entries, sorted (value descending, lower id first on ties).  k <= 64 (returns -1
+// above).  out_logp, out_idx: [rows, k].
+extern "C" int xft_beam_topk(const float* logits, int ld, int rows, int V, int k, float* out_logp, int* out_idx,
+                             cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (k < 1 || k > xft::kBeamMaxK || k > V) return -1;
+  cudaError_t e = launch_pdl(beam_topk_kernel, dim3(rows), dim3(1024), 0, st, logits, ld, V, k, out_logp, out_idx);
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }

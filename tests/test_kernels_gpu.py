@@ -197,6 +197,32 @@ def test_qkv_rope_cache(int8, style, rot_frac):
         _close(gpu[1], cpu[1], 5e-2, 2e-2, "v cache")
 
 
+@pytest.mark.parametrize("int8", [False, True])
+@pytest.mark.parametrize("D", [128, 64])
+def test_qkv_rope2d_cache(int8, D):
+    """ChatGLM-1: both position streams, the split and the cache append in one launch, against two fp32 rotations."""
+    from xfastertransformer_b200 import ops
+    T, hq, hkv, bs, nb = 23, 4, 4, 64, 5
+    g = torch.Generator().manual_seed(9)
+    qkv = torch.randn(T, (hq + 2 * hkv) * D, generator=g).bfloat16()
+    pos = torch.randint(0, 300, (T,), generator=g, dtype=torch.int32)
+    pos2 = torch.randint(0, 40, (T,), generator=g, dtype=torch.int32)
+    slots = torch.randperm(nb * bs, generator=g)[:T].int()
+    table = R.rope_table(512, D // 2)
+    cpu = _mk_cache(nb, hkv, bs, D, int8, "cpu")
+    gpu = _mk_cache(nb, hkv, bs, D, int8, "cuda")
+    want = ops.qkv_rope2d_cache(qkv.float(), hq, hkv, D, pos, pos2, table, *cpu, slots)
+    got = ops.qkv_rope2d_cache(qkv.cuda(), hq, hkv, D, pos.cuda(), pos2.cuda(), table.cuda(), *gpu, slots.cuda())
+    _ws().check_status()
+    _close(got, want, 5e-2, 2e-2, "q")
+    if int8:
+        for c, gq, s_c, s_g in ((cpu[0], gpu[0], cpu[2], gpu[2]), (cpu[1], gpu[1], cpu[3], gpu[3])):
+            _close(gq.float() * s_g[..., None], c.float() * s_c[..., None], 6e-2, 3e-2, "int8 cache")
+    else:
+        _close(gpu[0], cpu[0], 5e-2, 2e-2, "k cache")
+        _close(gpu[1], cpu[1], 5e-2, 2e-2, "v cache")
+
+
 def _fill_paged(B, kv_lens, hkv, D, bs, int8, g):
     nb_per = [(n + bs - 1) // bs for n in kv_lens]
     nb = sum(nb_per) + 2

@@ -83,3 +83,30 @@ def test_tiny_deepseek(dtype, tmp_path):
     want = torch.load(str(tmp_path / "cpu.pt"))
     rel = (got - want).abs().max().item() / max(want.abs().max().item(), 1e-6)
     assert rel < 0.1, rel
+
+
+@pytest.mark.parametrize("Hl,nope,rope,kvl,ql", [(16, 128, 64, 512, 1536), (5, 32, 16, 64, 0)])
+def test_mla_prep_splits_rotates_normalises_and_appends(Hl, nope, rope, kvl, ql):
+    """The one launch between the MLA projections and the MLA attention against the composed fp32 steps; q and kv are
+    column views of wider projection outputs, as the decoder passes them."""
+    from xfastertransformer_b200 import ops
+    g = torch.Generator().manual_seed(Hl + kvl)
+    T, bs, nb = 21, 64, 3
+    qfull = (torch.randn(T, Hl * (nope + rope) + 8, generator=g) * 0.7).bfloat16()
+    kvfull = (torch.randn(T, ql + kvl + rope, generator=g) * 0.7).bfloat16()
+    pos = torch.randint(0, 400, (T,), generator=g, dtype=torch.int32)
+    slots = torch.randperm(nb * bs, generator=g)[:T].int()
+    table = R.rope_table(512, rope)
+    w = 1 + 0.1 * torch.randn(kvl, generator=g)
+    c_cpu = torch.zeros(nb, 1, bs, kvl + rope, dtype=torch.bfloat16)
+    c_gpu = torch.zeros_like(c_cpu).cuda()
+    wn, wr = ops.mla_prep(qfull[:, : Hl * (nope + rope)].float(), kvfull[:, ql:].float(), Hl, nope, rope, kvl, pos, table,
+                          w, 1e-6, c_cpu, slots)
+    qg, kvg = qfull.cuda(), kvfull.cuda()
+    gn, gr = ops.mla_prep(qg[:, : Hl * (nope + rope)], kvg[:, ql:], Hl, nope, rope, kvl, pos.cuda(), table.cuda(),
+                          w.cuda(), 1e-6, c_gpu, slots.cuda())
+    from xfastertransformer_b200.ops import native as Nat
+    Nat.Workspace.get(gn.device).check_status()
+    assert torch.equal(gn.cpu().float(), wn.float().bfloat16().float())
+    torch.testing.assert_close(gr.cpu().float(), wr.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(c_gpu.cpu().float(), c_cpu.float(), rtol=2e-2, atol=2e-2)

@@ -78,3 +78,57 @@ def test_gpu_sampler_matches_reference():
     want = R.repetition_penalty(l.clone(), toks, 1.7, 0)
     got = native_sample.repetition_penalty(l.clone().cuda(), toks, 1.7, 0).cpu()
     assert torch.allclose(got, want)
+
+
+def test_beam_step_from_per_beam_topk_matches_full_vocabulary_step():
+    """`process_topk` (each beam's 2 x beams best continuations) takes the same decisions as `process` (the whole
+    vocabulary): tokens, source beams, running scores, finished hypotheses."""
+    import copy
+    from xfastertransformer_b200 import ops
+    from xfastertransformer_b200.runtime.sampler import BeamSearchScorer
+    from xfastertransformer_b200.runtime.sequence import SamplingMeta
+    g = torch.Generator().manual_seed(5)
+    for nb, V, eos in [(2, 50, 3), (4, 97, 0), (3, 5, 1)]:
+        cfg = SamplingMeta(num_beams=nb, max_length=64, eos_token_id=eos, pad_token_id=0, length_penalty=1.0,
+                           early_stopping=False)
+        a = BeamSearchScorer(3, cfg, 0)
+        b = copy.deepcopy(a)
+        for step in range(6):
+            logits = torch.randn(3 * nb, V, generator=g) * 3
+            ta, sa = a.process(torch.log_softmax(logits, -1))
+            tb, sb = b.process_topk(*ops.beam_topk(logits, min(2 * nb, V)))
+            assert ta.tolist() == tb.tolist() and sa.tolist() == sb.tolist(), (nb, V, step)
+            torch.testing.assert_close(a.beam_scores, b.beam_scores, rtol=1e-5, atol=1e-5)
+            assert a.done == b.done and a.seqs == b.seqs
+            assert [len(h.beams) for h in a.hyps] == [len(h.beams) for h in b.hyps]
+
+
+def test_beam_topk_reference_orders_ties_by_token_id():
+    from xfastertransformer_b200.ops import reference as R
+    x = torch.tensor([[1.0, 3.0, 3.0, -2.0, 3.0, 0.5]])
+    v, i = R.beam_topk(x, 4)
+    assert i.tolist() == [[1, 2, 4, 0]]
+    torch.testing.assert_close(v, torch.log_softmax(x, -1)[0, [1, 2, 4, 0]][None])
+
+
+@pytest.mark.gpu
+def test_gpu_beam_topk_matches_reference():
+    """Device beam step: log-softmax and the k best entries of each row against the fp32 reference; rows with many
+    equal logits come back in token-id order."""
+    from xfastertransformer_b200.ops import native_sample, reference as R
+    g = torch.Generator().manual_seed(11)
+    for rows, V, k in [(6, 32000, 8), (3, 151936, 64), (4, 50, 2), (2, 7, 7), (5, 1025, 1)]:
+        x = torch.randn(rows, V, generator=g) * 4
+        wv, wi = R.beam_topk(x, k)
+        gv, gi = native_sample.beam_topk(x.cuda(), k)
+        torch.testing.assert_close(gv.cpu(), wv, rtol=1e-5, atol=2e-4)
+        assert torch.equal(x.gather(1, gi.cpu()), x.gather(1, wi)), (rows, V, k)
+    x = torch.randint(-3, 4, (4, 5000), generator=g).float()      # 7 distinct values: ties everywhere
+    wv, wi = R.beam_topk(x, 16)
+    gv, gi = native_sample.beam_topk(x.cuda(), 16)
+    assert gi.cpu().tolist() == wi.tolist()
+    torch.testing.assert_close(gv.cpu(), wv, rtol=1e-5, atol=2e-4)
+    strided = torch.randn(3, 2 * 4096, generator=g).cuda()[:, :4096]      # a view with a row stride
+    gv, gi = native_sample.beam_topk(strided, 6)
+    wv, wi = R.beam_topk(strided.cpu(), 6)
+    assert gi.cpu().tolist() == wi.tolist()

@@ -549,15 +549,8 @@ class Decoder:
     def _rope2d_cache(self, L, qkv, b: Batch, cache, li):
         """ChatGLM-1: first half of each head rotates with the position stream, second half with
         the block-position stream (src/layers/rope_2d.cpp, src/models/chatglm.cpp:118-206)."""
-        T, D, hq, hkv = qkv.shape[0], self.D, self.hq, self.hkv
-        q = qkv[:, : hq * D].reshape(T, hq, D)
-        k = qkv[:, hq * D:(hq + hkv) * D].reshape(T, hkv, D)
-        v = qkv[:, (hq + hkv) * D:].reshape(T, hkv, D)
-        half = D // 2
-        q, k = ops.rope_apply(q, k, b.positions, self.rope_table, half, "half", 0)
-        q, k = ops.rope_apply(q, k, b.positions2, self.rope_table, half, "half", half)
-        R.kv_cache_write(k, v, cache.k[li], cache.v[li], b.slots, cache.ks[li], cache.vs[li])
-        return q.contiguous()
+        return ops.qkv_rope2d_cache(qkv, self.hq, self.hkv, self.D, b.positions, b.positions2, self.rope_table,
+                                    cache.k[li], cache.v[li], cache.ks[li], cache.vs[li], b.slots)
 
     def _mla(self, L: Layer, h, b: Batch, cache: PagedKVCache, li: int):
         c = self.cfg
@@ -566,7 +559,7 @@ class Decoder:
         Hl = self.hq
         if ql > 0:
             qa_kv = ops.linear(h, L.qkv_a)                       # [T, ql + kvl + rope]
-            qa = ops.rmsnorm(qa_kv[:, :ql].contiguous(), L.q_a_norm, self.eps)
+            qa = ops.rmsnorm(qa_kv[:, :ql], L.q_a_norm, self.eps)
             q = ops.linear(qa, L.q_b)
             kv = qa_kv[:, ql:]
         elif L.qkv_a is not None:
@@ -574,14 +567,8 @@ class Decoder:
             q, kv = both[:, : Hl * (nope + rope)], both[:, Hl * (nope + rope):]
         else:
             q, kv = ops.linear(h, L.q_direct), ops.linear(h, L.kv_a)
-        q = q.reshape(T, Hl, nope + rope)
-        ckv = ops.rmsnorm(kv[:, :kvl].contiguous(), L.kv_a_norm, self.eps)
-        kr = kv[:, kvl:].reshape(T, 1, rope)
-        q_nope = q[..., :nope].contiguous()
-        q_rope, kr = ops.rope_apply(q[..., nope:].contiguous(), kr.contiguous(), b.positions, self.rope_table,
-                                    rope, "interleaved", 0)
-        latent = torch.cat([ckv, kr.reshape(T, rope)], dim=-1)
-        ops.latent_cache_write(latent, cache.k[li], b.slots)
+        q_nope, q_rope = ops.mla_prep(q, kv, Hl, nope, rope, kvl, b.positions, self.rope_table, L.kv_a_norm, self.eps,
+                                      cache.k[li], b.slots)
         a = ops.mla_attention(q_nope, q_rope, cache.k[li], b.block_table, b.cu_q, b.kv_lens, L.w_uk, L.w_uv,
                               self.scale, absorbed=b.is_decode, meta=b)
         return a.reshape(T, Hl * vd)

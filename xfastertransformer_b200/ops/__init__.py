@@ -136,6 +136,24 @@ def qkv_rope_cache(qkv, hq, hkv, d, positions, table, rot_dim, style, kc, vc, ks
     return q.contiguous()
 
 
+def qkv_rope2d_cache(qkv, hq, hkv, d, positions, positions2, table, kc, vc, ks, vs, slots):
+    """ChatGLM-1's two-stream rotary with the cache append: the first half of every q / k head turns by `positions`,
+    the second half by `positions2` (block positions), both from one table [max_pos, d/2]; k / v go to the paged cache
+    at `slots`; returns q [T,hq,d].  One kernel on the GPU (reference: src/layers/rope_2d.cpp,
+    src/models/chatglm.cpp:118-206)."""
+    if _cuda(qkv):
+        return _nat().qkv_rope2d_cache(qkv, hq, hkv, d, positions, positions2, table, kc, vc, ks, vs, slots)
+    T = qkv.shape[0]
+    q = qkv[:, : hq * d].reshape(T, hq, d)
+    k = qkv[:, hq * d:(hq + hkv) * d].reshape(T, hkv, d)
+    v = qkv[:, (hq + hkv) * d:].reshape(T, hkv, d)
+    half = d // 2
+    q, k = R.rope_apply(q, k, positions, table, half, "half", 0)
+    q, k = R.rope_apply(q, k, positions2, table, half, "half", half)
+    R.kv_cache_write(k, v, kc, vc, slots, ks, vs)
+    return q.contiguous()
+
+
 def can_fuse_qkv_rope(W, T, D, kc, ks, q_norm_w, k_norm_w, style) -> bool:
     """True when the QKV product, RoPE and the cache append can run as one kernel (GPU, decode sizes)."""
     return _cuda(kc) and _nat().can_fuse_qkv_rope(W, T, D, kc, ks, q_norm_w, k_norm_w, style)
@@ -179,6 +197,21 @@ def latent_cache_write(latent, cache, slots):
     cache[(slots // blk).long(), 0, (slots % blk).long()] = latent.to(cache.dtype)
 
 
+def mla_prep(q, kv, Hl, nope, rope, kvl, positions, table, kv_norm_w, eps, cache, slots):
+    """What sits between the MLA projections and the MLA attention: split every query head of q [T, Hl*(nope+rope)]
+    into its no-position part and its rotated part (interleaved pairs), RMS-normalise the compressed KV kv[:, :kvl],
+    rotate the shared key part kv[:, kvl:], and append (normalised KV ‖ rotated key) to the latent cache at `slots`.
+    Returns (q_nope [T,Hl,nope], q_rope [T,Hl,rope]).  One kernel on the GPU."""
+    if _cuda(q) and cache.dtype == torch.bfloat16:
+        return _nat().mla_prep(q, kv, Hl, nope, rope, kvl, positions, table, kv_norm_w, eps, cache, slots)
+    T = q.shape[0]
+    q3 = q.reshape(T, Hl, nope + rope)
+    ckv = R.rmsnorm(kv[:, :kvl], kv_norm_w, eps)
+    q_rope, kr = R.rope_apply(q3[..., nope:], kv[:, kvl:].reshape(T, 1, rope), positions, table, rope, "interleaved", 0)
+    latent_cache_write(torch.cat([ckv, kr.reshape(T, rope)], dim=-1), cache, slots)
+    return q3[..., :nope].contiguous(), q_rope.contiguous()
+
+
 # -- MoE -----------------------------------------------------------------------------------
 def route(logits, kind, top_k, bias=None, n_group=1, topk_group=1, routed_scaling=1.0, norm_topk=True,
           scoring="sigmoid"):
@@ -204,6 +237,14 @@ def argmax_rows(logits):
     if _cuda(logits):
         return _nat().argmax_rows(logits)
     return R.argmax_rows(logits)
+
+
+def beam_topk(logits, k):
+    """(log-softmax values, token ids) of each row's k best entries, best first."""
+    if _cuda(logits):
+        from . import native_sample
+        return native_sample.beam_topk(logits, k)
+    return R.beam_topk(logits, k)
 
 
 def sample_top_k_top_p(logits, top_k, top_p, temperature, uniform):

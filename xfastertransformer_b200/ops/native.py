@@ -391,6 +391,22 @@ def qkv_rope_cache(qkv, hq, hkv, d, positions, table, rot_dim, style, kc, vc, ks
     return q
 
 
+def qkv_rope2d_cache(qkv, hq, hkv, d, positions, positions2, table, kc, vc, ks, vs, slots):
+    """ChatGLM-1: split, rotate the two halves of every q / k head by their own position stream, append k / v."""
+    qkv2, ldq = _rows2d(qkv)
+    T = qkv2.shape[0]
+    q = torch.empty(T, hq, d, dtype=torch.bfloat16, device=qkv.device)
+    ws = Workspace.get(qkv.device)
+    nb, _, bs, _ = kc.shape
+    fn = lib().xft_qkv_rope2d_cache
+    fn.restype = C.c_int
+    _check(fn(_p(qkv2), ldq, T, hq, hkv, d, _p(positions), _p(positions2), _p(table), d // 2, table.shape[0], _p(q),
+              _p(kc), _p(vc), _p(ks), _p(vs), int(ks is not None), bs, C.c_longlong(nb * bs), _p(slots), _p(ws.status),
+              _stream()), "qkv_rope2d_cache")
+    ws.launches += 1
+    return q
+
+
 def rope_apply(q, k, positions, table, rot_dim, style="half", rot_offset=0, q_scale=None):
     ws = Workspace.get(q.device)
     st = 0 if style == "half" else 1
@@ -414,6 +430,31 @@ def latent_cache_write(latent, cache, slots):
     _check(lib().xft_latent_write(_p(l2), ld, _p(cache), W, _p(slots), C.c_longlong(nb * bs), l2.shape[0],
                                   _p(ws.status), _stream()), "latent_write")
     ws.launches += 1
+
+
+def mla_prep(q, kv, Hl, nope, rope, kvl, positions, table, kv_norm_w, eps, cache, slots):
+    """q [T, Hl*(nope+rope)], kv [T, kvl+rope] (row views allowed) -> (q_nope [T,Hl,nope], q_rope [T,Hl,rope]); the
+    normalised compressed KV and the rotated shared key part land in the latent cache at `slots`."""
+    def rows(x):
+        if x.stride(1) != 1 or x.stride(0) % 2 or x.data_ptr() % 4:
+            x = x.contiguous()
+        return x, x.stride(0)
+    q2, ldq = rows(q)
+    kv2, ldkv = rows(kv)
+    T = q2.shape[0]
+    q_nope = torch.empty(T, Hl, nope, dtype=torch.bfloat16, device=q.device)
+    q_rope = torch.empty(T, Hl, rope, dtype=torch.bfloat16, device=q.device)
+    ws = Workspace.get(q.device)
+    nb, _, bs, W = cache.shape
+    if W != kvl + rope or cache.dtype != torch.bfloat16:
+        raise ValueError("mla_prep: latent cache must be bf16 rows of kv_lora_rank + rope")
+    fn = lib().xft_mla_prep
+    fn.restype = C.c_int
+    _check(fn(_p(q2), ldq, _p(kv2), ldkv, T, Hl, nope, rope, kvl, _p(positions), _p(table), table.shape[0],
+              _p(kv_norm_w), C.c_float(eps), _p(q_nope), _p(q_rope), _p(cache), C.c_longlong(nb * bs), _p(slots),
+              _p(ws.status), _stream()), "mla_prep")
+    ws.launches += 1
+    return q_nope, q_rope
 
 
 def plan_attn_splits(B, hkv, group, D, max_kv, int8=False):

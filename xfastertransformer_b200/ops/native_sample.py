@@ -23,6 +23,28 @@ def sample_top_k_top_p(logits, top_k, top_p, temperature, uniform):
     return out.long()
 
 
+BEAM_TOPK_MAX = 64
+
+
+def beam_topk(logits, k):
+    """Per row of fp32 logits [rows, V]: (log-softmax values [rows, k] fp32, token ids [rows, k] int64) of the k best
+    entries, best first, lower id first among equals.  k <= BEAM_TOPK_MAX."""
+    l2 = logits.reshape(-1, logits.shape[-1])
+    if l2.dtype != torch.float32 or l2.stride(1) != 1:
+        l2 = l2.float().contiguous()
+    rows, V = l2.shape
+    k = int(k)
+    if not 1 <= k <= min(V, BEAM_TOPK_MAX):
+        raise ValueError(f"beam_topk: k = {k} outside [1, min(vocab, {BEAM_TOPK_MAX})]")
+    vals = torch.empty(rows, k, dtype=torch.float32, device=l2.device)
+    idx = torch.empty(rows, k, dtype=torch.int32, device=l2.device)
+    lib = N.lib()
+    lib.xft_beam_topk.restype = C.c_int
+    N._check(lib.xft_beam_topk(N._p(l2), l2.stride(0), rows, V, k, N._p(vals), N._p(idx), N._stream()), "beam_topk")
+    N.Workspace.get(l2.device).launches += 1
+    return vals, idx.long()
+
+
 def repetition_penalty(logits, token_lists, penalty, vocab_offset=0):
     """In place on fp32 logits [rows, V]; `token_lists`: per-row iterable of token ids."""
     rows, V = logits.shape

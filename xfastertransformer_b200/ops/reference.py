@@ -579,3 +579,11 @@ def sample_top_k_top_p(logits: torch.Tensor, top_k: int, top_p: float, temperatu
 
 def log_softmax(logits: torch.Tensor) -> torch.Tensor:
     return torch.log_softmax(logits.float(), dim=-1)
+
+
+def beam_topk(logits: torch.Tensor, k: int):
+    """Per row: the k best log-softmax values and their token ids, best first, lower id first among equals (the part
+    of a beam-search step that touches the whole vocabulary, src/searchers/beam_search.cpp:356-540)."""
+    lp = torch.log_softmax(logits.float().reshape(-1, logits.shape[-1]), dim=-1)
+    order = torch.sort(lp, dim=-1, descending=True, stable=True).indices[:, :k]
+    return lp.gather(1, order), order

@@ -24,6 +24,7 @@ from typing import List, Optional, Sequence
 
 import torch
 
+from .. import ops
 from ..config import KV_DTYPES, ModelConfig, split_hybrid_dtype
 from ..models.decoder import Batch, Decoder
 from ..parallel.dist import CommError, DistContext
@@ -408,7 +409,7 @@ class Model:
             # prefill once per request, then fork each into num_beams cache-sharing sequences
             reqs = self.working
             local = self._run(reqs)
-            full = S.gather_logits(local, self.ctx, self.vocab_sizes).float().cpu()
+            full = S.gather_logits(local, self.ctx, self.vocab_sizes).float()
             for s in reqs:
                 s.past_len += len(s.pending)
                 s.pending = []
@@ -426,12 +427,17 @@ class Model:
             self._beam_pending = False
         else:
             local = self._run(self.working)
-            full = S.gather_logits(local, self.ctx, self.vocab_sizes).float().cpu()
+            full = S.gather_logits(local, self.ctx, self.vocab_sizes).float()
         if cfg.repetition_penalty != 1.0:
             full = S.apply_repetition_penalty(full, [s.prompt + g for s, g in zip(self.working, self.scorer.seqs)],
                                               cfg.repetition_penalty, 0)
-        logp = torch.log_softmax(full, -1)
-        toks, src = self.scorer.process(logp)
+        # The vocabulary stays where the logits are: each beam's log-softmax and its 2 x beams best continuations are
+        # found there, and only those pairs reach the scorer on the host.
+        k = min(2 * nb, full.shape[-1])
+        if k <= S.BEAM_TOPK_MAX:
+            toks, src = self.scorer.process_topk(*ops.beam_topk(full, k))
+        else:
+            toks, src = self.scorer.process(torch.log_softmax(full.cpu(), -1))
         ids = [s.seq_id for s in self.working]
         self.cache.reorder(ids, src.tolist())                 # beam reorder = block-table permutation
         old_gen = [list(s.generated) for s in self.working]

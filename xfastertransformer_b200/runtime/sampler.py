@@ -112,6 +112,9 @@ class BeamHypotheses:
         return self.worst >= best_sum_logprobs / (max(cur_len, 1) ** self.length_penalty)
 
 
+BEAM_TOPK_MAX = 64          # widest per-beam candidate list of `ops.beam_topk`
+
+
 class BeamSearchScorer:
     """Per-request beam bookkeeping.  `process` consumes the top 2*num_beams candidates of each
     request and returns the next (scores, tokens, source-beam indices)."""
@@ -134,12 +137,27 @@ class BeamSearchScorer:
         """logprobs: [bs*nb, vocab] log-softmax of the current step (host tensor)."""
         bs, nb = self.bs, self.nb
         V = logprobs.shape[-1]
-        eos, pad = self.cfg.eos_token_id, self.cfg.pad_token_id
         scores = logprobs + self.beam_scores.view(-1, 1)
         scores = scores.view(bs, nb * V)
         top_s, top_i = torch.topk(scores, 2 * nb, dim=1)
-        src_beam = top_i // V
-        tok = top_i % V
+        return self._advance(top_s, top_i // V, top_i % V)
+
+    def process_topk(self, logp: torch.Tensor, idx: torch.Tensor):
+        """Same step from each beam's own k >= min(2*nb, vocab) best continuations (`ops.beam_topk`): logp, idx
+        [bs*nb, k], sorted by value.  The best 2*nb of a request's nb*vocab candidates can take at most 2*nb from one
+        beam, so merging the per-beam lists loses nothing; only k values per beam cross to the host instead of the
+        vocabulary."""
+        bs, nb = self.bs, self.nb
+        k = logp.shape[-1]
+        scores = (logp.float().cpu() + self.beam_scores.view(-1, 1)).reshape(bs, nb * k)
+        top_s, top_i = torch.topk(scores, min(2 * nb, nb * k), dim=1)
+        tok = idx.cpu().long().reshape(bs, nb * k).gather(1, top_i)
+        return self._advance(top_s, top_i // k, tok)
+
+    def _advance(self, top_s: torch.Tensor, src_beam: torch.Tensor, tok: torch.Tensor):
+        """top_s, src_beam, tok: [bs, <= 2*nb] candidates of every request, best first."""
+        bs, nb = self.bs, self.nb
+        eos, pad = self.cfg.eos_token_id, self.cfg.pad_token_id
         cur_len = len(self.seqs[0]) + 1
         next_tokens = torch.full((bs, nb), pad if pad >= 0 else 0, dtype=torch.long)
         next_src = torch.zeros(bs, nb, dtype=torch.long)
@@ -150,7 +168,7 @@ class BeamSearchScorer:
                 next_scores[b] = self.beam_scores[b]
                 continue
             k = 0
-            for rank in range(2 * nb):
+            for rank in range(top_s.shape[1]):
                 t, s, sb = int(tok[b, rank]), float(top_s[b, rank]), int(src_beam[b, rank])
                 if t == eos and eos >= 0:
                     if rank >= nb:
