@@ -11,6 +11,7 @@
 #include <cstdio>
 #include <cstring>
 #include <fstream>
+#include <map>
 #include <random>
 #include <stdexcept>
 
@@ -98,7 +99,42 @@ std::vector<char> readFile(const std::string& path, size_t expect, int dt) {
 
 struct LayerWeights {
   DevBuf qkv, o, gateUp, down, n1, n2, qkvBias, qNorm, kNorm;
+  DevBuf n1b, n2b, oBias, fc1Bias, fc2Bias;      // LayerNorm biases, output-projection bias, biases of the two-matrix MLP
 };
+
+// What distinguishes one dense family from another (reference: one C++ class per family under src/models, selected by
+// the factory key of model_factory.h:57-114); the forward pass below reads these fields instead of being specialised.
+struct FamilySpec {
+  const char* name;
+  bool layerNorm = false;      // LayerNorm with bias instead of RMSNorm
+  int ropeStyle = 0;           // 0: pairs (i, i + rot/2); 1: pairs (2i, 2i + 1)
+  double rotFrac = 1.0;        // rotary dims / head dim
+  bool rope2d = false;         // ChatGLM-1: two position streams, one per half of the head
+  int mlp = 0;                 // 0: gate_proj / up_proj / down_proj; 1: dense_h_to_4h + bias -> act -> dense_4h_to_h + bias;
+                               // 2: merged gate‖up in dense_h_to_4h, dense_4h_to_h
+  int embedding = 0;           // 0 plain, 1 scaled by sqrt(hidden) (Gemma), 2 plus learned positions at offset 2 (OPT)
+  bool lognNtk = false;        // Qwen-1: dynamic-NTK base and log-n query scale beyond the training length
+  bool telechatNtk = false;    // TeleChat: NTK base from max(context, training length), table scale on long inputs
+  bool residFromNorm = false;  // ChatGLM-1: residual = sqrt(2 * layers) * normalised input
+  bool prefixLm = false;       // ChatGLM-1: the prompt up to its bos token attends in both directions
+};
+
+const FamilySpec* familySpec(const std::string& type) {
+  static const FamilySpec table[] = {
+      {"llama"}, {"yarn_llama"}, {"qwen2"}, {"qwen3"}, {"baichuan"},
+      {"gemma", false, 0, 1.0, false, 0, 1},
+      {"qwen", false, 0, 1.0, false, 0, 0, true},
+      {"telechat", false, 0, 1.0, false, 0, 0, false, true},
+      {"chatglm2", false, 1, 0.5, false, 2},
+      {"chatglm3", false, 1, 0.5, false, 2},
+      {"chatglm4", false, 1, 0.5, false, 2},
+      {"gpt", true, 0, 0.0, false, 1, 2},
+      {"chatglm", true, 0, 0.5, true, 1, 0, false, false, true, true},
+  };
+  for (const FamilySpec& f : table)
+    if (type == f.name) return &f;
+  return nullptr;
+}
 
 class Engine {
 public:
@@ -109,6 +145,12 @@ public:
   float eps = 1e-6f, ropeTheta = 10000.f, embedScale = 1.f;
   int act = 2;   // kernel activation code: 1 relu, 2 silu, 3 gelu
   bool qkNorm = false, kvInt8 = false;
+  FamilySpec spec{""};
+  int rotDim = 0;              // 0: no rotary table (OPT, ALiBi Baichuan)
+  int wpeRows = 0;             // OPT: rows of the learned position table
+  bool alibi = false;
+  int trainLen = 0;            // Qwen-1 seq_length / TeleChat training context
+  bool useDynamicNtk = true, useLognAttn = true;
 
   SequencePool pool;
   std::unique_ptr<BlockTables> tables;
@@ -133,12 +175,15 @@ private:
   void copyBlock(int src, int dst);
   std::string dir;
   int fileDt = 1;
-  DevBuf wte, lmHead, finalNorm, ropeTable_, ws, counters, status, attnCounters, partO, partMl;
+  const float* ropeFor(int maxKv, int maxQ);      // the rotary table of this pass (NTK families keep one per base)
+  DevBuf wte, wpe, lmHead, finalNorm, finalNormBias, ropeTable_, slopes_, ws, counters, status, attnCounters, partO, partMl;
+  std::map<long long, DevBuf> ntkTables_;         // by round(base): Qwen-1 / TeleChat tables beyond the first
+  RopeScaling ropeScaling_;
   std::vector<LayerWeights> lw;
   std::vector<DevBuf> kc, vc, ks, vs;
   int numBlocks = 0;
   // activations
-  DevBuf dIds, dPos, dSlots, dCu, dKv, dBt, x, x2, h, qkvBuf, q, att, g, rows, logits;
+  DevBuf dIds, dPos, dPos2, dPrefix, dQScale, dSlots, dCu, dKv, dBt, x, x2, h, qkvBuf, q, att, g, rows, logits;
   cudaStream_t st = nullptr;
   static constexpr int kBlock = 64;
   static constexpr size_t kWsBytes = 64u << 20;
@@ -171,10 +216,9 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
   Ini ini(path + "/config.ini");
   if (!ini.ok() || ini.sections().empty()) throw std::runtime_error("config.ini not found under " + path);
   type = ini.sections()[0];
-  static const char* ok[] = {"llama", "yarn_llama", "gemma", "qwen2", "qwen3", "baichuan"};
-  bool supported = false;
-  for (auto t : ok) supported |= type == t;
-  if (!supported) throw std::runtime_error("the native C++ engine runs the dense llama-style families; use the Python API for [" + type + "]");
+  const FamilySpec* fam = familySpec(type);
+  if (!fam) throw std::runtime_error("the native C++ engine runs the dense families; use the Python API for [" + type + "]");
+  spec = *fam;
   if (dt != DataType::bf16 && dt != DataType::fp16) throw std::runtime_error("the native C++ engine runs bf16 (fp16 weights are kept as bf16)");
   kvInt8 = kvdt == DataType::int8;
   heads = (int)ini.getInt(type, "head_num");
@@ -185,8 +229,8 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
   layers = (int)ini.getInt(type, "num_layer");
   vocab = (int)ini.getInt(type, "vocab_size");
   maxPos = std::max<int>({(int)ini.getInt(type, "max_pos_seq_len", 0), (int)ini.getInt(type, "model_max_length", 0), 2048});
-  if (type == "baichuan" && ini.getInt(type, "max_pos_seq_len", 0) <= 0)
-    throw std::runtime_error("ALiBi Baichuan models run through the Python API");
+  // Baichuan-13B has no rotary table: ALiBi slopes on the attention scores (src/layers/attn_baichuan.h:33-47)
+  alibi = type == "baichuan" && ini.getInt(type, "max_pos_seq_len", 0) <= 0;
   eps = (float)ini.getFloat(type, "layernorm_eps", ini.getFloat(type, "rms_norm_eps", 1e-6));
   ropeTheta = (float)ini.getFloat(type, "rope_theta", 10000.0);
   std::string rtype = ini.get(type, "rope_scaling_type", ini.get(type, "rope_type", ""));
@@ -203,12 +247,28 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
     if (rtype == "yarn") rs.tableScale = yarnMscale(rs.factor, 1.0);
   } else if (!rtype.empty() && rtype != "default") {
     throw std::runtime_error("rope scaling '" + rtype + "' runs through the Python API");
+  } else if (type.rfind("chatglm", 0) == 0 && type != "chatglm") {
+    // rope_ratio of the long-context GLM checkpoints multiplies the base
+    ropeTheta *= (float)ini.getFloat(type, "rope_scaling_factor", ini.getFloat(type, "scaling_factor", 1.0));
+  }
+  ropeScaling_ = rs;
+  rotDim = (alibi || spec.rotFrac <= 0.0) ? 0 : (int)(headDim * spec.rotFrac);
+  if (spec.lognNtk) {
+    trainLen = (int)ini.getInt(type, "seq_length", -1);
+    if (trainLen <= 0) trainLen = 8192;
+    useDynamicNtk = ini.getBool(type, "use_dynamic_ntk", true);
+    useLognAttn = ini.getBool(type, "use_logn_attn", true);
+  } else if (spec.telechatNtk) {
+    trainLen = (int)ini.getInt(type, "max_pos_seq_len", 0);
+    if (trainLen <= 0) trainLen = 2048;
   }
   endId = (int)ini.getInt(type, "end_id", ini.getInt(type, "start_id", 0));
   std::string a = ini.get(type, "activation_type", "silu");
   act = a.rfind("gelu", 0) == 0 ? 3 : a == "relu" ? 1 : 2;
+  if (spec.mlp == 1 && act == 2) act = 3;        // the two-matrix MLP is relu (OPT) or gelu
+  if (spec.mlp == 2) act = 2;                    // the merged gate‖up MLP of ChatGLM2+ is SwiGLU
   qkNorm = ini.getBool(type, "do_qk_norm", false);
-  if (type == "gemma") embedScale = std::sqrt((float)hidden);
+  if (spec.embedding == 1) embedScale = std::sqrt((float)hidden);
   std::string wdt = ini.get(type, "weight_data_type", "fp16");
   fileDt = wdt == "fp32" ? 0 : wdt == "bf16" ? 2 : 1;
   if (ini.get(type, "quant_qweight_data_type", "") != "") throw std::runtime_error("GPTQ checkpoints run through the Python API");
@@ -228,7 +288,18 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
     lmHead.reset(b.size() * 2);
     XFT_CUDA(cudaMemcpy(lmHead.p, b.data(), b.size() * 2, cudaMemcpyHostToDevice));
   }
+  if (spec.embedding == 2) {
+    // learned positions of OPT: max_pos_seq_len + 2 rows (the first two are never addressed by a real position)
+    wpeRows = (int)ini.getInt(type, "max_pos_seq_len", 0) + 2;
+    const size_t n = (size_t)wpeRows * hidden;
+    auto host = readFile(dir + "/model.wpe.bin", n * dtypeSize(fileDt), fileDt);
+    std::vector<uint16_t> b(n);
+    for (size_t i = 0; i < n; ++i) b[i] = floatToBf16(elemToFloat(host.data(), fileDt, i));
+    wpe.reset(n * 2);
+    XFT_CUDA(cudaMemcpy(wpe.p, b.data(), n * 2, cudaMemcpyHostToDevice));
+  }
   finalNorm = loadVector("model.final_layernorm.weight.bin", hidden);
+  if (spec.layerNorm) finalNormBias = loadVector("model.final_layernorm.bias.bin", hidden);
   lw.resize(layers);
   for (int i = 0; i < layers; ++i) {
     const std::string p = "model.layers." + std::to_string(i) + ".";
@@ -238,23 +309,45 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
     L.qkvBias = loadVector(p + "attention.query_key_value.bias.0.bin", qsz + 2 * kvsz, true);
     L.o.reset((size_t)hidden * qsz * 2);
     loadLinear(p + "attention.dense.weight.0.bin", qsz, hidden, L.o.p, 0, qsz);
-    L.gateUp.reset((size_t)2 * inter * hidden * 2);
-    loadLinear(p + "mlp.gate_proj.weight.0.bin", hidden, inter, L.gateUp.p, 0, hidden);
-    loadLinear(p + "mlp.up_proj.weight.0.bin", hidden, inter, L.gateUp.p, inter, hidden);
+    L.oBias = loadVector(p + "attention.dense.bias.bin", hidden, true);
+    if (spec.mlp == 1) {
+      L.gateUp.reset((size_t)inter * hidden * 2);
+      loadLinear(p + "mlp.dense_h_to_4h.weight.0.bin", hidden, inter, L.gateUp.p, 0, hidden);
+      L.fc1Bias = loadVector(p + "mlp.dense_h_to_4h.bias.0.bin", inter);
+      L.fc2Bias = loadVector(p + "mlp.dense_4h_to_h.bias.bin", hidden);
+    } else {
+      L.gateUp.reset((size_t)2 * inter * hidden * 2);
+      if (spec.mlp == 2) {
+        loadLinear(p + "mlp.dense_h_to_4h.weight.0.bin", hidden, 2 * inter, L.gateUp.p, 0, hidden);   // gate rows, then up rows
+      } else {
+        loadLinear(p + "mlp.gate_proj.weight.0.bin", hidden, inter, L.gateUp.p, 0, hidden);
+        loadLinear(p + "mlp.up_proj.weight.0.bin", hidden, inter, L.gateUp.p, inter, hidden);
+      }
+    }
     L.down.reset((size_t)hidden * inter * 2);
-    loadLinear(p + "mlp.down_proj.weight.0.bin", inter, hidden, L.down.p, 0, inter);
+    loadLinear(p + (spec.mlp == 0 ? "mlp.down_proj.weight.0.bin" : "mlp.dense_4h_to_h.weight.0.bin"), inter, hidden, L.down.p, 0,
+               inter);
     L.n1 = loadVector(p + "input_layernorm.weight.bin", hidden);
     L.n2 = loadVector(p + "post_attention_layernorm.weight.bin", hidden);
+    if (spec.layerNorm) {
+      L.n1b = loadVector(p + "input_layernorm.bias.bin", hidden);
+      L.n2b = loadVector(p + "post_attention_layernorm.bias.bin", hidden);
+    }
     if (qkNorm) {
       L.qNorm = loadVector(p + "attention.q_norm.weight.bin", headDim);
       L.kNorm = loadVector(p + "attention.k_norm.weight.bin", headDim);
     }
   }
-  // rotary table [maxPos, headDim] = cos(headDim/2) ‖ sin(headDim/2)
-  {
-    const std::vector<float> tab = ropeTable(maxPos, headDim, ropeTheta, rs);
+  // rotary table [maxPos, rotDim] = cos(rotDim/2) ‖ sin(rotDim/2); the NTK families build further tables on demand
+  if (rotDim > 0 && !spec.telechatNtk) {
+    const std::vector<float> tab = ropeTable(maxPos, rotDim, ropeTheta, rs);
     ropeTable_.reset(tab.size() * 4);
     XFT_CUDA(cudaMemcpy(ropeTable_.p, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice));
+  }
+  if (alibi) {
+    const std::vector<float> sl = alibiSlopes(heads);
+    slopes_.reset(sl.size() * 4);
+    XFT_CUDA(cudaMemcpy(slopes_.p, sl.data(), sl.size() * 4, cudaMemcpyHostToDevice));
   }
   ws.reset(kWsBytes);
   counters.reset(8192 * 4); XFT_CUDA(cudaMemset(counters.p, 0, counters.bytes));
@@ -269,6 +362,33 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
     const size_t per = (size_t)layers * kvHeads * kBlock * (2 * headDim * esz + (kvInt8 ? 8 : 0));
     ensureBlocks((int)std::max<size_t>(1, (size_t)(Env::get().kvCacheGb * (double)(1ull << 30)) / per));
   }
+}
+
+const float* Engine::ropeFor(int maxKv, int maxQ) {
+  if (rotDim <= 0) return nullptr;
+  double theta = ropeTheta;
+  if (spec.lognNtk) {
+    // Qwen-1 (src/layers/rotary_embedding_qwen.cpp:33-135): contexts within the training length use the base table
+    if (!useDynamicNtk || maxKv <= trainLen) return ropeTable_.as<float>();
+    theta = qwenNtkTheta(ropeTheta, rotDim, maxKv, trainLen);
+  } else if (spec.telechatNtk) {
+    theta = telechatNtkTheta(ropeTheta, rotDim, maxKv, trainLen);
+  } else {
+    return ropeTable_.as<float>();
+  }
+  const long long key = std::llround(theta);
+  auto it = ntkTables_.find(key);
+  if (it == ntkTables_.end()) {
+    RopeScaling rs;
+    // TeleChat scales a table by 0.1 ln(input / training) + 1 when it is first built during a pass with a longer
+    // input than the training length, and keeps it (src/layers/rotary_embedding_telechat.cpp:68-117)
+    if (spec.telechatNtk) rs.tableScale = telechatMscale(maxQ, trainLen);
+    const std::vector<float> tab = ropeTable(maxPos, rotDim, theta, rs);
+    DevBuf d(tab.size() * 4);
+    XFT_CUDA(cudaMemcpy(d.p, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice));
+    it = ntkTables_.emplace(key, std::move(d)).first;
+  }
+  return it->second.as<float>();
 }
 
 void Engine::ensureBlocks(int extra) {
@@ -336,7 +456,7 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
             std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count());
     }
   } step_log{t_begin, seqIds.size()};
-  std::vector<int> ids, pos, slots, cu{0}, kvl, rowsel;
+  std::vector<int> ids, pos, pos2, prefix, slots, cu{0}, kvl, rowsel;
   bool decode = true;
   int maxQ = 0, maxKv = 0;
   for (int sid : seqIds) {
@@ -346,7 +466,27 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
     if (tables->len(sid) > s.pastLen) tables->truncate(sid, s.pastLen);
     ensureBlocks((s.pastLen + n + kBlock - 1) / kBlock + 1);
     auto sl = tables->append(sid, n, [&](int a, int b) { copyBlock(a, b); });
-    for (int i = 0; i < n; ++i) { ids.push_back(s.pending[i]); pos.push_back(s.pastLen + i); slots.push_back(sl[i]); }
+    if (spec.rope2d) {
+      // ChatGLM-1 (src/models/chatglm.cpp:118-206): the position runs up to the [gMASK] / [MASK] slot and stays there
+      // from the bos token on; the block position is 0 in the context and counts 1, 2, ... from bos
+      const int kGmask = 130001, kMask = 130000, kBos = 130004;
+      const auto& pr = s.prompt;
+      auto find = [&](int tok) { auto it = std::find(pr.begin(), pr.end(), tok); return it == pr.end() ? -1 : (int)(it - pr.begin()); };
+      const int bos = find(kBos);
+      const int ctxLen = bos >= 0 ? bos : (int)pr.size() - 1;
+      int maskPos = find(kGmask);
+      if (maskPos < 0) maskPos = find(kMask);
+      if (maskPos < 0) maskPos = ctxLen;
+      for (int i = 0; i < n; ++i) {
+        const int p = s.pastLen + i;
+        pos.push_back(p < ctxLen ? p : maskPos);
+        pos2.push_back(p < ctxLen ? 0 : p - ctxLen + 1);
+      }
+      prefix.push_back(ctxLen);
+    } else {
+      for (int i = 0; i < n; ++i) pos.push_back(s.pastLen + i);
+    }
+    for (int i = 0; i < n; ++i) { ids.push_back(s.pending[i]); slots.push_back(sl[i]); }
     cu.push_back(cu.back() + n);
     kvl.push_back(s.pastLen + n);
     if (n != 1) decode = false;
@@ -354,7 +494,8 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
     maxKv = std::max(maxKv, s.pastLen + n);
     if (logitsAll) for (int i = cu[cu.size() - 2]; i < cu.back(); ++i) rowsel.push_back(i);
     else rowsel.push_back(cu.back() - 1);
-    if (s.pastLen + n > maxPos) throw std::runtime_error("sequence exceeds max_pos_seq_len");
+    if (s.pastLen + n > maxPos || (wpeRows > 0 && s.pastLen + n > wpeRows - 2))
+      throw std::runtime_error("sequence exceeds max_pos_seq_len");
   }
   const int T = (int)ids.size(), B = (int)seqIds.size(), R = (int)rowsel.size();
   size_t W = 1;
@@ -366,6 +507,18 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
     XFT_CUDA(cudaMemcpyAsync(d.p, v.data(), v.size() * 4, cudaMemcpyHostToDevice, st));
   };
   up(dIds, ids); up(dPos, pos); up(dSlots, slots); up(dCu, cu); up(dKv, kvl); up(dBt, bt); up(rows, rowsel);
+  if (spec.rope2d) { up(dPos2, pos2); up(dPrefix, prefix); }
+  const float* table = ropeFor(maxKv, maxQ);
+  const float* qScale = nullptr;
+  std::vector<float> qs;
+  if (spec.lognNtk && useLognAttn && maxKv > trainLen) {
+    // Qwen-1 log-n attention: queries beyond the training length are scaled by log(position + 1) / log(training length)
+    qs.resize(pos.size());
+    for (size_t i = 0; i < qs.size(); ++i) qs[i] = std::max(1.0f, std::log((float)pos[i] + 1.0f) / std::log((float)trainLen));
+    dQScale.ensure(qs.size() * 4 + 16);
+    XFT_CUDA(cudaMemcpyAsync(dQScale.p, qs.data(), qs.size() * 4, cudaMemcpyHostToDevice, st));
+    qScale = dQScale.as<float>();
+  }
   XFT_CUDA(cudaStreamSynchronize(st));   // host vectors go out of scope after this call
   const int qsz = heads * headDim, kvsz = kvHeads * headDim, qkvN = qsz + 2 * kvsz;
   x.ensure((size_t)T * hidden * 2); x2.ensure((size_t)T * hidden * 2); h.ensure((size_t)T * hidden * 2);
@@ -377,7 +530,8 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
     XFT_K(xft_gemm_bf16(X, K, Wt, wRows, K, Y, N, fp32, rowsT, N, K, gated, dualOff, bias, res, N, 1.0f, actc, nullptr,
                         ws.as<float>(), kWsBytes, counters.as<int>(), 8192, stp, 0, st));
   };
-  XFT_K(xft_embedding(dIds.as<int>(), wte.p, x.p, T, hidden, vocab, embedScale, nullptr, nullptr, 0, 0, stp, st));
+  XFT_K(xft_embedding(dIds.as<int>(), wte.p, x.p, T, hidden, vocab, embedScale, wpe.p, wpe.p ? dPos.as<int>() : nullptr, 2,
+                      wpeRows, stp, st));
   const int group = std::max(heads / std::max(kvHeads, 1), 1);
   int nsplit = 1;
   if (decode) {
@@ -390,33 +544,63 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
     if (nsplit > 1) { partO.ensure((size_t)B * heads * nsplit * headDim * 4); partMl.ensure((size_t)B * heads * nsplit * 8); }
   }
   const float scale = 1.0f / std::sqrt((float)headDim);
+  auto norm = [&](const void* in, const DevBuf& w, const DevBuf& b, void* out, int rowsT) {
+    if (spec.layerNorm) XFT_K(xft_layernorm(in, hidden, w.as<float>(), b.as<float>(), out, hidden, rowsT, hidden, eps, st));
+    else XFT_K(xft_rmsnorm(in, hidden, nullptr, 0, w.as<float>(), out, hidden, nullptr, rowsT, hidden, eps, st));
+  };
+  // ChatGLM-1 adds sqrt(2 * layers) times the NORMALISED input instead of the block input (src/models/chatglm.cpp)
+  const float resScale = spec.residFromNorm ? std::sqrt(2.0f * (float)layers) : 1.0f;
+  auto gemmRes = [&](const void* X, int K, const void* Wt, void* Y, const float* bias, const void* res) {
+    XFT_K(xft_gemm_bf16(X, K, Wt, hidden, K, Y, hidden, 0, T, hidden, K, 0, 0, bias, res, hidden, resScale, 0, nullptr,
+                        ws.as<float>(), kWsBytes, counters.as<int>(), 8192, stp, 0, st));
+  };
+  // three state buffers of T x hidden; which one plays which part rotates in the ChatGLM-1 flow
   void* cur = x.p;
   void* nxt = x2.p;
+  void* hb = h.p;
   for (int l = 0; l < layers; ++l) {
     LayerWeights& L = lw[l];
-    XFT_K(xft_rmsnorm(cur, hidden, nullptr, 0, L.n1.as<float>(), h.p, hidden, nullptr, T, hidden, eps, st));
-    gemm(h.p, hidden, L.qkv.p, qkvN, qkvBuf.p, qkvN, 0, 0, 0, L.qkvBias.as<float>(), nullptr, 0, T);
-    XFT_K(xft_qkv_rope_cache(qkvBuf.p, qkvN, T, heads, kvHeads, headDim, dPos.as<int>(), ropeTable_.as<float>(), headDim, 0, 0,
-                             maxPos, nullptr, L.qNorm.as<float>(), L.kNorm.as<float>(), eps, q.p, kc[l].p, vc[l].p,
-                             ks[l].as<float>(), vs[l].as<float>(), kvInt8 ? 1 : 0, kBlock, (long long)numBlocks * kBlock,
-                             dSlots.as<int>(), stp, st));
+    norm(cur, L.n1, L.n1b, hb, T);
+    gemm(hb, hidden, L.qkv.p, qkvN, qkvBuf.p, qkvN, 0, 0, 0, L.qkvBias.as<float>(), nullptr, 0, T);
+    if (spec.rope2d) {
+      XFT_K(xft_qkv_rope2d_cache(qkvBuf.p, qkvN, T, heads, kvHeads, headDim, dPos.as<int>(), dPos2.as<int>(), table, rotDim,
+                                 maxPos, q.p, kc[l].p, vc[l].p, ks[l].as<float>(), vs[l].as<float>(), kvInt8 ? 1 : 0, kBlock,
+                                 (long long)numBlocks * kBlock, dSlots.as<int>(), stp, st));
+    } else {
+      XFT_K(xft_qkv_rope_cache(qkvBuf.p, qkvN, T, heads, kvHeads, headDim, dPos.as<int>(), table, rotDim, spec.ropeStyle, 0,
+                               maxPos, qScale, L.qNorm.as<float>(), L.kNorm.as<float>(), eps, q.p, kc[l].p, vc[l].p,
+                               ks[l].as<float>(), vs[l].as<float>(), kvInt8 ? 1 : 0, kBlock, (long long)numBlocks * kBlock,
+                               dSlots.as<int>(), stp, st));
+    }
     XFT_K(xft_paged_attention(q.p, att.p, kc[l].p, vc[l].p, ks[l].as<float>(), vs[l].as<float>(), dBt.as<int>(), (int)W,
                               dCu.as<int>(), dKv.as<int>(), B, maxQ, heads, kvHeads, group, 0, headDim, kBlock, numBlocks,
-                              scale, nullptr, nullptr, decode ? 1 : 0, nsplit, partO.as<float>(), partMl.as<float>(),
-                              attnCounters.as<int>(), stp, st));
-    gemm(att.p, qsz, L.o.p, hidden, nxt, hidden, 0, 0, 0, nullptr, cur, 0, T);          // + residual
-    XFT_K(xft_rmsnorm(nxt, hidden, nullptr, 0, L.n2.as<float>(), h.p, hidden, nullptr, T, hidden, eps, st));
-    gemm(h.p, hidden, L.gateUp.p, 2 * inter, g.p, inter, 0, 1, inter, nullptr, nullptr, act, T);
-    gemm(g.p, inter, L.down.p, hidden, cur, hidden, 0, 0, 0, nullptr, nxt, 0, T);        // + residual, back into `cur`
+                              scale, slopes_.as<float>(), spec.prefixLm ? dPrefix.as<int>() : nullptr, decode ? 1 : 0, nsplit,
+                              partO.as<float>(), partMl.as<float>(), attnCounters.as<int>(), stp, st));
+    // attention output projection (+ bias) + residual
+    gemmRes(att.p, qsz, L.o.p, nxt, L.oBias.as<float>(), spec.residFromNorm ? hb : cur);
+    // ChatGLM-1 needs the normalised state again as the residual of the MLP: it goes to `cur`, whose content (the
+    // block input) is no longer needed; every other family normalises into the scratch buffer
+    void* hn = spec.residFromNorm ? cur : hb;
+    norm(nxt, L.n2, L.n2b, hn, T);
+    if (spec.mlp == 1) {
+      gemm(hn, hidden, L.gateUp.p, inter, g.p, inter, 0, 0, 0, L.fc1Bias.as<float>(), nullptr, act, T);
+    } else {
+      gemm(hn, hidden, L.gateUp.p, 2 * inter, g.p, inter, 0, 1, inter, nullptr, nullptr, act, T);
+    }
+    if (spec.residFromNorm) {
+      gemmRes(g.p, inter, L.down.p, hb, L.fc2Bias.as<float>(), hn);      // into the scratch, which becomes the state
+      std::swap(cur, hb);
+    } else {
+      gemmRes(g.p, inter, L.down.p, cur, L.fc2Bias.as<float>(), nxt);    // + residual, back into `cur`
+    }
   }
   // rows that need logits -> final norm -> lm_head (fp32)
-  h.ensure((size_t)R * hidden * 2);
   for (int r = 0; r < R; ++r)
     XFT_CUDA(cudaMemcpyAsync(static_cast<char*>(nxt) + (size_t)r * hidden * 2, static_cast<char*>(cur) + (size_t)rowsel[r] * hidden * 2,
                              (size_t)hidden * 2, cudaMemcpyDeviceToDevice, st));
-  XFT_K(xft_rmsnorm(nxt, hidden, nullptr, 0, finalNorm.as<float>(), h.p, hidden, nullptr, R, hidden, eps, st));
+  norm(nxt, finalNorm, finalNormBias, hb, R);
   logits.ensure((size_t)R * vocab * 4);
-  gemm(h.p, hidden, lmHead.p, vocab, logits.p, vocab, 1, 0, 0, nullptr, nullptr, 0, R);
+  gemm(hb, hidden, lmHead.p, vocab, logits.p, vocab, 1, 0, 0, nullptr, nullptr, 0, R);
   hostLogits.resize((size_t)R * vocab);
   XFT_CUDA(cudaMemcpyAsync(hostLogits.data(), logits.p, hostLogits.size() * 4, cudaMemcpyDeviceToHost, st));
   int hs = 0;

@@ -300,6 +300,9 @@ class ModelConfig:
             })
         if self.do_qk_norm:
             d["do_qk_norm"] = "1"
+        if self.model_type == "qwen":
+            d.update({"seq_length": str(self.seq_length), "use_logn_attn": str(int(self.use_logn_attn)),
+                      "use_dynamic_ntk": str(int(self.use_dynamic_ntk))})
         if extra:
             d.update(extra)
         cp[self.model_type] = d
