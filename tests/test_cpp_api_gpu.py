@@ -147,9 +147,11 @@ _CPP_FAMILIES = {
 def _cpu_oracle_logits(d, prompt, monkeypatch):
     """Last-position logits from the package's fp32 PyTorch path (XFT_ENGINE=CPU): none of the CUDA kernels."""
     import xfastertransformer_b200 as xft
+    from xfastertransformer_b200.parallel.dist import DistContext
     from xfastertransformer_b200.utils.flags import Env
     monkeypatch.setenv("XFT_ENGINE", "CPU")
     Env._inst = None
+    DistContext.reset()             # the process-wide context remembers its device
     try:
         m = xft.AutoModel.from_pretrained(d, dtype="bf16")
         assert m.model.ctx.device.type == "cpu"
@@ -157,6 +159,7 @@ def _cpu_oracle_logits(d, prompt, monkeypatch):
     finally:
         monkeypatch.delenv("XFT_ENGINE")
         Env._inst = None
+        DistContext.reset()
 
 
 @pytest.mark.parametrize("mt", sorted(_CPP_FAMILIES))
