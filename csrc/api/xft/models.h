@@ -6,9 +6,9 @@
 //   auto all = model.finalize();
 //
 // and the continuous-batching calls set_input(ids, seqIDs, maxLen) / forward() / freeSeqs().  The native engine
-// runs the dense decoder families (llama, yarn_llama, gemma, qwen, qwen2, qwen3, baichuan with RoPE or ALiBi, chatglm,
-// chatglm2 / 3 / 4, gpt (OPT), telechat) in bf16 on one B200; the mixture-of-experts families (mixtral, qwen3_moe,
-// deepseek_moe) and quantised weights run through the Python package.  It uses the same sm_100a kernels as the Python
+// runs llama, yarn_llama, gemma, qwen, qwen2, qwen3, baichuan (RoPE or ALiBi), chatglm, chatglm2 / 3 / 4, gpt (OPT),
+// telechat and the routed-expert families mixtral and qwen3_moe in bf16 on one B200; deepseek_moe (latent attention,
+// fp8 experts), quantised weights and more than one GPU run through the Python package.  It uses the same sm_100a kernels as the Python
 // package — greedy, top-k / top-p sampling and beam search (host scorer, beams fork and reorder paged KV block tables);
 // errors are exceptions (std::runtime_error), never exit().
 #pragma once

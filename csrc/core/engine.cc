@@ -100,6 +100,15 @@ std::vector<char> readFile(const std::string& path, size_t expect, int dt) {
 struct LayerWeights {
   DevBuf qkv, o, gateUp, down, n1, n2, qkvBias, qNorm, kNorm;
   DevBuf n1b, n2b, oBias, fc1Bias, fc2Bias;      // LayerNorm biases, output-projection bias, biases of the two-matrix MLP
+  DevBuf router, expGateUp, expDown;             // mixture of experts: [E, hidden], stacked [E * 2I, hidden], [E * hidden, I]
+};
+
+// A projection as the GEMMs see it: bf16 [rows, K], or per-output-channel codes (int8 [rows, K]; NF4 two codes per byte
+// [rows, K / 2]) with scale / zero point per row and, for int8 activations, the per-row sum of the codes.
+struct Lin {
+  const void* w = nullptr;       // bf16 weights (kind 0)
+  DevBuf q, scale, zero, wsum;
+  int rows = 0, K = 0, pitch = 0;       // pitch: bytes from one row of codes to the next
 };
 
 // What distinguishes one dense family from another (reference: one C++ class per family under src/models, selected by
@@ -111,12 +120,13 @@ struct FamilySpec {
   double rotFrac = 1.0;        // rotary dims / head dim
   bool rope2d = false;         // ChatGLM-1: two position streams, one per half of the head
   int mlp = 0;                 // 0: gate_proj / up_proj / down_proj; 1: dense_h_to_4h + bias -> act -> dense_4h_to_h + bias;
-                               // 2: merged gate‖up in dense_h_to_4h, dense_4h_to_h
+                               // 2: merged gate‖up in dense_h_to_4h, dense_4h_to_h; 3: routed experts (Mixtral, Qwen3-MoE)
   int embedding = 0;           // 0 plain, 1 scaled by sqrt(hidden) (Gemma), 2 plus learned positions at offset 2 (OPT)
   bool lognNtk = false;        // Qwen-1: dynamic-NTK base and log-n query scale beyond the training length
   bool telechatNtk = false;    // TeleChat: NTK base from max(context, training length), table scale on long inputs
   bool residFromNorm = false;  // ChatGLM-1: residual = sqrt(2 * layers) * normalised input
   bool prefixLm = false;       // ChatGLM-1: the prompt up to its bos token attends in both directions
+  int routeKind = 0;           // experts: 0 softmax over the top-k logits (Mixtral), 1 softmax then top-k, renormalised (Qwen3)
 };
 
 const FamilySpec* familySpec(const std::string& type) {
@@ -130,6 +140,8 @@ const FamilySpec* familySpec(const std::string& type) {
       {"chatglm4", false, 1, 0.5, false, 2},
       {"gpt", true, 0, 0.0, false, 1, 2},
       {"chatglm", true, 0, 0.5, true, 1, 0, false, false, true, true},
+      {"mixtral", false, 0, 1.0, false, 3, 0, false, false, false, false, 0},
+      {"qwen3_moe", false, 0, 1.0, false, 3, 0, false, false, false, false, 1},
   };
   for (const FamilySpec& f : table)
     if (type == f.name) return &f;
@@ -148,6 +160,8 @@ public:
   FamilySpec spec{""};
   int rotDim = 0;              // 0: no rotary table (OPT, ALiBi Baichuan)
   int wpeRows = 0;             // OPT: rows of the learned position table
+  int experts = 0, topK = 0, moeInter = 0;       // mixture of experts: count, experts per token, expert FFN width
+  int wq = 0;                  // layer projections: 0 bf16, 1 weight-only int8, 2 int8 weights x int8 activations, 3 NF4
   bool alibi = false;
   int trainLen = 0;            // Qwen-1 seq_length / TeleChat training context
   bool useDynamicNtk = true, useLognAttn = true;
@@ -175,14 +189,19 @@ private:
   void copyBlock(int src, int dst);
   std::string dir;
   int fileDt = 1;
+  void quantise(DevBuf& dense, int rows, int K, Lin& out);      // dense bf16 [rows, K] -> `out` per `wq`; frees `dense`
   const float* ropeFor(int maxKv, int maxQ);      // the rotary table of this pass (NTK families keep one per base)
   DevBuf wte, wpe, lmHead, finalNorm, finalNormBias, ropeTable_, slopes_, ws, counters, status, attnCounters, partO, partMl;
   std::map<long long, DevBuf> ntkTables_;         // by round(base): Qwen-1 / TeleChat tables beyond the first
   RopeScaling ropeScaling_;
   std::vector<LayerWeights> lw;
+  struct LayerLins { Lin qkv, o, gateUp, down; };
+  std::vector<LayerLins> lins;
+  DevBuf actQ, actScale, actZero, actSum, guBuf;   // int8 activations + their row statistics; gate‖up before the activation
   std::vector<DevBuf> kc, vc, ks, vs;
   int numBlocks = 0;
   // activations
+  DevBuf moeLogits, moeIdx, moeWts, moePos, moeSrc, moeRowW, moeTiles, moeMeta, moeXs, moeH1, moeYs;
   DevBuf dIds, dPos, dPos2, dPrefix, dQScale, dSlots, dCu, dKv, dBt, x, x2, h, qkvBuf, q, att, g, rows, logits;
   cudaStream_t st = nullptr;
   static constexpr int kBlock = 64;
@@ -219,7 +238,12 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
   const FamilySpec* fam = familySpec(type);
   if (!fam) throw std::runtime_error("the native C++ engine runs the dense families; use the Python API for [" + type + "]");
   spec = *fam;
-  if (dt != DataType::bf16 && dt != DataType::fp16) throw std::runtime_error("the native C++ engine runs bf16 (fp16 weights are kept as bf16)");
+  if (dt == DataType::int8) wq = 1;
+  else if (dt == DataType::w8a8) wq = 2;
+  else if (dt == DataType::nf4) wq = 3;
+  else if (dt != DataType::bf16 && dt != DataType::fp16)
+    throw std::runtime_error("the native C++ engine runs bf16 (fp16 weights are kept as bf16), int8, w8a8 and nf4 weights");
+  if (wq && spec.mlp == 3) throw std::runtime_error("quantised experts run through the Python API");
   kvInt8 = kvdt == DataType::int8;
   heads = (int)ini.getInt(type, "head_num");
   kvHeads = (int)ini.getInt(type, "kv_head_num", heads);
@@ -267,6 +291,16 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
   act = a.rfind("gelu", 0) == 0 ? 3 : a == "relu" ? 1 : 2;
   if (spec.mlp == 1 && act == 2) act = 3;        // the two-matrix MLP is relu (OPT) or gelu
   if (spec.mlp == 2) act = 2;                    // the merged gate‖up MLP of ChatGLM2+ is SwiGLU
+  if (spec.mlp == 3) {
+    experts = (int)ini.getInt(type, "sparse_experts", 0);
+    topK = (int)ini.getInt(type, "num_experts_per_tok", 0);
+    if (topK <= 0) topK = type == "mixtral" ? 2 : 8;
+    moeInter = type == "mixtral" ? 0 : (int)ini.getInt(type, "moe_intermediate_size", 0);
+    if (moeInter <= 0) moeInter = inter;
+    if (experts <= 0 || topK > experts || topK > 32 || moeInter % 8 || hidden % 8)
+      throw std::runtime_error("mixture of experts: sparse_experts / num_experts_per_tok / sizes are not usable");
+    if (a == "swiglu") act = 2;
+  }
   qkNorm = ini.getBool(type, "do_qk_norm", false);
   if (spec.embedding == 1) embedScale = std::sqrt((float)hidden);
   std::string wdt = ini.get(type, "weight_data_type", "fp16");
@@ -301,6 +335,7 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
   finalNorm = loadVector("model.final_layernorm.weight.bin", hidden);
   if (spec.layerNorm) finalNormBias = loadVector("model.final_layernorm.bias.bin", hidden);
   lw.resize(layers);
+  lins.resize(layers);
   for (int i = 0; i < layers; ++i) {
     const std::string p = "model.layers." + std::to_string(i) + ".";
     LayerWeights& L = lw[i];
@@ -310,7 +345,22 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
     L.o.reset((size_t)hidden * qsz * 2);
     loadLinear(p + "attention.dense.weight.0.bin", qsz, hidden, L.o.p, 0, qsz);
     L.oBias = loadVector(p + "attention.dense.bias.bin", hidden, true);
-    if (spec.mlp == 1) {
+    if (spec.mlp == 3) {
+      // router [hidden, experts] on disk -> [experts, hidden]; experts stacked: gate rows then up rows per expert, then
+      // the down matrices (the layout the grouped GEMM walks, src/layers/mlp_mixtral.h:95-187 keeps one MLP object each)
+      const bool mix = type == "mixtral";
+      const int I = moeInter;
+      L.router.reset((size_t)experts * hidden * 2);
+      loadLinear(p + (mix ? "moe.gate.weight.bin" : "mlp.gate.weight.0.bin"), hidden, experts, L.router.p, 0, hidden);
+      L.expGateUp.reset((size_t)experts * 2 * I * hidden * 2);
+      L.expDown.reset((size_t)experts * hidden * I * 2);
+      for (int e = 0; e < experts; ++e) {
+        const std::string ep = p + (mix ? "moe.sparse_experts." : "mlp.experts.") + std::to_string(e) + ".";
+        loadLinear(ep + (mix ? "w1.0.bin" : "gate_proj.weight.0.bin"), hidden, I, L.expGateUp.p, e * 2 * I, hidden);
+        loadLinear(ep + (mix ? "w2.0.bin" : "up_proj.weight.0.bin"), hidden, I, L.expGateUp.p, e * 2 * I + I, hidden);
+        loadLinear(ep + (mix ? "w3.0.bin" : "down_proj.weight.0.bin"), I, hidden, L.expDown.p, e * hidden, I);
+      }
+    } else if (spec.mlp == 1) {
       L.gateUp.reset((size_t)inter * hidden * 2);
       loadLinear(p + "mlp.dense_h_to_4h.weight.0.bin", hidden, inter, L.gateUp.p, 0, hidden);
       L.fc1Bias = loadVector(p + "mlp.dense_h_to_4h.bias.0.bin", inter);
@@ -324,9 +374,11 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
         loadLinear(p + "mlp.up_proj.weight.0.bin", hidden, inter, L.gateUp.p, inter, hidden);
       }
     }
-    L.down.reset((size_t)hidden * inter * 2);
-    loadLinear(p + (spec.mlp == 0 ? "mlp.down_proj.weight.0.bin" : "mlp.dense_4h_to_h.weight.0.bin"), inter, hidden, L.down.p, 0,
-               inter);
+    if (spec.mlp != 3) {
+      L.down.reset((size_t)hidden * inter * 2);
+      loadLinear(p + (spec.mlp == 0 ? "mlp.down_proj.weight.0.bin" : "mlp.dense_4h_to_h.weight.0.bin"), inter, hidden,
+                 L.down.p, 0, inter);
+    }
     L.n1 = loadVector(p + "input_layernorm.weight.bin", hidden);
     L.n2 = loadVector(p + "post_attention_layernorm.weight.bin", hidden);
     if (spec.layerNorm) {
@@ -336,6 +388,13 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
     if (qkNorm) {
       L.qNorm = loadVector(p + "attention.q_norm.weight.bin", headDim);
       L.kNorm = loadVector(p + "attention.k_norm.weight.bin", headDim);
+    }
+    LayerLins& Q = lins[i];
+    quantise(L.qkv, qsz + 2 * kvsz, hidden, Q.qkv);
+    quantise(L.o, hidden, qsz, Q.o);
+    if (spec.mlp != 3) {
+      quantise(L.gateUp, spec.mlp == 1 ? inter : 2 * inter, hidden, Q.gateUp);
+      quantise(L.down, hidden, inter, Q.down);
     }
   }
   // rotary table [maxPos, rotDim] = cos(rotDim/2) ‖ sin(rotDim/2); the NTK families build further tables on demand
@@ -362,6 +421,26 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
     const size_t per = (size_t)layers * kvHeads * kBlock * (2 * headDim * esz + (kvInt8 ? 8 : 0));
     ensureBlocks((int)std::max<size_t>(1, (size_t)(Env::get().kvCacheGb * (double)(1ull << 30)) / per));
   }
+}
+
+void Engine::quantise(DevBuf& dense, int rows, int K, Lin& out) {
+  out.rows = rows; out.K = K;
+  if (wq == 0) { out.w = dense.p; return; }
+  // the quantiser of the loader (same kernel as the Python package uses): per output channel, asymmetric int8 or NF4
+  if (wq == 3 && (K % 2)) throw std::runtime_error("nf4 weights need even input dimensions");
+  if (wq == 2 && (K % 16)) throw std::runtime_error("w8a8 weights need input dimensions that are multiples of 16");
+  // rows start on 16-byte boundaries (the GEMM reads them with TMA); codes in the padding are zero and meet
+  // zero-filled activations
+  const size_t rowBytes = ((wq == 3 ? (size_t)K / 2 : (size_t)K) + 15) / 16 * 16;
+  out.pitch = (int)rowBytes;
+  out.q.reset((size_t)rows * rowBytes);
+  XFT_CUDA(cudaMemsetAsync(out.q.p, 0, (size_t)rows * rowBytes, st));
+  out.scale.reset((size_t)rows * 4); out.zero.reset((size_t)rows * 4);
+  if (wq == 2) out.wsum.reset((size_t)rows * 4);
+  XFT_K(xft_quantize_rows(dense.p, 2, K, rows, K, wq == 3 ? 2 : 0, out.q.p, (long long)rowBytes, out.scale.as<float>(),
+                          out.zero.as<float>(), out.wsum.as<float>(), st));
+  XFT_CUDA(cudaStreamSynchronize(st));
+  dense.reset(0);
 }
 
 const float* Engine::ropeFor(int maxKv, int maxQ) {
@@ -523,7 +602,7 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
   const int qsz = heads * headDim, kvsz = kvHeads * headDim, qkvN = qsz + 2 * kvsz;
   x.ensure((size_t)T * hidden * 2); x2.ensure((size_t)T * hidden * 2); h.ensure((size_t)T * hidden * 2);
   qkvBuf.ensure((size_t)T * qkvN * 2); q.ensure((size_t)T * qsz * 2); att.ensure((size_t)T * qsz * 2);
-  g.ensure((size_t)T * inter * 2);
+  g.ensure((size_t)T * std::max(inter, 1) * 2);
   int* stp = status.as<int>();
   auto gemm = [&](const void* X, int K, const void* Wt, int wRows, void* Y, int N, int fp32, int gated, int dualOff,
                   const float* bias, const void* res, int actc, int rowsT) {
@@ -550,10 +629,50 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
   };
   // ChatGLM-1 adds sqrt(2 * layers) times the NORMALISED input instead of the block input (src/models/chatglm.cpp)
   const float resScale = spec.residFromNorm ? std::sqrt(2.0f * (float)layers) : 1.0f;
-  auto gemmRes = [&](const void* X, int K, const void* Wt, void* Y, const float* bias, const void* res) {
-    XFT_K(xft_gemm_bf16(X, K, Wt, hidden, K, Y, hidden, 0, T, hidden, K, 0, 0, bias, res, hidden, resScale, 0, nullptr,
-                        ws.as<float>(), kWsBytes, counters.as<int>(), 8192, stp, 0, st));
+  // one layer projection in whichever form its weights have: Y[T, N] = epilogue(X[T, K] · W^T); `gated`: W holds gate rows
+  // then up rows and Y = act(gate) * up
+  auto lin = [&](const Lin& Wt, const void* X, void* Y, int N, int gated, const float* bias, const void* res, float rscale,
+                 int actc) {
+    const int K = Wt.K;
+    if (wq == 0) {
+      XFT_K(xft_gemm_bf16(X, K, Wt.w, Wt.rows, K, Y, N, 0, T, N, K, gated, gated ? N : 0, bias, res, N, rscale, actc, nullptr,
+                          ws.as<float>(), kWsBytes, counters.as<int>(), 8192, stp, 0, st));
+    } else if (wq == 2) {
+      // dynamic per-token int8 activations, int8 tensor-core product, corrections for both zero points in the epilogue
+      actQ.ensure((size_t)T * K); actScale.ensure((size_t)T * 4); actZero.ensure((size_t)T * 4); actSum.ensure((size_t)T * 4);
+      XFT_K(xft_quant_act(X, K, actQ.p, K, actScale.as<float>(), actZero.as<float>(), actSum.as<float>(), T, K, st));
+      void* out = Y;
+      if (gated) { guBuf.ensure((size_t)T * 2 * N * 2); out = guBuf.p; }
+      const int n = gated ? 2 * N : N;
+      XFT_K(xft_w8a8_gemm(actQ.p, K, Wt.q.p, Wt.pitch, out, n, 0, T, n, K, actScale.as<float>(), actZero.as<float>(),
+                          actSum.as<float>(), Wt.scale.as<float>(), Wt.zero.as<float>(), Wt.wsum.as<float>(), bias,
+                          gated ? nullptr : res, N, rscale, gated ? 0 : actc, ws.as<float>(), kWsBytes, counters.as<int>(), 8192,
+                          stp, st));
+      if (gated) XFT_K(xft_gated_act(guBuf.p, Y, T, N, actc, st));
+    } else {
+      const bool nf4 = wq == 3;
+      const float* xsum = nullptr;
+      if (!nf4) {      // an asymmetric zero point contributes zero * sum(x) per output
+        actSum.ensure((size_t)T * 4);
+        XFT_K(xft_row_sum(X, K, actSum.as<float>(), T, K, st));
+        xsum = actSum.as<float>();
+      }
+      XFT_K(xft_qgemm(X, K, Wt.q.p, Wt.rows, Wt.pitch, nf4 ? 2 : 0, Y, N, 0, T, N, K, gated, gated ? N : 0,
+                      Wt.scale.as<float>(), nf4 ? nullptr : Wt.zero.as<float>(), xsum, 0, bias, res, N, rscale, actc,
+                      ws.as<float>(), kWsBytes, counters.as<int>(), 8192, stp, st));
+    }
   };
+  int moeBn = 16, moeMaxTiles = 0;
+  if (spec.mlp == 3) {
+    const int rowsMax = T * topK, avg = std::max(1, (rowsMax + experts - 1) / experts);
+    moeBn = avg <= 16 ? 16 : avg <= 32 ? 32 : avg <= 64 ? 64 : 128;      // token tile of the grouped GEMMs
+    moeMaxTiles = (rowsMax + moeBn - 1) / moeBn + experts;
+    moeLogits.ensure((size_t)T * experts * 4); moeIdx.ensure((size_t)rowsMax * 4); moeWts.ensure((size_t)rowsMax * 4);
+    moePos.ensure((size_t)rowsMax * 4); moeSrc.ensure((size_t)rowsMax * 4); moeRowW.ensure((size_t)rowsMax * 4);
+    moeTiles.ensure((size_t)moeMaxTiles * 16); moeMeta.ensure(8);
+    moeXs.ensure((size_t)rowsMax * hidden * 2); moeH1.ensure((size_t)rowsMax * moeInter * 2);
+    moeYs.ensure((size_t)rowsMax * hidden * 4);
+  }
   // three state buffers of T x hidden; which one plays which part rotates in the ChatGLM-1 flow
   void* cur = x.p;
   void* nxt = x2.p;
@@ -561,7 +680,8 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
   for (int l = 0; l < layers; ++l) {
     LayerWeights& L = lw[l];
     norm(cur, L.n1, L.n1b, hb, T);
-    gemm(hb, hidden, L.qkv.p, qkvN, qkvBuf.p, qkvN, 0, 0, 0, L.qkvBias.as<float>(), nullptr, 0, T);
+    const LayerLins& Q = lins[l];
+    lin(Q.qkv, hb, qkvBuf.p, qkvN, 0, L.qkvBias.as<float>(), nullptr, 1.0f, 0);
     if (spec.rope2d) {
       XFT_K(xft_qkv_rope2d_cache(qkvBuf.p, qkvN, T, heads, kvHeads, headDim, dPos.as<int>(), dPos2.as<int>(), table, rotDim,
                                  maxPos, q.p, kc[l].p, vc[l].p, ks[l].as<float>(), vs[l].as<float>(), kvInt8 ? 1 : 0, kBlock,
@@ -577,21 +697,38 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
                               scale, slopes_.as<float>(), spec.prefixLm ? dPrefix.as<int>() : nullptr, decode ? 1 : 0, nsplit,
                               partO.as<float>(), partMl.as<float>(), attnCounters.as<int>(), stp, st));
     // attention output projection (+ bias) + residual
-    gemmRes(att.p, qsz, L.o.p, nxt, L.oBias.as<float>(), spec.residFromNorm ? hb : cur);
+    lin(Q.o, att.p, nxt, hidden, 0, L.oBias.as<float>(), spec.residFromNorm ? hb : cur, resScale, 0);
     // ChatGLM-1 needs the normalised state again as the residual of the MLP: it goes to `cur`, whose content (the
     // block input) is no longer needed; every other family normalises into the scratch buffer
     void* hn = spec.residFromNorm ? cur : hb;
     norm(nxt, L.n2, L.n2b, hn, T);
+    if (spec.mlp == 3) {
+      // router logits (fp32) -> top-k experts and weights -> rows grouped by expert -> two grouped GEMMs (the second
+      // scales each row by its routing weight) -> per-token sum + residual
+      const int E = experts, k = topK, I = moeInter;
+      gemm(hn, hidden, L.router.p, E, moeLogits.p, E, 1, 0, 0, nullptr, nullptr, 0, T);
+      XFT_K(xft_moe_route(moeLogits.as<float>(), E, T, E, k, spec.routeKind, nullptr, 1, 1, 1.0f, 1, 1, moeIdx.as<int>(),
+                          moeWts.as<float>(), st));
+      XFT_K(xft_moe_plan(moeIdx.as<int>(), moeWts.as<float>(), T, k, 0, E, moeBn, moePos.as<int>(), moeSrc.as<int>(),
+                         moeRowW.as<float>(), moeTiles.p, moeMeta.as<int>(), moeMaxTiles, T * k, st));
+      XFT_K(xft_moe_gather(hn, hidden, moeSrc.as<int>(), moeMeta.as<int>(), moeXs.p, T * k, hidden, st));
+      XFT_K(xft_gemm_bf16_grouped(moeXs.p, hidden, T * k, L.expGateUp.p, E * 2 * I, hidden, moeH1.p, I, 0, I, hidden, 1, I,
+                                  2 * I, moeTiles.p, moeMeta.as<int>(), moeMaxTiles, moeBn, nullptr, act, stp, st));
+      XFT_K(xft_gemm_bf16_grouped(moeH1.p, I, T * k, L.expDown.p, E * hidden, I, moeYs.p, hidden, 1, hidden, I, 0, 0, hidden,
+                                  moeTiles.p, moeMeta.as<int>(), moeMaxTiles, moeBn, moeRowW.as<float>(), 0, stp, st));
+      XFT_K(xft_moe_combine(moeYs.as<float>(), moePos.as<int>(), k, nullptr, nxt, hidden, cur, nullptr, T, hidden, st));
+      continue;
+    }
     if (spec.mlp == 1) {
-      gemm(hn, hidden, L.gateUp.p, inter, g.p, inter, 0, 0, 0, L.fc1Bias.as<float>(), nullptr, act, T);
+      lin(Q.gateUp, hn, g.p, inter, 0, L.fc1Bias.as<float>(), nullptr, 1.0f, act);
     } else {
-      gemm(hn, hidden, L.gateUp.p, 2 * inter, g.p, inter, 0, 1, inter, nullptr, nullptr, act, T);
+      lin(Q.gateUp, hn, g.p, inter, 1, nullptr, nullptr, 1.0f, act);
     }
     if (spec.residFromNorm) {
-      gemmRes(g.p, inter, L.down.p, hb, L.fc2Bias.as<float>(), hn);      // into the scratch, which becomes the state
+      lin(Q.down, g.p, hb, hidden, 0, L.fc2Bias.as<float>(), hn, resScale, 0);      // into the scratch, which becomes the state
       std::swap(cur, hb);
     } else {
-      gemmRes(g.p, inter, L.down.p, cur, L.fc2Bias.as<float>(), nxt);    // + residual, back into `cur`
+      lin(Q.down, g.p, cur, hidden, 0, L.fc2Bias.as<float>(), nxt, resScale, 0);    // + residual, back into `cur`
     }
   }
   // rows that need logits -> final norm -> lm_head (fp32)

@@ -45,6 +45,22 @@ int xft_gemm_bf16_grouped(const void* X, int ldx, int x_rows, const void* W, int
                           int out_fp32, int N, int K, int gated, int dual_off, int group_w_rows, const void* group_tiles,
                           const int* num_group_tiles, int max_tiles, int bn, const float* col_scale, int act, int* status,
                           cudaStream_t st);
+// quantised weights: load-time quantiser (mode 0 int8, 1 uint4, 2 nf4), weight-only GEMM (qtype 0 int8, 1 int4, 2 nf4,
+// 3 fp8, 4 int4 fast layout), per-row activation sums / dynamic int8 activations, int8 x int8 GEMM, act(gate) * up
+int xft_quantize_rows(const void* w, int dtype, long long ldw, int rows, int K, int mode, void* q, long long ldq_bytes,
+                      float* scale, float* zero, float* wsum, cudaStream_t st);
+int xft_qgemm(const void* X, int ldx, const void* Wq, int w_rows, int ldw_bytes, int qtype, void* Y, int ldo, int out_fp32,
+              int T, int N, int K, int gated, int dual_off, const float* scale, const float* zero, const float* xsum,
+              int scale_ld, const float* bias, const void* residual, int ldr, float res_scale, int act, float* ws,
+              size_t ws_bytes, int* counters, int n_counters, int* status, cudaStream_t st);
+int xft_row_sum(const void* x, int ldx, float* out, int T, int K, cudaStream_t st);
+int xft_quant_act(const void* x, int ldx, void* q, int ldq, float* scale, float* zero, float* qsum, int T, int K,
+                  cudaStream_t st);
+int xft_w8a8_gemm(const void* qx, int ldqx, const void* Wq, int ldw, void* Y, int ldo, int out_fp32, int T, int N, int K,
+                  const float* a_scale, const float* a_zero, const float* a_qsum, const float* w_scale, const float* w_zero,
+                  const float* w_sum, const float* bias, const void* residual, int ldr, float res_scale, int act, float* ws,
+                  size_t ws_bytes, int* counters, int n_counters, int* status, cudaStream_t st);
+int xft_gated_act(const void* gu, void* out, int T, int I, int act, cudaStream_t st);
 int xft_sample_topk_topp(const float* logits, int ld, int rows, int V, int k, float top_p, float temperature,
                          const float* uniform, int* out, cudaStream_t st);
 }

@@ -582,6 +582,110 @@ __global__ void transpose_to_bf16_kernel(const S* __restrict__ src, long long ld
 }
 }  // namespace xft
 
+// Quantise-at-load (reference: MMHelper::convertWeight, src/utils/matmul_helper.h:205-373, a host loop there): one CTA per
+// output channel finds the row's range, derives scale and zero point and writes the codes.
+//   mode 0: int8, asymmetric:  scale = (max - min) / 255, zero = (max + min) / 2 + scale / 2, q = rint((w - zero) / scale) in
+//           [-128, 127]; `wsum` (optional) gets the sum of the codes (the W8A8 kernel's correction term)
+//   mode 1: uint4, asymmetric: scale = (max - min) / 15, zero = min, q in [0, 15], two codes per byte, even index low
+//   mode 2: NF4: scale = max|w|, zero = 0, q = nearest of the 16 NormalFloat levels (first on ties), packed like uint4
+// Divisions are IEEE-rounded so the codes equal those of the PyTorch formulation of the same arithmetic.
+namespace xft {
+__constant__ float kNf4Code[16] = {-1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,
+                                   -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
+                                   0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f,
+                                   0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
+
+template <typename S>
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const S* __restrict__ w, long long ldw, int K, int mode,
+                                                            uint8_t* __restrict__ q, long long ldq_bytes,
+                                                            float* __restrict__ scale, float* __restrict__ zero,
+                                                            float* __restrict__ wsum) {
+  __shared__ float s_mx[8], s_mn[8];
+  __shared__ int s_sum[8];
+  const int row = blockIdx.x, tid = threadIdx.x;
+  const S* src = w + (long long)row * ldw;
+  float mx = -INFINITY, mn = INFINITY;
+  for (int i = tid; i < K; i += 256) {
+    const float v = load_as_float<S>(src + i);
+    mx = fmaxf(mx, mode == 2 ? fabsf(v) : v);
+    mn = fminf(mn, v);
+  }
+  mx = warp_max(mx);
+  mn = -warp_max(-mn);
+  if ((tid & 31) == 0) { s_mx[tid >> 5] = mx; s_mn[tid >> 5] = mn; }
+  __syncthreads();
+  mx = s_mx[0]; mn = s_mn[0];
+  for (int i = 1; i < 8; ++i) { mx = fmaxf(mx, s_mx[i]); mn = fminf(mn, s_mn[i]); }
+  float sc, zp;
+  if (mode == 0) {
+    sc = fmaxf(__fdiv_rn(__fsub_rn(mx, mn), 255.0f), 1e-10f);
+    zp = __fadd_rn(__fmul_rn(__fadd_rn(mx, mn), 0.5f), __fmul_rn(0.5f, sc));
+  } else if (mode == 1) {
+    sc = fmaxf(__fdiv_rn(__fsub_rn(mx, mn), 15.0f), 1e-10f);
+    zp = mn;
+  } else {
+    sc = fmaxf(mx, 1e-10f);
+    zp = 0.f;
+  }
+  if (tid == 0) { scale[row] = sc; zero[row] = zp; }
+  uint8_t* dst = q + (long long)row * ldq_bytes;
+  int acc = 0;
+  if (mode == 0) {
+    for (int i = tid; i < K; i += 256) {
+      const float r = rintf(__fdiv_rn(__fsub_rn(load_as_float<S>(src + i), zp), sc));
+      const int c = (int)fminf(fmaxf(r, -128.f), 127.f);
+      reinterpret_cast<int8_t*>(dst)[i] = (int8_t)c;
+      acc += c;
+    }
+    if (wsum) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if ((tid & 31) == 0) s_sum[tid >> 5] = acc;
+      __syncthreads();
+      if (tid == 0) {
+        int t = 0;
+        for (int i = 0; i < 8; ++i) t += s_sum[i];
+        wsum[row] = (float)t;
+      }
+    }
+    return;
+  }
+  for (int i = tid; i < K / 2; i += 256) {         // one byte = codes 2i (low nibble) and 2i + 1 (high nibble)
+    int code[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const float v = load_as_float<S>(src + 2 * i + j);
+      if (mode == 1) {
+        code[j] = (int)fminf(fmaxf(rintf(__fdiv_rn(__fsub_rn(v, zp), sc)), 0.f), 15.f);
+      } else {
+        const float xn = __fdiv_rn(v, sc);
+        int best = 0;
+        float bd = fabsf(__fsub_rn(xn, kNf4Code[0]));
+        for (int c = 1; c < 16; ++c) {
+          const float d = fabsf(__fsub_rn(xn, kNf4Code[c]));
+          if (d < bd) { bd = d; best = c; }
+        }
+        code[j] = best;
+      }
+    }
+    dst[i] = (uint8_t)(code[0] | (code[1] << 4));
+  }
+}
+}  // namespace xft
+
+// w [rows, K] (dtype 0 fp32, 1 fp16, 2 bf16; row stride ldw elements) -> codes q (row stride ldq_bytes), scale[rows],
+// zero[rows], and for mode 0 optionally wsum[rows].  Modes 1 and 2 need an even K.
+extern "C" int xft_quantize_rows(const void* w, int dtype, long long ldw, int rows, int K, int mode, void* q,
+                                 long long ldq_bytes, float* scale, float* zero, float* wsum, cudaStream_t st) {
+  if (rows <= 0 || K <= 0) return 0;
+  if (mode < 0 || mode > 2 || (mode != 0 && (K & 1)) || !q || !scale || !zero) return -1;
+  uint8_t* qq = (uint8_t*)q;
+  if (dtype == 0) xft::quantize_rows_kernel<float><<<rows, 256, 0, st>>>((const float*)w, ldw, K, mode, qq, ldq_bytes, scale, zero, wsum);
+  else if (dtype == 1) xft::quantize_rows_kernel<__half><<<rows, 256, 0, st>>>((const __half*)w, ldw, K, mode, qq, ldq_bytes, scale, zero, wsum);
+  else xft::quantize_rows_kernel<xft::bf16><<<rows, 256, 0, st>>>((const xft::bf16*)w, ldw, K, mode, qq, ldq_bytes, scale, zero, wsum);
+  return (int)cudaGetLastError();
+}
+
 namespace xft {
 // e4m3 byte -> float (no NaN/Inf handling beyond what the format encodes: 0x7f / 0xff are NaN)
 __device__ __forceinline__ float e4m3_to_float(uint8_t v) {

@@ -141,6 +141,8 @@ _CPP_FAMILIES = {
     "gpt": dict(activation_type="relu"),
     "telechat": {},
     "chatglm": dict(activation_type="gelu"),
+    "mixtral": dict(sparse_experts=8, num_experts_per_tok=2),
+    "qwen3_moe": dict(sparse_experts=8, num_experts_per_tok=4, moe_intermediate_size=256, do_qk_norm=True, kv_head_num=2),
 }
 
 
@@ -164,7 +166,7 @@ def _cpu_oracle_logits(d, prompt, monkeypatch):
 
 @pytest.mark.parametrize("mt", sorted(_CPP_FAMILIES))
 def test_cpp_engine_families_match_python(mt, tmp_path, monkeypatch):
-    """Every dense family of the C++ engine (norm kind, biases, rotary variant, MLP layout, position scheme) against the
+    """Every family of the C++ engine (norm kind, biases, rotary variant, MLP layout or experts, position scheme) against the
     Python engine on the same synthetic checkpoint: last-prompt-token logits numerically, then greedy tokens.  Both GPU
     engines are also held against the fp32 PyTorch path of the package."""
     import xfastertransformer_b200 as xft
@@ -214,3 +216,35 @@ def test_cpp_engine_families_match_python(mt, tmp_path, monkeypatch):
             py.set_input_cb(tok.tolist(), sid, P + new + 2)
             lg = py.forward_cb().float().cpu()
     py.free_seqs(sid)
+
+
+@pytest.mark.parametrize("dtype", ["int8", "w8a8", "nf4"])
+def test_cpp_engine_quantised_weights(dtype, tmp_path, monkeypatch):
+    """Quantise-at-load in the C++ engine (per-channel int8 weight-only, int8 x int8, NF4): same codes and kernels as
+    the Python engine with that dtype, so the logits agree closely; both track the fp32 oracle of the dense model within
+    the quantisation error."""
+    import xfastertransformer_b200 as xft
+    from xfastertransformer_b200.tools.synthetic import preset, write_synthetic_checkpoint
+    lib = os.path.join(ROOT, "xfastertransformer_b200", "lib", "libxft_b200_torch.so")
+    if not os.path.exists(lib):
+        pytest.skip("torch binding not built")
+    torch.ops.load_library(lib)
+    d = str(tmp_path / "tiny")
+    write_synthetic_checkpoint(d, preset("tiny-llama", vocab_size=2000, kv_head_num=2), seed=6, dtype="bf16", std=0.08)
+    prompt = torch.randint(5, 1990, (2, 20), generator=torch.Generator().manual_seed(2))
+    P = prompt.shape[1]
+    oracle = _cpu_oracle_logits(d, prompt, monkeypatch)
+    py = xft.AutoModel.from_pretrained(d, dtype=dtype)
+    want = py(prompt)[:, -1].float().cpu()
+    m = torch.classes.xfastertransformer.AutoModel(d, dtype, "fp16")
+    ids = m.set_input_cb(prompt, None, None, torch.tensor([P + 4, P + 4]))
+    got = m.forward_cb().float().cpu()
+    assert m.free_seqs(ids)
+    top = oracle.abs().max().item()
+    assert (got - want).abs().max().item() <= 0.03 * top + 0.02, (dtype, (got - want).abs().max().item(), top)
+    assert (got - oracle).abs().max().item() <= (0.9 if dtype == "nf4" else 0.2) * top, (dtype, (got - oracle).abs().max().item())
+    m.config(P + 6, None, None, None, None, 100000, 0, None, None, None, None, None, None)
+    m.input(prompt)
+    while not m.is_done():
+        m.generate()
+    assert m.finalize().shape == (2, P + 6)

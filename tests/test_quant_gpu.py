@@ -70,3 +70,32 @@ def test_tiny_llama_quant_dtypes(dtype, tmp_path):
     assert rel < (0.6 if "4" in dtype else 0.15), rel   # per-channel 4-bit noise on random weights
     out = m.generate(ids, max_length=40)
     assert out.shape == (2, 40)
+
+
+@pytest.mark.parametrize("kind", ["int8", "w8a8", "int4", "nf4"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_quantize_at_load_kernel_matches_pytorch_formulation(kind, dtype):
+    """The load-time quantiser (one kernel per matrix) against the PyTorch formulation of the same arithmetic: scales and
+    zero points bit-equal, codes equal (a code may differ by one where the quotient sits on a rounding boundary)."""
+    from xfastertransformer_b200.ops import native_quant
+    g = torch.Generator().manual_seed(17)
+    for rows, K in [(70, 1000), (9, 4096), (3, 34)]:
+        w = (torch.randn(rows, K, generator=g) * 0.05).to(dtype)
+        w[0] = 0                                            # a constant row: scale clamps, codes stay finite
+        q, s, z, ws = native_quant.quantize_rows(w.cuda(), kind)
+        if kind in ("int8", "w8a8"):
+            wq, wsc, wz = R.quantize_int8_per_channel(w)
+        elif kind == "int4":
+            wq, wsc, wz = R.quantize_uint4_per_channel(w)
+        else:
+            wq, wsc, wz = R.quantize_nf4_per_channel(w)
+        assert torch.equal(s.cpu(), wsc) and torch.equal(z.cpu(), wz), (kind, dtype, rows, K)
+        if kind in ("int8", "w8a8"):
+            d = (q.cpu().int() - wq.int()).abs()
+        else:
+            d = (R.unpack_nibbles(q.cpu()).int() - R.unpack_nibbles(wq).int()).abs()
+        assert d.max().item() <= 1 and (d != 0).float().mean().item() < 1e-3, (kind, dtype, d.max().item())
+        if kind == "w8a8":
+            assert torch.equal(ws.cpu(), q.cpu().float().sum(1))
+        else:
+            assert ws is None

@@ -94,6 +94,31 @@ def _qgemm(x, W, n_out, gated, bias, act, residual, res_scale, out_dtype):
     return out
 
 
+_QMODE = {"int8": 0, "w8a8": 0, "int4": 1, "nf4": 2}
+_SRC_DT = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+
+def quantize_rows(w, kind):
+    """Quantise-at-load on the device: dense w [out, in] (fp32 / fp16 / bf16, on the GPU) -> (codes, scale[out],
+    zero[out], wsum[out] or None) in the layouts of `ops.reference.quantize_{int8,uint4,nf4}_per_channel`: int8 codes
+    [out, in], or two 4-bit codes per byte [out, in / 2].  `wsum` (sum of the codes per row) only for kind "w8a8"."""
+    if w.dim() != 2 or w.stride(1) != 1 or w.dtype not in _SRC_DT:
+        w = w.contiguous() if w.dtype in _SRC_DT else w.float().contiguous()
+    rows, K = w.shape
+    mode = _QMODE[kind]
+    if mode and K % 2:
+        raise ValueError("4-bit weights need an even input dimension")
+    q = torch.empty(rows, K if mode == 0 else K // 2, dtype=torch.int8 if mode == 0 else torch.uint8, device=w.device)
+    sz = torch.empty(3, rows, dtype=torch.float32, device=w.device)
+    wsum = sz[2] if kind == "w8a8" else None
+    fn = _lib().xft_quantize_rows
+    fn.restype = C.c_int
+    N._check(fn(N._p(w), _SRC_DT[w.dtype], C.c_longlong(w.stride(0)), rows, K, mode, N._p(q), C.c_longlong(q.stride(0)),
+                N._p(sz[0]), N._p(sz[1]), N._p(wsum), N._stream()), "quantize_rows")
+    N.Workspace.get(w.device).launches += 1
+    return q, sz[0], sz[1], wsum
+
+
 def quant_act(x2, ldx):
     """bf16 [T,K] -> (int8 [T,K], scale[T], zero[T], qsum[T]) per-row dynamic asymmetric."""
     T, K = x2.shape

@@ -116,21 +116,36 @@ def make_linear(w_out_in: torch.Tensor, kind: str, device=None, act_dtype: torch
             raise ValueError("fp8 weights need kind='fp8'")
         w = w_out_in.to(dt).contiguous()
         return LinearWeight(kind, w, in_features=w.shape[1], out_features=o)
+    # dense weights that are already on the GPU are quantised there by one kernel per matrix (same arithmetic as the
+    # PyTorch formulation in ops.reference, which serves CPU tensors)
+    on_gpu = w_out_in.is_cuda and w_out_in.dtype in (torch.float32, torch.float16, torch.bfloat16)
     if kind in ("int8", "w8a8"):
+        ws = None
         if w_out_in.dtype == torch.int8 and scale is not None:
             q, s, z = w_out_in.contiguous(), scale.float(), zero.float()
+        elif on_gpu:
+            from ..ops import native_quant
+            q, s, z, ws = native_quant.quantize_rows(w_out_in, kind)
         else:
             q, s, z = R.quantize_int8_per_channel(w_out_in)
-        ws = q.float().sum(1) if kind == "w8a8" else None
+        if kind == "w8a8" and ws is None:
+            ws = q.float().sum(1)
         return LinearWeight(kind, q, s, z, ws, in_features=q.shape[1], out_features=o)
     if kind == "int4":
         if w_out_in.dtype == torch.uint8 and scale is not None:
             p, s, z = w_out_in.contiguous(), scale.float(), zero.float()
+        elif on_gpu and w_out_in.shape[1] % 2 == 0:
+            from ..ops import native_quant
+            p, s, z, _ = native_quant.quantize_rows(w_out_in, kind)
         else:
             p, s, z = R.quantize_uint4_per_channel(w_out_in)
         return LinearWeight(kind, p, s, z, in_features=p.shape[1] * 2, out_features=o)
     if kind == "nf4":
-        p, s, z = R.quantize_nf4_per_channel(w_out_in)
+        if on_gpu and w_out_in.shape[1] % 2 == 0:
+            from ..ops import native_quant
+            p, s, z, _ = native_quant.quantize_rows(w_out_in, kind)
+        else:
+            p, s, z = R.quantize_nf4_per_channel(w_out_in)
         return LinearWeight(kind, p, s, z, in_features=p.shape[1] * 2, out_features=o)
     if kind == "fp8":
         if w_out_in.dtype == torch.float8_e4m3fn:
