@@ -142,7 +142,10 @@ _CPP_FAMILIES = {
     "telechat": {},
     "chatglm": dict(activation_type="gelu"),
     "mixtral": dict(sparse_experts=8, num_experts_per_tok=2),
-    "qwen3_moe": dict(sparse_experts=8, num_experts_per_tok=4, moe_intermediate_size=256, do_qk_norm=True, kv_head_num=2),
+    # every expert selected: the comparison with the fp32 oracle is then free of the discrete jumps a flipped near-tie
+    # between the 4th and 5th expert would cause (the top-k selection itself is checked against its oracle in
+    # tests/test_moe_gpu.py, and with Mixtral above)
+    "qwen3_moe": dict(sparse_experts=4, num_experts_per_tok=4, moe_intermediate_size=256, do_qk_norm=True, kv_head_num=2),
 }
 
 
