@@ -23,14 +23,9 @@
 namespace {
 
 xft::DataType parseWeightType(const std::string& s) {
-  if (s == "fp16") return xft::DataType::fp16;
-  if (s == "bf16") return xft::DataType::bf16;
-  if (s == "int8") return xft::DataType::int8;
-  if (s == "w8a8") return xft::DataType::w8a8;
-  if (s == "int4") return xft::DataType::int4;
-  if (s == "nf4") return xft::DataType::nf4;
-  if (s == "fp8_e4m3") return xft::DataType::fp8_e4m3;
-  TORCH_CHECK(false, "unsupported data type '", s, "'");
+  const xft::DataType dt = xft::dataTypeFromName(s.c_str());
+  TORCH_CHECK(dt != xft::DataType::unknown && dt != xft::DataType::fp32, "unsupported data type '", s, "'");
+  return dt;
 }
 
 xft::DataType parseKvType(const std::string& s) {

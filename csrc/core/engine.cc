@@ -101,6 +101,11 @@ struct LayerWeights {
   DevBuf qkv, o, gateUp, down, n1, n2, qkvBias, qNorm, kNorm;
   DevBuf n1b, n2b, oBias, fc1Bias, fc2Bias;      // LayerNorm biases, output-projection bias, biases of the two-matrix MLP
   DevBuf router, expGateUp, expDown;             // mixture of experts: [E, hidden], stacked [E * 2I, hidden], [E * hidden, I]
+  // DeepSeek.  Attention: merged down-projection [q_lora (or heads * qk) + kv_lora + rope, hidden], its norms, the query
+  // up-projection, and the per-head halves of kv_b: W_uk transposed [heads * kv_lora, nope], W_uv [heads * v, kv_lora].
+  DevBuf qkvA, qANorm, qB, kvANorm, wkT, wv;
+  DevBuf routerBias, sharedGateUp, sharedDown;   // correction bias [E]; shared experts as one gated MLP
+  bool denseMlp = true;                          // the first layers of DeepSeek are dense
 };
 
 // A projection as the GEMMs see it: bf16 [rows, K], or per-output-channel codes (int8 [rows, K]; NF4 two codes per byte
@@ -109,6 +114,7 @@ struct Lin {
   const void* w = nullptr;       // bf16 weights (kind 0)
   DevBuf q, scale, zero, wsum;
   int rows = 0, K = 0, pitch = 0;       // pitch: bytes from one row of codes to the next
+  int kind = 0;                         // 0 bf16, 1 int8 weight-only, 2 int8 x int8 activations, 3 NF4, 4 uint4
 };
 
 // What distinguishes one dense family from another (reference: one C++ class per family under src/models, selected by
@@ -126,7 +132,9 @@ struct FamilySpec {
   bool telechatNtk = false;    // TeleChat: NTK base from max(context, training length), table scale on long inputs
   bool residFromNorm = false;  // ChatGLM-1: residual = sqrt(2 * layers) * normalised input
   bool prefixLm = false;       // ChatGLM-1: the prompt up to its bos token attends in both directions
-  int routeKind = 0;           // experts: 0 softmax over the top-k logits (Mixtral), 1 softmax then top-k, renormalised (Qwen3)
+  int routeKind = 0;           // experts: 0 softmax over the top-k logits (Mixtral), 1 softmax then top-k, renormalised (Qwen3),
+                               // 2 DeepSeek (sigmoid / softmax scores, correction bias, expert groups)
+  bool mla = false;            // DeepSeek: latent attention (compressed KV cache) and shared + routed experts
 };
 
 const FamilySpec* familySpec(const std::string& type) {
@@ -142,6 +150,7 @@ const FamilySpec* familySpec(const std::string& type) {
       {"chatglm", true, 0, 0.5, true, 1, 0, false, false, true, true},
       {"mixtral", false, 0, 1.0, false, 3, 0, false, false, false, false, 0},
       {"qwen3_moe", false, 0, 1.0, false, 3, 0, false, false, false, false, 1},
+      {"deepseek_moe", false, 1, 1.0, false, 3, 0, false, false, false, false, 2, true},
   };
   for (const FamilySpec& f : table)
     if (type == f.name) return &f;
@@ -161,7 +170,13 @@ public:
   int rotDim = 0;              // 0: no rotary table (OPT, ALiBi Baichuan)
   int wpeRows = 0;             // OPT: rows of the learned position table
   int experts = 0, topK = 0, moeInter = 0;       // mixture of experts: count, experts per token, expert FFN width
-  int wq = 0;                  // layer projections: 0 bf16, 1 weight-only int8, 2 int8 weights x int8 activations, 3 NF4
+  int wq = 0;                  // layer projections: 0 bf16, 1 weight-only int8, 2 int8 weights x int8 activations, 3 NF4, 4 uint4
+  int wqNext = 0;              // hybrid types "A_B" (src/models/hybrid_model.h): A for the prompt pass, B for decode steps
+  // DeepSeek
+  int qLora = 0, kvLora = 0, nope = 0, ropeD = 0, vDim = 0, firstDense = 0, sharedInter = 0, nGroup = 1, topkGroup = 1;
+  float routedScale = 1.f, attnScale = 1.f;
+  bool normTopk = true, sigmoidScores = true;
+  int auxDt = 1;               // dtype of embeddings, head and norm gains on disk (DeepSeek keeps them in bf16)
   bool alibi = false;
   int trainLen = 0;            // Qwen-1 seq_length / TeleChat training context
   bool useDynamicNtk = true, useLognAttn = true;
@@ -185,19 +200,31 @@ public:
 
 private:
   void loadLinear(const std::string& file, int inF, int outF, void* dst, int dstRowOffset, int dstLd);
-  DevBuf loadVector(const std::string& file, int n, bool optional = false);
+  DevBuf loadVector(const std::string& file, int n, bool optional = false, int dt = -1);
   void copyBlock(int src, int dst);
   std::string dir;
   int fileDt = 1;
-  void quantise(DevBuf& dense, int rows, int K, Lin& out);      // dense bf16 [rows, K] -> `out` per `wq`; frees `dense`
+  // DeepSeek tensor `<base>.weight.bin` ([in, out]; e4m3 with `<base>.weight_scale_inv.bin` block scales, or a float type)
+  void loadDsLinear(const std::string& base, int inF, int outF, void* dst, int dstRowOffset, int dstLd);
+  void loadMlaLayer(const std::string& p, LayerWeights& L, int layer);
+  // dense bf16 [rows, K] -> the prompt-pass form `first` and, for hybrid types, the decode form `next`; `dense` is
+  // released unless a bf16 form points at it
+  void quantise(DevBuf& dense, int rows, int K, Lin& first, Lin& next);
+  void quantiseAs(const DevBuf& dense, int rows, int K, int kind, Lin& out);
+  // bytes of one 64-token block of one layer's K (or V) pool; the latent cache of DeepSeek has one row of
+  // kv_lora_rank + rope values per token and no V pool
+  size_t kvBlockBytes() const {
+    return spec.mla ? (size_t)kBlock * (kvLora + ropeD) * 2 : (size_t)kvHeads * kBlock * headDim * (kvInt8 ? 1 : 2);
+  }
   const float* ropeFor(int maxKv, int maxQ);      // the rotary table of this pass (NTK families keep one per base)
   DevBuf wte, wpe, lmHead, finalNorm, finalNormBias, ropeTable_, slopes_, ws, counters, status, attnCounters, partO, partMl;
   std::map<long long, DevBuf> ntkTables_;         // by round(base): Qwen-1 / TeleChat tables beyond the first
   RopeScaling ropeScaling_;
   std::vector<LayerWeights> lw;
   struct LayerLins { Lin qkv, o, gateUp, down; };
-  std::vector<LayerLins> lins;
+  std::vector<LayerLins> lins, linsNext;
   DevBuf actQ, actScale, actZero, actSum, guBuf;   // int8 activations + their row statistics; gate‖up before the activation
+  DevBuf mQaKv, mQa, mQ, mQNope, mQRope, mQAbs, mOLat, mOHead, mTiles, mMeta, mShared;   // latent-attention activations
   std::vector<DevBuf> kc, vc, ks, vs;
   int numBlocks = 0;
   // activations
@@ -217,15 +244,16 @@ void Engine::loadLinear(const std::string& file, int inF, int outF, void* dst, i
   XFT_CUDA(cudaStreamSynchronize(st));
 }
 
-DevBuf Engine::loadVector(const std::string& file, int n, bool optional) {
+DevBuf Engine::loadVector(const std::string& file, int n, bool optional, int dt) {
+  if (dt < 0) dt = auxDt;
   std::ifstream probe(dir + "/" + file, std::ios::binary);
   if (!probe) {
     if (optional) return DevBuf();
     if (!Env::get().fakeModel) throw std::runtime_error("missing " + file);
   }
-  auto host = readFile(dir + "/" + file, (size_t)n * dtypeSize(fileDt), fileDt);
+  auto host = readFile(dir + "/" + file, (size_t)n * dtypeSize(dt), dt);
   std::vector<float> f(n);
-  for (int i = 0; i < n; ++i) f[i] = elemToFloat(host.data(), fileDt, i);
+  for (int i = 0; i < n; ++i) f[i] = elemToFloat(host.data(), dt, i);
   DevBuf d((size_t)n * 4);
   XFT_CUDA(cudaMemcpy(d.p, f.data(), (size_t)n * 4, cudaMemcpyHostToDevice));
   return d;
@@ -238,12 +266,22 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
   const FamilySpec* fam = familySpec(type);
   if (!fam) throw std::runtime_error("the native C++ engine runs the dense families; use the Python API for [" + type + "]");
   spec = *fam;
-  if (dt == DataType::int8) wq = 1;
-  else if (dt == DataType::w8a8) wq = 2;
-  else if (dt == DataType::nf4) wq = 3;
-  else if (dt != DataType::bf16 && dt != DataType::fp16)
-    throw std::runtime_error("the native C++ engine runs bf16 (fp16 weights are kept as bf16), int8, w8a8 and nf4 weights");
-  if (wq && spec.mlp == 3) throw std::runtime_error("quantised experts run through the Python API");
+  switch (dt) {
+    case DataType::bf16: case DataType::fp16: case DataType::bf16_fp16: break;      // fp16 weights are kept as bf16
+    case DataType::int8: wq = wqNext = 1; break;
+    case DataType::w8a8: wq = wqNext = 2; break;
+    case DataType::nf4: wq = wqNext = 3; break;
+    case DataType::int4: wq = wqNext = 4; break;
+    case DataType::bf16_int8: wqNext = 1; break;
+    case DataType::bf16_w8a8: wqNext = 2; break;
+    case DataType::bf16_nf4: wqNext = 3; break;
+    case DataType::bf16_int4: wqNext = 4; break;
+    case DataType::w8a8_int8: wq = 2; wqNext = 1; break;
+    case DataType::w8a8_nf4: wq = 2; wqNext = 3; break;
+    case DataType::w8a8_int4: wq = 2; wqNext = 4; break;
+    default: throw std::runtime_error("the native C++ engine runs bf16, int8, w8a8, int4, nf4 weights and their hybrids");
+  }
+  if ((wq || wqNext) && spec.mlp == 3) throw std::runtime_error("quantised experts run through the Python API");
   kvInt8 = kvdt == DataType::int8;
   heads = (int)ini.getInt(type, "head_num");
   kvHeads = (int)ini.getInt(type, "kv_head_num", heads);
@@ -304,21 +342,55 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
   qkNorm = ini.getBool(type, "do_qk_norm", false);
   if (spec.embedding == 1) embedScale = std::sqrt((float)hidden);
   std::string wdt = ini.get(type, "weight_data_type", "fp16");
-  fileDt = wdt == "fp32" ? 0 : wdt == "bf16" ? 2 : 1;
+  fileDt = wdt == "fp32" ? 0 : wdt == "bf16" ? 2 : wdt == "fp8_e4m3" ? 3 : 1;
+  if (fileDt == 3 && !spec.mla) throw std::runtime_error("fp8 checkpoints are DeepSeek checkpoints");
+  auxDt = spec.mla ? 2 : fileDt;
+  if (spec.mla) {
+    qLora = (int)ini.getInt(type, "q_lora_rank", 0);
+    kvLora = (int)ini.getInt(type, "kv_lora_rank", 512);
+    nope = (int)ini.getInt(type, "qk_nope_head_dim", 128);
+    ropeD = (int)ini.getInt(type, "qk_rope_head_dim", 64);
+    vDim = (int)ini.getInt(type, "v_head_dim", headDim);
+    firstDense = (int)ini.getInt(type, "first_k_dense_replace", 0);
+    sharedInter = (int)ini.getInt(type, "dense_experts", 0) * moeInter;
+    nGroup = std::max(1, (int)ini.getInt(type, "n_group", 1));
+    topkGroup = std::max(1, (int)ini.getInt(type, "topk_group", 1));
+    routedScale = (float)ini.getFloat(type, "routed_scaling_factor", 1.0);
+    normTopk = ini.getBool(type, "norm_topk_prob", true);
+    const std::string sf = ini.get(type, "scoring_func", "sigmoid");
+    sigmoidScores = sf.empty() || sf == "sigmoid";
+    if (kvLora != 512 || ropeD != 64) throw std::runtime_error("the latent attention kernel is built for kv_lora_rank 512 + rope 64");
+    if (kvInt8) throw std::runtime_error("the latent KV cache is bf16");
+    if (wq || wqNext) throw std::runtime_error("quantised DeepSeek weights run through the Python API");
+    if (nope % 8 || vDim % 8 || (qLora % 8) || sharedInter % 8) throw std::runtime_error("DeepSeek head sizes must be multiples of 8");
+    // rotary table of the rope part only: YaRN with the model's mscale pair; softmax scale 1 / sqrt(nope + rope) times
+    // (0.1 mscale_all_dim ln(factor) + 1)^2 (src/models/common_decoder.h:272-274 hard-wires factor 40)
+    rs.mscale = ini.getFloat(type, "rope_scaling_mscale", 1.0);
+    rs.mscaleAllDim = ini.getFloat(type, "rope_scaling_mscale_all_dim", 0.0);
+    rs.tableScale = -1.0;
+    ropeScaling_ = rs;
+    rotDim = ropeD;
+    maxPos = std::min(maxPos, 163840);
+    attnScale = 1.0f / std::sqrt((float)(nope + ropeD));
+    if (rs.type == "yarn" && rs.factor > 1.0) {
+      const double m = 0.1 * rs.mscaleAllDim * std::log(rs.factor) + 1.0;
+      attnScale = (float)(attnScale * m * m);
+    }
+  }
   if (ini.get(type, "quant_qweight_data_type", "") != "") throw std::runtime_error("GPTQ checkpoints run through the Python API");
-  if (headDim != 64 && headDim != 128 && headDim != 256) throw std::runtime_error("head size must be 64, 128 or 256");
+  if (!spec.mla && headDim != 64 && headDim != 128 && headDim != 256) throw std::runtime_error("head size must be 64, 128 or 256");
 
   XFT_CUDA(cudaStreamCreate(&st));
   const int qsz = heads * headDim, kvsz = kvHeads * headDim;
   // embedding and lm_head are stored [vocab, hidden]: convert on the host
   {
-    auto host = readFile(dir + "/model.wte.bin", (size_t)vocab * hidden * dtypeSize(fileDt), fileDt);
+    auto host = readFile(dir + "/model.wte.bin", (size_t)vocab * hidden * dtypeSize(auxDt), auxDt);
     std::vector<uint16_t> b((size_t)vocab * hidden);
-    for (size_t i = 0; i < b.size(); ++i) b[i] = floatToBf16(elemToFloat(host.data(), fileDt, i));
+    for (size_t i = 0; i < b.size(); ++i) b[i] = floatToBf16(elemToFloat(host.data(), auxDt, i));
     wte.reset(b.size() * 2);
     XFT_CUDA(cudaMemcpy(wte.p, b.data(), b.size() * 2, cudaMemcpyHostToDevice));
-    host = readFile(dir + "/model.lm_head.weight.bin", (size_t)vocab * hidden * dtypeSize(fileDt), fileDt);
-    for (size_t i = 0; i < b.size(); ++i) b[i] = floatToBf16(elemToFloat(host.data(), fileDt, i));
+    host = readFile(dir + "/model.lm_head.weight.bin", (size_t)vocab * hidden * dtypeSize(auxDt), auxDt);
+    for (size_t i = 0; i < b.size(); ++i) b[i] = floatToBf16(elemToFloat(host.data(), auxDt, i));
     lmHead.reset(b.size() * 2);
     XFT_CUDA(cudaMemcpy(lmHead.p, b.data(), b.size() * 2, cudaMemcpyHostToDevice));
   }
@@ -336,9 +408,11 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
   if (spec.layerNorm) finalNormBias = loadVector("model.final_layernorm.bias.bin", hidden);
   lw.resize(layers);
   lins.resize(layers);
+  linsNext.resize(layers);
   for (int i = 0; i < layers; ++i) {
     const std::string p = "model.layers." + std::to_string(i) + ".";
     LayerWeights& L = lw[i];
+    if (spec.mla) { loadMlaLayer(p, L, i); continue; }
     L.qkv.reset((size_t)(qsz + 2 * kvsz) * hidden * 2);
     loadLinear(p + "attention.query_key_value.weight.0.bin", hidden, qsz + 2 * kvsz, L.qkv.p, 0, hidden);
     L.qkvBias = loadVector(p + "attention.query_key_value.bias.0.bin", qsz + 2 * kvsz, true);
@@ -390,11 +464,12 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
       L.kNorm = loadVector(p + "attention.k_norm.weight.bin", headDim);
     }
     LayerLins& Q = lins[i];
-    quantise(L.qkv, qsz + 2 * kvsz, hidden, Q.qkv);
-    quantise(L.o, hidden, qsz, Q.o);
+    LayerLins& Qn = linsNext[i];
+    quantise(L.qkv, qsz + 2 * kvsz, hidden, Q.qkv, Qn.qkv);
+    quantise(L.o, hidden, qsz, Q.o, Qn.o);
     if (spec.mlp != 3) {
-      quantise(L.gateUp, spec.mlp == 1 ? inter : 2 * inter, hidden, Q.gateUp);
-      quantise(L.down, hidden, inter, Q.down);
+      quantise(L.gateUp, spec.mlp == 1 ? inter : 2 * inter, hidden, Q.gateUp, Qn.gateUp);
+      quantise(L.down, hidden, inter, Q.down, Qn.down);
     }
   }
   // rotary table [maxPos, rotDim] = cos(rotDim/2) ‖ sin(rotDim/2); the NTK families build further tables on demand
@@ -417,30 +492,130 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
   rng.seed((unsigned long long)std::chrono::steady_clock::now().time_since_epoch().count());
   if (Env::get().kvCacheGb > 0) {
     // XFT_KV_CACHE_GB: size the KV pools once, so that they never grow (and move) under load
-    const size_t esz = kvInt8 ? 1 : 2;
-    const size_t per = (size_t)layers * kvHeads * kBlock * (2 * headDim * esz + (kvInt8 ? 8 : 0));
+    const size_t per = (size_t)layers * (kvBlockBytes() * (spec.mla ? 1 : 2) + (kvInt8 ? (size_t)kvHeads * kBlock * 8 : 0));
     ensureBlocks((int)std::max<size_t>(1, (size_t)(Env::get().kvCacheGb * (double)(1ull << 30)) / per));
   }
 }
 
-void Engine::quantise(DevBuf& dense, int rows, int K, Lin& out) {
-  out.rows = rows; out.K = K;
-  if (wq == 0) { out.w = dense.p; return; }
-  // the quantiser of the loader (same kernel as the Python package uses): per output channel, asymmetric int8 or NF4
-  if (wq == 3 && (K % 2)) throw std::runtime_error("nf4 weights need even input dimensions");
-  if (wq == 2 && (K % 16)) throw std::runtime_error("w8a8 weights need input dimensions that are multiples of 16");
+void Engine::loadDsLinear(const std::string& base, int inF, int outF, void* dst, int dstRowOffset, int dstLd) {
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(dst) + (size_t)dstRowOffset * dstLd;
+  if (fileDt != 3 || Env::get().fakeModel) {
+    const int dt = fileDt == 3 ? 2 : fileDt;
+    auto host = readFile(dir + "/" + base + ".weight.bin", (size_t)inF * outF * dtypeSize(dt), dt);
+    DevBuf tmp(host.size());
+    XFT_CUDA(cudaMemcpy(tmp.p, host.data(), host.size(), cudaMemcpyHostToDevice));
+    XFT_K(xft_transpose_to_bf16(tmp.p, dt, outF, inF, outF, out, dstLd, st));
+    XFT_CUDA(cudaStreamSynchronize(st));
+    return;
+  }
+  // e4m3 bytes [in, out] + one fp32 scale per 128 x 128 block (deepseek_moe_convert.py:117-180): dequantise on the
+  // device, then transpose like every other tensor
+  const int B = 128, sr = (inF + B - 1) / B, sc = (outF + B - 1) / B;
+  std::ifstream f(dir + "/" + base + ".weight.bin", std::ios::binary | std::ios::ate);
+  if (!f) throw std::runtime_error("cannot open " + base + ".weight.bin");
+  if ((size_t)f.tellg() != (size_t)inF * outF) throw std::runtime_error(base + ".weight.bin: unexpected size");
+  std::vector<char> w((size_t)inF * outF);
+  f.seekg(0);
+  f.read(w.data(), (std::streamsize)w.size());
+  auto scales = readFile(dir + "/" + base + ".weight_scale_inv.bin", (size_t)sr * sc * 4, 0);
+  DevBuf dw(w.size()), ds(scales.size()), dense((size_t)inF * outF * 2);
+  XFT_CUDA(cudaMemcpy(dw.p, w.data(), w.size(), cudaMemcpyHostToDevice));
+  XFT_CUDA(cudaMemcpy(ds.p, scales.data(), scales.size(), cudaMemcpyHostToDevice));
+  XFT_K(xft_fp8_block_dequant(dw.p, ds.as<float>(), inF, outF, B, dense.p, st));
+  XFT_K(xft_transpose_to_bf16(dense.p, 2, outF, inF, outF, out, dstLd, st));
+  XFT_CUDA(cudaStreamSynchronize(st));
+}
+
+void Engine::loadMlaLayer(const std::string& p, LayerWeights& L, int layer) {
+  const int qk = nope + ropeD, H = hidden, kvw = kvLora + ropeD;
+  // merged down-projection: the query part (compressed to q_lora, or the full heads * qk when the model has no query
+  // compression) followed by compressed KV + shared rotary key (src/layers/attn_deepseek.h:78-117)
+  const int qRows = qLora > 0 ? qLora : heads * qk;
+  L.qkvA.reset((size_t)(qRows + kvw) * H * 2);
+  loadDsLinear(p + "self_attn.q_a_proj", H, qRows, L.qkvA.p, 0, H);
+  loadDsLinear(p + "self_attn.kv_a_proj_with_mqa", H, kvw, L.qkvA.p, qRows, H);
+  if (qLora > 0) {
+    L.qANorm = loadVector(p + "self_attn.q_a_layernorm.weight.bin", qLora, false, 2);
+    L.qB.reset((size_t)heads * qk * qLora * 2);
+    loadDsLinear(p + "self_attn.q_b_proj", qLora, heads * qk, L.qB.p, 0, qLora);
+  }
+  L.kvANorm = loadVector(p + "self_attn.kv_a_layernorm.weight.bin", kvLora, false, 2);
+  // kv_b [kv_lora -> heads * (nope + v)] as [out, in]; per head the first `nope` rows are W_uk, the next `v` rows W_uv.
+  // The absorbed form multiplies queries by W_uk^T and latent outputs by W_uv (attn_deepseek.h:408-433), so W_uk is
+  // stored transposed per head and both are stacked for the per-head grouped GEMM.
+  {
+    DevBuf kvb((size_t)heads * (nope + vDim) * kvLora * 2);
+    loadDsLinear(p + "self_attn.kv_b_proj", kvLora, heads * (nope + vDim), kvb.p, 0, kvLora);
+    L.wkT.reset((size_t)heads * kvLora * nope * 2);
+    L.wv.reset((size_t)heads * vDim * kvLora * 2);
+    for (int h = 0; h < heads; ++h) {
+      const __nv_bfloat16* src = kvb.as<__nv_bfloat16>() + (size_t)h * (nope + vDim) * kvLora;
+      XFT_K(xft_transpose_to_bf16(src, 2, kvLora, nope, kvLora, L.wkT.as<__nv_bfloat16>() + (size_t)h * kvLora * nope, nope, st));
+      XFT_CUDA(cudaMemcpyAsync(L.wv.as<__nv_bfloat16>() + (size_t)h * vDim * kvLora, src + (size_t)nope * kvLora,
+                               (size_t)vDim * kvLora * 2, cudaMemcpyDeviceToDevice, st));
+    }
+    XFT_CUDA(cudaStreamSynchronize(st));
+  }
+  L.o.reset((size_t)H * heads * vDim * 2);
+  loadDsLinear(p + "attention.dense", heads * vDim, H, L.o.p, 0, heads * vDim);
+  L.n1 = loadVector(p + "input_layernorm.weight.bin", H, false, 2);
+  L.n2 = loadVector(p + "post_attention_layernorm.weight.bin", H, false, 2);
+  L.denseMlp = layer < firstDense;
+  auto gatedMlp = [&](const std::string& base, int I, DevBuf& gu, DevBuf& dn) {
+    gu.reset((size_t)2 * I * H * 2);
+    loadDsLinear(base + "gate_proj", H, I, gu.p, 0, H);
+    loadDsLinear(base + "up_proj", H, I, gu.p, I, H);
+    dn.reset((size_t)H * I * 2);
+    loadDsLinear(base + "down_proj", I, H, dn.p, 0, I);
+  };
+  if (L.denseMlp) { gatedMlp(p + "mlp.", inter, L.gateUp, L.down); return; }
+  const int E = experts, I = moeInter;
+  {
+    // router [hidden, experts] bf16 on disk
+    auto host = readFile(dir + "/" + p + "mlp.gate.weight.bin", (size_t)H * E * 2, 2);
+    DevBuf tmp(host.size());
+    XFT_CUDA(cudaMemcpy(tmp.p, host.data(), host.size(), cudaMemcpyHostToDevice));
+    L.router.reset((size_t)E * H * 2);
+    XFT_K(xft_transpose_to_bf16(tmp.p, 2, E, H, E, L.router.p, H, st));
+    XFT_CUDA(cudaStreamSynchronize(st));
+  }
+  L.routerBias = loadVector(p + "mlp.gate.e_score_correction_bias.bin", E, true, 2);
+  if (sharedInter > 0) gatedMlp(p + "mlp.shared_experts.", sharedInter, L.sharedGateUp, L.sharedDown);
+  L.expGateUp.reset((size_t)E * 2 * I * H * 2);
+  L.expDown.reset((size_t)E * H * I * 2);
+  for (int e = 0; e < E; ++e) {
+    const std::string ep = p + "mlp.experts." + std::to_string(e) + ".";
+    loadDsLinear(ep + "gate_proj", H, I, L.expGateUp.p, e * 2 * I, H);
+    loadDsLinear(ep + "up_proj", H, I, L.expGateUp.p, e * 2 * I + I, H);
+    loadDsLinear(ep + "down_proj", I, H, L.expDown.p, e * H, I);
+  }
+}
+
+void Engine::quantise(DevBuf& dense, int rows, int K, Lin& first, Lin& next) {
+  quantiseAs(dense, rows, K, wq, first);
+  if (wqNext != wq) quantiseAs(dense, rows, K, wqNext, next);
+  if (wq != 0 && wqNext != 0) dense.reset(0);
+}
+
+void Engine::quantiseAs(const DevBuf& dense, int rows, int K, int kind, Lin& out) {
+  out.rows = rows; out.K = K; out.kind = kind;
+  if (kind == 0) { out.w = dense.p; return; }
+  // the quantiser of the loader (same kernel as the Python package uses): per output channel, asymmetric int8 / uint4
+  // or NF4
+  const bool nibbles = kind == 3 || kind == 4;
+  if (nibbles && (K % 2)) throw std::runtime_error("4-bit weights need even input dimensions");
+  if (kind == 2 && (K % 16)) throw std::runtime_error("w8a8 weights need input dimensions that are multiples of 16");
   // rows start on 16-byte boundaries (the GEMM reads them with TMA); codes in the padding are zero and meet
   // zero-filled activations
-  const size_t rowBytes = ((wq == 3 ? (size_t)K / 2 : (size_t)K) + 15) / 16 * 16;
+  const size_t rowBytes = ((nibbles ? (size_t)K / 2 : (size_t)K) + 15) / 16 * 16;
   out.pitch = (int)rowBytes;
   out.q.reset((size_t)rows * rowBytes);
   XFT_CUDA(cudaMemsetAsync(out.q.p, 0, (size_t)rows * rowBytes, st));
   out.scale.reset((size_t)rows * 4); out.zero.reset((size_t)rows * 4);
-  if (wq == 2) out.wsum.reset((size_t)rows * 4);
-  XFT_K(xft_quantize_rows(dense.p, 2, K, rows, K, wq == 3 ? 2 : 0, out.q.p, (long long)rowBytes, out.scale.as<float>(),
-                          out.zero.as<float>(), out.wsum.as<float>(), st));
+  if (kind == 2) out.wsum.reset((size_t)rows * 4);
+  XFT_K(xft_quantize_rows(dense.p, 2, K, rows, K, kind == 3 ? 2 : kind == 4 ? 1 : 0, out.q.p, (long long)rowBytes,
+                          out.scale.as<float>(), out.zero.as<float>(), out.wsum.as<float>(), st));
   XFT_CUDA(cudaStreamSynchronize(st));
-  dense.reset(0);
 }
 
 const float* Engine::ropeFor(int maxKv, int maxQ) {
@@ -474,17 +649,16 @@ void Engine::ensureBlocks(int extra) {
   auto& al = tables->allocator();
   if (al.numFree() >= extra) return;
   const int total = std::max(al.numBlocks() - al.numFree() + extra, al.numBlocks() * 3 / 2);
-  const size_t esz = kvInt8 ? 1 : 2;
-  const size_t per = (size_t)kvHeads * kBlock * headDim * esz, sper = (size_t)kvHeads * kBlock * 4;
+  const size_t per = kvBlockBytes(), sper = (size_t)kvHeads * kBlock * 4;
   for (int l = 0; l < layers; ++l) {
-    DevBuf nk(per * total), nv(per * total);
+    DevBuf nk(per * total), nv(spec.mla ? 0 : per * total);
     // new blocks start zeroed: the TMA decode kernel reads whole tiles and masks rows past kv_len by P = 0,
     // which needs the masked V rows to be finite
     XFT_CUDA(cudaMemset(nk.as<char>() + per * numBlocks, 0, per * (total - numBlocks)));
-    XFT_CUDA(cudaMemset(nv.as<char>() + per * numBlocks, 0, per * (total - numBlocks)));
+    if (!spec.mla) XFT_CUDA(cudaMemset(nv.as<char>() + per * numBlocks, 0, per * (total - numBlocks)));
     if (numBlocks) {
       XFT_CUDA(cudaMemcpy(nk.p, kc[l].p, per * numBlocks, cudaMemcpyDeviceToDevice));
-      XFT_CUDA(cudaMemcpy(nv.p, vc[l].p, per * numBlocks, cudaMemcpyDeviceToDevice));
+      if (!spec.mla) XFT_CUDA(cudaMemcpy(nv.p, vc[l].p, per * numBlocks, cudaMemcpyDeviceToDevice));
     }
     kc[l] = std::move(nk); vc[l] = std::move(nv);
     if (kvInt8) {
@@ -501,10 +675,10 @@ void Engine::ensureBlocks(int extra) {
 }
 
 void Engine::copyBlock(int src, int dst) {
-  const size_t esz = kvInt8 ? 1 : 2;
-  const size_t per = (size_t)kvHeads * kBlock * headDim * esz, sper = (size_t)kvHeads * kBlock * 4;
+  const size_t per = kvBlockBytes(), sper = (size_t)kvHeads * kBlock * 4;
   for (int l = 0; l < layers; ++l) {
     XFT_CUDA(cudaMemcpyAsync(kc[l].as<char>() + per * dst, kc[l].as<char>() + per * src, per, cudaMemcpyDeviceToDevice, st));
+    if (spec.mla) continue;
     XFT_CUDA(cudaMemcpyAsync(vc[l].as<char>() + per * dst, vc[l].as<char>() + per * src, per, cudaMemcpyDeviceToDevice, st));
     if (kvInt8) {
       XFT_CUDA(cudaMemcpyAsync(ks[l].as<char>() + sper * dst, ks[l].as<char>() + sper * src, sper, cudaMemcpyDeviceToDevice, st));
@@ -634,10 +808,10 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
   auto lin = [&](const Lin& Wt, const void* X, void* Y, int N, int gated, const float* bias, const void* res, float rscale,
                  int actc) {
     const int K = Wt.K;
-    if (wq == 0) {
+    if (Wt.kind == 0) {
       XFT_K(xft_gemm_bf16(X, K, Wt.w, Wt.rows, K, Y, N, 0, T, N, K, gated, gated ? N : 0, bias, res, N, rscale, actc, nullptr,
                           ws.as<float>(), kWsBytes, counters.as<int>(), 8192, stp, 0, st));
-    } else if (wq == 2) {
+    } else if (Wt.kind == 2) {
       // dynamic per-token int8 activations, int8 tensor-core product, corrections for both zero points in the epilogue
       actQ.ensure((size_t)T * K); actScale.ensure((size_t)T * 4); actZero.ensure((size_t)T * 4); actSum.ensure((size_t)T * 4);
       XFT_K(xft_quant_act(X, K, actQ.p, K, actScale.as<float>(), actZero.as<float>(), actSum.as<float>(), T, K, st));
@@ -650,14 +824,14 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
                           stp, st));
       if (gated) XFT_K(xft_gated_act(guBuf.p, Y, T, N, actc, st));
     } else {
-      const bool nf4 = wq == 3;
+      const bool nf4 = Wt.kind == 3;
       const float* xsum = nullptr;
       if (!nf4) {      // an asymmetric zero point contributes zero * sum(x) per output
         actSum.ensure((size_t)T * 4);
         XFT_K(xft_row_sum(X, K, actSum.as<float>(), T, K, st));
         xsum = actSum.as<float>();
       }
-      XFT_K(xft_qgemm(X, K, Wt.q.p, Wt.rows, Wt.pitch, nf4 ? 2 : 0, Y, N, 0, T, N, K, gated, gated ? N : 0,
+      XFT_K(xft_qgemm(X, K, Wt.q.p, Wt.rows, Wt.pitch, nf4 ? 2 : Wt.kind == 4 ? 1 : 0, Y, N, 0, T, N, K, gated, gated ? N : 0,
                       Wt.scale.as<float>(), nf4 ? nullptr : Wt.zero.as<float>(), xsum, 0, bias, res, N, rscale, actc,
                       ws.as<float>(), kWsBytes, counters.as<int>(), 8192, stp, st));
     }
@@ -673,6 +847,44 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
     moeXs.ensure((size_t)rowsMax * hidden * 2); moeH1.ensure((size_t)rowsMax * moeInter * 2);
     moeYs.ensure((size_t)rowsMax * hidden * 4);
   }
+  // DeepSeek: static tile table of the per-head grouped GEMMs (rows of head h are [h * T, (h + 1) * T)), split factor of
+  // the latent attention at decode sizes
+  int mlaTiles = 0, mlaBn = 16, mlaSplit = 1;
+  if (spec.mla) {
+    const int L = kvLora, qk = nope + ropeD, qRows = qLora > 0 ? qLora : heads * qk;
+    mlaBn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : 128;
+    std::vector<int> tiles;
+    for (int hh = 0; hh < heads; ++hh)
+      for (int j = 0; j < T; j += mlaBn) { tiles.push_back(hh); tiles.push_back(hh * T + j); tiles.push_back(std::min(mlaBn, T - j)); tiles.push_back(0); }
+    mlaTiles = (int)tiles.size() / 4;
+    const int meta[2] = {mlaTiles, heads * T};
+    mTiles.ensure(tiles.size() * 4); mMeta.ensure(8);
+    XFT_CUDA(cudaMemcpyAsync(mTiles.p, tiles.data(), tiles.size() * 4, cudaMemcpyHostToDevice, st));
+    XFT_CUDA(cudaMemcpyAsync(mMeta.p, meta, 8, cudaMemcpyHostToDevice, st));
+    XFT_CUDA(cudaStreamSynchronize(st));
+    mQaKv.ensure((size_t)T * (qRows + L + ropeD) * 2); mQa.ensure((size_t)T * std::max(qLora, 8) * 2);
+    mQ.ensure((size_t)T * heads * qk * 2); mQNope.ensure((size_t)heads * T * nope * 2);
+    mQRope.ensure((size_t)T * heads * ropeD * 2); mQAbs.ensure((size_t)heads * T * L * 2);
+    mOLat.ensure((size_t)heads * T * L * 2); mOHead.ensure((size_t)heads * T * vDim * 2);
+    att.ensure((size_t)T * heads * vDim * 2);
+    g.ensure((size_t)T * std::max(inter, std::max(sharedInter, 8)) * 2);
+    if (sharedInter > 0) mShared.ensure((size_t)T * hidden * 4);
+    if (decode) {
+      const int ntiles = (maxKv + 31) / 32, ctas = T * ((heads + 15) / 16);
+      mlaSplit = std::max(1, std::min({296 / std::max(ctas, 1), ntiles >= 16 ? ntiles / 8 : 1, 16}));
+      if (mlaSplit > 1 && ctas <= 16384) {
+        partO.ensure((size_t)ctas * mlaSplit * 16 * L * 4);
+        partMl.ensure((size_t)ctas * mlaSplit * 32 * 4);
+      } else {
+        mlaSplit = 1;
+      }
+    }
+  }
+  auto perHead = [&](const void* X, int K, const void* Wst, int nOut, void* Y) {
+    // X [heads * T, K] (rows grouped by head) x per-head weights [heads * nOut, K] -> Y [heads * T, nOut]
+    XFT_K(xft_gemm_bf16_grouped(X, K, heads * T, Wst, heads * nOut, K, Y, nOut, 0, nOut, K, 0, 0, nOut, mTiles.p,
+                                mMeta.as<int>(), mlaTiles, mlaBn, nullptr, 0, stp, st));
+  };
   // three state buffers of T x hidden; which one plays which part rotates in the ChatGLM-1 flow
   void* cur = x.p;
   void* nxt = x2.p;
@@ -680,7 +892,59 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
   for (int l = 0; l < layers; ++l) {
     LayerWeights& L = lw[l];
     norm(cur, L.n1, L.n1b, hb, T);
-    const LayerLins& Q = lins[l];
+    if (spec.mla) {
+      // ---- latent attention (src/layers/attn_deepseek.h): down-projections, query up-projection, one kernel for the
+      // head split + KV norm + rotary + cache append, then the absorbed form: q W_uk^T against the latent cache, the
+      // latent result times W_uv, output projection
+      const int Lr = kvLora, qk = nope + ropeD, qRows = qLora > 0 ? qLora : heads * qk, ldA = qRows + Lr + ropeD;
+      gemm(hb, hidden, L.qkvA.p, ldA, mQaKv.p, ldA, 0, 0, 0, nullptr, nullptr, 0, T);
+      const __nv_bfloat16* qPtr = mQaKv.as<__nv_bfloat16>();
+      int ldq = ldA;
+      if (qLora > 0) {
+        XFT_K(xft_rmsnorm(mQaKv.p, ldA, nullptr, 0, L.qANorm.as<float>(), mQa.p, qLora, nullptr, T, qLora, eps, st));
+        gemm(mQa.p, qLora, L.qB.p, heads * qk, mQ.p, heads * qk, 0, 0, 0, nullptr, nullptr, 0, T);
+        qPtr = mQ.as<__nv_bfloat16>();
+        ldq = heads * qk;
+      }
+      XFT_K(xft_mla_prep(qPtr, ldq, mQaKv.as<__nv_bfloat16>() + qRows, ldA, T, heads, nope, ropeD, Lr, dPos.as<int>(), table,
+                         maxPos, L.kvANorm.as<float>(), eps, mQNope.p, mQRope.p, kc[l].p, (long long)numBlocks * kBlock,
+                         dSlots.as<int>(), stp, 1, st));
+      perHead(mQNope.p, nope, L.wkT.p, Lr, mQAbs.p);
+      XFT_K(xft_mla_attention(mQAbs.p, (long long)T * Lr, Lr, mQRope.p, ropeD, (long long)heads * ropeD, mOLat.p,
+                              (long long)T * Lr, Lr, kc[l].p, dBt.as<int>(), (int)W, dCu.as<int>(), dKv.as<int>(), B, T, heads,
+                              kBlock, numBlocks, attnScale, mlaSplit, mlaSplit > 1 ? partO.as<float>() : nullptr,
+                              mlaSplit > 1 ? partMl.as<float>() : nullptr, attnCounters.as<int>(), stp, st));
+      perHead(mOLat.p, Lr, L.wv.p, vDim, mOHead.p);
+      XFT_K(xft_swap_outer_dims(mOHead.p, att.p, heads, T, vDim, st));          // [heads, T, v] -> [T, heads * v]
+      gemm(att.p, heads * vDim, L.o.p, hidden, nxt, hidden, 0, 0, 0, nullptr, cur, 0, T);      // + residual
+      norm(nxt, L.n2, L.n2b, hb, T);
+      if (L.denseMlp) {
+        gemm(hb, hidden, L.gateUp.p, 2 * inter, g.p, inter, 0, 1, inter, nullptr, nullptr, act, T);
+        gemm(g.p, inter, L.down.p, hidden, cur, hidden, 0, 0, 0, nullptr, nxt, 0, T);
+        continue;
+      }
+      // ---- shared + routed experts (src/layers/moe_deepseek.h:121-196,285-353)
+      const int E = experts, k = topK, I = moeInter;
+      gemm(hb, hidden, L.router.p, E, moeLogits.p, E, 1, 0, 0, nullptr, nullptr, 0, T);
+      XFT_K(xft_moe_route(moeLogits.as<float>(), E, T, E, k, 2, L.routerBias.as<float>(), nGroup, topkGroup, routedScale,
+                          normTopk ? 1 : 0, sigmoidScores ? 1 : 0, moeIdx.as<int>(), moeWts.as<float>(), st));
+      XFT_K(xft_moe_plan(moeIdx.as<int>(), moeWts.as<float>(), T, k, 0, E, moeBn, moePos.as<int>(), moeSrc.as<int>(),
+                         moeRowW.as<float>(), moeTiles.p, moeMeta.as<int>(), moeMaxTiles, T * k, st));
+      XFT_K(xft_moe_gather(hb, hidden, moeSrc.as<int>(), moeMeta.as<int>(), moeXs.p, T * k, hidden, st));
+      XFT_K(xft_gemm_bf16_grouped(moeXs.p, hidden, T * k, L.expGateUp.p, E * 2 * I, hidden, moeH1.p, I, 0, I, hidden, 1, I,
+                                  2 * I, moeTiles.p, moeMeta.as<int>(), moeMaxTiles, moeBn, nullptr, 2, stp, st));
+      XFT_K(xft_gemm_bf16_grouped(moeH1.p, I, T * k, L.expDown.p, E * hidden, I, moeYs.p, hidden, 1, hidden, I, 0, 0, hidden,
+                                  moeTiles.p, moeMeta.as<int>(), moeMaxTiles, moeBn, moeRowW.as<float>(), 0, stp, st));
+      const float* sharedOut = nullptr;
+      if (sharedInter > 0) {
+        gemm(hb, hidden, L.sharedGateUp.p, 2 * sharedInter, g.p, sharedInter, 0, 1, sharedInter, nullptr, nullptr, 2, T);
+        gemm(g.p, sharedInter, L.sharedDown.p, hidden, mShared.p, hidden, 1, 0, 0, nullptr, nullptr, 0, T);
+        sharedOut = mShared.as<float>();
+      }
+      XFT_K(xft_moe_combine(moeYs.as<float>(), moePos.as<int>(), k, sharedOut, nxt, hidden, cur, nullptr, T, hidden, st));
+      continue;
+    }
+    const LayerLins& Q = (decode && wqNext != wq) ? linsNext[l] : lins[l];
     lin(Q.qkv, hb, qkvBuf.p, qkvN, 0, L.qkvBias.as<float>(), nullptr, 1.0f, 0);
     if (spec.rope2d) {
       XFT_K(xft_qkv_rope2d_cache(qkvBuf.p, qkvN, T, heads, kvHeads, headDim, dPos.as<int>(), dPos2.as<int>(), table, rotDim,

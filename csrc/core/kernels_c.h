@@ -61,6 +61,17 @@ int xft_w8a8_gemm(const void* qx, int ldqx, const void* Wq, int ldw, void* Y, in
                   const float* w_sum, const float* bias, const void* residual, int ldr, float res_scale, int act, float* ws,
                   size_t ws_bytes, int* counters, int n_counters, int* status, cudaStream_t st);
 int xft_gated_act(const void* gu, void* out, int T, int I, int act, cudaStream_t st);
+// DeepSeek latent attention: the steps between the projections and the attention in one launch; the attention over the
+// latent cache (q_abs / out: head stride, token stride in elements); [A, B, D] -> [B, A, D]
+int xft_mla_prep(const void* q, int ldq, const void* kv, int ldkv, int T, int Hl, int nope, int rope, int kvl,
+                 const int* positions, const float* table, int max_pos, const float* kv_norm_w, float eps, void* q_nope,
+                 void* q_rope, void* cache, long long nslots, const int* slots, int* status, int nope_head_major,
+                 cudaStream_t st);
+int xft_mla_attention(const void* q_abs, long long qa_sh, long long qa_st, const void* q_rope, long long qr_sh, long long qr_st,
+                      void* out, long long o_sh, long long o_st, const void* cache, const int* block_table, int bt_stride,
+                      const int* cu_q, const int* kv_lens, int B, int T, int hl, int bs, int num_blocks, float scale,
+                      int nsplit, float* part_o, float* part_ml, int* counters, int* status, cudaStream_t st);
+int xft_swap_outer_dims(const void* src, void* dst, int A, int B, int D, cudaStream_t st);
 int xft_sample_topk_topp(const float* logits, int ld, int rows, int V, int k, float top_p, float temperature,
                          const float* uniform, int* out, cudaStream_t st);
 }

@@ -352,9 +352,10 @@ struct MlaPrepParams {
   int T, Hl, nope, rope, kvl;
   const int* positions; const float* table; int max_pos;      // table [max_pos, rope] = cos(rope/2) ‖ sin(rope/2)
   const float* kv_norm_w; float eps;
-  bf16* q_nope; bf16* q_rope;        // [T, Hl, nope], [T, Hl, rope]
+  bf16* q_nope; bf16* q_rope;        // [T, Hl, nope] (or [Hl, T, nope] with nope_head_major), [T, Hl, rope]
   bf16* cache; long long nslots; const int* slots;            // [nslots, kvl + rope]
   int* status;
+  int nope_head_major;               // the per-head absorb GEMM reads its rows grouped by head
 };
 
 __global__ void __launch_bounds__(128) mla_prep_kernel(const MlaPrepParams p) {
@@ -370,7 +371,7 @@ __global__ void __launch_bounds__(128) mla_prep_kernel(const MlaPrepParams p) {
   const int half = p.rope / 2;
   if (h < p.Hl) {
     const bf16* src = p.q + (size_t)t * p.ldq + (size_t)h * (p.nope + p.rope);
-    bf16* dn = p.q_nope + ((size_t)t * p.Hl + h) * p.nope;
+    bf16* dn = p.q_nope + (p.nope_head_major ? (size_t)h * p.T + t : (size_t)t * p.Hl + h) * p.nope;
     for (int d = lane * 2; d < p.nope; d += 64)
       *reinterpret_cast<__nv_bfloat162*>(dn + d) = *reinterpret_cast<const __nv_bfloat162*>(src + d);
     bf16* dr = p.q_rope + ((size_t)t * p.Hl + h) * p.rope;
@@ -532,17 +533,39 @@ extern "C" int xft_latent_write(const void* latent, int ld, void* cache, int W, 
   return (int)cudaGetLastError();
 }
 
+// src [A, B, D] bf16 -> dst [B, A, D] (D a multiple of 8, 16-byte aligned rows): per-head results [heads, tokens, D] back
+// to token-major rows for the output projection.
+__global__ void __launch_bounds__(128) swap_outer_dims_kernel(const bf16* __restrict__ src, bf16* __restrict__ dst, int A,
+                                                              int B, int D) {
+  grid_dep_launch();
+  grid_dep_wait();
+  const long long row = blockIdx.x;            // a * B + b
+  const int a = (int)(row / B), b = (int)(row % B);
+  const bf16x8* s = reinterpret_cast<const bf16x8*>(src + row * D);
+  bf16x8* d = reinterpret_cast<bf16x8*>(dst + ((long long)b * A + a) * D);
+  for (int i = threadIdx.x; i < D / 8; i += 128) d[i] = s[i];
+}
+
+extern "C" int xft_swap_outer_dims(const void* src, void* dst, int A, int B, int D, cudaStream_t st) {
+  if (A <= 0 || B <= 0 || D <= 0) return 0;
+  if (D % 8 || (((uintptr_t)src | (uintptr_t)dst) & 15)) return -1;
+  cudaError_t e = launch_pdl(swap_outer_dims_kernel, dim3((unsigned)((long long)A * B)), dim3(128), 0, st, (const bf16*)src,
+                             (bf16*)dst, A, B, D);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}
+
 // q rows [T, Hl * (nope + rope)] (row stride ldq), kv rows [T, kvl + rope] (row stride ldkv); all of nope, rope, kvl,
-// ldq, ldkv and the cache row width even, pointers 4-byte aligned.
+// ldq, ldkv and the cache row width even, pointers 4-byte aligned.  With nope_head_major the no-position parts are
+// written as [Hl, T, nope].
 extern "C" int xft_mla_prep(const void* q, int ldq, const void* kv, int ldkv, int T, int Hl, int nope, int rope, int kvl,
                             const int* positions, const float* table, int max_pos, const float* kv_norm_w, float eps,
                             void* q_nope, void* q_rope, void* cache, long long nslots, const int* slots, int* status,
-                            cudaStream_t st) {
+                            int nope_head_major, cudaStream_t st) {
   if (T <= 0) return 0;
   if (Hl <= 0 || nope < 0 || rope <= 0 || kvl <= 0 || ((nope | rope | kvl | ldq | ldkv) & 1)) return -1;
   if (((uintptr_t)q | (uintptr_t)kv | (uintptr_t)q_nope | (uintptr_t)q_rope | (uintptr_t)cache) & 3) return -1;
   MlaPrepParams p{(const bf16*)q, ldq, (const bf16*)kv, ldkv, T, Hl, nope, rope, kvl, positions, table, max_pos,
-                  kv_norm_w, eps, (bf16*)q_nope, (bf16*)q_rope, (bf16*)cache, nslots, slots, status};
+                  kv_norm_w, eps, (bf16*)q_nope, (bf16*)q_rope, (bf16*)cache, nslots, slots, status, nope_head_major};
   const long long warps = (long long)T * (Hl + 1);
   cudaError_t e = launch_pdl(mla_prep_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, st, p);
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();

@@ -1,6 +1,6 @@
 // Command-line generation with the C++ API (reference: examples/cpp/example.cpp:352-545).
 //
-//   example -m <model dir> [-t <tokenizer.model>] [-d bf16|fp16|int8|w8a8|nf4] [--kv_cache_dtype fp16|int8] [-i "1 2 3 4"] [-l input_len]
+//   example -m <model dir> [-t <tokenizer.model>] [-d bf16|fp16|int8|w8a8|int4|nf4|bf16_int8|...] [--kv_cache_dtype fp16|int8] [-i "1 2 3 4"] [-l input_len]
 //           [-o out_len] [--prefix_len n] [-n num_beams] [-b batch] [--loop n] [--topK k] [--topP p]
 //           [--temperature t] [--repetPen r] [--do_sample] [--no_stream]
 // Same flag names as the reference.  -l pads the prompt to `input_len` tokens by repeating its third token (the
@@ -76,9 +76,8 @@ int main(int argc, char** argv) {
   }
   if (prefixLen < 0 || prefixLen >= (int)prompt.size()) { std::fprintf(stderr, "--prefix_len must be below the prompt length\n"); return 2; }
   try {
-    const xft::DataType wdt = dtype == "fp16" ? xft::DataType::fp16 : dtype == "int8" ? xft::DataType::int8
-                              : dtype == "w8a8" ? xft::DataType::w8a8 : dtype == "nf4" ? xft::DataType::nf4
-                                                                                      : xft::DataType::bf16;
+    const xft::DataType wdt = xft::dataTypeFromName(dtype.c_str());
+    if (wdt == xft::DataType::unknown) { std::fprintf(stderr, "unknown weight type %s\n", dtype.c_str()); return 2; }
     xft::AutoModel m(model, wdt,
                      kv == "int8" ? xft::DataType::int8 : xft::DataType::fp16);
     if (prefixLen > 0) {

@@ -221,11 +221,11 @@ def test_cpp_engine_families_match_python(mt, tmp_path, monkeypatch):
     py.free_seqs(sid)
 
 
-@pytest.mark.parametrize("dtype", ["int8", "w8a8", "nf4"])
+@pytest.mark.parametrize("dtype", ["int8", "w8a8", "nf4", "int4", "bf16_int8", "w8a8_nf4"])
 def test_cpp_engine_quantised_weights(dtype, tmp_path, monkeypatch):
-    """Quantise-at-load in the C++ engine (per-channel int8 weight-only, int8 x int8, NF4): same codes and kernels as
-    the Python engine with that dtype, so the logits agree closely; both track the fp32 oracle of the dense model within
-    the quantisation error."""
+    """Quantise-at-load in the C++ engine (per-channel int8 weight-only, int8 x int8, NF4, uint4, and hybrid types: one
+    form for the prompt pass, another for decode steps): same codes as the Python engine with that dtype, so the logits
+    agree closely; both track the fp32 oracle of the dense model within the quantisation error."""
     import xfastertransformer_b200 as xft
     from xfastertransformer_b200.tools.synthetic import preset, write_synthetic_checkpoint
     lib = os.path.join(ROOT, "xfastertransformer_b200", "lib", "libxft_b200_torch.so")
@@ -245,9 +245,82 @@ def test_cpp_engine_quantised_weights(dtype, tmp_path, monkeypatch):
     assert m.free_seqs(ids)
     top = oracle.abs().max().item()
     assert (got - want).abs().max().item() <= 0.03 * top + 0.02, (dtype, (got - want).abs().max().item(), top)
-    assert (got - oracle).abs().max().item() <= (0.9 if dtype == "nf4" else 0.2) * top, (dtype, (got - oracle).abs().max().item())
+    first = dtype.split("_")[0]
+    assert (got - oracle).abs().max().item() <= (0.9 if first in ("nf4", "int4") else 0.2) * top, (dtype, (got - oracle).abs().max().item())
     m.config(P + 6, None, None, None, None, 100000, 0, None, None, None, None, None, None)
     m.input(prompt)
     while not m.is_done():
         m.generate()
-    assert m.finalize().shape == (2, P + 6)
+    out = m.finalize()
+    assert out.shape == (2, P + 6)
+    # decode steps (the second type of a hybrid): teacher-forced through the Python engine of the same dtype
+    sid = py.set_input_cb(prompt.tolist(), None, P + 8)
+    lg = py.forward_cb().float().cpu()
+    for t in range(6):
+        tok = out[:, P + t].cpu()
+        best = lg.max(-1).values
+        assert (lg.gather(1, tok[:, None])[:, 0] >= best - 0.05 * best.abs() - 0.1).all(), (dtype, t, tok.tolist(), lg.argmax(-1).tolist())
+        if t + 1 < 6:
+            py.set_input_cb(tok.tolist(), sid, P + 8)
+            lg = py.forward_cb().float().cpu()
+    py.free_seqs(sid)
+
+
+@pytest.mark.parametrize("dtype,routing", [("bf16", "all"), ("fp8_e4m3", "all"), ("bf16", "grouped")])
+def test_cpp_engine_deepseek(dtype, routing, tmp_path, monkeypatch):
+    """DeepSeek in the C++ engine (latent attention with query compression, YaRN table, dense first layer, shared +
+    routed experts, e4m3 checkpoints dequantised at load) against the Python engine and the fp32 PyTorch path.
+    "all": every expert is selected, so the comparison has no discrete routing decisions in it and is tight on every row;
+    "grouped": 4 of 16 experts out of the 2 best of 4 groups — a near-tie may pick another expert for some token and move
+    that row's logits, so at least half of the rows must agree tightly (a wrong routing parameter would move all)."""
+    import xfastertransformer_b200 as xft
+    from xfastertransformer_b200.config import ModelConfig, RopeConfig
+    from xfastertransformer_b200.tools.synthetic import write_synthetic_checkpoint
+    lib = os.path.join(ROOT, "xfastertransformer_b200", "lib", "libxft_b200_torch.so")
+    if not os.path.exists(lib):
+        pytest.skip("torch binding not built")
+    torch.ops.load_library(lib)
+    route = dict(sparse_experts=8, n_group=1, topk_group=1, num_experts_per_tok=8) if routing == "all" else \
+        dict(sparse_experts=16, n_group=4, topk_group=2, num_experts_per_tok=4)
+    cfg = ModelConfig(model_type="deepseek_moe", num_layer=3, hidden_size=512, head_num=8, kv_head_num=8, size_per_head=128,
+                      inter_size=1024, vocab_size=1024, max_pos_seq_len=4096, q_lora_rank=256, kv_lora_rank=512,
+                      qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, moe_intermediate_size=256,
+                      first_k_dense_replace=1, dense_experts=1, routed_scaling_factor=2.5, topk_method="noaux_tc",
+                      norm_topk_prob=True, scoring_func="sigmoid", activation_type="silu", weight_data_type=dtype,
+                      start_id=0, end_id=1,
+                      rope=RopeConfig(theta=10000, scaling_type="yarn", scaling_factor=40, original_max_pos=4096,
+                                      beta_fast=32, beta_slow=1, mscale=1.0, mscale_all_dim=1.0), **route)
+    d = str(tmp_path / "ds")
+    write_synthetic_checkpoint(d, cfg, seed=0, dtype=dtype, std=0.05)
+    prompt = torch.randint(0, 1024, (4, 24), generator=torch.Generator().manual_seed(3))
+    P, new = prompt.shape[1], 6
+    oracle = _cpu_oracle_logits(d, prompt, monkeypatch)
+    py = xft.AutoModel.from_pretrained(d, dtype="bf16", kv_cache_dtype="bf16")
+    want = py(prompt)[:, -1].float().cpu()
+    m = torch.classes.xfastertransformer.AutoModel(d, "bf16", "fp16")
+    ids = m.set_input_cb(prompt, None, None, torch.tensor([P + 4] * 4))
+    got = m.forward_cb().float().cpu()
+    assert m.free_seqs(ids)
+    top = max(1.0, oracle.abs().max().item())
+    row_err = lambda a, b: (a - b).abs().amax(-1)
+    need = 4 if routing == "all" else 2
+    assert (row_err(got, oracle) < 0.1 * top).sum().item() >= need, (row_err(got, oracle).tolist(), top)
+    assert (row_err(got, want) < 0.06 * top + 0.03).sum().item() >= need, (row_err(got, want).tolist(), top)
+    # decode steps: latent cache append, split latent attention, block tables
+    m.config(P + new, None, None, None, None, 100000, 0, None, None, None, None, None, None)
+    m.input(prompt)
+    while not m.is_done():
+        m.generate()
+    out = m.finalize()
+    assert out.shape == (4, P + new) and torch.equal(out[:, :P].cpu(), prompt)
+    if routing == "all":
+        sid = py.set_input_cb(prompt.tolist(), None, P + new + 2)
+        lg = py.forward_cb().float().cpu()
+        for t in range(new):
+            tok = out[:, P + t].cpu()
+            best = lg.max(-1).values
+            assert (lg.gather(1, tok[:, None])[:, 0] >= best - 0.05 * best.abs() - 0.1).all(), (t, tok.tolist(), lg.argmax(-1).tolist())
+            if t + 1 < new:
+                py.set_input_cb(tok.tolist(), sid, P + new + 2)
+                lg = py.forward_cb().float().cpu()
+        py.free_seqs(sid)

@@ -434,7 +434,9 @@ def latent_cache_write(latent, cache, slots):
 
 def mla_prep(q, kv, Hl, nope, rope, kvl, positions, table, kv_norm_w, eps, cache, slots):
     """q [T, Hl*(nope+rope)], kv [T, kvl+rope] (row views allowed) -> (q_nope [T,Hl,nope], q_rope [T,Hl,rope]); the
-    normalised compressed KV and the rotated shared key part land in the latent cache at `slots`."""
+    normalised compressed KV and the rotated shared key part land in the latent cache at `slots`.  q_nope is a
+    [T,Hl,nope] VIEW of head-major storage [Hl,T,nope]: the absorb GEMM reads its rows grouped by head, so
+    `q_nope.transpose(0, 1)` is contiguous and costs no copy."""
     def rows(x):
         if x.stride(1) != 1 or x.stride(0) % 2 or x.data_ptr() % 4:
             x = x.contiguous()
@@ -442,7 +444,7 @@ def mla_prep(q, kv, Hl, nope, rope, kvl, positions, table, kv_norm_w, eps, cache
     q2, ldq = rows(q)
     kv2, ldkv = rows(kv)
     T = q2.shape[0]
-    q_nope = torch.empty(T, Hl, nope, dtype=torch.bfloat16, device=q.device)
+    q_nope = torch.empty(Hl, T, nope, dtype=torch.bfloat16, device=q.device)
     q_rope = torch.empty(T, Hl, rope, dtype=torch.bfloat16, device=q.device)
     ws = Workspace.get(q.device)
     nb, _, bs, W = cache.shape
@@ -452,9 +454,9 @@ def mla_prep(q, kv, Hl, nope, rope, kvl, positions, table, kv_norm_w, eps, cache
     fn.restype = C.c_int
     _check(fn(_p(q2), ldq, _p(kv2), ldkv, T, Hl, nope, rope, kvl, _p(positions), _p(table), table.shape[0],
               _p(kv_norm_w), C.c_float(eps), _p(q_nope), _p(q_rope), _p(cache), C.c_longlong(nb * bs), _p(slots),
-              _p(ws.status), _stream()), "mla_prep")
+              _p(ws.status), 1, _stream()), "mla_prep")
     ws.launches += 1
-    return q_nope, q_rope
+    return q_nope.transpose(0, 1), q_rope
 
 
 def plan_attn_splits(B, hkv, group, D, max_kv, int8=False):
