@@ -6,9 +6,11 @@
 //   auto all = model.finalize();
 //
 // and the continuous-batching calls set_input(ids, seqIDs, maxLen) / forward() / freeSeqs().  The native engine
-// runs llama, yarn_llama, gemma, qwen, qwen2, qwen3, baichuan (RoPE or ALiBi), chatglm, chatglm2 / 3 / 4, gpt (OPT),
-// telechat and the routed-expert families mixtral and qwen3_moe in bf16 on one B200; deepseek_moe (latent attention,
-// fp8 experts), quantised weights and more than one GPU run through the Python package.  It uses the same sm_100a kernels as the Python
+// runs all sixteen families on one B200: llama, yarn_llama, gemma, qwen, qwen2, qwen3, baichuan (RoPE or ALiBi), chatglm,
+// chatglm2 / 3 / 4, gpt (OPT), telechat, the routed-expert families mixtral and qwen3_moe, and deepseek_moe (latent
+// attention, shared + routed experts, e4m3 checkpoints dequantised to bf16 at load).  Dense families take bf16 / fp16,
+// int8, w8a8, int4, nf4 weights (quantised at load) and the hybrid types (one form for the prompt pass, one for decode
+// steps); the expert families run in bf16.  More than one GPU runs through the Python package.  It uses the same sm_100a kernels as the Python
 // package — greedy, top-k / top-p sampling and beam search (host scorer, beams fork and reorder paged KV block tables);
 // errors are exceptions (std::runtime_error), never exit().
 #pragma once
