@@ -10,7 +10,9 @@
 // chatglm2 / 3 / 4, gpt (OPT), telechat, the routed-expert families mixtral and qwen3_moe, and deepseek_moe (latent
 // attention, shared + routed experts, e4m3 checkpoints dequantised to bf16 at load).  Dense families take bf16 / fp16,
 // int8, w8a8, int4, nf4 weights (quantised at load) and the hybrid types (one form for the prompt pass, one for decode
-// steps); the expert families run in bf16.  More than one GPU runs through the Python package.  It uses the same sm_100a kernels as the Python
+// steps); the expert families run in bf16.  The dense families also run tensor-parallel over several ranks (heads,
+// FFN rows and lm_head rows split as the reference splits them); the expert families on more than one GPU run through
+// the Python package.  It uses the same sm_100a kernels as the Python
 // package — greedy, top-k / top-p sampling and beam search (host scorer, beams fork and reorder paged KV block tables);
 // errors are exceptions (std::runtime_error), never exit().
 #pragma once
@@ -26,7 +28,8 @@
 
 namespace xft {
 
-class Engine;   // csrc/core/engine.cc
+class Engine;         // csrc/core/engine.cc
+class Communicator;   // csrc/core/comm.h
 
 class Model {
 public:
@@ -65,8 +68,11 @@ public:
   void unsetPrefix();
   bool setStopWords(std::vector<std::vector<int>> stopWordsList);
 
-  bool isMaster() { return true; }
-  int getRank() { return 0; }
+  // Tensor-parallel ranks (one process per GPU, or thread ranks of one process) all make the same calls; the arguments
+  // of rank 0 (the master) are the ones every rank uses, as in the reference.
+  bool isMaster();
+  int getRank();
+  int getWorldSize();
   int getBatchSize() { return batchSize; }
   int getSeqLen() { return seqLen; }
   int getVocabSize();
@@ -76,7 +82,7 @@ public:
 
 protected:
   friend class ModelDecoder;          // the AbstractDecoder view of this model (makeDecoder)
-  void load(const std::string& path, DataType dt, DataType kv);
+  void load(const std::string& path, DataType dt, DataType kv, std::shared_ptr<Communicator> comm = nullptr);
   std::unique_ptr<Engine> engine;
   SearcherConfig configuration;
   std::vector<std::vector<int>> stopWords;
@@ -85,7 +91,11 @@ protected:
 
 class AutoModel : public Model {
 public:
+  // Rank and world size come from the launcher's environment (RANK / WORLD_SIZE, OMPI_COMM_WORLD_*, PMI_*): with more
+  // than one rank the dense families run tensor-parallel, one GPU per process, over NCCL.
   AutoModel(std::string modelPath, xft::DataType dataType, xft::DataType KVCacheDataType = xft::DataType::fp16);
+  // The same with an explicit communicator (csrc/core/comm.h: process ranks, or thread ranks inside one process).
+  AutoModel(std::string modelPath, xft::DataType dataType, xft::DataType KVCacheDataType, std::shared_ptr<Communicator> comm);
 };
 
 }  // namespace xft

@@ -81,6 +81,12 @@ def build(force=False, verbose=False):
         if os.path.exists(cb_src) and (force or _newer(cb_src, cb_bin, hdrs) or _newer(core, cb_bin)):
             _run(cxx + ["-o", cb_bin, cb_src, "-L", OUT, "-lxft_b200_core", "-lxft_b200_kernels", "-L",
                         "/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,/usr/local/cuda/lib64"], verbose)
+        tp_src = os.path.join(ROOT, "examples", "cpp", "tp_check.cpp")
+        tp_bin = os.path.join(OUT, "xft_tp_check")
+        if os.path.exists(tp_src) and (force or _newer(tp_src, tp_bin, hdrs) or _newer(core, tp_bin)):
+            _run(cxx + ["-o", tp_bin, tp_src, "-L", OUT, "-lxft_b200_core", "-lxft_b200_kernels", "-L",
+                        "/usr/local/cuda/lib64", "-lcudart", "-lpthread", "-Wl,-rpath,$ORIGIN",
+                        "-Wl,-rpath,/usr/local/cuda/lib64"], verbose)
         # torch custom-class binding (torch.classes.xfastertransformer.AutoModel) on top of the C++ runtime
         tb_src = os.path.join(api, "torch_binding.cc")
         tb_lib = os.path.join(OUT, "libxft_b200_torch.so")

@@ -17,6 +17,7 @@
 
 #include "arena.h"
 #include "beam.h"
+#include "comm.h"
 #include "dtypes.h"
 #include "env.h"
 #include "ini.h"
@@ -159,7 +160,14 @@ const FamilySpec* familySpec(const std::string& type) {
 
 class Engine {
 public:
-  Engine(const std::string& path, DataType dt, DataType kvdt);
+  Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_ptr<Communicator> comm = nullptr);
+  // tensor parallelism (src/layers/decoder_block.h + split_util.h): this rank holds the query heads [q0, q1) with the
+  // KV heads that cover them, rows [i0, i1) of the FFN and rows [v0, v1) of the lm_head.  After these ranges are set,
+  // `heads`, `kvHeads`, `inter` and `vocab` below are THIS RANK'S counts; the model's own are the ...G fields.
+  std::shared_ptr<Communicator> comm;
+  int rank = 0, world = 1;
+  int headsG = 0, kvHeadsG = 0, interG = 0, vocabG = 0;
+  int q0 = 0, kv0 = 0, i0 = 0, v0 = 0, qOff = 0, groupG = 1, vocabPad = 0;
   // hyper-parameters
   std::string type;
   int heads = 0, kvHeads = 0, headDim = 0, hidden = 0, inter = 0, layers = 0, vocab = 0, maxPos = 0, endId = 0;
@@ -199,8 +207,12 @@ public:
   void attachPrefix(SequenceMeta& s);
 
 private:
-  void loadLinear(const std::string& file, int inF, int outF, void* dst, int dstRowOffset, int dstLd);
-  DevBuf loadVector(const std::string& file, int n, bool optional = false, int dt = -1);
+  // file [inF, outF] -> dst rows [dstRowOffset, ...) = the outputs [o0, o1) over the inputs [n0, n1) (whole tensor when
+  // the ranges are left at -1), transposed to [out, in]
+  void loadLinear(const std::string& file, int inF, int outF, void* dst, int dstRowOffset, int dstLd, int o0 = -1, int o1 = -1,
+                  int n0 = -1, int n1 = -1);
+  // elements [e0, e1) of a vector of n (all of it by default)
+  DevBuf loadVector(const std::string& file, int n, bool optional = false, int dt = -1, int e0 = -1, int e1 = -1);
   void copyBlock(int src, int dst);
   std::string dir;
   int fileDt = 1;
@@ -229,37 +241,46 @@ private:
   int numBlocks = 0;
   // activations
   DevBuf moeLogits, moeIdx, moeWts, moePos, moeSrc, moeRowW, moeTiles, moeMeta, moeXs, moeH1, moeYs;
+  DevBuf gathered;             // logits slices of all ranks
   DevBuf dIds, dPos, dPos2, dPrefix, dQScale, dSlots, dCu, dKv, dBt, x, x2, h, qkvBuf, q, att, g, rows, logits;
   cudaStream_t st = nullptr;
   static constexpr int kBlock = 64;
   static constexpr size_t kWsBytes = 64u << 20;
 };
 
-void Engine::loadLinear(const std::string& file, int inF, int outF, void* dst, int dstRowOffset, int dstLd) {
+void Engine::loadLinear(const std::string& file, int inF, int outF, void* dst, int dstRowOffset, int dstLd, int o0, int o1,
+                        int n0, int n1) {
+  if (o0 < 0) { o0 = 0; o1 = outF; }
+  if (n0 < 0) { n0 = 0; n1 = inF; }
   auto host = readFile(dir + "/" + file, (size_t)inF * outF * dtypeSize(fileDt), fileDt);
   DevBuf tmp(host.size());
   XFT_CUDA(cudaMemcpy(tmp.p, host.data(), host.size(), cudaMemcpyHostToDevice));
-  XFT_K(xft_transpose_to_bf16(tmp.p, fileDt, outF, inF, outF, static_cast<__nv_bfloat16*>(dst) + (size_t)dstRowOffset * dstLd,
+  const char* src = tmp.as<char>() + ((size_t)n0 * outF + o0) * dtypeSize(fileDt);
+  XFT_K(xft_transpose_to_bf16(src, fileDt, outF, n1 - n0, o1 - o0, static_cast<__nv_bfloat16*>(dst) + (size_t)dstRowOffset * dstLd,
                               dstLd, st));
   XFT_CUDA(cudaStreamSynchronize(st));
 }
 
-DevBuf Engine::loadVector(const std::string& file, int n, bool optional, int dt) {
+DevBuf Engine::loadVector(const std::string& file, int n, bool optional, int dt, int e0, int e1) {
   if (dt < 0) dt = auxDt;
+  if (e0 < 0) { e0 = 0; e1 = n; }
   std::ifstream probe(dir + "/" + file, std::ios::binary);
   if (!probe) {
     if (optional) return DevBuf();
     if (!Env::get().fakeModel) throw std::runtime_error("missing " + file);
   }
   auto host = readFile(dir + "/" + file, (size_t)n * dtypeSize(dt), dt);
-  std::vector<float> f(n);
-  for (int i = 0; i < n; ++i) f[i] = elemToFloat(host.data(), dt, i);
-  DevBuf d((size_t)n * 4);
-  XFT_CUDA(cudaMemcpy(d.p, f.data(), (size_t)n * 4, cudaMemcpyHostToDevice));
+  const int m = e1 - e0;
+  std::vector<float> f(m);
+  for (int i = 0; i < m; ++i) f[i] = elemToFloat(host.data(), dt, (size_t)e0 + i);
+  DevBuf d((size_t)std::max(m, 1) * 4);
+  XFT_CUDA(cudaMemcpy(d.p, f.data(), (size_t)m * 4, cudaMemcpyHostToDevice));
   return d;
 }
 
-Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) {
+Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_ptr<Communicator> c) : comm(std::move(c)), dir(path) {
+  if (comm && comm->size() > 1) { rank = comm->rank(); world = comm->size(); comm->begin(); }
+  else comm.reset();
   Ini ini(path + "/config.ini");
   if (!ini.ok() || ini.sections().empty()) throw std::runtime_error("config.ini not found under " + path);
   type = ini.sections()[0];
@@ -378,21 +399,38 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
     }
   }
   if (ini.get(type, "quant_qweight_data_type", "") != "") throw std::runtime_error("GPTQ checkpoints run through the Python API");
+  headsG = heads; kvHeadsG = kvHeads; interG = inter; vocabG = vocab;
+  groupG = std::max(headsG / std::max(kvHeadsG, 1), 1);
+  if (world > 1) {
+    if (spec.mla || spec.mlp == 3) throw std::runtime_error("tensor-parallel expert families run through the Python API");
+    if (world > headsG) throw std::runtime_error("more tensor-parallel ranks than attention heads");
+    const HeadRange hr = headRange(headsG, kvHeadsG, world, rank);
+    q0 = hr.q0; kv0 = hr.kv0;
+    heads = hr.q1 - hr.q0; kvHeads = hr.kv1 - hr.kv0;
+    qOff = q0 - kv0 * groupG;                    // first local query head inside its KV group
+    const auto fr = taskRange(interG, world, rank);
+    i0 = fr.first; inter = fr.second - fr.first;
+    const auto vr = taskRange(vocabG, world, rank);
+    v0 = vr.first; vocab = vr.second - vr.first;
+    for (int r = 0; r < world; ++r) { const auto x = taskRange(vocabG, world, r); vocabPad = std::max(vocabPad, x.second - x.first); }
+    if (inter % 8 || (wq == 2 || wqNext == 2 ? inter % 16 : 0)) throw std::runtime_error("FFN slice of this rank is not a multiple of 8");
+  }
   if (!spec.mla && headDim != 64 && headDim != 128 && headDim != 256) throw std::runtime_error("head size must be 64, 128 or 256");
 
   XFT_CUDA(cudaStreamCreate(&st));
   const int qsz = heads * headDim, kvsz = kvHeads * headDim;
-  // embedding and lm_head are stored [vocab, hidden]: convert on the host
+  // embedding (whole) and this rank's rows of the lm_head; both are stored [vocab, hidden]: convert on the host
   {
-    auto host = readFile(dir + "/model.wte.bin", (size_t)vocab * hidden * dtypeSize(auxDt), auxDt);
-    std::vector<uint16_t> b((size_t)vocab * hidden);
+    auto host = readFile(dir + "/model.wte.bin", (size_t)vocabG * hidden * dtypeSize(auxDt), auxDt);
+    std::vector<uint16_t> b((size_t)vocabG * hidden);
     for (size_t i = 0; i < b.size(); ++i) b[i] = floatToBf16(elemToFloat(host.data(), auxDt, i));
     wte.reset(b.size() * 2);
     XFT_CUDA(cudaMemcpy(wte.p, b.data(), b.size() * 2, cudaMemcpyHostToDevice));
-    host = readFile(dir + "/model.lm_head.weight.bin", (size_t)vocab * hidden * dtypeSize(auxDt), auxDt);
-    for (size_t i = 0; i < b.size(); ++i) b[i] = floatToBf16(elemToFloat(host.data(), auxDt, i));
-    lmHead.reset(b.size() * 2);
-    XFT_CUDA(cudaMemcpy(lmHead.p, b.data(), b.size() * 2, cudaMemcpyHostToDevice));
+    host = readFile(dir + "/model.lm_head.weight.bin", (size_t)vocabG * hidden * dtypeSize(auxDt), auxDt);
+    const size_t nloc = (size_t)vocab * hidden, off = (size_t)v0 * hidden;
+    for (size_t i = 0; i < nloc; ++i) b[i] = floatToBf16(elemToFloat(host.data(), auxDt, off + i));
+    lmHead.reset(nloc * 2);
+    XFT_CUDA(cudaMemcpy(lmHead.p, b.data(), nloc * 2, cudaMemcpyHostToDevice));
   }
   if (spec.embedding == 2) {
     // learned positions of OPT: max_pos_seq_len + 2 rows (the first two are never addressed by a real position)
@@ -413,12 +451,32 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
     const std::string p = "model.layers." + std::to_string(i) + ".";
     LayerWeights& L = lw[i];
     if (spec.mla) { loadMlaLayer(p, L, i); continue; }
+    // merged QKV on disk: all query heads, then all key heads, then all value heads; this rank takes its query heads
+    // and the KV heads that cover them.  Row-parallel projections (attention output, FFN down) take the matching
+    // INPUT range; their bias is added on rank 0 only, so that the sum over ranks counts it once.
+    const int qszG = headsG * headDim, kvszG = kvHeadsG * headDim, qkvG = qszG + 2 * kvszG;
+    const std::string qkvFile = p + "attention.query_key_value.weight.0.bin", qkvBiasFile = p + "attention.query_key_value.bias.0.bin";
     L.qkv.reset((size_t)(qsz + 2 * kvsz) * hidden * 2);
-    loadLinear(p + "attention.query_key_value.weight.0.bin", hidden, qsz + 2 * kvsz, L.qkv.p, 0, hidden);
-    L.qkvBias = loadVector(p + "attention.query_key_value.bias.0.bin", qsz + 2 * kvsz, true);
+    if (world == 1) {
+      loadLinear(qkvFile, hidden, qkvG, L.qkv.p, 0, hidden);
+      L.qkvBias = loadVector(qkvBiasFile, qkvG, true);
+    } else {
+      const int kOff = qszG + kv0 * headDim, vOff = qszG + kvszG + kv0 * headDim;
+      loadLinear(qkvFile, hidden, qkvG, L.qkv.p, 0, hidden, q0 * headDim, q0 * headDim + qsz);
+      loadLinear(qkvFile, hidden, qkvG, L.qkv.p, qsz, hidden, kOff, kOff + kvsz);
+      loadLinear(qkvFile, hidden, qkvG, L.qkv.p, qsz + kvsz, hidden, vOff, vOff + kvsz);
+      DevBuf bq = loadVector(qkvBiasFile, qkvG, true, -1, q0 * headDim, q0 * headDim + qsz);
+      if (bq.p) {
+        DevBuf bk = loadVector(qkvBiasFile, qkvG, true, -1, kOff, kOff + kvsz), bv = loadVector(qkvBiasFile, qkvG, true, -1, vOff, vOff + kvsz);
+        L.qkvBias.reset((size_t)(qsz + 2 * kvsz) * 4);
+        XFT_CUDA(cudaMemcpy(L.qkvBias.p, bq.p, (size_t)qsz * 4, cudaMemcpyDeviceToDevice));
+        XFT_CUDA(cudaMemcpy(L.qkvBias.as<float>() + qsz, bk.p, (size_t)kvsz * 4, cudaMemcpyDeviceToDevice));
+        XFT_CUDA(cudaMemcpy(L.qkvBias.as<float>() + qsz + kvsz, bv.p, (size_t)kvsz * 4, cudaMemcpyDeviceToDevice));
+      }
+    }
     L.o.reset((size_t)hidden * qsz * 2);
-    loadLinear(p + "attention.dense.weight.0.bin", qsz, hidden, L.o.p, 0, qsz);
-    L.oBias = loadVector(p + "attention.dense.bias.bin", hidden, true);
+    loadLinear(p + "attention.dense.weight.0.bin", qszG, hidden, L.o.p, 0, qsz, 0, hidden, q0 * headDim, q0 * headDim + qsz);
+    if (rank == 0) L.oBias = loadVector(p + "attention.dense.bias.bin", hidden, true);
     if (spec.mlp == 3) {
       // router [hidden, experts] on disk -> [experts, hidden]; experts stacked: gate rows then up rows per expert, then
       // the down matrices (the layout the grouped GEMM walks, src/layers/mlp_mixtral.h:95-187 keeps one MLP object each)
@@ -436,22 +494,24 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
       }
     } else if (spec.mlp == 1) {
       L.gateUp.reset((size_t)inter * hidden * 2);
-      loadLinear(p + "mlp.dense_h_to_4h.weight.0.bin", hidden, inter, L.gateUp.p, 0, hidden);
-      L.fc1Bias = loadVector(p + "mlp.dense_h_to_4h.bias.0.bin", inter);
-      L.fc2Bias = loadVector(p + "mlp.dense_4h_to_h.bias.bin", hidden);
+      loadLinear(p + "mlp.dense_h_to_4h.weight.0.bin", hidden, interG, L.gateUp.p, 0, hidden, i0, i0 + inter);
+      L.fc1Bias = loadVector(p + "mlp.dense_h_to_4h.bias.0.bin", interG, false, -1, i0, i0 + inter);
+      if (rank == 0) L.fc2Bias = loadVector(p + "mlp.dense_4h_to_h.bias.bin", hidden);
     } else {
       L.gateUp.reset((size_t)2 * inter * hidden * 2);
       if (spec.mlp == 2) {
-        loadLinear(p + "mlp.dense_h_to_4h.weight.0.bin", hidden, 2 * inter, L.gateUp.p, 0, hidden);   // gate rows, then up rows
+        // gate rows, then up rows, in one tensor
+        loadLinear(p + "mlp.dense_h_to_4h.weight.0.bin", hidden, 2 * interG, L.gateUp.p, 0, hidden, i0, i0 + inter);
+        loadLinear(p + "mlp.dense_h_to_4h.weight.0.bin", hidden, 2 * interG, L.gateUp.p, inter, hidden, interG + i0, interG + i0 + inter);
       } else {
-        loadLinear(p + "mlp.gate_proj.weight.0.bin", hidden, inter, L.gateUp.p, 0, hidden);
-        loadLinear(p + "mlp.up_proj.weight.0.bin", hidden, inter, L.gateUp.p, inter, hidden);
+        loadLinear(p + "mlp.gate_proj.weight.0.bin", hidden, interG, L.gateUp.p, 0, hidden, i0, i0 + inter);
+        loadLinear(p + "mlp.up_proj.weight.0.bin", hidden, interG, L.gateUp.p, inter, hidden, i0, i0 + inter);
       }
     }
     if (spec.mlp != 3) {
       L.down.reset((size_t)hidden * inter * 2);
-      loadLinear(p + (spec.mlp == 0 ? "mlp.down_proj.weight.0.bin" : "mlp.dense_4h_to_h.weight.0.bin"), inter, hidden,
-                 L.down.p, 0, inter);
+      loadLinear(p + (spec.mlp == 0 ? "mlp.down_proj.weight.0.bin" : "mlp.dense_4h_to_h.weight.0.bin"), interG, hidden,
+                 L.down.p, 0, inter, 0, hidden, i0, i0 + inter);
     }
     L.n1 = loadVector(p + "input_layernorm.weight.bin", hidden);
     L.n2 = loadVector(p + "post_attention_layernorm.weight.bin", hidden);
@@ -479,9 +539,9 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt) : dir(path) 
     XFT_CUDA(cudaMemcpy(ropeTable_.p, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice));
   }
   if (alibi) {
-    const std::vector<float> sl = alibiSlopes(heads);
-    slopes_.reset(sl.size() * 4);
-    XFT_CUDA(cudaMemcpy(slopes_.p, sl.data(), sl.size() * 4, cudaMemcpyHostToDevice));
+    const std::vector<float> sl = alibiSlopes(headsG);          // this rank's heads take their own slopes
+    slopes_.reset((size_t)heads * 4);
+    XFT_CUDA(cudaMemcpy(slopes_.p, sl.data() + q0, (size_t)heads * 4, cudaMemcpyHostToDevice));
   }
   ws.reset(kWsBytes);
   counters.reset(8192 * 4); XFT_CUDA(cudaMemset(counters.p, 0, counters.bytes));
@@ -783,9 +843,9 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
     XFT_K(xft_gemm_bf16(X, K, Wt, wRows, K, Y, N, fp32, rowsT, N, K, gated, dualOff, bias, res, N, 1.0f, actc, nullptr,
                         ws.as<float>(), kWsBytes, counters.as<int>(), 8192, stp, 0, st));
   };
-  XFT_K(xft_embedding(dIds.as<int>(), wte.p, x.p, T, hidden, vocab, embedScale, wpe.p, wpe.p ? dPos.as<int>() : nullptr, 2,
+  XFT_K(xft_embedding(dIds.as<int>(), wte.p, x.p, T, hidden, vocabG, embedScale, wpe.p, wpe.p ? dPos.as<int>() : nullptr, 2,
                       wpeRows, stp, st));
-  const int group = std::max(heads / std::max(kvHeads, 1), 1);
+  const int group = groupG;
   int nsplit = 1;
   if (decode) {
     // bf16 caches run the TMA-ring kernel (64-key tiles, two CTAs per SM); int8 caches the cp.async kernel
@@ -957,11 +1017,14 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
                                dSlots.as<int>(), stp, st));
     }
     XFT_K(xft_paged_attention(q.p, att.p, kc[l].p, vc[l].p, ks[l].as<float>(), vs[l].as<float>(), dBt.as<int>(), (int)W,
-                              dCu.as<int>(), dKv.as<int>(), B, maxQ, heads, kvHeads, group, 0, headDim, kBlock, numBlocks,
+                              dCu.as<int>(), dKv.as<int>(), B, maxQ, heads, kvHeads, group, qOff, headDim, kBlock, numBlocks,
                               scale, slopes_.as<float>(), spec.prefixLm ? dPrefix.as<int>() : nullptr, decode ? 1 : 0, nsplit,
                               partO.as<float>(), partMl.as<float>(), attnCounters.as<int>(), stp, st));
     // attention output projection (+ bias) + residual
-    lin(Q.o, att.p, nxt, hidden, 0, L.oBias.as<float>(), spec.residFromNorm ? hb : cur, resScale, 0);
+    // row-parallel: every rank multiplies its slice; residual (and bias) enter on rank 0 only, then the ranks' results
+    // are summed (src/layers/decoder_block.h:122-134 reduceAdd)
+    lin(Q.o, att.p, nxt, hidden, 0, L.oBias.as<float>(), rank == 0 ? (spec.residFromNorm ? hb : cur) : nullptr, resScale, 0);
+    if (comm) comm->allReduceBf16(nxt, (size_t)T * hidden, st);
     // ChatGLM-1 needs the normalised state again as the residual of the MLP: it goes to `cur`, whose content (the
     // block input) is no longer needed; every other family normalises into the scratch buffer
     void* hn = spec.residFromNorm ? cur : hb;
@@ -989,10 +1052,12 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
       lin(Q.gateUp, hn, g.p, inter, 1, nullptr, nullptr, 1.0f, act);
     }
     if (spec.residFromNorm) {
-      lin(Q.down, g.p, hb, hidden, 0, L.fc2Bias.as<float>(), hn, resScale, 0);      // into the scratch, which becomes the state
+      lin(Q.down, g.p, hb, hidden, 0, L.fc2Bias.as<float>(), rank == 0 ? hn : nullptr, resScale, 0);   // into the scratch, which becomes the state
+      if (comm) comm->allReduceBf16(hb, (size_t)T * hidden, st);
       std::swap(cur, hb);
     } else {
-      lin(Q.down, g.p, cur, hidden, 0, L.fc2Bias.as<float>(), nxt, resScale, 0);    // + residual, back into `cur`
+      lin(Q.down, g.p, cur, hidden, 0, L.fc2Bias.as<float>(), rank == 0 ? nxt : nullptr, resScale, 0);    // + residual, back into `cur`
+      if (comm) comm->allReduceBf16(cur, (size_t)T * hidden, st);
     }
   }
   // rows that need logits -> final norm -> lm_head (fp32)
@@ -1000,13 +1065,36 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
     XFT_CUDA(cudaMemcpyAsync(static_cast<char*>(nxt) + (size_t)r * hidden * 2, static_cast<char*>(cur) + (size_t)rowsel[r] * hidden * 2,
                              (size_t)hidden * 2, cudaMemcpyDeviceToDevice, st));
   norm(nxt, finalNorm, finalNormBias, hb, R);
-  logits.ensure((size_t)R * vocab * 4);
-  gemm(hb, hidden, lmHead.p, vocab, logits.p, vocab, 1, 0, 0, nullptr, nullptr, 0, R);
-  hostLogits.resize((size_t)R * vocab);
-  XFT_CUDA(cudaMemcpyAsync(hostLogits.data(), logits.p, hostLogits.size() * 4, cudaMemcpyDeviceToHost, st));
   int hs = 0;
-  XFT_CUDA(cudaMemcpyAsync(&hs, stp, 4, cudaMemcpyDeviceToHost, st));
-  XFT_CUDA(cudaStreamSynchronize(st));
+  if (!comm) {
+    logits.ensure((size_t)R * vocab * 4);
+    gemm(hb, hidden, lmHead.p, vocab, logits.p, vocab, 1, 0, 0, nullptr, nullptr, 0, R);
+    hostLogits.resize((size_t)R * vocab);
+    XFT_CUDA(cudaMemcpyAsync(hostLogits.data(), logits.p, hostLogits.size() * 4, cudaMemcpyDeviceToHost, st));
+    XFT_CUDA(cudaMemcpyAsync(&hs, stp, 4, cudaMemcpyDeviceToHost, st));
+    XFT_CUDA(cudaStreamSynchronize(st));
+  } else {
+    // vocabulary-parallel head (src/layers/dist_linear.h:49-101): this rank's rows of the lm_head give a slice of every
+    // logits row; slices are padded to the widest rank's width, gathered, and put in order on the host
+    const size_t per = (size_t)R * vocabPad;
+    logits.ensure(per * 4);
+    gathered.ensure(per * world * 4);
+    XFT_CUDA(cudaMemsetAsync(logits.p, 0, per * 4, st));
+    XFT_K(xft_gemm_bf16(hb, hidden, lmHead.p, vocab, hidden, logits.p, vocabPad, 1, R, vocab, hidden, 0, 0, nullptr, nullptr, 0,
+                        1.0f, 0, nullptr, ws.as<float>(), kWsBytes, counters.as<int>(), 8192, stp, 0, st));
+    comm->allGatherF32(logits.as<float>(), gathered.as<float>(), per, st);
+    std::vector<float> all(per * world);
+    XFT_CUDA(cudaMemcpyAsync(all.data(), gathered.p, all.size() * 4, cudaMemcpyDeviceToHost, st));
+    XFT_CUDA(cudaMemcpyAsync(&hs, stp, 4, cudaMemcpyDeviceToHost, st));
+    XFT_CUDA(cudaStreamSynchronize(st));
+    hostLogits.resize((size_t)R * vocabG);
+    for (int r = 0; r < world; ++r) {
+      const auto vr = taskRange(vocabG, world, r);
+      for (int row = 0; row < R; ++row)
+        std::copy(all.begin() + r * per + (size_t)row * vocabPad, all.begin() + r * per + (size_t)row * vocabPad + (vr.second - vr.first),
+                  hostLogits.begin() + (size_t)row * vocabG + vr.first);
+    }
+  }
   if (hs != 0) { cudaMemset(stp, 0, 4); throw std::runtime_error("kernel status " + std::to_string(hs)); }
   for (int sid : seqIds) { SequenceMeta& s = pool.get(sid); s.pastLen += (int)s.pending.size(); s.pending.clear(); }
   return R;
@@ -1019,8 +1107,13 @@ Model::~Model() {
   Arena::device().trim();         // ... and a destroyed model returns its memory to the device
 }
 
-void Model::load(const std::string& path, DataType dt, DataType kv) { engine.reset(new Engine(path, dt, kv)); }
-int Model::getVocabSize() { return engine->vocab; }
+void Model::load(const std::string& path, DataType dt, DataType kv, std::shared_ptr<Communicator> comm) {
+  engine.reset(new Engine(path, dt, kv, std::move(comm)));
+}
+bool Model::isMaster() { return !engine || engine->rank == 0; }
+int Model::getRank() { return engine ? engine->rank : 0; }
+int Model::getWorldSize() { return engine ? engine->world : 1; }
+int Model::getVocabSize() { return engine->vocabG; }
 int Model::getMaxSeqLen() { return engine->maxPos; }
 
 void Model::config(int maxLen, int numBeams, int numBeamHypsToKeep, float lenPenalty, bool doEarlyStopping, int eosTokenId,
@@ -1031,6 +1124,31 @@ void Model::config(int maxLen, int numBeams, int numBeamHypsToKeep, float lenPen
   config(c, stopWordsList);
 }
 namespace {
+// Tensor-parallel ranks run the same program (as the reference's ranks do under mpirun, src/models/models.cpp:202-253):
+// what the caller passes on rank 0 is what every rank uses.  These helpers copy rank 0's arguments to the others.
+void syncValue(Engine& e, void* p, size_t bytes) { if (e.comm) e.comm->broadcastHost(p, bytes); }
+template <class T>
+void syncVector(Engine& e, std::vector<T>& v) {
+  if (!e.comm) return;
+  long long n = (long long)v.size();
+  syncValue(e, &n, sizeof(n));
+  v.resize((size_t)n);
+  if (n) syncValue(e, v.data(), (size_t)n * sizeof(T));
+}
+template <class T>
+void syncNested(Engine& e, std::vector<std::vector<T>>& v) {
+  if (!e.comm) return;
+  std::vector<long long> lens;
+  for (auto& r : v) lens.push_back((long long)r.size());
+  syncVector(e, lens);
+  std::vector<T> flat;
+  for (auto& r : v) flat.insert(flat.end(), r.begin(), r.end());
+  syncVector(e, flat);
+  v.assign(lens.size(), {});
+  size_t off = 0;
+  for (size_t i = 0; i < lens.size(); ++i) { v[i].assign(flat.begin() + off, flat.begin() + off + lens[i]); off += (size_t)lens[i]; }
+}
+
 // beams other than beam 0 are extra sequences of the pool; the request's own sequence stays in `working`
 void clearBeams(Engine& e) {
   for (size_t i = 0; i < e.beamSeqs.size(); ++i)
@@ -1045,7 +1163,7 @@ void clearBeams(Engine& e) {
 // request into numBeams sequences that share its KV blocks; later calls run all beams, pick the next beams on the
 // host and reorder the block tables (reference counts move, no KV data is copied until a shared tail block is written).
 std::vector<int32_t> beamStep(Engine& e, const SearcherConfig& c) {
-  const int nb = c.numBeams, bs = (int)e.working.size(), V = e.vocab;
+  const int nb = c.numBeams, bs = (int)e.working.size(), V = e.vocabG;
   std::vector<float> lp((size_t)bs * nb * V);
   if (!e.scorer) {
     e.forward(e.working, false);
@@ -1095,7 +1213,15 @@ std::vector<int32_t> beamStep(Engine& e, const SearcherConfig& c) {
 }
 }  // namespace
 
-void Model::config(SearcherConfig& c, const std::vector<std::vector<int>>& sw) {
+void Model::config(SearcherConfig& c0, const std::vector<std::vector<int>>& sw0) {
+  SearcherConfig c = c0;
+  std::vector<std::vector<int>> sw = sw0;
+  if (engine->comm) {
+    // one seed for all ranks, or their samplers would pick different tokens
+    if (c.doSample && c.seed == 0) c.seed = (unsigned long long)std::chrono::steady_clock::now().time_since_epoch().count() | 1ull;
+    syncValue(*engine, &c, sizeof(c));
+    syncNested(*engine, sw);
+  }
   if (c.numBeams > 1 && c.doSample) throw std::runtime_error("beam search with sampling is not supported");
   configuration = c;
   if (configuration.eosTokenId == -1) configuration.eosTokenId = engine->endId;
@@ -1107,6 +1233,8 @@ void Model::config(SearcherConfig& c, const std::vector<std::vector<int>>& sw) {
 bool Model::setStopWords(std::vector<std::vector<int>> sw) { stopWords = cleanStopWords(sw, configuration.eosTokenId); return true; }
 
 void Model::input(std::vector<int32_t>& ids, int batch) {
+  syncValue(*engine, &batch, sizeof(batch));
+  syncVector(*engine, ids);
   if (batch <= 0 || ids.size() % batch) throw std::invalid_argument("input ids do not divide into the batch");
   clearBeams(*engine);
   for (int id : engine->working) engine->release(id);
@@ -1138,6 +1266,7 @@ std::vector<int> Model::set_input(std::vector<int32_t>& ids, int batch, Searcher
 }
 std::vector<int> Model::set_input(std::vector<std::vector<int32_t>>& ids, SearcherConfig& c, const std::vector<std::vector<int>>& sw) {
   config(c, sw);
+  syncNested(*engine, ids);
   clearBeams(*engine);
   for (int id : engine->working) engine->release(id);
   engine->working.clear();
@@ -1154,6 +1283,9 @@ std::vector<int> Model::set_input(std::vector<std::vector<int32_t>>& ids, Search
 }
 
 std::vector<int> Model::set_input(std::vector<std::vector<int32_t>>& ids, std::vector<int> seqIDs, int maxLen) {
+  syncNested(*engine, ids);
+  syncVector(*engine, seqIDs);
+  syncValue(*engine, &maxLen, sizeof(maxLen));
   engine->cbActive.clear();
   if (seqIDs.empty()) {
     for (auto& p : ids) {
@@ -1185,7 +1317,7 @@ std::vector<int> Model::set_input(std::vector<int32_t>& ids, int batch, std::vec
 std::tuple<float*, int, int> Model::forward(bool logitsAll) {
   if (engine->cbActive.empty()) throw std::runtime_error("forward() before set_input()");
   const int rows = engine->forward(engine->cbActive, logitsAll);
-  return std::make_tuple(engine->hostLogits.data(), rows, engine->vocab);
+  return std::make_tuple(engine->hostLogits.data(), rows, engine->vocabG);
 }
 
 // AbstractDecoder over a loaded model (reference: the decoder objects behind include/abstract_decoder.h, i.e.
@@ -1213,13 +1345,13 @@ public:
       }
     }
     e.forward(seqs, logitsAll);
-    return std::make_tuple(e.hostLogits.data(), 0, e.vocab);
+    return std::make_tuple(e.hostLogits.data(), 0, e.vocabG);
   }
 
   std::tuple<float*, int, int> forward(const std::vector<int>& seqIDs, bool logitsAll) override {
     Engine& e = *model.engine;
     e.forward(seqIDs, logitsAll);
-    return std::make_tuple(e.hostLogits.data(), 0, e.vocab);
+    return std::make_tuple(e.hostLogits.data(), 0, e.vocabG);
   }
 
   void reorderCache(int* idx, int size) override {
@@ -1277,14 +1409,14 @@ std::vector<int32_t> Model::generate() {
     size_t r = 0;
     for (int id : active) {
       SequenceMeta& s = engine->pool.get(id);
-      float* l = engine->hostLogits.data() + r++ * engine->vocab;
+      float* l = engine->hostLogits.data() + r++ * engine->vocabG;
       if (c.repetitionPenalty != 1.0f) {
         std::vector<int32_t> all(s.prompt);
         all.insert(all.end(), s.generated.begin(), s.generated.end());
-        repetitionPenalty(l, engine->vocab, all, c.repetitionPenalty);
+        repetitionPenalty(l, engine->vocabG, all, c.repetitionPenalty);
       }
-      int tok = c.doSample ? sampleTopKTopP(l, engine->vocab, c.topK, c.topP, c.temperature, uni(engine->rng))
-                           : argmaxFirst(l, engine->vocab);
+      int tok = c.doSample ? sampleTopKTopP(l, engine->vocabG, c.topK, c.topP, c.temperature, uni(engine->rng))
+                           : argmaxFirst(l, engine->vocabG);
       s.stepForward(tok);
       // stop check (src/searchers/sampling.cpp:134-154): eos, or total_len + 1 >= max_len
       if (tok == c.eosTokenId || s.totalLen() >= s.maxLen || (!stopWords.empty() && matchStopWords(s.generated, stopWords)))
@@ -1325,6 +1457,7 @@ std::vector<int32_t> Model::finalize() {
 }
 
 bool Model::freeSeqs(std::vector<int>& seqIDs) {
+  syncVector(*engine, seqIDs);
   for (int id : seqIDs)
     if (engine->pool.has(id)) engine->release(id);
   auto& a = engine->cbActive;
@@ -1333,6 +1466,7 @@ bool Model::freeSeqs(std::vector<int>& seqIDs) {
 }
 
 void Model::setPrefix(std::vector<int32_t>& prefix) {
+  syncVector(*engine, prefix);
   unsetPrefix();
   const int n = (int)prefix.size() / 64 * 64;      // whole blocks only: sharers never write into a shared block
   if (n == 0) return;
@@ -1347,7 +1481,13 @@ void Model::unsetPrefix() {
 }
 
 AutoModel::AutoModel(std::string modelPath, xft::DataType dataType, xft::DataType KVCacheDataType) {
-  load(modelPath, dataType, KVCacheDataType);
+  // launched as one process per GPU (mpirun, torchrun): the ranks find each other through NCCL
+  const auto rw = rankFromEnv();
+  load(modelPath, dataType, KVCacheDataType, rw.second > 1 ? makeProcessCommunicator(rw.first, rw.second) : nullptr);
+}
+AutoModel::AutoModel(std::string modelPath, xft::DataType dataType, xft::DataType KVCacheDataType,
+                     std::shared_ptr<Communicator> comm) {
+  load(modelPath, dataType, KVCacheDataType, std::move(comm));
 }
 
 }  // namespace xft

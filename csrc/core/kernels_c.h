@@ -72,6 +72,8 @@ int xft_mla_attention(const void* q_abs, long long qa_sh, long long qa_st, const
                       const int* cu_q, const int* kv_lens, int B, int T, int hl, int bs, int num_blocks, float scale,
                       int nsplit, float* part_o, float* part_ml, int* counters, int* status, cudaStream_t st);
 int xft_swap_outer_dims(const void* src, void* dst, int A, int B, int D, cudaStream_t st);
+// dst[i] <- sum of srcs[s][i], bf16, all pointers on this GPU (srcs: host array of nsrc <= 8 device pointers)
+int xft_sum_bf16(void* dst, const void* const* srcs, int nsrc, size_t n, cudaStream_t st);
 int xft_sample_topk_topp(const float* logits, int ld, int rows, int V, int k, float top_p, float temperature,
                          const float* uniform, int* out, cudaStream_t st);
 }

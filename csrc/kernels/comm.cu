@@ -152,3 +152,27 @@ extern "C" int xft_ar_params_layout(long long* out, int n) {
   for (int i = 0; i < m && i < n; ++i) out[i] = v[i];
   return m;
 }
+
+// ---------------------------------------------------------------------------------------------- local sum
+// dst[i] <- sum over s of srcs[s][i] (fp32 accumulation, one rounding), n bf16 values; every pointer is memory of THIS
+// GPU.  The reduction step of the in-process (thread-rank) communicator of the C++ engine; dst may be one of the sources.
+namespace xft {
+struct SumSrcs { const __nv_bfloat16* p[8]; int n; };
+__global__ void __launch_bounds__(256) sum_bf16_kernel(__nv_bfloat16* dst, const SumSrcs s, size_t n) {
+  const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n) return;
+  float a = 0.f;
+  for (int k = 0; k < s.n; ++k) a += __bfloat162float(s.p[k][i]);
+  dst[i] = __float2bfloat16(a);
+}
+}  // namespace xft
+
+extern "C" int xft_sum_bf16(void* dst, const void* const* srcs, int nsrc, size_t n, cudaStream_t st) {
+  if (n == 0) return 0;
+  if (nsrc < 1 || nsrc > 8 || !dst || !srcs) return -1;
+  xft::SumSrcs s{};
+  s.n = nsrc;
+  for (int k = 0; k < nsrc; ++k) s.p[k] = (const __nv_bfloat16*)srcs[k];
+  xft::sum_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>((__nv_bfloat16*)dst, s, n);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,72 @@
+// Host-only test of the thread-rank communicator (csrc/core/comm.cc): the CUDA runtime calls and the device sum that
+// comm.cc makes are replaced by host stand-ins defined here, so the turn-taking protocol itself runs on a CPU box —
+// sums, gathers and broadcasts over many rounds with 1 to 8 ranks, no two ranks ever between collectives at once, and
+// a rank that leaves early makes the others fail instead of waiting for ever.  Built with -fsanitize=thread by
+// tests/test_cpp_runtime.py.
+#include <cuda_runtime.h>
+#include <cstdio>
+#include <cstring>
+#include <stdexcept>
+#include <cstdlib>
+#include <thread>
+#include <vector>
+#include "comm.h"
+extern "C" {
+cudaError_t cudaDeviceSynchronize() { return cudaSuccess; }
+cudaError_t cudaMemcpyAsync(void* d, const void* s, size_t n, cudaMemcpyKind, cudaStream_t) { std::memmove(d, s, n); return cudaSuccess; }
+cudaError_t cudaMemcpy(void* d, const void* s, size_t n, cudaMemcpyKind) { std::memmove(d, s, n); return cudaSuccess; }
+cudaError_t cudaStreamSynchronize(cudaStream_t) { return cudaSuccess; }
+cudaError_t cudaGetDeviceCount(int* n) { *n = 1; return cudaSuccess; }
+cudaError_t cudaSetDevice(int) { return cudaSuccess; }
+cudaError_t cudaMalloc(void** p, size_t n) { *p = malloc(n); return cudaSuccess; }
+cudaError_t cudaFree(void* p) { free(p); return cudaSuccess; }
+const char* cudaGetErrorString(cudaError_t) { return "stub"; }
+// "bf16" sum on host: treat as uint16 counters for the test
+int xft_sum_bf16(void* dst, const void* const* srcs, int nsrc, size_t n, cudaStream_t) {
+  std::vector<unsigned short> acc(n, 0);
+  for (int k = 0; k < nsrc; ++k) for (size_t i = 0; i < n; ++i) acc[i] += ((const unsigned short*)srcs[k])[i];
+  std::memcpy(dst, acc.data(), n * 2);
+  return 0;
+}
+}
+int main(int argc, char** argv) {
+  const int n = argc > 1 ? atoi(argv[1]) : 3;
+  auto comms = xft::makeThreadCommunicators(n);
+  std::vector<std::thread> th;
+  std::vector<int> ok(n, 0);
+  static int running = 0; static bool overlap = false;
+  for (int r = 0; r < n; ++r) th.emplace_back([&, r] {
+    auto c = comms[r];
+    try {
+      c->begin();
+      for (int it = 0; it < 200; ++it) {
+        // only one rank may be between collectives at a time
+        if (__sync_add_and_fetch(&running, 1) != 1) overlap = true;
+        std::vector<unsigned short> buf(16, (unsigned short)(r + 1 + it));
+        std::this_thread::yield();
+        __sync_sub_and_fetch(&running, 1);
+        c->allReduceBf16(buf.data(), 16, nullptr);
+        unsigned short want = 0; for (int k = 0; k < n; ++k) want += (unsigned short)(k + 1 + it);
+        if (buf[3] != want) throw std::runtime_error("bad sum");
+        std::vector<float> in(4, (float)r), out(4 * n, -1.f);
+        c->allGatherF32(in.data(), out.data(), 4, nullptr);
+        for (int k = 0; k < n; ++k) if (out[k * 4 + 1] != (float)k) throw std::runtime_error("bad gather");
+        long long v = r == 0 ? 777 + it : -1;
+        c->broadcastHost(&v, sizeof(v));
+        if (v != 777 + it) throw std::runtime_error("bad broadcast");
+        c->barrier();
+      }
+      ok[r] = 1;
+    } catch (const std::exception& e) { std::printf("rank %d: %s\n", r, e.what()); }
+    c->end();
+  });
+  for (auto& t : th) t.join();
+  int good = 0; for (int r = 0; r < n; ++r) good += ok[r];
+  std::printf("%d/%d ranks ok, overlap=%d\n", good, n, (int)overlap);
+  // a rank that leaves early: the others must fail, not hang
+  auto c2 = xft::makeThreadCommunicators(2);
+  std::thread a([&] { try { c2[0]->begin(); int x = 0; c2[0]->broadcastHost(&x, 4); c2[0]->broadcastHost(&x, 4); std::printf("rank0 unexpectedly passed\n"); } catch (const std::exception& e) { std::printf("rank0 failed as expected: %s\n", e.what()); } c2[0]->end(); });
+  std::thread b([&] { c2[1]->begin(); int x = 0; c2[1]->broadcastHost(&x, 4); c2[1]->end(); });
+  a.join(); b.join();
+  return good == n && !overlap ? 0 : 1;
+}

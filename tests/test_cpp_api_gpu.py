@@ -324,3 +324,28 @@ def test_cpp_engine_deepseek(dtype, routing, tmp_path, monkeypatch):
                 py.set_input_cb(tok.tolist(), sid, P + new + 2)
                 lg = py.forward_cb().float().cpu()
         py.free_seqs(sid)
+
+
+@pytest.mark.parametrize("case", ["llama-2", "llama-4", "llama-2-int8", "gpt-2", "chatglm2-2", "chatglm-2"])
+def test_cpp_tensor_parallel_thread_ranks(case, tmp_path):
+    """Tensor parallelism of the C++ engine on one GPU (examples/cpp/tp_check.cpp): N ranks as threads of one process,
+    each loading its heads / FFN rows / lm_head rows, against the single-rank engine — logits of the prompt pass and of
+    teacher-forced decode steps.  4 ranks over 2 KV heads share KV heads between ranks (query-head offset inside the
+    group) and split FFN and vocabulary unevenly; gpt / chatglm carry biases that must enter once; int8 quantises the
+    slices."""
+    from xfastertransformer_b200.config import ModelConfig
+    from xfastertransformer_b200.tools.synthetic import write_synthetic_checkpoint
+    exe = os.path.join(ROOT, "xfastertransformer_b200", "lib", "xft_tp_check")
+    if not os.path.exists(exe):
+        pytest.skip("tp_check not built")
+    parts = case.split("-")
+    fam, ranks, dtype = parts[0], parts[1], (parts[2] if len(parts) > 2 else "bf16")
+    kw = dict(model_type=fam, num_layer=2, hidden_size=256, head_num=4, kv_head_num=2, size_per_head=64, inter_size=688,
+              vocab_size=2000, max_pos_seq_len=512, activation_type="silu", weight_data_type="bf16", start_id=1, end_id=2)
+    if fam in ("gpt", "chatglm"):
+        kw.update(kv_head_num=4, activation_type="relu" if fam == "gpt" else "gelu")
+    d = str(tmp_path / "m")
+    write_synthetic_checkpoint(d, ModelConfig(**kw), seed=8, dtype="bf16", std=0.08)
+    r = subprocess.run([exe, "-m", d, "-n", ranks, "-d", dtype, "-o", "4"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "tensor-parallel ranks agree" in r.stdout, r.stdout

@@ -564,3 +564,27 @@ def test_cpp_sentencepiece_reader_matches_the_library(core, tmp_path, model_type
     assert out[0] == sp.bos_id() and out[n - 1] == sp.eos_id()
     core.xftc_tok_free(C.c_void_p(h))
     assert not core.xftc_tok_load(str(tmp_path / "missing.model").encode())
+
+
+@pytest.mark.parametrize("ranks", [1, 2, 3, 8])
+def test_thread_rank_communicator_protocol(ranks, tmp_path):
+    """The in-process tensor-parallel communicator of the C++ engine (csrc/core/comm.cc, thread ranks that take turns):
+    built with ThreadSanitizer against host stand-ins for the CUDA calls (csrc/tests/comm_selftest.cc), 200 rounds of
+    all-reduce / all-gather / broadcast / barrier per rank; a rank that leaves early fails the others."""
+    import shutil
+    import subprocess
+    if shutil.which("g++") is None:
+        pytest.skip("no g++")
+    ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = str(tmp_path / "comm_selftest")
+    cmd = ["g++", "-O1", "-g", "-std=c++17", "-fsanitize=thread", "-I", os.path.join(ROOT, "csrc", "core"), "-I",
+           os.path.join(ROOT, "csrc", "api"), "-I", "/usr/local/cuda/include",
+           os.path.join(ROOT, "csrc", "tests", "comm_selftest.cc"), os.path.join(ROOT, "csrc", "core", "comm.cc"), "-o", exe,
+           "-ldl", "-lpthread"]
+    b = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert b.returncode == 0, b.stderr[-3000:]
+    r = subprocess.run([exe, str(ranks)], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert f"{ranks}/{ranks} ranks ok, overlap=0" in r.stdout
+    assert "rank0 failed as expected" in r.stdout
+    assert "ThreadSanitizer" not in r.stderr
