@@ -43,7 +43,7 @@ class BuildPy(build_py):
 
 setup(
     name="xfastertransformer-b200",
-    version="0.2.0",
+    version="0.3.0",
     description="Blackwell-native (sm_100a) LLM inference engine with the API of xFasterTransformer",
     packages=find_packages(include=["xfastertransformer_b200", "xfastertransformer_b200.*", "xfastertransformer",
                                     "xfastertransformer.*"]),

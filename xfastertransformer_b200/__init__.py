@@ -6,7 +6,7 @@ Converters are imported lazily, as in the reference (``__init__.py:35-121``).
 from .automodel import AutoModel
 from .env import get_env
 
-__version__ = "0.2.0"
+__version__ = "0.3.0"
 
 _CONVERTERS = {
     "LlamaConvert": "llama_convert", "YiConvert": "llama_convert", "GemmaConvert": "llama_convert",
