@@ -485,6 +485,12 @@ class Decoder:
                 # interleaved prefill: the sum is started here and waited for by the driver of the two interleaved
                 # batches, after it has enqueued the other batch's next block (Decoder.forward_pair)
                 self._work = self.ctx.all_reduce_async(y)
+            elif peer is not None and y.is_cuda and y.numel() <= peer.slot and \
+                    y.dtype in (torch.float32, torch.bfloat16):
+                # decode sizes with a weight type (or a token count) the fused kernel does not take: the partial
+                # products are summed by the peer-memory one-shot kernel, which a CUDA graph can hold (a NCCL call
+                # cannot safely sit in one).  The decision depends on the shape only, so every rank takes it alike.
+                y = peer.all_reduce(y.contiguous())
             else:
                 y = self.ctx.all_reduce(y)
         return y

@@ -68,11 +68,14 @@ class CudaRunner:
                 per_rank = [sum(1 for s in seqs if s.owner == r) for r in range(ctx.dp_size)]
                 if max(self.bucket(n) if n else 0 for n in per_rank) > ctx.epcomm.max_tokens:
                     return False
-        if self.m.ctx.tp_size > 1 and self.m.decoder.has_moe:
-            # the experts' partial sums cross ranks through the peer-memory all-reduce, which holds at most `slot`
-            # values; without it the step would put a NCCL collective inside the captured graph
+        if self.m.ctx.tp_size > 1:
+            # every cross-rank sum of a captured step must be a peer-memory kernel (fused into the GEMM for bf16
+            # weights, the one-shot all-reduce for the experts' partial sums and for weight types the fused kernel does
+            # not take), which holds at most `slot` values; without it the step would put a NCCL collective inside the
+            # captured graph
             peer = getattr(self.m.ctx, "peer", None)
-            if peer is None or self.bucket(len(seqs)) * self.m.cfg.hidden_size > peer.slot:
+            rows = self.bucket(len(seqs))
+            if peer is None or rows * self.m.cfg.hidden_size > peer.slot:
                 return False
         return all(len(s.pending) == 1 and s.past_len > 0 for s in seqs)
 
