@@ -290,3 +290,75 @@ def test_builtin_gptq_quantizer_beats_round_to_nearest_and_converts(tmp_path):
     got = xft.AutoModel.from_pretrained(dst, dtype="int4")(ids)
     want = model(ids).logits.float()
     assert (got - want).abs().max().item() / want.abs().max().item() < 3e-2
+
+
+def test_builtin_awq_scale_search(tmp_path):
+    """The activation-aware step of tools/quantization/quantize_gptq.py: (1) with a few loud input channels the searched
+    scales cut the 4-bit output error of a layer; (2) folding the scales into a tiny Llama (norm gains, up_proj and
+    v_proj rows) leaves its logits unchanged; (3) the AWQ + GPTQ checkpoint is an ordinary GPTQ directory whose dense
+    twin stays closer to the original model than round-to-nearest does."""
+    from safetensors.torch import load_file
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from xfastertransformer_b200.tools.quantization import quantize_gptq as Q
+    g = torch.Generator().manual_seed(3)
+    n, fin, fout = 1024, 128, 96
+    X = torch.randn(n, fin, generator=g)
+    X[:, [3, 40, 77]] *= 25.0                               # loud channels: their weights matter most for the output
+    W = torch.randn(fout, fin, generator=g) * 0.1
+    H = 2.0 * X.t() @ X / n
+    s, ratio, best, base = Q.awq_search_scale([W], H, X.abs().mean(0), 4)
+    assert ratio > 0 and best < 0.7 * base, (ratio, best, base)
+    assert s[[3, 40, 77]].min() > s.median()                # the loud channels are the ones enlarged
+    qs, ss, zs = Q.rtn_quantize(W * s[None, :], 4)
+    qr, sr, zr = Q.rtn_quantize(W, 4)
+    deq = lambda q_, s_, z_: (q_ - z_[:, None]).float() * s_[:, None]
+    e_awq = ((X / s) @ deq(qs, ss, zs).t() - X @ W.t()).pow(2).mean().item()
+    e_rtn = (X @ deq(qr, sr, zr).t() - X @ W.t()).pow(2).mean().item()
+    assert e_awq < 0.7 * e_rtn, (e_awq, e_rtn)
+
+    torch.manual_seed(4)
+    cfg = LlamaConfig(vocab_size=256, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=4, max_position_embeddings=128, tie_word_embeddings=False)
+    model = LlamaForCausalLM(cfg).eval()
+    with torch.no_grad():
+        for layer in model.model.layers:                    # loud channels in the normalised state
+            layer.input_layernorm.weight[[5, 30]] *= 12.0
+            layer.post_attention_layernorm.weight[[9]] *= 12.0
+    src = tmp_path / "hf"
+    model.save_pretrained(str(src), safe_serialization=True)
+    ids = torch.randint(0, 256, (2, 24), generator=g)
+    want = model(ids).logits.float()
+    batches = [torch.randint(0, 256, (1, 32), generator=g) for _ in range(6)]
+    twin = LlamaForCausalLM.from_pretrained(str(src), torch_dtype=torch.float32).eval()
+    Q.apply_awq(twin, batches, bits=4)
+    changed = (twin.model.layers[0].input_layernorm.weight - model.model.layers[0].input_layernorm.weight).abs().max().item()
+    assert changed > 1e-3                                   # scales were found and folded in ...
+    assert (twin(ids).logits.float() - want).abs().max().item() < 2e-3 * want.abs().max().item()      # ... same function
+
+    def dense_twin(out_dir):
+        sd = load_file(os.path.join(out_dir, "model.safetensors"))
+        m = LlamaForCausalLM(cfg).eval()
+        state = {}
+        for name in m.state_dict():
+            base = name[: -len(".weight")] if name.endswith(".weight") else name
+            if base + ".qweight" in sd:
+                qw, qz, sc = sd[base + ".qweight"], sd[base + ".qzeros"], sd[base + ".scales"].float()[0]
+                shifts = torch.arange(8) * 4
+                lv = ((qw[:, None, :] >> shifts[None, :, None]) & 15).reshape(-1, qw.shape[1])
+                zp = (((qz[:, :, None] >> shifts[None, None, :]) & 15).reshape(-1) + 1) & 15
+                state[name] = ((lv - zp[None, :]).float() * sc[None, :]).t().contiguous()
+            else:
+                state[name] = sd[name]
+        m.load_state_dict(state)
+        return m
+
+    both = Q.quantize_checkpoint(str(src), str(tmp_path / "awq_gptq"), bits=4, samples=6, seq_len=32, awq=True)
+    e_both = (dense_twin(both)(ids).logits.float() - want).abs().mean().item()
+    rtn = LlamaForCausalLM.from_pretrained(str(src), torch_dtype=torch.float32).eval()
+    with torch.no_grad():
+        for name, mod in rtn.named_modules():
+            if isinstance(mod, torch.nn.Linear) and ".layers." in name:
+                q, sc, z = Q.rtn_quantize(mod.weight.data, 4)
+                mod.weight.data = deq(q, sc, z)
+    e_rtn_model = (rtn(ids).logits.float() - want).abs().mean().item()
+    assert e_both < e_rtn_model, (e_both, e_rtn_model)

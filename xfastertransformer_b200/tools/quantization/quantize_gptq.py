@@ -7,7 +7,7 @@ installed.  The output directory is what ``LlamaConvert().convert(dir, out, from
 ``quantization_config`` in ``config.json``.
 
     python -m xfastertransformer_b200.tools.quantization.quantize_gptq <hf_dir> <out_dir> --bits 4 \\
-        [--calib text_file] [--samples 32] [--seq-len 512] [--device cuda]
+        [--calib text_file] [--samples 32] [--seq-len 512] [--device cuda] [--awq]
 
 Algorithm (GPTQ, Frantar et al. 2022, per output channel = ``group_size -1``, asymmetric): for every linear layer the
 inputs of a calibration run give H = 2 XᵀX / n; columns are quantised one by one in their natural order and the rounding
@@ -75,6 +75,38 @@ def gptq_quantize(W: torch.Tensor, H: torch.Tensor, bits: int, damp: float = 0.0
     return Q.to(torch.int32), scale, zero.to(torch.int32)
 
 
+def awq_search_scale(weights, H: torch.Tensor, x_absmean: torch.Tensor, bits: int, grid: int = 20):
+    """Activation-aware scaling (AWQ, Lin et al. 2023) for linear layers that share one input: find per-input-channel
+    factors s so that quantising W * s and feeding x / s loses the least OUTPUT — channels with large activations get
+    their weight columns enlarged and so keep more of the grid.  s = mean|x|^ratio, normalised to sqrt(max * min) = 1,
+    ratio searched over `grid` values in [0, 1); the loss of a candidate is sum over the layers of tr(D H D^T) with
+    D = W - Q(W s) / s and H = X^T X of the shared input, so no activations need to be kept.  Returns (s [in], ratio,
+    loss at ratio, loss without scaling)."""
+    H = H.float()
+    xm = x_absmean.float().clamp_min(1e-8)
+
+    def loss_for(s):
+        tot = 0.0
+        for W in weights:
+            Wf = W.float()
+            q, sc, z = rtn_quantize(Wf * s[None, :], bits)
+            D = Wf - ((q - z[:, None]).float() * sc[:, None]) / s[None, :]
+            tot += float(((D @ H) * D).sum())
+        return tot
+
+    ones = torch.ones_like(xm)
+    base = loss_for(ones)
+    best = (ones, 0.0, base)
+    for i in range(1, grid):
+        ratio = i / grid
+        s = xm.pow(ratio).clamp_min(1e-4)
+        s = s / (s.max() * s.min()).sqrt()
+        l = loss_for(s)
+        if l < best[2]:
+            best = (s, ratio, l)
+    return best[0], best[1], best[2], base
+
+
 def pack_autogptq(q: torch.Tensor, scale: torch.Tensor, zero: torch.Tensor, bits: int) -> Dict[str, torch.Tensor]:
     """[out, in] levels -> AutoGPTQ tensors: qweight int32 [in / pack, out], qzeros int32 [1, out / pack] holding
     zero - 1 (modulo 2^bits), scales fp16 [1, out], g_idx zeros."""
@@ -92,9 +124,46 @@ def pack_autogptq(q: torch.Tensor, scale: torch.Tensor, zero: torch.Tensor, bits
             "g_idx": torch.zeros(in_f, dtype=torch.int32)}
 
 
+def calibrate(model, batches, device="cpu"):
+    """One pass of the calibration batches through the unquantised model.  Returns, per decoder linear (by module name):
+    the module, sum of 2 x^T x, sum of |x| per input channel, number of rows seen."""
+    targets = {name: mod for name, mod in model.named_modules()
+               if isinstance(mod, torch.nn.Linear) and ".layers." in name and name.endswith("_proj")}
+    hess = {name: torch.zeros(m.in_features, m.in_features, device=device) for name, m in targets.items()}
+    absmean = {name: torch.zeros(m.in_features, device=device) for name, m in targets.items()}
+    count = {name: 0 for name in targets}
+
+    def hook(name):
+        def fn(_, inp):
+            x = inp[0].detach().reshape(-1, inp[0].shape[-1]).float()
+            hess[name] += 2.0 * (x.t() @ x)
+            absmean[name] += x.abs().sum(0)
+            count[name] += x.shape[0]
+        return fn
+    handles = [m.register_forward_pre_hook(hook(n)) for n, m in targets.items()]
+    with torch.no_grad():
+        for b in batches:
+            model(b.to(device))
+    for h in handles:
+        h.remove()
+    return targets, hess, absmean, count
+
+
+def apply_awq(model, batches, bits: int = 4, device="cpu"):
+    """Calibrate and fold activation-aware scales into `model` in place (same function, friendlier weights); returns
+    the statistics of the SCALED model for a following `gptq_quantize`."""
+    targets, hess, absmean, count = calibrate(model, batches, device)
+    _apply_awq(model, targets, hess, absmean, count, bits)
+    return targets, hess, absmean, count
+
+
 def quantize_checkpoint(hf_dir: str, out_dir: str, bits: int = 4, calib: str = "", samples: int = 32, seq_len: int = 512,
-                        device: str = "cpu", seed: int = 0) -> str:
-    """Quantise every decoder linear of the HF causal LM in `hf_dir` and write an AutoGPTQ-format directory."""
+                        device: str = "cpu", seed: int = 0, awq: bool = False) -> str:
+    """Quantise every decoder linear of the HF causal LM in `hf_dir` and write an AutoGPTQ-format directory.  With
+    `awq`, an activation-aware scale search runs first (the reference's recipe puts AutoAWQ with `export_compatible` in
+    front of AutoGPTQ): the factors are folded into the weights and into whatever produces their input — the norm gain
+    for q / k / v and gate / up, the rows of up_proj for down_proj, the rows of v_proj for o_proj when their sizes match —
+    so the written model computes the same function before rounding and is an ordinary GPTQ checkpoint after it."""
     from safetensors.torch import save_file
     from transformers import AutoConfig, AutoModelForCausalLM
     if bits not in (4, 8):
@@ -111,23 +180,9 @@ def quantize_checkpoint(hf_dir: str, out_dir: str, bits: int = 4, calib: str = "
     else:
         # no text given: uniformly random token ids still exercise every input direction of every layer
         batches = [torch.randint(0, cfg.vocab_size, (1, seq_len), generator=g) for _ in range(samples)]
-    targets = {name: mod for name, mod in model.named_modules()
-               if isinstance(mod, torch.nn.Linear) and ".layers." in name and name.endswith("_proj")}
-    hess = {name: torch.zeros(m.in_features, m.in_features, device=device) for name, m in targets.items()}
-    count = {name: 0 for name in targets}
-
-    def hook(name):
-        def fn(_, inp):
-            x = inp[0].detach().reshape(-1, inp[0].shape[-1]).float()
-            hess[name] += 2.0 * (x.t() @ x)
-            count[name] += x.shape[0]
-        return fn
-    handles = [m.register_forward_pre_hook(hook(n)) for n, m in targets.items()]
-    with torch.no_grad():
-        for b in batches:
-            model(b.to(device))
-    for h in handles:
-        h.remove()
+    targets, hess, absmean, count = calibrate(model, batches, device)
+    if awq:
+        _apply_awq(model, targets, hess, absmean, count, bits)
     tensors = {}
     for name, p in model.state_dict().items():
         base = name[: -len(".weight")] if name.endswith(".weight") else None
@@ -150,6 +205,54 @@ def quantize_checkpoint(hf_dir: str, out_dir: str, bits: int = 4, calib: str = "
     return out_dir
 
 
+def _apply_awq(model, targets, hess, absmean, count, bits) -> None:
+    """Scale search per decoder layer and group of linears with a common input; weights, producers of their inputs and
+    the collected statistics are rewritten in place (x -> x / s turns H into diag(1/s) H diag(1/s))."""
+    by_layer: Dict[str, Dict[str, str]] = {}
+    for name in targets:
+        prefix, leaf = name.rsplit(".", 1)
+        layer = prefix.rsplit(".", 1)[0]                  # "...layers.N"
+        by_layer.setdefault(layer, {})[leaf] = name
+    mods = dict(model.named_modules())
+
+    def rescale_stats(names, s):
+        for n in names:
+            hess[n] = hess[n] / s[:, None] / s[None, :]
+            absmean[n] = absmean[n] / s
+
+    with torch.no_grad():
+        for layer, leaves in by_layer.items():
+            groups = []
+            if all(k in leaves for k in ("q_proj", "k_proj", "v_proj")) and (layer + ".input_layernorm") in mods:
+                groups.append((["q_proj", "k_proj", "v_proj"], ("norm", mods[layer + ".input_layernorm"])))
+            if "o_proj" in leaves and "v_proj" in leaves and \
+                    targets[leaves["v_proj"]].out_features == targets[leaves["o_proj"]].in_features:
+                groups.append((["o_proj"], ("rows", targets[leaves["v_proj"]])))
+            if all(k in leaves for k in ("gate_proj", "up_proj")) and (layer + ".post_attention_layernorm") in mods:
+                groups.append((["gate_proj", "up_proj"], ("norm", mods[layer + ".post_attention_layernorm"])))
+            if "down_proj" in leaves and "up_proj" in leaves:
+                groups.append((["down_proj"], ("rows", targets[leaves["up_proj"]])))
+            for members, (kind, producer) in groups:
+                names = [leaves[m] for m in members]
+                n0 = names[0]
+                H = hess[n0] / max(count[n0], 1)
+                s, ratio, _, _ = awq_search_scale([targets[n].weight.data for n in names], H,
+                                                  absmean[n0] / max(count[n0], 1), bits)
+                if ratio == 0.0:
+                    continue
+                for n in names:
+                    targets[n].weight.data = (targets[n].weight.data.float() * s[None, :]).to(targets[n].weight.dtype)
+                if kind == "norm":
+                    producer.weight.data = (producer.weight.data.float() / s).to(producer.weight.dtype)
+                    if getattr(producer, "bias", None) is not None:
+                        producer.bias.data = (producer.bias.data.float() / s).to(producer.bias.dtype)
+                else:
+                    producer.weight.data = (producer.weight.data.float() / s[:, None]).to(producer.weight.dtype)
+                    if producer.bias is not None:
+                        producer.bias.data = (producer.bias.data.float() / s).to(producer.bias.dtype)
+                rescale_stats(names, s)
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("hf_dir")
@@ -159,8 +262,9 @@ def main():
     ap.add_argument("--samples", type=int, default=32)
     ap.add_argument("--seq-len", type=int, default=512)
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
+    ap.add_argument("--awq", action="store_true", help="activation-aware scale search before GPTQ (the AutoAWQ step of the reference's recipe)")
     a = ap.parse_args()
-    print(quantize_checkpoint(a.hf_dir, a.out_dir, a.bits, a.calib, a.samples, a.seq_len, a.device))
+    print(quantize_checkpoint(a.hf_dir, a.out_dir, a.bits, a.calib, a.samples, a.seq_len, a.device, awq=a.awq))
 
 
 if __name__ == "__main__":
