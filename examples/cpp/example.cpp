@@ -9,7 +9,8 @@
 // Gemma, Yi, Baichuan, ChatGLM families) -i may be TEXT: it is tokenised by the built-in reader (csrc/core/tokenizer.h,
 // BOS prepended) and the generated ids are printed as text too; without -t, or when -i holds only numbers, -i is a list of
 // token ids.  Prints the generated ids / text, first-token latency and average next-token latency (the reference's
-// metrics).
+// metrics).  Started as several processes (mpirun -n N, or torchrun) the dense families run tensor-parallel, one GPU per
+// process; rank 0's flags decide and rank 0 prints.
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
@@ -97,7 +98,7 @@ int main(int argc, char** argv) {
         double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
         if (steps == 0) first = ms; else rest += ms;
         ++steps;
-        if (stream && batch == 1 && numBeams == 1) {
+        if (stream && batch == 1 && numBeams == 1 && m.isMaster()) {
           // ids stream one by one; text is printed once per run below (pieces only join into characters and words in
           // context)
           std::printf("%d ", next[0]);
@@ -105,6 +106,7 @@ int main(int argc, char** argv) {
         }
       }
       auto out = m.finalize();
+      if (!m.isMaster()) continue;          // tensor-parallel ranks (mpirun -n N example ...): rank 0 reports
       if (stream && batch == 1 && numBeams == 1) std::printf("\n");
       const size_t w = out.size() / batch;
       for (int b = 0; b < batch; ++b) {
