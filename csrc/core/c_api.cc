@@ -7,6 +7,7 @@
 #include <vector>
 
 #include "arena.h"
+#include "comm.h"
 #include "beam.h"
 #include "dtypes.h"
 #include "env.h"
@@ -116,6 +117,10 @@ double xftc_telechat_ntk_theta(double theta, int rot_dim, int kv_len, int train_
 double xftc_telechat_mscale(int input_len, int train_len) { return telechatMscale(input_len, train_len); }
 double xftc_qwen_ntk_theta(double theta, int rot_dim, int max_kv, int seq_len) { return qwenNtkTheta(theta, rot_dim, max_kv, seq_len); }
 void xftc_alibi_slopes(int n_heads, float* out) { auto v = alibiSlopes(n_heads); std::memcpy(out, v.data(), v.size() * sizeof(float)); }
+
+// ---- weight-type names (csrc/api/xft/dtype.h) and the launcher's rank variables (csrc/core/comm.cc)
+int xftc_dtype_from_name(const char* name) { return (int)dataTypeFromName(name); }
+void xftc_rank_from_env(int* rank, int* world) { auto rw = rankFromEnv(); *rank = rw.first; *world = rw.second; }
 
 // ---- caching arena (csrc/core/arena.cc) over malloc/free, for tests without a GPU
 void* xftc_arena_new_host() { return new Arena([](size_t n) { return std::malloc(n); }, [](void* p) { std::free(p); }); }

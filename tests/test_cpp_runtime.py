@@ -588,3 +588,30 @@ def test_thread_rank_communicator_protocol(ranks, tmp_path):
     assert f"{ranks}/{ranks} ranks ok, overlap=0" in r.stdout
     assert "rank0 failed as expected" in r.stdout
     assert "ThreadSanitizer" not in r.stderr
+
+
+def test_weight_type_names_and_launcher_ranks(core, monkeypatch):
+    """dataTypeFromName (csrc/api/xft/dtype.h) maps the package's dtype strings to the reference's enum values, and
+    rankFromEnv reads torchrun / Open MPI / MPICH variables (the first complete pair wins, none means one rank)."""
+    names = ["fp32", "bf16", "fp16", "int8", "w8a8", "int4", "nf4", "bf16_fp16", "bf16_int8", "bf16_w8a8", "bf16_int4",
+             "bf16_nf4", "w8a8_int8", "w8a8_int4", "w8a8_nf4", "fp8_e4m3"]
+    for i, n in enumerate(names):
+        assert core.xftc_dtype_from_name(n.encode()) == i, n
+    for bad in ("", "bf", "bf16_", "int8x", "BF16"):
+        assert core.xftc_dtype_from_name(bad.encode()) == len(names), bad       # DataType::unknown
+
+    def ranks():
+        r, w = C.c_int(-1), C.c_int(-1)
+        core.xftc_rank_from_env(C.byref(r), C.byref(w))
+        return r.value, w.value
+    for k in ("RANK", "WORLD_SIZE", "OMPI_COMM_WORLD_RANK", "OMPI_COMM_WORLD_SIZE", "PMI_RANK", "PMI_SIZE"):
+        monkeypatch.delenv(k, raising=False)
+    assert ranks() == (0, 1)
+    monkeypatch.setenv("PMI_RANK", "3"); monkeypatch.setenv("PMI_SIZE", "4")
+    assert ranks() == (3, 4)
+    monkeypatch.setenv("OMPI_COMM_WORLD_RANK", "1"); monkeypatch.setenv("OMPI_COMM_WORLD_SIZE", "2")
+    assert ranks() == (1, 2)
+    monkeypatch.setenv("RANK", "5")                      # incomplete pair: ignored
+    assert ranks() == (1, 2)
+    monkeypatch.setenv("WORLD_SIZE", "8")
+    assert ranks() == (5, 8)
