@@ -11,6 +11,7 @@
 #include "beam.h"
 #include "dtypes.h"
 #include "env.h"
+#include "gptq.h"
 #include "rope_tables.h"
 #include "runtime.h"
 #include "tokenizer.h"
@@ -117,6 +118,18 @@ double xftc_telechat_ntk_theta(double theta, int rot_dim, int kv_len, int train_
 double xftc_telechat_mscale(int input_len, int train_len) { return telechatMscale(input_len, train_len); }
 double xftc_qwen_ntk_theta(double theta, int rot_dim, int max_kv, int seq_len) { return qwenNtkTheta(theta, rot_dim, max_kv, seq_len); }
 void xftc_alibi_slopes(int n_heads, float* out) { auto v = alibiSlopes(n_heads); std::memcpy(out, v.data(), v.size() * sizeof(float)); }
+
+// ---- GPTQ tensor repacking (csrc/core/gptq.cc)
+void xftc_gptq_repack(const void* file, int in_f, int out_f, int uint4, int in0, int in1, int out0, int out1, int pitch, void* dst) {
+  gptqRepack((const uint8_t*)file, in_f, out_f, uint4 != 0, in0, in1, out0, out1, pitch, (uint8_t*)dst);
+}
+void xftc_gptq_dequant(const void* file, int in_f, int out_f, int uint4, int in0, int in1, int out0, int out1, const float* scale,
+                       const float* zero, float* dst) {
+  gptqDequant((const uint8_t*)file, in_f, out_f, uint4 != 0, in0, in1, out0, out1, scale, zero, dst);
+}
+void xftc_gptq_row_sums(const void* file, int in_f, int out_f, int uint4, int in0, int in1, int out0, int out1, float* dst) {
+  gptqRowSums((const uint8_t*)file, in_f, out_f, uint4 != 0, in0, in1, out0, out1, dst);
+}
 
 // ---- weight-type names (csrc/api/xft/dtype.h) and the launcher's rank variables (csrc/core/comm.cc)
 int xftc_dtype_from_name(const char* name) { return (int)dataTypeFromName(name); }

@@ -20,6 +20,7 @@
 #include "comm.h"
 #include "dtypes.h"
 #include "env.h"
+#include "gptq.h"
 #include "ini.h"
 #include "kernels_c.h"
 #include "rope_tables.h"
@@ -180,6 +181,7 @@ public:
   int experts = 0, topK = 0, moeInter = 0;       // mixture of experts: count, experts per token, expert FFN width
   int wq = 0;                  // layer projections: 0 bf16, 1 weight-only int8, 2 int8 weights x int8 activations, 3 NF4, 4 uint4
   int wqNext = 0;              // hybrid types "A_B" (src/models/hybrid_model.h): A for the prompt pass, B for decode steps
+  int gptq = 0;                // checkpoint holds GPTQ codes: 1 int8, 2 uint4 (0: dense tensors)
   // DeepSeek
   int qLora = 0, kvLora = 0, nope = 0, ropeD = 0, vDim = 0, firstDense = 0, sharedInter = 0, nGroup = 1, topkGroup = 1;
   float routedScale = 1.f, attnScale = 1.f;
@@ -223,6 +225,12 @@ private:
   // released unless a bf16 form points at it
   void quantise(DevBuf& dense, int rows, int K, Lin& first, Lin& next);
   void quantiseAs(const DevBuf& dense, int rows, int K, int kind, Lin& out);
+  struct LayerLins;
+  struct GptqPart { std::string base; int outF, o0, o1; };       // rows [o0, o1) of one tensor of outF outputs
+  // the projections of one layer from GPTQ tensors; rows of several tensors are stacked (q‖k‖v slices, gate‖up)
+  void loadGptqLayer(const std::string& p, LayerLins& first, LayerLins& next);
+  void loadGptq(const std::vector<GptqPart>& parts, int inF, int n0, int n1, Lin& first, Lin& next);
+  std::vector<DevBuf> gptqDense;                                  // dequantised tensors that bf16 projections point at
   // bytes of one 64-token block of one layer's K (or V) pool; the latent cache of DeepSeek has one row of
   // kv_lora_rank + rope values per token and no V pool
   size_t kvBlockBytes() const {
@@ -233,7 +241,7 @@ private:
   std::map<long long, DevBuf> ntkTables_;         // by round(base): Qwen-1 / TeleChat tables beyond the first
   RopeScaling ropeScaling_;
   std::vector<LayerWeights> lw;
-  struct LayerLins { Lin qkv, o, gateUp, down; };
+  struct LayerLins { Lin qkv, o, gateUp, down; };      // (declared above for the loaders)
   std::vector<LayerLins> lins, linsNext;
   DevBuf actQ, actScale, actZero, actSum, guBuf;   // int8 activations + their row statistics; gate‖up before the activation
   DevBuf mQaKv, mQa, mQ, mQNope, mQRope, mQAbs, mOLat, mOHead, mTiles, mMeta, mShared;   // latent-attention activations
@@ -398,7 +406,17 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_
       attnScale = (float)(attnScale * m * m);
     }
   }
-  if (ini.get(type, "quant_qweight_data_type", "") != "") throw std::runtime_error("GPTQ checkpoints run through the Python API");
+  {
+    // GPTQ-converted checkpoint (llama_convert.py:335-392): per-channel codes + fp32 scales and zeros on disk
+    const std::string qt = ini.get(type, "quant_qweight_data_type", "");
+    if (!qt.empty()) {
+      gptq = qt == "int8" ? 1 : qt == "uint4" ? 2 : 0;
+      if (!gptq) throw std::runtime_error("quant_qweight_data_type must be int8 or uint4");
+      if (ini.get(type, "quant_scales_data_type", "fp32") != "fp32" || ini.get(type, "quant_zeros_data_type", "fp32") != "fp32")
+        throw std::runtime_error("GPTQ scales and zeros must be fp32");
+      if (spec.mlp != 0 || spec.mla) throw std::runtime_error("GPTQ checkpoints exist for the llama-style families");
+    }
+  }
   headsG = heads; kvHeadsG = kvHeads; interG = inter; vocabG = vocab;
   groupG = std::max(headsG / std::max(kvHeadsG, 1), 1);
   if (world > 1) {
@@ -455,16 +473,21 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_
     // and the KV heads that cover them.  Row-parallel projections (attention output, FFN down) take the matching
     // INPUT range; their bias is added on rank 0 only, so that the sum over ranks counts it once.
     const int qszG = headsG * headDim, kvszG = kvHeadsG * headDim, qkvG = qszG + 2 * kvszG;
+    // GPTQ checkpoints hold codes instead of these dense tensors: loadGptqLayer below builds the projections from them
+    auto denseLoad = [&](const std::string& file, int inF, int outF, void* dst, int dstRow, int dstLd, int o0 = -1, int o1 = -1,
+                         int n0 = -1, int n1 = -1) {
+      if (!gptq) loadLinear(file, inF, outF, dst, dstRow, dstLd, o0, o1, n0, n1);
+    };
     const std::string qkvFile = p + "attention.query_key_value.weight.0.bin", qkvBiasFile = p + "attention.query_key_value.bias.0.bin";
-    L.qkv.reset((size_t)(qsz + 2 * kvsz) * hidden * 2);
+    if (!gptq) L.qkv.reset((size_t)(qsz + 2 * kvsz) * hidden * 2);
     if (world == 1) {
-      loadLinear(qkvFile, hidden, qkvG, L.qkv.p, 0, hidden);
+      denseLoad(qkvFile, hidden, qkvG, L.qkv.p, 0, hidden);
       L.qkvBias = loadVector(qkvBiasFile, qkvG, true);
     } else {
       const int kOff = qszG + kv0 * headDim, vOff = qszG + kvszG + kv0 * headDim;
-      loadLinear(qkvFile, hidden, qkvG, L.qkv.p, 0, hidden, q0 * headDim, q0 * headDim + qsz);
-      loadLinear(qkvFile, hidden, qkvG, L.qkv.p, qsz, hidden, kOff, kOff + kvsz);
-      loadLinear(qkvFile, hidden, qkvG, L.qkv.p, qsz + kvsz, hidden, vOff, vOff + kvsz);
+      denseLoad(qkvFile, hidden, qkvG, L.qkv.p, 0, hidden, q0 * headDim, q0 * headDim + qsz);
+      denseLoad(qkvFile, hidden, qkvG, L.qkv.p, qsz, hidden, kOff, kOff + kvsz);
+      denseLoad(qkvFile, hidden, qkvG, L.qkv.p, qsz + kvsz, hidden, vOff, vOff + kvsz);
       DevBuf bq = loadVector(qkvBiasFile, qkvG, true, -1, q0 * headDim, q0 * headDim + qsz);
       if (bq.p) {
         DevBuf bk = loadVector(qkvBiasFile, qkvG, true, -1, kOff, kOff + kvsz), bv = loadVector(qkvBiasFile, qkvG, true, -1, vOff, vOff + kvsz);
@@ -474,8 +497,8 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_
         XFT_CUDA(cudaMemcpy(L.qkvBias.as<float>() + qsz + kvsz, bv.p, (size_t)kvsz * 4, cudaMemcpyDeviceToDevice));
       }
     }
-    L.o.reset((size_t)hidden * qsz * 2);
-    loadLinear(p + "attention.dense.weight.0.bin", qszG, hidden, L.o.p, 0, qsz, 0, hidden, q0 * headDim, q0 * headDim + qsz);
+    if (!gptq) L.o.reset((size_t)hidden * qsz * 2);
+    denseLoad(p + "attention.dense.weight.0.bin", qszG, hidden, L.o.p, 0, qsz, 0, hidden, q0 * headDim, q0 * headDim + qsz);
     if (rank == 0) L.oBias = loadVector(p + "attention.dense.bias.bin", hidden, true);
     if (spec.mlp == 3) {
       // router [hidden, experts] on disk -> [experts, hidden]; experts stacked: gate rows then up rows per expert, then
@@ -483,34 +506,34 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_
       const bool mix = type == "mixtral";
       const int I = moeInter;
       L.router.reset((size_t)experts * hidden * 2);
-      loadLinear(p + (mix ? "moe.gate.weight.bin" : "mlp.gate.weight.0.bin"), hidden, experts, L.router.p, 0, hidden);
+      denseLoad(p + (mix ? "moe.gate.weight.bin" : "mlp.gate.weight.0.bin"), hidden, experts, L.router.p, 0, hidden);
       L.expGateUp.reset((size_t)experts * 2 * I * hidden * 2);
       L.expDown.reset((size_t)experts * hidden * I * 2);
       for (int e = 0; e < experts; ++e) {
         const std::string ep = p + (mix ? "moe.sparse_experts." : "mlp.experts.") + std::to_string(e) + ".";
-        loadLinear(ep + (mix ? "w1.0.bin" : "gate_proj.weight.0.bin"), hidden, I, L.expGateUp.p, e * 2 * I, hidden);
-        loadLinear(ep + (mix ? "w2.0.bin" : "up_proj.weight.0.bin"), hidden, I, L.expGateUp.p, e * 2 * I + I, hidden);
-        loadLinear(ep + (mix ? "w3.0.bin" : "down_proj.weight.0.bin"), I, hidden, L.expDown.p, e * hidden, I);
+        denseLoad(ep + (mix ? "w1.0.bin" : "gate_proj.weight.0.bin"), hidden, I, L.expGateUp.p, e * 2 * I, hidden);
+        denseLoad(ep + (mix ? "w2.0.bin" : "up_proj.weight.0.bin"), hidden, I, L.expGateUp.p, e * 2 * I + I, hidden);
+        denseLoad(ep + (mix ? "w3.0.bin" : "down_proj.weight.0.bin"), I, hidden, L.expDown.p, e * hidden, I);
       }
     } else if (spec.mlp == 1) {
-      L.gateUp.reset((size_t)inter * hidden * 2);
-      loadLinear(p + "mlp.dense_h_to_4h.weight.0.bin", hidden, interG, L.gateUp.p, 0, hidden, i0, i0 + inter);
+      if (!gptq) L.gateUp.reset((size_t)inter * hidden * 2);
+      denseLoad(p + "mlp.dense_h_to_4h.weight.0.bin", hidden, interG, L.gateUp.p, 0, hidden, i0, i0 + inter);
       L.fc1Bias = loadVector(p + "mlp.dense_h_to_4h.bias.0.bin", interG, false, -1, i0, i0 + inter);
       if (rank == 0) L.fc2Bias = loadVector(p + "mlp.dense_4h_to_h.bias.bin", hidden);
     } else {
-      L.gateUp.reset((size_t)2 * inter * hidden * 2);
+      if (!gptq) L.gateUp.reset((size_t)2 * inter * hidden * 2);
       if (spec.mlp == 2) {
         // gate rows, then up rows, in one tensor
-        loadLinear(p + "mlp.dense_h_to_4h.weight.0.bin", hidden, 2 * interG, L.gateUp.p, 0, hidden, i0, i0 + inter);
-        loadLinear(p + "mlp.dense_h_to_4h.weight.0.bin", hidden, 2 * interG, L.gateUp.p, inter, hidden, interG + i0, interG + i0 + inter);
+        denseLoad(p + "mlp.dense_h_to_4h.weight.0.bin", hidden, 2 * interG, L.gateUp.p, 0, hidden, i0, i0 + inter);
+        denseLoad(p + "mlp.dense_h_to_4h.weight.0.bin", hidden, 2 * interG, L.gateUp.p, inter, hidden, interG + i0, interG + i0 + inter);
       } else {
-        loadLinear(p + "mlp.gate_proj.weight.0.bin", hidden, interG, L.gateUp.p, 0, hidden, i0, i0 + inter);
-        loadLinear(p + "mlp.up_proj.weight.0.bin", hidden, interG, L.gateUp.p, inter, hidden, i0, i0 + inter);
+        denseLoad(p + "mlp.gate_proj.weight.0.bin", hidden, interG, L.gateUp.p, 0, hidden, i0, i0 + inter);
+        denseLoad(p + "mlp.up_proj.weight.0.bin", hidden, interG, L.gateUp.p, inter, hidden, i0, i0 + inter);
       }
     }
     if (spec.mlp != 3) {
-      L.down.reset((size_t)hidden * inter * 2);
-      loadLinear(p + (spec.mlp == 0 ? "mlp.down_proj.weight.0.bin" : "mlp.dense_4h_to_h.weight.0.bin"), interG, hidden,
+      if (!gptq) L.down.reset((size_t)hidden * inter * 2);
+      denseLoad(p + (spec.mlp == 0 ? "mlp.down_proj.weight.0.bin" : "mlp.dense_4h_to_h.weight.0.bin"), interG, hidden,
                  L.down.p, 0, inter, 0, hidden, i0, i0 + inter);
     }
     L.n1 = loadVector(p + "input_layernorm.weight.bin", hidden);
@@ -525,6 +548,7 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_
     }
     LayerLins& Q = lins[i];
     LayerLins& Qn = linsNext[i];
+    if (gptq) { loadGptqLayer(p, Q, Qn); continue; }
     quantise(L.qkv, qsz + 2 * kvsz, hidden, Q.qkv, Qn.qkv);
     quantise(L.o, hidden, qsz, Q.o, Qn.o);
     if (spec.mlp != 3) {
@@ -649,6 +673,90 @@ void Engine::loadMlaLayer(const std::string& p, LayerWeights& L, int layer) {
     loadDsLinear(ep + "up_proj", H, I, L.expGateUp.p, e * 2 * I + I, H);
     loadDsLinear(ep + "down_proj", I, H, L.expDown.p, e * H, I);
   }
+}
+
+void Engine::loadGptqLayer(const std::string& p, LayerLins& first, LayerLins& next) {
+  const int qszG = headsG * headDim, kvszG = kvHeadsG * headDim, qkvG = qszG + 2 * kvszG;
+  const int qsz = heads * headDim, kvsz = kvHeads * headDim;
+  const int kOff = qszG + kv0 * headDim, vOff = qszG + kvszG + kv0 * headDim;
+  const std::string qkv = p + "attention.query_key_value";
+  loadGptq({{qkv, qkvG, q0 * headDim, q0 * headDim + qsz}, {qkv, qkvG, kOff, kOff + kvsz}, {qkv, qkvG, vOff, vOff + kvsz}}, hidden, 0,
+           hidden, first.qkv, next.qkv);
+  loadGptq({{p + "attention.dense", hidden, 0, hidden}}, qszG, q0 * headDim, q0 * headDim + qsz, first.o, next.o);
+  loadGptq({{p + "mlp.gate_proj", interG, i0, i0 + inter}, {p + "mlp.up_proj", interG, i0, i0 + inter}}, hidden, 0, hidden,
+           first.gateUp, next.gateUp);
+  loadGptq({{p + "mlp.down_proj", hidden, 0, hidden}}, interG, i0, i0 + inter, first.down, next.down);
+}
+
+void Engine::loadGptq(const std::vector<GptqPart>& parts, int inF, int n0, int n1, Lin& first, Lin& next) {
+  const bool u4 = gptq == 2;
+  const int K = n1 - n0;
+  int rows = 0;
+  for (auto& pt : parts) rows += pt.o1 - pt.o0;
+  if (u4 && (K % 2)) throw std::runtime_error("uint4 GPTQ tensors need an even input range");
+  struct Host { std::vector<char> q; std::vector<float> s, z; };
+  std::vector<Host> host(parts.size());
+  for (size_t i = 0; i < parts.size(); ++i) {
+    const GptqPart& pt = parts[i];
+    if (u4 && (pt.outF % 2)) throw std::runtime_error("uint4 GPTQ tensors need an even output dimension");
+    host[i].q = readFile(dir + "/" + pt.base + ".qweight.0.bin", u4 ? (size_t)inF * pt.outF / 2 : (size_t)inF * pt.outF, 1 /* sized below */);
+    auto sb = readFile(dir + "/" + pt.base + ".scales.0.bin", (size_t)pt.outF * 4, 0);
+    auto zb = readFile(dir + "/" + pt.base + ".zeros.0.bin", (size_t)pt.outF * 4, 0);
+    host[i].s.resize(pt.outF); host[i].z.resize(pt.outF);
+    std::memcpy(host[i].s.data(), sb.data(), sb.size());
+    std::memcpy(host[i].z.data(), zb.data(), zb.size());
+  }
+  auto upload = [&](DevBuf& d, const void* src, size_t bytes) {
+    d.reset(bytes);
+    XFT_CUDA(cudaMemcpy(d.p, src, bytes, cudaMemcpyHostToDevice));
+  };
+  int denseAt = -1;                       // index into gptqDense of this projection's dequantised copy, made on demand
+  auto build = [&](int kind, Lin& out) {
+    const bool direct = (gptq == 1 && (kind == 1 || kind == 2)) || (gptq == 2 && kind == 4);
+    if (direct) {
+      // the stored codes are what the GEMM of this weight type reads: repack [in, out] -> [out, in] rows and keep them
+      out.rows = rows; out.K = K; out.kind = kind;
+      const size_t rowBytes = ((u4 ? (size_t)K / 2 : (size_t)K) + 15) / 16 * 16;
+      out.pitch = (int)rowBytes;
+      std::vector<uint8_t> codes((size_t)rows * rowBytes);
+      std::vector<float> sc(rows), zp(rows), sums(kind == 2 ? rows : 0);
+      int r = 0;
+      for (size_t i = 0; i < parts.size(); ++i) {
+        const GptqPart& pt = parts[i];
+        const uint8_t* f = reinterpret_cast<const uint8_t*>(host[i].q.data());
+        gptqRepack(f, inF, pt.outF, u4, n0, n1, pt.o0, pt.o1, (int)rowBytes, codes.data() + (size_t)r * rowBytes);
+        if (kind == 2) gptqRowSums(f, inF, pt.outF, u4, n0, n1, pt.o0, pt.o1, sums.data() + r);
+        std::copy(host[i].s.begin() + pt.o0, host[i].s.begin() + pt.o1, sc.begin() + r);
+        std::copy(host[i].z.begin() + pt.o0, host[i].z.begin() + pt.o1, zp.begin() + r);
+        r += pt.o1 - pt.o0;
+      }
+      upload(out.q, codes.data(), codes.size());
+      upload(out.scale, sc.data(), sc.size() * 4);
+      upload(out.zero, zp.data(), zp.size() * 4);
+      if (kind == 2) upload(out.wsum, sums.data(), sums.size() * 4);
+      return;
+    }
+    // another weight type was asked for: dequantise (w = q * scale + zero) and go the way of a dense checkpoint
+    if (denseAt < 0) {
+      std::vector<float> f32((size_t)rows * K);
+      int r = 0;
+      for (size_t i = 0; i < parts.size(); ++i) {
+        const GptqPart& pt = parts[i];
+        gptqDequant(reinterpret_cast<const uint8_t*>(host[i].q.data()), inF, pt.outF, u4, n0, n1, pt.o0, pt.o1, host[i].s.data(),
+                    host[i].z.data(), f32.data() + (size_t)r * K);
+        r += pt.o1 - pt.o0;
+      }
+      std::vector<uint16_t> b16(f32.size());
+      for (size_t i = 0; i < f32.size(); ++i) b16[i] = floatToBf16(f32[i]);
+      gptqDense.emplace_back();
+      upload(gptqDense.back(), b16.data(), b16.size() * 2);
+      denseAt = (int)gptqDense.size() - 1;
+    }
+    quantiseAs(gptqDense[denseAt], rows, K, kind, out);
+  };
+  build(wq, first);
+  if (wqNext != wq) build(wqNext, next);
+  if (denseAt >= 0 && wq != 0 && wqNext != 0) gptqDense.pop_back();      // no bf16 projection points at it
 }
 
 void Engine::quantise(DevBuf& dense, int rows, int K, Lin& first, Lin& next) {

@@ -95,37 +95,17 @@ def test_gptq_layout_roundtrip(tmp_path):
     from xfastertransformer_b200.ops import reference as R
     from xfastertransformer_b200.tools.synthetic import preset, write_synthetic_checkpoint
     import numpy as np
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from gptq_util import make_gptq_dir
     for qt in ("int8", "uint4"):
-        d = str(tmp_path / qt)
         cfg = preset("tiny-llama", vocab_size=512)
-        write_synthetic_checkpoint(d, cfg, seed=0, dtype="fp32", std=0.08)
-        base = xft.AutoModel.from_pretrained(d, dtype="bf16")
+        dense = str(tmp_path / (qt + "_dense"))
+        write_synthetic_checkpoint(dense, cfg, seed=0, dtype="fp32", std=0.08)
+        base = xft.AutoModel.from_pretrained(dense, dtype="bf16")
         ids = torch.randint(0, 512, (1, 12))
         want = base(ids)
-        H, I = cfg.hidden_size, cfg.inter_size
-        q_all = cfg.head_num * cfg.size_per_head + 2 * cfg.kv_head_num * cfg.size_per_head
-        for i in range(cfg.num_layer):
-            for name, (inf, outf) in {"attention.query_key_value": (H, q_all), "attention.dense": (H, H),
-                                      "mlp.gate_proj": (H, I), "mlp.up_proj": (H, I), "mlp.down_proj": (I, H)}.items():
-                f = os.path.join(d, f"model.layers.{i}.{name}.weight.0.bin")
-                w = torch.from_numpy(np.fromfile(f, dtype=np.float32).reshape(inf, outf)).t().contiguous()   # [out,in]
-                if qt == "int8":
-                    q, s, z = R.quantize_int8_per_channel(w)
-                    q.t().contiguous().numpy().tofile(f.replace(".weight.0.bin", ".qweight.0.bin"))
-                else:
-                    p, s, z = R.quantize_uint4_per_channel(w)
-                    qq = R.unpack_nibbles(p).t().contiguous()                    # [in, out], packed along out
-                    R.pack_nibbles(qq).numpy().tofile(f.replace(".weight.0.bin", ".qweight.0.bin"))
-                s.numpy().tofile(f.replace(".weight.0.bin", ".scales.0.bin"))
-                z.numpy().tofile(f.replace(".weight.0.bin", ".zeros.0.bin"))
-                os.remove(f)
-        import configparser
-        cp = configparser.ConfigParser()
-        cp.read(os.path.join(d, "config.ini"))
-        cp["llama"].update({"quant_qweight_data_type": qt, "quant_scales_data_type": "fp32",
-                            "quant_zeros_data_type": "fp32", "quant_groupsize": "-1"})
-        with open(os.path.join(d, "config.ini"), "w") as fh:
-            cp.write(fh)
+        d = make_gptq_dir(str(tmp_path / qt), cfg, qt, seed=0, std=0.08)
         m = xft.AutoModel.from_pretrained(d, dtype="int8" if qt == "int8" else "int4")
         got = m(ids)
         rel = (got - want).abs().max().item() / want.abs().max().item()

@@ -349,3 +349,34 @@ def test_cpp_tensor_parallel_thread_ranks(case, tmp_path):
     r = subprocess.run([exe, "-m", d, "-n", ranks, "-d", dtype, "-o", "4"], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "tensor-parallel ranks agree" in r.stdout, r.stdout
+
+
+@pytest.mark.parametrize("qt,dtype", [("int8", "int8"), ("uint4", "int4"), ("uint4", "bf16"), ("int8", "w8a8")])
+def test_cpp_engine_gptq_checkpoint(qt, dtype, tmp_path):
+    """GPTQ-converted checkpoints in the C++ engine: stored codes kept as they are when the weight type matches
+    (int8 -> int8 / w8a8, uint4 -> int4), dequantised otherwise — against the Python engine on the same directory; and
+    the same directory as two tensor-parallel thread ranks (slices of the code tensors) against one rank."""
+    import sys
+    import xfastertransformer_b200 as xft
+    from xfastertransformer_b200.tools.synthetic import preset
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from gptq_util import make_gptq_dir
+    lib = os.path.join(ROOT, "xfastertransformer_b200", "lib", "libxft_b200_torch.so")
+    if not os.path.exists(lib):
+        pytest.skip("torch binding not built")
+    torch.ops.load_library(lib)
+    d = make_gptq_dir(str(tmp_path / "g"), preset("tiny-llama", vocab_size=2000, kv_head_num=2), qt, seed=4)
+    prompt = torch.randint(5, 1990, (2, 20), generator=torch.Generator().manual_seed(2))
+    P = prompt.shape[1]
+    py = xft.AutoModel.from_pretrained(d, dtype=dtype)
+    want = py(prompt)[:, -1].float().cpu()
+    m = torch.classes.xfastertransformer.AutoModel(d, dtype, "fp16")
+    ids = m.set_input_cb(prompt, None, None, torch.tensor([P + 4, P + 4]))
+    got = m.forward_cb().float().cpu()
+    assert m.free_seqs(ids)
+    top = max(1.0, want.abs().max().item())
+    assert (got - want).abs().max().item() <= 0.03 * top + 0.02, (qt, dtype, (got - want).abs().max().item(), top)
+    exe = os.path.join(ROOT, "xfastertransformer_b200", "lib", "xft_tp_check")
+    if os.path.exists(exe) and qt == dtype.replace("int4", "uint4"):
+        r = subprocess.run([exe, "-m", d, "-n", "2", "-d", dtype, "-o", "2"], capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0 and "tensor-parallel ranks agree" in r.stdout, r.stdout + r.stderr

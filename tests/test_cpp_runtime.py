@@ -615,3 +615,47 @@ def test_weight_type_names_and_launcher_ranks(core, monkeypatch):
     assert ranks() == (1, 2)
     monkeypatch.setenv("WORLD_SIZE", "8")
     assert ranks() == (5, 8)
+
+
+@pytest.mark.parametrize("uint4", [False, True])
+def test_gptq_repack_matches_the_python_loader(core, uint4, tmp_path):
+    """csrc/core/gptq.cc against runtime/loader.py:gptq_linear on the same files: the [out, in] codes (uint4: repacked
+    along `in`), a tensor-parallel slice of them, the dequantised values and the per-row code sums."""
+    from xfastertransformer_b200.runtime.loader import WeightSource, write_bin
+    g = torch.Generator().manual_seed(13)
+    in_f, out_f = 48, 40
+    if uint4:
+        q = torch.randint(0, 16, (in_f, out_f), generator=g, dtype=torch.uint8)
+        disk = (q[:, 0::2] | (q[:, 1::2] << 4)).contiguous()
+        (tmp_path / "w.qweight.0.bin").write_bytes(disk.numpy().tobytes())
+    else:
+        q = torch.randint(-128, 128, (in_f, out_f), generator=g, dtype=torch.int8)
+        disk = q
+        (tmp_path / "w.qweight.0.bin").write_bytes(q.numpy().tobytes())
+    scale = torch.rand(out_f, generator=g) * 0.01 + 0.001
+    zero = torch.randn(out_f, generator=g) * 0.01
+    write_bin(str(tmp_path / "w.scales.0.bin"), scale, "fp32")
+    write_bin(str(tmp_path / "w.zeros.0.bin"), zero, "fp32")
+    src = WeightSource(str(tmp_path), "fp16", torch.device("cpu"))
+    raw = (C.c_uint8 * disk.numel()).from_buffer_copy(disk.numpy().tobytes())
+    for (i0, i1, o0, o1) in [(0, in_f, 0, out_f), (16, 48, 0, out_f), (0, in_f, 10, 30)]:
+        W = src.gptq_linear("w", in_f, out_f, "uint4" if uint4 else "int8", "int4" if uint4 else "int8",
+                            in_rng=(i0, i1), out_rng=(o0, o1))
+        K, rows = i1 - i0, o1 - o0
+        row_bytes = K // 2 if uint4 else K
+        pitch = (row_bytes + 15) // 16 * 16
+        out = (C.c_uint8 * (rows * pitch))()
+        core.xftc_gptq_repack(raw, in_f, out_f, int(uint4), i0, i1, o0, o1, pitch, out)
+        got = torch.frombuffer(bytearray(out), dtype=torch.uint8).view(rows, pitch)
+        want = W.w.view(torch.uint8) if not uint4 else W.w
+        assert torch.equal(got[:, :row_bytes], want.reshape(rows, row_bytes)), (uint4, i0, i1, o0, o1)
+        assert int(got[:, row_bytes:].sum()) == 0
+        deq = (C.c_float * (rows * K))()
+        sc = (C.c_float * out_f)(*scale.tolist())
+        zp = (C.c_float * out_f)(*zero.tolist())
+        core.xftc_gptq_dequant(raw, in_f, out_f, int(uint4), i0, i1, o0, o1, sc, zp, deq)
+        torch.testing.assert_close(torch.tensor(list(deq)).view(rows, K), R.dequant_weight(W), rtol=1e-6, atol=1e-7)
+        sums = (C.c_float * rows)()
+        core.xftc_gptq_row_sums(raw, in_f, out_f, int(uint4), i0, i1, o0, o1, sums)
+        codes = q[i0:i1, o0:o1].t().float()
+        assert list(sums) == codes.sum(1).tolist()
