@@ -10,7 +10,7 @@
 // chatglm2 / 3 / 4, gpt (OPT), telechat, the routed-expert families mixtral and qwen3_moe, and deepseek_moe (latent
 // attention, shared + routed experts, e4m3 checkpoints dequantised to bf16 at load).  Dense families take bf16 / fp16,
 // int8, w8a8, int4, nf4 weights (quantised at load) and the hybrid types (one form for the prompt pass, one for decode
-// steps); the expert families run in bf16.  The dense families also run tensor-parallel over several ranks (heads,
+// steps), from dense or GPTQ-converted checkpoints; the expert families run in bf16.  The dense families also run tensor-parallel over several ranks (heads,
 // FFN rows and lm_head rows split as the reference splits them); the expert families on more than one GPU run through
 // the Python package.  It uses the same sm_100a kernels as the Python
 // package — greedy, top-k / top-p sampling and beam search (host scorer, beams fork and reorder paged KV block tables);
