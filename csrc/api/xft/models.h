@@ -54,13 +54,27 @@ public:
                              const std::vector<std::vector<int>>& stopWordsList = {});
   std::vector<int> set_input(std::vector<std::vector<int32_t>>& inputIds, SearcherConfig& cfg,
                              const std::vector<std::vector<int>>& stopWordsList = {});
-  // continuous batching (used with forward()): new prompts when seqIDs is empty, else one next token per sequence
+  std::vector<int> set_input(std::vector<std::vector<int32_t>>& inputIds, int maxLen = -1, int numBeams = 1,
+                             int numBeamHypsToKeep = 1, float lenPenalty = 1.0f, bool doEarlyStopping = false,
+                             int eosTokenId = -1, int padTokenId = -1, bool doSample = false, float temperature = 1.0f,
+                             int topK = 50, float topP = 1.0f, float repetitionPenalty = 1.0f,
+                             const std::vector<std::vector<int>>& stopWordsList = {});
+  std::vector<int> set_input(std::vector<std::vector<int32_t>>& inputIds, std::vector<int> seqIDs, SearcherConfig& cfg,
+                             const std::vector<std::vector<int>>& stopWordsList = {});
+  // continuous batching (used with forward()): new prompts when seqIDs is empty, else one next token per sequence.
+  // maxLen as a vector: empty = the model's limit, one value for all, or one per new sequence.  (As in the reference,
+  // a call with only the ids is ambiguous between this group and the one above: pass seqIDs or maxLen.)
   std::vector<int> set_input(std::vector<std::vector<int32_t>>& inputIds, std::vector<int> seqIDs = {}, int maxLen = -1);
-  std::vector<int> set_input(std::vector<int32_t>& inputIds, int batchSize, std::vector<int> seqIDs, int maxLen = -1);
+  std::vector<int> set_input(std::vector<int32_t>& inputIds, int batchSize, std::vector<int> seqIDs = {}, int maxLen = -1);
+  std::vector<int> set_input(std::vector<int32_t>& inputIds, int batchSize, std::vector<int> seqIDs, const std::vector<int>& maxLen);
+  std::vector<int> set_input(std::vector<int32_t>& inputIds, std::vector<int32_t>& seqLens, std::vector<int> seqIDs,
+                             std::vector<int>& maxLen);
 
   bool isDone();
   // logits of the scheduled sequences: (pointer to fp32 [rows, vocab] on the host, rows, vocab)
-  std::tuple<float*, int, int> forward(bool logitsAll = false);
+  // (the default follows the reference: every position of a prompt pass; pass false for the last position only)
+  std::tuple<float*, int, int> forward(bool logitsAll = true);
+  void createSearcher(SearcherConfig& cfg);      // the reference's name for config(cfg)
   std::vector<int32_t> generate();     // one step: next token of every sequence of the current request
   std::vector<int32_t> finalize();     // prompt + generated, flattened, rows padded to equal length
   bool freeSeqs(std::vector<int>& seqIDs);
@@ -83,6 +97,7 @@ public:
 protected:
   friend class ModelDecoder;          // the AbstractDecoder view of this model (makeDecoder)
   void load(const std::string& path, DataType dt, DataType kv, std::shared_ptr<Communicator> comm = nullptr);
+  std::vector<int> cbSetInput(std::vector<std::vector<int32_t>>& ids, std::vector<int>& seqIDs, std::vector<int>& maxLens);
   std::unique_ptr<Engine> engine;
   SearcherConfig configuration;
   std::vector<std::vector<int>> stopWords;

@@ -1391,13 +1391,25 @@ std::vector<int> Model::set_input(std::vector<std::vector<int32_t>>& ids, Search
 }
 
 std::vector<int> Model::set_input(std::vector<std::vector<int32_t>>& ids, std::vector<int> seqIDs, int maxLen) {
+  std::vector<int> lens{maxLen};
+  return cbSetInput(ids, seqIDs, lens);
+}
+
+// The one implementation behind the continuous-batching set_input overloads.  maxLens: empty = the model's limit, one
+// value = the same for every new sequence, else one per new sequence (src/models/models.cpp:518-584).
+std::vector<int> Model::cbSetInput(std::vector<std::vector<int32_t>>& ids, std::vector<int>& seqIDs, std::vector<int>& maxLens) {
   syncNested(*engine, ids);
   syncVector(*engine, seqIDs);
-  syncValue(*engine, &maxLen, sizeof(maxLen));
+  syncVector(*engine, maxLens);
+  if (!(maxLens.empty() || maxLens.size() == 1 || maxLens.size() == ids.size()))
+    throw std::invalid_argument("maxLen: none, one, or one per sequence expected");
   engine->cbActive.clear();
   if (seqIDs.empty()) {
-    for (auto& p : ids) {
-      SequenceMeta& s = engine->pool.create(p, std::max(maxLen > 0 ? maxLen : engine->maxPos, (int)p.size() + 1));
+    for (size_t i = 0; i < ids.size(); ++i) {
+      auto& p = ids[i];
+      int m = maxLens.empty() ? -1 : maxLens.size() == 1 ? maxLens[0] : maxLens[i];
+      m = m > 0 ? std::min(m, engine->maxPos) : engine->maxPos;
+      SequenceMeta& s = engine->pool.create(p, std::max(m, (int)p.size() + 1));
       engine->tables->add(s.id);
       engine->attachPrefix(s);
       engine->cbActive.push_back(s.id);
@@ -1415,12 +1427,55 @@ std::vector<int> Model::set_input(std::vector<std::vector<int32_t>>& ids, std::v
   return engine->cbActive;
 }
 std::vector<int> Model::set_input(std::vector<int32_t>& ids, int batch, std::vector<int> seqIDs, int maxLen) {
+  std::vector<int> lens{maxLen};
+  return set_input(ids, batch, seqIDs, lens);
+}
+std::vector<int> Model::set_input(std::vector<int32_t>& ids, int batch, std::vector<int> seqIDs, const std::vector<int>& maxLen) {
+  syncValue(*engine, &batch, sizeof(batch));
+  syncVector(*engine, ids);
   if (batch <= 0 || ids.size() % batch) throw std::invalid_argument("input ids do not divide into the batch");
   const size_t n = ids.size() / batch;
   std::vector<std::vector<int32_t>> rows(batch);
   for (int b = 0; b < batch; ++b) rows[b].assign(ids.begin() + b * n, ids.begin() + (b + 1) * n);
-  return set_input(rows, seqIDs, maxLen);
+  std::vector<int> lens = maxLen;
+  return cbSetInput(rows, seqIDs, lens);
 }
+// prompts of different lengths in one flat vector (seqLens says where each ends); decode: one token per sequence id
+std::vector<int> Model::set_input(std::vector<int32_t>& ids, std::vector<int32_t>& seqLens, std::vector<int> seqIDs,
+                                  std::vector<int>& maxLen) {
+  syncVector(*engine, ids);
+  syncVector(*engine, seqLens);
+  syncVector(*engine, seqIDs);
+  std::vector<std::vector<int32_t>> rows;
+  if (seqIDs.empty()) {
+    size_t off = 0;
+    for (int32_t n : seqLens) {
+      if (n <= 0 || off + (size_t)n > ids.size()) throw std::invalid_argument("seqLens do not add up to the number of input ids");
+      rows.emplace_back(ids.begin() + off, ids.begin() + off + n);
+      off += (size_t)n;
+    }
+    if (off != ids.size()) throw std::invalid_argument("seqLens do not add up to the number of input ids");
+  } else {
+    for (int32_t t : ids) rows.push_back({t});
+  }
+  return cbSetInput(rows, seqIDs, maxLen);
+}
+// sequences of a continuous batch with a sampling configuration of their own call
+std::vector<int> Model::set_input(std::vector<std::vector<int32_t>>& ids, std::vector<int> seqIDs, SearcherConfig& c,
+                                  const std::vector<std::vector<int>>& sw) {
+  config(c, sw);
+  std::vector<int> lens{configuration.maxLen};
+  return cbSetInput(ids, seqIDs, lens);
+}
+std::vector<int> Model::set_input(std::vector<std::vector<int32_t>>& ids, int maxLen, int numBeams, int numBeamHypsToKeep,
+                                  float lenPenalty, bool doEarlyStopping, int eosTokenId, int padTokenId, bool doSample,
+                                  float temperature, int topK, float topP, float repetitionPenalty,
+                                  const std::vector<std::vector<int>>& sw) {
+  SearcherConfig c(maxLen, numBeams, numBeamHypsToKeep, lenPenalty, doEarlyStopping, eosTokenId, padTokenId, doSample,
+                   temperature, topK, topP, repetitionPenalty);
+  return set_input(ids, c, sw);
+}
+void Model::createSearcher(SearcherConfig& c) { config(c); }
 
 std::tuple<float*, int, int> Model::forward(bool logitsAll) {
   if (engine->cbActive.empty()) throw std::runtime_error("forward() before set_input()");

@@ -32,10 +32,10 @@ int argmaxRow(const float* row, int vocab) {
 // one sequence on its own: prefill, then one token per forward()
 std::vector<int> runAlone(xft::Model& m, const std::vector<int32_t>& prompt, int outLen) {
   std::vector<std::vector<int32_t>> in{prompt};
-  std::vector<int> ids = m.set_input(in, {}, (int)prompt.size() + outLen);
+  std::vector<int> ids = m.set_input(in, std::vector<int>{}, (int)prompt.size() + outLen);
   std::vector<int> out;
   for (int step = 0; step < outLen; ++step) {
-    auto [logits, rows, vocab] = m.forward();
+    auto [logits, rows, vocab] = m.forward(false);
     if (rows != 1) throw std::runtime_error("expected one row of logits");
     const int tok = argmaxRow(logits, vocab);
     out.push_back(tok);
@@ -96,8 +96,8 @@ int main(int argc, char** argv) {
     while (finished < nPrompts) {
       if (admitted < nPrompts && step % stride == 0) {
         std::vector<std::vector<int32_t>> in{prompts[admitted]};
-        std::vector<int> ids = m.set_input(in, {}, (int)prompts[admitted].size() + outLen);
-        auto [logits, rows, v] = m.forward();
+        std::vector<int> ids = m.set_input(in, std::vector<int>{}, (int)prompts[admitted].size() + outLen);
+        auto [logits, rows, v] = m.forward(false);
         if (rows != 1) throw std::runtime_error("prefill returned more than one row");
         live.push_back({admitted, ids[0], {argmaxRow(logits, v)}});
         ++admitted;
@@ -120,7 +120,7 @@ int main(int argc, char** argv) {
         std::vector<int> ids;
         for (auto& s : live) { toks.push_back({s.out.back()}); ids.push_back(s.id); }
         m.set_input(toks, ids);
-        auto [logits, rows, v] = m.forward();
+        auto [logits, rows, v] = m.forward(false);
         if (rows != (int)live.size()) throw std::runtime_error("decode returned a wrong number of rows");
         for (int r = 0; r < rows; ++r) live[r].out.push_back(argmaxRow(logits + (size_t)r * v, v));
       }

@@ -31,7 +31,7 @@ struct Trace {
 // the tokens when given, else the arg-max does
 void run(xft::Model& m, std::vector<std::vector<int32_t>> prompts, int steps, const Trace* forced, Trace& out) {
   const int B = (int)prompts.size();
-  std::vector<int> ids = m.set_input(prompts, {}, 256);
+  std::vector<int> ids = m.set_input(prompts, std::vector<int>{}, 256);
   for (int s = 0; s <= steps; ++s) {
     auto r = m.forward(false);
     const float* lg = std::get<0>(r);

@@ -659,3 +659,17 @@ def test_gptq_repack_matches_the_python_loader(core, uint4, tmp_path):
         core.xftc_gptq_row_sums(raw, in_f, out_f, int(uint4), i0, i1, o0, o1, sums)
         codes = q[i0:i1, o0:o1].t().float()
         assert list(sums) == codes.sum(1).tolist()
+
+
+def test_reference_call_forms_compile():
+    """Every call form of the reference's C++ Model API resolves against csrc/api/xft/models.h (a compile-only
+    translation unit, csrc/tests/api_signatures.cc)."""
+    import shutil
+    import subprocess
+    if shutil.which("g++") is None:
+        pytest.skip("no g++")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run(["g++", "-std=c++17", "-fsyntax-only", "-Wall", "-I", os.path.join(root, "csrc", "api"), "-I",
+                        "/usr/local/cuda/include", os.path.join(root, "csrc", "tests", "api_signatures.cc")],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-3000:]
