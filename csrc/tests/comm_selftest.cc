@@ -7,6 +7,7 @@
 #include <cstdio>
 #include <cstring>
 #include <stdexcept>
+#include <string>
 #include <cstdlib>
 #include <thread>
 #include <vector>
@@ -29,7 +30,35 @@ int xft_sum_bf16(void* dst, const void* const* srcs, int nsrc, size_t n, cudaStr
   return 0;
 }
 }
+// process-rank mode: `comm_selftest process <rank> <world> <id file>` — one of `world` processes; the communicator is the
+// NCCL one of comm.cc, talking to the stand-in library named by XFT_NCCL_LIB (csrc/tests/fake_nccl.cc)
+static int processRank(int rank, int world, const char* idFile) {
+  try {
+    auto c = xft::makeProcessCommunicator(rank, world, idFile);
+    if (!c || c->rank() != rank || c->size() != world) throw std::runtime_error("bad communicator");
+    // a host broadcast larger than the staging buffer (3 pieces)
+    std::vector<unsigned char> big(2500000, (unsigned char)(rank == 0 ? 0 : 0xee));
+    if (rank == 0) for (size_t i = 0; i < big.size(); ++i) big[i] = (unsigned char)(i * 7 + 3);
+    c->broadcastHost(big.data(), big.size());
+    for (size_t i = 0; i < big.size(); i += 9973) if (big[i] != (unsigned char)(i * 7 + 3)) throw std::runtime_error("bad broadcast");
+    std::vector<float> in(5, (float)(rank + 1)), out(5 * world, -1.f);
+    c->allGatherF32(in.data(), out.data(), 5, nullptr);
+    for (int r = 0; r < world; ++r) if (out[r * 5 + 2] != (float)(r + 1)) throw std::runtime_error("bad gather");
+    std::vector<unsigned short> h(33, (unsigned short)0x3f80);          // bf16 1.0
+    c->allReduceBf16(h.data(), h.size(), nullptr);
+    const unsigned short want[9] = {0, 0x3f80, 0x4000, 0x4040, 0x4080, 0x40a0, 0x40c0, 0x40e0, 0x4100};   // bf16 of 0..8
+    if (h[32] != want[world]) throw std::runtime_error("bad sum");
+    c->barrier();
+    std::printf("rank %d of %d ok\n", rank, world);
+    return 0;
+  } catch (const std::exception& e) {
+    std::printf("rank %d: %s\n", rank, e.what());
+    return 1;
+  }
+}
+
 int main(int argc, char** argv) {
+  if (argc > 4 && std::string(argv[1]) == "process") return processRank(atoi(argv[2]), atoi(argv[3]), argv[4]);
   const int n = argc > 1 ? atoi(argv[1]) : 3;
   auto comms = xft::makeThreadCommunicators(n);
   std::vector<std::thread> th;

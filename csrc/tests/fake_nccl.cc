@@ -1,0 +1,114 @@
+// A stand-in for libnccl.so.2 for tests WITHOUT GPUs: the seven entry points csrc/core/comm.cc resolves with dlsym,
+// working on HOST pointers between processes of one machine through a shared-memory file.  Built as a shared object by
+// tests/test_cpp_runtime.py and handed to the communicator through XFT_NCCL_LIB, next to host stand-ins for the CUDA
+// runtime calls (csrc/tests/comm_selftest.cc).  It implements just what the test needs: float32 / bfloat16 / uint8
+// data, sum, up to 8 ranks, messages up to 4 MiB.
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+namespace {
+constexpr size_t kSlot = 4u << 20;
+struct Shared {
+  std::atomic<int> arrived;
+  std::atomic<int> generation;
+  char pad[56];
+};
+struct Comm { int rank, world; Shared* sh; char* slots; size_t bytes; };
+struct Id { char bytes[128]; };
+
+void barrier(Comm* c) {
+  const int gen = c->sh->generation.load();
+  if (c->sh->arrived.fetch_add(1) + 1 == c->world) {
+    c->sh->arrived.store(0);
+    c->sh->generation.fetch_add(1);
+  } else {
+    for (long spin = 0; c->sh->generation.load() == gen; ++spin) {
+      if (spin > 200000000L) { std::fprintf(stderr, "fake nccl: barrier timed out\n"); std::_Exit(3); }
+      if ((spin & 1023) == 1023) usleep(50);
+    }
+  }
+}
+size_t elemSize(int dt) { return dt == 7 ? 4 : dt == 9 ? 2 : 1; }
+float bf16ToFloat(uint16_t h) { uint32_t u = (uint32_t)h << 16; float f; std::memcpy(&f, &u, 4); return f; }
+uint16_t floatToBf16(float f) { uint32_t u; std::memcpy(&u, &f, 4); u += 0x7fff + ((u >> 16) & 1); return (uint16_t)(u >> 16); }
+}  // namespace
+
+extern "C" {
+int ncclGetUniqueId(Id* id) {
+  std::memset(id, 0, sizeof(*id));
+  std::snprintf(id->bytes, sizeof(id->bytes), "/xft_fake_nccl_%d_%ld", (int)getpid(), (long)random());
+  return 0;
+}
+int ncclCommInitRank(void** comm, int world, Id id, int rank) {
+  if (world < 1 || world > 8) return 4;
+  const size_t bytes = sizeof(Shared) + (size_t)world * kSlot;
+  int fd = -1;
+  if (rank == 0) {
+    fd = shm_open(id.bytes, O_CREAT | O_RDWR, 0600);
+    if (fd < 0 || ftruncate(fd, (off_t)bytes) != 0) return 2;
+  } else {
+    for (int i = 0; i < 4000 && fd < 0; ++i) { fd = shm_open(id.bytes, O_RDWR, 0600); if (fd < 0) usleep(1000); }
+    if (fd < 0) return 2;
+    for (int i = 0; i < 4000; ++i) { off_t sz = lseek(fd, 0, SEEK_END); if ((size_t)sz >= bytes) break; usleep(1000); }
+  }
+  void* p = mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  close(fd);
+  if (p == MAP_FAILED) return 2;
+  Comm* c = new Comm{rank, world, static_cast<Shared*>(p), static_cast<char*>(p) + sizeof(Shared), bytes};
+  *comm = c;
+  barrier(c);
+  if (rank == 0) shm_unlink(id.bytes);
+  return 0;
+}
+int ncclCommDestroy(void* comm) {
+  Comm* c = static_cast<Comm*>(comm);
+  munmap(c->sh, c->bytes);
+  delete c;
+  return 0;
+}
+int ncclAllReduce(const void* send, void* recv, size_t count, int dt, int op, void* comm, void*) {
+  Comm* c = static_cast<Comm*>(comm);
+  const size_t bytes = count * elemSize(dt);
+  if (op != 0 || bytes > kSlot || (dt != 7 && dt != 9)) return 4;
+  std::memcpy(c->slots + (size_t)c->rank * kSlot, send, bytes);
+  barrier(c);
+  for (size_t i = 0; i < count; ++i) {
+    float a = 0.f;
+    for (int r = 0; r < c->world; ++r) {
+      const char* s = c->slots + (size_t)r * kSlot;
+      a += dt == 7 ? reinterpret_cast<const float*>(s)[i] : bf16ToFloat(reinterpret_cast<const uint16_t*>(s)[i]);
+    }
+    if (dt == 7) static_cast<float*>(recv)[i] = a; else static_cast<uint16_t*>(recv)[i] = floatToBf16(a);
+  }
+  barrier(c);
+  return 0;
+}
+int ncclAllGather(const void* send, void* recv, size_t count, int dt, void* comm, void*) {
+  Comm* c = static_cast<Comm*>(comm);
+  const size_t bytes = count * elemSize(dt);
+  if (bytes > kSlot) return 4;
+  std::memcpy(c->slots + (size_t)c->rank * kSlot, send, bytes);
+  barrier(c);
+  for (int r = 0; r < c->world; ++r) std::memcpy(static_cast<char*>(recv) + (size_t)r * bytes, c->slots + (size_t)r * kSlot, bytes);
+  barrier(c);
+  return 0;
+}
+int ncclBroadcast(const void* send, void* recv, size_t count, int dt, int root, void* comm, void*) {
+  Comm* c = static_cast<Comm*>(comm);
+  const size_t bytes = count * elemSize(dt);
+  if (bytes > kSlot) return 4;
+  if (c->rank == root) std::memcpy(c->slots + (size_t)root * kSlot, send, bytes);
+  barrier(c);
+  std::memcpy(recv, c->slots + (size_t)root * kSlot, bytes);
+  barrier(c);
+  return 0;
+}
+const char* ncclGetErrorString(int rc) { return rc == 0 ? "ok" : rc == 2 ? "fake nccl: shared memory" : "fake nccl: unsupported call"; }
+}

@@ -673,3 +673,36 @@ def test_reference_call_forms_compile():
                         "/usr/local/cuda/include", os.path.join(root, "csrc", "tests", "api_signatures.cc")],
                        capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stderr[-3000:]
+
+
+def test_process_rank_communicator_with_a_stand_in_nccl(tmp_path):
+    """The NCCL communicator of the C++ engine (csrc/core/comm.cc: library opened with dlopen, unique id handed over
+    through a file, host broadcasts in pieces through a staging buffer, bf16 sums, gathers) as 1 to 4 real processes,
+    against a stand-in NCCL over shared memory (csrc/tests/fake_nccl.cc) and host stand-ins for the CUDA calls; a rank
+    whose rank 0 never comes gives up after XFT_DIST_TIMEOUT_S with an error."""
+    import shutil
+    import subprocess
+    if shutil.which("g++") is None:
+        pytest.skip("no g++")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    fake = str(tmp_path / "libfake_nccl.so")
+    exe = str(tmp_path / "comm_selftest")
+    inc = ["-I", os.path.join(root, "csrc", "core"), "-I", os.path.join(root, "csrc", "api"), "-I", "/usr/local/cuda/include"]
+    for cmd in (["g++", "-O1", "-std=c++17", "-shared", "-fPIC", os.path.join(root, "csrc", "tests", "fake_nccl.cc"), "-o", fake,
+                 "-lrt", "-lpthread"],
+                ["g++", "-O1", "-std=c++17"] + inc + [os.path.join(root, "csrc", "tests", "comm_selftest.cc"),
+                                                     os.path.join(root, "csrc", "core", "comm.cc"), "-o", exe, "-ldl", "-lpthread"]):
+        b = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+        assert b.returncode == 0, b.stderr[-3000:]
+    env = dict(os.environ, XFT_NCCL_LIB=fake, XFT_DIST_TIMEOUT_S="30")
+    for world in (2, 4):
+        idf = str(tmp_path / f"id{world}")
+        procs = [subprocess.Popen([exe, "process", str(r), str(world), idf], env=env, stdout=subprocess.PIPE,
+                                  stderr=subprocess.STDOUT, text=True) for r in reversed(range(world))]   # rank 0 starts last
+        outs = [p.communicate(timeout=120)[0] for p in procs]
+        assert all(p.returncode == 0 for p in procs), outs
+        assert sorted(o.strip() for o in outs) == sorted(f"rank {r} of {world} ok" for r in range(world))
+        assert not os.path.exists(idf) and not os.path.exists(idf + ".ready")          # rank 0 removed the hand-over files
+    lone = subprocess.run([exe, "process", "1", "2", str(tmp_path / "never")], env=dict(env, XFT_DIST_TIMEOUT_S="1"),
+                          capture_output=True, text=True, timeout=60)
+    assert lone.returncode == 1 and "did not arrive" in lone.stdout
