@@ -241,7 +241,7 @@ private:
   std::map<long long, DevBuf> ntkTables_;         // by round(base): Qwen-1 / TeleChat tables beyond the first
   RopeScaling ropeScaling_;
   std::vector<LayerWeights> lw;
-  struct LayerLins { Lin qkv, o, gateUp, down; };      // (declared above for the loaders)
+  struct LayerLins { Lin qkv, o, gateUp, down; };
   std::vector<LayerLins> lins, linsNext;
   DevBuf actQ, actScale, actZero, actSum, guBuf;   // int8 activations + their row statistics; gate‖up before the activation
   DevBuf mQaKv, mQa, mQ, mQNope, mQRope, mQAbs, mOLat, mOHead, mTiles, mMeta, mShared;   // latent-attention activations
@@ -699,7 +699,8 @@ void Engine::loadGptq(const std::vector<GptqPart>& parts, int inF, int n0, int n
   for (size_t i = 0; i < parts.size(); ++i) {
     const GptqPart& pt = parts[i];
     if (u4 && (pt.outF % 2)) throw std::runtime_error("uint4 GPTQ tensors need an even output dimension");
-    host[i].q = readFile(dir + "/" + pt.base + ".qweight.0.bin", u4 ? (size_t)inF * pt.outF / 2 : (size_t)inF * pt.outF, 1 /* sized below */);
+    // (the last argument only matters for XFT_FAKE_MODEL, which has no meaning for a quantised checkpoint)
+    host[i].q = readFile(dir + "/" + pt.base + ".qweight.0.bin", u4 ? (size_t)inF * pt.outF / 2 : (size_t)inF * pt.outF, 1);
     auto sb = readFile(dir + "/" + pt.base + ".scales.0.bin", (size_t)pt.outF * 4, 0);
     auto zb = readFile(dir + "/" + pt.base + ".zeros.0.bin", (size_t)pt.outF * 4, 0);
     host[i].s.resize(pt.outF); host[i].z.resize(pt.outF);
