@@ -315,6 +315,17 @@ def test_example_cli_flags_follow_the_reference(core):
     assert r.returncode == 1 and "config.ini" in r.stderr and "input_len 2 is not longer" in r.stderr
     assert run("-m", "/nonexistent", "-i", "hello").returncode == 2           # text needs -t <tokenizer.model>
     assert run("-m", "/nonexistent", "-i", "1 2 3", "--prefix_len", "3").returncode == 2
+    r = run("-m", "/nonexistent", "-i", "1 2 3", "-d", "int3")               # weight types: the package's dtype strings
+    assert r.returncode == 2 and "unknown weight type int3" in r.stderr
+    for dt in ("int8", "w8a8", "int4", "nf4", "bf16_int8", "w8a8_nf4"):
+        r = run("-m", "/nonexistent", "-i", "1 2 3", "-d", dt)
+        assert r.returncode == 1 and "config.ini" in r.stderr, (dt, r.stderr)
+    tp = os.path.join(os.path.dirname(LIB), "xft_tp_check")
+    if os.path.exists(tp):
+        assert subprocess.run([tp], capture_output=True, text=True, timeout=60).returncode == 2
+        assert subprocess.run([tp, "-m", "/nonexistent", "-n", "1"], capture_output=True, text=True, timeout=60).returncode == 2
+        r = subprocess.run([tp, "-m", "/nonexistent", "-n", "2"], capture_output=True, text=True, timeout=60)
+        assert r.returncode == 1 and "config.ini" in r.stderr
 
 
 def test_rope_and_alibi_tables_match_python(core):
