@@ -151,6 +151,8 @@ std::vector<std::shared_ptr<Communicator>> makeThreadCommunicators(int n) {
 }
 
 std::pair<int, int> rankFromEnv() {
+  // SINGLE_INSTANCE=1 (src/utils/environment.h): this process is a model of its own whatever launched it
+  if (envInt("SINGLE_INSTANCE", 0) != 0) return {0, 1};
   static const char* pairs[][2] = {{"RANK", "WORLD_SIZE"}, {"OMPI_COMM_WORLD_RANK", "OMPI_COMM_WORLD_SIZE"}, {"PMI_RANK", "PMI_SIZE"}};
   for (auto& p : pairs) {
     const char* r = std::getenv(p[0]);

@@ -36,7 +36,8 @@ public:
 };
 
 // Rank and world size of this process from the launcher's environment (RANK / WORLD_SIZE of torchrun,
-// OMPI_COMM_WORLD_RANK / _SIZE of Open MPI, PMI_RANK / PMI_SIZE of MPICH); {0, 1} when none is set.
+// OMPI_COMM_WORLD_RANK / _SIZE of Open MPI, PMI_RANK / PMI_SIZE of MPICH); {0, 1} when none is set or when
+// SINGLE_INSTANCE=1 asks for a model per process.
 std::pair<int, int> rankFromEnv();
 
 // NCCL communicator of `world` process ranks.  `idFile`: path through which rank 0 hands the unique id to the others

@@ -615,7 +615,7 @@ def test_weight_type_names_and_launcher_ranks(core, monkeypatch):
         r, w = C.c_int(-1), C.c_int(-1)
         core.xftc_rank_from_env(C.byref(r), C.byref(w))
         return r.value, w.value
-    for k in ("RANK", "WORLD_SIZE", "OMPI_COMM_WORLD_RANK", "OMPI_COMM_WORLD_SIZE", "PMI_RANK", "PMI_SIZE"):
+    for k in ("RANK", "WORLD_SIZE", "OMPI_COMM_WORLD_RANK", "OMPI_COMM_WORLD_SIZE", "PMI_RANK", "PMI_SIZE", "SINGLE_INSTANCE"):
         monkeypatch.delenv(k, raising=False)
     assert ranks() == (0, 1)
     monkeypatch.setenv("PMI_RANK", "3"); monkeypatch.setenv("PMI_SIZE", "4")
@@ -626,6 +626,8 @@ def test_weight_type_names_and_launcher_ranks(core, monkeypatch):
     assert ranks() == (1, 2)
     monkeypatch.setenv("WORLD_SIZE", "8")
     assert ranks() == (5, 8)
+    monkeypatch.setenv("SINGLE_INSTANCE", "1")           # a model per process, whatever launched it
+    assert ranks() == (0, 1)
 
 
 @pytest.mark.parametrize("uint4", [False, True])
