@@ -113,7 +113,7 @@ def build_selftest(verbose=False):
     cdir = os.path.join(HERE, "core")
     src = os.path.join(HERE, "tests", "runtime_selftest.cc")
     out = os.path.join(OUT, "xft_runtime_selftest")
-    srcs = [os.path.join(cdir, f) for f in ("runtime.cc", "ini.cc", "beam.cc", "env.cc", "arena.cc", "rope_tables.cc", "tokenizer.cc")]
+    srcs = [os.path.join(cdir, f) for f in ("runtime.cc", "ini.cc", "beam.cc", "env.cc", "arena.cc", "rope_tables.cc", "tokenizer.cc", "bpe_tokenizer.cc", "gptq.cc")]
     hdrs = tuple(os.path.join(cdir, f) for f in os.listdir(cdir) if f.endswith(".h"))
     if any(_newer(s, out, hdrs) for s in srcs + [src]):
         _run(["g++", "-O1", "-g", "-std=c++17", "-fsanitize=address,undefined", "-fno-sanitize-recover=undefined",

@@ -1,5 +1,6 @@
 // C ABI over the host-side runtime so that Python (ctypes) and tests can drive the C++ twins of the layout
 // arithmetic, the block allocator and the samplers without a GPU.
+#include <algorithm>
 #include <chrono>
 #include <cstdlib>
 #include <cstring>
@@ -9,6 +10,7 @@
 #include "arena.h"
 #include "comm.h"
 #include "beam.h"
+#include "bpe_tokenizer.h"
 #include "dtypes.h"
 #include "env.h"
 #include "gptq.h"
@@ -118,6 +120,28 @@ double xftc_telechat_ntk_theta(double theta, int rot_dim, int kv_len, int train_
 double xftc_telechat_mscale(int input_len, int train_len) { return telechatMscale(input_len, train_len); }
 double xftc_qwen_ntk_theta(double theta, int rot_dim, int max_kv, int seq_len) { return qwenNtkTheta(theta, rot_dim, max_kv, seq_len); }
 void xftc_alibi_slopes(int n_heads, float* out) { auto v = alibiSlopes(n_heads); std::memcpy(out, v.data(), v.size() * sizeof(float)); }
+
+// ---- byte-level BPE tokenizer (csrc/core/bpe_tokenizer.cc); errors come back as a null handle + message
+static thread_local std::string g_bpeError;
+void* xftc_bpe_load(const char* path) {
+  try { return new BpeTokenizer(path); } catch (const std::exception& e) { g_bpeError = e.what(); return nullptr; }
+}
+const char* xftc_bpe_error() { return g_bpeError.c_str(); }
+void xftc_bpe_free(void* h) { delete static_cast<BpeTokenizer*>(h); }
+int xftc_bpe_vocab_size(void* h) { return static_cast<BpeTokenizer*>(h)->vocabSize(); }
+const char* xftc_bpe_pattern(void* h) { return static_cast<BpeTokenizer*>(h)->pattern(); }
+int xftc_bpe_special_id(void* h, const char* text) { return static_cast<BpeTokenizer*>(h)->specialId(text); }
+int xftc_bpe_encode(void* h, const char* text, int* out, int cap) {
+  auto ids = static_cast<BpeTokenizer*>(h)->encode(text);
+  for (int i = 0; i < (int)ids.size() && i < cap; ++i) out[i] = ids[i];
+  return (int)ids.size();
+}
+int xftc_bpe_decode(void* h, const int* ids, int n, char* out, int cap) {
+  std::string s = static_cast<BpeTokenizer*>(h)->decode(std::vector<int32_t>(ids, ids + n));
+  const int m = std::min((int)s.size(), cap - 1);
+  if (cap > 0) { std::memcpy(out, s.data(), m); out[m] = 0; }
+  return (int)s.size();
+}
 
 // ---- GPTQ tensor repacking (csrc/core/gptq.cc)
 void xftc_gptq_repack(const void* file, int in_f, int out_f, int uint4, int in0, int in1, int out0, int out1, int pitch, void* dst) {

@@ -10,13 +10,16 @@
 #include <fstream>
 #include <numeric>
 #include <set>
+#include <stdexcept>
 #include <string>
 #include <vector>
 
 #include "arena.h"
 #include "beam.h"
+#include "bpe_tokenizer.h"
 #include "dtypes.h"
 #include "env.h"
+#include "gptq.h"
 #include "ini.h"
 #include "rope_tables.h"
 #include "runtime.h"
@@ -336,6 +339,69 @@ static void testDtypes() {
   EXPECT(elemToFloat(reinterpret_cast<const char*>(hs), 2, 1) == 100.0f);
 }
 
+// Byte-level BPE reader: a hand-written tokenizer.json (alphabet a, b, c, space-character and two merges), malformed
+// files that must be refused with an exception, input bytes that are no UTF-8.
+static void testBpeTokenizer(const std::string& dir) {
+  const std::string good = dir + "/bpe_good.json";
+  {
+    std::ofstream f(good);
+    // "\u0120" is the alphabet character of the space byte
+    f << R"({"added_tokens": [{"id": 9, "content": "<|end|>"}],
+             "pre_tokenizer": {"type": "ByteLevel", "add_prefix_space": false, "use_regex": true},
+             "model": {"type": "BPE", "unk_token": null, "ignore_merges": false,
+                       "vocab": {"a": 0, "b": 1, "c": 2, "\u0120": 3, "ab": 4, "\u0120c": 5, "abab": 6, "!": 7, "1": 8},
+                       "merges": ["a b", ["\u0120", "c"], "ab ab"]}})";
+  }
+  BpeTokenizer t(good);
+  EXPECT(t.vocabSize() == 10 && t.specialId("<|end|>") == 9 && t.specialId("nope") == -1 && std::string(t.pattern()) == "gpt2");
+  EXPECT(t.encode("abab c") == std::vector<int32_t>({6, 5}));
+  EXPECT(t.encode("ab<|end|>ba") == std::vector<int32_t>({4, 9, 1, 0}));
+  EXPECT(t.encode("") .empty());
+  EXPECT(t.decode({6, 5, 9, 7}) == "abab c<|end|>!");
+  EXPECT(t.decode({-1, 99}) .empty());
+  // bytes outside the vocabulary (and not even UTF-8) are dropped, never read past the end
+  const std::string junk = std::string("a\xff\xfe") + "\xe4" + "b\xf0\x9f";
+  EXPECT(t.encode(junk) == std::vector<int32_t>({0, 1}));
+  const char* bad[] = {"", "{", "{\"model\": {\"vocab\": {\"a\": 0}, \"merges\": [}}", "{\"model\": \"x\"}",
+                       "{\"a\": \"\\u12\"}", "{\"a\": \"\\q\"}", "[1, 2", "{\"model\": {\"type\": \"WordPiece\", \"vocab\": {}, \"merges\": []}}",
+                       "{\"model\": {\"vocab\": {}, \"merges\": []}}"};
+  int refused = 0;
+  for (const char* text : bad) {
+    const std::string p = dir + "/bpe_bad.json";
+    { std::ofstream f(p); f << text; }
+    try { BpeTokenizer x(p); } catch (const std::runtime_error&) { ++refused; }
+  }
+  EXPECT(refused == (int)(sizeof(bad) / sizeof(bad[0])));
+  std::string deep(200, '[');
+  { std::ofstream f(dir + "/bpe_deep.json"); f << deep; }
+  bool threw = false;
+  try { BpeTokenizer x(dir + "/bpe_deep.json"); } catch (const std::runtime_error&) { threw = true; }
+  EXPECT(threw);
+}
+
+// GPTQ tensors: [in, out] codes -> [out, in] rows (uint4: repacked along `in`), slices, dequantised values, code sums.
+static void testGptq() {
+  const int inF = 6, outF = 4;
+  std::vector<uint8_t> i8(inF * outF);
+  for (int i = 0; i < inF; ++i) for (int o = 0; o < outF; ++o) i8[i * outF + o] = (uint8_t)(int8_t)(i * 10 + o - 20);
+  std::vector<uint8_t> rows(outF * 16, 0xAA);
+  gptqRepack(i8.data(), inF, outF, false, 0, inF, 0, outF, 16, rows.data());
+  EXPECT((int8_t)rows[2 * 16 + 5] == 5 * 10 + 2 - 20 && rows[2 * 16 + 6] == 0 && rows[15] == 0);
+  std::vector<uint8_t> u4(inF * outF / 2);
+  auto code = [](int i, int o) { return (i * 3 + o * 5) & 15; };
+  for (int i = 0; i < inF; ++i) for (int o = 0; o < outF; o += 2) u4[i * (outF / 2) + o / 2] = (uint8_t)(code(i, o) | (code(i, o + 1) << 4));
+  std::vector<uint8_t> r4(2 * 16, 0xAA);
+  gptqRepack(u4.data(), inF, outF, true, 2, 6, 1, 3, 16, r4.data());          // inputs 2..5 of outputs 1..2
+  EXPECT(r4[0] == (uint8_t)(code(2, 1) | (code(3, 1) << 4)) && r4[16 + 1] == (uint8_t)(code(4, 2) | (code(5, 2) << 4)) && r4[2] == 0);
+  const float sc[4] = {0.5f, 1.0f, 2.0f, 4.0f}, zp[4] = {0.f, -1.f, 1.f, 0.25f};
+  std::vector<float> deq(2 * 4);
+  gptqDequant(u4.data(), inF, outF, true, 2, 6, 1, 3, sc, zp, deq.data());
+  EXPECT(deq[0] == code(2, 1) * 1.0f - 1.f && deq[4 + 3] == code(5, 2) * 2.0f + 1.f);
+  float sums[2];
+  gptqRowSums(u4.data(), inF, outF, true, 2, 6, 1, 3, sums);
+  EXPECT(sums[0] == (float)(code(2, 1) + code(3, 1) + code(4, 1) + code(5, 1)));
+}
+
 int main(int argc, char** argv) {
   const std::string dir = argc > 1 ? argv[1] : "/tmp";
   testPartition();
@@ -348,6 +414,8 @@ int main(int argc, char** argv) {
   testArena();
   testRopeTables();
   testDtypes();
+  testBpeTokenizer(dir);
+  testGptq();
   std::printf("runtime_selftest: %d checks, %d failed\n", g_checks, g_failed);
   return g_failed ? 1 : 0;
 }

@@ -1,16 +1,18 @@
 // Command-line generation with the C++ API (reference: examples/cpp/example.cpp:352-545).
 //
-//   example -m <model dir> [-t <tokenizer.model>] [-d bf16|fp16|int8|w8a8|int4|nf4|bf16_int8|...] [--kv_cache_dtype fp16|int8] [-i "1 2 3 4"] [-l input_len]
-//           [-o out_len] [--prefix_len n] [-n num_beams] [-b batch] [--loop n] [--topK k] [--topP p]
-//           [--temperature t] [--repetPen r] [--do_sample] [--no_stream]
+//   example -m <model dir> [-t <tokenizer.model | tokenizer.json | dir>] [--bos id] [-d bf16|fp16|int8|w8a8|int4|nf4|bf16_int8|...]
+//           [--kv_cache_dtype fp16|int8] [-i "1 2 3 4"] [-l input_len] [-o out_len] [--prefix_len n] [-n num_beams]
+//           [-b batch] [--loop n] [--topK k] [--topP p] [--temperature t] [--repetPen r] [--do_sample] [--no_stream]
 // Same flag names as the reference.  -l pads the prompt to `input_len` tokens by repeating its third token (the
 // reference's way of making a long prompt for timing); --prefix_len shares the first n prompt tokens between the rows
-// of the batch through Model::setPrefix (whole 64-token blocks).  With -t (a SentencePiece model file: Llama, Mistral,
-// Gemma, Yi, Baichuan, ChatGLM families) -i may be TEXT: it is tokenised by the built-in reader (csrc/core/tokenizer.h,
-// BOS prepended) and the generated ids are printed as text too; without -t, or when -i holds only numbers, -i is a list of
-// token ids.  Prints the generated ids / text, first-token latency and average next-token latency (the reference's
-// metrics).  Started as several processes (mpirun -n N, or torchrun) the dense families run tensor-parallel, one GPU per
-// process; rank 0's flags decide and rank 0 prints.
+// of the batch through Model::setPrefix (whole 64-token blocks).  With -t, -i may be TEXT: it is tokenised by a
+// built-in reader and the generated ids are printed as text too.  -t takes a SentencePiece model file (*.model: Llama,
+// Mistral, Gemma, Yi, Baichuan, ChatGLM families; csrc/core/tokenizer.h, BOS prepended), or a tokenizer.json or the
+// directory that holds it (byte-level BPE: OPT, Qwen, Llama-3, ...; csrc/core/bpe_tokenizer.h; `--bos id` prepends a
+// token, e.g. 2 for OPT).  Without -t, or when -i holds only numbers, -i is a list of token ids.  Prints the generated
+// ids / text, first-token latency and average next-token latency (the reference's metrics).  Started as several
+// processes (mpirun -n N, or torchrun) the dense families run tensor-parallel, one GPU per process; rank 0's flags
+// decide and rank 0 prints.
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
@@ -21,12 +23,13 @@
 #include <string>
 #include <vector>
 
+#include "bpe_tokenizer.h"
 #include "tokenizer.h"
 #include "xft/models.h"
 
 int main(int argc, char** argv) {
   std::string model, dtype = "bf16", kv = "fp16", input = "1 15043 29892 920 526 366 29973", tokenPath;
-  int batch = 1, outLen = 32, loop = 1, topK = 50, numBeams = 1, inputLen = -1, prefixLen = 0;
+  int batch = 1, outLen = 32, loop = 1, topK = 50, numBeams = 1, inputLen = -1, prefixLen = 0, bosId = -1;
   float topP = 1.0f, temp = 1.0f, rep = 1.0f;
   bool sample = false, stream = true;
   for (int i = 1; i < argc; ++i) {
@@ -42,6 +45,7 @@ int main(int argc, char** argv) {
     else if (a == "-l" || a == "--input_len") inputLen = std::atoi(next().c_str());
     else if (a == "--prefix_len") prefixLen = std::atoi(next().c_str());
     else if (a == "-t" || a == "--token") tokenPath = next();
+    else if (a == "--bos") bosId = std::atoi(next().c_str());
     else if (a == "--topK") topK = std::atoi(next().c_str());
     else if (a == "-n" || a == "--num_beams") numBeams = std::atoi(next().c_str());
     else if (a == "--topP") topP = (float)std::atof(next().c_str());
@@ -53,22 +57,31 @@ int main(int argc, char** argv) {
   }
   if (model.empty()) { std::fprintf(stderr, "usage: example -m <model dir> [options]\n"); return 2; }
   std::vector<int32_t> prompt;
+  // -t: a SentencePiece model file (*.model), or a tokenizer.json / a directory with one (byte-level BPE)
   std::unique_ptr<xft::SentencePieceTokenizer> tok;
+  std::unique_ptr<xft::BpeTokenizer> bpe;
   const bool numeric = input.find_first_not_of("0123456789 \t") == std::string::npos;
   try {
-    if (!tokenPath.empty()) tok.reset(new xft::SentencePieceTokenizer(tokenPath));
+    if (!tokenPath.empty()) {
+      const bool spm = tokenPath.size() > 6 && tokenPath.compare(tokenPath.size() - 6, 6, ".model") == 0;
+      if (spm) tok.reset(new xft::SentencePieceTokenizer(tokenPath));
+      else bpe.reset(new xft::BpeTokenizer(tokenPath));
+    }
   } catch (const std::exception& e) {
     std::fprintf(stderr, "error: %s\n", e.what());
     return 1;
   }
   if (tok && !numeric) {
     prompt = tok->encode(input, /*addBos=*/true);
+  } else if (bpe && !numeric) {
+    prompt = bpe->encode(input);
+    if (bosId >= 0) prompt.insert(prompt.begin(), bosId);       // these tokenizers add no BOS by themselves
   } else {
     std::istringstream is(input);
     int v;
     while (is >> v) prompt.push_back(v);
   }
-  if (prompt.empty()) { std::fprintf(stderr, "-i takes token ids separated by spaces (or text, with -t <tokenizer.model>)\n"); return 2; }
+  if (prompt.empty()) { std::fprintf(stderr, "-i takes token ids separated by spaces (or text, with -t <tokenizer.model | tokenizer.json>)\n"); return 2; }
   if (inputLen > (int)prompt.size()) {
     const size_t at = prompt.size() > 2 ? 2 : prompt.size() - 1;
     prompt.insert(prompt.begin() + at, inputLen - prompt.size(), prompt[at]);
@@ -113,6 +126,10 @@ int main(int argc, char** argv) {
         std::printf("[%d] ", b);
         for (size_t i = prompt.size(); i < w; ++i) std::printf("%d ", out[b * w + i]);
         std::printf("\n");
+        if (bpe) {
+          std::vector<int32_t> gen(out.begin() + b * w + prompt.size(), out.begin() + (b + 1) * w);
+          std::printf("[%d] %s\n", b, bpe->decode(gen).c_str());
+        }
         if (tok) {
           std::vector<int32_t> gen(out.begin() + b * w + prompt.size(), out.begin() + (b + 1) * w);
           std::printf("[%d] %s\n", b, tok->decode(gen).c_str());

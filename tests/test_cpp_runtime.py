@@ -719,3 +719,91 @@ def test_process_rank_communicator_with_a_stand_in_nccl(tmp_path):
     lone = subprocess.run([exe, "process", "1", "2", str(tmp_path / "never")], env=dict(env, XFT_DIST_TIMEOUT_S="1"),
                           capture_output=True, text=True, timeout=60)
     assert lone.returncode == 1 and "did not arrive" in lone.stdout
+
+
+_BPE_CORPUS = [
+    "The quick brown fox jumps over the lazy dog. It's 2024, isn't it? We'll see; they've gone, I'm here, he'd say.",
+    "def tokenize(text: str) -> list[int]:\n    return [ord(c) for c in text]  # 123456 items, 3.14159 pi\n\n\n",
+    "Prices: $1,234.56 (approx.)   spaced    out\ttabs\there \n new lines \r\n and more... END!!! ???",
+    "naïve café déjà vu — über straße; 你好世界 这是一个测试 こんにちは 안녕하세요 Привет мир",
+    "email@example.com http://example.org/path?q=1&r=2 #hashtag @user 100% 50/50 a_b_c x-y-z",
+    "I'M SHOUTING, YOU'RE NOT. WE'VE 12345678 numbers 007 and 42nd Street's 'quoted' words",
+]
+
+
+def _train_bpe(tmp_path, style):
+    """A byte-level BPE tokenizer.json made with the `tokenizers` library: GPT-2 pre-tokenizer, or the regex split of
+    Llama-3 / Qwen2 in front of a plain byte-level mapping."""
+    from tokenizers import Regex, Tokenizer, decoders, models, pre_tokenizers, trainers
+    tok = Tokenizer(models.BPE())
+    if style == "gpt2":
+        tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=True)
+    else:
+        digits = r"\p{N}{1,3}" if style == "llama3" else r"\p{N}"
+        pat = (r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|" + digits +
+               r"| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+")
+        tok.pre_tokenizer = pre_tokenizers.Sequence([pre_tokenizers.Split(Regex(pat), behavior="isolated"),
+                                                     pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False)])
+    tok.decoder = decoders.ByteLevel()
+    trainer = trainers.BpeTrainer(vocab_size=600, special_tokens=["<|endoftext|>", "<|im_start|>"],
+                                  initial_alphabet=pre_tokenizers.ByteLevel.alphabet(), show_progress=False)
+    tok.train_from_iterator(_BPE_CORPUS * 3, trainer)
+    path = str(tmp_path / f"{style}.json")
+    tok.save(path)
+    return tok, path
+
+
+@pytest.mark.parametrize("style", ["gpt2", "llama3", "qwen2"])
+def test_bpe_tokenizer_matches_the_tokenizers_library(core, style, tmp_path):
+    """csrc/core/bpe_tokenizer.cc (tokenizer.json reader, pre-tokenizer patterns, byte-level BPE) against the Hugging
+    Face `tokenizers` library on the same file: ids of ASCII, accented, CJK / Hangul / Cyrillic text, code, numbers,
+    contractions in both cases, runs of spaces / tabs / newlines, added tokens in the text; decoding round-trips."""
+    tok, path = _train_bpe(tmp_path, style)
+    core.xftc_bpe_load.restype = C.c_void_p
+    core.xftc_bpe_pattern.restype = C.c_char_p
+    core.xftc_bpe_error.restype = C.c_char_p
+    h = core.xftc_bpe_load(path.encode())
+    assert h, core.xftc_bpe_error()
+    h = C.c_void_p(h)
+    try:
+        assert core.xftc_bpe_pattern(h).decode() == style
+        assert core.xftc_bpe_vocab_size(h) == tok.get_vocab_size()
+        assert core.xftc_bpe_special_id(h, b"<|im_start|>") == tok.token_to_id("<|im_start|>")
+        texts = _BPE_CORPUS + ["", " ", "  leading and trailing  ", "a", "\n", "x\n\n  y", "tab\t\tsep", "it'S Don'T we'Re",
+                               "<|im_start|>user\nhello<|endoftext|>", "12 345 6789012", "mixed123abc456", "...!!!\n\nnext"]
+        for t in texts:
+            want = tok.encode(t).ids
+            buf = (C.c_int * 4096)()
+            n = core.xftc_bpe_encode(h, t.encode(), buf, 4096)
+            got = list(buf[:n])
+            assert got == want, (style, t, got, want)
+            out = C.create_string_buffer(8192)
+            core.xftc_bpe_decode(h, (C.c_int * n)(*got), n, out, 8192)
+            assert out.value.decode() == t, (style, t)
+    finally:
+        core.xftc_bpe_free(h)
+    assert not core.xftc_bpe_load(str(tmp_path / "missing.json").encode())
+    assert b"cannot open tokenizer" in core.xftc_bpe_error()
+    if style == "gpt2":
+        # the older pair of files (vocab.json + merges.txt) in a directory gives the same ids
+        d = tmp_path / "pair"
+        d.mkdir()
+        tok.model.save(str(d))
+        h2 = C.c_void_p(core.xftc_bpe_load(str(d).encode()))
+        assert h2.value, core.xftc_bpe_error()
+        for t in _BPE_CORPUS:
+            buf = (C.c_int * 4096)()
+            n = core.xftc_bpe_encode(h2, t.encode(), buf, 4096)
+            assert list(buf[:n]) == tok.encode(t).ids
+        core.xftc_bpe_free(h2)
+        # the example CLI takes the file for -t: text is tokenised before the model is opened
+        import subprocess
+        exe = os.path.join(os.path.dirname(LIB), "xft_example")
+        if os.path.exists(exe):
+            r = subprocess.run([exe, "-m", "/nonexistent", "-t", path, "-i", "The quick brown fox", "--bos", "2"],
+                               capture_output=True, text=True, timeout=60)
+            assert r.returncode == 1 and "config.ini" in r.stderr          # got past the tokenizer, failed at the model
+            (tmp_path / "bad.json").write_text("{\"model\": {\"type\": \"Unigram\"}}")
+            r = subprocess.run([exe, "-m", "/nonexistent", "-t", str(tmp_path / "bad.json"), "-i", "hi"],
+                               capture_output=True, text=True, timeout=60)
+            assert r.returncode == 1 and "not a BPE tokenizer.json" in r.stderr
