@@ -6,8 +6,8 @@
 
 namespace xft {
 
-void BeamHypotheses::add(const std::vector<int32_t>& hyp, double sumLogprobs, int genLen) {
-  const double score = sumLogprobs / std::pow((double)std::max(genLen, 1), (double)lengthPenalty_);
+void BeamHypotheses::add(const std::vector<int32_t>& hyp, double sumLogprobs, int length) {
+  const double score = sumLogprobs / std::pow((double)std::max(length, 1), (double)lengthPenalty_);
   if ((int)beams_.size() < numBeams_ || score > worst_) {
     beams_.emplace_back(score, hyp);
     if ((int)beams_.size() > numBeams_) {
@@ -43,7 +43,7 @@ void BeamSearchScorer::process(const float* logprobs, int vocab, std::vector<int
   nextTokens.assign((size_t)bs_ * nb, pad_ >= 0 ? pad_ : 0);
   srcBeam.assign((size_t)bs_ * nb, 0);
   std::vector<double> nextScores((size_t)bs_ * nb, 0.0);
-  const int curLen = (int)seqs_[0].size() + 1;
+  const int gen = (int)seqs_[0].size();              // tokens every open beam has generated so far
   std::vector<std::pair<double, long long>> cand;
   for (int b = 0; b < bs_; ++b) {
     if (done_[b]) {
@@ -53,6 +53,7 @@ void BeamSearchScorer::process(const float* logprobs, int vocab, std::vector<int
       }
       continue;
     }
+    const int curLen = promptLen(b) + gen;             // the reference ranks by the length of the whole row of ids
     // top 2 * beams of (beam score + log-prob) over beams x vocab; ties go to the lower flat index, as torch.topk
     cand.clear();
     cand.reserve((size_t)nb * vocab);
@@ -99,7 +100,7 @@ std::vector<std::vector<int32_t>> BeamSearchScorer::finalize(const std::vector<s
     if (!done_[b] || (int)hyps_[b].beams().size() < nret_)
       for (int j = 0; j < nb_; ++j) {
         const auto& s = seqs_[(size_t)b * nb_ + j];
-        hyps_[b].add(s, scores_[(size_t)b * nb_ + j], (int)s.size());
+        hyps_[b].add(s, scores_[(size_t)b * nb_ + j], promptLen(b) + (int)s.size());
       }
     auto best = hyps_[b].beams();
     std::stable_sort(best.begin(), best.end(), [](const auto& a, const auto& c) { return a.first > c.first; });

@@ -13,7 +13,8 @@ class BeamHypotheses {
 public:
   BeamHypotheses(int numBeams, float lengthPenalty, bool earlyStopping)
       : numBeams_(numBeams), lengthPenalty_(lengthPenalty), earlyStopping_(earlyStopping) {}
-  void add(const std::vector<int32_t>& hyp, double sumLogprobs, int genLen);
+  // score = sumLogprobs / length ^ lengthPenalty
+  void add(const std::vector<int32_t>& hyp, double sumLogprobs, int length);
   bool isDone(double bestSumLogprobs, int curLen) const;
   const std::vector<std::pair<double, std::vector<int32_t>>>& beams() const { return beams_; }
 private:
@@ -29,6 +30,10 @@ public:
   BeamSearchScorer(int batch, int numBeams, float lengthPenalty, bool earlyStopping, int eosId, int padId,
                    int numReturn);
   bool isDone() const;
+  // Prompt length of every request (default 0).  As in the reference (src/searchers/beam_search.cpp:87-112,137-194, where
+  // a hypothesis is the whole row of input ids), the length that normalises a hypothesis' score is prompt + tokens
+  // generated before the closing one.
+  void setPromptLens(const std::vector<int>& lens) { promptLens_ = lens; }
   // logprobs: [batch * beams, vocab] (log-softmax of this step).  Outputs have batch * beams entries; srcBeam holds
   // flat indices into the previous step's beams.
   void process(const float* logprobs, int vocab, std::vector<int32_t>& nextTokens, std::vector<int>& srcBeam);
@@ -36,7 +41,9 @@ public:
   std::vector<std::vector<int32_t>> finalize(const std::vector<std::vector<int32_t>>& prompts, int maxLength);
   const std::vector<double>& beamScores() const { return scores_; }
 private:
+  int promptLen(int b) const { return b < (int)promptLens_.size() ? promptLens_[b] : 0; }
   int bs_, nb_, eos_, pad_, nret_;
+  std::vector<int> promptLens_;
   std::vector<BeamHypotheses> hyps_;
   std::vector<char> done_;
   std::vector<double> scores_;                       // [batch * beams]

@@ -78,6 +78,9 @@ void xftc_repetition_penalty(float* l, int n, const int* toks, int nt, float pen
 void* xftc_beam_new(int batch, int beams, float lenPenalty, int earlyStopping, int eos, int pad, int nret) {
   return new BeamSearchScorer(batch, beams, lenPenalty, earlyStopping != 0, eos, pad, nret);
 }
+void xftc_beam_set_prompt_lens(void* s, const int* lens, int n) {
+  static_cast<BeamSearchScorer*>(s)->setPromptLens(std::vector<int>(lens, lens + n));
+}
 void xftc_beam_delete(void* s) { delete static_cast<BeamSearchScorer*>(s); }
 int xftc_beam_done(void* s) { return static_cast<BeamSearchScorer*>(s)->isDone() ? 1 : 0; }
 void xftc_beam_process(void* s, const float* logprobs, int vocab, int32_t* tokens, int* src, int n) {

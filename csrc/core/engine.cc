@@ -1294,6 +1294,9 @@ std::vector<int32_t> beamStep(Engine& e, const SearcherConfig& c) {
       }
     }
     e.scorer.reset(new BeamSearchScorer(bs, nb, c.lenPenalty, c.doEarlyStopping, c.eosTokenId, c.padTokenId, c.numBeamHypsToKeep));
+    std::vector<int> promptLens;
+    for (int id : e.working) promptLens.push_back((int)e.pool.get(id).prompt.size());
+    e.scorer->setPromptLens(promptLens);
   } else {
     e.forward(e.beamSeqs, false);
     for (int i = 0; i < bs * nb; ++i) {

@@ -247,8 +247,10 @@ def test_cpp_beam_scorer_matches_python(core, early, lp, eos):
     bs, nb, V, steps, P = 3, 4, 23, 9, 5
     cfg = SamplingMeta(max_length=P + steps, num_beams=nb, num_return_sequences=2, length_penalty=lp, early_stopping=early,
                        eos_token_id=eos, pad_token_id=0)
-    py = BeamSearchScorer(bs, cfg, P)
+    plens = [P, P + 7, P + 2]                                   # the length that normalises scores includes the prompt
+    py = BeamSearchScorer(bs, cfg, plens)
     cc = c.xftc_beam_new(bs, nb, lp, int(early), eos, 0, 2)
+    c.xftc_beam_set_prompt_lens(ctypes.c_void_p(cc), (ctypes.c_int * bs)(*plens), bs)
     g = torch.Generator().manual_seed(int(lp * 10) + eos + 5)
     for step in range(steps):
         lp_t = torch.log_softmax(torch.randn(bs * nb, V, generator=g) * 2.0, -1).contiguous()

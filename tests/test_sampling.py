@@ -132,3 +132,39 @@ def test_gpu_beam_topk_matches_reference():
     gv, gi = native_sample.beam_topk(strided, 6)
     wv, wi = R.beam_topk(strided.cpu(), 6)
     assert gi.cpu().tolist() == wi.tolist()
+
+
+def test_beam_hypotheses_are_normalised_by_prompt_plus_generated_length():
+    """The reference scores a finished hypothesis as sum of log-probabilities / (length of the whole row of ids) **
+    length_penalty, the row being prompt + tokens generated before the closing one (src/searchers/beam_search.cpp:87-112,
+    161-171).  With a long prompt the normalisation barely changes between a short and a long continuation, so the short
+    one with the better sum wins; with no prompt the long one does."""
+    from xfastertransformer_b200.runtime.sampler import BeamSearchScorer
+    from xfastertransformer_b200.runtime.sequence import SamplingMeta
+    V, eos = 6, 1
+    cfg = SamplingMeta(num_beams=2, max_length=64, eos_token_id=eos, pad_token_id=0, length_penalty=1.0, early_stopping=False)
+
+    def run(prompt_len):
+        sc = BeamSearchScorer(1, cfg, prompt_len)
+        neg = -30.0
+        # step 1: beam 0 may stop (eos at -1.0) or go on with token 2 (-1.2); token 3 (-1.4) keeps a second beam alive
+        lp = torch.full((2, V), neg)
+        lp[0, eos], lp[0, 2], lp[0, 3] = -1.0, -1.2, -1.4
+        sc.process(lp)
+        # steps 2, 3: cheap continuations (token 4 at -0.1) for both beams, then the first beam closes cheaply
+        for _ in range(2):
+            lp = torch.full((2, V), neg)
+            lp[:, 4] = -0.1
+            sc.process(lp)
+        lp = torch.full((2, V), neg)
+        lp[0, eos], lp[0, 4], lp[1, 4] = -0.1, -5.0, -0.2
+        sc.process(lp)
+        return sc.hyps[0].beams
+
+    short_first = sorted(run(100), key=lambda x: -x[0])
+    long_first = sorted(run(0), key=lambda x: -x[0])
+    # hypotheses: short = [eos] with sum -1.0, long = [2, 4, 4, eos] with sum -1.5
+    assert short_first[0][1] == [eos] and abs(short_first[0][0] - (-1.0 / 100)) < 1e-6
+    assert abs(short_first[1][0] - (-1.5 / 103)) < 1e-6
+    assert long_first[0][1] == [2, 4, 4, eos] and abs(long_first[0][0] - (-1.5 / 3)) < 1e-6
+    assert abs(long_first[1][0] - (-1.0 / 1)) < 1e-6

@@ -422,7 +422,7 @@ class Model:
                     self.cache.fork(s.seq_id, c.seq_id)
                     beams.append(c)
             self.working = beams
-            self.scorer = S.BeamSearchScorer(len(reqs), cfg, 0)
+            self.scorer = S.BeamSearchScorer(len(reqs), cfg, [len(s.prompt) for s in reqs])
             full = full.repeat_interleave(nb, 0)
             self._beam_pending = False
         else:

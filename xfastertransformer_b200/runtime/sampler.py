@@ -93,8 +93,8 @@ class BeamHypotheses:
         self.beams: List[Tuple[float, List[int]]] = []
         self.worst = 1e9
 
-    def add(self, hyp: List[int], sum_logprobs: float, gen_len: int) -> None:
-        score = sum_logprobs / (max(gen_len, 1) ** self.length_penalty)
+    def add(self, hyp: List[int], sum_logprobs: float, length: int) -> None:
+        score = sum_logprobs / (max(length, 1) ** self.length_penalty)
         if len(self.beams) < self.num_beams or score > self.worst:
             self.beams.append((score, hyp))
             if len(self.beams) > self.num_beams:
@@ -119,10 +119,14 @@ class BeamSearchScorer:
     """Per-request beam bookkeeping.  `process` consumes the top 2*num_beams candidates of each
     request and returns the next (scores, tokens, source-beam indices)."""
 
-    def __init__(self, batch: int, cfg: SamplingMeta, prompt_len: int):
+    def __init__(self, batch: int, cfg: SamplingMeta, prompt_len=0):
+        """`prompt_len`: one length or one per request.  Hypotheses are ranked by sum of log-probabilities divided by
+        length ** length_penalty where, as in the reference (src/searchers/beam_search.cpp:87-112,137-194: the hypothesis
+        is the whole row of input ids), the length is prompt + tokens generated before the closing one."""
         self.bs, self.nb = batch, cfg.num_beams
         self.cfg = cfg
-        self.prompt_len = prompt_len
+        self.prompt_lens = [int(prompt_len)] * batch if isinstance(prompt_len, int) else [int(x) for x in prompt_len]
+        assert len(self.prompt_lens) == batch
         self.hyps = [BeamHypotheses(cfg.num_beams, cfg.length_penalty, cfg.early_stopping) for _ in range(batch)]
         self.done = [False] * batch
         self.beam_scores = torch.zeros(batch, cfg.num_beams)
@@ -158,7 +162,7 @@ class BeamSearchScorer:
         """top_s, src_beam, tok: [bs, <= 2*nb] candidates of every request, best first."""
         bs, nb = self.bs, self.nb
         eos, pad = self.cfg.eos_token_id, self.cfg.pad_token_id
-        cur_len = len(self.seqs[0]) + 1
+        gen = len(self.seqs[0])                        # tokens every open beam has generated so far
         next_tokens = torch.full((bs, nb), pad if pad >= 0 else 0, dtype=torch.long)
         next_src = torch.zeros(bs, nb, dtype=torch.long)
         next_scores = torch.zeros(bs, nb)
@@ -168,6 +172,7 @@ class BeamSearchScorer:
                 next_scores[b] = self.beam_scores[b]
                 continue
             k = 0
+            cur_len = self.prompt_lens[b] + gen
             for rank in range(top_s.shape[1]):
                 t, s, sb = int(tok[b, rank]), float(top_s[b, rank]), int(src_beam[b, rank])
                 if t == eos and eos >= 0:
@@ -197,7 +202,8 @@ class BeamSearchScorer:
         for b in range(bs):
             if not self.done[b] or len(self.hyps[b].beams) < nret:
                 for j in range(nb):
-                    self.hyps[b].add(self.seqs[b * nb + j], float(self.beam_scores[b, j]), len(self.seqs[b * nb + j]))
+                    self.hyps[b].add(self.seqs[b * nb + j], float(self.beam_scores[b, j]),
+                                     self.prompt_lens[b] + len(self.seqs[b * nb + j]))
             best = sorted(self.hyps[b].beams, key=lambda x: x[0], reverse=True)[:nret]
             for _, h in best:
                 out.append(prompts[b] + h)
