@@ -9,6 +9,7 @@
 #include <chrono>
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <fstream>
 #include <map>
@@ -62,7 +63,11 @@ struct DevBuf {
       if (!p) throw std::runtime_error("out of device memory allocating " + std::to_string(n) + " bytes");
     }
   }
-  void ensure(size_t n) { if (n > bytes) reset(n + n / 4); }
+  void ensure(size_t n) {
+    // grows with a quarter of slack, except under XFT_ARENA_EXACT (see arena.cc)
+    static const bool exact = [] { const char* v = std::getenv("XFT_ARENA_EXACT"); return v && *v && *v != '0'; }();
+    if (n > bytes) reset(exact ? n : n + n / 4);
+  }
   template <class T> T* as() const { return static_cast<T*>(p); }
 };
 

@@ -1,0 +1,168 @@
+// Drives the C++ engine through its whole public API over the host stand-in of the device library
+// (csrc/tests/mock_device.cc), without a GPU: every request shape the engine knows — batch generation with greedy
+// search, sampling and beams, continuous batching with ragged prompts that cross KV block borders, a sequence joining
+// and leaving, prefix sharing, all-position logits — for one model directory, weight type and KV type, on one rank or
+// on N thread ranks (tensor parallel).  The numbers are meaningless; what is checked is that the host side asks the
+// device library for memory it owns (AddressSanitizer + exact-size buffers), keeps its bookkeeping consistent, and
+// that ranks agree.
+//
+//   engine_hostcheck <model dir> <weight type> <kv type> <ranks>
+#include <cstdio>
+#include <cstdlib>
+#include <stdexcept>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "comm.h"
+#include "xft/models.h"
+
+namespace {
+
+#define CHECK(cond)                                                                                         \
+  do {                                                                                                      \
+    if (!(cond)) throw std::runtime_error(std::string("check failed: " #cond " (line ") + std::to_string(__LINE__) + ")"); \
+  } while (0)
+
+std::vector<int32_t> promptOf(int len, int vocab, int salt) {
+  std::vector<int32_t> p(len);
+  for (int i = 0; i < len; ++i) p[i] = 3 + (i * 7 + salt * 13) % (vocab - 3);
+  return p;
+}
+
+// everything one rank does; every rank of a tensor-parallel group makes the same calls
+std::vector<int32_t> exercise(xft::Model& m, bool experts) {
+  const int V = m.getVocabSize();
+  CHECK(V > 8 && m.getMaxSeqLen() >= 128);
+  std::vector<int32_t> trace;
+  // 1. batch generation, greedy: two equal-length prompts
+  {
+    const int P = 9, B = 2;
+    std::vector<int32_t> ids;
+    for (int b = 0; b < B; ++b) { auto p = promptOf(P, V, b); ids.insert(ids.end(), p.begin(), p.end()); }
+    m.config(P + 4, 1, 1, 1.0f, false, V + 5 /* never produced */, 0);
+    m.input(ids, B);
+    int steps = 0;
+    while (!m.isDone()) { auto next = m.generate(); CHECK((int)next.size() == B); ++steps; }
+    CHECK(steps == 4);
+    auto out = m.finalize();
+    CHECK((int)out.size() == B * (P + 4));
+    for (int b = 0; b < B; ++b) for (int i = 0; i < P; ++i) CHECK(out[b * (P + 4) + i] == ids[b * P + i]);
+    trace.insert(trace.end(), out.begin(), out.end());
+  }
+  // 2. sampling with a fixed seed and a repetition penalty
+  {
+    SearcherConfig c(14, 1, 1, 1.0f, false, V + 5, 0, true, 0.8f, 5, 0.9f, 1.2f);
+    c.seed = 1234;
+    std::vector<std::vector<int32_t>> prompts = {promptOf(6, V, 2), promptOf(11, V, 3)};       // ragged
+    m.set_input(prompts, c);
+    while (!m.isDone()) m.generate();
+    auto out = m.finalize();
+    CHECK(out.size() == 2 * 14);
+    trace.insert(trace.end(), out.begin(), out.end());
+  }
+  // 3. beam search, three beams, prompts that fill a KV block exactly and spill into the next one
+  {
+    const int P = 64, B = 2, nb = 3;
+    std::vector<int32_t> ids;
+    for (int b = 0; b < B; ++b) { auto p = promptOf(P, V, 4 + b); ids.insert(ids.end(), p.begin(), p.end()); }
+    m.config(P + 5, nb, 2, 1.0f, false, 1 /* eos may well appear */, 0);
+    m.input(ids, B);
+    int steps = 0;
+    while (!m.isDone() && steps < 8) { auto next = m.generate(); CHECK((int)next.size() == B * nb); ++steps; }
+    auto out = m.finalize();
+    CHECK(!out.empty() && out.size() % (B * 2) == 0);
+    trace.insert(trace.end(), out.begin(), out.end());
+  }
+  // 4. continuous batching: ragged prompts (one crosses a block border), decode, a third sequence joins, one leaves
+  {
+    std::vector<std::vector<int32_t>> prompts = {promptOf(5, V, 6), promptOf(70, V, 7)};
+    std::vector<int> ids = m.set_input(prompts, std::vector<int>{}, 100);
+    CHECK(ids.size() == 2);
+    auto r = m.forward(false);
+    CHECK(std::get<1>(r) == 2 && std::get<2>(r) == V);
+    for (int step = 0; step < 3; ++step) {
+      std::vector<std::vector<int32_t>> next = {{4 + step}, {5 + step}};
+      m.set_input(next, ids, 100);
+      r = m.forward(false);
+      CHECK(std::get<1>(r) == 2);
+    }
+    std::vector<std::vector<int32_t>> late = {promptOf(130, V, 8)};                              // three blocks
+    std::vector<int> id3 = m.set_input(late, std::vector<int>{}, 140);
+    r = m.forward(true);                                                                        // every position
+    CHECK(std::get<1>(r) == 130);
+    std::vector<int> first = {ids[0]};
+    CHECK(m.freeSeqs(first));
+    std::vector<int> both = {ids[1], id3[0]};
+    std::vector<std::vector<int32_t>> next = {{9}, {10}};
+    m.set_input(next, both, 140);
+    r = m.forward(false);
+    CHECK(std::get<1>(r) == 2);
+    const float* lg = std::get<0>(r);
+    for (int i = 0; i < 2 * V; ++i) CHECK(lg[i] == lg[i]);                                      // no NaN
+    trace.push_back((int32_t)(lg[3] * 1000));
+    CHECK(m.freeSeqs(both));
+  }
+  // 5. prefix sharing: 64 shared tokens (one whole block), two requests behind it
+  if (!experts) {
+    auto shared = promptOf(64, V, 9);
+    m.setPrefix(shared);
+    std::vector<int32_t> ids;
+    for (int b = 0; b < 2; ++b) { auto p = shared; auto tail = promptOf(6, V, 10 + b); p.insert(p.end(), tail.begin(), tail.end()); ids.insert(ids.end(), p.begin(), p.end()); }
+    m.config(70 + 3, 1, 1, 1.0f, false, V + 5, 0);
+    m.input(ids, 2);
+    while (!m.isDone()) m.generate();
+    auto out = m.finalize();
+    CHECK(out.size() == 2 * 73);
+    m.unsetPrefix();
+    trace.insert(trace.end(), out.begin(), out.end());
+  }
+  return trace;
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+  if (argc < 5) { std::fprintf(stderr, "usage: engine_hostcheck <model dir> <weight type> <kv type> <ranks>\n"); return 2; }
+  const std::string dir = argv[1];
+  const xft::DataType wdt = xft::dataTypeFromName(argv[2]);
+  const xft::DataType kdt = std::string(argv[3]) == "int8" ? xft::DataType::int8 : xft::DataType::fp16;
+  const int ranks = std::atoi(argv[4]);
+  const bool experts = dir.find("moe") != std::string::npos || dir.find("mixtral") != std::string::npos;
+  if (wdt == xft::DataType::unknown || ranks < 1 || ranks > 8) { std::fprintf(stderr, "bad arguments\n"); return 2; }
+  try {
+    if (ranks == 1) {
+      xft::AutoModel m(dir, wdt, kdt, nullptr);
+      CHECK(m.isMaster() && m.getRank() == 0 && m.getWorldSize() == 1);
+      auto t = exercise(m, experts);
+      std::printf("hostcheck ok: %zu values\n", t.size());
+      return 0;
+    }
+    auto comms = xft::makeThreadCommunicators(ranks);
+    std::vector<std::vector<int32_t>> traces(ranks);
+    std::vector<std::string> errors(ranks);
+    std::vector<std::thread> threads;
+    for (int r = 0; r < ranks; ++r)
+      threads.emplace_back([&, r] {
+        try {
+          comms[r]->begin();
+          xft::AutoModel m(dir, wdt, kdt, comms[r]);
+          if (m.getRank() != r || m.getWorldSize() != ranks || m.isMaster() != (r == 0)) throw std::runtime_error("rank bookkeeping");
+          traces[r] = exercise(m, experts);
+        } catch (const std::exception& e) {
+          errors[r] = e.what();
+        }
+        comms[r]->end();
+      });
+    for (auto& t : threads) t.join();
+    for (int r = 0; r < ranks; ++r)
+      if (!errors[r].empty()) { std::fprintf(stderr, "rank %d: %s\n", r, errors[r].c_str()); return 1; }
+    for (int r = 1; r < ranks; ++r)
+      if (traces[r] != traces[0]) { std::fprintf(stderr, "rank %d produced other tokens than rank 0\n", r); return 1; }
+    std::printf("hostcheck ok: %d ranks, %zu values each\n", ranks, traces[0].size());
+    return 0;
+  } catch (const std::exception& e) {
+    std::fprintf(stderr, "error: %s\n", e.what());
+    return 1;
+  }
+}
