@@ -184,6 +184,9 @@ public:
   int rotDim = 0;              // 0: no rotary table (OPT, ALiBi Baichuan)
   int wpeRows = 0;             // OPT: rows of the learned position table
   int experts = 0, topK = 0, moeInter = 0;       // mixture of experts: count, experts per token, expert FFN width
+  int sharedInterG = 0, s0 = 0;                  // DeepSeek shared experts: whole width, first column of this rank
+  int e0 = 0, e1 = 0;                            // experts kept by this rank: every rank routes every token, multiplies
+                                                 // the rows of its own experts, and the ranks' partial sums are added
   int wq = 0;                  // layer projections: 0 bf16, 1 weight-only int8, 2 int8 weights x int8 activations, 3 NF4, 4 uint4
   int wqNext = 0;              // hybrid types "A_B" (src/models/hybrid_model.h): A for the prompt pass, B for decode steps
   int gptq = 0;                // checkpoint holds GPTQ codes: 1 int8, 2 uint4 (0: dense tensors)
@@ -224,7 +227,8 @@ private:
   std::string dir;
   int fileDt = 1;
   // DeepSeek tensor `<base>.weight.bin` ([in, out]; e4m3 with `<base>.weight_scale_inv.bin` block scales, or a float type)
-  void loadDsLinear(const std::string& base, int inF, int outF, void* dst, int dstRowOffset, int dstLd);
+  void loadDsLinear(const std::string& base, int inF, int outF, void* dst, int dstRowOffset, int dstLd, int o0 = 0, int o1 = -1,
+                    int c0 = 0, int c1 = -1);
   void loadMlaLayer(const std::string& p, LayerWeights& L, int layer);
   // dense bf16 [rows, K] -> the prompt-pass form `first` and, for hybrid types, the decode form `next`; `dense` is
   // released unless a bf16 form points at it
@@ -387,6 +391,7 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_
     vDim = (int)ini.getInt(type, "v_head_dim", headDim);
     firstDense = (int)ini.getInt(type, "first_k_dense_replace", 0);
     sharedInter = (int)ini.getInt(type, "dense_experts", 0) * moeInter;
+    sharedInterG = sharedInter;
     nGroup = std::max(1, (int)ini.getInt(type, "n_group", 1));
     topkGroup = std::max(1, (int)ini.getInt(type, "topk_group", 1));
     routedScale = (float)ini.getFloat(type, "routed_scaling_factor", 1.0);
@@ -425,9 +430,11 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_
   headsG = heads; kvHeadsG = kvHeads; interG = inter; vocabG = vocab;
   groupG = std::max(headsG / std::max(kvHeadsG, 1), 1);
   if (world > 1) {
-    if (spec.mla || spec.mlp == 3) throw std::runtime_error("tensor-parallel expert families run through the Python API");
+    if ((spec.mlp == 3 || spec.mla) && world > experts) throw std::runtime_error("more ranks than experts");
     if (world > headsG) throw std::runtime_error("more tensor-parallel ranks than attention heads");
-    const HeadRange hr = headRange(headsG, kvHeadsG, world, rank);
+    // latent attention has no KV heads to share: every rank takes a run of query heads (with their slices of the query
+    // up-projection, of W_uk / W_uv and of the output projection), the latent cache is the same on every rank
+    const HeadRange hr = headRange(headsG, spec.mla ? headsG : kvHeadsG, world, rank);
     q0 = hr.q0; kv0 = hr.kv0;
     heads = hr.q1 - hr.q0; kvHeads = hr.kv1 - hr.kv0;
     qOff = q0 - kv0 * groupG;                    // first local query head inside its KV group
@@ -436,7 +443,20 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_
     const auto vr = taskRange(vocabG, world, rank);
     v0 = vr.first; vocab = vr.second - vr.first;
     for (int r = 0; r < world; ++r) { const auto x = taskRange(vocabG, world, r); vocabPad = std::max(vocabPad, x.second - x.first); }
-    if (inter % 8 || (wq == 2 || wqNext == 2 ? inter % 16 : 0)) throw std::runtime_error("FFN slice of this rank is not a multiple of 8");
+    if (spec.mlp != 3 && (inter % 8 || (wq == 2 || wqNext == 2 ? inter % 16 : 0)))
+      throw std::runtime_error("FFN slice of this rank is not a multiple of 8");
+    if (spec.mla && sharedInter > 0) {
+      const auto sr = taskRange(sharedInter, world, rank);
+      s0 = sr.first; sharedInter = sr.second - sr.first;
+      // a narrow shared expert may leave the last ranks without columns: they add nothing for it
+      if (sharedInter % 8) throw std::runtime_error("shared-expert slice of this rank is not a multiple of 8");
+    }
+  }
+  if (spec.mlp == 3 || spec.mla) {
+    // expert parallelism on replicated tokens (src/layers/mlp_mixtral.h:95-187 splits every expert's columns instead):
+    // whole experts per rank keep the grouped GEMMs at full width
+    const auto er = expertRange(experts, world, rank);
+    e0 = er.first; e1 = er.second;
   }
   if (!spec.mla && headDim != 64 && headDim != 128 && headDim != 256) throw std::runtime_error("head size must be 64, 128 or 256");
 
@@ -512,13 +532,15 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_
       const int I = moeInter;
       L.router.reset((size_t)experts * hidden * 2);
       denseLoad(p + (mix ? "moe.gate.weight.bin" : "mlp.gate.weight.0.bin"), hidden, experts, L.router.p, 0, hidden);
-      L.expGateUp.reset((size_t)experts * 2 * I * hidden * 2);
-      L.expDown.reset((size_t)experts * hidden * I * 2);
-      for (int e = 0; e < experts; ++e) {
+      const int EL = e1 - e0;
+      L.expGateUp.reset((size_t)EL * 2 * I * hidden * 2);
+      L.expDown.reset((size_t)EL * hidden * I * 2);
+      for (int e = e0; e < e1; ++e) {
         const std::string ep = p + (mix ? "moe.sparse_experts." : "mlp.experts.") + std::to_string(e) + ".";
-        denseLoad(ep + (mix ? "w1.0.bin" : "gate_proj.weight.0.bin"), hidden, I, L.expGateUp.p, e * 2 * I, hidden);
-        denseLoad(ep + (mix ? "w2.0.bin" : "up_proj.weight.0.bin"), hidden, I, L.expGateUp.p, e * 2 * I + I, hidden);
-        denseLoad(ep + (mix ? "w3.0.bin" : "down_proj.weight.0.bin"), I, hidden, L.expDown.p, e * hidden, I);
+        const int l = e - e0;
+        denseLoad(ep + (mix ? "w1.0.bin" : "gate_proj.weight.0.bin"), hidden, I, L.expGateUp.p, l * 2 * I, hidden);
+        denseLoad(ep + (mix ? "w2.0.bin" : "up_proj.weight.0.bin"), hidden, I, L.expGateUp.p, l * 2 * I + I, hidden);
+        denseLoad(ep + (mix ? "w3.0.bin" : "down_proj.weight.0.bin"), I, hidden, L.expDown.p, l * hidden, I);
       }
     } else if (spec.mlp == 1) {
       if (!gptq) L.gateUp.reset((size_t)inter * hidden * 2);
@@ -586,47 +608,64 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_
   }
 }
 
-void Engine::loadDsLinear(const std::string& base, int inF, int outF, void* dst, int dstRowOffset, int dstLd) {
+void Engine::loadDsLinear(const std::string& base, int inF, int outF, void* dst, int dstRowOffset, int dstLd, int o0, int o1,
+                          int c0, int c1) {
+  // the file holds [in, out]; the device wants rows [o0, o1) of the transpose with columns [c0, c1) (a tensor-parallel
+  // slice), written at row `dstRowOffset` of a matrix whose rows are dstLd long
+  if (o1 < 0) o1 = outF;
+  if (c1 < 0) c1 = inF;
+  const bool whole = o0 == 0 && o1 == outF && c0 == 0 && c1 == inF;
   __nv_bfloat16* out = static_cast<__nv_bfloat16*>(dst) + (size_t)dstRowOffset * dstLd;
+  DevBuf full;
+  __nv_bfloat16* target = out;
+  int targetLd = dstLd;
+  if (!whole) { full.reset((size_t)outF * inF * 2); target = full.as<__nv_bfloat16>(); targetLd = inF; }
   if (fileDt != 3 || Env::get().fakeModel) {
     const int dt = fileDt == 3 ? 2 : fileDt;
     auto host = readFile(dir + "/" + base + ".weight.bin", (size_t)inF * outF * dtypeSize(dt), dt);
     DevBuf tmp(host.size());
     XFT_CUDA(cudaMemcpy(tmp.p, host.data(), host.size(), cudaMemcpyHostToDevice));
-    XFT_K(xft_transpose_to_bf16(tmp.p, dt, outF, inF, outF, out, dstLd, st));
+    XFT_K(xft_transpose_to_bf16(tmp.p, dt, outF, inF, outF, target, targetLd, st));
     XFT_CUDA(cudaStreamSynchronize(st));
-    return;
+  } else {
+    // e4m3 bytes [in, out] + one fp32 scale per 128 x 128 block (deepseek_moe_convert.py:117-180): dequantise on the
+    // device, then transpose like every other tensor
+    const int B = 128, sr = (inF + B - 1) / B, sc = (outF + B - 1) / B;
+    std::ifstream f(dir + "/" + base + ".weight.bin", std::ios::binary | std::ios::ate);
+    if (!f) throw std::runtime_error("cannot open " + base + ".weight.bin");
+    if ((size_t)f.tellg() != (size_t)inF * outF) throw std::runtime_error(base + ".weight.bin: unexpected size");
+    std::vector<char> w((size_t)inF * outF);
+    f.seekg(0);
+    f.read(w.data(), (std::streamsize)w.size());
+    auto scales = readFile(dir + "/" + base + ".weight_scale_inv.bin", (size_t)sr * sc * 4, 0);
+    DevBuf dw(w.size()), ds(scales.size()), dense((size_t)inF * outF * 2);
+    XFT_CUDA(cudaMemcpy(dw.p, w.data(), w.size(), cudaMemcpyHostToDevice));
+    XFT_CUDA(cudaMemcpy(ds.p, scales.data(), scales.size(), cudaMemcpyHostToDevice));
+    XFT_K(xft_fp8_block_dequant(dw.p, ds.as<float>(), inF, outF, B, dense.p, st));
+    XFT_K(xft_transpose_to_bf16(dense.p, 2, outF, inF, outF, target, targetLd, st));
+    XFT_CUDA(cudaStreamSynchronize(st));
   }
-  // e4m3 bytes [in, out] + one fp32 scale per 128 x 128 block (deepseek_moe_convert.py:117-180): dequantise on the
-  // device, then transpose like every other tensor
-  const int B = 128, sr = (inF + B - 1) / B, sc = (outF + B - 1) / B;
-  std::ifstream f(dir + "/" + base + ".weight.bin", std::ios::binary | std::ios::ate);
-  if (!f) throw std::runtime_error("cannot open " + base + ".weight.bin");
-  if ((size_t)f.tellg() != (size_t)inF * outF) throw std::runtime_error(base + ".weight.bin: unexpected size");
-  std::vector<char> w((size_t)inF * outF);
-  f.seekg(0);
-  f.read(w.data(), (std::streamsize)w.size());
-  auto scales = readFile(dir + "/" + base + ".weight_scale_inv.bin", (size_t)sr * sc * 4, 0);
-  DevBuf dw(w.size()), ds(scales.size()), dense((size_t)inF * outF * 2);
-  XFT_CUDA(cudaMemcpy(dw.p, w.data(), w.size(), cudaMemcpyHostToDevice));
-  XFT_CUDA(cudaMemcpy(ds.p, scales.data(), scales.size(), cudaMemcpyHostToDevice));
-  XFT_K(xft_fp8_block_dequant(dw.p, ds.as<float>(), inF, outF, B, dense.p, st));
-  XFT_K(xft_transpose_to_bf16(dense.p, 2, outF, inF, outF, out, dstLd, st));
-  XFT_CUDA(cudaStreamSynchronize(st));
+  if (!whole) {
+    XFT_CUDA(cudaMemcpy2DAsync(out, (size_t)dstLd * 2, target + (size_t)o0 * inF + c0, (size_t)inF * 2, (size_t)(c1 - c0) * 2,
+                               (size_t)(o1 - o0), cudaMemcpyDeviceToDevice, st));
+    XFT_CUDA(cudaStreamSynchronize(st));
+  }
 }
 
 void Engine::loadMlaLayer(const std::string& p, LayerWeights& L, int layer) {
   const int qk = nope + ropeD, H = hidden, kvw = kvLora + ropeD;
-  // merged down-projection: the query part (compressed to q_lora, or the full heads * qk when the model has no query
-  // compression) followed by compressed KV + shared rotary key (src/layers/attn_deepseek.h:78-117)
+  // merged down-projection: the query part (compressed to q_lora, or this rank's heads * qk when the model has no query
+  // compression) followed by compressed KV + shared rotary key (src/layers/attn_deepseek.h:78-117).  With several ranks
+  // the compressed parts are computed by every rank; what follows them is split by query head.
   const int qRows = qLora > 0 ? qLora : heads * qk;
   L.qkvA.reset((size_t)(qRows + kvw) * H * 2);
-  loadDsLinear(p + "self_attn.q_a_proj", H, qRows, L.qkvA.p, 0, H);
+  if (qLora > 0) loadDsLinear(p + "self_attn.q_a_proj", H, qLora, L.qkvA.p, 0, H);
+  else loadDsLinear(p + "self_attn.q_a_proj", H, headsG * qk, L.qkvA.p, 0, H, q0 * qk, (q0 + heads) * qk);
   loadDsLinear(p + "self_attn.kv_a_proj_with_mqa", H, kvw, L.qkvA.p, qRows, H);
   if (qLora > 0) {
     L.qANorm = loadVector(p + "self_attn.q_a_layernorm.weight.bin", qLora, false, 2);
     L.qB.reset((size_t)heads * qk * qLora * 2);
-    loadDsLinear(p + "self_attn.q_b_proj", qLora, heads * qk, L.qB.p, 0, qLora);
+    loadDsLinear(p + "self_attn.q_b_proj", qLora, headsG * qk, L.qB.p, 0, qLora, q0 * qk, (q0 + heads) * qk);
   }
   L.kvANorm = loadVector(p + "self_attn.kv_a_layernorm.weight.bin", kvLora, false, 2);
   // kv_b [kv_lora -> heads * (nope + v)] as [out, in]; per head the first `nope` rows are W_uk, the next `v` rows W_uv.
@@ -634,7 +673,8 @@ void Engine::loadMlaLayer(const std::string& p, LayerWeights& L, int layer) {
   // stored transposed per head and both are stacked for the per-head grouped GEMM.
   {
     DevBuf kvb((size_t)heads * (nope + vDim) * kvLora * 2);
-    loadDsLinear(p + "self_attn.kv_b_proj", kvLora, heads * (nope + vDim), kvb.p, 0, kvLora);
+    loadDsLinear(p + "self_attn.kv_b_proj", kvLora, headsG * (nope + vDim), kvb.p, 0, kvLora, q0 * (nope + vDim),
+                 (q0 + heads) * (nope + vDim));
     L.wkT.reset((size_t)heads * kvLora * nope * 2);
     L.wv.reset((size_t)heads * vDim * kvLora * 2);
     for (int h = 0; h < heads; ++h) {
@@ -646,18 +686,19 @@ void Engine::loadMlaLayer(const std::string& p, LayerWeights& L, int layer) {
     XFT_CUDA(cudaStreamSynchronize(st));
   }
   L.o.reset((size_t)H * heads * vDim * 2);
-  loadDsLinear(p + "attention.dense", heads * vDim, H, L.o.p, 0, heads * vDim);
+  loadDsLinear(p + "attention.dense", headsG * vDim, H, L.o.p, 0, heads * vDim, 0, H, q0 * vDim, (q0 + heads) * vDim);
   L.n1 = loadVector(p + "input_layernorm.weight.bin", H, false, 2);
   L.n2 = loadVector(p + "post_attention_layernorm.weight.bin", H, false, 2);
   L.denseMlp = layer < firstDense;
-  auto gatedMlp = [&](const std::string& base, int I, DevBuf& gu, DevBuf& dn) {
+  // a gated MLP of whole width IG of which this rank keeps columns [c, c + I)
+  auto gatedMlp = [&](const std::string& base, int IG, int c, int I, DevBuf& gu, DevBuf& dn) {
     gu.reset((size_t)2 * I * H * 2);
-    loadDsLinear(base + "gate_proj", H, I, gu.p, 0, H);
-    loadDsLinear(base + "up_proj", H, I, gu.p, I, H);
+    loadDsLinear(base + "gate_proj", H, IG, gu.p, 0, H, c, c + I);
+    loadDsLinear(base + "up_proj", H, IG, gu.p, I, H, c, c + I);
     dn.reset((size_t)H * I * 2);
-    loadDsLinear(base + "down_proj", I, H, dn.p, 0, I);
+    loadDsLinear(base + "down_proj", IG, H, dn.p, 0, I, 0, H, c, c + I);
   };
-  if (L.denseMlp) { gatedMlp(p + "mlp.", inter, L.gateUp, L.down); return; }
+  if (L.denseMlp) { gatedMlp(p + "mlp.", interG, i0, inter, L.gateUp, L.down); return; }
   const int E = experts, I = moeInter;
   {
     // router [hidden, experts] bf16 on disk
@@ -669,14 +710,16 @@ void Engine::loadMlaLayer(const std::string& p, LayerWeights& L, int layer) {
     XFT_CUDA(cudaStreamSynchronize(st));
   }
   L.routerBias = loadVector(p + "mlp.gate.e_score_correction_bias.bin", E, true, 2);
-  if (sharedInter > 0) gatedMlp(p + "mlp.shared_experts.", sharedInter, L.sharedGateUp, L.sharedDown);
-  L.expGateUp.reset((size_t)E * 2 * I * H * 2);
-  L.expDown.reset((size_t)E * H * I * 2);
-  for (int e = 0; e < E; ++e) {
+  if (sharedInter > 0) gatedMlp(p + "mlp.shared_experts.", sharedInterG, s0, sharedInter, L.sharedGateUp, L.sharedDown);
+  const int EL = e1 - e0;
+  L.expGateUp.reset((size_t)EL * 2 * I * H * 2);
+  L.expDown.reset((size_t)EL * H * I * 2);
+  for (int e = e0; e < e1; ++e) {
     const std::string ep = p + "mlp.experts." + std::to_string(e) + ".";
-    loadDsLinear(ep + "gate_proj", H, I, L.expGateUp.p, e * 2 * I, H);
-    loadDsLinear(ep + "up_proj", H, I, L.expGateUp.p, e * 2 * I + I, H);
-    loadDsLinear(ep + "down_proj", I, H, L.expDown.p, e * H, I);
+    const int l = e - e0;
+    loadDsLinear(ep + "gate_proj", H, I, L.expGateUp.p, l * 2 * I, H);
+    loadDsLinear(ep + "up_proj", H, I, L.expGateUp.p, l * 2 * I + I, H);
+    loadDsLinear(ep + "down_proj", I, H, L.expDown.p, l * H, I);
   }
 }
 
@@ -1090,11 +1133,14 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
                               mlaSplit > 1 ? partMl.as<float>() : nullptr, attnCounters.as<int>(), stp, st));
       perHead(mOLat.p, Lr, L.wv.p, vDim, mOHead.p);
       XFT_K(xft_swap_outer_dims(mOHead.p, att.p, heads, T, vDim, st));          // [heads, T, v] -> [T, heads * v]
-      gemm(att.p, heads * vDim, L.o.p, hidden, nxt, hidden, 0, 0, 0, nullptr, cur, 0, T);      // + residual
+      // row-parallel with several ranks: the residual enters on rank 0, the ranks' products are added
+      gemm(att.p, heads * vDim, L.o.p, hidden, nxt, hidden, 0, 0, 0, nullptr, rank == 0 ? cur : nullptr, 0, T);
+      if (comm) comm->allReduceBf16(nxt, (size_t)T * hidden, st);
       norm(nxt, L.n2, L.n2b, hb, T);
       if (L.denseMlp) {
         gemm(hb, hidden, L.gateUp.p, 2 * inter, g.p, inter, 0, 1, inter, nullptr, nullptr, act, T);
-        gemm(g.p, inter, L.down.p, hidden, cur, hidden, 0, 0, 0, nullptr, nxt, 0, T);
+        gemm(g.p, inter, L.down.p, hidden, cur, hidden, 0, 0, 0, nullptr, rank == 0 ? nxt : nullptr, 0, T);
+        if (comm) comm->allReduceBf16(cur, (size_t)T * hidden, st);
         continue;
       }
       // ---- shared + routed experts (src/layers/moe_deepseek.h:121-196,285-353)
@@ -1102,12 +1148,14 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
       gemm(hb, hidden, L.router.p, E, moeLogits.p, E, 1, 0, 0, nullptr, nullptr, 0, T);
       XFT_K(xft_moe_route(moeLogits.as<float>(), E, T, E, k, 2, L.routerBias.as<float>(), nGroup, topkGroup, routedScale,
                           normTopk ? 1 : 0, sigmoidScores ? 1 : 0, moeIdx.as<int>(), moeWts.as<float>(), st));
-      XFT_K(xft_moe_plan(moeIdx.as<int>(), moeWts.as<float>(), T, k, 0, E, moeBn, moePos.as<int>(), moeSrc.as<int>(),
+      // several ranks: rows only for this rank's experts [e0, e1), a column slice of the shared experts, sums added
+      const int EL = e1 - e0;
+      XFT_K(xft_moe_plan(moeIdx.as<int>(), moeWts.as<float>(), T, k, e0, e1, moeBn, moePos.as<int>(), moeSrc.as<int>(),
                          moeRowW.as<float>(), moeTiles.p, moeMeta.as<int>(), moeMaxTiles, T * k, st));
       XFT_K(xft_moe_gather(hb, hidden, moeSrc.as<int>(), moeMeta.as<int>(), moeXs.p, T * k, hidden, st));
-      XFT_K(xft_gemm_bf16_grouped(moeXs.p, hidden, T * k, L.expGateUp.p, E * 2 * I, hidden, moeH1.p, I, 0, I, hidden, 1, I,
+      XFT_K(xft_gemm_bf16_grouped(moeXs.p, hidden, T * k, L.expGateUp.p, EL * 2 * I, hidden, moeH1.p, I, 0, I, hidden, 1, I,
                                   2 * I, moeTiles.p, moeMeta.as<int>(), moeMaxTiles, moeBn, nullptr, 2, stp, st));
-      XFT_K(xft_gemm_bf16_grouped(moeH1.p, I, T * k, L.expDown.p, E * hidden, I, moeYs.p, hidden, 1, hidden, I, 0, 0, hidden,
+      XFT_K(xft_gemm_bf16_grouped(moeH1.p, I, T * k, L.expDown.p, EL * hidden, I, moeYs.p, hidden, 1, hidden, I, 0, 0, hidden,
                                   moeTiles.p, moeMeta.as<int>(), moeMaxTiles, moeBn, moeRowW.as<float>(), 0, stp, st));
       const float* sharedOut = nullptr;
       if (sharedInter > 0) {
@@ -1115,7 +1163,9 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
         gemm(g.p, sharedInter, L.sharedDown.p, hidden, mShared.p, hidden, 1, 0, 0, nullptr, nullptr, 0, T);
         sharedOut = mShared.as<float>();
       }
-      XFT_K(xft_moe_combine(moeYs.as<float>(), moePos.as<int>(), k, sharedOut, nxt, hidden, cur, nullptr, T, hidden, st));
+      XFT_K(xft_moe_combine(moeYs.as<float>(), moePos.as<int>(), k, sharedOut, rank == 0 ? nxt : nullptr, hidden, cur, nullptr, T,
+                            hidden, st));
+      if (comm) comm->allReduceBf16(cur, (size_t)T * hidden, st);
       continue;
     }
     const LayerLins& Q = (decode && wqNext != wq) ? linsNext[l] : lins[l];
@@ -1150,14 +1200,19 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
       gemm(hn, hidden, L.router.p, E, moeLogits.p, E, 1, 0, 0, nullptr, nullptr, 0, T);
       XFT_K(xft_moe_route(moeLogits.as<float>(), E, T, E, k, spec.routeKind, nullptr, 1, 1, 1.0f, 1, 1, moeIdx.as<int>(),
                           moeWts.as<float>(), st));
-      XFT_K(xft_moe_plan(moeIdx.as<int>(), moeWts.as<float>(), T, k, 0, E, moeBn, moePos.as<int>(), moeSrc.as<int>(),
+      // with several ranks: only the pairs of this rank's experts [e0, e1) get rows; the residual enters on rank 0 and
+      // the ranks' sums are added
+      const int EL = e1 - e0;
+      XFT_K(xft_moe_plan(moeIdx.as<int>(), moeWts.as<float>(), T, k, e0, e1, moeBn, moePos.as<int>(), moeSrc.as<int>(),
                          moeRowW.as<float>(), moeTiles.p, moeMeta.as<int>(), moeMaxTiles, T * k, st));
       XFT_K(xft_moe_gather(hn, hidden, moeSrc.as<int>(), moeMeta.as<int>(), moeXs.p, T * k, hidden, st));
-      XFT_K(xft_gemm_bf16_grouped(moeXs.p, hidden, T * k, L.expGateUp.p, E * 2 * I, hidden, moeH1.p, I, 0, I, hidden, 1, I,
+      XFT_K(xft_gemm_bf16_grouped(moeXs.p, hidden, T * k, L.expGateUp.p, EL * 2 * I, hidden, moeH1.p, I, 0, I, hidden, 1, I,
                                   2 * I, moeTiles.p, moeMeta.as<int>(), moeMaxTiles, moeBn, nullptr, act, stp, st));
-      XFT_K(xft_gemm_bf16_grouped(moeH1.p, I, T * k, L.expDown.p, E * hidden, I, moeYs.p, hidden, 1, hidden, I, 0, 0, hidden,
+      XFT_K(xft_gemm_bf16_grouped(moeH1.p, I, T * k, L.expDown.p, EL * hidden, I, moeYs.p, hidden, 1, hidden, I, 0, 0, hidden,
                                   moeTiles.p, moeMeta.as<int>(), moeMaxTiles, moeBn, moeRowW.as<float>(), 0, stp, st));
-      XFT_K(xft_moe_combine(moeYs.as<float>(), moePos.as<int>(), k, nullptr, nxt, hidden, cur, nullptr, T, hidden, st));
+      XFT_K(xft_moe_combine(moeYs.as<float>(), moePos.as<int>(), k, nullptr, rank == 0 ? nxt : nullptr, hidden, cur, nullptr, T,
+                            hidden, st));
+      if (comm) comm->allReduceBf16(cur, (size_t)T * hidden, st);
       continue;
     }
     if (spec.mlp == 1) {

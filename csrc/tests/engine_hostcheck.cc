@@ -7,6 +7,13 @@
 // that ranks agree.
 //
 //   engine_hostcheck <model dir> <weight type> <kv type> <ranks>
+//
+// With the arithmetic of the stand-in switched on (XFT_MOCK_MATH=1) a second form records logits for a comparison with
+// another implementation of the model: the prompts of <ids file> ("B P steps" and then B * P token ids) go through the
+// continuous-batching calls, `steps` greedy tokens follow one at a time, and <out file> receives B, V, steps + 1 as
+// int32, the logits of every pass [steps + 1, B, V] as fp32 and the token chosen after each pass [steps + 1, B] as int32.
+//
+//   engine_hostcheck logits <model dir> <weight type> <kv type> <ranks> <ids file> <out file>
 #include <cstdio>
 #include <cstdlib>
 #include <stdexcept>
@@ -120,9 +127,96 @@ std::vector<int32_t> exercise(xft::Model& m, bool experts) {
   return trace;
 }
 
+struct LogitsRun {
+  int B = 0, P = 0, steps = 0;
+  std::vector<int32_t> ids;
+  std::vector<float> logits;       // [steps + 1, B, V]
+  std::vector<int32_t> tokens;     // [steps + 1, B]
+  int V = 0;
+};
+
+void recordLogits(xft::Model& m, LogitsRun& run) {
+  std::vector<std::vector<int32_t>> prompts(run.B);
+  for (int b = 0; b < run.B; ++b) prompts[b].assign(run.ids.begin() + (size_t)b * run.P, run.ids.begin() + (size_t)(b + 1) * run.P);
+  const int maxLen = run.P + run.steps + 2;
+  std::vector<int> seqs = m.set_input(prompts, std::vector<int>{}, maxLen);
+  run.V = m.getVocabSize();
+  for (int s = 0; s <= run.steps; ++s) {
+    auto r = m.forward(false);
+    CHECK(std::get<1>(r) == run.B && std::get<2>(r) == run.V);
+    const float* lg = std::get<0>(r);
+    run.logits.insert(run.logits.end(), lg, lg + (size_t)run.B * run.V);
+    std::vector<std::vector<int32_t>> next(run.B);
+    for (int b = 0; b < run.B; ++b) {
+      int best = 0;
+      for (int v = 1; v < run.V; ++v) if (lg[(size_t)b * run.V + v] > lg[(size_t)b * run.V + best]) best = v;
+      run.tokens.push_back(best);
+      next[b].assign(1, best);
+    }
+    if (s < run.steps) m.set_input(next, seqs, maxLen);
+  }
+  CHECK(m.freeSeqs(seqs));
+}
+
+int logitsMain(int argc, char** argv) {
+  if (argc < 8) { std::fprintf(stderr, "usage: engine_hostcheck logits <model dir> <weight type> <kv type> <ranks> <ids file> <out file>\n"); return 2; }
+  const std::string dir = argv[2];
+  const xft::DataType wdt = xft::dataTypeFromName(argv[3]);
+  const xft::DataType kdt = std::string(argv[4]) == "int8" ? xft::DataType::int8 : xft::DataType::fp16;
+  const int ranks = std::atoi(argv[5]);
+  if (wdt == xft::DataType::unknown || ranks < 1 || ranks > 8) { std::fprintf(stderr, "bad arguments\n"); return 2; }
+  LogitsRun proto;
+  {
+    FILE* f = std::fopen(argv[6], "r");
+    if (!f || std::fscanf(f, "%d %d %d", &proto.B, &proto.P, &proto.steps) != 3) { std::fprintf(stderr, "cannot read %s\n", argv[6]); return 2; }
+    proto.ids.resize((size_t)proto.B * proto.P);
+    for (auto& v : proto.ids) if (std::fscanf(f, "%d", &v) != 1) { std::fprintf(stderr, "short ids file\n"); std::fclose(f); return 2; }
+    std::fclose(f);
+  }
+  std::vector<LogitsRun> runs(ranks, proto);
+  std::vector<std::string> errors(ranks);
+  if (ranks == 1) {
+    xft::AutoModel m(dir, wdt, kdt, nullptr);
+    recordLogits(m, runs[0]);
+  } else {
+    auto comms = xft::makeThreadCommunicators(ranks);
+    std::vector<std::thread> threads;
+    for (int r = 0; r < ranks; ++r)
+      threads.emplace_back([&, r] {
+        try {
+          comms[r]->begin();
+          xft::AutoModel m(dir, wdt, kdt, comms[r]);
+          recordLogits(m, runs[r]);
+        } catch (const std::exception& e) {
+          errors[r] = e.what();
+        }
+        comms[r]->end();
+      });
+    for (auto& t : threads) t.join();
+  }
+  bool failed = false;
+  for (int r = 0; r < ranks; ++r)
+    if (!errors[r].empty()) { std::fprintf(stderr, "rank %d: %s\n", r, errors[r].c_str()); failed = true; }
+  if (failed) return 1;
+  for (int r = 1; r < ranks; ++r)
+    if (runs[r].logits != runs[0].logits || runs[r].tokens != runs[0].tokens) { std::fprintf(stderr, "rank %d sees other logits than rank 0\n", r); return 1; }
+  FILE* f = std::fopen(argv[7], "wb");
+  if (!f) { std::fprintf(stderr, "cannot write %s\n", argv[7]); return 2; }
+  const int32_t head[3] = {runs[0].B, runs[0].V, runs[0].steps + 1};
+  std::fwrite(head, 4, 3, f);
+  std::fwrite(runs[0].logits.data(), 4, runs[0].logits.size(), f);
+  std::fwrite(runs[0].tokens.data(), 4, runs[0].tokens.size(), f);
+  std::fclose(f);
+  std::printf("hostcheck logits ok: %d ranks, %d x %d x %d\n", ranks, head[2], head[0], head[1]);
+  return 0;
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
+  if (argc >= 2 && std::string(argv[1]) == "logits") {
+    try { return logitsMain(argc, argv); } catch (const std::exception& e) { std::fprintf(stderr, "error: %s\n", e.what()); return 1; }
+  }
   if (argc < 5) { std::fprintf(stderr, "usage: engine_hostcheck <model dir> <weight type> <kv type> <ranks>\n"); return 2; }
   const std::string dir = argv[1];
   const xft::DataType wdt = xft::dataTypeFromName(argv[2]);
@@ -155,8 +249,10 @@ int main(int argc, char** argv) {
         comms[r]->end();
       });
     for (auto& t : threads) t.join();
+    bool failed = false;
     for (int r = 0; r < ranks; ++r)
-      if (!errors[r].empty()) { std::fprintf(stderr, "rank %d: %s\n", r, errors[r].c_str()); return 1; }
+      if (!errors[r].empty()) { std::fprintf(stderr, "rank %d: %s\n", r, errors[r].c_str()); failed = true; }
+    if (failed) return 1;
     for (int r = 1; r < ranks; ++r)
       if (traces[r] != traces[0]) { std::fprintf(stderr, "rank %d produced other tokens than rank 0\n", r); return 1; }
     std::printf("hostcheck ok: %d ranks, %zu values each\n", ranks, traces[0].size());

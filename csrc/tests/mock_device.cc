@@ -10,9 +10,18 @@
 //
 // The few results the host logic depends on are produced for real: the routing (valid expert ids), the expert plan
 // (rows grouped by expert, tile table, counts) and logits that differ per row and step so that searchers move.
+//
+// With XFT_MOCK_MATH=1 the stand-ins of the bf16 path ALSO compute what the real kernels compute (fp32 arithmetic,
+// results rounded to bf16 where the kernels round): embedding, norms, GEMMs with their epilogues, rotary + cache append,
+// paged attention (grouped heads, ALiBi, prefix mask, int8 cache), routing, grouped expert GEMMs, combine, the latent-
+// attention steps, the sum of the thread-rank all-reduce.  The engine's logits can then be compared, on a CPU box, with
+// the PyTorch fp32 path of the package for every family, and tensor-parallel ranks with a single rank: that checks what
+// the touch checks cannot — which rows of which file went where, offsets of heads and experts, position tables.  The
+// quantised GEMMs stay touch-only.
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cmath>
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
@@ -54,6 +63,50 @@ void wrRows(void* p, long long rows, long long cols, long long ld, size_t esz, i
 }
 const uint16_t kBf16Small = 0x3c00;      // bf16 of 0.0078125: keeps activations finite and tiny
 
+const bool g_math = [] { const char* v = std::getenv("XFT_MOCK_MATH"); return v && *v && *v != '0'; }();
+
+inline float bf(uint16_t h) { uint32_t u = (uint32_t)h << 16; float f; std::memcpy(&f, &u, 4); return f; }
+inline uint16_t tobf(float f) {           // round to nearest even, as __float2bfloat16
+  uint32_t u; std::memcpy(&u, &f, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return 0x7fc0;
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return (uint16_t)(u >> 16);
+}
+inline float rbf(float f) { return bf(tobf(f)); }
+inline float halfToFloat(uint16_t h) {
+  const int e = (h >> 10) & 31, m = h & 1023;
+  float v = e == 0 ? std::ldexp((float)m, -24) : e == 31 ? (m ? NAN : INFINITY) : std::ldexp((float)(m | 1024), e - 25);
+  return (h & 0x8000) ? -v : v;
+}
+inline float e4m3ToFloat(uint8_t b) {
+  const int e = (b >> 3) & 15, m = b & 7;
+  float v = e == 0 ? std::ldexp((float)m, -9) : (e == 15 && m == 7) ? NAN : std::ldexp((float)(m | 8), e - 10);
+  return (b & 0x80) ? -v : v;
+}
+inline float actf(float x, int act) {
+  switch (act) {
+    case 1: return std::max(x, 0.f);
+    case 2: return x / (1.f + std::exp(-x));
+    case 3: { const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x); return 0.5f * x * (1.f + std::tanh(u)); }
+    default: return x;
+  }
+}
+inline const uint16_t* bfp(const void* p) { return static_cast<const uint16_t*>(p); }
+inline uint16_t* bfp(void* p) { return static_cast<uint16_t*>(p); }
+
+// acc[n] = sum_k x[k] * W[n, k] for n in [0, rows): bf16 operands, fp32 sums
+void dots(const uint16_t* x, int K, const uint16_t* W, long long ldw, int rows, std::vector<float>& acc) {
+  std::vector<float> xf(K);
+  for (int k = 0; k < K; ++k) xf[k] = bf(x[k]);
+  acc.resize(rows);
+  for (int n = 0; n < rows; ++n) {
+    const uint16_t* w = W + (size_t)n * ldw;
+    float a = 0.f;
+    for (int k = 0; k < K; ++k) a += xf[k] * bf(w[k]);
+    acc[n] = a;
+  }
+}
+
 }  // namespace
 
 // ------------------------------------------------------------------------------------------------ CUDA runtime
@@ -64,6 +117,11 @@ cudaError_t cudaMallocHost(void** p, size_t n) { *p = std::calloc(1, n ? n : 1);
 cudaError_t cudaFreeHost(void* p) { std::free(p); return cudaSuccess; }
 cudaError_t cudaMemcpy(void* d, const void* s, size_t n, cudaMemcpyKind) { if (n) std::memmove(d, s, n); return cudaSuccess; }
 cudaError_t cudaMemcpyAsync(void* d, const void* s, size_t n, cudaMemcpyKind, cudaStream_t) { if (n) std::memmove(d, s, n); return cudaSuccess; }
+cudaError_t cudaMemcpy2DAsync(void* d, size_t dpitch, const void* s, size_t spitch, size_t width, size_t height, cudaMemcpyKind,
+                              cudaStream_t) {
+  for (size_t r = 0; r < height; ++r) std::memmove(static_cast<char*>(d) + r * dpitch, static_cast<const char*>(s) + r * spitch, width);
+  return cudaSuccess;
+}
 cudaError_t cudaMemset(void* d, int v, size_t n) { if (n) std::memset(d, v, n); return cudaSuccess; }
 cudaError_t cudaMemsetAsync(void* d, int v, size_t n, cudaStream_t) { if (n) std::memset(d, v, n); return cudaSuccess; }
 cudaError_t cudaStreamCreate(cudaStream_t* s) { static char token; *s = reinterpret_cast<cudaStream_t>(&token); return cudaSuccess; }
@@ -79,7 +137,7 @@ const char* cudaGetErrorString(cudaError_t) { return "mock device error"; }
 // ------------------------------------------------------------------------------------------------ kernel library
 extern "C" {
 
-int xft_embedding(const int* ids, const void* table, void* out, int T, int H, int vocab, float, const void* pos_table,
+int xft_embedding(const int* ids, const void* table, void* out, int T, int H, int vocab, float scale, const void* pos_table,
                   const int* positions, int pos_offset, int npos, int*, cudaStream_t) {
   rd(ids, (size_t)T * 4);
   for (int t = 0; t < T; ++t) {
@@ -94,39 +152,93 @@ int xft_embedding(const int* ids, const void* table, void* out, int T, int H, in
   uint16_t* o = static_cast<uint16_t*>(out);
   wrRows(out, T, H, H, 2);
   for (size_t i = 0; i < (size_t)T * H; ++i) o[i] = kBf16Small;
+  if (!g_math) return 0;
+  for (int t = 0; t < T; ++t)
+    for (int i = 0; i < H; ++i) {
+      const uint16_t raw = bfp(table)[(size_t)ids[t] * H + i];
+      if (scale == 1.f && !pos_table) { o[(size_t)t * H + i] = raw; continue; }
+      float x = bf(raw) * scale;
+      if (pos_table) x += bf(bfp(pos_table)[(size_t)(positions[t] + pos_offset) * H + i]);
+      o[(size_t)t * H + i] = tobf(x);
+    }
   return 0;
 }
 
 int xft_rmsnorm(const void* x, int ldx, const void* res, int ldr, const float* w, void* y, int ldy, void* h_out, int T, int H,
-                float, cudaStream_t) {
+                float eps, cudaStream_t) {
   rdRows(x, T, H, ldx, 2);
   if (res) rdRows(res, T, H, ldr, 2);
   rd(w, (size_t)H * 4);
-  wrRows(y, T, H, ldy, 2);
-  if (h_out) wrRows(h_out, T, H, H, 2);
+  std::vector<float> row(g_math ? H : 0);
+  if (g_math)                                     // before the writes: y may alias x
+    for (int t = 0; t < T; ++t) {
+      float ss = 0.f;
+      for (int i = 0; i < H; ++i) {
+        float f = bf(bfp(x)[(size_t)t * ldx + i]);
+        if (res) f = rbf(f + bf(bfp(res)[(size_t)t * ldr + i]));
+        row[i] = f; ss += f * f;
+      }
+      const float inv = 1.f / std::sqrt(ss / H + eps);
+      for (int i = 0; i < H; ++i) {
+        if (res && h_out) bfp(h_out)[(size_t)t * H + i] = tobf(row[i]);
+        bfp(y)[(size_t)t * ldy + i] = tobf(row[i] * inv * w[i]);
+      }
+    }
+  else {
+    wrRows(y, T, H, ldy, 2);
+    if (h_out) wrRows(h_out, T, H, H, 2);
+  }
   return 0;
 }
 
-int xft_layernorm(const void* x, int ldx, const float* w, const float* b, void* y, int ldy, int T, int H, float, cudaStream_t) {
+int xft_layernorm(const void* x, int ldx, const float* w, const float* b, void* y, int ldy, int T, int H, float eps, cudaStream_t) {
   rdRows(x, T, H, ldx, 2);
   rd(w, (size_t)H * 4);
   rd(b, (size_t)H * 4);
-  wrRows(y, T, H, ldy, 2);
+  if (!g_math) { wrRows(y, T, H, ldy, 2); return 0; }
+  std::vector<float> row(H);
+  for (int t = 0; t < T; ++t) {
+    float s = 0.f, vs = 0.f;
+    for (int i = 0; i < H; ++i) { row[i] = bf(bfp(x)[(size_t)t * ldx + i]); s += row[i]; }
+    const float mu = s / H;
+    for (int i = 0; i < H; ++i) vs += (row[i] - mu) * (row[i] - mu);
+    const float inv = 1.f / std::sqrt(vs / H + eps);
+    for (int i = 0; i < H; ++i) bfp(y)[(size_t)t * ldy + i] = tobf((row[i] - mu) * inv * w[i] + b[i]);
+  }
   return 0;
 }
 
 int xft_gemm_bf16(const void* X, int ldx, const void* W, int w_rows, int ldw, void* Y, int ldo, int out_fp32, int T, int N,
-                  int K, int gated, int dual_off, const float* bias, const void* residual, int ldr, float, int, const float* row_scale,
-                  float* ws, size_t ws_bytes, int* counters, int n_counters, int* status, int, cudaStream_t) {
-  need(w_rows >= (gated ? dual_off + N : N), "gemm: weight has fewer rows than outputs");
+                  int K, int gated, int dual_off, const float* bias, const void* residual, int ldr, float res_scale, int act,
+                  const float* row_scale, float* ws, size_t ws_bytes, int* counters, int n_counters, int* status, int, cudaStream_t) {
+  const int rows = gated ? dual_off + N : N;
+  need(w_rows >= rows, "gemm: weight has fewer rows than outputs");
   rdRows(X, T, K, ldx, 2);
-  rdRows(W, gated ? dual_off + N : N, K, ldw, 2);
-  if (bias) rd(bias, (size_t)(gated ? dual_off + N : N) * 4);
+  rdRows(W, rows, K, ldw, 2);
+  if (bias) rd(bias, (size_t)rows * 4);
   if (residual) rdRows(residual, T, N, ldr, 2);
-  if (row_scale) rd(row_scale, (size_t)T * 4);
+  if (row_scale) rd(row_scale, (size_t)N * 4);
   if (ws) { rd(ws, 1); rd(reinterpret_cast<char*>(ws) + ws_bytes - 1, 1); }
   if (counters) rd(counters, (size_t)n_counters * 4);
   if (status) rd(status, 4);
+  if (g_math) {
+    // y = act(acc * row_scale[n] + bias[n]) [* (acc_up + bias_up)] + res_scale * residual   (Y may alias the residual)
+    std::vector<float> acc, out(N);
+    for (int t = 0; t < T; ++t) {
+      dots(bfp(X) + (size_t)t * ldx, K, bfp(W), ldw, rows, acc);
+      for (int n = 0; n < N; ++n) {
+        const float rs = row_scale ? row_scale[n] : 1.f;
+        float x = actf(acc[n] * rs + (bias ? bias[n] : 0.f), act);
+        if (gated) x *= acc[dual_off + n] * rs + (bias ? bias[dual_off + n] : 0.f);
+        if (residual) x += res_scale * bf(bfp(residual)[(size_t)t * ldr + n]);
+        out[n] = x;
+      }
+      for (int n = 0; n < N; ++n)
+        if (out_fp32) static_cast<float*>(Y)[(size_t)t * ldo + n] = out[n];
+        else bfp(Y)[(size_t)t * ldo + n] = tobf(out[n]);
+    }
+    return 0;
+  }
   if (out_fp32) {
     // logits and router scores: a different, deterministic number per (row, column) so that searches and routing move
     wrRows(Y, T, N, ldo, 4);
@@ -158,9 +270,62 @@ static void touchCache(void* kc, void* vc, float* ks, float* vs, int int8_cache,
   }
 }
 
+// the split of a fused QKV row, per-head RMSNorm, rotary (one or two streams) and the paged append, as the kernel does them
+static void ropeCacheMath(const void* qkv, int ldq, int T, int hq, int hkv, int D, const int* positions, const int* positions2,
+                          const float* table, int rot, int style, int rot_off, const float* q_scale, const float* q_norm_w,
+                          const float* k_norm_w, float eps, void* q_out, void* kc, void* vc, float* ks, float* vs, int int8_cache,
+                          int bs, const int* slots) {
+  std::vector<float> v(D);
+  for (int t = 0; t < T; ++t)
+    for (int h = 0; h < hq + 2 * hkv; ++h) {
+      const uint16_t* src = bfp(qkv) + (size_t)t * ldq + (size_t)h * D;
+      for (int d = 0; d < D; ++d) v[d] = bf(src[d]);
+      const bool is_q = h < hq, is_k = !is_q && h < hq + hkv;
+      const float* nw = is_q ? q_norm_w : is_k ? k_norm_w : nullptr;
+      if (nw) {
+        float ss = 0.f;
+        for (int d = 0; d < D; ++d) ss += v[d] * v[d];
+        const float inv = 1.f / std::sqrt(ss / D + eps);
+        for (int d = 0; d < D; ++d) v[d] = rbf(v[d] * inv * nw[d]);
+      }
+      if ((is_q || is_k) && table && rot > 0) {
+        const int half = rot / 2;
+        for (int stream = 0; stream < (positions2 ? 2 : 1); ++stream) {
+          const float* cs = table + (size_t)(stream ? positions2[t] : positions[t]) * rot;
+          const int off = rot_off + stream * rot;
+          for (int i = 0; i < half; ++i) {
+            const int a = off + (style == 0 ? i : 2 * i), b = off + (style == 0 ? i + half : 2 * i + 1);
+            const float x1 = v[a], x2 = v[b];
+            v[a] = x1 * cs[i] - x2 * cs[half + i];
+            v[b] = x2 * cs[i] + x1 * cs[half + i];
+          }
+        }
+      }
+      if (is_q) {
+        const float qs = q_scale ? q_scale[t] : 1.f;
+        for (int d = 0; d < D; ++d) bfp(q_out)[((size_t)t * hq + h) * D + d] = tobf(v[d] * qs);
+        continue;
+      }
+      const int kh = is_k ? h - hq : h - hq - hkv;
+      const long long blk = slots[t] / bs, off = slots[t] % bs;
+      const size_t base = (size_t)(blk * hkv + kh) * bs + off;
+      if (int8_cache) {
+        float am = 0.f;
+        for (int d = 0; d < D; ++d) am = std::max(am, std::fabs(v[d]));
+        const float sc = am / 127.f, inv = sc > 1e-20f ? 1.f / sc : 0.f;
+        int8_t* dst = static_cast<int8_t*>(is_k ? kc : vc) + base * D;
+        for (int d = 0; d < D; ++d) dst[d] = (int8_t)std::min(std::max(std::nearbyint(v[d] * inv), -127.f), 127.f);
+        (is_k ? ks : vs)[base] = sc;
+      } else {
+        uint16_t* dst = bfp(is_k ? kc : vc) + base * D;
+        for (int d = 0; d < D; ++d) dst[d] = tobf(v[d]);
+      }
+    }
+}
+
 int xft_qkv_rope_cache(const void* qkv, int ldq, int T, int hq, int hkv, int D, const int* positions, const float* table, int rot,
-                       int, int rot_off, int max_pos, const float* q_scale, const float* q_norm_w, const float* k_norm_w, float,
-                       void* q_out, void* kc, void* vc, float* ks, float* vs, int int8_cache, int bs, long long nslots,
+                       int style, int rot_off, int max_pos, const float* q_scale, const float* q_norm_w, const float* k_norm_w,
+                       float eps, void* q_out, void* kc, void* vc, float* ks, float* vs, int int8_cache, int bs, long long nslots,
                        const int* slots, int*, cudaStream_t) {
   rdRows(qkv, T, (long long)(hq + 2 * hkv) * D, ldq, 2);
   if (table && rot > 0) {
@@ -175,6 +340,9 @@ int xft_qkv_rope_cache(const void* qkv, int ldq, int T, int hq, int hkv, int D, 
   if (k_norm_w) rd(k_norm_w, (size_t)D * 4);
   wrRows(q_out, T, (long long)hq * D, (long long)hq * D, 2);
   touchCache(kc, vc, ks, vs, int8_cache, hkv, D, bs, nslots, slots, T);
+  if (g_math)
+    ropeCacheMath(qkv, ldq, T, hq, hkv, D, positions, nullptr, table, rot, style, rot_off, q_scale, q_norm_w, k_norm_w, eps, q_out,
+                  kc, vc, ks, vs, int8_cache, bs, slots);
   return 0;
 }
 
@@ -190,12 +358,15 @@ int xft_qkv_rope2d_cache(const void* qkv, int ldq, int T, int hq, int hkv, int D
   }
   wrRows(q_out, T, (long long)hq * D, (long long)hq * D, 2);
   touchCache(kc, vc, ks, vs, int8_cache, hkv, D, bs, nslots, slots, T);
+  if (g_math)
+    ropeCacheMath(qkv, ldq, T, hq, hkv, D, positions, positions2, table, rot, 0, 0, nullptr, nullptr, nullptr, 0.f, q_out, kc, vc,
+                  ks, vs, int8_cache, bs, slots);
   return 0;
 }
 
 int xft_paged_attention(const void* q, void* out, const void* kc, const void* vc, const float* ks, const float* vs,
                         const int* block_table, int bt_stride, const int* cu_q, const int* kv_lens, int B, int max_q, int hq,
-                        int hkv, int group, int q_off, int HD, int bs, int num_blocks, float, const float* slopes,
+                        int hkv, int group, int q_off, int HD, int bs, int num_blocks, float scale, const float* slopes,
                         const int* prefix_lens, int decode, int nsplit, float* part_o, float* part_ml, int* split_counters,
                         int* status, cudaStream_t) {
   rd(cu_q, (size_t)(B + 1) * 4);
@@ -230,6 +401,39 @@ int xft_paged_attention(const void* q, void* out, const void* kc, const void* vc
   }
   if (status) rd(status, 4);
   wrRows(out, T, (long long)hq * HD, (long long)hq * HD, 2);
+  if (!g_math) return 0;
+  std::vector<float> sc, o(HD);
+  for (int b = 0; b < B; ++b) {
+    const int nq = cu_q[b + 1] - cu_q[b], L = kv_lens[b], prefix = prefix_lens ? prefix_lens[b] : 0;
+    for (int i = 0; i < nq; ++i)
+      for (int h = 0; h < hq; ++h) {
+        const int t = cu_q[b] + i, qp = L - nq + i, kvh = std::min((h + q_off) / group, hkv - 1);
+        const uint16_t* qv = bfp(q) + ((size_t)t * hq + h) * HD;
+        sc.assign(L, -INFINITY);
+        float mx = -INFINITY;
+        for (int key = 0; key < L; ++key) {
+          if (!(key <= qp || key < prefix)) continue;
+          const size_t row = ((size_t)block_table[(size_t)b * bt_stride + key / bs] * hkv + kvh) * bs + key % bs;
+          float a = 0.f;
+          if (int8) { const int8_t* kr = static_cast<const int8_t*>(kc) + row * HD; for (int d = 0; d < HD; ++d) a += bf(qv[d]) * kr[d]; a *= ks[row]; }
+          else { const uint16_t* kr = bfp(kc) + row * HD; for (int d = 0; d < HD; ++d) a += bf(qv[d]) * bf(kr[d]); }
+          a *= scale;
+          if (slopes) a += slopes[h] * (float)(key - qp);
+          sc[key] = a; mx = std::max(mx, a);
+        }
+        float den = 0.f;
+        std::fill(o.begin(), o.end(), 0.f);
+        for (int key = 0; key < L; ++key) {
+          if (sc[key] == -INFINITY) continue;
+          const float pw = std::exp(sc[key] - mx);
+          den += pw;
+          const size_t row = ((size_t)block_table[(size_t)b * bt_stride + key / bs] * hkv + kvh) * bs + key % bs;
+          if (int8) { const int8_t* vr = static_cast<const int8_t*>(vc) + row * HD; for (int d = 0; d < HD; ++d) o[d] += pw * vs[row] * vr[d]; }
+          else { const uint16_t* vr = bfp(vc) + row * HD; for (int d = 0; d < HD; ++d) o[d] += pw * bf(vr[d]); }
+        }
+        for (int d = 0; d < HD; ++d) bfp(out)[((size_t)t * hq + h) * HD + d] = tobf(o[d] / den);
+      }
+  }
   return 0;
 }
 
@@ -237,6 +441,12 @@ int xft_transpose_to_bf16(const void* src, int dtype, long long ld_src, int rows
   const size_t esz = dtype == 0 ? 4 : 2;
   rdRows(src, rows, cols, ld_src, esz);
   wrRows(dst, cols, rows, ld_dst, 2);
+  for (int r = 0; r < rows; ++r)             // real in both modes: weights pass through here at load
+    for (int c = 0; c < cols; ++c) {
+      const size_t i = (size_t)r * ld_src + c;
+      const float f = dtype == 0 ? static_cast<const float*>(src)[i] : dtype == 1 ? halfToFloat(bfp(src)[i]) : bf(bfp(src)[i]);
+      bfp(dst)[(size_t)c * ld_dst + r] = tobf(f);
+    }
   return 0;
 }
 
@@ -244,6 +454,10 @@ int xft_fp8_block_dequant(const void* src, const float* scale, long long rows, i
   rd(src, (size_t)rows * cols);
   rd(scale, (size_t)((rows + block - 1) / block) * ((cols + block - 1) / block) * 4);
   wr(dst, (size_t)rows * cols * 2);
+  const int sc_cols = (cols + block - 1) / block;
+  for (long long r = 0; r < rows; ++r)
+    for (int c = 0; c < cols; ++c)
+      bfp(dst)[r * cols + c] = tobf(e4m3ToFloat(static_cast<const uint8_t*>(src)[r * cols + c]) * scale[(r / block) * sc_cols + c / block]);
   return 0;
 }
 
@@ -311,24 +525,78 @@ int xft_w8a8_gemm(const void* qx, int ldqx, const void* Wq, int ldw, void* Y, in
   return 0;
 }
 
-int xft_gated_act(const void* gu, void* out, int T, int I, int, cudaStream_t) {
+int xft_gated_act(const void* gu, void* out, int T, int I, int act, cudaStream_t) {
   rdRows(gu, T, 2LL * I, 2LL * I, 2);
   wrRows(out, T, I, I, 2);
+  if (g_math)
+    for (int t = 0; t < T; ++t)
+      for (int c = 0; c < I; ++c)
+        bfp(out)[(size_t)t * I + c] = tobf(actf(bf(bfp(gu)[(size_t)t * 2 * I + c]), act) * bf(bfp(gu)[(size_t)t * 2 * I + I + c]));
   return 0;
 }
 
 // ---- routed experts: these three produce real results, the host logic and the later stand-ins depend on them
-int xft_moe_route(const float* logits, int ld, int T, int E, int k, int, const float* bias, int n_group, int topk_group, float, int,
-                  int, int* idx, float* w, cudaStream_t) {
+int xft_moe_route(const float* logits, int ld, int T, int E, int k, int kind, const float* bias, int n_group, int topk_group,
+                  float scaling, int norm_topk, int sigmoid, int* idx, float* w, cudaStream_t) {
   need(k >= 1 && k <= E && n_group >= 1 && topk_group >= 1 && topk_group <= n_group && E % n_group == 0, "route: bad configuration");
   rdRows(logits, T, E, ld, 4);
   if (bias) rd(bias, (size_t)E * 4);
+  std::vector<float> score(E), sel(E);
   for (int t = 0; t < T; ++t) {
-    // top k by value (first index wins ties): distinct, valid expert ids
-    std::vector<int> order(E);
-    for (int e = 0; e < E; ++e) order[e] = e;
-    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return logits[(size_t)t * ld + a] > logits[(size_t)t * ld + b]; });
-    for (int j = 0; j < k; ++j) { idx[(size_t)t * k + j] = order[j]; w[(size_t)t * k + j] = 1.0f / k; }
+    const float* x = logits + (size_t)t * ld;
+    if (!g_math) {
+      // top k by value (first index wins ties): distinct, valid expert ids
+      std::vector<int> order(E);
+      for (int e = 0; e < E; ++e) order[e] = e;
+      std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return x[a] > x[b]; });
+      for (int j = 0; j < k; ++j) { idx[(size_t)t * k + j] = order[j]; w[(size_t)t * k + j] = 1.0f / k; }
+      continue;
+    }
+    // kind 0: softmax over the k best logits; 1: softmax over all, k best, renormalised; 2: softmax or sigmoid scores,
+    // selection on score + bias inside the best groups, weights from the unbiased scores
+    if (kind == 0) {
+      for (int e = 0; e < E; ++e) score[e] = sel[e] = x[e];
+    } else {
+      const bool softmax = kind == 1 || !sigmoid;
+      float mx = -INFINITY, sum = 0.f;
+      for (int e = 0; e < E; ++e) mx = std::max(mx, x[e]);
+      for (int e = 0; e < E; ++e) { score[e] = softmax ? std::exp(x[e] - mx) : 1.f / (1.f + std::exp(-x[e])); sum += score[e]; }
+      for (int e = 0; e < E; ++e) { if (softmax) score[e] /= sum; sel[e] = score[e] + ((kind == 2 && bias) ? bias[e] : 0.f); }
+    }
+    if (kind == 2 && n_group > 1) {
+      const int gsz = E / n_group;
+      std::vector<float> gs(n_group);
+      for (int g = 0; g < n_group; ++g) {
+        float a = -INFINITY, b = -INFINITY;
+        for (int i = 0; i < gsz; ++i) { const float v = sel[g * gsz + i]; if (v > a) { b = a; a = v; } else if (v > b) b = v; }
+        gs[g] = a + b;
+      }
+      std::vector<char> keep(n_group, 0);
+      for (int j = 0; j < topk_group; ++j) {
+        int bi = -1; float bv = -INFINITY;
+        for (int g = 0; g < n_group; ++g) if (!keep[g] && (bi < 0 || gs[g] > bv)) { bv = gs[g]; bi = g; }
+        keep[bi] = 1;
+      }
+      for (int e = 0; e < E; ++e) if (!keep[e / gsz]) sel[e] = -INFINITY;
+    }
+    float wsum = 0.f;
+    for (int j = 0; j < k; ++j) {
+      int bi = 0; float bv = sel[0];                      // lowest index wins ties
+      for (int e = 1; e < E; ++e) if (sel[e] > bv) { bv = sel[e]; bi = e; }
+      idx[(size_t)t * k + j] = bi; w[(size_t)t * k + j] = score[bi]; wsum += score[bi];
+      sel[bi] = -INFINITY;
+    }
+    float* wt = w + (size_t)t * k;
+    if (kind == 0) {
+      float mx = -INFINITY, den = 0.f;
+      for (int j = 0; j < k; ++j) mx = std::max(mx, wt[j]);
+      for (int j = 0; j < k; ++j) den += std::exp(wt[j] - mx);
+      for (int j = 0; j < k; ++j) wt[j] = std::exp(wt[j] - mx) / den;
+    } else if (kind == 1) {
+      if (norm_topk) for (int j = 0; j < k; ++j) wt[j] /= wsum;
+    } else {
+      for (int j = 0; j < k; ++j) wt[j] = (norm_topk ? wt[j] / (wsum + 1e-20f) : wt[j]) * scaling;
+    }
   }
   return 0;
 }
@@ -362,13 +630,14 @@ int xft_moe_gather(const void* x, int ldx, const int* src_tok, const int* meta, 
   for (int r = 0; r < meta[1]; ++r) {
     rd(static_cast<const char*>(x) + (size_t)src_tok[r] * ldx * 2, (size_t)H * 2);
     wr(static_cast<char*>(xs) + (size_t)r * H * 2, (size_t)H * 2);
+    std::memcpy(static_cast<char*>(xs) + (size_t)r * H * 2, static_cast<const char*>(x) + (size_t)src_tok[r] * ldx * 2, (size_t)H * 2);
   }
   return 0;
 }
 
 int xft_gemm_bf16_grouped(const void* X, int ldx, int x_rows, const void* W, int w_rows, int ldw, void* Y, int ldo, int out_fp32,
                           int N, int K, int gated, int dual_off, int group_w_rows, const void* group_tiles,
-                          const int* num_group_tiles, int max_tiles, int bn, const float* col_scale, int, int* status, cudaStream_t) {
+                          const int* num_group_tiles, int max_tiles, int bn, const float* col_scale, int act, int* status, cudaStream_t) {
   const int* tl = static_cast<const int*>(group_tiles);
   const int nt = num_group_tiles[0];
   need(nt <= max_tiles, "grouped gemm: tile count beyond the table");
@@ -381,6 +650,18 @@ int xft_gemm_bf16_grouped(const void* X, int ldx, int x_rows, const void* W, int
     rdRows(static_cast<const char*>(W) + (size_t)g * group_w_rows * ldw * 2, rows_w, K, ldw, 2);
     if (col_scale) rd(col_scale + r0, (size_t)nr * 4);
     wrRows(static_cast<char*>(Y) + (size_t)r0 * ldo * (out_fp32 ? 4 : 2), nr, N, ldo, out_fp32 ? 4 : 2);
+    if (!g_math) continue;
+    std::vector<float> acc;
+    for (int r = r0; r < r0 + nr; ++r) {
+      dots(bfp(X) + (size_t)r * ldx, K, bfp(W) + (size_t)g * group_w_rows * ldw, ldw, rows_w, acc);
+      for (int n = 0; n < N; ++n) {
+        float x = actf(acc[n], act);
+        if (gated) x *= acc[dual_off + n];
+        if (col_scale) x *= col_scale[r];
+        if (out_fp32) static_cast<float*>(Y)[(size_t)r * ldo + n] = x;
+        else bfp(Y)[(size_t)r * ldo + n] = tobf(x);
+      }
+    }
   }
   if (status) rd(status, 4);
   return 0;
@@ -391,14 +672,22 @@ int xft_moe_combine(const float* ys, const int* pos, int k, const float* add1, c
   for (int i = 0; i < T * k; ++i) if (pos[i] >= 0) rd(ys + (size_t)pos[i] * H, (size_t)H * 4);
   if (add1) rd(add1, (size_t)T * H * 4);
   if (add2) rdRows(add2, T, H, ld2, 2);
-  if (y32) wr(y32, (size_t)T * H * 4); else wrRows(y, T, H, H, 2);
+  if (!g_math) { if (y32) wr(y32, (size_t)T * H * 4); else wrRows(y, T, H, H, 2); return 0; }
+  for (int t = 0; t < T; ++t)                     // y may alias add2: element by element
+    for (int i = 0; i < H; ++i) {
+      float a = 0.f;
+      for (int j = 0; j < k; ++j) if (pos[(size_t)t * k + j] >= 0) a += ys[(size_t)pos[(size_t)t * k + j] * H + i];
+      if (add1) a += add1[(size_t)t * H + i];
+      if (add2) a += bf(bfp(add2)[(size_t)t * ld2 + i]);
+      if (y32) y32[(size_t)t * H + i] = a; else bfp(y)[(size_t)t * H + i] = tobf(a);
+    }
   return 0;
 }
 
 // ---- latent attention
 int xft_mla_prep(const void* q, int ldq, const void* kv, int ldkv, int T, int Hl, int nope, int rope, int kvl, const int* positions,
-                 const float* table, int max_pos, const float* kv_norm_w, float, void* q_nope, void* q_rope, void* cache,
-                 long long nslots, const int* slots, int*, int, cudaStream_t) {
+                 const float* table, int max_pos, const float* kv_norm_w, float eps, void* q_nope, void* q_rope, void* cache,
+                 long long nslots, const int* slots, int*, int nope_head_major, cudaStream_t) {
   rdRows(q, T, (long long)Hl * (nope + rope), ldq, 2);
   rdRows(kv, T, kvl + rope, ldkv, 2);
   rd(kv_norm_w, (size_t)kvl * 4);
@@ -410,12 +699,39 @@ int xft_mla_prep(const void* q, int ldq, const void* kv, int ldkv, int T, int Hl
   }
   wr(q_nope, (size_t)T * Hl * nope * 2);
   wr(q_rope, (size_t)T * Hl * rope * 2);
+  if (!g_math) return 0;
+  const int half = rope / 2;
+  for (int t = 0; t < T; ++t) {
+    const float* cs = table + (size_t)positions[t] * rope;
+    for (int h = 0; h < Hl; ++h) {
+      const uint16_t* src = bfp(q) + (size_t)t * ldq + (size_t)h * (nope + rope);
+      uint16_t* dn = bfp(q_nope) + (nope_head_major ? (size_t)h * T + t : (size_t)t * Hl + h) * nope;
+      std::memcpy(dn, src, (size_t)nope * 2);
+      uint16_t* dr = bfp(q_rope) + ((size_t)t * Hl + h) * rope;
+      for (int i = 0; i < half; ++i) {
+        const float x1 = bf(src[nope + 2 * i]), x2 = bf(src[nope + 2 * i + 1]);
+        dr[2 * i] = tobf(x1 * cs[i] - x2 * cs[half + i]);
+        dr[2 * i + 1] = tobf(x2 * cs[i] + x1 * cs[half + i]);
+      }
+    }
+    const uint16_t* src = bfp(kv) + (size_t)t * ldkv;
+    uint16_t* dst = bfp(cache) + (size_t)slots[t] * (kvl + rope);
+    float ss = 0.f;
+    for (int d = 0; d < kvl; ++d) ss += bf(src[d]) * bf(src[d]);
+    const float inv = 1.f / std::sqrt(ss / kvl + eps);
+    for (int d = 0; d < kvl; ++d) dst[d] = tobf(bf(src[d]) * inv * kv_norm_w[d]);
+    for (int i = 0; i < half; ++i) {
+      const float x1 = bf(src[kvl + 2 * i]), x2 = bf(src[kvl + 2 * i + 1]);
+      dst[kvl + 2 * i] = tobf(x1 * cs[i] - x2 * cs[half + i]);
+      dst[kvl + 2 * i + 1] = tobf(x2 * cs[i] + x1 * cs[half + i]);
+    }
+  }
   return 0;
 }
 
 int xft_mla_attention(const void* q_abs, long long qa_sh, long long qa_st, const void* q_rope, long long qr_sh, long long qr_st,
                       void* out, long long o_sh, long long o_st, const void* cache, const int* block_table, int bt_stride,
-                      const int* cu_q, const int* kv_lens, int B, int T, int hl, int bs, int num_blocks, float, int nsplit,
+                      const int* cu_q, const int* kv_lens, int B, int T, int hl, int bs, int num_blocks, float scale, int nsplit,
                       float* part_o, float* part_ml, int* counters, int*, cudaStream_t) {
   const int L = 512, R = 64;
   need(cu_q[B] == T, "mla: token count mismatch");
@@ -440,18 +756,57 @@ int xft_mla_attention(const void* q_abs, long long qa_sh, long long qa_st, const
     wr(part_o, ctas * nsplit * 16 * L * 4);
     wr(part_ml, ctas * nsplit * 32 * 4);
   }
+  if (!g_math) return 0;
+  // S = q_abs . c_kv + q_rope . k_rope over the latent rows [c_kv (512) | k_rope (64)], causal; O = softmax(S) . c_kv
+  std::vector<float> sc, o(L);
+  for (int b = 0; b < B; ++b) {
+    const int nq = cu_q[b + 1] - cu_q[b], len = kv_lens[b];
+    for (int i = 0; i < nq; ++i)
+      for (int h = 0; h < hl; ++h) {
+        const int t = cu_q[b] + i, qp = len - nq + i;
+        const uint16_t* qa = bfp(q_abs) + (size_t)h * qa_sh + (size_t)t * qa_st;
+        const uint16_t* qr = bfp(q_rope) + (size_t)h * qr_sh + (size_t)t * qr_st;
+        sc.assign(qp + 1, 0.f);
+        float mx = -INFINITY;
+        for (int key = 0; key <= qp; ++key) {
+          const uint16_t* row = bfp(cache) + ((size_t)block_table[(size_t)b * bt_stride + key / bs] * bs + key % bs) * (L + R);
+          float a = 0.f;
+          for (int d = 0; d < L; ++d) a += bf(qa[d]) * bf(row[d]);
+          for (int d = 0; d < R; ++d) a += bf(qr[d]) * bf(row[L + d]);
+          sc[key] = a * scale; mx = std::max(mx, sc[key]);
+        }
+        float den = 0.f;
+        std::fill(o.begin(), o.end(), 0.f);
+        for (int key = 0; key <= qp; ++key) {
+          const uint16_t* row = bfp(cache) + ((size_t)block_table[(size_t)b * bt_stride + key / bs] * bs + key % bs) * (L + R);
+          const float pw = std::exp(sc[key] - mx);
+          den += pw;
+          for (int d = 0; d < L; ++d) o[d] += pw * bf(row[d]);
+        }
+        uint16_t* dst = bfp(out) + (size_t)h * o_sh + (size_t)t * o_st;
+        for (int d = 0; d < L; ++d) dst[d] = tobf(o[d] / den);
+      }
+  }
   return 0;
 }
 
 int xft_swap_outer_dims(const void* src, void* dst, int A, int B, int D, cudaStream_t) {
   rd(src, (size_t)A * B * D * 2);
   wr(dst, (size_t)A * B * D * 2);
+  for (int a = 0; a < A; ++a)
+    for (int b = 0; b < B; ++b)
+      std::memcpy(bfp(dst) + ((size_t)b * A + a) * D, bfp(src) + ((size_t)a * B + b) * D, (size_t)D * 2);
   return 0;
 }
 
 int xft_sum_bf16(void* dst, const void* const* srcs, int nsrc, size_t n, cudaStream_t) {
   for (int k = 0; k < nsrc; ++k) rd(srcs[k], n * 2);
-  wr(dst, n * 2);
+  if (!g_math) { wr(dst, n * 2); return 0; }
+  for (size_t i = 0; i < n; ++i) {                // dst may be one of the sources
+    float a = 0.f;
+    for (int k = 0; k < nsrc; ++k) a += bf(bfp(srcs[k])[i]);
+    bfp(dst)[i] = tobf(a);
+  }
   return 0;
 }
 }

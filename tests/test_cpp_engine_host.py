@@ -2,13 +2,18 @@
 shape over a host stand-in of the device library (csrc/tests/mock_device.cc) whose kernels touch exactly the memory the
 real ones read and write; AddressSanitizer + UndefinedBehaviorSanitizer + exact-size buffers (XFT_ARENA_EXACT) then check
 buffer sizes, strides, slot / block arithmetic and tensor-parallel ranges for every family, weight type and rank count,
-and that thread ranks produce the same tokens."""
+and that thread ranks produce the same tokens.  With the stand-in's arithmetic switched on (XFT_MOCK_MATH) the engine's
+logits are compared with the fp32 PyTorch path of the package, on one rank and on tensor-parallel thread ranks."""
 import os
 import shutil
 import subprocess
 import sys
 
+import struct
+
+import numpy as np
 import pytest
+import torch
 
 from xfastertransformer_b200.config import ModelConfig, RopeConfig
 
@@ -21,7 +26,7 @@ def hostcheck(tmp_path_factory):
     if shutil.which("g++") is None:
         pytest.skip("no g++")
     exe = str(tmp_path_factory.mktemp("hostcheck") / "engine_hostcheck")
-    cmd = ["g++", "-O1", "-g", "-std=c++17", "-fsanitize=address,undefined", "-fno-sanitize-recover=undefined",
+    cmd = ["g++", "-O2", "-g", "-std=c++17", "-fsanitize=address,undefined", "-fno-sanitize-recover=undefined",
            "-fno-omit-frame-pointer", "-I", os.path.join(ROOT, "csrc", "api"), "-I", os.path.join(ROOT, "csrc", "core"),
            "-I", "/usr/local/cuda/include", os.path.join(ROOT, "csrc", "tests", "engine_hostcheck.cc"),
            os.path.join(ROOT, "csrc", "tests", "mock_device.cc")] + [os.path.join(ROOT, "csrc", "core", f) for f in CORE] + \
@@ -69,8 +74,10 @@ def _config_dir(tmp_path, fam):
 def test_engine_host_side_every_family(hostcheck, fam, tmp_path):
     d = _config_dir(tmp_path, fam)
     _run(hostcheck, d, "bf16", "fp16", 1)
-    if fam in _DENSE:
-        _run(hostcheck, d, "bf16", "int8" if fam != "chatglm" else "fp16", 2)          # tensor parallel, two thread ranks
+    # two thread ranks: tensor-parallel attention and FFN; whole experts per rank for the routed families
+    _run(hostcheck, d, "bf16", "int8" if fam != "chatglm" else "fp16", 2)
+    if fam == "qwen3_moe":
+        _run(hostcheck, d, "bf16", "fp16", 4)                                          # 6 experts over 4 ranks: 2, 2, 1, 1
 
 
 @pytest.mark.parametrize("fam", ["llama", "chatglm2", "gpt"])
@@ -80,6 +87,19 @@ def test_engine_host_side_weight_types(hostcheck, fam, dtype, tmp_path):
     _run(hostcheck, d, dtype, "fp16", 1)
     if dtype in ("int8", "w8a8_nf4"):
         _run(hostcheck, d, dtype, "int8", 3)                                           # three ranks: uneven ranges
+
+
+def _deepseek_config(**kw):
+    base = dict(model_type="deepseek_moe", num_layer=3, hidden_size=256, head_num=4, kv_head_num=4, size_per_head=128,
+                inter_size=512, vocab_size=300, max_pos_seq_len=4096, q_lora_rank=64, kv_lora_rank=512,
+                qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, moe_intermediate_size=128,
+                first_k_dense_replace=1, dense_experts=1, sparse_experts=8, routed_scaling_factor=2.5,
+                topk_method="noaux_tc", n_group=1, topk_group=1, num_experts_per_tok=8, norm_topk_prob=True,
+                scoring_func="sigmoid", activation_type="silu", weight_data_type="bf16", start_id=0, end_id=1,
+                rope=RopeConfig(theta=10000, scaling_type="yarn", scaling_factor=40, original_max_pos=4096,
+                                beta_fast=32, beta_slow=1, mscale=1.0, mscale_all_dim=1.0))
+    base.update(kw)
+    return ModelConfig(**base)
 
 
 def test_engine_host_side_deepseek(hostcheck, tmp_path):
@@ -94,10 +114,13 @@ def test_engine_host_side_deepseek(hostcheck, tmp_path):
     d = str(tmp_path / "deepseek_moe")
     cfg.to_ini(d)
     _run(hostcheck, d, "bf16", "fp16", 1)
+    _run(hostcheck, d, "bf16", "fp16", 2)                       # heads, dense FFN, shared experts and experts split
+    _run(hostcheck, d, "bf16", "fp16", 4)                       # one head per rank; the narrow shared expert leaves ranks empty
     cfg.q_lora_rank = 0                                                                # no query compression
     d2 = str(tmp_path / "deepseek_moe_noq")
     cfg.to_ini(d2)
     _run(hostcheck, d2, "bf16", "fp16", 1)
+    _run(hostcheck, d2, "bf16", "fp16", 3)
 
 
 @pytest.mark.parametrize("qt,dtype", [("int8", "int8"), ("int8", "w8a8"), ("uint4", "int4"), ("uint4", "bf16_int8")])
@@ -109,3 +132,118 @@ def test_engine_host_side_gptq_checkpoint(hostcheck, qt, dtype, tmp_path):
     d = make_gptq_dir(str(tmp_path / "gptq"), cfg, qt, seed=1)
     _run(hostcheck, d, dtype, "fp16", 1, fake=False)
     _run(hostcheck, d, dtype, "fp16", 2, fake=False)
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# numerics: the C++ engine over the arithmetic stand-in against the package's fp32 PyTorch path
+
+def _engine_logits(exe, d, ranks, prompt, steps, kv="fp16", wdt="bf16"):
+    B, P = prompt.shape
+    idf, outf = os.path.join(d, "ids.txt"), os.path.join(d, "logits.%d.bin" % ranks)
+    with open(idf, "w") as f:
+        f.write("%d %d %d\n" % (B, P, steps) + " ".join(str(int(x)) for x in prompt.flatten().tolist()) + "\n")
+    env = dict(os.environ, XFT_MOCK_MATH="1", XFT_ARENA_EXACT="1", ASAN_OPTIONS="detect_leaks=1")
+    env.pop("XFT_FAKE_MODEL", None)
+    r = subprocess.run([exe, "logits", d, wdt, kv, str(ranks), idf, outf], env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0 and "hostcheck logits ok" in r.stdout, (d, ranks, r.stdout[-500:], r.stderr[-3000:])
+    raw = open(outf, "rb").read()
+    b, v, n = struct.unpack("iii", raw[:12])
+    lg = np.frombuffer(raw, dtype=np.float32, count=n * b * v, offset=12).reshape(n, b, v)
+    tk = np.frombuffer(raw, dtype=np.int32, count=n * b, offset=12 + 4 * n * b * v).reshape(n, b)
+    return torch.from_numpy(lg.copy()), torch.from_numpy(tk.copy())
+
+
+def _oracle_logits(d, prompt, tokens, monkeypatch):
+    """Teacher-forced logits [steps + 1, B, V] of the PyTorch path: the prompt, then the engine's tokens one at a time."""
+    import xfastertransformer_b200 as xft
+    from xfastertransformer_b200.parallel.dist import DistContext
+    from xfastertransformer_b200.utils.flags import Env
+    monkeypatch.setenv("XFT_ENGINE", "CPU")
+    Env._inst = None
+    DistContext.reset()
+    try:
+        m = xft.AutoModel.from_pretrained(d, dtype="bf16")
+        P, steps = prompt.shape[1], tokens.shape[0] - 1
+        sid = m.set_input_cb(prompt.tolist(), None, P + steps + 2)
+        rows = [m.forward_cb().float()]
+        for s in range(steps):
+            m.set_input_cb(tokens[s].tolist(), sid, P + steps + 2)
+            rows.append(m.forward_cb().float())
+        m.free_seqs(sid)
+        return torch.stack(rows, 0)
+    finally:
+        monkeypatch.delenv("XFT_ENGINE")
+        Env._inst = None
+        DistContext.reset()
+
+
+_NUMERIC = dict(_FAMILIES)
+# every expert selected: no discrete routing decision that a last-bit difference could flip
+_NUMERIC["mixtral"] = dict(sparse_experts=4, num_experts_per_tok=4)
+_NUMERIC["qwen3_moe"] = dict(sparse_experts=4, num_experts_per_tok=4, moe_intermediate_size=128, do_qk_norm=True)
+_NUMERIC["mixtral-top2"] = dict(sparse_experts=6, num_experts_per_tok=2)
+
+
+def _synthetic_dir(tmp_path, fam, extra):
+    from xfastertransformer_b200.tools.synthetic import write_synthetic_checkpoint
+    kw = dict(_BASE, model_type=fam.split("-")[0])
+    kw.update(extra)
+    cfg = ModelConfig(**kw)
+    if fam == "yarn_llama":
+        cfg.rope.scaling_type, cfg.rope.scaling_factor, cfg.rope.original_max_pos = "yarn", 4.0, 128
+    d = str(tmp_path / fam)
+    write_synthetic_checkpoint(d, cfg, seed=3, dtype="bf16", std=0.08)
+    return d
+
+
+@pytest.mark.parametrize("fam", sorted(_NUMERIC))
+def test_engine_logits_match_pytorch(hostcheck, fam, tmp_path, monkeypatch):
+    """Prompt pass and four decode steps of every family: logits of the C++ engine (bf16 roundings where the kernels round)
+    within a bf16 tolerance of the fp32 PyTorch path, on one rank and on tensor-parallel thread ranks; ranks among
+    themselves must agree bit for bit (the harness checks that)."""
+    d = _synthetic_dir(tmp_path, fam, _NUMERIC[fam])
+    prompt = torch.randint(5, 290, (2, 20), generator=torch.Generator().manual_seed(4))
+    steps = 4
+    plans = ((1, "fp16"), (2, "fp16"), (3 if fam in ("llama", "chatglm4", "gpt") else 2, "int8"))
+    for ranks, kv in plans:
+        got, tokens = _engine_logits(hostcheck, d, ranks, prompt, steps, kv=kv)
+        want = _oracle_logits(d, prompt, tokens, monkeypatch)
+        top = max(1.0, want.abs().max().item())
+        err = (got - want).abs().amax(-1)                   # [steps + 1, B]
+        if fam == "mixtral-top2":
+            # a near-tie may send a token to another expert: most rows must agree tightly
+            assert (err < 0.04 * top).float().mean().item() >= 0.7, (fam, ranks, err.tolist(), top)
+        elif fam in ("mixtral", "qwen3_moe"):
+            # the expert layers of these random models amplify rounding differences on some rows (the same rows move by
+            # as much when the stand-in rounds differently), so: most rows tight, every row bounded
+            assert err.median().item() < 0.03 * top and err.max().item() < 0.15 * top, (fam, ranks, err.tolist(), top)
+        else:
+            assert err.max().item() < (0.04 if kv == "fp16" else 0.08) * top, (fam, ranks, kv, err.tolist(), top)
+
+
+@pytest.mark.parametrize("case", ["bf16", "fp8_e4m3", "no-q-lora", "grouped"])
+def test_engine_logits_match_pytorch_deepseek(hostcheck, case, tmp_path, monkeypatch):
+    """DeepSeek (latent attention, YaRN table, dense first layer, shared + routed experts; e4m3 files dequantised at load)
+    on 1, 2 and 3 or 4 thread ranks against the fp32 PyTorch path.  "grouped" routes 4 of 16 experts out of the 2 best of
+    4 groups: a near-tie may pick another expert for a token, so there most rows must agree tightly."""
+    from xfastertransformer_b200.tools.synthetic import write_synthetic_checkpoint
+    kw = {}
+    if case == "fp8_e4m3":
+        kw["weight_data_type"] = "fp8_e4m3"
+    if case == "no-q-lora":
+        kw["q_lora_rank"] = 0
+    if case == "grouped":
+        kw.update(sparse_experts=16, n_group=4, topk_group=2, num_experts_per_tok=4)
+    cfg = _deepseek_config(**kw)
+    d = str(tmp_path / "ds")
+    write_synthetic_checkpoint(d, cfg, seed=0, dtype=cfg.weight_data_type, std=0.05)
+    prompt = torch.randint(0, 300, (2, 20), generator=torch.Generator().manual_seed(3))
+    for ranks in (1, 2, 3 if case == "no-q-lora" else 4):
+        got, tokens = _engine_logits(hostcheck, d, ranks, prompt, 3)
+        want = _oracle_logits(d, prompt, tokens, monkeypatch)
+        top = max(1.0, want.abs().max().item())
+        err = (got - want).abs().amax(-1)
+        if case == "grouped":
+            assert (err < 0.04 * top).float().mean().item() >= 0.6, (case, ranks, err.tolist(), top)
+        else:
+            assert err.max().item() < 0.04 * top, (case, ranks, err.tolist(), top)
