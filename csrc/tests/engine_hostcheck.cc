@@ -14,6 +14,12 @@
 // int32, the logits of every pass [steps + 1, B, V] as fp32 and the token chosen after each pass [steps + 1, B] as int32.
 //
 //   engine_hostcheck logits <model dir> <weight type> <kv type> <ranks> <ids file> <out file>
+//
+// A third form runs the batch generation calls (config / input / generate / finalize) with `beams` beams and writes the
+// rows that finalize() returns: B, row length as int32, then the rows.  `steps` of the ids file is the number of new
+// tokens, eos is token `eos` (-1: none).
+//
+//   engine_hostcheck generate <model dir> <weight type> <kv type> <ranks> <ids file> <out file> <beams> <eos>
 #include <cstdio>
 #include <cstdlib>
 #include <stdexcept>
@@ -158,7 +164,21 @@ void recordLogits(xft::Model& m, LogitsRun& run) {
   CHECK(m.freeSeqs(seqs));
 }
 
+void recordGenerate(xft::Model& m, LogitsRun& run, int beams, int eos) {
+  run.V = m.getVocabSize();
+  const int maxLen = run.P + run.steps;
+  m.config(maxLen, beams, 1, 1.0f, false, eos < 0 ? run.V + 5 : eos, 0);
+  m.input(run.ids, run.B);
+  int guard = 0;
+  while (!m.isDone() && guard++ <= run.steps) m.generate();
+  CHECK(m.isDone());
+  run.tokens = m.finalize();
+  CHECK(!run.tokens.empty() && run.tokens.size() % run.B == 0);
+}
+
 int logitsMain(int argc, char** argv) {
+  const bool gen = std::string(argv[1]) == "generate";
+  const int beams = gen && argc >= 9 ? std::atoi(argv[8]) : 1, eos = gen && argc >= 10 ? std::atoi(argv[9]) : -1;
   if (argc < 8) { std::fprintf(stderr, "usage: engine_hostcheck logits <model dir> <weight type> <kv type> <ranks> <ids file> <out file>\n"); return 2; }
   const std::string dir = argv[2];
   const xft::DataType wdt = xft::dataTypeFromName(argv[3]);
@@ -177,7 +197,7 @@ int logitsMain(int argc, char** argv) {
   std::vector<std::string> errors(ranks);
   if (ranks == 1) {
     xft::AutoModel m(dir, wdt, kdt, nullptr);
-    recordLogits(m, runs[0]);
+    if (gen) recordGenerate(m, runs[0], beams, eos); else recordLogits(m, runs[0]);
   } else {
     auto comms = xft::makeThreadCommunicators(ranks);
     std::vector<std::thread> threads;
@@ -186,7 +206,7 @@ int logitsMain(int argc, char** argv) {
         try {
           comms[r]->begin();
           xft::AutoModel m(dir, wdt, kdt, comms[r]);
-          recordLogits(m, runs[r]);
+          if (gen) recordGenerate(m, runs[r], beams, eos); else recordLogits(m, runs[r]);
         } catch (const std::exception& e) {
           errors[r] = e.what();
         }
@@ -202,6 +222,14 @@ int logitsMain(int argc, char** argv) {
     if (runs[r].logits != runs[0].logits || runs[r].tokens != runs[0].tokens) { std::fprintf(stderr, "rank %d sees other logits than rank 0\n", r); return 1; }
   FILE* f = std::fopen(argv[7], "wb");
   if (!f) { std::fprintf(stderr, "cannot write %s\n", argv[7]); return 2; }
+  if (gen) {
+    const int32_t head[2] = {runs[0].B, (int32_t)(runs[0].tokens.size() / runs[0].B)};
+    std::fwrite(head, 4, 2, f);
+    std::fwrite(runs[0].tokens.data(), 4, runs[0].tokens.size(), f);
+    std::fclose(f);
+    std::printf("hostcheck generate ok: %d ranks, %d rows of %d\n", ranks, head[0], head[1]);
+    return 0;
+  }
   const int32_t head[3] = {runs[0].B, runs[0].V, runs[0].steps + 1};
   std::fwrite(head, 4, 3, f);
   std::fwrite(runs[0].logits.data(), 4, runs[0].logits.size(), f);
@@ -214,7 +242,7 @@ int logitsMain(int argc, char** argv) {
 }  // namespace
 
 int main(int argc, char** argv) {
-  if (argc >= 2 && std::string(argv[1]) == "logits") {
+  if (argc >= 2 && (std::string(argv[1]) == "logits" || std::string(argv[1]) == "generate")) {
     try { return logitsMain(argc, argv); } catch (const std::exception& e) { std::fprintf(stderr, "error: %s\n", e.what()); return 1; }
   }
   if (argc < 5) { std::fprintf(stderr, "usage: engine_hostcheck <model dir> <weight type> <kv type> <ranks>\n"); return 2; }

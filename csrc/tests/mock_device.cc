@@ -17,7 +17,8 @@
 // attention steps, the sum of the thread-rank all-reduce.  The engine's logits can then be compared, on a CPU box, with
 // the PyTorch fp32 path of the package for every family, and tensor-parallel ranks with a single rank: that checks what
 // the touch checks cannot — which rows of which file went where, offsets of heads and experts, position tables.  The
-// quantised GEMMs stay touch-only.
+// load-time quantiser and the quantised GEMMs (int8 / uint4 / NF4 weight-only, int8 x int8) follow the kernels' formulas
+// too, so quantised and GPTQ checkpoints are compared the same way.
 #include <cuda_runtime.h>
 
 #include <algorithm>
@@ -91,6 +92,10 @@ inline float actf(float x, int act) {
     default: return x;
   }
 }
+const float kNf4Code[16] = {-1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,
+                            -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
+                            0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f,
+                            0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
 inline const uint16_t* bfp(const void* p) { return static_cast<const uint16_t*>(p); }
 inline uint16_t* bfp(void* p) { return static_cast<uint16_t*>(p); }
 
@@ -470,12 +475,52 @@ int xft_quantize_rows(const void* w, int dtype, long long ldw, int rows, int K, 
   wr(scale, (size_t)rows * 4);
   wr(zero, (size_t)rows * 4);
   if (wsum) wr(wsum, (size_t)rows * 4);
+  if (!g_math) return 0;
+  // mode 0: int8, scale = (max - min) / 255, zero = (max + min) / 2 + scale / 2, code in [-128, 127]; mode 1: uint4,
+  // scale = (max - min) / 15, zero = min; mode 2: NF4, scale = max|w|, nearest code (first on ties); low nibble first
+  auto at = [&](int r, int i) {
+    const size_t k = (size_t)r * ldw + i;
+    return dtype == 0 ? static_cast<const float*>(w)[k] : dtype == 1 ? halfToFloat(bfp(w)[k]) : bf(bfp(w)[k]);
+  };
+  for (int r = 0; r < rows; ++r) {
+    float mx = -INFINITY, mn = INFINITY;
+    for (int i = 0; i < K; ++i) { const float v = at(r, i); mx = std::max(mx, mode == 2 ? std::fabs(v) : v); mn = std::min(mn, v); }
+    float sc, zp;
+    if (mode == 0) { sc = std::max((mx - mn) / 255.0f, 1e-10f); zp = (mx + mn) * 0.5f + 0.5f * sc; }
+    else if (mode == 1) { sc = std::max((mx - mn) / 15.0f, 1e-10f); zp = mn; }
+    else { sc = std::max(mx, 1e-10f); zp = 0.f; }
+    scale[r] = sc; zero[r] = zp;
+    uint8_t* dst = static_cast<uint8_t*>(q) + (size_t)r * ldq_bytes;
+    if (mode == 0) {
+      int acc = 0;
+      for (int i = 0; i < K; ++i) {
+        const int c = (int)std::min(std::max(std::nearbyint((at(r, i) - zp) / sc), -128.f), 127.f);
+        reinterpret_cast<int8_t*>(dst)[i] = (int8_t)c; acc += c;
+      }
+      if (wsum) wsum[r] = (float)acc;
+      continue;
+    }
+    for (int i = 0; i < K / 2; ++i) {
+      int code[2];
+      for (int j = 0; j < 2; ++j) {
+        const float v = at(r, 2 * i + j);
+        if (mode == 1) { code[j] = (int)std::min(std::max(std::nearbyint((v - zp) / sc), 0.f), 15.f); continue; }
+        const float xn = v / sc;
+        int best = 0; float bd = std::fabs(xn - kNf4Code[0]);
+        for (int c = 1; c < 16; ++c) { const float d = std::fabs(xn - kNf4Code[c]); if (d < bd) { bd = d; best = c; } }
+        code[j] = best;
+      }
+      dst[i] = (uint8_t)(code[0] | (code[1] << 4));
+    }
+  }
   return 0;
 }
 
 int xft_row_sum(const void* x, int ldx, float* out, int T, int K, cudaStream_t) {
   rdRows(x, T, K, ldx, 2);
   wr(out, (size_t)T * 4);
+  if (g_math)
+    for (int t = 0; t < T; ++t) { float a = 0.f; for (int i = 0; i < K; ++i) a += bf(bfp(x)[(size_t)t * ldx + i]); out[t] = a; }
   return 0;
 }
 
@@ -483,13 +528,25 @@ int xft_quant_act(const void* x, int ldx, void* q, int ldq, float* scale, float*
   rdRows(x, T, K, ldx, 2);
   wrRows(q, T, K, ldq, 1);
   wr(scale, (size_t)T * 4); wr(zero, (size_t)T * 4); wr(qsum, (size_t)T * 4);
+  if (!g_math) return 0;
+  for (int t = 0; t < T; ++t) {            // zero = (min + max) / 2, scale = max|x - zero| / 127
+    float mx = -INFINITY, mn = INFINITY;
+    for (int i = 0; i < K; ++i) { const float v = bf(bfp(x)[(size_t)t * ldx + i]); mx = std::max(mx, v); mn = std::min(mn, v); }
+    const float z = 0.5f * (mx + mn), sc = std::max(std::max(mx - z, z - mn) / 127.f, 1e-10f), inv = 1.f / sc;
+    float acc = 0.f;
+    for (int i = 0; i < K; ++i) {
+      const float r = std::min(std::max(std::nearbyint((bf(bfp(x)[(size_t)t * ldx + i]) - z) * inv), -127.f), 127.f);
+      static_cast<int8_t*>(q)[(size_t)t * ldq + i] = (int8_t)r; acc += r;
+    }
+    scale[t] = sc; zero[t] = z; qsum[t] = acc;
+  }
   return 0;
 }
 
 int xft_qgemm(const void* X, int ldx, const void* Wq, int w_rows, int ldw_bytes, int qtype, void* Y, int ldo, int out_fp32, int T,
               int N, int K, int gated, int dual_off, const float* scale, const float* zero, const float* xsum, int, const float* bias,
-              const void* residual, int ldr, float, int, float* ws, size_t ws_bytes, int* counters, int n_counters, int* status,
-              cudaStream_t) {
+              const void* residual, int ldr, float res_scale, int act, float* ws, size_t ws_bytes, int* counters, int n_counters,
+              int* status, cudaStream_t) {
   const int rows = gated ? dual_off + N : N;
   need(w_rows >= rows, "qgemm: weight has fewer rows than outputs");
   need(qtype == 0 || qtype == 1 || qtype == 2, "qgemm: weight type not used by the engine");
@@ -503,14 +560,38 @@ int xft_qgemm(const void* X, int ldx, const void* Wq, int w_rows, int ldw_bytes,
   if (ws) rd(reinterpret_cast<char*>(ws) + ws_bytes - 1, 1);
   if (counters) rd(counters, (size_t)n_counters * 4);
   if (status) rd(status, 4);
-  wrRows(Y, T, N, ldo, out_fp32 ? 4 : 2);
+  if (!g_math) { wrRows(Y, T, N, ldo, out_fp32 ? 4 : 2); return 0; }
+  // the codes (NF4: the code book rounded to bf16) meet bf16 activations with fp32 sums; scale and zero act on the sums:
+  // y = act(scale[n] * acc + zero[n] * sum_k x + bias[n]) [* (the same for the up rows)] + res_scale * residual
+  std::vector<float> wf((size_t)rows * K), xf(K), out(N);
+  for (int n = 0; n < rows; ++n) {
+    const uint8_t* wr_ = static_cast<const uint8_t*>(Wq) + (size_t)n * ldw_bytes;
+    for (int k = 0; k < K; ++k) {
+      if (qtype == 0) { wf[(size_t)n * K + k] = (float)reinterpret_cast<const int8_t*>(wr_)[k]; continue; }
+      const int code = (wr_[k / 2] >> (4 * (k & 1))) & 15;
+      wf[(size_t)n * K + k] = qtype == 2 ? rbf(kNf4Code[code]) : (float)code;
+    }
+  }
+  for (int t = 0; t < T; ++t) {
+    for (int k = 0; k < K; ++k) xf[k] = bf(bfp(X)[(size_t)t * ldx + k]);
+    const float xs = (zero && xsum) ? xsum[t] : 0.f;
+    auto dot = [&](int n) { float a = 0.f; for (int k = 0; k < K; ++k) a += xf[k] * wf[(size_t)n * K + k]; return a; };
+    for (int n = 0; n < N; ++n) {
+      float x = actf(dot(n) * scale[n] + (zero ? zero[n] : 0.f) * xs + (bias ? bias[n] : 0.f), act);
+      if (gated) x *= dot(dual_off + n) * scale[dual_off + n] + (zero ? zero[dual_off + n] : 0.f) * xs + (bias ? bias[dual_off + n] : 0.f);
+      if (residual) x += res_scale * bf(bfp(residual)[(size_t)t * ldr + n]);
+      out[n] = x;
+    }
+    for (int n = 0; n < N; ++n)
+      if (out_fp32) static_cast<float*>(Y)[(size_t)t * ldo + n] = out[n]; else bfp(Y)[(size_t)t * ldo + n] = tobf(out[n]);
+  }
   return 0;
 }
 
 int xft_w8a8_gemm(const void* qx, int ldqx, const void* Wq, int ldw, void* Y, int ldo, int out_fp32, int T, int N, int K,
                   const float* a_scale, const float* a_zero, const float* a_qsum, const float* w_scale, const float* w_zero,
-                  const float* w_sum, const float* bias, const void* residual, int ldr, float, int, float* ws, size_t ws_bytes,
-                  int* counters, int n_counters, int* status, cudaStream_t) {
+                  const float* w_sum, const float* bias, const void* residual, int ldr, float res_scale, int act, float* ws,
+                  size_t ws_bytes, int* counters, int n_counters, int* status, cudaStream_t) {
   need(K % 16 == 0, "w8a8: K must be a multiple of 16");
   rdRows(qx, T, K, ldqx, 1);
   rdRows(Wq, N, K, ldw, 1);
@@ -521,7 +602,24 @@ int xft_w8a8_gemm(const void* qx, int ldqx, const void* Wq, int ldw, void* Y, in
   if (ws) rd(reinterpret_cast<char*>(ws) + ws_bytes - 1, 1);
   if (counters) rd(counters, (size_t)n_counters * 4);
   if (status) rd(status, 4);
-  wrRows(Y, T, N, ldo, out_fp32 ? 4 : 2);
+  if (!g_math) { wrRows(Y, T, N, ldo, out_fp32 ? 4 : 2); return 0; }
+  // y = sa * sw * acc + sa * zw * sum(qx) + za * sw * sum(qw) + K * za * zw (+ bias, activation, residual), integer sums
+  std::vector<float> out(N);
+  for (int t = 0; t < T; ++t) {
+    const int8_t* xr = static_cast<const int8_t*>(qx) + (size_t)t * ldqx;
+    for (int n = 0; n < N; ++n) {
+      const int8_t* wr_ = static_cast<const int8_t*>(Wq) + (size_t)n * ldw;
+      int acc = 0;
+      for (int k = 0; k < K; ++k) acc += (int)xr[k] * (int)wr_[k];
+      float x = a_scale[t] * w_scale[n] * (float)acc + a_scale[t] * w_zero[n] * a_qsum[t] + a_zero[t] * w_scale[n] * w_sum[n] +
+                (float)K * a_zero[t] * w_zero[n] + (bias ? bias[n] : 0.f);
+      x = actf(x, act);
+      if (residual) x += res_scale * bf(bfp(residual)[(size_t)t * ldr + n]);
+      out[n] = x;
+    }
+    for (int n = 0; n < N; ++n)
+      if (out_fp32) static_cast<float*>(Y)[(size_t)t * ldo + n] = out[n]; else bfp(Y)[(size_t)t * ldo + n] = tobf(out[n]);
+  }
   return 0;
 }
 

@@ -247,3 +247,114 @@ def test_engine_logits_match_pytorch_deepseek(hostcheck, case, tmp_path, monkeyp
             assert (err < 0.04 * top).float().mean().item() >= 0.6, (case, ranks, err.tolist(), top)
         else:
             assert err.max().item() < 0.04 * top, (case, ranks, err.tolist(), top)
+
+
+@pytest.mark.parametrize("beams,eos", [(1, -1), (3, 299), (4, 17)])
+def test_engine_generation_matches_pytorch(hostcheck, beams, eos, tmp_path, monkeypatch):
+    """config / input / generate / finalize of the C++ engine (greedy; beam search with the host scorer, beams forking
+    and reordering block tables, an eos that ends hypotheses early) against generate() of the package's PyTorch path on
+    one and two thread ranks.  Greedy tokens must be equal; beams amplify last-bit differences (a flipped near-tie changes
+    which hypotheses survive), so there the sequence log-probability under the fp32 model is compared."""
+    import xfastertransformer_b200 as xft
+    from xfastertransformer_b200.parallel.dist import DistContext
+    from xfastertransformer_b200.tools.synthetic import preset, write_synthetic_checkpoint
+    from xfastertransformer_b200.utils.flags import Env
+    d = str(tmp_path / "tiny")
+    write_synthetic_checkpoint(d, preset("tiny-llama", vocab_size=300), seed=5, dtype="bf16", std=0.15)
+    prompt = torch.tensor([[5, 17, 99, 200, 3, 42, 7], [9, 8, 250, 6, 5, 4, 3]])
+    P, new = prompt.shape[1], 10
+    monkeypatch.setenv("XFT_ENGINE", "CPU")
+    Env._inst = None
+    DistContext.reset()
+    try:
+        py = xft.AutoModel.from_pretrained(d, dtype="bf16")
+        want = py.generate(prompt, max_length=P + new, num_beams=beams, eos_token_id=eos if eos >= 0 else 100000, pad_token_id=0)
+
+        def seq_logprob(row):
+            n = len(row)
+            while n > P and row[n - 1] == 0:      # padding
+                n -= 1
+            ids = torch.tensor([row[:n]])
+            lp = torch.log_softmax(py(ids[:, :-1]).float()[0], -1)
+            return sum(float(lp[t - 1, ids[0, t]]) for t in range(P, n)) / max(n - P, 1)
+
+        for ranks in (1, 2):
+            idf, outf = os.path.join(d, "ids.txt"), os.path.join(d, "gen.bin")
+            with open(idf, "w") as f:
+                f.write("2 %d %d\n" % (P, new) + " ".join(str(int(x)) for x in prompt.flatten().tolist()) + "\n")
+            env = dict(os.environ, XFT_MOCK_MATH="1", XFT_ARENA_EXACT="1", ASAN_OPTIONS="detect_leaks=1")
+            r = subprocess.run([hostcheck, "generate", d, "bf16", "fp16", str(ranks), idf, outf, str(beams), str(eos)], env=env,
+                               capture_output=True, text=True, timeout=900)
+            assert r.returncode == 0 and "hostcheck generate ok" in r.stdout, (r.stdout[-500:], r.stderr[-3000:])
+            raw = open(outf, "rb").read()
+            b, n = struct.unpack("ii", raw[:8])
+            got = torch.from_numpy(np.frombuffer(raw, dtype=np.int32, offset=8).reshape(b, n).copy()).long()
+            assert b == 2 and torch.equal(got[:, :P], prompt)
+            if beams == 1:
+                assert torch.equal(got, want[:, :n].long()), (got.tolist(), want.tolist())
+                continue
+            for row in range(2):
+                g, w = seq_logprob(got[row].tolist()), seq_logprob(want[row].tolist())
+                assert g >= w - max(0.25, 0.1 * abs(w)), (beams, ranks, row, g, w, got[row].tolist(), want[row].tolist())
+    finally:
+        monkeypatch.delenv("XFT_ENGINE")
+        Env._inst = None
+        DistContext.reset()
+
+
+def _same_dtype_oracle(d, dtype, prompt, tokens, monkeypatch):
+    """Teacher-forced logits of the package's PyTorch path with the same weight type (the same quantisation formulas)."""
+    import xfastertransformer_b200 as xft
+    from xfastertransformer_b200.parallel.dist import DistContext
+    from xfastertransformer_b200.utils.flags import Env
+    monkeypatch.setenv("XFT_ENGINE", "CPU")
+    Env._inst = None
+    DistContext.reset()
+    try:
+        m = xft.AutoModel.from_pretrained(d, dtype=dtype)
+        P, steps = prompt.shape[1], tokens.shape[0] - 1
+        sid = m.set_input_cb(prompt.tolist(), None, P + steps + 2)
+        rows = [m.forward_cb().float()]
+        for s in range(steps):
+            m.set_input_cb(tokens[s].tolist(), sid, P + steps + 2)
+            rows.append(m.forward_cb().float())
+        m.free_seqs(sid)
+        return torch.stack(rows, 0)
+    finally:
+        monkeypatch.delenv("XFT_ENGINE")
+        Env._inst = None
+        DistContext.reset()
+
+
+@pytest.mark.parametrize("dtype", ["int8", "w8a8", "int4", "nf4", "bf16_int8", "w8a8_nf4"])
+def test_engine_logits_quantised_weights(hostcheck, dtype, tmp_path, monkeypatch):
+    """Quantise-at-load in the C++ engine (the stand-in follows the quantiser's and the quantised GEMMs' formulas) against
+    the PyTorch path with the same weight type: the codes are the same, so the logits agree within bf16 roundings
+    (int8 x int8: within the difference between quantising bf16 and fp32 activations).  On two ranks a row-parallel slice
+    gets its own per-channel range, so only int8 — whose quantisation error is small — is compared there."""
+    d = _synthetic_dir(tmp_path, "llama", {})
+    prompt = torch.randint(5, 290, (2, 20), generator=torch.Generator().manual_seed(4))
+    for ranks in (1, 2) if dtype in ("int8", "bf16_int8") else (1,):
+        got, tokens = _engine_logits(hostcheck, d, ranks, prompt, 3, wdt=dtype)
+        want = _same_dtype_oracle(d, dtype, prompt, tokens, monkeypatch)
+        top = max(1.0, want.abs().max().item())
+        err = (got - want).abs().amax(-1)
+        tol = (0.1 if dtype.startswith("w8a8") else 0.04) * (1.5 if ranks > 1 else 1.0)
+        assert err.max().item() < tol * top, (dtype, ranks, err.tolist(), top)
+
+
+@pytest.mark.parametrize("qt,dtype", [("int8", "int8"), ("int8", "w8a8"), ("int8", "bf16"), ("uint4", "int4"), ("uint4", "bf16_int8")])
+def test_engine_logits_gptq_checkpoint(hostcheck, qt, dtype, tmp_path, monkeypatch):
+    """A GPTQ-converted directory through the C++ engine (codes kept when the weight type matches, dequantised and
+    requantised otherwise; code tensors sliced for two ranks) against the Python loader on the same files.  Per-channel
+    scales do not change with the slicing, so two ranks are held to the same tolerance as one."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from gptq_util import make_gptq_dir
+    d = make_gptq_dir(str(tmp_path / "gptq"), ModelConfig(**dict(_BASE, model_type="llama")), qt, seed=1)
+    prompt = torch.randint(5, 290, (2, 20), generator=torch.Generator().manual_seed(4))
+    for ranks in (1, 2):
+        got, tokens = _engine_logits(hostcheck, d, ranks, prompt, 3, wdt=dtype)
+        want = _same_dtype_oracle(d, dtype, prompt, tokens, monkeypatch)
+        top = max(1.0, want.abs().max().item())
+        err = (got - want).abs().amax(-1)
+        assert err.max().item() < (0.1 if dtype == "w8a8" else 0.04) * top, (qt, dtype, ranks, err.tolist(), top)
