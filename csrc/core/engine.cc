@@ -230,6 +230,7 @@ private:
   void loadDsLinear(const std::string& base, int inF, int outF, void* dst, int dstRowOffset, int dstLd, int o0 = 0, int o1 = -1,
                     int c0 = 0, int c1 = -1);
   void loadMlaLayer(const std::string& p, LayerWeights& L, int layer);
+  void requantiseRows(DevBuf& w, size_t rows, int K);
   // dense bf16 [rows, K] -> the prompt-pass form `first` and, for hybrid types, the decode form `next`; `dense` is
   // released unless a bf16 form points at it
   void quantise(DevBuf& dense, int rows, int K, Lin& first, Lin& next);
@@ -319,7 +320,7 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_
     case DataType::w8a8_int4: wq = 2; wqNext = 4; break;
     default: throw std::runtime_error("the native C++ engine runs bf16, int8, w8a8, int4, nf4 weights and their hybrids");
   }
-  if ((wq || wqNext) && spec.mlp == 3) throw std::runtime_error("quantised experts run through the Python API");
+  if (wq != wqNext && spec.mlp == 3) throw std::runtime_error("hybrid weight types for the expert families run through the Python API");
   kvInt8 = kvdt == DataType::int8;
   heads = (int)ini.getInt(type, "head_num");
   kvHeads = (int)ini.getInt(type, "kv_head_num", heads);
@@ -542,6 +543,12 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_
         denseLoad(ep + (mix ? "w2.0.bin" : "up_proj.weight.0.bin"), hidden, I, L.expGateUp.p, l * 2 * I + I, hidden);
         denseLoad(ep + (mix ? "w3.0.bin" : "down_proj.weight.0.bin"), I, hidden, L.expDown.p, l * hidden, I);
       }
+      if (wq) {
+        // quantised weight types: the experts take the VALUES of the quantised weights and stay bf16 on the device (the
+        // grouped GEMM multiplies bf16), as in the Python engine; the attention projections are quantised for real
+        requantiseRows(L.expGateUp, (size_t)EL * 2 * I, hidden);
+        requantiseRows(L.expDown, (size_t)EL * hidden, I);
+      }
     } else if (spec.mlp == 1) {
       if (!gptq) L.gateUp.reset((size_t)inter * hidden * 2);
       denseLoad(p + "mlp.dense_h_to_4h.weight.0.bin", hidden, interG, L.gateUp.p, 0, hidden, i0, i0 + inter);
@@ -605,6 +612,51 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_
     // XFT_KV_CACHE_GB: size the KV pools once, so that they never grow (and move) under load
     const size_t per = (size_t)layers * (kvBlockBytes() * (spec.mla ? 1 : 2) + (kvInt8 ? (size_t)kvHeads * kBlock * 8 : 0));
     ensureBlocks((int)std::max<size_t>(1, (size_t)(Env::get().kvCacheGb * (double)(1ull << 30)) / per));
+  }
+}
+
+// Every row of a bf16 matrix [rows, K] is replaced by its quantised-and-restored value under the weight type `wq`
+// (per output channel, the formulas of xft_quantize_rows: asymmetric int8, asymmetric uint4, NF4), on the host.
+void Engine::requantiseRows(DevBuf& w, size_t rows, int K) {
+  static const float nf4[16] = {-1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,
+                                -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
+                                0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f,
+                                0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
+  const int mode = wq == 3 ? 2 : wq == 4 ? 1 : 0;
+  const size_t chunk = std::max<size_t>(1, ((size_t)64 << 20) / ((size_t)K * 2));      // 64 MiB of rows at a time
+  std::vector<uint16_t> host;
+  std::vector<float> v(K);
+  for (size_t r0 = 0; r0 < rows; r0 += chunk) {
+    const size_t n = std::min(chunk, rows - r0);
+    host.resize(n * K);
+    char* dev = static_cast<char*>(w.p) + r0 * K * 2;
+    XFT_CUDA(cudaMemcpy(host.data(), dev, n * K * 2, cudaMemcpyDeviceToHost));
+    for (size_t r = 0; r < n; ++r) {
+      uint16_t* row = host.data() + r * K;
+      float mx = -INFINITY, mn = INFINITY;
+      for (int i = 0; i < K; ++i) {
+        v[i] = bf16ToFloat(row[i]);
+        mx = std::max(mx, mode == 2 ? std::fabs(v[i]) : v[i]);
+        mn = std::min(mn, v[i]);
+      }
+      if (mode == 0) {
+        const float sc = std::max((mx - mn) / 255.0f, 1e-10f), zp = (mx + mn) * 0.5f + 0.5f * sc;
+        for (int i = 0; i < K; ++i) row[i] = floatToBf16(std::min(std::max(std::nearbyint((v[i] - zp) / sc), -128.f), 127.f) * sc + zp);
+      } else if (mode == 1) {
+        const float sc = std::max((mx - mn) / 15.0f, 1e-10f);
+        for (int i = 0; i < K; ++i) row[i] = floatToBf16(std::min(std::max(std::nearbyint((v[i] - mn) / sc), 0.f), 15.f) * sc + mn);
+      } else {
+        const float sc = std::max(mx, 1e-10f);
+        for (int i = 0; i < K; ++i) {
+          const float xn = v[i] / sc;
+          int best = 0;
+          float bd = std::fabs(xn - nf4[0]);
+          for (int c = 1; c < 16; ++c) { const float d = std::fabs(xn - nf4[c]); if (d < bd) { bd = d; best = c; } }
+          row[i] = floatToBf16(nf4[best] * sc);
+        }
+      }
+    }
+    XFT_CUDA(cudaMemcpy(dev, host.data(), n * K * 2, cudaMemcpyHostToDevice));
   }
 }
 

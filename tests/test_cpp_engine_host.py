@@ -102,6 +102,14 @@ def _deepseek_config(**kw):
     return ModelConfig(**base)
 
 
+@pytest.mark.parametrize("fam", ["mixtral", "qwen3_moe"])
+@pytest.mark.parametrize("dtype", ["int8", "w8a8", "nf4", "int4"])
+def test_engine_host_side_quantised_expert_families(hostcheck, fam, dtype, tmp_path):
+    d = _config_dir(tmp_path, fam)
+    _run(hostcheck, d, dtype, "int8", 1)
+    _run(hostcheck, d, dtype, "fp16", 2)
+
+
 def test_engine_host_side_deepseek(hostcheck, tmp_path):
     cfg = ModelConfig(model_type="deepseek_moe", num_layer=3, hidden_size=256, head_num=4, kv_head_num=4, size_per_head=128,
                       inter_size=512, vocab_size=300, max_pos_seq_len=4096, q_lora_rank=64, kv_lora_rank=512,
@@ -358,3 +366,18 @@ def test_engine_logits_gptq_checkpoint(hostcheck, qt, dtype, tmp_path, monkeypat
         top = max(1.0, want.abs().max().item())
         err = (got - want).abs().amax(-1)
         assert err.max().item() < (0.1 if dtype == "w8a8" else 0.04) * top, (qt, dtype, ranks, err.tolist(), top)
+
+
+@pytest.mark.parametrize("fam", ["mixtral", "qwen3_moe"])
+@pytest.mark.parametrize("dtype", ["int8", "w8a8", "nf4"])
+def test_engine_logits_quantised_expert_families(hostcheck, fam, dtype, tmp_path, monkeypatch):
+    """Expert families with a quantised weight type: the attention projections are quantised for real, the experts take
+    the values of the quantised weights and stay bf16 on the device — what the Python engine does, against which the
+    logits are held (every expert selected, so no routing decision can flip)."""
+    d = _synthetic_dir(tmp_path, fam, _NUMERIC[fam])
+    prompt = torch.randint(5, 290, (2, 20), generator=torch.Generator().manual_seed(4))
+    got, tokens = _engine_logits(hostcheck, d, 1, prompt, 3, wdt=dtype)
+    want = _same_dtype_oracle(d, dtype, prompt, tokens, monkeypatch)
+    top = max(1.0, want.abs().max().item())
+    err = (got - want).abs().amax(-1)
+    assert err.median().item() < (0.06 if dtype == "w8a8" else 0.03) * top and err.max().item() < 0.15 * top, (fam, dtype, err.tolist(), top)
