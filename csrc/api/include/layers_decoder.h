@@ -1,0 +1,4 @@
+// The reference's header name (include/layers_decoder.h); the layer-level calls are declared together in csrc/api/xft/layers.h
+// (device pointers here, host pointers there).
+#pragma once
+#include "../xft/layers.h"

@@ -690,6 +690,27 @@ def test_reference_call_forms_compile():
     assert r.returncode == 0, r.stderr[-3000:]
 
 
+def test_reference_header_names(tmp_path):
+    """`#include "xfastertransformer.h"` (and the other header names of the reference's include/ directory) resolve from
+    csrc/api/include; its host-side bf16 value type rounds to nearest even."""
+    import shutil
+    import subprocess
+    if shutil.which("g++") is None:
+        pytest.skip("no g++")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = str(tmp_path / "include_names")
+    r = subprocess.run(["g++", "-std=c++17", "-Wall", "-Wextra", "-Werror", "-I", os.path.join(root, "csrc", "api", "include"), "-I",
+                        "/usr/local/cuda/include", os.path.join(root, "csrc", "tests", "include_names.cc"), "-o", exe],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-3000:]
+    out = subprocess.run([exe], capture_output=True, text=True, timeout=60)
+    assert out.returncode == 0 and out.stdout.split()[:2] == ["1", "3"], out.stdout
+    for name in ("abstract_decoder", "abstract_searcher", "bfloat16", "bit_cast", "dtype", "layers_attention", "layers_decoder",
+                 "layers_gemm", "layers_mlp", "layers_norm", "layers_rotary_embedding", "layers_token_embedding", "models",
+                 "xfastertransformer"):
+        assert os.path.exists(os.path.join(root, "csrc", "api", "include", name + ".h")), name
+
+
 def test_process_rank_communicator_with_a_stand_in_nccl(tmp_path):
     """The NCCL communicator of the C++ engine (csrc/core/comm.cc: library opened with dlopen, unique id handed over
     through a file, host broadcasts in pieces through a staging buffer, bf16 sums, gathers) as 1 to 4 real processes,
