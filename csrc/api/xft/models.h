@@ -10,7 +10,7 @@
 // chatglm2 / 3 / 4, gpt (OPT), telechat, the routed-expert families mixtral and qwen3_moe, and deepseek_moe (latent
 // attention, shared + routed experts, e4m3 checkpoints dequantised to bf16 at load).  Dense families take bf16 / fp16,
 // int8, w8a8, int4, nf4 weights (quantised at load) and the hybrid types (one form for the prompt pass, one for decode
-// steps), from dense or GPTQ-converted checkpoints; Mixtral and Qwen3-MoE take the plain quantised types (experts keep the
+// steps), from dense or GPTQ-converted checkpoints; Mixtral and Qwen3-MoE take the quantised and hybrid types (experts keep the
 // quantised values in bf16), DeepSeek runs in bf16.  Every family also runs on several
 // ranks: heads, FFN rows and lm_head rows are split as the reference splits them; routed experts are kept whole, a run
 // of experts per rank, every rank routing every token (DeepSeek: query heads with their slices of the up-projections,

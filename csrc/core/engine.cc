@@ -108,6 +108,7 @@ struct LayerWeights {
   DevBuf qkv, o, gateUp, down, n1, n2, qkvBias, qNorm, kNorm;
   DevBuf n1b, n2b, oBias, fc1Bias, fc2Bias;      // LayerNorm biases, output-projection bias, biases of the two-matrix MLP
   DevBuf router, expGateUp, expDown;             // mixture of experts: [E, hidden], stacked [E * 2I, hidden], [E * hidden, I]
+  DevBuf expGateUpNext, expDownNext;             // hybrid weight types: the experts as the decode steps see them
   // DeepSeek.  Attention: merged down-projection [q_lora (or heads * qk) + kv_lora + rope, hidden], its norms, the query
   // up-projection, and the per-head halves of kv_b: W_uk transposed [heads * kv_lora, nope], W_uv [heads * v, kv_lora].
   DevBuf qkvA, qANorm, qB, kvANorm, wkT, wv;
@@ -230,7 +231,7 @@ private:
   void loadDsLinear(const std::string& base, int inF, int outF, void* dst, int dstRowOffset, int dstLd, int o0 = 0, int o1 = -1,
                     int c0 = 0, int c1 = -1);
   void loadMlaLayer(const std::string& p, LayerWeights& L, int layer);
-  void requantiseRows(DevBuf& w, size_t rows, int K);
+  void requantiseRows(DevBuf& w, size_t rows, int K, int kind);
   // dense bf16 [rows, K] -> the prompt-pass form `first` and, for hybrid types, the decode form `next`; `dense` is
   // released unless a bf16 form points at it
   void quantise(DevBuf& dense, int rows, int K, Lin& first, Lin& next);
@@ -320,7 +321,6 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_
     case DataType::w8a8_int4: wq = 2; wqNext = 4; break;
     default: throw std::runtime_error("the native C++ engine runs bf16, int8, w8a8, int4, nf4 weights and their hybrids");
   }
-  if (wq != wqNext && spec.mlp == 3) throw std::runtime_error("hybrid weight types for the expert families run through the Python API");
   kvInt8 = kvdt == DataType::int8;
   heads = (int)ini.getInt(type, "head_num");
   kvHeads = (int)ini.getInt(type, "kv_head_num", heads);
@@ -543,11 +543,23 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_
         denseLoad(ep + (mix ? "w2.0.bin" : "up_proj.weight.0.bin"), hidden, I, L.expGateUp.p, l * 2 * I + I, hidden);
         denseLoad(ep + (mix ? "w3.0.bin" : "down_proj.weight.0.bin"), I, hidden, L.expDown.p, l * hidden, I);
       }
+      // quantised weight types: the experts take the VALUES of the quantised weights and stay bf16 on the device (the
+      // grouped GEMM multiplies bf16), as in the Python engine; the attention projections are quantised for real.  A
+      // hybrid type keeps a second stack for the decode steps.
+      if (wqNext != wq) {
+        const size_t gu = (size_t)EL * 2 * I * hidden * 2, dn = (size_t)EL * hidden * I * 2;
+        L.expGateUpNext.reset(gu);
+        L.expDownNext.reset(dn);
+        XFT_CUDA(cudaMemcpy(L.expGateUpNext.p, L.expGateUp.p, gu, cudaMemcpyDeviceToDevice));
+        XFT_CUDA(cudaMemcpy(L.expDownNext.p, L.expDown.p, dn, cudaMemcpyDeviceToDevice));
+        if (wqNext) {
+          requantiseRows(L.expGateUpNext, (size_t)EL * 2 * I, hidden, wqNext);
+          requantiseRows(L.expDownNext, (size_t)EL * hidden, I, wqNext);
+        }
+      }
       if (wq) {
-        // quantised weight types: the experts take the VALUES of the quantised weights and stay bf16 on the device (the
-        // grouped GEMM multiplies bf16), as in the Python engine; the attention projections are quantised for real
-        requantiseRows(L.expGateUp, (size_t)EL * 2 * I, hidden);
-        requantiseRows(L.expDown, (size_t)EL * hidden, I);
+        requantiseRows(L.expGateUp, (size_t)EL * 2 * I, hidden, wq);
+        requantiseRows(L.expDown, (size_t)EL * hidden, I, wq);
       }
     } else if (spec.mlp == 1) {
       if (!gptq) L.gateUp.reset((size_t)inter * hidden * 2);
@@ -615,14 +627,14 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_
   }
 }
 
-// Every row of a bf16 matrix [rows, K] is replaced by its quantised-and-restored value under the weight type `wq`
+// Every row of a bf16 matrix [rows, K] is replaced by its quantised-and-restored value under the weight type `kind`
 // (per output channel, the formulas of xft_quantize_rows: asymmetric int8, asymmetric uint4, NF4), on the host.
-void Engine::requantiseRows(DevBuf& w, size_t rows, int K) {
+void Engine::requantiseRows(DevBuf& w, size_t rows, int K, int kind) {
   static const float nf4[16] = {-1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,
                                 -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
                                 0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f,
                                 0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
-  const int mode = wq == 3 ? 2 : wq == 4 ? 1 : 0;
+  const int mode = kind == 3 ? 2 : kind == 4 ? 1 : 0;
   const size_t chunk = std::max<size_t>(1, ((size_t)64 << 20) / ((size_t)K * 2));      // 64 MiB of rows at a time
   std::vector<uint16_t> host;
   std::vector<float> v(K);
@@ -1258,9 +1270,12 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
       XFT_K(xft_moe_plan(moeIdx.as<int>(), moeWts.as<float>(), T, k, e0, e1, moeBn, moePos.as<int>(), moeSrc.as<int>(),
                          moeRowW.as<float>(), moeTiles.p, moeMeta.as<int>(), moeMaxTiles, T * k, st));
       XFT_K(xft_moe_gather(hn, hidden, moeSrc.as<int>(), moeMeta.as<int>(), moeXs.p, T * k, hidden, st));
-      XFT_K(xft_gemm_bf16_grouped(moeXs.p, hidden, T * k, L.expGateUp.p, EL * 2 * I, hidden, moeH1.p, I, 0, I, hidden, 1, I,
+      const bool nextStack = decode && wqNext != wq;
+      const void* wGateUp = nextStack ? L.expGateUpNext.p : L.expGateUp.p;
+      const void* wDown = nextStack ? L.expDownNext.p : L.expDown.p;
+      XFT_K(xft_gemm_bf16_grouped(moeXs.p, hidden, T * k, wGateUp, EL * 2 * I, hidden, moeH1.p, I, 0, I, hidden, 1, I,
                                   2 * I, moeTiles.p, moeMeta.as<int>(), moeMaxTiles, moeBn, nullptr, act, stp, st));
-      XFT_K(xft_gemm_bf16_grouped(moeH1.p, I, T * k, L.expDown.p, EL * hidden, I, moeYs.p, hidden, 1, hidden, I, 0, 0, hidden,
+      XFT_K(xft_gemm_bf16_grouped(moeH1.p, I, T * k, wDown, EL * hidden, I, moeYs.p, hidden, 1, hidden, I, 0, 0, hidden,
                                   moeTiles.p, moeMeta.as<int>(), moeMaxTiles, moeBn, moeRowW.as<float>(), 0, stp, st));
       XFT_K(xft_moe_combine(moeYs.as<float>(), moePos.as<int>(), k, nullptr, rank == 0 ? nxt : nullptr, hidden, cur, nullptr, T,
                             hidden, st));

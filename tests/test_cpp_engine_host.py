@@ -113,7 +113,7 @@ def _deepseek_config(**kw):
 
 
 @pytest.mark.parametrize("fam", ["mixtral", "qwen3_moe"])
-@pytest.mark.parametrize("dtype", ["int8", "w8a8", "nf4", "int4"])
+@pytest.mark.parametrize("dtype", ["int8", "w8a8", "nf4", "int4", "bf16_int8", "w8a8_nf4"])
 def test_engine_host_side_quantised_expert_families(hostcheck, fam, dtype, tmp_path):
     d = _config_dir(tmp_path, fam)
     _run(hostcheck, d, dtype, "int8", 1)
@@ -379,15 +379,17 @@ def test_engine_logits_gptq_checkpoint(hostcheck, qt, dtype, tmp_path, monkeypat
 
 
 @pytest.mark.parametrize("fam", ["mixtral", "qwen3_moe"])
-@pytest.mark.parametrize("dtype", ["int8", "w8a8", "nf4"])
+@pytest.mark.parametrize("dtype", ["int8", "w8a8", "nf4", "bf16_int8", "w8a8_nf4"])
 def test_engine_logits_quantised_expert_families(hostcheck, fam, dtype, tmp_path, monkeypatch):
     """Expert families with a quantised weight type: the attention projections are quantised for real, the experts take
     the values of the quantised weights and stay bf16 on the device — what the Python engine does, against which the
-    logits are held (every expert selected, so no routing decision can flip)."""
+    logits are held (every expert selected, so no routing decision can flip).  A hybrid type keeps two expert stacks:
+    the first type's for the prompt pass, the second's for the decode steps."""
     d = _synthetic_dir(tmp_path, fam, _NUMERIC[fam])
     prompt = torch.randint(5, 290, (2, 20), generator=torch.Generator().manual_seed(4))
     got, tokens = _engine_logits(hostcheck, d, 1, prompt, 3, wdt=dtype)
     want = _same_dtype_oracle(d, dtype, prompt, tokens, monkeypatch)
     top = max(1.0, want.abs().max().item())
     err = (got - want).abs().amax(-1)
-    assert err.median().item() < (0.06 if dtype == "w8a8" else 0.03) * top and err.max().item() < 0.15 * top, (fam, dtype, err.tolist(), top)
+    assert err.median().item() < (0.06 if dtype.startswith("w8a8") else 0.03) * top and err.max().item() < 0.15 * top, \
+        (fam, dtype, err.tolist(), top)
