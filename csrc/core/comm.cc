@@ -10,6 +10,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <fstream>
+#include <functional>
 #include <mutex>
 #include <stdexcept>
 #include <thread>
@@ -30,19 +31,20 @@ int envInt(const char* name, int def) {
 }
 
 // ------------------------------------------------------------------------------------------------ thread ranks
-// Shared state of one group of thread ranks.  `turn` is the rank that may run; everyone else sleeps.  A collective is
-// entered by the ranks in turn order; each leaves its arguments and hands the turn on; the last one to arrive performs
-// the operation for all (after a device-wide synchronise, so every rank's producer kernels are complete), bumps
-// `epoch` and gives the turn to the first rank.
-struct ThreadGroup {
+// Shared by every thread rank of one world: `turn` is the rank that may run, everyone else sleeps.  A rank that reaches
+// an operation it cannot finish alone leaves its arguments and hands the turn to the next rank; when the turn comes
+// back and the operation is still open, it hands the turn on again.  Whoever completes an operation (the last arriver of
+// a collective, the receiver of a message) does the work — after a device-wide synchronise, so every rank's producer
+// kernels are complete — and keeps running.  When the turn goes round with nobody able to go on, the program has
+// deadlocked (a rank waits for an operation its partner never reaches): every waiting rank fails.
+struct Sched {
   std::mutex mu;
   std::condition_variable cv;
-  int n = 0, turn = 0, arrived = 0, alive = 0;
-  long long epoch = 0;
-  bool broken = false;                   // a rank left in the middle of the program
+  int n = 0, turn = 0, stalls = 0;
+  bool broken = false;
   std::vector<char> gone;
-  std::vector<void*> a, b;               // per-rank arguments of the collective in flight
-  std::vector<cudaStream_t> streams;
+  struct Mail { const void* buf = nullptr; size_t n = 0; bool posted = false; };
+  std::vector<Mail> mail;                // [source * n + destination], world ranks
 
   int nextAlive(int r) const {
     for (int i = 1; i <= n; ++i) { const int c = (r + i) % n; if (!gone[c]) return c; }
@@ -50,103 +52,214 @@ struct ThreadGroup {
   }
 };
 
+// One group of ranks that runs collectives together: the world, or what split() made of it
+struct Coll {
+  std::vector<int> members;              // world ranks, in group order
+  int arrived = 0;
+  long long epoch = 0;
+  std::vector<void*> a, b;               // per-member arguments of the collective in flight
+  std::vector<int> color, key;           // split(): what each member asked for ...
+  std::vector<std::shared_ptr<Coll>> made;   // ... and the group it got
+
+  explicit Coll(std::vector<int> m) : members(std::move(m)) {
+    const size_t n = members.size();
+    a.assign(n, nullptr); b.assign(n, nullptr); color.assign(n, 0); key.assign(n, 0); made.assign(n, nullptr);
+  }
+};
+
 class ThreadComm : public Communicator {
 public:
-  ThreadComm(std::shared_ptr<ThreadGroup> g, int rank) : g_(std::move(g)), rank_(rank) {}
+  ThreadComm(std::shared_ptr<Sched> s, std::shared_ptr<Coll> c, int worldRank, bool isWorld)
+      : s_(std::move(s)), c_(std::move(c)), me_(worldRank), isWorld_(isWorld), started_(!isWorld) {
+    idx_ = (int)(std::find(c_->members.begin(), c_->members.end(), me_) - c_->members.begin());
+  }
   ~ThreadComm() override { end(); }
-  int rank() const override { return rank_; }
-  int size() const override { return g_->n; }
+  int rank() const override { return idx_; }
+  int size() const override { return (int)c_->members.size(); }
 
   void begin() override {
-    std::unique_lock<std::mutex> lk(g_->mu);
-    g_->cv.wait(lk, [&] { return g_->turn == rank_ || g_->broken; });
+    if (!isWorld_) return;
+    std::unique_lock<std::mutex> lk(s_->mu);
+    s_->cv.wait(lk, [&] { return s_->turn == me_ || s_->broken; });
     started_ = true;
   }
 
+  // the rank leaves the world (a sub-group's end() is nothing: its ranks leave through the world communicator)
   void end() override {
-    std::unique_lock<std::mutex> lk(g_->mu);
+    if (!isWorld_) return;
+    std::unique_lock<std::mutex> lk(s_->mu);
     if (ended_) return;
     ended_ = true;
-    g_->gone[rank_] = 1;
-    g_->alive--;
-    if (g_->arrived > 0) g_->broken = true;          // the others are inside a collective this rank will never join
-    if (g_->turn == rank_) g_->turn = g_->nextAlive(rank_);
-    g_->cv.notify_all();
+    s_->gone[me_] = 1;
+    if (s_->turn == me_) s_->turn = s_->nextAlive(me_);
+    s_->cv.notify_all();
   }
 
   void allReduceBf16(void* buf, size_t n, cudaStream_t st) override {
-    collective(buf, nullptr, st, [&](ThreadGroup& g) {
+    collective(buf, nullptr, [&](Coll& g) {
       std::vector<const void*> srcs(g.a.begin(), g.a.end());
-      // the sum lands in rank 0's buffer, then every other rank's buffer receives a copy
-      if (xft_sum_bf16(g.a[0], srcs.data(), g.n, n, st) != 0) throw std::runtime_error("xft_sum_bf16 failed");
-      for (int r = 1; r < g.n; ++r) cudaOk(cudaMemcpyAsync(g.a[r], g.a[0], n * 2, cudaMemcpyDeviceToDevice, st), "all-reduce copy");
+      // the sum lands in the first member's buffer, then every other member's buffer receives a copy
+      if (xft_sum_bf16(g.a[0], srcs.data(), (int)g.members.size(), n, st) != 0) throw std::runtime_error("xft_sum_bf16 failed");
+      for (size_t r = 1; r < g.members.size(); ++r)
+        cudaOk(cudaMemcpyAsync(g.a[r], g.a[0], n * 2, cudaMemcpyDeviceToDevice, st), "all-reduce copy");
     });
   }
 
   void allGatherF32(const float* in, float* out, size_t n, cudaStream_t st) override {
-    collective(const_cast<float*>(in), out, st, [&](ThreadGroup& g) {
-      for (int dst = 0; dst < g.n; ++dst)
-        for (int src = 0; src < g.n; ++src)
-          cudaOk(cudaMemcpyAsync(static_cast<float*>(g.b[dst]) + (size_t)src * n, g.a[src], n * 4, cudaMemcpyDeviceToDevice, st),
+    collective(const_cast<float*>(in), out, [&](Coll& g) {
+      for (size_t dst = 0; dst < g.members.size(); ++dst)
+        for (size_t src = 0; src < g.members.size(); ++src)
+          cudaOk(cudaMemcpyAsync(static_cast<float*>(g.b[dst]) + src * n, g.a[src], n * 4, cudaMemcpyDeviceToDevice, st),
                  "all-gather copy");
     });
   }
 
-  void broadcastHost(void* data, size_t bytes) override {
-    collective(data, nullptr, nullptr, [&](ThreadGroup& g) {
-      for (int r = 1; r < g.n; ++r) std::memcpy(g.a[r], g.a[0], bytes);
+  void broadcastHost(void* data, size_t bytes, int root) override {
+    if (root < 0 || root >= size()) throw std::runtime_error("broadcast: bad root");
+    collective(data, nullptr, [&](Coll& g) {
+      for (size_t r = 0; r < g.members.size(); ++r)
+        if ((int)r != root) std::memcpy(g.a[r], g.a[root], bytes);
     });
   }
 
-  void barrier() override { collective(nullptr, nullptr, nullptr, [](ThreadGroup&) {}); }
+  void barrier() override { collective(nullptr, nullptr, [](Coll&) {}); }
 
-private:
-  template <class Op>
-  void collective(void* a, void* b, cudaStream_t st, Op op) {
-    std::unique_lock<std::mutex> lk(g_->mu);
-    if (!started_ || g_->turn != rank_) throw std::runtime_error("thread rank ran out of turn (begin() not called?)");
-    if (g_->broken || g_->alive != g_->n) throw std::runtime_error("a tensor-parallel rank has left");
-    g_->a[rank_] = a; g_->b[rank_] = b; g_->streams[rank_] = st;
-    const long long my = g_->epoch;
-    if (++g_->arrived == g_->n) {
-      // every rank's work up to here is on the device queue: wait for all of it, do the operation, wait for that too
-      try {
-        cudaOk(cudaDeviceSynchronize(), "collective (before)");
-        op(*g_);
-        cudaOk(cudaDeviceSynchronize(), "collective (after)");
-      } catch (...) {
-        g_->broken = true;               // the sleeping ranks wake up and fail too instead of waiting for ever
-        g_->cv.notify_all();
-        throw;
-      }
-      g_->arrived = 0;
-      g_->epoch++;
-      g_->turn = g_->nextAlive(g_->n - 1);      // the first rank runs first again
-      g_->cv.notify_all();
-      if (g_->turn != rank_) g_->cv.wait(lk, [&] { return g_->turn == rank_ || g_->broken; });
-    } else {
-      g_->turn = g_->nextAlive(rank_);
-      g_->cv.notify_all();
-      g_->cv.wait(lk, [&] { return (g_->epoch != my && g_->turn == rank_) || g_->broken; });
-    }
-    if (g_->broken) throw std::runtime_error("a tensor-parallel rank has left");
+  void sendBf16(const void* buf, size_t n, int peer, cudaStream_t) override {
+    std::unique_lock<std::mutex> lk(s_->mu);
+    const int to = enter(peer);
+    Sched::Mail& m = s_->mail[(size_t)me_ * s_->n + to];
+    if (m.posted) throw std::runtime_error("send: the previous message to this rank is still waiting");
+    m.buf = buf; m.n = n; m.posted = true;
+    s_->stalls = 0;
+    yieldUntil(lk, [&] { if (s_->gone[to]) throw std::runtime_error("a rank has left"); return !m.posted; });
   }
 
-  std::shared_ptr<ThreadGroup> g_;
-  int rank_;
-  bool started_ = false, ended_ = false;
+  void recvBf16(void* buf, size_t n, int peer, cudaStream_t st) override {
+    std::unique_lock<std::mutex> lk(s_->mu);
+    const int from = enter(peer);
+    Sched::Mail& m = s_->mail[(size_t)from * s_->n + me_];
+    yieldUntil(lk, [&] { if (!m.posted && s_->gone[from]) throw std::runtime_error("a rank has left"); return m.posted; });
+    try {
+      if (m.n != n) throw std::runtime_error("receive: the sender's message has another size");
+      cudaOk(cudaDeviceSynchronize(), "receive (before)");
+      cudaOk(cudaMemcpyAsync(buf, m.buf, n * 2, cudaMemcpyDeviceToDevice, st), "receive copy");
+      cudaOk(cudaDeviceSynchronize(), "receive (after)");
+    } catch (...) {
+      s_->broken = true;
+      s_->cv.notify_all();
+      throw;
+    }
+    m.posted = false;                    // the sender goes on when its turn comes
+    s_->stalls = 0;
+  }
+
+  std::shared_ptr<Communicator> split(int color, int key) override {
+    {
+      std::unique_lock<std::mutex> lk(s_->mu);
+      c_->color[idx_] = color; c_->key[idx_] = key;
+    }
+    collective(nullptr, nullptr, [](Coll& g) {
+      const int n = (int)g.members.size();
+      std::vector<char> done(n, 0);
+      for (int i = 0; i < n; ++i) {
+        if (done[i]) continue;
+        std::vector<int> grp;
+        for (int j = i; j < n; ++j) if (g.color[j] == g.color[i]) grp.push_back(j);
+        std::stable_sort(grp.begin(), grp.end(), [&](int x, int y) { return g.key[x] < g.key[y]; });
+        std::vector<int> world;
+        for (int j : grp) world.push_back(g.members[j]);
+        auto made = std::make_shared<Coll>(world);
+        for (int j : grp) { g.made[j] = made; done[j] = 1; }
+      }
+    });
+    std::unique_lock<std::mutex> lk(s_->mu);
+    return std::make_shared<ThreadComm>(s_, c_->made[idx_], me_, false);
+  }
+
+private:
+  // common entry checks of an operation (lock held): this rank has the turn, the world is whole; returns the world rank of
+  // group member `peer`
+  int enter(int peer) {
+    if (!started_ || s_->turn != me_) throw std::runtime_error("thread rank ran out of turn (begin() not called?)");
+    if (s_->broken) throw std::runtime_error("a tensor-parallel rank has left");
+    if (peer < 0 || peer >= size() || c_->members[peer] == me_) throw std::runtime_error("bad peer rank");
+    return c_->members[peer];
+  }
+  bool membersAlive() const {
+    for (int m : c_->members) if (s_->gone[m]) return false;
+    return true;
+  }
+
+  // Give the turn away until `ready()` holds and the turn is back (lock held on entry and on return).
+  template <class Ready>
+  void yieldUntil(std::unique_lock<std::mutex>& lk, Ready ready) {
+    Sched& s = *s_;
+    for (;;) {
+      if (s.broken) throw std::runtime_error("a tensor-parallel rank has left");
+      if (s.turn == me_) {
+        if (ready()) { s.stalls = 0; return; }
+        const int next = s.nextAlive(me_);
+        if (next == me_ || ++s.stalls > 4 * s.n + 4) {
+          s.broken = true;               // nobody can go on: the sleeping ranks wake up and fail too
+          s.cv.notify_all();
+          throw std::runtime_error("thread ranks are waiting for one another (an operation no partner reaches)");
+        }
+        s.turn = next;
+        s.cv.notify_all();
+      }
+      s.cv.wait(lk, [&] { return s.turn == me_ || s.broken; });
+    }
+  }
+
+  template <class Op>
+  void collective(void* a, void* b, Op op) {
+    std::unique_lock<std::mutex> lk(s_->mu);
+    if (!started_ || s_->turn != me_) throw std::runtime_error("thread rank ran out of turn (begin() not called?)");
+    if (s_->broken || !membersAlive()) throw std::runtime_error("a tensor-parallel rank has left");
+    Coll& g = *c_;
+    g.a[idx_] = a; g.b[idx_] = b;
+    s_->stalls = 0;
+    const long long my = g.epoch;
+    if (++g.arrived == (int)g.members.size()) {
+      // every member's work up to here is on the device queue: wait for all of it, do the operation, wait for that too
+      try {
+        cudaOk(cudaDeviceSynchronize(), "collective (before)");
+        op(g);
+        cudaOk(cudaDeviceSynchronize(), "collective (after)");
+      } catch (...) {
+        s_->broken = true;               // the sleeping ranks wake up and fail too instead of waiting for ever
+        s_->cv.notify_all();
+        throw;
+      }
+      g.arrived = 0;
+      g.epoch++;
+      return;                            // the others go on as the turn reaches them
+    }
+    yieldUntil(lk, [&] {
+      if (g.epoch == my && !membersAlive()) throw std::runtime_error("a tensor-parallel rank has left");
+      return g.epoch != my;
+    });
+  }
+
+  std::shared_ptr<Sched> s_;
+  std::shared_ptr<Coll> c_;
+  int me_, idx_ = 0;
+  bool isWorld_, started_, ended_ = false;
 };
 
 }  // namespace
 
 std::vector<std::shared_ptr<Communicator>> makeThreadCommunicators(int n) {
   if (n < 1 || n > 8) throw std::runtime_error("thread ranks: 1 to 8");
-  auto g = std::make_shared<ThreadGroup>();
-  g->n = g->alive = n;
-  g->gone.assign(n, 0);
-  g->a.assign(n, nullptr); g->b.assign(n, nullptr); g->streams.assign(n, nullptr);
+  auto s = std::make_shared<Sched>();
+  s->n = n;
+  s->gone.assign(n, 0);
+  s->mail.assign((size_t)n * n, Sched::Mail());
+  std::vector<int> all(n);
+  for (int r = 0; r < n; ++r) all[r] = r;
+  auto world = std::make_shared<Coll>(all);
   std::vector<std::shared_ptr<Communicator>> out;
-  for (int r = 0; r < n; ++r) out.push_back(std::make_shared<ThreadComm>(g, r));
+  for (int r = 0; r < n; ++r) out.push_back(std::make_shared<ThreadComm>(s, world, r, true));
   return out;
 }
 
@@ -176,6 +289,9 @@ struct NcclApi {
   int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
   int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
   int (*Broadcast)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+  int (*Send)(const void*, size_t, int, int, void*, cudaStream_t) = nullptr;              // pipeline stages only
+  int (*Recv)(void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+  int (*CommSplit)(void*, int, int, void**, void*) = nullptr;                             // NCCL 2.18 and later
   const char* (*GetErrorString)(int) = nullptr;
 
   static NcclApi& get() {
@@ -197,6 +313,9 @@ struct NcclApi {
       api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(sym("ncclAllReduce"));
       api.AllGather = reinterpret_cast<decltype(api.AllGather)>(sym("ncclAllGather"));
       api.Broadcast = reinterpret_cast<decltype(api.Broadcast)>(sym("ncclBroadcast"));
+      api.Send = reinterpret_cast<decltype(api.Send)>(sym("ncclSend"));
+      api.Recv = reinterpret_cast<decltype(api.Recv)>(sym("ncclRecv"));
+      api.CommSplit = reinterpret_cast<decltype(api.CommSplit)>(sym("ncclCommSplit"));
       api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(sym("ncclGetErrorString"));
     });
     return api;
@@ -248,6 +367,10 @@ public:
     barrier();
     if (rank == 0) { std::remove(ready.c_str()); std::remove(path.c_str()); }
   }
+  // a communicator NCCL made out of another one (split)
+  NcclComm(void* comm, int rank, int world) : rank_(rank), world_(world), comm_(comm) {
+    cudaOk(cudaMalloc(&stage_, kStage), "cudaMalloc (staging)");
+  }
   ~NcclComm() override {
     if (stage_) cudaFree(stage_);
     if (comm_) NcclApi::get().CommDestroy(comm_);
@@ -260,15 +383,46 @@ public:
   void allGatherF32(const float* in, float* out, size_t n, cudaStream_t st) override {
     check(NcclApi::get().AllGather(in, out, n, 7 /* fp32 */, comm_, st), "ncclAllGather");
   }
-  void broadcastHost(void* data, size_t bytes) override {
+  void broadcastHost(void* data, size_t bytes, int root) override {
     // through a device staging buffer, in pieces
     for (size_t off = 0; off < bytes; off += kStage) {
       const size_t n = std::min(kStage, bytes - off);
-      if (rank_ == 0) cudaOk(cudaMemcpy(stage_, static_cast<char*>(data) + off, n, cudaMemcpyHostToDevice), "broadcast (stage in)");
-      check(NcclApi::get().Broadcast(stage_, stage_, n, 1 /* uint8 */, 0, comm_, nullptr), "ncclBroadcast");
+      if (rank_ == root) cudaOk(cudaMemcpy(stage_, static_cast<char*>(data) + off, n, cudaMemcpyHostToDevice), "broadcast (stage in)");
+      check(NcclApi::get().Broadcast(stage_, stage_, n, 1 /* uint8 */, root, comm_, nullptr), "ncclBroadcast");
       cudaOk(cudaStreamSynchronize(nullptr), "broadcast");
-      if (rank_ != 0) cudaOk(cudaMemcpy(static_cast<char*>(data) + off, stage_, n, cudaMemcpyDeviceToHost), "broadcast (stage out)");
+      if (rank_ != root) cudaOk(cudaMemcpy(static_cast<char*>(data) + off, stage_, n, cudaMemcpyDeviceToHost), "broadcast (stage out)");
     }
+  }
+  void sendBf16(const void* buf, size_t n, int peer, cudaStream_t st) override {
+    NcclApi& api = NcclApi::get();
+    if (!api.Send) throw std::runtime_error("this NCCL library has no ncclSend");
+    check(api.Send(buf, n, 9 /* bf16 */, peer, comm_, st), "ncclSend");
+  }
+  void recvBf16(void* buf, size_t n, int peer, cudaStream_t st) override {
+    NcclApi& api = NcclApi::get();
+    if (!api.Recv) throw std::runtime_error("this NCCL library has no ncclRecv");
+    check(api.Recv(buf, n, 9 /* bf16 */, peer, comm_, st), "ncclRecv");
+  }
+  std::shared_ptr<Communicator> split(int color, int key) override {
+    NcclApi& api = NcclApi::get();
+    if (!api.CommSplit) throw std::runtime_error("pipeline stages with tensor-parallel groups need ncclCommSplit (NCCL 2.18 or later)");
+    // rank and size of the new communicator: every rank tells the others its colour and key
+    std::vector<float> mine = {(float)color, (float)key}, all((size_t)2 * world_);
+    float* dev = static_cast<float*>(stage_);
+    cudaOk(cudaMemcpy(dev, mine.data(), 8, cudaMemcpyHostToDevice), "split");
+    check(api.AllGather(dev, dev + 2, 2, 7 /* fp32 */, comm_, nullptr), "ncclAllGather (split)");
+    cudaOk(cudaStreamSynchronize(nullptr), "split");
+    cudaOk(cudaMemcpy(all.data(), dev + 2, all.size() * 4, cudaMemcpyDeviceToHost), "split");
+    int newRank = 0, newSize = 0;
+    for (int r = 0; r < world_; ++r) {
+      if ((int)all[2 * r] != color) continue;
+      ++newSize;
+      const int k = (int)all[2 * r + 1];
+      if (k < key || (k == key && r < rank_)) ++newRank;
+    }
+    void* sub = nullptr;
+    check(api.CommSplit(comm_, color, key, &sub, nullptr), "ncclCommSplit");
+    return std::make_shared<NcclComm>(sub, newRank, newSize);
   }
   void barrier() override {
     check(NcclApi::get().AllReduce(stage_, stage_, 1, 7, 0, comm_, nullptr), "barrier");

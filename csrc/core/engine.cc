@@ -171,7 +171,14 @@ public:
   // tensor parallelism (src/layers/decoder_block.h + split_util.h): this rank holds the query heads [q0, q1) with the
   // KV heads that cover them, rows [i0, i1) of the FFN and rows [v0, v1) of the lm_head.  After these ranges are set,
   // `heads`, `kvHeads`, `inter` and `vocab` below are THIS RANK'S counts; the model's own are the ...G fields.
-  std::shared_ptr<Communicator> comm;
+  // `worldComm`: every rank (arguments of rank 0, stage boundaries, the logits of the last stage); `comm`: the tensor-
+  // parallel group of this pipeline stage (the same object when there is one stage; null when the group has one rank)
+  std::shared_ptr<Communicator> worldComm, comm;
+  int worldRank = 0, worldSize = 1;
+  // pipeline stages (XFT_PIPELINE_STAGE, src/models/common_decoder.h:389-391,497-498): world = stages x tensor-parallel
+  // ranks; stage s runs layers [l0, l1), receives the hidden state of stage s - 1 and hands its own to stage s + 1; the
+  // last stage computes the logits and every rank receives them
+  int pp = 1, ppRank = 0, l0 = 0, l1 = 0;
   int rank = 0, world = 1;
   int headsG = 0, kvHeadsG = 0, interG = 0, vocabG = 0;
   int q0 = 0, kv0 = 0, i0 = 0, v0 = 0, qOff = 0, groupG = 1, vocabPad = 0;
@@ -297,9 +304,22 @@ DevBuf Engine::loadVector(const std::string& file, int n, bool optional, int dt,
   return d;
 }
 
-Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_ptr<Communicator> c) : comm(std::move(c)), dir(path) {
-  if (comm && comm->size() > 1) { rank = comm->rank(); world = comm->size(); comm->begin(); }
-  else comm.reset();
+Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_ptr<Communicator> c) : worldComm(std::move(c)), dir(path) {
+  if (worldComm && worldComm->size() > 1) { worldRank = worldComm->rank(); worldSize = worldComm->size(); worldComm->begin(); }
+  else worldComm.reset();
+  pp = worldComm ? Env::get().pipelineStage : 1;
+  if (pp > 1) {
+    if (worldSize % pp) throw std::runtime_error("XFT_PIPELINE_STAGE does not divide the number of ranks");
+    const int tp = worldSize / pp;
+    ppRank = worldRank / tp;
+    rank = worldRank % tp;
+    world = tp;
+    if (tp > 1) comm = worldComm->split(ppRank, rank);
+  } else {
+    comm = worldComm;
+    rank = worldRank;
+    world = worldSize;
+  }
   Ini ini(path + "/config.ini");
   if (!ini.ok() || ini.sections().empty()) throw std::runtime_error("config.ini not found under " + path);
   type = ini.sections()[0];
@@ -328,6 +348,8 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_
   hidden = (int)ini.getInt(type, "hidden_size", heads * headDim);
   inter = (int)ini.getInt(type, "inter_size");
   layers = (int)ini.getInt(type, "num_layer");
+  if (pp > layers) throw std::runtime_error("more pipeline stages than layers");
+  { const auto lr = ppLayerRange(layers, pp, ppRank); l0 = lr.first; l1 = lr.second; }
   vocab = (int)ini.getInt(type, "vocab_size");
   maxPos = std::max<int>({(int)ini.getInt(type, "max_pos_seq_len", 0), (int)ini.getInt(type, "model_max_length", 0), 2048});
   // Baichuan-13B has no rotary table: ALiBi slopes on the attention scores (src/layers/attn_baichuan.h:33-47)
@@ -491,7 +513,7 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_
   lw.resize(layers);
   lins.resize(layers);
   linsNext.resize(layers);
-  for (int i = 0; i < layers; ++i) {
+  for (int i = l0; i < l1; ++i) {
     const std::string p = "model.layers." + std::to_string(i) + ".";
     LayerWeights& L = lw[i];
     if (spec.mla) { loadMlaLayer(p, L, i); continue; }
@@ -622,7 +644,7 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_
   rng.seed((unsigned long long)std::chrono::steady_clock::now().time_since_epoch().count());
   if (Env::get().kvCacheGb > 0) {
     // XFT_KV_CACHE_GB: size the KV pools once, so that they never grow (and move) under load
-    const size_t per = (size_t)layers * (kvBlockBytes() * (spec.mla ? 1 : 2) + (kvInt8 ? (size_t)kvHeads * kBlock * 8 : 0));
+    const size_t per = (size_t)(l1 - l0) * (kvBlockBytes() * (spec.mla ? 1 : 2) + (kvInt8 ? (size_t)kvHeads * kBlock * 8 : 0));
     ensureBlocks((int)std::max<size_t>(1, (size_t)(Env::get().kvCacheGb * (double)(1ull << 30)) / per));
   }
 }
@@ -931,7 +953,7 @@ void Engine::ensureBlocks(int extra) {
   if (al.numFree() >= extra) return;
   const int total = std::max(al.numBlocks() - al.numFree() + extra, al.numBlocks() * 3 / 2);
   const size_t per = kvBlockBytes(), sper = (size_t)kvHeads * kBlock * 4;
-  for (int l = 0; l < layers; ++l) {
+  for (int l = l0; l < l1; ++l) {
     DevBuf nk(per * total), nv(spec.mla ? 0 : per * total);
     // new blocks start zeroed: the TMA decode kernel reads whole tiles and masks rows past kv_len by P = 0,
     // which needs the masked V rows to be finite
@@ -957,7 +979,7 @@ void Engine::ensureBlocks(int extra) {
 
 void Engine::copyBlock(int src, int dst) {
   const size_t per = kvBlockBytes(), sper = (size_t)kvHeads * kBlock * 4;
-  for (int l = 0; l < layers; ++l) {
+  for (int l = l0; l < l1; ++l) {
     XFT_CUDA(cudaMemcpyAsync(kc[l].as<char>() + per * dst, kc[l].as<char>() + per * src, per, cudaMemcpyDeviceToDevice, st));
     if (spec.mla) continue;
     XFT_CUDA(cudaMemcpyAsync(vc[l].as<char>() + per * dst, vc[l].as<char>() + per * src, per, cudaMemcpyDeviceToDevice, st));
@@ -1064,8 +1086,9 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
     XFT_K(xft_gemm_bf16(X, K, Wt, wRows, K, Y, N, fp32, rowsT, N, K, gated, dualOff, bias, res, N, 1.0f, actc, nullptr,
                         ws.as<float>(), kWsBytes, counters.as<int>(), 8192, stp, 0, st));
   };
-  XFT_K(xft_embedding(dIds.as<int>(), wte.p, x.p, T, hidden, vocabG, embedScale, wpe.p, wpe.p ? dPos.as<int>() : nullptr, 2,
-                      wpeRows, stp, st));
+  if (ppRank == 0)
+    XFT_K(xft_embedding(dIds.as<int>(), wte.p, x.p, T, hidden, vocabG, embedScale, wpe.p, wpe.p ? dPos.as<int>() : nullptr, 2,
+                        wpeRows, stp, st));
   const int group = groupG;
   int nsplit = 1;
   if (decode) {
@@ -1170,7 +1193,8 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
   void* cur = x.p;
   void* nxt = x2.p;
   void* hb = h.p;
-  for (int l = 0; l < layers; ++l) {
+  if (ppRank > 0) worldComm->recvBf16(cur, (size_t)T * hidden, worldRank - world, st);      // the state the stage before left
+  for (int l = l0; l < l1; ++l) {
     LayerWeights& L = lw[l];
     norm(cur, L.n1, L.n1b, hb, T);
     if (spec.mla) {
@@ -1296,13 +1320,23 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
       if (comm) comm->allReduceBf16(cur, (size_t)T * hidden, st);
     }
   }
-  // rows that need logits -> final norm -> lm_head (fp32)
-  for (int r = 0; r < R; ++r)
-    XFT_CUDA(cudaMemcpyAsync(static_cast<char*>(nxt) + (size_t)r * hidden * 2, static_cast<char*>(cur) + (size_t)rowsel[r] * hidden * 2,
-                             (size_t)hidden * 2, cudaMemcpyDeviceToDevice, st));
-  norm(nxt, finalNorm, finalNormBias, hb, R);
   int hs = 0;
-  if (!comm) {
+  const bool lastStage = ppRank == pp - 1;
+  if (!lastStage) {
+    // hand the state to the same tensor-parallel rank of the next stage; the logits come back from the last one
+    worldComm->sendBf16(cur, (size_t)T * hidden, worldRank + world, st);
+    XFT_CUDA(cudaMemcpyAsync(&hs, stp, 4, cudaMemcpyDeviceToHost, st));
+    XFT_CUDA(cudaStreamSynchronize(st));
+  }
+  // rows that need logits -> final norm -> lm_head (fp32)
+  if (lastStage) {
+    for (int r = 0; r < R; ++r)
+      XFT_CUDA(cudaMemcpyAsync(static_cast<char*>(nxt) + (size_t)r * hidden * 2, static_cast<char*>(cur) + (size_t)rowsel[r] * hidden * 2,
+                               (size_t)hidden * 2, cudaMemcpyDeviceToDevice, st));
+    norm(nxt, finalNorm, finalNormBias, hb, R);
+  }
+  if (!lastStage) {
+  } else if (!comm) {
     logits.ensure((size_t)R * vocab * 4);
     gemm(hb, hidden, lmHead.p, vocab, logits.p, vocab, 1, 0, 0, nullptr, nullptr, 0, R);
     hostLogits.resize((size_t)R * vocab);
@@ -1332,6 +1366,11 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
     }
   }
   if (hs != 0) { cudaMemset(stp, 0, 4); throw std::runtime_error("kernel status " + std::to_string(hs)); }
+  if (pp > 1) {
+    // every rank samples from the same logits: they travel from the first rank of the last stage
+    hostLogits.resize((size_t)R * vocabG);
+    worldComm->broadcastHost(hostLogits.data(), hostLogits.size() * 4, (pp - 1) * world);
+  }
   for (int sid : seqIds) { SequenceMeta& s = pool.get(sid); s.pastLen += (int)s.pending.size(); s.pending.clear(); }
   return R;
 }
@@ -1346,9 +1385,9 @@ Model::~Model() {
 void Model::load(const std::string& path, DataType dt, DataType kv, std::shared_ptr<Communicator> comm) {
   engine.reset(new Engine(path, dt, kv, std::move(comm)));
 }
-bool Model::isMaster() { return !engine || engine->rank == 0; }
-int Model::getRank() { return engine ? engine->rank : 0; }
-int Model::getWorldSize() { return engine ? engine->world : 1; }
+bool Model::isMaster() { return !engine || engine->worldRank == 0; }
+int Model::getRank() { return engine ? engine->worldRank : 0; }
+int Model::getWorldSize() { return engine ? engine->worldSize : 1; }
 int Model::getVocabSize() { return engine->vocabG; }
 int Model::getMaxSeqLen() { return engine->maxPos; }
 
@@ -1362,10 +1401,10 @@ void Model::config(int maxLen, int numBeams, int numBeamHypsToKeep, float lenPen
 namespace {
 // Tensor-parallel ranks run the same program (as the reference's ranks do under mpirun, src/models/models.cpp:202-253):
 // what the caller passes on rank 0 is what every rank uses.  These helpers copy rank 0's arguments to the others.
-void syncValue(Engine& e, void* p, size_t bytes) { if (e.comm) e.comm->broadcastHost(p, bytes); }
+void syncValue(Engine& e, void* p, size_t bytes) { if (e.worldComm) e.worldComm->broadcastHost(p, bytes); }
 template <class T>
 void syncVector(Engine& e, std::vector<T>& v) {
-  if (!e.comm) return;
+  if (!e.worldComm) return;
   long long n = (long long)v.size();
   syncValue(e, &n, sizeof(n));
   v.resize((size_t)n);
@@ -1373,7 +1412,7 @@ void syncVector(Engine& e, std::vector<T>& v) {
 }
 template <class T>
 void syncNested(Engine& e, std::vector<std::vector<T>>& v) {
-  if (!e.comm) return;
+  if (!e.worldComm) return;
   std::vector<long long> lens;
   for (auto& r : v) lens.push_back((long long)r.size());
   syncVector(e, lens);
@@ -1455,7 +1494,7 @@ std::vector<int32_t> beamStep(Engine& e, const SearcherConfig& c) {
 void Model::config(SearcherConfig& c0, const std::vector<std::vector<int>>& sw0) {
   SearcherConfig c = c0;
   std::vector<std::vector<int>> sw = sw0;
-  if (engine->comm) {
+  if (engine->worldComm) {
     // one seed for all ranks, or their samplers would pick different tokens
     if (c.doSample && c.seed == 0) c.seed = (unsigned long long)std::chrono::steady_clock::now().time_since_epoch().count() | 1ull;
     syncValue(*engine, &c, sizeof(c));

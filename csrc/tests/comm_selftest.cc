@@ -1,7 +1,8 @@
 // Host-only test of the thread-rank communicator (csrc/core/comm.cc): the CUDA runtime calls and the device sum that
 // comm.cc makes are replaced by host stand-ins defined here, so the turn-taking protocol itself runs on a CPU box —
-// sums, gathers and broadcasts over many rounds with 1 to 8 ranks, no two ranks ever between collectives at once, and
-// a rank that leaves early makes the others fail instead of waiting for ever.  Built with -fsanitize=thread by
+// sums, gathers, broadcasts, messages between neighbours and sub-group collectives over many rounds with 1 to 8 ranks,
+// no two ranks ever between operations at once; a rank that leaves early, or ranks that wait for one another, make the
+// others fail instead of waiting for ever.  Built with -fsanitize=thread by
 // tests/test_cpp_runtime.py.
 #include <cuda_runtime.h>
 #include <cstdio>
@@ -49,6 +50,26 @@ static int processRank(int rank, int world, const char* idFile) {
     const unsigned short want[9] = {0, 0x3f80, 0x4000, 0x4040, 0x4080, 0x40a0, 0x40c0, 0x40e0, 0x4100};   // bf16 of 0..8
     if (h[32] != want[world]) throw std::runtime_error("bad sum");
     c->barrier();
+    // a ring of messages (pipeline stage boundaries), a broadcast from the last rank, and pairs made by a split
+    if (world > 1) {
+      std::vector<unsigned short> msg(1000, (unsigned short)(100 + rank)), got(1000, 0);
+      if (rank > 0) c->recvBf16(got.data(), got.size(), rank - 1, nullptr);
+      if (rank + 1 < world) c->sendBf16(msg.data(), msg.size(), rank + 1, nullptr);
+      if (rank > 0 && got[999] != (unsigned short)(100 + rank - 1)) throw std::runtime_error("bad message");
+      long long v = rank == world - 1 ? 4242 : -1;
+      c->broadcastHost(&v, sizeof(v), world - 1);
+      if (v != 4242) throw std::runtime_error("bad broadcast from the last rank");
+    }
+    if (world == 4) {
+      auto sub = c->split(rank / 2, rank % 2);
+      if (sub->size() != 2 || sub->rank() != rank % 2) throw std::runtime_error("bad split");
+      std::vector<unsigned short> one(8, (unsigned short)0x3f80);
+      sub->allReduceBf16(one.data(), one.size(), nullptr);
+      if (one[7] != 0x4000) throw std::runtime_error("bad sum in the sub-group");
+      long long v = rank % 2 == 0 ? 1000 + rank / 2 : -1;
+      sub->broadcastHost(&v, sizeof(v));
+      if (v != 1000 + rank / 2) throw std::runtime_error("bad broadcast in the sub-group");
+    }
     std::printf("rank %d of %d ok\n", rank, world);
     return 0;
   } catch (const std::exception& e) {
@@ -84,6 +105,27 @@ int main(int argc, char** argv) {
         c->broadcastHost(&v, sizeof(v));
         if (v != 777 + it) throw std::runtime_error("bad broadcast");
         c->barrier();
+        // a pipeline: a message from every rank to the next one, then a broadcast from the last rank
+        std::vector<unsigned short> msg(32, (unsigned short)(r * 3 + it)), got(32, 0);
+        if (r > 0) c->recvBf16(got.data(), 32, r - 1, nullptr);
+        if (r + 1 < n) c->sendBf16(msg.data(), 32, r + 1, nullptr);
+        if (r > 0 && got[31] != (unsigned short)((r - 1) * 3 + it)) throw std::runtime_error("bad message");
+        long long w = r == n - 1 ? 31 + it : -1;
+        c->broadcastHost(&w, sizeof(w), n - 1);
+        if (w != 31 + it) throw std::runtime_error("bad broadcast from the last rank");
+      }
+      if (n >= 4 && n % 2 == 0) {
+        // sub-groups (the tensor-parallel group of a pipeline stage): pairs {0,1}, {2,3}, ... sum among themselves, and
+        // a message crosses from each pair to the next while the world communicator stays usable
+        auto sub = c->split(r / 2, r % 2);
+        if (sub->size() != 2 || sub->rank() != r % 2) throw std::runtime_error("bad split");
+        for (int it = 0; it < 50; ++it) {
+          std::vector<unsigned short> buf(8, (unsigned short)(r + it));
+          if (r >= 2) c->recvBf16(buf.data(), 8, r - 2, nullptr);
+          sub->allReduceBf16(buf.data(), 8, nullptr);
+          if (r + 2 < n) c->sendBf16(buf.data(), 8, r + 2, nullptr);
+          c->barrier();
+        }
       }
       ok[r] = 1;
     } catch (const std::exception& e) { std::printf("rank %d: %s\n", r, e.what()); }
@@ -97,5 +139,15 @@ int main(int argc, char** argv) {
   std::thread a([&] { try { c2[0]->begin(); int x = 0; c2[0]->broadcastHost(&x, 4); c2[0]->broadcastHost(&x, 4); std::printf("rank0 unexpectedly passed\n"); } catch (const std::exception& e) { std::printf("rank0 failed as expected: %s\n", e.what()); } c2[0]->end(); });
   std::thread b([&] { c2[1]->begin(); int x = 0; c2[1]->broadcastHost(&x, 4); c2[1]->end(); });
   a.join(); b.join();
-  return good == n && !overlap ? 0 : 1;
+  // two ranks that wait for a message from each other: both must fail, not hang
+  auto c3 = xft::makeThreadCommunicators(2);
+  int failed = 0;
+  auto waits = [&](int r) {
+    try { c3[r]->begin(); unsigned short x[4]; c3[r]->recvBf16(x, 4, 1 - r, nullptr); std::printf("rank%d unexpectedly received\n", r); }
+    catch (const std::exception& e) { __sync_add_and_fetch(&failed, 1); std::printf("rank%d failed as expected: %s\n", r, e.what()); }
+    c3[r]->end();
+  };
+  std::thread d(waits, 0), e(waits, 1);
+  d.join(); e.join();
+  return good == n && !overlap && failed == 2 ? 0 : 1;
 }

@@ -1,8 +1,9 @@
-// A stand-in for libnccl.so.2 for tests WITHOUT GPUs: the seven entry points csrc/core/comm.cc resolves with dlsym,
+// A stand-in for libnccl.so.2 for tests WITHOUT GPUs: the entry points csrc/core/comm.cc resolves with dlsym,
 // working on HOST pointers between processes of one machine through a shared-memory file.  Built as a shared object by
 // tests/test_cpp_runtime.py and handed to the communicator through XFT_NCCL_LIB, next to host stand-ins for the CUDA
 // runtime calls (csrc/tests/comm_selftest.cc).  It implements just what the test needs: float32 / bfloat16 / uint8
-// data, sum, up to 8 ranks, messages up to 4 MiB.
+// data, sum, up to 8 ranks, messages up to 4 MiB; point-to-point messages go through the sender's slot (one message per
+// pair at a time, the sender waits until it is taken); a split makes a new shared-memory file per colour.
 #include <fcntl.h>
 #include <sys/mman.h>
 #include <unistd.h>
@@ -18,9 +19,11 @@ constexpr size_t kSlot = 4u << 20;
 struct Shared {
   std::atomic<int> arrived;
   std::atomic<int> generation;
-  char pad[56];
+  std::atomic<int> mail[64];             // [source * 8 + destination]: 1 while a message waits in the source's slot
+  std::atomic<int> splits;               // how many splits this communicator has made (names of the new files)
+  char pad[52];
 };
-struct Comm { int rank, world; Shared* sh; char* slots; size_t bytes; };
+struct Comm { int rank, world; Shared* sh; char* slots; size_t bytes; char name[128]; };
 struct Id { char bytes[128]; };
 
 void barrier(Comm* c) {
@@ -61,7 +64,8 @@ int ncclCommInitRank(void** comm, int world, Id id, int rank) {
   void* p = mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
   close(fd);
   if (p == MAP_FAILED) return 2;
-  Comm* c = new Comm{rank, world, static_cast<Shared*>(p), static_cast<char*>(p) + sizeof(Shared), bytes};
+  Comm* c = new Comm{rank, world, static_cast<Shared*>(p), static_cast<char*>(p) + sizeof(Shared), bytes, {0}};
+  std::snprintf(c->name, sizeof(c->name), "%s", id.bytes);
   *comm = c;
   barrier(c);
   if (rank == 0) shm_unlink(id.bytes);
@@ -109,6 +113,55 @@ int ncclBroadcast(const void* send, void* recv, size_t count, int dt, int root, 
   std::memcpy(recv, c->slots + (size_t)root * kSlot, bytes);
   barrier(c);
   return 0;
+}
+// point to point: the message waits in the second half of the sender's slot, so a collective in flight is not disturbed
+int ncclSend(const void* send, size_t count, int dt, int peer, void* comm, void*) {
+  Comm* c = static_cast<Comm*>(comm);
+  const size_t bytes = count * elemSize(dt);
+  if (bytes > kSlot / 2 || peer < 0 || peer >= c->world || peer == c->rank) return 4;
+  std::atomic<int>& flag = c->sh->mail[c->rank * 8 + peer];
+  std::memcpy(c->slots + (size_t)c->rank * kSlot + kSlot / 2, send, bytes);
+  flag.store(1);
+  for (long spin = 0; flag.load() != 0; ++spin) {
+    if (spin > 200000000L) { std::fprintf(stderr, "fake nccl: send timed out\n"); std::_Exit(3); }
+    if ((spin & 1023) == 1023) usleep(50);
+  }
+  return 0;
+}
+int ncclRecv(void* recv, size_t count, int dt, int peer, void* comm, void*) {
+  Comm* c = static_cast<Comm*>(comm);
+  const size_t bytes = count * elemSize(dt);
+  if (bytes > kSlot / 2 || peer < 0 || peer >= c->world || peer == c->rank) return 4;
+  std::atomic<int>& flag = c->sh->mail[peer * 8 + c->rank];
+  for (long spin = 0; flag.load() != 1; ++spin) {
+    if (spin > 200000000L) { std::fprintf(stderr, "fake nccl: receive timed out\n"); std::_Exit(3); }
+    if ((spin & 1023) == 1023) usleep(50);
+  }
+  std::memcpy(recv, c->slots + (size_t)peer * kSlot + kSlot / 2, bytes);
+  flag.store(0);
+  return 0;
+}
+int ncclCommSplit(void* comm, int color, int key, void** out, void*) {
+  Comm* c = static_cast<Comm*>(comm);
+  // everyone publishes (colour, key), then works out its group, its rank in it and the group's file name
+  int* mine = reinterpret_cast<int*>(c->slots + (size_t)c->rank * kSlot);
+  mine[0] = color; mine[1] = key;
+  barrier(c);
+  int rank = 0, world = 0;
+  for (int r = 0; r < c->world; ++r) {
+    const int* o = reinterpret_cast<const int*>(c->slots + (size_t)r * kSlot);
+    if (o[0] != color) continue;
+    ++world;
+    if (o[1] < key || (o[1] == key && r < c->rank)) ++rank;
+  }
+  const int serial = c->sh->splits.load();
+  barrier(c);
+  if (c->rank == 0) c->sh->splits.fetch_add(1);
+  Id id;
+  std::memset(&id, 0, sizeof(id));
+  std::snprintf(id.bytes, sizeof(id.bytes), "%.90s_s%d_c%d", c->name, serial, color);
+  barrier(c);
+  return ncclCommInitRank(out, world, id, rank);
 }
 const char* ncclGetErrorString(int rc) { return rc == 0 ? "ok" : rc == 2 ? "fake nccl: shared memory" : "fake nccl: unsupported call"; }
 }

@@ -46,8 +46,9 @@ def hostcheck(tmp_path_factory):
     return exe
 
 
-def _run(exe, d, dtype, kv, ranks, fake=True):
-    env = dict(os.environ, XFT_ARENA_EXACT="1", ASAN_OPTIONS="detect_leaks=1", UBSAN_OPTIONS="print_stacktrace=1")
+def _run(exe, d, dtype, kv, ranks, fake=True, stages=1):
+    env = dict(os.environ, XFT_ARENA_EXACT="1", ASAN_OPTIONS="detect_leaks=1", UBSAN_OPTIONS="print_stacktrace=1",
+               XFT_PIPELINE_STAGE=str(stages))
     if fake:
         env["XFT_FAKE_MODEL"] = "2"
     else:
@@ -155,12 +156,12 @@ def test_engine_host_side_gptq_checkpoint(hostcheck, qt, dtype, tmp_path):
 # ------------------------------------------------------------------------------------------------------------------
 # numerics: the C++ engine over the arithmetic stand-in against the package's fp32 PyTorch path
 
-def _engine_logits(exe, d, ranks, prompt, steps, kv="fp16", wdt="bf16"):
+def _engine_logits(exe, d, ranks, prompt, steps, kv="fp16", wdt="bf16", stages=1):
     B, P = prompt.shape
     idf, outf = os.path.join(d, "ids.txt"), os.path.join(d, "logits.%d.bin" % ranks)
     with open(idf, "w") as f:
         f.write("%d %d %d\n" % (B, P, steps) + " ".join(str(int(x)) for x in prompt.flatten().tolist()) + "\n")
-    env = dict(os.environ, XFT_MOCK_MATH="1", XFT_ARENA_EXACT="1", ASAN_OPTIONS="detect_leaks=1")
+    env = dict(os.environ, XFT_MOCK_MATH="1", XFT_ARENA_EXACT="1", ASAN_OPTIONS="detect_leaks=1", XFT_PIPELINE_STAGE=str(stages))
     env.pop("XFT_FAKE_MODEL", None)
     r = subprocess.run([exe, "logits", d, wdt, kv, str(ranks), idf, outf], env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0 and "hostcheck logits ok" in r.stdout, (d, ranks, r.stdout[-500:], r.stderr[-3000:])
@@ -393,3 +394,51 @@ def test_engine_logits_quantised_expert_families(hostcheck, fam, dtype, tmp_path
     err = (got - want).abs().amax(-1)
     assert err.median().item() < (0.06 if dtype.startswith("w8a8") else 0.03) * top and err.max().item() < 0.15 * top, \
         (fam, dtype, err.tolist(), top)
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# pipeline stages (XFT_PIPELINE_STAGE): world = stages x tensor-parallel ranks
+
+@pytest.mark.parametrize("fam,stages,ranks", [("llama", 2, 2), ("llama", 2, 4), ("llama", 3, 3), ("chatglm", 2, 2), ("gpt", 2, 4),
+                                              ("mixtral", 2, 4), ("qwen3_moe", 4, 4)])
+def test_engine_host_side_pipeline_stages(hostcheck, fam, stages, ranks, tmp_path):
+    """Every request shape (batch generation, sampling, beams, continuous batching, prefix sharing) with the layers cut
+    into pipeline stages: each stage keeps the KV cache of its own layers, the hidden state crosses the stage borders,
+    the logits come back from the last stage, and every rank must end with the same tokens."""
+    kw = dict(_BASE, model_type=fam, num_layer=4)
+    kw.update(_FAMILIES[fam])
+    d = str(tmp_path / fam)
+    ModelConfig(**kw).to_ini(d)
+    _run(hostcheck, d, "bf16", "int8" if fam == "llama" else "fp16", ranks, stages=stages)
+
+
+@pytest.mark.parametrize("fam,stages,ranks", [("llama", 2, 2), ("llama", 2, 4), ("llama", 3, 6), ("chatglm", 2, 2), ("telechat", 4, 4),
+                                              ("mixtral", 2, 4)])
+def test_engine_logits_pipeline_stages(hostcheck, fam, stages, ranks, tmp_path, monkeypatch):
+    """Logits of a model cut into pipeline stages (with tensor-parallel groups inside the stages where ranks > stages; four
+    layers over three stages: 2 + 1 + 1) against the fp32 PyTorch path."""
+    d = _synthetic_dir(tmp_path, fam, dict(_NUMERIC[fam], num_layer=4))
+    prompt = torch.randint(5, 290, (2, 20), generator=torch.Generator().manual_seed(4))
+    got, tokens = _engine_logits(hostcheck, d, ranks, prompt, 3, stages=stages)
+    want = _oracle_logits(d, prompt, tokens, monkeypatch)
+    top = max(1.0, want.abs().max().item())
+    err = (got - want).abs().amax(-1)
+    if fam == "mixtral":
+        assert err.median().item() < 0.03 * top and err.max().item() < 0.15 * top, (fam, stages, ranks, err.tolist(), top)
+    else:
+        assert err.max().item() < 0.04 * top, (fam, stages, ranks, err.tolist(), top)
+
+
+def test_engine_logits_pipeline_stages_deepseek(hostcheck, tmp_path, monkeypatch):
+    """DeepSeek over three stages (the dense first layer alone on stage 0) and over two stages of two ranks each."""
+    from xfastertransformer_b200.tools.synthetic import write_synthetic_checkpoint
+    cfg = _deepseek_config()
+    d = str(tmp_path / "ds")
+    write_synthetic_checkpoint(d, cfg, seed=0, dtype="bf16", std=0.05)
+    prompt = torch.randint(0, 300, (2, 20), generator=torch.Generator().manual_seed(3))
+    for stages, ranks in ((3, 3), (2, 4)):
+        got, tokens = _engine_logits(hostcheck, d, ranks, prompt, 3, stages=stages)
+        want = _oracle_logits(d, prompt, tokens, monkeypatch)
+        top = max(1.0, want.abs().max().item())
+        err = (got - want).abs().amax(-1)
+        assert err.max().item() < 0.04 * top, (stages, ranks, err.tolist(), top)
