@@ -2,9 +2,10 @@
 // are threads of this process (csrc/core/comm.h: they take turns, collectives are done on the host side of the device
 // queue), and the logits of the prompt pass and of a few decode steps are compared.  What it covers: the head / FFN /
 // vocabulary ranges every rank loads, bias and residual entering once, the sums after the two row-parallel projections,
-// the gathered head — everything of the multi-process NCCL mode except the NCCL calls themselves.
+// the gathered head — everything of the multi-process NCCL mode except the NCCL calls themselves.  With -s the ranks
+// form that many pipeline stages (ranks / stages tensor-parallel ranks each), as XFT_PIPELINE_STAGE does for processes.
 //
-//   tp_check -m <model dir> [-n ranks] [-d bf16|int8|...] [--kv_cache_dtype fp16|int8] [-o decode steps] [--tol t]
+//   tp_check -m <model dir> [-n ranks] [-s stages] [-d bf16|int8|...] [--kv_cache_dtype fp16|int8] [-o decode steps] [--tol t]
 //
 // (The reference has no counterpart: its ranks are always MPI processes.)
 #include <algorithm>
@@ -54,20 +55,26 @@ void run(xft::Model& m, std::vector<std::vector<int32_t>> prompts, int steps, co
 
 int main(int argc, char** argv) {
   std::string model, dtype = "bf16", kv = "fp16";
-  int ranks = 2, steps = 4;
+  int ranks = 2, steps = 4, stages = 0;
   double tol = 0.05;
   for (int i = 1; i < argc; ++i) {
     const std::string a = argv[i];
     auto next = [&]() -> std::string { if (i + 1 >= argc) { std::fprintf(stderr, "missing value for %s\n", a.c_str()); std::exit(2); } return argv[++i]; };
     if (a == "-m") model = next();
     else if (a == "-n") ranks = std::atoi(next().c_str());
+    else if (a == "-s") stages = std::atoi(next().c_str());
     else if (a == "-d") dtype = next();
     else if (a == "--kv_cache_dtype") kv = next();
     else if (a == "-o") steps = std::atoi(next().c_str());
     else if (a == "--tol") tol = std::atof(next().c_str());
     else { std::fprintf(stderr, "unknown flag %s\n", a.c_str()); return 2; }
   }
-  if (model.empty() || ranks < 2 || ranks > 8) { std::fprintf(stderr, "usage: tp_check -m <model dir> [-n 2..8] [-d dtype] [-o steps]\n"); return 2; }
+  if (model.empty() || ranks < 2 || ranks > 8 || stages < 0 || (stages > 0 && ranks % stages)) {
+    std::fprintf(stderr, "usage: tp_check -m <model dir> [-n 2..8] [-s stages, a divisor of the ranks] [-d dtype] [-o steps]\n");
+    return 2;
+  }
+  // the runtime reads its flags once, at first use: set the stage count before any model exists
+  if (stages > 0) setenv("XFT_PIPELINE_STAGE", std::to_string(stages).c_str(), 1);
   const xft::DataType wdt = xft::dataTypeFromName(dtype.c_str());
   const xft::DataType kdt = kv == "int8" ? xft::DataType::int8 : xft::DataType::fp16;
   if (wdt == xft::DataType::unknown) { std::fprintf(stderr, "unknown weight type %s\n", dtype.c_str()); return 2; }

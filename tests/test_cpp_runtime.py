@@ -328,6 +328,9 @@ def test_example_cli_flags_follow_the_reference(core):
         assert subprocess.run([tp, "-m", "/nonexistent", "-n", "1"], capture_output=True, text=True, timeout=60).returncode == 2
         r = subprocess.run([tp, "-m", "/nonexistent", "-n", "2"], capture_output=True, text=True, timeout=60)
         assert r.returncode == 1 and "config.ini" in r.stderr
+        assert subprocess.run([tp, "-m", "/nonexistent", "-n", "4", "-s", "3"], capture_output=True, text=True, timeout=60).returncode == 2
+        r = subprocess.run([tp, "-m", "/nonexistent", "-n", "4", "-s", "2"], capture_output=True, text=True, timeout=60)
+        assert r.returncode == 1 and "config.ini" in r.stderr
 
 
 def test_rope_and_alibi_tables_match_python(core):
