@@ -43,6 +43,11 @@ def hostcheck(tmp_path_factory):
     b = subprocess.run(["g++", "-fsanitize=address,undefined"] + [o for o, _ in jobs] + ["-o", exe, "-ldl", "-lpthread"],
                        capture_output=True, text=True, timeout=900)
     assert b.returncode == 0, b.stderr[-4000:]
+    # the example programs over the same stand-in (everything but the harness's own main)
+    for prog in ("tp_check", "cb_check"):
+        b = subprocess.run(["g++", "-O1"] + flags + [os.path.join(ROOT, "examples", "cpp", prog + ".cpp")] + [o for o, _ in jobs[1:]] +
+                           ["-o", str(out / prog), "-ldl", "-lpthread"], capture_output=True, text=True, timeout=900)
+        assert b.returncode == 0, b.stderr[-4000:]
     return exe
 
 
@@ -442,3 +447,19 @@ def test_engine_logits_pipeline_stages_deepseek(hostcheck, tmp_path, monkeypatch
         top = max(1.0, want.abs().max().item())
         err = (got - want).abs().amax(-1)
         assert err.max().item() < 0.04 * top, (stages, ranks, err.tolist(), top)
+
+
+def test_example_programs_over_the_stand_in(hostcheck, tmp_path):
+    """examples/cpp/cb_check.cpp (sequences decoded alone and inside a staggered continuous batch must agree) and
+    examples/cpp/tp_check.cpp (thread ranks — tensor-parallel, or pipeline stages with -s — against a single rank), built
+    over the arithmetic stand-in and run on a CPU box."""
+    d = _synthetic_dir(tmp_path, "llama", dict(num_layer=4))
+    here = os.path.dirname(hostcheck)
+    env = dict(os.environ, XFT_MOCK_MATH="1", XFT_ARENA_EXACT="1", ASAN_OPTIONS="detect_leaks=1")
+    env.pop("XFT_FAKE_MODEL", None)
+    r = subprocess.run([os.path.join(here, "cb_check"), "-m", d, "-n", "5", "-o", "6", "--stride", "2", "--min_len", "4", "--max_len", "70"],
+                       env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, (r.stdout[-1500:], r.stderr[-1500:])
+    for extra in (["-n", "2"], ["-n", "3", "-d", "int8", "--kv_cache_dtype", "int8"], ["-n", "4", "-s", "2"], ["-n", "2", "-s", "2"]):
+        r = subprocess.run([os.path.join(here, "tp_check"), "-m", d, "-o", "3"] + extra, env=env, capture_output=True, text=True, timeout=900)
+        assert r.returncode == 0, (extra, r.stdout[-1500:], r.stderr[-1500:])
