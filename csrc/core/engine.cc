@@ -220,6 +220,7 @@ public:
 
   // Runs the pending inputs of `ids`; logits land in hostLogits [rows, vocab].  Returns rows.
   int forward(const std::vector<int>& ids, bool logitsAll);
+  int forwardPart(const std::vector<int>& ids, bool logitsAll, bool shareLogits);
   void ensureBlocks(int extra);
   void release(int id) { tables->free(id); pool.remove(id); }
   void attachPrefix(SequenceMeta& s);
@@ -1001,7 +1002,27 @@ void Engine::attachPrefix(SequenceMeta& s) {
   }
 }
 
+// One forward pass.  Over pipeline stages the sequences may be cut into XFT_MAX_REQUEST_NUM micro-batches: a stage hands
+// micro-batch m on and starts on m + 1 while the next stage works on m (the sends are asynchronous on the stream); the
+// last stage collects the logits of all of them and every rank receives them once, at the end.
 int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
+  const int parts = pp > 1 ? std::min<int>(Env::get().maxRequestNum, (int)seqIds.size()) : 1;
+  if (parts <= 1) return forwardPart(seqIds, logitsAll, true);
+  std::vector<float> all;
+  int rows = 0;
+  for (int m = 0; m < parts; ++m) {
+    const size_t b = seqIds.size() * m / parts, e = seqIds.size() * (m + 1) / parts;
+    const int r = forwardPart(std::vector<int>(seqIds.begin() + b, seqIds.begin() + e), logitsAll, false);
+    if (ppRank == pp - 1) all.insert(all.end(), hostLogits.begin(), hostLogits.begin() + (size_t)r * vocabG);
+    rows += r;
+  }
+  hostLogits.swap(all);
+  hostLogits.resize((size_t)rows * vocabG);
+  worldComm->broadcastHost(hostLogits.data(), hostLogits.size() * 4, (pp - 1) * world);
+  return rows;
+}
+
+int Engine::forwardPart(const std::vector<int>& seqIds, bool logitsAll, bool shareLogits) {
   TimeLine tl("Decoder.forward");
   const auto t_begin = std::chrono::steady_clock::now();
   struct StepLog {
@@ -1366,7 +1387,7 @@ int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
     }
   }
   if (hs != 0) { cudaMemset(stp, 0, 4); throw std::runtime_error("kernel status " + std::to_string(hs)); }
-  if (pp > 1) {
+  if (pp > 1 && shareLogits) {
     // every rank samples from the same logits: they travel from the first rank of the last stage
     hostLogits.resize((size_t)R * vocabG);
     worldComm->broadcastHost(hostLogits.data(), hostLogits.size() * 4, (pp - 1) * world);

@@ -43,6 +43,7 @@ Env& Env::get() {
 void Env::reload() {
   verbose = envInt("XFT_VERBOSE", 0);
   pipelineStage = std::max(1, envInt("XFT_PIPELINE_STAGE", 1));
+  maxRequestNum = std::max(1, envInt("XFT_MAX_REQUEST_NUM", 1));
   fakeModel = envInt("XFT_FAKE_MODEL", 0);
   fakeLoadInfo = envInt("XFT_FAKE_LOAD_INFO", 0) != 0;
   timeline = envInt("XFT_TIMELINE", 0) != 0;

@@ -16,6 +16,7 @@ public:
 
   int verbose = 0;                     // XFT_VERBOSE: 0 quiet, 1 per-step timings, 2 per-kernel notes
   int pipelineStage = 1;               // XFT_PIPELINE_STAGE
+  int maxRequestNum = 1;               // XFT_MAX_REQUEST_NUM: micro-batches of one forward pass over pipeline stages
   int fakeModel = 0;                   // XFT_FAKE_MODEL: 1 zeros, 2 random N(0, 0.02)
   bool fakeLoadInfo = false;           // XFT_FAKE_LOAD_INFO
   bool timeline = false;               // XFT_TIMELINE

@@ -51,9 +51,9 @@ def hostcheck(tmp_path_factory):
     return exe
 
 
-def _run(exe, d, dtype, kv, ranks, fake=True, stages=1):
+def _run(exe, d, dtype, kv, ranks, fake=True, stages=1, micro=1):
     env = dict(os.environ, XFT_ARENA_EXACT="1", ASAN_OPTIONS="detect_leaks=1", UBSAN_OPTIONS="print_stacktrace=1",
-               XFT_PIPELINE_STAGE=str(stages))
+               XFT_PIPELINE_STAGE=str(stages), XFT_MAX_REQUEST_NUM=str(micro))
     if fake:
         env["XFT_FAKE_MODEL"] = "2"
     else:
@@ -161,12 +161,13 @@ def test_engine_host_side_gptq_checkpoint(hostcheck, qt, dtype, tmp_path):
 # ------------------------------------------------------------------------------------------------------------------
 # numerics: the C++ engine over the arithmetic stand-in against the package's fp32 PyTorch path
 
-def _engine_logits(exe, d, ranks, prompt, steps, kv="fp16", wdt="bf16", stages=1):
+def _engine_logits(exe, d, ranks, prompt, steps, kv="fp16", wdt="bf16", stages=1, micro=1):
     B, P = prompt.shape
     idf, outf = os.path.join(d, "ids.txt"), os.path.join(d, "logits.%d.bin" % ranks)
     with open(idf, "w") as f:
         f.write("%d %d %d\n" % (B, P, steps) + " ".join(str(int(x)) for x in prompt.flatten().tolist()) + "\n")
-    env = dict(os.environ, XFT_MOCK_MATH="1", XFT_ARENA_EXACT="1", ASAN_OPTIONS="detect_leaks=1", XFT_PIPELINE_STAGE=str(stages))
+    env = dict(os.environ, XFT_MOCK_MATH="1", XFT_ARENA_EXACT="1", ASAN_OPTIONS="detect_leaks=1", XFT_PIPELINE_STAGE=str(stages),
+               XFT_MAX_REQUEST_NUM=str(micro))
     env.pop("XFT_FAKE_MODEL", None)
     r = subprocess.run([exe, "logits", d, wdt, kv, str(ranks), idf, outf], env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0 and "hostcheck logits ok" in r.stdout, (d, ranks, r.stdout[-500:], r.stderr[-3000:])
@@ -463,3 +464,20 @@ def test_example_programs_over_the_stand_in(hostcheck, tmp_path):
     for extra in (["-n", "2"], ["-n", "3", "-d", "int8", "--kv_cache_dtype", "int8"], ["-n", "4", "-s", "2"], ["-n", "2", "-s", "2"]):
         r = subprocess.run([os.path.join(here, "tp_check"), "-m", d, "-o", "3"] + extra, env=env, capture_output=True, text=True, timeout=900)
         assert r.returncode == 0, (extra, r.stdout[-1500:], r.stderr[-1500:])
+
+
+def test_engine_pipeline_micro_batches(hostcheck, tmp_path, monkeypatch):
+    """XFT_MAX_REQUEST_NUM cuts the sequences of a forward pass into micro-batches that travel through the stages one
+    after the other; the logits are collected on the last stage and shared once.  Every request shape with 2 and 3
+    micro-batches, and the logits of three sequences in two micro-batches (2 + 1) against the fp32 PyTorch path."""
+    kw = dict(_BASE, model_type="llama", num_layer=4)
+    d = str(tmp_path / "cfg")
+    ModelConfig(**kw).to_ini(d)
+    _run(hostcheck, d, "bf16", "fp16", 2, stages=2, micro=2)
+    _run(hostcheck, d, "bf16", "int8", 4, stages=2, micro=3)
+    d2 = _synthetic_dir(tmp_path, "llama", dict(num_layer=4))
+    prompt = torch.randint(5, 290, (3, 20), generator=torch.Generator().manual_seed(4))
+    got, tokens = _engine_logits(hostcheck, d2, 4, prompt, 3, stages=2, micro=2)
+    want = _oracle_logits(d2, prompt, tokens, monkeypatch)
+    top = max(1.0, want.abs().max().item())
+    assert (got - want).abs().max().item() < 0.04 * top
