@@ -183,7 +183,10 @@ int logitsMain(int argc, char** argv) {
   const std::string dir = argv[2];
   const xft::DataType wdt = xft::dataTypeFromName(argv[3]);
   const xft::DataType kdt = std::string(argv[4]) == "int8" ? xft::DataType::int8 : xft::DataType::fp16;
-  const int ranks = std::atoi(argv[5]);
+  // <ranks> = "env": this process is ONE rank of a group of processes; rank and world size come from the launcher's
+  // variables, the ranks meet through the NCCL communicator (in tests: a stand-in library named by XFT_NCCL_LIB)
+  const bool procs = std::string(argv[5]) == "env";
+  const int ranks = procs ? 1 : std::atoi(argv[5]);
   if (wdt == xft::DataType::unknown || ranks < 1 || ranks > 8) { std::fprintf(stderr, "bad arguments\n"); return 2; }
   LogitsRun proto;
   {
@@ -195,7 +198,11 @@ int logitsMain(int argc, char** argv) {
   }
   std::vector<LogitsRun> runs(ranks, proto);
   std::vector<std::string> errors(ranks);
-  if (ranks == 1) {
+  if (procs) {
+    xft::AutoModel m(dir, wdt, kdt);
+    if (gen) recordGenerate(m, runs[0], beams, eos); else recordLogits(m, runs[0]);
+    if (!m.isMaster()) { std::printf("hostcheck rank %d of %d done\n", m.getRank(), m.getWorldSize()); return 0; }
+  } else if (ranks == 1) {
     xft::AutoModel m(dir, wdt, kdt, nullptr);
     if (gen) recordGenerate(m, runs[0], beams, eos); else recordLogits(m, runs[0]);
   } else {

@@ -43,6 +43,10 @@ def hostcheck(tmp_path_factory):
     b = subprocess.run(["g++", "-fsanitize=address,undefined"] + [o for o, _ in jobs] + ["-o", exe, "-ldl", "-lpthread"],
                        capture_output=True, text=True, timeout=900)
     assert b.returncode == 0, b.stderr[-4000:]
+    # a stand-in NCCL for the runs with process ranks
+    b = subprocess.run(["g++", "-O1", "-g", "-std=c++17", "-shared", "-fPIC", os.path.join(ROOT, "csrc", "tests", "fake_nccl.cc"), "-o",
+                        str(out / "libfake_nccl.so"), "-lrt", "-lpthread"], capture_output=True, text=True, timeout=900)
+    assert b.returncode == 0, b.stderr[-4000:]
     # the example programs over the same stand-in (everything but the harness's own main)
     for prog in ("tp_check", "cb_check"):
         b = subprocess.run(["g++", "-O1"] + flags + [os.path.join(ROOT, "examples", "cpp", prog + ".cpp")] + [o for o, _ in jobs[1:]] +
@@ -481,3 +485,43 @@ def test_engine_pipeline_micro_batches(hostcheck, tmp_path, monkeypatch):
     want = _oracle_logits(d2, prompt, tokens, monkeypatch)
     top = max(1.0, want.abs().max().item())
     assert (got - want).abs().max().item() < 0.04 * top
+
+
+@pytest.mark.parametrize("fam,world,stages", [("llama", 2, 1), ("llama", 4, 2), ("chatglm2", 3, 1), ("mixtral", 2, 1), ("llama", 2, 2)])
+def test_engine_process_ranks_over_stand_in_nccl(hostcheck, fam, world, stages, tmp_path, monkeypatch):
+    """The engine as REAL processes, one per rank, that find their rank in the launcher's variables and meet through the
+    NCCL communicator (csrc/core/comm.cc: library opened with dlopen, id through a file, bf16 sums, gathers, host
+    broadcasts, and for pipeline stages send / receive and the split into tensor-parallel groups) — against a stand-in
+    NCCL over shared memory and the arithmetic stand-in of the device library.  Rank 0 writes the logits, which are
+    compared with the fp32 PyTorch path."""
+    d = _synthetic_dir(tmp_path, fam, dict(_NUMERIC[fam], num_layer=4))
+    prompt = torch.randint(5, 290, (2, 20), generator=torch.Generator().manual_seed(4))
+    steps = 3
+    idf, outf = os.path.join(d, "ids.txt"), os.path.join(d, "logits.procs.bin")
+    with open(idf, "w") as f:
+        f.write("2 20 %d\n" % steps + " ".join(str(int(x)) for x in prompt.flatten().tolist()) + "\n")
+    here = os.path.dirname(hostcheck)
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, XFT_MOCK_MATH="1", XFT_ARENA_EXACT="1", ASAN_OPTIONS="detect_leaks=1", RANK=str(r), WORLD_SIZE=str(world),
+                   LOCAL_RANK=str(r), XFT_NCCL_LIB=os.path.join(here, "libfake_nccl.so"), XFT_COMM_ID_FILE=str(tmp_path / "nccl_id"),
+                   XFT_DIST_TIMEOUT_S="60", XFT_PIPELINE_STAGE=str(stages))
+        for k in ("XFT_FAKE_MODEL", "SINGLE_INSTANCE", "OMPI_COMM_WORLD_RANK", "PMI_RANK"):
+            env.pop(k, None)
+        procs.append(subprocess.Popen([hostcheck, "logits", d, "bf16", "fp16", "env", idf, outf], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.PIPE, text=True))
+    outs = [p.communicate(timeout=600) for p in procs]
+    for r, (p, (so, se)) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0, (r, so[-500:], se[-3000:])
+    assert "hostcheck logits ok" in outs[0][0]
+    raw = open(outf, "rb").read()
+    b, v, n = struct.unpack("iii", raw[:12])
+    got = torch.from_numpy(np.frombuffer(raw, dtype=np.float32, count=n * b * v, offset=12).reshape(n, b, v).copy())
+    tokens = torch.from_numpy(np.frombuffer(raw, dtype=np.int32, count=n * b, offset=12 + 4 * n * b * v).reshape(n, b).copy())
+    want = _oracle_logits(d, prompt, tokens, monkeypatch)
+    top = max(1.0, want.abs().max().item())
+    err = (got - want).abs().amax(-1)
+    if fam == "mixtral":
+        assert err.median().item() < 0.03 * top and err.max().item() < 0.15 * top, (fam, world, err.tolist(), top)
+    else:
+        assert err.max().item() < 0.04 * top, (fam, world, stages, err.tolist(), top)
