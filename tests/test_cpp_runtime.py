@@ -424,7 +424,8 @@ def test_host_numeric_conversions_match_torch(core):
 
 
 def test_cmake_tree_configures_and_runs_the_native_tests(tmp_path):
-    """CMakeLists.txt: the tree configures for sm_100a, the native unit-test target builds and passes under ctest (the
+    """CMakeLists.txt: the tree configures for sm_100a, the native unit-test targets (the runtime's unit tests, the engine
+    over the stand-in device library) build and pass under ctest (the
     kernel and core libraries are built the same way; that takes minutes and is left to `cmake --build`)."""
     import shutil
     import subprocess
@@ -438,8 +439,8 @@ def test_cmake_tree_configures_and_runs_the_native_tests(tmp_path):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     flags = open(os.path.join(b, "CMakeFiles", "xft_b200_kernels.dir", "flags.make")).read()
     assert "compute_100a" in flags and "sm_100a" in flags                  # Blackwell's architecture-specific target
-    r = subprocess.run(["cmake", "--build", b, "--target", "xft_runtime_selftest", "-j", "4"], capture_output=True, text=True,
-                       timeout=600, env=env)
+    r = subprocess.run(["cmake", "--build", b, "--target", "xft_runtime_selftest", "xft_engine_hostcheck", "-j", "8"],
+                       capture_output=True, text=True, timeout=900, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     r = subprocess.run(["ctest", "--output-on-failure"], cwd=b, capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0 and "100% tests passed" in r.stdout, r.stdout[-2000:]
