@@ -525,3 +525,24 @@ def test_engine_process_ranks_over_stand_in_nccl(hostcheck, fam, world, stages, 
         assert err.median().item() < 0.03 * top and err.max().item() < 0.15 * top, (fam, world, err.tolist(), top)
     else:
         assert err.max().item() < 0.04 * top, (fam, world, stages, err.tolist(), top)
+
+
+def test_gpu_rank_cases_over_the_stand_in(hostcheck, tmp_path):
+    """The cases of tests/test_zzz_cpp_ranks_gpu.py (tp_check on expert families, DeepSeek, pipeline stages) with the same
+    checkpoints and tolerances, over the arithmetic stand-in: what runs there on a GPU has run here first."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("cpp_ranks_gpu", os.path.join(ROOT, "tests", "test_zzz_cpp_ranks_gpu.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    exe = os.path.join(os.path.dirname(hostcheck), "tp_check")
+    env = dict(os.environ, XFT_MOCK_MATH="1", XFT_ARENA_EXACT="1", ASAN_OPTIONS="detect_leaks=1")
+    for k in ("XFT_FAKE_MODEL", "XFT_PIPELINE_STAGE"):
+        env.pop(k, None)
+    for i, case in enumerate(sorted(mod.CASES)):
+        sub = tmp_path / ("c%d" % i)
+        sub.mkdir()
+        mod.tp_check_case(exe, case, sub, env=env)
+    for i, ranks in enumerate((["-n", "2"], ["-n", "4", "-s", "2"])):
+        sub = tmp_path / ("d%d" % i)
+        sub.mkdir()
+        mod.deepseek_case(exe, ranks, sub, env=env)
