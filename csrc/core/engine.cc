@@ -15,6 +15,7 @@
 #include <map>
 #include <random>
 #include <stdexcept>
+#include <thread>
 
 #include "arena.h"
 #include "beam.h"
@@ -660,36 +661,47 @@ void Engine::requantiseRows(DevBuf& w, size_t rows, int K, int kind) {
   const int mode = kind == 3 ? 2 : kind == 4 ? 1 : 0;
   const size_t chunk = std::max<size_t>(1, ((size_t)64 << 20) / ((size_t)K * 2));      // 64 MiB of rows at a time
   std::vector<uint16_t> host;
-  std::vector<float> v(K);
   for (size_t r0 = 0; r0 < rows; r0 += chunk) {
     const size_t n = std::min(chunk, rows - r0);
     host.resize(n * K);
     char* dev = static_cast<char*>(w.p) + r0 * K * 2;
     XFT_CUDA(cudaMemcpy(host.data(), dev, n * K * 2, cudaMemcpyDeviceToHost));
-    for (size_t r = 0; r < n; ++r) {
-      uint16_t* row = host.data() + r * K;
-      float mx = -INFINITY, mn = INFINITY;
-      for (int i = 0; i < K; ++i) {
-        v[i] = bf16ToFloat(row[i]);
-        mx = std::max(mx, mode == 2 ? std::fabs(v[i]) : v[i]);
-        mn = std::min(mn, v[i]);
-      }
-      if (mode == 0) {
-        const float sc = std::max((mx - mn) / 255.0f, 1e-10f), zp = (mx + mn) * 0.5f + 0.5f * sc;
-        for (int i = 0; i < K; ++i) row[i] = floatToBf16(std::min(std::max(std::nearbyint((v[i] - zp) / sc), -128.f), 127.f) * sc + zp);
-      } else if (mode == 1) {
-        const float sc = std::max((mx - mn) / 15.0f, 1e-10f);
-        for (int i = 0; i < K; ++i) row[i] = floatToBf16(std::min(std::max(std::nearbyint((v[i] - mn) / sc), 0.f), 15.f) * sc + mn);
-      } else {
-        const float sc = std::max(mx, 1e-10f);
+    // rows are independent: spread them over the host cores
+    const unsigned workers = (unsigned)std::min<size_t>(std::max(1u, std::thread::hardware_concurrency()), std::max<size_t>(1, n / 64));
+    auto work = [&](size_t first, size_t last) {
+      std::vector<float> v(K);
+      for (size_t r = first; r < last; ++r) {
+        uint16_t* row = host.data() + r * K;
+        float mx = -INFINITY, mn = INFINITY;
         for (int i = 0; i < K; ++i) {
-          const float xn = v[i] / sc;
-          int best = 0;
-          float bd = std::fabs(xn - nf4[0]);
-          for (int c = 1; c < 16; ++c) { const float d = std::fabs(xn - nf4[c]); if (d < bd) { bd = d; best = c; } }
-          row[i] = floatToBf16(nf4[best] * sc);
+          v[i] = bf16ToFloat(row[i]);
+          mx = std::max(mx, mode == 2 ? std::fabs(v[i]) : v[i]);
+          mn = std::min(mn, v[i]);
+        }
+        if (mode == 0) {
+          const float sc = std::max((mx - mn) / 255.0f, 1e-10f), zp = (mx + mn) * 0.5f + 0.5f * sc;
+          for (int i = 0; i < K; ++i) row[i] = floatToBf16(std::min(std::max(std::nearbyint((v[i] - zp) / sc), -128.f), 127.f) * sc + zp);
+        } else if (mode == 1) {
+          const float sc = std::max((mx - mn) / 15.0f, 1e-10f);
+          for (int i = 0; i < K; ++i) row[i] = floatToBf16(std::min(std::max(std::nearbyint((v[i] - mn) / sc), 0.f), 15.f) * sc + mn);
+        } else {
+          const float sc = std::max(mx, 1e-10f);
+          for (int i = 0; i < K; ++i) {
+            const float xn = v[i] / sc;
+            int best = 0;
+            float bd = std::fabs(xn - nf4[0]);
+            for (int c = 1; c < 16; ++c) { const float d = std::fabs(xn - nf4[c]); if (d < bd) { bd = d; best = c; } }
+            row[i] = floatToBf16(nf4[best] * sc);
+          }
         }
       }
+    };
+    if (workers <= 1) {
+      work(0, n);
+    } else {
+      std::vector<std::thread> pool;
+      for (unsigned w = 0; w < workers; ++w) pool.emplace_back(work, n * w / workers, n * (w + 1) / workers);
+      for (auto& t : pool) t.join();
     }
     XFT_CUDA(cudaMemcpy(dev, host.data(), n * K * 2, cudaMemcpyHostToDevice));
   }
