@@ -8,7 +8,8 @@
 // and the continuous-batching calls set_input(ids, seqIDs, maxLen) / forward() / freeSeqs().  The native engine
 // runs all sixteen families on one B200: llama, yarn_llama, gemma, qwen, qwen2, qwen3, baichuan (RoPE or ALiBi), chatglm,
 // chatglm2 / 3 / 4, gpt (OPT), telechat, the routed-expert families mixtral and qwen3_moe, and deepseek_moe (latent
-// attention, shared + routed experts, e4m3 checkpoints dequantised to bf16 at load).  Dense families take bf16 / fp16,
+// attention, shared + routed experts; from e4m3 checkpoints the routed experts stay e4m3 on the device, the rest is
+// dequantised to bf16 at load).  Dense families take bf16 / fp16,
 // int8, w8a8, int4, nf4 weights (quantised at load) and the hybrid types (one form for the prompt pass, one for decode
 // steps), from dense or GPTQ-converted checkpoints; Mixtral and Qwen3-MoE take the quantised and hybrid types (experts keep the
 // quantised values in bf16), DeepSeek runs in bf16.  Every family also runs on several

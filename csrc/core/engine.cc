@@ -110,6 +110,10 @@ struct LayerWeights {
   DevBuf n1b, n2b, oBias, fc1Bias, fc2Bias;      // LayerNorm biases, output-projection bias, biases of the two-matrix MLP
   DevBuf router, expGateUp, expDown;             // mixture of experts: [E, hidden], stacked [E * 2I, hidden], [E * hidden, I]
   DevBuf expGateUpNext, expDownNext;             // hybrid weight types: the experts as the decode steps see them
+  // DeepSeek e4m3 checkpoints: the experts stay e4m3 on the device (bytes in expGateUp / expDown, one fp32 scale per
+  // 128 x 128 block here), the grouped GEMM expands tiles on the way to the tensor core
+  DevBuf expGateUpScale, expDownScale;
+  bool fp8Experts = false;
   // DeepSeek.  Attention: merged down-projection [q_lora (or heads * qk) + kv_lora + rope, hidden], its norms, the query
   // up-projection, and the per-head halves of kv_b: W_uk transposed [heads * kv_lora, nope], W_uv [heads * v, kv_lora].
   DevBuf qkvA, qANorm, qB, kvANorm, wkT, wv;
@@ -241,6 +245,7 @@ private:
                     int c0 = 0, int c1 = -1);
   void loadMlaLayer(const std::string& p, LayerWeights& L, int layer);
   void requantiseRows(DevBuf& w, size_t rows, int K, int kind);
+  void loadFp8Expert(const std::string& base, int inF, int outF, uint8_t* bytes, float* scales);
   // dense bf16 [rows, K] -> the prompt-pass form `first` and, for hybrid types, the decode form `next`; `dense` is
   // released unless a bf16 form points at it
   void quantise(DevBuf& dense, int rows, int K, Lin& first, Lin& next);
@@ -811,6 +816,30 @@ void Engine::loadMlaLayer(const std::string& p, LayerWeights& L, int layer) {
   L.routerBias = loadVector(p + "mlp.gate.e_score_correction_bias.bin", E, true, 2);
   if (sharedInter > 0) gatedMlp(p + "mlp.shared_experts.", sharedInterG, s0, sharedInter, L.sharedGateUp, L.sharedDown);
   const int EL = e1 - e0;
+  // e4m3 files whose sizes fit the grouped e4m3 GEMM (whole 128 x 128 blocks) keep the experts in e4m3: half the bytes of
+  // bf16 on the device and in every decode step (XFT_FP8_EXPERTS=0 dequantises them like the other tensors)
+  const char* fp8Env = std::getenv("XFT_FP8_EXPERTS");
+  L.fp8Experts = fileDt == 3 && !Env::get().fakeModel && I % 128 == 0 && H % 128 == 0 && !(fp8Env && *fp8Env == '0');
+  if (L.fp8Experts) {
+    const size_t guRows = (size_t)EL * 2 * I, dnRows = (size_t)EL * H;
+    const int guBlocks = H / 128, dnBlocks = I / 128;                 // scale columns: blocks along the reduction
+    std::vector<uint8_t> gu(guRows * H), dn(dnRows * I);
+    std::vector<float> gus(guRows / 128 * guBlocks), dns(dnRows / 128 * dnBlocks);
+    for (int e = e0; e < e1; ++e) {
+      const std::string ep = p + "mlp.experts." + std::to_string(e) + ".";
+      const size_t l = (size_t)(e - e0);
+      loadFp8Expert(ep + "gate_proj", H, I, gu.data() + l * 2 * I * H, gus.data() + l * (2 * I / 128) * guBlocks);
+      loadFp8Expert(ep + "up_proj", H, I, gu.data() + (l * 2 * I + I) * H, gus.data() + (l * (2 * I / 128) + I / 128) * guBlocks);
+      loadFp8Expert(ep + "down_proj", I, H, dn.data() + l * H * I, dns.data() + l * (H / 128) * dnBlocks);
+    }
+    L.expGateUp.reset(gu.size()); L.expDown.reset(dn.size());
+    L.expGateUpScale.reset(gus.size() * 4); L.expDownScale.reset(dns.size() * 4);
+    XFT_CUDA(cudaMemcpy(L.expGateUp.p, gu.data(), gu.size(), cudaMemcpyHostToDevice));
+    XFT_CUDA(cudaMemcpy(L.expDown.p, dn.data(), dn.size(), cudaMemcpyHostToDevice));
+    XFT_CUDA(cudaMemcpy(L.expGateUpScale.p, gus.data(), gus.size() * 4, cudaMemcpyHostToDevice));
+    XFT_CUDA(cudaMemcpy(L.expDownScale.p, dns.data(), dns.size() * 4, cudaMemcpyHostToDevice));
+    return;
+  }
   L.expGateUp.reset((size_t)EL * 2 * I * H * 2);
   L.expDown.reset((size_t)EL * H * I * 2);
   for (int e = e0; e < e1; ++e) {
@@ -820,6 +849,27 @@ void Engine::loadMlaLayer(const std::string& p, LayerWeights& L, int layer) {
     loadDsLinear(ep + "up_proj", H, I, L.expGateUp.p, l * 2 * I + I, H);
     loadDsLinear(ep + "down_proj", I, H, L.expDown.p, l * H, I);
   }
+}
+
+// One expert matrix of an e4m3 checkpoint: the file holds bytes [in, out] and fp32 scales [in / 128, out / 128]; the device
+// wants rows of outputs — bytes [out, in], scales [out / 128, in / 128] — written at `bytes` / `scales` (rows contiguous).
+void Engine::loadFp8Expert(const std::string& base, int inF, int outF, uint8_t* bytes, float* scales) {
+  std::ifstream f(dir + "/" + base + ".weight.bin", std::ios::binary | std::ios::ate);
+  if (!f) throw std::runtime_error("cannot open " + base + ".weight.bin");
+  if ((size_t)f.tellg() != (size_t)inF * outF) throw std::runtime_error(base + ".weight.bin: unexpected size");
+  std::vector<uint8_t> w((size_t)inF * outF);
+  f.seekg(0);
+  f.read(reinterpret_cast<char*>(w.data()), (std::streamsize)w.size());
+  constexpr int T = 64;                       // transpose in tiles: both sides stay in cache
+  for (int i0 = 0; i0 < inF; i0 += T)
+    for (int o0 = 0; o0 < outF; o0 += T)
+      for (int i = i0; i < std::min(i0 + T, inF); ++i)
+        for (int o = o0; o < std::min(o0 + T, outF); ++o) bytes[(size_t)o * inF + i] = w[(size_t)i * outF + o];
+  const int sr = inF / 128, sc = outF / 128;
+  auto s = readFile(dir + "/" + base + ".weight_scale_inv.bin", (size_t)sr * sc * 4, 0);
+  const float* sv = reinterpret_cast<const float*>(s.data());
+  for (int i = 0; i < sr; ++i)
+    for (int o = 0; o < sc; ++o) scales[(size_t)o * sr + i] = sv[(size_t)i * sc + o];
 }
 
 void Engine::loadGptqLayer(const std::string& p, LayerLins& first, LayerLins& next) {
@@ -1274,10 +1324,19 @@ int Engine::forwardPart(const std::vector<int>& seqIds, bool logitsAll, bool sha
       XFT_K(xft_moe_plan(moeIdx.as<int>(), moeWts.as<float>(), T, k, e0, e1, moeBn, moePos.as<int>(), moeSrc.as<int>(),
                          moeRowW.as<float>(), moeTiles.p, moeMeta.as<int>(), moeMaxTiles, T * k, st));
       XFT_K(xft_moe_gather(hb, hidden, moeSrc.as<int>(), moeMeta.as<int>(), moeXs.p, T * k, hidden, st));
-      XFT_K(xft_gemm_bf16_grouped(moeXs.p, hidden, T * k, L.expGateUp.p, EL * 2 * I, hidden, moeH1.p, I, 0, I, hidden, 1, I,
-                                  2 * I, moeTiles.p, moeMeta.as<int>(), moeMaxTiles, moeBn, nullptr, 2, stp, st));
-      XFT_K(xft_gemm_bf16_grouped(moeH1.p, I, T * k, L.expDown.p, EL * hidden, I, moeYs.p, hidden, 1, hidden, I, 0, 0, hidden,
-                                  moeTiles.p, moeMeta.as<int>(), moeMaxTiles, moeBn, moeRowW.as<float>(), 0, stp, st));
+      if (L.fp8Experts) {
+        XFT_K(xft_qgemm_grouped(moeXs.p, hidden, T * k, L.expGateUp.p, EL * 2 * I, hidden, moeH1.p, I, 0, I, hidden, 1, I, 2 * I,
+                                L.expGateUpScale.as<float>(), hidden / 128, moeTiles.p, moeMeta.as<int>(), moeMaxTiles, moeBn,
+                                nullptr, 2, stp, st));
+        XFT_K(xft_qgemm_grouped(moeH1.p, I, T * k, L.expDown.p, EL * hidden, I, moeYs.p, hidden, 1, hidden, I, 0, 0, hidden,
+                                L.expDownScale.as<float>(), I / 128, moeTiles.p, moeMeta.as<int>(), moeMaxTiles, moeBn,
+                                moeRowW.as<float>(), 0, stp, st));
+      } else {
+        XFT_K(xft_gemm_bf16_grouped(moeXs.p, hidden, T * k, L.expGateUp.p, EL * 2 * I, hidden, moeH1.p, I, 0, I, hidden, 1, I,
+                                    2 * I, moeTiles.p, moeMeta.as<int>(), moeMaxTiles, moeBn, nullptr, 2, stp, st));
+        XFT_K(xft_gemm_bf16_grouped(moeH1.p, I, T * k, L.expDown.p, EL * hidden, I, moeYs.p, hidden, 1, hidden, I, 0, 0, hidden,
+                                    moeTiles.p, moeMeta.as<int>(), moeMaxTiles, moeBn, moeRowW.as<float>(), 0, stp, st));
+      }
       const float* sharedOut = nullptr;
       if (sharedInter > 0) {
         gemm(hb, hidden, L.sharedGateUp.p, 2 * sharedInter, g.p, sharedInter, 0, 1, sharedInter, nullptr, nullptr, 2, T);

@@ -53,6 +53,12 @@ int xft_qgemm(const void* X, int ldx, const void* Wq, int w_rows, int ldw_bytes,
               int T, int N, int K, int gated, int dual_off, const float* scale, const float* zero, const float* xsum,
               int scale_ld, const float* bias, const void* residual, int ldr, float res_scale, int act, float* ws,
               size_t ws_bytes, int* counters, int n_counters, int* status, cudaStream_t st);
+// grouped (expert) form for e4m3 weights: Wq stacks the experts' [group_w_rows, K] bytes, scale their
+// [group_w_rows / 128, scale_ld] block scales (scale_ld = blocks along K); tiles / counts from xft_moe_plan
+int xft_qgemm_grouped(const void* X, int ldx, int x_rows, const void* Wq, int w_rows, int ldw_bytes, void* Y, int ldo,
+                      int out_fp32, int N, int K, int gated, int dual_off, int group_w_rows, const float* scale, int scale_ld,
+                      const void* group_tiles, const int* num_group_tiles, int max_tiles, int bn, const float* col_scale,
+                      int act, int* status, cudaStream_t st);
 int xft_row_sum(const void* x, int ldx, float* out, int T, int K, cudaStream_t st);
 int xft_quant_act(const void* x, int ldx, void* q, int ldq, float* scale, float* zero, float* qsum, int T, int K,
                   cudaStream_t st);

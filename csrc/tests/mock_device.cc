@@ -765,6 +765,55 @@ int xft_gemm_bf16_grouped(const void* X, int ldx, int x_rows, const void* W, int
   return 0;
 }
 
+// the same for experts kept in e4m3: bytes [w_rows, K], one fp32 scale per 128 x 128 block ([w_rows / 128, scale_ld]); a
+// weight enters the product as bf16(e4m3 * scale), as in the kernel that expands tiles in shared memory
+int xft_qgemm_grouped(const void* X, int ldx, int x_rows, const void* Wq, int w_rows, int ldw_bytes, void* Y, int ldo, int out_fp32,
+                      int N, int K, int gated, int dual_off, int group_w_rows, const float* scale, int scale_ld,
+                      const void* group_tiles, const int* num_group_tiles, int max_tiles, int bn, const float* col_scale, int act,
+                      int* status, cudaStream_t) {
+  static const bool report = [] {
+    const char* v = std::getenv("XFT_MOCK_REPORT");          // tests ask which path ran
+    if (v && *v && *v != '0') std::atexit([] { std::fprintf(stderr, "mock device: grouped e4m3 gemm ran\n"); });
+    return true;
+  }();
+  (void)report;
+  need(group_w_rows % 128 == 0 && (!gated || dual_off % 128 == 0) && K % 16 == 0, "grouped e4m3 gemm: sizes are not whole blocks");
+  need(scale_ld >= (K + 127) / 128, "grouped e4m3 gemm: scale rows shorter than the blocks along K");
+  const int* tl = static_cast<const int*>(group_tiles);
+  const int nt = num_group_tiles[0];
+  need(nt <= max_tiles, "grouped e4m3 gemm: tile count beyond the table");
+  const int rows_w = gated ? dual_off + N : N;
+  const uint8_t* W = static_cast<const uint8_t*>(Wq);
+  for (int i = 0; i < nt; ++i) {
+    const int g = tl[4 * i], r0 = tl[4 * i + 1], nr = tl[4 * i + 2];
+    need(nr >= 1 && nr <= bn && r0 >= 0 && r0 + nr <= x_rows, "grouped e4m3 gemm: tile outside the rows");
+    need((long long)g * group_w_rows + rows_w <= w_rows, "grouped e4m3 gemm: group outside the stacked weights");
+    rdRows(static_cast<const char*>(X) + (size_t)r0 * ldx * 2, nr, K, ldx, 2);
+    rdRows(W + (size_t)g * group_w_rows * ldw_bytes, rows_w, K, ldw_bytes, 1);
+    rd(scale + (size_t)(g * group_w_rows / 128) * scale_ld, (size_t)((rows_w + 127) / 128) * scale_ld * 4);
+    if (col_scale) rd(col_scale + r0, (size_t)nr * 4);
+    wrRows(static_cast<char*>(Y) + (size_t)r0 * ldo * (out_fp32 ? 4 : 2), nr, N, ldo, out_fp32 ? 4 : 2);
+    if (!g_math) continue;
+    std::vector<float> wf((size_t)rows_w * K), xf(K);
+    for (int n = 0; n < rows_w; ++n) {
+      const size_t row = (size_t)g * group_w_rows + n;
+      for (int k = 0; k < K; ++k) wf[(size_t)n * K + k] = rbf(e4m3ToFloat(W[row * ldw_bytes + k]) * scale[(row >> 7) * scale_ld + (k >> 7)]);
+    }
+    for (int r = r0; r < r0 + nr; ++r) {
+      for (int k = 0; k < K; ++k) xf[k] = bf(bfp(X)[(size_t)r * ldx + k]);
+      auto dot = [&](int n) { float a = 0.f; for (int k = 0; k < K; ++k) a += xf[k] * wf[(size_t)n * K + k]; return a; };
+      for (int n = 0; n < N; ++n) {
+        float x = actf(dot(n), act);
+        if (gated) x *= dot(dual_off + n);
+        if (col_scale) x *= col_scale[r];
+        if (out_fp32) static_cast<float*>(Y)[(size_t)r * ldo + n] = x; else bfp(Y)[(size_t)r * ldo + n] = tobf(x);
+      }
+    }
+  }
+  if (status) rd(status, 4);
+  return 0;
+}
+
 int xft_moe_combine(const float* ys, const int* pos, int k, const float* add1, const void* add2, int ld2, void* y, float* y32, int T,
                     int H, cudaStream_t) {
   for (int i = 0; i < T * k; ++i) if (pos[i] >= 0) rd(ys + (size_t)pos[i] * H, (size_t)H * 4);

@@ -165,7 +165,7 @@ def test_engine_host_side_gptq_checkpoint(hostcheck, qt, dtype, tmp_path):
 # ------------------------------------------------------------------------------------------------------------------
 # numerics: the C++ engine over the arithmetic stand-in against the package's fp32 PyTorch path
 
-def _engine_logits(exe, d, ranks, prompt, steps, kv="fp16", wdt="bf16", stages=1, micro=1):
+def _engine_logits(exe, d, ranks, prompt, steps, kv="fp16", wdt="bf16", stages=1, micro=1, extra_env=None, expect_stderr=None):
     B, P = prompt.shape
     idf, outf = os.path.join(d, "ids.txt"), os.path.join(d, "logits.%d.bin" % ranks)
     with open(idf, "w") as f:
@@ -173,8 +173,11 @@ def _engine_logits(exe, d, ranks, prompt, steps, kv="fp16", wdt="bf16", stages=1
     env = dict(os.environ, XFT_MOCK_MATH="1", XFT_ARENA_EXACT="1", ASAN_OPTIONS="detect_leaks=1", XFT_PIPELINE_STAGE=str(stages),
                XFT_MAX_REQUEST_NUM=str(micro))
     env.pop("XFT_FAKE_MODEL", None)
+    env.update(extra_env or {})
     r = subprocess.run([exe, "logits", d, wdt, kv, str(ranks), idf, outf], env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0 and "hostcheck logits ok" in r.stdout, (d, ranks, r.stdout[-500:], r.stderr[-3000:])
+    if expect_stderr is not None:
+        assert (expect_stderr[0] in r.stderr) == expect_stderr[1], r.stderr[-1000:]
     raw = open(outf, "rb").read()
     b, v, n = struct.unpack("iii", raw[:12])
     lg = np.frombuffer(raw, dtype=np.float32, count=n * b * v, offset=12).reshape(n, b, v)
@@ -267,8 +270,11 @@ def test_engine_logits_match_pytorch_deepseek(hostcheck, case, tmp_path, monkeyp
     d = str(tmp_path / "ds")
     write_synthetic_checkpoint(d, cfg, seed=0, dtype=cfg.weight_data_type, std=0.05)
     prompt = torch.randint(0, 300, (2, 20), generator=torch.Generator().manual_seed(3))
+    ran = "mock device: grouped e4m3 gemm ran"
     for ranks in (1, 2, 3 if case == "no-q-lora" else 4):
-        got, tokens = _engine_logits(hostcheck, d, ranks, prompt, 3)
+        # e4m3 files keep the experts in e4m3 on the device (the grouped e4m3 GEMM runs); bf16 files never reach it
+        got, tokens = _engine_logits(hostcheck, d, ranks, prompt, 3, extra_env={"XFT_MOCK_REPORT": "1"},
+                                     expect_stderr=(ran, case == "fp8_e4m3"))
         want = _oracle_logits(d, prompt, tokens, monkeypatch)
         top = max(1.0, want.abs().max().item())
         err = (got - want).abs().amax(-1)
@@ -276,6 +282,12 @@ def test_engine_logits_match_pytorch_deepseek(hostcheck, case, tmp_path, monkeyp
             assert (err < 0.04 * top).float().mean().item() >= 0.6, (case, ranks, err.tolist(), top)
         else:
             assert err.max().item() < 0.04 * top, (case, ranks, err.tolist(), top)
+    if case == "fp8_e4m3":
+        # XFT_FP8_EXPERTS=0: the experts are dequantised like every other tensor; same logits
+        got2, _ = _engine_logits(hostcheck, d, 1, prompt, 3, extra_env={"XFT_MOCK_REPORT": "1", "XFT_FP8_EXPERTS": "0"},
+                                 expect_stderr=(ran, False))
+        got1, _ = _engine_logits(hostcheck, d, 1, prompt, 3)
+        assert (got1 - got2).abs().max().item() < 0.02 * top
 
 
 @pytest.mark.parametrize("beams,eos", [(1, -1), (3, 299), (4, 17)])
