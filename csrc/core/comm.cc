@@ -30,6 +30,12 @@ int envInt(const char* name, int def) {
   return v && *v ? std::atoi(v) : def;
 }
 
+}  // namespace
+
+void Communicator::waitStream(cudaStream_t st) { cudaOk(cudaStreamSynchronize(st), "cudaStreamSynchronize"); }
+
+namespace {
+
 // ------------------------------------------------------------------------------------------------ thread ranks
 // Shared by every thread rank of one world: `turn` is the rank that may run, everyone else sleeps.  A rank that reaches
 // an operation it cannot finish alone leaves its arguments and hands the turn to the next rank; when the turn comes
@@ -292,6 +298,8 @@ struct NcclApi {
   int (*Send)(const void*, size_t, int, int, void*, cudaStream_t) = nullptr;              // pipeline stages only
   int (*Recv)(void*, size_t, int, int, void*, cudaStream_t) = nullptr;
   int (*CommSplit)(void*, int, int, void**, void*) = nullptr;                             // NCCL 2.18 and later
+  int (*CommAbort)(void*) = nullptr;                                                      // failure handling
+  int (*CommGetAsyncError)(void*, int*) = nullptr;
   const char* (*GetErrorString)(int) = nullptr;
 
   static NcclApi& get() {
@@ -316,6 +324,8 @@ struct NcclApi {
       api.Send = reinterpret_cast<decltype(api.Send)>(sym("ncclSend"));
       api.Recv = reinterpret_cast<decltype(api.Recv)>(sym("ncclRecv"));
       api.CommSplit = reinterpret_cast<decltype(api.CommSplit)>(sym("ncclCommSplit"));
+      api.CommAbort = reinterpret_cast<decltype(api.CommAbort)>(sym("ncclCommAbort"));
+      api.CommGetAsyncError = reinterpret_cast<decltype(api.CommGetAsyncError)>(sym("ncclCommGetAsyncError"));
       api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(sym("ncclGetErrorString"));
     });
     return api;
@@ -389,7 +399,7 @@ public:
       const size_t n = std::min(kStage, bytes - off);
       if (rank_ == root) cudaOk(cudaMemcpy(stage_, static_cast<char*>(data) + off, n, cudaMemcpyHostToDevice), "broadcast (stage in)");
       check(NcclApi::get().Broadcast(stage_, stage_, n, 1 /* uint8 */, root, comm_, nullptr), "ncclBroadcast");
-      cudaOk(cudaStreamSynchronize(nullptr), "broadcast");
+      waitStream(nullptr);
       if (rank_ != root) cudaOk(cudaMemcpy(static_cast<char*>(data) + off, stage_, n, cudaMemcpyDeviceToHost), "broadcast (stage out)");
     }
   }
@@ -411,7 +421,7 @@ public:
     float* dev = static_cast<float*>(stage_);
     cudaOk(cudaMemcpy(dev, mine.data(), 8, cudaMemcpyHostToDevice), "split");
     check(api.AllGather(dev, dev + 2, 2, 7 /* fp32 */, comm_, nullptr), "ncclAllGather (split)");
-    cudaOk(cudaStreamSynchronize(nullptr), "split");
+    waitStream(nullptr);
     cudaOk(cudaMemcpy(all.data(), dev + 2, all.size() * 4, cudaMemcpyDeviceToHost), "split");
     int newRank = 0, newSize = 0;
     for (int r = 0; r < world_; ++r) {
@@ -426,7 +436,33 @@ public:
   }
   void barrier() override {
     check(NcclApi::get().AllReduce(stage_, stage_, 1, 7, 0, comm_, nullptr), "barrier");
-    cudaOk(cudaStreamSynchronize(nullptr), "barrier");
+    waitStream(nullptr);
+  }
+
+  // cudaStreamSynchronize with a limit: polls the stream (busily at first — a decode step's collectives take
+  // microseconds — then with short sleeps) and NCCL's asynchronous error state
+  void waitStream(cudaStream_t st) override {
+    NcclApi& api = NcclApi::get();
+    const double limit = (double)envInt("XFT_DIST_TIMEOUT_S", 1800);
+    const auto t0 = std::chrono::steady_clock::now();
+    for (long spin = 0;; ++spin) {
+      const cudaError_t q = cudaStreamQuery(st);
+      if (q == cudaSuccess) return;
+      if (q != cudaErrorNotReady) cudaOk(q, "cudaStreamQuery");
+      int async = 0;
+      const bool bad = comm_ && api.CommGetAsyncError && (spin & 255) == 255 && api.CommGetAsyncError(comm_, &async) == 0 && async != 0;
+      const double waited = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+      if (bad || waited > limit) {
+        // give the communicator up: its kernels leave the device, so the process can report and end
+        if (comm_ && api.CommAbort) api.CommAbort(comm_);
+        comm_ = nullptr;
+        throw std::runtime_error(bad ? std::string("NCCL reported an asynchronous error (a rank was lost?): ") +
+                                           (api.GetErrorString ? api.GetErrorString(async) : std::to_string(async))
+                                     : "a collective did not finish within " + std::to_string((long)limit) +
+                                           " s (XFT_DIST_TIMEOUT_S): a rank was lost");
+      }
+      if (waited > 2e-3) std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
   }
 
 private:

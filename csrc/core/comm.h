@@ -38,6 +38,10 @@ public:
   // Collective over all ranks: the communicator of the ranks that pass the same `color`, ordered by `key` (the tensor-
   // parallel group of one pipeline stage).
   virtual std::shared_ptr<Communicator> split(int color, int key) = 0;
+  // Wait until the work queued on `st` is done.  Process ranks bound the wait: when a collective does not finish within
+  // XFT_DIST_TIMEOUT_S seconds (a rank was lost) or NCCL reports an asynchronous error, the communicator is aborted and
+  // std::runtime_error is thrown instead of waiting for ever.
+  virtual void waitStream(cudaStream_t st);
   // thread ranks: wait for this rank's first turn / give the turn up for good (no-ops for process ranks)
   virtual void begin() {}
   virtual void end() {}

@@ -1418,7 +1418,7 @@ int Engine::forwardPart(const std::vector<int>& seqIds, bool logitsAll, bool sha
     // hand the state to the same tensor-parallel rank of the next stage; the logits come back from the last one
     worldComm->sendBf16(cur, (size_t)T * hidden, worldRank + world, st);
     XFT_CUDA(cudaMemcpyAsync(&hs, stp, 4, cudaMemcpyDeviceToHost, st));
-    XFT_CUDA(cudaStreamSynchronize(st));
+    worldComm->waitStream(st);
   }
   // rows that need logits -> final norm -> lm_head (fp32)
   if (lastStage) {
@@ -1434,7 +1434,9 @@ int Engine::forwardPart(const std::vector<int>& seqIds, bool logitsAll, bool sha
     hostLogits.resize((size_t)R * vocab);
     XFT_CUDA(cudaMemcpyAsync(hostLogits.data(), logits.p, hostLogits.size() * 4, cudaMemcpyDeviceToHost, st));
     XFT_CUDA(cudaMemcpyAsync(&hs, stp, 4, cudaMemcpyDeviceToHost, st));
-    XFT_CUDA(cudaStreamSynchronize(st));
+    // with ranks before this one (pipeline stages) the stream holds a receive: wait with the communicator's limit
+    if (worldComm) worldComm->waitStream(st);
+    else XFT_CUDA(cudaStreamSynchronize(st));
   } else {
     // vocabulary-parallel head (src/layers/dist_linear.h:49-101): this rank's rows of the lm_head give a slice of every
     // logits row; slices are padded to the widest rank's width, gathered, and put in order on the host
@@ -1448,7 +1450,7 @@ int Engine::forwardPart(const std::vector<int>& seqIds, bool logitsAll, bool sha
     std::vector<float> all(per * world);
     XFT_CUDA(cudaMemcpyAsync(all.data(), gathered.p, all.size() * 4, cudaMemcpyDeviceToHost, st));
     XFT_CUDA(cudaMemcpyAsync(&hs, stp, 4, cudaMemcpyDeviceToHost, st));
-    XFT_CUDA(cudaStreamSynchronize(st));
+    comm->waitStream(st);                  // the sums and the gather of this step: a lost rank ends the wait with an error
     hostLogits.resize((size_t)R * vocabG);
     for (int r = 0; r < world; ++r) {
       const auto vr = taskRange(vocabG, world, r);

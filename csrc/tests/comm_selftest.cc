@@ -18,6 +18,8 @@ cudaError_t cudaDeviceSynchronize() { return cudaSuccess; }
 cudaError_t cudaMemcpyAsync(void* d, const void* s, size_t n, cudaMemcpyKind, cudaStream_t) { std::memmove(d, s, n); return cudaSuccess; }
 cudaError_t cudaMemcpy(void* d, const void* s, size_t n, cudaMemcpyKind) { std::memmove(d, s, n); return cudaSuccess; }
 cudaError_t cudaStreamSynchronize(cudaStream_t) { return cudaSuccess; }
+// XFT_STUB_STREAM_BUSY=1: a stream whose work never finishes (what a collective looks like when a rank is lost)
+cudaError_t cudaStreamQuery(cudaStream_t) { const char* v = getenv("XFT_STUB_STREAM_BUSY"); return v && *v == '1' ? cudaErrorNotReady : cudaSuccess; }
 cudaError_t cudaGetDeviceCount(int* n) { *n = 1; return cudaSuccess; }
 cudaError_t cudaSetDevice(int) { return cudaSuccess; }
 cudaError_t cudaMalloc(void** p, size_t n) { *p = malloc(n); return cudaSuccess; }

@@ -163,5 +163,12 @@ int ncclCommSplit(void* comm, int color, int key, void** out, void*) {
   barrier(c);
   return ncclCommInitRank(out, world, id, rank);
 }
+// failure handling: the stand-in can be told to report an asynchronous error; an abort just lets go of the mapping
+int ncclCommGetAsyncError(void*, int* err) {
+  const char* v = std::getenv("XFT_FAKE_NCCL_ASYNC_ERROR");
+  *err = v && *v == '1' ? 6 : 0;
+  return 0;
+}
+int ncclCommAbort(void* comm) { return ncclCommDestroy(comm); }
 const char* ncclGetErrorString(int rc) { return rc == 0 ? "ok" : rc == 2 ? "fake nccl: shared memory" : "fake nccl: unsupported call"; }
 }

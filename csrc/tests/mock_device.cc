@@ -131,6 +131,7 @@ cudaError_t cudaMemset(void* d, int v, size_t n) { if (n) std::memset(d, v, n); 
 cudaError_t cudaMemsetAsync(void* d, int v, size_t n, cudaStream_t) { if (n) std::memset(d, v, n); return cudaSuccess; }
 cudaError_t cudaStreamCreate(cudaStream_t* s) { static char token; *s = reinterpret_cast<cudaStream_t>(&token); return cudaSuccess; }
 cudaError_t cudaStreamSynchronize(cudaStream_t) { return cudaSuccess; }
+cudaError_t cudaStreamQuery(cudaStream_t) { return cudaSuccess; }
 cudaError_t cudaDeviceSynchronize() { return cudaSuccess; }
 cudaError_t cudaGetLastError() { return cudaSuccess; }
 cudaError_t cudaGetDeviceCount(int* n) { *n = 1; return cudaSuccess; }

@@ -719,7 +719,8 @@ def test_process_rank_communicator_with_a_stand_in_nccl(tmp_path):
     """The NCCL communicator of the C++ engine (csrc/core/comm.cc: library opened with dlopen, unique id handed over
     through a file, host broadcasts in pieces through a staging buffer, bf16 sums, gathers) as 1 to 4 real processes,
     against a stand-in NCCL over shared memory (csrc/tests/fake_nccl.cc) and host stand-ins for the CUDA calls; a rank
-    whose rank 0 never comes gives up after XFT_DIST_TIMEOUT_S with an error."""
+    whose rank 0 never comes gives up after XFT_DIST_TIMEOUT_S with an error, and so does a rank whose collective never
+    finishes or for which NCCL reports an asynchronous error (bounded wait, communicator aborted)."""
     import shutil
     import subprocess
     if shutil.which("g++") is None:
@@ -746,6 +747,20 @@ def test_process_rank_communicator_with_a_stand_in_nccl(tmp_path):
     lone = subprocess.run([exe, "process", "1", "2", str(tmp_path / "never")], env=dict(env, XFT_DIST_TIMEOUT_S="1"),
                           capture_output=True, text=True, timeout=60)
     assert lone.returncode == 1 and "did not arrive" in lone.stdout
+    # a collective that never finishes (the stream stays busy: what a lost rank looks like): the wait gives up after
+    # XFT_DIST_TIMEOUT_S, the communicator is aborted, the rank reports instead of waiting for ever ...
+    for extra, words in ((dict(XFT_DIST_TIMEOUT_S="1"), "did not finish within 1 s"),
+                         # ... and at once when NCCL itself reports an asynchronous error
+                         (dict(XFT_DIST_TIMEOUT_S="60", XFT_FAKE_NCCL_ASYNC_ERROR="1"), "asynchronous error")):
+        idf = str(tmp_path / "id_lost")
+        e2 = dict(env, XFT_STUB_STREAM_BUSY="1", **extra)
+        procs = [subprocess.Popen([exe, "process", str(r), "2", idf], env=e2, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+                 for r in (1, 0)]
+        outs = [p.communicate(timeout=60)[0] for p in procs]
+        assert all(p.returncode == 1 for p in procs) and all(words in o for o in outs), outs
+        for f in (idf, idf + ".ready"):
+            if os.path.exists(f):
+                os.remove(f)
 
 
 _BPE_CORPUS = [
