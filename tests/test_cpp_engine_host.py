@@ -554,7 +554,7 @@ def test_gpu_rank_cases_over_the_stand_in(hostcheck, tmp_path):
         sub = tmp_path / ("c%d" % i)
         sub.mkdir()
         mod.tp_check_case(exe, case, sub, env=env)
-    for i, ranks in enumerate((["-n", "2"], ["-n", "4", "-s", "2"])):
+    for i, (ranks, dtype) in enumerate(((["-n", "2"], "bf16"), (["-n", "4", "-s", "2"], "bf16"), (["-n", "2"], "fp8_e4m3"))):
         sub = tmp_path / ("d%d" % i)
         sub.mkdir()
-        mod.deepseek_case(exe, ranks, sub, env=env)
+        mod.deepseek_case(exe, ranks, sub, env=env, dtype=dtype)
