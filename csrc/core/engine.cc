@@ -245,6 +245,9 @@ private:
                     int c0 = 0, int c1 = -1);
   void loadMlaLayer(const std::string& p, LayerWeights& L, int layer);
   void requantiseRows(DevBuf& w, size_t rows, int K, int kind);
+  // XFT_DEBUG_DIR: the hidden state [T, hidden] at a named point of the forward pass goes to a file and a log line
+  void dumpState(const std::string& name, const void* state, int T);
+  long long debugStep = 0;
   void loadFp8Expert(const std::string& base, int inF, int outF, uint8_t* bytes, float* scales);
   // dense bf16 [rows, K] -> the prompt-pass form `first` and, for hybrid types, the decode form `next`; `dense` is
   // released unless a bf16 form points at it
@@ -654,6 +657,34 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_
     const size_t per = (size_t)(l1 - l0) * (kvBlockBytes() * (spec.mla ? 1 : 2) + (kvInt8 ? (size_t)kvHeads * kBlock * 8 : 0));
     ensureBlocks((int)std::max<size_t>(1, (size_t)(Env::get().kvCacheGb * (double)(1ull << 30)) / per));
   }
+}
+
+// Tensor dumps for debugging (reference: src/utils/debugger.h, dumpMatrix calls compiled in with -DDEBUG).  Here a run-time
+// switch, with the names and the log line of the Python engine (utils/debugger.py) so that the two can be compared file
+// by file: <dir>/rank<r>_step<k>_<name>.bin holds the first 64 rows as fp32, <dir>/rank<r>.log one summary line each.
+void Engine::dumpState(const std::string& name, const void* state, int T) {
+  const std::string& d = Env::get().debugDir;
+  if (d.empty()) return;
+  const int rows = std::min(T, 64);
+  std::vector<uint16_t> raw((size_t)rows * hidden);
+  XFT_CUDA(cudaStreamSynchronize(st));
+  XFT_CUDA(cudaMemcpy(raw.data(), state, raw.size() * 2, cudaMemcpyDeviceToHost));
+  std::vector<float> v(raw.size());
+  double sum = 0, amax = 0;
+  for (size_t i = 0; i < raw.size(); ++i) { v[i] = bf16ToFloat(raw[i]); sum += v[i]; amax = std::max(amax, (double)std::fabs(v[i])); }
+  const std::string base = d + "/rank" + std::to_string(worldRank);
+  {
+    std::ofstream f(base + "_step" + std::to_string(debugStep) + "_" + name + ".bin", std::ios::binary | std::ios::trunc);
+    if (!f) throw std::runtime_error("XFT_DEBUG_DIR: cannot write under " + d);
+    f.write(reinterpret_cast<const char*>(v.data()), (std::streamsize)(v.size() * 4));
+  }
+  char line[512];
+  std::string first;
+  for (size_t i = 0; i < std::min<size_t>(6, v.size()); ++i) { char b[32]; std::snprintf(b, sizeof(b), "%s%.5g", i ? ", " : "", v[i]); first += b; }
+  std::snprintf(line, sizeof(line), "step %lld %s: shape (%d, %d) dtype bf16 mean %.6g absmax %.6g first [%s]\n", debugStep, name.c_str(),
+                T, hidden, raw.empty() ? 0.0 : sum / (double)raw.size(), amax, first.c_str());
+  std::ofstream log(base + ".log", std::ios::app);
+  log << line;
 }
 
 // Every row of a bf16 matrix [rows, K] is replaced by its quantised-and-restored value under the weight type `kind`
@@ -1277,6 +1308,11 @@ int Engine::forwardPart(const std::vector<int>& seqIds, bool logitsAll, bool sha
   void* nxt = x2.p;
   void* hb = h.p;
   if (ppRank > 0) worldComm->recvBf16(cur, (size_t)T * hidden, worldRank - world, st);      // the state the stage before left
+  const bool dbg = !Env::get().debugDir.empty();
+  if (dbg) { ++debugStep; if (ppRank == 0) dumpState("embedding", cur, T); }
+  auto dumpLayer = [&](int l, const char* what, const void* state) {
+    if (dbg) dumpState("layer" + std::to_string(l) + "_" + what, state, T);
+  };
   for (int l = l0; l < l1; ++l) {
     LayerWeights& L = lw[l];
     norm(cur, L.n1, L.n1b, hb, T);
@@ -1307,11 +1343,13 @@ int Engine::forwardPart(const std::vector<int>& seqIds, bool logitsAll, bool sha
       // row-parallel with several ranks: the residual enters on rank 0, the ranks' products are added
       gemm(att.p, heads * vDim, L.o.p, hidden, nxt, hidden, 0, 0, 0, nullptr, rank == 0 ? cur : nullptr, 0, T);
       if (comm) comm->allReduceBf16(nxt, (size_t)T * hidden, st);
+      dumpLayer(l, "attn_out", nxt);
       norm(nxt, L.n2, L.n2b, hb, T);
       if (L.denseMlp) {
         gemm(hb, hidden, L.gateUp.p, 2 * inter, g.p, inter, 0, 1, inter, nullptr, nullptr, act, T);
         gemm(g.p, inter, L.down.p, hidden, cur, hidden, 0, 0, 0, nullptr, rank == 0 ? nxt : nullptr, 0, T);
         if (comm) comm->allReduceBf16(cur, (size_t)T * hidden, st);
+        dumpLayer(l, "ffn_out", cur);
         continue;
       }
       // ---- shared + routed experts (src/layers/moe_deepseek.h:121-196,285-353)
@@ -1346,6 +1384,7 @@ int Engine::forwardPart(const std::vector<int>& seqIds, bool logitsAll, bool sha
       XFT_K(xft_moe_combine(moeYs.as<float>(), moePos.as<int>(), k, sharedOut, rank == 0 ? nxt : nullptr, hidden, cur, nullptr, T,
                             hidden, st));
       if (comm) comm->allReduceBf16(cur, (size_t)T * hidden, st);
+      dumpLayer(l, "ffn_out", cur);
       continue;
     }
     const LayerLins& Q = (decode && wqNext != wq) ? linsNext[l] : lins[l];
@@ -1369,6 +1408,7 @@ int Engine::forwardPart(const std::vector<int>& seqIds, bool logitsAll, bool sha
     // are summed (src/layers/decoder_block.h:122-134 reduceAdd)
     lin(Q.o, att.p, nxt, hidden, 0, L.oBias.as<float>(), rank == 0 ? (spec.residFromNorm ? hb : cur) : nullptr, resScale, 0);
     if (comm) comm->allReduceBf16(nxt, (size_t)T * hidden, st);
+    dumpLayer(l, "attn_out", nxt);
     // ChatGLM-1 needs the normalised state again as the residual of the MLP: it goes to `cur`, whose content (the
     // block input) is no longer needed; every other family normalises into the scratch buffer
     void* hn = spec.residFromNorm ? cur : hb;
@@ -1396,6 +1436,7 @@ int Engine::forwardPart(const std::vector<int>& seqIds, bool logitsAll, bool sha
       XFT_K(xft_moe_combine(moeYs.as<float>(), moePos.as<int>(), k, nullptr, rank == 0 ? nxt : nullptr, hidden, cur, nullptr, T,
                             hidden, st));
       if (comm) comm->allReduceBf16(cur, (size_t)T * hidden, st);
+      dumpLayer(l, "ffn_out", cur);
       continue;
     }
     if (spec.mlp == 1) {
@@ -1411,6 +1452,7 @@ int Engine::forwardPart(const std::vector<int>& seqIds, bool logitsAll, bool sha
       lin(Q.down, g.p, cur, hidden, 0, L.fc2Bias.as<float>(), rank == 0 ? nxt : nullptr, resScale, 0);    // + residual, back into `cur`
       if (comm) comm->allReduceBf16(cur, (size_t)T * hidden, st);
     }
+    dumpLayer(l, "ffn_out", cur);
   }
   int hs = 0;
   const bool lastStage = ppRank == pp - 1;

@@ -558,3 +558,46 @@ def test_gpu_rank_cases_over_the_stand_in(hostcheck, tmp_path):
         sub = tmp_path / ("d%d" % i)
         sub.mkdir()
         mod.deepseek_case(exe, ranks, sub, env=env, dtype=dtype)
+
+
+@pytest.mark.parametrize("fam", ["llama", "chatglm", "mixtral"])
+def test_engine_debug_dumps_match_python_layer_by_layer(hostcheck, fam, tmp_path, monkeypatch):
+    """XFT_DEBUG_DIR: the C++ engine writes the hidden state after the embedding and after every attention and FFN block
+    under the names the Python engine uses, so the two can be compared layer by layer — done here for the prompt pass
+    (the C++ side over the arithmetic stand-in, the Python side on its fp32 path)."""
+    import xfastertransformer_b200 as xft
+    from xfastertransformer_b200.parallel.dist import DistContext
+    from xfastertransformer_b200.utils import debugger
+    from xfastertransformer_b200.utils.flags import Env
+    d = _synthetic_dir(tmp_path, fam, _NUMERIC[fam])
+    prompt = torch.randint(5, 290, (2, 20), generator=torch.Generator().manual_seed(4))
+    cpp_dir, py_dir = str(tmp_path / "cpp_dump"), str(tmp_path / "py_dump")
+    os.makedirs(cpp_dir)
+    _engine_logits(hostcheck, d, 1, prompt, 0, extra_env={"XFT_DEBUG_DIR": cpp_dir})
+    monkeypatch.setenv("XFT_ENGINE", "CPU")
+    monkeypatch.setenv("XFT_DEBUG_DIR", py_dir)
+    Env._inst = None
+    DistContext.reset()
+    try:
+        m = xft.AutoModel.from_pretrained(d, dtype="bf16")
+        first = debugger._step + 1
+        sid = m.set_input_cb(prompt.tolist(), None, 30)
+        m.forward_cb()
+        m.free_seqs(sid)
+    finally:
+        monkeypatch.delenv("XFT_ENGINE")
+        monkeypatch.delenv("XFT_DEBUG_DIR")
+        Env._inst = None
+        DistContext.reset()
+    names = ["embedding"] + ["layer%d_%s_out" % (l, w) for l in range(2) for w in ("attn", "ffn")]
+    log = open(os.path.join(cpp_dir, "rank0.log")).read()
+    for name in names:
+        got = torch.from_numpy(np.fromfile(os.path.join(cpp_dir, "rank0_step1_%s.bin" % name), dtype=np.float32).reshape(-1, 256))
+        want = torch.load(os.path.join(py_dir, "rank0_step%d_%s.pt" % (first, name)))
+        assert got.shape == want.shape == (40, 256), (name, got.shape, want.shape)
+        scale = max(1.0, want.abs().max().item())
+        # (the expert layers of the random Mixtral amplify rounding differences on single elements; see the logits test)
+        diff = (got - want).abs()
+        assert diff.max().item() < (0.06 if fam == "mixtral" else 0.03) * scale and diff.mean().item() < 0.005 * scale, \
+            (fam, name, diff.max().item(), diff.mean().item(), scale)
+        assert ("step 1 %s: shape (40, 256) dtype bf16" % name) in log
