@@ -92,7 +92,14 @@ std::vector<char> fakeTensor(const std::string& path, size_t bytes, int dt, int 
 }
 
 std::vector<char> readFile(const std::string& path, size_t expect, int dt) {
-  if (const int fake = xft::Env::get().fakeModel) return fakeTensor(path, expect, dt, fake);
+  if (const int fake = xft::Env::get().fakeModel) {
+    // XFT_FAKE_LOAD_INFO: say which tensor a real load would have read here
+    if (xft::Env::get().fakeLoadInfo) {
+      const size_t cut = path.find_last_of('/');
+      std::printf("[fake load] %s %zu bytes\n", path.substr(cut == std::string::npos ? 0 : cut + 1).c_str(), expect);
+    }
+    return fakeTensor(path, expect, dt, fake);
+  }
   std::ifstream f(path, std::ios::binary | std::ios::ate);
   if (!f) throw std::runtime_error("cannot open " + path);
   size_t sz = (size_t)f.tellg();

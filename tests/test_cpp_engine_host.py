@@ -601,3 +601,14 @@ def test_engine_debug_dumps_match_python_layer_by_layer(hostcheck, fam, tmp_path
         assert diff.max().item() < (0.06 if fam == "mixtral" else 0.03) * scale and diff.mean().item() < 0.005 * scale, \
             (fam, name, diff.max().item(), diff.mean().item(), scale)
         assert ("step 1 %s: shape (40, 256) dtype bf16" % name) in log
+
+
+def test_engine_fake_load_info(hostcheck, tmp_path):
+    """XFT_FAKE_LOAD_INFO with XFT_FAKE_MODEL: the engine names every tensor a real load would have read."""
+    d = _config_dir(tmp_path, "llama")
+    env = dict(os.environ, XFT_FAKE_MODEL="2", XFT_FAKE_LOAD_INFO="1", XFT_ARENA_EXACT="1")
+    r = subprocess.run([hostcheck, d, "bf16", "fp16", "1"], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "hostcheck ok" in r.stdout, r.stderr[-2000:]
+    for name in ("model.wte.bin", "model.lm_head.weight.bin", "model.layers.1.attention.query_key_value.weight.0.bin",
+                 "model.layers.0.mlp.down_proj.weight.0.bin", "model.final_layernorm.weight.bin"):
+        assert "[fake load] " + name in r.stdout, name
