@@ -112,6 +112,26 @@ std::vector<char> readFile(const std::string& path, size_t expect, int dt) {
 
 }  // namespace
 
+// XFT_VERBOSE >= 1: one line per GEMM-shaped call in the reference's format (src/utils/verbose.h:24-83),
+// `xft_verbose,exec,gpu,api,<kernel>,m<M>n<N>k<K>,<ms>`; the stream is synchronised on both sides of the call.
+struct VerboseCall {
+  cudaStream_t st;
+  const char* kernel;
+  int m, n, k;
+  bool on;
+  std::chrono::steady_clock::time_point t0;
+  VerboseCall(cudaStream_t s, const char* name, int m_, int n_, int k_)
+      : st(s), kernel(name), m(m_), n(n_), k(k_), on(xft::Env::get().verbose >= 1) {
+    if (on) { cudaStreamSynchronize(st); t0 = std::chrono::steady_clock::now(); }
+  }
+  ~VerboseCall() {
+    if (!on) return;
+    cudaStreamSynchronize(st);
+    const double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    std::printf("xft_verbose,exec,gpu,api,%s,m%dn%dk%d,%.6f\n", kernel, m, n, k, ms);
+  }
+};
+
 struct LayerWeights {
   DevBuf qkv, o, gateUp, down, n1, n2, qkvBias, qNorm, kNorm;
   DevBuf n1b, n2b, oBias, fc1Bias, fc2Bias;      // LayerNorm biases, output-projection bias, biases of the two-matrix MLP
@@ -1204,6 +1224,7 @@ int Engine::forwardPart(const std::vector<int>& seqIds, bool logitsAll, bool sha
   int* stp = status.as<int>();
   auto gemm = [&](const void* X, int K, const void* Wt, int wRows, void* Y, int N, int fp32, int gated, int dualOff,
                   const float* bias, const void* res, int actc, int rowsT) {
+    VerboseCall v(st, "gemm_bf16", rowsT, gated ? 2 * N : N, K);
     XFT_K(xft_gemm_bf16(X, K, Wt, wRows, K, Y, N, fp32, rowsT, N, K, gated, dualOff, bias, res, N, 1.0f, actc, nullptr,
                         ws.as<float>(), kWsBytes, counters.as<int>(), 8192, stp, 0, st));
   };
@@ -1233,6 +1254,8 @@ int Engine::forwardPart(const std::vector<int>& seqIds, bool logitsAll, bool sha
   auto lin = [&](const Lin& Wt, const void* X, void* Y, int N, int gated, const float* bias, const void* res, float rscale,
                  int actc) {
     const int K = Wt.K;
+    VerboseCall v(st, Wt.kind == 0 ? "gemm_bf16" : Wt.kind == 2 ? "gemm_w8a8" : Wt.kind == 3 ? "gemm_nf4" : Wt.kind == 4 ? "gemm_int4" : "gemm_int8",
+                  T, gated ? 2 * N : N, K);
     if (Wt.kind == 0) {
       XFT_K(xft_gemm_bf16(X, K, Wt.w, Wt.rows, K, Y, N, 0, T, N, K, gated, gated ? N : 0, bias, res, N, rscale, actc, nullptr,
                           ws.as<float>(), kWsBytes, counters.as<int>(), 8192, stp, 0, st));

@@ -612,3 +612,20 @@ def test_engine_fake_load_info(hostcheck, tmp_path):
     for name in ("model.wte.bin", "model.lm_head.weight.bin", "model.layers.1.attention.query_key_value.weight.0.bin",
                  "model.layers.0.mlp.down_proj.weight.0.bin", "model.final_layernorm.weight.bin"):
         assert "[fake load] " + name in r.stdout, name
+
+
+def test_engine_verbose_lines(hostcheck, tmp_path):
+    """XFT_VERBOSE=1: one line per GEMM-shaped call in the reference's format, with the shapes of the call."""
+    d = _config_dir(tmp_path, "llama")
+    with open(os.path.join(d, "ids.txt"), "w") as f:
+        f.write("1 4 0\n5 6 7 8\n")
+    env = dict(os.environ, XFT_FAKE_MODEL="2", XFT_VERBOSE="1")
+    r = subprocess.run([hostcheck, "logits", d, "int8", "fp16", "1", os.path.join(d, "ids.txt"), os.path.join(d, "o.bin")], env=env,
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [l for l in r.stdout.splitlines() if l.startswith("xft_verbose,exec,gpu,api,")]
+    # per layer: qkv, o, gate‖up, down (int8 weights), and the bf16 lm_head on the last row
+    assert "xft_verbose,exec,gpu,api,gemm_int8,m4n512k256," in r.stdout                 # QKV: (4 + 2 * 2) heads of 64
+    assert "xft_verbose,exec,gpu,api,gemm_int8,m4n1024k256," in r.stdout                # gate and up: 2 x 512
+    assert "xft_verbose,exec,gpu,api,gemm_bf16,m1n300k256," in r.stdout                 # lm_head
+    assert len(lines) == 2 * 4 + 1 and all(float(l.rsplit(",", 1)[1]) >= 0 for l in lines), lines
