@@ -62,6 +62,10 @@ void wrRows(void* p, long long rows, long long cols, long long ld, size_t esz, i
   need(ld >= cols || rows <= 1, "row stride smaller than the row");
   for (long long r = 0; r < rows; ++r) wr(static_cast<char*>(p) + (size_t)r * ld * esz, (size_t)cols * esz, value);
 }
+// what the tensor maps of the real GEMMs need: a 16-byte aligned base and a row pitch that is a multiple of 16 bytes
+void needTma(const void* p, long long ld, size_t esz, const char* what) {
+  need((reinterpret_cast<uintptr_t>(p) & 15) == 0 && (ld * (long long)esz) % 16 == 0, what);
+}
 const uint16_t kBf16Small = 0x3c00;      // bf16 of 0.0078125: keeps activations finite and tiny
 
 const bool g_math = [] { const char* v = std::getenv("XFT_MOCK_MATH"); return v && *v && *v != '0'; }();
@@ -219,6 +223,8 @@ int xft_gemm_bf16(const void* X, int ldx, const void* W, int w_rows, int ldw, vo
                   const float* row_scale, float* ws, size_t ws_bytes, int* counters, int n_counters, int* status, int, cudaStream_t) {
   const int rows = gated ? dual_off + N : N;
   need(w_rows >= rows, "gemm: weight has fewer rows than outputs");
+  needTma(X, ldx, 2, "gemm: activations are not aligned for a tensor map");
+  needTma(W, ldw, 2, "gemm: weights are not aligned for a tensor map");
   rdRows(X, T, K, ldx, 2);
   rdRows(W, rows, K, ldw, 2);
   if (bias) rd(bias, (size_t)rows * 4);
@@ -552,6 +558,8 @@ int xft_qgemm(const void* X, int ldx, const void* Wq, int w_rows, int ldw_bytes,
   need(w_rows >= rows, "qgemm: weight has fewer rows than outputs");
   need(qtype == 0 || qtype == 1 || qtype == 2, "qgemm: weight type not used by the engine");
   need(ldw_bytes % 16 == 0, "qgemm: code rows must start on 16-byte boundaries");
+  needTma(X, ldx, 2, "qgemm: activations are not aligned for a tensor map");
+  needTma(Wq, ldw_bytes, 1, "qgemm: codes are not aligned for a tensor map");
   rdRows(X, T, K, ldx, 2);
   rdRows(Wq, rows, qtype == 0 ? K : K / 2, ldw_bytes, 1);
   rd(scale, (size_t)rows * 4);
@@ -594,6 +602,8 @@ int xft_w8a8_gemm(const void* qx, int ldqx, const void* Wq, int ldw, void* Y, in
                   const float* w_sum, const float* bias, const void* residual, int ldr, float res_scale, int act, float* ws,
                   size_t ws_bytes, int* counters, int n_counters, int* status, cudaStream_t) {
   need(K % 16 == 0, "w8a8: K must be a multiple of 16");
+  needTma(qx, ldqx, 1, "w8a8: activations are not aligned for a tensor map");
+  needTma(Wq, ldw, 1, "w8a8: weights are not aligned for a tensor map");
   rdRows(qx, T, K, ldqx, 1);
   rdRows(Wq, N, K, ldw, 1);
   rd(a_scale, (size_t)T * 4); rd(a_zero, (size_t)T * 4); rd(a_qsum, (size_t)T * 4);
@@ -740,6 +750,8 @@ int xft_gemm_bf16_grouped(const void* X, int ldx, int x_rows, const void* W, int
   const int* tl = static_cast<const int*>(group_tiles);
   const int nt = num_group_tiles[0];
   need(nt <= max_tiles, "grouped gemm: tile count beyond the table");
+  needTma(X, ldx, 2, "grouped gemm: activations are not aligned for a tensor map");
+  needTma(W, ldw, 2, "grouped gemm: weights are not aligned for a tensor map");
   const int rows_w = gated ? dual_off + N : N;
   for (int i = 0; i < nt; ++i) {
     const int g = tl[4 * i], r0 = tl[4 * i + 1], nr = tl[4 * i + 2];
@@ -780,6 +792,8 @@ int xft_qgemm_grouped(const void* X, int ldx, int x_rows, const void* Wq, int w_
   (void)report;
   need(group_w_rows % 128 == 0 && (!gated || dual_off % 128 == 0) && K % 16 == 0, "grouped e4m3 gemm: sizes are not whole blocks");
   need(scale_ld >= (K + 127) / 128, "grouped e4m3 gemm: scale rows shorter than the blocks along K");
+  needTma(X, ldx, 2, "grouped e4m3 gemm: activations are not aligned for a tensor map");
+  needTma(Wq, ldw_bytes, 1, "grouped e4m3 gemm: weights are not aligned for a tensor map");
   const int* tl = static_cast<const int*>(group_tiles);
   const int nt = num_group_tiles[0];
   need(nt <= max_tiles, "grouped e4m3 gemm: tile count beyond the table");
