@@ -149,6 +149,7 @@ extern "C" {
 
 int xft_embedding(const int* ids, const void* table, void* out, int T, int H, int vocab, float scale, const void* pos_table,
                   const int* positions, int pos_offset, int npos, int*, cudaStream_t) {
+  need(H % 8 == 0, "embedding: hidden size must be a multiple of 8");
   rd(ids, (size_t)T * 4);
   for (int t = 0; t < T; ++t) {
     need(ids[t] >= 0 && ids[t] < vocab, "embedding: token id outside the vocabulary");
@@ -176,6 +177,7 @@ int xft_embedding(const int* ids, const void* table, void* out, int T, int H, in
 
 int xft_rmsnorm(const void* x, int ldx, const void* res, int ldr, const float* w, void* y, int ldy, void* h_out, int T, int H,
                 float eps, cudaStream_t) {
+  need(H % 8 == 0 && ldx % 8 == 0 && ldy % 8 == 0 && (!res || ldr % 8 == 0), "rmsnorm: sizes and strides must be multiples of 8");
   rdRows(x, T, H, ldx, 2);
   if (res) rdRows(res, T, H, ldr, 2);
   rd(w, (size_t)H * 4);
@@ -339,6 +341,7 @@ int xft_qkv_rope_cache(const void* qkv, int ldq, int T, int hq, int hkv, int D, 
                        int style, int rot_off, int max_pos, const float* q_scale, const float* q_norm_w, const float* k_norm_w,
                        float eps, void* q_out, void* kc, void* vc, float* ks, float* vs, int int8_cache, int bs, long long nslots,
                        const int* slots, int*, cudaStream_t) {
+  need(D <= 256 && D % 2 == 0, "rope + cache: head size must be even and at most 256");
   rdRows(qkv, T, (long long)(hq + 2 * hkv) * D, ldq, 2);
   if (table && rot > 0) {
     need(rot_off + rot <= D, "rotary range outside the head");
@@ -361,7 +364,7 @@ int xft_qkv_rope_cache(const void* qkv, int ldq, int T, int hq, int hkv, int D, 
 int xft_qkv_rope2d_cache(const void* qkv, int ldq, int T, int hq, int hkv, int D, const int* positions, const int* positions2,
                          const float* table, int rot, int max_pos, void* q_out, void* kc, void* vc, float* ks, float* vs,
                          int int8_cache, int bs, long long nslots, const int* slots, int*, cudaStream_t) {
-  need(2 * rot <= D, "two-stream rotary wider than the head");
+  need(2 * rot <= D && D <= 256 && D % 2 == 0 && rot > 0 && rot % 2 == 0, "two-stream rotary: bad head or rotary size");
   rdRows(qkv, T, (long long)(hq + 2 * hkv) * D, ldq, 2);
   for (int t = 0; t < T; ++t) {
     need(positions[t] >= 0 && positions[t] < max_pos && positions2[t] >= 0 && positions2[t] < max_pos, "rotary position outside the table");
@@ -381,6 +384,7 @@ int xft_paged_attention(const void* q, void* out, const void* kc, const void* vc
                         int hkv, int group, int q_off, int HD, int bs, int num_blocks, float scale, const float* slopes,
                         const int* prefix_lens, int decode, int nsplit, float* part_o, float* part_ml, int* split_counters,
                         int* status, cudaStream_t) {
+  need(bs % 64 == 0 && (HD == 64 || HD == 128 || HD == 256), "attention: block size must be a multiple of 64, head size 64 / 128 / 256");
   rd(cu_q, (size_t)(B + 1) * 4);
   rd(kv_lens, (size_t)B * 4);
   const int T = cu_q[B];
@@ -648,6 +652,7 @@ int xft_gated_act(const void* gu, void* out, int T, int I, int act, cudaStream_t
 int xft_moe_route(const float* logits, int ld, int T, int E, int k, int kind, const float* bias, int n_group, int topk_group,
                   float scaling, int norm_topk, int sigmoid, int* idx, float* w, cudaStream_t) {
   need(k >= 1 && k <= E && n_group >= 1 && topk_group >= 1 && topk_group <= n_group && E % n_group == 0, "route: bad configuration");
+  need(E <= 4096 && k <= 32 && n_group <= 31, "route: more experts, choices or groups than the kernel takes");
   rdRows(logits, T, E, ld, 4);
   if (bias) rd(bias, (size_t)E * 4);
   std::vector<float> score(E), sel(E);
@@ -712,6 +717,7 @@ int xft_moe_route(const float* logits, int ld, int T, int E, int k, int kind, co
 
 int xft_moe_plan(const int* idx, const float* w, int T, int k, int e0, int e1, int bn, int* pos, int* src_tok, float* row_w,
                  void* tiles, int* meta, int max_tiles, int max_rows, cudaStream_t) {
+  need(e1 > e0 && e1 - e0 <= 256, "plan: between 1 and 256 experts per rank");
   int* tl = static_cast<int*>(tiles);
   int rows = 0, nt = 0;
   for (int i = 0; i < T * k; ++i) pos[i] = -1;
@@ -735,7 +741,7 @@ int xft_moe_plan(const int* idx, const float* w, int T, int k, int e0, int e1, i
 }
 
 int xft_moe_gather(const void* x, int ldx, const int* src_tok, const int* meta, void* xs, int max_rows, int H, cudaStream_t) {
-  need(meta[1] <= max_rows, "gather: more rows than the buffer holds");
+  need(meta[1] <= max_rows && H % 8 == 0, "gather: more rows than the buffer holds, or a hidden size that is not a multiple of 8");
   for (int r = 0; r < meta[1]; ++r) {
     rd(static_cast<const char*>(x) + (size_t)src_tok[r] * ldx * 2, (size_t)H * 2);
     wr(static_cast<char*>(xs) + (size_t)r * H * 2, (size_t)H * 2);
@@ -850,6 +856,9 @@ int xft_moe_combine(const float* ys, const int* pos, int k, const float* add1, c
 int xft_mla_prep(const void* q, int ldq, const void* kv, int ldkv, int T, int Hl, int nope, int rope, int kvl, const int* positions,
                  const float* table, int max_pos, const float* kv_norm_w, float eps, void* q_nope, void* q_rope, void* cache,
                  long long nslots, const int* slots, int*, int nope_head_major, cudaStream_t) {
+  need(Hl > 0 && rope > 0 && kvl > 0 && ((nope | rope | kvl | ldq | ldkv) & 1) == 0, "mla_prep: sizes and strides must be even");
+  need(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(kv) | reinterpret_cast<uintptr_t>(q_nope) |
+         reinterpret_cast<uintptr_t>(q_rope) | reinterpret_cast<uintptr_t>(cache)) & 3) == 0, "mla_prep: pointers must be 4-byte aligned");
   rdRows(q, T, (long long)Hl * (nope + rope), ldq, 2);
   rdRows(kv, T, kvl + rope, ldkv, 2);
   rd(kv_norm_w, (size_t)kvl * 4);
@@ -896,7 +905,7 @@ int xft_mla_attention(const void* q_abs, long long qa_sh, long long qa_st, const
                       const int* cu_q, const int* kv_lens, int B, int T, int hl, int bs, int num_blocks, float scale, int nsplit,
                       float* part_o, float* part_ml, int* counters, int*, cudaStream_t) {
   const int L = 512, R = 64;
-  need(cu_q[B] == T, "mla: token count mismatch");
+  need(cu_q[B] == T && bs % 32 == 0, "mla: token count mismatch, or a block size that is not a multiple of 32");
   for (int h = 0; h < hl; ++h)
     for (int t = 0; t < T; ++t) {
       rd(static_cast<const char*>(q_abs) + ((size_t)h * qa_sh + (size_t)t * qa_st) * 2, (size_t)L * 2);
