@@ -6,7 +6,8 @@
 // XFT_ARENA_EXACT=1 (buffers get exactly the size asked for), a run of the engine over this library checks the host
 // side of every family x weight type x rank count: buffer sizes, strides, block and slot arithmetic, the tensor-
 // parallel ranges, the order of collectives.  Indices that the real kernels would refuse through their status word
-// (a slot or block outside the pool) abort here.
+// (a slot or block outside the pool) abort here, and so do arguments the real entry points reject: operands that are not
+// aligned for a tensor map (16-byte base and row pitch), sizes and strides the kernels' vector accesses cannot take.
 //
 // The few results the host logic depends on are produced for real: the routing (valid expert ids), the expert plan
 // (rows grouped by expert, tile table, counts) and logits that differ per row and step so that searchers move.

@@ -1,9 +1,12 @@
 """The C++ engine's host side on a CPU box: csrc/tests/engine_hostcheck.cc drives xft::AutoModel through every request
 shape over a host stand-in of the device library (csrc/tests/mock_device.cc) whose kernels touch exactly the memory the
-real ones read and write; AddressSanitizer + UndefinedBehaviorSanitizer + exact-size buffers (XFT_ARENA_EXACT) then check
-buffer sizes, strides, slot / block arithmetic and tensor-parallel ranges for every family, weight type and rank count,
-and that thread ranks produce the same tokens.  With the stand-in's arithmetic switched on (XFT_MOCK_MATH) the engine's
-logits are compared with the fp32 PyTorch path of the package, on one rank and on tensor-parallel thread ranks."""
+real ones read and write and refuse what the real entry points refuse; AddressSanitizer + UndefinedBehaviorSanitizer +
+exact-size buffers (XFT_ARENA_EXACT) then check buffer sizes, strides, slot / block arithmetic and the ranges of every
+rank for every family, weight type and rank layout, and that ranks produce the same tokens.  With the stand-in's arithmetic
+switched on (XFT_MOCK_MATH) the engine's logits are compared with the PyTorch path of the package: every family,
+quantised and GPTQ checkpoints, tensor- and expert-parallel thread ranks, pipeline stages with micro-batches, real
+process ranks over a stand-in NCCL, greedy and beam generation, the per-layer debug dumps; the example programs and the
+cases of the GPU thread-rank tests run over it too."""
 import os
 import shutil
 import subprocess
