@@ -1122,23 +1122,46 @@ void Engine::attachPrefix(SequenceMeta& s) {
   }
 }
 
-// One forward pass.  Over pipeline stages the sequences may be cut into XFT_MAX_REQUEST_NUM micro-batches: a stage hands
-// micro-batch m on and starts on m + 1 while the next stage works on m (the sends are asynchronous on the stream); the
-// last stage collects the logits of all of them and every rank receives them once, at the end.
+// One forward pass, cut into groups of whole sequences where that is asked for (as the Python engine cuts it):
+//  * XFT_MAX_BATCH_TOKENS: when the pending tokens of several sequences exceed the budget, the sequences run in groups of
+//    at most that many tokens, each a ragged batch of its own, so the activation buffers stay bounded;
+//  * over pipeline stages, XFT_MAX_REQUEST_NUM micro-batches: a stage hands micro-batch m on and starts on m + 1 while
+//    the next stage works on m (the sends are asynchronous on the stream).
+// The logits of the groups are put together in the order of the sequences; over pipeline stages the last stage collects
+// them and every rank receives them once, at the end.
 int Engine::forward(const std::vector<int>& seqIds, bool logitsAll) {
-  const int parts = pp > 1 ? std::min<int>(Env::get().maxRequestNum, (int)seqIds.size()) : 1;
-  if (parts <= 1) return forwardPart(seqIds, logitsAll, true);
+  std::vector<std::vector<int>> groups(1, seqIds);
+  const long long cap = Env::get().maxBatchTokens;
+  long long pendingTokens = 0;
+  bool prompt = false;
+  for (int sid : seqIds) { const size_t n = pool.get(sid).pending.size(); pendingTokens += (long long)n; prompt = prompt || n > 1; }
+  if (seqIds.size() > 1 && cap > 0 && pendingTokens > cap && prompt) {
+    groups.assign(1, {});
+    long long n = 0;
+    for (int sid : seqIds) {
+      const long long mine = (long long)pool.get(sid).pending.size();
+      if (!groups.back().empty() && n + mine > cap) { groups.emplace_back(); n = 0; }
+      groups.back().push_back(sid);
+      n += mine;
+    }
+  }
+  const int micro = pp > 1 ? std::min<int>(Env::get().maxRequestNum, (int)seqIds.size()) : 1;
+  if (groups.size() == 1 && micro > 1) {
+    groups.clear();
+    for (int m = 0; m < micro; ++m)
+      groups.emplace_back(seqIds.begin() + seqIds.size() * m / micro, seqIds.begin() + seqIds.size() * (m + 1) / micro);
+  }
+  if (groups.size() == 1) return forwardPart(seqIds, logitsAll, true);
   std::vector<float> all;
   int rows = 0;
-  for (int m = 0; m < parts; ++m) {
-    const size_t b = seqIds.size() * m / parts, e = seqIds.size() * (m + 1) / parts;
-    const int r = forwardPart(std::vector<int>(seqIds.begin() + b, seqIds.begin() + e), logitsAll, false);
+  for (const auto& g : groups) {
+    const int r = forwardPart(g, logitsAll, false);
     if (ppRank == pp - 1) all.insert(all.end(), hostLogits.begin(), hostLogits.begin() + (size_t)r * vocabG);
     rows += r;
   }
   hostLogits.swap(all);
   hostLogits.resize((size_t)rows * vocabG);
-  worldComm->broadcastHost(hostLogits.data(), hostLogits.size() * 4, (pp - 1) * world);
+  if (pp > 1) worldComm->broadcastHost(hostLogits.data(), hostLogits.size() * 4, (pp - 1) * world);
   return rows;
 }
 

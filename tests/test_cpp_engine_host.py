@@ -632,3 +632,22 @@ def test_engine_verbose_lines(hostcheck, tmp_path):
     assert "xft_verbose,exec,gpu,api,gemm_int8,m4n1024k256," in r.stdout                # gate and up: 2 x 512
     assert "xft_verbose,exec,gpu,api,gemm_bf16,m1n300k256," in r.stdout                 # lm_head
     assert len(lines) == 2 * 4 + 1 and all(float(l.rsplit(",", 1)[1]) >= 0 for l in lines), lines
+
+
+@pytest.mark.parametrize("fam,ranks,stages", [("llama", 1, 1), ("chatglm", 2, 1), ("llama", 2, 2)])
+def test_engine_token_budget_groups(hostcheck, fam, ranks, stages, tmp_path):
+    """XFT_MAX_BATCH_TOKENS: three prompts of 20 tokens under a budget of 25 run as three groups (45 under a budget of 45:
+    two groups), the logits are put together in the order of the sequences — the same numbers as in one pass, since a
+    sequence never shares arithmetic with its neighbours; every request shape also runs under a small budget."""
+    d = _synthetic_dir(tmp_path, fam, dict(_NUMERIC[fam], num_layer=2))
+    prompt = torch.randint(5, 290, (3, 20), generator=torch.Generator().manual_seed(4))
+    whole, tok0 = _engine_logits(hostcheck, d, ranks, prompt, 2, stages=stages)
+    for budget in ("25", "45"):
+        got, tok = _engine_logits(hostcheck, d, ranks, prompt, 2, stages=stages, extra_env={"XFT_MAX_BATCH_TOKENS": budget})
+        assert torch.equal(tok, tok0) and torch.equal(got, whole), (budget, (got - whole).abs().max().item())
+    cfg = str(tmp_path / "cfg")
+    ModelConfig(**dict(_BASE, model_type=fam.split("-")[0], **_FAMILIES[fam])).to_ini(cfg)
+    env = dict(os.environ, XFT_FAKE_MODEL="2", XFT_ARENA_EXACT="1", ASAN_OPTIONS="detect_leaks=1", XFT_MAX_BATCH_TOKENS="70",
+               XFT_PIPELINE_STAGE=str(stages))
+    r = subprocess.run([hostcheck, cfg, "bf16", "fp16", str(ranks)], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "hostcheck ok" in r.stdout, (r.stdout[-500:], r.stderr[-3000:])
