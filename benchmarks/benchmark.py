@@ -19,6 +19,44 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
 
+def build_prompt_ids(tok, a, path, json):
+    """[batch, input_tokens] token ids from the reference's prompt sources (benchmark/benchmark.py:204-270)."""
+    import torch
+
+    def fit(t):
+        while len(t) < a.input_tokens:
+            t = t + t
+        return t[:a.input_tokens]
+
+    if a.input_prompt:
+        return torch.tensor([fit(tok(a.input_prompt, add_special_tokens=True)["input_ids"])] * a.batch_size)
+    if path.endswith(".sonnet"):
+        # prompts that share their first --sonnet_prefix_len tokens (prefix sharing / prefix cache runs): the prefix is
+        # the head of the poem, the rest of each prompt is a different run of lines
+        lines = [l for l in open(path, encoding="utf-8").read().splitlines() if l.strip()]
+        prefix, k = [], 0
+        while len(prefix) < a.sonnet_prefix_len and k < len(lines):
+            prefix += tok(lines[k] + "\n", add_special_tokens=(k == 0))["input_ids"]
+            k += 1
+        prefix = prefix[:min(a.sonnet_prefix_len, a.input_tokens)]
+        rows = []
+        for r in range(max(1, a.sonnet_count)):
+            tail, j = [], (k + 7 * r) % max(len(lines), 1)
+            while len(prefix) + len(tail) < a.input_tokens:
+                tail += tok(lines[j % len(lines)] + "\n", add_special_tokens=False)["input_ids"]
+                j += 1
+            rows.append((prefix + tail)[:a.input_tokens])
+        return torch.tensor(rows)
+    if path.endswith(".txt"):
+        pool = [l for l in open(path, encoding="utf-8").read().splitlines() if l.strip()]
+        return torch.tensor([fit(tok(pool[i % len(pool)], add_special_tokens=True)["input_ids"]) for i in range(a.batch_size)])
+    if not path.endswith(".json"):
+        raise ValueError("prompt files are .json, .txt or .sonnet")
+    prompts = json.load(open(path))
+    text = prompts.get(str(a.input_tokens)) or prompts.get("long_unit", "It is a truth universally acknowledged. ") * (a.input_tokens // 8 + 1)
+    return torch.tensor([fit(tok(text, add_special_tokens=True)["input_ids"])] * a.batch_size)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model_path", "-m", default="")
@@ -27,8 +65,15 @@ def main():
     ap.add_argument("--dtype", "-d", default="bf16")
     ap.add_argument("--kv_cache_dtype", "-kvd", default="fp16")
     ap.add_argument("--batch_size", "-bs", type=int, default=1)
-    ap.add_argument("--input_tokens", "-in", type=int, default=32)
-    ap.add_argument("--output_tokens", "-out", type=int, default=32)
+    ap.add_argument("--input_tokens", "--token_in", "-in", dest="input_tokens", type=int, default=32)
+    ap.add_argument("--output_tokens", "--token_out", "-out", dest="output_tokens", type=int, default=32)
+    # the reference's prompt options (benchmark/benchmark.py:76-91); they need --token_path
+    ap.add_argument("--input_prompt", default=None, help="prompt text instead of an entry of the prompt file")
+    ap.add_argument("--prompt_path", default="", help=".json (token count -> text; default: the bundled prompt.json), .txt (one prompt "
+                    "per line), or .sonnet (poem lines: --sonnet_count prompts that share a prefix of --sonnet_prefix_len tokens)")
+    ap.add_argument("--padding", default="True", help="accepted for the reference's command lines; prompts of one batch have one length here")
+    ap.add_argument("--sonnet_prefix_len", type=int, default=200)
+    ap.add_argument("--sonnet_count", type=int, default=20)
     ap.add_argument("--iteration", "-i", type=int, default=3)
     ap.add_argument("--warmup", "-w", type=int, default=1)
     ap.add_argument("--beam_width", type=int, default=1)
@@ -53,16 +98,14 @@ def main():
     vocab = model.model.cfg.vocab_size
     ids = torch.randint(5, max(vocab - 1, 6), (a.batch_size, a.input_tokens), generator=torch.Generator().manual_seed(1))
     if a.token_path:
-        # real text: the prompt.json entry of that length, or the filler sentence repeated, cut to the token count
+        # real text: the prompt given, an entry of the prompt file of that length, or the filler sentence repeated — cut to
+        # the token count
         import json
         from transformers import AutoTokenizer
         tok = AutoTokenizer.from_pretrained(a.token_path)
-        prompts = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "prompt.json")))
-        text = prompts.get(str(a.input_tokens)) or prompts["long_unit"] * (a.input_tokens // 8 + 1)
-        t = tok(text, add_special_tokens=True)["input_ids"]
-        while len(t) < a.input_tokens:
-            t = t + t
-        ids = torch.tensor([t[:a.input_tokens]] * a.batch_size)
+        path = a.prompt_path or os.path.join(os.path.dirname(os.path.abspath(__file__)), "prompt.json")
+        ids = build_prompt_ids(tok, a, path, json)
+        a.batch_size, a.input_tokens = ids.shape
     max_len = a.input_tokens + a.output_tokens
 
     def sync():

@@ -31,6 +31,15 @@ class IdStreamer:
         print()
 
 
+def boolean_string(v):
+    """The reference's demos take `--flag True` / `--flag False` (examples/pytorch/demo.py:52-58); a bare `--flag` means True."""
+    if isinstance(v, bool):
+        return v
+    if v.lower() not in ("true", "false"):
+        raise argparse.ArgumentTypeError("expected True or False")
+    return v.lower() == "true"
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("-m", "--model_path", required=True)
@@ -39,15 +48,17 @@ def main():
     ap.add_argument("--kv_cache_dtype", default="fp16")
     ap.add_argument("--input", default="Once upon a time, there existed a little girl who liked to have adventures.")
     ap.add_argument("--ids", default="")
-    ap.add_argument("--output_len", type=int, default=64)
+    ap.add_argument("-o", "--output_len", type=int, default=64)
     ap.add_argument("--num_beams", type=int, default=1)
-    ap.add_argument("--do_sample", action="store_true")
+    ap.add_argument("--do_sample", nargs="?", const=True, default=False, type=boolean_string)
+    ap.add_argument("--padding", nargs="?", const=True, default=False, type=boolean_string,
+                    help="accepted for the reference's command lines: one prompt needs no padding")
     ap.add_argument("--temperature", type=float, default=1.0)
     ap.add_argument("--top_k", type=int, default=50)
     ap.add_argument("--top_p", type=float, default=1.0)
     ap.add_argument("--rep_penalty", type=float, default=1.0)
-    ap.add_argument("--streaming", action="store_true")
-    ap.add_argument("--chat", action="store_true", help="read prompts from stdin in a loop")
+    ap.add_argument("--streaming", nargs="?", const=True, default=False, type=boolean_string)
+    ap.add_argument("--chat", nargs="?", const=True, default=False, type=boolean_string, help="read prompts from stdin in a loop")
     a = ap.parse_args()
     import torch
 

@@ -665,3 +665,92 @@ def test_openai_server_emits_every_token_of_a_speculative_step(tmp_path, monkeyp
         httpd.shutdown()
         monkeypatch.delenv("XFT_SPEC_NGRAM")
         Env.get().reload()
+
+
+def test_benchmark_prompt_sources_of_the_reference(tiny, tmp_path):
+    """benchmarks/benchmark.py takes the reference's flag names (--token_in / --token_out, --input_prompt, --prompt_path
+    with .json / .txt / .sonnet files, --sonnet_prefix_len / --sonnet_count, --padding): prompts are cut or repeated to
+    the token count; the sonnet prompts share their first --sonnet_prefix_len tokens and differ after them."""
+    import argparse
+    import importlib.util
+    import json as json_mod
+    spec = importlib.util.spec_from_file_location("bench_cli", os.path.join(ROOT, "benchmarks", "benchmark.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+
+    class Tok:                                   # a word-level stand-in for a Hugging Face tokenizer
+        def __call__(self, text, add_special_tokens=True):
+            return {"input_ids": ([1] if add_special_tokens else []) + [3 + (hash(w) % 200) for w in text.split()]}
+
+    a = argparse.Namespace(input_tokens=24, batch_size=3, input_prompt=None, sonnet_prefix_len=10, sonnet_count=4)
+    poem = tmp_path / "poem.sonnet"
+    poem.write_text("\n".join("line %d of the poem has a few words in it" % i for i in range(40)) + "\n")
+    ids = mod.build_prompt_ids(Tok(), a, str(poem), json_mod)
+    assert ids.shape == (4, 24)
+    assert all(torch.equal(ids[r, :10], ids[0, :10]) for r in range(4)) and len({tuple(r.tolist()) for r in ids}) == 4
+    txt = tmp_path / "p.txt"
+    txt.write_text("first prompt here\nsecond one is a little longer than that\n")
+    ids = mod.build_prompt_ids(Tok(), a, str(txt), json_mod)
+    assert ids.shape == (3, 24) and not torch.equal(ids[0], ids[1]) and torch.equal(ids[0], ids[2])
+    js = tmp_path / "p.json"
+    js.write_text(json_mod.dumps({"24": "exact entry for twenty four tokens", "long_unit": "filler words "}))
+    ids = mod.build_prompt_ids(Tok(), a, str(js), json_mod)
+    assert ids.shape == (3, 24) and torch.equal(ids[0], ids[1])
+    a.input_prompt = "an explicit prompt"
+    assert mod.build_prompt_ids(Tok(), a, str(js), json_mod).shape == (3, 24)
+    with pytest.raises(ValueError):
+        a.input_prompt = None
+        mod.build_prompt_ids(Tok(), a, str(tmp_path / "p.csv"), json_mod)
+    # the reference's spelling of the length flags on the command line
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "benchmarks", "benchmark.py"), "--model_path", tiny, "--dtype", "bf16",
+                        "--batch_size", "1", "--token_in", "8", "--token_out", "3", "--iteration", "1", "--warmup", "0", "--padding", "False"],
+                       env=dict(os.environ, XFT_ENGINE="CPU"), capture_output=True, text=True, timeout=600, cwd=str(tmp_path))
+    assert r.returncode == 0 and "input_tokens: 8" in r.stdout.replace("  ", " ").replace("  ", " "), r.stdout[-800:] + r.stderr[-800:]
+
+
+def test_demo_takes_the_reference_command_line(tiny, tmp_path):
+    """examples/pytorch/demo.py with the reference's spelling of the boolean options (`--streaming False --chat False
+    --do_sample True --padding False`, examples/pytorch/demo.py:61-74 there) and with bare flags."""
+    demo = os.path.join(ROOT, "examples", "pytorch", "demo.py")
+    env = dict(os.environ, XFT_ENGINE="CPU", PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    for extra in (["--streaming", "False", "--chat", "False", "--do_sample", "True", "--top_k", "3", "--padding", "False", "-o", "4"],
+                  ["--streaming", "--output_len", "4"]):
+        r = subprocess.run([sys.executable, demo, "-m", tiny, "-d", "bf16", "--ids", "5 6 7 8"] + extra, env=env, capture_output=True,
+                           text=True, timeout=600, cwd=str(tmp_path))
+        assert r.returncode == 0 and "[4 tokens in" in r.stdout, r.stdout[-800:] + r.stderr[-1500:]
+    r = subprocess.run([sys.executable, demo, "-m", tiny, "--chat", "maybe"], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 2 and "expected True or False" in r.stderr
+
+
+def test_text_modes_of_the_example_scripts(tmp_path):
+    """examples/pytorch/demo_offline_cb.py and prefix_sharing.py with the reference's text options (-t tokenizer, -i prompt
+    file, -s sorted answers; --input / --prefix_len / --output_len): a small byte-level BPE tokenizer trained here stands
+    in for a model's."""
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers, trainers
+    from transformers import PreTrainedTokenizerFast
+    from xfastertransformer_b200.tools.synthetic import preset, write_synthetic_checkpoint
+    tok = Tokenizer(models.BPE())
+    tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+    tok.decoder = decoders.ByteLevel()
+    corpus = ["Once upon a time, there existed a little girl who liked to have adventures.", "The capital of France is Paris.",
+              "Explain why the sky is blue. Write a haiku about the sea. List three prime numbers."] * 4
+    tok.train_from_iterator(corpus, trainers.BpeTrainer(vocab_size=400, special_tokens=["<|endoftext|>"],
+                                                        initial_alphabet=pre_tokenizers.ByteLevel.alphabet(), show_progress=False))
+    tdir = str(tmp_path / "tok")
+    PreTrainedTokenizerFast(tokenizer_object=tok, eos_token="<|endoftext|>").save_pretrained(tdir)
+    d = str(tmp_path / "tiny")
+    write_synthetic_checkpoint(d, preset("tiny-llama", vocab_size=512), seed=0, dtype="bf16", std=0.05)
+    env = dict(os.environ, XFT_ENGINE="CPU", PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    prompts = tmp_path / "prompts.txt"
+    prompts.write_text("The capital of France is\n\nWrite a haiku about the sea.\nList three prime numbers.\n")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "examples", "pytorch", "demo_offline_cb.py"), "-m", d, "-t", tdir, "-i",
+                        str(prompts), "-s", "--output_len", "4", "--kv_cache_dtype", "fp16"], env=env, capture_output=True, text=True,
+                       timeout=600)
+    assert r.returncode == 0, r.stdout[-800:] + r.stderr[-1500:]
+    shown = [l for l in r.stdout.splitlines() if l.startswith("[")]
+    assert [l[:3] for l in shown] == ["[0]", "[1]", "[2]"] and "'The capital of France is'" in shown[0]      # -s: in prompt order
+    assert "3 requests" in r.stdout
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "examples", "pytorch", "prefix_sharing.py"), "-m", d, "-t", tdir,
+                        "--prefix_len", "70", "--output_len", "4", "--streaming", "False", "--padding", "False"], env=env,
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "identical: True" in r.stdout, r.stdout[-800:] + r.stderr[-1500:]
