@@ -24,14 +24,24 @@ _dec = lambda b: json.loads(b.decode()) if b else {}
 
 
 class Servicer:
-    def __init__(self, model):
+    def __init__(self, model, defaults=None):
         self.model = model
         self.lock = threading.Lock()      # one generation at a time: the engine state is per request
+        # generation settings of the launcher's command line (the reference fixes them there, server.py:67-73); a request
+        # that carries a field overrides it
+        self.defaults = dict(num_beams=1, do_sample=False, temperature=1.0, top_k=50, top_p=1.0, repetition_penalty=1.0,
+                             output_len=None)
+        self.defaults.update(defaults or {})
 
     def _kwargs(self, q):
-        kw = dict(max_length=q.get("max_length", 128), num_beams=q.get("num_beams", 1), do_sample=q.get("do_sample", False),
-                  temperature=q.get("temperature", 1.0), top_k=q.get("top_k", 50), top_p=q.get("top_p", 1.0),
-                  repetition_penalty=q.get("repetition_penalty", 1.0), eos_token_id=q.get("eos_token_id", -1),
+        d = self.defaults
+        max_length = q.get("max_length")
+        if max_length is None:
+            bs = int(q.get("batch_size", 1))
+            max_length = len(q["Ids"]) // max(bs, 1) + d["output_len"] if d["output_len"] else 128
+        kw = dict(max_length=max_length, num_beams=q.get("num_beams", d["num_beams"]), do_sample=q.get("do_sample", d["do_sample"]),
+                  temperature=q.get("temperature", d["temperature"]), top_k=q.get("top_k", d["top_k"]), top_p=q.get("top_p", d["top_p"]),
+                  repetition_penalty=q.get("repetition_penalty", d["repetition_penalty"]), eos_token_id=q.get("eos_token_id", -1),
                   pad_token_id=q.get("pad_token_id", -1))
         return kw
 
@@ -79,9 +89,9 @@ class Servicer:
         return {"status": "SERVING"}
 
 
-def serve_grpc(model, port: int, workers: int = 4):
+def serve_grpc(model, port: int, workers: int = 4, defaults=None):
     import grpc
-    sv = Servicer(model)
+    sv = Servicer(model, defaults)
     handlers = {
         "predict": grpc.unary_unary_rpc_method_handler(sv.predict, request_deserializer=_dec, response_serializer=_enc),
         "predict_stream": grpc.unary_stream_rpc_method_handler(sv.predict_stream, request_deserializer=_dec,
@@ -95,9 +105,9 @@ def serve_grpc(model, port: int, workers: int = 4):
     return server, bound
 
 
-def serve_http(model, port: int):
+def serve_http(model, port: int, defaults=None):
     from http.server import BaseHTTPRequestHandler, HTTPServer
-    sv = Servicer(model)
+    sv = Servicer(model, defaults)
 
     class H(BaseHTTPRequestHandler):
         def log_message(self, *a):
@@ -146,23 +156,35 @@ class Client:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--model_path", required=True)
-    ap.add_argument("--dtype", default="bf16")
+    ap.add_argument("-m", "--model_path", required=True)
+    ap.add_argument("-d", "--dtype", default="bf16")
     ap.add_argument("--kv_cache_dtype", default="fp16")
     ap.add_argument("--port", type=int, default=50051)
     ap.add_argument("--http", action="store_true")
+    # the reference's launcher fixes the generation settings on its command line (serving/grpc_launcher/server.py:67-73);
+    # here they are the defaults of requests that do not carry the field
+    boolean = lambda v: str(v).lower() == "true"
+    ap.add_argument("--num_beams", type=int, default=1)
+    ap.add_argument("--output_len", type=int, default=None, help="tokens to generate beyond the prompt when a request has no max_length")
+    ap.add_argument("--do_sample", type=boolean, default=False)
+    ap.add_argument("--temperature", type=float, default=1.0)
+    ap.add_argument("--top_p", type=float, default=1.0)
+    ap.add_argument("--top_k", type=int, default=50)
+    ap.add_argument("--rep_penalty", type=float, default=1.0)
     a = ap.parse_args()
+    defaults = dict(num_beams=a.num_beams, output_len=a.output_len, do_sample=a.do_sample, temperature=a.temperature, top_p=a.top_p,
+                    top_k=a.top_k, repetition_penalty=a.rep_penalty)
     import xfastertransformer_b200 as xft
     model = xft.AutoModel.from_pretrained(a.model_path, dtype=a.dtype, kv_cache_dtype=a.kv_cache_dtype)
     if model.rank != 0:
         model.follow()                   # follower: execute whatever rank 0 calls (exits on shutdown)
         return
     if a.http:
-        srv, port = serve_http(model, a.port)
+        srv, port = serve_http(model, a.port, defaults)
         print(f"HTTP serving on :{port}", flush=True)
         threading.Event().wait()
     else:
-        srv, port = serve_grpc(model, a.port)
+        srv, port = serve_grpc(model, a.port, defaults=defaults)
         print(f"gRPC serving on :{port}", flush=True)
         srv.wait_for_termination()
 

@@ -754,3 +754,19 @@ def test_text_modes_of_the_example_scripts(tmp_path):
                         "--prefix_len", "70", "--output_len", "4", "--streaming", "False", "--padding", "False"], env=env,
                        capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "identical: True" in r.stdout, r.stdout[-800:] + r.stderr[-1500:]
+
+
+def test_launcher_defaults_from_the_command_line(tiny):
+    """serving/server.py: the reference fixes the generation settings on the launcher's command line (--output_len,
+    --num_beams, --do_sample, ...); here they are the defaults of requests that do not carry the field."""
+    import xfastertransformer_b200 as xft
+    from serving.server import Servicer
+    model = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+    sv = Servicer(model, dict(output_len=3, num_beams=2))
+    kw = sv._kwargs({"Ids": [5, 6, 7, 8, 9, 10], "batch_size": 2})
+    assert kw["max_length"] == 3 + 3 and kw["num_beams"] == 2 and kw["top_k"] == 50
+    kw = sv._kwargs({"Ids": [5, 6, 7], "max_length": 9, "num_beams": 1})
+    assert kw["max_length"] == 9 and kw["num_beams"] == 1
+    out = sv.predict({"Ids": [5, 6, 7, 8], "batch_size": 1, "num_beams": 1})
+    assert out["seq_len"] == 4 + 3
+    assert Servicer(model)._kwargs({"Ids": [1, 2]})["max_length"] == 128
