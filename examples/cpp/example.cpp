@@ -33,12 +33,20 @@ int main(int argc, char** argv) {
   float topP = 1.0f, temp = 1.0f, rep = 1.0f;
   bool sample = false, stream = true;
   for (int i = 1; i < argc; ++i) {
-    std::string a = argv[i];
-    auto next = [&]() -> std::string { if (i + 1 >= argc) { std::fprintf(stderr, "missing value for %s\n", a.c_str()); std::exit(2); } return argv[++i]; };
+    std::string a = argv[i], inlineValue;
+    // `--name=value`, as the reference's option parser takes it besides `--name value`
+    const size_t eq = a.rfind("--", 0) == 0 ? a.find('=') : std::string::npos;
+    const bool hasInline = eq != std::string::npos;
+    if (hasInline) { inlineValue = a.substr(eq + 1); a = a.substr(0, eq); }
+    auto next = [&]() -> std::string {
+      if (hasInline) return inlineValue;
+      if (i + 1 >= argc) { std::fprintf(stderr, "missing value for %s\n", a.c_str()); std::exit(2); }
+      return argv[++i];
+    };
     if (a == "-m" || a == "--model") model = next();
     else if (a == "-d" || a == "--dtype") dtype = next();
     else if (a == "--kv_cache_dtype") kv = next();
-    else if (a == "-i" || a == "--input_ids") input = next();
+    else if (a == "-i" || a == "--input" || a == "--input_ids") input = next();
     else if (a == "-b" || a == "--batch_size") batch = std::atoi(next().c_str());
     else if (a == "-o" || a == "--output_len") outLen = std::atoi(next().c_str());
     else if (a == "--loop") loop = std::atoi(next().c_str());

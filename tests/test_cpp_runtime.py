@@ -317,6 +317,8 @@ def test_example_cli_flags_follow_the_reference(core):
     assert r.returncode == 1 and "config.ini" in r.stderr and "input_len 2 is not longer" in r.stderr
     assert run("-m", "/nonexistent", "-i", "hello").returncode == 2           # text needs -t <tokenizer.model>
     assert run("-m", "/nonexistent", "-i", "1 2 3", "--prefix_len", "3").returncode == 2
+    r = run("--model=/nonexistent", "--input=1 2 3", "--output_len=4", "--num_beams", "2")    # the reference's long forms
+    assert r.returncode == 1 and "config.ini" in r.stderr
     r = run("-m", "/nonexistent", "-i", "1 2 3", "-d", "int3")               # weight types: the package's dtype strings
     assert r.returncode == 2 and "unknown weight type int3" in r.stderr
     for dt in ("int8", "w8a8", "int4", "nf4", "bf16_int8", "w8a8_nf4"):
