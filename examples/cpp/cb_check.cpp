@@ -5,8 +5,10 @@
 // in the middle of their decode, and finished sequences are freed while others keep running.  Batch composition
 // must not change what a sequence generates, so both passes have to produce the same tokens.
 //
-//   cb_check -m <model dir> [-d bf16] [--kv_cache_dtype fp16|int8] [-n prompts] [-o out_len] [--stride k]
-//            [--min_len a] [--max_len b] [--seed s] [--tolerate t]
+//   cb_check -m <model dir> [-d bf16|int8|...] [--kv_cache_dtype fp16|int8] [-n prompts] [-o out_len] [--stride k]
+//            [--min_len a] [--max_len b] [--seed s] [--tolerate t] [-t <tokenizer.model | tokenizer.json | dir>] [-i <prompt>]
+// The prompts are random token ids; `-i` (token ids, or text with `-t`, as the reference's checker takes it) replaces the
+// first of them.
 // Exit code 0 when every sequence agrees (up to `--tolerate` late divergences caused by bf16 near-ties), 1 otherwise.
 #include <algorithm>
 #include <cstdio>
@@ -14,10 +16,13 @@
 #include <map>
 #include <memory>
 #include <random>
+#include <sstream>
 #include <stdexcept>
 #include <string>
 #include <vector>
 
+#include "bpe_tokenizer.h"
+#include "tokenizer.h"
 #include "xft/models.h"
 
 namespace {
@@ -51,7 +56,7 @@ std::vector<int> runAlone(xft::Model& m, const std::vector<int32_t>& prompt, int
 }  // namespace
 
 int main(int argc, char** argv) {
-  std::string model, dtype = "bf16", kv = "fp16";
+  std::string model, dtype = "bf16", kv = "fp16", tokenPath, input;
   int nPrompts = 6, outLen = 16, stride = 3, minLen = 4, maxLen = 40, tolerate = 0;
   unsigned seed = 1234;
   for (int i = 1; i < argc; ++i) {
@@ -70,12 +75,30 @@ int main(int argc, char** argv) {
     else if (a == "--max_len") maxLen = std::atoi(next().c_str());
     else if (a == "--seed") seed = (unsigned)std::atoi(next().c_str());
     else if (a == "--tolerate") tolerate = std::atoi(next().c_str());
+    else if (a == "-t" || a == "--token") tokenPath = next();
+    else if (a == "-i" || a == "--input") input = next();
     else { std::fprintf(stderr, "unknown flag %s\n", a.c_str()); return 2; }
   }
   if (model.empty()) { std::fprintf(stderr, "usage: cb_check -m <model dir> [options]\n"); return 2; }
+  const xft::DataType wdt = xft::dataTypeFromName(dtype.c_str());
+  if (wdt == xft::DataType::unknown) { std::fprintf(stderr, "unknown weight type %s\n", dtype.c_str()); return 2; }
   try {
-    xft::AutoModel m(model, dtype == "fp16" ? xft::DataType::fp16 : xft::DataType::bf16,
-                     kv == "int8" ? xft::DataType::int8 : xft::DataType::fp16);
+    // the prompt of -i: token ids, or text through the tokenizer of -t
+    std::vector<int32_t> given;
+    if (!input.empty()) {
+      if (input.find_first_not_of("0123456789 \t") == std::string::npos) {
+        std::istringstream is(input);
+        for (int v; is >> v;) given.push_back(v);
+      } else if (tokenPath.empty()) {
+        std::fprintf(stderr, "-i takes token ids separated by spaces, or text with -t <tokenizer.model | tokenizer.json>\n");
+        return 2;
+      } else if (tokenPath.size() > 6 && tokenPath.compare(tokenPath.size() - 6, 6, ".model") == 0) {
+        given = xft::SentencePieceTokenizer(tokenPath).encode(input, /*addBos=*/true);
+      } else {
+        given = xft::BpeTokenizer(tokenPath).encode(input);
+      }
+    }
+    xft::AutoModel m(model, wdt, kv == "int8" ? xft::DataType::int8 : xft::DataType::fp16);
     const int vocab = m.getVocabSize();
     std::mt19937 rng(seed);
     std::vector<std::vector<int32_t>> prompts(nPrompts);
@@ -83,6 +106,10 @@ int main(int argc, char** argv) {
       const int len = minLen + (int)(rng() % (unsigned)std::max(1, maxLen - minLen + 1));
       p.resize(len);
       for (auto& t : p) t = 3 + (int)(rng() % (unsigned)std::max(1, vocab - 3));
+    }
+    if (!given.empty() && !prompts.empty()) {
+      for (int t : given) if (t < 0 || t >= vocab) throw std::runtime_error("-i: token id outside the vocabulary");
+      prompts[0] = given;
     }
     // pass 1: alone
     std::vector<std::vector<int>> alone;

@@ -51,8 +51,10 @@ def hostcheck(tmp_path_factory):
                         str(out / "libfake_nccl.so"), "-lrt", "-lpthread"], capture_output=True, text=True, timeout=900)
     assert b.returncode == 0, b.stderr[-4000:]
     # the example programs over the same stand-in (everything but the harness's own main)
+    tokenizers = [os.path.join(ROOT, "csrc", "core", f) for f in ("tokenizer.cc", "bpe_tokenizer.cc")]
     for prog in ("tp_check", "cb_check"):
         b = subprocess.run(["g++", "-O1"] + flags + [os.path.join(ROOT, "examples", "cpp", prog + ".cpp")] + [o for o, _ in jobs[1:]] +
+                           (tokenizers if prog == "cb_check" else []) +
                            ["-o", str(out / prog), "-ldl", "-lpthread"], capture_output=True, text=True, timeout=900)
         assert b.returncode == 0, b.stderr[-4000:]
     return exe
@@ -480,6 +482,14 @@ def test_example_programs_over_the_stand_in(hostcheck, tmp_path):
     r = subprocess.run([os.path.join(here, "cb_check"), "-m", d, "-n", "5", "-o", "6", "--stride", "2", "--min_len", "4", "--max_len", "70"],
                        env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, (r.stdout[-1500:], r.stderr[-1500:])
+    # a quantised weight type by name, and a prompt given as ids (the reference's -i)
+    r = subprocess.run([os.path.join(here, "cb_check"), "-m", d, "-d", "w8a8", "-n", "3", "-o", "4", "-i", "5 6 7 8 9 10 11", "--tolerate", "1"],
+                       env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, (r.stdout[-1500:], r.stderr[-1500:])
+    assert subprocess.run([os.path.join(here, "cb_check"), "-m", d, "-d", "int3"], env=env, capture_output=True, text=True,
+                          timeout=60).returncode == 2
+    assert subprocess.run([os.path.join(here, "cb_check"), "-m", d, "-i", "some text"], env=env, capture_output=True, text=True,
+                          timeout=60).returncode == 2                     # text needs -t
     for extra in (["-n", "2"], ["-n", "3", "-d", "int8", "--kv_cache_dtype", "int8"], ["-n", "4", "-s", "2"], ["-n", "2", "-s", "2"]):
         r = subprocess.run([os.path.join(here, "tp_check"), "-m", d, "-o", "3"] + extra, env=env, capture_output=True, text=True, timeout=900)
         assert r.returncode == 0, (extra, r.stdout[-1500:], r.stderr[-1500:])
