@@ -31,6 +31,8 @@ case "${1:-ut}" in
       XFT_FAKE_MODEL=2 xfastertransformer_b200/lib/xft_example -m "examples/model_config/$model" -d "$dt" \
         --kv_cache_dtype "$kv" -b "$bs" -l "$inp" -o "$outp" --no_stream | tail -1
     done
-    XFT_FAKE_MODEL=2 xfastertransformer_b200/lib/xft_tp_check -m examples/model_config/llama-2-7b -n 2 -o 2 ;;
+    XFT_FAKE_MODEL=2 xfastertransformer_b200/lib/xft_tp_check -m examples/model_config/llama-2-7b -n 2 -o 2
+    # ... and as two pipeline stages of two tensor-parallel ranks
+    XFT_FAKE_MODEL=2 xfastertransformer_b200/lib/xft_tp_check -m examples/model_config/llama-2-7b -n 4 -s 2 -o 2 ;;
   *) echo "usage: $0 {build|ut|model|cpp}"; exit 2 ;;
 esac
