@@ -718,8 +718,12 @@ def test_demo_takes_the_reference_command_line(tiny, tmp_path):
         r = subprocess.run([sys.executable, demo, "-m", tiny, "-d", "bf16", "--ids", "5 6 7 8"] + extra, env=env, capture_output=True,
                            text=True, timeout=600, cwd=str(tmp_path))
         assert r.returncode == 0 and "[4 tokens in" in r.stdout, r.stdout[-800:] + r.stderr[-1500:]
-    r = subprocess.run([sys.executable, demo, "-m", tiny, "--chat", "maybe"], env=env, capture_output=True, text=True, timeout=600)
-    assert r.returncode == 2 and "expected True or False" in r.stderr
+    sys.path.insert(0, os.path.dirname(demo))
+    import argparse
+    from demo import boolean_string
+    assert boolean_string("True") is True and boolean_string("false") is False and boolean_string(True) is True
+    with pytest.raises(argparse.ArgumentTypeError):
+        boolean_string("maybe")
 
 
 def test_text_modes_of_the_example_scripts(tmp_path):

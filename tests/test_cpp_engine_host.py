@@ -22,6 +22,7 @@ from xfastertransformer_b200.config import ModelConfig, RopeConfig
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CORE = ["engine.cc", "comm.cc", "runtime.cc", "ini.cc", "beam.cc", "env.cc", "arena.cc", "rope_tables.cc", "gptq.cc"]
+TOKENIZERS = ["tokenizer.cc", "bpe_tokenizer.cc"]            # only the cb_check program reads tokenizer files
 
 
 @pytest.fixture(scope="module")
@@ -33,7 +34,7 @@ def hostcheck(tmp_path_factory):
     flags = ["-g", "-std=c++17", "-fsanitize=address,undefined", "-fno-sanitize-recover=undefined", "-fno-omit-frame-pointer",
              "-I", os.path.join(ROOT, "csrc", "api"), "-I", os.path.join(ROOT, "csrc", "core"), "-I", "/usr/local/cuda/include"]
     srcs = [os.path.join(ROOT, "csrc", "tests", "engine_hostcheck.cc"), os.path.join(ROOT, "csrc", "tests", "mock_device.cc")] + \
-           [os.path.join(ROOT, "csrc", "core", f) for f in CORE]
+           [os.path.join(ROOT, "csrc", "core", f) for f in CORE + TOKENIZERS]
     # one compiler process per source, side by side; the stand-in's arithmetic loops want -O2, the engine compiles faster at -O1
     jobs = []
     for src in srcs:
@@ -43,7 +44,9 @@ def hostcheck(tmp_path_factory):
     for obj, job in jobs:
         log = job.communicate(timeout=900)[0]
         assert job.returncode == 0, log[-4000:]
-    b = subprocess.run(["g++", "-fsanitize=address,undefined"] + [o for o, _ in jobs] + ["-o", exe, "-ldl", "-lpthread"],
+    engine_objs = [o for o, _ in jobs[:len(jobs) - len(TOKENIZERS)]]
+    tokenizer_objs = [o for o, _ in jobs[len(jobs) - len(TOKENIZERS):]]
+    b = subprocess.run(["g++", "-fsanitize=address,undefined"] + engine_objs + ["-o", exe, "-ldl", "-lpthread"],
                        capture_output=True, text=True, timeout=900)
     assert b.returncode == 0, b.stderr[-4000:]
     # a stand-in NCCL for the runs with process ranks
@@ -51,10 +54,9 @@ def hostcheck(tmp_path_factory):
                         str(out / "libfake_nccl.so"), "-lrt", "-lpthread"], capture_output=True, text=True, timeout=900)
     assert b.returncode == 0, b.stderr[-4000:]
     # the example programs over the same stand-in (everything but the harness's own main)
-    tokenizers = [os.path.join(ROOT, "csrc", "core", f) for f in ("tokenizer.cc", "bpe_tokenizer.cc")]
     for prog in ("tp_check", "cb_check"):
-        b = subprocess.run(["g++", "-O1"] + flags + [os.path.join(ROOT, "examples", "cpp", prog + ".cpp")] + [o for o, _ in jobs[1:]] +
-                           (tokenizers if prog == "cb_check" else []) +
+        b = subprocess.run(["g++", "-O1"] + flags + [os.path.join(ROOT, "examples", "cpp", prog + ".cpp")] + engine_objs[1:] +
+                           (tokenizer_objs if prog == "cb_check" else []) +
                            ["-o", str(out / prog), "-ldl", "-lpthread"], capture_output=True, text=True, timeout=900)
         assert b.returncode == 0, b.stderr[-4000:]
     return exe
