@@ -361,7 +361,7 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_
   if (!ini.ok() || ini.sections().empty()) throw std::runtime_error("config.ini not found under " + path);
   type = ini.sections()[0];
   const FamilySpec* fam = familySpec(type);
-  if (!fam) throw std::runtime_error("the native C++ engine runs the dense families; use the Python API for [" + type + "]");
+  if (!fam) throw std::runtime_error("config.ini names a model type this engine does not know: [" + type + "]");
   spec = *fam;
   switch (dt) {
     case DataType::bf16: case DataType::fp16: case DataType::bf16_fp16: break;      // fp16 weights are kept as bf16
@@ -406,7 +406,7 @@ Engine::Engine(const std::string& path, DataType dt, DataType kvdt, std::shared_
     // Llama YaRN scales the table by 0.1 ln(factor) + 1 (yarn_scaled_rotary_embedding.cpp:26-84)
     if (rtype == "yarn") rs.tableScale = yarnMscale(rs.factor, 1.0);
   } else if (!rtype.empty() && rtype != "default") {
-    throw std::runtime_error("rope scaling '" + rtype + "' runs through the Python API");
+    throw std::runtime_error("rope scaling '" + rtype + "' is not supported (linear and yarn are)");
   } else if (type.rfind("chatglm", 0) == 0 && type != "chatglm") {
     // rope_ratio of the long-context GLM checkpoints multiplies the base
     ropeTheta *= (float)ini.getFloat(type, "rope_scaling_factor", ini.getFloat(type, "scaling_factor", 1.0));
