@@ -22,6 +22,22 @@ def _cpu(monkeypatch):
     monkeypatch.setenv("XFT_ENGINE", "CPU")
 
 
+def _run_script(path, argv, capsys):
+    """main() of an example script in this process (a new interpreter costs ten seconds of imports)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("script_" + os.path.basename(path).replace(".", "_"), path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    old = sys.argv
+    sys.argv = [path] + list(argv)
+    try:
+        capsys.readouterr()
+        mod.main()
+    finally:
+        sys.argv = old
+    return capsys.readouterr().out
+
+
 @pytest.fixture(scope="module")
 def tiny(tmp_path_factory):
     d = str(tmp_path_factory.mktemp("tiny"))
@@ -708,16 +724,14 @@ def test_benchmark_prompt_sources_of_the_reference(tiny, tmp_path):
     assert r.returncode == 0 and "input_tokens: 8" in r.stdout.replace("  ", " ").replace("  ", " "), r.stdout[-800:] + r.stderr[-800:]
 
 
-def test_demo_takes_the_reference_command_line(tiny, tmp_path):
+def test_demo_takes_the_reference_command_line(tiny, tmp_path, capsys):
     """examples/pytorch/demo.py with the reference's spelling of the boolean options (`--streaming False --chat False
     --do_sample True --padding False`, examples/pytorch/demo.py:61-74 there) and with bare flags."""
     demo = os.path.join(ROOT, "examples", "pytorch", "demo.py")
-    env = dict(os.environ, XFT_ENGINE="CPU", PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
     for extra in (["--streaming", "False", "--chat", "False", "--do_sample", "True", "--top_k", "3", "--padding", "False", "-o", "4"],
                   ["--streaming", "--output_len", "4"]):
-        r = subprocess.run([sys.executable, demo, "-m", tiny, "-d", "bf16", "--ids", "5 6 7 8"] + extra, env=env, capture_output=True,
-                           text=True, timeout=600, cwd=str(tmp_path))
-        assert r.returncode == 0 and "[4 tokens in" in r.stdout, r.stdout[-800:] + r.stderr[-1500:]
+        out = _run_script(demo, ["-m", tiny, "-d", "bf16", "--ids", "5 6 7 8"] + extra, capsys)
+        assert "[4 tokens in" in out, out[-800:]
     sys.path.insert(0, os.path.dirname(demo))
     import argparse
     from demo import boolean_string
@@ -726,7 +740,7 @@ def test_demo_takes_the_reference_command_line(tiny, tmp_path):
         boolean_string("maybe")
 
 
-def test_text_modes_of_the_example_scripts(tmp_path):
+def test_text_modes_of_the_example_scripts(tmp_path, capsys):
     """examples/pytorch/demo_offline_cb.py and prefix_sharing.py with the reference's text options (-t tokenizer, -i prompt
     file, -s sorted answers; --input / --prefix_len / --output_len): a small byte-level BPE tokenizer trained here stands
     in for a model's."""
@@ -744,33 +758,13 @@ def test_text_modes_of_the_example_scripts(tmp_path):
     PreTrainedTokenizerFast(tokenizer_object=tok, eos_token="<|endoftext|>").save_pretrained(tdir)
     d = str(tmp_path / "tiny")
     write_synthetic_checkpoint(d, preset("tiny-llama", vocab_size=512), seed=0, dtype="bf16", std=0.05)
-    env = dict(os.environ, XFT_ENGINE="CPU", PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
     prompts = tmp_path / "prompts.txt"
     prompts.write_text("The capital of France is\n\nWrite a haiku about the sea.\nList three prime numbers.\n")
-    r = subprocess.run([sys.executable, os.path.join(ROOT, "examples", "pytorch", "demo_offline_cb.py"), "-m", d, "-t", tdir, "-i",
-                        str(prompts), "-s", "--output_len", "4", "--kv_cache_dtype", "fp16"], env=env, capture_output=True, text=True,
-                       timeout=600)
-    assert r.returncode == 0, r.stdout[-800:] + r.stderr[-1500:]
-    shown = [l for l in r.stdout.splitlines() if l.startswith("[")]
+    out = _run_script(os.path.join(ROOT, "examples", "pytorch", "demo_offline_cb.py"),
+                      ["-m", d, "-t", tdir, "-i", str(prompts), "-s", "--output_len", "4", "--kv_cache_dtype", "fp16"], capsys)
+    shown = [l for l in out.splitlines() if l.startswith("[")]
     assert [l[:3] for l in shown] == ["[0]", "[1]", "[2]"] and "'The capital of France is'" in shown[0]      # -s: in prompt order
-    assert "3 requests" in r.stdout
-    r = subprocess.run([sys.executable, os.path.join(ROOT, "examples", "pytorch", "prefix_sharing.py"), "-m", d, "-t", tdir,
-                        "--prefix_len", "70", "--output_len", "4", "--streaming", "False", "--padding", "False"], env=env,
-                       capture_output=True, text=True, timeout=600)
-    assert r.returncode == 0 and "identical: True" in r.stdout, r.stdout[-800:] + r.stderr[-1500:]
-
-
-def test_launcher_defaults_from_the_command_line(tiny):
-    """serving/server.py: the reference fixes the generation settings on the launcher's command line (--output_len,
-    --num_beams, --do_sample, ...); here they are the defaults of requests that do not carry the field."""
-    import xfastertransformer_b200 as xft
-    from serving.server import Servicer
-    model = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
-    sv = Servicer(model, dict(output_len=3, num_beams=2))
-    kw = sv._kwargs({"Ids": [5, 6, 7, 8, 9, 10], "batch_size": 2})
-    assert kw["max_length"] == 3 + 3 and kw["num_beams"] == 2 and kw["top_k"] == 50
-    kw = sv._kwargs({"Ids": [5, 6, 7], "max_length": 9, "num_beams": 1})
-    assert kw["max_length"] == 9 and kw["num_beams"] == 1
-    out = sv.predict({"Ids": [5, 6, 7, 8], "batch_size": 1, "num_beams": 1})
-    assert out["seq_len"] == 4 + 3
-    assert Servicer(model)._kwargs({"Ids": [1, 2]})["max_length"] == 128
+    assert "3 requests" in out
+    out = _run_script(os.path.join(ROOT, "examples", "pytorch", "prefix_sharing.py"),
+                      ["-m", d, "-t", tdir, "--prefix_len", "70", "--output_len", "4", "--streaming", "False", "--padding", "False"], capsys)
+    assert "identical: True" in out, out[-800:]
