@@ -768,3 +768,19 @@ def test_text_modes_of_the_example_scripts(tmp_path, capsys):
     out = _run_script(os.path.join(ROOT, "examples", "pytorch", "prefix_sharing.py"),
                       ["-m", d, "-t", tdir, "--prefix_len", "70", "--output_len", "4", "--streaming", "False", "--padding", "False"], capsys)
     assert "identical: True" in out, out[-800:]
+
+
+def test_launcher_defaults_from_the_command_line(tiny):
+    """serving/server.py: the reference fixes the generation settings on the launcher's command line (--output_len,
+    --num_beams, --do_sample, ...); here they are the defaults of requests that do not carry the field."""
+    import xfastertransformer_b200 as xft
+    from serving.server import Servicer
+    model = xft.AutoModel.from_pretrained(tiny, dtype="bf16")
+    sv = Servicer(model, dict(output_len=3, num_beams=2))
+    kw = sv._kwargs({"Ids": [5, 6, 7, 8, 9, 10], "batch_size": 2})
+    assert kw["max_length"] == 3 + 3 and kw["num_beams"] == 2 and kw["top_k"] == 50
+    kw = sv._kwargs({"Ids": [5, 6, 7], "max_length": 9, "num_beams": 1})
+    assert kw["max_length"] == 9 and kw["num_beams"] == 1
+    out = sv.predict({"Ids": [5, 6, 7, 8], "batch_size": 1, "num_beams": 1})
+    assert out["seq_len"] == 4 + 3
+    assert Servicer(model)._kwargs({"Ids": [1, 2]})["max_length"] == 128
