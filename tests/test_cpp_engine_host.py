@@ -663,3 +663,13 @@ def test_engine_token_budget_groups(hostcheck, fam, ranks, stages, tmp_path):
                XFT_PIPELINE_STAGE=str(stages))
     r = subprocess.run([hostcheck, cfg, "bf16", "fp16", str(ranks)], env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "hostcheck ok" in r.stdout, (r.stdout[-500:], r.stderr[-3000:])
+
+
+@pytest.mark.parametrize("dtype,ranks", [("bf16", 5), ("w8a8", 8), ("nf4", 3)])
+def test_engine_host_side_odd_sizes_and_rank_counts(hostcheck, dtype, ranks, tmp_path):
+    """Sizes that do not divide: 8 query heads over 2 KV heads, an FFN of 1408 (22 x 64), an odd vocabulary (4003), on 3, 5
+    and 8 ranks — ranks share KV heads, the FFN and vocabulary slices differ in width."""
+    cfg = ModelConfig(**dict(_BASE, model_type="llama", hidden_size=512, head_num=8, kv_head_num=2, inter_size=1408, vocab_size=4003))
+    d = str(tmp_path / "odd")
+    cfg.to_ini(d)
+    _run(hostcheck, d, dtype, "int8", ranks)
