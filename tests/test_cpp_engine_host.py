@@ -673,3 +673,15 @@ def test_engine_host_side_odd_sizes_and_rank_counts(hostcheck, dtype, ranks, tmp
     d = str(tmp_path / "odd")
     cfg.to_ini(d)
     _run(hostcheck, d, dtype, "int8", ranks)
+
+
+def test_engine_logits_odd_sizes_on_many_ranks(hostcheck, tmp_path, monkeypatch):
+    """The logits of a model whose sizes do not divide (8 query heads over 2 KV heads, FFN 1408, vocabulary 1003) on 5 and
+    8 tensor-parallel ranks against the fp32 PyTorch path."""
+    d = _synthetic_dir(tmp_path, "llama", dict(hidden_size=512, head_num=8, kv_head_num=2, inter_size=1408, vocab_size=1003))
+    prompt = torch.randint(5, 990, (2, 20), generator=torch.Generator().manual_seed(4))
+    for ranks in (5, 8):
+        got, tokens = _engine_logits(hostcheck, d, ranks, prompt, 2)
+        want = _oracle_logits(d, prompt, tokens, monkeypatch)
+        top = max(1.0, want.abs().max().item())
+        assert (got - want).abs().max().item() < 0.04 * top, (ranks, (got - want).abs().max().item(), top)
