@@ -8,7 +8,9 @@
 #include <sys/mman.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <atomic>
+#include <chrono>
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
@@ -26,14 +28,26 @@ struct Shared {
 struct Comm { int rank, world; Shared* sh; char* slots; size_t bytes; char name[128]; };
 struct Id { char bytes[128]; };
 
+// Waits give up after XFT_DIST_TIMEOUT_S seconds (120 when unset): a test on a loaded machine must not fail because a
+// sibling process was slow, yet a lost rank must not hang it for ever.
+struct Deadline {
+  std::chrono::steady_clock::time_point end;
+  Deadline() {
+    const char* v = std::getenv("XFT_DIST_TIMEOUT_S");
+    end = std::chrono::steady_clock::now() + std::chrono::seconds(v && *v ? std::max(1, std::atoi(v)) : 120);
+  }
+  bool passed(long spin) const { return (spin & 4095) == 4095 && std::chrono::steady_clock::now() > end; }
+};
+
 void barrier(Comm* c) {
   const int gen = c->sh->generation.load();
   if (c->sh->arrived.fetch_add(1) + 1 == c->world) {
     c->sh->arrived.store(0);
     c->sh->generation.fetch_add(1);
   } else {
+    const Deadline limit;
     for (long spin = 0; c->sh->generation.load() == gen; ++spin) {
-      if (spin > 200000000L) { std::fprintf(stderr, "fake nccl: barrier timed out\n"); std::_Exit(3); }
+      if (limit.passed(spin)) { std::fprintf(stderr, "fake nccl: barrier timed out\n"); std::_Exit(3); }
       if ((spin & 1023) == 1023) usleep(50);
     }
   }
@@ -122,8 +136,9 @@ int ncclSend(const void* send, size_t count, int dt, int peer, void* comm, void*
   std::atomic<int>& flag = c->sh->mail[c->rank * 8 + peer];
   std::memcpy(c->slots + (size_t)c->rank * kSlot + kSlot / 2, send, bytes);
   flag.store(1);
+  const Deadline limit;
   for (long spin = 0; flag.load() != 0; ++spin) {
-    if (spin > 200000000L) { std::fprintf(stderr, "fake nccl: send timed out\n"); std::_Exit(3); }
+    if (limit.passed(spin)) { std::fprintf(stderr, "fake nccl: send timed out\n"); std::_Exit(3); }
     if ((spin & 1023) == 1023) usleep(50);
   }
   return 0;
@@ -133,8 +148,9 @@ int ncclRecv(void* recv, size_t count, int dt, int peer, void* comm, void*) {
   const size_t bytes = count * elemSize(dt);
   if (bytes > kSlot / 2 || peer < 0 || peer >= c->world || peer == c->rank) return 4;
   std::atomic<int>& flag = c->sh->mail[peer * 8 + c->rank];
+  const Deadline limit;
   for (long spin = 0; flag.load() != 1; ++spin) {
-    if (spin > 200000000L) { std::fprintf(stderr, "fake nccl: receive timed out\n"); std::_Exit(3); }
+    if (limit.passed(spin)) { std::fprintf(stderr, "fake nccl: receive timed out\n"); std::_Exit(3); }
     if ((spin & 1023) == 1023) usleep(50);
   }
   std::memcpy(recv, c->slots + (size_t)peer * kSlot + kSlot / 2, bytes);

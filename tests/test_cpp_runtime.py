@@ -751,7 +751,7 @@ def test_process_rank_communicator_with_a_stand_in_nccl(tmp_path):
     assert lone.returncode == 1 and "did not arrive" in lone.stdout
     # a collective that never finishes (the stream stays busy: what a lost rank looks like): the wait gives up after
     # XFT_DIST_TIMEOUT_S, the communicator is aborted, the rank reports instead of waiting for ever ...
-    for extra, words in ((dict(XFT_DIST_TIMEOUT_S="1"), "did not finish within 1 s"),
+    for extra, words in ((dict(XFT_DIST_TIMEOUT_S="3"), "did not finish within 3 s"),
                          # ... and at once when NCCL itself reports an asynchronous error
                          (dict(XFT_DIST_TIMEOUT_S="60", XFT_FAKE_NCCL_ASYNC_ERROR="1"), "asynchronous error")):
         idf = str(tmp_path / "id_lost")
