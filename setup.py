@@ -47,7 +47,7 @@ setup(
     description="Blackwell-native (sm_100a) LLM inference engine with the API of xFasterTransformer",
     packages=find_packages(include=["xfastertransformer_b200", "xfastertransformer_b200.*", "xfastertransformer",
                                     "xfastertransformer.*"]),
-    package_data={"xfastertransformer_b200": ["lib/*.so", "lib/xft_example", "lib/xft_cb_check"]},
+    package_data={"xfastertransformer_b200": ["lib/*.so", "lib/xft_example", "lib/xft_cb_check", "lib/xft_tp_check"]},
     python_requires=">=3.10",
     install_requires=["torch", "numpy"],
     extras_require={"convert": ["transformers", "safetensors", "sentencepiece"], "serving": ["grpcio", "fastapi", "uvicorn"]},
