@@ -685,3 +685,32 @@ def test_engine_logits_odd_sizes_on_many_ranks(hostcheck, tmp_path, monkeypatch)
         want = _oracle_logits(d, prompt, tokens, monkeypatch)
         top = max(1.0, want.abs().max().item())
         assert (got - want).abs().max().item() < 0.04 * top, (ranks, (got - want).abs().max().item(), top)
+
+
+def test_engine_thread_ranks_under_thread_sanitizer(tmp_path):
+    """Race detection: the whole engine as thread ranks under ThreadSanitizer — the ranks share process-wide state (the
+    device arena, the flags, cached tables), which is safe only because one rank runs at a time.  Tensor-parallel ranks
+    with int8 KV, pipeline stages with micro-batches, expert-parallel ranks: no report."""
+    if shutil.which("g++") is None:
+        pytest.skip("no g++")
+    flags = ["-O1", "-g", "-std=c++17", "-fsanitize=thread", "-I", os.path.join(ROOT, "csrc", "api"), "-I", os.path.join(ROOT, "csrc", "core"),
+             "-I", "/usr/local/cuda/include"]
+    srcs = [os.path.join(ROOT, "csrc", "tests", "engine_hostcheck.cc"), os.path.join(ROOT, "csrc", "tests", "mock_device.cc")] + \
+           [os.path.join(ROOT, "csrc", "core", f) for f in CORE]
+    jobs = []
+    for src in srcs:
+        obj = str(tmp_path / (os.path.basename(src) + ".o"))
+        jobs.append((obj, subprocess.Popen(["g++"] + flags + ["-c", src, "-o", obj], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    for obj, job in jobs:
+        log = job.communicate(timeout=900)[0]
+        assert job.returncode == 0, log[-4000:]
+    exe = str(tmp_path / "hostcheck_tsan")
+    b = subprocess.run(["g++", "-fsanitize=thread"] + [o for o, _ in jobs] + ["-o", exe, "-ldl", "-lpthread"], capture_output=True, text=True,
+                       timeout=900)
+    assert b.returncode == 0, b.stderr[-4000:]
+    for fam, dtype, kv, ranks, extra in (("llama", "bf16", "int8", 4, {}), ("llama", "w8a8", "fp16", 4, dict(XFT_PIPELINE_STAGE="2", XFT_MAX_REQUEST_NUM="2")),
+                                         ("qwen3_moe", "bf16", "fp16", 4, {})):
+        d = _config_dir(tmp_path, fam)
+        env = dict(os.environ, XFT_FAKE_MODEL="2", **extra)
+        r = subprocess.run([exe, d, dtype, kv, str(ranks)], env=env, capture_output=True, text=True, timeout=900)
+        assert r.returncode == 0 and "hostcheck ok" in r.stdout and "ThreadSanitizer" not in r.stderr, (fam, r.stdout[-300:], r.stderr[-3000:])
